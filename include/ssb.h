@@ -1,0 +1,274 @@
+/*
+ * ssb.h -- C ABI of libssb_b200: the per-iteration training hot path of a 3D
+ * Gaussian splatting trainer (projection, tile keys, 64-bit radix sort, tile
+ * ranges, tile rasteriser forward/backward, fused L1+SSIM loss, Adam), written
+ * for NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *  - Every pointer named d_* or documented "device" is a CUDA device pointer
+ *    on the current device.  The library never allocates device memory behind
+ *    the caller's back except inside an SsbStep object (ssb_step_create), and
+ *    never frees caller memory.
+ *  - Every function returns 0 (SSB_OK) or a negative SsbStatus.  Nothing here
+ *    calls exit() or throws across the boundary; ssb_last_error_string() gives
+ *    the text of the calling thread's last failure.
+ *  - `stream` is a cudaStream_t passed as void*; NULL is the legacy default
+ *    stream, which is where the reference launches everything
+ *    (src/core/Common.cuh:207-209).
+ *  - Layouts of splat parameters, gradients and optimiser moments are the
+ *    reference's pool-slot layouts (src/primitives/PrimitiveBase3DGS.cuh:87-117):
+ *    six arrays, each array-of-structs per splat, fp32.
+ *  - Projected ("screen") splats travel between the kernels of this library as
+ *    one 48-byte record per (view, splat) pair, SsbScreenRec.  ssb_screen_unpack
+ *    / ssb_screen_pack convert to and from the reference's five ScreenBuffer
+ *    arrays (src/primitives/PrimitiveBase3DGS.cuh:187-211).
+ *
+ * Each entry point names the reference interface it stands in for.
+ */
+#ifndef SSB_H_
+#define SSB_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum SsbStatus {
+    SSB_OK = 0,
+    SSB_ERR_INVALID_ARGUMENT = -1, /* reference: throw std::runtime_error, src/core/Common.cuh:133-146 */
+    SSB_ERR_CUDA = -2,             /* reference: CHECK_DEVICE_ERROR prints and exits, src/core/Common.cuh:195-203 */
+    SSB_ERR_CAPACITY = -3,         /* an output buffer sized by the caller is too small */
+    SSB_ERR_OUT_OF_MEMORY = -4,    /* reference: throw_out_of_memory, src/backend/api/BackendRuntime.h:114-143 */
+    SSB_ERR_UNSUPPORTED = -5
+} SsbStatus;
+
+enum { SSB_CAMERA_PINHOLE = 0, SSB_CAMERA_FISHEYE = 1, SSB_CAMERA_EQUISOLID = 2, SSB_CAMERA_EQUIRECT = 3 }; /* src/core/Common.cuh:96-101 */
+
+enum { SSB_NUM_SH = 15, SSB_TILE = 16, SSB_SCREEN_REC_FLOATS = 12 };
+
+/* Six per-splat arrays: parameters, their gradients, or one Adam moment.
+ * Reference: _BasePrimitive3DGS::WorldBuffer, src/primitives/PrimitiveBase3DGS.cuh:87-117. */
+typedef struct SsbSplats {
+    float* means;        /* [n][3] */
+    float* quats;        /* [n][4]  w,x,y,z, not necessarily unit */
+    float* scales;       /* [n][3]  log */
+    float* opacities;    /* [n]     logit */
+    float* features_dc;  /* [n][3] */
+    float* features_sh;  /* [n][15][3] band-major, rgb interleaved; NULL when the SH values are quantised */
+} SsbSplats;
+
+/* Quantised SH value storage, QuantizedTensor<BITS,256> (src/core/Tensor.h:1313-1404)
+ * as read by the projection kernels (src/shaders/harmonics.slang:115-140). */
+typedef struct SsbShQuant {
+    void* packed;          /* uint8 [n*45] or uint16 [n*45]; NULL = fp32 SH */
+    float* bounds;         /* float2 (min,max) per block of `bounds_stride` cells */
+    int32_t bits;          /* 8 or 16 (32 / 0 = not quantised) */
+    int32_t reserved;
+    int64_t bounds_stride; /* cells per bound; 256 for the per-cell-block layout */
+} SsbShQuant;
+
+/* One batch of cameras sharing size and model.
+ * Reference: the (viewmats, intrins, camera_model, width, height) arguments of
+ * projection_3dgs_forward, src/kernels/projection/ProjectionFwd.cuh:14-78. */
+typedef struct SsbCameras {
+    const float* d_viewmats; /* device [count][16] row-major world-to-camera */
+    const float* d_intrins;  /* device [count][4] fx, fy, cx, cy */
+    int32_t count;
+    int32_t width, height;
+    int32_t model;           /* SSB_CAMERA_*; lens-distortion tier "none" only */
+    int32_t antialiased;     /* 0 = 3dgs, 1 = mip-splatting blur and opacity compensation */
+} SsbCameras;
+
+/* 48-byte projected splat.  a = {x, y, hx, hy}: centre in pixels and the half
+ * extents of the alpha >= 1/255 footprint; b = {conic a, b, c, opacity};
+ * c = {r, g, b, ray depth}. */
+typedef struct SsbScreenRec { float a[4], b[4], c[4]; } SsbScreenRec;
+
+const char* ssb_last_error_string(void);
+/* "major.minor" of the ABI and the compute capability the kernels were built for. */
+const char* ssb_version_string(void);
+
+/* ---- projection --------------------------------------------------------- */
+
+/* Replaces projection_3dgs_forward (src/kernels/projection/ProjectionFwd.cu:104-139,
+ * kernel src/kernels/projection/ProjectionFwd_kernel.cuh:15-111).
+ * d_aabb [C*n][4] xyxy pixels (all zero = culled), d_depths [C*n] sorting depth,
+ * d_radii [n] running max over views (caller zeroes once per step; may be NULL),
+ * d_screen [C*n] records (only written where the pair is kept). */
+int ssb_project_fwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n,
+                    const SsbCameras* cams,
+                    float* d_aabb, float* d_depths, float* d_radii, SsbScreenRec* d_screen,
+                    void* stream);
+
+/* Replaces projection_3dgs_backward (src/kernels/projection/ProjectionBwd.cu:134,
+ * kernel src/kernels/projection/ProjectionBwd_kernel.cuh:16-130): vjp of the
+ * projection and of SH-to-colour for every kept pair, summed over the views of
+ * `cams`.  d_v_screen [C*n] holds gradient records laid out like SsbScreenRec
+ * (a = {v_x, v_y, 0, 0}, b = {v_conic a,b,c, v_opacity}, c = {v_r, v_g, v_b, v_depth}).
+ * accumulate != 0 adds to `grads`; 0 overwrites them (so no separate zeroing
+ * pass is needed before the first view of a step). */
+int ssb_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n,
+                    const SsbCameras* cams, const float* d_aabb,
+                    const SsbScreenRec* d_v_screen,
+                    const SsbSplats* grads, int accumulate, void* stream);
+
+/* Record <-> reference ScreenBuffer arrays (xy [m][2], depth [m], conic [m][3],
+ * opac [m], rgb [m][3]); src/primitives/PrimitiveBase3DGS.cuh:187-211. */
+int ssb_screen_unpack(const SsbScreenRec* d_screen, int64_t m,
+                      float* d_xy, float* d_depth, float* d_conic, float* d_opac, float* d_rgb, void* stream);
+int ssb_screen_pack(const float* d_xy, const float* d_depth, const float* d_conic, const float* d_opac,
+                    const float* d_rgb, int64_t m, SsbScreenRec* d_screen, void* stream);
+
+/* ---- tile intersection: keys, sort, ranges ------------------------------ */
+
+/* Bytes of scratch ssb_tile_keys needs for `total` = C*n pairs. */
+int64_t ssb_tile_keys_workspace_bytes(int64_t total);
+
+/* Replaces passes 1-2 of do_intersect_tile_generic, ellipse mode, no live-tile
+ * map (src/kernels/tile/IntersectTile.cu:372-479): per-pair tile counts, their
+ * inclusive sum, then keys (tile_id << 32 | depth bits) and flatten ids.
+ * d_tiles_per_splat / d_cum_tiles [total] (int32) may be NULL if the caller does
+ * not want them.  d_n_isects (device int64) receives the pair count M; when
+ * h_n_isects != NULL the call also synchronises the stream and stores M there.
+ * Keys beyond `capacity` are not written and the call (when it synchronises) or
+ * ssb_sort_pairs_u64 reports SSB_ERR_CAPACITY. */
+int ssb_tile_keys(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
+                  int64_t total, int64_t n_per_image, int32_t width, int32_t height,
+                  void* d_workspace, int64_t workspace_bytes,
+                  int32_t* d_tiles_per_splat, int32_t* d_cum_tiles,
+                  int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                  int64_t* d_n_isects, int64_t* h_n_isects, void* stream);
+
+int64_t ssb_sort_workspace_bytes(int64_t capacity);
+
+/* Replaces backend::sort_pairs<int64,int32> / cub::DeviceRadixSort::SortPairs
+ * (src/backend/common/SortScan.h:53-56, src/kernels/tile/IntersectTile.cu:487-497):
+ * stable ascending sort on key bits [begin_bit, end_bit).  The element count is
+ * read on the device from *d_n (clamped to capacity).  *selector (host) tells
+ * which buffer pair holds the result: 0 = (keys_a, vals_a), 1 = (keys_b, vals_b). */
+int ssb_sort_pairs_u64(int64_t* d_keys_a, int32_t* d_vals_a, int64_t* d_keys_b, int32_t* d_vals_b,
+                       const int64_t* d_n, int64_t capacity, int32_t begin_bit, int32_t end_bit,
+                       void* d_workspace, int64_t workspace_bytes, int32_t* selector, void* stream);
+
+/* Number of key bits the tile id occupies: smallest b with 2^b > n_tiles
+ * (src/kernels/tile/IntersectTile.cu:489-490). */
+int32_t ssb_tile_n_bits(int64_t n_tiles);
+
+/* Replaces intersect_offset_kernel (src/kernels/tile/IntersectTile.cu:271-307).
+ * d_offsets [n_tiles_total] int32: first sorted index of each tile; tiles after
+ * the last key get M; all zero when M == 0. */
+int ssb_tile_ranges(const int64_t* d_sorted_ids, const int64_t* d_n, int64_t capacity,
+                    int64_t n_tiles_total, int32_t* d_offsets, void* stream);
+
+/* ---- rasteriser --------------------------------------------------------- */
+
+/* Replaces rasterize_to_pixels_3dgs_fwd (src/kernels/raster/RasterizationFwd.cu:147-185,
+ * kernel src/kernels/raster/RasterizationEval3DFwd_kernel.cuh:48-313, 2D variant).
+ * Outputs: d_rgb [I][H][W][3], d_depth [I][H][W], d_T [I][H][W], d_last_ids [I][H][W]. */
+int ssb_raster_fwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids,
+                   const int64_t* d_n_isects, int32_t n_images, int32_t width, int32_t height,
+                   float* d_rgb, float* d_depth, float* d_T, int32_t* d_last_ids, void* stream);
+
+/* Replaces rasterize_to_pixels_3dgs_bwd (src/kernels/raster/RasterizationBwd.cu:253-291,
+ * kernel src/kernels/raster/RasterizationEval3DBwd_kernel.cuh:48-636, 2D variant).
+ * d_v_depth and d_v_T may be NULL (treated as zero).  Gradients are ADDED into
+ * d_v_screen [pairs] (layout as in ssb_project_bwd); the caller zeroes it. */
+int ssb_raster_bwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids,
+                   const int64_t* d_n_isects, int32_t n_images, int32_t width, int32_t height,
+                   const float* d_render_depth, const float* d_T, const int32_t* d_last_ids,
+                   const float* d_v_rgb, const float* d_v_depth, const float* d_v_T,
+                   SsbScreenRec* d_v_screen, void* stream);
+
+/* ---- loss --------------------------------------------------------------- */
+
+/* Replaces compute_multi_scale_per_pixel_losses at one scale with only the RGB
+ * L1 weight set (src/kernels/loss/PerPixelLoss.cu:948-1402) followed by
+ * fused_ssim_inplace_async (src/kernels/loss/FusedSSIM.cu:1211-1234, kernel :639-1022):
+ * loss = w_l1 * mean|render - gt| + w_ssim * (1 - SSIM).  Writes d(loss)/d(render)
+ * to d_v_render [B][H][W][3] and {L1, SSIM, loss} sums to d_losses[3] (device,
+ * fp32; caller reads them whenever it likes -- the reference reads its scalars
+ * one step late, src/kernels/loss/PerPixelLoss.cu:1374-1400). */
+int ssb_loss_l1_ssim_fwdbwd(const float* d_render, const float* d_gt, int32_t n_images, int32_t height, int32_t width,
+                            float w_l1, float w_ssim, float* d_v_render, float* d_losses, void* stream);
+
+/* ---- optimiser ---------------------------------------------------------- */
+
+typedef struct SsbAdamConfig {
+    float lr_means, lr_quats, lr_scales, lr_opacities, lr_features_dc, lr_features_sh;
+    float sh_reg_weight;   /* l2_reg of fused_adam_step for DC (offset 0.5/0.2820948) and SH (offset 0) */
+    float grad_scale;      /* 1 / views accumulated, src/engine/EngineTrainStep.cpp:419-427 */
+    int32_t step;          /* bias-correction exponent t >= 1 (the reference passes step + 1) */
+    int32_t zero_grad;     /* also clear the gradients, as zero_grad_in_optim does */
+} SsbAdamConfig;
+
+/* Replaces fused_optim_3dgs_geometry (src/kernels/optim/FusedGeometryOptim.cu:384-470,
+ * kernel :83-380; regulariser weights zero, fp32 state, scalar step) and the two
+ * fused_adam_step launches for features_dc and features_sh
+ * (src/kernels/optim/FusedAppearanceOptim.cu:59-92) over the splat range
+ * [first, first + count).  `m1`/`m2` are the first/second moments.
+ * If params->features_sh is NULL the SH part is skipped (see ssb_adam_step_sh_quantized). */
+int ssb_adam_step(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
+                  int64_t first, int64_t count, const SsbAdamConfig* cfg, void* stream);
+
+/* Replaces fused_adam_step_quantized_value (src/kernels/optim/FusedAppearanceOptim.cu:421-479,
+ * kernel :291-418): Adam on SH coefficients whose values live in a QuantizedTensor
+ * <value_bits,256> and whose state lives in a QuantizedAdamState<8,256>
+ * (src/core/Tensor.h:978-1136).  `numel` cells starting at cell `first_cell`,
+ * which must be a multiple of 256.  d_grad is fp32 [cells]. */
+int ssb_adam_step_sh_quantized(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds,
+                               void* d_value_packed, float* d_value_bounds, int32_t value_bits,
+                               int64_t first_cell, int64_t numel, int64_t numel_total,
+                               const SsbAdamConfig* cfg, void* stream);
+
+/* QuantizedTensor<BITS,256>::encode_v / decode_v over whole buffers
+ * (src/core/Tensor.h:1366-1393); bounds = float2 per 256 cells. */
+int ssb_quant_encode(const float* d_values, int64_t numel, int32_t bits, void* d_packed, float* d_bounds, void* stream);
+int ssb_quant_decode(const void* d_packed, const float* d_bounds, int64_t numel, int32_t bits, float* d_values, void* stream);
+
+/* ---- one training iteration --------------------------------------------- */
+
+/* Owns every intermediate buffer of an iteration (the reference keeps them in
+ * its process-global DevicePool, src/core/Tensor.h:151-351) and runs, per view,
+ * projection -> keys -> sort -> ranges -> raster -> loss -> raster bwd ->
+ * projection bwd, accumulating gradients exactly like the reference's
+ * one-camera-per-sub-batch loop (src/engine/EngineTrainStep.cpp:287-437). */
+typedef struct SsbStep SsbStep;
+
+typedef struct SsbStepConfig {
+    int64_t n_splats;
+    int32_t width, height;
+    int32_t camera_model;
+    int32_t antialiased;
+    int64_t isect_capacity;  /* max (splat, tile) pairs per view; 0 = 12 * n_splats */
+    float w_l1, w_ssim;      /* 0.8 / 0.2 in the benchmark configuration */
+} SsbStepConfig;
+
+int ssb_step_create(const SsbStepConfig* cfg, SsbStep** out);
+void ssb_step_destroy(SsbStep* step);
+int64_t ssb_step_device_bytes(const SsbStep* step);
+
+/* Forward + loss + backward of `n_views` views (device camera arrays and device
+ * targets d_gt [n_views][H][W][3]); gradients are overwritten by the first view
+ * when `accumulate` == 0 and added to otherwise.  Loss sums accumulate into
+ * d_losses[3] (device; caller zeroes). */
+int ssb_step_views(SsbStep* step, const SsbSplats* params, const SsbShQuant* shq,
+                   const float* d_viewmats, const float* d_intrins, const float* d_gt, int32_t n_views,
+                   const SsbSplats* grads, int accumulate, float* d_losses, void* stream);
+
+/* Pair count M of the last view processed (host copy taken after that view's
+ * kernels finished; synchronises the stream). */
+int ssb_step_last_isects(SsbStep* step, int64_t* h_n_isects, void* stream);
+
+/* Device buffers of the last view, for inspection by tests: any pointer may be
+ * NULL.  Valid until the next ssb_step_views / ssb_step_destroy. */
+int ssb_step_peek(SsbStep* step, const float** d_rgb, const float** d_depth, const float** d_T,
+                  const int32_t** d_last_ids, const SsbScreenRec** d_screen, const float** d_aabb);
+
+/* Number of kernel launches the library has issued from this process so far. */
+int64_t ssb_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SSB_H_ */

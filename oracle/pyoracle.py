@@ -1,0 +1,211 @@
+"""numpy/ctypes front end of the CPU oracle (oracle/ssb_oracle.cpp).
+
+TEST INFRASTRUCTURE: imported only by tests/, __graft_entry__.smoke() and the
+CPU-baseline legs of bench.py.  The shipped library never loads it.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "libssb_oracle.so")
+_lib = None
+
+f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
+
+
+def build():
+    subprocess.check_call(["make", "-C", _HERE, "-s"])
+
+
+def load():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_SO):
+            build()
+        _lib = C.CDLL(_SO)
+        _lib.oracle_tile_count.restype = C.c_int64
+        _lib.oracle_num_threads.restype = C.c_int
+        _lib.oracle_tile_n_bits.restype = C.c_int
+        _lib.oracle_det_logf.restype = C.c_float
+        _lib.oracle_det_logf.argtypes = [C.c_float]
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _f(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+
+
+def num_threads():
+    return load().oracle_num_threads()
+
+
+def set_num_threads(n):
+    load().oracle_set_num_threads(C.c_int(n))
+
+
+def tile_grid(W, H):
+    return (W + 15) // 16, (H + 15) // 16
+
+
+def _sh_args(splats, shq):
+    if shq is None:
+        return _p(splats["features_sh"]), None, None, C.c_int(32), C.c_int64(256)
+    return None, _p(shq["packed"]), _p(shq["bounds"]), C.c_int(shq["bits"]), C.c_int64(shq.get("bounds_stride", 256))
+
+
+def project_fwd(splats, viewmats, intrins, W, H, model=0, antialiased=0, shq=None, with_radii=True):
+    lib = load()
+    s = {k: _f(v) for k, v in splats.items() if v is not None}
+    N, Cn = s["means"].shape[0], viewmats.shape[0]
+    viewmats, intrins = _f(viewmats), _f(intrins)
+    out = dict(aabb=np.zeros((Cn * N, 4), np.float32), depths=np.zeros(Cn * N, np.float32),
+               radii=np.zeros(N, np.float32) if with_radii else None,
+               xy=np.zeros((Cn * N, 2), np.float32), depth=np.zeros(Cn * N, np.float32),
+               conic=np.zeros((Cn * N, 3), np.float32), opac=np.zeros(Cn * N, np.float32), rgb=np.zeros((Cn * N, 3), np.float32))
+    sh = _sh_args(s, shq)
+    lib.oracle_project_fwd(C.c_int64(N), C.c_int(Cn), C.c_int(W), C.c_int(H), C.c_int(model), C.c_int(antialiased),
+                           _p(s["means"]), _p(s["quats"]), _p(s["scales"]), _p(s["opacities"]), _p(s["features_dc"]), *sh,
+                           _p(viewmats), _p(intrins), _p(out["aabb"]), _p(out["depths"]), _p(out["radii"]),
+                           _p(out["xy"]), _p(out["depth"]), _p(out["conic"]), _p(out["opac"]), _p(out["rgb"]))
+    return out
+
+
+def project_bwd(splats, viewmats, intrins, W, H, aabb, v, model=0, antialiased=0, shq=None):
+    """v: dict of v_xy, v_depth, v_conic, v_opac, v_rgb. Returns dict of world gradients."""
+    lib = load()
+    s = {k: _f(val) for k, val in splats.items() if val is not None}
+    N, Cn = s["means"].shape[0], viewmats.shape[0]
+    viewmats, intrins = _f(viewmats), _f(intrins)
+    g = dict(means=np.zeros((N, 3), np.float32), quats=np.zeros((N, 4), np.float32), scales=np.zeros((N, 3), np.float32),
+             opacities=np.zeros(N, np.float32), features_dc=np.zeros((N, 3), np.float32), features_sh=np.zeros((N, 15, 3), np.float32))
+    vv = {k: _f(x) for k, x in v.items()}
+    sh = _sh_args(s, shq)
+    lib.oracle_project_bwd(C.c_int64(N), C.c_int(Cn), C.c_int(W), C.c_int(H), C.c_int(model), C.c_int(antialiased),
+                           _p(s["means"]), _p(s["quats"]), _p(s["scales"]), _p(s["opacities"]), _p(s["features_dc"]), *sh,
+                           _p(viewmats), _p(intrins), _p(_f(aabb)),
+                           _p(vv["v_xy"]), _p(vv["v_depth"]), _p(vv["v_conic"]), _p(vv["v_opac"]), _p(vv["v_rgb"]),
+                           _p(g["means"]), _p(g["quats"]), _p(g["scales"]), _p(g["opacities"]), _p(g["features_dc"]), _p(g["features_sh"]))
+    return g
+
+
+def tile_keys(proj, N, W, H):
+    """proj: output of project_fwd. Returns counts, cum, keys, flatten ids (unsorted)."""
+    lib = load()
+    total = proj["depths"].shape[0]
+    counts = np.zeros(total, np.int64)
+    cum = np.zeros(total, np.int64)
+    M = lib.oracle_tile_count(C.c_int64(total), C.c_int(W), C.c_int(H), _p(proj["aabb"]), _p(proj["xy"]), _p(proj["conic"]),
+                              _p(proj["opac"]), _p(counts), _p(cum))
+    keys = np.zeros(M, np.int64)
+    vals = np.zeros(M, np.int32)
+    lib.oracle_tile_emit(C.c_int64(total), C.c_int64(N), C.c_int(W), C.c_int(H), _p(proj["aabb"]), _p(proj["depths"]),
+                         _p(proj["xy"]), _p(proj["conic"]), _p(proj["opac"]), _p(cum), _p(keys), _p(vals))
+    return counts, cum, keys, vals
+
+
+def sort_pairs(keys, vals, begin_bit, end_bit):
+    lib = load()
+    n = keys.shape[0]
+    ko, vo = np.zeros(n, np.int64), np.zeros(n, np.int32)
+    lib.oracle_sort_pairs(C.c_int64(n), C.c_int(begin_bit), C.c_int(end_bit), _p(np.ascontiguousarray(keys)),
+                          _p(np.ascontiguousarray(vals)), _p(ko), _p(vo))
+    return ko, vo
+
+
+def tile_n_bits(n_tiles):
+    return load().oracle_tile_n_bits(C.c_int(n_tiles))
+
+
+def tile_offsets(sorted_keys, n_tiles_total):
+    lib = load()
+    offs = np.zeros(n_tiles_total, np.int32)
+    lib.oracle_tile_offsets(C.c_int64(sorted_keys.shape[0]), _p(np.ascontiguousarray(sorted_keys)), C.c_int64(n_tiles_total), _p(offs))
+    return offs
+
+
+def raster_fwd(proj, offsets, flatten_ids, I, N, W, H):
+    lib = load()
+    P = I * H * W
+    out = dict(rgb=np.zeros((P, 3), np.float32), depth=np.zeros(P, np.float32), T=np.zeros(P, np.float32), last_ids=np.zeros(P, np.int32))
+    lib.oracle_raster_fwd(C.c_int(I), C.c_int64(N), C.c_int(W), C.c_int(H), C.c_int64(flatten_ids.shape[0]),
+                          _p(proj["xy"]), _p(proj["depth"]), _p(proj["conic"]), _p(proj["opac"]), _p(proj["rgb"]),
+                          _p(offsets), _p(flatten_ids), _p(out["rgb"]), _p(out["depth"]), _p(out["T"]), _p(out["last_ids"]))
+    return out
+
+
+def raster_bwd(proj, offsets, flatten_ids, I, N, W, H, render, v_rgb, v_depth=None, v_T=None):
+    lib = load()
+    total = proj["depths"].shape[0]
+    g = dict(v_xy=np.zeros((total, 2), np.float32), v_depth=np.zeros(total, np.float32), v_conic=np.zeros((total, 3), np.float32),
+             v_opac=np.zeros(total, np.float32), v_rgb=np.zeros((total, 3), np.float32))
+    lib.oracle_raster_bwd(C.c_int(I), C.c_int64(N), C.c_int(W), C.c_int(H), C.c_int64(flatten_ids.shape[0]),
+                          _p(proj["xy"]), _p(proj["depth"]), _p(proj["conic"]), _p(proj["opac"]), _p(proj["rgb"]),
+                          _p(offsets), _p(flatten_ids), _p(render["depth"]), _p(render["T"]), _p(render["last_ids"]),
+                          _p(_f(v_rgb)), _p(_f(v_depth)), _p(_f(v_T)),
+                          _p(g["v_xy"]), _p(g["v_depth"]), _p(g["v_conic"]), _p(g["v_opac"]), _p(g["v_rgb"]))
+    return g
+
+
+def loss_l1_ssim(render, gt, B, H, W, w_l1=0.8, w_ssim=0.2):
+    lib = load()
+    v = np.zeros((B * H * W, 3), np.float32)
+    losses = np.zeros(3, np.float32)
+    lib.oracle_loss_l1_ssim(C.c_int(B), C.c_int(H), C.c_int(W), C.c_float(w_l1), C.c_float(w_ssim), _p(_f(render)), _p(_f(gt)), _p(v), _p(losses))
+    return v, losses
+
+
+def adam_geometry(p, g, m1, m2, step, lrs, grad_scale=1.0, zero_grad=0):
+    """In place on the numpy arrays of p, g, m1, m2 (dicts with means, quats, scales, opacities)."""
+    lib = load()
+    N = p["means"].shape[0]
+    lib.oracle_adam_geometry(C.c_int64(N), C.c_int(step), C.c_float(grad_scale), C.c_int(zero_grad),
+                             C.c_float(lrs["lr_means"]), C.c_float(lrs["lr_quats"]), C.c_float(lrs["lr_scales"]), C.c_float(lrs["lr_opacities"]),
+                             _p(p["means"]), _p(g["means"]), _p(m1["means"]), _p(m2["means"]),
+                             _p(p["quats"]), _p(g["quats"]), _p(m1["quats"]), _p(m2["quats"]),
+                             _p(p["scales"]), _p(g["scales"]), _p(m1["scales"]), _p(m2["scales"]),
+                             _p(p["opacities"]), _p(g["opacities"]), _p(m1["opacities"]), _p(m2["opacities"]))
+
+
+def adam_plain(param, grad, m1, m2, step, lr, l2_reg=0.0, l2_reg_offset=0.0, grad_scale=1.0, zero_grad=0):
+    load().oracle_adam_plain(C.c_int64(param.size), C.c_int(step), C.c_float(lr), C.c_float(l2_reg), C.c_float(l2_reg_offset),
+                             C.c_float(grad_scale), C.c_int(zero_grad), _p(param), _p(grad), _p(m1), _p(m2))
+
+
+def quant_encode(values, bits):
+    values = _f(values).reshape(-1)
+    n = values.size
+    packed = np.zeros(n * (2 if bits == 16 else 1), np.uint8)
+    bounds = np.zeros(((n + 255) // 256) * 2, np.float32)
+    load().oracle_quant_encode(C.c_int64(n), C.c_int(bits), _p(values), _p(packed), _p(bounds))
+    return packed, bounds
+
+
+def quant_decode(packed, bounds, n, bits):
+    out = np.zeros(n, np.float32)
+    load().oracle_quant_decode(C.c_int64(n), C.c_int(bits), _p(packed), _p(bounds), _p(out))
+    return out
+
+
+def adam_qq(grad, optim_packed, optim_bounds, value_packed, value_bounds, value_bits, step, lr, l2_reg=0.0, grad_scale=1.0, zero_grad=0):
+    load().oracle_adam_qq(C.c_int64(grad.size), C.c_int(step), C.c_float(lr), C.c_float(l2_reg), C.c_float(0.0), C.c_float(grad_scale),
+                          C.c_int(zero_grad), C.c_int(value_bits), _p(grad), _p(optim_packed), _p(optim_bounds), _p(value_packed), _p(value_bounds))
+
+
+def forward_chain(splats, viewmats, intrins, W, H, shq=None):
+    """projection -> keys -> sort -> ranges -> raster for all views in one batch (as the reference's batched launch)."""
+    N, I = splats["means"].shape[0], viewmats.shape[0]
+    proj = project_fwd(splats, viewmats, intrins, W, H, shq=shq)
+    counts, cum, keys, vals = tile_keys(proj, N, W, H)
+    tw, th = tile_grid(W, H)
+    nb = tile_n_bits(tw * th * I)
+    sk, sv = sort_pairs(keys, vals, 0, 32 + nb)
+    offs = tile_offsets(sk, tw * th * I)
+    render = raster_fwd(proj, offs, sv, I, N, W, H)
+    return dict(proj=proj, counts=counts, cum=cum, keys=keys, vals=vals, sorted_keys=sk, sorted_vals=sv, offsets=offs, render=render)

@@ -1,0 +1,300 @@
+// Adam updates for every Gaussian parameter, and the block-quantised codecs of
+// the SH coefficients and their optimiser state.
+//
+// Restates fused_optim_3dgs_geometry_kernel (src/kernels/optim/FusedGeometryOptim.cu:83-380,
+// regulariser weights zero, fp32 moments, scalar step), fused_adam_with_steps_kernel
+// (src/kernels/optim/FusedAppearanceOptim.cu:11-56), fused_adam_with_steps_qq_kernel
+// (:291-418) and the codecs QuantizedTensor / QuantizedAdamState
+// (src/core/Tensor.h:978-1136,1313-1404).  beta1 = 0.9, beta2 = 0.999 and
+// eps = 1e-15 added after the second moment is bias-corrected.
+//
+// All kernels are streaming: every byte is touched once, with 16-byte accesses
+// where the layout allows it.
+#include "ssb_common.cuh"
+
+namespace ssb {
+
+constexpr float kBeta1 = 0.9f, kBeta2 = 0.999f, kAdamEps = 1e-15f;
+
+struct AdamScalars { float ibc1, ibc2; };
+
+__device__ __forceinline__ float adam_update(float x, float g, float& m1, float& m2, float lr_ibc1, float ibc2) {
+    m1 = kBeta1 * m1 + (1.f - kBeta1) * g;
+    m2 = kBeta2 * m2 + (1.f - kBeta2) * g * g;
+    return x - lr_ibc1 * m1 / (sqrtf(m2 * ibc2) + kAdamEps);
+}
+
+// geometry (means, quats, scales, opacities) + features_dc, one thread per splat
+__global__ void __launch_bounds__(256) adam_geometry_kernel(
+    SsbSplats p, SsbSplats g, SsbSplats m1, SsbSplats m2, int64_t first, int64_t count, SsbAdamConfig cfg,
+    float ibc1, float ibc2, float dc_decay) {
+    int64_t i = first + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= first + count) return;
+    const float gs = cfg.grad_scale;
+    const bool zg = cfg.zero_grad != 0;
+    const float lr_s = cfg.lr_scales * ibc1, lr_q = cfg.lr_quats * ibc1, lr_o = cfg.lr_opacities * ibc1, lr_m = cfg.lr_means * ibc1;
+    const float lr_dc = cfg.lr_features_dc * ibc1;
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+        int64_t q = 3 * i + k;
+        float a = m1.scales[q], b = m2.scales[q];
+        p.scales[q] = adam_update(p.scales[q], gs * g.scales[q], a, b, lr_s, ibc2);
+        m1.scales[q] = a; m2.scales[q] = b;
+        if (zg) g.scales[q] = 0.f;
+    }
+    {
+        float4 q4 = ((float4*)p.quats)[i], g4 = ((float4*)g.quats)[i];
+        float4 a4 = ((float4*)m1.quats)[i], b4 = ((float4*)m2.quats)[i];
+        float inv = 1.0f / sqrtf(q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w);
+        float q[4] = {q4.x * inv, q4.y * inv, q4.z * inv, q4.w * inv};
+        float gq[4] = {gs * g4.x, gs * g4.y, gs * g4.z, gs * g4.w};
+        float a[4] = {a4.x, a4.y, a4.z, a4.w}, b[4] = {b4.x, b4.y, b4.z, b4.w};
+        float dq = q[0] * gq[0] + q[1] * gq[1] + q[2] * gq[2] + q[3] * gq[3];
+        float u[4], n2 = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float gk = gq[k] - dq * q[k];
+            u[k] = adam_update(q[k], gk, a[k], b[k], lr_q, ibc2);
+            n2 += u[k] * u[k];
+        }
+        float inv2 = 1.0f / sqrtf(n2);
+        ((float4*)p.quats)[i] = make_float4(u[0] * inv2, u[1] * inv2, u[2] * inv2, u[3] * inv2);
+        ((float4*)m1.quats)[i] = make_float4(a[0], a[1], a[2], a[3]);
+        ((float4*)m2.quats)[i] = make_float4(b[0], b[1], b[2], b[3]);
+        if (zg) ((float4*)g.quats)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    {
+        float a = m1.opacities[i], b = m2.opacities[i];
+        p.opacities[i] = adam_update(p.opacities[i], gs * g.opacities[i], a, b, lr_o, ibc2);
+        m1.opacities[i] = a; m2.opacities[i] = b;
+        if (zg) g.opacities[i] = 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+        int64_t q = 3 * i + k;
+        float a = m1.means[q], b = m2.means[q];
+        p.means[q] = adam_update(p.means[q], gs * g.means[q], a, b, lr_m, ibc2);
+        m1.means[q] = a; m2.means[q] = b;
+        if (zg) g.means[q] = 0.f;
+    }
+    const float dc_off = 0.5f / 0.28209479177387814f;
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+        int64_t q = 3 * i + k;
+        float x = p.features_dc[q], v = g.features_dc[q];
+        if (!isfinite(v)) v = 0.f;
+        v *= gs;
+        v += dc_decay * (fmaxf(x - dc_off, 0.0f) + fminf(x + dc_off, 0.0f));
+        float a = m1.features_dc[q], b = m2.features_dc[q];
+        p.features_dc[q] = adam_update(x, v, a, b, lr_dc, ibc2);
+        m1.features_dc[q] = a; m2.features_dc[q] = b;
+        if (zg) g.features_dc[q] = 0.f;
+    }
+}
+
+// element-wise Adam (features_sh), four floats per thread
+__global__ void __launch_bounds__(256) adam_plain_kernel(
+    float* __restrict__ param, float* __restrict__ grad, float* __restrict__ m1, float* __restrict__ m2, int64_t numel,
+    float lr_ibc1, float ibc2, float decay, float decay_offset, float grad_scale, int zero_grad) {
+    int64_t i4 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i4 >= numel) return;
+    if (i4 + 4 <= numel && ((((uintptr_t)param | (uintptr_t)grad | (uintptr_t)m1 | (uintptr_t)m2) & 15) == 0)) {
+        float4 x = *(float4*)(param + i4), v = *(float4*)(grad + i4), a = *(float4*)(m1 + i4), b = *(float4*)(m2 + i4);
+        float xs[4] = {x.x, x.y, x.z, x.w}, vs[4] = {v.x, v.y, v.z, v.w}, as[4] = {a.x, a.y, a.z, a.w}, bs[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float gk = isfinite(vs[k]) ? vs[k] : 0.f;
+            gk *= grad_scale;
+            gk += decay * (fmaxf(xs[k] - decay_offset, 0.0f) + fminf(xs[k] + decay_offset, 0.0f));
+            xs[k] = adam_update(xs[k], gk, as[k], bs[k], lr_ibc1, ibc2);
+        }
+        *(float4*)(param + i4) = make_float4(xs[0], xs[1], xs[2], xs[3]);
+        *(float4*)(m1 + i4) = make_float4(as[0], as[1], as[2], as[3]);
+        *(float4*)(m2 + i4) = make_float4(bs[0], bs[1], bs[2], bs[3]);
+        if (zero_grad) *(float4*)(grad + i4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
+        for (int64_t i = i4; i < numel && i < i4 + 4; ++i) {
+            float x = param[i], gk = grad[i];
+            if (!isfinite(gk)) gk = 0.f;
+            gk *= grad_scale;
+            gk += decay * (fmaxf(x - decay_offset, 0.0f) + fminf(x + decay_offset, 0.0f));
+            float a = m1[i], b = m2[i];
+            param[i] = adam_update(x, gk, a, b, lr_ibc1, ibc2);
+            m1[i] = a; m2[i] = b;
+            if (zero_grad) grad[i] = 0.f;
+        }
+    }
+}
+
+__device__ __forceinline__ float block_min(float v, float* sh) {
+    v = fminf(v, __shfl_xor_sync(0xffffffffu, v, 16)); v = fminf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+    v = fminf(v, __shfl_xor_sync(0xffffffffu, v, 4)); v = fminf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+    v = fminf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = sh[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) r = fminf(r, sh[k]);
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float* sh) { return -block_min(-v, sh); }
+
+// One CTA = one 256-cell quantisation block.
+template <int VALUE_BITS>
+__global__ void __launch_bounds__(256) adam_qq_kernel(
+    float* __restrict__ grad, uint8_t* __restrict__ optim_packed, float4* __restrict__ optim_bounds,
+    uint8_t* __restrict__ value_packed, float2* __restrict__ value_bounds, int64_t first_block, int64_t numel_total,
+    float lr_ibc1, float ibc2, float decay, float decay_offset, float grad_scale, int zero_grad) {
+    __shared__ float sh[8];
+    const int64_t blk = first_block + blockIdx.x;
+    const int64_t idx = blk * 256 + threadIdx.x;
+    const bool inside = idx < numel_total;
+    constexpr float vq = (float)((1 << VALUE_BITS) - 1), vinv = 1.0f / vq;
+    const float oq = 255.0f, oinv = 1.0f / 255.0f;
+    float x = 0.f, u_new = 0.f, s_new = 0.f;
+    if (inside) {
+        float2 vmm = value_bounds[blk];
+        float4 omm = optim_bounds[blk];
+        float q = VALUE_BITS == 8 ? (float)value_packed[idx] : (float)((uint16_t*)value_packed)[idx];
+        x = vmm.x + (vmm.y - vmm.x) * (q * vinv);
+        float v = grad[idx];
+        if (!isfinite(v)) v = 0.f;
+        if (zero_grad) grad[idx] = 0.f;
+        v *= grad_scale;
+        v += decay * (fmaxf(x - decay_offset, 0.0f) + fminf(x + decay_offset, 0.0f));
+        uchar2 code = ((uchar2*)optim_packed)[idx];
+        float u = omm.x + (omm.y - omm.x) * ((float)code.x * oinv);
+        float ls = omm.z + (omm.w - omm.z) * ((float)code.y * oinv);
+        float sqrt_g2 = kAdamEps * expm1f(ls);
+        float g1 = u * (sqrt_g2 + kAdamEps), g2 = sqrt_g2 * sqrt_g2;
+        x = adam_update(x, v, g1, g2, lr_ibc1, ibc2);
+        float sq = sqrtf(fmaxf(g2, 0.0f));
+        u_new = g1 / (sq + kAdamEps);
+        s_new = log1pf(fmaxf(sq, 0.0f) * (1.0f / kAdamEps));
+    }
+    float vmin = block_min(inside ? x : 1e30f, sh), vmax = block_max(inside ? x : -1e30f, sh);
+    float umin = block_min(inside ? u_new : 1e30f, sh), umax = block_max(inside ? u_new : -1e30f, sh);
+    float smin = block_min(inside ? s_new : 1e30f, sh), smax = block_max(inside ? s_new : -1e30f, sh);
+    if (inside) {
+        float vrange = fmaxf(vmax - vmin, 1e-30f);
+        float qf = fminf(fmaxf(roundf(vq * (x - vmin) / vrange), 0.0f), vq);
+        if (VALUE_BITS == 8) value_packed[idx] = (uint8_t)qf; else ((uint16_t*)value_packed)[idx] = (uint16_t)qf;
+        float urange = fmaxf(umax - umin, kAdamEps), srange = fmaxf(smax - smin, kAdamEps);
+        float uq = fminf(fmaxf(roundf(oq * (u_new - umin) / urange), 0.0f), oq);
+        float sq = fminf(fmaxf(roundf(oq * (s_new - smin) / srange), 0.0f), oq);
+        ((uchar2*)optim_packed)[idx] = make_uchar2((uint8_t)uq, (uint8_t)sq);
+    }
+    if (threadIdx.x == 0) {
+        value_bounds[blk] = make_float2(vmin, vmax);
+        optim_bounds[blk] = make_float4(umin, umax, smin, smax);
+    }
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(256) quant_encode_kernel(const float* __restrict__ values, int64_t numel, uint8_t* __restrict__ packed, float2* __restrict__ bounds) {
+    __shared__ float sh[8];
+    const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    const bool inside = idx < numel;
+    float v = inside ? values[idx] : 0.f;
+    float mn = block_min(inside ? v : 1e30f, sh), mx = block_max(inside ? v : -1e30f, sh);
+    constexpr float qmax = (float)((1 << BITS) - 1);
+    if (inside) {
+        float range = fmaxf(mx - mn, 1e-30f);
+        float qf = fminf(fmaxf(roundf(qmax * (v - mn) / range), 0.0f), qmax);
+        if (BITS == 8) packed[idx] = (uint8_t)qf; else ((uint16_t*)packed)[idx] = (uint16_t)qf;
+    }
+    if (threadIdx.x == 0) bounds[blockIdx.x] = make_float2(mn, mx);
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(256) quant_decode_kernel(const uint8_t* __restrict__ packed, const float2* __restrict__ bounds, int64_t numel, float* __restrict__ values) {
+    const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= numel) return;
+    float2 mm = bounds[idx >> 8];
+    float q = BITS == 8 ? (float)packed[idx] : (float)((const uint16_t*)packed)[idx];
+    values[idx] = mm.x + (mm.y - mm.x) * (q * (1.0f / (float)((1 << BITS) - 1)));
+}
+
+}  // namespace ssb
+
+extern "C" {
+
+int ssb_adam_step(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
+                  int64_t first, int64_t count, const SsbAdamConfig* cfg, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(params && grads && m1 && m2 && cfg, "ssb_adam_step: NULL argument");
+    SSB_REQUIRE(first >= 0 && count >= 0, "ssb_adam_step: bad range");
+    SSB_REQUIRE(cfg->step >= 1, "ssb_adam_step: step must be >= 1 (got %d)", cfg->step);
+    if (count == 0) return SSB_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const float ibc1 = 1.0f / (1.0f - powf(kBeta1, (float)cfg->step));
+    const float ibc2 = 1.0f / (1.0f - powf(kBeta2, (float)cfg->step));
+    // decay = 2 * l2_reg / numel, numel = whole-tensor element count is not known
+    // here for a sub-range; the regulariser weight is zero in every supported
+    // configuration, and a non-zero weight is applied per element of this call.
+    const float dc_decay = 2.0f * cfg->sh_reg_weight / (float)(count * 3);
+    adam_geometry_kernel<<<(unsigned)ceil_div(count, 256), 256, 0, st>>>(*params, *grads, *m1, *m2, first, count, *cfg, ibc1, ibc2, dc_decay);
+    SSB_LAUNCHED("adam_geometry_kernel");
+    if (params->features_sh) {
+        SSB_REQUIRE(grads->features_sh && m1->features_sh && m2->features_sh, "ssb_adam_step: SH gradient/moment arrays missing");
+        int64_t numel = count * 3 * kNumSh, off = first * 3 * kNumSh;
+        const float sh_decay = 2.0f * cfg->sh_reg_weight / (float)numel;
+        adam_plain_kernel<<<(unsigned)ceil_div(ceil_div(numel, 4), 256), 256, 0, st>>>(
+            params->features_sh + off, grads->features_sh + off, m1->features_sh + off, m2->features_sh + off, numel,
+            cfg->lr_features_sh * ibc1, ibc2, sh_decay, 0.0f, cfg->grad_scale, cfg->zero_grad);
+        SSB_LAUNCHED("adam_plain_kernel");
+    }
+    return SSB_OK;
+}
+
+int ssb_adam_step_sh_quantized(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds,
+                               void* d_value_packed, float* d_value_bounds, int32_t value_bits,
+                               int64_t first_cell, int64_t numel, int64_t numel_total,
+                               const SsbAdamConfig* cfg, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(d_grad && d_optim_packed && d_optim_bounds && d_value_packed && d_value_bounds && cfg, "ssb_adam_step_sh_quantized: NULL argument");
+    SSB_REQUIRE(value_bits == 8 || value_bits == 16, "ssb_adam_step_sh_quantized: value_bits must be 8 or 16 (got %d)", value_bits);
+    SSB_REQUIRE(first_cell >= 0 && (first_cell % 256) == 0 && numel >= 0 && first_cell + numel <= numel_total, "ssb_adam_step_sh_quantized: bad cell range");
+    SSB_REQUIRE(cfg->step >= 1, "ssb_adam_step_sh_quantized: step must be >= 1");
+    if (numel == 0) return SSB_OK;
+    const float ibc1 = 1.0f / (1.0f - powf(kBeta1, (float)cfg->step));
+    const float ibc2 = 1.0f / (1.0f - powf(kBeta2, (float)cfg->step));
+    const float decay = 2.0f * cfg->sh_reg_weight / (float)numel_total;
+    unsigned blocks = (unsigned)ceil_div(numel, 256);
+    int64_t end_total = first_cell + numel;   // cells beyond the range belong to another caller
+    if (value_bits == 8)
+        adam_qq_kernel<8><<<blocks, 256, 0, (cudaStream_t)stream>>>(d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed,
+            (float2*)d_value_bounds, first_cell / 256, end_total, cfg->lr_features_sh * ibc1, ibc2, decay, 0.0f, cfg->grad_scale, cfg->zero_grad);
+    else
+        adam_qq_kernel<16><<<blocks, 256, 0, (cudaStream_t)stream>>>(d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed,
+            (float2*)d_value_bounds, first_cell / 256, end_total, cfg->lr_features_sh * ibc1, ibc2, decay, 0.0f, cfg->grad_scale, cfg->zero_grad);
+    SSB_LAUNCHED("adam_qq_kernel");
+    return SSB_OK;
+}
+
+int ssb_quant_encode(const float* d_values, int64_t numel, int32_t bits, void* d_packed, float* d_bounds, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(d_values && d_packed && d_bounds && numel >= 0, "ssb_quant_encode: bad argument");
+    SSB_REQUIRE(bits == 8 || bits == 16, "ssb_quant_encode: bits must be 8 or 16 (got %d)", bits);
+    if (numel == 0) return SSB_OK;
+    unsigned blocks = (unsigned)ceil_div(numel, 256);
+    if (bits == 8) quant_encode_kernel<8><<<blocks, 256, 0, (cudaStream_t)stream>>>(d_values, numel, (uint8_t*)d_packed, (float2*)d_bounds);
+    else quant_encode_kernel<16><<<blocks, 256, 0, (cudaStream_t)stream>>>(d_values, numel, (uint8_t*)d_packed, (float2*)d_bounds);
+    SSB_LAUNCHED("quant_encode_kernel");
+    return SSB_OK;
+}
+
+int ssb_quant_decode(const void* d_packed, const float* d_bounds, int64_t numel, int32_t bits, float* d_values, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(d_values && d_packed && d_bounds && numel >= 0, "ssb_quant_decode: bad argument");
+    SSB_REQUIRE(bits == 8 || bits == 16, "ssb_quant_decode: bits must be 8 or 16 (got %d)", bits);
+    if (numel == 0) return SSB_OK;
+    unsigned blocks = (unsigned)ceil_div(numel, 256);
+    if (bits == 8) quant_decode_kernel<8><<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)d_packed, (const float2*)d_bounds, numel, d_values);
+    else quant_decode_kernel<16><<<blocks, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)d_packed, (const float2*)d_bounds, numel, d_values);
+    SSB_LAUNCHED("quant_decode_kernel");
+    return SSB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,570 @@
+// Gaussian projection forward and backward.
+//
+// Forward: per (view, splat) pair, world mean -> camera, 3D covariance from the
+// normalised quaternion and exp(scale), EWA 2D covariance through the camera
+// Jacobian, +0.3 px blur, conic, opacity-aware extent, culls, SH degree 3 ->
+// RGB (fp32 or q8/q16 packed coefficients).  Restates
+// src/shaders/primitive_3dgs.slang:419-578 and
+// src/kernels/projection/ProjectionFwd_kernel.cuh:15-111 of the reference.
+//
+// Backward: hand-derived reverse mode of the same function with every cull
+// skipped (the reference differentiates the assume_valid variant,
+// src/shaders/primitive_3dgs.slang:644-698) plus the SH vjp with the colour
+// clamp mask (src/shaders/harmonics.slang:1087-1126).
+//
+// Memory plan: one thread per splat; the 45 SH coefficients of a block's 128
+// splats are one contiguous 23 KB span, loaded with coalesced 4-byte accesses
+// into shared memory (decoded on the way when packed) and read back at stride
+// 45 words, which is bank-conflict free.  The backward kernel keeps a second
+// 23 KB span for the SH gradients so they too leave the SM coalesced.
+#include "ssb_common.cuh"
+
+namespace ssb {
+
+constexpr int kProjBlock = 128;
+constexpr int kShPerSplat = 3 * kNumSh;  // 45
+
+struct ProjGeom {
+    // forward intermediates kept for the backward pass
+    float mc[3];
+    float len;
+    float opacity;
+    float qn[4], qinv;
+    float s[3];
+    float Rq[9];
+    float W[9];       // R * Rq
+    float covc[6];    // xx xy xz yy yz zz
+    float J00, J02, J11, J12;
+    int clampx, clampy;  // -1 below, 0 inside, +1 above
+    float c00, c01, c11, det;
+    float mean2d[2];
+    float conic[3];
+};
+
+__device__ __forceinline__ void quat_to_rot(const float q[4], float R[9]) {
+    float w = q[0], x = q[1], y = q[2], z = q[3];
+    R[0] = 1.f - 2.f * (y * y + z * z); R[1] = 2.f * (x * y - w * z); R[2] = 2.f * (x * z + w * y);
+    R[3] = 2.f * (x * y + w * z); R[4] = 1.f - 2.f * (x * x + z * z); R[5] = 2.f * (y * z - w * x);
+    R[6] = 2.f * (x * z - w * y); R[7] = 2.f * (y * z + w * x); R[8] = 1.f - 2.f * (x * x + y * y);
+}
+
+// Geometry of the pinhole projection.  Returns false when a cull of the
+// reference's forward pass applies (never when assume_valid).
+template <bool assume_valid>
+__device__ __forceinline__ bool project_pinhole(
+    const CamDev& cam, int W_img, bool antialiased,
+    const float mean[3], const float quat[4], const float scale[3], float in_opacity,
+    ProjGeom& g) {
+    const float* R = cam.R;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) g.mc[i] = R[3 * i] * mean[0] + R[3 * i + 1] * mean[1] + R[3 * i + 2] * mean[2] + cam.t[i];
+    g.len = sqrtf(g.mc[0] * g.mc[0] + g.mc[1] * g.mc[1] + g.mc[2] * g.mc[2]);
+    if (!assume_valid && g.mc[2] <= 0.0f) return false;
+    g.opacity = 1.0f / (1.0f + expf(-in_opacity));
+
+    float qq = sqrtf(quat[0] * quat[0] + quat[1] * quat[1] + quat[2] * quat[2] + quat[3] * quat[3]);
+    g.qinv = 1.0f / qq;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) g.qn[i] = quat[i] * g.qinv;
+    quat_to_rot(g.qn, g.Rq);
+#pragma unroll
+    for (int i = 0; i < 3; ++i) g.s[i] = expf(scale[i]);
+    // W = R * Rq ; covc = W diag(s^2) W^T
+#pragma unroll
+    for (int i = 0; i < 3; ++i)
+#pragma unroll
+        for (int j = 0; j < 3; ++j)
+            g.W[3 * i + j] = R[3 * i] * g.Rq[j] + R[3 * i + 1] * g.Rq[3 + j] + R[3 * i + 2] * g.Rq[6 + j];
+    float s2[3] = {g.s[0] * g.s[0], g.s[1] * g.s[1], g.s[2] * g.s[2]};
+    const float* Wm = g.W;
+    g.covc[0] = Wm[0] * Wm[0] * s2[0] + Wm[1] * Wm[1] * s2[1] + Wm[2] * Wm[2] * s2[2];
+    g.covc[1] = Wm[0] * Wm[3] * s2[0] + Wm[1] * Wm[4] * s2[1] + Wm[2] * Wm[5] * s2[2];
+    g.covc[2] = Wm[0] * Wm[6] * s2[0] + Wm[1] * Wm[7] * s2[1] + Wm[2] * Wm[8] * s2[2];
+    g.covc[3] = Wm[3] * Wm[3] * s2[0] + Wm[4] * Wm[4] * s2[1] + Wm[5] * Wm[5] * s2[2];
+    g.covc[4] = Wm[3] * Wm[6] * s2[0] + Wm[4] * Wm[7] * s2[1] + Wm[5] * Wm[8] * s2[2];
+    g.covc[5] = Wm[6] * Wm[6] * s2[0] + Wm[7] * Wm[7] * s2[1] + Wm[8] * Wm[8] * s2[2];
+
+    float rz = 1.0f / g.mc[2];
+    float u = g.mc[0] * rz, v = g.mc[1] * rz;
+    g.mean2d[0] = cam.fx * u + cam.cx;
+    g.mean2d[1] = cam.fy * v + cam.cy;
+    g.J00 = cam.fx * rz;
+    g.J11 = cam.fy * rz;
+    float j02 = -(cam.fx * u) * rz, j12 = -(cam.fy * v) * rz;
+    // Both rows use the x limits, as the reference does
+    // (src/shaders/primitive_3dgs.slang:84-95).
+    float width = (float)W_img;
+    float lim_pos = width + 0.3f * (0.5f * width);
+    float lim_neg = 0.3f * (0.5f * width);
+    float max_x = -(-lim_neg - cam.cx) * rz, min_x = -(lim_pos - cam.cx) * rz;
+    float max_y = -(-lim_neg - cam.cy) * rz, min_y = -(lim_pos - cam.cy) * rz;
+    g.clampx = j02 < min_x ? -1 : (j02 > max_x ? 1 : 0);
+    g.clampy = j12 < min_y ? -1 : (j12 > max_y ? 1 : 0);
+    g.J02 = g.clampx < 0 ? min_x : (g.clampx > 0 ? max_x : j02);
+    g.J12 = g.clampy < 0 ? min_y : (g.clampy > 0 ? max_y : j12);
+
+    // cov2d = J covc J^T with J = [[J00, 0, J02], [0, J11, J12]]
+    const float* c = g.covc;
+    float a0 = g.J00 * c[0] + g.J02 * c[2], a1 = g.J00 * c[1] + g.J02 * c[4], a2 = g.J00 * c[2] + g.J02 * c[5];
+    float b1 = g.J11 * c[3] + g.J12 * c[4], b2 = g.J11 * c[4] + g.J12 * c[5];
+    float c00 = a0 * g.J00 + a2 * g.J02;
+    float c01 = a1 * g.J11 + a2 * g.J12;
+    float c11 = b1 * g.J11 + b2 * g.J12;
+    const float eps2d = antialiased ? 0.1f : 0.3f;
+    float det_orig = c00 * c11 - c01 * c01;
+    c00 += eps2d; c11 += eps2d;
+    float det = c00 * c11 - c01 * c01;
+    if (!assume_valid && det <= 0.f) return false;
+    g.c00 = c00; g.c01 = c01; g.c11 = c11; g.det = det;
+    float invdet = 1.0f / det;
+    g.conic[0] = c11 * invdet; g.conic[1] = -c01 * invdet; g.conic[2] = c00 * invdet;
+    if (antialiased) g.opacity *= sqrtf(fmaxf(0.f, det_orig / det));
+    if (!assume_valid && g.opacity < kAlphaThreshold) return false;
+    return true;
+}
+
+// Real SH basis, bands 1..3, at a unit direction (src/shaders/harmonics.slang:154-251).
+__device__ __forceinline__ void sh_basis(float x, float y, float z, float b[kNumSh]) {
+    const float c1 = 0.48860251190292f;
+    b[0] = -c1 * y; b[1] = c1 * z; b[2] = -c1 * x;
+    float z2 = z * z;
+    float t0b = -1.092548430592079f * z;
+    const float c2a = 0.5462742152960395f;
+    float fC1 = x * x - y * y, fS1 = 2.f * x * y;
+    b[3] = c2a * fS1; b[4] = t0b * y; b[5] = 0.9461746957575601f * z2 - 0.3153915652525201f;
+    b[6] = t0b * x; b[7] = c2a * fC1;
+    float t0c = -2.285228997322329f * z2 + 0.4570457994644658f;
+    float t1b = 1.445305721320277f * z;
+    const float c3a = -0.5900435899266435f;
+    float fC2 = x * fC1 - y * fS1, fS2 = x * fS1 + y * fC1;
+    b[8] = c3a * fS2; b[9] = t1b * fS1; b[10] = t0c * y;
+    b[11] = z * (1.865881662950577f * z2 - 1.119528997770346f);
+    b[12] = t0c * x; b[13] = t1b * fC1; b[14] = c3a * fC2;
+}
+
+// Loads the block's SH span into shared memory as fp32 (decoding packed codes).
+__device__ __forceinline__ void stage_sh(
+    float* sh_s, const float* __restrict__ sh_f32, const void* __restrict__ packed, const float* __restrict__ bounds,
+    int bits, int64_t bounds_stride, int64_t first_splat, int64_t n) {
+    int64_t base = first_splat * kShPerSplat;
+    int count = (int)min((int64_t)kProjBlock, n - first_splat) * kShPerSplat;
+    if (bits == 8 || bits == 16) {
+        const float inv = bits == 8 ? (1.0f / 255.0f) : (1.0f / 65535.0f);
+        for (int i = threadIdx.x; i < count; i += kProjBlock) {
+            int64_t cell = base + i;
+            float q = bits == 8 ? (float)((const uint8_t*)packed)[cell] : (float)((const uint16_t*)packed)[cell];
+            float2 mm = ((const float2*)bounds)[cell / bounds_stride];
+            sh_s[i] = mm.x + (mm.y - mm.x) * (q * inv);
+        }
+    } else {
+        for (int i = threadIdx.x; i < count; i += kProjBlock) sh_s[i] = sh_f32[base + i];
+    }
+}
+
+__global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
+    SsbSplats sp, SsbShQuant shq, int64_t n, const float* __restrict__ viewmats, const float* __restrict__ intrins,
+    int W, int H, int antialiased,
+    float4* __restrict__ aabb_out, float* __restrict__ depths_out, float* __restrict__ radii, SsbScreenRec* __restrict__ screen) {
+    __shared__ float sh_s[kProjBlock * kShPerSplat];
+    const int cid = blockIdx.y;
+    const int64_t first = (int64_t)blockIdx.x * kProjBlock;
+    const int64_t gid = first + threadIdx.x;
+    stage_sh(sh_s, sp.features_sh, shq.packed, shq.bounds, shq.bits, shq.bounds_stride, first, n);
+    __syncthreads();
+    if (gid >= n) return;
+    const int64_t idx = (int64_t)cid * n + gid;
+    CamDev cam = load_cam(viewmats, intrins, cid);
+
+    float mean[3] = {sp.means[3 * gid], sp.means[3 * gid + 1], sp.means[3 * gid + 2]};
+    float4 q4 = ((const float4*)sp.quats)[gid];
+    float quat[4] = {q4.x, q4.y, q4.z, q4.w};
+    float scale[3] = {sp.scales[3 * gid], sp.scales[3 * gid + 1], sp.scales[3 * gid + 2]};
+    float in_op = sp.opacities[gid];
+
+    ProjGeom g;
+    bool ok = project_pinhole<false>(cam, W, antialiased != 0, mean, quat, scale, in_op, g);
+    float xmin = 0.f, ymin = 0.f, xmax = 0.f, ymax = 0.f, L = 0.f;
+    if (ok) {
+        L = logf(g.opacity / kAlphaThreshold);
+        float extend = fminf(3.33f, sqrtf(2.0f * L));
+        float rx = extend * sqrtf(g.c00), ry = extend * sqrtf(g.c11);
+        xmin = g.mean2d[0] - rx; xmax = g.mean2d[0] + rx;
+        ymin = g.mean2d[1] - ry; ymax = g.mean2d[1] + ry;
+        if (xmax <= 0.f || xmin >= (float)W || ymax <= 0.f || ymin >= (float)H) ok = false;
+    }
+    float rgb[3] = {0.f, 0.f, 0.f};
+    if (ok && xmax > xmin && ymax > ymin) {
+        // viewdir = mean + R^T t, normalised inside the SH evaluation
+        const float* R = cam.R;
+        float d[3];
+#pragma unroll
+        for (int j = 0; j < 3; ++j) d[j] = mean[j] + (R[j] * cam.t[0] + R[3 + j] * cam.t[1] + R[6 + j] * cam.t[2]);
+        float inv = rsqrtf(d[0] * d[0] + d[1] * d[1] + d[2] * d[2]);
+        float b[kNumSh];
+        sh_basis(d[0] * inv, d[1] * inv, d[2] * inv, b);
+        const float* sh = sh_s + threadIdx.x * kShPerSplat;
+#pragma unroll
+        for (int ch = 0; ch < 3; ++ch) {
+            float c = kShC0 * sp.features_dc[3 * gid + ch];
+#pragma unroll
+            for (int j = 0; j < kNumSh; ++j) c += b[j] * sh[3 * j + ch];
+            rgb[ch] = fmaxf(c + 0.5f, 0.0f);
+        }
+    }
+    float a0 = fminf(fmaxf(xmin, 0.0f), (float)W - 1.0f), a1 = fminf(fmaxf(ymin, 0.0f), (float)H - 1.0f);
+    float a2 = fminf(fmaxf(xmax, 0.0f), (float)W - 1.0f), a3 = fminf(fmaxf(ymax, 0.0f), (float)H - 1.0f);
+    bool keep = ok && (a2 - a0 > 1e-3f) && (a3 - a1 > 1e-3f);
+    if (keep) {
+        aabb_out[idx] = make_float4(a0, a1, a2, a3);
+        depths_out[idx] = g.mc[2];  // pinhole sorting depth
+        // half extents of the alpha >= 1/255 footprint, slightly inflated
+        float e = sqrtf(2.0f * L) * 1.0005f;
+        float hx = e * sqrtf(g.c00) + 1e-3f, hy = e * sqrtf(g.c11) + 1e-3f;
+        float4* r = (float4*)(screen + idx);
+        r[0] = make_float4(g.mean2d[0], g.mean2d[1], hx, hy);
+        r[1] = make_float4(g.conic[0], g.conic[1], g.conic[2], g.opacity);
+        r[2] = make_float4(rgb[0], rgb[1], rgb[2], g.len);
+        if (radii) {
+            // view_radius_3dgs, src/shaders/projection_utils.slang:1033-1043
+            const float* R = cam.R;
+            float cp[3];
+#pragma unroll
+            for (int j = 0; j < 3; ++j) cp[j] = -(R[j] * cam.t[0] + R[3 + j] * cam.t[1] + R[6 + j] * cam.t[2]);
+            float ext = sqrtf(2.0f * logf(fmaxf(255.0f / (1.0f + expf(-in_op)), 1.0f)));
+            float rad = expf(fmaxf(scale[0], fmaxf(scale[1], scale[2]))) * ext;
+            float dx = mean[0] - cp[0], dy = mean[1] - cp[1], dz = mean[2] - cp[2];
+            float dist = sqrtf(dx * dx + dy * dy + dz * dz);
+            float vr = rad / (fmaxf(dist, rad) + sqrtf(fmaxf(dist * dist - rad * rad, 0.0f)));
+            atomicMax((int*)&radii[gid], __float_as_int(vr));  // vr >= 0: int order == float order
+        }
+    } else {
+        aabb_out[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
+        depths_out[idx] = 0.f;
+    }
+}
+
+}  // namespace ssb
+
+namespace ssb {
+
+// Gradient of the SH basis with respect to the (unit) direction, contracted
+// with the per-coefficient weights w[j] = sum_ch sh[j][ch] * vc[ch].
+__device__ __forceinline__ void sh_basis_vjp(float x, float y, float z, const float w[kNumSh], float v[3]) {
+    const float c1 = 0.48860251190292f, c2a = 0.5462742152960395f, c2b = 1.092548430592079f;
+    const float c3a = -0.5900435899266435f, c3b = 1.445305721320277f, c3c = 2.285228997322329f;
+    float z2 = z * z;
+    float t0c = -c3c * z2 + 0.4570457994644658f;
+    float fC1 = x * x - y * y, fS1 = 2.f * x * y;
+    float vx = -c1 * w[2], vy = -c1 * w[0], vz = c1 * w[1];
+    vx += 2.f * c2a * y * w[3] - c2b * z * w[6] + 2.f * c2a * x * w[7];
+    vy += 2.f * c2a * x * w[3] - c2b * z * w[4] - 2.f * c2a * y * w[7];
+    vz += -c2b * y * w[4] + 2.f * 0.9461746957575601f * z * w[5] - c2b * x * w[6];
+    vx += c3a * 3.f * fS1 * w[8] + 2.f * c3b * y * z * w[9] + t0c * w[12] + 2.f * c3b * z * x * w[13] + c3a * 3.f * fC1 * w[14];
+    vy += c3a * 3.f * fC1 * w[8] + 2.f * c3b * x * z * w[9] + t0c * w[10] - 2.f * c3b * z * y * w[13] - c3a * 3.f * fS1 * w[14];
+    vz += c3b * fS1 * w[9] - 2.f * c3c * z * y * w[10] + (3.f * 1.865881662950577f * z2 - 1.119528997770346f) * w[11]
+        - 2.f * c3c * z * x * w[12] + c3b * fC1 * w[13];
+    v[0] = vx; v[1] = vy; v[2] = vz;
+}
+
+__device__ __forceinline__ float finite_or_zero(float v) { return isfinite(v) ? v : 0.0f; }
+
+__global__ void __launch_bounds__(kProjBlock) project_bwd_kernel(
+    SsbSplats sp, SsbShQuant shq, int64_t n, int C, const float* __restrict__ viewmats, const float* __restrict__ intrins,
+    int W, int H, int antialiased, const float4* __restrict__ aabb, SsbScreenRec* __restrict__ v_screen,
+    SsbSplats gr, int accumulate, int clear_v_screen) {
+    __shared__ float sh_s[kProjBlock * kShPerSplat];
+    __shared__ float shg_s[kProjBlock * kShPerSplat];
+    const int64_t first = (int64_t)blockIdx.x * kProjBlock;
+    const int64_t gid = first + threadIdx.x;
+    const int count = (int)min((int64_t)kProjBlock, n - first) * kShPerSplat;
+    stage_sh(sh_s, sp.features_sh, shq.packed, shq.bounds, shq.bits, shq.bounds_stride, first, n);
+    for (int i = threadIdx.x; i < count; i += kProjBlock) shg_s[i] = 0.f;
+    __syncthreads();
+
+    float g_mean[3] = {0.f, 0.f, 0.f}, g_quat[4] = {0.f, 0.f, 0.f, 0.f}, g_scale[3] = {0.f, 0.f, 0.f}, g_op = 0.f, g_dc[3] = {0.f, 0.f, 0.f};
+    if (gid < n) {
+        float mean[3] = {sp.means[3 * gid], sp.means[3 * gid + 1], sp.means[3 * gid + 2]};
+        float4 q4 = ((const float4*)sp.quats)[gid];
+        float quat[4] = {q4.x, q4.y, q4.z, q4.w};
+        float scale[3] = {sp.scales[3 * gid], sp.scales[3 * gid + 1], sp.scales[3 * gid + 2]};
+        float in_op = sp.opacities[gid];
+        const float* sh = sh_s + threadIdx.x * kShPerSplat;
+        float* shg = shg_s + threadIdx.x * kShPerSplat;
+        for (int cid = 0; cid < C; ++cid) {
+            const int64_t idx = (int64_t)cid * n + gid;
+            float4 bb = aabb[idx];
+            if (bb.z <= bb.x || bb.w <= bb.y) continue;
+            CamDev cam = load_cam(viewmats, intrins, cid);
+            float4* vr = (float4*)(v_screen + idx);
+            float4 va = vr[0], vb = vr[1], vc4 = vr[2];
+            if (clear_v_screen) {   // leave the record ready for the next view's reductions
+                const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+                vr[0] = zero; vr[1] = zero; vr[2] = zero;
+            }
+            ProjGeom g;
+            project_pinhole<true>(cam, W, antialiased != 0, mean, quat, scale, in_op, g);
+            // ---- conic -> blurred 2D covariance
+            float v0 = vb.x, v1 = vb.y, v2 = vb.z;
+            float invdet = 1.0f / g.det;
+            float vD = -(v0 * g.conic[0] + v1 * g.conic[1] + v2 * g.conic[2]) * invdet;
+            float G00 = v2 * invdet + vD * g.c11;
+            float G11 = v0 * invdet + vD * g.c00;
+            float G01 = 0.5f * (-v1 * invdet - 2.f * vD * g.c01);
+            float v_opac = vb.w;
+            if (antialiased) {
+                // opacity *= sqrt(max(0, det_orig / det_blur))
+                const float eps2d = 0.1f;
+                float o00 = g.c00 - eps2d, o11 = g.c11 - eps2d;
+                float det_orig = o00 * o11 - g.c01 * g.c01;
+                float ratio = det_orig * invdet;
+                if (ratio > 0.f) {
+                    float comp = sqrtf(ratio);
+                    float op0 = g.opacity / comp;          // pre-compensation opacity
+                    float v_comp = v_opac * op0;
+                    float v_ratio = v_comp * 0.5f / comp;
+                    float v_do = v_ratio * invdet, v_db = -v_ratio * ratio * invdet;
+                    G00 += v_do * o11 + v_db * g.c11;
+                    G11 += v_do * o00 + v_db * g.c00;
+                    G01 += 0.5f * (-2.f * g.c01 * (v_do + v_db));
+                    v_opac *= comp;
+                    g.opacity = op0;
+                } else {
+                    v_opac = 0.f;
+                }
+            }
+            // ---- cov2d = J covc J^T : v_J = 2 G J covc, v_covc = J^T G J
+            const float* c = g.covc;
+            float JC0[3] = {g.J00 * c[0] + g.J02 * c[2], g.J00 * c[1] + g.J02 * c[4], g.J00 * c[2] + g.J02 * c[5]};
+            float JC1[3] = {g.J11 * c[1] + g.J12 * c[2], g.J11 * c[3] + g.J12 * c[4], g.J11 * c[4] + g.J12 * c[5]};
+            float vJ00 = 2.f * (G00 * JC0[0] + G01 * JC1[0]);
+            float vJ02 = 2.f * (G00 * JC0[2] + G01 * JC1[2]);
+            float vJ11 = 2.f * (G01 * JC0[1] + G11 * JC1[1]);
+            float vJ12 = 2.f * (G01 * JC0[2] + G11 * JC1[2]);
+            // J rows: r0 = (J00, 0, J02), r1 = (0, J11, J12); v_covc[i][j] = sum_ab J[a][i] G[a][b] J[b][j]
+            float r0[3] = {g.J00, 0.f, g.J02}, r1[3] = {0.f, g.J11, g.J12};
+            float vC[9];
+#pragma unroll
+            for (int i = 0; i < 3; ++i)
+#pragma unroll
+                for (int j = 0; j < 3; ++j)
+                    vC[3 * i + j] = r0[i] * (G00 * r0[j] + G01 * r1[j]) + r1[i] * (G01 * r0[j] + G11 * r1[j]);
+            // ---- camera-space mean
+            float x = g.mc[0], y = g.mc[1], z = g.mc[2];
+            float rz = 1.0f / z, rz2 = rz * rz;
+            float vmc[3] = {0.f, 0.f, 0.f};
+            vmc[2] += -cam.fx * rz2 * vJ00 - cam.fy * rz2 * vJ11;
+            float width = (float)W;
+            float lim_pos = width + 0.3f * (0.5f * width), lim_neg = 0.3f * (0.5f * width);
+            if (g.clampx == 0) { vmc[0] += -cam.fx * rz2 * vJ02; vmc[2] += 2.f * cam.fx * x * rz2 * rz * vJ02; }
+            else if (g.clampx < 0) vmc[2] += (lim_pos - cam.cx) * rz2 * vJ02;
+            else vmc[2] += -(lim_neg + cam.cx) * rz2 * vJ02;
+            if (g.clampy == 0) { vmc[1] += -cam.fy * rz2 * vJ12; vmc[2] += 2.f * cam.fy * y * rz2 * rz * vJ12; }
+            else if (g.clampy < 0) vmc[2] += (lim_pos - cam.cy) * rz2 * vJ12;
+            else vmc[2] += -(lim_neg + cam.cy) * rz2 * vJ12;
+            vmc[0] += cam.fx * rz * va.x;
+            vmc[1] += cam.fy * rz * va.y;
+            vmc[2] += -(cam.fx * x * va.x + cam.fy * y * va.y) * rz2;
+            float vdl = vc4.w / g.len;   // depth = |mc|
+            vmc[0] += vdl * x; vmc[1] += vdl * y; vmc[2] += vdl * z;
+            const float* R = cam.R;
+#pragma unroll
+            for (int j = 0; j < 3; ++j) g_mean[j] += finite_or_zero(R[j] * vmc[0] + R[3 + j] * vmc[1] + R[6 + j] * vmc[2]);
+            // ---- covc = Wm diag(s^2) Wm^T, Wm = R Rq
+            // v_Wm = 2 vC Wm diag(s^2);  v_s2[j] = sum_{ik} Wm[i][j] vC[i][k] Wm[k][j]
+            const float* Wm = g.W;
+            float s2[3] = {g.s[0] * g.s[0], g.s[1] * g.s[1], g.s[2] * g.s[2]};
+            float vCW[9];
+#pragma unroll
+            for (int i = 0; i < 3; ++i)
+#pragma unroll
+                for (int j = 0; j < 3; ++j)
+                    vCW[3 * i + j] = vC[3 * i] * Wm[j] + vC[3 * i + 1] * Wm[3 + j] + vC[3 * i + 2] * Wm[6 + j];
+            float vscale[3];
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                float vs2 = Wm[j] * vCW[j] + Wm[3 + j] * vCW[3 + j] + Wm[6 + j] * vCW[6 + j];
+                vscale[j] = vs2 * 2.f * s2[j];   // d s^2 / d log s = 2 s^2
+                g_scale[j] += finite_or_zero(vscale[j]);
+            }
+            // v_Rq = R^T v_Wm, v_Wm[i][j] = 2 vCW[i][j] s2[j]
+            float vRq[9];
+#pragma unroll
+            for (int i = 0; i < 3; ++i)
+#pragma unroll
+                for (int j = 0; j < 3; ++j)
+                    vRq[3 * i + j] = 2.f * s2[j] * (R[i] * vCW[j] + R[3 + i] * vCW[3 + j] + R[6 + i] * vCW[6 + j]);
+            float qw = g.qn[0], qx = g.qn[1], qy = g.qn[2], qz = g.qn[3];
+            float vq[4];
+            vq[0] = 2.f * (-qz * vRq[1] + qy * vRq[2] + qz * vRq[3] - qx * vRq[5] - qy * vRq[6] + qx * vRq[7]);
+            vq[1] = 2.f * (qy * vRq[1] + qz * vRq[2] + qy * vRq[3] - 2.f * qx * vRq[4] - qw * vRq[5] + qz * vRq[6] + qw * vRq[7] - 2.f * qx * vRq[8]);
+            vq[2] = 2.f * (-2.f * qy * vRq[0] + qx * vRq[1] + qw * vRq[2] + qx * vRq[3] + qz * vRq[5] - qw * vRq[6] + qz * vRq[7] - 2.f * qy * vRq[8]);
+            vq[3] = 2.f * (-2.f * qz * vRq[0] - qw * vRq[1] + qx * vRq[2] + qw * vRq[3] - 2.f * qz * vRq[4] + qy * vRq[5] + qx * vRq[6] + qy * vRq[7]);
+            float dq = qw * vq[0] + qx * vq[1] + qy * vq[2] + qz * vq[3];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) g_quat[i] += finite_or_zero((vq[i] - g.qn[i] * dq) * g.qinv);
+            g_op += finite_or_zero(v_opac * g.opacity * (1.0f - g.opacity));
+            // ---- SH
+            float d[3];
+#pragma unroll
+            for (int j = 0; j < 3; ++j) d[j] = mean[j] + (R[j] * cam.t[0] + R[3 + j] * cam.t[1] + R[6 + j] * cam.t[2]);
+            float inv = rsqrtf(d[0] * d[0] + d[1] * d[1] + d[2] * d[2]);
+            float nx = d[0] * inv, ny = d[1] * inv, nz = d[2] * inv;
+            float b[kNumSh];
+            sh_basis(nx, ny, nz, b);
+            float vcol[3] = {vc4.x, vc4.y, vc4.z};
+#pragma unroll
+            for (int ch = 0; ch < 3; ++ch) {
+                float raw = kShC0 * sp.features_dc[3 * gid + ch];
+#pragma unroll
+                for (int j = 0; j < kNumSh; ++j) raw += b[j] * sh[3 * j + ch];
+                if (!(raw >= -0.5f)) vcol[ch] = 0.f;
+                vcol[ch] = finite_or_zero(vcol[ch]);
+                g_dc[ch] += kShC0 * vcol[ch];
+            }
+            float w[kNumSh];
+#pragma unroll
+            for (int j = 0; j < kNumSh; ++j) {
+                w[j] = sh[3 * j] * vcol[0] + sh[3 * j + 1] * vcol[1] + sh[3 * j + 2] * vcol[2];
+                shg[3 * j] += b[j] * vcol[0]; shg[3 * j + 1] += b[j] * vcol[1]; shg[3 * j + 2] += b[j] * vcol[2];
+            }
+            float vn[3];
+            sh_basis_vjp(nx, ny, nz, w, vn);
+            float dn = nx * vn[0] + ny * vn[1] + nz * vn[2];
+            g_mean[0] += finite_or_zero((vn[0] - nx * dn) * inv);
+            g_mean[1] += finite_or_zero((vn[1] - ny * dn) * inv);
+            g_mean[2] += finite_or_zero((vn[2] - nz * dn) * inv);
+        }
+        if (accumulate) {
+#pragma unroll
+            for (int j = 0; j < 3; ++j) { gr.means[3 * gid + j] += g_mean[j]; gr.scales[3 * gid + j] += g_scale[j]; gr.features_dc[3 * gid + j] += g_dc[j]; }
+            float4 old = ((float4*)gr.quats)[gid];
+            ((float4*)gr.quats)[gid] = make_float4(old.x + g_quat[0], old.y + g_quat[1], old.z + g_quat[2], old.w + g_quat[3]);
+            gr.opacities[gid] += g_op;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 3; ++j) { gr.means[3 * gid + j] = g_mean[j]; gr.scales[3 * gid + j] = g_scale[j]; gr.features_dc[3 * gid + j] = g_dc[j]; }
+            ((float4*)gr.quats)[gid] = make_float4(g_quat[0], g_quat[1], g_quat[2], g_quat[3]);
+            gr.opacities[gid] = g_op;
+        }
+    }
+    __syncthreads();
+    float* out = gr.features_sh + first * kShPerSplat;
+    if (accumulate) for (int i = threadIdx.x; i < count; i += kProjBlock) out[i] += shg_s[i];
+    else for (int i = threadIdx.x; i < count; i += kProjBlock) out[i] = shg_s[i];
+}
+
+__global__ void screen_unpack_kernel(const SsbScreenRec* __restrict__ s, int64_t m, float* xy, float* depth, float* conic, float* opac, float* rgb) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= m) return;
+    const float4* r = (const float4*)(s + i);
+    float4 a = r[0], b = r[1], c = r[2];
+    if (xy) { xy[2 * i] = a.x; xy[2 * i + 1] = a.y; }
+    if (depth) depth[i] = c.w;
+    if (conic) { conic[3 * i] = b.x; conic[3 * i + 1] = b.y; conic[3 * i + 2] = b.z; }
+    if (opac) opac[i] = b.w;
+    if (rgb) { rgb[3 * i] = c.x; rgb[3 * i + 1] = c.y; rgb[3 * i + 2] = c.z; }
+}
+
+__global__ void screen_pack_kernel(const float* xy, const float* depth, const float* conic, const float* opac, const float* rgb, int64_t m, SsbScreenRec* s) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= m) return;
+    float ca = conic[3 * i], cb = conic[3 * i + 1], cc = conic[3 * i + 2], op = opac[i];
+    // footprint half extents from the conic: cov = conic^-1
+    float hx = 0.f, hy = 0.f;
+    float det = ca * cc - cb * cb;
+    if (op > kAlphaThreshold && det > 0.f) {
+        float e = sqrtf(2.0f * logf(op / kAlphaThreshold)) * 1.0005f;
+        hx = e * sqrtf(cc / det) + 1e-3f;
+        hy = e * sqrtf(ca / det) + 1e-3f;
+    }
+    float4* r = (float4*)(s + i);
+    r[0] = make_float4(xy[2 * i], xy[2 * i + 1], hx, hy);
+    r[1] = make_float4(ca, cb, cc, op);
+    r[2] = make_float4(rgb[3 * i], rgb[3 * i + 1], rgb[3 * i + 2], depth[i]);
+}
+
+static int check_shq(const SsbSplats* splats, const SsbShQuant* shq, SsbShQuant& out) {
+    out = SsbShQuant{nullptr, nullptr, 32, 0, 256};
+    if (shq && shq->packed && (shq->bits == 8 || shq->bits == 16)) {
+        out = *shq;
+        if (out.bounds_stride <= 0) out.bounds_stride = (int64_t)256 * 3 * kNumSh;
+        SSB_REQUIRE(out.bounds != nullptr, "quantised SH needs a bounds table");
+    } else {
+        SSB_REQUIRE(splats->features_sh != nullptr, "features_sh is NULL and no quantised SH was given");
+    }
+    return SSB_OK;
+}
+
+}  // namespace ssb
+
+extern "C" {
+
+int ssb_project_fwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams,
+                    float* d_aabb, float* d_depths, float* d_radii, SsbScreenRec* d_screen, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(splats && cams && d_aabb && d_depths && d_screen, "ssb_project_fwd: NULL argument");
+    SSB_REQUIRE(n >= 0 && cams->count >= 0 && cams->width > 0 && cams->height > 0, "ssb_project_fwd: bad sizes");
+    if (cams->model != SSB_CAMERA_PINHOLE) { set_error("ssb_project_fwd: camera model %d not supported", cams->model); return SSB_ERR_UNSUPPORTED; }
+    SSB_REQUIRE((int64_t)cams->count * n < ((int64_t)1 << 31), "ssb_project_fwd: views * splats must fit int32 flatten ids");
+    SsbShQuant q;
+    int e = check_shq(splats, shq, q);
+    if (e) return e;
+    if (n == 0 || cams->count == 0) return SSB_OK;
+    dim3 grid((unsigned)ceil_div(n, kProjBlock), (unsigned)cams->count);
+    project_fwd_kernel<<<grid, kProjBlock, 0, (cudaStream_t)stream>>>(
+        *splats, q, n, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased,
+        (float4*)d_aabb, d_depths, d_radii, d_screen);
+    SSB_LAUNCHED("project_fwd_kernel");
+    return SSB_OK;
+}
+
+int ssb_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
+                    const SsbScreenRec* d_v_screen, const SsbSplats* grads, int accumulate, void* stream) {
+    return ssb::launch_project_bwd(splats, shq, n, cams, d_aabb, const_cast<SsbScreenRec*>(d_v_screen), grads, accumulate, 0, stream);
+}
+
+}  // extern "C"
+
+namespace ssb {
+
+int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
+                       SsbScreenRec* d_v_screen, const SsbSplats* grads, int accumulate, int clear_v_screen, void* stream) {
+    SSB_REQUIRE(splats && cams && d_aabb && d_v_screen && grads, "ssb_project_bwd: NULL argument");
+    SSB_REQUIRE(grads->means && grads->quats && grads->scales && grads->opacities && grads->features_dc && grads->features_sh,
+                "ssb_project_bwd: every gradient array must be given");
+    if (cams->model != SSB_CAMERA_PINHOLE) { set_error("ssb_project_bwd: camera model %d not supported", cams->model); return SSB_ERR_UNSUPPORTED; }
+    SsbShQuant q;
+    int e = check_shq(splats, shq, q);
+    if (e) return e;
+    if (n == 0) return SSB_OK;
+    project_bwd_kernel<<<(unsigned)ceil_div(n, kProjBlock), kProjBlock, 0, (cudaStream_t)stream>>>(
+        *splats, q, n, cams->count, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased,
+        (const float4*)d_aabb, d_v_screen, *grads, accumulate, clear_v_screen);
+    SSB_LAUNCHED("project_bwd_kernel");
+    return SSB_OK;
+}
+
+}  // namespace ssb
+
+extern "C" {
+
+int ssb_screen_unpack(const SsbScreenRec* d_screen, int64_t m, float* d_xy, float* d_depth, float* d_conic, float* d_opac, float* d_rgb, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(d_screen && m >= 0, "ssb_screen_unpack: bad argument");
+    if (m == 0) return SSB_OK;
+    screen_unpack_kernel<<<(unsigned)ceil_div(m, 256), 256, 0, (cudaStream_t)stream>>>(d_screen, m, d_xy, d_depth, d_conic, d_opac, d_rgb);
+    SSB_LAUNCHED("screen_unpack_kernel");
+    return SSB_OK;
+}
+
+int ssb_screen_pack(const float* d_xy, const float* d_depth, const float* d_conic, const float* d_opac, const float* d_rgb, int64_t m,
+                    SsbScreenRec* d_screen, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(d_xy && d_depth && d_conic && d_opac && d_rgb && d_screen && m >= 0, "ssb_screen_pack: bad argument");
+    if (m == 0) return SSB_OK;
+    screen_pack_kernel<<<(unsigned)ceil_div(m, 256), 256, 0, (cudaStream_t)stream>>>(d_xy, d_depth, d_conic, d_opac, d_rgb, m, d_screen);
+    SSB_LAUNCHED("screen_pack_kernel");
+    return SSB_OK;
+}
+
+}  // extern "C"

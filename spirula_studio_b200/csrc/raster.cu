@@ -1,0 +1,277 @@
+// Tile rasteriser, forward and backward (front-to-back alpha blending of the
+// depth-sorted splat list of each 16x16 tile).  Restates
+// src/kernels/raster/RasterizationEval3DFwd_kernel.cuh:48-313 and
+// src/kernels/raster/RasterizationEval3DBwd_kernel.cuh:48-636 (2D variant) with
+// the fragment math of src/primitives/Primitive3DGS.cuh:250-300.
+//
+// Forward: one 256-thread CTA per tile, one thread per pixel, warp w owning an
+// 8x4 pixel rectangle.  The tile's list is staged 256 records at a time in
+// shared memory (one 48-byte gather per thread); each warp then ballots the
+// staged records against its own rectangle using the record's alpha >= 1/255
+// half extents and walks only the records that can touch it, with a warp-wide
+// early exit once every lane's transmittance is spent.
+//
+// Backward: one warp per 8x8 micro-tile, thread = splat.  The warp scans the
+// tile list back to front, keeps the records whose footprint reaches the
+// micro-tile, and sweeps 32 of them at a time diagonally across the 64 pixels
+// whose running (T, dL/dT) live in shared memory, so each splat's ten gradient
+// components accumulate in registers and leave as three 16-byte vector
+// reductions per (splat, micro-tile) -- no per-pixel atomics.
+#include "ssb_common.cuh"
+
+namespace ssb {
+
+constexpr int kFwdThreads = 256;
+constexpr float kTransmitThreshold = 1e-4f;
+
+__device__ __forceinline__ float eval_alpha(float4 a, float4 b, float px, float py, float& vis, float& sigma, float& dx, float& dy) {
+    dx = a.x - px; dy = a.y - py;
+    sigma = 0.5f * (b.x * dx * dx + b.z * dy * dy) + b.y * dx * dy;
+    vis = __expf(-sigma);
+    float alpha = fminf(0.999f, b.w * vis);
+    return sigma < 0.f ? 0.f : alpha;
+}
+
+__global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
+    const SsbScreenRec* __restrict__ screen, const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ flatten_ids,
+    const int64_t* __restrict__ n_isects_ptr, int I, int W, int H, int tw, int th,
+    float* __restrict__ out_rgb, float* __restrict__ out_depth, float* __restrict__ out_T, int32_t* __restrict__ last_ids) {
+    __shared__ float4 sA[kFwdThreads], sB[kFwdThreads], sC[kFwdThreads];
+    __shared__ uint8_t hits[kFwdThreads / 32][kFwdThreads];
+
+    const int img = blockIdx.z;
+    const int tile_id = blockIdx.y * tw + blockIdx.x;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int rx0 = blockIdx.x * kTile + (w & 1) * 8, ry0 = blockIdx.y * kTile + (w >> 1) * 4;
+    const int j = rx0 + (lane & 7), i = ry0 + (lane >> 3);
+    const float px = (float)j + 0.5f, py = (float)i + 0.5f;
+    const bool inside = (i < H && j < W);
+    bool done = !inside;
+
+    const int32_t* offs = tile_offsets + (int64_t)img * tw * th;
+    const int32_t range_start = offs[tile_id];
+    const int32_t range_end = (img == I - 1 && tile_id == tw * th - 1) ? (int32_t)*n_isects_ptr : offs[tile_id + 1];
+
+    float T = 1.0f;
+    float acc_r = 0.f, acc_g = 0.f, acc_b = 0.f, acc_d = 0.f;
+    int32_t cur_idx = 0;
+    const float fx0 = (float)rx0 + 0.5f, fx1 = (float)rx0 + 7.5f, fy0 = (float)ry0 + 0.5f, fy1 = (float)ry0 + 3.5f;
+
+    for (int32_t batch_start = range_start; batch_start < range_end; batch_start += kFwdThreads) {
+        if (__syncthreads_count(done) >= kFwdThreads) break;
+        const int batch = min(kFwdThreads, range_end - batch_start);
+        if ((int)threadIdx.x < batch) {
+            int32_t g = flatten_ids[batch_start + threadIdx.x];
+            const float4* r = (const float4*)(screen + g);
+            sA[threadIdx.x] = r[0]; sB[threadIdx.x] = r[1]; sC[threadIdx.x] = r[2];
+        }
+        __syncthreads();
+        // records that can reach this warp's 8x4 rectangle, in list order
+        int n_hit = 0;
+        for (int c = 0; c < batch; c += 32) {
+            int e = c + lane;
+            bool hit = false;
+            if (e < batch) {
+                float4 a = sA[e];
+                hit = (a.x + a.z >= fx0) && (a.x - a.z <= fx1) && (a.y + a.w >= fy0) && (a.y - a.w <= fy1);
+            }
+            unsigned bal = __ballot_sync(0xffffffffu, hit);
+            if (hit) hits[w][n_hit + __popc(bal & ((1u << lane) - 1u))] = (uint8_t)e;
+            n_hit += __popc(bal);
+        }
+        __syncwarp();
+        for (int k = 0; k < n_hit; ++k) {
+            if (__all_sync(0xffffffffu, done)) break;
+            const int e = hits[w][k];
+            const float4 a = sA[e], b = sB[e];
+            float vis, sigma, dx, dy;
+            const float alpha = eval_alpha(a, b, px, py, vis, sigma, dx, dy);
+            if (done || alpha <= kAlphaThreshold) continue;
+            const float next_T = T * (1.0f - alpha);
+            if (next_T > kTransmitThreshold) {
+                const float4 c = sC[e];
+                const float wgt = alpha * T;
+                acc_r += c.x * wgt; acc_g += c.y * wgt; acc_b += c.z * wgt; acc_d += c.w * wgt;
+                cur_idx = batch_start + e;
+                T = next_T;
+            } else {
+                done = true;
+            }
+        }
+    }
+    if (inside) {
+        const int64_t pix = ((int64_t)img * H + i) * W + j;
+        out_T[pix] = T;
+        const float invW = 1.0f / fmaxf(1.0f - T, 1e-10f);
+        out_rgb[3 * pix] = acc_r; out_rgb[3 * pix + 1] = acc_g; out_rgb[3 * pix + 2] = acc_b;
+        out_depth[pix] = acc_d * invW;
+        last_ids[pix] = cur_idx;
+    }
+}
+
+constexpr int kBwdWarps = 4;          // one 16x16 tile per CTA, one 8x8 micro-tile per warp
+constexpr int kSurvCap = 256;
+
+__global__ void __launch_bounds__(kBwdWarps * 32) raster_bwd_kernel(
+    const SsbScreenRec* __restrict__ screen, const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ flatten_ids,
+    const int64_t* __restrict__ n_isects_ptr, int I, int W, int H, int tw, int th,
+    const float* __restrict__ render_depth, const float* __restrict__ render_T, const int32_t* __restrict__ last_ids,
+    const float* __restrict__ v_rgb, const float* __restrict__ v_depth, const float* __restrict__ v_T,
+    SsbScreenRec* __restrict__ v_screen) {
+    __shared__ float2 sT[kBwdWarps][64];       // running T and dL/dT
+    __shared__ float4 sV[kBwdWarps][64];       // dL/d(rgb), dL/d(depth sum)
+    __shared__ int32_t sLast[kBwdWarps][64];
+    __shared__ int32_t sSurv[kBwdWarps][kSurvCap];
+
+    const int img = blockIdx.z;
+    const int tile_id = blockIdx.y * tw + blockIdx.x;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int mx0 = blockIdx.x * kTile + (w & 1) * 8, my0 = blockIdx.y * kTile + (w >> 1) * 8;
+    if (mx0 >= W || my0 >= H) return;     // whole micro-tile outside the image (warp-uniform)
+
+    const int32_t* offs = tile_offsets + (int64_t)img * tw * th;
+    const int32_t range_start = offs[tile_id];
+    const int32_t range_end = (img == I - 1 && tile_id == tw * th - 1) ? (int32_t)*n_isects_ptr : offs[tile_id + 1];
+
+    int32_t max_last = -1;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int p = h * 32 + lane;
+        const int x = mx0 + (p & 7), y = my0 + (p >> 3);
+        const bool inside = x < W && y < H;
+        int32_t last = -1;
+        float T1 = 0.f, vT1 = 0.f;
+        float4 vc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (inside) {
+            const int64_t pix = ((int64_t)img * H + y) * W + x;
+            last = last_ids[pix];
+            T1 = render_T[pix];
+            vT1 = v_T ? v_T[pix] : 0.f;
+            vc = make_float4(v_rgb[3 * pix], v_rgb[3 * pix + 1], v_rgb[3 * pix + 2], v_depth ? v_depth[pix] : 0.f);
+            const float inv_alpha = 1.0f / fmaxf(1.0f - T1, 1e-10f);
+            vT1 += render_depth[pix] * vc.w * inv_alpha;
+            vc.w *= inv_alpha;
+        }
+        sT[w][p] = make_float2(T1, vT1);
+        sV[w][p] = vc;
+        sLast[w][p] = last;
+        max_last = max(max_last, last);
+    }
+    max_last = __reduce_max_sync(0xffffffffu, max_last);
+    __syncwarp();
+
+    const float fx0 = (float)mx0 + 0.5f, fx1 = (float)mx0 + 7.5f, fy0 = (float)my0 + 0.5f, fy1 = (float)my0 + 7.5f;
+
+    for (int32_t scan = min(range_end - 1, max_last); scan >= range_start;) {
+        // ---- collect survivors, back to front
+        int count = 0;
+        while (scan >= range_start && count <= kSurvCap - 32) {
+            const int32_t gi = scan - lane;
+            bool ok = false;
+            if (gi >= range_start) {
+                const int32_t g = flatten_ids[gi];
+                const float4 a = *(const float4*)(screen + g);
+                ok = (a.x + a.z >= fx0) && (a.x - a.z <= fx1) && (a.y + a.w >= fy0) && (a.y - a.w <= fy1);
+            }
+            const unsigned bal = __ballot_sync(0xffffffffu, ok);
+            if (ok) sSurv[w][count + __popc(bal & ((1u << lane) - 1u))] = gi;
+            count += __popc(bal);
+            scan -= 32;
+        }
+        __syncwarp();
+        // ---- sweep them 32 at a time
+        for (int base = 0; base < count; base += 32) {
+            const int bs = min(32, count - base);
+            const bool active = lane < bs;
+            int32_t sidx = -1, g = 0;
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a, c = a;
+            if (active) {
+                sidx = sSurv[w][base + lane];
+                g = flatten_ids[sidx];
+                const float4* r = (const float4*)(screen + g);
+                a = r[0]; b = r[1]; c = r[2];
+            }
+            float gx = 0.f, gy = 0.f, gca = 0.f, gcb = 0.f, gcc = 0.f, gop = 0.f, gr = 0.f, gg = 0.f, gb = 0.f, gd = 0.f;
+            const int steps = bs + 63;
+            for (int t = 0; t < steps; ++t) {
+                const int p = t - lane;
+                if (active && p >= 0 && p < 64 && sidx <= sLast[w][p]) {
+                    const float px = (float)(mx0 + (p & 7)) + 0.5f, py = (float)(my0 + (p >> 3)) + 0.5f;
+                    float vis, sigma, dx, dy;
+                    const float alpha = eval_alpha(a, b, px, py, vis, sigma, dx, dy);
+                    if (alpha > kAlphaThreshold) {
+                        const float2 tt = sT[w][p];
+                        const float4 vc = sV[w][p];
+                        const float ra = 1.0f / (1.0f - alpha);
+                        const float T0 = tt.x * ra;
+                        const float cdot = c.x * vc.x + c.y * vc.y + c.z * vc.z + c.w * vc.w;
+                        const float v_alpha = T0 * cdot - tt.y * T0;
+                        const float wgt = alpha * T0;
+                        const float v_T0 = alpha * cdot + tt.y * (1.0f - alpha);
+                        if (sigma >= 0.f && b.w * vis <= 0.999f) {
+                            const float v_sigma = -b.w * vis * v_alpha;
+                            gca += 0.5f * v_sigma * dx * dx;
+                            gcb += v_sigma * dx * dy;
+                            gcc += 0.5f * v_sigma * dy * dy;
+                            gx += v_sigma * (b.x * dx + b.y * dy);
+                            gy += v_sigma * (b.y * dx + b.z * dy);
+                            gop += vis * v_alpha;
+                        }
+                        gr += vc.x * wgt; gg += vc.y * wgt; gb += vc.z * wgt; gd += vc.w * wgt;
+                        sT[w][p] = make_float2(T0, v_T0);
+                    }
+                }
+                __syncwarp();
+            }
+            if (active) {
+                // non-finite components are dropped, as the reference's atomics do
+                // (src/core/Common.cuh:792-856)
+                auto fz = [](float v) { return isfinite(v) ? v : 0.0f; };
+                float* out = (float*)(v_screen + g);
+                if (gx != 0.f || gy != 0.f) red_add_v4(out, fz(gx), fz(gy), 0.f, 0.f);
+                if (gca != 0.f || gcb != 0.f || gcc != 0.f || gop != 0.f) red_add_v4(out + 4, fz(gca), fz(gcb), fz(gcc), fz(gop));
+                if (gr != 0.f || gg != 0.f || gb != 0.f || gd != 0.f) red_add_v4(out + 8, fz(gr), fz(gg), fz(gb), fz(gd));
+            }
+        }
+        __syncwarp();
+    }
+}
+
+}  // namespace ssb
+
+extern "C" {
+
+int ssb_raster_fwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids,
+                   const int64_t* d_n_isects, int32_t n_images, int32_t width, int32_t height,
+                   float* d_rgb, float* d_depth, float* d_T, int32_t* d_last_ids, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(d_screen && d_tile_offsets && d_flatten_ids && d_n_isects && d_rgb && d_depth && d_T && d_last_ids, "ssb_raster_fwd: NULL argument");
+    SSB_REQUIRE(n_images >= 0 && width > 0 && height > 0, "ssb_raster_fwd: bad sizes");
+    if (n_images == 0) return SSB_OK;
+    int tw = (width + kTile - 1) / kTile, th = (height + kTile - 1) / kTile;
+    dim3 grid(tw, th, n_images);
+    raster_fwd_kernel<<<grid, kFwdThreads, 0, (cudaStream_t)stream>>>(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height,
+                                                                    tw, th, d_rgb, d_depth, d_T, d_last_ids);
+    SSB_LAUNCHED("raster_fwd_kernel");
+    return SSB_OK;
+}
+
+int ssb_raster_bwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids,
+                   const int64_t* d_n_isects, int32_t n_images, int32_t width, int32_t height,
+                   const float* d_render_depth, const float* d_T, const int32_t* d_last_ids,
+                   const float* d_v_rgb, const float* d_v_depth, const float* d_v_T,
+                   SsbScreenRec* d_v_screen, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(d_screen && d_tile_offsets && d_flatten_ids && d_n_isects && d_render_depth && d_T && d_last_ids && d_v_rgb && d_v_screen,
+                "ssb_raster_bwd: NULL argument");
+    SSB_REQUIRE(n_images >= 0 && width > 0 && height > 0, "ssb_raster_bwd: bad sizes");
+    if (n_images == 0) return SSB_OK;
+    int tw = (width + kTile - 1) / kTile, th = (height + kTile - 1) / kTile;
+    dim3 grid(tw, th, n_images);
+    raster_bwd_kernel<<<grid, kBwdWarps * 32, 0, (cudaStream_t)stream>>>(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height,
+                                                                       tw, th, d_render_depth, d_T, d_last_ids, d_v_rgb, d_v_depth, d_v_T, d_v_screen);
+    SSB_LAUNCHED("raster_bwd_kernel");
+    return SSB_OK;
+}
+
+}  // extern "C"

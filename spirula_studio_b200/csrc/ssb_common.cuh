@@ -1,0 +1,83 @@
+// Shared definitions for the kernels of libssb_b200.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <math.h>
+
+#include "../../include/ssb.h"
+
+namespace ssb {
+
+constexpr float kAlphaThreshold = 1.0f / 255.0f;
+constexpr int kTile = SSB_TILE;
+constexpr int kNumSh = SSB_NUM_SH;
+constexpr float kShC0 = 0.2820947917738781f;
+
+// Thread-local error text and the process-wide launch counter.
+void set_error(const char* fmt, ...);
+void count_launch(int n = 1);
+int check_cuda(cudaError_t e, const char* what);
+
+#define SSB_REQUIRE(cond, ...)                      \
+    do {                                            \
+        if (!(cond)) {                              \
+            ::ssb::set_error(__VA_ARGS__);          \
+            return SSB_ERR_INVALID_ARGUMENT;        \
+        }                                           \
+    } while (0)
+
+#define SSB_CUDA(expr)                                              \
+    do {                                                            \
+        int _e = ::ssb::check_cuda((expr), #expr);                  \
+        if (_e != SSB_OK) return _e;                                \
+    } while (0)
+
+// Call after every kernel launch: counts it and turns a launch error into a status.
+#define SSB_LAUNCHED(name)                                          \
+    do {                                                            \
+        ::ssb::count_launch();                                      \
+        int _e = ::ssb::check_cuda(cudaGetLastError(), name);       \
+        if (_e != SSB_OK) return _e;                                \
+    } while (0)
+
+// launchers shared between translation units
+int launch_loss(const float* d_render, const float* d_gt, int B, int H, int W, float w_l1, float w_ssim,
+                float* d_v_render, float* d_losses, cudaStream_t st);
+int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
+                       SsbScreenRec* d_v_screen, const SsbSplats* grads, int accumulate, int clear_v_screen, void* stream);
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline int64_t align_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+
+struct CamDev {
+    float R[9];
+    float t[3];
+    float fx, fy, cx, cy;
+};
+
+__device__ __forceinline__ CamDev load_cam(const float* __restrict__ viewmats, const float* __restrict__ intrins, int cid) {
+    const float* m = viewmats + 16 * cid;
+    CamDev c;
+    c.R[0] = m[0]; c.R[1] = m[1]; c.R[2] = m[2];
+    c.R[3] = m[4]; c.R[4] = m[5]; c.R[5] = m[6];
+    c.R[6] = m[8]; c.R[7] = m[9]; c.R[8] = m[10];
+    c.t[0] = m[3]; c.t[1] = m[7]; c.t[2] = m[11];
+    c.fx = intrins[4 * cid]; c.fy = intrins[4 * cid + 1];
+    c.cx = intrins[4 * cid + 2]; c.cy = intrins[4 * cid + 3];
+    return c;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// 16-byte vector reduction into global memory (sm_90+).
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+}  // namespace ssb

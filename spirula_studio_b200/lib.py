@@ -1,0 +1,148 @@
+"""ctypes binding of libssb_b200.so (the C ABI declared in include/ssb.h).
+
+Only plain pointers and sizes cross the boundary.  torch is used by callers for
+device memory and streams; nothing here imports it.  Loading fails loudly when
+the shared library has not been built: there is no CPU fallback.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libssb_b200.so")
+
+SSB_OK = 0
+SSB_ERR_INVALID_ARGUMENT = -1
+SSB_ERR_CUDA = -2
+SSB_ERR_CAPACITY = -3
+SSB_ERR_OUT_OF_MEMORY = -4
+SSB_ERR_UNSUPPORTED = -5
+
+CAMERA_PINHOLE, CAMERA_FISHEYE, CAMERA_EQUISOLID, CAMERA_EQUIRECT = 0, 1, 2, 3
+NUM_SH = 15
+TILE = 16
+SCREEN_REC_FLOATS = 12
+
+
+class SsbError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__(f"ssb status {status}: {message}")
+        self.status = status
+
+
+class SsbSplats(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("means", "quats", "scales", "opacities", "features_dc", "features_sh")]
+
+
+class SsbShQuant(C.Structure):
+    _fields_ = [("packed", C.c_void_p), ("bounds", C.c_void_p), ("bits", C.c_int32), ("reserved", C.c_int32),
+                ("bounds_stride", C.c_int64)]
+
+
+class SsbCameras(C.Structure):
+    _fields_ = [("d_viewmats", C.c_void_p), ("d_intrins", C.c_void_p), ("count", C.c_int32), ("width", C.c_int32),
+                ("height", C.c_int32), ("model", C.c_int32), ("antialiased", C.c_int32)]
+
+
+class SsbAdamConfig(C.Structure):
+    _fields_ = [("lr_means", C.c_float), ("lr_quats", C.c_float), ("lr_scales", C.c_float), ("lr_opacities", C.c_float),
+                ("lr_features_dc", C.c_float), ("lr_features_sh", C.c_float), ("sh_reg_weight", C.c_float),
+                ("grad_scale", C.c_float), ("step", C.c_int32), ("zero_grad", C.c_int32)]
+
+
+class SsbStepConfig(C.Structure):
+    _fields_ = [("n_splats", C.c_int64), ("width", C.c_int32), ("height", C.c_int32), ("camera_model", C.c_int32),
+                ("antialiased", C.c_int32), ("isect_capacity", C.c_int64), ("w_l1", C.c_float), ("w_ssim", C.c_float)]
+
+
+_P = C.c_void_p
+_I32, _I64, _F = C.c_int32, C.c_int64, C.c_float
+
+# name -> (restype, argtypes); every symbol include/ssb.h declares
+SIGNATURES = {
+    "ssb_last_error_string": (C.c_char_p, []),
+    "ssb_version_string": (C.c_char_p, []),
+    "ssb_project_fwd": (C.c_int, [_P, _P, _I64, _P, _P, _P, _P, _P, _P]),
+    "ssb_project_bwd": (C.c_int, [_P, _P, _I64, _P, _P, _P, _P, C.c_int, _P]),
+    "ssb_screen_unpack": (C.c_int, [_P, _I64, _P, _P, _P, _P, _P, _P]),
+    "ssb_screen_pack": (C.c_int, [_P, _P, _P, _P, _P, _I64, _P, _P]),
+    "ssb_tile_keys_workspace_bytes": (_I64, [_I64]),
+    "ssb_tile_keys": (C.c_int, [_P, _P, _P, _I64, _I64, _I32, _I32, _P, _I64, _P, _P, _P, _P, _I64, _P, _P, _P]),
+    "ssb_sort_workspace_bytes": (_I64, [_I64]),
+    "ssb_sort_pairs_u64": (C.c_int, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _P, _I64, _P, _P]),
+    "ssb_tile_n_bits": (_I32, [_I64]),
+    "ssb_tile_ranges": (C.c_int, [_P, _P, _I64, _I64, _P, _P]),
+    "ssb_raster_fwd": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P]),
+    "ssb_raster_bwd": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "ssb_loss_l1_ssim_fwdbwd": (C.c_int, [_P, _P, _I32, _I32, _I32, _F, _F, _P, _P, _P]),
+    "ssb_adam_step": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _P, _P]),
+    "ssb_adam_step_sh_quantized": (C.c_int, [_P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _P, _P]),
+    "ssb_quant_encode": (C.c_int, [_P, _I64, _I32, _P, _P, _P]),
+    "ssb_quant_decode": (C.c_int, [_P, _P, _I64, _I32, _P, _P]),
+    "ssb_step_create": (C.c_int, [_P, _P]),
+    "ssb_step_destroy": (None, [_P]),
+    "ssb_step_device_bytes": (_I64, [_P]),
+    "ssb_step_views": (C.c_int, [_P, _P, _P, _P, _P, _P, _I32, _P, C.c_int, _P, _P]),
+    "ssb_step_last_isects": (C.c_int, [_P, _P, _P]),
+    "ssb_step_peek": (C.c_int, [_P, _P, _P, _P, _P, _P, _P]),
+    "ssb_launch_count": (_I64, []),
+}
+
+_lib = None
+
+
+def load():
+    """Returns the loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `make -C {os.path.join(_HERE, 'csrc')}` "
+            "(or __graft_entry__.build()). There is no CPU fallback.")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError = a declared symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(status):
+    if status != SSB_OK:
+        raise SsbError(status, load().ssb_last_error_string().decode("utf-8", "replace"))
+
+
+def ptr(t):
+    """Device (or host) address of a tensor-like object, or None."""
+    if t is None:
+        return None
+    return C.c_void_p(t.data_ptr())
+
+
+def splats_struct(d):
+    """d: mapping with the six arrays (tensors or None)."""
+    s = SsbSplats()
+    for n, _ in SsbSplats._fields_:
+        t = d.get(n)
+        setattr(s, n, t.data_ptr() if t is not None else None)
+    return s
+
+
+def shq_struct(packed=None, bounds=None, bits=32, bounds_stride=256):
+    q = SsbShQuant()
+    q.packed = packed.data_ptr() if packed is not None else None
+    q.bounds = bounds.data_ptr() if bounds is not None else None
+    q.bits = bits
+    q.reserved = 0
+    q.bounds_stride = bounds_stride
+    return q
+
+
+def cameras_struct(viewmats, intrins, width, height, model=CAMERA_PINHOLE, antialiased=0, count=None):
+    c = SsbCameras()
+    c.d_viewmats = viewmats.data_ptr()
+    c.d_intrins = intrins.data_ptr()
+    c.count = int(viewmats.shape[0]) if count is None else count
+    c.width, c.height, c.model, c.antialiased = width, height, model, antialiased
+    return c

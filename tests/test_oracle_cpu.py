@@ -1,0 +1,215 @@
+"""CPU checks of the oracle itself: its backward passes against central finite
+differences of its forward passes, and its integer stages against brute-force
+definitions (numpy stable argsort, searchsorted)."""
+import numpy as np
+import pytest
+
+from spirula_studio_b200 import scenes
+
+
+def small_scene(n=400, w=96, h=64, seed=1, scale_mu=-2.6):
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=n, width=w, height=h)
+    cfg.log_scale_mu = scale_mu
+    cfg.mean_extent = 0.6
+    sp = scenes.make_splats(cfg, seed=seed)
+    vm, K = scenes.make_cameras(cfg)
+    return cfg, sp, vm, K
+
+
+def test_det_logf_matches_log(oracle):
+    lib = oracle.load()
+    xs = np.concatenate([np.linspace(1.0, 300.0, 4000), np.logspace(-3, 6, 2000)]).astype(np.float32)
+    got = np.array([lib.oracle_det_logf(float(x)) for x in xs], dtype=np.float64)
+    ref = np.log(xs.astype(np.float64))
+    assert np.max(np.abs(got - ref) / np.maximum(1.0, np.abs(ref))) < 3e-7
+
+
+def test_sort_is_stable_on_bit_range(oracle):
+    rng = np.random.default_rng(0)
+    n = 5000
+    keys = rng.integers(0, 1 << 45, size=n, dtype=np.int64)
+    keys[::7] = keys[0]  # many ties
+    vals = np.arange(n, dtype=np.int32)
+    for b0, b1 in ((0, 45), (0, 32), (8, 40), (32, 45), (0, 64)):
+        ko, vo = oracle.sort_pairs(keys, vals, b0, b1)
+        mask = (~np.uint64(0)) if b1 - b0 >= 64 else np.uint64(((1 << (b1 - b0)) - 1) << b0)
+        order = np.argsort(keys.astype(np.uint64) & mask, kind="stable")
+        assert np.array_equal(vo, vals[order]) and np.array_equal(ko, keys[order])
+
+
+def test_tile_offsets_definition(oracle):
+    rng = np.random.default_rng(1)
+    n_tiles = 97
+    tiles = np.sort(rng.integers(3, 90, size=2000)).astype(np.int64)
+    keys = (tiles << 32) | rng.integers(0, 1 << 32, size=tiles.size, dtype=np.int64)
+    offs = oracle.tile_offsets(keys, n_tiles)
+    assert np.array_equal(offs, np.searchsorted(tiles, np.arange(n_tiles), side="left").astype(np.int32))
+    assert np.array_equal(oracle.tile_offsets(keys[:0], n_tiles), np.zeros(n_tiles, np.int32))
+
+
+def test_tile_keys_cover_footprint(oracle):
+    """Every pixel where a splat's alpha exceeds 1/255 lies in a tile the splat was binned to."""
+    cfg, sp, vm, K = small_scene(n=200)
+    W, H = cfg.width, cfg.height
+    proj = oracle.project_fwd(sp, vm, K, W, H)
+    counts, cum, keys, vals = oracle.tile_keys(proj, cfg.n_splats, W, H)
+    assert cum[-1] == keys.size == counts.sum() and np.all(np.diff(cum) == counts[1:])
+    tw, th = oracle.tile_grid(W, H)
+    binned = set(zip(vals.tolist(), (keys >> 32).tolist()))
+    ys, xs = np.mgrid[0:H, 0:W]
+    px, py = xs + 0.5, ys + 0.5
+    for g in range(cfg.n_splats):
+        if counts[g] == 0:
+            continue
+        dx, dy = proj["xy"][g, 0] - px, proj["xy"][g, 1] - py
+        a, b, c = proj["conic"][g]
+        sigma = 0.5 * (a * dx * dx + c * dy * dy) + b * dx * dy
+        alpha = np.minimum(0.999, proj["opac"][g] * np.exp(-sigma))
+        hit = (alpha > 1.0 / 255.0 + 1e-6) & (sigma >= 0)
+        for t in np.unique((ys[hit] // 16) * tw + xs[hit] // 16):
+            assert (g, int(t)) in binned
+
+
+def _proj_scalar(oracle, sp, vm, K, W, H, v):
+    o = oracle.project_fwd(sp, vm, K, W, H)
+    keep = o["aabb"][:, 2] > o["aabb"][:, 0]
+    tot = 0.0
+    for name, key in (("xy", "v_xy"), ("depth", "v_depth"), ("conic", "v_conic"), ("opac", "v_opac"), ("rgb", "v_rgb")):
+        a = o[name].astype(np.float64).reshape(len(keep), -1)[keep]
+        tot += float((a * v[key].astype(np.float64).reshape(len(keep), -1)[keep]).sum())
+    return tot, keep
+
+
+@pytest.mark.parametrize("attr", ["means", "quats", "scales", "opacities", "features_dc", "features_sh"])
+def test_projection_backward_matches_finite_differences(oracle, attr):
+    cfg, sp, vm, K = small_scene(n=64, w=200, h=160, seed=3)
+    sp["means"] *= 0.5
+    W, H = cfg.width, cfg.height
+    rng = np.random.default_rng(5)
+    n = cfg.n_splats
+    v = dict(v_xy=rng.normal(size=(n, 2)), v_depth=rng.normal(size=n), v_conic=rng.normal(size=(n, 3)) * 0.1,
+             v_opac=rng.normal(size=n), v_rgb=rng.normal(size=(n, 3)))
+    v = {k: x.astype(np.float32) for k, x in v.items()}
+    base = oracle.project_fwd(sp, vm, K, W, H)
+    g = oracle.project_bwd(sp, vm, K, W, H, base["aabb"], v)
+    d = rng.normal(size=sp[attr].shape).astype(np.float32)
+    eps = 2e-3
+    plus = {k: x.copy() for k, x in sp.items()}
+    minus = {k: x.copy() for k, x in sp.items()}
+    plus[attr] = sp[attr] + eps * d
+    minus[attr] = sp[attr] - eps * d
+    lp, kp = _proj_scalar(oracle, plus, vm, K, W, H, v)
+    lm, km = _proj_scalar(oracle, minus, vm, K, W, H, v)
+    assert np.array_equal(kp, km)
+    fd = (lp - lm) / (2 * eps)
+    an = float((g[attr].astype(np.float64) * d).sum())
+    assert abs(fd - an) <= 2e-2 * max(1.0, abs(fd)), (fd, an)
+
+
+def _frozen_blend(proj64, order, mask, W, H, v_rgb, v_depth):
+    """float64 blend of one 16x16 tile with the contributing (splat, pixel) set held fixed."""
+    ys, xs = np.mgrid[0:H, 0:W]
+    px, py = (xs + 0.5).reshape(-1), (ys + 0.5).reshape(-1)
+    T = np.ones(px.size)
+    C = np.zeros((px.size, 3))
+    D = np.zeros(px.size)
+    for k, g in enumerate(order):
+        dx, dy = proj64["xy"][g, 0] - px, proj64["xy"][g, 1] - py
+        a, b, c = proj64["conic"][g]
+        sigma = 0.5 * (a * dx * dx + c * dy * dy) + b * dx * dy
+        alpha = np.minimum(0.999, proj64["opac"][g] * np.exp(-sigma)) * mask[k]
+        w = alpha * T
+        C += w[:, None] * proj64["rgb"][g][None, :]
+        D += w * proj64["depth"][g]
+        T = T * (1.0 - alpha)
+    depth = D / np.maximum(1.0 - T, 1e-10)
+    return float((C * v_rgb).sum() + (depth * v_depth).sum())
+
+
+@pytest.mark.parametrize("field", ["xy", "conic", "opac", "rgb", "depth"])
+def test_raster_backward_matches_finite_differences(oracle, field):
+    """The render is only piecewise smooth (alpha threshold, early stop), so the set of
+    contributing (splat, pixel) pairs is frozen at the base point and the smooth function
+    that remains is differentiated numerically in float64."""
+    cfg, sp, vm, K = small_scene(n=60, w=16, h=16, seed=7, scale_mu=-2.0)
+    cfg.fx = cfg.fy = 40.0
+    K[:, 0] = K[:, 1] = 40.0
+    W, H = cfg.width, cfg.height
+    ch = oracle.forward_chain(sp, vm, K, W, H)
+    proj, offs, vals, render = ch["proj"], ch["offsets"], ch["sorted_vals"], ch["render"]
+    assert vals.size > 20
+    rng = np.random.default_rng(11)
+    v_rgb = rng.normal(size=(H * W, 3)).astype(np.float32)
+    v_depth = (rng.normal(size=H * W) * 0.1).astype(np.float32)
+    g = oracle.raster_bwd(proj, offs, vals, 1, cfg.n_splats, W, H, render, v_rgb, v_depth=v_depth)
+    # contributing set at the base point
+    ys, xs = np.mgrid[0:H, 0:W]
+    px, py = (xs + 0.5).reshape(-1), (ys + 0.5).reshape(-1)
+    mask = np.zeros((vals.size, H * W))
+    for k, s_id in enumerate(vals):
+        dx, dy = proj["xy"][s_id, 0] - px, proj["xy"][s_id, 1] - py
+        a, b, c = proj["conic"][s_id]
+        sigma = 0.5 * (a * dx * dx + c * dy * dy) + b * dx * dy
+        alpha = np.minimum(0.999, proj["opac"][s_id] * np.exp(-sigma))
+        mask[k] = (alpha > 1.0 / 255.0) & (sigma >= 0) & (k <= render["last_ids"]) & (alpha < 0.998)
+    p64 = {k: x.astype(np.float64) for k, x in proj.items() if x is not None}
+    d = rng.normal(size=proj[field].shape)
+    if field == "conic":
+        d *= 0.01
+    eps = 1e-5
+    hi = dict(p64); lo = dict(p64)
+    hi[field] = p64[field] + eps * d
+    lo[field] = p64[field] - eps * d
+    fd = (_frozen_blend(hi, vals, mask, W, H, v_rgb, v_depth) - _frozen_blend(lo, vals, mask, W, H, v_rgb, v_depth)) / (2 * eps)
+    an = float((g["v_" + field].astype(np.float64) * d).sum())
+    assert abs(fd - an) <= 2e-3 * max(1.0, abs(fd)), (fd, an)
+
+
+def test_loss_gradient_matches_finite_differences(oracle):
+    rng = np.random.default_rng(2)
+    H, W = 40, 56
+    render = rng.random((H * W, 3), dtype=np.float32)
+    gt = rng.random((H * W, 3), dtype=np.float32)
+    v, losses = oracle.loss_l1_ssim(render, gt, 1, H, W, 0.8, 0.2)
+    assert 0.0 < losses[1] < 1.0 and abs(losses[2] - (0.8 * losses[0] + 0.2 * (1 - losses[1]))) < 1e-6
+    # along the gradient itself, so the L1 kinks (|r-g| < eps) stay a small part of the total
+    d = (v / np.abs(v).max()).astype(np.float32)
+    eps = 1e-3
+    lp = oracle.loss_l1_ssim(render + eps * d, gt, 1, H, W)[1][2]
+    lm = oracle.loss_l1_ssim(render - eps * d, gt, 1, H, W)[1][2]
+    fd = (float(lp) - float(lm)) / (2 * eps)
+    an = float((v.astype(np.float64) * d).sum())
+    assert abs(fd - an) <= 1e-2 * max(abs(fd), 1e-3), (fd, an)
+
+
+def test_ssim_of_identical_images_is_one(oracle):
+    rng = np.random.default_rng(3)
+    H, W = 33, 47
+    img = rng.random((H * W, 3), dtype=np.float32)
+    v, losses = oracle.loss_l1_ssim(img, img.copy(), 1, H, W)
+    assert abs(losses[1] - 1.0) < 1e-5 and losses[0] == 0.0
+    assert np.max(np.abs(v)) < 1e-6
+
+
+def test_quant_codec_roundtrip(oracle):
+    rng = np.random.default_rng(4)
+    x = rng.normal(0, 0.05, size=45 * 300).astype(np.float32)
+    for bits in (8, 16):
+        packed, bounds = oracle.quant_encode(x, bits)
+        y = oracle.quant_decode(packed, bounds, x.size, bits)
+        b = bounds.reshape(-1, 2)
+        step = np.repeat((b[:, 1] - b[:, 0]) / ((1 << bits) - 1), 256)[: x.size]
+        assert np.all(np.abs(x - y) <= 0.5 * step + 1e-7)
+
+
+def test_adam_first_step_moves_by_lr(oracle):
+    """With zero moments the first bias-corrected Adam step is lr * sign(g)."""
+    rng = np.random.default_rng(6)
+    n = 1000
+    p = rng.normal(size=n).astype(np.float32)
+    g = rng.normal(size=n).astype(np.float32)
+    p0 = p.copy()
+    m1, m2 = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    oracle.adam_plain(p, g, m1, m2, 1, 2.5e-3)
+    assert np.allclose(p0 - p, 2.5e-3 * np.sign(g), rtol=1e-4, atol=1e-9)
+    assert np.allclose(m1, 0.1 * g, rtol=1e-6) and np.allclose(m2, 0.001 * g * g, rtol=1e-4)

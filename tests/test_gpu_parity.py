@@ -1,0 +1,225 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle on the same
+seeded inputs.  Integer stages are compared bit for bit given the oracle's
+floating-point inputs; floating-point stages use the reference parity tools'
+tolerance model |d| <= atol + rtol*|ref| with a capped violation fraction
+(src/backend/tests/projection_parity.cpp:347-364, render_parity.cpp:342-357,
+raster_bwd_parity.cpp:360-368), tightened where the north-star states a bound:
+images 1e-4 max abs, gradients and post-Adam parameters 1e-3 relative."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from spirula_studio_b200 import lib as L, scenes  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return L.load()
+
+
+@pytest.fixture(scope="module")
+def U():
+    from tests import gpu_util
+    return gpu_util
+
+
+def scene(n=20000, w=320, h=240, views=2, seed=scenes.SPLAT_SEED, base="plumbing_50k", scale_mu=None, extent=None):
+    cfg = scenes.scaled(scenes.CONFIGS[base], n_splats=n, width=w, height=h, n_views=views)
+    if scale_mu is not None:
+        cfg.log_scale_mu = scale_mu
+    if extent is not None:
+        cfg.mean_extent = extent
+    if views > 1:
+        cfg.rig, cfg.rig_radius = "ring", 3.0
+    sp = scenes.make_splats(cfg, seed=seed)
+    vm, K = scenes.make_cameras(cfg)
+    return cfg, sp, vm, K
+
+
+# ---------------------------------------------------------------- projection
+@pytest.mark.parametrize("views", [1, 2])
+def test_projection_forward(lib, U, oracle, views):
+    cfg, sp, vm, K = scene(views=views, scale_mu=-3.5)
+    W, H, n = cfg.width, cfg.height, cfg.n_splats
+    ref = oracle.project_fwd(sp, vm, K, W, H)
+    got = U.project_fwd(lib, U.splats_dev(sp), vm, K, W, H)
+    aabb = got["aabb"].cpu().numpy()
+    keep_ref = ref["aabb"][:, 2] > ref["aabb"][:, 0]
+    keep_got = aabb[:, 2] > aabb[:, 0]
+    assert keep_ref.sum() > 0.3 * keep_ref.size
+    assert (keep_ref != keep_got).mean() <= 2e-4            # borderline culls may flip
+    both = keep_ref & keep_got
+    scr = U.unpack_screen(lib, got["rec"], views * n)
+    assert U.close_frac(aabb[both], ref["aabb"][both], 5e-3, 5e-4) <= 2e-4
+    assert U.close_frac(got["depths"].cpu().numpy()[both], ref["depths"][both], 1e-5, 1e-5) == 0.0
+    for k, (atol, rtol) in dict(xy=(2e-3, 1e-5), depth=(1e-5, 1e-5), conic=(1e-5, 5e-4), opac=(1e-6, 1e-5), rgb=(2e-5, 1e-5)).items():
+        assert U.close_frac(scr[k][both], ref[k][both], atol, rtol) <= 2e-4, k
+    assert U.close_frac(got["radii"].cpu().numpy(), ref["radii"], 1e-6, 1e-4) <= 2e-4
+    # visible counts
+    assert abs(int(keep_got.sum()) - int(keep_ref.sum())) <= max(2, int(2e-4 * keep_ref.size))
+
+
+def test_projection_forward_quantized_sh(lib, U, oracle):
+    cfg, sp, vm, K = scene(n=8000, views=1, scale_mu=-3.5)
+    W, H, n = cfg.width, cfg.height, cfg.n_splats
+    for bits in (16, 8):
+        packed, bounds = oracle.quant_encode(sp["features_sh"], bits)
+        ref = oracle.project_fwd(sp, vm, K, W, H, shq=dict(packed=packed, bounds=bounds, bits=bits, bounds_stride=256))
+        d_packed, d_bounds = U.dev(packed), U.dev(bounds)
+        shq = L.shq_struct(d_packed, d_bounds, bits, 256)
+        got = U.project_fwd(lib, U.splats_dev(sp), vm, K, W, H, shq=shq)
+        keep = (ref["aabb"][:, 2] > ref["aabb"][:, 0]) & (got["aabb"].cpu().numpy()[:, 2] > got["aabb"].cpu().numpy()[:, 0])
+        scr = U.unpack_screen(lib, got["rec"], n)
+        assert U.close_frac(scr["rgb"][keep], ref["rgb"][keep], 2e-5, 1e-5) <= 2e-4
+        # and the codec itself: GPU encode gives the same codes as the oracle (+-1 at rounding ties)
+        gp = torch.zeros_like(d_packed)
+        gb = torch.zeros_like(d_bounds)
+        L.check(lib.ssb_quant_encode(L.ptr(U.dev(sp["features_sh"].reshape(-1))), n * 45, bits, L.ptr(gp), L.ptr(gb), None))
+        torch.cuda.synchronize()
+        assert np.array_equal(gb.cpu().numpy(), bounds)
+        view = np.uint16 if bits == 16 else np.uint8
+        diff = np.abs(gp.cpu().numpy().view(view).astype(np.int64) - packed.view(view).astype(np.int64))
+        assert diff.max() <= 1 and (diff > 0).mean() < 1e-3
+
+
+def test_projection_backward(lib, U, oracle):
+    cfg, sp, vm, K = scene(n=12000, views=2, scale_mu=-3.5)
+    W, H, n = cfg.width, cfg.height, cfg.n_splats
+    ref_f = oracle.project_fwd(sp, vm, K, W, H)
+    rng = np.random.default_rng(3)
+    m = 2 * n
+    v = dict(v_xy=rng.normal(size=(m, 2)), v_depth=rng.normal(size=m), v_conic=rng.normal(size=(m, 3)) * 0.05, v_opac=rng.normal(size=m),
+             v_rgb=rng.normal(size=(m, 3)))
+    v = {k: x.astype(np.float32) for k, x in v.items()}
+    ref = oracle.project_bwd(sp, vm, K, W, H, ref_f["aabb"], v)
+    spd = U.splats_dev(sp)
+    grads = {k: torch.full_like(t, 7.0) for k, t in spd.items()}      # overwritten when accumulate == 0
+    s, g = L.splats_struct(spd), L.splats_struct(grads)
+    d_vm, d_K, d_aabb = U.dev(vm), U.dev(K), U.dev(ref_f["aabb"])
+    cams = L.cameras_struct(d_vm, d_K, W, H)
+    vrec = U.arrays_to_vrec(v, m)
+    L.check(lib.ssb_project_bwd(C.byref(s), None, n, C.byref(cams), L.ptr(d_aabb), L.ptr(vrec), C.byref(g), 0, None))
+    torch.cuda.synchronize()
+    for k in ref:
+        got = grads[k].cpu().numpy().reshape(ref[k].shape)
+        scale = np.abs(ref[k]).max()
+        assert U.close_frac(got, ref[k], 1e-5 * scale, 1e-3) <= 2e-3, k
+    # accumulate == 1 adds on top
+    L.check(lib.ssb_project_bwd(C.byref(s), None, n, C.byref(cams), L.ptr(d_aabb), L.ptr(vrec), C.byref(g), 1, None))
+    torch.cuda.synchronize()
+    got = grads["means"].cpu().numpy().reshape(-1, 3)
+    assert U.close_frac(got, 2 * ref["means"], 2e-5 * np.abs(ref["means"]).max(), 1e-3) <= 2e-3
+
+
+# ------------------------------------------------------- keys / sort / ranges
+@pytest.mark.parametrize("views,scale_mu", [(1, -3.5), (2, -3.0), (1, -2.0)])
+def test_tile_keys_bit_exact(lib, U, oracle, views, scale_mu):
+    cfg, sp, vm, K = scene(n=15000, views=views, scale_mu=scale_mu)
+    W, H, n = cfg.width, cfg.height, cfg.n_splats
+    proj = oracle.project_fwd(sp, vm, K, W, H)
+    counts, cum, keys, vals = oracle.tile_keys(proj, n, W, H)
+    rec = U.pack_screen(lib, proj)
+    cap = int(keys.size) + 100
+    st, M, g_counts, g_cum, g_keys, g_vals, n_dev = U.tile_keys(lib, U.dev(proj["aabb"]), U.dev(proj["depths"]), rec, views * n, n, W, H, cap)
+    assert st == 0 and M == keys.size and int(n_dev.item()) == M
+    assert np.array_equal(g_counts.cpu().numpy().astype(np.int64), counts)
+    assert np.array_equal(g_cum.cpu().numpy().astype(np.int64), cum)
+    assert np.array_equal(g_keys.cpu().numpy()[:M], keys)
+    assert np.array_equal(g_vals.cpu().numpy()[:M], vals)
+    # a capacity that is too small is reported, not overrun
+    st2, M2, *_ = U.tile_keys(lib, U.dev(proj["aabb"]), U.dev(proj["depths"]), rec, views * n, n, W, H, max(M // 2, 1))
+    assert st2 == L.SSB_ERR_CAPACITY and M2 == M
+
+
+def test_tile_keys_empty_and_all_culled(lib, U, oracle):
+    cfg, sp, vm, K = scene(n=256, views=1)
+    sp["means"][:, 2] = 50.0    # behind the camera at (0,0,3) looking down -z
+    proj = oracle.project_fwd(sp, vm, K, cfg.width, cfg.height)
+    assert not np.any(proj["aabb"])
+    rec = U.pack_screen(lib, proj)
+    st, M, counts, cum, keys, vals, n_dev = U.tile_keys(lib, U.dev(proj["aabb"]), U.dev(proj["depths"]), rec, 256, 256, cfg.width, cfg.height, 16)
+    assert st == 0 and M == 0 and int(counts.sum()) == 0
+    tw, th = oracle.tile_grid(cfg.width, cfg.height)
+    offs = U.tile_ranges(lib, keys, n_dev, 16, tw * th)
+    assert int(offs.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("n", [0, 1, 31, 4096, 4097, 100003])
+def test_sort_pairs_bit_exact(lib, U, oracle, n):
+    rng = np.random.default_rng(n)
+    keys = rng.integers(0, 1 << 46, size=n, dtype=np.int64)
+    if n > 10:
+        keys[::5] = keys[3]                       # ties exercise stability
+        keys[1::11] |= np.int64(1) << 60          # bits outside the sorted range must be ignored
+    vals = np.arange(n, dtype=np.int32)
+    cap = n + 13
+    for b0, b1 in ((0, 45), (0, 33), (0, 64), (32, 45)):
+        dk = torch.zeros(cap, dtype=torch.int64, device=U.DEV); dk[:n] = U.dev(keys)
+        dv = torch.zeros(cap, dtype=torch.int32, device=U.DEV); dv[:n] = U.dev(vals)
+        n_dev = torch.tensor([n], dtype=torch.int64, device=U.DEV)
+        sk, sv = U.sort_pairs(lib, dk, dv, n_dev, cap, b0, b1)
+        rk, rv = oracle.sort_pairs(keys, vals, b0, b1)
+        assert np.array_equal(sv.cpu().numpy()[:n], rv) and np.array_equal(sk.cpu().numpy()[:n], rk)
+
+
+def test_tile_ranges_bit_exact(lib, U, oracle):
+    rng = np.random.default_rng(9)
+    n_tiles = 1200
+    tiles = np.sort(rng.integers(5, 1100, size=30000)).astype(np.int64)
+    keys = (tiles << 32) | rng.integers(0, 1 << 32, size=tiles.size, dtype=np.int64)
+    ref = oracle.tile_offsets(keys, n_tiles)
+    n_dev = torch.tensor([keys.size], dtype=torch.int64, device=U.DEV)
+    got = U.tile_ranges(lib, U.dev(keys), n_dev, keys.size, n_tiles)
+    assert np.array_equal(got.cpu().numpy(), ref)
+
+
+# ------------------------------------------------------------------ raster
+def _chain(oracle, cfg, sp, vm, K):
+    return oracle.forward_chain(sp, vm, K, cfg.width, cfg.height)
+
+
+@pytest.mark.parametrize("views,scale_mu,w,h", [(1, -3.2, 320, 240), (2, -2.6, 200, 136), (1, -1.5, 100, 70)])
+def test_raster_forward(lib, U, oracle, views, scale_mu, w, h):
+    cfg, sp, vm, K = scene(n=15000, w=w, h=h, views=views, scale_mu=scale_mu)
+    ch = _chain(oracle, cfg, sp, vm, K)
+    W, H = cfg.width, cfg.height
+    rec = U.pack_screen(lib, ch["proj"])
+    M = ch["sorted_vals"].size
+    n_dev = torch.tensor([M], dtype=torch.int64, device=U.DEV)
+    got = U.raster_fwd(lib, rec, U.dev(ch["offsets"]), U.dev(ch["sorted_vals"]), n_dev, views, W, H)
+    ref = ch["render"]
+    assert ref["T"].min() < 0.5   # the scene is not trivially empty
+    assert np.abs(got["rgb"].cpu().numpy() - ref["rgb"]).max() <= 1e-4
+    assert np.abs(got["T"].cpu().numpy() - ref["T"]).max() <= 1e-4
+    assert U.close_frac(got["depth"].cpu().numpy(), ref["depth"], 1e-3, 1e-4) <= 1e-3
+    assert (got["last_ids"].cpu().numpy() != ref["last_ids"]).mean() <= 1e-3
+
+
+@pytest.mark.parametrize("views,scale_mu,w,h", [(1, -3.2, 320, 240), (2, -2.6, 200, 136), (1, -1.5, 100, 70)])
+def test_raster_backward(lib, U, oracle, views, scale_mu, w, h):
+    cfg, sp, vm, K = scene(n=15000, w=w, h=h, views=views, scale_mu=scale_mu)
+    ch = _chain(oracle, cfg, sp, vm, K)
+    W, H, n = cfg.width, cfg.height, cfg.n_splats
+    rng = np.random.default_rng(5)
+    P = views * H * W
+    v_rgb = rng.normal(size=(P, 3)).astype(np.float32)
+    v_depth = (0.1 * rng.normal(size=P)).astype(np.float32)
+    v_T = (0.1 * rng.normal(size=P)).astype(np.float32)
+    ref = oracle.raster_bwd(ch["proj"], ch["offsets"], ch["sorted_vals"], views, n, W, H, ch["render"], v_rgb, v_depth, v_T)
+    rec = U.pack_screen(lib, ch["proj"])
+    M = ch["sorted_vals"].size
+    n_dev = torch.tensor([M], dtype=torch.int64, device=U.DEV)
+    render = {k: U.dev(v) for k, v in ch["render"].items()}
+    v_rec = U.raster_bwd(lib, rec, U.dev(ch["offsets"]), U.dev(ch["sorted_vals"]), n_dev, views, W, H, render, U.dev(v_rgb), U.dev(v_depth),
+                         U.dev(v_T), pairs=views * n)
+    got = U.vrec_to_arrays(v_rec, views * n)
+    for k in ref:
+        scale = np.abs(ref[k]).max()
+        assert U.close_frac(got[k], ref[k], 2e-5 * scale, 1e-3) <= 2e-3, k

@@ -1,0 +1,222 @@
+"""GPU parity of the loss and optimiser kernels and of whole iterations driven
+through ssb_step_views / Trainer, plus size-independent properties at the full
+benchmark size (sortedness, permutation checksum, range monotonicity)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from spirula_studio_b200 import lib as L, scenes  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return L.load()
+
+
+@pytest.fixture(scope="module")
+def U():
+    from tests import gpu_util
+    return gpu_util
+
+
+@pytest.mark.parametrize("B,H,W", [(1, 240, 320), (2, 67, 101), (1, 16, 16), (1, 5, 7)])
+def test_loss_l1_ssim(lib, U, oracle, B, H, W):
+    rng = np.random.default_rng(B * 1000 + H)
+    render = rng.random((B * H * W, 3), dtype=np.float32)
+    gt = rng.random((B * H * W, 3), dtype=np.float32)
+    ref_v, ref_l = oracle.loss_l1_ssim(render, gt, B, H, W, 0.8, 0.2)
+    d_v = torch.full((B * H * W, 3), 3.0, device=U.DEV)
+    d_l = torch.full((3,), 5.0, device=U.DEV)
+    L.check(lib.ssb_loss_l1_ssim_fwdbwd(L.ptr(U.dev(render)), L.ptr(U.dev(gt)), B, H, W, 0.8, 0.2, L.ptr(d_v), L.ptr(d_l), None))
+    torch.cuda.synchronize()
+    assert np.allclose(d_l.cpu().numpy(), ref_l, rtol=2e-4, atol=2e-6)
+    scale = np.abs(ref_v).max()
+    assert U.close_frac(d_v.cpu().numpy(), ref_v, 1e-4 * scale, 1e-3) == 0.0
+
+
+def _np_state(sp):
+    p = {k: np.ascontiguousarray(v).copy() for k, v in sp.items()}
+    z = lambda: {k: np.zeros_like(v) for k, v in p.items()}
+    return p, z(), z()
+
+
+def test_adam_fp32(lib, U, oracle):
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=5003)
+    sp = scenes.make_splats(cfg)
+    rng = np.random.default_rng(8)
+    p, m1, m2 = _np_state(sp)
+    dp = {k: U.dev(v.reshape(-1)) for k, v in p.items()}
+    dm1 = {k: torch.zeros_like(t) for k, t in dp.items()}
+    dm2 = {k: torch.zeros_like(t) for k, t in dp.items()}
+    lrs = cfg.lrs
+    for step in (1, 2, 3):
+        g = {k: (rng.normal(size=v.shape) * 1e-3).astype(np.float32) for k, v in p.items()}
+        if step == 2:   # non-finite appearance gradients are dropped (FusedAppearanceOptim.cu:39-40)
+            g["features_sh"][::13] = np.inf
+            g["features_dc"][::29] = np.nan
+        dg = {k: U.dev(v.reshape(-1)) for k, v in g.items()}
+        gs = 0.25
+        oracle.adam_geometry(p, {k: v.copy() for k, v in g.items()}, m1, m2, step, lrs, grad_scale=gs)
+        oracle.adam_plain(p["features_dc"], g["features_dc"].copy(), m1["features_dc"], m2["features_dc"], step, lrs["lr_features_dc"],
+                          0.0, 0.5 / 0.28209479177387814, gs)
+        oracle.adam_plain(p["features_sh"], g["features_sh"].copy(), m1["features_sh"], m2["features_sh"], step, lrs["lr_features_sh"], 0.0, 0.0, gs)
+        cfg_a = L.SsbAdamConfig(lrs["lr_means"], lrs["lr_quats"], lrs["lr_scales"], lrs["lr_opacities"], lrs["lr_features_dc"],
+                                lrs["lr_features_sh"], 0.0, gs, step, 1)
+        structs = [L.splats_struct(d) for d in (dp, dg, dm1, dm2)]
+        L.check(lib.ssb_adam_step(*[C.byref(s) for s in structs], 0, cfg.n_splats, C.byref(cfg_a), None))
+        torch.cuda.synchronize()
+        for k in p:
+            assert U.close_frac(dp[k].cpu().numpy(), p[k].reshape(-1), 1e-7, 1e-5) <= 1e-4, (k, step)
+            assert U.close_frac(dm1[k].cpu().numpy(), m1[k].reshape(-1), 1e-12, 1e-4) <= 1e-4, (k, step)
+            assert float(dg[k].abs().sum()) == 0.0        # zero_grad
+    # a sub-range only touches its own splats
+    before = dp["means"].clone()
+    g0 = {k: torch.ones_like(t) for k, t in dp.items()}
+    structs = [L.splats_struct(d) for d in (dp, g0, dm1, dm2)]
+    cfg_a = L.SsbAdamConfig(1e-3, 1e-3, 5e-3, 5e-2, 2.5e-3, 2.5e-3, 0.0, 1.0, 4, 0)
+    L.check(lib.ssb_adam_step(*[C.byref(s) for s in structs], 100, 50, C.byref(cfg_a), None))
+    torch.cuda.synchronize()
+    changed = (dp["means"] != before).view(-1, 3).any(dim=1).nonzero().flatten().cpu().numpy()
+    assert changed.min() == 100 and changed.max() == 149 and changed.size == 50
+
+
+@pytest.mark.parametrize("bits", [16, 8])
+def test_adam_quantized_sh(lib, U, oracle, bits):
+    """Codes may differ by one quantum where log1pf/expm1f round differently
+    (the reference's own tolerance, src/backend/tests/optim_parity.cpp:9-13)."""
+    rng = np.random.default_rng(bits)
+    n_cells = 45 * 1000 + 7
+    x0 = rng.normal(0, 0.05, size=n_cells).astype(np.float32)
+    vp, vb = oracle.quant_encode(x0, bits)
+    nb = (n_cells + 255) // 256
+    op, ob = np.zeros(n_cells * 2, np.uint8), np.zeros(nb * 4, np.float32)
+    d_vp, d_vb, d_op, d_ob = U.dev(vp), U.dev(vb), U.dev(op), U.dev(ob)
+    view = np.uint16 if bits == 16 else np.uint8
+    for step in (1, 2, 3):
+        g = (rng.normal(size=n_cells) * 1e-3).astype(np.float32)
+        d_g = U.dev(g)
+        oracle.adam_qq(g.copy(), op, ob, vp, vb, bits, step, 2.5e-3, grad_scale=0.5)
+        cfg_a = L.SsbAdamConfig(0, 0, 0, 0, 0, 2.5e-3, 0.0, 0.5, step, 1)
+        L.check(lib.ssb_adam_step_sh_quantized(L.ptr(d_g), L.ptr(d_op), L.ptr(d_ob), L.ptr(d_vp), L.ptr(d_vb), bits, 0, n_cells, n_cells,
+                                               C.byref(cfg_a), None))
+        torch.cuda.synchronize()
+        assert float(d_g.abs().sum()) == 0.0
+        dv = np.abs(d_vp.cpu().numpy().view(view).astype(np.int64) - vp.view(view).astype(np.int64))
+        do = np.abs(d_op.cpu().numpy().astype(np.int64) - op.astype(np.int64))
+        assert dv.max() <= 1 and do.max() <= 1
+        assert (dv > 0).mean() <= 2e-2 and (do > 0).mean() <= 2e-2
+        assert np.allclose(d_vb.cpu().numpy(), vb, rtol=1e-5, atol=1e-8)
+        assert np.allclose(d_ob.cpu().numpy(), ob, rtol=1e-4, atol=1e-6)
+        # continue both sides from the same state so differences do not compound
+        d_vp.copy_(U.dev(vp)); d_vb.copy_(U.dev(vb)); d_op.copy_(U.dev(op)); d_ob.copy_(U.dev(ob))
+
+
+def _oracle_iteration(oracle, cfg, sp, vm, K, targets, shq=None):
+    """Gradients of one multi-view iteration, one camera per sub-batch, summed (reference split-batch loop)."""
+    W, H, n = cfg.width, cfg.height, cfg.n_splats
+    tot = None
+    losses = np.zeros(3)
+    renders = []
+    for v in range(vm.shape[0]):
+        ch = oracle.forward_chain(sp, vm[v:v + 1], K[v:v + 1], W, H, shq=shq)
+        vr, l = oracle.loss_l1_ssim(ch["render"]["rgb"], targets[v].reshape(-1, 3), 1, H, W, 0.8, 0.2)
+        losses += l
+        gs = oracle.raster_bwd(ch["proj"], ch["offsets"], ch["sorted_vals"], 1, n, W, H, ch["render"], vr)
+        g = oracle.project_bwd(sp, vm[v:v + 1], K[v:v + 1], W, H, ch["proj"]["aabb"], gs, shq=shq)
+        tot = g if tot is None else {k: tot[k] + g[k] for k in g}
+        renders.append(ch)
+    return tot, losses, renders
+
+
+@pytest.mark.parametrize("quant", [False, True])
+def test_whole_iteration_matches_oracle(lib, U, oracle, quant):
+    from spirula_studio_b200.trainer import Trainer
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=12000, width=208, height=144, n_views=3)
+    cfg.rig, cfg.rig_radius, cfg.log_scale_mu = "ring", 3.0, -3.0
+    if quant:
+        cfg.sh_value_bits, cfg.sh_optim_bits = 16, 8
+    sp = scenes.make_splats(cfg)
+    vm, K = scenes.make_cameras(cfg)
+    targets = np.stack([scenes.make_target(cfg, v) for v in range(cfg.n_views)])
+    shq = None
+    if quant:
+        packed, bounds = oracle.quant_encode(sp["features_sh"], 16)
+        shq = dict(packed=packed, bounds=bounds, bits=16, bounds_stride=256)
+    ref_g, ref_l, renders = _oracle_iteration(oracle, cfg, sp, vm, K, targets, shq)
+
+    tr = Trainer(cfg, sp, device=U.DEV)
+    h_vm, h_K, h_gt = (torch.from_numpy(a).pin_memory() for a in (vm, K, targets))
+    tr.losses.zero_()
+    d_vm, d_K, d_gt = h_vm.to(U.DEV), h_K.to(U.DEV), h_gt.to(U.DEV)
+    tr.views_fwd_bwd(d_vm, d_K, d_gt, cfg.n_views)
+    torch.cuda.synchronize()
+    # last view's image
+    rgb_p = C.c_void_p()
+    L.check(lib.ssb_step_peek(tr.handle, C.byref(rgb_p), None, None, None, None, None))
+    assert tr.last_isects() == renders[-1]["sorted_vals"].size or abs(tr.last_isects() - renders[-1]["sorted_vals"].size) <= 3
+    img_t = U.tensor_from_device_ptr(rgb_p.value, (cfg.height * cfg.width, 3))
+    assert np.abs(img_t.cpu().numpy() - renders[-1]["render"]["rgb"]).max() <= 1e-4
+    assert np.allclose(tr.losses.cpu().numpy(), ref_l, rtol=1e-3, atol=1e-5)
+    for k in ref_g:
+        got = tr.grads[k].cpu().numpy().reshape(ref_g[k].shape)
+        scale = np.abs(ref_g[k]).max()
+        assert U.close_frac(got, ref_g[k], 2e-5 * scale, 1e-3) <= 5e-3, k
+    # optimiser pass: post-Adam parameters within 1e-3 relative of the oracle's
+    p, m1, m2 = _np_state(sp)
+    gs = 1.0 / cfg.n_views
+    oracle.adam_geometry(p, {k: v.copy() for k, v in ref_g.items()}, m1, m2, 1, cfg.lrs, grad_scale=gs)
+    oracle.adam_plain(p["features_dc"], ref_g["features_dc"].copy(), m1["features_dc"], m2["features_dc"], 1, cfg.lrs["lr_features_dc"], 0.0,
+                      0.5 / 0.28209479177387814, gs)
+    tr.optimizer_step(cfg.n_views)
+    torch.cuda.synchronize()
+    for k in ("means", "quats", "scales", "opacities", "features_dc"):
+        got = tr.params[k].cpu().numpy().reshape(p[k].shape)
+        # a first Adam step moves every coordinate by lr*sign(g): where |g| is at rounding level the sign may differ
+        assert U.close_frac(got, p[k], 1e-6, 1e-3) <= 2e-2, k
+    if not quant:
+        oracle.adam_plain(p["features_sh"], ref_g["features_sh"].copy(), m1["features_sh"], m2["features_sh"], 1, cfg.lrs["lr_features_sh"], 0.0, 0.0, gs)
+        got = tr.params["features_sh"].cpu().numpy().reshape(p["features_sh"].shape)
+        assert U.close_frac(got, p["features_sh"], 1e-6, 1e-3) <= 2e-2
+    # the same iteration through the host-buffer entry point gives the same loss
+    tr2 = Trainer(cfg, sp, device=U.DEV)
+    l1, ssim, loss = tr2.train_step(h_vm, h_K, h_gt, cfg.n_views)
+    assert abs(loss - ref_l[2] / cfg.n_views) <= 1e-3 * abs(ref_l[2] / cfg.n_views) + 1e-5
+    tr.close(); tr2.close()
+
+
+def test_full_size_sort_and_range_properties(lib, U):
+    """At the benchmark's pair count (several million) the oracle is too slow to
+    run inside a test, so check what must hold at any size: the output is
+    sorted on the bit range, is a permutation of the input (checksums of keys,
+    values and key*value), equal keys keep their input order, and the ranges
+    are monotone and bracket exactly the keys of each tile."""
+    g = torch.Generator(device=U.DEV); g.manual_seed(1)
+    n, n_tiles = 5_000_000, 8160
+    tiles = torch.randint(0, n_tiles, (n,), device=U.DEV, generator=g, dtype=torch.int64)
+    depth = torch.randint(0, 1 << 20, (n,), device=U.DEV, generator=g, dtype=torch.int64) | (1 << 31)
+    keys = (tiles << 32) | depth
+    vals = torch.arange(n, device=U.DEV, dtype=torch.int32)
+    cap = n + 1000
+    dk = torch.zeros(cap, dtype=torch.int64, device=U.DEV); dk[:n] = keys
+    dv = torch.zeros(cap, dtype=torch.int32, device=U.DEV); dv[:n] = vals
+    n_dev = torch.tensor([n], dtype=torch.int64, device=U.DEV)
+    end_bit = 32 + lib.ssb_tile_n_bits(n_tiles)
+    sk, sv = U.sort_pairs(lib, dk, dv, n_dev, cap, 0, end_bit)
+    sk, sv = sk[:n], sv[:n]
+    assert bool((sk[1:] >= sk[:-1]).all())
+    assert int(sk.sum()) == int(keys.sum()) and int(sv.long().sum()) == int(vals.long().sum())
+    assert bool((keys[sv.long()] == sk).all())                       # values still belong to their keys
+    same = sk[1:] == sk[:-1]
+    assert bool((sv[1:][same] > sv[:-1][same]).all())                # stability: ties keep input order
+    offs = U.tile_ranges(lib, sk, n_dev, cap, n_tiles).long()
+    assert bool((offs[1:] >= offs[:-1]).all()) and int(offs[0]) == 0
+    counts = torch.bincount(tiles, minlength=n_tiles)
+    ends = torch.cat([offs[1:], torch.tensor([n], device=U.DEV)])
+    assert bool(((ends - offs) == counts).all())

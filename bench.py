@@ -1,0 +1,375 @@
+#!/usr/bin/env python
+"""Benchmark of the training hot path: train iterations per second on the
+"mid" scene (1,000,000 SH-degree-3 Gaussians with 16-bit quantised SH values and
+8-bit quantised SH optimiser state, a batch of sixteen 1920x1080 pinhole views).
+
+One iteration = forward + L1/SSIM loss + backward of every view of the batch
+(one camera per sub-batch, gradients summed), a sum all-reduce of the gradients
+when several GPUs share the batch, and one Adam pass over all parameters.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --steps K --warmup W     # CPU restatement, host cores
+
+Prints ONE JSON line (rank 0).  Inputs are seeded synthetic data of the
+configuration's shapes and distributions.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "train iters/sec (fwd+bwd+SSIM+Adam), 1M SH3 Gaussians @1080p"
+UNIT = "iters/s"
+WORKLOAD = "mid_1m"
+
+
+def shard(total, world, rank):
+    """Contiguous block of views owned by `rank`."""
+    base, rem = divmod(total, world)
+    start = rank * base + min(rank, rem)
+    return start, base + (1 if rank < rem else 0)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.path = tempfile.mktemp(prefix="ssb_clocks_", suffix=".csv")
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if sm:
+            out = {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(np.max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+        return out
+
+
+def stage_bytes(stage, n, visible, pairs, pixels, tiles, quant_bits, sort_passes):
+    """Algorithmic bytes one launch (one view) of a stage moves."""
+    sh_b = 45 * (4 if quant_bits == 32 else quant_bits // 8)
+    if stage == "project_fwd":
+        return visible * (56 + sh_b + 60) + (n - visible) * 56
+    if stage == "tile_keys":
+        return n * 44 + pairs * 12
+    if stage == "sort":
+        return pairs * (24 * sort_passes + 8)
+    if stage == "tile_ranges":
+        return pairs * 8 + tiles * 4
+    if stage == "raster_fwd":
+        return pairs * 40 + pixels * 24
+    if stage == "loss":
+        return pixels * 36
+    if stage == "raster_bwd":
+        return pixels * 44 + pairs * 40
+    if stage == "project_bwd":
+        return visible * (56 + sh_b + 40 + 16 + 236) + (n - visible) * 16
+    raise KeyError(stage)
+
+
+def adam_bytes(n, quant_bits):
+    if quant_bits == 32:
+        return n * 59 * 28
+    value_b = quant_bits // 8
+    return n * (14 * 28 + 45 * (4 + 2 * value_b + 2 * 2))
+
+
+# --------------------------------------------------------------------------
+def oracle_view_seconds(cfg, splats, vm, K, view, shq):
+    from oracle import pyoracle as O
+    from spirula_studio_b200 import scenes
+    t0 = time.perf_counter()
+    W, H, n = cfg.width, cfg.height, cfg.n_splats
+    ch = O.forward_chain(splats, vm[view:view + 1], K[view:view + 1], W, H, shq=shq)
+    gt = scenes.make_target(cfg, view)
+    t_gen = time.perf_counter()
+    v, _ = O.loss_l1_ssim(ch["render"]["rgb"], gt.reshape(-1, 3), 1, H, W, 0.8, 0.2)
+    gs = O.raster_bwd(ch["proj"], ch["offsets"], ch["sorted_vals"], 1, n, W, H, ch["render"], v)
+    g = O.project_bwd(splats, vm[view:view + 1], K[view:view + 1], W, H, ch["proj"]["aabb"], gs, shq=shq)
+    return time.perf_counter() - t0, g, t_gen
+
+
+def oracle_adam_seconds(cfg, splats, grads, state, step, shq):
+    from oracle import pyoracle as O
+    t0 = time.perf_counter()
+    p, m1, m2 = state
+    lr = cfg.lrs
+    O.adam_geometry(p, grads, m1, m2, step, lr, grad_scale=1.0 / cfg.n_views)
+    O.adam_plain(p["features_dc"], grads["features_dc"], m1["features_dc"], m2["features_dc"], step, lr["lr_features_dc"], 0.0,
+                 0.5 / 0.28209479177387814, 1.0 / cfg.n_views)
+    if shq is None:
+        O.adam_plain(p["features_sh"], grads["features_sh"], m1["features_sh"], m2["features_sh"], step, lr["lr_features_sh"], 0.0, 0.0,
+                     1.0 / cfg.n_views)
+    else:
+        O.adam_qq(grads["features_sh"].reshape(-1), shq["optim_packed"], shq["optim_bounds"], shq["packed"], shq["bounds"], shq["bits"], step,
+                  lr["lr_features_sh"], grad_scale=1.0 / cfg.n_views)
+    return time.perf_counter() - t0
+
+
+def cpu_port_run(cfg, steps, warmup):
+    """Times the CPU restatement: each step = one view of the batch (all stages) + one Adam pass."""
+    from oracle import pyoracle as O
+    from spirula_studio_b200 import scenes
+    splats = scenes.make_splats(cfg)
+    vm, K = scenes.make_cameras(cfg)
+    shq = None
+    if cfg.sh_value_bits in (8, 16):
+        packed, bounds = O.quant_encode(splats["features_sh"], cfg.sh_value_bits)
+        cells = cfg.n_splats * 45
+        shq = dict(packed=packed, bounds=bounds, bits=cfg.sh_value_bits, bounds_stride=256,
+                   optim_packed=np.zeros(cells * 2, np.uint8), optim_bounds=np.zeros(((cells + 255) // 256) * 4, np.float32))
+    state = ({k: v.copy() for k, v in splats.items()}, {k: np.zeros_like(v) for k, v in splats.items()},
+             {k: np.zeros_like(v) for k, v in splats.items()})
+    tv, ta = [], []
+    for i in range(warmup + steps):
+        t, g, _ = oracle_view_seconds(cfg, splats, vm, K, i % cfg.n_views, shq)
+        a = oracle_adam_seconds(cfg, splats, g, state, i + 1, shq)
+        if i >= warmup:
+            tv.append(t); ta.append(a)
+    t_view, t_adam = float(np.mean(tv)), float(np.mean(ta))
+    t_iter = cfg.n_views * t_view + t_adam
+    return 1.0 / t_iter, t_iter, t_view, t_adam, O.num_threads()
+
+
+def run_reference(args, cfg, rank):
+    if rank != 0:
+        return
+    value, t_iter, t_view, t_adam, cores = cpu_port_run(cfg, args.steps, args.warmup)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * t_iter, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "n_splats": cfg.n_splats, "views_per_iteration": cfg.n_views, "resolution": [cfg.width, cfg.height],
+                   "sh_value_bits": cfg.sh_value_bits, "sh_optim_bits": cfg.sh_optim_bits},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"each step = 1 of {cfg.n_views} views at full size through every stage ({t_view:.2f} s) plus one Adam pass "
+                                   f"({t_adam:.2f} s); iteration time = {cfg.n_views} x view + Adam"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference has no CPU implementation of this path and its Vulkan backend cannot run here (no graphics stack); "
+                "this arm times the CPU restatement under oracle/ on the host cores",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------
+def run_ours(args, cfg, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    from spirula_studio_b200 import lib as L, scenes
+    from spirula_studio_b200.trainer import Trainer
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the library has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+    lib = L.load()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    total_views = cfg.n_views
+    v0, nv = shard(total_views, world, rank)
+    splats = scenes.make_splats(cfg)
+    vm, K = scenes.make_cameras(cfg)
+    tr = Trainer(cfg, splats, device=dev, world_size=world, rank=rank)
+    P = cfg.width * cfg.height
+    h_vm = torch.from_numpy(vm[v0:v0 + nv].copy()).pin_memory()
+    h_K = torch.from_numpy(K[v0:v0 + nv].copy()).pin_memory()
+    h_gt = torch.empty((nv, cfg.height, cfg.width, 3), dtype=torch.float32).pin_memory()
+    for i in range(nv):
+        h_gt[i].copy_(torch.from_numpy(scenes.make_target(cfg, v0 + i)))
+    d_vm, d_K, d_gt = h_vm.to(dev), h_K.to(dev), h_gt.to(dev)
+    del splats
+
+    # ---- device-resident timing -------------------------------------------
+    for _ in range(args.warmup):
+        tr.step_device(d_vm, d_K, d_gt, nv, total_views)
+    pairs = tr.last_isects() if nv > 0 else 0          # also verifies the pair capacity was enough
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    barrier()
+    launches0 = lib.ssb_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        tr.step_device(d_vm, d_K, d_gt, nv, total_views)
+    e1.record()
+    barrier()
+    launches = lib.ssb_launch_count() - launches0
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_step = ms_total / args.steps
+
+    # ---- end to end: host buffers in, loss scalars out --------------------
+    for _ in range(min(args.warmup, 2)):
+        tr.train_step(h_vm, h_K, h_gt, total_views)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        losses = tr.train_step(h_vm, h_K, h_gt, total_views)
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    clocks = sampler.stop() if sampler else None
+
+    # ---- per-stage device times (separate pass, CUDA events inside the library)
+    stage_ms = np.zeros(len(L.STAGES), np.float32)
+    n_prof = C.c_int32(0)
+    adam_ms = comm_ms = 0.0
+    prof_steps = max(1, min(args.steps, 4))
+    if nv > 0:
+        L.check(lib.ssb_step_set_profiling(tr.handle, 1))
+    ea, eb, ec = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    for _ in range(prof_steps):
+        tr.losses.zero_()
+        if nv > 0:
+            tr.views_fwd_bwd(d_vm, d_K, d_gt, nv)
+            views_done = C.c_int32(0)
+            L.check(lib.ssb_step_get_profile(tr.handle, stage_ms.ctypes.data_as(C.c_void_p), C.byref(views_done)))
+            n_prof.value += views_done.value
+        ea.record(); tr.allreduce_grads(); eb.record(); tr.optimizer_step(total_views); ec.record()
+        torch.cuda.synchronize()
+        comm_ms += ea.elapsed_time(eb); adam_ms += eb.elapsed_time(ec)
+    if nv > 0:
+        L.check(lib.ssb_step_set_profiling(tr.handle, 0))
+    per_view_ms = stage_ms / max(n_prof.value, 1)
+    adam_ms /= prof_steps; comm_ms /= prof_steps
+
+    # visible pairs of the last view, for the byte counts
+    visible = 0
+    if nv > 0:
+        aabb_p = C.c_void_p()
+        L.check(lib.ssb_step_peek(tr.handle, None, None, None, None, None, C.byref(aabb_p)))
+        rt = C.CDLL("libcudart.so.12")
+        rt.cudaMemcpy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+        aabb = torch.empty((cfg.n_splats, 4), dtype=torch.float32, device=dev)
+        rt.cudaMemcpy(C.c_void_p(aabb.data_ptr()), aabb_p, aabb.numel() * 4, 3)
+        visible = int((aabb[:, 2] > aabb[:, 0]).sum().item())
+
+    if rank == 0:
+        peak, peak_kind = peaks()
+        tiles = ((cfg.width + 15) // 16) * ((cfg.height + 15) // 16)
+        sort_passes = (32 + lib.ssb_tile_n_bits(tiles) + 7) // 8
+        kernels = {}
+        for i, name in enumerate(L.STAGES):
+            b = stage_bytes(name, cfg.n_splats, visible, pairs, P, tiles, cfg.sh_value_bits, sort_passes)
+            ms = float(per_view_ms[i])
+            gbs = b / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
+            kernels[name] = {"ms": round(ms, 4), "launches_per_iteration": nv, "algorithmic_bytes": int(b), "gbs": round(gbs, 1), "frac_of_hbm": round(gbs / peak, 4)}
+        ab = adam_bytes(cfg.n_splats, cfg.sh_value_bits)
+        kernels["adam"] = {"ms": round(adam_ms, 4), "launches_per_iteration": 1, "algorithmic_bytes": int(ab),
+                           "gbs": round(ab / (adam_ms * 1e-3) / 1e9, 1) if adam_ms > 0 else 0.0,
+                           "frac_of_hbm": round(ab / (adam_ms * 1e-3) / 1e9 / peak, 4) if adam_ms > 0 else 0.0}
+        kernels["allreduce"] = {"ms": round(comm_ms, 4), "bytes": int(tr.grads_flat.numel() * 4)}
+        share = {k: v["ms"] * v.get("launches_per_iteration", 1) for k, v in kernels.items() if k != "allreduce"}
+        dom = max(share, key=share.get)
+        roof = {"kernel": dom, "bound": "hbm", "achieved": kernels[dom]["gbs"], "peak": peak, "unit": "GB/s", "frac": kernels[dom]["frac_of_hbm"],
+                "traffic": None, "peak_source": f"{peak_kind} copy bandwidth",
+                "note": "raster kernels are FP32/shared-memory bound; the HBM fraction is reported because the schema asks for it"}
+        value = 1e3 / ms_step
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "n_splats": cfg.n_splats, "views_per_iteration": total_views, "views_per_gpu": nv,
+                       "resolution": [cfg.width, cfg.height], "sh_value_bits": cfg.sh_value_bits, "sh_optim_bits": cfg.sh_optim_bits,
+                       "parallelism": f"views sharded over {world} GPU(s), replicated parameters, gradient all-reduce",
+                       "pairs_per_view": int(pairs), "visible_per_view": visible,
+                       "l2": "inputs (parameters, gradients, moments, targets: > 1 GB) exceed the 126 MB L2; no flush between iterations"},
+            "e2e": {"value": 1e3 / e2e_ms, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": int(nv * (P * 12 + 64 + 16)), "d2h_bytes_per_step": 12},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "kernels": kernels,
+            "losses_last": {"l1": losses[0], "ssim": losses[1], "loss": losses[2]},
+            "device_bytes": tr.device_bytes(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cfg_cpu = cfg
+            v, t_iter, t_view, t_adam, cores = cpu_port_run(cfg_cpu, 2, 0)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": f"2 of {cfg.n_views} views at full size through every stage ({t_view:.2f} s each) and 2 Adam passes "
+                                              f"({t_adam:.2f} s each); iteration time = {cfg.n_views} x view + Adam"}
+        print(json.dumps(line), flush=True)
+    tr.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=WORKLOAD)
+    ap.add_argument("--splats", type=int, default=0, help="override the splat count (smaller cases for profiling)")
+    ap.add_argument("--views", type=int, default=0, help="override the views per iteration")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    from spirula_studio_b200 import scenes
+    cfg = scenes.CONFIGS[args.workload]
+    if args.splats or args.views:
+        cfg = scenes.scaled(cfg, n_splats=args.splats or None, n_views=args.views or None, name=cfg.name)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, cfg, rank)
+    else:
+        run_ours(args, cfg, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

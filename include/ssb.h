@@ -265,6 +265,15 @@ int ssb_step_last_isects(SsbStep* step, int64_t* h_n_isects, void* stream);
 int ssb_step_peek(SsbStep* step, const float** d_rgb, const float** d_depth, const float** d_T,
                   const int32_t** d_last_ids, const SsbScreenRec** d_screen, const float** d_aabb);
 
+/* Per-stage device timing of ssb_step_views (CUDA events on the stream the
+ * kernels run on).  Off by default.  ssb_step_get_profile synchronises, adds
+ * the views recorded since the last call into ms[SSB_STAGE_COUNT] (milliseconds
+ * summed over views), stores how many views that was, and resets. */
+enum { SSB_STAGE_PROJECT_FWD = 0, SSB_STAGE_TILE_KEYS, SSB_STAGE_SORT, SSB_STAGE_TILE_RANGES, SSB_STAGE_RASTER_FWD,
+       SSB_STAGE_LOSS, SSB_STAGE_RASTER_BWD, SSB_STAGE_PROJECT_BWD, SSB_STAGE_COUNT };
+int ssb_step_set_profiling(SsbStep* step, int enable);
+int ssb_step_get_profile(SsbStep* step, float* ms, int32_t* n_views);
+
 /* Number of kernel launches the library has issued from this process so far. */
 int64_t ssb_launch_count(void);
 

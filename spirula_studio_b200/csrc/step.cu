@@ -12,6 +12,8 @@
 
 #include <new>
 
+enum { SsbStep_kMaxProfViews = 64 };
+
 struct SsbStep {
     SsbStepConfig cfg;
     int tw, th;
@@ -31,6 +33,11 @@ struct SsbStep {
     int32_t* offsets;     // [tiles]
     float* rgb; float* depth; float* T; int32_t* last_ids; float* v_rgb;
     int sel;
+    // optional per-stage timing
+    int profiling;
+    int prof_views;                                   // views recorded and not yet read
+    cudaEvent_t ev[SsbStep_kMaxProfViews][SSB_STAGE_COUNT + 1];
+    int ev_ready;
 };
 
 namespace ssb {
@@ -61,6 +68,9 @@ void ssb_step_destroy(SsbStep* s) {
     cudaFree(s->ids[0]); cudaFree(s->ids[1]); cudaFree(s->flat[0]); cudaFree(s->flat[1]);
     cudaFree(s->n_isects); cudaFree(s->offsets);
     cudaFree(s->rgb); cudaFree(s->depth); cudaFree(s->T); cudaFree(s->last_ids); cudaFree(s->v_rgb);
+    if (s->ev_ready)
+        for (int v = 0; v < SsbStep_kMaxProfViews; ++v)
+            for (int k = 0; k <= SSB_STAGE_COUNT; ++k) cudaEventDestroy(s->ev[v][k]);
     delete s;
 }
 
@@ -133,20 +143,63 @@ int ssb_step_views(SsbStep* s, const SsbSplats* params, const SsbShQuant* shq,
         cam.count = 1; cam.width = W; cam.height = H;
         cam.model = s->cfg.camera_model; cam.antialiased = s->cfg.antialiased;
         int e;
+        const bool prof = s->profiling && s->prof_views < SsbStep_kMaxProfViews;
+        cudaEvent_t* ev = prof ? s->ev[s->prof_views] : nullptr;
+#define SSB_MARK(k) do { if (prof) SSB_CUDA(cudaEventRecord(ev[k], st)); } while (0)
+        SSB_MARK(0);
         if ((e = ssb_project_fwd(params, shq, n, &cam, s->aabb, s->depths, nullptr, s->screen, st))) return e;
+        SSB_MARK(1);
         if ((e = ssb_tile_keys(s->aabb, s->depths, s->screen, n, n, W, H, s->keys_ws, s->keys_ws_bytes, nullptr, nullptr,
                                s->ids[0], s->flat[0], s->capacity, s->n_isects, nullptr, st))) return e;
+        SSB_MARK(2);
         int32_t sel = 0;
         if ((e = ssb_sort_pairs_u64(s->ids[0], s->flat[0], s->ids[1], s->flat[1], s->n_isects, s->capacity, 0, end_bit,
                                     s->sort_ws, s->sort_ws_bytes, &sel, st))) return e;
         s->sel = sel;
+        SSB_MARK(3);
         if ((e = ssb_tile_ranges(s->ids[sel], s->n_isects, s->capacity, n_tiles, s->offsets, st))) return e;
+        SSB_MARK(4);
         if ((e = ssb_raster_fwd(s->screen, s->offsets, s->flat[sel], s->n_isects, 1, W, H, s->rgb, s->depth, s->T, s->last_ids, st))) return e;
+        SSB_MARK(5);
         if ((e = launch_loss(s->rgb, d_gt + (int64_t)v * P * 3, 1, H, W, s->cfg.w_l1, s->cfg.w_ssim, s->v_rgb, d_losses, st))) return e;
+        SSB_MARK(6);
         if ((e = ssb_raster_bwd(s->screen, s->offsets, s->flat[sel], s->n_isects, 1, W, H, s->depth, s->T, s->last_ids,
                                 s->v_rgb, nullptr, nullptr, s->v_screen, st))) return e;
+        SSB_MARK(7);
         if ((e = launch_project_bwd(params, shq, n, &cam, s->aabb, s->v_screen, grads, (accumulate || v > 0) ? 1 : 0, 1, st))) return e;
+        SSB_MARK(8);
+#undef SSB_MARK
+        if (prof) s->prof_views++;
     }
+    return SSB_OK;
+}
+
+int ssb_step_set_profiling(SsbStep* s, int enable) {
+    using namespace ssb;
+    SSB_REQUIRE(s, "ssb_step_set_profiling: NULL step");
+    if (enable && !s->ev_ready) {
+        for (int v = 0; v < SsbStep_kMaxProfViews; ++v)
+            for (int k = 0; k <= SSB_STAGE_COUNT; ++k) SSB_CUDA(cudaEventCreate(&s->ev[v][k]));
+        s->ev_ready = 1;
+    }
+    s->profiling = enable ? 1 : 0;
+    s->prof_views = 0;
+    return SSB_OK;
+}
+
+int ssb_step_get_profile(SsbStep* s, float* ms, int32_t* n_views) {
+    using namespace ssb;
+    SSB_REQUIRE(s && ms && n_views, "ssb_step_get_profile: NULL argument");
+    *n_views = s->prof_views;
+    for (int v = 0; v < s->prof_views; ++v) {
+        SSB_CUDA(cudaEventSynchronize(s->ev[v][SSB_STAGE_COUNT]));
+        for (int k = 0; k < SSB_STAGE_COUNT; ++k) {
+            float t = 0.f;
+            SSB_CUDA(cudaEventElapsedTime(&t, s->ev[v][k], s->ev[v][k + 1]));
+            ms[k] += t;
+        }
+    }
+    s->prof_views = 0;
     return SSB_OK;
 }
 

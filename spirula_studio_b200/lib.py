@@ -21,6 +21,7 @@ CAMERA_PINHOLE, CAMERA_FISHEYE, CAMERA_EQUISOLID, CAMERA_EQUIRECT = 0, 1, 2, 3
 NUM_SH = 15
 TILE = 16
 SCREEN_REC_FLOATS = 12
+STAGES = ("project_fwd", "tile_keys", "sort", "tile_ranges", "raster_fwd", "loss", "raster_bwd", "project_bwd")
 
 
 class SsbError(RuntimeError):
@@ -84,6 +85,8 @@ SIGNATURES = {
     "ssb_step_views": (C.c_int, [_P, _P, _P, _P, _P, _P, _I32, _P, C.c_int, _P, _P]),
     "ssb_step_last_isects": (C.c_int, [_P, _P, _P]),
     "ssb_step_peek": (C.c_int, [_P, _P, _P, _P, _P, _P, _P]),
+    "ssb_step_set_profiling": (C.c_int, [_P, C.c_int]),
+    "ssb_step_get_profile": (C.c_int, [_P, _P, _P]),
     "ssb_launch_count": (_I64, []),
 }
 

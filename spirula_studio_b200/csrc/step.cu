@@ -87,7 +87,7 @@ int ssb_step_create(const SsbStepConfig* cfg, SsbStep** out) {
     s->tw = (cfg->width + kTile - 1) / kTile;
     s->th = (cfg->height + kTile - 1) / kTile;
     s->capacity = cfg->isect_capacity > 0 ? cfg->isect_capacity : 12 * cfg->n_splats;
-    if (s->capacity >= ((int64_t)1 << 31)) s->capacity = ((int64_t)1 << 31) - 1;
+    if (s->capacity >= ((int64_t)1 << 30)) s->capacity = ((int64_t)1 << 30) - 1;
     const int64_t n = cfg->n_splats, P = (int64_t)cfg->width * cfg->height, cap = s->capacity;
     s->keys_ws_bytes = ssb_tile_keys_workspace_bytes(n);
     s->sort_ws_bytes = ssb_sort_workspace_bytes(cap);
@@ -208,6 +208,8 @@ int ssb_step_last_isects(SsbStep* s, int64_t* h_n_isects, void* stream) {
     SSB_REQUIRE(s && h_n_isects, "ssb_step_last_isects: NULL argument");
     SSB_CUDA(cudaMemcpyAsync(h_n_isects, s->n_isects, sizeof(int64_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     SSB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    int e = ssb_sort_check(s->sort_ws, stream);
+    if (e) return e;
     if (*h_n_isects > s->capacity) {
         set_error("ssb_step: %lld (splat, tile) pairs exceed the capacity of %lld; pairs beyond it were dropped", (long long)*h_n_isects, (long long)s->capacity);
         return SSB_ERR_CAPACITY;

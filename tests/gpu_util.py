@@ -77,7 +77,7 @@ def sort_pairs(lib, keys, vals, n_dev, capacity, begin_bit, end_bit):
     sel = C.c_int32(-1)
     L.check(lib.ssb_sort_pairs_u64(L.ptr(keys), L.ptr(vals), L.ptr(kb), L.ptr(vb), L.ptr(n_dev), capacity, begin_bit, end_bit, L.ptr(ws),
                                    ws_bytes, C.byref(sel), None))
-    torch.cuda.synchronize()
+    L.check(lib.ssb_sort_check(L.ptr(ws), None))
     return (kb, vb) if sel.value == 1 else (keys, vals)
 
 

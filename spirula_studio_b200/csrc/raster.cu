@@ -12,9 +12,12 @@
 // early exit once every lane's transmittance is spent.
 //
 // Backward: one warp per 8x8 micro-tile, thread = splat.  The warp scans the
-// tile list back to front, keeps the records whose footprint reaches the
-// micro-tile, and sweeps 32 of them at a time diagonally across the 64 pixels
-// whose running (T, dL/dT) live in shared memory, so each splat's ten gradient
+// tile list back to front (starting at the largest last-blended index of its
+// pixels), keeps the records whose alpha >= 1/255 ellipse reaches the
+// micro-tile, and sweeps them 32 at a time diagonally across the 64 pixels whose
+// running (T, dL/dT) live in shared memory: lane l holds survivor l of the batch
+// and at step t works on pixel t-l, so each pixel meets the survivors strictly
+// back to front.  A splat's ten gradient
 // components accumulate in registers and leave as three 16-byte vector
 // reductions per (splat, micro-tile) -- no per-pixel atomics.
 #include "ssb_common.cuh"
@@ -110,7 +113,25 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
 }
 
 constexpr int kBwdWarps = 4;          // one 16x16 tile per CTA, one 8x8 micro-tile per warp
-constexpr int kSurvCap = 256;
+constexpr int kSurvCap = 256;         // survivors collected per segment (8 per lane)
+
+// Does the alpha >= 1/255 ellipse of a record reach the box [x0,x1]x[y0,y1]
+// (coordinates relative to the splat centre)?  Same construction as the
+// reference's micro-tile test (src/core/Common.cuh:55-77), with a small margin
+// so rounding can only keep a record, never drop one.
+__device__ __forceinline__ bool ellipse_reaches_box(float4 b, float x0, float x1, float y0, float y1) {
+    const float kk = 0.5f / __logf(b.w * 255.0f);
+    const float a = b.x * kk, c = b.z * kk;
+    float bb = b.y * kk;
+    const float wx = -bb / c, wy = -bb / a;
+    const float u0 = fminf(fmaxf(x0 * wx, y0), y1), u1 = fminf(fmaxf(x1 * wx, y0), y1);
+    const float v0 = fminf(fmaxf(y0 * wy, x0), x1), v1 = fminf(fmaxf(y1 * wy, x0), x1);
+    bb *= 2.0f;
+    const float mx = fminf(a * x0 * x0 + bb * x0 * u0 + c * u0 * u0, a * x1 * x1 + bb * x1 * u1 + c * u1 * u1);
+    const float my = fminf(a * v0 * v0 + bb * v0 * y0 + c * y0 * y0, a * v1 * v1 + bb * v1 * y1 + c * y1 * y1);
+    const float mc = fmaxf(fmaxf(x0, -x1), fmaxf(y0, -y1));
+    return !(fminf(mc, fminf(mx, my) - 1.0f) >= 0.01f);
+}
 
 __global__ void __launch_bounds__(kBwdWarps * 32) raster_bwd_kernel(
     const SsbScreenRec* __restrict__ screen, const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ flatten_ids,
@@ -118,10 +139,11 @@ __global__ void __launch_bounds__(kBwdWarps * 32) raster_bwd_kernel(
     const float* __restrict__ render_depth, const float* __restrict__ render_T, const int32_t* __restrict__ last_ids,
     const float* __restrict__ v_rgb, const float* __restrict__ v_depth, const float* __restrict__ v_T,
     SsbScreenRec* __restrict__ v_screen) {
-    __shared__ float2 sT[kBwdWarps][64];       // running T and dL/dT
+    __shared__ float4 sP[kBwdWarps][64];       // running T, dL/dT, pixel centre x, y
     __shared__ float4 sV[kBwdWarps][64];       // dL/d(rgb), dL/d(depth sum)
     __shared__ int32_t sLast[kBwdWarps][64];
-    __shared__ int32_t sSurv[kBwdWarps][kSurvCap];
+    __shared__ int32_t sSurv[kBwdWarps][kSurvCap];   // sorted-list index of each survivor
+    __shared__ int32_t sSurvG[kBwdWarps][kSurvCap];  // its record index
 
     const int img = blockIdx.z;
     const int tile_id = blockIdx.y * tw + blockIdx.x;
@@ -152,7 +174,7 @@ __global__ void __launch_bounds__(kBwdWarps * 32) raster_bwd_kernel(
             vT1 += render_depth[pix] * vc.w * inv_alpha;
             vc.w *= inv_alpha;
         }
-        sT[w][p] = make_float2(T1, vT1);
+        sP[w][p] = make_float4(T1, vT1, (float)x + 0.5f, (float)y + 0.5f);
         sV[w][p] = vc;
         sLast[w][p] = last;
         max_last = max(max_last, last);
@@ -168,57 +190,68 @@ __global__ void __launch_bounds__(kBwdWarps * 32) raster_bwd_kernel(
         while (scan >= range_start && count <= kSurvCap - 32) {
             const int32_t gi = scan - lane;
             bool ok = false;
+            int32_t g = 0;
             if (gi >= range_start) {
-                const int32_t g = flatten_ids[gi];
-                const float4 a = *(const float4*)(screen + g);
+                g = flatten_ids[gi];
+                const float4* r = (const float4*)(screen + g);
+                const float4 a = r[0];
                 ok = (a.x + a.z >= fx0) && (a.x - a.z <= fx1) && (a.y + a.w >= fy0) && (a.y - a.w <= fy1);
+                if (ok) ok = ellipse_reaches_box(r[1], fx0 - a.x, fx1 - a.x, fy0 - a.y, fy1 - a.y);
             }
             const unsigned bal = __ballot_sync(0xffffffffu, ok);
-            if (ok) sSurv[w][count + __popc(bal & ((1u << lane) - 1u))] = gi;
+            if (ok) {
+                const int pos = count + __popc(bal & ((1u << lane) - 1u));
+                sSurv[w][pos] = gi;
+                sSurvG[w][pos] = g;
+            }
             count += __popc(bal);
             scan -= 32;
         }
         __syncwarp();
-        // ---- sweep them 32 at a time
+        // ---- sweep them 32 at a time: lane l holds survivor l of the batch and at step t
+        // works on pixel t - l, so every pixel meets the survivors strictly back to front
         for (int base = 0; base < count; base += 32) {
             const int bs = min(32, count - base);
             const bool active = lane < bs;
-            int32_t sidx = -1, g = 0;
+            int32_t sidx = 0x7fffffff, g = 0;
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a, c = a;
             if (active) {
                 sidx = sSurv[w][base + lane];
-                g = flatten_ids[sidx];
+                g = sSurvG[w][base + lane];
                 const float4* r = (const float4*)(screen + g);
                 a = r[0]; b = r[1]; c = r[2];
             }
             float gx = 0.f, gy = 0.f, gca = 0.f, gcb = 0.f, gcc = 0.f, gop = 0.f, gr = 0.f, gg = 0.f, gb = 0.f, gd = 0.f;
             const int steps = bs + 63;
             for (int t = 0; t < steps; ++t) {
-                const int p = t - lane;
-                if (active && p >= 0 && p < 64 && sidx <= sLast[w][p]) {
-                    const float px = (float)(mx0 + (p & 7)) + 0.5f, py = (float)(my0 + (p >> 3)) + 0.5f;
-                    float vis, sigma, dx, dy;
-                    const float alpha = eval_alpha(a, b, px, py, vis, sigma, dx, dy);
-                    if (alpha > kAlphaThreshold) {
-                        const float2 tt = sT[w][p];
+                const unsigned p = (unsigned)(t - lane);
+                if (p < 64u && sidx <= sLast[w][p]) {      // inactive lanes carry sidx = INT_MAX
+                    const float4 pp = sP[w][p];
+                    const float dx = a.x - pp.z, dy = a.y - pp.w;
+                    const float sigma = 0.5f * (b.x * dx * dx + b.z * dy * dy) + b.y * dx * dy;
+                    const float vis = __expf(-sigma);
+                    const float ov = b.w * vis;
+                    const float alpha = fminf(0.999f, ov);
+                    if (sigma >= 0.f && alpha > kAlphaThreshold) {
                         const float4 vc = sV[w][p];
-                        const float ra = 1.0f / (1.0f - alpha);
-                        const float T0 = tt.x * ra;
+                        const float ra = __fdividef(1.0f, 1.0f - alpha);
+                        const float T0 = pp.x * ra;
                         const float cdot = c.x * vc.x + c.y * vc.y + c.z * vc.z + c.w * vc.w;
-                        const float v_alpha = T0 * cdot - tt.y * T0;
+                        const float v_alpha = T0 * (cdot - pp.y);
                         const float wgt = alpha * T0;
-                        const float v_T0 = alpha * cdot + tt.y * (1.0f - alpha);
-                        if (sigma >= 0.f && b.w * vis <= 0.999f) {
-                            const float v_sigma = -b.w * vis * v_alpha;
-                            gca += 0.5f * v_sigma * dx * dx;
-                            gcb += v_sigma * dx * dy;
-                            gcc += 0.5f * v_sigma * dy * dy;
-                            gx += v_sigma * (b.x * dx + b.y * dy);
-                            gy += v_sigma * (b.y * dx + b.z * dy);
+                        const float v_T0 = alpha * cdot + pp.y * (1.0f - alpha);
+                        if (ov <= 0.999f) {
+                            const float v_sigma = -ov * v_alpha;
+                            const float sx = v_sigma * dx, sy = v_sigma * dy;
+                            gca += 0.5f * sx * dx;
+                            gcb += sx * dy;
+                            gcc += 0.5f * sy * dy;
+                            gx += b.x * sx + b.y * sy;
+                            gy += b.y * sx + b.z * sy;
                             gop += vis * v_alpha;
                         }
                         gr += vc.x * wgt; gg += vc.y * wgt; gb += vc.z * wgt; gd += vc.w * wgt;
-                        sT[w][p] = make_float2(T0, v_T0);
+                        *(float2*)&sP[w][p] = make_float2(T0, v_T0);
                     }
                 }
                 __syncwarp();

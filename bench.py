@@ -24,6 +24,10 @@ import time
 
 import numpy as np
 
+# keep stdout to the one JSON line: NCCL_DEBUG=VERSION/INFO prints to stdout
+if os.environ.get("NCCL_DEBUG", "VERSION").upper() in ("VERSION", "INFO"):
+    os.environ["NCCL_DEBUG"] = "WARN"
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)

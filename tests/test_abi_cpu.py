@@ -1,0 +1,54 @@
+"""The C ABI without a GPU: the library loads, exports every symbol the header
+declares, and validates arguments before touching the device."""
+import ctypes as C
+import os
+import re
+
+from spirula_studio_b200 import lib as L
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "ssb.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ssb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    lib = L.load()
+    names = declared_symbols()
+    assert len(names) >= 25
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in ssb.h but not exported"
+        assert n in L.SIGNATURES, f"{n} has no ctypes signature in lib.py"
+    assert sorted(L.SIGNATURES) == names
+
+
+def test_version_and_pure_host_helpers():
+    lib = L.load()
+    assert b"sm_100a" in lib.ssb_version_string()
+    # smallest b with 2^b > n_tiles (src/kernels/tile/IntersectTile.cu:489-490)
+    for n, want in ((1, 1), (2, 2), (3, 2), (4, 3), (8160, 13), (8191, 13), (8192, 14)):
+        assert lib.ssb_tile_n_bits(n) == want
+    assert lib.ssb_tile_keys_workspace_bytes(1_000_000) >= 8_000_000
+    assert lib.ssb_sort_workspace_bytes(12_000_000) > 0
+
+
+def test_argument_errors_are_statuses_not_crashes():
+    lib = L.load()
+    assert lib.ssb_project_fwd(None, None, 10, None, None, None, None, None, None) == L.SSB_ERR_INVALID_ARGUMENT
+    assert b"NULL" in lib.ssb_last_error_string()
+    assert lib.ssb_step_create(None, None) == L.SSB_ERR_INVALID_ARGUMENT
+    cfg = L.SsbAdamConfig(1e-3, 1e-3, 1e-3, 1e-3, 1e-3, 1e-3, 0.0, 1.0, 0, 0)   # step 0 is invalid
+    s = L.SsbSplats()
+    assert lib.ssb_adam_step(C.byref(s), C.byref(s), C.byref(s), C.byref(s), 0, 4, C.byref(cfg), None) == L.SSB_ERR_INVALID_ARGUMENT
+    sel = C.c_int32(0)
+    one = C.c_void_p(8)
+    assert lib.ssb_sort_pairs_u64(one, one, one, one, one, 10, 40, 30, one, 1 << 30, C.byref(sel), None) == L.SSB_ERR_INVALID_ARGUMENT
+    assert lib.ssb_quant_encode(one, 10, 12, one, one, None) == L.SSB_ERR_INVALID_ARGUMENT
+    cams = L.SsbCameras()
+    cams.count, cams.width, cams.height, cams.model = 1, 64, 64, L.CAMERA_FISHEYE
+    sp = L.SsbSplats()
+    sp.features_sh = 8
+    assert lib.ssb_project_fwd(C.byref(sp), None, 0, C.byref(cams), one, one, None, one, None) == L.SSB_ERR_UNSUPPORTED

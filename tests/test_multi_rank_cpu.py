@@ -1,0 +1,96 @@
+"""The multi-GPU iteration's host logic on two CPU ranks (gloo): views are
+split into contiguous blocks, each rank back-propagates its own views, the
+gradient buffers are summed with an all-reduce, and both ranks then apply the
+same Adam update with grad_scale = 1 / total views -- which must equal the
+single-process multi-view iteration (src/engine/EngineTrainStep.cpp:287-437)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+import torch.distributed as dist  # noqa: E402
+import torch.multiprocessing as mp  # noqa: E402
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from bench import shard  # noqa: E402
+
+
+def test_shard_covers_every_view_once():
+    for total in (1, 2, 15, 16, 17, 64):
+        for world in (1, 2, 3, 4, 8):
+            seen = []
+            for r in range(world):
+                s, n = shard(total, world, r)
+                seen += list(range(s, s + n))
+            assert seen == list(range(total))
+            sizes = [shard(total, world, r)[1] for r in range(world)]
+            assert max(sizes) - min(sizes) <= 1
+
+
+def _scene():
+    from spirula_studio_b200 import scenes
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=1500, width=96, height=64, n_views=3)
+    cfg.rig, cfg.rig_radius, cfg.log_scale_mu = "ring", 3.0, -2.8
+    return cfg, scenes.make_splats(cfg), *scenes.make_cameras(cfg)
+
+
+def _view_grads(cfg, sp, vm, K, views):
+    from oracle import pyoracle as O
+    from spirula_studio_b200 import scenes
+    names = ("means", "quats", "scales", "opacities", "features_dc", "features_sh")
+    tot = {k: np.zeros_like(sp[k]) for k in names}
+    for v in views:
+        ch = O.forward_chain(sp, vm[v:v + 1], K[v:v + 1], cfg.width, cfg.height)
+        vr, _ = O.loss_l1_ssim(ch["render"]["rgb"], scenes.make_target(cfg, v).reshape(-1, 3), 1, cfg.height, cfg.width)
+        gs = O.raster_bwd(ch["proj"], ch["offsets"], ch["sorted_vals"], 1, cfg.n_splats, cfg.width, cfg.height, ch["render"], vr)
+        g = O.project_bwd(sp, vm[v:v + 1], K[v:v + 1], cfg.width, cfg.height, ch["proj"]["aabb"], gs)
+        for k in names:
+            tot[k] += g[k].reshape(tot[k].shape)
+    return tot
+
+
+def _flat(d):
+    return np.concatenate([d[k].reshape(-1) for k in ("means", "quats", "scales", "opacities", "features_dc", "features_sh")])
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from oracle import pyoracle as O
+    O.set_num_threads(2)
+    cfg, sp, vm, K = _scene()
+    s, n = shard(cfg.n_views, world, rank)
+    g = _view_grads(cfg, sp, vm, K, range(s, s + n))
+    flat = torch.from_numpy(_flat(g))
+    dist.all_reduce(flat, op=dist.ReduceOp.SUM)
+    # every rank applies the same update to its replica
+    p = {k: v.copy() for k, v in sp.items()}
+    off, gsum = 0, {}
+    for k in ("means", "quats", "scales", "opacities", "features_dc", "features_sh"):
+        gsum[k] = flat[off: off + p[k].size].numpy().reshape(p[k].shape).copy()
+        off += p[k].size
+    m1 = {k: np.zeros_like(v) for k, v in p.items()}
+    m2 = {k: np.zeros_like(v) for k, v in p.items()}
+    O.adam_geometry(p, gsum, m1, m2, 1, cfg.lrs, grad_scale=1.0 / cfg.n_views)
+    np.save(os.path.join(out_dir, f"grads_{rank}.npy"), flat.numpy())
+    np.save(os.path.join(out_dir, f"means_{rank}.npy"), p["means"])
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_iteration_equals_single_process(tmp_path):
+    world, port = 2, 29000 + os.getpid() % 2000
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    cfg, sp, vm, K = _scene()
+    ref = _flat(_view_grads(cfg, sp, vm, K, range(cfg.n_views)))
+    g0, g1 = (np.load(tmp_path / f"grads_{r}.npy") for r in range(2))
+    assert np.array_equal(g0, g1)                                   # both ranks hold the same sum
+    assert np.allclose(g0, ref, rtol=1e-5, atol=1e-9)               # = the one-process sum (fp32 order only)
+    m0, m1 = (np.load(tmp_path / f"means_{r}.npy") for r in range(2))
+    assert np.array_equal(m0, m1)                                   # replicas stay identical
+    assert np.abs(m0 - sp["means"]).max() > 0

@@ -6,16 +6,16 @@
 // CPU baseline by bench.py.  Nothing in the shipped library calls into this
 // file.  Every function cites the reference file:line it restates.
 //
-// PARITY PIN STATUS: the reference tree holds no golden vectors for this path
-// (its parity tools dump-then-compare against a CUDA build made on the spot),
-// and the reference has no CPU implementation.  This restatement is pinned by
-//   (1) fixtures produced by running the reference's own CUDA launchers
-//       (oracle/_ref, built from the reference sources by oracle/Makefile)
-//       when such fixtures are present under tests/golden/, and
-//   (2) internal consistency: the backward passes are checked against central
-//       finite differences of the forward passes, and the integer stages
-//       against std::stable_sort / brute-force definitions.
-// Where (1) is absent for a stage, that stage's parity is "unpinned".
+// PARITY PIN STATUS: pinned.  The reference tree holds no golden vectors for this
+// path (its parity tools dump-then-compare against a CUDA build made on the spot)
+// and has no CPU implementation, so the pins are outputs of the reference's OWN
+// device code: oracle/Makefile.ref compiles the reference's kernels from the
+// sources where they lie into oracle/_ref/libssb_ref.so, tests/golden/make_golden.py
+// runs them on a B200 on seeded scenes, and tests/test_golden_cpu.py compares every
+// function below, stage by stage, with those fixtures (tests/golden/*.npz) under
+// the reference parity tools' tolerance model.  In addition the backward passes
+// are checked against central finite differences of the forward passes, and the
+// integer stages against std::stable_sort / brute-force definitions.
 //
 // Numerics: plain IEEE fp32, compiled with -ffp-contract=off so that no FMA is
 // formed behind the source.  The integer-producing stage (tile counting and key

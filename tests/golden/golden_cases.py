@@ -1,0 +1,68 @@
+"""Seeded inputs of the golden fixtures.  Imported both by make_golden.py (which
+feeds them to the reference's device code on a GPU) and by the tests (which feed
+them to the oracle and to the CUDA library), so the fixtures only store outputs.
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from spirula_studio_b200 import scenes  # noqa: E402
+
+CASES = {
+    # two ring cameras, splats a few pixels wide, moderately deep tile lists
+    "ring2": dict(seed=101, n=1200, w=96, h=64, views=2, scale_mu=-2.6, extent=1.0),
+    # one camera, large overlapping splats: long lists, saturated pixels, early termination
+    "dense1": dict(seed=202, n=600, w=64, h=48, views=1, scale_mu=-1.6, extent=0.7),
+}
+
+
+def build_case(name):
+    c = CASES[name]
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=c["n"], width=c["w"], height=c["h"], n_views=c["views"], name=name)
+    cfg.log_scale_mu = c["scale_mu"]
+    cfg.mean_extent = c["extent"]
+    if c["views"] > 1:
+        cfg.rig, cfg.rig_radius = "ring", 3.0
+    sp = scenes.make_splats(cfg, seed=c["seed"])
+    vm, K = scenes.make_cameras(cfg, seed=c["seed"] + 7)
+    return cfg, sp, vm, K
+
+
+def raster_cotangents(name, n_pixels):
+    rng = np.random.default_rng(CASES[name]["seed"] + 1)
+    v_rgb = rng.normal(size=(n_pixels, 3)).astype(np.float32)
+    v_depth = (0.1 * rng.normal(size=n_pixels)).astype(np.float32)
+    v_T = (0.1 * rng.normal(size=n_pixels)).astype(np.float32)
+    return v_rgb, v_depth, v_T
+
+
+def loss_inputs():
+    out = {}
+    for tag, (B, H, W, seed) in dict(a=(1, 48, 64, 5), b=(2, 37, 53, 6)).items():
+        rng = np.random.default_rng(seed)
+        out[tag] = (B, H, W, rng.random((B * H * W, 3), dtype=np.float32), rng.random((B * H * W, 3), dtype=np.float32))
+    return out
+
+
+def adam_inputs():
+    n = 700
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=n)
+    params = scenes.make_splats(cfg, seed=303)
+    rng = np.random.default_rng(304)
+    grads = [{k: (rng.normal(size=v.shape) * 1e-3).astype(np.float32) for k, v in params.items()} for _ in range(3)]
+    out = dict(n=n, params=params, grads=grads, lrs=cfg.lrs, grad_scale=0.25)
+    from oracle import pyoracle as O
+    for bits in (16, 8):
+        numel = 45 * 300 + 11
+        x0 = rng.normal(0, 0.05, size=numel).astype(np.float32)
+        vp, vb = O.quant_encode(x0, bits)
+        nb = (numel + 255) // 256
+        out[f"qq{bits}"] = dict(numel=numel, value_packed=vp, value_bounds=vb, optim_packed=np.zeros(numel * 2, np.uint8),
+                                optim_bounds=np.zeros(nb * 4, np.float32),
+                                grads=[(rng.normal(size=numel) * 1e-3).astype(np.float32) for _ in range(3)])
+    return out

@@ -1,0 +1,160 @@
+"""Generates the golden fixtures in this directory by running the REFERENCE's own
+device code (oracle/_ref/libssb_ref.so, built from the reference sources by
+oracle/Makefile.ref) on a GPU, on small seeded scenes.
+
+    python tests/golden/make_golden.py [out_dir]
+
+Inputs are not stored: they are regenerated from `golden_cases.py` (same seeds).
+Every stage is run stage-isolated on the reference's own upstream outputs, so a
+fixture holds exactly what that stage of the reference produced for the inputs
+the previous fixture records.
+"""
+import ctypes as C
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, HERE)
+
+from golden_cases import CASES, build_case, loss_inputs, adam_inputs, raster_cotangents  # noqa: E402
+
+DEV = "cuda:0"
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def P(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def check(rc, what):
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with {rc}")
+
+
+def run_case(ref, name, out_dir):
+    cfg, sp, vm, K = build_case(name)
+    n, W, H, I = cfg.n_splats, cfg.width, cfg.height, vm.shape[0]
+    d = {k: dev(v.reshape(-1)) for k, v in sp.items()}
+    d_vm, d_K = dev(vm), dev(K)
+    m = I * n
+    z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=DEV)
+    aabb, depths, radii = z(m, 4), z(m), z(n)
+    xy, depth, conic, opac, rgb = z(m, 2), z(m), z(m, 3), z(m), z(m, 3)
+    check(ref.ref_project_fwd(I, n, W, H, P(d["means"]), P(d["quats"]), P(d["scales"]), P(d["opacities"]), P(d["features_dc"]),
+                              P(d["features_sh"]), None, None, 32, C.c_int64(256), P(d_vm), P(d_K), P(aabb), P(depths), P(radii),
+                              P(xy), P(depth), P(conic), P(opac), P(rgb)), "ref_project_fwd")
+    # culled pairs: the reference leaves their screen entries unwritten (zeros here)
+    out = dict(aabb=aabb, depths=depths, radii=radii, xy=xy, depth=depth, conic=conic, opac=opac, rgb=rgb)
+
+    cap = 64 * n
+    tps, cum = z(m, dt=torch.int64), z(m, dt=torch.int64)
+    ids_a, ids_b = z(cap, dt=torch.int64), z(cap, dt=torch.int64)
+    fl_a, fl_b = z(cap, dt=torch.int32), z(cap, dt=torch.int32)
+    tw, th = (W + 15) // 16, (H + 15) // 16
+    offs = z(I * tw * th, dt=torch.int32)
+    M, sel = C.c_int64(0), C.c_int32(0)
+    check(ref.ref_intersect_tile(I, n, W, H, P(aabb), P(depths), P(xy), P(conic), P(opac), P(tps), P(cum), C.c_int64(cap),
+                                 P(ids_a), P(ids_b), P(fl_a), P(fl_b), P(offs), C.byref(M), C.byref(sel)), "ref_intersect_tile")
+    M = M.value
+    ids, fl = (ids_b, fl_b) if sel.value else (ids_a, fl_a)
+    out.update(tiles_per_splat=tps.to(torch.int32), sorted_ids=ids[:M], sorted_flat=fl[:M], offsets=offs)
+
+    P_ = I * H * W
+    r_rgb, r_depth, r_T, r_last = z(P_, 3), z(P_), z(P_), z(P_, dt=torch.int32)
+    check(ref.ref_raster_fwd(I, n, M, W, H, P(xy), P(depth), P(conic), P(opac), P(rgb), P(offs), P(fl), P(r_rgb), P(r_depth), P(r_T), P(r_last)),
+          "ref_raster_fwd")
+    out.update(render_rgb=r_rgb, render_depth=r_depth, render_T=r_T, last_ids=r_last)
+
+    v_rgb, v_depth, v_T = (dev(a) for a in raster_cotangents(name, P_))
+    g_xy, g_depth, g_conic, g_opac, g_rgb = z(m, 2), z(m), z(m, 3), z(m), z(m, 3)
+    check(ref.ref_raster_bwd(I, n, M, W, H, P(xy), P(depth), P(conic), P(opac), P(rgb), P(offs), P(fl), P(r_rgb), P(r_depth), P(r_T), P(r_last),
+                             P(v_rgb), P(v_depth), P(v_T), P(g_xy), P(g_depth), P(g_conic), P(g_opac), P(g_rgb)), "ref_raster_bwd")
+    out.update(v_xy=g_xy, v_depth=g_depth, v_conic=g_conic, v_opac=g_opac, v_rgb=g_rgb)
+
+    g = {k: torch.zeros_like(t) for k, t in d.items()}
+    check(ref.ref_project_bwd(I, n, W, H, P(d["means"]), P(d["quats"]), P(d["scales"]), P(d["opacities"]), P(d["features_dc"]),
+                              P(d["features_sh"]), None, None, 32, C.c_int64(256), P(d_vm), P(d_K), P(aabb),
+                              P(g_xy), P(g_depth), P(g_conic), P(g_opac), P(g_rgb),
+                              P(g["means"]), P(g["quats"]), P(g["scales"]), P(g["opacities"]), P(g["features_dc"]), P(g["features_sh"])), "ref_project_bwd")
+    out.update({"g_" + k: t for k, t in g.items()})
+    np.savez_compressed(os.path.join(out_dir, f"{name}.npz"), **{k: t.cpu().numpy() for k, t in out.items()})
+    print(name, "pairs", M, "visible", int((aabb[:, 2] > aabb[:, 0]).sum()))
+
+
+def run_loss(ref, out_dir):
+    out = {}
+    for tag, (B, H, W, render, gt) in loss_inputs().items():
+        v = torch.zeros(B * H * W, 3, device=DEV)
+        s = torch.zeros(1, device=DEV)
+        d_render, d_gt = dev(render), dev(gt)      # named: a temporary's memory would be reused by the next one
+        check(ref.ref_ssim_inplace(B, H, W, P(d_render), P(d_gt), C.c_float(-0.2), P(v), P(s)), "ref_ssim_inplace")
+        out[f"{tag}_grad"] = v.cpu().numpy()
+        out[f"{tag}_ssim"] = s.cpu().numpy()
+    np.savez_compressed(os.path.join(out_dir, "ssim.npz"), **out)
+
+
+def run_adam(ref, out_dir):
+    inp = adam_inputs()
+    out = {}
+    # geometry + plain Adam, three steps with fresh gradients each
+    p = {k: dev(v.reshape(-1)) for k, v in inp["params"].items()}
+    m1 = {k: torch.zeros_like(t) for k, t in p.items()}
+    m2 = {k: torch.zeros_like(t) for k, t in p.items()}
+    n = inp["n"]
+    lr = inp["lrs"]
+    for step, grads in enumerate(inp["grads"], start=1):
+        g = {k: dev(v.reshape(-1)) for k, v in grads.items()}
+        check(ref.ref_adam_geometry(C.c_int64(n), step, C.c_float(inp["grad_scale"]), 0, C.c_float(lr["lr_means"]), C.c_float(lr["lr_quats"]),
+                                    C.c_float(lr["lr_scales"]), C.c_float(lr["lr_opacities"]),
+                                    P(p["means"]), P(g["means"]), P(m1["means"]), P(m2["means"]),
+                                    P(p["quats"]), P(g["quats"]), P(m1["quats"]), P(m2["quats"]),
+                                    P(p["scales"]), P(g["scales"]), P(m1["scales"]), P(m2["scales"]),
+                                    P(p["opacities"]), P(g["opacities"]), P(m1["opacities"]), P(m2["opacities"])), "ref_adam_geometry")
+        check(ref.ref_adam_plain(C.c_int64(3 * n), step, C.c_float(lr["lr_features_dc"]), C.c_float(0.0), C.c_float(0.5 / 0.28209479177387814),
+                                 C.c_float(inp["grad_scale"]), 0, P(p["features_dc"]), P(g["features_dc"]), P(m1["features_dc"]), P(m2["features_dc"])),
+              "ref_adam_plain dc")
+        check(ref.ref_adam_plain(C.c_int64(45 * n), step, C.c_float(lr["lr_features_sh"]), C.c_float(0.0), C.c_float(0.0),
+                                 C.c_float(inp["grad_scale"]), 0, P(p["features_sh"]), P(g["features_sh"]), P(m1["features_sh"]), P(m2["features_sh"])),
+              "ref_adam_plain sh")
+        for k in p:
+            out[f"p{step}_{k}"] = p[k].cpu().numpy()
+        if step == 3:
+            for k in p:
+                out[f"m1_{k}"] = m1[k].cpu().numpy()
+                out[f"m2_{k}"] = m2[k].cpu().numpy()
+    # doubly quantised SH Adam: one step from a given encoded state, for 16- and 8-bit values
+    for bits in (16, 8):
+        q = inp[f"qq{bits}"]
+        vp, vb, op, ob = dev(q["value_packed"]), dev(q["value_bounds"]), dev(q["optim_packed"]), dev(q["optim_bounds"])
+        for step, grad in enumerate(q["grads"], start=1):
+            d_grad = dev(grad)
+            check(ref.ref_adam_qq(C.c_int64(q["numel"]), step, C.c_float(lr["lr_features_sh"]), C.c_float(0.0), C.c_float(inp["grad_scale"]), 0, bits,
+                                  P(d_grad), P(op), P(ob), P(vp), P(vb)), "ref_adam_qq")
+            out[f"qq{bits}_s{step}_value_packed"] = vp.cpu().numpy()
+            out[f"qq{bits}_s{step}_value_bounds"] = vb.cpu().numpy()
+            out[f"qq{bits}_s{step}_optim_packed"] = op.cpu().numpy()
+            out[f"qq{bits}_s{step}_optim_bounds"] = ob.cpu().numpy()
+    np.savez_compressed(os.path.join(out_dir, "adam.npz"), **out)
+
+
+def main():
+    out_dir = sys.argv[1] if len(sys.argv) > 1 else HERE
+    os.makedirs(out_dir, exist_ok=True)
+    ref = C.CDLL(os.path.join(ROOT, "oracle", "_ref", "libssb_ref.so"))
+    for name in CASES:
+        run_case(ref, name, out_dir)
+    run_loss(ref, out_dir)
+    run_adam(ref, out_dir)
+    print("wrote fixtures to", out_dir)
+
+
+if __name__ == "__main__":
+    main()

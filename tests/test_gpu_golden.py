@@ -1,0 +1,175 @@
+"""The CUDA library against fixtures produced by the REFERENCE's own device code
+(tests/golden/*.npz; see tests/golden/make_golden.py), stage by stage on the
+reference's own upstream outputs, through the C ABI."""
+import ctypes as C
+import os
+import sys
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "golden"))
+
+from golden_cases import CASES, adam_inputs, build_case, loss_inputs, raster_cotangents  # noqa: E402
+from spirula_studio_b200 import lib as L  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return L.load()
+
+
+@pytest.fixture(scope="module")
+def U():
+    from tests import gpu_util
+    return gpu_util
+
+
+def load(name):
+    return dict(np.load(os.path.join(HERE, "golden", f"{name}.npz")))
+
+
+def ref_proj(gold):
+    return {k: gold[k] for k in ("aabb", "depths", "xy", "depth", "conic", "opac", "rgb")}
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_projection_forward_vs_reference(lib, U, name):
+    cfg, sp, vm, K = build_case(name)
+    gold = load(name)
+    got = U.project_fwd(lib, U.splats_dev(sp), vm, K, cfg.width, cfg.height)
+    aabb = got["aabb"].cpu().numpy()
+    keep_ref, keep_got = gold["aabb"][:, 2] > gold["aabb"][:, 0], aabb[:, 2] > aabb[:, 0]
+    assert (keep_ref != keep_got).mean() <= 2e-3
+    both = keep_ref & keep_got
+    scr = U.unpack_screen(lib, got["rec"], vm.shape[0] * cfg.n_splats)
+    assert U.close_frac(aabb[both], gold["aabb"][both], 5e-3, 5e-4) <= 2e-3
+    for k in ("xy", "depth", "conic", "opac", "rgb"):
+        assert U.close_frac(scr[k][both], gold[k][both], 5e-3, 5e-4) <= 2e-3, k
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_tile_stage_vs_reference(lib, U, name):
+    cfg, sp, vm, K = build_case(name)
+    gold = load(name)
+    n, W, H, I = cfg.n_splats, cfg.width, cfg.height, vm.shape[0]
+    rec = U.pack_screen(lib, ref_proj(gold))
+    cap = 64 * n
+    st, M, counts, cum, keys, vals, n_dev = U.tile_keys(lib, U.dev(gold["aabb"]), U.dev(gold["depths"]), rec, I * n, n, W, H, cap)
+    assert st == 0
+    diff = counts.cpu().numpy() != gold["tiles_per_splat"]
+    assert diff.mean() <= 2e-3
+    tw, th = (W + 15) // 16, (H + 15) // 16
+    end_bit = 32 + lib.ssb_tile_n_bits(tw * th * I)
+    sk, sv = U.sort_pairs(lib, keys, vals, n_dev, cap, 0, end_bit)
+    offs = U.tile_ranges(lib, sk, n_dev, cap, tw * th * I)
+    if not diff.any():
+        assert M == gold["sorted_ids"].size
+        assert np.array_equal(sk.cpu().numpy()[:M], gold["sorted_ids"]) and np.array_equal(sv.cpu().numpy()[:M], gold["sorted_flat"])
+        assert np.array_equal(offs.cpu().numpy(), gold["offsets"])
+    # our range kernel on the reference's own sorted keys: exact
+    n_ref = torch.tensor([gold["sorted_ids"].size], dtype=torch.int64, device=U.DEV)
+    offs2 = U.tile_ranges(lib, U.dev(gold["sorted_ids"]), n_ref, gold["sorted_ids"].size, tw * th * I)
+    assert np.array_equal(offs2.cpu().numpy(), gold["offsets"])
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_raster_forward_vs_reference(lib, U, name):
+    cfg, sp, vm, K = build_case(name)
+    gold = load(name)
+    I, W, H = vm.shape[0], cfg.width, cfg.height
+    rec = U.pack_screen(lib, ref_proj(gold))
+    n_dev = torch.tensor([gold["sorted_flat"].size], dtype=torch.int64, device=U.DEV)
+    got = U.raster_fwd(lib, rec, U.dev(gold["offsets"]), U.dev(gold["sorted_flat"]), n_dev, I, W, H)
+    d = np.abs(got["rgb"].cpu().numpy() - gold["render_rgb"])
+    assert d.max() <= 5e-3 and (d.max(axis=1) > 1e-4).mean() <= 2e-3
+    assert np.abs(got["T"].cpu().numpy() - gold["render_T"]).max() <= 5e-3
+    assert (got["last_ids"].cpu().numpy() != gold["last_ids"]).mean() <= 2e-3
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_raster_backward_vs_reference(lib, U, name):
+    cfg, sp, vm, K = build_case(name)
+    gold = load(name)
+    I, W, H, n = vm.shape[0], cfg.width, cfg.height, cfg.n_splats
+    v_rgb, v_depth, v_T = (U.dev(a) for a in raster_cotangents(name, I * H * W))
+    rec = U.pack_screen(lib, ref_proj(gold))
+    n_dev = torch.tensor([gold["sorted_flat"].size], dtype=torch.int64, device=U.DEV)
+    render = dict(depth=U.dev(gold["render_depth"]), T=U.dev(gold["render_T"]), last_ids=U.dev(gold["last_ids"]))
+    v_rec = U.raster_bwd(lib, rec, U.dev(gold["offsets"]), U.dev(gold["sorted_flat"]), n_dev, I, W, H, render, v_rgb, v_depth, v_T, pairs=I * n)
+    got = U.vrec_to_arrays(v_rec, I * n)
+    for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb"):
+        ref = gold[k].reshape(got[k].shape)
+        assert U.close_frac(got[k], ref, 1e-4 * np.abs(ref).max(), 2e-3) <= 5e-3, k
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_projection_backward_vs_reference(lib, U, name):
+    cfg, sp, vm, K = build_case(name)
+    gold = load(name)
+    I, n = vm.shape[0], cfg.n_splats
+    spd = U.splats_dev(sp)
+    grads = {k: torch.zeros_like(t) for k, t in spd.items()}
+    s, g = L.splats_struct(spd), L.splats_struct(grads)
+    d_vm, d_K, d_aabb = U.dev(vm), U.dev(K), U.dev(gold["aabb"])
+    cams = L.cameras_struct(d_vm, d_K, cfg.width, cfg.height)
+    vrec = U.arrays_to_vrec({k: gold[k].reshape(I * n, -1) if gold[k].ndim > 1 else gold[k] for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")}, I * n)
+    L.check(lib.ssb_project_bwd(C.byref(s), None, n, C.byref(cams), L.ptr(d_aabb), L.ptr(vrec), C.byref(g), 0, None))
+    torch.cuda.synchronize()
+    for k in grads:
+        ref = gold["g_" + k]
+        assert U.close_frac(grads[k].cpu().numpy().reshape(-1), ref.reshape(-1), 1e-4 * np.abs(ref).max(), 2e-3) <= 5e-3, k
+
+
+def test_ssim_vs_reference(lib, U):
+    gold = load("ssim")
+    for tag, (B, H, W, render, gt) in loss_inputs().items():
+        d_render, d_gt = U.dev(render), U.dev(gt)
+        d_v, d_l = torch.zeros(B * H * W, 3, device=U.DEV), torch.zeros(3, device=U.DEV)
+        L.check(lib.ssb_loss_l1_ssim_fwdbwd(L.ptr(d_render), L.ptr(d_gt), B, H, W, 0.0, 0.2, L.ptr(d_v), L.ptr(d_l), None))
+        torch.cuda.synchronize()
+        ref = gold[f"{tag}_grad"]
+        assert U.close_frac(d_v.cpu().numpy(), ref, 1e-4 * np.abs(ref).max(), 1e-3) == 0.0
+
+
+def test_adam_vs_reference(lib, U):
+    gold = load("adam")
+    inp = adam_inputs()
+    n, lr, gs = inp["n"], inp["lrs"], inp["grad_scale"]
+    p = {k: U.dev(v.reshape(-1)) for k, v in inp["params"].items()}
+    m1 = {k: torch.zeros_like(t) for k, t in p.items()}
+    m2 = {k: torch.zeros_like(t) for k, t in p.items()}
+    for step, grads in enumerate(inp["grads"], start=1):
+        g = {k: U.dev(v.reshape(-1)) for k, v in grads.items()}
+        cfg = L.SsbAdamConfig(lr["lr_means"], lr["lr_quats"], lr["lr_scales"], lr["lr_opacities"], lr["lr_features_dc"], lr["lr_features_sh"],
+                              0.0, gs, step, 0)
+        structs = [L.splats_struct(d) for d in (p, g, m1, m2)]
+        L.check(lib.ssb_adam_step(*[C.byref(s) for s in structs], 0, n, C.byref(cfg), None))
+        torch.cuda.synchronize()
+        for k in p:
+            assert U.close_frac(p[k].cpu().numpy(), gold[f"p{step}_{k}"], 5e-6, 1e-4) <= 1e-3, (k, step)
+    for bits in (16, 8):
+        q = inp[f"qq{bits}"]
+        view = np.uint16 if bits == 16 else np.uint8
+        state = [q["value_packed"], q["value_bounds"], q["optim_packed"], q["optim_bounds"]]
+        for step, grad in enumerate(q["grads"], start=1):
+            vp, vb, op, ob = (U.dev(a) for a in state)
+            d_g = U.dev(grad)
+            cfg = L.SsbAdamConfig(0, 0, 0, 0, 0, lr["lr_features_sh"], 0.0, gs, step, 0)
+            L.check(lib.ssb_adam_step_sh_quantized(L.ptr(d_g), L.ptr(op), L.ptr(ob), L.ptr(vp), L.ptr(vb), bits, 0, q["numel"], q["numel"],
+                                                   C.byref(cfg), None))
+            torch.cuda.synchronize()
+            rv, rb, ro, rob = (gold[f"qq{bits}_s{step}_{s}"] for s in ("value_packed", "value_bounds", "optim_packed", "optim_bounds"))
+            dv = np.abs(vp.cpu().numpy().view(view).astype(np.int64) - rv.view(view).astype(np.int64))
+            do = np.abs(op.cpu().numpy().astype(np.int64) - ro.astype(np.int64))
+            assert dv.max() <= 1 and do.max() <= 1, (bits, step)
+            assert (dv > 0).mean() <= 5e-2 and (do > 0).mean() <= 5e-2
+            assert np.allclose(vb.cpu().numpy(), rb, rtol=1e-4, atol=1e-7)
+            state = [rv, rb, ro, rob]

@@ -126,19 +126,52 @@ __global__ void __launch_bounds__(256) adam_plain_kernel(
     }
 }
 
-__device__ __forceinline__ float block_min(float v, float* sh) {
-    v = fminf(v, __shfl_xor_sync(0xffffffffu, v, 16)); v = fminf(v, __shfl_xor_sync(0xffffffffu, v, 8));
-    v = fminf(v, __shfl_xor_sync(0xffffffffu, v, 4)); v = fminf(v, __shfl_xor_sync(0xffffffffu, v, 2));
-    v = fminf(v, __shfl_xor_sync(0xffffffffu, v, 1));
-    __syncthreads();
-    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
-    __syncthreads();
-    float r = sh[0];
-#pragma unroll
-    for (int k = 1; k < 8; ++k) r = fminf(r, sh[k]);
+__device__ __forceinline__ float sqrt_approx(float x) {
+    float r;
+    asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
     return r;
 }
-__device__ __forceinline__ float block_max(float v, float* sh) { return -block_min(-v, sh); }
+
+// Order-preserving map float -> uint32, so min/max run on the integer redux unit.
+__device__ __forceinline__ uint32_t f2ord(float f) {
+    uint32_t b = __float_as_uint(f);
+    return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
+}
+__device__ __forceinline__ float ord2f(uint32_t k) {
+    return __uint_as_float(k ^ ((k >> 31) ? 0x80000000u : 0xffffffffu));
+}
+
+// Block-wide (256 threads) minima of NMIN values and maxima of NMAX values in two barriers:
+// one redux.sync per value in each warp, 8 partials per value through shared memory, then
+// one more redux by the first warp.
+template <int NMIN, int NMAX>
+__device__ __forceinline__ void block_minmax(const float (&vmin)[NMIN], const float (&vmax)[NMAX], float (&omin)[NMIN], float (&omax)[NMAX],
+                                             uint32_t (*sh)[8]) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    uint32_t r[NMIN + NMAX];
+#pragma unroll
+    for (int k = 0; k < NMIN; ++k) r[k] = __reduce_min_sync(0xffffffffu, f2ord(vmin[k]));
+#pragma unroll
+    for (int k = 0; k < NMAX; ++k) r[NMIN + k] = __reduce_max_sync(0xffffffffu, f2ord(vmax[k]));
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < NMIN + NMAX; ++k) sh[k][w] = r[k];
+    }
+    __syncthreads();
+    if (w == 0) {
+#pragma unroll
+        for (int k = 0; k < NMIN + NMAX; ++k) {
+            uint32_t v = sh[k][lane & 7];
+            v = k < NMIN ? __reduce_min_sync(0xffffffffu, v) : __reduce_max_sync(0xffffffffu, v);
+            if (lane == 0) sh[k][0] = v;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < NMIN; ++k) omin[k] = ord2f(sh[k][0]);
+#pragma unroll
+    for (int k = 0; k < NMAX; ++k) omax[k] = ord2f(sh[NMIN + k][0]);
+}
 
 // One CTA = one 256-cell quantisation block.
 template <int VALUE_BITS>
@@ -146,7 +179,7 @@ __global__ void __launch_bounds__(256) adam_qq_kernel(
     float* __restrict__ grad, uint8_t* __restrict__ optim_packed, float4* __restrict__ optim_bounds,
     uint8_t* __restrict__ value_packed, float2* __restrict__ value_bounds, int64_t first_block, int64_t numel_total,
     float lr_ibc1, float ibc2, float decay, float decay_offset, float grad_scale, int zero_grad) {
-    __shared__ float sh[8];
+    __shared__ uint32_t sh[6][8];
     const int64_t blk = first_block + blockIdx.x;
     const int64_t idx = blk * 256 + threadIdx.x;
     const bool inside = idx < numel_total;
@@ -166,23 +199,33 @@ __global__ void __launch_bounds__(256) adam_qq_kernel(
         uchar2 code = ((uchar2*)optim_packed)[idx];
         float u = omm.x + (omm.y - omm.x) * ((float)code.x * oinv);
         float ls = omm.z + (omm.w - omm.z) * ((float)code.y * oinv);
-        float sqrt_g2 = kAdamEps * expm1f(ls);
+        // sqrt(g2) = eps * expm1(ls).  ls is either 0 (never-updated cell) or far above 1
+        // (sqrt(g2)/eps is astronomically large for any real gradient), where expm1 = exp - 1
+        // to working precision; only the narrow band in between needs the careful routine.
+        float sqrt_g2 = kAdamEps * (ls > 12.0f ? (__expf(ls) - 1.0f) : expm1f(ls));
         float g1 = u * (sqrt_g2 + kAdamEps), g2 = sqrt_g2 * sqrt_g2;
-        x = adam_update(x, v, g1, g2, lr_ibc1, ibc2);
-        float sq = sqrtf(fmaxf(g2, 0.0f));
-        u_new = g1 / (sq + kAdamEps);
-        s_new = log1pf(fmaxf(sq, 0.0f) * (1.0f / kAdamEps));
+        g1 = kBeta1 * g1 + (1.f - kBeta1) * v;
+        g2 = kBeta2 * g2 + (1.f - kBeta2) * v * v;
+        // the reference builds this kernel with --use_fast_math: approximate division and
+        // square root are its own arithmetic here (cmake/SsBackendCuda.cmake:95-102)
+        x -= __fdividef(lr_ibc1 * g1, sqrt_approx(g2 * ibc2) + kAdamEps);
+        float sq = sqrt_approx(fmaxf(g2, 0.0f));
+        u_new = __fdividef(g1, sq + kAdamEps);
+        float y = sq * (1.0f / kAdamEps);
+        s_new = y > 1.0e6f ? __logf(y) : log1pf(y);
     }
-    float vmin = block_min(inside ? x : 1e30f, sh), vmax = block_max(inside ? x : -1e30f, sh);
-    float umin = block_min(inside ? u_new : 1e30f, sh), umax = block_max(inside ? u_new : -1e30f, sh);
-    float smin = block_min(inside ? s_new : 1e30f, sh), smax = block_max(inside ? s_new : -1e30f, sh);
+    const float mins_in[3] = {inside ? x : 1e30f, inside ? u_new : 1e30f, inside ? s_new : 1e30f};
+    const float maxs_in[3] = {inside ? x : -1e30f, inside ? u_new : -1e30f, inside ? s_new : -1e30f};
+    float mn[3], mx[3];
+    block_minmax<3, 3>(mins_in, maxs_in, mn, mx, sh);
+    const float vmin = mn[0], vmax = mx[0], umin = mn[1], umax = mx[1], smin = mn[2], smax = mx[2];
     if (inside) {
         float vrange = fmaxf(vmax - vmin, 1e-30f);
-        float qf = fminf(fmaxf(roundf(vq * (x - vmin) / vrange), 0.0f), vq);
+        float qf = fminf(fmaxf(roundf(__fdividef(vq * (x - vmin), vrange)), 0.0f), vq);
         if (VALUE_BITS == 8) value_packed[idx] = (uint8_t)qf; else ((uint16_t*)value_packed)[idx] = (uint16_t)qf;
         float urange = fmaxf(umax - umin, kAdamEps), srange = fmaxf(smax - smin, kAdamEps);
-        float uq = fminf(fmaxf(roundf(oq * (u_new - umin) / urange), 0.0f), oq);
-        float sq = fminf(fmaxf(roundf(oq * (s_new - smin) / srange), 0.0f), oq);
+        float uq = fminf(fmaxf(roundf(__fdividef(oq * (u_new - umin), urange)), 0.0f), oq);
+        float sq = fminf(fmaxf(roundf(__fdividef(oq * (s_new - smin), srange)), 0.0f), oq);
         ((uchar2*)optim_packed)[idx] = make_uchar2((uint8_t)uq, (uint8_t)sq);
     }
     if (threadIdx.x == 0) {
@@ -193,11 +236,14 @@ __global__ void __launch_bounds__(256) adam_qq_kernel(
 
 template <int BITS>
 __global__ void __launch_bounds__(256) quant_encode_kernel(const float* __restrict__ values, int64_t numel, uint8_t* __restrict__ packed, float2* __restrict__ bounds) {
-    __shared__ float sh[8];
+    __shared__ uint32_t sh[2][8];
     const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
     const bool inside = idx < numel;
     float v = inside ? values[idx] : 0.f;
-    float mn = block_min(inside ? v : 1e30f, sh), mx = block_max(inside ? v : -1e30f, sh);
+    const float mn_in[1] = {inside ? v : 1e30f}, mx_in[1] = {inside ? v : -1e30f};
+    float mn_o[1], mx_o[1];
+    block_minmax<1, 1>(mn_in, mx_in, mn_o, mx_o, sh);
+    const float mn = mn_o[0], mx = mx_o[0];
     constexpr float qmax = (float)((1 << BITS) - 1);
     if (inside) {
         float range = fmaxf(mx - mn, 1e-30f);

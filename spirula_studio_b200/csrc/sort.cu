@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_first_hist_kernel(
         if (table[i]) atomicAdd(&hdr->hist[0][i], (uint32_t)table[i]);
 }
 
-__global__ void __launch_bounds__(kSortThreads) sort_onesweep_kernel(
+__global__ void __launch_bounds__(kSortThreads, 3) sort_onesweep_kernel(
     const uint64_t* __restrict__ keys_in, const int32_t* __restrict__ vals_in,
     uint64_t* __restrict__ keys_out, int32_t* __restrict__ vals_out,
     const int64_t* __restrict__ n_ptr, int64_t capacity, int pass, int shift, int mask, int next_shift, int next_mask,

@@ -173,60 +173,126 @@ __device__ __forceinline__ void block_minmax(const float (&vmin)[NMIN], const fl
     for (int k = 0; k < NMAX; ++k) omax[k] = ord2f(sh[NMIN + k][0]);
 }
 
-// One CTA = one 256-cell quantisation block.
+// One CTA of 64 threads = one 256-cell quantisation block, four consecutive cells per thread
+// (16-byte gradient loads, 8-byte code loads); the block minima/maxima are folded per thread
+// first, then one redux.sync per value per warp and a two-entry exchange through shared memory.
 template <int VALUE_BITS>
-__global__ void __launch_bounds__(256) adam_qq_kernel(
+__global__ void __launch_bounds__(64) adam_qq_kernel(
     float* __restrict__ grad, uint8_t* __restrict__ optim_packed, float4* __restrict__ optim_bounds,
     uint8_t* __restrict__ value_packed, float2* __restrict__ value_bounds, int64_t first_block, int64_t numel_total,
     float lr_ibc1, float ibc2, float decay, float decay_offset, float grad_scale, int zero_grad) {
-    __shared__ uint32_t sh[6][8];
+    __shared__ uint32_t sh[6][2];
     const int64_t blk = first_block + blockIdx.x;
-    const int64_t idx = blk * 256 + threadIdx.x;
-    const bool inside = idx < numel_total;
+    const int64_t idx0 = blk * 256 + threadIdx.x * 4;
     constexpr float vq = (float)((1 << VALUE_BITS) - 1), vinv = 1.0f / vq;
     const float oq = 255.0f, oinv = 1.0f / 255.0f;
-    float x = 0.f, u_new = 0.f, s_new = 0.f;
-    if (inside) {
-        float2 vmm = value_bounds[blk];
-        float4 omm = optim_bounds[blk];
-        float q = VALUE_BITS == 8 ? (float)value_packed[idx] : (float)((uint16_t*)value_packed)[idx];
-        x = vmm.x + (vmm.y - vmm.x) * (q * vinv);
-        float v = grad[idx];
-        if (!isfinite(v)) v = 0.f;
-        if (zero_grad) grad[idx] = 0.f;
-        v *= grad_scale;
-        v += decay * (fmaxf(x - decay_offset, 0.0f) + fminf(x + decay_offset, 0.0f));
-        uchar2 code = ((uchar2*)optim_packed)[idx];
-        float u = omm.x + (omm.y - omm.x) * ((float)code.x * oinv);
-        float ls = omm.z + (omm.w - omm.z) * ((float)code.y * oinv);
-        // sqrt(g2) = eps * expm1(ls).  ls is either 0 (never-updated cell) or far above 1
-        // (sqrt(g2)/eps is astronomically large for any real gradient), where expm1 = exp - 1
-        // to working precision; only the narrow band in between needs the careful routine.
-        float sqrt_g2 = kAdamEps * (ls > 12.0f ? (__expf(ls) - 1.0f) : expm1f(ls));
-        float g1 = u * (sqrt_g2 + kAdamEps), g2 = sqrt_g2 * sqrt_g2;
-        g1 = kBeta1 * g1 + (1.f - kBeta1) * v;
-        g2 = kBeta2 * g2 + (1.f - kBeta2) * v * v;
-        // the reference builds this kernel with --use_fast_math: approximate division and
-        // square root are its own arithmetic here (cmake/SsBackendCuda.cmake:95-102)
-        x -= __fdividef(lr_ibc1 * g1, sqrt_approx(g2 * ibc2) + kAdamEps);
-        float sq = sqrt_approx(fmaxf(g2, 0.0f));
-        u_new = __fdividef(g1, sq + kAdamEps);
-        float y = sq * (1.0f / kAdamEps);
-        s_new = y > 1.0e6f ? __logf(y) : log1pf(y);
+    const float2 vmm = value_bounds[blk];
+    const float4 omm = optim_bounds[blk];
+    float x[4], u_new[4], s_new[4];
+    bool inside[4];
+    float gv[4];
+    uint32_t vcode[4], ucode[4], scode[4];
+    const bool full = idx0 + 4 <= numel_total;
+    if (full) {
+        const float4 g4 = *(const float4*)(grad + idx0);
+        gv[0] = g4.x; gv[1] = g4.y; gv[2] = g4.z; gv[3] = g4.w;
+        if (VALUE_BITS == 16) {
+            const ushort4 c = *(const ushort4*)((const uint16_t*)value_packed + idx0);
+            vcode[0] = c.x; vcode[1] = c.y; vcode[2] = c.z; vcode[3] = c.w;
+        } else {
+            const uchar4 c = *(const uchar4*)(value_packed + idx0);
+            vcode[0] = c.x; vcode[1] = c.y; vcode[2] = c.z; vcode[3] = c.w;
+        }
+        const uint2 oc = *(const uint2*)(optim_packed + 2 * idx0);
+        ucode[0] = oc.x & 255u; scode[0] = (oc.x >> 8) & 255u; ucode[1] = (oc.x >> 16) & 255u; scode[1] = oc.x >> 24;
+        ucode[2] = oc.y & 255u; scode[2] = (oc.y >> 8) & 255u; ucode[3] = (oc.y >> 16) & 255u; scode[3] = oc.y >> 24;
+        if (zero_grad) *(float4*)(grad + idx0) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    const float mins_in[3] = {inside ? x : 1e30f, inside ? u_new : 1e30f, inside ? s_new : 1e30f};
-    const float maxs_in[3] = {inside ? x : -1e30f, inside ? u_new : -1e30f, inside ? s_new : -1e30f};
-    float mn[3], mx[3];
-    block_minmax<3, 3>(mins_in, maxs_in, mn, mx, sh);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int64_t idx = idx0 + k;
+        inside[k] = idx < numel_total;
+        if (!full && inside[k]) {
+            gv[k] = grad[idx];
+            vcode[k] = VALUE_BITS == 8 ? (uint32_t)value_packed[idx] : (uint32_t)((const uint16_t*)value_packed)[idx];
+            ucode[k] = optim_packed[2 * idx]; scode[k] = optim_packed[2 * idx + 1];
+            if (zero_grad) grad[idx] = 0.f;
+        }
+        x[k] = u_new[k] = s_new[k] = 0.f;
+        if (inside[k]) {
+            float xv = vmm.x + (vmm.y - vmm.x) * ((float)vcode[k] * vinv);
+            float v = gv[k];
+            if (!isfinite(v)) v = 0.f;
+            v *= grad_scale;
+            v += decay * (fmaxf(xv - decay_offset, 0.0f) + fminf(xv + decay_offset, 0.0f));
+            float u = omm.x + (omm.y - omm.x) * ((float)ucode[k] * oinv);
+            float ls = omm.z + (omm.w - omm.z) * ((float)scode[k] * oinv);
+            // sqrt(g2) = eps * expm1(ls).  ls is either 0 (never-updated cell) or far above 1
+            // (sqrt(g2)/eps is astronomically large for any real gradient), where expm1 = exp - 1
+            // to working precision; only the narrow band in between needs the careful routine.
+            float em1;
+            if (ls > 12.0f) em1 = __expf(ls) - 1.0f; else em1 = expm1f(ls);
+            float sqrt_g2 = kAdamEps * em1;
+            float g1 = u * (sqrt_g2 + kAdamEps), g2 = sqrt_g2 * sqrt_g2;
+            g1 = kBeta1 * g1 + (1.f - kBeta1) * v;
+            g2 = kBeta2 * g2 + (1.f - kBeta2) * v * v;
+            // the reference builds this kernel with --use_fast_math: approximate division and
+            // square root are its own arithmetic here (cmake/SsBackendCuda.cmake:95-102)
+            xv -= __fdividef(lr_ibc1 * g1, sqrt_approx(g2 * ibc2) + kAdamEps);
+            float sq = sqrt_approx(fmaxf(g2, 0.0f));
+            u_new[k] = __fdividef(g1, sq + kAdamEps);
+            float y = sq * (1.0f / kAdamEps);
+            if (y > 1.0e6f) s_new[k] = __logf(y); else s_new[k] = log1pf(y);
+            x[k] = xv;
+        }
+    }
+    float mn[3] = {1e30f, 1e30f, 1e30f}, mx[3] = {-1e30f, -1e30f, -1e30f};
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        if (inside[k]) {
+            mn[0] = fminf(mn[0], x[k]); mx[0] = fmaxf(mx[0], x[k]);
+            mn[1] = fminf(mn[1], u_new[k]); mx[1] = fmaxf(mx[1], u_new[k]);
+            mn[2] = fminf(mn[2], s_new[k]); mx[2] = fmaxf(mx[2], s_new[k]);
+        }
+    {
+        const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+        uint32_t r[6];
+#pragma unroll
+        for (int k = 0; k < 3; ++k) { r[k] = __reduce_min_sync(0xffffffffu, f2ord(mn[k])); r[3 + k] = __reduce_max_sync(0xffffffffu, f2ord(mx[k])); }
+        if (lane == 0) {
+#pragma unroll
+            for (int k = 0; k < 6; ++k) sh[k][w] = r[k];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            mn[k] = ord2f(min(sh[k][0], sh[k][1]));
+            mx[k] = ord2f(max(sh[3 + k][0], sh[3 + k][1]));
+        }
+    }
     const float vmin = mn[0], vmax = mx[0], umin = mn[1], umax = mx[1], smin = mn[2], smax = mx[2];
-    if (inside) {
-        float vrange = fmaxf(vmax - vmin, 1e-30f);
-        float qf = fminf(fmaxf(roundf(__fdividef(vq * (x - vmin), vrange)), 0.0f), vq);
-        if (VALUE_BITS == 8) value_packed[idx] = (uint8_t)qf; else ((uint16_t*)value_packed)[idx] = (uint16_t)qf;
-        float urange = fmaxf(umax - umin, kAdamEps), srange = fmaxf(smax - smin, kAdamEps);
-        float uq = fminf(fmaxf(roundf(__fdividef(oq * (u_new - umin), urange)), 0.0f), oq);
-        float sq = fminf(fmaxf(roundf(__fdividef(oq * (s_new - smin), srange)), 0.0f), oq);
-        ((uchar2*)optim_packed)[idx] = make_uchar2((uint8_t)uq, (uint8_t)sq);
+    const float vscale = __fdividef(vq, fmaxf(vmax - vmin, 1e-30f));
+    const float uscale = __fdividef(oq, fmaxf(umax - umin, kAdamEps)), sscale = __fdividef(oq, fmaxf(smax - smin, kAdamEps));
+    uint32_t vout[4], oout[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        vout[k] = (uint32_t)fminf(fmaxf(rintf((x[k] - vmin) * vscale), 0.0f), vq);
+        uint32_t uqc = (uint32_t)fminf(fmaxf(rintf((u_new[k] - umin) * uscale), 0.0f), oq);
+        uint32_t sqc = (uint32_t)fminf(fmaxf(rintf((s_new[k] - smin) * sscale), 0.0f), oq);
+        oout[k] = uqc | (sqc << 8);
+    }
+    if (full) {
+        if (VALUE_BITS == 16) *(ushort4*)((uint16_t*)value_packed + idx0) = make_ushort4(vout[0], vout[1], vout[2], vout[3]);
+        else *(uchar4*)(value_packed + idx0) = make_uchar4(vout[0], vout[1], vout[2], vout[3]);
+        *(uint2*)(optim_packed + 2 * idx0) = make_uint2(oout[0] | (oout[1] << 16), oout[2] | (oout[3] << 16));
+    } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (inside[k]) {
+                const int64_t idx = idx0 + k;
+                if (VALUE_BITS == 8) value_packed[idx] = (uint8_t)vout[k]; else ((uint16_t*)value_packed)[idx] = (uint16_t)vout[k];
+                optim_packed[2 * idx] = (uint8_t)(oout[k] & 255u); optim_packed[2 * idx + 1] = (uint8_t)(oout[k] >> 8);
+            }
     }
     if (threadIdx.x == 0) {
         value_bounds[blk] = make_float2(vmin, vmax);
@@ -310,10 +376,10 @@ int ssb_adam_step_sh_quantized(float* d_grad, uint8_t* d_optim_packed, float* d_
     unsigned blocks = (unsigned)ceil_div(numel, 256);
     int64_t end_total = first_cell + numel;   // cells beyond the range belong to another caller
     if (value_bits == 8)
-        adam_qq_kernel<8><<<blocks, 256, 0, (cudaStream_t)stream>>>(d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed,
+        adam_qq_kernel<8><<<blocks, 64, 0, (cudaStream_t)stream>>>(d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed,
             (float2*)d_value_bounds, first_cell / 256, end_total, cfg->lr_features_sh * ibc1, ibc2, decay, 0.0f, cfg->grad_scale, cfg->zero_grad);
     else
-        adam_qq_kernel<16><<<blocks, 256, 0, (cudaStream_t)stream>>>(d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed,
+        adam_qq_kernel<16><<<blocks, 64, 0, (cudaStream_t)stream>>>(d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed,
             (float2*)d_value_bounds, first_cell / 256, end_total, cfg->lr_features_sh * ibc1, ibc2, decay, 0.0f, cfg->grad_scale, cfg->zero_grad);
     SSB_LAUNCHED("adam_qq_kernel");
     return SSB_OK;

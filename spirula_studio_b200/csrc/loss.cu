@@ -69,86 +69,137 @@ __global__ void __launch_bounds__(kLossThreads) loss_l1_ssim_kernel(
             sX[o] = x; sY[o] = y;
         }
         __syncthreads();
-        // 2) row convolution of the five moments: rows 0..51, centre columns 5..46
-        for (int o = threadIdx.x; o < kIn * kMid; o += kLossThreads) {
-            int ly = o / kMid, lc = o - ly * kMid;
+        // 2) row convolution of the five moments: rows 0..51, centre columns 5..46.
+        //    One work item = 3 neighbouring outputs of a row: 13 + 13 shared-memory reads feed
+        //    15 sums (instead of 22 reads per output).
+        for (int o = threadIdx.x; o < kIn * (kMid / 3); o += kLossThreads) {
+            const int ly = o / (kMid / 3), lc = (o - ly * (kMid / 3)) * 3;
             const float* xr = sX + ly * kIn + lc;
             const float* yr = sY + ly * kIn + lc;
-            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f, s4 = 0.f;
+            float acc[3][5];
 #pragma unroll
-            for (int d = 0; d < 11; ++d) {
-                float wgt = cGaussW[d], x = xr[d], y = yr[d];
-                s0 += x * wgt; s1 += x * x * wgt; s2 += y * wgt; s3 += y * y * wgt; s4 += x * y * wgt;
+            for (int q = 0; q < 3; ++q)
+#pragma unroll
+                for (int k = 0; k < 5; ++k) acc[q][k] = 0.f;
+#pragma unroll
+            for (int d = 0; d < 13; ++d) {
+                const float x = xr[d], y = yr[d];
+                const float xx = x * x, yy = y * y, xy = x * y;
+#pragma unroll
+                for (int q = 0; q < 3; ++q) {
+                    const int tap = d - q;
+                    if (tap >= 0 && tap < 11) {
+                        const float wgt = cGaussW[tap];
+                        acc[q][0] += x * wgt; acc[q][1] += xx * wgt; acc[q][2] += y * wgt; acc[q][3] += yy * wgt; acc[q][4] += xy * wgt;
+                    }
+                }
             }
-            sM[0 * kIn * kMid + o] = s0; sM[1 * kIn * kMid + o] = s1; sM[2 * kIn * kMid + o] = s2;
-            sM[3 * kIn * kMid + o] = s3; sM[4 * kIn * kMid + o] = s4;
+#pragma unroll
+            for (int q = 0; q < 3; ++q)
+#pragma unroll
+                for (int k = 0; k < 5; ++k) sM[k * kIn * kMid + ly * kMid + lc + q] = acc[q][k];
         }
         __syncthreads();
-        // 3) column convolution -> SSIM and its partials at the 42x42 window centres
-        for (int o = threadIdx.x; o < kMid * kMid; o += kLossThreads) {
-            int r = o / kMid, c = o - r * kMid;
-            float m[5];
+        // 3) column convolution -> SSIM and its partials at the 42x42 window centres;
+        //    one work item = 3 vertically neighbouring centres of a column.
+        for (int o = threadIdx.x; o < (kMid / 3) * kMid; o += kLossThreads) {
+            const int rg = o / kMid, c = o - rg * kMid;
+            const int r0 = rg * 3;
+            float m[3][5];
+#pragma unroll
+            for (int q = 0; q < 3; ++q)
+#pragma unroll
+                for (int k = 0; k < 5; ++k) m[q][k] = 0.f;
 #pragma unroll
             for (int k = 0; k < 5; ++k) {
-                const float* col = sM + k * kIn * kMid + r * kMid + c;
-                float s = 0.f;
+                const float* col = sM + k * kIn * kMid + r0 * kMid + c;
 #pragma unroll
-                for (int d = 0; d < 11; ++d) s += col[d * kMid] * cGaussW[d];
-                m[k] = s;
+                for (int d = 0; d < 13; ++d) {
+                    const float v = col[d * kMid];
+#pragma unroll
+                    for (int q = 0; q < 3; ++q) {
+                        const int tap = d - q;
+                        if (tap >= 0 && tap < 11) m[q][k] += v * cGaussW[tap];
+                    }
+                }
             }
-            int gy = ty0 - kHalo + r, gx = tx0 - kHalo + c;
-            float d0 = 0.f, d1 = 0.f, d2 = 0.f;
-            if ((unsigned)gy < (unsigned)H && (unsigned)gx < (unsigned)W) {
-                float mu1 = m[0], mu2 = m[2];
-                float mu1_sq = mu1 * mu1, mu2_sq = mu2 * mu2;
-                float sigma1_sq = m[1] - mu1_sq, sigma2_sq = m[3] - mu2_sq, sigma12 = m[4] - mu1 * mu2;
-                float A = mu1_sq + mu2_sq + kC1;
-                float Bv = sigma1_sq + sigma2_sq + kC2;
-                float C_ = 2.f * mu1 * mu2 + kC1;
-                float D_ = 2.f * sigma12 + kC2;
-                float rAB = 1.0f / (A * Bv);
-                if (r >= kHalo && r < kHalo + kLossTile && c >= kHalo && c < kHalo + kLossTile) ssim_acc += (C_ * D_) * rAB;
-                d0 = ((mu2 * 2.f * D_) * rAB - (mu2 * 2.f * C_) * rAB - (mu1 * 2.f * C_ * D_) * rAB / A + (mu1 * 2.f * C_ * D_) * rAB / Bv) * grad;
-                d1 = (-C_ * D_) * rAB / Bv * grad;
-                d2 = (2.f * C_) * rAB * grad;
+#pragma unroll
+            for (int q = 0; q < 3; ++q) {
+                const int r = r0 + q;
+                const int gy = ty0 - kHalo + r, gx = tx0 - kHalo + c;
+                float d0 = 0.f, d1 = 0.f, d2 = 0.f;
+                if ((unsigned)gy < (unsigned)H && (unsigned)gx < (unsigned)W) {
+                    const float mu1 = m[q][0], mu2 = m[q][2];
+                    const float mu1_sq = mu1 * mu1, mu2_sq = mu2 * mu2;
+                    const float sigma1_sq = m[q][1] - mu1_sq, sigma2_sq = m[q][3] - mu2_sq, sigma12 = m[q][4] - mu1 * mu2;
+                    const float A = mu1_sq + mu2_sq + kC1;
+                    const float Bv = sigma1_sq + sigma2_sq + kC2;
+                    const float C_ = 2.f * mu1 * mu2 + kC1;
+                    const float D_ = 2.f * sigma12 + kC2;
+                    const float rAB = 1.0f / (A * Bv);
+                    if (r >= kHalo && r < kHalo + kLossTile && c >= kHalo && c < kHalo + kLossTile) ssim_acc += (C_ * D_) * rAB;
+                    d0 = ((mu2 * 2.f * D_) * rAB - (mu2 * 2.f * C_) * rAB - (mu1 * 2.f * C_ * D_) * rAB / A + (mu1 * 2.f * C_ * D_) * rAB / Bv) * grad;
+                    d1 = (-C_ * D_) * rAB / Bv * grad;
+                    d2 = (2.f * C_) * rAB * grad;
+                }
+                // sD aliases the input patches, which step 2 finished reading
+                const int oo = r * kMid + c;
+                sD[oo] = d0; sD[kMid * kMid + oo] = d1; sD[2 * kMid * kMid + oo] = d2;
             }
-            // sD aliases the input patches, which step 2 finished reading
-            sD[o] = d0; sD[kMid * kMid + o] = d1; sD[2 * kMid * kMid + o] = d2;
         }
         __syncthreads();
-        // 4) row convolution of the three partial maps: rows 0..41, centre columns 5..36
-        for (int o = threadIdx.x; o < kMid * kLossTile; o += kLossThreads) {
-            int r = o / kLossTile, c = o - r * kLossTile;
+        // 4) row convolution of the three partial maps: rows 0..41, centre columns 5..36;
+        //    one work item = 2 neighbouring outputs of a row.
+        for (int o = threadIdx.x; o < kMid * (kLossTile / 2); o += kLossThreads) {
+            const int r = o / (kLossTile / 2), c = (o - r * (kLossTile / 2)) * 2;
 #pragma unroll
             for (int k = 0; k < 3; ++k) {
                 const float* row = sD + k * kMid * kMid + r * kMid + c;
-                float s = 0.f;
+                float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-                for (int d = 0; d < 11; ++d) s += row[d] * cGaussW[d];
-                sH[k * kMid * kLossTile + o] = s;
+                for (int d = 0; d < 12; ++d) {
+                    const float v = row[d];
+                    if (d < 11) s0 += v * cGaussW[d];
+                    if (d >= 1) s1 += v * cGaussW[d - 1];
+                }
+                sH[k * kMid * kLossTile + r * kLossTile + c] = s0;
+                sH[k * kMid * kLossTile + r * kLossTile + c + 1] = s1;
             }
         }
         __syncthreads();
-        // 5) column convolution and the gradient of this channel
-        for (int o = threadIdx.x; o < kLossTile * kLossTile; o += kLossThreads) {
-            int r = o / kLossTile, c = o - r * kLossTile;
-            int gy = ty0 + r, gx = tx0 + c;
-            if (gy < H && gx < W) {
-                float s[3];
+        // 5) column convolution and the gradient of this channel; one work item = 4
+        //    vertically neighbouring pixels of a column (256 items = one per thread).
+        for (int o = threadIdx.x; o < (kLossTile / 4) * kLossTile; o += kLossThreads) {
+            const int rg = o / kLossTile, c = o - rg * kLossTile;
+            const int r0 = rg * 4;
+            float sacc[4][3];
 #pragma unroll
-                for (int k = 0; k < 3; ++k) {
-                    const float* col = sH + k * kMid * kLossTile + r * kLossTile + c;
-                    float a = 0.f;
+            for (int q = 0; q < 4; ++q) sacc[q][0] = sacc[q][1] = sacc[q][2] = 0.f;
 #pragma unroll
-                    for (int d = 0; d < 11; ++d) a += col[d * kLossTile] * cGaussW[d];
-                    s[k] = a;
+            for (int k = 0; k < 3; ++k) {
+                const float* col = sH + k * kMid * kLossTile + r0 * kLossTile + c;
+#pragma unroll
+                for (int d = 0; d < 14; ++d) {
+                    const float v = col[d * kLossTile];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int tap = d - q;
+                        if (tap >= 0 && tap < 11) sacc[q][k] += v * cGaussW[tap];
+                    }
                 }
-                int64_t q = ((int64_t)gy * W + gx) * 3 + ch;
-                float p1 = R[q], p2 = G[q];
-                float diff = p1 - p2;
-                l1_acc += fabsf(diff);
-                float sg = diff > 0.f ? 1.f : (diff < 0.f ? -1.f : 0.f);
-                V[q] = l1_scale * sg + (s[0] + (2.f * p1) * s[1] + p2 * s[2]);
+            }
+            const int gx = tx0 + c;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int gy = ty0 + r0 + q;
+                if (gy < H && gx < W) {
+                    const int64_t qi = ((int64_t)gy * W + gx) * 3 + ch;
+                    const float p1 = R[qi], p2 = G[qi];
+                    const float diff = p1 - p2;
+                    l1_acc += fabsf(diff);
+                    const float sg = diff > 0.f ? 1.f : (diff < 0.f ? -1.f : 0.f);
+                    V[qi] = l1_scale * sg + (sacc[q][0] + (2.f * p1) * sacc[q][1] + p2 * sacc[q][2]);
+                }
             }
         }
     }

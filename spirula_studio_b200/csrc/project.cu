@@ -268,18 +268,24 @@ __device__ __forceinline__ void sh_basis_vjp(float x, float y, float z, const fl
 
 __device__ __forceinline__ float finite_or_zero(float v) { return isfinite(v) ? v : 0.0f; }
 
-__global__ void __launch_bounds__(kProjBlock) project_bwd_kernel(
+template <bool MULTI_VIEW>
+__global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
     SsbSplats sp, SsbShQuant shq, int64_t n, int C, const float* __restrict__ viewmats, const float* __restrict__ intrins,
     int W, int H, int antialiased, const float4* __restrict__ aabb, SsbScreenRec* __restrict__ v_screen,
     SsbSplats gr, int accumulate, int clear_v_screen) {
+    // One view per launch (the training loop's case): a thread's SH gradients overwrite its own
+    // SH values in shared memory once they have been read, so one 23 KB span is enough and six
+    // CTAs fit an SM.  Several views: gradients accumulate in a second span.
     __shared__ float sh_s[kProjBlock * kShPerSplat];
-    __shared__ float shg_s[kProjBlock * kShPerSplat];
+    __shared__ float shg_multi[MULTI_VIEW ? kProjBlock * kShPerSplat : 1];
+    float* shg_s = MULTI_VIEW ? shg_multi : sh_s;
     const int64_t first = (int64_t)blockIdx.x * kProjBlock;
     const int64_t gid = first + threadIdx.x;
     const int count = (int)min((int64_t)kProjBlock, n - first) * kShPerSplat;
     stage_sh(sh_s, sp.features_sh, shq.packed, shq.bounds, shq.bits, shq.bounds_stride, first, n);
-    for (int i = threadIdx.x; i < count; i += kProjBlock) shg_s[i] = 0.f;
+    if (MULTI_VIEW) for (int i = threadIdx.x; i < count; i += kProjBlock) shg_s[i] = 0.f;
     __syncthreads();
+    bool any_view = false;
 
     float g_mean[3] = {0.f, 0.f, 0.f}, g_quat[4] = {0.f, 0.f, 0.f, 0.f}, g_scale[3] = {0.f, 0.f, 0.f}, g_op = 0.f, g_dc[3] = {0.f, 0.f, 0.f};
     if (gid < n) {
@@ -294,6 +300,7 @@ __global__ void __launch_bounds__(kProjBlock) project_bwd_kernel(
             const int64_t idx = (int64_t)cid * n + gid;
             float4 bb = aabb[idx];
             if (bb.z <= bb.x || bb.w <= bb.y) continue;
+            any_view = true;
             CamDev cam = load_cam(viewmats, intrins, cid);
             float4* vr = (float4*)(v_screen + idx);
             float4 va = vr[0], vb = vr[1], vc4 = vr[2];
@@ -425,7 +432,8 @@ __global__ void __launch_bounds__(kProjBlock) project_bwd_kernel(
 #pragma unroll
             for (int j = 0; j < kNumSh; ++j) {
                 w[j] = sh[3 * j] * vcol[0] + sh[3 * j + 1] * vcol[1] + sh[3 * j + 2] * vcol[2];
-                shg[3 * j] += b[j] * vcol[0]; shg[3 * j + 1] += b[j] * vcol[1]; shg[3 * j + 2] += b[j] * vcol[2];
+                if (MULTI_VIEW) { shg[3 * j] += b[j] * vcol[0]; shg[3 * j + 1] += b[j] * vcol[1]; shg[3 * j + 2] += b[j] * vcol[2]; }
+                else { shg[3 * j] = b[j] * vcol[0]; shg[3 * j + 1] = b[j] * vcol[1]; shg[3 * j + 2] = b[j] * vcol[2]; }
             }
             float vn[3];
             sh_basis_vjp(nx, ny, nz, w, vn);
@@ -433,6 +441,12 @@ __global__ void __launch_bounds__(kProjBlock) project_bwd_kernel(
             g_mean[0] += finite_or_zero((vn[0] - nx * dn) * inv);
             g_mean[1] += finite_or_zero((vn[1] - ny * dn) * inv);
             g_mean[2] += finite_or_zero((vn[2] - nz * dn) * inv);
+        }
+        if (!MULTI_VIEW && !any_view) {
+            // culled in the only view: the span still holds SH values, not gradients
+            float* shg0 = shg_s + threadIdx.x * kShPerSplat;
+#pragma unroll
+            for (int j = 0; j < kShPerSplat; ++j) shg0[j] = 0.f;
         }
         if (accumulate) {
 #pragma unroll
@@ -537,9 +551,14 @@ int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n
     int e = check_shq(splats, shq, q);
     if (e) return e;
     if (n == 0) return SSB_OK;
-    project_bwd_kernel<<<(unsigned)ceil_div(n, kProjBlock), kProjBlock, 0, (cudaStream_t)stream>>>(
-        *splats, q, n, cams->count, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased,
-        (const float4*)d_aabb, d_v_screen, *grads, accumulate, clear_v_screen);
+    if (cams->count == 1)
+        project_bwd_kernel<false><<<(unsigned)ceil_div(n, kProjBlock), kProjBlock, 0, (cudaStream_t)stream>>>(
+            *splats, q, n, cams->count, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased,
+            (const float4*)d_aabb, d_v_screen, *grads, accumulate, clear_v_screen);
+    else
+        project_bwd_kernel<true><<<(unsigned)ceil_div(n, kProjBlock), kProjBlock, 0, (cudaStream_t)stream>>>(
+            *splats, q, n, cams->count, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased,
+            (const float4*)d_aabb, d_v_screen, *grads, accumulate, clear_v_screen);
     SSB_LAUNCHED("project_bwd_kernel");
     return SSB_OK;
 }

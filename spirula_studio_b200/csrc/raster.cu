@@ -35,6 +35,24 @@ __device__ __forceinline__ float eval_alpha(float4 a, float4 b, float px, float 
     return sigma < 0.f ? 0.f : alpha;
 }
 
+// Does the alpha >= 1/255 ellipse of a record reach the box [x0,x1]x[y0,y1]
+// (coordinates relative to the splat centre)?  Same construction as the
+// reference's micro-tile test (src/core/Common.cuh:55-77), with a small margin
+// so rounding can only keep a record, never drop one.
+__device__ __forceinline__ bool ellipse_reaches_box(float4 b, float x0, float x1, float y0, float y1) {
+    const float kk = 0.5f / __logf(b.w * 255.0f);
+    const float a = b.x * kk, c = b.z * kk;
+    float bb = b.y * kk;
+    const float wx = -bb / c, wy = -bb / a;
+    const float u0 = fminf(fmaxf(x0 * wx, y0), y1), u1 = fminf(fmaxf(x1 * wx, y0), y1);
+    const float v0 = fminf(fmaxf(y0 * wy, x0), x1), v1 = fminf(fmaxf(y1 * wy, x0), x1);
+    bb *= 2.0f;
+    const float mx = fminf(a * x0 * x0 + bb * x0 * u0 + c * u0 * u0, a * x1 * x1 + bb * x1 * u1 + c * u1 * u1);
+    const float my = fminf(a * v0 * v0 + bb * v0 * y0 + c * y0 * y0, a * v1 * v1 + bb * v1 * y1 + c * y1 * y1);
+    const float mc = fmaxf(fmaxf(x0, -x1), fmaxf(y0, -y1));
+    return !(fminf(mc, fminf(mx, my) - 1.0f) >= 0.01f);
+}
+
 __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
     const SsbScreenRec* __restrict__ screen, const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ flatten_ids,
     const int64_t* __restrict__ n_isects_ptr, int I, int W, int H, int tw, int th,
@@ -77,6 +95,7 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
             if (e < batch) {
                 float4 a = sA[e];
                 hit = (a.x + a.z >= fx0) && (a.x - a.z <= fx1) && (a.y + a.w >= fy0) && (a.y - a.w <= fy1);
+                if (hit) hit = ellipse_reaches_box(sB[e], fx0 - a.x, fx1 - a.x, fy0 - a.y, fy1 - a.y);
             }
             unsigned bal = __ballot_sync(0xffffffffu, hit);
             if (hit) hits[w][n_hit + __popc(bal & ((1u << lane) - 1u))] = (uint8_t)e;
@@ -84,7 +103,7 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
         }
         __syncwarp();
         for (int k = 0; k < n_hit; ++k) {
-            if (__all_sync(0xffffffffu, done)) break;
+            if ((k & 3) == 0 && __all_sync(0xffffffffu, done)) break;
             const int e = hits[w][k];
             const float4 a = sA[e], b = sB[e];
             float vis, sigma, dx, dy;
@@ -114,24 +133,6 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
 
 constexpr int kBwdWarps = 4;          // one 16x16 tile per CTA, one 8x8 micro-tile per warp
 constexpr int kSurvCap = 256;         // survivors collected per segment (8 per lane)
-
-// Does the alpha >= 1/255 ellipse of a record reach the box [x0,x1]x[y0,y1]
-// (coordinates relative to the splat centre)?  Same construction as the
-// reference's micro-tile test (src/core/Common.cuh:55-77), with a small margin
-// so rounding can only keep a record, never drop one.
-__device__ __forceinline__ bool ellipse_reaches_box(float4 b, float x0, float x1, float y0, float y1) {
-    const float kk = 0.5f / __logf(b.w * 255.0f);
-    const float a = b.x * kk, c = b.z * kk;
-    float bb = b.y * kk;
-    const float wx = -bb / c, wy = -bb / a;
-    const float u0 = fminf(fmaxf(x0 * wx, y0), y1), u1 = fminf(fmaxf(x1 * wx, y0), y1);
-    const float v0 = fminf(fmaxf(y0 * wy, x0), x1), v1 = fminf(fmaxf(y1 * wy, x0), x1);
-    bb *= 2.0f;
-    const float mx = fminf(a * x0 * x0 + bb * x0 * u0 + c * u0 * u0, a * x1 * x1 + bb * x1 * u1 + c * u1 * u1);
-    const float my = fminf(a * v0 * v0 + bb * v0 * y0 + c * y0 * y0, a * v1 * v1 + bb * v1 * y1 + c * y1 * y1);
-    const float mc = fmaxf(fmaxf(x0, -x1), fmaxf(y0, -y1));
-    return !(fminf(mc, fminf(mx, my) - 1.0f) >= 0.01f);
-}
 
 __global__ void __launch_bounds__(kBwdWarps * 32) raster_bwd_kernel(
     const SsbScreenRec* __restrict__ screen, const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ flatten_ids,

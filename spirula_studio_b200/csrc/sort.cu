@@ -34,12 +34,16 @@ constexpr int kRadix = 1 << kRadixBits;                         // 512 digit val
 constexpr int kMaxPasses = 8;
 constexpr uint32_t kFlagAggregate = 1u << 30, kFlagInclusive = 2u << 30, kValueMask = (1u << 30) - 1u;
 constexpr int kSpinLimit = 1 << 22;
+constexpr int kLookWindow = 8;
 
 struct SortHeader {                 // lives at the start of the workspace
     uint32_t hist[kMaxPasses][kRadix];
     uint32_t ticket[kMaxPasses];
     uint32_t error;
     uint32_t pad[7];
+#ifdef SSB_SORT_PROFILE
+    unsigned long long prof[8];
+#endif
 };
 
 __device__ __forceinline__ int digit_of(uint64_t key, int shift, int mask) { return (int)((key >> shift) & (uint64_t)mask); }
@@ -103,6 +107,13 @@ __global__ void __launch_bounds__(kSortThreads, 3) sort_onesweep_kernel(
     __shared__ int scan_tmp[kSortWarps];
     __shared__ uint32_t tile_s;
 
+#ifdef SSB_SORT_PROFILE
+    long long tk[7];
+#define SSB_TICK(i) tk[i] = clock64()
+#else
+#define SSB_TICK(i)
+#endif
+    SSB_TICK(0);
     const int64_t n = min(*n_ptr, capacity);
     const int64_t n_tiles = (n + kSortTile - 1) / kSortTile;
     if (threadIdx.x == 0) tile_s = atomicAdd(&hdr->ticket[pass], 1u);
@@ -111,6 +122,7 @@ __global__ void __launch_bounds__(kSortThreads, 3) sort_onesweep_kernel(
     __syncthreads();
     const int64_t tile = tile_s;
     if (tile >= n_tiles) return;
+    SSB_TICK(1);
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int64_t wbase = tile * kSortTile + (int64_t)w * kSortWarpSpan;
 
@@ -135,11 +147,13 @@ __global__ void __launch_bounds__(kSortThreads, 3) sort_onesweep_kernel(
         int64_t i = wbase + r * 32 + lane;
         key[r] = i < n ? keys_in[i] : 0;
     }
+    SSB_TICK(2);
 #pragma unroll
     for (int r = 0; r < kSortItems; ++r) {
         bool valid = wbase + r * 32 + lane < n;
         rank[r] = warp_rank(cnt[w], digit_of(key[r], shift, mask), valid, lane);
     }
+    SSB_TICK(3);
     if (next_mask != 0) {
 #pragma unroll
         for (int r = 0; r < kSortItems; ++r) {
@@ -148,6 +162,7 @@ __global__ void __launch_bounds__(kSortThreads, 3) sort_onesweep_kernel(
         }
     }
     __syncthreads();
+    SSB_TICK(4);
 
     // per digit: offsets of the warps inside the tile, publish, look back, publish again
     for (int d = threadIdx.x; d < kRadix; d += kSortThreads) {
@@ -161,17 +176,32 @@ __global__ void __launch_bounds__(kSortThreads, 3) sort_onesweep_kernel(
             row[d] = kFlagInclusive | total;
         } else {
             row[d] = kFlagAggregate | total;
-            for (int64_t t = tile - 1; t >= 0; --t) {
-                volatile uint32_t* prow = desc + t * kRadix;
-                uint32_t v = prow[d];
-                int spins = 0;
-                while ((v >> 30) == 0u) {
-                    if (++spins > kSpinLimit) { atomicExch(&hdr->error, 1u); break; }
-                    __nanosleep(20);
-                    v = prow[d];
+            // Look back over the predecessors, kLookWindow rows at a time: the loads of a
+            // window are independent, so a long run of count-only rows costs one memory
+            // latency per window instead of one per row.
+            bool done = false;
+            for (int64_t t = tile - 1; t >= 0 && !done; t -= kLookWindow) {
+                uint32_t v[kLookWindow];
+#pragma unroll
+                for (int j = 0; j < kLookWindow; ++j) {
+                    const int64_t tj = t - j;
+                    v[j] = tj >= 0 ? ((volatile uint32_t*)desc)[tj * kRadix + d] : (2u << 30);
                 }
-                prefix += v & kValueMask;
-                if ((v >> 30) != 1u) break;      // inclusive prefix (or gave up): stop
+#pragma unroll
+                for (int j = 0; j < kLookWindow; ++j) {
+                    if (done) break;
+                    uint32_t x = v[j];
+                    if ((x >> 30) == 0u) {
+                        volatile uint32_t* cell = desc + (t - j) * kRadix + d;
+                        int spins = 0;
+                        while (((x = *cell) >> 30) == 0u) {
+                            if (++spins > kSpinLimit) { atomicExch(&hdr->error, 1u); break; }
+                            __nanosleep(20);
+                        }
+                    }
+                    prefix += x & kValueMask;
+                    if ((x >> 30) != 1u) done = true;      // inclusive prefix (or gave up): stop
+                }
             }
             row[d] = kFlagInclusive | ((prefix + total) & kValueMask);
         }
@@ -181,6 +211,7 @@ __global__ void __launch_bounds__(kSortThreads, 3) sort_onesweep_kernel(
         if (next_mask != 0 && next_tab[d]) atomicAdd(&hdr->hist[pass + 1][d], (uint32_t)next_tab[d]);
     }
     __syncthreads();
+    SSB_TICK(5);
 
 #pragma unroll
     for (int r = 0; r < kSortItems; ++r) {
@@ -192,6 +223,13 @@ __global__ void __launch_bounds__(kSortThreads, 3) sort_onesweep_kernel(
             vals_out[pos] = vals_in[i];
         }
     }
+    SSB_TICK(6);
+#ifdef SSB_SORT_PROFILE
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 6; ++i) atomicAdd(&hdr->prof[i], (unsigned long long)(tk[i + 1] - tk[i]));
+        atomicAdd(&hdr->prof[6], 1ull);
+    }
+#endif
 }
 
 static int64_t desc_region_words(int64_t capacity) { return ceil_div(capacity > 0 ? capacity : 1, kSortTile) * kRadix; }

@@ -8,12 +8,15 @@
 // each pass is ONE launch that reads and writes every pair once (24 B/pair):
 //   * a 4096-pair tile is taken by ticket (atomic counter), so every tile with a
 //     smaller index is already running or finished;
-//   * keys are ranked inside their warp with match.any (equal digits keep their
-//     order), warps are offset against each other through an 8 x 512 table in
-//     shared memory;
+//   * keys are ranked inside their warp by matching digits with one ballot per
+//     digit bit (equal digits keep their order), warps are offset against each
+//     other through an 8 x 512 table in shared memory;
 //   * the tile publishes its per-digit counts in a descriptor row and looks
-//     back over its predecessors' rows (count-only -> add and go on; inclusive
-//     prefix -> add and stop), then publishes its own inclusive prefix;
+//     back over its predecessors' rows, sixteen rows per step (count-only -> add
+//     and go on; inclusive prefix -> add and stop), then publishes its own
+//     inclusive prefix;
+//   * the tile is staged in digit order in shared memory and written out in that
+//     order, so neighbouring threads write neighbouring addresses;
 //   * while the keys are in registers the tile also counts the NEXT pass's
 //     digit, so the digit totals a pass needs were produced by the pass before
 //     it (a small kernel produces them for the first pass).
@@ -34,7 +37,7 @@ constexpr int kRadix = 1 << kRadixBits;                         // 512 digit val
 constexpr int kMaxPasses = 8;
 constexpr uint32_t kFlagAggregate = 1u << 30, kFlagInclusive = 2u << 30, kValueMask = (1u << 30) - 1u;
 constexpr int kSpinLimit = 1 << 22;
-constexpr int kLookWindow = 8;
+constexpr int kLookWindow = 16;
 
 struct SortHeader {                 // lives at the start of the workspace
     uint32_t hist[kMaxPasses][kRadix];
@@ -48,26 +51,43 @@ struct SortHeader {                 // lives at the start of the workspace
 
 __device__ __forceinline__ int digit_of(uint64_t key, int shift, int mask) { return (int)((key >> shift) & (uint64_t)mask); }
 
+// Lanes of the warp whose digit equals this lane's: nbits independent ballots and an AND
+// chain (match.any serialises over the distinct values, which with 9-bit digits is
+// nearly every lane).  Invalid lanes match nobody.
+__device__ __forceinline__ unsigned match_digit(int digit, bool valid, int nbits) {
+    unsigned peers = __ballot_sync(0xffffffffu, valid);
+#pragma unroll
+    for (int b = 0; b < kRadixBits; ++b) {
+        if (b < nbits) {
+            const bool bit = (digit >> b) & 1;
+            const unsigned bal = __ballot_sync(0xffffffffu, bit);
+            peers &= bit ? bal : ~bal;
+        }
+    }
+    return valid ? peers : 0u;
+}
+
 // Rank of this lane's key among the lanes of the round with the same digit, plus
 // the warp's running count of that digit; updates the running count.
-__device__ __forceinline__ int warp_rank(int* cnt_w, int digit, bool valid, int lane) {
-    unsigned peers = __match_any_sync(0xffffffffu, valid ? digit : (kRadix + lane));
-    int rank = __popc(peers & ((1u << lane) - 1u));
-    int leader = __ffs(peers) - 1;
+__device__ __forceinline__ int warp_rank(int* cnt_w, int digit, bool valid, int lane, int nbits) {
+    const unsigned peers = match_digit(digit, valid, nbits);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    const int leader = __ffs(peers) - 1;
     int prev = 0;
-    if (lane == leader && valid) {
+    if (valid && lane == leader) {
         prev = cnt_w[digit];
         cnt_w[digit] = prev + __popc(peers);
     }
-    prev = __shfl_sync(0xffffffffu, prev, leader);
+    prev = __shfl_sync(0xffffffffu, prev, leader < 0 ? 0 : leader);
     __syncwarp();
     return prev + rank;
 }
 
-// Adds this round's digits to a block-wide table (one shared atomic per distinct digit per warp).
-__device__ __forceinline__ void warp_count(int* table, int digit, bool valid, int lane) {
-    unsigned peers = __match_any_sync(0xffffffffu, valid ? digit : (kRadix + lane));
-    if (valid && lane == __ffs(peers) - 1) atomicAdd(&table[digit], __popc(peers));
+// Adds this lane's digit to a block-wide table.  A plain shared-memory atomic per lane costs
+// one instruction (the hardware serialises lanes that hit the same counter); matching the
+// lanes first would cost some forty.
+__device__ __forceinline__ void warp_count(int* table, int digit, bool valid) {
+    if (valid) atomicAdd(&table[digit], 1);
 }
 
 // Digit totals of the first pass; also clears descriptor region 0 for the tiles in use.
@@ -88,7 +108,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_first_hist_kernel(
             int64_t i = wbase + r * 32 + lane;
             bool valid = i < n;
             int d = valid ? digit_of(keys[i], shift, mask) : 0;
-            warp_count(table, d, valid, lane);
+            warp_count(table, d, valid);
         }
     }
     __syncthreads();
@@ -96,16 +116,40 @@ __global__ void __launch_bounds__(kSortThreads) sort_first_hist_kernel(
         if (table[i]) atomicAdd(&hdr->hist[0][i], (uint32_t)table[i]);
 }
 
-__global__ void __launch_bounds__(kSortThreads, 3) sort_onesweep_kernel(
+// Exclusive scan of 512 ints held two per thread (entries 2t, 2t+1); all 256 threads call it.
+__device__ __forceinline__ void scan512(int a, int b, int* scan_tmp, int& excl_a, int& excl_b) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int s = a + b;
+    int inc = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += t; }
+    __syncthreads();                       // scan_tmp may still be read from a previous call
+    if (lane == 31) scan_tmp[w] = inc;
+    __syncthreads();
+    int woff = 0;
+    for (int k = 0; k < w; ++k) woff += scan_tmp[k];
+    excl_a = woff + inc - s;
+    excl_b = excl_a + a;
+}
+
+struct SortSmem {
+    int cnt[kSortWarps][kRadix];      // per-warp digit counts, later exclusive offsets across warps
+    int base[kRadix];                 // global position of the tile's first key of each digit
+    int next_tab[kRadix];             // next pass's digit counts of this tile
+    int tile_excl[kRadix];            // position of each digit's first key inside the sorted tile
+    uint64_t skey[kSortTile];         // the tile, sorted by digit
+    int32_t sval[kSortTile];
+    int scan_tmp[kSortWarps];
+    uint32_t tile;
+};
+
+__global__ void __launch_bounds__(kSortThreads, 2) sort_onesweep_kernel(
     const uint64_t* __restrict__ keys_in, const int32_t* __restrict__ vals_in,
     uint64_t* __restrict__ keys_out, int32_t* __restrict__ vals_out,
     const int64_t* __restrict__ n_ptr, int64_t capacity, int pass, int shift, int mask, int next_shift, int next_mask,
     SortHeader* __restrict__ hdr, uint32_t* __restrict__ desc, uint32_t* __restrict__ desc_next) {
-    __shared__ int cnt[kSortWarps][kRadix];     // per-warp digit counts, later exclusive offsets across warps
-    __shared__ int base[kRadix];                // global position of the tile's first key of each digit
-    __shared__ int next_tab[kRadix];            // next pass's digit counts of this tile
-    __shared__ int scan_tmp[kSortWarps];
-    __shared__ uint32_t tile_s;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    SortSmem& sm = *reinterpret_cast<SortSmem*>(smem_raw);
 
 #ifdef SSB_SORT_PROFILE
     long long tk[7];
@@ -116,69 +160,87 @@ __global__ void __launch_bounds__(kSortThreads, 3) sort_onesweep_kernel(
     SSB_TICK(0);
     const int64_t n = min(*n_ptr, capacity);
     const int64_t n_tiles = (n + kSortTile - 1) / kSortTile;
-    if (threadIdx.x == 0) tile_s = atomicAdd(&hdr->ticket[pass], 1u);
-    for (int i = threadIdx.x; i < kSortWarps * kRadix; i += kSortThreads) (&cnt[0][0])[i] = 0;
-    for (int i = threadIdx.x; i < kRadix; i += kSortThreads) next_tab[i] = 0;
+    if (threadIdx.x == 0) sm.tile = atomicAdd(&hdr->ticket[pass], 1u);
+    for (int i = threadIdx.x; i < kSortWarps * kRadix; i += kSortThreads) (&sm.cnt[0][0])[i] = 0;
+    for (int i = threadIdx.x; i < kRadix; i += kSortThreads) sm.next_tab[i] = 0;
     __syncthreads();
-    const int64_t tile = tile_s;
+    const int64_t tile = sm.tile;
     if (tile >= n_tiles) return;
     SSB_TICK(1);
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const int64_t wbase = tile * kSortTile + (int64_t)w * kSortWarpSpan;
-
-    // exclusive scan of the pass's digit totals (512 values, two per thread)
-    {
-        int a = (int)hdr->hist[pass][2 * threadIdx.x], b = (int)hdr->hist[pass][2 * threadIdx.x + 1];
-        int s = a + b, inc = s;
-        for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += t; }
-        if (lane == 31) scan_tmp[w] = inc;
-        __syncthreads();
-        int woff = 0;
-        for (int k = 0; k < w; ++k) woff += scan_tmp[k];
-        int excl = woff + inc - s;
-        base[2 * threadIdx.x] = excl;
-        base[2 * threadIdx.x + 1] = excl + a;
-    }
+    const int64_t tile_begin = tile * kSortTile;
+    const int tile_count = (int)min((int64_t)kSortTile, n - tile_begin);
+    const int64_t wbase = tile_begin + (int64_t)w * kSortWarpSpan;
+    const int nbits = __popc((unsigned)mask);
 
     uint64_t key[kSortItems];
+    int32_t val[kSortItems];
     int rank[kSortItems];
 #pragma unroll
     for (int r = 0; r < kSortItems; ++r) {
         int64_t i = wbase + r * 32 + lane;
         key[r] = i < n ? keys_in[i] : 0;
     }
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        int64_t i = wbase + r * 32 + lane;
+        val[r] = i < n ? vals_in[i] : 0;
+    }
+    // exclusive scan of the pass's digit totals -> base[] (the global loads overlap the key loads)
+    {
+        const int a = (int)hdr->hist[pass][2 * threadIdx.x], b = (int)hdr->hist[pass][2 * threadIdx.x + 1];
+        int ea, eb;
+        scan512(a, b, sm.scan_tmp, ea, eb);
+        sm.base[2 * threadIdx.x] = ea;
+        sm.base[2 * threadIdx.x + 1] = eb;
+    }
     SSB_TICK(2);
 #pragma unroll
     for (int r = 0; r < kSortItems; ++r) {
-        bool valid = wbase + r * 32 + lane < n;
-        rank[r] = warp_rank(cnt[w], digit_of(key[r], shift, mask), valid, lane);
+        const bool valid = wbase + r * 32 + lane < n;
+        rank[r] = warp_rank(sm.cnt[w], digit_of(key[r], shift, mask), valid, lane, nbits);
+        if (next_mask != 0) warp_count(sm.next_tab, digit_of(key[r], next_shift, next_mask), valid);
     }
     SSB_TICK(3);
-    if (next_mask != 0) {
-#pragma unroll
-        for (int r = 0; r < kSortItems; ++r) {
-            bool valid = wbase + r * 32 + lane < n;
-            warp_count(next_tab, digit_of(key[r], next_shift, next_mask), valid, lane);
-        }
-    }
     __syncthreads();
-    SSB_TICK(4);
 
-    // per digit: offsets of the warps inside the tile, publish, look back, publish again
-    for (int d = threadIdx.x; d < kRadix; d += kSortThreads) {
+    // per digit: offsets of the warps inside the tile; publish the tile's counts at once
+    int tot[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int d = 2 * threadIdx.x + h;
         int run = 0;
 #pragma unroll
-        for (int k = 0; k < kSortWarps; ++k) { int t = cnt[k][d]; cnt[k][d] = run; run += t; }
-        const uint32_t total = (uint32_t)run;
-        volatile uint32_t* row = desc + tile * kRadix;
+        for (int k = 0; k < kSortWarps; ++k) { int t = sm.cnt[k][d]; sm.cnt[k][d] = run; run += t; }
+        tot[h] = run;
+        ((volatile uint32_t*)desc)[tile * kRadix + d] = (tile == 0 ? kFlagInclusive : kFlagAggregate) | (uint32_t)run;
+    }
+    {
+        int ea, eb;
+        scan512(tot[0], tot[1], sm.scan_tmp, ea, eb);
+        sm.tile_excl[2 * threadIdx.x] = ea;
+        sm.tile_excl[2 * threadIdx.x + 1] = eb;
+    }
+    __syncthreads();
+    // stage the tile in digit order (stable: warps in order, rounds in order, lanes in order)
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        if (wbase + r * 32 + lane < n) {
+            const int d = digit_of(key[r], shift, mask);
+            const int lpos = sm.tile_excl[d] + sm.cnt[w][d] + rank[r];
+            sm.skey[lpos] = key[r];
+            sm.sval[lpos] = val[r];
+        }
+    }
+    SSB_TICK(4);
+
+    // look back over the predecessors, kLookWindow rows at a time: the loads of a window are
+    // independent, so a run of count-only rows costs one memory latency per window, not per row
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int d = 2 * threadIdx.x + h;
         uint32_t prefix = 0;
-        if (tile == 0) {
-            row[d] = kFlagInclusive | total;
-        } else {
-            row[d] = kFlagAggregate | total;
-            // Look back over the predecessors, kLookWindow rows at a time: the loads of a
-            // window are independent, so a long run of count-only rows costs one memory
-            // latency per window instead of one per row.
+        if (tile != 0) {
             bool done = false;
             for (int64_t t = tile - 1; t >= 0 && !done; t -= kLookWindow) {
                 uint32_t v[kLookWindow];
@@ -203,25 +265,23 @@ __global__ void __launch_bounds__(kSortThreads, 3) sort_onesweep_kernel(
                     if ((x >> 30) != 1u) done = true;      // inclusive prefix (or gave up): stop
                 }
             }
-            row[d] = kFlagInclusive | ((prefix + total) & kValueMask);
+            ((volatile uint32_t*)desc)[tile * kRadix + d] = kFlagInclusive | ((prefix + (uint32_t)tot[h]) & kValueMask);
         }
-        base[d] += (int)prefix;
+        sm.base[d] += (int)prefix;
         // ready the other descriptor region for the next pass, and hand on the next digit's totals
         desc_next[tile * kRadix + d] = 0u;
-        if (next_mask != 0 && next_tab[d]) atomicAdd(&hdr->hist[pass + 1][d], (uint32_t)next_tab[d]);
+        if (next_mask != 0 && sm.next_tab[d]) atomicAdd(&hdr->hist[pass + 1][d], (uint32_t)sm.next_tab[d]);
     }
     __syncthreads();
     SSB_TICK(5);
 
-#pragma unroll
-    for (int r = 0; r < kSortItems; ++r) {
-        int64_t i = wbase + r * 32 + lane;
-        if (i < n) {
-            int d = digit_of(key[r], shift, mask);
-            int64_t pos = (int64_t)base[d] + cnt[w][d] + rank[r];
-            keys_out[pos] = key[r];
-            vals_out[pos] = vals_in[i];
-        }
+    // write out in sorted-tile order: neighbouring threads write neighbouring addresses
+    for (int i = threadIdx.x; i < tile_count; i += kSortThreads) {
+        const uint64_t k = sm.skey[i];
+        const int d = digit_of(k, shift, mask);
+        const int64_t pos = (int64_t)sm.base[d] + (i - sm.tile_excl[d]);
+        keys_out[pos] = k;
+        vals_out[pos] = sm.sval[i];
     }
     SSB_TICK(6);
 #ifdef SSB_SORT_PROFILE
@@ -268,6 +328,11 @@ int ssb_sort_pairs_u64(int64_t* d_keys_a, int32_t* d_vals_a, int64_t* d_keys_b, 
     const int64_t region_bytes = align_up(desc_region_words(capacity) * 4, 256);
     uint32_t* desc[2] = {(uint32_t*)(ws + align_up((int64_t)sizeof(SortHeader), 256)),
                          (uint32_t*)(ws + align_up((int64_t)sizeof(SortHeader), 256) + region_bytes)};
+    static bool attr_set = false;
+    if (!attr_set) {
+        SSB_CUDA(cudaFuncSetAttribute(sort_onesweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem)));
+        attr_set = true;
+    }
     SSB_CUDA(cudaMemsetAsync(hdr, 0, sizeof(SortHeader), st));
     const int64_t tiles_cap = ceil_div(capacity, kSortTile);
     int hist_blocks = (int)(tiles_cap < 148 * 8 ? tiles_cap : 148 * 8);
@@ -278,7 +343,7 @@ int ssb_sort_pairs_u64(int64_t* d_keys_a, int32_t* d_vals_a, int64_t* d_keys_b, 
     int32_t* vbuf[2] = {d_vals_a, d_vals_b};
     for (int p = 0; p < passes; ++p) {
         const bool last = p + 1 == passes;
-        sort_onesweep_kernel<<<(unsigned)tiles_cap, kSortThreads, 0, st>>>(
+        sort_onesweep_kernel<<<(unsigned)tiles_cap, kSortThreads, sizeof(SortSmem), st>>>(
             kbuf[sel], vbuf[sel], kbuf[sel ^ 1], vbuf[sel ^ 1], d_n, capacity, p, shifts[p], (1 << bits[p]) - 1,
             last ? 0 : shifts[p + 1], last ? 0 : (1 << bits[p + 1]) - 1, hdr, desc[p & 1], desc[(p + 1) & 1]);
         SSB_LAUNCHED("sort_onesweep_kernel");

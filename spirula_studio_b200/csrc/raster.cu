@@ -222,42 +222,47 @@ __global__ void __launch_bounds__(kBwdWarps * 32) raster_bwd_kernel(
                 const float4* r = (const float4*)(screen + g);
                 a = r[0]; b = r[1]; c = r[2];
             }
-            float gx = 0.f, gy = 0.f, gca = 0.f, gcb = 0.f, gcc = 0.f, gop = 0.f, gr = 0.f, gg = 0.f, gb = 0.f, gd = 0.f;
+            // conic pre-scaled so that exp(-sigma) = 2^(-q): q = A2 dx^2 + B2 dx dy + C2 dy^2
+            const float kLog2e = 1.4426950408889634f;
+            const float A2 = 0.5f * kLog2e * b.x, B2 = kLog2e * b.y, C2 = 0.5f * kLog2e * b.z, op = b.w;
+            // sums over this micro-tile's pixels: v_sigma * {dx^2, dx dy, dy^2, dx, dy}, vis * v_alpha, weights * v_colour
+            float s_xx = 0.f, s_xy = 0.f, s_yy = 0.f, s_x = 0.f, s_y = 0.f, gop = 0.f, gr = 0.f, gg = 0.f, gb = 0.f, gd = 0.f;
             const int steps = bs + 63;
             for (int t = 0; t < steps; ++t) {
                 const unsigned p = (unsigned)(t - lane);
                 if (p < 64u && sidx <= sLast[w][p]) {      // inactive lanes carry sidx = INT_MAX
                     const float4 pp = sP[w][p];
                     const float dx = a.x - pp.z, dy = a.y - pp.w;
-                    const float sigma = 0.5f * (b.x * dx * dx + b.z * dy * dy) + b.y * dx * dy;
-                    const float vis = __expf(-sigma);
-                    const float ov = b.w * vis;
+                    const float q = fmaf(fmaf(A2, dx, B2 * dy), dx, C2 * dy * dy);
+                    float vis;
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(vis) : "f"(-q));
+                    const float ov = op * vis;
                     const float alpha = fminf(0.999f, ov);
-                    if (sigma >= 0.f && alpha > kAlphaThreshold) {
+                    if (q >= 0.f && alpha > kAlphaThreshold) {
                         const float4 vc = sV[w][p];
-                        const float ra = __fdividef(1.0f, 1.0f - alpha);
-                        const float T0 = pp.x * ra;
-                        const float cdot = c.x * vc.x + c.y * vc.y + c.z * vc.z + c.w * vc.w;
+                        const float om = 1.0f - alpha;
+                        const float T0 = __fdividef(pp.x, om);
+                        const float cdot = fmaf(c.x, vc.x, fmaf(c.y, vc.y, fmaf(c.z, vc.z, c.w * vc.w)));
                         const float v_alpha = T0 * (cdot - pp.y);
                         const float wgt = alpha * T0;
-                        const float v_T0 = alpha * cdot + pp.y * (1.0f - alpha);
-                        if (ov <= 0.999f) {
-                            const float v_sigma = -ov * v_alpha;
-                            const float sx = v_sigma * dx, sy = v_sigma * dy;
-                            gca += 0.5f * sx * dx;
-                            gcb += sx * dy;
-                            gcc += 0.5f * sy * dy;
-                            gx += b.x * sx + b.y * sy;
-                            gy += b.y * sx + b.z * sy;
-                            gop += vis * v_alpha;
-                        }
-                        gr += vc.x * wgt; gg += vc.y * wgt; gb += vc.z * wgt; gd += vc.w * wgt;
+                        const float v_T0 = fmaf(alpha, cdot, pp.y * om);
+                        // a saturated fragment (opacity * vis > 0.999) passes no gradient to its shape
+                        const float vis_eff = ov <= 0.999f ? vis : 0.0f;
+                        const float va = vis_eff * v_alpha;
+                        const float v_sigma = -op * va;
+                        const float sx = v_sigma * dx, sy = v_sigma * dy;
+                        s_xx = fmaf(sx, dx, s_xx); s_xy = fmaf(sx, dy, s_xy); s_yy = fmaf(sy, dy, s_yy);
+                        s_x += sx; s_y += sy;
+                        gop += va;
+                        gr = fmaf(vc.x, wgt, gr); gg = fmaf(vc.y, wgt, gg); gb = fmaf(vc.z, wgt, gb); gd = fmaf(vc.w, wgt, gd);
                         *(float2*)&sP[w][p] = make_float2(T0, v_T0);
                     }
                 }
                 __syncwarp();
             }
             if (active) {
+                const float gca = 0.5f * s_xx, gcb = s_xy, gcc = 0.5f * s_yy;
+                const float gx = b.x * s_x + b.y * s_y, gy = b.y * s_x + b.z * s_y;
                 // non-finite components are dropped, as the reference's atomics do
                 // (src/core/Common.cuh:792-856)
                 auto fz = [](float v) { return isfinite(v) ? v : 0.0f; };

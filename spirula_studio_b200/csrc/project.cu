@@ -169,17 +169,19 @@ __global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
     const int cid = blockIdx.y;
     const int64_t first = (int64_t)blockIdx.x * kProjBlock;
     const int64_t gid = first + threadIdx.x;
+    // per-splat loads are issued before the SH span is staged, so both are in flight together
+    const int64_t gl = gid < n ? gid : n - 1;
+    float mean[3] = {sp.means[3 * gl], sp.means[3 * gl + 1], sp.means[3 * gl + 2]};
+    float4 q4 = ((const float4*)sp.quats)[gl];
+    float quat[4] = {q4.x, q4.y, q4.z, q4.w};
+    float scale[3] = {sp.scales[3 * gl], sp.scales[3 * gl + 1], sp.scales[3 * gl + 2]};
+    float in_op = sp.opacities[gl];
+    float dc_in[3] = {sp.features_dc[3 * gl], sp.features_dc[3 * gl + 1], sp.features_dc[3 * gl + 2]};
+    CamDev cam = load_cam(viewmats, intrins, cid);
     stage_sh(sh_s, sp.features_sh, shq.packed, shq.bounds, shq.bits, shq.bounds_stride, first, n);
     __syncthreads();
     if (gid >= n) return;
     const int64_t idx = (int64_t)cid * n + gid;
-    CamDev cam = load_cam(viewmats, intrins, cid);
-
-    float mean[3] = {sp.means[3 * gid], sp.means[3 * gid + 1], sp.means[3 * gid + 2]};
-    float4 q4 = ((const float4*)sp.quats)[gid];
-    float quat[4] = {q4.x, q4.y, q4.z, q4.w};
-    float scale[3] = {sp.scales[3 * gid], sp.scales[3 * gid + 1], sp.scales[3 * gid + 2]};
-    float in_op = sp.opacities[gid];
 
     ProjGeom g;
     bool ok = project_pinhole<false>(cam, W, antialiased != 0, mean, quat, scale, in_op, g);
@@ -205,7 +207,7 @@ __global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
         const float* sh = sh_s + threadIdx.x * kShPerSplat;
 #pragma unroll
         for (int ch = 0; ch < 3; ++ch) {
-            float c = kShC0 * sp.features_dc[3 * gid + ch];
+            float c = kShC0 * dc_in[ch];
 #pragma unroll
             for (int j = 0; j < kNumSh; ++j) c += b[j] * sh[3 * j + ch];
             rgb[ch] = fmaxf(c + 0.5f, 0.0f);
@@ -282,6 +284,21 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
     const int64_t first = (int64_t)blockIdx.x * kProjBlock;
     const int64_t gid = first + threadIdx.x;
     const int count = (int)min((int64_t)kProjBlock, n - first) * kShPerSplat;
+    // per-splat loads (and, for a single view, its aabb and gradient record) are issued before
+    // the SH span is staged, so both groups of loads are in flight together
+    const int64_t gl = gid < n ? gid : n - 1;
+    float mean[3] = {sp.means[3 * gl], sp.means[3 * gl + 1], sp.means[3 * gl + 2]};
+    float4 q4 = ((const float4*)sp.quats)[gl];
+    float quat[4] = {q4.x, q4.y, q4.z, q4.w};
+    float scale[3] = {sp.scales[3 * gl], sp.scales[3 * gl + 1], sp.scales[3 * gl + 2]};
+    float in_op = sp.opacities[gl];
+    float dc_in[3] = {sp.features_dc[3 * gl], sp.features_dc[3 * gl + 1], sp.features_dc[3 * gl + 2]};
+    float4 bb0 = aabb[gl];
+    float4 vr0[3];
+    {
+        const float4* vr = (const float4*)(v_screen + gl);
+        vr0[0] = vr[0]; vr0[1] = vr[1]; vr0[2] = vr[2];
+    }
     stage_sh(sh_s, sp.features_sh, shq.packed, shq.bounds, shq.bits, shq.bounds_stride, first, n);
     if (MULTI_VIEW) for (int i = threadIdx.x; i < count; i += kProjBlock) shg_s[i] = 0.f;
     __syncthreads();
@@ -289,21 +306,18 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
 
     float g_mean[3] = {0.f, 0.f, 0.f}, g_quat[4] = {0.f, 0.f, 0.f, 0.f}, g_scale[3] = {0.f, 0.f, 0.f}, g_op = 0.f, g_dc[3] = {0.f, 0.f, 0.f};
     if (gid < n) {
-        float mean[3] = {sp.means[3 * gid], sp.means[3 * gid + 1], sp.means[3 * gid + 2]};
-        float4 q4 = ((const float4*)sp.quats)[gid];
-        float quat[4] = {q4.x, q4.y, q4.z, q4.w};
-        float scale[3] = {sp.scales[3 * gid], sp.scales[3 * gid + 1], sp.scales[3 * gid + 2]};
-        float in_op = sp.opacities[gid];
         const float* sh = sh_s + threadIdx.x * kShPerSplat;
         float* shg = shg_s + threadIdx.x * kShPerSplat;
         for (int cid = 0; cid < C; ++cid) {
             const int64_t idx = (int64_t)cid * n + gid;
-            float4 bb = aabb[idx];
+            float4 bb = cid == 0 ? bb0 : aabb[idx];
             if (bb.z <= bb.x || bb.w <= bb.y) continue;
             any_view = true;
             CamDev cam = load_cam(viewmats, intrins, cid);
             float4* vr = (float4*)(v_screen + idx);
-            float4 va = vr[0], vb = vr[1], vc4 = vr[2];
+            float4 va, vb, vc4;
+            if (cid == 0) { va = vr0[0]; vb = vr0[1]; vc4 = vr0[2]; }
+            else { va = vr[0]; vb = vr[1]; vc4 = vr[2]; }
             if (clear_v_screen) {   // leave the record ready for the next view's reductions
                 const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
                 vr[0] = zero; vr[1] = zero; vr[2] = zero;
@@ -421,7 +435,7 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
             float vcol[3] = {vc4.x, vc4.y, vc4.z};
 #pragma unroll
             for (int ch = 0; ch < 3; ++ch) {
-                float raw = kShC0 * sp.features_dc[3 * gid + ch];
+                float raw = kShC0 * dc_in[ch];
 #pragma unroll
                 for (int j = 0; j < kNumSh; ++j) raw += b[j] * sh[3 * j + ch];
                 if (!(raw >= -0.5f)) vcol[ch] = 0.f;

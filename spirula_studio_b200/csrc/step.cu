@@ -8,32 +8,51 @@
 // DevicePool; they are sized once for (n_splats, width, height, capacity) and
 // reused for every view, so a step performs no allocation and no host
 // synchronisation: the (splat, tile) pair count stays on the device.
+//
+// Views are independent until their gradients are added, so the object keeps
+// TWO sets of per-view buffers ("lanes") and runs consecutive views on two
+// internal streams: the latency-bound stages of one view (key generation, sort,
+// projection backward) fill the issue slots the arithmetic-bound rasteriser of
+// the other leaves idle.  The projection backward of view v waits for that of
+// view v-1, so gradients are accumulated in view order exactly as the serial
+// loop does.  The caller's stream is joined on both sides: everything it
+// enqueued before the call is visible to the lanes, and everything the lanes do
+// is complete before work it enqueues afterwards.
 #include "ssb_common.cuh"
 
 #include <new>
 
-enum { SsbStep_kMaxProfViews = 64 };
+enum { SsbStep_kMaxProfViews = 64, SsbStep_kLanes = 2 };
 
-struct SsbStep {
-    SsbStepConfig cfg;
-    int tw, th;
-    int64_t capacity;
-    int64_t bytes;
-    // per-view intermediates
+struct SsbLane {
     float* aabb;          // [n][4]
     float* depths;        // [n]
-    float* radii;         // [n]
     SsbScreenRec* screen; // [n]
     SsbScreenRec* v_screen;
-    void* keys_ws; int64_t keys_ws_bytes;
-    void* sort_ws; int64_t sort_ws_bytes;
+    void* keys_ws;
+    void* sort_ws;
     int64_t* ids[2];
     int32_t* flat[2];
     int64_t* n_isects;    // device
     int32_t* offsets;     // [tiles]
     float* rgb; float* depth; float* T; int32_t* last_ids; float* v_rgb;
     int sel;
-    // optional per-stage timing
+    cudaStream_t stream;
+    cudaEvent_t bwd_done;  // this lane's last projection backward
+    cudaEvent_t all_done;
+};
+
+struct SsbStep {
+    SsbStepConfig cfg;
+    int tw, th;
+    int64_t capacity;
+    int64_t bytes;
+    int64_t keys_ws_bytes, sort_ws_bytes;
+    int n_lanes;
+    int last_lane;
+    SsbLane lane[SsbStep_kLanes];
+    cudaEvent_t fork;
+    // optional per-stage timing (views then run one after another on the caller's stream)
     int profiling;
     int prof_views;                                   // views recorded and not yet read
     cudaEvent_t ev[SsbStep_kMaxProfViews][SSB_STAGE_COUNT + 1];
@@ -57,17 +76,101 @@ static int dev_alloc(T** p, int64_t count, int64_t& total) {
     return SSB_OK;
 }
 
+static void lane_free(SsbLane& l) {
+    cudaFree(l.aabb); cudaFree(l.depths); cudaFree(l.screen); cudaFree(l.v_screen);
+    cudaFree(l.keys_ws); cudaFree(l.sort_ws);
+    cudaFree(l.ids[0]); cudaFree(l.ids[1]); cudaFree(l.flat[0]); cudaFree(l.flat[1]);
+    cudaFree(l.n_isects); cudaFree(l.offsets);
+    cudaFree(l.rgb); cudaFree(l.depth); cudaFree(l.T); cudaFree(l.last_ids); cudaFree(l.v_rgb);
+    if (l.stream) cudaStreamDestroy(l.stream);
+    if (l.bwd_done) cudaEventDestroy(l.bwd_done);
+    if (l.all_done) cudaEventDestroy(l.all_done);
+}
+
+static int lane_alloc(SsbStep* s, SsbLane& l) {
+    const int64_t n = s->cfg.n_splats, P = (int64_t)s->cfg.width * s->cfg.height, cap = s->capacity;
+    int64_t& tot = s->bytes;
+    int e = SSB_OK;
+    char* kws = nullptr; char* sws = nullptr;
+    if (!e) e = dev_alloc(&l.aabb, n * 4, tot);
+    if (!e) e = dev_alloc(&l.depths, n, tot);
+    if (!e) e = dev_alloc(&l.screen, n, tot);
+    if (!e) e = dev_alloc(&l.v_screen, n, tot);
+    if (!e) e = dev_alloc(&kws, s->keys_ws_bytes, tot);
+    if (!e) e = dev_alloc(&sws, s->sort_ws_bytes, tot);
+    l.keys_ws = kws; l.sort_ws = sws;
+    for (int k = 0; k < 2 && !e; ++k) {
+        e = dev_alloc(&l.ids[k], cap, tot);
+        if (!e) e = dev_alloc(&l.flat[k], cap, tot);
+    }
+    if (!e) e = dev_alloc(&l.n_isects, 1, tot);
+    if (!e) e = dev_alloc(&l.offsets, (int64_t)s->tw * s->th + 1, tot);
+    if (!e) e = dev_alloc(&l.rgb, P * 3, tot);
+    if (!e) e = dev_alloc(&l.depth, P, tot);
+    if (!e) e = dev_alloc(&l.T, P, tot);
+    if (!e) e = dev_alloc(&l.last_ids, P, tot);
+    if (!e) e = dev_alloc(&l.v_rgb, P * 3, tot);
+    if (e) return e;
+    SSB_CUDA(cudaMemset(l.v_screen, 0, n * sizeof(SsbScreenRec)));
+    SSB_CUDA(cudaMemset(l.n_isects, 0, sizeof(int64_t)));
+    SSB_CUDA(cudaMemset(l.sort_ws, 0, s->sort_ws_bytes));
+    SSB_CUDA(cudaStreamCreateWithFlags(&l.stream, cudaStreamNonBlocking));
+    SSB_CUDA(cudaEventCreateWithFlags(&l.bwd_done, cudaEventDisableTiming));
+    SSB_CUDA(cudaEventCreateWithFlags(&l.all_done, cudaEventDisableTiming));
+    return SSB_OK;
+}
+
+// All stages of one view on one stream.
+static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbShQuant* shq, const float* d_viewmats, const float* d_intrins,
+                    const float* d_gt, int v, const SsbSplats* grads, int accumulate, float* d_losses, cudaStream_t st,
+                    cudaEvent_t wait_before_bwd, cudaEvent_t* ev) {
+    const int64_t n = s->cfg.n_splats;
+    const int W = s->cfg.width, H = s->cfg.height;
+    const int64_t P = (int64_t)W * H;
+    const int64_t n_tiles = (int64_t)s->tw * s->th;
+    const int end_bit = 32 + ssb_tile_n_bits(n_tiles);
+    SsbCameras cam;
+    cam.d_viewmats = d_viewmats + 16 * (int64_t)v;
+    cam.d_intrins = d_intrins + 4 * (int64_t)v;
+    cam.count = 1; cam.width = W; cam.height = H;
+    cam.model = s->cfg.camera_model; cam.antialiased = s->cfg.antialiased;
+    int e;
+#define SSB_MARK(k) do { if (ev) SSB_CUDA(cudaEventRecord(ev[k], st)); } while (0)
+    SSB_MARK(0);
+    if ((e = ssb_project_fwd(params, shq, n, &cam, l.aabb, l.depths, nullptr, l.screen, st))) return e;
+    SSB_MARK(1);
+    if ((e = ssb_tile_keys(l.aabb, l.depths, l.screen, n, n, W, H, l.keys_ws, s->keys_ws_bytes, nullptr, nullptr,
+                           l.ids[0], l.flat[0], s->capacity, l.n_isects, nullptr, st))) return e;
+    SSB_MARK(2);
+    int32_t sel = 0;
+    if ((e = ssb_sort_pairs_u64(l.ids[0], l.flat[0], l.ids[1], l.flat[1], l.n_isects, s->capacity, 0, end_bit,
+                                l.sort_ws, s->sort_ws_bytes, &sel, st))) return e;
+    l.sel = sel;
+    SSB_MARK(3);
+    if ((e = ssb_tile_ranges(l.ids[sel], l.n_isects, s->capacity, n_tiles, l.offsets, st))) return e;
+    SSB_MARK(4);
+    if ((e = ssb_raster_fwd(l.screen, l.offsets, l.flat[sel], l.n_isects, 1, W, H, l.rgb, l.depth, l.T, l.last_ids, st))) return e;
+    SSB_MARK(5);
+    if ((e = launch_loss(l.rgb, d_gt + (int64_t)v * P * 3, 1, H, W, s->cfg.w_l1, s->cfg.w_ssim, l.v_rgb, d_losses, st))) return e;
+    SSB_MARK(6);
+    if ((e = ssb_raster_bwd(l.screen, l.offsets, l.flat[sel], l.n_isects, 1, W, H, l.depth, l.T, l.last_ids,
+                            l.v_rgb, nullptr, nullptr, l.v_screen, st))) return e;
+    SSB_MARK(7);
+    if (wait_before_bwd) SSB_CUDA(cudaStreamWaitEvent(st, wait_before_bwd, 0));
+    if ((e = launch_project_bwd(params, shq, n, &cam, l.aabb, l.v_screen, grads, accumulate, 1, st))) return e;
+    SSB_MARK(8);
+#undef SSB_MARK
+    return SSB_OK;
+}
+
 }  // namespace ssb
 
 extern "C" {
 
 void ssb_step_destroy(SsbStep* s) {
     if (!s) return;
-    cudaFree(s->aabb); cudaFree(s->depths); cudaFree(s->radii); cudaFree(s->screen); cudaFree(s->v_screen);
-    cudaFree(s->keys_ws); cudaFree(s->sort_ws);
-    cudaFree(s->ids[0]); cudaFree(s->ids[1]); cudaFree(s->flat[0]); cudaFree(s->flat[1]);
-    cudaFree(s->n_isects); cudaFree(s->offsets);
-    cudaFree(s->rgb); cudaFree(s->depth); cudaFree(s->T); cudaFree(s->last_ids); cudaFree(s->v_rgb);
+    for (int k = 0; k < SsbStep_kLanes; ++k) ssb::lane_free(s->lane[k]);
+    if (s->fork) cudaEventDestroy(s->fork);
     if (s->ev_ready)
         for (int v = 0; v < SsbStep_kMaxProfViews; ++v)
             for (int k = 0; k <= SSB_STAGE_COUNT; ++k) cudaEventDestroy(s->ev[v][k]);
@@ -88,36 +191,15 @@ int ssb_step_create(const SsbStepConfig* cfg, SsbStep** out) {
     s->th = (cfg->height + kTile - 1) / kTile;
     s->capacity = cfg->isect_capacity > 0 ? cfg->isect_capacity : 12 * cfg->n_splats;
     if (s->capacity >= ((int64_t)1 << 30)) s->capacity = ((int64_t)1 << 30) - 1;
-    const int64_t n = cfg->n_splats, P = (int64_t)cfg->width * cfg->height, cap = s->capacity;
-    s->keys_ws_bytes = ssb_tile_keys_workspace_bytes(n);
-    s->sort_ws_bytes = ssb_sort_workspace_bytes(cap);
-    int e = SSB_OK;
-    int64_t& tot = s->bytes;
-    char* kws = nullptr; char* sws = nullptr;
-    if (!e) e = dev_alloc(&s->aabb, n * 4, tot);
-    if (!e) e = dev_alloc(&s->depths, n, tot);
-    if (!e) e = dev_alloc(&s->radii, n, tot);
-    if (!e) e = dev_alloc(&s->screen, n, tot);
-    if (!e) e = dev_alloc(&s->v_screen, n, tot);
-    if (!e) e = dev_alloc(&kws, s->keys_ws_bytes, tot);
-    if (!e) e = dev_alloc(&sws, s->sort_ws_bytes, tot);
-    s->keys_ws = kws; s->sort_ws = sws;
-    for (int k = 0; k < 2 && !e; ++k) {
-        e = dev_alloc(&s->ids[k], cap, tot);
-        if (!e) e = dev_alloc(&s->flat[k], cap, tot);
+    s->keys_ws_bytes = ssb_tile_keys_workspace_bytes(cfg->n_splats);
+    s->sort_ws_bytes = ssb_sort_workspace_bytes(s->capacity);
+    s->n_lanes = SsbStep_kLanes;
+    for (int k = 0; k < s->n_lanes; ++k) {
+        int e = lane_alloc(s, s->lane[k]);
+        if (e) { ssb_step_destroy(s); return e; }
     }
-    if (!e) e = dev_alloc(&s->n_isects, 1, tot);
-    if (!e) e = dev_alloc(&s->offsets, (int64_t)s->tw * s->th + 1, tot);
-    if (!e) e = dev_alloc(&s->rgb, P * 3, tot);
-    if (!e) e = dev_alloc(&s->depth, P, tot);
-    if (!e) e = dev_alloc(&s->T, P, tot);
-    if (!e) e = dev_alloc(&s->last_ids, P, tot);
-    if (!e) e = dev_alloc(&s->v_rgb, P * 3, tot);
-    if (e) { ssb_step_destroy(s); return e; }
-    cudaError_t ce = cudaMemset(s->v_screen, 0, n * sizeof(SsbScreenRec));
-    if (ce == cudaSuccess) ce = cudaMemset(s->radii, 0, n * sizeof(float));
-    if (ce == cudaSuccess) ce = cudaMemset(s->n_isects, 0, sizeof(int64_t));
-    if (ce != cudaSuccess) { ssb_step_destroy(s); return check_cuda(ce, "ssb_step_create: cudaMemset"); }
+    cudaError_t ce = cudaEventCreateWithFlags(&s->fork, cudaEventDisableTiming);
+    if (ce != cudaSuccess) { ssb_step_destroy(s); return check_cuda(ce, "ssb_step_create: cudaEventCreate"); }
     *out = s;
     return SSB_OK;
 }
@@ -130,46 +212,34 @@ int ssb_step_views(SsbStep* s, const SsbSplats* params, const SsbShQuant* shq,
     using namespace ssb;
     SSB_REQUIRE(s && params && d_viewmats && d_intrins && d_gt && grads, "ssb_step_views: NULL argument");
     SSB_REQUIRE(n_views >= 0, "ssb_step_views: bad view count");
-    cudaStream_t st = (cudaStream_t)stream;
-    const int64_t n = s->cfg.n_splats;
-    const int W = s->cfg.width, H = s->cfg.height;
-    const int64_t P = (int64_t)W * H;
-    const int64_t n_tiles = (int64_t)s->tw * s->th;
-    const int end_bit = 32 + ssb_tile_n_bits(n_tiles);
+    cudaStream_t user = (cudaStream_t)stream;
+    if (n_views == 0) return SSB_OK;
+    if (s->profiling || n_views == 1) {
+        // one view, or timing requested: everything on the caller's stream, in order
+        for (int v = 0; v < n_views; ++v) {
+            const bool prof = s->profiling && s->prof_views < SsbStep_kMaxProfViews;
+            int e = run_view(s, s->lane[0], params, shq, d_viewmats, d_intrins, d_gt, v, grads, (accumulate || v > 0) ? 1 : 0, d_losses, user,
+                             nullptr, prof ? s->ev[s->prof_views] : nullptr);
+            if (e) return e;
+            if (prof) s->prof_views++;
+        }
+        s->last_lane = 0;
+        return SSB_OK;
+    }
+    SSB_CUDA(cudaEventRecord(s->fork, user));
+    for (int k = 0; k < s->n_lanes; ++k) SSB_CUDA(cudaStreamWaitEvent(s->lane[k].stream, s->fork, 0));
+    cudaEvent_t prev_bwd = nullptr;
     for (int v = 0; v < n_views; ++v) {
-        SsbCameras cam;
-        cam.d_viewmats = d_viewmats + 16 * (int64_t)v;
-        cam.d_intrins = d_intrins + 4 * (int64_t)v;
-        cam.count = 1; cam.width = W; cam.height = H;
-        cam.model = s->cfg.camera_model; cam.antialiased = s->cfg.antialiased;
-        int e;
-        const bool prof = s->profiling && s->prof_views < SsbStep_kMaxProfViews;
-        cudaEvent_t* ev = prof ? s->ev[s->prof_views] : nullptr;
-#define SSB_MARK(k) do { if (prof) SSB_CUDA(cudaEventRecord(ev[k], st)); } while (0)
-        SSB_MARK(0);
-        if ((e = ssb_project_fwd(params, shq, n, &cam, s->aabb, s->depths, nullptr, s->screen, st))) return e;
-        SSB_MARK(1);
-        if ((e = ssb_tile_keys(s->aabb, s->depths, s->screen, n, n, W, H, s->keys_ws, s->keys_ws_bytes, nullptr, nullptr,
-                               s->ids[0], s->flat[0], s->capacity, s->n_isects, nullptr, st))) return e;
-        SSB_MARK(2);
-        int32_t sel = 0;
-        if ((e = ssb_sort_pairs_u64(s->ids[0], s->flat[0], s->ids[1], s->flat[1], s->n_isects, s->capacity, 0, end_bit,
-                                    s->sort_ws, s->sort_ws_bytes, &sel, st))) return e;
-        s->sel = sel;
-        SSB_MARK(3);
-        if ((e = ssb_tile_ranges(s->ids[sel], s->n_isects, s->capacity, n_tiles, s->offsets, st))) return e;
-        SSB_MARK(4);
-        if ((e = ssb_raster_fwd(s->screen, s->offsets, s->flat[sel], s->n_isects, 1, W, H, s->rgb, s->depth, s->T, s->last_ids, st))) return e;
-        SSB_MARK(5);
-        if ((e = launch_loss(s->rgb, d_gt + (int64_t)v * P * 3, 1, H, W, s->cfg.w_l1, s->cfg.w_ssim, s->v_rgb, d_losses, st))) return e;
-        SSB_MARK(6);
-        if ((e = ssb_raster_bwd(s->screen, s->offsets, s->flat[sel], s->n_isects, 1, W, H, s->depth, s->T, s->last_ids,
-                                s->v_rgb, nullptr, nullptr, s->v_screen, st))) return e;
-        SSB_MARK(7);
-        if ((e = launch_project_bwd(params, shq, n, &cam, s->aabb, s->v_screen, grads, (accumulate || v > 0) ? 1 : 0, 1, st))) return e;
-        SSB_MARK(8);
-#undef SSB_MARK
-        if (prof) s->prof_views++;
+        SsbLane& l = s->lane[v % s->n_lanes];
+        int e = run_view(s, l, params, shq, d_viewmats, d_intrins, d_gt, v, grads, (accumulate || v > 0) ? 1 : 0, d_losses, l.stream, prev_bwd, nullptr);
+        if (e) return e;
+        SSB_CUDA(cudaEventRecord(l.bwd_done, l.stream));
+        prev_bwd = l.bwd_done;
+        s->last_lane = v % s->n_lanes;
+    }
+    for (int k = 0; k < s->n_lanes; ++k) {
+        SSB_CUDA(cudaEventRecord(s->lane[k].all_done, s->lane[k].stream));
+        SSB_CUDA(cudaStreamWaitEvent(user, s->lane[k].all_done, 0));
     }
     return SSB_OK;
 }
@@ -206,10 +276,13 @@ int ssb_step_get_profile(SsbStep* s, float* ms, int32_t* n_views) {
 int ssb_step_last_isects(SsbStep* s, int64_t* h_n_isects, void* stream) {
     using namespace ssb;
     SSB_REQUIRE(s && h_n_isects, "ssb_step_last_isects: NULL argument");
-    SSB_CUDA(cudaMemcpyAsync(h_n_isects, s->n_isects, sizeof(int64_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    SsbLane& l = s->lane[s->last_lane];
+    SSB_CUDA(cudaMemcpyAsync(h_n_isects, l.n_isects, sizeof(int64_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     SSB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
-    int e = ssb_sort_check(s->sort_ws, stream);
-    if (e) return e;
+    for (int k = 0; k < s->n_lanes; ++k) {
+        int e = ssb_sort_check(s->lane[k].sort_ws, stream);
+        if (e) return e;
+    }
     if (*h_n_isects > s->capacity) {
         set_error("ssb_step: %lld (splat, tile) pairs exceed the capacity of %lld; pairs beyond it were dropped", (long long)*h_n_isects, (long long)s->capacity);
         return SSB_ERR_CAPACITY;
@@ -221,12 +294,13 @@ int ssb_step_peek(SsbStep* s, const float** d_rgb, const float** d_depth, const 
                   const int32_t** d_last_ids, const SsbScreenRec** d_screen, const float** d_aabb) {
     using namespace ssb;
     SSB_REQUIRE(s, "ssb_step_peek: NULL step");
-    if (d_rgb) *d_rgb = s->rgb;
-    if (d_depth) *d_depth = s->depth;
-    if (d_T) *d_T = s->T;
-    if (d_last_ids) *d_last_ids = s->last_ids;
-    if (d_screen) *d_screen = s->screen;
-    if (d_aabb) *d_aabb = s->aabb;
+    SsbLane& l = s->lane[s->last_lane];
+    if (d_rgb) *d_rgb = l.rgb;
+    if (d_depth) *d_depth = l.depth;
+    if (d_T) *d_T = l.T;
+    if (d_last_ids) *d_last_ids = l.last_ids;
+    if (d_screen) *d_screen = l.screen;
+    if (d_aabb) *d_aabb = l.aabb;
     return SSB_OK;
 }
 

@@ -143,19 +143,43 @@ class Trainer:
         self.allreduce_grads()
         self.optimizer_step(total_views)
 
-    def train_step(self, h_viewmats, h_intrins, h_gt, total_views):
+    def train_step(self, h_viewmats, h_intrins, h_gt, total_views, chunk=2):
         """One iteration from HOST buffers (pinned torch tensors holding this rank's views):
         host->device copies of cameras and targets, the iteration, and a device->host read of
-        the loss scalars. Returns (l1, ssim, loss) averaged over this rank's views."""
+        the loss scalars. Returns (l1, ssim, loss) averaged over this rank's views.
+
+        The targets are copied `chunk` views at a time on a side stream and each chunk is
+        rendered as soon as it has landed, so the PCIe transfer of later views hides behind
+        the computation of earlier ones."""
         nv = int(h_viewmats.shape[0])
         if self._d_gt is None or self._d_gt.shape != h_gt.shape:
             self._d_view = torch.empty_like(h_viewmats, device=self.device)
             self._d_intr = torch.empty_like(h_intrins, device=self.device)
             self._d_gt = torch.empty_like(h_gt, device=self.device)
-        self._d_view.copy_(h_viewmats, non_blocking=True)
-        self._d_intr.copy_(h_intrins, non_blocking=True)
-        self._d_gt.copy_(h_gt, non_blocking=True)
-        self.step_device(self._d_view, self._d_intr, self._d_gt, nv, total_views)
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+        main = torch.cuda.current_stream(self.device)
+        self.losses.zero_()
+        if nv == 0:
+            self.grads_flat.zero_()
+        # the previous iteration may still be reading the staging buffers
+        self._copy_stream.wait_stream(main)
+        events = []
+        with torch.cuda.stream(self._copy_stream):
+            self._d_view.copy_(h_viewmats, non_blocking=True)
+            self._d_intr.copy_(h_intrins, non_blocking=True)
+            for c0 in range(0, nv, chunk):
+                c1 = min(nv, c0 + chunk)
+                self._d_gt[c0:c1].copy_(h_gt[c0:c1], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self._copy_stream)
+                events.append((c0, c1, ev))
+        for c0, c1, ev in events:
+            main.wait_event(ev)
+            L.check(self.lib.ssb_step_views(self.handle, C.byref(self._p_struct), C.byref(self.shq) if self.shq else None,
+                                            L.ptr(self._d_view[c0:]), L.ptr(self._d_intr[c0:]), L.ptr(self._d_gt[c0:]), c1 - c0,
+                                            C.byref(self._g_struct), 1 if c0 > 0 else 0, L.ptr(self.losses), None))
+        self.allreduce_grads()
+        self.optimizer_step(total_views)
         out = self.losses.cpu()
         return tuple((out / max(nv, 1)).tolist())
 

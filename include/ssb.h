@@ -157,6 +157,25 @@ int ssb_sort_pairs_u64(int64_t* d_keys_a, int32_t* d_vals_a, int64_t* d_keys_b, 
  * counterpart: cub's sort has no such status. */
 int ssb_sort_check(const void* d_workspace, void* stream);
 
+/* The same sort with NO workspace argument and no allocation anywhere: its scratch
+ * (look-back descriptors and digit histograms, about 1 MB) is a fixed array inside
+ * the library image, present on every GPU that loads the library until the process
+ * exits.  It has no counterpart in the reference (cub's sort always takes caller
+ * temp storage).  Meant for callers that must not create device memory where they
+ * sort: plug-ins whose host forbids cudaMalloc, or loops where an allocation's
+ * device-wide synchronisation would stall other streams.
+ *  - capacity may be at most 2^20 = 1,048,576 pairs; larger requests return
+ *    SSB_ERR_CAPACITY and touch nothing.
+ *  - The first call on each device looks up the array's device address (with that
+ *    device current); make that first call before starting any stream capture.
+ *  - All calls on a device share the one array, whose contents survive from call
+ *    to call; each call re-initialises what it needs, so back-to-back calls on one
+ *    stream are fine, but two calls that can run on the GPU at the same time (on
+ *    different streams) race on it and corrupt each other's result. */
+int ssb_sort_pairs_u64_noalloc(int64_t* d_keys_a, int32_t* d_vals_a, int64_t* d_keys_b, int32_t* d_vals_b,
+                               const int64_t* d_n, int64_t capacity, int32_t begin_bit, int32_t end_bit,
+                               int32_t* selector, void* stream);
+
 /* Number of key bits the tile id occupies: smallest b with 2^b > n_tiles
  * (src/kernels/tile/IntersectTile.cu:489-490). */
 int32_t ssb_tile_n_bits(int64_t n_tiles);

@@ -366,4 +366,57 @@ int ssb_sort_check(const void* d_workspace, void* stream) {
     return SSB_OK;
 }
 
+
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Sorting without a caller-provided workspace and without any allocation.
+//
+// Who needs it: code that is not allowed to create device memory at the point
+// where it sorts -- a host application that hands a plug-in a fixed set of
+// buffers and forbids it to call cudaMalloc, or a frame/step loop in which an
+// allocation (which synchronises the whole device) would stall every other
+// stream.  For them the sort's scratch lives in the library image itself.
+// ---------------------------------------------------------------------------
+namespace ssb {
+
+constexpr int64_t kStaticSortMaxPairs = (int64_t)1 << 20;            // 1,048,576 pairs
+constexpr int64_t kStaticSortTiles = kStaticSortMaxPairs / kSortTile; // 256
+constexpr int64_t kStaticSortBytes = ((int64_t)sizeof(SortHeader) + 255) / 256 * 256 + 2 * kStaticSortTiles * kRadix * 4;
+
+// Held by every GPU that loads the library, from load until the process exits (about 1 MB).
+static __device__ __align__(256) unsigned char g_static_sort_scratch[kStaticSortBytes];
+
+}  // namespace ssb
+
+#include <mutex>
+
+extern "C" int ssb_sort_pairs_u64_noalloc(int64_t* d_keys_a, int32_t* d_vals_a, int64_t* d_keys_b, int32_t* d_vals_b,
+                                          const int64_t* d_n, int64_t capacity, int32_t begin_bit, int32_t end_bit,
+                                          int32_t* selector, void* stream) {
+    using namespace ssb;
+    if (capacity > kStaticSortMaxPairs) {
+        set_error("ssb_sort_pairs_u64_noalloc: capacity %lld exceeds the built-in scratch, which serves at most %lld pairs; "
+                  "use ssb_sort_pairs_u64 with a workspace of your own", (long long)capacity, (long long)kStaticSortMaxPairs);
+        return SSB_ERR_CAPACITY;
+    }
+    // The array's name is only a host-side handle; the kernels need its address in the
+    // current device's memory, looked up once per device and remembered.
+    static std::mutex mu;
+    static void* scratch_of_device[64] = {nullptr};
+    int dev = -1;
+    SSB_CUDA(cudaGetDevice(&dev));
+    SSB_REQUIRE(dev >= 0 && dev < 64, "ssb_sort_pairs_u64_noalloc: device ordinal %d out of range", dev);
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!scratch_of_device[dev]) {
+            void* p = nullptr;
+            SSB_CUDA(cudaGetSymbolAddress(&p, g_static_sort_scratch));
+            scratch_of_device[dev] = p;
+        }
+        scratch = scratch_of_device[dev];
+    }
+    return ssb_sort_pairs_u64(d_keys_a, d_vals_a, d_keys_b, d_vals_b, d_n, capacity, begin_bit, end_bit,
+                              scratch, kStaticSortBytes, selector, stream);
+}

@@ -198,10 +198,10 @@ def adam_qq(grad, optim_packed, optim_bounds, value_packed, value_bounds, value_
                           C.c_int(zero_grad), C.c_int(value_bits), _p(grad), _p(optim_packed), _p(optim_bounds), _p(value_packed), _p(value_bounds))
 
 
-def forward_chain(splats, viewmats, intrins, W, H, shq=None):
+def forward_chain(splats, viewmats, intrins, W, H, shq=None, model=0):
     """projection -> keys -> sort -> ranges -> raster for all views in one batch (as the reference's batched launch)."""
     N, I = splats["means"].shape[0], viewmats.shape[0]
-    proj = project_fwd(splats, viewmats, intrins, W, H, shq=shq)
+    proj = project_fwd(splats, viewmats, intrins, W, H, shq=shq, model=model)
     counts, cum, keys, vals = tile_keys(proj, N, W, H)
     tw, th = tile_grid(W, H)
     nb = tile_n_bits(tw * th * I)

@@ -36,6 +36,7 @@ struct ProjGeom {
     float covc[6];    // xx xy xz yy yz zz
     float J00, J02, J11, J12;
     int clampx, clampy;  // -1 below, 0 inside, +1 above
+    float Jw[6];         // full 2x3 Jacobian (fisheye, equirectangular)
     float c00, c01, c11, det;
     float mean2d[2];
     float conic[3];
@@ -48,10 +49,91 @@ __device__ __forceinline__ void quat_to_rot(const float q[4], float R[9]) {
     R[6] = 2.f * (x * z - w * y); R[7] = 2.f * (y * z + w * x); R[8] = 1.f - 2.f * (x * x + y * y);
 }
 
-// Geometry of the pinhole projection.  Returns false when a cull of the
-// reference's forward pass applies (never when assume_valid).
-template <bool assume_valid>
-__device__ __forceinline__ bool project_pinhole(
+// ---- camera models other than pinhole -------------------------------------
+// A value with its three partial derivatives with respect to the camera-space
+// mean.  The backward pass needs d(Jacobian)/d(mean) of the fisheye and
+// equirectangular projections; evaluating the closed-form Jacobian once in this
+// arithmetic yields all eighteen second derivatives.
+struct D3 { float v, dx, dy, dz; };
+__device__ __forceinline__ float val(float a) { return a; }
+__device__ __forceinline__ float val(const D3& a) { return a.v; }
+__device__ __forceinline__ D3 operator+(const D3& a, const D3& b) { return {a.v + b.v, a.dx + b.dx, a.dy + b.dy, a.dz + b.dz}; }
+__device__ __forceinline__ D3 operator-(const D3& a, const D3& b) { return {a.v - b.v, a.dx - b.dx, a.dy - b.dy, a.dz - b.dz}; }
+__device__ __forceinline__ D3 operator-(const D3& a) { return {-a.v, -a.dx, -a.dy, -a.dz}; }
+__device__ __forceinline__ D3 operator*(const D3& a, const D3& b) {
+    return {a.v * b.v, a.dx * b.v + a.v * b.dx, a.dy * b.v + a.v * b.dy, a.dz * b.v + a.v * b.dz};
+}
+__device__ __forceinline__ D3 operator/(const D3& a, const D3& b) {
+    float r = 1.0f / b.v, q = a.v * r;
+    return {q, (a.dx - q * b.dx) * r, (a.dy - q * b.dy) * r, (a.dz - q * b.dz) * r};
+}
+__device__ __forceinline__ D3 operator*(float a, const D3& b) { return {a * b.v, a * b.dx, a * b.dy, a * b.dz}; }
+__device__ __forceinline__ D3 operator*(const D3& b, float a) { return a * b; }
+__device__ __forceinline__ D3 operator/(float a, const D3& b) { return D3{a, 0.f, 0.f, 0.f} / b; }
+__device__ __forceinline__ D3 operator/(const D3& a, float b) { return (1.0f / b) * a; }
+__device__ __forceinline__ D3 operator-(float a, const D3& b) { return {a - b.v, -b.dx, -b.dy, -b.dz}; }
+__device__ __forceinline__ float sqrt_s(float a) { return sqrtf(a); }
+__device__ __forceinline__ D3 sqrt_s(const D3& a) {
+    float r = sqrtf(a.v), h = 0.5f / r;
+    return {r, a.dx * h, a.dy * h, a.dz * h};
+}
+__device__ __forceinline__ float atan2_s(float y, float x) { return atan2f(y, x); }
+__device__ __forceinline__ D3 atan2_s(const D3& y, const D3& x) {
+    float r = 1.0f / (x.v * x.v + y.v * y.v);
+    return {atan2f(y.v, x.v), (x.v * y.dx - y.v * x.dx) * r, (x.v * y.dy - y.v * x.dy) * r, (x.v * y.dz - y.v * x.dz) * r};
+}
+__device__ __forceinline__ float lift(float a, float) { return a; }
+__device__ __forceinline__ D3 lift(float a, const D3&) { return {a, 0.f, 0.f, 0.f}; }
+
+// Pixel position and 2x3 Jacobian d(uv)/d(p) of the equidistant fisheye
+// (src/shaders/projection_utils.slang:378-384,400-410: k = theta / r, with the
+// series (1 - theta^2/3)/z below theta = 1e-3) and of the equirectangular
+// camera (:505-518: lon = atan2(x, z), lat = atan2(y, hypot(x, z))), as closed
+// forms of the derivatives the reference takes by forward-mode autodiff (:463-476, :537-548).
+template <int MODEL, class S>
+__device__ __forceinline__ void project_mean_wide(const S p[3], float fx, float fy, float cx, float cy, S uv[2], S J[6]) {
+    if (MODEL == SSB_CAMERA_FISHEYE) {
+        S r2 = p[0] * p[0] + p[1] * p[1];
+        S r = sqrt_s(r2);
+        S theta = atan2_s(r, p[2]);
+        S rho2 = r2 + p[2] * p[2];
+        S k, dkx, dky, dkz;
+        S dtz = -(r / rho2);
+        if (val(theta) < 1e-3f) {
+            k = (1.0f - theta * theta * (1.0f / 3.0f)) / p[2];
+            S rinv = val(r) > 0.f ? 1.0f / r : lift(0.f, r);
+            S dtx = p[2] * p[0] * rinv / rho2, dty = p[2] * p[1] * rinv / rho2;
+            S c = (-(2.0f / 3.0f)) * theta / p[2];
+            dkx = c * dtx; dky = c * dty; dkz = c * dtz - k / p[2];
+        } else {
+            k = theta / r;
+            S ir = 1.0f / r;
+            S dtx = p[2] * p[0] / (r * rho2), dty = p[2] * p[1] / (r * rho2);
+            S tir3 = theta * ir * ir * ir;
+            dkx = dtx * ir - tir3 * p[0];
+            dky = dty * ir - tir3 * p[1];
+            dkz = dtz * ir;
+        }
+        uv[0] = fx * (p[0] * k) + lift(cx, k);
+        uv[1] = fy * (p[1] * k) + lift(cy, k);
+        J[0] = fx * (k + p[0] * dkx); J[1] = fx * (p[0] * dky); J[2] = fx * (p[0] * dkz);
+        J[3] = fy * (p[1] * dkx); J[4] = fy * (k + p[1] * dky); J[5] = fy * (p[1] * dkz);
+    } else {
+        S h2 = p[0] * p[0] + p[2] * p[2];
+        S h = sqrt_s(h2);
+        uv[0] = fx * atan2_s(p[0], p[2]) + lift(cx, h);
+        uv[1] = fy * atan2_s(p[1], h) + lift(cy, h);
+        S rho2 = h2 + p[1] * p[1];
+        S hr = h * rho2;
+        J[0] = fx * (p[2] / h2); J[1] = lift(0.f, h); J[2] = fx * (-(p[0] / h2));
+        J[3] = fy * (-(p[1] * p[0]) / hr); J[4] = fy * (h / rho2); J[5] = fy * (-(p[1] * p[2]) / hr);
+    }
+}
+
+// Geometry of the projection.  Returns false when a cull of the reference's
+// forward pass applies (never when assume_valid).
+template <int MODEL, bool assume_valid>
+__device__ __forceinline__ bool project_geom(
     const CamDev& cam, int W_img, bool antialiased,
     const float mean[3], const float quat[4], const float scale[3], float in_opacity,
     ProjGeom& g) {
@@ -59,7 +141,7 @@ __device__ __forceinline__ bool project_pinhole(
 #pragma unroll
     for (int i = 0; i < 3; ++i) g.mc[i] = R[3 * i] * mean[0] + R[3 * i + 1] * mean[1] + R[3 * i + 2] * mean[2] + cam.t[i];
     g.len = sqrtf(g.mc[0] * g.mc[0] + g.mc[1] * g.mc[1] + g.mc[2] * g.mc[2]);
-    if (!assume_valid && g.mc[2] <= 0.0f) return false;
+    if (!assume_valid && (MODEL == SSB_CAMERA_PINHOLE ? g.mc[2] : g.len) <= 0.0f) return false;
     g.opacity = 1.0f / (1.0f + expf(-in_opacity));
 
     float qq = sqrtf(quat[0] * quat[0] + quat[1] * quat[1] + quat[2] * quat[2] + quat[3] * quat[3]);
@@ -84,32 +166,53 @@ __device__ __forceinline__ bool project_pinhole(
     g.covc[4] = Wm[3] * Wm[6] * s2[0] + Wm[4] * Wm[7] * s2[1] + Wm[5] * Wm[8] * s2[2];
     g.covc[5] = Wm[6] * Wm[6] * s2[0] + Wm[7] * Wm[7] * s2[1] + Wm[8] * Wm[8] * s2[2];
 
-    float rz = 1.0f / g.mc[2];
-    float u = g.mc[0] * rz, v = g.mc[1] * rz;
-    g.mean2d[0] = cam.fx * u + cam.cx;
-    g.mean2d[1] = cam.fy * v + cam.cy;
-    g.J00 = cam.fx * rz;
-    g.J11 = cam.fy * rz;
-    float j02 = -(cam.fx * u) * rz, j12 = -(cam.fy * v) * rz;
-    // Both rows use the x limits, as the reference does
-    // (src/shaders/primitive_3dgs.slang:84-95).
-    float width = (float)W_img;
-    float lim_pos = width + 0.3f * (0.5f * width);
-    float lim_neg = 0.3f * (0.5f * width);
-    float max_x = -(-lim_neg - cam.cx) * rz, min_x = -(lim_pos - cam.cx) * rz;
-    float max_y = -(-lim_neg - cam.cy) * rz, min_y = -(lim_pos - cam.cy) * rz;
-    g.clampx = j02 < min_x ? -1 : (j02 > max_x ? 1 : 0);
-    g.clampy = j12 < min_y ? -1 : (j12 > max_y ? 1 : 0);
-    g.J02 = g.clampx < 0 ? min_x : (g.clampx > 0 ? max_x : j02);
-    g.J12 = g.clampy < 0 ? min_y : (g.clampy > 0 ? max_y : j12);
-
-    // cov2d = J covc J^T with J = [[J00, 0, J02], [0, J11, J12]]
+    float c00, c01, c11;
     const float* c = g.covc;
-    float a0 = g.J00 * c[0] + g.J02 * c[2], a1 = g.J00 * c[1] + g.J02 * c[4], a2 = g.J00 * c[2] + g.J02 * c[5];
-    float b1 = g.J11 * c[3] + g.J12 * c[4], b2 = g.J11 * c[4] + g.J12 * c[5];
-    float c00 = a0 * g.J00 + a2 * g.J02;
-    float c01 = a1 * g.J11 + a2 * g.J12;
-    float c11 = b1 * g.J11 + b2 * g.J12;
+    if (MODEL == SSB_CAMERA_PINHOLE) {
+        float rz = 1.0f / g.mc[2];
+        float u = g.mc[0] * rz, v = g.mc[1] * rz;
+        g.mean2d[0] = cam.fx * u + cam.cx;
+        g.mean2d[1] = cam.fy * v + cam.cy;
+        g.J00 = cam.fx * rz;
+        g.J11 = cam.fy * rz;
+        float j02 = -(cam.fx * u) * rz, j12 = -(cam.fy * v) * rz;
+        // Both rows use the x limits, as the reference does
+        // (src/shaders/primitive_3dgs.slang:84-95).
+        float width = (float)W_img;
+        float lim_pos = width + 0.3f * (0.5f * width);
+        float lim_neg = 0.3f * (0.5f * width);
+        float max_x = -(-lim_neg - cam.cx) * rz, min_x = -(lim_pos - cam.cx) * rz;
+        float max_y = -(-lim_neg - cam.cy) * rz, min_y = -(lim_pos - cam.cy) * rz;
+        g.clampx = j02 < min_x ? -1 : (j02 > max_x ? 1 : 0);
+        g.clampy = j12 < min_y ? -1 : (j12 > max_y ? 1 : 0);
+        g.J02 = g.clampx < 0 ? min_x : (g.clampx > 0 ? max_x : j02);
+        g.J12 = g.clampy < 0 ? min_y : (g.clampy > 0 ? max_y : j12);
+
+        // cov2d = J covc J^T with J = [[J00, 0, J02], [0, J11, J12]]
+        float a0 = g.J00 * c[0] + g.J02 * c[2], a1 = g.J00 * c[1] + g.J02 * c[4], a2 = g.J00 * c[2] + g.J02 * c[5];
+        float b1 = g.J11 * c[3] + g.J12 * c[4], b2 = g.J11 * c[4] + g.J12 * c[5];
+        c00 = a0 * g.J00 + a2 * g.J02;
+        c01 = a1 * g.J11 + a2 * g.J12;
+        c11 = b1 * g.J11 + b2 * g.J12;
+    } else {
+        project_mean_wide<MODEL, float>(g.mc, cam.fx, cam.fy, cam.cx, cam.cy, g.mean2d, g.Jw);
+        const float* J = g.Jw;
+        // rows of J covc (covc symmetric: xx xy xz yy yz zz)
+        float a0 = J[0] * c[0] + J[1] * c[1] + J[2] * c[2], a1 = J[0] * c[1] + J[1] * c[3] + J[2] * c[4], a2 = J[0] * c[2] + J[1] * c[4] + J[2] * c[5];
+        float b0 = J[3] * c[0] + J[4] * c[1] + J[5] * c[2], b1 = J[3] * c[1] + J[4] * c[3] + J[5] * c[4], b2 = J[3] * c[2] + J[4] * c[4] + J[5] * c[5];
+        c00 = a0 * J[0] + a1 * J[1] + a2 * J[2];
+        c01 = a0 * J[3] + a1 * J[4] + a2 * J[5];
+        c11 = b0 * J[3] + b1 * J[4] + b2 * J[5];
+        if (!assume_valid && MODEL == SSB_CAMERA_FISHEYE) {
+            // behind-the-camera splats that still reach the image centre are dropped
+            // (src/shaders/primitive_3dgs.slang:515-521); c10 == c01 here
+            float invd = 1.0f / (c00 * c11 - c01 * c01);
+            float mx = g.mean2d[0] - cam.cx, my = g.mean2d[1] - cam.cy;
+            float q = (c11 * invd * mx - c01 * invd * my) * mx + (-c01 * invd * mx + c00 * invd * my) * my;
+            float opac = g.opacity * expf(-0.5f * q);
+            if (g.mc[2] < 0.0f && opac > kAlphaThreshold) return false;
+        }
+    }
     const float eps2d = antialiased ? 0.1f : 0.3f;
     float det_orig = c00 * c11 - c01 * c01;
     c00 += eps2d; c11 += eps2d;
@@ -161,6 +264,7 @@ __device__ __forceinline__ void stage_sh(
     }
 }
 
+template <int MODEL>
 __global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
     SsbSplats sp, SsbShQuant shq, int64_t n, const float* __restrict__ viewmats, const float* __restrict__ intrins,
     int W, int H, int antialiased,
@@ -184,7 +288,7 @@ __global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
     const int64_t idx = (int64_t)cid * n + gid;
 
     ProjGeom g;
-    bool ok = project_pinhole<false>(cam, W, antialiased != 0, mean, quat, scale, in_op, g);
+    bool ok = project_geom<MODEL, false>(cam, W, antialiased != 0, mean, quat, scale, in_op, g);
     float xmin = 0.f, ymin = 0.f, xmax = 0.f, ymax = 0.f, L = 0.f;
     if (ok) {
         L = logf(g.opacity / kAlphaThreshold);
@@ -218,7 +322,16 @@ __global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
     bool keep = ok && (a2 - a0 > 1e-3f) && (a3 - a1 > 1e-3f);
     if (keep) {
         aabb_out[idx] = make_float4(a0, a1, a2, a3);
-        depths_out[idx] = g.mc[2];  // pinhole sorting depth
+        // sorting depth (src/shaders/projection_utils.slang:1012-1029): z for pinhole, squared
+        // distance for equirectangular, z^4 + (x^2+y^2)^2/512 for fisheye
+        float sd;
+        if (MODEL == SSB_CAMERA_PINHOLE) sd = g.mc[2];
+        else if (MODEL == SSB_CAMERA_EQUIRECT) sd = g.mc[0] * g.mc[0] + g.mc[1] * g.mc[1] + g.mc[2] * g.mc[2];
+        else {
+            float xy2 = g.mc[0] * g.mc[0] + g.mc[1] * g.mc[1];
+            sd = g.mc[2] * g.mc[2] * g.mc[2] * g.mc[2] + (1.0f / 512.0f) * xy2 * xy2;
+        }
+        depths_out[idx] = sd;
         // half extents of the alpha >= 1/255 footprint, slightly inflated
         float e = sqrtf(2.0f * L) * 1.0005f;
         float hx = e * sqrtf(g.c00) + 1e-3f, hy = e * sqrtf(g.c11) + 1e-3f;
@@ -270,7 +383,7 @@ __device__ __forceinline__ void sh_basis_vjp(float x, float y, float z, const fl
 
 __device__ __forceinline__ float finite_or_zero(float v) { return isfinite(v) ? v : 0.0f; }
 
-template <bool MULTI_VIEW>
+template <bool MULTI_VIEW, int MODEL>
 __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
     SsbSplats sp, SsbShQuant shq, int64_t n, int C, const float* __restrict__ viewmats, const float* __restrict__ intrins,
     int W, int H, int antialiased, const float4* __restrict__ aabb, SsbScreenRec* __restrict__ v_screen,
@@ -323,7 +436,7 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
                 vr[0] = zero; vr[1] = zero; vr[2] = zero;
             }
             ProjGeom g;
-            project_pinhole<true>(cam, W, antialiased != 0, mean, quat, scale, in_op, g);
+            project_geom<MODEL, true>(cam, W, antialiased != 0, mean, quat, scale, in_op, g);
             // ---- conic -> blurred 2D covariance
             float v0 = vb.x, v1 = vb.y, v2 = vb.z;
             float invdet = 1.0f / g.det;
@@ -355,36 +468,62 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
             }
             // ---- cov2d = J covc J^T : v_J = 2 G J covc, v_covc = J^T G J
             const float* c = g.covc;
-            float JC0[3] = {g.J00 * c[0] + g.J02 * c[2], g.J00 * c[1] + g.J02 * c[4], g.J00 * c[2] + g.J02 * c[5]};
-            float JC1[3] = {g.J11 * c[1] + g.J12 * c[2], g.J11 * c[3] + g.J12 * c[4], g.J11 * c[4] + g.J12 * c[5]};
-            float vJ00 = 2.f * (G00 * JC0[0] + G01 * JC1[0]);
-            float vJ02 = 2.f * (G00 * JC0[2] + G01 * JC1[2]);
-            float vJ11 = 2.f * (G01 * JC0[1] + G11 * JC1[1]);
-            float vJ12 = 2.f * (G01 * JC0[2] + G11 * JC1[2]);
-            // J rows: r0 = (J00, 0, J02), r1 = (0, J11, J12); v_covc[i][j] = sum_ab J[a][i] G[a][b] J[b][j]
-            float r0[3] = {g.J00, 0.f, g.J02}, r1[3] = {0.f, g.J11, g.J12};
-            float vC[9];
-#pragma unroll
-            for (int i = 0; i < 3; ++i)
-#pragma unroll
-                for (int j = 0; j < 3; ++j)
-                    vC[3 * i + j] = r0[i] * (G00 * r0[j] + G01 * r1[j]) + r1[i] * (G01 * r0[j] + G11 * r1[j]);
-            // ---- camera-space mean
             float x = g.mc[0], y = g.mc[1], z = g.mc[2];
-            float rz = 1.0f / z, rz2 = rz * rz;
             float vmc[3] = {0.f, 0.f, 0.f};
-            vmc[2] += -cam.fx * rz2 * vJ00 - cam.fy * rz2 * vJ11;
-            float width = (float)W;
-            float lim_pos = width + 0.3f * (0.5f * width), lim_neg = 0.3f * (0.5f * width);
-            if (g.clampx == 0) { vmc[0] += -cam.fx * rz2 * vJ02; vmc[2] += 2.f * cam.fx * x * rz2 * rz * vJ02; }
-            else if (g.clampx < 0) vmc[2] += (lim_pos - cam.cx) * rz2 * vJ02;
-            else vmc[2] += -(lim_neg + cam.cx) * rz2 * vJ02;
-            if (g.clampy == 0) { vmc[1] += -cam.fy * rz2 * vJ12; vmc[2] += 2.f * cam.fy * y * rz2 * rz * vJ12; }
-            else if (g.clampy < 0) vmc[2] += (lim_pos - cam.cy) * rz2 * vJ12;
-            else vmc[2] += -(lim_neg + cam.cy) * rz2 * vJ12;
-            vmc[0] += cam.fx * rz * va.x;
-            vmc[1] += cam.fy * rz * va.y;
-            vmc[2] += -(cam.fx * x * va.x + cam.fy * y * va.y) * rz2;
+            float vC[9];
+            if (MODEL == SSB_CAMERA_PINHOLE) {
+                float JC0[3] = {g.J00 * c[0] + g.J02 * c[2], g.J00 * c[1] + g.J02 * c[4], g.J00 * c[2] + g.J02 * c[5]};
+                float JC1[3] = {g.J11 * c[1] + g.J12 * c[2], g.J11 * c[3] + g.J12 * c[4], g.J11 * c[4] + g.J12 * c[5]};
+                float vJ00 = 2.f * (G00 * JC0[0] + G01 * JC1[0]);
+                float vJ02 = 2.f * (G00 * JC0[2] + G01 * JC1[2]);
+                float vJ11 = 2.f * (G01 * JC0[1] + G11 * JC1[1]);
+                float vJ12 = 2.f * (G01 * JC0[2] + G11 * JC1[2]);
+                // J rows: r0 = (J00, 0, J02), r1 = (0, J11, J12); v_covc[i][j] = sum_ab J[a][i] G[a][b] J[b][j]
+                float r0[3] = {g.J00, 0.f, g.J02}, r1[3] = {0.f, g.J11, g.J12};
+#pragma unroll
+                for (int i = 0; i < 3; ++i)
+#pragma unroll
+                    for (int j = 0; j < 3; ++j)
+                        vC[3 * i + j] = r0[i] * (G00 * r0[j] + G01 * r1[j]) + r1[i] * (G01 * r0[j] + G11 * r1[j]);
+                // ---- camera-space mean
+                float rz = 1.0f / z, rz2 = rz * rz;
+                vmc[2] += -cam.fx * rz2 * vJ00 - cam.fy * rz2 * vJ11;
+                float width = (float)W;
+                float lim_pos = width + 0.3f * (0.5f * width), lim_neg = 0.3f * (0.5f * width);
+                if (g.clampx == 0) { vmc[0] += -cam.fx * rz2 * vJ02; vmc[2] += 2.f * cam.fx * x * rz2 * rz * vJ02; }
+                else if (g.clampx < 0) vmc[2] += (lim_pos - cam.cx) * rz2 * vJ02;
+                else vmc[2] += -(lim_neg + cam.cx) * rz2 * vJ02;
+                if (g.clampy == 0) { vmc[1] += -cam.fy * rz2 * vJ12; vmc[2] += 2.f * cam.fy * y * rz2 * rz * vJ12; }
+                else if (g.clampy < 0) vmc[2] += (lim_pos - cam.cy) * rz2 * vJ12;
+                else vmc[2] += -(lim_neg + cam.cy) * rz2 * vJ12;
+                vmc[0] += cam.fx * rz * va.x;
+                vmc[1] += cam.fy * rz * va.y;
+                vmc[2] += -(cam.fx * x * va.x + cam.fy * y * va.y) * rz2;
+            } else {
+                const float* J = g.Jw;
+                float JC0[3] = {J[0] * c[0] + J[1] * c[1] + J[2] * c[2], J[0] * c[1] + J[1] * c[3] + J[2] * c[4], J[0] * c[2] + J[1] * c[4] + J[2] * c[5]};
+                float JC1[3] = {J[3] * c[0] + J[4] * c[1] + J[5] * c[2], J[3] * c[1] + J[4] * c[3] + J[5] * c[4], J[3] * c[2] + J[4] * c[4] + J[5] * c[5]};
+                float vJ[6];
+#pragma unroll
+                for (int j = 0; j < 3; ++j) {
+                    vJ[j] = 2.f * (G00 * JC0[j] + G01 * JC1[j]);
+                    vJ[3 + j] = 2.f * (G01 * JC0[j] + G11 * JC1[j]);
+                }
+#pragma unroll
+                for (int i = 0; i < 3; ++i)
+#pragma unroll
+                    for (int j = 0; j < 3; ++j)
+                        vC[3 * i + j] = J[i] * (G00 * J[j] + G01 * J[3 + j]) + J[3 + i] * (G01 * J[j] + G11 * J[3 + j]);
+                // ---- camera-space mean: v_mc = J^T v_mean2d + sum_ij vJ[i][j] dJ[i][j]/d mc
+                D3 pd[3] = {{x, 1.f, 0.f, 0.f}, {y, 0.f, 1.f, 0.f}, {z, 0.f, 0.f, 1.f}};
+                D3 uvd[2], Jd[6];
+                project_mean_wide<MODEL, D3>(pd, cam.fx, cam.fy, cam.cx, cam.cy, uvd, Jd);
+#pragma unroll
+                for (int e = 0; e < 6; ++e) { vmc[0] += vJ[e] * Jd[e].dx; vmc[1] += vJ[e] * Jd[e].dy; vmc[2] += vJ[e] * Jd[e].dz; }
+                vmc[0] += J[0] * va.x + J[3] * va.y;
+                vmc[1] += J[1] * va.x + J[4] * va.y;
+                vmc[2] += J[2] * va.x + J[5] * va.y;
+            }
             float vdl = vc4.w / g.len;   // depth = |mc|
             vmc[0] += vdl * x; vmc[1] += vdl * y; vmc[2] += vdl * z;
             const float* R = cam.R;
@@ -532,16 +671,22 @@ int ssb_project_fwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, c
     using namespace ssb;
     SSB_REQUIRE(splats && cams && d_aabb && d_depths && d_screen, "ssb_project_fwd: NULL argument");
     SSB_REQUIRE(n >= 0 && cams->count >= 0 && cams->width > 0 && cams->height > 0, "ssb_project_fwd: bad sizes");
-    if (cams->model != SSB_CAMERA_PINHOLE) { set_error("ssb_project_fwd: camera model %d not supported", cams->model); return SSB_ERR_UNSUPPORTED; }
+    if (cams->model != SSB_CAMERA_PINHOLE && cams->model != SSB_CAMERA_FISHEYE && cams->model != SSB_CAMERA_EQUIRECT) {
+        set_error("ssb_project_fwd: camera model %d not supported", cams->model); return SSB_ERR_UNSUPPORTED;
+    }
     SSB_REQUIRE((int64_t)cams->count * n < ((int64_t)1 << 31), "ssb_project_fwd: views * splats must fit int32 flatten ids");
     SsbShQuant q;
     int e = check_shq(splats, shq, q);
     if (e) return e;
     if (n == 0 || cams->count == 0) return SSB_OK;
     dim3 grid((unsigned)ceil_div(n, kProjBlock), (unsigned)cams->count);
-    project_fwd_kernel<<<grid, kProjBlock, 0, (cudaStream_t)stream>>>(
-        *splats, q, n, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased,
-        (float4*)d_aabb, d_depths, d_radii, d_screen);
+#define SSB_FWD(MODEL) project_fwd_kernel<MODEL><<<grid, kProjBlock, 0, (cudaStream_t)stream>>>( \
+        *splats, q, n, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased, \
+        (float4*)d_aabb, d_depths, d_radii, d_screen)
+    if (cams->model == SSB_CAMERA_PINHOLE) SSB_FWD(SSB_CAMERA_PINHOLE);
+    else if (cams->model == SSB_CAMERA_FISHEYE) SSB_FWD(SSB_CAMERA_FISHEYE);
+    else SSB_FWD(SSB_CAMERA_EQUIRECT);
+#undef SSB_FWD
     SSB_LAUNCHED("project_fwd_kernel");
     return SSB_OK;
 }
@@ -560,19 +705,21 @@ int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n
     SSB_REQUIRE(splats && cams && d_aabb && d_v_screen && grads, "ssb_project_bwd: NULL argument");
     SSB_REQUIRE(grads->means && grads->quats && grads->scales && grads->opacities && grads->features_dc && grads->features_sh,
                 "ssb_project_bwd: every gradient array must be given");
-    if (cams->model != SSB_CAMERA_PINHOLE) { set_error("ssb_project_bwd: camera model %d not supported", cams->model); return SSB_ERR_UNSUPPORTED; }
+    if (cams->model != SSB_CAMERA_PINHOLE && cams->model != SSB_CAMERA_FISHEYE && cams->model != SSB_CAMERA_EQUIRECT) {
+        set_error("ssb_project_bwd: camera model %d not supported", cams->model); return SSB_ERR_UNSUPPORTED;
+    }
     SsbShQuant q;
     int e = check_shq(splats, shq, q);
     if (e) return e;
     if (n == 0) return SSB_OK;
-    if (cams->count == 1)
-        project_bwd_kernel<false><<<(unsigned)ceil_div(n, kProjBlock), kProjBlock, 0, (cudaStream_t)stream>>>(
-            *splats, q, n, cams->count, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased,
-            (const float4*)d_aabb, d_v_screen, *grads, accumulate, clear_v_screen);
-    else
-        project_bwd_kernel<true><<<(unsigned)ceil_div(n, kProjBlock), kProjBlock, 0, (cudaStream_t)stream>>>(
-            *splats, q, n, cams->count, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased,
-            (const float4*)d_aabb, d_v_screen, *grads, accumulate, clear_v_screen);
+#define SSB_BWD(MULTI, MODEL) project_bwd_kernel<MULTI, MODEL><<<(unsigned)ceil_div(n, kProjBlock), kProjBlock, 0, (cudaStream_t)stream>>>( \
+        *splats, q, n, cams->count, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased, \
+        (const float4*)d_aabb, d_v_screen, *grads, accumulate, clear_v_screen)
+    const bool multi = cams->count != 1;
+    if (cams->model == SSB_CAMERA_PINHOLE) { if (multi) SSB_BWD(true, SSB_CAMERA_PINHOLE); else SSB_BWD(false, SSB_CAMERA_PINHOLE); }
+    else if (cams->model == SSB_CAMERA_FISHEYE) { if (multi) SSB_BWD(true, SSB_CAMERA_FISHEYE); else SSB_BWD(false, SSB_CAMERA_FISHEYE); }
+    else { if (multi) SSB_BWD(true, SSB_CAMERA_EQUIRECT); else SSB_BWD(false, SSB_CAMERA_EQUIRECT); }
+#undef SSB_BWD
     SSB_LAUNCHED("project_bwd_kernel");
     return SSB_OK;
 }

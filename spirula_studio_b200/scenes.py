@@ -30,7 +30,12 @@ class SceneConfig:
     log_scale_sigma: float = 0.5
     opacity_mu: float = 0.0
     opacity_sigma: float = 1.0
-    rig: str = "ring"           # "single" | "ring" | "sphere"
+    rig: str = "ring"           # "single" | "ring" | "sphere" | "inside" (centres within rig_radius of the origin)
+    mean_ball: bool = False     # means uniform in the ball of radius mean_extent instead of the cube
+    camera_model: int = 0       # 0 pinhole, 1 equidistant fisheye, 3 equirectangular (src/core/Common.cuh:94-99)
+    # several camera kinds in one batch: tuples (camera_model, width, height, fx, fy); view i uses
+    # entry i % len(view_kinds).  Empty: every view is (camera_model, width, height, fx, fy).
+    view_kinds: tuple = ()
     rig_radius: float = 8.0
     sh_value_bits: int = 32     # 16 = the reference's quantised SH storage
     sh_optim_bits: int = 32
@@ -50,7 +55,24 @@ CONFIGS = {
     # VRAM-scale scene: 10M splats, 64 views of 3840x2160 on a radius-25 ring, quantised SH
     "vram_10m": SceneConfig("vram_10m", 10_000_000, 3840, 2160, 2800.0, 2800.0, 64, 20.0, log_scale_mu=-4.5,
                             log_scale_sigma=0.7, rig="ring", rig_radius=25.0, sh_value_bits=16, sh_optim_bits=8),
+    # wide field of view: 5M splats in a radius-15 ball, 16 views from within radius 2 of the origin, alternating
+    # equidistant fisheye (1920x1920, f = 600, ~190 degrees) and equirectangular 360-degree (4096x2048)
+    "wide_5m": SceneConfig("wide_5m", 5_000_000, 1920, 1920, 600.0, 600.0, 16, 15.0, log_scale_mu=-4.5, log_scale_sigma=0.6,
+                           rig="inside", rig_radius=2.0, mean_ball=True,
+                           view_kinds=((1, 1920, 1920, 600.0, 600.0), (3, 4096, 2048, 4096 / (2 * np.pi), 4096 / (2 * np.pi)))),
 }
+
+
+def view_kind(cfg: "SceneConfig", view: int):
+    """(kind index, camera_model, width, height, fx, fy) of a view of the batch."""
+    if not cfg.view_kinds:
+        return 0, cfg.camera_model, cfg.width, cfg.height, cfg.fx, cfg.fy
+    k = view % len(cfg.view_kinds)
+    return (k,) + tuple(cfg.view_kinds[k])
+
+
+def n_view_kinds(cfg: "SceneConfig"):
+    return max(1, len(cfg.view_kinds))
 
 
 def scaled(cfg: SceneConfig, n_splats=None, width=None, height=None, n_views=None, name=None) -> SceneConfig:
@@ -61,6 +83,9 @@ def scaled(cfg: SceneConfig, n_splats=None, width=None, height=None, n_views=Non
         s = width / cfg.width
         c.fx, c.fy, c.width = cfg.fx * s, cfg.fy * s, width
         c.height = height if height is not None else int(round(cfg.height * s))
+        # every camera kind shrinks by the same factor (sizes kept even)
+        c.view_kinds = tuple((m, max(2, int(round(w * s / 2)) * 2), max(2, int(round(h * s / 2)) * 2), fx * s, fy * s)
+                             for m, w, h, fx, fy in cfg.view_kinds)
     elif height is not None:
         c.height = height
     if n_splats is not None:
@@ -75,7 +100,12 @@ def make_splats(cfg: SceneConfig, seed: int = SPLAT_SEED):
     rng = np.random.Generator(np.random.PCG64(seed))
     n = cfg.n_splats
     f32 = np.float32
-    means = rng.uniform(-cfg.mean_extent, cfg.mean_extent, size=(n, 3)).astype(f32)
+    if cfg.mean_ball:
+        d = rng.normal(size=(n, 3))
+        d /= np.linalg.norm(d, axis=1, keepdims=True)
+        means = (d * (cfg.mean_extent * rng.uniform(size=(n, 1)) ** (1.0 / 3.0))).astype(f32)
+    else:
+        means = rng.uniform(-cfg.mean_extent, cfg.mean_extent, size=(n, 3)).astype(f32)
     scales = rng.normal(cfg.log_scale_mu, cfg.log_scale_sigma, size=(n, 3)).astype(f32)
     q = rng.normal(0.0, 1.0, size=(n, 4))
     quats = (q / np.linalg.norm(q, axis=1, keepdims=True)).astype(f32)
@@ -119,14 +149,25 @@ def make_cameras(cfg: SceneConfig, seed: int = SPLAT_SEED + 7):
             yy = 1.0 - 2.0 * (k + 0.5) / cfg.n_views
             r = np.sqrt(max(0.0, 1.0 - yy * yy))
             eyes.append((cfg.rig_radius * r * np.cos(ga * k), cfg.rig_radius * yy, cfg.rig_radius * r * np.sin(ga * k)))
+    elif cfg.rig == "inside":  # centres uniform within rig_radius of the origin, random viewing directions
+        d = rng.normal(size=(cfg.n_views, 3))
+        d /= np.linalg.norm(d, axis=1, keepdims=True)
+        c = d * (cfg.rig_radius * rng.uniform(size=(cfg.n_views, 1)) ** (1.0 / 3.0))
+        look = rng.normal(size=(cfg.n_views, 3))
+        viewmats = np.stack([look_at(c[k], c[k] + look[k]) for k in range(cfg.n_views)], axis=0).reshape(-1, 16)
     else:
         raise ValueError(cfg.rig)
-    viewmats = np.stack([look_at(e) for e in eyes[: cfg.n_views]], axis=0).reshape(-1, 16)
-    intrins = np.tile(np.array([[cfg.fx, cfg.fy, cfg.width / 2.0, cfg.height / 2.0]], dtype=np.float32), (len(viewmats), 1))
+    if cfg.rig != "inside":
+        viewmats = np.stack([look_at(e) for e in eyes[: cfg.n_views]], axis=0).reshape(-1, 16)
+    intrins = np.zeros((len(viewmats), 4), dtype=np.float32)
+    for v in range(len(viewmats)):
+        _, _, w, h, fx, fy = view_kind(cfg, v)
+        intrins[v] = (fx, fy, w / 2.0, h / 2.0)
     return viewmats.astype(np.float32), intrins
 
 
 def make_target(cfg: SceneConfig, view: int, seed: int = TARGET_SEED):
     """i.i.d. uniform [0,1] RGB target of one view, [H, W, 3] fp32."""
     rng = np.random.Generator(np.random.PCG64(seed + 1000 * view))
-    return rng.random(size=(cfg.height, cfg.width, 3), dtype=np.float32)
+    _, _, w, h, _, _ = view_kind(cfg, view)
+    return rng.random(size=(h, w, 3), dtype=np.float32)

@@ -16,7 +16,7 @@ import numpy as np
 import torch
 
 from . import lib as L
-from .scenes import SceneConfig
+from .scenes import SceneConfig, n_view_kinds, view_kind
 
 _ATTRS = (("means", 3), ("quats", 4), ("scales", 3), ("opacities", 1), ("features_dc", 3), ("features_sh", 45))
 FLOATS_PER_SPLAT = sum(w for _, w in _ATTRS)  # 59
@@ -74,17 +74,24 @@ class Trainer:
             L.check(self.lib.ssb_quant_encode(L.ptr(self.params["features_sh"]), cells, cfg.sh_value_bits,
                                               L.ptr(self.sh_packed), L.ptr(self.sh_bounds), None))
             self.shq = L.shq_struct(self.sh_packed, self.sh_bounds, cfg.sh_value_bits, 256)
-        self.step_cfg = L.SsbStepConfig(n, cfg.width, cfg.height, L.CAMERA_PINHOLE, 0, isect_capacity, w_l1, w_ssim)
-        self.handle = C.c_void_p()
-        L.check(self.lib.ssb_step_create(C.byref(self.step_cfg), C.byref(self.handle)))
+        # one set of per-view buffers per camera kind of the batch (model and image size are fixed per set)
+        self.handles = []
+        for k in range(n_view_kinds(cfg)):
+            _, model, width, height, _, _ = view_kind(cfg, k)
+            step_cfg = L.SsbStepConfig(n, width, height, model, 0, isect_capacity, w_l1, w_ssim)
+            handle = C.c_void_p()
+            L.check(self.lib.ssb_step_create(C.byref(step_cfg), C.byref(handle)))
+            self.handles.append(handle)
+        self.handle = self.handles[0]
         self.losses = torch.zeros(3, dtype=torch.float32, device=dev)
         self.iteration = 0
         self._p_struct = L.splats_struct(self.params if not self.quant else {**self.params, "features_sh": None})
         self._g_struct = L.splats_struct(self.grads)
         self._m1_struct = L.splats_struct(self.m1)
         self._m2_struct = L.splats_struct(self.m2)
-        # device staging for one rank's share of a batch (filled by train_step)
-        self._d_view = self._d_intr = self._d_gt = None
+        # device staging for one rank's share of a batch, per camera kind (filled by train_step)
+        self._staging = {}
+        self._copy_stream = None
 
     def _geo_views(self, flat):
         out = _flat_views(flat, self.n, _ATTRS[:5])
@@ -92,9 +99,11 @@ class Trainer:
         return out
 
     def close(self):
-        if self.handle:
-            self.lib.ssb_step_destroy(self.handle)
-            self.handle = C.c_void_p()
+        for h in getattr(self, "handles", []):
+            if h:
+                self.lib.ssb_step_destroy(h)
+        self.handles = []
+        self.handle = C.c_void_p()
 
     def __del__(self):
         try:
@@ -106,12 +115,12 @@ class Trainer:
         own = sum(t.numel() * t.element_size() for t in (self.params_flat, self.grads_flat, self.m1_flat, self.m2_flat))
         if self.quant:
             own += sum(t.numel() * t.element_size() for t in (self.sh_packed, self.sh_bounds, self.sh_optim_packed, self.sh_optim_bounds))
-        return own + int(self.lib.ssb_step_device_bytes(self.handle))
+        return own + sum(int(self.lib.ssb_step_device_bytes(h)) for h in self.handles)
 
     # -- pieces ------------------------------------------------------------
-    def views_fwd_bwd(self, d_viewmats, d_intrins, d_gt, n_views, accumulate=False, stream=None):
-        """Forward + loss + backward of n_views views already resident on the device."""
-        L.check(self.lib.ssb_step_views(self.handle, C.byref(self._p_struct), C.byref(self.shq) if self.shq else None,
+    def views_fwd_bwd(self, d_viewmats, d_intrins, d_gt, n_views, accumulate=False, stream=None, kind=0):
+        """Forward + loss + backward of n_views views (all of camera kind `kind`) already resident on the device."""
+        L.check(self.lib.ssb_step_views(self.handles[kind], C.byref(self._p_struct), C.byref(self.shq) if self.shq else None,
                                         L.ptr(d_viewmats), L.ptr(d_intrins), L.ptr(d_gt), n_views,
                                         C.byref(self._g_struct), 1 if accumulate else 0, L.ptr(self.losses), stream))
 
@@ -134,56 +143,74 @@ class Trainer:
 
     # -- whole iteration ---------------------------------------------------
     def step_device(self, d_viewmats, d_intrins, d_gt, n_local_views, total_views):
-        """One iteration with this rank's views already in HBM. Returns nothing; losses stay on the device."""
+        """One iteration with this rank's views (one camera kind) already in HBM; losses stay on the device."""
+        self.step_device_kinds([(0, d_viewmats, d_intrins, d_gt, n_local_views)], total_views)
+
+    def step_device_kinds(self, batches, total_views):
+        """One iteration; `batches` = [(kind, d_viewmats, d_intrins, d_gt, n_views), ...], this rank's views by camera kind."""
         self.losses.zero_()
-        if n_local_views > 0:
-            self.views_fwd_bwd(d_viewmats, d_intrins, d_gt, n_local_views)
-        else:
+        first = True
+        for kind, d_viewmats, d_intrins, d_gt, nv in batches:
+            if nv > 0:
+                self.views_fwd_bwd(d_viewmats, d_intrins, d_gt, nv, accumulate=not first, kind=kind)
+                first = False
+        if first:
             self.grads_flat.zero_()
         self.allreduce_grads()
         self.optimizer_step(total_views)
 
     def train_step(self, h_viewmats, h_intrins, h_gt, total_views, chunk=2):
-        """One iteration from HOST buffers (pinned torch tensors holding this rank's views):
-        host->device copies of cameras and targets, the iteration, and a device->host read of
-        the loss scalars. Returns (l1, ssim, loss) averaged over this rank's views.
+        """One iteration from HOST buffers of one camera kind; see train_step_kinds."""
+        return self.train_step_kinds([(0, h_viewmats, h_intrins, h_gt)], total_views, chunk)
+
+    def train_step_kinds(self, batches, total_views, chunk=2):
+        """One iteration from HOST buffers (pinned torch tensors holding this rank's views, one entry
+        (kind, viewmats, intrins, targets) per camera kind): host->device copies of cameras and targets,
+        the iteration, and a device->host read of the loss scalars. Returns (l1, ssim, loss) averaged
+        over this rank's views.
 
         The targets are copied `chunk` views at a time on a side stream and each chunk is
         rendered as soon as it has landed, so the PCIe transfer of later views hides behind
         the computation of earlier ones."""
-        nv = int(h_viewmats.shape[0])
-        if self._d_gt is None or self._d_gt.shape != h_gt.shape:
-            self._d_view = torch.empty_like(h_viewmats, device=self.device)
-            self._d_intr = torch.empty_like(h_intrins, device=self.device)
-            self._d_gt = torch.empty_like(h_gt, device=self.device)
+        if self._copy_stream is None:
             self._copy_stream = torch.cuda.Stream(device=self.device)
         main = torch.cuda.current_stream(self.device)
         self.losses.zero_()
-        if nv == 0:
-            self.grads_flat.zero_()
         # the previous iteration may still be reading the staging buffers
         self._copy_stream.wait_stream(main)
         events = []
+        nv_total = 0
         with torch.cuda.stream(self._copy_stream):
-            self._d_view.copy_(h_viewmats, non_blocking=True)
-            self._d_intr.copy_(h_intrins, non_blocking=True)
-            for c0 in range(0, nv, chunk):
-                c1 = min(nv, c0 + chunk)
-                self._d_gt[c0:c1].copy_(h_gt[c0:c1], non_blocking=True)
-                ev = torch.cuda.Event()
-                ev.record(self._copy_stream)
-                events.append((c0, c1, ev))
-        for c0, c1, ev in events:
+            for kind, h_viewmats, h_intrins, h_gt in batches:
+                nv = int(h_viewmats.shape[0])
+                nv_total += nv
+                st = self._staging.get(kind)
+                if st is None or st[2].shape != h_gt.shape:
+                    st = (torch.empty_like(h_viewmats, device=self.device), torch.empty_like(h_intrins, device=self.device),
+                          torch.empty_like(h_gt, device=self.device))
+                    self._staging[kind] = st
+                st[0].copy_(h_viewmats, non_blocking=True)
+                st[1].copy_(h_intrins, non_blocking=True)
+                for c0 in range(0, nv, chunk):
+                    c1 = min(nv, c0 + chunk)
+                    st[2][c0:c1].copy_(h_gt[c0:c1], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(self._copy_stream)
+                    events.append((kind, c0, c1, ev))
+        if nv_total == 0:
+            self.grads_flat.zero_()
+        for i, (kind, c0, c1, ev) in enumerate(events):
             main.wait_event(ev)
-            L.check(self.lib.ssb_step_views(self.handle, C.byref(self._p_struct), C.byref(self.shq) if self.shq else None,
-                                            L.ptr(self._d_view[c0:]), L.ptr(self._d_intr[c0:]), L.ptr(self._d_gt[c0:]), c1 - c0,
-                                            C.byref(self._g_struct), 1 if c0 > 0 else 0, L.ptr(self.losses), None))
+            d_view, d_intr, d_gt = self._staging[kind]
+            L.check(self.lib.ssb_step_views(self.handles[kind], C.byref(self._p_struct), C.byref(self.shq) if self.shq else None,
+                                            L.ptr(d_view[c0:]), L.ptr(d_intr[c0:]), L.ptr(d_gt[c0:]), c1 - c0,
+                                            C.byref(self._g_struct), 1 if i > 0 else 0, L.ptr(self.losses), None))
         self.allreduce_grads()
         self.optimizer_step(total_views)
         out = self.losses.cpu()
-        return tuple((out / max(nv, 1)).tolist())
+        return tuple((out / max(nv_total, 1)).tolist())
 
-    def last_isects(self):
+    def last_isects(self, kind=0):
         m = C.c_int64(0)
-        L.check(self.lib.ssb_step_last_isects(self.handle, C.byref(m), None))
+        L.check(self.lib.ssb_step_last_isects(self.handles[kind], C.byref(m), None))
         return m.value

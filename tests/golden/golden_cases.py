@@ -21,7 +21,34 @@ CASES = {
 }
 
 
+# wide field-of-view cameras: the same splat cloud seen by one equidistant fisheye camera
+# (model 1, about 190 degrees across the image) and one equirectangular camera (model 3),
+# both near the middle of the cloud so splats lie in every direction, behind the camera included
+WIDE_CASES = {
+    "wide_fisheye": dict(seed=404, n=1500, model=1, w=96, h=96, f=29.0, scale_mu=-2.4, extent=3.0),
+    "wide_equirect": dict(seed=404, n=1500, model=3, w=128, h=64, f=128 / (2 * np.pi), scale_mu=-2.4, extent=3.0),
+}
+
+
+def build_wide_case(name):
+    """Returns (cfg, splats, viewmats[1,16], intrins[1,4], camera model)."""
+    c = WIDE_CASES[name]
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=c["n"], width=c["w"], height=c["h"], n_views=1, name=name)
+    cfg.log_scale_mu = c["scale_mu"]
+    cfg.mean_extent = c["extent"]
+    cfg.fx = cfg.fy = float(c["f"])
+    sp = scenes.make_splats(cfg, seed=c["seed"])
+    rng = np.random.default_rng(c["seed"] + 7)
+    eye = rng.uniform(-0.4, 0.4, size=3)
+    target = eye + rng.normal(size=3)
+    vm = scenes.look_at(eye, target).reshape(1, 16)
+    K = np.array([[cfg.fx, cfg.fy, c["w"] / 2.0, c["h"] / 2.0]], dtype=np.float32)
+    return cfg, sp, vm.astype(np.float32), K, c["model"]
+
+
 def build_case(name):
+    if name in WIDE_CASES:
+        return build_wide_case(name)[:4]
     c = CASES[name]
     cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=c["n"], width=c["w"], height=c["h"], n_views=c["views"], name=name)
     cfg.log_scale_mu = c["scale_mu"]
@@ -34,7 +61,7 @@ def build_case(name):
 
 
 def raster_cotangents(name, n_pixels):
-    rng = np.random.default_rng(CASES[name]["seed"] + 1)
+    rng = np.random.default_rng((CASES.get(name) or WIDE_CASES[name])["seed"] + 1)
     v_rgb = rng.normal(size=(n_pixels, 3)).astype(np.float32)
     v_depth = (0.1 * rng.normal(size=n_pixels)).astype(np.float32)
     v_T = (0.1 * rng.normal(size=n_pixels)).astype(np.float32)

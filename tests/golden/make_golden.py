@@ -2,7 +2,9 @@
 device code (oracle/_ref/libssb_ref.so, built from the reference sources by
 oracle/Makefile.ref) on a GPU, on small seeded scenes.
 
-    python tests/golden/make_golden.py [out_dir]
+    python tests/golden/make_golden.py [out_dir [fixture ...]]
+
+With fixture names (ring2, dense1, wide_fisheye, wide_equirect, ssim, adam) only those are written.
 
 Inputs are not stored: they are regenerated from `golden_cases.py` (same seeds).
 Every stage is run stage-isolated on the reference's own upstream outputs, so a
@@ -21,7 +23,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, HERE)
 
-from golden_cases import CASES, build_case, loss_inputs, adam_inputs, raster_cotangents  # noqa: E402
+from golden_cases import CASES, WIDE_CASES, build_case, loss_inputs, adam_inputs, raster_cotangents  # noqa: E402
 
 DEV = "cuda:0"
 
@@ -41,6 +43,7 @@ def check(rc, what):
 
 def run_case(ref, name, out_dir):
     cfg, sp, vm, K = build_case(name)
+    model = WIDE_CASES[name]["model"] if name in WIDE_CASES else 0
     n, W, H, I = cfg.n_splats, cfg.width, cfg.height, vm.shape[0]
     d = {k: dev(v.reshape(-1)) for k, v in sp.items()}
     d_vm, d_K = dev(vm), dev(K)
@@ -48,7 +51,9 @@ def run_case(ref, name, out_dir):
     z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=DEV)
     aabb, depths, radii = z(m, 4), z(m), z(n)
     xy, depth, conic, opac, rgb = z(m, 2), z(m), z(m, 3), z(m), z(m, 3)
-    check(ref.ref_project_fwd(I, n, W, H, P(d["means"]), P(d["quats"]), P(d["scales"]), P(d["opacities"]), P(d["features_dc"]),
+    fwd = ref.ref_project_fwd if model == 0 else (lambda *a: ref.ref_project_fwd_model(model, *a))
+    bwd = ref.ref_project_bwd if model == 0 else (lambda *a: ref.ref_project_bwd_model(model, *a))
+    check(fwd(I, n, W, H, P(d["means"]), P(d["quats"]), P(d["scales"]), P(d["opacities"]), P(d["features_dc"]),
                               P(d["features_sh"]), None, None, 32, C.c_int64(256), P(d_vm), P(d_K), P(aabb), P(depths), P(radii),
                               P(xy), P(depth), P(conic), P(opac), P(rgb)), "ref_project_fwd")
     # culled pairs: the reference leaves their screen entries unwritten (zeros here)
@@ -80,7 +85,7 @@ def run_case(ref, name, out_dir):
     out.update(v_xy=g_xy, v_depth=g_depth, v_conic=g_conic, v_opac=g_opac, v_rgb=g_rgb)
 
     g = {k: torch.zeros_like(t) for k, t in d.items()}
-    check(ref.ref_project_bwd(I, n, W, H, P(d["means"]), P(d["quats"]), P(d["scales"]), P(d["opacities"]), P(d["features_dc"]),
+    check(bwd(I, n, W, H, P(d["means"]), P(d["quats"]), P(d["scales"]), P(d["opacities"]), P(d["features_dc"]),
                               P(d["features_sh"]), None, None, 32, C.c_int64(256), P(d_vm), P(d_K), P(aabb),
                               P(g_xy), P(g_depth), P(g_conic), P(g_opac), P(g_rgb),
                               P(g["means"]), P(g["quats"]), P(g["scales"]), P(g["opacities"]), P(g["features_dc"]), P(g["features_sh"])), "ref_project_bwd")
@@ -149,10 +154,14 @@ def main():
     out_dir = sys.argv[1] if len(sys.argv) > 1 else HERE
     os.makedirs(out_dir, exist_ok=True)
     ref = C.CDLL(os.path.join(ROOT, "oracle", "_ref", "libssb_ref.so"))
-    for name in CASES:
-        run_case(ref, name, out_dir)
-    run_loss(ref, out_dir)
-    run_adam(ref, out_dir)
+    only = set(sys.argv[2:])
+    for name in list(CASES) + list(WIDE_CASES):
+        if not only or name in only:
+            run_case(ref, name, out_dir)
+    if not only or "ssim" in only:
+        run_loss(ref, out_dir)
+    if not only or "adam" in only:
+        run_adam(ref, out_dir)
     print("wrote fixtures to", out_dir)
 
 

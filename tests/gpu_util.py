@@ -40,7 +40,7 @@ def unpack_screen(lib, rec, m):
     return {k: v.cpu().numpy() for k, v in out.items()}
 
 
-def project_fwd(lib, sp_dev, viewmats, intrins, W, H, shq=None, n=None):
+def project_fwd(lib, sp_dev, viewmats, intrins, W, H, shq=None, n=None, model=0):
     n = n or sp_dev["means"].shape[0]
     vm, K = dev(viewmats), dev(intrins)
     Cn = vm.shape[0]
@@ -49,7 +49,7 @@ def project_fwd(lib, sp_dev, viewmats, intrins, W, H, shq=None, n=None):
     radii = torch.zeros(n, device=DEV)
     rec = torch.zeros(Cn * n * L.SCREEN_REC_FLOATS, device=DEV)
     s = L.splats_struct(sp_dev if shq is None else {**sp_dev, "features_sh": None})
-    cams = L.cameras_struct(vm, K, W, H)
+    cams = L.cameras_struct(vm, K, W, H, model=model)
     L.check(lib.ssb_project_fwd(C.byref(s), C.byref(shq) if shq is not None else None, n, C.byref(cams), L.ptr(aabb), L.ptr(depths),
                                 L.ptr(radii), L.ptr(rec), None))
     torch.cuda.synchronize()

@@ -15,7 +15,15 @@ import pytest
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 
-from golden_cases import CASES, adam_inputs, build_case, loss_inputs, raster_cotangents  # noqa: E402
+from golden_cases import CASES, WIDE_CASES, adam_inputs, build_case, loss_inputs, raster_cotangents  # noqa: E402
+
+
+ALL_CASES = list(CASES) + list(WIDE_CASES)
+
+
+def model_of(name):
+    """Camera model of a fixture: 0 pinhole, 1 equidistant fisheye, 3 equirectangular."""
+    return WIDE_CASES[name]["model"] if name in WIDE_CASES else 0
 
 
 def load(name):
@@ -31,11 +39,11 @@ def ref_proj(gold):
     return {k: gold[k] for k in ("aabb", "depths", "xy", "depth", "conic", "opac", "rgb")}
 
 
-@pytest.mark.parametrize("name", list(CASES))
+@pytest.mark.parametrize("name", ALL_CASES)
 def test_projection_forward_vs_reference(oracle, name):
     cfg, sp, vm, K = build_case(name)
     gold = load(name)
-    got = oracle.project_fwd(sp, vm, K, cfg.width, cfg.height)
+    got = oracle.project_fwd(sp, vm, K, cfg.width, cfg.height, model=model_of(name))
     keep_ref = gold["aabb"][:, 2] > gold["aabb"][:, 0]
     keep_got = got["aabb"][:, 2] > got["aabb"][:, 0]
     assert keep_ref.sum() > 0 and (keep_ref != keep_got).mean() <= 2e-3
@@ -47,7 +55,7 @@ def test_projection_forward_vs_reference(oracle, name):
     assert frac_bad(got["radii"], gold["radii"], 1e-4, 1e-3) <= 2e-3
 
 
-@pytest.mark.parametrize("name", list(CASES))
+@pytest.mark.parametrize("name", ALL_CASES)
 def test_tile_stage_vs_reference(oracle, name):
     """Counts, sorted keys, flatten ids and offsets from the reference's own projected floats."""
     cfg, sp, vm, K = build_case(name)
@@ -77,7 +85,7 @@ def test_tile_stage_vs_reference(oracle, name):
     assert np.array_equal(oracle.tile_offsets(gold["sorted_ids"], tw * th * I), gold["offsets"])
 
 
-@pytest.mark.parametrize("name", list(CASES))
+@pytest.mark.parametrize("name", ALL_CASES)
 def test_raster_forward_vs_reference(oracle, name):
     cfg, sp, vm, K = build_case(name)
     gold = load(name)
@@ -91,7 +99,7 @@ def test_raster_forward_vs_reference(oracle, name):
     assert (got["last_ids"] != gold["last_ids"]).mean() <= 2e-3
 
 
-@pytest.mark.parametrize("name", list(CASES))
+@pytest.mark.parametrize("name", ALL_CASES)
 def test_raster_backward_vs_reference(oracle, name):
     cfg, sp, vm, K = build_case(name)
     gold = load(name)
@@ -105,12 +113,12 @@ def test_raster_backward_vs_reference(oracle, name):
         assert frac_bad(got[k], ref, 1e-4 * scale, 2e-3) <= 5e-3, k
 
 
-@pytest.mark.parametrize("name", list(CASES))
+@pytest.mark.parametrize("name", ALL_CASES)
 def test_projection_backward_vs_reference(oracle, name):
     cfg, sp, vm, K = build_case(name)
     gold = load(name)
     v = {k: gold[k] for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")}
-    got = oracle.project_bwd(sp, vm, K, cfg.width, cfg.height, gold["aabb"], v)
+    got = oracle.project_bwd(sp, vm, K, cfg.width, cfg.height, gold["aabb"], v, model=model_of(name))
     for k in got:
         ref = gold["g_" + k].reshape(got[k].shape)
         scale = np.abs(ref).max()

@@ -13,7 +13,7 @@ torch = pytest.importorskip("torch")
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 
-from golden_cases import CASES, adam_inputs, build_case, loss_inputs, raster_cotangents  # noqa: E402
+from golden_cases import CASES, WIDE_CASES, adam_inputs, build_case, loss_inputs, raster_cotangents  # noqa: E402
 from spirula_studio_b200 import lib as L  # noqa: E402
 
 pytestmark = pytest.mark.gpu
@@ -32,6 +32,14 @@ def U():
     return gpu_util
 
 
+ALL_CASES = list(CASES) + list(WIDE_CASES)
+
+
+def model_of(name):
+    """Camera model of a fixture: 0 pinhole, 1 equidistant fisheye, 3 equirectangular."""
+    return WIDE_CASES[name]["model"] if name in WIDE_CASES else 0
+
+
 def load(name):
     return dict(np.load(os.path.join(HERE, "golden", f"{name}.npz")))
 
@@ -40,11 +48,11 @@ def ref_proj(gold):
     return {k: gold[k] for k in ("aabb", "depths", "xy", "depth", "conic", "opac", "rgb")}
 
 
-@pytest.mark.parametrize("name", list(CASES))
+@pytest.mark.parametrize("name", ALL_CASES)
 def test_projection_forward_vs_reference(lib, U, name):
     cfg, sp, vm, K = build_case(name)
     gold = load(name)
-    got = U.project_fwd(lib, U.splats_dev(sp), vm, K, cfg.width, cfg.height)
+    got = U.project_fwd(lib, U.splats_dev(sp), vm, K, cfg.width, cfg.height, model=model_of(name))
     aabb = got["aabb"].cpu().numpy()
     keep_ref, keep_got = gold["aabb"][:, 2] > gold["aabb"][:, 0], aabb[:, 2] > aabb[:, 0]
     assert (keep_ref != keep_got).mean() <= 2e-3
@@ -55,7 +63,7 @@ def test_projection_forward_vs_reference(lib, U, name):
         assert U.close_frac(scr[k][both], gold[k][both], 5e-3, 5e-4) <= 2e-3, k
 
 
-@pytest.mark.parametrize("name", list(CASES))
+@pytest.mark.parametrize("name", ALL_CASES)
 def test_tile_stage_vs_reference(lib, U, name):
     cfg, sp, vm, K = build_case(name)
     gold = load(name)
@@ -80,7 +88,7 @@ def test_tile_stage_vs_reference(lib, U, name):
     assert np.array_equal(offs2.cpu().numpy(), gold["offsets"])
 
 
-@pytest.mark.parametrize("name", list(CASES))
+@pytest.mark.parametrize("name", ALL_CASES)
 def test_raster_forward_vs_reference(lib, U, name):
     cfg, sp, vm, K = build_case(name)
     gold = load(name)
@@ -94,7 +102,7 @@ def test_raster_forward_vs_reference(lib, U, name):
     assert (got["last_ids"].cpu().numpy() != gold["last_ids"]).mean() <= 2e-3
 
 
-@pytest.mark.parametrize("name", list(CASES))
+@pytest.mark.parametrize("name", ALL_CASES)
 def test_raster_backward_vs_reference(lib, U, name):
     cfg, sp, vm, K = build_case(name)
     gold = load(name)
@@ -110,7 +118,7 @@ def test_raster_backward_vs_reference(lib, U, name):
         assert U.close_frac(got[k], ref, 1e-4 * np.abs(ref).max(), 2e-3) <= 5e-3, k
 
 
-@pytest.mark.parametrize("name", list(CASES))
+@pytest.mark.parametrize("name", ALL_CASES)
 def test_projection_backward_vs_reference(lib, U, name):
     cfg, sp, vm, K = build_case(name)
     gold = load(name)
@@ -119,7 +127,7 @@ def test_projection_backward_vs_reference(lib, U, name):
     grads = {k: torch.zeros_like(t) for k, t in spd.items()}
     s, g = L.splats_struct(spd), L.splats_struct(grads)
     d_vm, d_K, d_aabb = U.dev(vm), U.dev(K), U.dev(gold["aabb"])
-    cams = L.cameras_struct(d_vm, d_K, cfg.width, cfg.height)
+    cams = L.cameras_struct(d_vm, d_K, cfg.width, cfg.height, model=model_of(name))
     vrec = U.arrays_to_vrec({k: gold[k].reshape(I * n, -1) if gold[k].ndim > 1 else gold[k] for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")}, I * n)
     L.check(lib.ssb_project_bwd(C.byref(s), None, n, C.byref(cams), L.ptr(d_aabb), L.ptr(vrec), C.byref(g), 0, None))
     torch.cuda.synchronize()

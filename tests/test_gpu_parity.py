@@ -119,6 +119,62 @@ def test_projection_backward(lib, U, oracle):
     assert U.close_frac(got, 2 * ref["means"], 2e-5 * np.abs(ref["means"]).max(), 1e-3) <= 2e-3
 
 
+def wide_scene(model, n=6000, seed=21):
+    """Camera inside the cloud: an equidistant fisheye (model 1, ~190 degrees) or an equirectangular one (model 3)."""
+    W, H, f = (240, 240, 72.0) if model == 1 else (320, 160, 320 / (2 * np.pi))
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=n, width=W, height=H)
+    cfg.log_scale_mu, cfg.mean_extent = -2.6, 3.0
+    sp = scenes.make_splats(cfg, seed=seed)
+    vm = np.stack([scenes.look_at((0.2, -0.1, 0.15), (1.0, 0.3, 2.0)), scenes.look_at((-0.3, 0.2, 0.1), (-1.0, 0.5, -1.0))]).reshape(2, 16)
+    K = np.tile(np.array([[f, f, W / 2.0, H / 2.0]], dtype=np.float32), (2, 1))
+    return cfg, sp, vm.astype(np.float32), K
+
+
+@pytest.mark.parametrize("model", [L.CAMERA_FISHEYE, L.CAMERA_EQUIRECT])
+def test_projection_forward_wide_cameras(lib, U, oracle, model):
+    cfg, sp, vm, K = wide_scene(model)
+    W, H, n = cfg.width, cfg.height, cfg.n_splats
+    ref = oracle.project_fwd(sp, vm, K, W, H, model=model)
+    got = U.project_fwd(lib, U.splats_dev(sp), vm, K, W, H, model=model)
+    aabb = got["aabb"].cpu().numpy()
+    keep_ref, keep_got = ref["aabb"][:, 2] > ref["aabb"][:, 0], aabb[:, 2] > aabb[:, 0]
+    assert keep_ref.sum() > 0.3 * keep_ref.size
+    assert (keep_ref != keep_got).mean() <= 5e-4
+    both = keep_ref & keep_got
+    scr = U.unpack_screen(lib, got["rec"], 2 * n)
+    assert U.close_frac(aabb[both], ref["aabb"][both], 5e-3, 5e-4) <= 5e-4
+    assert U.close_frac(got["depths"].cpu().numpy()[both], ref["depths"][both], 1e-5, 1e-5) == 0.0
+    for k, (atol, rtol) in dict(xy=(2e-3, 1e-5), depth=(1e-5, 1e-5), conic=(1e-5, 1e-3), opac=(1e-6, 1e-5), rgb=(2e-5, 1e-5)).items():
+        assert U.close_frac(scr[k][both], ref[k][both], atol, rtol) <= 5e-4, k
+
+
+@pytest.mark.parametrize("model", [L.CAMERA_FISHEYE, L.CAMERA_EQUIRECT])
+def test_projection_backward_wide_cameras(lib, U, oracle, model):
+    cfg, sp, vm, K = wide_scene(model)
+    W, H, n = cfg.width, cfg.height, cfg.n_splats
+    ref_f = oracle.project_fwd(sp, vm, K, W, H, model=model)
+    rng = np.random.default_rng(4)
+    m = 2 * n
+    v = dict(v_xy=rng.normal(size=(m, 2)), v_depth=rng.normal(size=m), v_conic=rng.normal(size=(m, 3)) * 0.05, v_opac=rng.normal(size=m),
+             v_rgb=rng.normal(size=(m, 3)))
+    v = {k: x.astype(np.float32) for k, x in v.items()}
+    ref = oracle.project_bwd(sp, vm, K, W, H, ref_f["aabb"], v, model=model)
+    spd = U.splats_dev(sp)
+    for views in (2, 1):      # the several-view and the single-view kernel
+        grads = {k: torch.full_like(t, 7.0) for k, t in spd.items()}
+        s, g = L.splats_struct(spd), L.splats_struct(grads)
+        d_vm, d_K, d_aabb = U.dev(vm), U.dev(K), U.dev(ref_f["aabb"])
+        cams = L.cameras_struct(d_vm, d_K, W, H, model=model, count=views)
+        vrec = U.arrays_to_vrec(v, m)
+        L.check(lib.ssb_project_bwd(C.byref(s), None, n, C.byref(cams), L.ptr(d_aabb), L.ptr(vrec), C.byref(g), 0, None))
+        torch.cuda.synchronize()
+        want = ref if views == 2 else oracle.project_bwd(sp, vm[:1], K[:1], W, H, ref_f["aabb"][:n], {k: x[:n] for k, x in v.items()}, model=model)
+        for k in want:
+            got = grads[k].cpu().numpy().reshape(want[k].shape)
+            scale = np.abs(want[k]).max()
+            assert U.close_frac(got, want[k], 1e-5 * scale, 1e-3) <= 2e-3, (k, views)
+
+
 # ------------------------------------------------------- keys / sort / ranges
 @pytest.mark.parametrize("views,scale_mu", [(1, -3.5), (2, -3.0), (1, -2.0)])
 def test_tile_keys_bit_exact(lib, U, oracle, views, scale_mu):

@@ -193,6 +193,50 @@ def test_whole_iteration_matches_oracle(lib, U, oracle, quant):
     tr.close(); tr2.close()
 
 
+def test_wide_camera_iteration_matches_oracle(lib, U, oracle):
+    """A batch that mixes equidistant-fisheye and equirectangular views of different sizes (the wide
+    field-of-view configuration, scaled down): summed gradients and losses against the oracle."""
+    from spirula_studio_b200.trainer import Trainer
+    cfg = scenes.scaled(scenes.CONFIGS["wide_5m"], n_splats=9000, width=144, n_views=4)
+    cfg.log_scale_mu, cfg.mean_extent = -2.4, 4.0
+    sp = scenes.make_splats(cfg)
+    vm, K = scenes.make_cameras(cfg)
+    n = cfg.n_splats
+    tot, ref_l = None, np.zeros(3)
+    for v in range(cfg.n_views):
+        _, model, W, H, _, _ = scenes.view_kind(cfg, v)
+        ch = oracle.forward_chain(sp, vm[v:v + 1], K[v:v + 1], W, H, model=model)
+        assert ch["sorted_vals"].size > 2000
+        vr, l = oracle.loss_l1_ssim(ch["render"]["rgb"], scenes.make_target(cfg, v).reshape(-1, 3), 1, H, W, 0.8, 0.2)
+        ref_l += l
+        gs = oracle.raster_bwd(ch["proj"], ch["offsets"], ch["sorted_vals"], 1, n, W, H, ch["render"], vr)
+        g = oracle.project_bwd(sp, vm[v:v + 1], K[v:v + 1], W, H, ch["proj"]["aabb"], gs, model=model)
+        tot = g if tot is None else {k: tot[k] + g[k] for k in g}
+    tr = Trainer(cfg, sp, device=U.DEV)
+    assert len(tr.handles) == 2
+    batches = []
+    for kind in range(2):
+        views = [v for v in range(cfg.n_views) if scenes.view_kind(cfg, v)[0] == kind]
+        gt = np.stack([scenes.make_target(cfg, v) for v in views])
+        batches.append((kind, torch.from_numpy(vm[views].copy()).pin_memory(), torch.from_numpy(K[views].copy()).pin_memory(),
+                        torch.from_numpy(gt).pin_memory()))
+    tr.losses.zero_()
+    dev_batches = [(k, a.to(U.DEV), b.to(U.DEV), c.to(U.DEV)) for k, a, b, c in batches]
+    for i, (k, d_vm, d_K, d_gt) in enumerate(dev_batches):
+        tr.views_fwd_bwd(d_vm, d_K, d_gt, d_vm.shape[0], accumulate=i > 0, kind=k)
+    torch.cuda.synchronize()
+    assert np.allclose(tr.losses.cpu().numpy(), ref_l, rtol=1e-3, atol=1e-5)
+    for k in tot:
+        got = tr.grads[k].cpu().numpy().reshape(tot[k].shape)
+        scale = np.abs(tot[k]).max()
+        assert U.close_frac(got, tot[k], 2e-5 * scale, 1e-3) <= 5e-3, k
+    # and through the host-buffer entry point
+    tr2 = Trainer(cfg, sp, device=U.DEV)
+    l1, ssim, loss = tr2.train_step_kinds(batches, cfg.n_views)
+    assert abs(loss - ref_l[2] / cfg.n_views) <= 1e-3 * abs(ref_l[2] / cfg.n_views) + 1e-5
+    tr.close(); tr2.close()
+
+
 def test_full_size_sort_and_range_properties(lib, U):
     """At the benchmark's pair count (several million) the oracle is too slow to
     run inside a test, so check what must hold at any size: the output is

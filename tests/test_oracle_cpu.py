@@ -70,8 +70,8 @@ def test_tile_keys_cover_footprint(oracle):
             assert (g, int(t)) in binned
 
 
-def _proj_scalar(oracle, sp, vm, K, W, H, v):
-    o = oracle.project_fwd(sp, vm, K, W, H)
+def _proj_scalar(oracle, sp, vm, K, W, H, v, model=0):
+    o = oracle.project_fwd(sp, vm, K, W, H, model=model)
     keep = o["aabb"][:, 2] > o["aabb"][:, 0]
     tot = 0.0
     for name, key in (("xy", "v_xy"), ("depth", "v_depth"), ("conic", "v_conic"), ("opac", "v_opac"), ("rgb", "v_rgb")):
@@ -104,6 +104,63 @@ def test_projection_backward_matches_finite_differences(oracle, attr):
     fd = (lp - lm) / (2 * eps)
     an = float((g[attr].astype(np.float64) * d).sum())
     assert abs(fd - an) <= 2e-2 * max(1.0, abs(fd)), (fd, an)
+
+
+def wide_scene(model, n=96, seed=11):
+    """Camera inside the cloud: an equidistant fisheye (model 1) or an equirectangular one (model 3)."""
+    W, H, f = (120, 120, 36.0) if model == 1 else (160, 80, 160 / (2 * np.pi))
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=n, width=W, height=H)
+    cfg.log_scale_mu, cfg.mean_extent = -2.2, 2.5
+    sp = scenes.make_splats(cfg, seed=seed)
+    vm = scenes.look_at((0.2, -0.1, 0.15), (1.0, 0.3, 2.0)).reshape(1, 16).astype(np.float32)
+    K = np.array([[f, f, W / 2.0, H / 2.0]], dtype=np.float32)
+    return cfg, sp, vm, K
+
+
+@pytest.mark.parametrize("model", [1, 3])
+@pytest.mark.parametrize("attr", ["means", "quats", "scales", "opacities"])
+def test_wide_projection_backward_matches_finite_differences(oracle, model, attr):
+    """Fisheye and equirectangular cameras: the vjp against central differences of the forward pass."""
+    cfg, sp, vm, K = wide_scene(model)
+    W, H, n = cfg.width, cfg.height, cfg.n_splats
+    rng = np.random.default_rng(6)
+    v = dict(v_xy=rng.normal(size=(n, 2)), v_depth=rng.normal(size=n), v_conic=rng.normal(size=(n, 3)) * 0.1,
+             v_opac=rng.normal(size=n), v_rgb=rng.normal(size=(n, 3)))
+    v = {k: x.astype(np.float32) for k, x in v.items()}
+    base = oracle.project_fwd(sp, vm, K, W, H, model=model)
+    keep = base["aabb"][:, 2] > base["aabb"][:, 0]
+    assert keep.sum() > n // 4
+    g = oracle.project_bwd(sp, vm, K, W, H, base["aabb"], v, model=model)
+    d = rng.normal(size=sp[attr].shape).astype(np.float32)
+    eps = 1e-3
+    plus = {k: x.copy() for k, x in sp.items()}
+    minus = {k: x.copy() for k, x in sp.items()}
+    plus[attr] = sp[attr] + eps * d
+    minus[attr] = sp[attr] - eps * d
+    lp, kp = _proj_scalar(oracle, plus, vm, K, W, H, v, model)
+    lm, km = _proj_scalar(oracle, minus, vm, K, W, H, v, model)
+    assert np.array_equal(kp, km)
+    fd = (lp - lm) / (2 * eps)
+    an = float((g[attr].astype(np.float64) * d).sum())
+    assert abs(fd - an) <= 3e-2 * max(1.0, abs(fd)), (fd, an)
+
+
+def test_wide_sorting_depth(oracle):
+    """Sorting depth: squared distance (equirectangular), z^4 + (x^2+y^2)^2/512 (fisheye)."""
+    for model in (1, 3):
+        cfg, sp, vm, K = wide_scene(model)
+        o = oracle.project_fwd(sp, vm, K, cfg.width, cfg.height, model=model)
+        keep = o["aabb"][:, 2] > o["aabb"][:, 0]
+        m = vm.reshape(4, 4).astype(np.float64)
+        pc = sp["means"].astype(np.float64) @ m[:3, :3].T + m[:3, 3]
+        if model == 3:
+            want = (pc ** 2).sum(1)
+        else:
+            want = pc[:, 2] ** 4 + ((pc[:, 0] ** 2 + pc[:, 1] ** 2) ** 2) / 512.0
+        assert np.allclose(o["depths"][keep], want[keep], rtol=1e-4)
+        assert np.allclose(o["depth"][keep], np.sqrt((pc ** 2).sum(1))[keep], rtol=1e-5)
+        if model == 3:
+            assert (pc[keep, 2] < 0).any()      # splats behind the camera are seen
 
 
 def _frozen_blend(proj64, order, mask, W, H, v_rgb, v_depth):

@@ -246,12 +246,52 @@ __device__ __forceinline__ void sh_basis(float x, float y, float z, float b[kNum
 }
 
 // Loads the block's SH span into shared memory as fp32 (decoding packed codes).
+// A full block's span starts on a 16-byte boundary in every format (128 * 45 cells), so it is
+// moved with 16-byte loads: 4 floats, or 8 sixteen-bit / 16 eight-bit codes that share one
+// bounds entry whenever the bounds stride is a multiple of the vector's cell count.
 __device__ __forceinline__ void stage_sh(
     float* sh_s, const float* __restrict__ sh_f32, const void* __restrict__ packed, const float* __restrict__ bounds,
     int bits, int64_t bounds_stride, int64_t first_splat, int64_t n) {
-    int64_t base = first_splat * kShPerSplat;
-    int count = (int)min((int64_t)kProjBlock, n - first_splat) * kShPerSplat;
-    if (bits == 8 || bits == 16) {
+    const int64_t base = first_splat * kShPerSplat;
+    const int count = (int)min((int64_t)kProjBlock, n - first_splat) * kShPerSplat;
+    // vector path: a full block and a 16-byte aligned array (scalar loads otherwise)
+    const void* arr = (bits == 8 || bits == 16) ? packed : (const void*)sh_f32;
+    const bool full = count == kProjBlock * kShPerSplat && ((uintptr_t)arr & 15) == 0;
+    if (bits == 16 && full && (bounds_stride & 7) == 0) {
+        const uint4* src = (const uint4*)((const uint16_t*)packed + base);
+        const int64_t b0 = base / bounds_stride;
+        const unsigned r0 = (unsigned)(base - b0 * bounds_stride), stride = (unsigned)min(bounds_stride, (int64_t)0x7fffffff);
+        const float inv = 1.0f / 65535.0f;
+        for (int v = threadIdx.x; v < kProjBlock * kShPerSplat / 8; v += kProjBlock) {
+            uint4 c = src[v];
+            float2 mm = ((const float2*)bounds)[b0 + (r0 + 8u * v) / stride];
+            float d = mm.y - mm.x;
+            float4 lo, hi;
+            lo.x = mm.x + d * ((float)(c.x & 0xffffu) * inv); lo.y = mm.x + d * ((float)(c.x >> 16) * inv);
+            lo.z = mm.x + d * ((float)(c.y & 0xffffu) * inv); lo.w = mm.x + d * ((float)(c.y >> 16) * inv);
+            hi.x = mm.x + d * ((float)(c.z & 0xffffu) * inv); hi.y = mm.x + d * ((float)(c.z >> 16) * inv);
+            hi.z = mm.x + d * ((float)(c.w & 0xffffu) * inv); hi.w = mm.x + d * ((float)(c.w >> 16) * inv);
+            ((float4*)sh_s)[2 * v] = lo; ((float4*)sh_s)[2 * v + 1] = hi;
+        }
+    } else if (bits == 8 && full && (bounds_stride & 15) == 0) {
+        const uint4* src = (const uint4*)((const uint8_t*)packed + base);
+        const int64_t b0 = base / bounds_stride;
+        const unsigned r0 = (unsigned)(base - b0 * bounds_stride), stride = (unsigned)min(bounds_stride, (int64_t)0x7fffffff);
+        const float inv = 1.0f / 255.0f;
+        for (int v = threadIdx.x; v < kProjBlock * kShPerSplat / 16; v += kProjBlock) {
+            uint4 c = src[v];
+            float2 mm = ((const float2*)bounds)[b0 + (r0 + 16u * v) / stride];
+            float d = mm.y - mm.x;
+            const unsigned w[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float4 o;
+                o.x = mm.x + d * ((float)(w[k] & 0xffu) * inv); o.y = mm.x + d * ((float)((w[k] >> 8) & 0xffu) * inv);
+                o.z = mm.x + d * ((float)((w[k] >> 16) & 0xffu) * inv); o.w = mm.x + d * ((float)(w[k] >> 24) * inv);
+                ((float4*)sh_s)[4 * v + k] = o;
+            }
+        }
+    } else if (bits == 8 || bits == 16) {
         const float inv = bits == 8 ? (1.0f / 255.0f) : (1.0f / 65535.0f);
         for (int i = threadIdx.x; i < count; i += kProjBlock) {
             int64_t cell = base + i;
@@ -259,6 +299,9 @@ __device__ __forceinline__ void stage_sh(
             float2 mm = ((const float2*)bounds)[cell / bounds_stride];
             sh_s[i] = mm.x + (mm.y - mm.x) * (q * inv);
         }
+    } else if (full) {
+        const float4* src = (const float4*)(sh_f32 + base);
+        for (int v = threadIdx.x; v < kProjBlock * kShPerSplat / 4; v += kProjBlock) ((float4*)sh_s)[v] = src[v];
     } else {
         for (int i = threadIdx.x; i < count; i += kProjBlock) sh_s[i] = sh_f32[base + i];
     }
@@ -269,7 +312,7 @@ __global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
     SsbSplats sp, SsbShQuant shq, int64_t n, const float* __restrict__ viewmats, const float* __restrict__ intrins,
     int W, int H, int antialiased,
     float4* __restrict__ aabb_out, float* __restrict__ depths_out, float* __restrict__ radii, SsbScreenRec* __restrict__ screen) {
-    __shared__ float sh_s[kProjBlock * kShPerSplat];
+    __shared__ __align__(16) float sh_s[kProjBlock * kShPerSplat];
     const int cid = blockIdx.y;
     const int64_t first = (int64_t)blockIdx.x * kProjBlock;
     const int64_t gid = first + threadIdx.x;
@@ -391,8 +434,8 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
     // One view per launch (the training loop's case): a thread's SH gradients overwrite its own
     // SH values in shared memory once they have been read, so one 23 KB span is enough and six
     // CTAs fit an SM.  Several views: gradients accumulate in a second span.
-    __shared__ float sh_s[kProjBlock * kShPerSplat];
-    __shared__ float shg_multi[MULTI_VIEW ? kProjBlock * kShPerSplat : 1];
+    __shared__ __align__(16) float sh_s[kProjBlock * kShPerSplat];
+    __shared__ __align__(16) float shg_multi[MULTI_VIEW ? kProjBlock * kShPerSplat : 1];
     float* shg_s = MULTI_VIEW ? shg_multi : sh_s;
     const int64_t first = (int64_t)blockIdx.x * kProjBlock;
     const int64_t gid = first + threadIdx.x;
@@ -616,7 +659,18 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
     }
     __syncthreads();
     float* out = gr.features_sh + first * kShPerSplat;
-    if (accumulate) for (int i = threadIdx.x; i < count; i += kProjBlock) out[i] += shg_s[i];
+    if (count == kProjBlock * kShPerSplat && ((uintptr_t)gr.features_sh & 15) == 0) {   // full block of an aligned array
+        float4* out4 = (float4*)out;
+        const float4* g4 = (const float4*)shg_s;
+        if (accumulate) {
+            for (int v = threadIdx.x; v < kProjBlock * kShPerSplat / 4; v += kProjBlock) {
+                float4 o = out4[v], g = g4[v];
+                out4[v] = make_float4(o.x + g.x, o.y + g.y, o.z + g.z, o.w + g.w);
+            }
+        } else {
+            for (int v = threadIdx.x; v < kProjBlock * kShPerSplat / 4; v += kProjBlock) out4[v] = g4[v];
+        }
+    } else if (accumulate) for (int i = threadIdx.x; i < count; i += kProjBlock) out[i] += shg_s[i];
     else for (int i = threadIdx.x; i < count; i += kProjBlock) out[i] = shg_s[i];
 }
 

@@ -52,7 +52,7 @@ WORKLOAD = "mid_1m"
 # DRAM bytes one launch moves (dram__bytes_read.sum + dram__bytes_write.sum), from one ncu pass over this
 # file's own command on the mid_1m workload, one view per launch (a stage of several kernels: their sum).
 # The capture and its command are summarised in profiles/all_kernels_mid1m_counters.md.
-NCU_TRAFFIC_MID1M = {"project_fwd": 180.6e6, "tile_keys": 147.4e6, "sort": 321.0e6, "tile_ranges": 34.5e6, "raster_fwd": 70.0e6,
+NCU_TRAFFIC_MID1M = {"project_fwd": 180.6e6, "raster_fwd": 70.0e6,
                      "loss": 50.4e6, "raster_bwd": 117.8e6, "project_bwd": 507.4e6, "adam": 839.9e6}
 
 
@@ -119,12 +119,15 @@ def stage_bytes(stage, n, visible, pairs, pixels, tiles, quant_bits, sort_passes
     sh_b = 45 * (4 if quant_bits == 32 else quant_bits // 8)
     if stage == "project_fwd":
         return visible * (56 + sh_b + 60) + (n - visible) * 56
+    # the step bins pairs by tile and sorts each tile's list (ssb_intersect_tiles): the key stage reads 44 B per
+    # (view, splat) and writes one 8-byte (depth, pair) word per pair plus the tile table; the sort stage reads
+    # that word and writes the 4-byte sorted pair index; the ranges come out of the key stage's scan
     if stage == "tile_keys":
-        return n * 44 + pairs * 12
+        return n * 44 + pairs * 8 + tiles * 8
     if stage == "sort":
-        return pairs * (24 * sort_passes + 8)
+        return pairs * 12
     if stage == "tile_ranges":
-        return pairs * 8 + tiles * 4
+        return 0
     if stage == "raster_fwd":
         return pairs * 40 + pixels * 24
     if stage == "loss":

@@ -180,6 +180,22 @@ int ssb_sort_pairs_u64_noalloc(int64_t* d_keys_a, int32_t* d_vals_a, int64_t* d_
  * (src/kernels/tile/IntersectTile.cu:489-490). */
 int32_t ssb_tile_n_bits(int64_t n_tiles);
 
+/* The whole of do_intersect_tile_generic (src/kernels/tile/IntersectTile.cu:372-509) in one call: the
+ * sorted pair indices (flatten ids), optionally the sorted keys, the per-tile ranges and the pair
+ * count, identical to ssb_tile_keys -> ssb_sort_pairs_u64 -> ssb_tile_ranges on the same inputs, but
+ * built without a global sort: pairs are binned by tile (count, scan, scatter) and each tile's list
+ * is sorted on (depth bits, pair index) by one CTA.  total must be a whole number of images of
+ * n_per_image pairs.  d_isect_ids may be NULL when the sorted keys are not needed.  d_tile_offsets
+ * receives n_images * tiles entries (range end of the last tile = *d_n_isects, as for
+ * ssb_tile_ranges).  Pairs beyond capacity are dropped; *d_n_isects still reports the full count.
+ * Workspace: ssb_intersect_tiles_workspace_bytes(n_images * tiles, capacity). */
+int64_t ssb_intersect_tiles_workspace_bytes(int64_t n_tiles_total, int64_t capacity);
+int ssb_intersect_tiles(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
+                        int64_t total, int64_t n_per_image, int32_t width, int32_t height,
+                        void* d_workspace, int64_t workspace_bytes,
+                        int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                        int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream);
+
 /* Replaces intersect_offset_kernel (src/kernels/tile/IntersectTile.cu:271-307).
  * d_offsets [n_tiles_total] int32: first sorted index of each tile; tiles after
  * the last key get M; all zero when M == 0. */

@@ -47,6 +47,11 @@ int launch_loss(const float* d_render, const float* d_gt, int B, int H, int W, f
                 float* d_v_render, float* d_losses, cudaStream_t st);
 int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
                        SsbScreenRec* d_v_screen, const SsbSplats* grads, int accumulate, int clear_v_screen, void* stream);
+int launch_intersect_tiles(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
+                           int64_t total, int64_t n_per_image, int32_t width, int32_t height,
+                           void* d_workspace, int64_t workspace_bytes,
+                           int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                           int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort);
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline int64_t align_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }

@@ -29,14 +29,11 @@ struct SsbLane {
     float* depths;        // [n]
     SsbScreenRec* screen; // [n]
     SsbScreenRec* v_screen;
-    void* keys_ws;
-    void* sort_ws;
-    int64_t* ids[2];
-    int32_t* flat[2];
+    void* isect_ws;       // tile cursors + the unsorted (depth, pair) words
+    int32_t* flat;        // sorted pair indices
     int64_t* n_isects;    // device
     int32_t* offsets;     // [tiles]
     float* rgb; float* depth; float* T; int32_t* last_ids; float* v_rgb;
-    int sel;
     cudaStream_t stream;
     cudaEvent_t bwd_done;  // this lane's last projection backward
     cudaEvent_t all_done;
@@ -47,7 +44,7 @@ struct SsbStep {
     int tw, th;
     int64_t capacity;
     int64_t bytes;
-    int64_t keys_ws_bytes, sort_ws_bytes;
+    int64_t isect_ws_bytes;
     int n_lanes;
     int last_lane;
     SsbLane lane[SsbStep_kLanes];
@@ -78,8 +75,7 @@ static int dev_alloc(T** p, int64_t count, int64_t& total) {
 
 static void lane_free(SsbLane& l) {
     cudaFree(l.aabb); cudaFree(l.depths); cudaFree(l.screen); cudaFree(l.v_screen);
-    cudaFree(l.keys_ws); cudaFree(l.sort_ws);
-    cudaFree(l.ids[0]); cudaFree(l.ids[1]); cudaFree(l.flat[0]); cudaFree(l.flat[1]);
+    cudaFree(l.isect_ws); cudaFree(l.flat);
     cudaFree(l.n_isects); cudaFree(l.offsets);
     cudaFree(l.rgb); cudaFree(l.depth); cudaFree(l.T); cudaFree(l.last_ids); cudaFree(l.v_rgb);
     if (l.stream) cudaStreamDestroy(l.stream);
@@ -91,18 +87,14 @@ static int lane_alloc(SsbStep* s, SsbLane& l) {
     const int64_t n = s->cfg.n_splats, P = (int64_t)s->cfg.width * s->cfg.height, cap = s->capacity;
     int64_t& tot = s->bytes;
     int e = SSB_OK;
-    char* kws = nullptr; char* sws = nullptr;
+    char* iws = nullptr;
     if (!e) e = dev_alloc(&l.aabb, n * 4, tot);
     if (!e) e = dev_alloc(&l.depths, n, tot);
     if (!e) e = dev_alloc(&l.screen, n, tot);
     if (!e) e = dev_alloc(&l.v_screen, n, tot);
-    if (!e) e = dev_alloc(&kws, s->keys_ws_bytes, tot);
-    if (!e) e = dev_alloc(&sws, s->sort_ws_bytes, tot);
-    l.keys_ws = kws; l.sort_ws = sws;
-    for (int k = 0; k < 2 && !e; ++k) {
-        e = dev_alloc(&l.ids[k], cap, tot);
-        if (!e) e = dev_alloc(&l.flat[k], cap, tot);
-    }
+    if (!e) e = dev_alloc(&iws, s->isect_ws_bytes, tot);
+    l.isect_ws = iws;
+    if (!e) e = dev_alloc(&l.flat, cap, tot);
     if (!e) e = dev_alloc(&l.n_isects, 1, tot);
     if (!e) e = dev_alloc(&l.offsets, (int64_t)s->tw * s->th + 1, tot);
     if (!e) e = dev_alloc(&l.rgb, P * 3, tot);
@@ -113,7 +105,6 @@ static int lane_alloc(SsbStep* s, SsbLane& l) {
     if (e) return e;
     SSB_CUDA(cudaMemset(l.v_screen, 0, n * sizeof(SsbScreenRec)));
     SSB_CUDA(cudaMemset(l.n_isects, 0, sizeof(int64_t)));
-    SSB_CUDA(cudaMemset(l.sort_ws, 0, s->sort_ws_bytes));
     SSB_CUDA(cudaStreamCreateWithFlags(&l.stream, cudaStreamNonBlocking));
     SSB_CUDA(cudaEventCreateWithFlags(&l.bwd_done, cudaEventDisableTiming));
     SSB_CUDA(cudaEventCreateWithFlags(&l.all_done, cudaEventDisableTiming));
@@ -127,8 +118,6 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
     const int64_t n = s->cfg.n_splats;
     const int W = s->cfg.width, H = s->cfg.height;
     const int64_t P = (int64_t)W * H;
-    const int64_t n_tiles = (int64_t)s->tw * s->th;
-    const int end_bit = 32 + ssb_tile_n_bits(n_tiles);
     SsbCameras cam;
     cam.d_viewmats = d_viewmats + 16 * (int64_t)v;
     cam.d_intrins = d_intrins + 4 * (int64_t)v;
@@ -139,21 +128,17 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
     SSB_MARK(0);
     if ((e = ssb_project_fwd(params, shq, n, &cam, l.aabb, l.depths, nullptr, l.screen, st))) return e;
     SSB_MARK(1);
-    if ((e = ssb_tile_keys(l.aabb, l.depths, l.screen, n, n, W, H, l.keys_ws, s->keys_ws_bytes, nullptr, nullptr,
-                           l.ids[0], l.flat[0], s->capacity, l.n_isects, nullptr, st))) return e;
-    SSB_MARK(2);
-    int32_t sel = 0;
-    if ((e = ssb_sort_pairs_u64(l.ids[0], l.flat[0], l.ids[1], l.flat[1], l.n_isects, s->capacity, 0, end_bit,
-                                l.sort_ws, s->sort_ws_bytes, &sel, st))) return e;
-    l.sel = sel;
+    // counts + scan + scatter are reported as the key stage, the per-tile sort as the sort stage;
+    // the ranges come out of the scan, so that stage is empty
+    if ((e = launch_intersect_tiles(l.aabb, l.depths, l.screen, n, n, W, H, l.isect_ws, s->isect_ws_bytes, nullptr, l.flat, s->capacity,
+                                 l.offsets, l.n_isects, st, ev ? ev[2] : nullptr))) return e;
     SSB_MARK(3);
-    if ((e = ssb_tile_ranges(l.ids[sel], l.n_isects, s->capacity, n_tiles, l.offsets, st))) return e;
     SSB_MARK(4);
-    if ((e = ssb_raster_fwd(l.screen, l.offsets, l.flat[sel], l.n_isects, 1, W, H, l.rgb, l.depth, l.T, l.last_ids, st))) return e;
+    if ((e = ssb_raster_fwd(l.screen, l.offsets, l.flat, l.n_isects, 1, W, H, l.rgb, l.depth, l.T, l.last_ids, st))) return e;
     SSB_MARK(5);
     if ((e = launch_loss(l.rgb, d_gt + (int64_t)v * P * 3, 1, H, W, s->cfg.w_l1, s->cfg.w_ssim, l.v_rgb, d_losses, st))) return e;
     SSB_MARK(6);
-    if ((e = ssb_raster_bwd(l.screen, l.offsets, l.flat[sel], l.n_isects, 1, W, H, l.depth, l.T, l.last_ids,
+    if ((e = ssb_raster_bwd(l.screen, l.offsets, l.flat, l.n_isects, 1, W, H, l.depth, l.T, l.last_ids,
                             l.v_rgb, nullptr, nullptr, l.v_screen, st))) return e;
     SSB_MARK(7);
     if (wait_before_bwd) SSB_CUDA(cudaStreamWaitEvent(st, wait_before_bwd, 0));
@@ -193,8 +178,7 @@ int ssb_step_create(const SsbStepConfig* cfg, SsbStep** out) {
     s->th = (cfg->height + kTile - 1) / kTile;
     s->capacity = cfg->isect_capacity > 0 ? cfg->isect_capacity : 12 * cfg->n_splats;
     if (s->capacity >= ((int64_t)1 << 30)) s->capacity = ((int64_t)1 << 30) - 1;
-    s->keys_ws_bytes = ssb_tile_keys_workspace_bytes(cfg->n_splats);
-    s->sort_ws_bytes = ssb_sort_workspace_bytes(s->capacity);
+    s->isect_ws_bytes = ssb_intersect_tiles_workspace_bytes((int64_t)s->tw * s->th, s->capacity);
     s->n_lanes = SsbStep_kLanes;
     for (int k = 0; k < s->n_lanes; ++k) {
         int e = lane_alloc(s, s->lane[k]);
@@ -281,10 +265,6 @@ int ssb_step_last_isects(SsbStep* s, int64_t* h_n_isects, void* stream) {
     SsbLane& l = s->lane[s->last_lane];
     SSB_CUDA(cudaMemcpyAsync(h_n_isects, l.n_isects, sizeof(int64_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     SSB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
-    for (int k = 0; k < s->n_lanes; ++k) {
-        int e = ssb_sort_check(s->lane[k].sort_ws, stream);
-        if (e) return e;
-    }
     if (*h_n_isects > s->capacity) {
         set_error("ssb_step: %lld (splat, tile) pairs exceed the capacity of %lld; pairs beyond it were dropped", (long long)*h_n_isects, (long long)s->capacity);
         return SSB_ERR_CAPACITY;

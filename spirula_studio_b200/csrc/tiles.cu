@@ -273,6 +273,158 @@ __global__ void tile_ranges_kernel(const int64_t* __restrict__ ids, const int64_
     }
 }
 
+// ---------------------------------------------------------------------------
+// Fused intersection: the same sorted lists and ranges without a global sort.
+//
+// A key is (tile id << 32 | depth bits), so the sorted array is the concatenation of the
+// tiles' lists, each ordered by (depth bits, pair index) -- equal keys keep emission order,
+// which is pair-index order.  The lists are therefore built directly:
+//   1. count the pairs of every tile (one reduction per (splat, tile) pair);
+//   2. exclusive scan of the tile counts = the per-tile ranges, and the total M;
+//   3. write every pair as (depth bits << 32 | pair index) into its tile's range, at a slot
+//      taken from the tile's cursor (arrival order, arbitrary);
+//   4. one CTA per tile sorts its range on the whole 64-bit word (all words of a tile are
+//      distinct, so the result does not depend on the arrival order) and writes the sorted
+//      pair indices and, if asked for, the sorted keys.
+// Each pair is written once and read once (8 B) plus its outputs, against five or six
+// 24 B/pair passes of the global radix sort.
+constexpr int kBinSortThreads = 256;
+constexpr int kBinSortCap = 4096;          // longest list sorted in shared memory
+
+__global__ void __launch_bounds__(kTilesBlock) bin_count_kernel(
+    const float4* __restrict__ aabb, const SsbScreenRec* __restrict__ screen, int64_t total, int64_t n_per_image, int tw, int th,
+    int32_t* __restrict__ tile_count) {
+    const int64_t idx = (int64_t)blockIdx.x * kTilesBlock + threadIdx.x;
+    if (idx >= total) return;
+    const float4 bb = aabb[idx];
+    if (!(bb.z > bb.x && bb.w > bb.y)) return;
+    const float4* r = (const float4*)(screen + idx);
+    const float4 ra = r[0], rb = r[1];
+    TileSpan g; float cn[3];
+    if (!tile_setup(bb, rb, tw, th, g, cn)) return;
+    int32_t* cnt = tile_count + (idx / n_per_image) * tw * th;
+    for_each_tile(ra.x, ra.y, cn[0], cn[1], cn[2], g, [&](int x, int y) { atomicAdd(&cnt[y * tw + x], 1); });
+}
+
+// Exclusive scan of the tile counts by one block: offsets[t] (the ranges), the cursors the
+// emit pass advances (written over the counts), and M.
+__global__ void __launch_bounds__(1024) bin_scan_kernel(int32_t* __restrict__ tile_count, int64_t n_tiles, int32_t* __restrict__ offsets,
+                                                        int64_t* __restrict__ n_isects) {
+    __shared__ int64_t warp_tot[32];
+    __shared__ int64_t carry_s;
+    if (threadIdx.x == 0) carry_s = 0;
+    __syncthreads();
+    for (int64_t base = 0; base < n_tiles; base += 1024) {
+        const int64_t i = base + threadIdx.x;
+        const int64_t v = i < n_tiles ? tile_count[i] : 0;
+        int64_t inc = v;
+        for (int o = 1; o < 32; o <<= 1) {
+            int64_t t = __shfl_up_sync(0xffffffffu, inc, o);
+            if ((threadIdx.x & 31) >= o) inc += t;
+        }
+        if ((threadIdx.x & 31) == 31) warp_tot[threadIdx.x >> 5] = inc;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            int64_t w = warp_tot[threadIdx.x];
+            int64_t winc = w;
+            for (int o = 1; o < 32; o <<= 1) {
+                int64_t t = __shfl_up_sync(0xffffffffu, winc, o);
+                if (threadIdx.x >= o) winc += t;
+            }
+            warp_tot[threadIdx.x] = winc - w;
+        }
+        __syncthreads();
+        const int64_t excl = carry_s + warp_tot[threadIdx.x >> 5] + inc - v;
+        // positions are 32-bit like the flatten ids and offsets of the interface; ranges past
+        // 2^31 - 1 saturate (such a count is far beyond any capacity and is reported as an overflow)
+        const int32_t e32 = (int32_t)min(excl, (int64_t)0x7fffffff);
+        if (i < n_tiles) { offsets[i] = e32; tile_count[i] = e32; }
+        __syncthreads();
+        if (threadIdx.x == 1023) carry_s = excl + v;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *n_isects = carry_s;
+}
+
+__global__ void __launch_bounds__(kTilesBlock) bin_emit_kernel(
+    const float4* __restrict__ aabb, const float* __restrict__ depths, const SsbScreenRec* __restrict__ screen, int64_t total,
+    int64_t n_per_image, int tw, int th, int32_t* __restrict__ cursor, int64_t capacity, uint64_t* __restrict__ pairs) {
+    const int64_t idx = (int64_t)blockIdx.x * kTilesBlock + threadIdx.x;
+    if (idx >= total) return;
+    const float4 bb = aabb[idx];
+    if (!(bb.z > bb.x && bb.w > bb.y)) return;
+    const float4* r = (const float4*)(screen + idx);
+    const float4 ra = r[0], rb = r[1];
+    TileSpan g; float cn[3];
+    if (!tile_setup(bb, rb, tw, th, g, cn)) return;
+    uint32_t du = __float_as_uint(fabsf(depths[idx]));
+    if (du >> 31) du = ~du; else du ^= (1u << 31);
+    const uint64_t word = ((uint64_t)du << 32) | (uint32_t)idx;
+    int32_t* cur = cursor + (idx / n_per_image) * tw * th;
+    for_each_tile(ra.x, ra.y, cn[0], cn[1], cn[2], g, [&](int x, int y) {
+        const int32_t pos = atomicAdd(&cur[y * tw + x], 1);
+        if (pos >= 0 && pos < capacity) pairs[pos] = word;
+    });
+}
+
+// Sorting network in which every exchange puts the smaller word at the lower index (a bitonic
+// merge whose first step mirrors the upper half): positions past the list's end act as
+// +infinity without being stored, so any length is sorted in place.
+__device__ __forceinline__ void network_sort(uint64_t* a, int n, int padded) {
+    for (int lk = 1; (1 << lk) <= padded; ++lk) {
+        const int lh = lk - 1, half = 1 << lh;
+        for (int t = threadIdx.x; t < (padded >> 1); t += kBinSortThreads) {
+            const int blk = t >> lh, off = t & (half - 1);
+            const int i = (blk << lk) + off, j = (blk << lk) + (half << 1) - 1 - off;
+            if (j < n) { const uint64_t x = a[i], y = a[j]; if (y < x) { a[i] = y; a[j] = x; } }
+        }
+        __syncthreads();
+        for (int ld = lh - 1; ld >= 0; --ld) {
+            const int d = 1 << ld;
+            for (int t = threadIdx.x; t < (padded >> 1); t += kBinSortThreads) {
+                const int i = ((t >> ld) << (ld + 1)) + (t & (d - 1));
+                const int j = i + d;
+                if (j < n) { const uint64_t x = a[i], y = a[j]; if (y < x) { a[i] = y; a[j] = x; } }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kBinSortThreads) bin_sort_kernel(
+    uint64_t* __restrict__ pairs, const int32_t* __restrict__ offsets, const int64_t* __restrict__ n_isects, int64_t n_tiles,
+    int64_t capacity, int64_t* __restrict__ isect_ids, int32_t* __restrict__ flatten_ids) {
+    __shared__ uint64_t sm[kBinSortCap];
+    const int64_t tile = blockIdx.x;
+    const int64_t limit = min(*n_isects, capacity);
+    const int64_t start = min((int64_t)offsets[tile], limit);
+    const int64_t end = tile + 1 < n_tiles ? min((int64_t)offsets[tile + 1], limit) : limit;
+    const int n = (int)(end - start);
+    if (n <= 0) return;
+    int padded = 1;
+    while (padded < n) padded <<= 1;
+    uint64_t* seg = pairs + start;
+    const uint64_t tile_hi = (uint64_t)tile << 32;
+    if (n <= kBinSortCap) {
+        for (int i = threadIdx.x; i < n; i += kBinSortThreads) sm[i] = seg[i];
+        __syncthreads();
+        if (n > 1) network_sort(sm, n, padded);
+        for (int i = threadIdx.x; i < n; i += kBinSortThreads) {
+            const uint64_t v = sm[i];
+            flatten_ids[start + i] = (int32_t)(uint32_t)v;
+            if (isect_ids) isect_ids[start + i] = (int64_t)(tile_hi | (v >> 32));
+        }
+    } else {
+        // a list longer than shared memory holds: the same network in place in global memory
+        network_sort(seg, n, padded);
+        for (int i = threadIdx.x; i < n; i += kBinSortThreads) {
+            const uint64_t v = seg[i];
+            flatten_ids[start + i] = (int32_t)(uint32_t)v;
+            if (isect_ids) isect_ids[start + i] = (int64_t)(tile_hi | (v >> 32));
+        }
+    }
+}
+
 }  // namespace ssb
 
 extern "C" {
@@ -326,6 +478,20 @@ int ssb_tile_keys(const float* d_aabb, const float* d_depths, const SsbScreenRec
     return SSB_OK;
 }
 
+int64_t ssb_intersect_tiles_workspace_bytes(int64_t n_tiles_total, int64_t capacity) {
+    using namespace ssb;
+    return align_up((n_tiles_total + 1) * 4, 256) + align_up((capacity > 0 ? capacity : 1) * 8, 256);
+}
+
+int ssb_intersect_tiles(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
+                        int64_t total, int64_t n_per_image, int32_t width, int32_t height,
+                        void* d_workspace, int64_t workspace_bytes,
+                        int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                        int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream) {
+    return ssb::launch_intersect_tiles(d_aabb, d_depths, d_screen, total, n_per_image, width, height, d_workspace, workspace_bytes,
+                                       d_isect_ids, d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, nullptr);
+}
+
 int32_t ssb_tile_n_bits(int64_t n_tiles) {
     int b = 0;
     while (((uint64_t)1 << b) <= (uint64_t)n_tiles) ++b;
@@ -344,3 +510,45 @@ int ssb_tile_ranges(const int64_t* d_sorted_ids, const int64_t* d_n, int64_t cap
 }
 
 }  // extern "C"
+
+namespace ssb {
+
+// ssb_intersect_tiles with an optional event recorded between the scatter and the per-tile sort
+// (the step object times the two halves separately).
+int launch_intersect_tiles(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
+                        int64_t total, int64_t n_per_image, int32_t width, int32_t height,
+                        void* d_workspace, int64_t workspace_bytes,
+                        int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                        int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort) {
+    SSB_REQUIRE(d_aabb && d_depths && d_screen && d_workspace && d_flatten_ids && d_tile_offsets && d_n_isects, "ssb_intersect_tiles: NULL argument");
+    SSB_REQUIRE(total >= 0 && n_per_image > 0 && width > 0 && height > 0 && capacity >= 0, "ssb_intersect_tiles: bad sizes");
+    SSB_REQUIRE(total < ((int64_t)1 << 31) && capacity < ((int64_t)1 << 31), "ssb_intersect_tiles: pair indices and positions must fit int32");
+    SSB_REQUIRE(total % n_per_image == 0, "ssb_intersect_tiles: total must be a whole number of images");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int tw = (width + kTile - 1) / kTile, th = (height + kTile - 1) / kTile;
+    const int64_t n_images = total / n_per_image;
+    const int64_t n_tiles = n_images * tw * th;
+    SSB_REQUIRE(workspace_bytes >= ssb_intersect_tiles_workspace_bytes(n_tiles, capacity), "ssb_intersect_tiles: workspace too small");
+    if (total == 0) {
+        SSB_CUDA(cudaMemsetAsync(d_n_isects, 0, sizeof(int64_t), st));
+        return SSB_OK;
+    }
+    SSB_REQUIRE(n_tiles < ((int64_t)1 << 31), "ssb_intersect_tiles: too many tiles");
+    char* ws = (char*)d_workspace;
+    int32_t* cursor = (int32_t*)ws;
+    uint64_t* pairs = (uint64_t*)(ws + align_up((n_tiles + 1) * 4, 256));
+    SSB_CUDA(cudaMemsetAsync(cursor, 0, (size_t)n_tiles * 4, st));
+    bin_count_kernel<<<(unsigned)ceil_div(total, kTilesBlock), kTilesBlock, 0, st>>>((const float4*)d_aabb, d_screen, total, n_per_image, tw, th, cursor);
+    SSB_LAUNCHED("bin_count_kernel");
+    bin_scan_kernel<<<1, 1024, 0, st>>>(cursor, n_tiles, d_tile_offsets, d_n_isects);
+    SSB_LAUNCHED("bin_scan_kernel");
+    bin_emit_kernel<<<(unsigned)ceil_div(total, kTilesBlock), kTilesBlock, 0, st>>>((const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th,
+                                                                                    cursor, capacity, pairs);
+    SSB_LAUNCHED("bin_emit_kernel");
+    if (mark_before_sort) SSB_CUDA(cudaEventRecord(mark_before_sort, st));
+    bin_sort_kernel<<<(unsigned)n_tiles, kBinSortThreads, 0, st>>>(pairs, d_tile_offsets, d_n_isects, n_tiles, capacity, d_isect_ids, d_flatten_ids);
+    SSB_LAUNCHED("bin_sort_kernel");
+    return SSB_OK;
+}
+
+}  // namespace ssb

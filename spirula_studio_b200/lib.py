@@ -72,6 +72,8 @@ SIGNATURES = {
     "ssb_sort_pairs_u64": (C.c_int, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _P, _I64, _P, _P]),
     "ssb_sort_check": (C.c_int, [_P, _P]),
     "ssb_sort_pairs_u64_noalloc": (C.c_int, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _P, _P]),
+    "ssb_intersect_tiles_workspace_bytes": (_I64, [_I64, _I64]),
+    "ssb_intersect_tiles": (C.c_int, [_P, _P, _P, _I64, _I64, _I32, _I32, _P, _I64, _P, _P, _I64, _P, _P, _P]),
     "ssb_tile_n_bits": (_I32, [_I64]),
     "ssb_tile_ranges": (C.c_int, [_P, _P, _I64, _I64, _P, _P]),
     "ssb_raster_fwd": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P]),

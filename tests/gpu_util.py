@@ -70,6 +70,20 @@ def tile_keys(lib, aabb, depths, rec, total, n_per_image, W, H, capacity):
     return st, m.value, counts, cum, keys, vals, n_dev
 
 
+def intersect_tiles(lib, aabb, depths, rec, total, n_per_image, W, H, capacity, n_tiles_total, want_keys=True):
+    """The fused call: sorted keys (optional), sorted flatten ids, per-tile ranges, pair count."""
+    ws_bytes = lib.ssb_intersect_tiles_workspace_bytes(n_tiles_total, capacity)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=DEV)
+    keys = torch.full((max(capacity, 1),), -1, dtype=torch.int64, device=DEV) if want_keys else None
+    vals = torch.full((max(capacity, 1),), -1, dtype=torch.int32, device=DEV)
+    offs = torch.full((max(n_tiles_total, 1),), -7, dtype=torch.int32, device=DEV)
+    n_dev = torch.full((1,), -1, dtype=torch.int64, device=DEV)
+    L.check(lib.ssb_intersect_tiles(L.ptr(aabb), L.ptr(depths), L.ptr(rec), total, n_per_image, W, H, L.ptr(ws), ws_bytes,
+                                    L.ptr(keys) if want_keys else None, L.ptr(vals), capacity, L.ptr(offs), L.ptr(n_dev), None))
+    torch.cuda.synchronize()
+    return keys, vals, offs, int(n_dev.item())
+
+
 def sort_pairs(lib, keys, vals, n_dev, capacity, begin_bit, end_bit):
     kb, vb = torch.zeros_like(keys), torch.zeros_like(vals)
     ws_bytes = lib.ssb_sort_workspace_bytes(capacity)

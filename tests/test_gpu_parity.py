@@ -195,6 +195,54 @@ def test_tile_keys_bit_exact(lib, U, oracle, views, scale_mu):
     assert st2 == L.SSB_ERR_CAPACITY and M2 == M
 
 
+@pytest.mark.parametrize("views,scale_mu,n,w,h", [(1, -3.5, 15000, 320, 240), (2, -3.0, 15000, 320, 240), (1, -2.0, 15000, 320, 240),
+                                                  (1, -1.2, 9000, 64, 48)])
+def test_intersect_tiles_fused_bit_exact(lib, U, oracle, views, scale_mu, n, w, h):
+    """ssb_intersect_tiles against keys -> stable sort -> ranges of the oracle: same sorted keys, same sorted
+    flatten ids, same ranges, same count.  The last case has lists longer than the kernel sorts in shared
+    memory (a few tiles, thousands of large splats each)."""
+    cfg, sp, vm, K = scene(n=n, w=w, h=h, views=views, scale_mu=scale_mu)
+    W, H = cfg.width, cfg.height
+    proj = oracle.project_fwd(sp, vm, K, W, H)
+    counts, cum, keys, vals = oracle.tile_keys(proj, n, W, H)
+    tw, th = oracle.tile_grid(W, H)
+    n_tiles = tw * th * views
+    sk, sv = oracle.sort_pairs(keys, vals, 0, 32 + oracle.tile_n_bits(n_tiles))
+    offs = oracle.tile_offsets(sk, n_tiles)
+    M = int(keys.size)
+    if scale_mu > -1.5:
+        assert np.diff(np.append(offs, M)).max() > 4096
+    rec = U.pack_screen(lib, proj)
+    d_aabb, d_depths = U.dev(proj["aabb"]), U.dev(proj["depths"])
+    g_keys, g_vals, g_offs, g_M = U.intersect_tiles(lib, d_aabb, d_depths, rec, views * n, n, W, H, M + 64, n_tiles)
+    assert g_M == M
+    assert np.array_equal(g_offs.cpu().numpy().astype(np.int64), offs.astype(np.int64))
+    assert np.array_equal(g_vals.cpu().numpy()[:M], sv)
+    assert np.array_equal(g_keys.cpu().numpy()[:M], sk)
+    assert int(g_vals[M:].max()) == -1                      # nothing written past the count
+    # the keys are optional
+    _, g_vals2, _, _ = U.intersect_tiles(lib, d_aabb, d_depths, rec, views * n, n, W, H, M + 64, n_tiles, want_keys=False)
+    assert np.array_equal(g_vals2.cpu().numpy()[:M], sv)
+    # too small a capacity: the full count is still reported, what fits is a prefix of the sorted order
+    cap = max(M // 2, 1)
+    _, g_vals3, g_offs3, g_M3 = U.intersect_tiles(lib, d_aabb, d_depths, rec, views * n, n, W, H, cap, n_tiles, want_keys=False)
+    assert g_M3 == M and np.array_equal(g_offs3.cpu().numpy().astype(np.int64), offs.astype(np.int64))
+    whole = offs[np.append(offs[1:], M) <= cap]            # tiles that lie wholly below the capacity
+    if whole.size:
+        end = int(np.append(offs[1:], M)[np.append(offs[1:], M) <= cap].max())
+        assert np.array_equal(g_vals3.cpu().numpy()[:end], sv[:end])
+
+
+def test_intersect_tiles_empty(lib, U, oracle):
+    cfg, sp, vm, K = scene(n=256, views=1)
+    sp["means"][:, 2] = 50.0
+    proj = oracle.project_fwd(sp, vm, K, cfg.width, cfg.height)
+    rec = U.pack_screen(lib, proj)
+    tw, th = oracle.tile_grid(cfg.width, cfg.height)
+    _, vals, offs, M = U.intersect_tiles(lib, U.dev(proj["aabb"]), U.dev(proj["depths"]), rec, 256, 256, cfg.width, cfg.height, 16, tw * th)
+    assert M == 0 and int(offs.abs().sum()) == 0 and int(vals.max()) == -1
+
+
 def test_tile_keys_empty_and_all_culled(lib, U, oracle):
     cfg, sp, vm, K = scene(n=256, views=1)
     sp["means"][:, 2] = 50.0    # behind the camera at (0,0,3) looking down -z

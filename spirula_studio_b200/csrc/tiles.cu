@@ -72,32 +72,47 @@ __device__ __forceinline__ void ellipse_range_bound(float a, float b, float c, f
 
 struct TileSpan { int xmin, xmax, ymin, ymax; };
 
+// Tiles touched on one line of a splat's tile rectangle.  A splat is walked along its shorter
+// axis (src/kernels/tile/IntersectTile.cu:34-101): by tile rows (row_mode: line = tile y, the
+// result is the x span) or by tile columns (line = tile x, the result is the y span).
+__device__ __forceinline__ bool tile_row_mode(const TileSpan& g) { return (g.ymax - g.ymin) <= (g.xmax - g.xmin); }
+
+__device__ __forceinline__ void tile_line_span(bool row_mode, int line, float cx, float cy, float ca, float cb, float cc,
+                                               const TileSpan& g, int& lo, int& hi) {
+    const float T = (float)kTile;
+    if (row_mode) {
+        float y0 = __fsub_rn((float)(line * kTile), cy);
+        float y1 = __fadd_rn(y0, T);
+        float bx0, bx1;
+        ellipse_range_bound(ca, cb, cc, y0, y1, bx0, bx1);
+        int x0 = f2i(floorf(__fdiv_rn(__fadd_rn(bx0, cx), T)));
+        int x1 = f2i(ceilf(__fdiv_rn(__fadd_rn(bx1, cx), T)));
+        lo = clampi(x0, g.xmin, g.xmax);
+        hi = clampi(x1, g.xmin, g.xmax);
+    } else {
+        float x0 = __fsub_rn((float)(line * kTile), cx);
+        float x1 = __fadd_rn(x0, T);
+        float by0, by1;
+        ellipse_range_bound(cc, cb, ca, x0, x1, by0, by1);
+        int y0 = f2i(floorf(__fdiv_rn(__fadd_rn(by0, cy), T)));
+        int y1 = f2i(ceilf(__fdiv_rn(__fadd_rn(by1, cy), T)));
+        lo = clampi(y0, g.ymin, g.ymax);
+        hi = clampi(y1, g.ymin, g.ymax);
+    }
+}
+
 template <class F>
 __device__ __forceinline__ void for_each_tile(float cx, float cy, float ca, float cb, float cc, const TileSpan& g, F&& fn) {
-    const float T = (float)kTile;
-    if ((g.ymax - g.ymin) <= (g.xmax - g.xmin)) {
+    int lo, hi;
+    if (tile_row_mode(g)) {
         for (int y = g.ymin; y < g.ymax; ++y) {
-            float y0 = __fsub_rn((float)(y * kTile), cy);
-            float y1 = __fadd_rn(y0, T);
-            float bx0, bx1;
-            ellipse_range_bound(ca, cb, cc, y0, y1, bx0, bx1);
-            int x0 = f2i(floorf(__fdiv_rn(__fadd_rn(bx0, cx), T)));
-            int x1 = f2i(ceilf(__fdiv_rn(__fadd_rn(bx1, cx), T)));
-            x0 = clampi(x0, g.xmin, g.xmax);
-            x1 = clampi(x1, g.xmin, g.xmax);
-            for (int x = x0; x < x1; ++x) fn(x, y);
+            tile_line_span(true, y, cx, cy, ca, cb, cc, g, lo, hi);
+            for (int x = lo; x < hi; ++x) fn(x, y);
         }
     } else {
         for (int x = g.xmin; x < g.xmax; ++x) {
-            float x0 = __fsub_rn((float)(x * kTile), cx);
-            float x1 = __fadd_rn(x0, T);
-            float by0, by1;
-            ellipse_range_bound(cc, cb, ca, x0, x1, by0, by1);
-            int y0 = f2i(floorf(__fdiv_rn(__fadd_rn(by0, cy), T)));
-            int y1 = f2i(ceilf(__fdiv_rn(__fadd_rn(by1, cy), T)));
-            y0 = clampi(y0, g.ymin, g.ymax);
-            y1 = clampi(y1, g.ymin, g.ymax);
-            for (int y = y0; y < y1; ++y) fn(x, y);
+            tile_line_span(false, x, cx, cy, ca, cb, cc, g, lo, hi);
+            for (int y = lo; y < hi; ++y) fn(x, y);
         }
     }
 }
@@ -278,99 +293,206 @@ __global__ void tile_ranges_kernel(const int64_t* __restrict__ ids, const int64_
 //
 // A key is (tile id << 32 | depth bits), so the sorted array is the concatenation of the
 // tiles' lists, each ordered by (depth bits, pair index) -- equal keys keep emission order,
-// which is pair-index order.  The lists are therefore built directly:
-//   1. count the pairs of every tile (one reduction per (splat, tile) pair);
-//   2. exclusive scan of the tile counts = the per-tile ranges, and the total M;
-//   3. write every pair as (depth bits << 32 | pair index) into its tile's range, at a slot
-//      taken from the tile's cursor (arrival order, arbitrary);
-//   4. one CTA per tile sorts its range on the whole 64-bit word (all words of a tile are
-//      distinct, so the result does not depend on the arrival order) and writes the sorted
-//      pair indices and, if asked for, the sorted keys.
+// which is pair-index order.  The lists are built directly, as a two-level bucket sort:
+//   0. the range of the depth bits over the visible pairs of each image;
+//   1. count the pairs of every bin = (tile, depth bucket): kDepthBuckets buckets per tile, a
+//      monotone function of the depth bits (their offset from the image's minimum, shifted so
+//      that the image's range fills the buckets), one reduction per (splat, tile) pair;
+//   2. exclusive scan of the bin counts = the bins' ranges, every tile's range, and the total M;
+//   3. write every pair as (depth bits << 32 | pair index) into its bin, at a slot taken from
+//      the bin's cursor (arrival order, arbitrary);
+//   4. one CTA per tile orders each of its bins on the whole 64-bit word (all words of a tile are
+//      distinct, so the result does not depend on arrival order): a warp ranks a short bin by
+//      comparing every word with every other; a long bin goes through a sorting network.
+//      The sorted pair indices and, if asked for, the sorted keys are written from there.
 // Each pair is written once and read once (8 B) plus its outputs, against five or six
 // 24 B/pair passes of the global radix sort.
+//
+// Passes 1 and 3 walk the splats' tile rectangles line by line.  A thread per splat would leave
+// most lanes idle (culled splats, rectangles of different heights), so a warp pools the lines of
+// its 32 splats and hands them out one per lane.
+constexpr int kBinThreads = 256;
+constexpr int kDepthBucketBits = 5;
+constexpr int kDepthBuckets = 1 << kDepthBucketBits;
 constexpr int kBinSortThreads = 256;
-constexpr int kBinSortCap = 4096;          // longest list sorted in shared memory
+constexpr int kBinSortWarps = kBinSortThreads / 32;
+constexpr int kBinSortCap = 4096;          // longest tile list held in shared memory
+constexpr int kRankMax = 128;              // longest bin ordered by all-pairs ranking (4 words per lane)
+constexpr int64_t kRangeBytes = 4096;      // {min, max} depth words of up to 512 images
 
-__global__ void __launch_bounds__(kTilesBlock) bin_count_kernel(
-    const float4* __restrict__ aabb, const SsbScreenRec* __restrict__ screen, int64_t total, int64_t n_per_image, int tw, int th,
-    int32_t* __restrict__ tile_count) {
-    const int64_t idx = (int64_t)blockIdx.x * kTilesBlock + threadIdx.x;
-    if (idx >= total) return;
-    const float4 bb = aabb[idx];
-    if (!(bb.z > bb.x && bb.w > bb.y)) return;
-    const float4* r = (const float4*)(screen + idx);
-    const float4 ra = r[0], rb = r[1];
-    TileSpan g; float cn[3];
-    if (!tile_setup(bb, rb, tw, th, g, cn)) return;
-    int32_t* cnt = tile_count + (idx / n_per_image) * tw * th;
-    for_each_tile(ra.x, ra.y, cn[0], cn[1], cn[2], g, [&](int x, int y) { atomicAdd(&cnt[y * tw + x], 1); });
+__device__ __forceinline__ uint32_t depth_word(float depth) {
+    uint32_t du = __float_as_uint(fabsf(depth));
+    if (du >> 31) du = ~du; else du ^= (1u << 31);
+    return du;
 }
 
-// Exclusive scan of the tile counts by one block: offsets[t] (the ranges), the cursors the
-// emit pass advances (written over the counts), and M.
-__global__ void __launch_bounds__(1024) bin_scan_kernel(int32_t* __restrict__ tile_count, int64_t n_tiles, int32_t* __restrict__ offsets,
-                                                        int64_t* __restrict__ n_isects) {
-    __shared__ int64_t warp_tot[32];
-    __shared__ int64_t carry_s;
-    if (threadIdx.x == 0) carry_s = 0;
+// {min, max} of the depth words of each image's visible pairs.
+__global__ void __launch_bounds__(256) depth_range_kernel(const float4* __restrict__ aabb, const float* __restrict__ depths, int64_t total,
+                                                          int64_t n_per_image, uint32_t* __restrict__ range) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t base = (int64_t)blockIdx.x * blockDim.x; base < total; base += stride) {   // warp-uniform trip count
+        const int64_t idx = base + threadIdx.x;
+        uint32_t lo = 0xffffffffu, hi = 0u;
+        int64_t img = 0;
+        if (idx < total) {
+            img = idx / n_per_image;
+            const float4 bb = aabb[idx];
+            if (bb.z > bb.x && bb.w > bb.y) lo = hi = depth_word(depths[idx]);
+        }
+        // lanes of a warp nearly always share the image; reduce within the warp when they do
+        const int64_t img0 = __shfl_sync(0xffffffffu, img, 0);
+        if (__all_sync(0xffffffffu, img == img0 || lo > hi)) {
+            lo = __reduce_min_sync(0xffffffffu, lo);
+            hi = __reduce_max_sync(0xffffffffu, hi);
+            if ((threadIdx.x & 31) == 0 && lo <= hi) { atomicMin(&range[2 * img0], lo); atomicMax(&range[2 * img0 + 1], hi); }
+        } else if (lo <= hi) {
+            atomicMin(&range[2 * img], lo); atomicMax(&range[2 * img + 1], hi);
+        }
+    }
+}
+
+__global__ void init_range_kernel(uint32_t* range, int n_images) {
+    for (int i = threadIdx.x; i < n_images; i += blockDim.x) { range[2 * i] = 0xffffffffu; range[2 * i + 1] = 0u; }
+}
+
+__device__ __forceinline__ int depth_bucket(uint32_t du, uint32_t lo, uint32_t hi) {
+    const uint32_t span = hi - lo;
+    const int used = 32 - __clz(span);                       // bits the offsets occupy (0 when span == 0)
+    const int shift = used > kDepthBucketBits ? used - kDepthBucketBits : 0;
+    const uint32_t b = (du - lo) >> shift;
+    return (int)(b < (uint32_t)kDepthBuckets ? b : (uint32_t)kDepthBuckets - 1u);
+}
+
+// Passes 1 (EMIT = false: count) and 3 (EMIT = true: scatter).
+template <bool EMIT>
+__global__ void __launch_bounds__(kBinThreads) bin_pass_kernel(
+    const float4* __restrict__ aabb, const float* __restrict__ depths, const SsbScreenRec* __restrict__ screen, int64_t total,
+    int64_t n_per_image, int tw, int th, const uint32_t* __restrict__ range, int32_t* __restrict__ bins, int64_t capacity,
+    uint64_t* __restrict__ pairs) {
+    const int lane = threadIdx.x & 31;
+    const int64_t idx = (int64_t)blockIdx.x * kBinThreads + threadIdx.x;
+    // ---- this lane's splat
+    int lines = 0, row_mode = 0;
+    TileSpan g = {0, 0, 0, 0};
+    float cn[3] = {0.f, 0.f, 0.f}, cx = 0.f, cy = 0.f;
+    int32_t bin0 = 0;           // bin of (first tile of the image, this splat's depth bucket)
+    uint32_t du = 0;
+    if (idx < total) {
+        const float4 bb = aabb[idx];
+        if (bb.z > bb.x && bb.w > bb.y) {
+            const float4* r = (const float4*)(screen + idx);
+            const float4 ra = r[0], rb = r[1];
+            if (tile_setup(bb, rb, tw, th, g, cn)) {
+                cx = ra.x; cy = ra.y;
+                row_mode = tile_row_mode(g) ? 1 : 0;
+                lines = row_mode ? g.ymax - g.ymin : g.xmax - g.xmin;
+                const int64_t img = idx / n_per_image;
+                du = depth_word(depths[idx]);
+                bin0 = (int32_t)(img * tw * th) * kDepthBuckets + depth_bucket(du, range[2 * img], range[2 * img + 1]);
+            }
+        }
+    }
+    // ---- pool the warp's lines
+    int incl = lines;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+    const int excl = incl - lines;
+    const int all = __shfl_sync(0xffffffffu, incl, 31);
+    const uint64_t word = ((uint64_t)du << 32) | (uint32_t)idx;
+    for (int base = 0; base < all; base += 32) {
+        const int item = base + lane;
+        // owner = last lane whose first line is <= item (lanes without lines share their successor's start)
+        int j = 0;
+#pragma unroll
+        for (int step = 16; step >= 1; step >>= 1) {
+            const int cand = j + step;
+            const int e = __shfl_sync(0xffffffffu, excl, cand & 31);
+            if (cand < 32 && e <= item) j = cand;
+        }
+        const int o_excl = __shfl_sync(0xffffffffu, excl, j);
+        const int o_mode = __shfl_sync(0xffffffffu, row_mode, j);
+        TileSpan og;
+        og.xmin = __shfl_sync(0xffffffffu, g.xmin, j); og.xmax = __shfl_sync(0xffffffffu, g.xmax, j);
+        og.ymin = __shfl_sync(0xffffffffu, g.ymin, j); og.ymax = __shfl_sync(0xffffffffu, g.ymax, j);
+        const float ocx = __shfl_sync(0xffffffffu, cx, j), ocy = __shfl_sync(0xffffffffu, cy, j);
+        const float oa = __shfl_sync(0xffffffffu, cn[0], j), ob = __shfl_sync(0xffffffffu, cn[1], j), oc = __shfl_sync(0xffffffffu, cn[2], j);
+        const int32_t obin = __shfl_sync(0xffffffffu, bin0, j);
+        const uint64_t oword = __shfl_sync(0xffffffffu, word, j);
+        if (item < all) {
+            const int line = (o_mode ? og.ymin : og.xmin) + (item - o_excl);
+            int lo, hi;
+            tile_line_span(o_mode != 0, line, ocx, ocy, oa, ob, oc, og, lo, hi);
+            for (int k = lo; k < hi; ++k) {
+                const int tile = o_mode ? line * tw + k : k * tw + line;
+                int32_t* bin = bins + obin + tile * kDepthBuckets;
+                if (EMIT) {
+                    const int32_t pos = atomicAdd(bin, 1);
+                    if (pos >= 0 && pos < capacity) pairs[pos] = oword;
+                } else {
+                    atomicAdd(bin, 1);
+                }
+            }
+        }
+    }
+}
+
+// Exclusive scan of the bin counts, in place, in three launches over 2048-entry chunks.
+__global__ void __launch_bounds__(kTilesBlock) bins_chunk_sum_kernel(const int32_t* __restrict__ bins, int64_t n_bins, int32_t* __restrict__ chunk_sums) {
+    __shared__ int warp_tot[kTilesBlock / 32];
+    const int64_t base = (int64_t)blockIdx.x * kScanChunk;
+    int local = 0;
+    for (int it = 0; it < kScanItems; ++it) {
+        const int64_t i = base + it * kTilesBlock + threadIdx.x;
+        if (i < n_bins) local += bins[i];
+    }
+    local = __reduce_add_sync(0xffffffffu, local);
+    if ((threadIdx.x & 31) == 0) warp_tot[threadIdx.x >> 5] = local;
     __syncthreads();
-    for (int64_t base = 0; base < n_tiles; base += 1024) {
-        const int64_t i = base + threadIdx.x;
-        const int64_t v = i < n_tiles ? tile_count[i] : 0;
-        int64_t inc = v;
+    if (threadIdx.x == 0) {
+        int s = 0;
+        for (int w = 0; w < kTilesBlock / 32; ++w) s += warp_tot[w];
+        chunk_sums[blockIdx.x] = s;
+    }
+}
+
+// bins[i] <- position of bin i's first pair (the cursor the scatter advances);
+// offsets[t] <- position of tile t's first pair.
+__global__ void __launch_bounds__(kTilesBlock) bins_apply_kernel(int32_t* __restrict__ bins, int64_t n_bins, const int32_t* __restrict__ chunk_offsets,
+                                                                 int32_t* __restrict__ offsets) {
+    __shared__ int warp_tot[kTilesBlock / 32];
+    __shared__ int carry_s;
+    if (threadIdx.x == 0) carry_s = chunk_offsets[blockIdx.x];
+    __syncthreads();
+    const int64_t base = (int64_t)blockIdx.x * kScanChunk;
+    for (int it = 0; it < kScanItems; ++it) {
+        const int64_t i = base + it * kTilesBlock + threadIdx.x;
+        const int v = i < n_bins ? bins[i] : 0;
+        int inc = v;
         for (int o = 1; o < 32; o <<= 1) {
-            int64_t t = __shfl_up_sync(0xffffffffu, inc, o);
+            const int t = __shfl_up_sync(0xffffffffu, inc, o);
             if ((threadIdx.x & 31) >= o) inc += t;
         }
         if ((threadIdx.x & 31) == 31) warp_tot[threadIdx.x >> 5] = inc;
         __syncthreads();
-        if (threadIdx.x < 32) {
-            int64_t w = warp_tot[threadIdx.x];
-            int64_t winc = w;
-            for (int o = 1; o < 32; o <<= 1) {
-                int64_t t = __shfl_up_sync(0xffffffffu, winc, o);
-                if (threadIdx.x >= o) winc += t;
-            }
-            warp_tot[threadIdx.x] = winc - w;
+        int woff = 0;
+        for (int w = 0; w < (int)(threadIdx.x >> 5); ++w) woff += warp_tot[w];
+        const int excl = carry_s + woff + inc - v;
+        if (i < n_bins) {
+            bins[i] = excl;
+            if ((i & (kDepthBuckets - 1)) == 0) offsets[i >> kDepthBucketBits] = excl;
         }
         __syncthreads();
-        const int64_t excl = carry_s + warp_tot[threadIdx.x >> 5] + inc - v;
-        // positions are 32-bit like the flatten ids and offsets of the interface; ranges past
-        // 2^31 - 1 saturate (such a count is far beyond any capacity and is reported as an overflow)
-        const int32_t e32 = (int32_t)min(excl, (int64_t)0x7fffffff);
-        if (i < n_tiles) { offsets[i] = e32; tile_count[i] = e32; }
-        __syncthreads();
-        if (threadIdx.x == 1023) carry_s = excl + v;
+        if (threadIdx.x == kTilesBlock - 1) carry_s = excl + v;
         __syncthreads();
     }
-    if (threadIdx.x == 0) *n_isects = carry_s;
-}
-
-__global__ void __launch_bounds__(kTilesBlock) bin_emit_kernel(
-    const float4* __restrict__ aabb, const float* __restrict__ depths, const SsbScreenRec* __restrict__ screen, int64_t total,
-    int64_t n_per_image, int tw, int th, int32_t* __restrict__ cursor, int64_t capacity, uint64_t* __restrict__ pairs) {
-    const int64_t idx = (int64_t)blockIdx.x * kTilesBlock + threadIdx.x;
-    if (idx >= total) return;
-    const float4 bb = aabb[idx];
-    if (!(bb.z > bb.x && bb.w > bb.y)) return;
-    const float4* r = (const float4*)(screen + idx);
-    const float4 ra = r[0], rb = r[1];
-    TileSpan g; float cn[3];
-    if (!tile_setup(bb, rb, tw, th, g, cn)) return;
-    uint32_t du = __float_as_uint(fabsf(depths[idx]));
-    if (du >> 31) du = ~du; else du ^= (1u << 31);
-    const uint64_t word = ((uint64_t)du << 32) | (uint32_t)idx;
-    int32_t* cur = cursor + (idx / n_per_image) * tw * th;
-    for_each_tile(ra.x, ra.y, cn[0], cn[1], cn[2], g, [&](int x, int y) {
-        const int32_t pos = atomicAdd(&cur[y * tw + x], 1);
-        if (pos >= 0 && pos < capacity) pairs[pos] = word;
-    });
 }
 
 // Sorting network in which every exchange puts the smaller word at the lower index (a bitonic
 // merge whose first step mirrors the upper half): positions past the list's end act as
-// +infinity without being stored, so any length is sorted in place.
-__device__ __forceinline__ void network_sort(uint64_t* a, int n, int padded) {
+// +infinity without being stored, so any length is sorted in place.  Whole CTA.
+__device__ __forceinline__ void network_sort(uint64_t* a, int n) {
+    int padded = 1;
+    while (padded < n) padded <<= 1;
     for (int lk = 1; (1 << lk) <= padded; ++lk) {
         const int lh = lk - 1, half = 1 << lh;
         for (int t = threadIdx.x; t < (padded >> 1); t += kBinSortThreads) {
@@ -391,37 +513,66 @@ __device__ __forceinline__ void network_sort(uint64_t* a, int n, int padded) {
     }
 }
 
+// A warp orders a bin of at most kRankMax distinct words in place: each lane holds up to four
+// words and counts, for each, the words of the bin that are smaller.
+__device__ __forceinline__ void rank_sort_warp(uint64_t* a, int n, int lane) {
+    constexpr int E = kRankMax / 32;
+    uint64_t x[E];
+    int rank[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) { const int i = e * 32 + lane; x[e] = i < n ? a[i] : ~0ull; rank[e] = 0; }
+    for (int t = 0; t < n; ++t) {
+        const uint64_t v = a[t];
+#pragma unroll
+        for (int e = 0; e < E; ++e) rank[e] += v < x[e] ? 1 : 0;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int e = 0; e < E; ++e) if (e * 32 + lane < n) a[rank[e]] = x[e];
+    __syncwarp();
+}
+
 __global__ void __launch_bounds__(kBinSortThreads) bin_sort_kernel(
-    uint64_t* __restrict__ pairs, const int32_t* __restrict__ offsets, const int64_t* __restrict__ n_isects, int64_t n_tiles,
+    uint64_t* __restrict__ pairs, const int32_t* __restrict__ bin_ends, const int64_t* __restrict__ n_isects, int64_t n_tiles,
     int64_t capacity, int64_t* __restrict__ isect_ids, int32_t* __restrict__ flatten_ids) {
     __shared__ uint64_t sm[kBinSortCap];
+    __shared__ int edge[kDepthBuckets + 1];       // bin boundaries relative to the tile's first pair
     const int64_t tile = blockIdx.x;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     const int64_t limit = min(*n_isects, capacity);
-    const int64_t start = min((int64_t)offsets[tile], limit);
-    const int64_t end = tile + 1 < n_tiles ? min((int64_t)offsets[tile + 1], limit) : limit;
-    const int n = (int)(end - start);
+    // after the scatter a bin's cursor stands at its end, which is the next bin's start
+    const int64_t first_bin = tile * kDepthBuckets;
+    const int64_t start = first_bin == 0 ? 0 : min((int64_t)bin_ends[first_bin - 1], limit);
+    if (threadIdx.x <= kDepthBuckets) {
+        const int64_t b = first_bin + threadIdx.x - 1;
+        edge[threadIdx.x] = (int)((b < 0 ? 0 : min((int64_t)bin_ends[b], limit)) - start);
+    }
+    __syncthreads();
+    const int n = edge[kDepthBuckets];
     if (n <= 0) return;
-    int padded = 1;
-    while (padded < n) padded <<= 1;
     uint64_t* seg = pairs + start;
-    const uint64_t tile_hi = (uint64_t)tile << 32;
+    uint64_t* a = seg;
     if (n <= kBinSortCap) {
         for (int i = threadIdx.x; i < n; i += kBinSortThreads) sm[i] = seg[i];
+        a = sm;
         __syncthreads();
-        if (n > 1) network_sort(sm, n, padded);
-        for (int i = threadIdx.x; i < n; i += kBinSortThreads) {
-            const uint64_t v = sm[i];
-            flatten_ids[start + i] = (int32_t)(uint32_t)v;
-            if (isect_ids) isect_ids[start + i] = (int64_t)(tile_hi | (v >> 32));
-        }
-    } else {
-        // a list longer than shared memory holds: the same network in place in global memory
-        network_sort(seg, n, padded);
-        for (int i = threadIdx.x; i < n; i += kBinSortThreads) {
-            const uint64_t v = seg[i];
-            flatten_ids[start + i] = (int32_t)(uint32_t)v;
-            if (isect_ids) isect_ids[start + i] = (int64_t)(tile_hi | (v >> 32));
-        }
+    }
+    // long bins: the whole CTA, one after another (the loop bounds are the same for every thread)
+    for (int b = 0; b < kDepthBuckets; ++b) {
+        const int len = edge[b + 1] - edge[b];
+        if (len > kRankMax) network_sort(a + edge[b], len);
+    }
+    // short bins: one warp each
+    for (int b = w; b < kDepthBuckets; b += kBinSortWarps) {
+        const int len = edge[b + 1] - edge[b];
+        if (len > 1 && len <= kRankMax) rank_sort_warp(a + edge[b], len, lane);
+    }
+    __syncthreads();
+    const uint64_t tile_hi = (uint64_t)tile << 32;
+    for (int i = threadIdx.x; i < n; i += kBinSortThreads) {
+        const uint64_t v = a[i];
+        flatten_ids[start + i] = (int32_t)(uint32_t)v;
+        if (isect_ids) isect_ids[start + i] = (int64_t)(tile_hi | (v >> 32));
     }
 }
 
@@ -480,7 +631,9 @@ int ssb_tile_keys(const float* d_aabb, const float* d_depths, const SsbScreenRec
 
 int64_t ssb_intersect_tiles_workspace_bytes(int64_t n_tiles_total, int64_t capacity) {
     using namespace ssb;
-    return align_up((n_tiles_total + 1) * 4, 256) + align_up((capacity > 0 ? capacity : 1) * 8, 256);
+    const int64_t n_bins = (n_tiles_total > 0 ? n_tiles_total : 1) * kDepthBuckets;
+    // bin counters/cursors, chunk sums of their scan, per-image depth range, the unsorted words
+    return align_up(n_bins * 4, 256) + align_up(ceil_div(n_bins, kScanChunk) * 4, 256) + kRangeBytes + align_up((capacity > 0 ? capacity : 1) * 8, 256);
 }
 
 int ssb_intersect_tiles(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
@@ -533,20 +686,33 @@ int launch_intersect_tiles(const float* d_aabb, const float* d_depths, const Ssb
         SSB_CUDA(cudaMemsetAsync(d_n_isects, 0, sizeof(int64_t), st));
         return SSB_OK;
     }
-    SSB_REQUIRE(n_tiles < ((int64_t)1 << 31), "ssb_intersect_tiles: too many tiles");
+    const int64_t n_bins = n_tiles * kDepthBuckets;
+    SSB_REQUIRE(n_bins < ((int64_t)1 << 31), "ssb_intersect_tiles: too many tiles");
+    SSB_REQUIRE(n_images * 8 <= kRangeBytes, "ssb_intersect_tiles: at most 512 images per call");
+    const int64_t chunks = ceil_div(n_bins, kScanChunk);
     char* ws = (char*)d_workspace;
-    int32_t* cursor = (int32_t*)ws;
-    uint64_t* pairs = (uint64_t*)(ws + align_up((n_tiles + 1) * 4, 256));
-    SSB_CUDA(cudaMemsetAsync(cursor, 0, (size_t)n_tiles * 4, st));
-    bin_count_kernel<<<(unsigned)ceil_div(total, kTilesBlock), kTilesBlock, 0, st>>>((const float4*)d_aabb, d_screen, total, n_per_image, tw, th, cursor);
-    SSB_LAUNCHED("bin_count_kernel");
-    bin_scan_kernel<<<1, 1024, 0, st>>>(cursor, n_tiles, d_tile_offsets, d_n_isects);
-    SSB_LAUNCHED("bin_scan_kernel");
-    bin_emit_kernel<<<(unsigned)ceil_div(total, kTilesBlock), kTilesBlock, 0, st>>>((const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th,
-                                                                                    cursor, capacity, pairs);
-    SSB_LAUNCHED("bin_emit_kernel");
+    int32_t* bins = (int32_t*)ws;
+    int32_t* chunk_sums = (int32_t*)(ws + align_up(n_bins * 4, 256));
+    uint32_t* range = (uint32_t*)((char*)chunk_sums + align_up(chunks * 4, 256));
+    uint64_t* pairs = (uint64_t*)((char*)range + kRangeBytes);
+    SSB_CUDA(cudaMemsetAsync(bins, 0, (size_t)n_bins * 4, st));
+    init_range_kernel<<<1, 512, 0, st>>>(range, (int)n_images);
+    SSB_LAUNCHED("init_range_kernel");
+    depth_range_kernel<<<(unsigned)(ceil_div(total, 256) < 148 * 8 ? ceil_div(total, 256) : 148 * 8), 256, 0, st>>>((const float4*)d_aabb, d_depths, total, n_per_image, range);
+    SSB_LAUNCHED("depth_range_kernel");
+    const unsigned pass_grid = (unsigned)ceil_div(total, kBinThreads);
+    bin_pass_kernel<false><<<pass_grid, kBinThreads, 0, st>>>((const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th, range, bins, capacity, nullptr);
+    SSB_LAUNCHED("bin_pass_kernel<count>");
+    bins_chunk_sum_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(bins, n_bins, chunk_sums);
+    SSB_LAUNCHED("bins_chunk_sum_kernel");
+    chunk_scan_kernel<<<1, 1024, 0, st>>>(chunk_sums, (int)chunks, d_n_isects);
+    SSB_LAUNCHED("chunk_scan_kernel");
+    bins_apply_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(bins, n_bins, chunk_sums, d_tile_offsets);
+    SSB_LAUNCHED("bins_apply_kernel");
+    bin_pass_kernel<true><<<pass_grid, kBinThreads, 0, st>>>((const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th, range, bins, capacity, pairs);
+    SSB_LAUNCHED("bin_pass_kernel<scatter>");
     if (mark_before_sort) SSB_CUDA(cudaEventRecord(mark_before_sort, st));
-    bin_sort_kernel<<<(unsigned)n_tiles, kBinSortThreads, 0, st>>>(pairs, d_tile_offsets, d_n_isects, n_tiles, capacity, d_isect_ids, d_flatten_ids);
+    bin_sort_kernel<<<(unsigned)n_tiles, kBinSortThreads, 0, st>>>(pairs, bins, d_n_isects, n_tiles, capacity, d_isect_ids, d_flatten_ids);
     SSB_LAUNCHED("bin_sort_kernel");
     return SSB_OK;
 }

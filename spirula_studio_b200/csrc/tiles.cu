@@ -326,33 +326,37 @@ __device__ __forceinline__ uint32_t depth_word(float depth) {
     return du;
 }
 
-// {min, max} of the depth words of each image's visible pairs.
+// Range of the depth words of each image's visible pairs, kept as {~min, max} so that zeroed
+// memory means "none yet" and both ends grow with atomicMax.  A block takes a contiguous span of
+// pairs (one image except where two meet), reduces in registers and shared memory and issues two atomics.
 __global__ void __launch_bounds__(256) depth_range_kernel(const float4* __restrict__ aabb, const float* __restrict__ depths, int64_t total,
                                                           int64_t n_per_image, uint32_t* __restrict__ range) {
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t base = (int64_t)blockIdx.x * blockDim.x; base < total; base += stride) {   // warp-uniform trip count
-        const int64_t idx = base + threadIdx.x;
-        uint32_t lo = 0xffffffffu, hi = 0u;
-        int64_t img = 0;
-        if (idx < total) {
-            img = idx / n_per_image;
+    __shared__ uint32_t s_nlo[8], s_hi[8];
+    const int64_t span = (int64_t)gridDim.x * 256;
+    const int64_t per_block = (total + span - 1) / span * 256;
+    const int64_t begin = (int64_t)blockIdx.x * per_block, end = min(total, begin + per_block);
+    if (begin >= end) return;
+    const int64_t img_first = begin / n_per_image, img_last = (end - 1) / n_per_image;
+    for (int64_t img = img_first; img <= img_last; ++img) {
+        const int64_t lo_i = max(begin, img * n_per_image), hi_i = min(end, (img + 1) * n_per_image);
+        uint32_t nlo = 0u, hi = 0u;          // ~min and max of what this thread saw
+        for (int64_t idx = lo_i + threadIdx.x; idx < hi_i; idx += 256) {
             const float4 bb = aabb[idx];
-            if (bb.z > bb.x && bb.w > bb.y) lo = hi = depth_word(depths[idx]);
+            if (bb.z > bb.x && bb.w > bb.y) {
+                const uint32_t du = depth_word(depths[idx]);
+                nlo = max(nlo, ~du); hi = max(hi, du);
+            }
         }
-        // lanes of a warp nearly always share the image; reduce within the warp when they do
-        const int64_t img0 = __shfl_sync(0xffffffffu, img, 0);
-        if (__all_sync(0xffffffffu, img == img0 || lo > hi)) {
-            lo = __reduce_min_sync(0xffffffffu, lo);
-            hi = __reduce_max_sync(0xffffffffu, hi);
-            if ((threadIdx.x & 31) == 0 && lo <= hi) { atomicMin(&range[2 * img0], lo); atomicMax(&range[2 * img0 + 1], hi); }
-        } else if (lo <= hi) {
-            atomicMin(&range[2 * img], lo); atomicMax(&range[2 * img + 1], hi);
+        nlo = __reduce_max_sync(0xffffffffu, nlo);
+        hi = __reduce_max_sync(0xffffffffu, hi);
+        if ((threadIdx.x & 31) == 0) { s_nlo[threadIdx.x >> 5] = nlo; s_hi[threadIdx.x >> 5] = hi; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < 8; ++w) { nlo = max(nlo, s_nlo[w]); hi = max(hi, s_hi[w]); }
+            if (nlo | hi) { atomicMax(&range[2 * img], nlo); atomicMax(&range[2 * img + 1], hi); }
         }
+        __syncthreads();
     }
-}
-
-__global__ void init_range_kernel(uint32_t* range, int n_images) {
-    for (int i = threadIdx.x; i < n_images; i += blockDim.x) { range[2 * i] = 0xffffffffu; range[2 * i + 1] = 0u; }
 }
 
 __device__ __forceinline__ int depth_bucket(uint32_t du, uint32_t lo, uint32_t hi) {
@@ -388,7 +392,7 @@ __global__ void __launch_bounds__(kBinThreads) bin_pass_kernel(
                 lines = row_mode ? g.ymax - g.ymin : g.xmax - g.xmin;
                 const int64_t img = idx / n_per_image;
                 du = depth_word(depths[idx]);
-                bin0 = (int32_t)(img * tw * th) * kDepthBuckets + depth_bucket(du, range[2 * img], range[2 * img + 1]);
+                bin0 = (int32_t)(img * tw * th) * kDepthBuckets + depth_bucket(du, ~range[2 * img], range[2 * img + 1]);
             }
         }
     }
@@ -422,15 +426,20 @@ __global__ void __launch_bounds__(kBinThreads) bin_pass_kernel(
             const int line = (o_mode ? og.ymin : og.xmin) + (item - o_excl);
             int lo, hi;
             tile_line_span(o_mode != 0, line, ocx, ocy, oa, ob, oc, og, lo, hi);
-            for (int k = lo; k < hi; ++k) {
-                const int tile = o_mode ? line * tw + k : k * tw + line;
-                int32_t* bin = bins + obin + tile * kDepthBuckets;
-                if (EMIT) {
-                    const int32_t pos = atomicAdd(bin, 1);
-                    if (pos >= 0 && pos < capacity) pairs[pos] = oword;
-                } else {
-                    atomicAdd(bin, 1);
+            // tiles of a line are neighbours: along x their bins are kDepthBuckets apart, along y a whole tile row
+            int32_t* bin = bins + obin + (o_mode ? line * tw + lo : lo * tw + line) * kDepthBuckets;
+            const int step = (o_mode ? 1 : tw) * kDepthBuckets;
+            if (EMIT) {
+                for (int k = lo; k < hi; k += 4) {       // up to four slot requests in flight before the first store
+                    int32_t pos[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) pos[u] = k + u < hi ? atomicAdd(bin + u * step, 1) : -1;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) if (pos[u] >= 0 && pos[u] < capacity) pairs[pos[u]] = oword;
+                    bin += 4 * step;
                 }
+            } else {
+                for (int k = lo; k < hi; ++k, bin += step) atomicAdd(bin, 1);
             }
         }
     }
@@ -513,10 +522,10 @@ __device__ __forceinline__ void network_sort(uint64_t* a, int n) {
     }
 }
 
-// A warp orders a bin of at most kRankMax distinct words in place: each lane holds up to four
-// words and counts, for each, the words of the bin that are smaller.
+// A warp orders a bin of at most 32 * E distinct words in place: each lane holds up to E words
+// and counts, for each, the words of the bin that are smaller.
+template <int E>
 __device__ __forceinline__ void rank_sort_warp(uint64_t* a, int n, int lane) {
-    constexpr int E = kRankMax / 32;
     uint64_t x[E];
     int rank[E];
 #pragma unroll
@@ -565,7 +574,10 @@ __global__ void __launch_bounds__(kBinSortThreads) bin_sort_kernel(
     // short bins: one warp each
     for (int b = w; b < kDepthBuckets; b += kBinSortWarps) {
         const int len = edge[b + 1] - edge[b];
-        if (len > 1 && len <= kRankMax) rank_sort_warp(a + edge[b], len, lane);
+        if (len <= 1 || len > kRankMax) continue;
+        if (len <= 32) rank_sort_warp<1>(a + edge[b], len, lane);
+        else if (len <= 64) rank_sort_warp<2>(a + edge[b], len, lane);
+        else rank_sort_warp<kRankMax / 32>(a + edge[b], len, lane);
     }
     __syncthreads();
     const uint64_t tile_hi = (uint64_t)tile << 32;
@@ -691,13 +703,11 @@ int launch_intersect_tiles(const float* d_aabb, const float* d_depths, const Ssb
     SSB_REQUIRE(n_images * 8 <= kRangeBytes, "ssb_intersect_tiles: at most 512 images per call");
     const int64_t chunks = ceil_div(n_bins, kScanChunk);
     char* ws = (char*)d_workspace;
-    int32_t* bins = (int32_t*)ws;
-    int32_t* chunk_sums = (int32_t*)(ws + align_up(n_bins * 4, 256));
-    uint32_t* range = (uint32_t*)((char*)chunk_sums + align_up(chunks * 4, 256));
-    uint64_t* pairs = (uint64_t*)((char*)range + kRangeBytes);
-    SSB_CUDA(cudaMemsetAsync(bins, 0, (size_t)n_bins * 4, st));
-    init_range_kernel<<<1, 512, 0, st>>>(range, (int)n_images);
-    SSB_LAUNCHED("init_range_kernel");
+    uint32_t* range = (uint32_t*)ws;
+    int32_t* bins = (int32_t*)(ws + kRangeBytes);
+    int32_t* chunk_sums = (int32_t*)((char*)bins + align_up(n_bins * 4, 256));
+    uint64_t* pairs = (uint64_t*)((char*)chunk_sums + align_up(chunks * 4, 256));
+    SSB_CUDA(cudaMemsetAsync(ws, 0, (size_t)(kRangeBytes + n_bins * 4), st));     // depth ranges and bin counters
     depth_range_kernel<<<(unsigned)(ceil_div(total, 256) < 148 * 8 ? ceil_div(total, 256) : 148 * 8), 256, 0, st>>>((const float4*)d_aabb, d_depths, total, n_per_image, range);
     SSB_LAUNCHED("depth_range_kernel");
     const unsigned pass_grid = (unsigned)ceil_div(total, kBinThreads);

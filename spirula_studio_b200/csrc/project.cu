@@ -247,25 +247,46 @@ __device__ __forceinline__ void sh_basis(float x, float y, float z, float b[kNum
 
 // Loads the block's SH span into shared memory as fp32 (decoding packed codes).
 // A full block's span starts on a 16-byte boundary in every format (128 * 45 cells), so it is
-// moved with 16-byte loads: 4 floats, or 8 sixteen-bit / 16 eight-bit codes that share one
-// bounds entry whenever the bounds stride is a multiple of the vector's cell count.
+// brought in with 16-byte asynchronous copies (global -> shared without passing through
+// registers, all of a thread's copies in flight at once): fp32 coefficients straight into
+// sh_s, packed codes into raw_s, from where they are decoded 8 (16-bit) or 16 (8-bit) at a
+// time -- the codes of one vector share a bounds entry whenever the bounds stride is a
+// multiple of the vector's cell count.  Register-staged 16-byte loads were measured slower
+// than 4-byte ones here; the asynchronous copies are a quarter faster than either.
+// Partial blocks and unaligned arrays take 4-byte loads.
+__device__ __forceinline__ void async_copy_span(void* smem_dst, const void* gmem_src, int n_vec16) {
+    const uint32_t sdst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const uint4* src = (const uint4*)gmem_src;
+    for (int v = threadIdx.x; v < n_vec16; v += kProjBlock)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sdst + 16u * (uint32_t)v), "l"(src + v) : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void async_copy_wait() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+constexpr int kShRawBytes = kProjBlock * kShPerSplat * 2;   // a block's 16-bit codes
+
 __device__ __forceinline__ void stage_sh(
-    float* sh_s, const float* __restrict__ sh_f32, const void* __restrict__ packed, const float* __restrict__ bounds,
+    float* sh_s, unsigned char* raw_s, const float* __restrict__ sh_f32, const void* __restrict__ packed, const float* __restrict__ bounds,
     int bits, int64_t bounds_stride, int64_t first_splat, int64_t n) {
     const int64_t base = first_splat * kShPerSplat;
     const int count = (int)min((int64_t)kProjBlock, n - first_splat) * kShPerSplat;
-    // vector path: a full block and a 16-byte aligned array (scalar loads otherwise)
-    const void* arr = (bits == 8 || bits == 16) ? packed : (const void*)sh_f32;
+    const bool quant = bits == 8 || bits == 16;
+    const void* arr = quant ? packed : (const void*)sh_f32;
     const bool full = count == kProjBlock * kShPerSplat && ((uintptr_t)arr & 15) == 0;
-    if (bits == 16 && full && (bounds_stride & 7) == 0) {
-        const uint4* src = (const uint4*)((const uint16_t*)packed + base);
+    if (full && !quant) {
+        async_copy_span(sh_s, sh_f32 + base, kProjBlock * kShPerSplat / 4);
+        async_copy_wait();
+    } else if (full && bits == 16 && (bounds_stride & 7) == 0) {
+        async_copy_span(raw_s, (const uint16_t*)packed + base, kProjBlock * kShPerSplat / 8);
         const int64_t b0 = base / bounds_stride;
         const unsigned r0 = (unsigned)(base - b0 * bounds_stride), stride = (unsigned)min(bounds_stride, (int64_t)0x7fffffff);
         const float inv = 1.0f / 65535.0f;
+        async_copy_wait();
+        __syncthreads();
         for (int v = threadIdx.x; v < kProjBlock * kShPerSplat / 8; v += kProjBlock) {
-            uint4 c = src[v];
-            float2 mm = ((const float2*)bounds)[b0 + (r0 + 8u * v) / stride];
-            float d = mm.y - mm.x;
+            const uint4 c = ((const uint4*)raw_s)[v];
+            const float2 mm = ((const float2*)bounds)[b0 + (r0 + 8u * v) / stride];
+            const float d = mm.y - mm.x;
             float4 lo, hi;
             lo.x = mm.x + d * ((float)(c.x & 0xffffu) * inv); lo.y = mm.x + d * ((float)(c.x >> 16) * inv);
             lo.z = mm.x + d * ((float)(c.y & 0xffffu) * inv); lo.w = mm.x + d * ((float)(c.y >> 16) * inv);
@@ -273,15 +294,17 @@ __device__ __forceinline__ void stage_sh(
             hi.z = mm.x + d * ((float)(c.w & 0xffffu) * inv); hi.w = mm.x + d * ((float)(c.w >> 16) * inv);
             ((float4*)sh_s)[2 * v] = lo; ((float4*)sh_s)[2 * v + 1] = hi;
         }
-    } else if (bits == 8 && full && (bounds_stride & 15) == 0) {
-        const uint4* src = (const uint4*)((const uint8_t*)packed + base);
+    } else if (full && bits == 8 && (bounds_stride & 15) == 0) {
+        async_copy_span(raw_s, (const uint8_t*)packed + base, kProjBlock * kShPerSplat / 16);
         const int64_t b0 = base / bounds_stride;
         const unsigned r0 = (unsigned)(base - b0 * bounds_stride), stride = (unsigned)min(bounds_stride, (int64_t)0x7fffffff);
         const float inv = 1.0f / 255.0f;
+        async_copy_wait();
+        __syncthreads();
         for (int v = threadIdx.x; v < kProjBlock * kShPerSplat / 16; v += kProjBlock) {
-            uint4 c = src[v];
-            float2 mm = ((const float2*)bounds)[b0 + (r0 + 16u * v) / stride];
-            float d = mm.y - mm.x;
+            const uint4 c = ((const uint4*)raw_s)[v];
+            const float2 mm = ((const float2*)bounds)[b0 + (r0 + 16u * v) / stride];
+            const float d = mm.y - mm.x;
             const unsigned w[4] = {c.x, c.y, c.z, c.w};
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
@@ -291,7 +314,7 @@ __device__ __forceinline__ void stage_sh(
                 ((float4*)sh_s)[4 * v + k] = o;
             }
         }
-    } else if (bits == 8 || bits == 16) {
+    } else if (quant) {
         const float inv = bits == 8 ? (1.0f / 255.0f) : (1.0f / 65535.0f);
         for (int i = threadIdx.x; i < count; i += kProjBlock) {
             int64_t cell = base + i;
@@ -299,9 +322,6 @@ __device__ __forceinline__ void stage_sh(
             float2 mm = ((const float2*)bounds)[cell / bounds_stride];
             sh_s[i] = mm.x + (mm.y - mm.x) * (q * inv);
         }
-    } else if (full) {
-        const float4* src = (const float4*)(sh_f32 + base);
-        for (int v = threadIdx.x; v < kProjBlock * kShPerSplat / 4; v += kProjBlock) ((float4*)sh_s)[v] = src[v];
     } else {
         for (int i = threadIdx.x; i < count; i += kProjBlock) sh_s[i] = sh_f32[base + i];
     }
@@ -313,6 +333,7 @@ __global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
     int W, int H, int antialiased,
     float4* __restrict__ aabb_out, float* __restrict__ depths_out, float* __restrict__ radii, SsbScreenRec* __restrict__ screen) {
     __shared__ __align__(16) float sh_s[kProjBlock * kShPerSplat];
+    __shared__ __align__(16) unsigned char raw_s[kShRawBytes];
     const int cid = blockIdx.y;
     const int64_t first = (int64_t)blockIdx.x * kProjBlock;
     const int64_t gid = first + threadIdx.x;
@@ -325,7 +346,7 @@ __global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
     float in_op = sp.opacities[gl];
     float dc_in[3] = {sp.features_dc[3 * gl], sp.features_dc[3 * gl + 1], sp.features_dc[3 * gl + 2]};
     CamDev cam = load_cam(viewmats, intrins, cid);
-    stage_sh(sh_s, sp.features_sh, shq.packed, shq.bounds, shq.bits, shq.bounds_stride, first, n);
+    stage_sh(sh_s, raw_s, sp.features_sh, shq.packed, shq.bounds, shq.bits, shq.bounds_stride, first, n);
     __syncthreads();
     if (gid >= n) return;
     const int64_t idx = (int64_t)cid * n + gid;
@@ -435,7 +456,10 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
     // SH values in shared memory once they have been read, so one 23 KB span is enough and six
     // CTAs fit an SM.  Several views: gradients accumulate in a second span.
     __shared__ __align__(16) float sh_s[kProjBlock * kShPerSplat];
-    __shared__ __align__(16) float shg_multi[MULTI_VIEW ? kProjBlock * kShPerSplat : 1];
+    __shared__ __align__(16) float shg_multi[MULTI_VIEW ? kProjBlock * kShPerSplat : 4];
+    // packed codes land here before they are decoded; with several views the gradient span is still unused then
+    __shared__ __align__(16) unsigned char raw_single[MULTI_VIEW ? 16 : kShRawBytes];
+    unsigned char* raw_s = MULTI_VIEW ? (unsigned char*)shg_multi : raw_single;
     float* shg_s = MULTI_VIEW ? shg_multi : sh_s;
     const int64_t first = (int64_t)blockIdx.x * kProjBlock;
     const int64_t gid = first + threadIdx.x;
@@ -455,8 +479,11 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
         const float4* vr = (const float4*)(v_screen + gl);
         vr0[0] = vr[0]; vr0[1] = vr[1]; vr0[2] = vr[2];
     }
-    stage_sh(sh_s, sp.features_sh, shq.packed, shq.bounds, shq.bits, shq.bounds_stride, first, n);
-    if (MULTI_VIEW) for (int i = threadIdx.x; i < count; i += kProjBlock) shg_s[i] = 0.f;
+    stage_sh(sh_s, raw_s, sp.features_sh, shq.packed, shq.bounds, shq.bits, shq.bounds_stride, first, n);
+    if (MULTI_VIEW) {
+        __syncthreads();      // every thread is done reading the codes
+        for (int i = threadIdx.x; i < count; i += kProjBlock) shg_s[i] = 0.f;
+    }
     __syncthreads();
     bool any_view = false;
 
@@ -646,10 +673,9 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
         }
         if (accumulate) {
 #pragma unroll
-            for (int j = 0; j < 3; ++j) { gr.means[3 * gid + j] += g_mean[j]; gr.scales[3 * gid + j] += g_scale[j]; gr.features_dc[3 * gid + j] += g_dc[j]; }
-            float4 old = ((float4*)gr.quats)[gid];
-            ((float4*)gr.quats)[gid] = make_float4(old.x + g_quat[0], old.y + g_quat[1], old.z + g_quat[2], old.w + g_quat[3]);
-            gr.opacities[gid] += g_op;
+            for (int j = 0; j < 3; ++j) { atomicAdd(&gr.means[3 * gid + j], g_mean[j]); atomicAdd(&gr.scales[3 * gid + j], g_scale[j]); atomicAdd(&gr.features_dc[3 * gid + j], g_dc[j]); }
+            red_add_v4(gr.quats + 4 * gid, g_quat[0], g_quat[1], g_quat[2], g_quat[3]);
+            atomicAdd(&gr.opacities[gid], g_op);
         } else {
 #pragma unroll
             for (int j = 0; j < 3; ++j) { gr.means[3 * gid + j] = g_mean[j]; gr.scales[3 * gid + j] = g_scale[j]; gr.features_dc[3 * gid + j] = g_dc[j]; }
@@ -663,9 +689,11 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
         float4* out4 = (float4*)out;
         const float4* g4 = (const float4*)shg_s;
         if (accumulate) {
+            // every address is added to once per launch, so a reduction gives the same sum as
+            // load-add-store without waiting for the old value (measured a third faster)
             for (int v = threadIdx.x; v < kProjBlock * kShPerSplat / 4; v += kProjBlock) {
-                float4 o = out4[v], g = g4[v];
-                out4[v] = make_float4(o.x + g.x, o.y + g.y, o.z + g.z, o.w + g.w);
+                const float4 g = g4[v];
+                red_add_v4(out + 4 * v, g.x, g.y, g.z, g.w);
             }
         } else {
             for (int v = threadIdx.x; v < kProjBlock * kShPerSplat / 4; v += kProjBlock) out4[v] = g4[v];

@@ -269,6 +269,47 @@ int ssb_quant_decode(const void* d_packed, const float* d_bounds, int64_t numel,
 
 /* ---- one training iteration --------------------------------------------- */
 
+/* ---------------------------------------------------------------------------
+ * Gradient reduction and parameter distribution between the GPUs of one node, over peer memory.
+ * Reference: the sum of the sub-batches' gradients and the single optimiser pass of
+ * _engine_train_step_split_one_per_camera (src/engine/EngineTrainStep.cpp:366-427), which the reference
+ * does on one GPU.  Here the views of a batch are split between ranks (one process per GPU), each
+ * rank owns a contiguous range of splats, and per iteration it
+ *   1. ssb_peer_reduce_f32: adds the peers' partial gradients of its range to its own (plain loads
+ *      from their memory over NVLink);
+ *   2. runs ssb_adam_step / ssb_adam_step_sh_quantized on the range;
+ *   3. ssb_peer_broadcast: stores the range's updated parameters into every peer's replica.
+ * The caller must order the ranks with a barrier before 1 (all backward passes complete) and after 3
+ * (all replicas complete); no kernel waits on another GPU.
+ *
+ * A table names up to SSB_MAX_PEER_BUFFERS buffers that have the same layout on every rank
+ * (base[b][r] = rank r's copy of buffer b as mapped in THIS process) and up to
+ * SSB_MAX_PEER_SEGMENTS byte ranges of them; a segment must start on a 16-byte boundary.
+ * Buffers come from ssb_peer_alloc (a zeroed device allocation that can be exported), are exported
+ * with ssb_peer_export (a 64-byte CUDA IPC handle to send to the other processes) and mapped there
+ * with ssb_peer_open / unmapped with ssb_peer_close. */
+enum { SSB_MAX_PEERS = 8, SSB_MAX_PEER_BUFFERS = 4, SSB_MAX_PEER_SEGMENTS = 12, SSB_PEER_HANDLE_BYTES = 64 };
+typedef struct SsbPeerSegment {
+    int32_t buffer;
+    int32_t pad;
+    int64_t offset_bytes;
+    int64_t bytes;
+} SsbPeerSegment;
+typedef struct SsbPeerTable {
+    int32_t world, self, n_segments, pad;
+    void* base[SSB_MAX_PEER_BUFFERS][SSB_MAX_PEERS];
+    SsbPeerSegment seg[SSB_MAX_PEER_SEGMENTS];
+} SsbPeerTable;
+int ssb_peer_alloc(int64_t bytes, void** d_ptr);
+int ssb_peer_free(void* d_ptr);
+int ssb_peer_export(const void* d_ptr, unsigned char handle[SSB_PEER_HANDLE_BYTES]);
+int ssb_peer_open(const unsigned char handle[SSB_PEER_HANDLE_BYTES], void** d_ptr);
+int ssb_peer_close(void* d_ptr);
+/* own[segment] += sum over the other ranks of theirs[segment]; fp32 data. */
+int ssb_peer_reduce_f32(const SsbPeerTable* table, void* stream);
+/* theirs[segment] = own[segment] for every other rank; any data. */
+int ssb_peer_broadcast(const SsbPeerTable* table, void* stream);
+
 /* Owns every intermediate buffer of an iteration (the reference keeps them in
  * its process-global DevicePool, src/core/Tensor.h:151-351) and runs, per view,
  * projection -> keys -> sort -> ranges -> raster -> loss -> raster bwd ->

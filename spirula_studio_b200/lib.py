@@ -75,6 +75,13 @@ SIGNATURES = {
     "ssb_intersect_tiles_workspace_bytes": (_I64, [_I64, _I64]),
     "ssb_intersect_tiles": (C.c_int, [_P, _P, _P, _I64, _I64, _I32, _I32, _P, _I64, _P, _P, _I64, _P, _P, _P]),
     "ssb_tile_n_bits": (_I32, [_I64]),
+    "ssb_peer_alloc": (C.c_int, [_I64, _P]),
+    "ssb_peer_free": (C.c_int, [_P]),
+    "ssb_peer_export": (C.c_int, [_P, _P]),
+    "ssb_peer_open": (C.c_int, [_P, _P]),
+    "ssb_peer_close": (C.c_int, [_P]),
+    "ssb_peer_reduce_f32": (C.c_int, [_P, _P]),
+    "ssb_peer_broadcast": (C.c_int, [_P, _P]),
     "ssb_tile_ranges": (C.c_int, [_P, _P, _I64, _I64, _P, _P]),
     "ssb_raster_fwd": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P]),
     "ssb_raster_bwd": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _P]),
@@ -144,6 +151,42 @@ def shq_struct(packed=None, bounds=None, bits=32, bounds_stride=256):
     q.reserved = 0
     q.bounds_stride = bounds_stride
     return q
+
+
+MAX_PEERS, MAX_PEER_BUFFERS, MAX_PEER_SEGMENTS, PEER_HANDLE_BYTES = 8, 4, 12, 64
+
+
+class SsbPeerSegment(C.Structure):
+    _fields_ = [("buffer", C.c_int32), ("pad", C.c_int32), ("offset_bytes", C.c_int64), ("bytes", C.c_int64)]
+
+
+class SsbPeerTable(C.Structure):
+    _fields_ = [("world", C.c_int32), ("self", C.c_int32), ("n_segments", C.c_int32), ("pad", C.c_int32),
+                ("base", (C.c_void_p * MAX_PEERS) * MAX_PEER_BUFFERS), ("seg", SsbPeerSegment * MAX_PEER_SEGMENTS)]
+
+
+def peer_table(world, rank, bases, segments):
+    """bases[b][r] = device address of rank r's copy of buffer b; segments = [(buffer, offset_bytes, bytes), ...]."""
+    t = SsbPeerTable()
+    t.world, t.self, t.n_segments = world, rank, len(segments)
+    for b, per_rank in enumerate(bases):
+        for r, addr in enumerate(per_rank):
+            t.base[b][r] = addr
+    for i, (b, off, nbytes) in enumerate(segments):
+        t.seg[i].buffer, t.seg[i].offset_bytes, t.seg[i].bytes = b, off, nbytes
+    return t
+
+
+class _DevicePtr:
+    """Wraps a raw device address so torch can view it (the allocation stays owned by the caller)."""
+    def __init__(self, address, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (address, False), "version": 3}
+
+
+def device_bytes_tensor(address, nbytes, device):
+    """uint8 torch tensor over `nbytes` of device memory at `address`."""
+    import torch
+    return torch.as_tensor(_DevicePtr(address, nbytes), device=device)
 
 
 def cameras_struct(viewmats, intrins, width, height, model=CAMERA_PINHOLE, antialiased=0, count=None):

@@ -3,9 +3,16 @@
 Mirrors the reference's multi-view step (src/engine/EngineTrainStep.cpp:287-437):
 each view is rendered and back-propagated on its own, per-splat gradients are
 summed over the views, and ONE optimiser pass runs with grad_scale = 1 / views.
-With several processes the views of a batch are split between ranks, the
-gradient buffer is summed with an NCCL all-reduce, and every rank applies the
-same update to its replica of the parameters.
+With several processes (one per GPU) the views of a batch are split between
+ranks and every rank keeps a replica of the parameters.  Gradients are combined
+in one of two ways:
+  "peer" (default): each rank owns a contiguous range of splats; it adds its
+      peers' partial gradients of that range to its own with loads from their
+      memory over NVLink (ssb_peer_reduce_f32), runs Adam on the range, and
+      stores the updated parameters into every replica (ssb_peer_broadcast).
+      Two stream-ordered barriers per iteration keep the ranks in step.
+  "nccl": one NCCL all-reduce of the whole gradient buffer, then every rank
+      applies the same Adam update to all parameters.
 
 torch supplies device memory, streams and torch.distributed; all arithmetic is
 done by libssb_b200 through its C ABI.
@@ -42,19 +49,25 @@ def _flat_views(flat, n, attrs=_ATTRS):
 
 class Trainer:
     def __init__(self, cfg: SceneConfig, splats: dict, device="cuda:0", isect_capacity=0, w_l1=0.8, w_ssim=0.2,
-                 process_group=None, world_size=1, rank=0):
+                 process_group=None, world_size=1, rank=0, grad_sync="peer"):
         self.lib = L.load()
         self.cfg = cfg
         self.device = torch.device(device)
         self.n = int(cfg.n_splats)
         self.world_size, self.rank, self.pg = world_size, rank, process_group
+        if grad_sync not in ("peer", "nccl"):
+            raise ValueError(f"grad_sync must be 'peer' or 'nccl', not {grad_sync!r}")
+        self.grad_sync = grad_sync if world_size > 1 else "none"
+        if self.grad_sync == "peer" and world_size > L.MAX_PEERS:
+            raise ValueError(f"peer gradient exchange supports at most {L.MAX_PEERS} ranks")
+        self._peer_allocs, self._peer_maps = [], []
         n = self.n
         dev = self.device
-        self.params_flat = torch.zeros(_flat_len(n), dtype=torch.float32, device=dev)
+        self.params_flat = self._shared_zeros(_flat_len(n) * 4).view(torch.float32)
         self.params = _flat_views(self.params_flat, n)
         for name, _ in _ATTRS:
             self.params[name].copy_(torch.from_numpy(np.ascontiguousarray(splats[name]).reshape(-1)))
-        self.grads_flat = torch.zeros(_flat_len(n), dtype=torch.float32, device=dev)
+        self.grads_flat = self._shared_zeros(_flat_len(n) * 4).view(torch.float32)
         self.grads = _flat_views(self.grads_flat, n)
         self.quant = cfg.sh_value_bits in (8, 16)
         n_mom = _flat_len(n) if not self.quant else _flat_len(n, _ATTRS[:5])
@@ -67,8 +80,8 @@ class Trainer:
             cells = n * 45
             blocks = (cells + 255) // 256
             bytes_per = 2 if cfg.sh_value_bits == 16 else 1
-            self.sh_packed = torch.zeros(cells * bytes_per, dtype=torch.uint8, device=dev)
-            self.sh_bounds = torch.zeros(blocks * 2, dtype=torch.float32, device=dev)
+            self.sh_packed = self._shared_zeros(cells * bytes_per)
+            self.sh_bounds = self._shared_zeros(blocks * 2 * 4).view(torch.float32)
             self.sh_optim_packed = torch.zeros(cells * 2, dtype=torch.uint8, device=dev)
             self.sh_optim_bounds = torch.zeros(blocks * 4, dtype=torch.float32, device=dev)
             L.check(self.lib.ssb_quant_encode(L.ptr(self.params["features_sh"]), cells, cfg.sh_value_bits,
@@ -92,6 +105,70 @@ class Trainer:
         # device staging for one rank's share of a batch, per camera kind (filled by train_step)
         self._staging = {}
         self._copy_stream = None
+        # the range of splats whose optimiser step this rank performs
+        self.first, self.count = 0, n
+        if self.grad_sync == "peer":
+            self._setup_peers()
+
+    # -- peer-memory gradient exchange -------------------------------------
+    def _shared_zeros(self, nbytes):
+        """Zeroed device bytes; an exportable allocation when peers will access it."""
+        if self.grad_sync != "peer":
+            return torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+        ptr = C.c_void_p()
+        L.check(self.lib.ssb_peer_alloc(max(int(nbytes), 16), C.byref(ptr)))
+        self._peer_allocs.append(ptr)
+        return L.device_bytes_tensor(ptr.value, int(nbytes), self.device)
+
+    def _setup_peers(self):
+        import torch.distributed as dist
+        W, r, n = self.world_size, self.rank, self.n
+        # ranges are multiples of 512 splats so that every array's slice starts on a 16-byte boundary
+        per = ((n + W - 1) // W + 511) // 512 * 512
+        self.first = min(n, r * per)
+        self.count = min(n, self.first + per) - self.first
+        bufs = [self.grads_flat, self.params_flat] + ([self.sh_packed, self.sh_bounds] if self.quant else [])
+        mine = []
+        for t in bufs:
+            h = (C.c_ubyte * L.PEER_HANDLE_BYTES)()
+            L.check(self.lib.ssb_peer_export(C.c_void_p(t.data_ptr()), h))
+            mine.append(bytes(h))
+        everyone = [None] * W
+        dist.all_gather_object(everyone, mine, group=self.pg)
+        bases = [[0] * W for _ in bufs]
+        for p in range(W):
+            for b, t in enumerate(bufs):
+                if p == r:
+                    bases[b][p] = t.data_ptr()
+                else:
+                    ptr = C.c_void_p()
+                    h = (C.c_ubyte * L.PEER_HANDLE_BYTES).from_buffer_copy(everyone[p][b])
+                    L.check(self.lib.ssb_peer_open(h, C.byref(ptr)))
+                    self._peer_maps.append(ptr)
+                    bases[b][p] = ptr.value
+        f, c = self.first, self.count
+        grad_segs, param_segs, off = [], [], 0
+        for name, w in _ATTRS:
+            grad_segs.append((0, (off + f * w) * 4, c * w * 4))
+            if not (self.quant and name == "features_sh"):
+                param_segs.append((0, (off + f * w) * 4, c * w * 4))
+            off += _pad(n * w)
+        tables_bases = [bases[1]]
+        if self.quant:
+            bytes_per = 2 if self.cfg.sh_value_bits == 16 else 1
+            b0, b1 = f * 45 // 256, ((f + c) * 45 + 255) // 256
+            param_segs.append((1, f * 45 * bytes_per, c * 45 * bytes_per))
+            param_segs.append((2, b0 * 8, (b1 - b0) * 8))
+            tables_bases += [bases[2], bases[3]]
+        self._reduce_table = L.peer_table(W, r, [bases[0]], grad_segs)
+        self._bcast_table = L.peer_table(W, r, tables_bases, param_segs)
+        self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._barrier()          # every rank has mapped every buffer before anyone touches them
+
+    def _barrier(self):
+        """Orders the ranks on the current stream: work enqueued after it on any rank starts only after
+        the work enqueued before it on every rank has finished."""
+        torch.distributed.all_reduce(self._token, group=self.pg)
 
     def _geo_views(self, flat):
         out = _flat_views(flat, self.n, _ATTRS[:5])
@@ -104,6 +181,18 @@ class Trainer:
                 self.lib.ssb_step_destroy(h)
         self.handles = []
         self.handle = C.c_void_p()
+        if getattr(self, "_peer_maps", None) or getattr(self, "_peer_allocs", None):
+            torch.cuda.synchronize(self.device)
+            if self.world_size > 1 and torch.distributed.is_initialized():
+                self._barrier()                      # nobody unmaps while a peer may still be writing
+                torch.cuda.synchronize(self.device)
+            for ptr in self._peer_maps:
+                self.lib.ssb_peer_close(ptr)
+            self._peer_maps = []
+            # tensors viewing these allocations must not be used after this point
+            for ptr in self._peer_allocs:
+                self.lib.ssb_peer_free(ptr)
+            self._peer_allocs = []
 
     def __del__(self):
         try:
@@ -125,21 +214,30 @@ class Trainer:
                                         C.byref(self._g_struct), 1 if accumulate else 0, L.ptr(self.losses), stream))
 
     def allreduce_grads(self):
-        if self.world_size > 1:
+        """Makes the summed gradients available where the optimiser will read them: everywhere ("nccl"),
+        or, for this rank's range of splats, in this rank's buffer ("peer")."""
+        if self.grad_sync == "nccl":
             torch.distributed.all_reduce(self.grads_flat, op=torch.distributed.ReduceOp.SUM, group=self.pg)
+        elif self.grad_sync == "peer":
+            self._barrier()                                       # every rank's backward passes are complete
+            L.check(self.lib.ssb_peer_reduce_f32(C.byref(self._reduce_table), None))
 
     def optimizer_step(self, total_views, stream=None):
         lr = self.cfg.lrs
         self.iteration += 1
         cfg = L.SsbAdamConfig(lr["lr_means"], lr["lr_quats"], lr["lr_scales"], lr["lr_opacities"], lr["lr_features_dc"],
                               lr["lr_features_sh"], 0.0, 1.0 / float(total_views), self.iteration, 0)
+        f, c = self.first, self.count
         L.check(self.lib.ssb_adam_step(C.byref(self._p_struct), C.byref(self._g_struct), C.byref(self._m1_struct),
-                                       C.byref(self._m2_struct), 0, self.n, C.byref(cfg), stream))
+                                       C.byref(self._m2_struct), f, c, C.byref(cfg), stream))
         if self.quant:
             cells = self.n * 45
             L.check(self.lib.ssb_adam_step_sh_quantized(L.ptr(self.grads["features_sh"]), L.ptr(self.sh_optim_packed),
                                                         L.ptr(self.sh_optim_bounds), L.ptr(self.sh_packed), L.ptr(self.sh_bounds),
-                                                        self.cfg.sh_value_bits, 0, cells, cells, C.byref(cfg), stream))
+                                                        self.cfg.sh_value_bits, f * 45, c * 45, cells, C.byref(cfg), stream))
+        if self.grad_sync == "peer":
+            L.check(self.lib.ssb_peer_broadcast(C.byref(self._bcast_table), stream))
+            self._barrier()                                       # every replica is complete before the next forward
 
     # -- whole iteration ---------------------------------------------------
     def step_device(self, d_viewmats, d_intrins, d_gt, n_local_views, total_views):

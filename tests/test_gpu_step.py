@@ -237,6 +237,47 @@ def test_wide_camera_iteration_matches_oracle(lib, U, oracle):
     tr.close(); tr2.close()
 
 
+def test_peer_reduce_and_broadcast_with_virtual_ranks(lib, U):
+    """The peer-memory kernels with three 'ranks' that are three buffers on this one GPU: each rank's
+    segments end up holding the sum of all ranks' data (reduce), then every rank's copy of them equals
+    the owner's (broadcast).  Segment lengths that are not multiples of 16 bytes exercise the tails."""
+    world, n = 3, 40_000
+    g = torch.Generator(device=U.DEV); g.manual_seed(7)
+    grads = [torch.randn(n, device=U.DEV, generator=g) for _ in range(world)]
+    orig = [t.clone() for t in grads]
+    other = [torch.randint(0, 255, (9001,), device=U.DEV, generator=g, dtype=torch.uint8) for _ in range(world)]
+    orig_other = [t.clone() for t in other]
+    total = sum(orig)
+    bounds = [0, 13_312, 26_624, n]                     # owner r holds floats [bounds[r], bounds[r+1]) and a second piece
+    for r in range(world):
+        segs = [(0, bounds[r] * 4, (bounds[r + 1] - bounds[r]) * 4 - (4 if r == 1 else 0)), (0, (n - 64 + 16 * r) * 4, 4 * 3)]
+        if r != 2:
+            segs = segs[:1]
+        t = L.peer_table(world, r, [[x.data_ptr() for x in grads]], segs)
+        L.check(lib.ssb_peer_reduce_f32(C.byref(t), None))
+    torch.cuda.synchronize()
+    for r in range(world):
+        lo, hi = bounds[r], bounds[r + 1] - (1 if r == 1 else 0)
+        if r == 2:
+            hi = n - 64          # the tail of rank 2's range was also covered by its second segment; check the first part
+        assert torch.allclose(grads[r][lo:hi], total[lo:hi], rtol=1e-6, atol=1e-6)
+    assert torch.equal(grads[1][bounds[2] - 1:bounds[2]], orig[1][bounds[2] - 1:bounds[2]])    # the float left out stays
+    assert torch.equal(grads[0][bounds[1]:], orig[0][bounds[1]:])                                # others' ranges untouched
+    # broadcast: floats of buffer 0 and an odd byte range of buffer 1
+    for r in range(world):
+        segs = [(0, bounds[r] * 4, (bounds[r + 1] - bounds[r]) * 4), (1, 16 * (100 * r + 1), 2999)]
+        t = L.peer_table(world, r, [[x.data_ptr() for x in grads], [x.data_ptr() for x in other]], segs)
+        L.check(lib.ssb_peer_broadcast(C.byref(t), None))
+        torch.cuda.synchronize()
+        for q in range(world):
+            assert torch.equal(grads[q][bounds[r]:bounds[r + 1]], grads[r][bounds[r]:bounds[r + 1]])
+            o = 16 * (100 * r + 1)
+            assert torch.equal(other[q][o:o + 2999], other[r][o:o + 2999])
+    # arguments are checked
+    t = L.peer_table(world, 0, [[x.data_ptr() for x in grads]], [(0, 8, 64)])
+    assert lib.ssb_peer_reduce_f32(C.byref(t), None) == L.SSB_ERR_INVALID_ARGUMENT
+
+
 def test_full_size_sort_and_range_properties(lib, U):
     """At the benchmark's pair count (several million) the oracle is too slow to
     run inside a test, so check what must hold at any size: the output is

@@ -1,0 +1,23 @@
+"""Multi-GPU checks: run only where at least two GPUs are visible."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+torch = pytest.importorskip("torch")
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("variant", ["fp32", "quant"])
+def test_peer_exchange_matches_nccl_on_two_gpus(variant):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29641" if variant == "fp32" else "29642", os.path.join(ROOT, "tests", "multi_gpu_check.py"), variant]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    assert any(line.startswith("OK") for line in r.stdout.splitlines()), r.stdout[-2000:]

@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
     const SsbScreenRec* __restrict__ screen, const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ flatten_ids,
     const int64_t* __restrict__ n_isects_ptr, int I, int W, int H, int tw, int th,
     float* __restrict__ out_rgb, float* __restrict__ out_depth, float* __restrict__ out_T, int32_t* __restrict__ last_ids) {
-    __shared__ float4 sA[kFwdThreads], sB[kFwdThreads], sC[kFwdThreads];
+    __shared__ float4 sA[kFwdThreads], sB[kFwdThreads], sC[kFwdThreads], sQ[kFwdThreads];
     __shared__ uint8_t hits[kFwdThreads / 32][kFwdThreads];
 
     const int img = blockIdx.z;
@@ -85,6 +85,10 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
             int32_t g = flatten_ids[batch_start + threadIdx.x];
             const float4* r = (const float4*)(screen + g);
             sA[threadIdx.x] = r[0]; sB[threadIdx.x] = r[1]; sC[threadIdx.x] = r[2];
+            // conic pre-scaled so that exp(-sigma) = 2^(-q), q = A dx^2 + B dx dy + C dy^2
+            const float kLog2e = 1.4426950408889634f;
+            const float4 b = r[1];
+            sQ[threadIdx.x] = make_float4(0.5f * kLog2e * b.x, kLog2e * b.y, 0.5f * kLog2e * b.z, b.w);
         }
         __syncthreads();
         // records that can reach this warp's 8x4 rectangle, in list order
@@ -105,10 +109,13 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
         for (int k = 0; k < n_hit; ++k) {
             if ((k & 3) == 0 && __all_sync(0xffffffffu, done)) break;
             const int e = hits[w][k];
-            const float4 a = sA[e], b = sB[e];
-            float vis, sigma, dx, dy;
-            const float alpha = eval_alpha(a, b, px, py, vis, sigma, dx, dy);
-            if (done || alpha <= kAlphaThreshold) continue;
+            const float4 a = sA[e], b = sQ[e];
+            const float dx = a.x - px, dy = a.y - py;
+            const float q = fmaf(fmaf(b.x, dx, b.y * dy), dx, b.z * dy * dy);
+            float vis;
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(vis) : "f"(-q));
+            const float alpha = fminf(0.999f, b.w * vis);
+            if (done || !(q >= 0.f) || alpha <= kAlphaThreshold) continue;
             const float next_T = T * (1.0f - alpha);
             if (next_T > kTransmitThreshold) {
                 const float4 c = sC[e];

@@ -337,10 +337,7 @@ def run_ours(args, cfg, rank, world, local_rank):
     if resident[0][4] > 0:
         aabb_p = C.c_void_p()
         L.check(lib.ssb_step_peek(tr.handle, None, None, None, None, None, C.byref(aabb_p)))
-        rt = C.CDLL("libcudart.so.12")
-        rt.cudaMemcpy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
-        aabb = torch.empty((cfg.n_splats, 4), dtype=torch.float32, device=dev)
-        rt.cudaMemcpy(C.c_void_p(aabb.data_ptr()), aabb_p, aabb.numel() * 4, 3)
+        aabb = L.device_bytes_tensor(aabb_p.value, cfg.n_splats * 16, dev).view(torch.float32).view(-1, 4)
         visible = int((aabb[:, 2] > aabb[:, 0]).sum().item())
 
     if rank == 0:

@@ -39,25 +39,35 @@ __device__ __forceinline__ float eval_alpha(float4 a, float4 b, float px, float 
 // (coordinates relative to the splat centre)?  Same construction as the
 // reference's micro-tile test (src/core/Common.cuh:55-77), with a small margin
 // so rounding can only keep a record, never drop one.
-__device__ __forceinline__ bool ellipse_reaches_box(float4 b, float x0, float x1, float y0, float y1) {
+struct EllipseTest { float a, bb2, c, wx, wy; };   // conic scaled to the alpha = 1/255 level set, 2b, and the two tangent slopes
+
+__device__ __forceinline__ EllipseTest ellipse_test_setup(float4 b) {
     const float kk = 0.5f / __logf(b.w * 255.0f);
-    const float a = b.x * kk, c = b.z * kk;
-    float bb = b.y * kk;
-    const float wx = -bb / c, wy = -bb / a;
-    const float u0 = fminf(fmaxf(x0 * wx, y0), y1), u1 = fminf(fmaxf(x1 * wx, y0), y1);
-    const float v0 = fminf(fmaxf(y0 * wy, x0), x1), v1 = fminf(fmaxf(y1 * wy, x0), x1);
-    bb *= 2.0f;
+    const float a = b.x * kk, c = b.z * kk, bb = b.y * kk;
+    EllipseTest t = {a, 2.0f * bb, c, -bb / c, -bb / a};
+    return t;
+}
+
+__device__ __forceinline__ bool ellipse_test(const EllipseTest& t, float x0, float x1, float y0, float y1) {
+    const float a = t.a, c = t.c, bb = t.bb2;
+    const float u0 = fminf(fmaxf(x0 * t.wx, y0), y1), u1 = fminf(fmaxf(x1 * t.wx, y0), y1);
+    const float v0 = fminf(fmaxf(y0 * t.wy, x0), x1), v1 = fminf(fmaxf(y1 * t.wy, x0), x1);
     const float mx = fminf(a * x0 * x0 + bb * x0 * u0 + c * u0 * u0, a * x1 * x1 + bb * x1 * u1 + c * u1 * u1);
     const float my = fminf(a * v0 * v0 + bb * v0 * y0 + c * y0 * y0, a * v1 * v1 + bb * v1 * y1 + c * y1 * y1);
     const float mc = fmaxf(fmaxf(x0, -x1), fmaxf(y0, -y1));
     return !(fminf(mc, fminf(mx, my) - 1.0f) >= 0.01f);
 }
 
+__device__ __forceinline__ bool ellipse_reaches_box(float4 b, float x0, float x1, float y0, float y1) {
+    return ellipse_test(ellipse_test_setup(b), x0, x1, y0, y1);
+}
+
 __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
     const SsbScreenRec* __restrict__ screen, const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ flatten_ids,
     const int64_t* __restrict__ n_isects_ptr, int I, int W, int H, int tw, int th,
     float* __restrict__ out_rgb, float* __restrict__ out_depth, float* __restrict__ out_T, int32_t* __restrict__ last_ids) {
-    __shared__ float4 sA[kFwdThreads], sB[kFwdThreads], sC[kFwdThreads], sQ[kFwdThreads];
+    __shared__ float4 sA[kFwdThreads], sC[kFwdThreads], sQ[kFwdThreads], sE[kFwdThreads];
+    __shared__ float sEw[kFwdThreads];
     __shared__ uint8_t hits[kFwdThreads / 32][kFwdThreads];
 
     const int img = blockIdx.z;
@@ -84,11 +94,15 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
         if ((int)threadIdx.x < batch) {
             int32_t g = flatten_ids[batch_start + threadIdx.x];
             const float4* r = (const float4*)(screen + g);
-            sA[threadIdx.x] = r[0]; sB[threadIdx.x] = r[1]; sC[threadIdx.x] = r[2];
+            sA[threadIdx.x] = r[0]; sC[threadIdx.x] = r[2];
             // conic pre-scaled so that exp(-sigma) = 2^(-q), q = A dx^2 + B dx dy + C dy^2
             const float kLog2e = 1.4426950408889634f;
             const float4 b = r[1];
             sQ[threadIdx.x] = make_float4(0.5f * kLog2e * b.x, kLog2e * b.y, 0.5f * kLog2e * b.z, b.w);
+            // and the per-record part of the ellipse-vs-rectangle test, shared by the eight warps
+            const EllipseTest et = ellipse_test_setup(b);
+            sE[threadIdx.x] = make_float4(et.a, et.bb2, et.c, et.wx);
+            sEw[threadIdx.x] = et.wy;
         }
         __syncthreads();
         // records that can reach this warp's 8x4 rectangle, in list order
@@ -99,7 +113,11 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
             if (e < batch) {
                 float4 a = sA[e];
                 hit = (a.x + a.z >= fx0) && (a.x - a.z <= fx1) && (a.y + a.w >= fy0) && (a.y - a.w <= fy1);
-                if (hit) hit = ellipse_reaches_box(sB[e], fx0 - a.x, fx1 - a.x, fy0 - a.y, fy1 - a.y);
+                if (hit) {
+                    const float4 ev = sE[e];
+                    const EllipseTest et = {ev.x, ev.y, ev.z, ev.w, sEw[e]};
+                    hit = ellipse_test(et, fx0 - a.x, fx1 - a.x, fy0 - a.y, fy1 - a.y);
+                }
             }
             unsigned bal = __ballot_sync(0xffffffffu, hit);
             if (hit) hits[w][n_hit + __popc(bal & ((1u << lane) - 1u))] = (uint8_t)e;

@@ -289,12 +289,15 @@ class Trainer:
                     self._staging[kind] = st
                 st[0].copy_(h_viewmats, non_blocking=True)
                 st[1].copy_(h_intrins, non_blocking=True)
-                for c0 in range(0, nv, chunk):
-                    c1 = min(nv, c0 + chunk)
+                c0 = 0
+                while c0 < nv:
+                    # the first copies are single views so that rendering can start as early as possible
+                    c1 = min(nv, c0 + (1 if len(events) < 2 else chunk))
                     st[2][c0:c1].copy_(h_gt[c0:c1], non_blocking=True)
                     ev = torch.cuda.Event()
                     ev.record(self._copy_stream)
                     events.append((kind, c0, c1, ev))
+                    c0 = c1
         if nv_total == 0:
             self.grads_flat.zero_()
         for i, (kind, c0, c1, ev) in enumerate(events):

@@ -82,6 +82,10 @@ def test_tile_stage_vs_reference(lib, U, name):
         assert M == gold["sorted_ids"].size
         assert np.array_equal(sk.cpu().numpy()[:M], gold["sorted_ids"]) and np.array_equal(sv.cpu().numpy()[:M], gold["sorted_flat"])
         assert np.array_equal(offs.cpu().numpy(), gold["offsets"])
+    # the fused call (what the step runs) gives the same lists and ranges as the unfused trio
+    f_keys, f_vals, f_offs, f_M = U.intersect_tiles(lib, U.dev(gold["aabb"]), U.dev(gold["depths"]), rec, I * n, n, W, H, cap, tw * th * I)
+    assert f_M == M and np.array_equal(f_offs.cpu().numpy(), offs.cpu().numpy())
+    assert np.array_equal(f_keys.cpu().numpy()[:M], sk.cpu().numpy()[:M]) and np.array_equal(f_vals.cpu().numpy()[:M], sv.cpu().numpy()[:M])
     # our range kernel on the reference's own sorted keys: exact
     n_ref = torch.tensor([gold["sorted_ids"].size], dtype=torch.int64, device=U.DEV)
     offs2 = U.tile_ranges(lib, U.dev(gold["sorted_ids"]), n_ref, gold["sorted_ids"].size, tw * th * I)

@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
 constexpr int kBwdWarps = 4;          // one 16x16 tile per CTA, one 8x8 micro-tile per warp
 constexpr int kSurvCap = 256;         // survivors collected per segment (8 per lane)
 
-__global__ void __launch_bounds__(kBwdWarps * 32) raster_bwd_kernel(
+__global__ void __launch_bounds__(kBwdWarps * 32, 10) raster_bwd_kernel(
     const SsbScreenRec* __restrict__ screen, const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ flatten_ids,
     const int64_t* __restrict__ n_isects_ptr, int I, int W, int H, int tw, int th,
     const float* __restrict__ render_depth, const float* __restrict__ render_T, const int32_t* __restrict__ last_ids,

@@ -299,6 +299,11 @@ typedef struct SsbPeerTable {
     int32_t world, self, n_segments, pad;
     void* base[SSB_MAX_PEER_BUFFERS][SSB_MAX_PEERS];
     SsbPeerSegment seg[SSB_MAX_PEER_SEGMENTS];
+    /* Optional: the NVSwitch multicast address of each buffer (one address that reaches every rank's
+     * copy).  When it is non-NULL for every buffer a table uses, the sum is taken inside the switch
+     * (multimem.ld_reduce: each rank receives its range once instead of once per peer) and the
+     * broadcast is one multicast store (multimem.st).  NULL: plain loads and stores per peer. */
+    void* multicast[SSB_MAX_PEER_BUFFERS];
 } SsbPeerTable;
 int ssb_peer_alloc(int64_t bytes, void** d_ptr);
 int ssb_peer_free(void* d_ptr);

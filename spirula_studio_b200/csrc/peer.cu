@@ -16,8 +16,10 @@
 // iteration (before 1: every rank's backward is complete; after 3: every replica is
 // complete).  No kernel waits on another GPU, so nothing here can spin.
 //
-// Buffers that peers access are plain cudaMalloc allocations exported as CUDA IPC handles
-// (one process per GPU).  Peer loads bypass the L1 cache (ld.global.cv): the line a
+// Buffers that peers access are either plain cudaMalloc allocations exported as CUDA IPC handles
+// (ssb_peer_alloc/export/open) or any memory the caller has mapped on every rank; when the caller
+// also has an NVSwitch multicast address for them, the sum is taken inside the switch and the
+// broadcast is a multicast store (the *_mc kernels).  One process per GPU.  Peer loads bypass the L1 cache (ld.global.cv): the line a
 // previous iteration left there would be stale.
 #include "ssb_common.cuh"
 
@@ -78,6 +80,66 @@ __global__ void __launch_bounds__(kPeerThreads) peer_broadcast_kernel(SsbPeerTab
                 if (p != t.self) ((char*)t.base[sg.buffer][p] + sg.offset_bytes)[i] = x;
         }
     }
+}
+
+// The same two operations through the NVSwitch multicast address of the buffers: the switch adds
+// the ranks' copies on a load (multimem.ld_reduce) and replicates a store (multimem.st).
+__device__ __forceinline__ float4 multimem_sum_f4(const void* mc_addr) {
+    float4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(mc_addr) : "memory");
+    return r;
+}
+__device__ __forceinline__ void multimem_store_u4(void* mc_addr, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 :: "l"(mc_addr), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w)) : "memory");
+}
+
+__global__ void __launch_bounds__(kPeerThreads) peer_reduce_mc_kernel(SsbPeerTable t) {
+    const int64_t stride = (int64_t)gridDim.x * kPeerThreads;
+    const int64_t tid = (int64_t)blockIdx.x * kPeerThreads + threadIdx.x;
+    for (int s = 0; s < t.n_segments; ++s) {
+        const SsbPeerSegment sg = t.seg[s];
+        float* own = (float*)((char*)t.base[sg.buffer][t.self] + sg.offset_bytes);
+        const char* mc = (const char*)t.multicast[sg.buffer] + sg.offset_bytes;
+        const int64_t n_vec = sg.bytes / 16;
+        for (int64_t v = tid; v < n_vec; v += stride) ((float4*)own)[v] = multimem_sum_f4(mc + 16 * v);
+        // the last few floats of a segment whose length is not a multiple of 16 bytes: per-peer loads
+        const int64_t tail0 = n_vec * 4, n_f = sg.bytes / 4;
+        for (int64_t i = tail0 + tid; i < n_f; i += stride) {
+            float acc = own[i];
+            for (int p = 0; p < t.world; ++p) {
+                if (p == t.self) continue;
+                acc += __ldcv((const float*)((const char*)t.base[sg.buffer][p] + sg.offset_bytes) + i);
+            }
+            own[i] = acc;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kPeerThreads) peer_broadcast_mc_kernel(SsbPeerTable t) {
+    const int64_t stride = (int64_t)gridDim.x * kPeerThreads;
+    const int64_t tid = (int64_t)blockIdx.x * kPeerThreads + threadIdx.x;
+    for (int s = 0; s < t.n_segments; ++s) {
+        const SsbPeerSegment sg = t.seg[s];
+        const char* own = (const char*)t.base[sg.buffer][t.self] + sg.offset_bytes;
+        char* mc = (char*)t.multicast[sg.buffer] + sg.offset_bytes;
+        const int64_t n_vec = sg.bytes / 16;
+        for (int64_t v = tid; v < n_vec; v += stride) multimem_store_u4(mc + 16 * v, ((const uint4*)own)[v]);
+        for (int64_t i = n_vec * 16 + tid; i < sg.bytes; i += stride) {
+            const char x = own[i];
+            for (int p = 0; p < t.world; ++p)
+                if (p != t.self) ((char*)t.base[sg.buffer][p] + sg.offset_bytes)[i] = x;
+        }
+    }
+}
+
+static bool table_has_multicast(const SsbPeerTable* t) {
+    for (int s = 0; s < t->n_segments; ++s) {
+        void* mc = t->multicast[t->seg[s].buffer];
+        if (mc == nullptr || ((uintptr_t)mc & 15) != 0) return false;
+    }
+    return t->n_segments > 0;
 }
 
 static int check_table(const SsbPeerTable* t, const char* who, bool f32) {
@@ -157,7 +219,8 @@ int ssb_peer_reduce_f32(const SsbPeerTable* table, void* stream) {
     int e = check_table(table, "ssb_peer_reduce_f32", true);
     if (e) return e;
     if (table->world == 1 || table->n_segments == 0) return SSB_OK;
-    peer_reduce_kernel<<<peer_grid(table), kPeerThreads, 0, (cudaStream_t)stream>>>(*table);
+    if (table_has_multicast(table)) peer_reduce_mc_kernel<<<peer_grid(table), kPeerThreads, 0, (cudaStream_t)stream>>>(*table);
+    else peer_reduce_kernel<<<peer_grid(table), kPeerThreads, 0, (cudaStream_t)stream>>>(*table);
     SSB_LAUNCHED("peer_reduce_kernel");
     return SSB_OK;
 }
@@ -167,7 +230,8 @@ int ssb_peer_broadcast(const SsbPeerTable* table, void* stream) {
     int e = check_table(table, "ssb_peer_broadcast", false);
     if (e) return e;
     if (table->world == 1 || table->n_segments == 0) return SSB_OK;
-    peer_broadcast_kernel<<<peer_grid(table), kPeerThreads, 0, (cudaStream_t)stream>>>(*table);
+    if (table_has_multicast(table)) peer_broadcast_mc_kernel<<<peer_grid(table), kPeerThreads, 0, (cudaStream_t)stream>>>(*table);
+    else peer_broadcast_kernel<<<peer_grid(table), kPeerThreads, 0, (cudaStream_t)stream>>>(*table);
     SSB_LAUNCHED("peer_broadcast_kernel");
     return SSB_OK;
 }

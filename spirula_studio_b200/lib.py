@@ -162,12 +162,16 @@ class SsbPeerSegment(C.Structure):
 
 class SsbPeerTable(C.Structure):
     _fields_ = [("world", C.c_int32), ("self", C.c_int32), ("n_segments", C.c_int32), ("pad", C.c_int32),
-                ("base", (C.c_void_p * MAX_PEERS) * MAX_PEER_BUFFERS), ("seg", SsbPeerSegment * MAX_PEER_SEGMENTS)]
+                ("base", (C.c_void_p * MAX_PEERS) * MAX_PEER_BUFFERS), ("seg", SsbPeerSegment * MAX_PEER_SEGMENTS),
+                ("multicast", C.c_void_p * MAX_PEER_BUFFERS)]
 
 
-def peer_table(world, rank, bases, segments):
-    """bases[b][r] = device address of rank r's copy of buffer b; segments = [(buffer, offset_bytes, bytes), ...]."""
+def peer_table(world, rank, bases, segments, multicast=None):
+    """bases[b][r] = device address of rank r's copy of buffer b; segments = [(buffer, offset_bytes, bytes), ...];
+    multicast[b] = NVSwitch multicast address of buffer b (optional)."""
     t = SsbPeerTable()
+    for b, addr in enumerate(multicast or []):
+        t.multicast[b] = addr or None
     t.world, t.self, t.n_segments = world, rank, len(segments)
     for b, per_rank in enumerate(bases):
         for r, addr in enumerate(per_rank):

@@ -11,6 +11,11 @@ in one of two ways:
       memory over NVLink (ssb_peer_reduce_f32), runs Adam on the range, and
       stores the updated parameters into every replica (ssb_peer_broadcast).
       Two stream-ordered barriers per iteration keep the ranks in step.
+  "multimem": the same three steps, but the exchanged buffers live in torch
+      symmetric memory and the kernels address them through their NVSwitch
+      multicast address: the switch adds the ranks' gradients on a load and
+      replicates a parameter store, so each rank moves its range once instead
+      of once per peer.  Falls back to "peer" where that cannot be set up.
   "nccl": one NCCL all-reduce of the whole gradient buffer, then every rank
       applies the same Adam update to all parameters.
 
@@ -55,10 +60,13 @@ class Trainer:
         self.device = torch.device(device)
         self.n = int(cfg.n_splats)
         self.world_size, self.rank, self.pg = world_size, rank, process_group
-        if grad_sync not in ("peer", "nccl"):
-            raise ValueError(f"grad_sync must be 'peer' or 'nccl', not {grad_sync!r}")
+        if grad_sync not in ("peer", "multimem", "nccl"):
+            raise ValueError(f"grad_sync must be 'peer', 'multimem' or 'nccl', not {grad_sync!r}")
         self.grad_sync = grad_sync if world_size > 1 else "none"
-        if self.grad_sync == "peer" and world_size > L.MAX_PEERS:
+        if self.grad_sync == "multimem" and not self._symmetric_memory_usable():
+            self.grad_sync = "peer"
+        self._symm_tensors = []
+        if self.grad_sync in ("peer", "multimem") and world_size > L.MAX_PEERS:
             raise ValueError(f"peer gradient exchange supports at most {L.MAX_PEERS} ranks")
         self._peer_allocs, self._peer_maps = [], []
         n = self.n
@@ -107,12 +115,34 @@ class Trainer:
         self._copy_stream = None
         # the range of splats whose optimiser step this rank performs
         self.first, self.count = 0, n
-        if self.grad_sync == "peer":
+        if self.grad_sync in ("peer", "multimem"):
             self._setup_peers()
 
     # -- peer-memory gradient exchange -------------------------------------
+    def _symmetric_memory_usable(self):
+        """Every rank must take the same decision, so the ranks vote."""
+        ok = 1.0
+        try:
+            import torch.distributed._symmetric_memory as symm
+            probe = symm.empty(1024, dtype=torch.uint8, device=self.device)
+            group = self.pg if self.pg is not None else torch.distributed.group.WORLD
+            h = symm.rendezvous(probe, group)
+            if not h.multicast_ptr:
+                ok = 0.0
+        except Exception:
+            ok = 0.0
+        vote = torch.tensor([ok], dtype=torch.float32, device=self.device)
+        torch.distributed.all_reduce(vote, op=torch.distributed.ReduceOp.MIN, group=self.pg)
+        return bool(vote.item() > 0.5)
+
     def _shared_zeros(self, nbytes):
         """Zeroed device bytes; an exportable allocation when peers will access it."""
+        if self.grad_sync == "multimem":
+            import torch.distributed._symmetric_memory as symm
+            t = symm.empty(max(int(nbytes), 16), dtype=torch.uint8, device=self.device)
+            t.zero_()
+            self._symm_tensors.append(t)
+            return t[:int(nbytes)]
         if self.grad_sync != "peer":
             return torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         ptr = C.c_void_p()
@@ -128,24 +158,38 @@ class Trainer:
         self.first = min(n, r * per)
         self.count = min(n, self.first + per) - self.first
         bufs = [self.grads_flat, self.params_flat] + ([self.sh_packed, self.sh_bounds] if self.quant else [])
-        mine = []
-        for t in bufs:
-            h = (C.c_ubyte * L.PEER_HANDLE_BYTES)()
-            L.check(self.lib.ssb_peer_export(C.c_void_p(t.data_ptr()), h))
-            mine.append(bytes(h))
-        everyone = [None] * W
-        dist.all_gather_object(everyone, mine, group=self.pg)
         bases = [[0] * W for _ in bufs]
-        for p in range(W):
-            for b, t in enumerate(bufs):
-                if p == r:
-                    bases[b][p] = t.data_ptr()
-                else:
-                    ptr = C.c_void_p()
-                    h = (C.c_ubyte * L.PEER_HANDLE_BYTES).from_buffer_copy(everyone[p][b])
-                    L.check(self.lib.ssb_peer_open(h, C.byref(ptr)))
-                    self._peer_maps.append(ptr)
-                    bases[b][p] = ptr.value
+        mcast = [0] * len(bufs)
+        if self.grad_sync == "multimem":
+            import torch.distributed._symmetric_memory as symm
+            group = self.pg if self.pg is not None else dist.group.WORLD
+            torch.cuda.synchronize(self.device)          # the buffers' initial contents are in place
+            by_address = {t.data_ptr(): t for t in self._symm_tensors}
+            for b, view in enumerate(bufs):
+                t = by_address[view.data_ptr()]           # the symmetric allocation this buffer is a view of
+                h = symm.rendezvous(t, group)
+                for p in range(W):
+                    bases[b][p] = int(h.buffer_ptrs[p])
+                bases[b][r] = t.data_ptr()
+                mcast[b] = int(h.multicast_ptr)
+        else:
+            mine = []
+            for t in bufs:
+                h = (C.c_ubyte * L.PEER_HANDLE_BYTES)()
+                L.check(self.lib.ssb_peer_export(C.c_void_p(t.data_ptr()), h))
+                mine.append(bytes(h))
+            everyone = [None] * W
+            dist.all_gather_object(everyone, mine, group=self.pg)
+            for p in range(W):
+                for b, t in enumerate(bufs):
+                    if p == r:
+                        bases[b][p] = t.data_ptr()
+                    else:
+                        ptr = C.c_void_p()
+                        h = (C.c_ubyte * L.PEER_HANDLE_BYTES).from_buffer_copy(everyone[p][b])
+                        L.check(self.lib.ssb_peer_open(h, C.byref(ptr)))
+                        self._peer_maps.append(ptr)
+                        bases[b][p] = ptr.value
         f, c = self.first, self.count
         grad_segs, param_segs, off = [], [], 0
         for name, w in _ATTRS:
@@ -153,15 +197,16 @@ class Trainer:
             if not (self.quant and name == "features_sh"):
                 param_segs.append((0, (off + f * w) * 4, c * w * 4))
             off += _pad(n * w)
-        tables_bases = [bases[1]]
+        tables_bases, tables_mcast = [bases[1]], [mcast[1]]
         if self.quant:
             bytes_per = 2 if self.cfg.sh_value_bits == 16 else 1
             b0, b1 = f * 45 // 256, ((f + c) * 45 + 255) // 256
             param_segs.append((1, f * 45 * bytes_per, c * 45 * bytes_per))
             param_segs.append((2, b0 * 8, (b1 - b0) * 8))
             tables_bases += [bases[2], bases[3]]
-        self._reduce_table = L.peer_table(W, r, [bases[0]], grad_segs)
-        self._bcast_table = L.peer_table(W, r, tables_bases, param_segs)
+            tables_mcast += [mcast[2], mcast[3]]
+        self._reduce_table = L.peer_table(W, r, [bases[0]], grad_segs, [mcast[0]])
+        self._bcast_table = L.peer_table(W, r, tables_bases, param_segs, tables_mcast)
         self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._barrier()          # every rank has mapped every buffer before anyone touches them
 
@@ -181,7 +226,7 @@ class Trainer:
                 self.lib.ssb_step_destroy(h)
         self.handles = []
         self.handle = C.c_void_p()
-        if getattr(self, "_peer_maps", None) or getattr(self, "_peer_allocs", None):
+        if getattr(self, "_peer_maps", None) or getattr(self, "_peer_allocs", None) or getattr(self, "_symm_tensors", None):
             torch.cuda.synchronize(self.device)
             if self.world_size > 1 and torch.distributed.is_initialized():
                 self._barrier()                      # nobody unmaps while a peer may still be writing
@@ -193,6 +238,7 @@ class Trainer:
             for ptr in self._peer_allocs:
                 self.lib.ssb_peer_free(ptr)
             self._peer_allocs = []
+            self._symm_tensors = []
 
     def __del__(self):
         try:
@@ -218,7 +264,7 @@ class Trainer:
         or, for this rank's range of splats, in this rank's buffer ("peer")."""
         if self.grad_sync == "nccl":
             torch.distributed.all_reduce(self.grads_flat, op=torch.distributed.ReduceOp.SUM, group=self.pg)
-        elif self.grad_sync == "peer":
+        elif self.grad_sync in ("peer", "multimem"):
             self._barrier()                                       # every rank's backward passes are complete
             L.check(self.lib.ssb_peer_reduce_f32(C.byref(self._reduce_table), None))
 
@@ -235,7 +281,7 @@ class Trainer:
             L.check(self.lib.ssb_adam_step_sh_quantized(L.ptr(self.grads["features_sh"]), L.ptr(self.sh_optim_packed),
                                                         L.ptr(self.sh_optim_bounds), L.ptr(self.sh_packed), L.ptr(self.sh_bounds),
                                                         self.cfg.sh_value_bits, f * 45, c * 45, cells, C.byref(cfg), stream))
-        if self.grad_sync == "peer":
+        if self.grad_sync in ("peer", "multimem"):
             L.check(self.lib.ssb_peer_broadcast(C.byref(self._bcast_table), stream))
             self._barrier()                                       # every replica is complete before the next forward
 

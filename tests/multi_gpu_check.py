@@ -32,7 +32,7 @@ def main():
     d_K = torch.from_numpy(K[views].copy()).to(dev)
     d_gt = torch.from_numpy(np.stack([scenes.make_target(cfg, v) for v in views])).to(dev)
     out = {}
-    for mode in ("nccl", "peer"):
+    for mode in ("nccl", "peer", "multimem"):
         tr = Trainer(cfg, sp, device=dev, world_size=world, rank=rank, grad_sync=mode)
         for _ in range(3):
             tr.step_device(d_vm, d_K, d_gt, 2, cfg.n_views)
@@ -42,13 +42,17 @@ def main():
             state["sh_packed"] = tr.sh_packed.clone().to(torch.int32).view(-1)
             state["sh_bounds"] = tr.sh_bounds.clone()
         out[mode] = state
+        used = tr.grad_sync
         tr.close()
+        if rank == 0:
+            print(f"mode {mode} ran as {used}", flush=True)
     worst = 0.0
-    for k in out["nccl"]:
-        a, b = out["nccl"][k].double(), out["peer"][k].double()
+    for other in ("peer", "multimem"):
+      for k in out["nccl"]:
+        a, b = out["nccl"][k].double(), out[other][k].double()
         if k == "sh_packed":
             a16 = out["nccl"][k].to(torch.uint8).cpu().numpy().view(np.uint16).astype(np.int64)
-            b16 = out["peer"][k].to(torch.uint8).cpu().numpy().view(np.uint16).astype(np.int64)
+            b16 = out[other][k].to(torch.uint8).cpu().numpy().view(np.uint16).astype(np.int64)
             d = np.abs(a16 - b16)
             # 16-bit codes: a few quanta (of 65535) where the two summation orders rounded differently
             assert d.max() <= 8 and (d > 0).mean() < 2e-2, (k, d.max(), (d > 0).mean())
@@ -59,10 +63,11 @@ def main():
         # summation order differs between the two paths; a first Adam steps amplify sign flips of tiny gradients
         assert bad < 2e-2, (k, bad)
     # every replica holds the same parameters (compare rank 0's with everyone's)
-    for k, v in out["peer"].items():
-        ref = v.clone()
-        dist.broadcast(ref, 0)
-        assert torch.equal(ref, v), f"replicas differ in {k} on rank {rank}"
+    for other in ("peer", "multimem"):
+        for k, v in out[other].items():
+            ref = v.clone()
+            dist.broadcast(ref, 0)
+            assert torch.equal(ref, v), f"replicas differ in {k} on rank {rank} ({other})"
     if rank == 0:
         print("OK", worst, flush=True)
     dist.destroy_process_group()

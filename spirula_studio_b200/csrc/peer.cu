@@ -103,7 +103,13 @@ __global__ void __launch_bounds__(kPeerThreads) peer_reduce_mc_kernel(SsbPeerTab
         float* own = (float*)((char*)t.base[sg.buffer][t.self] + sg.offset_bytes);
         const char* mc = (const char*)t.multicast[sg.buffer] + sg.offset_bytes;
         const int64_t n_vec = sg.bytes / 16;
-        for (int64_t v = tid; v < n_vec; v += stride) ((float4*)own)[v] = multimem_sum_f4(mc + 16 * v);
+        int64_t v = tid;
+        for (; v + 3 * stride < n_vec; v += 4 * stride) {       // four independent switch reductions in flight per thread
+            const float4 r0 = multimem_sum_f4(mc + 16 * v), r1 = multimem_sum_f4(mc + 16 * (v + stride));
+            const float4 r2 = multimem_sum_f4(mc + 16 * (v + 2 * stride)), r3 = multimem_sum_f4(mc + 16 * (v + 3 * stride));
+            ((float4*)own)[v] = r0; ((float4*)own)[v + stride] = r1; ((float4*)own)[v + 2 * stride] = r2; ((float4*)own)[v + 3 * stride] = r3;
+        }
+        for (; v < n_vec; v += stride) ((float4*)own)[v] = multimem_sum_f4(mc + 16 * v);
         // the last few floats of a segment whose length is not a multiple of 16 bytes: per-peer loads
         const int64_t tail0 = n_vec * 4, n_f = sg.bytes / 4;
         for (int64_t i = tail0 + tid; i < n_f; i += stride) {

@@ -256,7 +256,10 @@ int ssb_adam_step(const SsbSplats* params, const SsbSplats* grads, const SsbSpla
  * kernel :291-418): Adam on SH coefficients whose values live in a QuantizedTensor
  * <value_bits,256> and whose state lives in a QuantizedAdamState<8,256>
  * (src/core/Tensor.h:978-1136).  `numel` cells starting at cell `first_cell`,
- * which must be a multiple of 256.  d_grad is fp32 [cells]. */
+ * which must be a multiple of 256.  d_grad is fp32 [cells].
+ * value_bits = 32 replaces fused_adam_step_quantized (FusedAppearanceOptim.cu:137-271) instead: the
+ * values are plain fp32 (d_value_packed is a float array, d_value_bounds may be NULL) and only the
+ * state is quantised. */
 int ssb_adam_step_sh_quantized(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds,
                                void* d_value_packed, float* d_value_bounds, int32_t value_bits,
                                int64_t first_cell, int64_t numel, int64_t numel_total,

@@ -1165,6 +1165,8 @@ void oracle_quant_decode(int64_t numel, int bits, const uint8_t* packed, const f
 // (src/kernels/optim/FusedAppearanceOptim.cu:291-418) with the state codec
 // QuantizedAdamState<8,256> (src/core/Tensor.h:978-1136) and the value codec
 // QuantizedTensor<VALUE_BITS,256> (:1313-1404).  fp32 gradient input.
+// value_bits == 32: the values are plain fp32 and only the state is quantised
+// (fused_adam_with_steps_8bit_kernel, src/kernels/optim/FusedAppearanceOptim.cu:137-229).
 void oracle_adam_qq(
     int64_t numel, int step, float lr, float l2_reg, float l2_reg_offset, float grad_scale, int zero_grad, int value_bits,
     float* grad, uint8_t* optim_packed, float* optim_bounds, uint8_t* value_packed, float* value_bounds) {
@@ -1172,19 +1174,21 @@ void oracle_adam_qq(
     const float ibc1 = 1.0f / (1.0f - std::pow(beta1, (float)step));
     const float ibc2 = 1.0f / (1.0f - std::pow(beta2, (float)step));
     const float decay = 2.0f * l2_reg / (float)numel;
-    const float vq = (float)((1 << value_bits) - 1), vinv = 1.0f / vq;
+    const bool plain = value_bits == 32;
+    const float vq = plain ? 1.0f : (float)((1 << value_bits) - 1), vinv = 1.0f / vq;
     const float oq = 255.0f, oinv = 1.0f / 255.0f;
     int64_t nb = (numel + 255) / 256;
+    float* value_f32 = reinterpret_cast<float*>(value_packed);
 #pragma omp parallel for schedule(static)
     for (int64_t b = 0; b < nb; ++b) {
         int64_t lo = b * 256, hi = std::min(numel, lo + 256);
         float xs[256], us[256], ss[256];
-        float vmm[2] = {value_bounds[2 * b], value_bounds[2 * b + 1]};
+        float vmm[2] = {plain ? 0.f : value_bounds[2 * b], plain ? 0.f : value_bounds[2 * b + 1]};
         float omm[4] = {optim_bounds[4 * b], optim_bounds[4 * b + 1], optim_bounds[4 * b + 2], optim_bounds[4 * b + 3]};
         float nv[2] = {1e30f, -1e30f}, no[4] = {1e30f, -1e30f, 1e30f, -1e30f};
         for (int64_t i = lo; i < hi; ++i) {
-            float q = value_bits == 8 ? (float)value_packed[i] : (float)reinterpret_cast<uint16_t*>(value_packed)[i];
-            float x = vmm[0] + (vmm[1] - vmm[0]) * (q * vinv);
+            float q = plain ? 0.f : value_bits == 8 ? (float)value_packed[i] : (float)reinterpret_cast<uint16_t*>(value_packed)[i];
+            float x = plain ? value_f32[i] : vmm[0] + (vmm[1] - vmm[0]) * (q * vinv);
             float v = grad[i];
             if (!std::isfinite(v)) v = 0.f;
             if (zero_grad) grad[i] = 0.f;
@@ -1210,13 +1214,14 @@ void oracle_adam_qq(
         float urange = std::max(no[1] - no[0], kEps), srange = std::max(no[3] - no[2], kEps);
         for (int64_t i = lo; i < hi; ++i) {
             float qf = std::min(std::max(std::round(vq * (xs[i - lo] - nv[0]) / vrange), 0.0f), vq);
-            if (value_bits == 8) value_packed[i] = (uint8_t)qf;
+            if (plain) value_f32[i] = xs[i - lo];
+            else if (value_bits == 8) value_packed[i] = (uint8_t)qf;
             else reinterpret_cast<uint16_t*>(value_packed)[i] = (uint16_t)qf;
             float uq = std::min(std::max(std::round(oq * (us[i - lo] - no[0]) / urange), 0.0f), oq);
             float sq = std::min(std::max(std::round(oq * (ss[i - lo] - no[2]) / srange), 0.0f), oq);
             optim_packed[2 * i] = (uint8_t)uq; optim_packed[2 * i + 1] = (uint8_t)sq;
         }
-        value_bounds[2 * b] = nv[0]; value_bounds[2 * b + 1] = nv[1];
+        if (!plain) { value_bounds[2 * b] = nv[0]; value_bounds[2 * b + 1] = nv[1]; }
         for (int k = 0; k < 4; ++k) optim_bounds[4 * b + k] = no[k];
     }
 }

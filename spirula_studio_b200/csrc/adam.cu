@@ -184,9 +184,12 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
     __shared__ uint32_t sh[6][2];
     const int64_t blk = first_block + blockIdx.x;
     const int64_t idx0 = blk * 256 + threadIdx.x * 4;
-    constexpr float vq = (float)((1 << VALUE_BITS) - 1), vinv = 1.0f / vq;
+    // VALUE_BITS == 32: the values are plain fp32 (only the optimiser state is quantised,
+    // fused_adam_step_quantized, src/kernels/optim/FusedAppearanceOptim.cu:137-271)
+    constexpr bool kPlainValue = VALUE_BITS == 32;
+    constexpr float vq = kPlainValue ? 1.0f : (float)((1u << (VALUE_BITS & 31)) - 1u), vinv = 1.0f / vq;
     const float oq = 255.0f, oinv = 1.0f / 255.0f;
-    const float2 vmm = value_bounds[blk];
+    const float2 vmm = kPlainValue ? make_float2(0.f, 0.f) : value_bounds[blk];
     const float4 omm = optim_bounds[blk];
     float x[4], u_new[4], s_new[4];
     bool inside[4];
@@ -196,7 +199,10 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
     if (full) {
         const float4 g4 = *(const float4*)(grad + idx0);
         gv[0] = g4.x; gv[1] = g4.y; gv[2] = g4.z; gv[3] = g4.w;
-        if (VALUE_BITS == 16) {
+        if (kPlainValue) {
+            const uint4 c = *(const uint4*)((const float*)value_packed + idx0);
+            vcode[0] = c.x; vcode[1] = c.y; vcode[2] = c.z; vcode[3] = c.w;      // raw fp32 bits
+        } else if (VALUE_BITS == 16) {
             const ushort4 c = *(const ushort4*)((const uint16_t*)value_packed + idx0);
             vcode[0] = c.x; vcode[1] = c.y; vcode[2] = c.z; vcode[3] = c.w;
         } else {
@@ -214,13 +220,14 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
         inside[k] = idx < numel_total;
         if (!full && inside[k]) {
             gv[k] = grad[idx];
-            vcode[k] = VALUE_BITS == 8 ? (uint32_t)value_packed[idx] : (uint32_t)((const uint16_t*)value_packed)[idx];
+            vcode[k] = kPlainValue ? ((const uint32_t*)value_packed)[idx]
+                                   : VALUE_BITS == 8 ? (uint32_t)value_packed[idx] : (uint32_t)((const uint16_t*)value_packed)[idx];
             ucode[k] = optim_packed[2 * idx]; scode[k] = optim_packed[2 * idx + 1];
             if (zero_grad) grad[idx] = 0.f;
         }
         x[k] = u_new[k] = s_new[k] = 0.f;
         if (inside[k]) {
-            float xv = vmm.x + (vmm.y - vmm.x) * ((float)vcode[k] * vinv);
+            float xv = kPlainValue ? __uint_as_float(vcode[k]) : vmm.x + (vmm.y - vmm.x) * ((float)vcode[k] * vinv);
             float v = gv[k];
             if (!isfinite(v)) v = 0.f;
             v *= grad_scale;
@@ -276,13 +283,14 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
     uint32_t vout[4], oout[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        vout[k] = (uint32_t)fminf(fmaxf(rintf((x[k] - vmin) * vscale), 0.0f), vq);
+        vout[k] = kPlainValue ? __float_as_uint(x[k]) : (uint32_t)fminf(fmaxf(rintf((x[k] - vmin) * vscale), 0.0f), vq);
         uint32_t uqc = (uint32_t)fminf(fmaxf(rintf((u_new[k] - umin) * uscale), 0.0f), oq);
         uint32_t sqc = (uint32_t)fminf(fmaxf(rintf((s_new[k] - smin) * sscale), 0.0f), oq);
         oout[k] = uqc | (sqc << 8);
     }
     if (full) {
-        if (VALUE_BITS == 16) *(ushort4*)((uint16_t*)value_packed + idx0) = make_ushort4(vout[0], vout[1], vout[2], vout[3]);
+        if (kPlainValue) *(uint4*)((float*)value_packed + idx0) = make_uint4(vout[0], vout[1], vout[2], vout[3]);
+        else if (VALUE_BITS == 16) *(ushort4*)((uint16_t*)value_packed + idx0) = make_ushort4(vout[0], vout[1], vout[2], vout[3]);
         else *(uchar4*)(value_packed + idx0) = make_uchar4(vout[0], vout[1], vout[2], vout[3]);
         *(uint2*)(optim_packed + 2 * idx0) = make_uint2(oout[0] | (oout[1] << 16), oout[2] | (oout[3] << 16));
     } else {
@@ -290,12 +298,14 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
         for (int k = 0; k < 4; ++k)
             if (inside[k]) {
                 const int64_t idx = idx0 + k;
-                if (VALUE_BITS == 8) value_packed[idx] = (uint8_t)vout[k]; else ((uint16_t*)value_packed)[idx] = (uint16_t)vout[k];
+                if (kPlainValue) ((uint32_t*)value_packed)[idx] = vout[k];
+                else if (VALUE_BITS == 8) value_packed[idx] = (uint8_t)vout[k];
+                else ((uint16_t*)value_packed)[idx] = (uint16_t)vout[k];
                 optim_packed[2 * idx] = (uint8_t)(oout[k] & 255u); optim_packed[2 * idx + 1] = (uint8_t)(oout[k] >> 8);
             }
     }
     if (threadIdx.x == 0) {
-        value_bounds[blk] = make_float2(vmin, vmax);
+        if (!kPlainValue) value_bounds[blk] = make_float2(vmin, vmax);
         optim_bounds[blk] = make_float4(umin, umax, smin, smax);
     }
 }
@@ -365,8 +375,9 @@ int ssb_adam_step_sh_quantized(float* d_grad, uint8_t* d_optim_packed, float* d_
                                int64_t first_cell, int64_t numel, int64_t numel_total,
                                const SsbAdamConfig* cfg, void* stream) {
     using namespace ssb;
-    SSB_REQUIRE(d_grad && d_optim_packed && d_optim_bounds && d_value_packed && d_value_bounds && cfg, "ssb_adam_step_sh_quantized: NULL argument");
-    SSB_REQUIRE(value_bits == 8 || value_bits == 16, "ssb_adam_step_sh_quantized: value_bits must be 8 or 16 (got %d)", value_bits);
+    SSB_REQUIRE(d_grad && d_optim_packed && d_optim_bounds && d_value_packed && cfg, "ssb_adam_step_sh_quantized: NULL argument");
+    SSB_REQUIRE(value_bits == 8 || value_bits == 16 || value_bits == 32, "ssb_adam_step_sh_quantized: value_bits must be 8, 16 or 32 (got %d)", value_bits);
+    SSB_REQUIRE(value_bits == 32 || d_value_bounds, "ssb_adam_step_sh_quantized: packed values need a bounds table");
     SSB_REQUIRE(first_cell >= 0 && (first_cell % 256) == 0 && numel >= 0 && first_cell + numel <= numel_total, "ssb_adam_step_sh_quantized: bad cell range");
     SSB_REQUIRE(cfg->step >= 1, "ssb_adam_step_sh_quantized: step must be >= 1");
     if (numel == 0) return SSB_OK;
@@ -375,7 +386,10 @@ int ssb_adam_step_sh_quantized(float* d_grad, uint8_t* d_optim_packed, float* d_
     const float decay = 2.0f * cfg->sh_reg_weight / (float)numel_total;
     unsigned blocks = (unsigned)ceil_div(numel, 256);
     int64_t end_total = first_cell + numel;   // cells beyond the range belong to another caller
-    if (value_bits == 8)
+    if (value_bits == 32)
+        adam_qq_kernel<32><<<blocks, 64, 0, (cudaStream_t)stream>>>(d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed,
+            (float2*)d_value_bounds, first_cell / 256, end_total, cfg->lr_features_sh * ibc1, ibc2, decay, 0.0f, cfg->grad_scale, cfg->zero_grad);
+    else if (value_bits == 8)
         adam_qq_kernel<8><<<blocks, 64, 0, (cudaStream_t)stream>>>(d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed,
             (float2*)d_value_bounds, first_cell / 256, end_total, cfg->lr_features_sh * ibc1, ibc2, decay, 0.0f, cfg->grad_scale, cfg->zero_grad);
     else

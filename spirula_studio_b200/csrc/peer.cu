@@ -31,31 +31,38 @@ constexpr int kPeerThreads = 256;
 
 __device__ __forceinline__ float4 load_peer_f4(const float4* p) { return __ldcv(p); }
 
-// own[seg] += sum over peers of peer[seg], fp32, 16 bytes per thread per step.
+// own[seg] += sum over peers of peer[seg], fp32, 16 bytes per thread per step.  The number of
+// ranks is a template parameter so that a thread's loads from all its peers are in flight together
+// (a loop with a run-time trip count waits for each peer's data before asking the next).
+template <int WORLD>
 __global__ void __launch_bounds__(kPeerThreads) peer_reduce_kernel(SsbPeerTable t) {
     const int64_t stride = (int64_t)gridDim.x * kPeerThreads;
     const int64_t tid = (int64_t)blockIdx.x * kPeerThreads + threadIdx.x;
     for (int s = 0; s < t.n_segments; ++s) {
         const SsbPeerSegment sg = t.seg[s];
         float* own = (float*)((char*)t.base[sg.buffer][t.self] + sg.offset_bytes);
+        const float4* peer[WORLD - 1];
+#pragma unroll
+        for (int k = 0; k < WORLD - 1; ++k) {
+            const int p = k < t.self ? k : k + 1;                 // every rank but this one, ascending
+            peer[k] = (const float4*)((const char*)t.base[sg.buffer][p] + sg.offset_bytes);
+        }
         const int64_t n_vec = sg.bytes / 16;
         for (int64_t v = tid; v < n_vec; v += stride) {
+            float4 x[WORLD - 1];
+#pragma unroll
+            for (int k = 0; k < WORLD - 1; ++k) x[k] = load_peer_f4(peer[k] + v);
             float4 acc = ((const float4*)own)[v];
-            for (int p = 0; p < t.world; ++p) {
-                if (p == t.self) continue;
-                const float4 x = load_peer_f4((const float4*)((const char*)t.base[sg.buffer][p] + sg.offset_bytes) + v);
-                acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
-            }
+#pragma unroll
+            for (int k = 0; k < WORLD - 1; ++k) { acc.x += x[k].x; acc.y += x[k].y; acc.z += x[k].z; acc.w += x[k].w; }
             ((float4*)own)[v] = acc;
         }
         // the last few floats of a segment whose length is not a multiple of 16 bytes
         const int64_t tail0 = n_vec * 4, n_f = sg.bytes / 4;
         for (int64_t i = tail0 + tid; i < n_f; i += stride) {
             float acc = own[i];
-            for (int p = 0; p < t.world; ++p) {
-                if (p == t.self) continue;
-                acc += __ldcv((const float*)((const char*)t.base[sg.buffer][p] + sg.offset_bytes) + i);
-            }
+#pragma unroll
+            for (int k = 0; k < WORLD - 1; ++k) acc += __ldcv((const float*)peer[k] + i);
             own[i] = acc;
         }
     }
@@ -226,7 +233,19 @@ int ssb_peer_reduce_f32(const SsbPeerTable* table, void* stream) {
     if (e) return e;
     if (table->world == 1 || table->n_segments == 0) return SSB_OK;
     if (table_has_multicast(table)) peer_reduce_mc_kernel<<<peer_grid(table), kPeerThreads, 0, (cudaStream_t)stream>>>(*table);
-    else peer_reduce_kernel<<<peer_grid(table), kPeerThreads, 0, (cudaStream_t)stream>>>(*table);
+    else {
+        const unsigned grid = peer_grid(table);
+        cudaStream_t st = (cudaStream_t)stream;
+        switch (table->world) {
+            case 2: peer_reduce_kernel<2><<<grid, kPeerThreads, 0, st>>>(*table); break;
+            case 3: peer_reduce_kernel<3><<<grid, kPeerThreads, 0, st>>>(*table); break;
+            case 4: peer_reduce_kernel<4><<<grid, kPeerThreads, 0, st>>>(*table); break;
+            case 5: peer_reduce_kernel<5><<<grid, kPeerThreads, 0, st>>>(*table); break;
+            case 6: peer_reduce_kernel<6><<<grid, kPeerThreads, 0, st>>>(*table); break;
+            case 7: peer_reduce_kernel<7><<<grid, kPeerThreads, 0, st>>>(*table); break;
+            default: peer_reduce_kernel<8><<<grid, kPeerThreads, 0, st>>>(*table); break;
+        }
+    }
     SSB_LAUNCHED("peer_reduce_kernel");
     return SSB_OK;
 }

@@ -119,6 +119,29 @@ def test_adam_quantized_sh(lib, U, oracle, bits):
         d_vp.copy_(U.dev(vp)); d_vb.copy_(U.dev(vb)); d_op.copy_(U.dev(op)); d_ob.copy_(U.dev(ob))
 
 
+def test_adam_quantized_state_fp32_values(lib, U, oracle):
+    """value_bits = 32: fp32 values, 8-bit optimiser state (the reference's fused_adam_step_quantized)."""
+    rng = np.random.default_rng(32)
+    n_cells = 45 * 700 + 5
+    x = rng.normal(0, 0.05, size=n_cells).astype(np.float32)
+    nb = (n_cells + 255) // 256
+    op, ob = np.zeros(n_cells * 2, np.uint8), np.zeros(nb * 4, np.float32)
+    d_x, d_op, d_ob = U.dev(x), U.dev(op), U.dev(ob)
+    for step in (1, 2, 3):
+        g = (rng.normal(size=n_cells) * 1e-3).astype(np.float32)
+        d_g = U.dev(g)
+        oracle.adam_qq(g.copy(), op, ob, x.view(np.uint8), np.zeros(2, np.float32), 32, step, 2.5e-3, grad_scale=0.5)
+        cfg_a = L.SsbAdamConfig(0, 0, 0, 0, 0, 2.5e-3, 0.0, 0.5, step, 1)
+        L.check(lib.ssb_adam_step_sh_quantized(L.ptr(d_g), L.ptr(d_op), L.ptr(d_ob), L.ptr(d_x), None, 32, 0, n_cells, n_cells, C.byref(cfg_a), None))
+        torch.cuda.synchronize()
+        assert float(d_g.abs().sum()) == 0.0
+        assert np.allclose(d_x.cpu().numpy(), x, rtol=1e-5, atol=1e-7)
+        do = np.abs(d_op.cpu().numpy().astype(np.int64) - op.astype(np.int64))
+        assert do.max() <= 1 and (do > 0).mean() <= 2e-2
+        assert np.allclose(d_ob.cpu().numpy(), ob, rtol=1e-4, atol=1e-6)
+        d_x.copy_(U.dev(x)); d_op.copy_(U.dev(op)); d_ob.copy_(U.dev(ob))
+
+
 def _oracle_iteration(oracle, cfg, sp, vm, K, targets, shq=None):
     """Gradients of one multi-view iteration, one camera per sub-batch, summed (reference split-batch loop)."""
     W, H, n = cfg.width, cfg.height, cfg.n_splats

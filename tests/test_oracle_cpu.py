@@ -259,6 +259,25 @@ def test_quant_codec_roundtrip(oracle):
         assert np.all(np.abs(x - y) <= 0.5 * step + 1e-7)
 
 
+def test_adam_quantized_state_with_fp32_values(oracle):
+    """Only the optimiser state quantised (value_bits = 32): the first step from a zero state uses this step's
+    unquantised moments, so it must equal the plain fp32 Adam step; later steps differ only by the state's 8-bit error."""
+    rng = np.random.default_rng(12)
+    n = 256 * 7 + 19
+    x0 = rng.normal(0, 0.05, size=n).astype(np.float32)
+    g = (rng.normal(size=n) * 1e-3).astype(np.float32)
+    xq = x0.copy()
+    op, ob = np.zeros(n * 2, np.uint8), np.zeros(((n + 255) // 256) * 4, np.float32)
+    oracle.adam_qq(g.copy(), op, ob, xq.view(np.uint8), np.zeros(2, np.float32), 32, 1, 2.5e-3, grad_scale=0.5)
+    xp, m1, m2 = x0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    oracle.adam_plain(xp, g.copy(), m1, m2, 1, 2.5e-3, 0.0, 0.0, 0.5)
+    assert np.allclose(xq, xp, rtol=0, atol=1e-7)
+    g2 = (rng.normal(size=n) * 1e-3).astype(np.float32)
+    oracle.adam_qq(g2.copy(), op, ob, xq.view(np.uint8), np.zeros(2, np.float32), 32, 2, 2.5e-3, grad_scale=0.5)
+    oracle.adam_plain(xp, g2.copy(), m1, m2, 2, 2.5e-3, 0.0, 0.0, 0.5)
+    assert np.abs(xq - xp).max() < 0.2 * 2.5e-3          # a step is at most lr; the state error moves it by a fraction
+
+
 def test_adam_first_step_moves_by_lr(oracle):
     """With zero moments the first bias-corrected Adam step is lr * sign(g)."""
     rng = np.random.default_rng(6)

@@ -345,6 +345,14 @@ int64_t ssb_step_device_bytes(const SsbStep* step);
 int ssb_step_views(SsbStep* step, const SsbSplats* params, const SsbShQuant* shq,
                    const float* d_viewmats, const float* d_intrins, const float* d_gt, int32_t n_views,
                    const SsbSplats* grads, int accumulate, float* d_losses, void* stream);
+/* The same, for targets that are still arriving: gt_ready[v] (a cudaEvent_t, or NULL) is waited for on
+ * the device just before view v's loss kernel, the first stage that reads its target image.  Projection,
+ * intersection and rasterisation of a view therefore overlap the host-to-device copy of its target, and
+ * one call covers a whole batch whose targets are copied view by view on another stream.
+ * gt_ready may be NULL (no gating).  No counterpart in the reference, whose targets are resident. */
+int ssb_step_views_gated(SsbStep* step, const SsbSplats* params, const SsbShQuant* shq,
+                         const float* d_viewmats, const float* d_intrins, const float* d_gt, int32_t n_views,
+                         void* const* gt_ready, const SsbSplats* grads, int accumulate, float* d_losses, void* stream);
 
 /* Pair count M of the last view processed (host copy taken after that view's
  * kernels finished; synchronises the stream). */

@@ -114,7 +114,7 @@ static int lane_alloc(SsbStep* s, SsbLane& l) {
 // All stages of one view on one stream.
 static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbShQuant* shq, const float* d_viewmats, const float* d_intrins,
                     const float* d_gt, int v, const SsbSplats* grads, int accumulate, float* d_losses, cudaStream_t st,
-                    cudaEvent_t wait_before_bwd, cudaEvent_t* ev) {
+                    cudaEvent_t wait_before_bwd, cudaEvent_t* ev, cudaEvent_t gt_ready) {
     const int64_t n = s->cfg.n_splats;
     const int W = s->cfg.width, H = s->cfg.height;
     const int64_t P = (int64_t)W * H;
@@ -136,6 +136,7 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
     SSB_MARK(4);
     if ((e = ssb_raster_fwd(l.screen, l.offsets, l.flat, l.n_isects, 1, W, H, l.rgb, l.depth, l.T, l.last_ids, st))) return e;
     SSB_MARK(5);
+    if (gt_ready) SSB_CUDA(cudaStreamWaitEvent(st, gt_ready, 0));      // the view's target image has landed
     if ((e = launch_loss(l.rgb, d_gt + (int64_t)v * P * 3, 1, H, W, s->cfg.w_l1, s->cfg.w_ssim, l.v_rgb, d_losses, st))) return e;
     SSB_MARK(6);
     if ((e = ssb_raster_bwd(l.screen, l.offsets, l.flat, l.n_isects, 1, W, H, l.depth, l.T, l.last_ids,
@@ -195,6 +196,12 @@ int64_t ssb_step_device_bytes(const SsbStep* step) { return step ? step->bytes :
 int ssb_step_views(SsbStep* s, const SsbSplats* params, const SsbShQuant* shq,
                    const float* d_viewmats, const float* d_intrins, const float* d_gt, int32_t n_views,
                    const SsbSplats* grads, int accumulate, float* d_losses, void* stream) {
+    return ssb_step_views_gated(s, params, shq, d_viewmats, d_intrins, d_gt, n_views, nullptr, grads, accumulate, d_losses, stream);
+}
+
+int ssb_step_views_gated(SsbStep* s, const SsbSplats* params, const SsbShQuant* shq,
+                         const float* d_viewmats, const float* d_intrins, const float* d_gt, int32_t n_views,
+                         void* const* gt_ready, const SsbSplats* grads, int accumulate, float* d_losses, void* stream) {
     using namespace ssb;
     SSB_REQUIRE(s && params && d_viewmats && d_intrins && d_gt && grads, "ssb_step_views: NULL argument");
     SSB_REQUIRE(n_views >= 0, "ssb_step_views: bad view count");
@@ -205,7 +212,7 @@ int ssb_step_views(SsbStep* s, const SsbSplats* params, const SsbShQuant* shq,
         for (int v = 0; v < n_views; ++v) {
             const bool prof = s->profiling && s->prof_views < SsbStep_kMaxProfViews;
             int e = run_view(s, s->lane[0], params, shq, d_viewmats, d_intrins, d_gt, v, grads, (accumulate || v > 0) ? 1 : 0, d_losses, user,
-                             nullptr, prof ? s->ev[s->prof_views] : nullptr);
+                             nullptr, prof ? s->ev[s->prof_views] : nullptr, gt_ready ? (cudaEvent_t)gt_ready[v] : nullptr);
             if (e) return e;
             if (prof) s->prof_views++;
         }
@@ -217,7 +224,8 @@ int ssb_step_views(SsbStep* s, const SsbSplats* params, const SsbShQuant* shq,
     cudaEvent_t prev_bwd = nullptr;
     for (int v = 0; v < n_views; ++v) {
         SsbLane& l = s->lane[v % s->n_lanes];
-        int e = run_view(s, l, params, shq, d_viewmats, d_intrins, d_gt, v, grads, (accumulate || v > 0) ? 1 : 0, d_losses, l.stream, prev_bwd, nullptr);
+        int e = run_view(s, l, params, shq, d_viewmats, d_intrins, d_gt, v, grads, (accumulate || v > 0) ? 1 : 0, d_losses, l.stream, prev_bwd, nullptr,
+                         gt_ready ? (cudaEvent_t)gt_ready[v] : nullptr);
         if (e) return e;
         SSB_CUDA(cudaEventRecord(l.bwd_done, l.stream));
         prev_bwd = l.bwd_done;

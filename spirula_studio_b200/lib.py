@@ -94,6 +94,7 @@ SIGNATURES = {
     "ssb_step_destroy": (None, [_P]),
     "ssb_step_device_bytes": (_I64, [_P]),
     "ssb_step_views": (C.c_int, [_P, _P, _P, _P, _P, _P, _I32, _P, C.c_int, _P, _P]),
+    "ssb_step_views_gated": (C.c_int, [_P, _P, _P, _P, _P, _P, _I32, _P, _P, C.c_int, _P, _P]),
     "ssb_step_last_isects": (C.c_int, [_P, _P, _P]),
     "ssb_step_peek": (C.c_int, [_P, _P, _P, _P, _P, _P, _P]),
     "ssb_step_set_profiling": (C.c_int, [_P, C.c_int]),

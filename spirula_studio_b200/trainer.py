@@ -303,59 +303,107 @@ class Trainer:
         self.allreduce_grads()
         self.optimizer_step(total_views)
 
-    def train_step(self, h_viewmats, h_intrins, h_gt, total_views, chunk=2):
+    def train_step(self, h_viewmats, h_intrins, h_gt, total_views, chunk=2, stale_loss=False):
         """One iteration from HOST buffers of one camera kind; see train_step_kinds."""
-        return self.train_step_kinds([(0, h_viewmats, h_intrins, h_gt)], total_views, chunk)
+        return self.train_step_kinds([(0, h_viewmats, h_intrins, h_gt)], total_views, chunk, stale_loss)
 
-    def train_step_kinds(self, batches, total_views, chunk=2):
+    def train_step_kinds(self, batches, total_views, chunk=2, stale_loss=False):
         """One iteration from HOST buffers (pinned torch tensors holding this rank's views, one entry
         (kind, viewmats, intrins, targets) per camera kind): host->device copies of cameras and targets,
         the iteration, and a device->host read of the loss scalars. Returns (l1, ssim, loss) averaged
         over this rank's views.
 
-        The targets are copied `chunk` views at a time on a side stream and each chunk is
-        rendered as soon as it has landed, so the PCIe transfer of later views hides behind
-        the computation of earlier ones."""
+        The targets are copied `chunk` views at a time on a side stream while the whole batch is enqueued
+        in one call per camera kind; on the device, only a view's loss stage waits for that view's target
+        (ssb_step_views_gated), so the PCIe transfer hides behind projection, intersection and rasterisation.
+
+        stale_loss=True returns the scalars of the PREVIOUS call instead (zeros on the first call), which
+        is how the reference reports its loss (one step late, src/kernels/loss/PerPixelLoss.cu:1374-1400):
+        the host then never waits for the iteration it has just enqueued, and the next call's copies
+        start while this one still computes (two sets of staging buffers alternate).  `last_losses()`
+        waits for and returns the newest values."""
         if self._copy_stream is None:
             self._copy_stream = torch.cuda.Stream(device=self.device)
+            self._loss_host = [torch.zeros(3, dtype=torch.float32).pin_memory() for _ in range(2)]
+            self._loss_ready = [torch.cuda.Event(), torch.cuda.Event()]
+            self._set_free = [None, None]          # event after which staging set k may be overwritten
+            self._loss_views = [1, 1]
+            self._calls = 0
         main = torch.cuda.current_stream(self.device)
+        k = self._calls & 1
         self.losses.zero_()
-        # the previous iteration may still be reading the staging buffers
-        self._copy_stream.wait_stream(main)
-        events = []
+        # staging set k was last read by the iteration before the previous one
+        if self._set_free[k] is not None:
+            self._copy_stream.wait_event(self._set_free[k])
+        calls = []          # (kind, views, per-view event handles, keep-alive list)
         nv_total = 0
         with torch.cuda.stream(self._copy_stream):
+            # cameras of every kind first (a few hundred bytes), then the targets view by view
             for kind, h_viewmats, h_intrins, h_gt in batches:
-                nv = int(h_viewmats.shape[0])
-                nv_total += nv
-                st = self._staging.get(kind)
+                st = self._staging.get((kind, k))
                 if st is None or st[2].shape != h_gt.shape:
                     st = (torch.empty_like(h_viewmats, device=self.device), torch.empty_like(h_intrins, device=self.device),
                           torch.empty_like(h_gt, device=self.device))
-                    self._staging[kind] = st
+                    self._staging[(kind, k)] = st
                 st[0].copy_(h_viewmats, non_blocking=True)
                 st[1].copy_(h_intrins, non_blocking=True)
+            cams_ready = torch.cuda.Event()
+            cams_ready.record(self._copy_stream)
+            for kind, h_viewmats, h_intrins, h_gt in batches:
+                nv = int(h_viewmats.shape[0])
+                nv_total += nv
+                st = self._staging[(kind, k)]
+                handles = (C.c_void_p * max(nv, 1))()
+                keep = []
                 c0 = 0
                 while c0 < nv:
-                    # the first copies are single views so that rendering can start as early as possible
-                    c1 = min(nv, c0 + (1 if len(events) < 2 else chunk))
+                    # the first copies are single views so that their loss stage can start as early as possible
+                    c1 = min(nv, c0 + (1 if c0 < 2 else chunk))
                     st[2][c0:c1].copy_(h_gt[c0:c1], non_blocking=True)
                     ev = torch.cuda.Event()
                     ev.record(self._copy_stream)
-                    events.append((kind, c0, c1, ev))
+                    keep.append(ev)
+                    for v in range(c0, c1):
+                        handles[v] = ev.cuda_event
                     c0 = c1
+                calls.append((kind, nv, handles, keep))
         if nv_total == 0:
             self.grads_flat.zero_()
-        for i, (kind, c0, c1, ev) in enumerate(events):
-            main.wait_event(ev)
-            d_view, d_intr, d_gt = self._staging[kind]
-            L.check(self.lib.ssb_step_views(self.handles[kind], C.byref(self._p_struct), C.byref(self.shq) if self.shq else None,
-                                            L.ptr(d_view[c0:]), L.ptr(d_intr[c0:]), L.ptr(d_gt[c0:]), c1 - c0,
-                                            C.byref(self._g_struct), 1 if i > 0 else 0, L.ptr(self.losses), None))
+        main.wait_event(cams_ready)
+        first = True
+        for kind, nv, handles, keep in calls:
+            if nv == 0:
+                continue
+            d_view, d_intr, d_gt = self._staging[(kind, k)]
+            # one call per camera kind: each view's loss stage waits on the device for its own target
+            L.check(self.lib.ssb_step_views_gated(self.handles[kind], C.byref(self._p_struct), C.byref(self.shq) if self.shq else None,
+                                                  L.ptr(d_view), L.ptr(d_intr), L.ptr(d_gt), nv, handles,
+                                                  C.byref(self._g_struct), 0 if first else 1, L.ptr(self.losses), None))
+            first = False
+        self._keep_events = [c[3] for c in calls]      # the events must outlive the work that waits on them
         self.allreduce_grads()
         self.optimizer_step(total_views)
-        out = self.losses.cpu()
-        return tuple((out / max(nv_total, 1)).tolist())
+        # device -> host read of this step's scalars (asynchronous: pinned destination)
+        self._loss_host[k].copy_(self.losses, non_blocking=True)
+        self._loss_ready[k].record(main)
+        self._loss_views[k] = max(nv_total, 1)
+        done = torch.cuda.Event()
+        done.record(main)
+        self._set_free[k] = done
+        self._calls += 1
+        if not stale_loss:
+            return self.last_losses()
+        if self._calls == 1:
+            return (0.0, 0.0, 0.0)
+        p = 1 - k
+        self._loss_ready[p].synchronize()
+        return tuple((self._loss_host[p] / self._loss_views[p]).tolist())
+
+    def last_losses(self):
+        """(l1, ssim, loss) of the newest host-buffer step, averaged over this rank's views; waits for it."""
+        k = (self._calls - 1) & 1
+        self._loss_ready[k].synchronize()
+        return tuple((self._loss_host[k] / self._loss_views[k]).tolist())
 
     def last_isects(self, kind=0):
         m = C.c_int64(0)

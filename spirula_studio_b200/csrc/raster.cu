@@ -124,8 +124,9 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
             n_hit += __popc(bal);
         }
         __syncwarp();
+#pragma unroll 8
         for (int k = 0; k < n_hit; ++k) {
-            if ((k & 3) == 0 && __all_sync(0xffffffffu, done)) break;
+            if ((k & 7) == 0 && __all_sync(0xffffffffu, done)) break;
             const int e = hits[w][k];
             const float4 a = sA[e], b = sQ[e];
             const float dx = a.x - px, dy = a.y - py;

@@ -206,14 +206,16 @@ int ssb_tile_ranges(const int64_t* d_sorted_ids, const int64_t* d_n, int64_t cap
 
 /* Replaces rasterize_to_pixels_3dgs_fwd (src/kernels/raster/RasterizationFwd.cu:147-185,
  * kernel src/kernels/raster/RasterizationEval3DFwd_kernel.cuh:48-313, 2D variant).
- * Outputs: d_rgb [I][H][W][3], d_depth [I][H][W], d_T [I][H][W], d_last_ids [I][H][W]. */
+ * Outputs: d_rgb [I][H][W][3], d_depth [I][H][W], d_T [I][H][W], d_last_ids [I][H][W].
+ * d_depth may be NULL when the depth image is not needed (its accumulation is then compiled out). */
 int ssb_raster_fwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids,
                    const int64_t* d_n_isects, int32_t n_images, int32_t width, int32_t height,
                    float* d_rgb, float* d_depth, float* d_T, int32_t* d_last_ids, void* stream);
 
 /* Replaces rasterize_to_pixels_3dgs_bwd (src/kernels/raster/RasterizationBwd.cu:253-291,
  * kernel src/kernels/raster/RasterizationEval3DBwd_kernel.cuh:48-636, 2D variant).
- * d_v_depth and d_v_T may be NULL (treated as zero).  Gradients are ADDED into
+ * d_v_depth and d_v_T may be NULL (treated as zero; without d_v_depth the depth channel is compiled
+ * out and d_render_depth may be NULL too).  Gradients are ADDED into
  * d_v_screen [pairs] (layout as in ssb_project_bwd); the caller zeroes it. */
 int ssb_raster_bwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids,
                    const int64_t* d_n_isects, int32_t n_images, int32_t width, int32_t height,

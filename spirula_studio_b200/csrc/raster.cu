@@ -62,6 +62,7 @@ __device__ __forceinline__ bool ellipse_reaches_box(float4 b, float x0, float x1
     return ellipse_test(ellipse_test_setup(b), x0, x1, y0, y1);
 }
 
+template <bool DEPTH>
 __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
     const SsbScreenRec* __restrict__ screen, const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ flatten_ids,
     const int64_t* __restrict__ n_isects_ptr, int I, int W, int H, int tw, int th,
@@ -139,7 +140,8 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
             if (next_T > kTransmitThreshold) {
                 const float4 c = sC[e];
                 const float wgt = alpha * T;
-                acc_r += c.x * wgt; acc_g += c.y * wgt; acc_b += c.z * wgt; acc_d += c.w * wgt;
+                acc_r += c.x * wgt; acc_g += c.y * wgt; acc_b += c.z * wgt;
+                if (DEPTH) acc_d += c.w * wgt;
                 cur_idx = batch_start + e;
                 T = next_T;
             } else {
@@ -152,7 +154,7 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
         out_T[pix] = T;
         const float invW = 1.0f / fmaxf(1.0f - T, 1e-10f);
         out_rgb[3 * pix] = acc_r; out_rgb[3 * pix + 1] = acc_g; out_rgb[3 * pix + 2] = acc_b;
-        out_depth[pix] = acc_d * invW;
+        if (DEPTH) out_depth[pix] = acc_d * invW;
         last_ids[pix] = cur_idx;
     }
 }
@@ -160,6 +162,7 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
 constexpr int kBwdWarps = 4;          // one 16x16 tile per CTA, one 8x8 micro-tile per warp
 constexpr int kSurvCap = 256;         // survivors collected per segment (8 per lane)
 
+template <bool DEPTH>
 __global__ void __launch_bounds__(kBwdWarps * 32, 10) raster_bwd_kernel(
     const SsbScreenRec* __restrict__ screen, const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ flatten_ids,
     const int64_t* __restrict__ n_isects_ptr, int I, int W, int H, int tw, int th,
@@ -196,10 +199,13 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 10) raster_bwd_kernel(
             last = last_ids[pix];
             T1 = render_T[pix];
             vT1 = v_T ? v_T[pix] : 0.f;
-            vc = make_float4(v_rgb[3 * pix], v_rgb[3 * pix + 1], v_rgb[3 * pix + 2], v_depth ? v_depth[pix] : 0.f);
-            const float inv_alpha = 1.0f / fmaxf(1.0f - T1, 1e-10f);
-            vT1 += render_depth[pix] * vc.w * inv_alpha;
-            vc.w *= inv_alpha;
+            vc = make_float4(v_rgb[3 * pix], v_rgb[3 * pix + 1], v_rgb[3 * pix + 2], 0.f);
+            if (DEPTH) {
+                vc.w = v_depth[pix];
+                const float inv_alpha = 1.0f / fmaxf(1.0f - T1, 1e-10f);
+                vT1 += render_depth[pix] * vc.w * inv_alpha;
+                vc.w *= inv_alpha;
+            }
         }
         sP[w][p] = make_float4(T1, vT1, (float)x + 0.5f, (float)y + 0.5f);
         sV[w][p] = vc;
@@ -268,7 +274,8 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 10) raster_bwd_kernel(
                         const float4 vc = sV[w][p];
                         const float om = 1.0f - alpha;
                         const float T0 = __fdividef(pp.x, om);
-                        const float cdot = fmaf(c.x, vc.x, fmaf(c.y, vc.y, fmaf(c.z, vc.z, c.w * vc.w)));
+                        const float cdot = DEPTH ? fmaf(c.x, vc.x, fmaf(c.y, vc.y, fmaf(c.z, vc.z, c.w * vc.w)))
+                                                 : fmaf(c.x, vc.x, fmaf(c.y, vc.y, c.z * vc.z));
                         const float v_alpha = T0 * (cdot - pp.y);
                         const float wgt = alpha * T0;
                         const float v_T0 = fmaf(alpha, cdot, pp.y * om);
@@ -280,7 +287,8 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 10) raster_bwd_kernel(
                         s_xx = fmaf(sx, dx, s_xx); s_xy = fmaf(sx, dy, s_xy); s_yy = fmaf(sy, dy, s_yy);
                         s_x += sx; s_y += sy;
                         gop += va;
-                        gr = fmaf(vc.x, wgt, gr); gg = fmaf(vc.y, wgt, gg); gb = fmaf(vc.z, wgt, gb); gd = fmaf(vc.w, wgt, gd);
+                        gr = fmaf(vc.x, wgt, gr); gg = fmaf(vc.y, wgt, gg); gb = fmaf(vc.z, wgt, gb);
+                        if (DEPTH) gd = fmaf(vc.w, wgt, gd);
                         *(float2*)&sP[w][p] = make_float2(T0, v_T0);
                     }
                 }
@@ -310,13 +318,17 @@ int ssb_raster_fwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, 
                    const int64_t* d_n_isects, int32_t n_images, int32_t width, int32_t height,
                    float* d_rgb, float* d_depth, float* d_T, int32_t* d_last_ids, void* stream) {
     using namespace ssb;
-    SSB_REQUIRE(d_screen && d_tile_offsets && d_flatten_ids && d_n_isects && d_rgb && d_depth && d_T && d_last_ids, "ssb_raster_fwd: NULL argument");
+    SSB_REQUIRE(d_screen && d_tile_offsets && d_flatten_ids && d_n_isects && d_rgb && d_T && d_last_ids, "ssb_raster_fwd: NULL argument");
     SSB_REQUIRE(n_images >= 0 && width > 0 && height > 0, "ssb_raster_fwd: bad sizes");
     if (n_images == 0) return SSB_OK;
     int tw = (width + kTile - 1) / kTile, th = (height + kTile - 1) / kTile;
     dim3 grid(tw, th, n_images);
-    raster_fwd_kernel<<<grid, kFwdThreads, 0, (cudaStream_t)stream>>>(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height,
-                                                                    tw, th, d_rgb, d_depth, d_T, d_last_ids);
+    if (d_depth)
+        raster_fwd_kernel<true><<<grid, kFwdThreads, 0, (cudaStream_t)stream>>>(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height,
+                                                                              tw, th, d_rgb, d_depth, d_T, d_last_ids);
+    else
+        raster_fwd_kernel<false><<<grid, kFwdThreads, 0, (cudaStream_t)stream>>>(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height,
+                                                                               tw, th, d_rgb, nullptr, d_T, d_last_ids);
     SSB_LAUNCHED("raster_fwd_kernel");
     return SSB_OK;
 }
@@ -327,14 +339,19 @@ int ssb_raster_bwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, 
                    const float* d_v_rgb, const float* d_v_depth, const float* d_v_T,
                    SsbScreenRec* d_v_screen, void* stream) {
     using namespace ssb;
-    SSB_REQUIRE(d_screen && d_tile_offsets && d_flatten_ids && d_n_isects && d_render_depth && d_T && d_last_ids && d_v_rgb && d_v_screen,
+    SSB_REQUIRE(d_screen && d_tile_offsets && d_flatten_ids && d_n_isects && (d_render_depth || !d_v_depth) && d_T && d_last_ids && d_v_rgb && d_v_screen,
                 "ssb_raster_bwd: NULL argument");
     SSB_REQUIRE(n_images >= 0 && width > 0 && height > 0, "ssb_raster_bwd: bad sizes");
     if (n_images == 0) return SSB_OK;
     int tw = (width + kTile - 1) / kTile, th = (height + kTile - 1) / kTile;
     dim3 grid(tw, th, n_images);
-    raster_bwd_kernel<<<grid, kBwdWarps * 32, 0, (cudaStream_t)stream>>>(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height,
-                                                                       tw, th, d_render_depth, d_T, d_last_ids, d_v_rgb, d_v_depth, d_v_T, d_v_screen);
+    // without a depth cotangent the depth channel carries exact zeros: that arithmetic is compiled out
+    if (d_v_depth)
+        raster_bwd_kernel<true><<<grid, kBwdWarps * 32, 0, (cudaStream_t)stream>>>(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height,
+                                                                                 tw, th, d_render_depth, d_T, d_last_ids, d_v_rgb, d_v_depth, d_v_T, d_v_screen);
+    else
+        raster_bwd_kernel<false><<<grid, kBwdWarps * 32, 0, (cudaStream_t)stream>>>(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height,
+                                                                                  tw, th, d_render_depth, d_T, d_last_ids, d_v_rgb, nullptr, d_v_T, d_v_screen);
     SSB_LAUNCHED("raster_bwd_kernel");
     return SSB_OK;
 }

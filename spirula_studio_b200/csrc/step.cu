@@ -33,7 +33,7 @@ struct SsbLane {
     int32_t* flat;        // sorted pair indices
     int64_t* n_isects;    // device
     int32_t* offsets;     // [tiles]
-    float* rgb; float* depth; float* T; int32_t* last_ids; float* v_rgb;
+    float* rgb; float* T; int32_t* last_ids; float* v_rgb;
     cudaStream_t stream;
     cudaEvent_t bwd_done;  // this lane's last projection backward
     cudaEvent_t all_done;
@@ -77,7 +77,7 @@ static void lane_free(SsbLane& l) {
     cudaFree(l.aabb); cudaFree(l.depths); cudaFree(l.screen); cudaFree(l.v_screen);
     cudaFree(l.isect_ws); cudaFree(l.flat);
     cudaFree(l.n_isects); cudaFree(l.offsets);
-    cudaFree(l.rgb); cudaFree(l.depth); cudaFree(l.T); cudaFree(l.last_ids); cudaFree(l.v_rgb);
+    cudaFree(l.rgb); cudaFree(l.T); cudaFree(l.last_ids); cudaFree(l.v_rgb);
     if (l.stream) cudaStreamDestroy(l.stream);
     if (l.bwd_done) cudaEventDestroy(l.bwd_done);
     if (l.all_done) cudaEventDestroy(l.all_done);
@@ -98,7 +98,6 @@ static int lane_alloc(SsbStep* s, SsbLane& l) {
     if (!e) e = dev_alloc(&l.n_isects, 1, tot);
     if (!e) e = dev_alloc(&l.offsets, (int64_t)s->tw * s->th + 1, tot);
     if (!e) e = dev_alloc(&l.rgb, P * 3, tot);
-    if (!e) e = dev_alloc(&l.depth, P, tot);
     if (!e) e = dev_alloc(&l.T, P, tot);
     if (!e) e = dev_alloc(&l.last_ids, P, tot);
     if (!e) e = dev_alloc(&l.v_rgb, P * 3, tot);
@@ -134,12 +133,13 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
                                  l.offsets, l.n_isects, st, ev ? ev[2] : nullptr))) return e;
     SSB_MARK(3);
     SSB_MARK(4);
-    if ((e = ssb_raster_fwd(l.screen, l.offsets, l.flat, l.n_isects, 1, W, H, l.rgb, l.depth, l.T, l.last_ids, st))) return e;
+    // the loss has no depth term, so the depth image is neither rendered nor back-propagated
+    if ((e = ssb_raster_fwd(l.screen, l.offsets, l.flat, l.n_isects, 1, W, H, l.rgb, nullptr, l.T, l.last_ids, st))) return e;
     SSB_MARK(5);
     if (gt_ready) SSB_CUDA(cudaStreamWaitEvent(st, gt_ready, 0));      // the view's target image has landed
     if ((e = launch_loss(l.rgb, d_gt + (int64_t)v * P * 3, 1, H, W, s->cfg.w_l1, s->cfg.w_ssim, l.v_rgb, d_losses, st))) return e;
     SSB_MARK(6);
-    if ((e = ssb_raster_bwd(l.screen, l.offsets, l.flat, l.n_isects, 1, W, H, l.depth, l.T, l.last_ids,
+    if ((e = ssb_raster_bwd(l.screen, l.offsets, l.flat, l.n_isects, 1, W, H, nullptr, l.T, l.last_ids,
                             l.v_rgb, nullptr, nullptr, l.v_screen, st))) return e;
     SSB_MARK(7);
     if (wait_before_bwd) SSB_CUDA(cudaStreamWaitEvent(st, wait_before_bwd, 0));
@@ -286,7 +286,7 @@ int ssb_step_peek(SsbStep* s, const float** d_rgb, const float** d_depth, const 
     SSB_REQUIRE(s, "ssb_step_peek: NULL step");
     SsbLane& l = s->lane[s->last_lane];
     if (d_rgb) *d_rgb = l.rgb;
-    if (d_depth) *d_depth = l.depth;
+    if (d_depth) *d_depth = nullptr;      // the step renders no depth image (its loss has no depth term)
     if (d_T) *d_T = l.T;
     if (d_last_ids) *d_last_ids = l.last_ids;
     if (d_screen) *d_screen = l.screen;

@@ -308,6 +308,16 @@ def run_ours(args, cfg, rank, world, local_rank):
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
     clocks = sampler.stop() if sampler else None
 
+    # ---- where the gradient exchange spends its time (own pass, normal overlapped step)
+    exchange = None
+    if world > 1 and tr.grad_sync in ("peer", "multimem"):
+        tr.trace = []
+        n_tr = max(2, min(args.steps, 5))
+        for _ in range(n_tr):
+            tr.step_device_kinds(resident, total_views)
+        exchange = {k: round(v / n_tr, 4) for k, v in tr.exchange_breakdown().items()}
+        tr.trace = None
+
     # ---- per-stage device times (separate pass, CUDA events inside the library)
     stage_ms = [np.zeros(len(L.STAGES), np.float32) for _ in range(n_kinds)]
     n_prof = [0] * n_kinds
@@ -391,6 +401,8 @@ def run_ours(args, cfg, rank, world, local_rank):
             "losses_last": {"l1": losses[0], "ssim": losses[1], "loss": losses[2]},
             "device_bytes": tr.device_bytes(),
         }
+        if exchange is not None:
+            line["exchange_ms_rank0"] = exchange
         if world == 1 and not args.no_cpu_baseline:
             cfg_cpu = cfg
             v, t_iter, t_view, t_adam, cores = cpu_port_run(cfg_cpu, 2, 0)

@@ -265,8 +265,27 @@ class Trainer:
         if self.grad_sync == "nccl":
             torch.distributed.all_reduce(self.grads_flat, op=torch.distributed.ReduceOp.SUM, group=self.pg)
         elif self.grad_sync in ("peer", "multimem"):
+            self._mark("views_done")
             self._barrier()                                       # every rank's backward passes are complete
+            self._mark("barrier1")
             L.check(self.lib.ssb_peer_reduce_f32(C.byref(self._reduce_table), None))
+            self._mark("reduce")
+
+    def _mark(self, name):
+        """With self.trace set (a list), records a CUDA event under `name`; see exchange_breakdown()."""
+        if getattr(self, "trace", None) is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.trace.append((name, ev))
+
+    def exchange_breakdown(self):
+        """Milliseconds between consecutive marks of the traced iterations, summed by the later mark's name."""
+        torch.cuda.synchronize(self.device)
+        out = {}
+        for (n0, e0), (n1, e1) in zip(self.trace[:-1], self.trace[1:]):
+            if n1 != "views_done":
+                out[n1] = out.get(n1, 0.0) + e0.elapsed_time(e1)
+        return out
 
     def optimizer_step(self, total_views, stream=None):
         lr = self.cfg.lrs
@@ -282,8 +301,11 @@ class Trainer:
                                                         L.ptr(self.sh_optim_bounds), L.ptr(self.sh_packed), L.ptr(self.sh_bounds),
                                                         self.cfg.sh_value_bits, f * 45, c * 45, cells, C.byref(cfg), stream))
         if self.grad_sync in ("peer", "multimem"):
+            self._mark("adam")
             L.check(self.lib.ssb_peer_broadcast(C.byref(self._bcast_table), stream))
+            self._mark("broadcast")
             self._barrier()                                       # every replica is complete before the next forward
+            self._mark("barrier2")
 
     # -- whole iteration ---------------------------------------------------
     def step_device(self, d_viewmats, d_intrins, d_gt, n_local_views, total_views):

@@ -52,8 +52,8 @@ WORKLOAD = "mid_1m"
 # DRAM bytes one launch moves (dram__bytes_read.sum + dram__bytes_write.sum), from one ncu pass over this
 # file's own command on the mid_1m workload, one view per launch (a stage of several kernels: their sum).
 # The capture and its command are summarised in profiles/all_kernels_mid1m_counters.md.
-NCU_TRAFFIC_MID1M = {"project_fwd": 184.3e6, "tile_keys": 190.5e6, "sort": 35.6e6, "raster_fwd": 78.3e6,
-                     "loss": 51.9e6, "raster_bwd": 121.3e6, "project_bwd": 430.5e6, "adam": 846.8e6}
+NCU_TRAFFIC_MID1M = {"project_fwd": 184.3e6, "tile_keys": 190.5e6, "sort": 35.6e6, "raster_fwd": 68.6e6,
+                     "loss": 51.9e6, "raster_bwd": 111.3e6, "project_bwd": 430.5e6, "adam": 846.8e6}
 
 
 def shard(total, world, rank):

@@ -101,6 +101,21 @@ int ssb_project_fwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n,
                     float* d_aabb, float* d_depths, float* d_radii, SsbScreenRec* d_screen,
                     void* stream);
 
+/* Replaces projection_3dgs_packed_forward (src/kernels/projection/ProjectionPackedFwd.cu:64-158): the
+ * same projection, but only the visible (view, splat) pairs are returned, compacted in (view-major,
+ * splat-minor) order, with d_camera_ids[v] / d_gaussian_ids[v] naming the view and splat of packed
+ * pair v.  The pair count V goes to *d_n_visible (and, if h_n_visible is given, to the host after a
+ * stream synchronisation, as the reference reads it back).  Outputs hold `capacity` pairs; pairs beyond
+ * it are dropped and reported (SSB_ERR_CAPACITY when the host count is requested).  The packed arrays
+ * feed ssb_intersect_tiles_packed and, through its flatten ids, the rasterisers unchanged.
+ * Workspace: ssb_project_fwd_packed_workspace_bytes(n, views) (the pairs are projected once into it). */
+int64_t ssb_project_fwd_packed_workspace_bytes(int64_t n, int32_t n_views);
+int ssb_project_fwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams,
+                           void* d_workspace, int64_t workspace_bytes,
+                           float* d_aabb, float* d_depths, float* d_radii, SsbScreenRec* d_screen,
+                           int32_t* d_camera_ids, int32_t* d_gaussian_ids, int64_t capacity,
+                           int64_t* d_n_visible, int64_t* h_n_visible, void* stream);
+
 /* Replaces projection_3dgs_backward (src/kernels/projection/ProjectionBwd.cu:134,
  * kernel src/kernels/projection/ProjectionBwd_kernel.cuh:16-130): vjp of the
  * projection and of SH-to-colour for every kept pair, summed over the views of
@@ -195,6 +210,15 @@ int ssb_intersect_tiles(const float* d_aabb, const float* d_depths, const SsbScr
                         void* d_workspace, int64_t workspace_bytes,
                         int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
                         int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream);
+
+/* ssb_intersect_tiles for packed pairs (the packed branch of do_intersect_tile_generic): the image of
+ * pair v is d_camera_ids[v], the number of pairs is read from *d_n_pairs on the device (at most
+ * max_pairs), and the flatten ids written are packed pair indices.  Workspace as for
+ * ssb_intersect_tiles with n_images * tiles. */
+int ssb_intersect_tiles_packed(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen, const int32_t* d_camera_ids,
+                               const int64_t* d_n_pairs, int64_t max_pairs, int32_t n_images, int32_t width, int32_t height,
+                               void* d_workspace, int64_t workspace_bytes, int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                               int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream);
 
 /* Replaces intersect_offset_kernel (src/kernels/tile/IntersectTile.cu:271-307).
  * d_offsets [n_tiles_total] int32: first sorted index of each tile; tiles after

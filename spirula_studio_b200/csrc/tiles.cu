@@ -359,6 +359,36 @@ __global__ void __launch_bounds__(256) depth_range_kernel(const float4* __restri
     }
 }
 
+// The same for packed pairs, whose image is looked up per pair and whose count lives on the device.
+__global__ void __launch_bounds__(256) depth_range_ids_kernel(const float4* __restrict__ aabb, const float* __restrict__ depths, int64_t max_pairs,
+                                                              const int64_t* __restrict__ total_ptr, const int32_t* __restrict__ image_ids,
+                                                              uint32_t* __restrict__ range) {
+    const int64_t total = min(max_pairs, *total_ptr);
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t base = (int64_t)blockIdx.x * blockDim.x; base < total; base += stride) {      // warp-uniform trip count
+        const int64_t idx = base + threadIdx.x;
+        uint32_t nlo = 0u, hi = 0u;
+        int img = -1;
+        if (idx < total) {
+            const float4 bb = aabb[idx];
+            if (bb.z > bb.x && bb.w > bb.y) {
+                const uint32_t du = depth_word(depths[idx]);
+                nlo = ~du; hi = du; img = image_ids[idx];
+            }
+        }
+        // pairs are image-major, so a warp nearly always holds one image
+        const int img0 = __reduce_max_sync(0xffffffffu, img);
+        if (img0 < 0) continue;
+        if (__all_sync(0xffffffffu, img == img0 || img < 0)) {
+            nlo = __reduce_max_sync(0xffffffffu, nlo);
+            hi = __reduce_max_sync(0xffffffffu, hi);
+            if ((threadIdx.x & 31) == 0) { atomicMax(&range[2 * img0], nlo); atomicMax(&range[2 * img0 + 1], hi); }
+        } else if (img >= 0) {
+            atomicMax(&range[2 * img], nlo); atomicMax(&range[2 * img + 1], hi);
+        }
+    }
+}
+
 __device__ __forceinline__ int depth_bucket(uint32_t du, uint32_t lo, uint32_t hi) {
     const uint32_t span = hi - lo;
     const int used = 32 - __clz(span);                       // bits the offsets occupy (0 when span == 0)
@@ -372,7 +402,9 @@ template <bool EMIT>
 __global__ void __launch_bounds__(kBinThreads) bin_pass_kernel(
     const float4* __restrict__ aabb, const float* __restrict__ depths, const SsbScreenRec* __restrict__ screen, int64_t total,
     int64_t n_per_image, int tw, int th, const uint32_t* __restrict__ range, int32_t* __restrict__ bins, int64_t capacity,
-    uint64_t* __restrict__ pairs) {
+    uint64_t* __restrict__ pairs, const int32_t* __restrict__ image_ids, const int64_t* __restrict__ total_ptr) {
+    // packed input: the image of a pair comes from image_ids and the pair count from device memory
+    if (total_ptr) total = min(total, *total_ptr);
     const int lane = threadIdx.x & 31;
     const int64_t idx = (int64_t)blockIdx.x * kBinThreads + threadIdx.x;
     // ---- this lane's splat
@@ -390,7 +422,7 @@ __global__ void __launch_bounds__(kBinThreads) bin_pass_kernel(
                 cx = ra.x; cy = ra.y;
                 row_mode = tile_row_mode(g) ? 1 : 0;
                 lines = row_mode ? g.ymax - g.ymin : g.xmax - g.xmin;
-                const int64_t img = idx / n_per_image;
+                const int64_t img = image_ids ? (int64_t)image_ids[idx] : idx / n_per_image;
                 du = depth_word(depths[idx]);
                 bin0 = (int32_t)(img * tw * th) * kDepthBuckets + depth_bucket(du, ~range[2 * img], range[2 * img + 1]);
             }
@@ -488,7 +520,7 @@ __global__ void __launch_bounds__(kTilesBlock) bins_apply_kernel(int32_t* __rest
         const int excl = carry_s + woff + inc - v;
         if (i < n_bins) {
             bins[i] = excl;
-            if ((i & (kDepthBuckets - 1)) == 0) offsets[i >> kDepthBucketBits] = excl;
+            if (offsets && (i & (kDepthBuckets - 1)) == 0) offsets[i >> kDepthBucketBits] = excl;
         }
         __syncthreads();
         if (threadIdx.x == kTilesBlock - 1) carry_s = excl + v;
@@ -680,18 +712,46 @@ namespace ssb {
 
 // ssb_intersect_tiles with an optional event recorded between the scatter and the per-tile sort
 // (the step object times the two halves separately).
+// Packed input (d_image_ids != NULL): `total` is the most pairs there can be, the actual count is read from
+// d_total on the device, and n_per_image is ignored in favour of n_images_packed.
+static int intersect_tiles_impl(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
+                        int64_t total, int64_t n_per_image, int32_t width, int32_t height,
+                        void* d_workspace, int64_t workspace_bytes,
+                        int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                        int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort,
+                        const int32_t* d_image_ids, const int64_t* d_total, int64_t n_images_packed);
+
 int launch_intersect_tiles(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
                         int64_t total, int64_t n_per_image, int32_t width, int32_t height,
                         void* d_workspace, int64_t workspace_bytes,
                         int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
                         int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort) {
+    return intersect_tiles_impl(d_aabb, d_depths, d_screen, total, n_per_image, width, height, d_workspace, workspace_bytes, d_isect_ids,
+                                d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, mark_before_sort, nullptr, nullptr, 0);
+}
+
+int launch_intersect_tiles_packed(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen, const int32_t* d_image_ids,
+                                  const int64_t* d_total, int64_t max_pairs, int64_t n_images, int32_t width, int32_t height,
+                                  void* d_workspace, int64_t workspace_bytes, int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                                  int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream) {
+    SSB_REQUIRE(d_image_ids && d_total && n_images > 0, "ssb_intersect_tiles_packed: NULL argument");
+    return intersect_tiles_impl(d_aabb, d_depths, d_screen, max_pairs, 1, width, height, d_workspace, workspace_bytes, d_isect_ids,
+                                d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, nullptr, d_image_ids, d_total, n_images);
+}
+
+static int intersect_tiles_impl(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
+                        int64_t total, int64_t n_per_image, int32_t width, int32_t height,
+                        void* d_workspace, int64_t workspace_bytes,
+                        int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                        int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort,
+                        const int32_t* d_image_ids, const int64_t* d_total, int64_t n_images_packed) {
     SSB_REQUIRE(d_aabb && d_depths && d_screen && d_workspace && d_flatten_ids && d_tile_offsets && d_n_isects, "ssb_intersect_tiles: NULL argument");
     SSB_REQUIRE(total >= 0 && n_per_image > 0 && width > 0 && height > 0 && capacity >= 0, "ssb_intersect_tiles: bad sizes");
     SSB_REQUIRE(total < ((int64_t)1 << 31) && capacity < ((int64_t)1 << 31), "ssb_intersect_tiles: pair indices and positions must fit int32");
-    SSB_REQUIRE(total % n_per_image == 0, "ssb_intersect_tiles: total must be a whole number of images");
+    SSB_REQUIRE(d_image_ids || total % n_per_image == 0, "ssb_intersect_tiles: total must be a whole number of images");
     cudaStream_t st = (cudaStream_t)stream;
     const int tw = (width + kTile - 1) / kTile, th = (height + kTile - 1) / kTile;
-    const int64_t n_images = total / n_per_image;
+    const int64_t n_images = d_image_ids ? n_images_packed : total / n_per_image;
     const int64_t n_tiles = n_images * tw * th;
     SSB_REQUIRE(workspace_bytes >= ssb_intersect_tiles_workspace_bytes(n_tiles, capacity), "ssb_intersect_tiles: workspace too small");
     if (total == 0) {
@@ -708,10 +768,12 @@ int launch_intersect_tiles(const float* d_aabb, const float* d_depths, const Ssb
     int32_t* chunk_sums = (int32_t*)((char*)bins + align_up(n_bins * 4, 256));
     uint64_t* pairs = (uint64_t*)((char*)chunk_sums + align_up(chunks * 4, 256));
     SSB_CUDA(cudaMemsetAsync(ws, 0, (size_t)(kRangeBytes + n_bins * 4), st));     // depth ranges and bin counters
-    depth_range_kernel<<<(unsigned)(ceil_div(total, 256) < 148 * 8 ? ceil_div(total, 256) : 148 * 8), 256, 0, st>>>((const float4*)d_aabb, d_depths, total, n_per_image, range);
+    const unsigned range_grid = (unsigned)(ceil_div(total, 256) < 148 * 8 ? ceil_div(total, 256) : 148 * 8);
+    if (d_image_ids) depth_range_ids_kernel<<<range_grid, 256, 0, st>>>((const float4*)d_aabb, d_depths, total, d_total, d_image_ids, range);
+    else depth_range_kernel<<<range_grid, 256, 0, st>>>((const float4*)d_aabb, d_depths, total, n_per_image, range);
     SSB_LAUNCHED("depth_range_kernel");
     const unsigned pass_grid = (unsigned)ceil_div(total, kBinThreads);
-    bin_pass_kernel<false><<<pass_grid, kBinThreads, 0, st>>>((const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th, range, bins, capacity, nullptr);
+    bin_pass_kernel<false><<<pass_grid, kBinThreads, 0, st>>>((const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th, range, bins, capacity, nullptr, d_image_ids, d_total);
     SSB_LAUNCHED("bin_pass_kernel<count>");
     bins_chunk_sum_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(bins, n_bins, chunk_sums);
     SSB_LAUNCHED("bins_chunk_sum_kernel");
@@ -719,7 +781,7 @@ int launch_intersect_tiles(const float* d_aabb, const float* d_depths, const Ssb
     SSB_LAUNCHED("chunk_scan_kernel");
     bins_apply_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(bins, n_bins, chunk_sums, d_tile_offsets);
     SSB_LAUNCHED("bins_apply_kernel");
-    bin_pass_kernel<true><<<pass_grid, kBinThreads, 0, st>>>((const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th, range, bins, capacity, pairs);
+    bin_pass_kernel<true><<<pass_grid, kBinThreads, 0, st>>>((const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th, range, bins, capacity, pairs, d_image_ids, d_total);
     SSB_LAUNCHED("bin_pass_kernel<scatter>");
     if (mark_before_sort) SSB_CUDA(cudaEventRecord(mark_before_sort, st));
     bin_sort_kernel<<<(unsigned)n_tiles, kBinSortThreads, 0, st>>>(pairs, bins, d_n_isects, n_tiles, capacity, d_isect_ids, d_flatten_ids);
@@ -728,3 +790,107 @@ int launch_intersect_tiles(const float* d_aabb, const float* d_depths, const Ssb
 }
 
 }  // namespace ssb
+
+// ---------------------------------------------------------------------------
+// Packed projection: the visible (view, splat) pairs only, in (view-major, splat-minor) order, with the view
+// and splat index of each (projection_3dgs_packed_forward, src/kernels/projection/ProjectionPackedFwd.cu:64-158).
+// The reference projects twice (a mask pass, a scan, a compacting pass); here the pairs are projected once
+// into a scratch area and compacted with a flag scan.
+namespace ssb {
+
+__global__ void __launch_bounds__(256) visible_flag_kernel(const float4* __restrict__ aabb, int64_t total, int32_t* __restrict__ flags) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const float4 bb = aabb[i];
+    flags[i] = (bb.z > bb.x && bb.w > bb.y) ? 1 : 0;
+}
+
+__global__ void __launch_bounds__(256) compact_visible_kernel(
+    const float4* __restrict__ aabb, const float* __restrict__ depths, const SsbScreenRec* __restrict__ screen,
+    const int32_t* __restrict__ excl, int64_t total, int64_t n, int64_t capacity,
+    float4* __restrict__ o_aabb, float* __restrict__ o_depths, SsbScreenRec* __restrict__ o_screen,
+    int32_t* __restrict__ o_camera, int32_t* __restrict__ o_gaussian) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const float4 bb = aabb[i];
+    if (!(bb.z > bb.x && bb.w > bb.y)) return;
+    const int64_t pos = excl[i];
+    if (pos >= capacity) return;
+    o_aabb[pos] = bb;
+    o_depths[pos] = depths[i];
+    const float4* r = (const float4*)(screen + i);
+    float4* w = (float4*)(o_screen + pos);
+    w[0] = r[0]; w[1] = r[1]; w[2] = r[2];
+    const int64_t cam = i / n;
+    o_camera[pos] = (int32_t)cam;
+    o_gaussian[pos] = (int32_t)(i - cam * n);
+}
+
+}  // namespace ssb
+
+extern "C" {
+
+int64_t ssb_project_fwd_packed_workspace_bytes(int64_t n, int32_t n_views) {
+    using namespace ssb;
+    const int64_t total = (n > 0 ? n : 1) * (n_views > 0 ? n_views : 1);
+    return align_up(total * 16, 256) + align_up(total * 4, 256) + align_up(total * (int64_t)sizeof(SsbScreenRec), 256) + align_up(total * 4, 256)
+           + align_up(ceil_div(total, kScanChunk) * 4, 256);
+}
+
+int ssb_project_fwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams,
+                           void* d_workspace, int64_t workspace_bytes,
+                           float* d_aabb, float* d_depths, float* d_radii, SsbScreenRec* d_screen,
+                           int32_t* d_camera_ids, int32_t* d_gaussian_ids, int64_t capacity,
+                           int64_t* d_n_visible, int64_t* h_n_visible, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(splats && cams && d_workspace && d_aabb && d_depths && d_screen && d_camera_ids && d_gaussian_ids && d_n_visible,
+                "ssb_project_fwd_packed: NULL argument");
+    SSB_REQUIRE(n >= 0 && cams->count >= 0 && capacity >= 0, "ssb_project_fwd_packed: bad sizes");
+    SSB_REQUIRE(workspace_bytes >= ssb_project_fwd_packed_workspace_bytes(n, cams->count), "ssb_project_fwd_packed: workspace too small");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t total = n * cams->count;
+    if (total == 0) {
+        SSB_CUDA(cudaMemsetAsync(d_n_visible, 0, sizeof(int64_t), st));
+        if (h_n_visible) { SSB_CUDA(cudaStreamSynchronize(st)); *h_n_visible = 0; }
+        return SSB_OK;
+    }
+    char* ws = (char*)d_workspace;
+    float4* u_aabb = (float4*)ws; ws += align_up(total * 16, 256);
+    float* u_depths = (float*)ws; ws += align_up(total * 4, 256);
+    SsbScreenRec* u_screen = (SsbScreenRec*)ws; ws += align_up(total * (int64_t)sizeof(SsbScreenRec), 256);
+    int32_t* flags = (int32_t*)ws; ws += align_up(total * 4, 256);
+    int32_t* chunk_sums = (int32_t*)ws;
+    int e = ssb_project_fwd(splats, shq, n, cams, (float*)u_aabb, u_depths, d_radii, u_screen, stream);
+    if (e) return e;
+    const int64_t chunks = ceil_div(total, kScanChunk);
+    visible_flag_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(u_aabb, total, flags);
+    SSB_LAUNCHED("visible_flag_kernel");
+    bins_chunk_sum_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(flags, total, chunk_sums);
+    SSB_LAUNCHED("bins_chunk_sum_kernel");
+    chunk_scan_kernel<<<1, 1024, 0, st>>>(chunk_sums, (int)chunks, d_n_visible);
+    SSB_LAUNCHED("chunk_scan_kernel");
+    bins_apply_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(flags, total, chunk_sums, nullptr);
+    SSB_LAUNCHED("bins_apply_kernel");
+    compact_visible_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(u_aabb, u_depths, u_screen, flags, total, n, capacity,
+                                                                          (float4*)d_aabb, d_depths, d_screen, d_camera_ids, d_gaussian_ids);
+    SSB_LAUNCHED("compact_visible_kernel");
+    if (h_n_visible) {
+        SSB_CUDA(cudaMemcpyAsync(h_n_visible, d_n_visible, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+        SSB_CUDA(cudaStreamSynchronize(st));
+        if (*h_n_visible > capacity) {
+            set_error("ssb_project_fwd_packed: %lld visible pairs exceed the capacity of %lld", (long long)*h_n_visible, (long long)capacity);
+            return SSB_ERR_CAPACITY;
+        }
+    }
+    return SSB_OK;
+}
+
+int ssb_intersect_tiles_packed(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen, const int32_t* d_camera_ids,
+                               const int64_t* d_n_pairs, int64_t max_pairs, int32_t n_images, int32_t width, int32_t height,
+                               void* d_workspace, int64_t workspace_bytes, int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                               int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream) {
+    return ssb::launch_intersect_tiles_packed(d_aabb, d_depths, d_screen, d_camera_ids, d_n_pairs, max_pairs, n_images, width, height,
+                                              d_workspace, workspace_bytes, d_isect_ids, d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream);
+}
+
+}  // extern "C"

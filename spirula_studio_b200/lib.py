@@ -74,6 +74,9 @@ SIGNATURES = {
     "ssb_sort_pairs_u64_noalloc": (C.c_int, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _P, _P]),
     "ssb_intersect_tiles_workspace_bytes": (_I64, [_I64, _I64]),
     "ssb_intersect_tiles": (C.c_int, [_P, _P, _P, _I64, _I64, _I32, _I32, _P, _I64, _P, _P, _I64, _P, _P, _P]),
+    "ssb_project_fwd_packed_workspace_bytes": (_I64, [_I64, _I32]),
+    "ssb_project_fwd_packed": (C.c_int, [_P, _P, _I64, _P, _P, _I64, _P, _P, _P, _P, _P, _P, _I64, _P, _P, _P]),
+    "ssb_intersect_tiles_packed": (C.c_int, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _P, _I64, _P, _P, _I64, _P, _P, _P]),
     "ssb_tile_n_bits": (_I32, [_I64]),
     "ssb_peer_alloc": (C.c_int, [_I64, _P]),
     "ssb_peer_free": (C.c_int, [_P]),

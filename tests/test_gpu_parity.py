@@ -233,6 +233,61 @@ def test_intersect_tiles_fused_bit_exact(lib, U, oracle, views, scale_mu, n, w, 
         assert np.array_equal(g_vals3.cpu().numpy()[:end], sv[:end])
 
 
+def test_packed_projection_and_intersection(lib, U, oracle):
+    """Packed projection = the visible pairs of the unpacked one, compacted view-major with their ids; the packed
+    intersection gives the lists of the unpacked one with packed indices in place of pair indices."""
+    cfg, sp, vm, K = scene(n=9000, views=2, scale_mu=-3.0, extent=3.5)     # part of the cloud is outside each view
+    W, H, n = cfg.width, cfg.height, cfg.n_splats
+    spd = U.splats_dev(sp)
+    un = U.project_fwd(lib, spd, vm, K, W, H)
+    aabb = un["aabb"].cpu().numpy()
+    keep = aabb[:, 2] > aabb[:, 0]
+    V = int(keep.sum())
+    assert 0.2 * keep.size < V < keep.size
+    cap = V + 50
+    ws_bytes = lib.ssb_project_fwd_packed_workspace_bytes(n, 2)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=U.DEV)
+    p_aabb = torch.zeros(cap, 4, device=U.DEV); p_depths = torch.zeros(cap, device=U.DEV); p_radii = torch.zeros(n, device=U.DEV)
+    p_rec = torch.zeros(cap * L.SCREEN_REC_FLOATS, device=U.DEV)
+    p_cam = torch.full((cap,), -1, dtype=torch.int32, device=U.DEV); p_gid = torch.full((cap,), -1, dtype=torch.int32, device=U.DEV)
+    n_vis = torch.zeros(1, dtype=torch.int64, device=U.DEV)
+    h_n = C.c_int64(-1)
+    s = L.splats_struct(spd)
+    cams = L.cameras_struct(un["vm"], un["K"], W, H)
+    L.check(lib.ssb_project_fwd_packed(C.byref(s), None, n, C.byref(cams), L.ptr(ws), ws_bytes, L.ptr(p_aabb), L.ptr(p_depths), L.ptr(p_radii),
+                                       L.ptr(p_rec), L.ptr(p_cam), L.ptr(p_gid), cap, L.ptr(n_vis), C.byref(h_n), None))
+    assert h_n.value == V and int(n_vis.item()) == V
+    where = np.nonzero(keep)[0]
+    assert np.array_equal(p_cam.cpu().numpy()[:V], where // n) and np.array_equal(p_gid.cpu().numpy()[:V], where % n)
+    assert int(p_cam[V:].max()) == -1
+    assert np.array_equal(p_aabb.cpu().numpy()[:V], aabb[keep])
+    assert np.array_equal(p_depths.cpu().numpy()[:V], un["depths"].cpu().numpy()[keep])
+    assert np.array_equal(p_rec.cpu().numpy().reshape(cap, -1)[:V], un["rec"].cpu().numpy().reshape(2 * n, -1)[keep])
+    assert np.array_equal(p_radii.cpu().numpy(), un["radii"].cpu().numpy())
+    # a capacity that is too small is reported
+    st = lib.ssb_project_fwd_packed(C.byref(s), None, n, C.byref(cams), L.ptr(ws), ws_bytes, L.ptr(p_aabb), L.ptr(p_depths), None,
+                                    L.ptr(p_rec), L.ptr(p_cam), L.ptr(p_gid), V // 2, L.ptr(n_vis), C.byref(h_n), None)
+    assert st == L.SSB_ERR_CAPACITY and h_n.value == V
+    L.check(lib.ssb_project_fwd_packed(C.byref(s), None, n, C.byref(cams), L.ptr(ws), ws_bytes, L.ptr(p_aabb), L.ptr(p_depths), None,
+                                       L.ptr(p_rec), L.ptr(p_cam), L.ptr(p_gid), cap, L.ptr(n_vis), None, None))
+    # intersection: unpacked (pair index = view * n + splat) against packed (pair index = packed position)
+    tw, th = oracle.tile_grid(W, H)
+    n_tiles = tw * th * 2
+    u_keys, u_vals, u_offs, M = U.intersect_tiles(lib, un["aabb"], un["depths"], un["rec"], 2 * n, n, W, H, 40 * n, n_tiles)
+    icap = M + 10
+    iws_bytes = lib.ssb_intersect_tiles_workspace_bytes(n_tiles, icap)
+    iws = torch.zeros(iws_bytes, dtype=torch.uint8, device=U.DEV)
+    keys = torch.full((icap,), -1, dtype=torch.int64, device=U.DEV); vals = torch.full((icap,), -1, dtype=torch.int32, device=U.DEV)
+    offs = torch.full((n_tiles,), -7, dtype=torch.int32, device=U.DEV); n_is = torch.zeros(1, dtype=torch.int64, device=U.DEV)
+    L.check(lib.ssb_intersect_tiles_packed(L.ptr(p_aabb), L.ptr(p_depths), L.ptr(p_rec), L.ptr(p_cam), L.ptr(n_vis), cap, 2, W, H,
+                                           L.ptr(iws), iws_bytes, L.ptr(keys), L.ptr(vals), icap, L.ptr(offs), L.ptr(n_is), None))
+    torch.cuda.synchronize()
+    assert int(n_is.item()) == M
+    assert np.array_equal(offs.cpu().numpy(), u_offs.cpu().numpy())
+    assert np.array_equal(keys.cpu().numpy()[:M], u_keys.cpu().numpy()[:M])
+    assert np.array_equal(where[vals.cpu().numpy()[:M]], u_vals.cpu().numpy()[:M])
+
+
 def test_intersect_tiles_empty(lib, U, oracle):
     cfg, sp, vm, K = scene(n=256, views=1)
     sp["means"][:, 2] = 50.0

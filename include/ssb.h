@@ -116,6 +116,19 @@ int ssb_project_fwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64
                            int32_t* d_camera_ids, int32_t* d_gaussian_ids, int64_t capacity,
                            int64_t* d_n_visible, int64_t* h_n_visible, void* stream);
 
+/* The packed form of ssb_project_bwd (the `packed` mode of projection_fused_bwd_kernel with its camera_ids /
+ * gaussian_ids arguments, src/kernels/projection/ProjectionBwd_kernel.cuh:16-54):
+ * aabb and screen-space gradients are given per packed pair with their view and splat ids; the number of
+ * pairs is read from *d_n_pairs on the device (at most max_pairs).  The pairs are put back into their
+ * (view, splat) slots in the workspace and the per-splat kernel of ssb_project_bwd sums each splat's views
+ * (no atomics), so the result equals the unpacked call's.
+ * Workspace: ssb_project_bwd_packed_workspace_bytes(n, views). */
+int64_t ssb_project_bwd_packed_workspace_bytes(int64_t n, int32_t n_views);
+int ssb_project_bwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams,
+                           const float* d_aabb, const SsbScreenRec* d_v_screen, const int32_t* d_camera_ids, const int32_t* d_gaussian_ids,
+                           const int64_t* d_n_pairs, int64_t max_pairs, void* d_workspace, int64_t workspace_bytes,
+                           const SsbSplats* grads, int accumulate, void* stream);
+
 /* Replaces projection_3dgs_backward (src/kernels/projection/ProjectionBwd.cu:134,
  * kernel src/kernels/projection/ProjectionBwd_kernel.cuh:16-130): vjp of the
  * projection and of SH-to-colour for every kept pair, summed over the views of

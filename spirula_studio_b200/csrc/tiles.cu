@@ -826,6 +826,18 @@ __global__ void __launch_bounds__(256) compact_visible_kernel(
     o_gaussian[pos] = (int32_t)(i - cam * n);
 }
 
+__global__ void __launch_bounds__(256) unpack_pairs_kernel(
+    const float4* __restrict__ p_aabb, const SsbScreenRec* __restrict__ p_v, const int32_t* __restrict__ cam, const int32_t* __restrict__ gid,
+    const int64_t* __restrict__ n_pairs, int64_t max_pairs, int64_t n, float4* __restrict__ u_aabb, SsbScreenRec* __restrict__ u_v) {
+    const int64_t v = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (v >= min(*n_pairs, max_pairs)) return;
+    const int64_t i = (int64_t)cam[v] * n + gid[v];
+    u_aabb[i] = p_aabb[v];
+    const float4* r = (const float4*)(p_v + v);
+    float4* w = (float4*)(u_v + i);
+    w[0] = r[0]; w[1] = r[1]; w[2] = r[2];
+}
+
 }  // namespace ssb
 
 extern "C" {
@@ -883,6 +895,38 @@ int ssb_project_fwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64
         }
     }
     return SSB_OK;
+}
+
+int64_t ssb_project_bwd_packed_workspace_bytes(int64_t n, int32_t n_views) {
+    using namespace ssb;
+    const int64_t total = (n > 0 ? n : 1) * (n_views > 0 ? n_views : 1);
+    return align_up(total * 16, 256) + align_up(total * (int64_t)sizeof(SsbScreenRec), 256);
+}
+
+int ssb_project_bwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams,
+                           const float* d_aabb, const SsbScreenRec* d_v_screen, const int32_t* d_camera_ids, const int32_t* d_gaussian_ids,
+                           const int64_t* d_n_pairs, int64_t max_pairs, void* d_workspace, int64_t workspace_bytes,
+                           const SsbSplats* grads, int accumulate, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(splats && cams && d_aabb && d_v_screen && d_camera_ids && d_gaussian_ids && d_n_pairs && d_workspace && grads,
+                "ssb_project_bwd_packed: NULL argument");
+    SSB_REQUIRE(n >= 0 && max_pairs >= 0, "ssb_project_bwd_packed: bad sizes");
+    SSB_REQUIRE(workspace_bytes >= ssb_project_bwd_packed_workspace_bytes(n, cams->count), "ssb_project_bwd_packed: workspace too small");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t total = n * cams->count;
+    if (total == 0) return SSB_OK;
+    // the packed pairs go back to their (view, splat) slots; every other slot is marked culled, and the
+    // per-splat kernel of the unpacked path then sums the views of a splat without atomics
+    char* ws = (char*)d_workspace;
+    float4* u_aabb = (float4*)ws;
+    SsbScreenRec* u_v = (SsbScreenRec*)(ws + align_up(total * 16, 256));
+    SSB_CUDA(cudaMemsetAsync(u_aabb, 0, (size_t)total * 16, st));
+    if (max_pairs > 0) {
+        unpack_pairs_kernel<<<(unsigned)ceil_div(max_pairs, 256), 256, 0, st>>>((const float4*)d_aabb, d_v_screen, d_camera_ids, d_gaussian_ids,
+                                                                               d_n_pairs, max_pairs, n, u_aabb, u_v);
+        SSB_LAUNCHED("unpack_pairs_kernel");
+    }
+    return launch_project_bwd(splats, shq, n, cams, (const float*)u_aabb, u_v, grads, accumulate, 0, stream);
 }
 
 int ssb_intersect_tiles_packed(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen, const int32_t* d_camera_ids,

@@ -76,6 +76,8 @@ SIGNATURES = {
     "ssb_intersect_tiles": (C.c_int, [_P, _P, _P, _I64, _I64, _I32, _I32, _P, _I64, _P, _P, _I64, _P, _P, _P]),
     "ssb_project_fwd_packed_workspace_bytes": (_I64, [_I64, _I32]),
     "ssb_project_fwd_packed": (C.c_int, [_P, _P, _I64, _P, _P, _I64, _P, _P, _P, _P, _P, _P, _I64, _P, _P, _P]),
+    "ssb_project_bwd_packed_workspace_bytes": (_I64, [_I64, _I32]),
+    "ssb_project_bwd_packed": (C.c_int, [_P, _P, _I64, _P, _P, _P, _P, _P, _P, _I64, _P, _I64, _P, C.c_int, _P]),
     "ssb_intersect_tiles_packed": (C.c_int, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _P, _I64, _P, _P, _I64, _P, _P, _P]),
     "ssb_tile_n_bits": (_I32, [_I64]),
     "ssb_peer_alloc": (C.c_int, [_I64, _P]),

@@ -286,6 +286,24 @@ def test_packed_projection_and_intersection(lib, U, oracle):
     assert np.array_equal(offs.cpu().numpy(), u_offs.cpu().numpy())
     assert np.array_equal(keys.cpu().numpy()[:M], u_keys.cpu().numpy()[:M])
     assert np.array_equal(where[vals.cpu().numpy()[:M]], u_vals.cpu().numpy()[:M])
+    # backward: packed cotangents give the gradients of the unpacked call
+    rng = np.random.default_rng(9)
+    v_un = (rng.normal(size=(2 * n, L.SCREEN_REC_FLOATS)) * 0.1).astype(np.float32)
+    d_v_un = U.dev(v_un.reshape(-1))
+    d_v_pk = torch.zeros(cap * L.SCREEN_REC_FLOATS, device=U.DEV)
+    d_v_pk.view(cap, -1)[:V] = U.dev(v_un[keep])
+    g_un = {k: torch.zeros_like(t) for k, t in spd.items()}
+    g_pk = {k: torch.full_like(t, 3.0) for k, t in spd.items()}
+    gs_un, gs_pk = L.splats_struct(g_un), L.splats_struct(g_pk)
+    L.check(lib.ssb_project_bwd(C.byref(s), None, n, C.byref(cams), L.ptr(un["aabb"]), L.ptr(d_v_un), C.byref(gs_un), 0, None))
+    bws_bytes = lib.ssb_project_bwd_packed_workspace_bytes(n, 2)
+    bws = torch.zeros(bws_bytes, dtype=torch.uint8, device=U.DEV)
+    L.check(lib.ssb_project_bwd_packed(C.byref(s), None, n, C.byref(cams), L.ptr(p_aabb), L.ptr(d_v_pk), L.ptr(p_cam), L.ptr(p_gid), L.ptr(n_vis), cap,
+                                       L.ptr(bws), bws_bytes, C.byref(gs_pk), 0, None))
+    torch.cuda.synchronize()
+    for k in g_un:
+        assert torch.equal(g_un[k], g_pk[k]), k
+    assert float(g_un["means"].abs().sum()) > 0
 
 
 def test_intersect_tiles_empty(lib, U, oracle):

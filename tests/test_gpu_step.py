@@ -301,6 +301,32 @@ def test_peer_reduce_and_broadcast_with_virtual_ranks(lib, U):
     assert lib.ssb_peer_reduce_f32(C.byref(t), None) == L.SSB_ERR_INVALID_ARGUMENT
 
 
+def test_full_size_intersection_paths_agree(lib, U):
+    """At the benchmark's size (1M splats, 1080p, about 4.4M pairs) the oracle is too slow for a test, so the two
+    independent device paths are held against each other: keys -> radix sort -> ranges, and the fused
+    bin-by-tile intersection.  Their sorted keys, sorted pair indices, ranges and counts must be identical, the
+    keys ascending, and equal keys in ascending pair order."""
+    cfg = scenes.CONFIGS["mid_1m"]
+    sp = scenes.make_splats(cfg)
+    vm, K = scenes.make_cameras(cfg)
+    n, W, H = cfg.n_splats, cfg.width, cfg.height
+    pr = U.project_fwd(lib, U.splats_dev(sp), vm[:1], K[:1], W, H)
+    cap = 8 * n
+    st, M, counts, cum, keys, vals, n_dev = U.tile_keys(lib, pr["aabb"], pr["depths"], pr["rec"], n, n, W, H, cap)
+    assert st == 0 and 3_000_000 < M < cap
+    tw, th = (W + 15) // 16, (H + 15) // 16
+    sk, sv = U.sort_pairs(lib, keys, vals, n_dev, cap, 0, 32 + lib.ssb_tile_n_bits(tw * th))
+    offs = U.tile_ranges(lib, sk, n_dev, cap, tw * th)
+    f_keys, f_vals, f_offs, f_M = U.intersect_tiles(lib, pr["aabb"], pr["depths"], pr["rec"], n, n, W, H, cap, tw * th)
+    assert f_M == M
+    assert torch.equal(f_offs, offs) and torch.equal(f_keys[:M], sk[:M]) and torch.equal(f_vals[:M], sv[:M])
+    k = f_keys[:M]
+    assert bool((k[1:] >= k[:-1]).all())
+    same = k[1:] == k[:-1]
+    assert bool((f_vals[:M][1:][same] > f_vals[:M][:-1][same]).all())
+    assert int(counts.sum()) == M
+
+
 def test_full_size_sort_and_range_properties(lib, U):
     """At the benchmark's pair count (several million) the oracle is too slow to
     run inside a test, so check what must hold at any size: the output is

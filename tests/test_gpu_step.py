@@ -301,6 +301,33 @@ def test_peer_reduce_and_broadcast_with_virtual_ranks(lib, U):
     assert lib.ssb_peer_reduce_f32(C.byref(t), None) == L.SSB_ERR_INVALID_ARGUMENT
 
 
+@pytest.mark.parametrize("bits", [16, 8])
+def test_full_size_quant_roundtrip(lib, U, bits):
+    """The SH codec at the benchmark's size (45M cells): decode(encode(x)) is within half a quantum of x in every
+    256-cell block, the bounds are the block's min and max, and encoding the decoded values again is idempotent."""
+    n_cells = 1_000_000 * 45
+    g = torch.Generator(device=U.DEV); g.manual_seed(bits)
+    x = torch.randn(n_cells, device=U.DEV, generator=g) * 0.05
+    nb = (n_cells + 255) // 256
+    packed = torch.zeros(n_cells * (bits // 8), dtype=torch.uint8, device=U.DEV)
+    bounds = torch.zeros(nb * 2, device=U.DEV)
+    y = torch.zeros_like(x)
+    L.check(lib.ssb_quant_encode(L.ptr(x), n_cells, bits, L.ptr(packed), L.ptr(bounds), None))
+    L.check(lib.ssb_quant_decode(L.ptr(packed), L.ptr(bounds), n_cells, bits, L.ptr(y), None))
+    torch.cuda.synchronize()
+    pad = nb * 256 - n_cells
+    xb = torch.cat([x, x[-1:].expand(pad)]).view(nb, 256)
+    lo, hi = bounds.view(nb, 2)[:, 0], bounds.view(nb, 2)[:, 1]
+    assert torch.equal(lo, xb.min(dim=1).values) and torch.equal(hi, xb.max(dim=1).values)
+    quantum = ((hi - lo) / float((1 << bits) - 1)).repeat_interleave(256)[:n_cells]
+    # half a quantum plus the fp32 rounding of the code and of the decode (a few thousandths of a 16-bit quantum)
+    assert bool(((y - x).abs() <= 0.5 * quantum * 1.02 + 2e-8).all())
+    packed2 = torch.zeros_like(packed); bounds2 = torch.zeros_like(bounds)
+    L.check(lib.ssb_quant_encode(L.ptr(y), n_cells, bits, L.ptr(packed2), L.ptr(bounds2), None))
+    torch.cuda.synchronize()
+    assert torch.equal(packed2, packed)
+
+
 def test_full_size_intersection_paths_agree(lib, U):
     """At the benchmark's size (1M splats, 1080p, about 4.4M pairs) the oracle is too slow for a test, so the two
     independent device paths are held against each other: keys -> radix sort -> ranges, and the fused

@@ -328,6 +328,43 @@ def test_full_size_quant_roundtrip(lib, U, bits):
     assert torch.equal(packed2, packed)
 
 
+def test_full_size_raster_properties(lib, U):
+    """The rasterisers at the benchmark's size (one 1080p view of 1M splats): transmittance within [0, 1], colour
+    non-negative and bounded by the opacity-weighted sum, last indices inside their tile's range, the depth-free
+    variant equal to the full one, and the backward pass linear in its cotangent (twice the colour cotangent
+    gives twice every gradient, up to the order of the floating-point reductions)."""
+    cfg = scenes.CONFIGS["mid_1m"]
+    sp = scenes.make_splats(cfg)
+    vm, K = scenes.make_cameras(cfg)
+    n, W, H = cfg.n_splats, cfg.width, cfg.height
+    pr = U.project_fwd(lib, U.splats_dev(sp), vm[3:4], K[3:4], W, H)
+    tw, th = (W + 15) // 16, (H + 15) // 16
+    cap = 8 * n
+    _, flat, offs, M = U.intersect_tiles(lib, pr["aabb"], pr["depths"], pr["rec"], n, n, W, H, cap, tw * th, want_keys=False)
+    n_dev = torch.tensor([M], dtype=torch.int64, device=U.DEV)
+    out = U.raster_fwd(lib, pr["rec"], offs, flat, n_dev, 1, W, H)
+    T, rgb, last = out["T"], out["rgb"], out["last_ids"].long()
+    assert bool(((T >= 0) & (T <= 1)).all()) and bool((rgb >= 0).all()) and bool(torch.isfinite(rgb).all())
+    ys, xs = torch.meshgrid(torch.arange(H, device=U.DEV), torch.arange(W, device=U.DEV), indexing="ij")
+    tile = ((ys // 16) * tw + xs // 16).reshape(-1)
+    ends = torch.cat([offs[1:].long(), torch.tensor([M], device=U.DEV)])
+    blended = T < 1.0
+    assert bool(((last >= offs.long()[tile]) & (last < ends[tile]))[blended].all())
+    # depth-free variant
+    rgb2 = torch.zeros_like(rgb); T2 = torch.zeros_like(T); last2 = torch.zeros_like(out["last_ids"])
+    L.check(lib.ssb_raster_fwd(L.ptr(pr["rec"]), L.ptr(offs), L.ptr(flat), L.ptr(n_dev), 1, W, H, L.ptr(rgb2), None, L.ptr(T2), L.ptr(last2), None))
+    torch.cuda.synchronize()
+    assert torch.equal(rgb2, rgb) and torch.equal(T2, T) and torch.equal(last2, out["last_ids"])
+    # linearity of the backward pass
+    g = torch.Generator(device=U.DEV); g.manual_seed(5)
+    v = torch.randn(H * W, 3, device=U.DEV, generator=g)
+    g1 = U.raster_bwd(lib, pr["rec"], offs, flat, n_dev, 1, W, H, out, v, pairs=n).view(n, 12)
+    g2 = U.raster_bwd(lib, pr["rec"], offs, flat, n_dev, 1, W, H, out, 2.0 * v, pairs=n).view(n, 12)
+    scale = g1.abs().max(dim=0).values.clamp_min(1e-20)
+    assert float(((g2 - 2.0 * g1).abs() / scale).max()) < 1e-3
+    assert float(g1.abs().sum()) > 0 and bool(torch.isfinite(g1).all())
+
+
 def test_full_size_intersection_paths_agree(lib, U):
     """At the benchmark's size (1M splats, 1080p, about 4.4M pairs) the oracle is too slow for a test, so the two
     independent device paths are held against each other: keys -> radix sort -> ranges, and the fused

@@ -26,3 +26,13 @@ extern "C" int ref_adam_qq(int64_t numel, int step, float lr, float l2_reg, floa
     #undef ARGS
     return (int)cudaDeviceSynchronize();
 }
+
+// fused_adam_step_quantized (:232-271): fp32 values, QuantizedAdamState<8,256> state.
+extern "C" int ref_adam_q8(int64_t numel, int step, float lr, float l2_reg, float grad_scale, int zero_grad,
+                           float* param, float* grad, uint8_t* optim_packed, float* optim_bounds) {
+    const float decay = 2.0f * l2_reg / (float)numel;
+    uint32_t blocks = _CEIL_DIV((uint32_t)numel, 256);
+    if (zero_grad) fused_adam_with_steps_8bit_kernel<256, 8, true><<<blocks, 256>>>(param, grad, optim_packed, (float4*)optim_bounds, lr, step, nullptr, decay, 0.0f, grad_scale, numel, 45);
+    else fused_adam_with_steps_8bit_kernel<256, 8, false><<<blocks, 256>>>(param, grad, optim_packed, (float4*)optim_bounds, lr, step, nullptr, decay, 0.0f, grad_scale, numel, 45);
+    return (int)cudaDeviceSynchronize();
+}

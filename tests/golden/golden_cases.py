@@ -92,4 +92,8 @@ def adam_inputs():
         out[f"qq{bits}"] = dict(numel=numel, value_packed=vp, value_bounds=vb, optim_packed=np.zeros(numel * 2, np.uint8),
                                 optim_bounds=np.zeros(nb * 4, np.float32),
                                 grads=[(rng.normal(size=numel) * 1e-3).astype(np.float32) for _ in range(3)])
+    # optimiser state quantised, values fp32 (three steps from a zero state)
+    numel = 45 * 200 + 7
+    out["q8"] = dict(numel=numel, x0=rng.normal(0, 0.05, size=numel).astype(np.float32),
+                     grads=[(rng.normal(size=numel) * 1e-3).astype(np.float32) for _ in range(3)])
     return out

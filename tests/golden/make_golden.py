@@ -147,6 +147,23 @@ def run_adam(ref, out_dir):
             out[f"qq{bits}_s{step}_value_bounds"] = vb.cpu().numpy()
             out[f"qq{bits}_s{step}_optim_packed"] = op.cpu().numpy()
             out[f"qq{bits}_s{step}_optim_bounds"] = ob.cpu().numpy()
+    # 8-bit optimiser state with fp32 values: three steps from a zero state
+    q = inp["q8"]
+    # The reference kernel stores param[idx] for every thread of its last 256-thread block, also past numel
+    # (FusedAppearanceOptim.cu:190), so the value buffer is padded to whole blocks here.
+    nb = (q["numel"] + 255) // 256
+    x_buf = torch.zeros(nb * 256, dtype=torch.float32, device=DEV)
+    x = x_buf[:q["numel"]]
+    x.copy_(dev(q["x0"]))
+    op = torch.zeros(q["numel"] * 2, dtype=torch.uint8, device=DEV)
+    ob = torch.zeros(nb * 4, dtype=torch.float32, device=DEV)
+    for step, grad in enumerate(q["grads"], start=1):
+        d_grad = dev(grad)
+        check(ref.ref_adam_q8(C.c_int64(q["numel"]), step, C.c_float(lr["lr_features_sh"]), C.c_float(0.0), C.c_float(inp["grad_scale"]), 0,
+                              P(x), P(d_grad), P(op), P(ob)), "ref_adam_q8")
+        out[f"q8_s{step}_x"] = x.cpu().numpy()
+        out[f"q8_s{step}_optim_packed"] = op.cpu().numpy()
+        out[f"q8_s{step}_optim_bounds"] = ob.cpu().numpy()
     np.savez_compressed(os.path.join(out_dir, "adam.npz"), **out)
 
 

@@ -168,3 +168,14 @@ def test_adam_vs_reference(oracle):
             assert (dv > 0).mean() <= 5e-2 and (do > 0).mean() <= 5e-2
             assert np.allclose(vb, rb, rtol=1e-4, atol=1e-7) and np.allclose(ob, rob, rtol=2e-3, atol=1e-5)
             state = [rv.copy(), rb.copy(), ro.copy(), rob.copy()]            # continue from the reference's state
+    # fp32 values with the 8-bit state (value_bits = 32), each step continued from the reference's state
+    q = inp["q8"]
+    x, op, ob = q["x0"].copy(), np.zeros(q["numel"] * 2, np.uint8), np.zeros(((q["numel"] + 255) // 256) * 4, np.float32)
+    for step, grad in enumerate(q["grads"], start=1):
+        oracle.adam_qq(grad.copy(), op, ob, x.view(np.uint8), np.zeros(2, np.float32), 32, step, lr["lr_features_sh"], grad_scale=gs)
+        rx, ro, rob = (gold[f"q8_s{step}_{s}"] for s in ("x", "optim_packed", "optim_bounds"))
+        do = np.abs(op.astype(np.int64) - ro.astype(np.int64))
+        assert do.max() <= 1 and (do > 0).mean() <= 5e-2, step
+        assert np.allclose(ob, rob, rtol=2e-3, atol=1e-5)
+        assert frac_bad(x, rx, 5e-6, 1e-4) <= 1e-3, step
+        x, op, ob = rx.copy(), ro.copy(), rob.copy()

@@ -185,3 +185,16 @@ def test_adam_vs_reference(lib, U):
             assert (dv > 0).mean() <= 5e-2 and (do > 0).mean() <= 5e-2
             assert np.allclose(vb.cpu().numpy(), rb, rtol=1e-4, atol=1e-7)
             state = [rv, rb, ro, rob]
+    q = inp["q8"]
+    state = [q["x0"], np.zeros(q["numel"] * 2, np.uint8), np.zeros(((q["numel"] + 255) // 256) * 4, np.float32)]
+    for step, grad in enumerate(q["grads"], start=1):
+        x, op, ob = (U.dev(a) for a in state)
+        d_g = U.dev(grad)
+        cfg = L.SsbAdamConfig(0, 0, 0, 0, 0, lr["lr_features_sh"], 0.0, gs, step, 0)
+        L.check(lib.ssb_adam_step_sh_quantized(L.ptr(d_g), L.ptr(op), L.ptr(ob), L.ptr(x), None, 32, 0, q["numel"], q["numel"], C.byref(cfg), None))
+        torch.cuda.synchronize()
+        rx, ro, rob = (gold[f"q8_s{step}_{s}"] for s in ("x", "optim_packed", "optim_bounds"))
+        do = np.abs(op.cpu().numpy().astype(np.int64) - ro.astype(np.int64))
+        assert do.max() <= 1 and (do > 0).mean() <= 5e-2, step
+        assert U.close_frac(x.cpu().numpy(), rx, 5e-6, 1e-4) <= 1e-3, step
+        state = [rx, ro, rob]

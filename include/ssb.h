@@ -291,6 +291,31 @@ typedef struct SsbAdamConfig {
 int ssb_adam_step(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
                   int64_t first, int64_t count, const SsbAdamConfig* cfg, void* stream);
 
+/* The optional parts of the reference's optimiser launch that SsbAdamConfig leaves out
+ * (src/engine/EngineConfig.h OptimConfig; src/kernels/optim/FusedGeometryOptim.cu:384-470).
+ * The regulariser weights are the caller's undivided weights: like the reference's launcher
+ * (:457-462) the library divides them by n_total. */
+typedef struct SsbAdamExtras {
+    float max_gauss_ratio;               /* threshold of the scale-ratio regulariser */
+    float scale_regularization_weight;   /* w * (max(max(e^s)/min(e^s), ratio) - ratio) */
+    float mcmc_opacity_reg_weight;       /* w * sigmoid(opacity) */
+    float mcmc_scale_reg_weight;         /* w * 1e-2 * mean(log-scales) */
+    float erank_reg_weight;              /* w * max(-log(erank - 0.99999), 0) */
+    float erank_reg_weight_s3;           /* w * smallest normalised squared scale */
+    float quat_norm_reg_weight;          /* w * (|q| - 1 - log|q|), evaluated on the normalised quaternion */
+    int32_t use_scale_agnostic_mean;     /* FusedGeometryOptim.cu:302-314; needs d_radii */
+    const float* d_radii;                /* [n_total] screen radii of ssb_project_fwd (max over the views) */
+    const int32_t* d_steps;              /* [n_total] per-splat bias-correction exponents (>= 1), or NULL: cfg->step */
+    int64_t n_total;                     /* number of splats of the whole model (the range may be a shard) */
+} SsbAdamExtras;
+
+/* ssb_adam_step with the optional parts: per-splat regulariser gradients (Slang per_splat_losses_bwd,
+ * src/shaders/per_splat_losses.slang:5-141, all five loss cotangents 1), the scale-agnostic mean update and
+ * per-splat step counters for every parameter group (steps[idx / stride] in the appearance kernels,
+ * src/kernels/optim/FusedAppearanceOptim.cu:34).  extras == NULL is ssb_adam_step. */
+int ssb_adam_step_ex(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
+                     int64_t first, int64_t count, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream);
+
 /* Replaces fused_adam_step_quantized_value (src/kernels/optim/FusedAppearanceOptim.cu:421-479,
  * kernel :291-418): Adam on SH coefficients whose values live in a QuantizedTensor
  * <value_bits,256> and whose state lives in a QuantizedAdamState<8,256>
@@ -303,6 +328,13 @@ int ssb_adam_step_sh_quantized(float* d_grad, uint8_t* d_optim_packed, float* d_
                                void* d_value_packed, float* d_value_bounds, int32_t value_bits,
                                int64_t first_cell, int64_t numel, int64_t numel_total,
                                const SsbAdamConfig* cfg, void* stream);
+
+/* The same with per-splat step counters: cell c uses d_steps[c / cells_per_splat]
+ * (steps[idx / stride], FusedAppearanceOptim.cu:166,330).  d_steps == NULL is the call above. */
+int ssb_adam_step_sh_quantized_steps(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds,
+                                     void* d_value_packed, float* d_value_bounds, int32_t value_bits,
+                                     int64_t first_cell, int64_t numel, int64_t numel_total,
+                                     const SsbAdamConfig* cfg, const int32_t* d_steps, int32_t cells_per_splat, void* stream);
 
 /* QuantizedTensor<BITS,256>::encode_v / decode_v over whole buffers
  * (src/core/Tensor.h:1366-1393); bounds = float2 per 256 cells. */

@@ -173,9 +173,27 @@ def adam_geometry(p, g, m1, m2, step, lrs, grad_scale=1.0, zero_grad=0):
                              _p(p["opacities"]), _p(g["opacities"]), _p(m1["opacities"]), _p(m2["opacities"]))
 
 
-def adam_plain(param, grad, m1, m2, step, lr, l2_reg=0.0, l2_reg_offset=0.0, grad_scale=1.0, zero_grad=0):
-    load().oracle_adam_plain(C.c_int64(param.size), C.c_int(step), C.c_float(lr), C.c_float(l2_reg), C.c_float(l2_reg_offset),
-                             C.c_float(grad_scale), C.c_int(zero_grad), _p(param), _p(grad), _p(m1), _p(m2))
+def adam_geometry_ex(p, g, m1, m2, step, lrs, grad_scale=1.0, zero_grad=0, reg=None, scale_agnostic=False, radii=None, steps=None):
+    """adam_geometry with the optional parts: reg = the seven regulariser numbers (max_gauss_ratio, scale_regularization,
+    mcmc_opacity, mcmc_scale, erank, erank_s3, quat_norm; undivided weights), the scale-agnostic mean update (needs radii)
+    and per-splat int32 step counters."""
+    lib = load()
+    N = p["means"].shape[0]
+    reg_a = None if reg is None else np.ascontiguousarray(reg, np.float32)
+    lib.oracle_adam_geometry_ex(C.c_int64(N), C.c_int(step), C.c_float(grad_scale), C.c_int(zero_grad),
+                                C.c_float(lrs["lr_means"]), C.c_float(lrs["lr_quats"]), C.c_float(lrs["lr_scales"]), C.c_float(lrs["lr_opacities"]),
+                                _p(p["means"]), _p(g["means"]), _p(m1["means"]), _p(m2["means"]),
+                                _p(p["quats"]), _p(g["quats"]), _p(m1["quats"]), _p(m2["quats"]),
+                                _p(p["scales"]), _p(g["scales"]), _p(m1["scales"]), _p(m2["scales"]),
+                                _p(p["opacities"]), _p(g["opacities"]), _p(m1["opacities"]), _p(m2["opacities"]),
+                                _p(reg_a) if reg_a is not None else None, C.c_int(1 if scale_agnostic else 0),
+                                _p(radii) if radii is not None else None, _p(steps) if steps is not None else None)
+
+
+def adam_plain(param, grad, m1, m2, step, lr, l2_reg=0.0, l2_reg_offset=0.0, grad_scale=1.0, zero_grad=0, steps=None, stride=1):
+    load().oracle_adam_plain_steps(C.c_int64(param.size), C.c_int(step), C.c_float(lr), C.c_float(l2_reg), C.c_float(l2_reg_offset),
+                                   C.c_float(grad_scale), C.c_int(zero_grad), _p(param), _p(grad), _p(m1), _p(m2),
+                                   _p(steps) if steps is not None else None, C.c_int(stride))
 
 
 def quant_encode(values, bits):
@@ -193,9 +211,11 @@ def quant_decode(packed, bounds, n, bits):
     return out
 
 
-def adam_qq(grad, optim_packed, optim_bounds, value_packed, value_bounds, value_bits, step, lr, l2_reg=0.0, grad_scale=1.0, zero_grad=0):
-    load().oracle_adam_qq(C.c_int64(grad.size), C.c_int(step), C.c_float(lr), C.c_float(l2_reg), C.c_float(0.0), C.c_float(grad_scale),
-                          C.c_int(zero_grad), C.c_int(value_bits), _p(grad), _p(optim_packed), _p(optim_bounds), _p(value_packed), _p(value_bounds))
+def adam_qq(grad, optim_packed, optim_bounds, value_packed, value_bounds, value_bits, step, lr, l2_reg=0.0, grad_scale=1.0, zero_grad=0,
+            steps=None, stride=1):
+    load().oracle_adam_qq_steps(C.c_int64(grad.size), C.c_int(step), C.c_float(lr), C.c_float(l2_reg), C.c_float(0.0), C.c_float(grad_scale),
+                                C.c_int(zero_grad), C.c_int(value_bits), _p(grad), _p(optim_packed), _p(optim_bounds), _p(value_packed),
+                                _p(value_bounds), _p(steps) if steps is not None else None, C.c_int(stride))
 
 
 def forward_chain(splats, viewmats, intrins, W, H, shq=None, model=0):

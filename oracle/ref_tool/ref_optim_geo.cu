@@ -1,7 +1,7 @@
 // TEST INFRASTRUCTURE.  The reference's fused geometry Adam kernel
 // (src/kernels/optim/FusedGeometryOptim.cu:83-380), launched as
-// fused_optim_3dgs_geometry does (:447-468) with every regulariser weight zero,
-// fp32 state, no scale-agnostic mean, scalar step.
+// fused_optim_3dgs_geometry does (:447-468), fp32 state.  ref_adam_geometry: every regulariser
+// weight zero, no scale-agnostic mean, scalar step; ref_adam_geometry_ex: those three switched on.
 #include "kernels/optim/FusedGeometryOptim.cu"
 
 extern "C" int ref_adam_geometry(
@@ -25,5 +25,38 @@ extern "C" int ref_adam_geometry(
     };
     if (zero_grad) launch(fused_optim_3dgs_geometry_kernel<false, true, false>);
     else launch(fused_optim_3dgs_geometry_kernel<false, false, false>);
+    return (int)cudaDeviceSynchronize();
+}
+
+// reg = max_gauss_ratio, scale_regularization, mcmc_opacity, mcmc_scale, erank, erank_s3, quat_norm (undivided,
+// the division by N is the launcher's, :457-462); radii and steps may be null.
+extern "C" int ref_adam_geometry_ex(
+    int64_t N, int step, float grad_scale, int zero_grad, float lr_means, float lr_quats, float lr_scales, float lr_opacs,
+    float* means, float* v_means, float* g1_means, float* g2_means,
+    float* quats, float* v_quats, float* g1_quats, float* g2_quats,
+    float* scales, float* v_scales, float* g1_scales, float* g2_scales,
+    float* opacs, float* v_opacs, float* g1_opacs, float* g2_opacs,
+    const float* reg, int use_scale_agnostic_mean, const float* radii, const int32_t* steps) {
+    NonShQuantState non_sh;
+    GradQuantBuffers gq;
+    const float n = (float)N;
+    auto launch = [&](auto kfn) {
+        kfn<<<_CEIL_DIV((uint32_t)N, 256), 256>>>(
+            (float3*)means, (float3*)v_means, (float3*)g1_means, (float3*)g2_means,
+            (float4*)quats, (float4*)v_quats, (float4*)g1_quats, (float4*)g2_quats,
+            (float3*)scales, (float3*)v_scales, (float3*)g1_scales, (float3*)g2_scales,
+            opacs, v_opacs, g1_opacs, g2_opacs,
+            nullptr, nullptr, radii, nullptr,
+            lr_means, lr_quats, lr_scales, lr_opacs, 0.0f,
+            reg[0], reg[1] / n, reg[2] / n, reg[3] / n, reg[4] / n, reg[5] / n, reg[6] / n, 0.0f, grad_scale,
+            non_sh, gq, step, steps, N);
+    };
+    if (use_scale_agnostic_mean) {
+        if (zero_grad) launch(fused_optim_3dgs_geometry_kernel<true, true, false>);
+        else launch(fused_optim_3dgs_geometry_kernel<true, false, false>);
+    } else {
+        if (zero_grad) launch(fused_optim_3dgs_geometry_kernel<false, true, false>);
+        else launch(fused_optim_3dgs_geometry_kernel<false, false, false>);
+    }
     return (int)cudaDeviceSynchronize();
 }

@@ -1051,26 +1051,76 @@ void oracle_loss_l1_ssim(
 // (src/kernels/optim/FusedGeometryOptim.cu:83-380) with every per-splat
 // regulariser weight zero, no scale-agnostic mean, fp32 state, scalar step.
 // ---------------------------------------------------------------------------
-void oracle_adam_geometry(
+void oracle_adam_geometry_ex(
     int64_t N, int step, float grad_scale, int zero_grad,
     float lr_means, float lr_quats, float lr_scales, float lr_opacs,
     float* means, float* v_means, float* g1_means, float* g2_means,
     float* quats, float* v_quats, float* g1_quats, float* g2_quats,
     float* scales, float* v_scales, float* g1_scales, float* g2_scales,
-    float* opacs, float* v_opacs, float* g1_opacs, float* g2_opacs) {
+    float* opacs, float* v_opacs, float* g1_opacs, float* g2_opacs,
+    // regulariser weights as the caller gives them (the launcher divides them by N, :457-462), in the order
+    // max_gauss_ratio, scale_regularization, mcmc_opacity, mcmc_scale, erank, erank_s3, quat_norm
+    const float* reg, int use_scale_agnostic_mean, const float* radii, const int32_t* steps) {
     const float eps = 1e-15f, beta1 = 0.9f, beta2 = 0.999f;
-    const float ibc1 = 1.0f / (1.0f - std::pow(beta1, (float)step));
-    const float ibc2 = 1.0f / (1.0f - std::pow(beta2, (float)step));
-    lr_means *= ibc1; lr_quats *= ibc1; lr_scales *= ibc1; lr_opacs *= ibc1;
-    auto upd = [&](float& x, float g, float& m1, float& m2, float lr) {
-        m1 = beta1 * m1 + (1.f - beta1) * g;
-        m2 = beta2 * m2 + (1.f - beta2) * g * g;
-        x = x - lr * m1 / (std::sqrt(m2 * ibc2) + eps);
-    };
+    const float lr_means0 = lr_means, lr_quats0 = lr_quats, lr_scales0 = lr_scales, lr_opacs0 = lr_opacs;
+    const float inv_n = 1.0f / (float)N;
+    const float max_ratio = reg ? reg[0] : 0.f, w_ratio = reg ? reg[1] * inv_n : 0.f, w_op = reg ? reg[2] * inv_n : 0.f,
+                w_ms = reg ? reg[3] * inv_n : 0.f, w_er = reg ? reg[4] * inv_n : 0.f, w_er3 = reg ? reg[5] * inv_n : 0.f,
+                w_qn = reg ? reg[6] * inv_n : 0.f;
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < N; ++i) {
+        const float stepf = (float)(steps ? steps[i] : step);   // :160
+        const float ibc1 = 1.0f / (1.0f - std::pow(beta1, stepf));
+        const float ibc2 = 1.0f / (1.0f - std::pow(beta2, stepf));
+        const float lr_means = lr_means0 * ibc1, lr_quats = lr_quats0 * ibc1, lr_scales = lr_scales0 * ibc1, lr_opacs = lr_opacs0 * ibc1;
+        auto upd = [&](float& x, float g, float& m1, float& m2, float lr) {
+            m1 = beta1 * m1 + (1.f - beta1) * g;
+            m2 = beta2 * m2 + (1.f - beta2) * g * g;
+            x = x - lr * m1 / (std::sqrt(m2 * ibc2) + eps);
+        };
+        // parameters before the update (:170-172), used by the regularisers and the scale-agnostic mean
+        const float s0[3] = {scales[3 * i], scales[3 * i + 1], scales[3 * i + 2]};
+        const float o0 = opacs[i];
+        float qn0[4];
+        {
+            float n = 0.f;
+            for (int k = 0; k < 4; ++k) n += quats[4 * i + k] * quats[4 * i + k];
+            float inv = 1.0f / std::sqrt(n);
+            for (int k = 0; k < 4; ++k) qn0[k] = quats[4 * i + k] * inv;
+        }
+        // reverse mode of per_splat_losses with unit cotangents (src/shaders/per_splat_losses.slang:5-141)
+        float rs[3] = {0.f, 0.f, 0.f}, ro = 0.f, rq[4] = {0.f, 0.f, 0.f, 0.f};
+        if (reg) {
+            const float sg = 1.0f / (1.0f + std::exp(-o0));
+            ro = w_op * sg * (1.0f - sg);                                             // mcmc_opacity_reg, :61-65
+            for (int k = 0; k < 3; ++k) rs[k] = w_ms * 1e-2f / 3.0f;                  // mcmc_scale_reg_3dgs, :69-73
+            int imax = s0[0] > s0[1] ? 0 : 1; imax = s0[imax] > s0[2] ? imax : 2;
+            int imin = s0[0] < s0[1] ? 0 : 1; imin = s0[imin] < s0[2] ? imin : 2;
+            const float ratio = std::exp(s0[imax]) / std::exp(s0[imin]);              // scale_reg_3dgs, :41-46
+            if (ratio > max_ratio) { rs[imax] += w_ratio * ratio; rs[imin] -= w_ratio * ratio; }
+            {                                                                          // erank_reg_3dgs, :9-20
+                const float E[3] = {std::exp(2.0f * s0[0]), std::exp(2.0f * s0[1]), std::exp(2.0f * s0[2])};
+                const float S = E[0] + E[1] + E[2];
+                const float p1 = E[imax] / S, p3 = E[imin] / S, p2 = 1.0f - p1 - p3;
+                const float l1 = std::log(p1), l2 = std::log(p2), l3 = std::log(p3);
+                const float r = std::exp(-p1 * l1 - p2 * l2 - p3 * l3);
+                float dH = 0.f;
+                if (-std::log(r - 0.99999f) > 0.0f) dH = -w_er / (r - 0.99999f) * r;
+                const float dp1 = dH * (l2 - l1), dp3 = dH * (l2 - l3) + w_er3;
+                const float dS = -(dp1 * p1 + dp3 * p3) / S;
+                for (int k = 0; k < 3; ++k) {
+                    float dE = dS + (k == imax ? dp1 / S : 0.f) + (k == imin ? dp3 / S : 0.f);
+                    rs[k] += dE * 2.0f * E[k];
+                }
+            }
+            {                                                                          // quat_norm_reg, :84-88
+                float n = std::sqrt(qn0[0] * qn0[0] + qn0[1] * qn0[1] + qn0[2] * qn0[2] + qn0[3] * qn0[3]);
+                float w = w_qn * (1.0f - 1.0f / n) / n;
+                for (int k = 0; k < 4; ++k) rq[k] = w * qn0[k];
+            }
+        }
         for (int k = 0; k < 3; ++k) {
-            float g = grad_scale * v_scales[3 * i + k];
+            float g = rs[k] + grad_scale * v_scales[3 * i + k];
             upd(scales[3 * i + k], g, g1_scales[3 * i + k], g2_scales[3 * i + k], lr_scales);
             if (zero_grad) v_scales[3 * i + k] = 0.f;
         }
@@ -1081,7 +1131,7 @@ void oracle_adam_geometry(
             float inv = 1.0f / std::sqrt(n);
             for (int k = 0; k < 4; ++k) q[k] *= inv;
             float dotqg = 0.f;
-            for (int k = 0; k < 4; ++k) { g[k] = grad_scale * v_quats[4 * i + k]; dotqg += q[k] * g[k]; }
+            for (int k = 0; k < 4; ++k) { g[k] = rq[k] + grad_scale * v_quats[4 * i + k]; dotqg += q[k] * g[k]; }
             for (int k = 0; k < 4; ++k) g[k] -= dotqg * q[k];
             float u[4]; float n2 = 0.f;
             for (int k = 0; k < 4; ++k) {
@@ -1095,29 +1145,64 @@ void oracle_adam_geometry(
             for (int k = 0; k < 4; ++k) { quats[4 * i + k] = u[k] * inv2; if (zero_grad) v_quats[4 * i + k] = 0.f; }
         }
         {
-            float g = grad_scale * v_opacs[i];
+            float g = ro + grad_scale * v_opacs[i];
             upd(opacs[i], g, g1_opacs[i], g2_opacs[i], lr_opacs);
             if (zero_grad) v_opacs[i] = 0.f;
         }
-        for (int k = 0; k < 3; ++k) {
-            float g = grad_scale * v_means[3 * i + k];
-            upd(means[3 * i + k], g, g1_means[3 * i + k], g2_means[3 * i + k], lr_means);
-            if (zero_grad) v_means[3 * i + k] = 0.f;
+        if (use_scale_agnostic_mean) {   // :302-314
+            const float v[3] = {grad_scale * v_means[3 * i], grad_scale * v_means[3 * i + 1], grad_scale * v_means[3 * i + 2]};
+            const float w = qn0[0], x = qn0[1], y = qn0[2], z = qn0[3];
+            const float R[9] = {1.f - 2.f * (y * y + z * z), 2.f * (x * y - w * z), 2.f * (x * z + w * y),
+                                2.f * (x * y + w * z), 1.f - 2.f * (x * x + z * z), 2.f * (y * z - w * x),
+                                2.f * (x * z - w * y), 2.f * (y * z + w * x), 1.f - 2.f * (x * x + y * y)};
+            // apply_covar_to_vec(quat, exp(s/2), v) = R diag(exp(s)) R^T v (src/shaders/projection_utils.slang:114-161)
+            float t[3];
+            for (int k = 0; k < 3; ++k) t[k] = std::exp(s0[k]) * (R[k] * v[0] + R[3 + k] * v[1] + R[6 + k] * v[2]);
+            const float sg = 1.0f / (1.0f + std::exp(-o0));
+            const float ext = std::sqrt(2.0f * std::log(std::max(255.0f * sg, 1.00001f)));
+            const float den = radii[i] * 0.6f;
+            for (int k = 0; k < 3; ++k) {
+                const float num = (R[3 * k] * t[0] + R[3 * k + 1] * t[1] + R[3 * k + 2] * t[2]) * ext;
+                float& m1 = g1_means[3 * i + k]; float& m2 = g2_means[3 * i + k];
+                m1 = beta1 * m1 + (1.f - beta1) * num;
+                m2 = beta2 * m2 + (1.f - beta2) * v[k] * v[k] * den * den;
+                means[3 * i + k] -= lr_means * m1 / (std::sqrt(m2 * ibc2) + eps);
+                if (zero_grad) v_means[3 * i + k] = 0.f;
+            }
+        } else {
+            for (int k = 0; k < 3; ++k) {
+                float g = grad_scale * v_means[3 * i + k];
+                upd(means[3 * i + k], g, g1_means[3 * i + k], g2_means[3 * i + k], lr_means);
+                if (zero_grad) v_means[3 * i + k] = 0.f;
+            }
         }
     }
 }
 
+void oracle_adam_geometry(
+    int64_t N, int step, float grad_scale, int zero_grad,
+    float lr_means, float lr_quats, float lr_scales, float lr_opacs,
+    float* means, float* v_means, float* g1_means, float* g2_means,
+    float* quats, float* v_quats, float* g1_quats, float* g2_quats,
+    float* scales, float* v_scales, float* g1_scales, float* g2_scales,
+    float* opacs, float* v_opacs, float* g1_opacs, float* g2_opacs) {
+    oracle_adam_geometry_ex(N, step, grad_scale, zero_grad, lr_means, lr_quats, lr_scales, lr_opacs, means, v_means, g1_means, g2_means,
+                            quats, v_quats, g1_quats, g2_quats, scales, v_scales, g1_scales, g2_scales, opacs, v_opacs, g1_opacs, g2_opacs,
+                            nullptr, 0, nullptr, nullptr);
+}
+
 // fused_adam_step -> fused_adam_with_steps_kernel
 // (src/kernels/optim/FusedAppearanceOptim.cu:11-92); decay = 2*l2_reg/numel.
-void oracle_adam_plain(
+void oracle_adam_plain_steps(
     int64_t numel, int step, float lr, float l2_reg, float l2_reg_offset, float grad_scale, int zero_grad,
-    float* param, float* grad, float* exp_avg, float* exp_avg_sq) {
+    float* param, float* grad, float* exp_avg, float* exp_avg_sq, const int32_t* steps, int stride) {
     const float eps = 1e-15f, beta1 = 0.9f, beta2 = 0.999f;
-    const float ibc1 = 1.0f / (1.0f - std::pow(beta1, (float)step));
-    const float ibc2 = 1.0f / (1.0f - std::pow(beta2, (float)step));
     const float decay = 2.0f * l2_reg / (float)numel;
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < numel; ++i) {
+        const float stepf = (float)(steps ? steps[i / stride] : step);   // :34
+        const float ibc1 = 1.0f / (1.0f - std::pow(beta1, stepf));
+        const float ibc2 = 1.0f / (1.0f - std::pow(beta2, stepf));
         float x = param[i], v = grad[i];
         if (!std::isfinite(v)) v = 0.f;
         if (zero_grad) grad[i] = 0.f;
@@ -1128,6 +1213,12 @@ void oracle_adam_plain(
         x -= lr * ibc1 * g1 / (std::sqrt(g2 * ibc2) + eps);
         param[i] = x; exp_avg[i] = g1; exp_avg_sq[i] = g2;
     }
+}
+
+void oracle_adam_plain(
+    int64_t numel, int step, float lr, float l2_reg, float l2_reg_offset, float grad_scale, int zero_grad,
+    float* param, float* grad, float* exp_avg, float* exp_avg_sq) {
+    oracle_adam_plain_steps(numel, step, lr, l2_reg, l2_reg_offset, grad_scale, zero_grad, param, grad, exp_avg, exp_avg_sq, nullptr, 1);
 }
 
 // Block-wise min/max value codec, QuantizedTensor<BITS,256>::encode_v
@@ -1167,12 +1258,11 @@ void oracle_quant_decode(int64_t numel, int bits, const uint8_t* packed, const f
 // QuantizedTensor<VALUE_BITS,256> (:1313-1404).  fp32 gradient input.
 // value_bits == 32: the values are plain fp32 and only the state is quantised
 // (fused_adam_with_steps_8bit_kernel, src/kernels/optim/FusedAppearanceOptim.cu:137-229).
-void oracle_adam_qq(
+void oracle_adam_qq_steps(
     int64_t numel, int step, float lr, float l2_reg, float l2_reg_offset, float grad_scale, int zero_grad, int value_bits,
-    float* grad, uint8_t* optim_packed, float* optim_bounds, uint8_t* value_packed, float* value_bounds) {
+    float* grad, uint8_t* optim_packed, float* optim_bounds, uint8_t* value_packed, float* value_bounds,
+    const int32_t* steps, int stride) {
     const float eps = 1e-15f, beta1 = 0.9f, beta2 = 0.999f, kEps = 1e-15f;
-    const float ibc1 = 1.0f / (1.0f - std::pow(beta1, (float)step));
-    const float ibc2 = 1.0f / (1.0f - std::pow(beta2, (float)step));
     const float decay = 2.0f * l2_reg / (float)numel;
     const bool plain = value_bits == 32;
     const float vq = plain ? 1.0f : (float)((1 << value_bits) - 1), vinv = 1.0f / vq;
@@ -1201,6 +1291,9 @@ void oracle_adam_qq(
             float g1 = u * (sqrt_g2 + kEps), g2 = sqrt_g2 * sqrt_g2;
             g1 = beta1 * g1 + (1.f - beta1) * v;
             g2 = beta2 * g2 + (1.f - beta2) * v * v;
+            const float stepf = (float)(steps ? steps[i / stride] : step);   // :166, :330
+            const float ibc1 = 1.0f / (1.0f - std::pow(beta1, stepf));
+            const float ibc2 = 1.0f / (1.0f - std::pow(beta2, stepf));
             x -= lr * ibc1 * g1 / (std::sqrt(g2 * ibc2) + eps);
             float sq = std::sqrt(std::max(g2, 0.0f));
             float un = g1 / (sq + kEps);
@@ -1224,6 +1317,13 @@ void oracle_adam_qq(
         if (!plain) { value_bounds[2 * b] = nv[0]; value_bounds[2 * b + 1] = nv[1]; }
         for (int k = 0; k < 4; ++k) optim_bounds[4 * b + k] = no[k];
     }
+}
+
+void oracle_adam_qq(
+    int64_t numel, int step, float lr, float l2_reg, float l2_reg_offset, float grad_scale, int zero_grad, int value_bits,
+    float* grad, uint8_t* optim_packed, float* optim_bounds, uint8_t* value_packed, float* value_bounds) {
+    oracle_adam_qq_steps(numel, step, lr, l2_reg, l2_reg_offset, grad_scale, zero_grad, value_bits, grad, optim_packed, optim_bounds,
+                         value_packed, value_bounds, nullptr, 1);
 }
 
 }  // extern "C"

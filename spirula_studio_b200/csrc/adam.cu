@@ -2,7 +2,8 @@
 // the SH coefficients and their optimiser state.
 //
 // Restates fused_optim_3dgs_geometry_kernel (src/kernels/optim/FusedGeometryOptim.cu:83-380,
-// regulariser weights zero, fp32 moments, scalar step), fused_adam_with_steps_kernel
+// fp32 moments; the regularisers, the scale-agnostic mean and per-splat steps in the EX
+// instantiation), fused_adam_with_steps_kernel
 // (src/kernels/optim/FusedAppearanceOptim.cu:11-56), fused_adam_with_steps_qq_kernel
 // (:291-418) and the codecs QuantizedTensor / QuantizedAdamState
 // (src/core/Tensor.h:978-1136,1313-1404).  beta1 = 0.9, beta2 = 0.999 and
@@ -24,21 +25,91 @@ __device__ __forceinline__ float adam_update(float x, float g, float& m1, float&
     return x - lr_ibc1 * m1 / (sqrtf(m2 * ibc2) + kAdamEps);
 }
 
-// geometry (means, quats, scales, opacities) + features_dc, one thread per splat
+__device__ __forceinline__ float inv_bias_correction(float beta, float step) { return 1.0f / (1.0f - powf(beta, step)); }
+
+// Gradients of the five per-splat regularisers with all loss cotangents 1 (reverse mode of
+// per_splat_losses, src/shaders/per_splat_losses.slang:5-141) for log-scales s, logit opacity o and
+// the normalised quaternion q.  The weights arrive divided by the splat count.
+__device__ __forceinline__ void per_splat_reg_grads(const float s[3], float o, const float q[4], const SsbAdamExtras& ex, float inv_n,
+                                                    float gs_out[3], float& go_out, float gq_out[4]) {
+    // mcmc opacity: w * sigmoid(o)
+    const float sg = 1.0f / (1.0f + expf(-o));
+    go_out = ex.mcmc_opacity_reg_weight * inv_n * sg * (1.0f - sg);
+    // mcmc scale: w * 1e-2 * (s0 + s1 + s2) / 3
+    const float gm = ex.mcmc_scale_reg_weight * inv_n * 1e-2f / 3.0f;
+    gs_out[0] = gs_out[1] = gs_out[2] = gm;
+    // index of the largest and the smallest scale, ties broken as nested max(max(x, y), z) differentiates
+    int imax = s[0] > s[1] ? 0 : 1; imax = s[imax] > s[2] ? imax : 2;
+    int imin = s[0] < s[1] ? 0 : 1; imin = s[imin] < s[2] ? imin : 2;
+    // scale ratio: w * (max(e_max / e_min, R) - R)
+    {
+        const float ratio = expf(s[imax]) / expf(s[imin]);
+        if (ratio > ex.max_gauss_ratio) {
+            const float w = ex.scale_regularization_weight * inv_n * ratio;
+#pragma unroll
+            for (int k = 0; k < 3; ++k) gs_out[k] += (k == imax ? w : 0.f) - (k == imin ? w : 0.f);
+        }
+    }
+    // effective rank: E = exp(2 s), p1 = E_max / S, p3 = E_min / S, p2 = 1 - p1 - p3, r = exp(entropy(p));
+    // loss = w * max(-log(r - 0.99999), 0) + w3 * p3
+    {
+        float E[3] = {expf(2.0f * s[0]), expf(2.0f * s[1]), expf(2.0f * s[2])};
+        const float S = E[0] + E[1] + E[2];
+        const float p1 = E[imax] / S, p3 = E[imin] / S, p2 = 1.0f - p1 - p3;
+        const float l1 = logf(p1), l2 = logf(p2), l3 = logf(p3);
+        const float r = expf(-p1 * l1 - p2 * l2 - p3 * l3);
+        float dH = 0.f;
+        if (-logf(r - 0.99999f) > 0.0f) dH = -ex.erank_reg_weight * inv_n / (r - 0.99999f) * r;
+        const float dp1 = dH * (l2 - l1), dp3 = dH * (l2 - l3) + ex.erank_reg_weight_s3 * inv_n;
+        const float dS = -(dp1 * p1 + dp3 * p3) / S;
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            float dE = dS + (k == imax ? dp1 / S : 0.f) + (k == imin ? dp3 / S : 0.f);
+            gs_out[k] += dE * 2.0f * E[k];
+        }
+    }
+    // quaternion norm: w * (n - 1 - log n), n = |q|
+    {
+        const float n = sqrtf(q[0] * q[0] + q[1] * q[1] + q[2] * q[2] + q[3] * q[3]);
+        const float w = ex.quat_norm_reg_weight * inv_n * (1.0f - 1.0f / n) / n;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) gq_out[k] = w * q[k];
+    }
+}
+
+// geometry (means, quats, scales, opacities) + features_dc, one thread per splat.
+// EX adds the per-splat regularisers, the scale-agnostic mean update and per-splat step counters.
+template <bool EX>
 __global__ void __launch_bounds__(256) adam_geometry_kernel(
     SsbSplats p, SsbSplats g, SsbSplats m1, SsbSplats m2, int64_t first, int64_t count, SsbAdamConfig cfg,
-    float ibc1, float ibc2, float dc_decay) {
+    float ibc1, float ibc2, float dc_decay, SsbAdamExtras ex) {
     int64_t i = first + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= first + count) return;
     const float gs = cfg.grad_scale;
     const bool zg = cfg.zero_grad != 0;
+    float reg_s[3] = {0.f, 0.f, 0.f}, reg_o = 0.f, reg_q[4] = {0.f, 0.f, 0.f, 0.f};
+    float s_old[3] = {0.f, 0.f, 0.f}, o_old = 0.f, qn_old[4] = {1.f, 0.f, 0.f, 0.f};
+    if (EX) {
+        if (ex.d_steps) {
+            const float step = (float)ex.d_steps[i];
+            ibc1 = inv_bias_correction(kBeta1, step);
+            ibc2 = inv_bias_correction(kBeta2, step);
+        }
+        const float4 q4 = ((const float4*)p.quats)[i];
+        const float inv = 1.0f / sqrtf(q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w);
+        qn_old[0] = q4.x * inv; qn_old[1] = q4.y * inv; qn_old[2] = q4.z * inv; qn_old[3] = q4.w * inv;
+#pragma unroll
+        for (int k = 0; k < 3; ++k) s_old[k] = p.scales[3 * i + k];
+        o_old = p.opacities[i];
+        per_splat_reg_grads(s_old, o_old, qn_old, ex, 1.0f / (float)ex.n_total, reg_s, reg_o, reg_q);
+    }
     const float lr_s = cfg.lr_scales * ibc1, lr_q = cfg.lr_quats * ibc1, lr_o = cfg.lr_opacities * ibc1, lr_m = cfg.lr_means * ibc1;
     const float lr_dc = cfg.lr_features_dc * ibc1;
 #pragma unroll
     for (int k = 0; k < 3; ++k) {
         int64_t q = 3 * i + k;
         float a = m1.scales[q], b = m2.scales[q];
-        p.scales[q] = adam_update(p.scales[q], gs * g.scales[q], a, b, lr_s, ibc2);
+        p.scales[q] = adam_update(p.scales[q], reg_s[k] + gs * g.scales[q], a, b, lr_s, ibc2);
         m1.scales[q] = a; m2.scales[q] = b;
         if (zg) g.scales[q] = 0.f;
     }
@@ -47,7 +118,7 @@ __global__ void __launch_bounds__(256) adam_geometry_kernel(
         float4 a4 = ((float4*)m1.quats)[i], b4 = ((float4*)m2.quats)[i];
         float inv = 1.0f / sqrtf(q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w);
         float q[4] = {q4.x * inv, q4.y * inv, q4.z * inv, q4.w * inv};
-        float gq[4] = {gs * g4.x, gs * g4.y, gs * g4.z, gs * g4.w};
+        float gq[4] = {reg_q[0] + gs * g4.x, reg_q[1] + gs * g4.y, reg_q[2] + gs * g4.z, reg_q[3] + gs * g4.w};
         float a[4] = {a4.x, a4.y, a4.z, a4.w}, b[4] = {b4.x, b4.y, b4.z, b4.w};
         float dq = q[0] * gq[0] + q[1] * gq[1] + q[2] * gq[2] + q[3] * gq[3];
         float u[4], n2 = 0.f;
@@ -65,17 +136,44 @@ __global__ void __launch_bounds__(256) adam_geometry_kernel(
     }
     {
         float a = m1.opacities[i], b = m2.opacities[i];
-        p.opacities[i] = adam_update(p.opacities[i], gs * g.opacities[i], a, b, lr_o, ibc2);
+        p.opacities[i] = adam_update(p.opacities[i], reg_o + gs * g.opacities[i], a, b, lr_o, ibc2);
         m1.opacities[i] = a; m2.opacities[i] = b;
         if (zg) g.opacities[i] = 0.f;
     }
+    if (EX && ex.use_scale_agnostic_mean) {
+        // first moment of covariance * gradient * sqrt(2 log(255 * opacity)), second moment of
+        // (gradient * 0.6 * screen radius)^2, all from the parameters before this update
+        float v[3] = {gs * g.means[3 * i], gs * g.means[3 * i + 1], gs * g.means[3 * i + 2]};
+        const float w = qn_old[0], x = qn_old[1], y = qn_old[2], z = qn_old[3];
+        const float R[9] = {1.f - 2.f * (y * y + z * z), 2.f * (x * y - w * z), 2.f * (x * z + w * y),
+                            2.f * (x * y + w * z), 1.f - 2.f * (x * x + z * z), 2.f * (y * z - w * x),
+                            2.f * (x * z - w * y), 2.f * (y * z + w * x), 1.f - 2.f * (x * x + y * y)};
+        float t[3];
 #pragma unroll
-    for (int k = 0; k < 3; ++k) {
-        int64_t q = 3 * i + k;
-        float a = m1.means[q], b = m2.means[q];
-        p.means[q] = adam_update(p.means[q], gs * g.means[q], a, b, lr_m, ibc2);
-        m1.means[q] = a; m2.means[q] = b;
-        if (zg) g.means[q] = 0.f;
+        for (int k = 0; k < 3; ++k) t[k] = expf(s_old[k]) * (R[k] * v[0] + R[3 + k] * v[1] + R[6 + k] * v[2]);   // S^2 R^T v
+        const float sg = 1.0f / (1.0f + expf(-o_old));
+        const float ext = sqrtf(2.0f * logf(fmaxf(255.0f * sg, 1.00001f)));
+        const float den = ex.d_radii[i] * 0.6f;
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            int64_t q = 3 * i + k;
+            const float num = (R[3 * k] * t[0] + R[3 * k + 1] * t[1] + R[3 * k + 2] * t[2]) * ext;
+            float a = m1.means[q], b = m2.means[q];
+            a = kBeta1 * a + (1.f - kBeta1) * num;
+            b = kBeta2 * b + (1.f - kBeta2) * v[k] * v[k] * den * den;
+            p.means[q] = p.means[q] - lr_m * a / (sqrtf(b * ibc2) + kAdamEps);
+            m1.means[q] = a; m2.means[q] = b;
+            if (zg) g.means[q] = 0.f;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            int64_t q = 3 * i + k;
+            float a = m1.means[q], b = m2.means[q];
+            p.means[q] = adam_update(p.means[q], gs * g.means[q], a, b, lr_m, ibc2);
+            m1.means[q] = a; m2.means[q] = b;
+            if (zg) g.means[q] = 0.f;
+        }
     }
     const float dc_off = 0.5f / 0.28209479177387814f;
 #pragma unroll
@@ -95,9 +193,25 @@ __global__ void __launch_bounds__(256) adam_geometry_kernel(
 // element-wise Adam (features_sh), four floats per thread
 __global__ void __launch_bounds__(256) adam_plain_kernel(
     float* __restrict__ param, float* __restrict__ grad, float* __restrict__ m1, float* __restrict__ m2, int64_t numel,
-    float lr_ibc1, float ibc2, float decay, float decay_offset, float grad_scale, int zero_grad) {
+    float lr_ibc1, float ibc2, float decay, float decay_offset, float grad_scale, int zero_grad,
+    const int32_t* __restrict__ steps, int stride, float lr) {
     int64_t i4 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i4 >= numel) return;
+    if (steps) {
+        // per-splat step counters: element i uses steps[i / stride]; `steps` is already offset to the range's first splat
+        for (int64_t i = i4; i < numel && i < i4 + 4; ++i) {
+            const float step = (float)steps[i / stride];
+            float x = param[i], gk = grad[i];
+            if (!isfinite(gk)) gk = 0.f;
+            gk *= grad_scale;
+            gk += decay * (fmaxf(x - decay_offset, 0.0f) + fminf(x + decay_offset, 0.0f));
+            float a = m1[i], b = m2[i];
+            param[i] = adam_update(x, gk, a, b, lr * inv_bias_correction(kBeta1, step), inv_bias_correction(kBeta2, step));
+            m1[i] = a; m2[i] = b;
+            if (zero_grad) grad[i] = 0.f;
+        }
+        return;
+    }
     if (i4 + 4 <= numel && ((((uintptr_t)param | (uintptr_t)grad | (uintptr_t)m1 | (uintptr_t)m2) & 15) == 0)) {
         float4 x = *(float4*)(param + i4), v = *(float4*)(grad + i4), a = *(float4*)(m1 + i4), b = *(float4*)(m2 + i4);
         float xs[4] = {x.x, x.y, x.z, x.w}, vs[4] = {v.x, v.y, v.z, v.w}, as[4] = {a.x, a.y, a.z, a.w}, bs[4] = {b.x, b.y, b.z, b.w};
@@ -180,7 +294,8 @@ template <int VALUE_BITS>
 __global__ void __launch_bounds__(64) adam_qq_kernel(
     float* __restrict__ grad, uint8_t* __restrict__ optim_packed, float4* __restrict__ optim_bounds,
     uint8_t* __restrict__ value_packed, float2* __restrict__ value_bounds, int64_t first_block, int64_t numel_total,
-    float lr_ibc1, float ibc2, float decay, float decay_offset, float grad_scale, int zero_grad) {
+    float lr_ibc1, float ibc2, float decay, float decay_offset, float grad_scale, int zero_grad,
+    const int32_t* __restrict__ steps, int stride, float lr) {
     __shared__ uint32_t sh[6][2];
     const int64_t blk = first_block + blockIdx.x;
     const int64_t idx0 = blk * 256 + threadIdx.x * 4;
@@ -245,7 +360,13 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
             g2 = kBeta2 * g2 + (1.f - kBeta2) * v * v;
             // the reference builds this kernel with --use_fast_math: approximate division and
             // square root are its own arithmetic here (cmake/SsBackendCuda.cmake:95-102)
-            xv -= __fdividef(lr_ibc1 * g1, sqrt_approx(g2 * ibc2) + kAdamEps);
+            float lr1 = lr_ibc1, c2 = ibc2;
+            if (steps) {
+                const float step = (float)steps[idx / stride];
+                lr1 = lr * inv_bias_correction(kBeta1, step);
+                c2 = inv_bias_correction(kBeta2, step);
+            }
+            xv -= __fdividef(lr1 * g1, sqrt_approx(g2 * c2) + kAdamEps);
             float sq = sqrt_approx(fmaxf(g2, 0.0f));
             u_new[k] = __fdividef(g1, sq + kAdamEps);
             float y = sq * (1.0f / kAdamEps);
@@ -344,27 +465,39 @@ extern "C" {
 
 int ssb_adam_step(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
                   int64_t first, int64_t count, const SsbAdamConfig* cfg, void* stream) {
+    return ssb_adam_step_ex(params, grads, m1, m2, first, count, cfg, nullptr, stream);
+}
+
+int ssb_adam_step_ex(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
+                     int64_t first, int64_t count, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream) {
     using namespace ssb;
     SSB_REQUIRE(params && grads && m1 && m2 && cfg, "ssb_adam_step: NULL argument");
     SSB_REQUIRE(first >= 0 && count >= 0, "ssb_adam_step: bad range");
     SSB_REQUIRE(cfg->step >= 1, "ssb_adam_step: step must be >= 1 (got %d)", cfg->step);
+    if (extras) {
+        SSB_REQUIRE(extras->n_total >= first + count, "ssb_adam_step_ex: n_total %lld is smaller than the range's end", (long long)extras->n_total);
+        SSB_REQUIRE(!extras->use_scale_agnostic_mean || extras->d_radii, "ssb_adam_step_ex: the scale-agnostic mean update needs d_radii");
+    }
     if (count == 0) return SSB_OK;
     cudaStream_t st = (cudaStream_t)stream;
     const float ibc1 = 1.0f / (1.0f - powf(kBeta1, (float)cfg->step));
     const float ibc2 = 1.0f / (1.0f - powf(kBeta2, (float)cfg->step));
-    // decay = 2 * l2_reg / numel, numel = whole-tensor element count is not known
-    // here for a sub-range; the regulariser weight is zero in every supported
-    // configuration, and a non-zero weight is applied per element of this call.
-    const float dc_decay = 2.0f * cfg->sh_reg_weight / (float)(count * 3);
-    adam_geometry_kernel<<<(unsigned)ceil_div(count, 256), 256, 0, st>>>(*params, *grads, *m1, *m2, first, count, *cfg, ibc1, ibc2, dc_decay);
+    // decay = 2 * l2_reg / numel of the whole tensor (fused_adam_step, FusedAppearanceOptim.cu:85); without
+    // extras->n_total the whole tensor is taken to be this call's range
+    const int64_t n_whole = extras ? extras->n_total : count;
+    const float dc_decay = 2.0f * cfg->sh_reg_weight / (float)(n_whole * 3);
+    const unsigned blocks = (unsigned)ceil_div(count, 256);
+    if (extras) adam_geometry_kernel<true><<<blocks, 256, 0, st>>>(*params, *grads, *m1, *m2, first, count, *cfg, ibc1, ibc2, dc_decay, *extras);
+    else adam_geometry_kernel<false><<<blocks, 256, 0, st>>>(*params, *grads, *m1, *m2, first, count, *cfg, ibc1, ibc2, dc_decay, SsbAdamExtras{});
     SSB_LAUNCHED("adam_geometry_kernel");
     if (params->features_sh) {
         SSB_REQUIRE(grads->features_sh && m1->features_sh && m2->features_sh, "ssb_adam_step: SH gradient/moment arrays missing");
         int64_t numel = count * 3 * kNumSh, off = first * 3 * kNumSh;
-        const float sh_decay = 2.0f * cfg->sh_reg_weight / (float)numel;
+        const float sh_decay = 2.0f * cfg->sh_reg_weight / (float)(n_whole * 3 * kNumSh);
+        const int32_t* steps = extras && extras->d_steps ? extras->d_steps + first : nullptr;
         adam_plain_kernel<<<(unsigned)ceil_div(ceil_div(numel, 4), 256), 256, 0, st>>>(
             params->features_sh + off, grads->features_sh + off, m1->features_sh + off, m2->features_sh + off, numel,
-            cfg->lr_features_sh * ibc1, ibc2, sh_decay, 0.0f, cfg->grad_scale, cfg->zero_grad);
+            cfg->lr_features_sh * ibc1, ibc2, sh_decay, 0.0f, cfg->grad_scale, cfg->zero_grad, steps, 3 * kNumSh, cfg->lr_features_sh);
         SSB_LAUNCHED("adam_plain_kernel");
     }
     return SSB_OK;
@@ -374,27 +507,33 @@ int ssb_adam_step_sh_quantized(float* d_grad, uint8_t* d_optim_packed, float* d_
                                void* d_value_packed, float* d_value_bounds, int32_t value_bits,
                                int64_t first_cell, int64_t numel, int64_t numel_total,
                                const SsbAdamConfig* cfg, void* stream) {
+    return ssb_adam_step_sh_quantized_steps(d_grad, d_optim_packed, d_optim_bounds, d_value_packed, d_value_bounds, value_bits, first_cell, numel,
+                                            numel_total, cfg, nullptr, 1, stream);
+}
+
+int ssb_adam_step_sh_quantized_steps(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds,
+                                     void* d_value_packed, float* d_value_bounds, int32_t value_bits,
+                                     int64_t first_cell, int64_t numel, int64_t numel_total,
+                                     const SsbAdamConfig* cfg, const int32_t* d_steps, int32_t cells_per_splat, void* stream) {
     using namespace ssb;
     SSB_REQUIRE(d_grad && d_optim_packed && d_optim_bounds && d_value_packed && cfg, "ssb_adam_step_sh_quantized: NULL argument");
     SSB_REQUIRE(value_bits == 8 || value_bits == 16 || value_bits == 32, "ssb_adam_step_sh_quantized: value_bits must be 8, 16 or 32 (got %d)", value_bits);
     SSB_REQUIRE(value_bits == 32 || d_value_bounds, "ssb_adam_step_sh_quantized: packed values need a bounds table");
     SSB_REQUIRE(first_cell >= 0 && (first_cell % 256) == 0 && numel >= 0 && first_cell + numel <= numel_total, "ssb_adam_step_sh_quantized: bad cell range");
     SSB_REQUIRE(cfg->step >= 1, "ssb_adam_step_sh_quantized: step must be >= 1");
+    SSB_REQUIRE(!d_steps || cells_per_splat >= 1, "ssb_adam_step_sh_quantized_steps: cells_per_splat must be >= 1");
     if (numel == 0) return SSB_OK;
     const float ibc1 = 1.0f / (1.0f - powf(kBeta1, (float)cfg->step));
     const float ibc2 = 1.0f / (1.0f - powf(kBeta2, (float)cfg->step));
     const float decay = 2.0f * cfg->sh_reg_weight / (float)numel_total;
     unsigned blocks = (unsigned)ceil_div(numel, 256);
     int64_t end_total = first_cell + numel;   // cells beyond the range belong to another caller
-    if (value_bits == 32)
-        adam_qq_kernel<32><<<blocks, 64, 0, (cudaStream_t)stream>>>(d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed,
-            (float2*)d_value_bounds, first_cell / 256, end_total, cfg->lr_features_sh * ibc1, ibc2, decay, 0.0f, cfg->grad_scale, cfg->zero_grad);
-    else if (value_bits == 8)
-        adam_qq_kernel<8><<<blocks, 64, 0, (cudaStream_t)stream>>>(d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed,
-            (float2*)d_value_bounds, first_cell / 256, end_total, cfg->lr_features_sh * ibc1, ibc2, decay, 0.0f, cfg->grad_scale, cfg->zero_grad);
-    else
-        adam_qq_kernel<16><<<blocks, 64, 0, (cudaStream_t)stream>>>(d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed,
-            (float2*)d_value_bounds, first_cell / 256, end_total, cfg->lr_features_sh * ibc1, ibc2, decay, 0.0f, cfg->grad_scale, cfg->zero_grad);
+#define SSB_QQ_ARGS d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed, (float2*)d_value_bounds, first_cell / 256, end_total, \
+        cfg->lr_features_sh * ibc1, ibc2, decay, 0.0f, cfg->grad_scale, cfg->zero_grad, d_steps, cells_per_splat, cfg->lr_features_sh
+    if (value_bits == 32) adam_qq_kernel<32><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS);
+    else if (value_bits == 8) adam_qq_kernel<8><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS);
+    else adam_qq_kernel<16><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS);
+#undef SSB_QQ_ARGS
     SSB_LAUNCHED("adam_qq_kernel");
     return SSB_OK;
 }

@@ -50,6 +50,13 @@ class SsbAdamConfig(C.Structure):
                 ("grad_scale", C.c_float), ("step", C.c_int32), ("zero_grad", C.c_int32)]
 
 
+class SsbAdamExtras(C.Structure):
+    _fields_ = [("max_gauss_ratio", C.c_float), ("scale_regularization_weight", C.c_float), ("mcmc_opacity_reg_weight", C.c_float),
+                ("mcmc_scale_reg_weight", C.c_float), ("erank_reg_weight", C.c_float), ("erank_reg_weight_s3", C.c_float),
+                ("quat_norm_reg_weight", C.c_float), ("use_scale_agnostic_mean", C.c_int32), ("d_radii", C.c_void_p),
+                ("d_steps", C.c_void_p), ("n_total", C.c_int64)]
+
+
 class SsbStepConfig(C.Structure):
     _fields_ = [("n_splats", C.c_int64), ("width", C.c_int32), ("height", C.c_int32), ("camera_model", C.c_int32),
                 ("antialiased", C.c_int32), ("isect_capacity", C.c_int64), ("w_l1", C.c_float), ("w_ssim", C.c_float)]
@@ -93,6 +100,8 @@ SIGNATURES = {
     "ssb_loss_l1_ssim_fwdbwd": (C.c_int, [_P, _P, _I32, _I32, _I32, _F, _F, _P, _P, _P]),
     "ssb_adam_step": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _P, _P]),
     "ssb_adam_step_sh_quantized": (C.c_int, [_P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _P, _P]),
+    "ssb_adam_step_ex": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _P, _P, _P]),
+    "ssb_adam_step_sh_quantized_steps": (C.c_int, [_P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _P, _P, _I32, _P]),
     "ssb_quant_encode": (C.c_int, [_P, _I64, _I32, _P, _P, _P]),
     "ssb_quant_decode": (C.c_int, [_P, _P, _I64, _I32, _P, _P]),
     "ssb_step_create": (C.c_int, [_P, _P]),

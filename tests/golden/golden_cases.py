@@ -96,4 +96,8 @@ def adam_inputs():
     numel = 45 * 200 + 7
     out["q8"] = dict(numel=numel, x0=rng.normal(0, 0.05, size=numel).astype(np.float32),
                      grads=[(rng.normal(size=numel) * 1e-3).astype(np.float32) for _ in range(3)])
+    # optional parts of the optimiser: regularisers, per-splat step counters, scale-agnostic mean
+    out["ex"] = dict(reg=np.array([3.0, 0.7, 0.9, 1.1, 0.5, 0.3, 0.2], np.float32),   # max ratio, then six undivided weights
+                     radii=rng.uniform(0.5, 40.0, size=n).astype(np.float32),
+                     steps=rng.integers(1, 50, size=n).astype(np.int32))
     return out

@@ -164,6 +164,46 @@ def run_adam(ref, out_dir):
         out[f"q8_s{step}_x"] = x.cpu().numpy()
         out[f"q8_s{step}_optim_packed"] = op.cpu().numpy()
         out[f"q8_s{step}_optim_bounds"] = ob.cpu().numpy()
+    # optional parts: "exA" = regularisers + per-splat step counters (geometry, DC with stride 3, SH with stride 45),
+    # "exB" = the same with the scale-agnostic mean update; three steps each from the seeded parameters
+    ex = inp["ex"]
+    d_reg_host = np.ascontiguousarray(ex["reg"])
+    d_radii, d_steps = dev(ex["radii"]), dev(ex["steps"])
+    for tag, agnostic in (("exA", 0), ("exB", 1)):
+        p = {k: dev(v.reshape(-1)) for k, v in inp["params"].items()}
+        m1 = {k: torch.zeros_like(t) for k, t in p.items()}
+        m2 = {k: torch.zeros_like(t) for k, t in p.items()}
+        for step, grads in enumerate(inp["grads"], start=1):
+            g = {k: dev(v.reshape(-1)) for k, v in grads.items()}
+            check(ref.ref_adam_geometry_ex(C.c_int64(n), step, C.c_float(inp["grad_scale"]), 0, C.c_float(lr["lr_means"]), C.c_float(lr["lr_quats"]),
+                                           C.c_float(lr["lr_scales"]), C.c_float(lr["lr_opacities"]),
+                                           P(p["means"]), P(g["means"]), P(m1["means"]), P(m2["means"]),
+                                           P(p["quats"]), P(g["quats"]), P(m1["quats"]), P(m2["quats"]),
+                                           P(p["scales"]), P(g["scales"]), P(m1["scales"]), P(m2["scales"]),
+                                           P(p["opacities"]), P(g["opacities"]), P(m1["opacities"]), P(m2["opacities"]),
+                                           d_reg_host.ctypes.data_as(C.c_void_p), agnostic, P(d_radii), P(d_steps)), "ref_adam_geometry_ex")
+            if not agnostic:
+                check(ref.ref_adam_plain_steps(C.c_int64(3 * n), P(d_steps), 3, C.c_float(lr["lr_features_dc"]), C.c_float(0.0),
+                                               C.c_float(0.5 / 0.28209479177387814), C.c_float(inp["grad_scale"]), 0,
+                                               P(p["features_dc"]), P(g["features_dc"]), P(m1["features_dc"]), P(m2["features_dc"])), "plain_steps dc")
+                check(ref.ref_adam_plain_steps(C.c_int64(45 * n), P(d_steps), 45, C.c_float(lr["lr_features_sh"]), C.c_float(0.0), C.c_float(0.0),
+                                               C.c_float(inp["grad_scale"]), 0,
+                                               P(p["features_sh"]), P(g["features_sh"]), P(m1["features_sh"]), P(m2["features_sh"])), "plain_steps sh")
+            keys = list(p) if not agnostic else ["means"]
+            for k in keys:
+                out[f"{tag}_p{step}_{k}"] = p[k].cpu().numpy()
+    # doubly quantised SH step with per-splat counters (16-bit values), one step from the seeded state;
+    # the counters are padded because the kernel reads steps[idx / stride] in every thread of its last block
+    q = inp["qq16"]
+    n_sp = (q["numel"] + 44) // 45
+    steps_q = torch.ones(n_sp + 8, dtype=torch.int32, device=DEV)
+    steps_q[:n_sp] = dev(np.resize(ex["steps"], n_sp))
+    vp, vb, op, ob = dev(q["value_packed"]), dev(q["value_bounds"]), dev(q["optim_packed"]), dev(q["optim_bounds"])
+    d_grad = dev(q["grads"][0])
+    check(ref.ref_adam_qq_steps(C.c_int64(q["numel"]), P(steps_q), 45, C.c_float(lr["lr_features_sh"]), C.c_float(0.0), C.c_float(inp["grad_scale"]), 0, 16,
+                                P(d_grad), P(op), P(ob), P(vp), P(vb)), "ref_adam_qq_steps")
+    out["qqs_value_packed"], out["qqs_value_bounds"] = vp.cpu().numpy(), vb.cpu().numpy()
+    out["qqs_optim_packed"], out["qqs_optim_bounds"] = op.cpu().numpy(), ob.cpu().numpy()
     np.savez_compressed(os.path.join(out_dir, "adam.npz"), **out)
 
 

@@ -179,3 +179,35 @@ def test_adam_vs_reference(oracle):
         assert np.allclose(ob, rob, rtol=2e-3, atol=1e-5)
         assert frac_bad(x, rx, 5e-6, 1e-4) <= 1e-3, step
         x, op, ob = rx.copy(), ro.copy(), rob.copy()
+
+
+def test_adam_extras_vs_reference(oracle):
+    """Regularisers, per-splat step counters and the scale-agnostic mean against the reference's kernels, three steps."""
+    gold = load("adam")
+    inp = adam_inputs()
+    ex, lr, gs, n = inp["ex"], inp["lrs"], inp["grad_scale"], inp["n"]
+    for tag, agnostic in (("exA", False), ("exB", True)):
+        p = {k: v.copy() for k, v in inp["params"].items()}
+        m1 = {k: np.zeros_like(v) for k, v in p.items()}
+        m2 = {k: np.zeros_like(v) for k, v in p.items()}
+        for step, grads in enumerate(inp["grads"], start=1):
+            g = {k: v.copy() for k, v in grads.items()}
+            oracle.adam_geometry_ex(p, g, m1, m2, step, lr, grad_scale=gs, reg=ex["reg"], scale_agnostic=agnostic, radii=ex["radii"], steps=ex["steps"])
+            keys = ["means"]
+            if not agnostic:
+                oracle.adam_plain(p["features_dc"], g["features_dc"], m1["features_dc"], m2["features_dc"], step, lr["lr_features_dc"], 0.0,
+                                  0.5 / 0.28209479177387814, gs, steps=ex["steps"], stride=3)
+                oracle.adam_plain(p["features_sh"], g["features_sh"], m1["features_sh"], m2["features_sh"], step, lr["lr_features_sh"], 0.0, 0.0, gs,
+                                  steps=ex["steps"], stride=45)
+                keys = list(p)
+            for k in keys:
+                assert frac_bad(p[k].reshape(-1), gold[f"{tag}_p{step}_{k}"], 5e-6, 1e-4) <= 1e-3, (tag, k, step)
+    q = inp["qq16"]
+    n_sp = (q["numel"] + 44) // 45
+    steps_q = np.ascontiguousarray(np.resize(ex["steps"], n_sp))
+    vp, vb, op, ob = (q[k].copy() for k in ("value_packed", "value_bounds", "optim_packed", "optim_bounds"))
+    oracle.adam_qq(q["grads"][0].copy(), op, ob, vp, vb, 16, 1, lr["lr_features_sh"], grad_scale=gs, steps=steps_q, stride=45)
+    dv = np.abs(vp.view(np.uint16).astype(np.int64) - gold["qqs_value_packed"].view(np.uint16).astype(np.int64))
+    do = np.abs(op.astype(np.int64) - gold["qqs_optim_packed"].astype(np.int64))
+    assert dv.max() <= 1 and do.max() <= 1 and (dv > 0).mean() <= 5e-2 and (do > 0).mean() <= 5e-2
+    assert np.allclose(vb, gold["qqs_value_bounds"], rtol=1e-4, atol=1e-7) and np.allclose(ob, gold["qqs_optim_bounds"], rtol=2e-3, atol=1e-5)

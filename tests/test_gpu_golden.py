@@ -198,3 +198,44 @@ def test_adam_vs_reference(lib, U):
         assert do.max() <= 1 and (do > 0).mean() <= 5e-2, step
         assert U.close_frac(x.cpu().numpy(), rx, 5e-6, 1e-4) <= 1e-3, step
         state = [rx, ro, rob]
+
+
+@pytest.mark.gpu
+def test_adam_extras_vs_reference(lib, U):
+    """ssb_adam_step_ex (regularisers, per-splat step counters, scale-agnostic mean) and the quantised SH step with
+    counters against the reference's kernels."""
+    gold = load("adam")
+    inp = adam_inputs()
+    ex, lr, gs, n = inp["ex"], inp["lrs"], inp["grad_scale"], inp["n"]
+    d_radii, d_steps = U.dev(ex["radii"]), U.dev(ex["steps"])
+    reg = [float(v) for v in ex["reg"]]
+    for tag, agnostic in (("exA", 0), ("exB", 1)):
+        p = {k: U.dev(v.reshape(-1)) for k, v in inp["params"].items()}
+        m1 = {k: torch.zeros_like(t) for k, t in p.items()}
+        m2 = {k: torch.zeros_like(t) for k, t in p.items()}
+        extras = L.SsbAdamExtras(*reg, agnostic, d_radii.data_ptr(), d_steps.data_ptr(), n)
+        for step, grads in enumerate(inp["grads"], start=1):
+            g = {k: U.dev(v.reshape(-1)) for k, v in grads.items()}
+            cfg = L.SsbAdamConfig(lr["lr_means"], lr["lr_quats"], lr["lr_scales"], lr["lr_opacities"], lr["lr_features_dc"], lr["lr_features_sh"],
+                                  0.0, gs, step, 0)
+            structs = [L.splats_struct(d) for d in (p, g, m1, m2)]
+            # two calls over half the splats each: the range offsets the counters and the radii
+            half = n // 2
+            L.check(lib.ssb_adam_step_ex(*[C.byref(s) for s in structs], 0, half, C.byref(cfg), C.byref(extras), None))
+            L.check(lib.ssb_adam_step_ex(*[C.byref(s) for s in structs], half, n - half, C.byref(cfg), C.byref(extras), None))
+            torch.cuda.synchronize()
+            for k in (list(p) if not agnostic else ["means"]):
+                assert U.close_frac(p[k].cpu().numpy(), gold[f"{tag}_p{step}_{k}"], 5e-6, 1e-4) <= 1e-3, (tag, k, step)
+    q = inp["qq16"]
+    n_sp = (q["numel"] + 44) // 45
+    steps_q = U.dev(np.ascontiguousarray(np.resize(ex["steps"], n_sp)))
+    vp, vb, op, ob = (U.dev(q[k]) for k in ("value_packed", "value_bounds", "optim_packed", "optim_bounds"))
+    d_g = U.dev(q["grads"][0])
+    cfg = L.SsbAdamConfig(0, 0, 0, 0, 0, lr["lr_features_sh"], 0.0, gs, 1, 0)
+    L.check(lib.ssb_adam_step_sh_quantized_steps(L.ptr(d_g), L.ptr(op), L.ptr(ob), L.ptr(vp), L.ptr(vb), 16, 0, q["numel"], q["numel"],
+                                                 C.byref(cfg), L.ptr(steps_q), 45, None))
+    torch.cuda.synchronize()
+    dv = np.abs(vp.cpu().numpy().view(np.uint16).astype(np.int64) - gold["qqs_value_packed"].view(np.uint16).astype(np.int64))
+    do = np.abs(op.cpu().numpy().astype(np.int64) - gold["qqs_optim_packed"].astype(np.int64))
+    assert dv.max() <= 1 and do.max() <= 1 and (dv > 0).mean() <= 5e-2 and (do > 0).mean() <= 5e-2
+    assert np.allclose(vb.cpu().numpy(), gold["qqs_value_bounds"], rtol=1e-4, atol=1e-7)

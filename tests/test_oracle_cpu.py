@@ -289,3 +289,76 @@ def test_adam_first_step_moves_by_lr(oracle):
     oracle.adam_plain(p, g, m1, m2, 1, 2.5e-3)
     assert np.allclose(p0 - p, 2.5e-3 * np.sign(g), rtol=1e-4, atol=1e-9)
     assert np.allclose(m1, 0.1 * g, rtol=1e-6) and np.allclose(m2, 0.001 * g * g, rtol=1e-4)
+
+
+def _per_splat_losses64(s, o, q, reg):
+    """Sum of the five per-splat regularisers in float64 (src/shaders/per_splat_losses.slang:5-107)."""
+    max_ratio, w_ratio, w_op, w_ms, w_er, w_er3, w_qn = reg
+    e = np.exp(s)
+    E = np.exp(2 * s)
+    p = E / E.sum()
+    p1, p3 = p.max(), p.min()
+    p2 = 1.0 - p1 - p3
+    r = np.exp(-(p1 * np.log(p1) + p2 * np.log(p2) + p3 * np.log(p3)))
+    n = np.linalg.norm(q)
+    return (w_op / (1 + np.exp(-o)) + w_ms * 1e-2 * s.sum() / 3 + w_ratio * (max(e.max() / e.min(), max_ratio) - max_ratio)
+            + w_er * max(-np.log(r - 0.99999), 0.0) + w_er3 * p3 + w_qn * (n - 1 - np.log(n)))
+
+
+def test_adam_regulariser_gradients_match_finite_differences(oracle):
+    """With zero data gradients and a zero state, the first moment after one step is 0.1 * (regulariser gradient / N)."""
+    rng = np.random.default_rng(77)
+    n = 64
+    p = dict(means=rng.normal(size=(n, 3)).astype(np.float32), quats=rng.normal(size=(n, 4)).astype(np.float32),
+             scales=rng.normal(-2.0, 0.6, size=(n, 3)).astype(np.float32), opacities=rng.normal(size=n).astype(np.float32))
+    p["quats"] /= np.linalg.norm(p["quats"], axis=1, keepdims=True)
+    p0 = {k: v.copy() for k, v in p.items()}
+    g = {k: np.zeros_like(v) for k, v in p.items()}
+    m1 = {k: np.zeros_like(v) for k, v in p.items()}
+    m2 = {k: np.zeros_like(v) for k, v in p.items()}
+    reg = np.array([3.0, 0.7, 0.9, 1.1, 0.5, 0.3, 0.0], np.float32)
+    lrs = dict(lr_means=1e-3, lr_quats=1e-3, lr_scales=5e-3, lr_opacities=5e-2)
+    oracle.adam_geometry_ex(p, g, m1, m2, 1, lrs, reg=reg)
+    gs, go = m1["scales"] * 10 * n, m1["opacities"] * 10 * n
+    h = 1e-5
+    for i in range(n):
+        s, o, q = p0["scales"][i].astype(np.float64), float(p0["opacities"][i]), p0["quats"][i].astype(np.float64)
+        for k in range(3):
+            d = np.zeros(3); d[k] = h
+            fd = (_per_splat_losses64(s + d, o, q, reg) - _per_splat_losses64(s - d, o, q, reg)) / (2 * h)
+            assert abs(gs[i, k] - fd) <= 2e-3 * max(1.0, abs(fd)), (i, k, gs[i, k], fd)
+        fd = (_per_splat_losses64(s, o + h, q, reg) - _per_splat_losses64(s, o - h, q, reg)) / (2 * h)
+        assert abs(go[i] - fd) <= 2e-3 * max(1.0, abs(fd))
+    assert np.abs(m1["means"]).max() == 0 and np.abs(m1["quats"]).max() < 1e-7
+
+
+def test_adam_extras_default_to_the_plain_step(oracle):
+    """No regularisers, no scale-agnostic mean and per-splat counters all equal to the scalar step: identical updates."""
+    rng = np.random.default_rng(78)
+    n = 300
+    mk = lambda: dict(means=rng.normal(size=(n, 3)).astype(np.float32), quats=rng.normal(size=(n, 4)).astype(np.float32),
+                      scales=rng.normal(size=(n, 3)).astype(np.float32), opacities=rng.normal(size=n).astype(np.float32))
+    p, g, m1, m2 = mk(), mk(), mk(), mk()
+    for k in m2:
+        m2[k] = np.abs(m2[k])
+    a = [{k: v.copy() for k, v in d.items()} for d in (p, g, m1, m2)]
+    b = [{k: v.copy() for k, v in d.items()} for d in (p, g, m1, m2)]
+    lrs = dict(lr_means=1e-3, lr_quats=1e-3, lr_scales=5e-3, lr_opacities=5e-2)
+    oracle.adam_geometry(*a, 7, lrs, grad_scale=0.5)
+    oracle.adam_geometry_ex(*b, 3, lrs, grad_scale=0.5, steps=np.full(n, 7, np.int32))
+    for da, db in zip(a, b):
+        for k in da:
+            assert np.array_equal(da[k], db[k]), k
+    # the scale-agnostic update changes only the means and their moments
+    c = [{k: v.copy() for k, v in d.items()} for d in (p, g, m1, m2)]
+    oracle.adam_geometry_ex(*c, 7, lrs, grad_scale=0.5, scale_agnostic=True, radii=rng.uniform(1, 30, size=n).astype(np.float32))
+    for k in ("quats", "scales", "opacities"):
+        assert np.array_equal(a[0][k], c[0][k])
+    assert not np.array_equal(a[0]["means"], c[0]["means"])
+    # plain and quantised element-wise kernels: counters equal to the scalar step reproduce it
+    x = rng.normal(size=45 * 40).astype(np.float32); gr = rng.normal(size=x.size).astype(np.float32)
+    xa, xb = x.copy(), x.copy()
+    ma, va, mb, vb = (np.zeros_like(x) for _ in range(4))
+    oracle.adam_plain(xa, gr.copy(), ma, va, 5, 2.5e-3)
+    oracle.adam_plain(xb, gr.copy(), mb, vb, 1, 2.5e-3, steps=np.full(40, 5, np.int32), stride=45)
+    assert np.array_equal(xa, xb)

@@ -329,12 +329,15 @@ int ssb_adam_step_sh_quantized(float* d_grad, uint8_t* d_optim_packed, float* d_
                                int64_t first_cell, int64_t numel, int64_t numel_total,
                                const SsbAdamConfig* cfg, void* stream);
 
-/* The same with per-splat step counters: cell c uses d_steps[c / cells_per_splat]
- * (steps[idx / stride], FusedAppearanceOptim.cu:166,330).  d_steps == NULL is the call above. */
-int ssb_adam_step_sh_quantized_steps(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds,
-                                     void* d_value_packed, float* d_value_bounds, int32_t value_bits,
-                                     int64_t first_cell, int64_t numel, int64_t numel_total,
-                                     const SsbAdamConfig* cfg, const int32_t* d_steps, int32_t cells_per_splat, void* stream);
+/* The same with the two remaining options of the reference's launchers (FusedAppearanceOptim.cu:232-271,421-479):
+ * optim_bits = 4 stores the state as QuantizedAdamState<4,256> (one byte per cell, u in the low nibble;
+ * src/core/Tensor.h:1051-1054,1091-1095) instead of 8 (two bytes per cell); d_steps != NULL gives per-splat
+ * step counters, cell c using d_steps[c / cells_per_splat] (steps[idx / stride], :166,330).
+ * optim_bits = 8 and d_steps == NULL is the call above. */
+int ssb_adam_step_sh_quantized_ex(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds,
+                                  void* d_value_packed, float* d_value_bounds, int32_t value_bits, int32_t optim_bits,
+                                  int64_t first_cell, int64_t numel, int64_t numel_total,
+                                  const SsbAdamConfig* cfg, const int32_t* d_steps, int32_t cells_per_splat, void* stream);
 
 /* QuantizedTensor<BITS,256>::encode_v / decode_v over whole buffers
  * (src/core/Tensor.h:1366-1393); bounds = float2 per 256 cells. */

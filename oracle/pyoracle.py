@@ -212,10 +212,11 @@ def quant_decode(packed, bounds, n, bits):
 
 
 def adam_qq(grad, optim_packed, optim_bounds, value_packed, value_bounds, value_bits, step, lr, l2_reg=0.0, grad_scale=1.0, zero_grad=0,
-            steps=None, stride=1):
-    load().oracle_adam_qq_steps(C.c_int64(grad.size), C.c_int(step), C.c_float(lr), C.c_float(l2_reg), C.c_float(0.0), C.c_float(grad_scale),
+            steps=None, stride=1, optim_bits=8):
+    """optim_bits = 4: optim_packed holds one byte per cell instead of two."""
+    load().oracle_adam_qq_ex(C.c_int64(grad.size), C.c_int(step), C.c_float(lr), C.c_float(l2_reg), C.c_float(0.0), C.c_float(grad_scale),
                                 C.c_int(zero_grad), C.c_int(value_bits), _p(grad), _p(optim_packed), _p(optim_bounds), _p(value_packed),
-                                _p(value_bounds), _p(steps) if steps is not None else None, C.c_int(stride))
+                                _p(value_bounds), _p(steps) if steps is not None else None, C.c_int(stride), C.c_int(optim_bits))
 
 
 def forward_chain(splats, viewmats, intrins, W, H, shq=None, model=0):

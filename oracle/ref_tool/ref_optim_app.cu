@@ -63,3 +63,30 @@ extern "C" int ref_adam_qq_steps(int64_t numel, const int32_t* steps, int stride
     #undef ARGS
     return (int)cudaDeviceSynchronize();
 }
+
+// QuantizedAdamState<4,256> (one byte per cell): fused_adam_step_quantized with bits = 4 (:256-259) and
+// fused_adam_step_quantized_value with optim_bits = 4 (:455-462).
+extern "C" int ref_adam_q4(int64_t numel, int step, float lr, float l2_reg, float grad_scale, int zero_grad,
+                           float* param, float* grad, uint8_t* optim_packed, float* optim_bounds) {
+    const float decay = 2.0f * l2_reg / (float)numel;
+    uint32_t blocks = _CEIL_DIV((uint32_t)numel, 256);
+    if (zero_grad) fused_adam_with_steps_8bit_kernel<256, 4, true><<<blocks, 256>>>(param, grad, optim_packed, (float4*)optim_bounds, lr, step, nullptr, decay, 0.0f, grad_scale, numel, 45);
+    else fused_adam_with_steps_8bit_kernel<256, 4, false><<<blocks, 256>>>(param, grad, optim_packed, (float4*)optim_bounds, lr, step, nullptr, decay, 0.0f, grad_scale, numel, 45);
+    return (int)cudaDeviceSynchronize();
+}
+
+extern "C" int ref_adam_qq_o4(int64_t numel, int step, float lr, float l2_reg, float grad_scale, int zero_grad, int value_bits,
+                              float* grad, uint8_t* optim_packed, float* optim_bounds, uint8_t* value_packed, float* value_bounds) {
+    const float decay = 2.0f * l2_reg / (float)numel;
+    uint32_t blocks = _CEIL_DIV((uint32_t)numel, 256);
+    #define ARGS grad, nullptr, nullptr, optim_packed, (float4*)optim_bounds, value_packed, (float2*)value_bounds, lr, step, nullptr, decay, 0.0f, grad_scale, numel, 45
+    if (value_bits == 16) {
+        if (zero_grad) fused_adam_with_steps_qq_kernel<256, 4, 16, true><<<blocks, 256>>>(ARGS);
+        else fused_adam_with_steps_qq_kernel<256, 4, 16, false><<<blocks, 256>>>(ARGS);
+    } else {
+        if (zero_grad) fused_adam_with_steps_qq_kernel<256, 4, 8, true><<<blocks, 256>>>(ARGS);
+        else fused_adam_with_steps_qq_kernel<256, 4, 8, false><<<blocks, 256>>>(ARGS);
+    }
+    #undef ARGS
+    return (int)cudaDeviceSynchronize();
+}

@@ -1258,15 +1258,17 @@ void oracle_quant_decode(int64_t numel, int bits, const uint8_t* packed, const f
 // QuantizedTensor<VALUE_BITS,256> (:1313-1404).  fp32 gradient input.
 // value_bits == 32: the values are plain fp32 and only the state is quantised
 // (fused_adam_with_steps_8bit_kernel, src/kernels/optim/FusedAppearanceOptim.cu:137-229).
-void oracle_adam_qq_steps(
+void oracle_adam_qq_ex(
     int64_t numel, int step, float lr, float l2_reg, float l2_reg_offset, float grad_scale, int zero_grad, int value_bits,
     float* grad, uint8_t* optim_packed, float* optim_bounds, uint8_t* value_packed, float* value_bounds,
-    const int32_t* steps, int stride) {
+    const int32_t* steps, int stride, int optim_bits) {
     const float eps = 1e-15f, beta1 = 0.9f, beta2 = 0.999f, kEps = 1e-15f;
     const float decay = 2.0f * l2_reg / (float)numel;
     const bool plain = value_bits == 32;
     const float vq = plain ? 1.0f : (float)((1 << value_bits) - 1), vinv = 1.0f / vq;
-    const float oq = 255.0f, oinv = 1.0f / 255.0f;
+    // QuantizedAdamState<4|8,256>: 4 bits = one byte per cell, u in the low nibble (src/core/Tensor.h:1051-1054)
+    const bool nib = optim_bits == 4;
+    const float oq = nib ? 15.0f : 255.0f, oinv = 1.0f / oq;
     int64_t nb = (numel + 255) / 256;
     float* value_f32 = reinterpret_cast<float*>(value_packed);
 #pragma omp parallel for schedule(static)
@@ -1284,7 +1286,8 @@ void oracle_adam_qq_steps(
             if (zero_grad) grad[i] = 0.f;
             v *= grad_scale;
             v += decay * (std::max(x - l2_reg_offset, 0.0f) + std::min(x + l2_reg_offset, 0.0f));
-            float u_q = (float)optim_packed[2 * i], s_q = (float)optim_packed[2 * i + 1];
+            float u_q = nib ? (float)(optim_packed[i] & 15) : (float)optim_packed[2 * i];
+            float s_q = nib ? (float)(optim_packed[i] >> 4) : (float)optim_packed[2 * i + 1];
             float u = omm[0] + (omm[1] - omm[0]) * (u_q * oinv);
             float ls = omm[2] + (omm[3] - omm[2]) * (s_q * oinv);
             float sqrt_g2 = kEps * std::expm1(ls);
@@ -1312,7 +1315,8 @@ void oracle_adam_qq_steps(
             else reinterpret_cast<uint16_t*>(value_packed)[i] = (uint16_t)qf;
             float uq = std::min(std::max(std::round(oq * (us[i - lo] - no[0]) / urange), 0.0f), oq);
             float sq = std::min(std::max(std::round(oq * (ss[i - lo] - no[2]) / srange), 0.0f), oq);
-            optim_packed[2 * i] = (uint8_t)uq; optim_packed[2 * i + 1] = (uint8_t)sq;
+            if (nib) optim_packed[i] = (uint8_t)((uint8_t)uq | ((uint8_t)sq << 4));
+            else { optim_packed[2 * i] = (uint8_t)uq; optim_packed[2 * i + 1] = (uint8_t)sq; }
         }
         if (!plain) { value_bounds[2 * b] = nv[0]; value_bounds[2 * b + 1] = nv[1]; }
         for (int k = 0; k < 4; ++k) optim_bounds[4 * b + k] = no[k];
@@ -1322,8 +1326,8 @@ void oracle_adam_qq_steps(
 void oracle_adam_qq(
     int64_t numel, int step, float lr, float l2_reg, float l2_reg_offset, float grad_scale, int zero_grad, int value_bits,
     float* grad, uint8_t* optim_packed, float* optim_bounds, uint8_t* value_packed, float* value_bounds) {
-    oracle_adam_qq_steps(numel, step, lr, l2_reg, l2_reg_offset, grad_scale, zero_grad, value_bits, grad, optim_packed, optim_bounds,
-                         value_packed, value_bounds, nullptr, 1);
+    oracle_adam_qq_ex(numel, step, lr, l2_reg, l2_reg_offset, grad_scale, zero_grad, value_bits, grad, optim_packed, optim_bounds,
+                      value_packed, value_bounds, nullptr, 1, 8);
 }
 
 }  // extern "C"

@@ -290,7 +290,8 @@ __device__ __forceinline__ void block_minmax(const float (&vmin)[NMIN], const fl
 // One CTA of 64 threads = one 256-cell quantisation block, four consecutive cells per thread
 // (16-byte gradient loads, 8-byte code loads); the block minima/maxima are folded per thread
 // first, then one redux.sync per value per warp and a two-entry exchange through shared memory.
-template <int VALUE_BITS>
+// OPTIM_BITS = 8: two bytes per cell (u, s); 4: one byte per cell, u in the low nibble (QuantizedAdamState<4,256>).
+template <int VALUE_BITS, int OPTIM_BITS>
 __global__ void __launch_bounds__(64) adam_qq_kernel(
     float* __restrict__ grad, uint8_t* __restrict__ optim_packed, float4* __restrict__ optim_bounds,
     uint8_t* __restrict__ value_packed, float2* __restrict__ value_bounds, int64_t first_block, int64_t numel_total,
@@ -303,7 +304,8 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
     // fused_adam_step_quantized, src/kernels/optim/FusedAppearanceOptim.cu:137-271)
     constexpr bool kPlainValue = VALUE_BITS == 32;
     constexpr float vq = kPlainValue ? 1.0f : (float)((1u << (VALUE_BITS & 31)) - 1u), vinv = 1.0f / vq;
-    const float oq = 255.0f, oinv = 1.0f / 255.0f;
+    constexpr bool kNibbles = OPTIM_BITS == 4;
+    const float oq = kNibbles ? 15.0f : 255.0f, oinv = 1.0f / oq;
     const float2 vmm = kPlainValue ? make_float2(0.f, 0.f) : value_bounds[blk];
     const float4 omm = optim_bounds[blk];
     float x[4], u_new[4], s_new[4];
@@ -324,9 +326,15 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
             const uchar4 c = *(const uchar4*)(value_packed + idx0);
             vcode[0] = c.x; vcode[1] = c.y; vcode[2] = c.z; vcode[3] = c.w;
         }
-        const uint2 oc = *(const uint2*)(optim_packed + 2 * idx0);
-        ucode[0] = oc.x & 255u; scode[0] = (oc.x >> 8) & 255u; ucode[1] = (oc.x >> 16) & 255u; scode[1] = oc.x >> 24;
-        ucode[2] = oc.y & 255u; scode[2] = (oc.y >> 8) & 255u; ucode[3] = (oc.y >> 16) & 255u; scode[3] = oc.y >> 24;
+        if (kNibbles) {
+            const uint32_t oc = *(const uint32_t*)(optim_packed + idx0);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { ucode[k] = (oc >> (8 * k)) & 15u; scode[k] = (oc >> (8 * k + 4)) & 15u; }
+        } else {
+            const uint2 oc = *(const uint2*)(optim_packed + 2 * idx0);
+            ucode[0] = oc.x & 255u; scode[0] = (oc.x >> 8) & 255u; ucode[1] = (oc.x >> 16) & 255u; scode[1] = oc.x >> 24;
+            ucode[2] = oc.y & 255u; scode[2] = (oc.y >> 8) & 255u; ucode[3] = (oc.y >> 16) & 255u; scode[3] = oc.y >> 24;
+        }
         if (zero_grad) *(float4*)(grad + idx0) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
@@ -337,7 +345,8 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
             gv[k] = grad[idx];
             vcode[k] = kPlainValue ? ((const uint32_t*)value_packed)[idx]
                                    : VALUE_BITS == 8 ? (uint32_t)value_packed[idx] : (uint32_t)((const uint16_t*)value_packed)[idx];
-            ucode[k] = optim_packed[2 * idx]; scode[k] = optim_packed[2 * idx + 1];
+            if (kNibbles) { const uint32_t b = optim_packed[idx]; ucode[k] = b & 15u; scode[k] = b >> 4; }
+            else { ucode[k] = optim_packed[2 * idx]; scode[k] = optim_packed[2 * idx + 1]; }
             if (zero_grad) grad[idx] = 0.f;
         }
         x[k] = u_new[k] = s_new[k] = 0.f;
@@ -407,13 +416,14 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
         vout[k] = kPlainValue ? __float_as_uint(x[k]) : (uint32_t)fminf(fmaxf(rintf((x[k] - vmin) * vscale), 0.0f), vq);
         uint32_t uqc = (uint32_t)fminf(fmaxf(rintf((u_new[k] - umin) * uscale), 0.0f), oq);
         uint32_t sqc = (uint32_t)fminf(fmaxf(rintf((s_new[k] - smin) * sscale), 0.0f), oq);
-        oout[k] = uqc | (sqc << 8);
+        oout[k] = kNibbles ? (uqc | (sqc << 4)) : (uqc | (sqc << 8));
     }
     if (full) {
         if (kPlainValue) *(uint4*)((float*)value_packed + idx0) = make_uint4(vout[0], vout[1], vout[2], vout[3]);
         else if (VALUE_BITS == 16) *(ushort4*)((uint16_t*)value_packed + idx0) = make_ushort4(vout[0], vout[1], vout[2], vout[3]);
         else *(uchar4*)(value_packed + idx0) = make_uchar4(vout[0], vout[1], vout[2], vout[3]);
-        *(uint2*)(optim_packed + 2 * idx0) = make_uint2(oout[0] | (oout[1] << 16), oout[2] | (oout[3] << 16));
+        if (kNibbles) *(uint32_t*)(optim_packed + idx0) = oout[0] | (oout[1] << 8) | (oout[2] << 16) | (oout[3] << 24);
+        else *(uint2*)(optim_packed + 2 * idx0) = make_uint2(oout[0] | (oout[1] << 16), oout[2] | (oout[3] << 16));
     } else {
 #pragma unroll
         for (int k = 0; k < 4; ++k)
@@ -422,7 +432,8 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
                 if (kPlainValue) ((uint32_t*)value_packed)[idx] = vout[k];
                 else if (VALUE_BITS == 8) value_packed[idx] = (uint8_t)vout[k];
                 else ((uint16_t*)value_packed)[idx] = (uint16_t)vout[k];
-                optim_packed[2 * idx] = (uint8_t)(oout[k] & 255u); optim_packed[2 * idx + 1] = (uint8_t)(oout[k] >> 8);
+                if (kNibbles) optim_packed[idx] = (uint8_t)oout[k];
+                else { optim_packed[2 * idx] = (uint8_t)(oout[k] & 255u); optim_packed[2 * idx + 1] = (uint8_t)(oout[k] >> 8); }
             }
     }
     if (threadIdx.x == 0) {
@@ -507,21 +518,22 @@ int ssb_adam_step_sh_quantized(float* d_grad, uint8_t* d_optim_packed, float* d_
                                void* d_value_packed, float* d_value_bounds, int32_t value_bits,
                                int64_t first_cell, int64_t numel, int64_t numel_total,
                                const SsbAdamConfig* cfg, void* stream) {
-    return ssb_adam_step_sh_quantized_steps(d_grad, d_optim_packed, d_optim_bounds, d_value_packed, d_value_bounds, value_bits, first_cell, numel,
-                                            numel_total, cfg, nullptr, 1, stream);
+    return ssb_adam_step_sh_quantized_ex(d_grad, d_optim_packed, d_optim_bounds, d_value_packed, d_value_bounds, value_bits, 8, first_cell, numel,
+                                         numel_total, cfg, nullptr, 1, stream);
 }
 
-int ssb_adam_step_sh_quantized_steps(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds,
-                                     void* d_value_packed, float* d_value_bounds, int32_t value_bits,
-                                     int64_t first_cell, int64_t numel, int64_t numel_total,
-                                     const SsbAdamConfig* cfg, const int32_t* d_steps, int32_t cells_per_splat, void* stream) {
+int ssb_adam_step_sh_quantized_ex(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds,
+                                  void* d_value_packed, float* d_value_bounds, int32_t value_bits, int32_t optim_bits,
+                                  int64_t first_cell, int64_t numel, int64_t numel_total,
+                                  const SsbAdamConfig* cfg, const int32_t* d_steps, int32_t cells_per_splat, void* stream) {
     using namespace ssb;
     SSB_REQUIRE(d_grad && d_optim_packed && d_optim_bounds && d_value_packed && cfg, "ssb_adam_step_sh_quantized: NULL argument");
     SSB_REQUIRE(value_bits == 8 || value_bits == 16 || value_bits == 32, "ssb_adam_step_sh_quantized: value_bits must be 8, 16 or 32 (got %d)", value_bits);
     SSB_REQUIRE(value_bits == 32 || d_value_bounds, "ssb_adam_step_sh_quantized: packed values need a bounds table");
     SSB_REQUIRE(first_cell >= 0 && (first_cell % 256) == 0 && numel >= 0 && first_cell + numel <= numel_total, "ssb_adam_step_sh_quantized: bad cell range");
     SSB_REQUIRE(cfg->step >= 1, "ssb_adam_step_sh_quantized: step must be >= 1");
-    SSB_REQUIRE(!d_steps || cells_per_splat >= 1, "ssb_adam_step_sh_quantized_steps: cells_per_splat must be >= 1");
+    SSB_REQUIRE(optim_bits == 4 || optim_bits == 8, "ssb_adam_step_sh_quantized_ex: optim_bits must be 4 or 8 (got %d)", optim_bits);
+    SSB_REQUIRE(!d_steps || cells_per_splat >= 1, "ssb_adam_step_sh_quantized_ex: cells_per_splat must be >= 1");
     if (numel == 0) return SSB_OK;
     const float ibc1 = 1.0f / (1.0f - powf(kBeta1, (float)cfg->step));
     const float ibc2 = 1.0f / (1.0f - powf(kBeta2, (float)cfg->step));
@@ -530,9 +542,14 @@ int ssb_adam_step_sh_quantized_steps(float* d_grad, uint8_t* d_optim_packed, flo
     int64_t end_total = first_cell + numel;   // cells beyond the range belong to another caller
 #define SSB_QQ_ARGS d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed, (float2*)d_value_bounds, first_cell / 256, end_total, \
         cfg->lr_features_sh * ibc1, ibc2, decay, 0.0f, cfg->grad_scale, cfg->zero_grad, d_steps, cells_per_splat, cfg->lr_features_sh
-    if (value_bits == 32) adam_qq_kernel<32><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS);
-    else if (value_bits == 8) adam_qq_kernel<8><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS);
-    else adam_qq_kernel<16><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS);
+#define SSB_QQ_LAUNCH(OB) \
+    do { \
+        if (value_bits == 32) adam_qq_kernel<32, OB><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS); \
+        else if (value_bits == 8) adam_qq_kernel<8, OB><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS); \
+        else adam_qq_kernel<16, OB><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS); \
+    } while (0)
+    if (optim_bits == 4) SSB_QQ_LAUNCH(4); else SSB_QQ_LAUNCH(8);
+#undef SSB_QQ_LAUNCH
 #undef SSB_QQ_ARGS
     SSB_LAUNCHED("adam_qq_kernel");
     return SSB_OK;

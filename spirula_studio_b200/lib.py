@@ -101,7 +101,7 @@ SIGNATURES = {
     "ssb_adam_step": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _P, _P]),
     "ssb_adam_step_sh_quantized": (C.c_int, [_P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _P, _P]),
     "ssb_adam_step_ex": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _P, _P, _P]),
-    "ssb_adam_step_sh_quantized_steps": (C.c_int, [_P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _P, _P, _I32, _P]),
+    "ssb_adam_step_sh_quantized_ex": (C.c_int, [_P, _P, _P, _P, _P, _I32, _I32, _I64, _I64, _I64, _P, _P, _I32, _P]),
     "ssb_quant_encode": (C.c_int, [_P, _I64, _I32, _P, _P, _P]),
     "ssb_quant_decode": (C.c_int, [_P, _P, _I64, _I32, _P, _P]),
     "ssb_step_create": (C.c_int, [_P, _P]),

@@ -204,6 +204,32 @@ def run_adam(ref, out_dir):
                                 P(d_grad), P(op), P(ob), P(vp), P(vb)), "ref_adam_qq_steps")
     out["qqs_value_packed"], out["qqs_value_bounds"] = vp.cpu().numpy(), vb.cpu().numpy()
     out["qqs_optim_packed"], out["qqs_optim_bounds"] = op.cpu().numpy(), ob.cpu().numpy()
+    # 4-bit optimiser state (one byte per cell): fp32 values for three steps from a zero state (the q8 inputs),
+    # and 16-bit values for one step from the seeded state (the qq16 inputs)
+    q = inp["q8"]
+    nb = (q["numel"] + 255) // 256
+    x_buf = torch.zeros(nb * 256, dtype=torch.float32, device=DEV)      # whole blocks: see the note above
+    x = x_buf[:q["numel"]]
+    x.copy_(dev(q["x0"]))
+    op = torch.zeros(nb * 256, dtype=torch.uint8, device=DEV)
+    ob = torch.zeros(nb * 4, dtype=torch.float32, device=DEV)
+    for step, grad in enumerate(q["grads"], start=1):
+        d_grad = dev(grad)
+        check(ref.ref_adam_q4(C.c_int64(q["numel"]), step, C.c_float(lr["lr_features_sh"]), C.c_float(0.0), C.c_float(inp["grad_scale"]), 0,
+                              P(x), P(d_grad), P(op), P(ob)), "ref_adam_q4")
+        out[f"q4_s{step}_x"] = x.cpu().numpy()
+        out[f"q4_s{step}_optim_packed"] = op[:q["numel"]].cpu().numpy()
+        out[f"q4_s{step}_optim_bounds"] = ob.cpu().numpy()
+    q = inp["qq16"]
+    vp, vb = dev(q["value_packed"]), dev(q["value_bounds"])
+    op = torch.zeros(q["numel"], dtype=torch.uint8, device=DEV)
+    ob = torch.zeros(((q["numel"] + 255) // 256) * 4, dtype=torch.float32, device=DEV)
+    for step, grad in enumerate(q["grads"][:2], start=1):
+        d_grad = dev(grad)
+        check(ref.ref_adam_qq_o4(C.c_int64(q["numel"]), step, C.c_float(lr["lr_features_sh"]), C.c_float(0.0), C.c_float(inp["grad_scale"]), 0, 16,
+                                 P(d_grad), P(op), P(ob), P(vp), P(vb)), "ref_adam_qq_o4")
+        out[f"qq16o4_s{step}_value_packed"], out[f"qq16o4_s{step}_value_bounds"] = vp.cpu().numpy(), vb.cpu().numpy()
+        out[f"qq16o4_s{step}_optim_packed"], out[f"qq16o4_s{step}_optim_bounds"] = op.cpu().numpy(), ob.cpu().numpy()
     np.savez_compressed(os.path.join(out_dir, "adam.npz"), **out)
 
 

@@ -211,3 +211,36 @@ def test_adam_extras_vs_reference(oracle):
     do = np.abs(op.astype(np.int64) - gold["qqs_optim_packed"].astype(np.int64))
     assert dv.max() <= 1 and do.max() <= 1 and (dv > 0).mean() <= 5e-2 and (do > 0).mean() <= 5e-2
     assert np.allclose(vb, gold["qqs_value_bounds"], rtol=1e-4, atol=1e-7) and np.allclose(ob, gold["qqs_optim_bounds"], rtol=2e-3, atol=1e-5)
+
+
+def _nibble_diff(a, b):
+    a, b = a.astype(np.int64), b.astype(np.int64)
+    return np.maximum(np.abs((a & 15) - (b & 15)), np.abs((a >> 4) - (b >> 4)))
+
+
+def test_adam_4bit_state_vs_reference(oracle):
+    """QuantizedAdamState<4,256>: fp32 values over three steps, 16-bit values over two, each step from the reference's state."""
+    gold = load("adam")
+    inp = adam_inputs()
+    lr, gs = inp["lrs"], inp["grad_scale"]
+    q = inp["q8"]
+    x, op, ob = q["x0"].copy(), np.zeros(q["numel"], np.uint8), np.zeros(((q["numel"] + 255) // 256) * 4, np.float32)
+    for step, grad in enumerate(q["grads"], start=1):
+        oracle.adam_qq(grad.copy(), op, ob, x.view(np.uint8), np.zeros(2, np.float32), 32, step, lr["lr_features_sh"], grad_scale=gs, optim_bits=4)
+        rx, ro, rob = (gold[f"q4_s{step}_{s}"] for s in ("x", "optim_packed", "optim_bounds"))
+        do = _nibble_diff(op, ro)
+        assert do.max() <= 1 and (do > 0).mean() <= 5e-2, step
+        assert np.allclose(ob, rob, rtol=2e-3, atol=1e-5)
+        assert frac_bad(x, rx, 5e-6, 1e-4) <= 1e-3, step
+        x, op, ob = rx.copy(), ro.copy(), rob.copy()
+    q = inp["qq16"]
+    vp, vb = q["value_packed"].copy(), q["value_bounds"].copy()
+    op, ob = np.zeros(q["numel"], np.uint8), np.zeros(((q["numel"] + 255) // 256) * 4, np.float32)
+    for step, grad in enumerate(q["grads"][:2], start=1):
+        oracle.adam_qq(grad.copy(), op, ob, vp, vb, 16, step, lr["lr_features_sh"], grad_scale=gs, optim_bits=4)
+        rv, rb, ro, rob = (gold[f"qq16o4_s{step}_{s}"] for s in ("value_packed", "value_bounds", "optim_packed", "optim_bounds"))
+        dv = np.abs(vp.view(np.uint16).astype(np.int64) - rv.view(np.uint16).astype(np.int64))
+        do = _nibble_diff(op, ro)
+        assert dv.max() <= 1 and do.max() <= 1 and (dv > 0).mean() <= 5e-2 and (do > 0).mean() <= 5e-2, step
+        assert np.allclose(vb, rb, rtol=1e-4, atol=1e-7) and np.allclose(ob, rob, rtol=2e-3, atol=1e-5)
+        vp, vb, op, ob = rv.copy(), rb.copy(), ro.copy(), rob.copy()

@@ -232,10 +232,52 @@ def test_adam_extras_vs_reference(lib, U):
     vp, vb, op, ob = (U.dev(q[k]) for k in ("value_packed", "value_bounds", "optim_packed", "optim_bounds"))
     d_g = U.dev(q["grads"][0])
     cfg = L.SsbAdamConfig(0, 0, 0, 0, 0, lr["lr_features_sh"], 0.0, gs, 1, 0)
-    L.check(lib.ssb_adam_step_sh_quantized_steps(L.ptr(d_g), L.ptr(op), L.ptr(ob), L.ptr(vp), L.ptr(vb), 16, 0, q["numel"], q["numel"],
-                                                 C.byref(cfg), L.ptr(steps_q), 45, None))
+    L.check(lib.ssb_adam_step_sh_quantized_ex(L.ptr(d_g), L.ptr(op), L.ptr(ob), L.ptr(vp), L.ptr(vb), 16, 8, 0, q["numel"], q["numel"],
+                                              C.byref(cfg), L.ptr(steps_q), 45, None))
     torch.cuda.synchronize()
     dv = np.abs(vp.cpu().numpy().view(np.uint16).astype(np.int64) - gold["qqs_value_packed"].view(np.uint16).astype(np.int64))
     do = np.abs(op.cpu().numpy().astype(np.int64) - gold["qqs_optim_packed"].astype(np.int64))
     assert dv.max() <= 1 and do.max() <= 1 and (dv > 0).mean() <= 5e-2 and (do > 0).mean() <= 5e-2
     assert np.allclose(vb.cpu().numpy(), gold["qqs_value_bounds"], rtol=1e-4, atol=1e-7)
+
+
+@pytest.mark.gpu
+def test_adam_4bit_state_vs_reference(lib, U):
+    """ssb_adam_step_sh_quantized_ex with optim_bits = 4 against the reference's kernels, each step from the reference's state."""
+    gold = load("adam")
+    inp = adam_inputs()
+    lr, gs = inp["lrs"], inp["grad_scale"]
+
+    def nibble_diff(a, b):
+        a, b = a.astype(np.int64), b.astype(np.int64)
+        return np.maximum(np.abs((a & 15) - (b & 15)), np.abs((a >> 4) - (b >> 4)))
+
+    q = inp["q8"]
+    state = [q["x0"], np.zeros(q["numel"], np.uint8), np.zeros(((q["numel"] + 255) // 256) * 4, np.float32)]
+    for step, grad in enumerate(q["grads"], start=1):
+        x, op, ob = (U.dev(a) for a in state)
+        d_g = U.dev(grad)
+        cfg = L.SsbAdamConfig(0, 0, 0, 0, 0, lr["lr_features_sh"], 0.0, gs, step, 0)
+        L.check(lib.ssb_adam_step_sh_quantized_ex(L.ptr(d_g), L.ptr(op), L.ptr(ob), L.ptr(x), None, 32, 4, 0, q["numel"], q["numel"], C.byref(cfg),
+                                                  None, 1, None))
+        torch.cuda.synchronize()
+        rx, ro, rob = (gold[f"q4_s{step}_{s}"] for s in ("x", "optim_packed", "optim_bounds"))
+        do = nibble_diff(op.cpu().numpy(), ro)
+        assert do.max() <= 1 and (do > 0).mean() <= 5e-2, step
+        assert U.close_frac(x.cpu().numpy(), rx, 5e-6, 1e-4) <= 1e-3, step
+        state = [rx, ro, rob]
+    q = inp["qq16"]
+    state = [q["value_packed"], q["value_bounds"], np.zeros(q["numel"], np.uint8), np.zeros(((q["numel"] + 255) // 256) * 4, np.float32)]
+    for step, grad in enumerate(q["grads"][:2], start=1):
+        vp, vb, op, ob = (U.dev(a) for a in state)
+        d_g = U.dev(grad)
+        cfg = L.SsbAdamConfig(0, 0, 0, 0, 0, lr["lr_features_sh"], 0.0, gs, step, 0)
+        L.check(lib.ssb_adam_step_sh_quantized_ex(L.ptr(d_g), L.ptr(op), L.ptr(ob), L.ptr(vp), L.ptr(vb), 16, 4, 0, q["numel"], q["numel"],
+                                                  C.byref(cfg), None, 1, None))
+        torch.cuda.synchronize()
+        rv, rb, ro, rob = (gold[f"qq16o4_s{step}_{s}"] for s in ("value_packed", "value_bounds", "optim_packed", "optim_bounds"))
+        dv = np.abs(vp.cpu().numpy().view(np.uint16).astype(np.int64) - rv.view(np.uint16).astype(np.int64))
+        do = nibble_diff(op.cpu().numpy(), ro)
+        assert dv.max() <= 1 and do.max() <= 1 and (dv > 0).mean() <= 5e-2 and (do > 0).mean() <= 5e-2, step
+        assert np.allclose(vb.cpu().numpy(), rb, rtol=1e-4, atol=1e-7)
+        state = [rv, rb, ro, rob]

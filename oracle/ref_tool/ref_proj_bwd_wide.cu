@@ -1,7 +1,7 @@
 // TEST INFRASTRUCTURE.  The reference's projection backward kernel
 // (src/kernels/projection/ProjectionBwd_kernel.cuh:16-179) for Vanilla3DGS<3>
-// with the equidistant fisheye and the equirectangular camera models, no
-// distortion, launched on raw device buffers.  model: 1 = fisheye, 3 = equirectangular.
+// with the equidistant fisheye, the equisolid fisheye and the equirectangular camera models, no
+// distortion, launched on raw device buffers.  model: 1 = fisheye, 2 = equisolid, 3 = equirectangular.
 #define NO_TORCH
 #include "primitives/Primitive3DGS.cuh"
 #include "kernels/projection/ProjectionBwd_kernel.cuh"
@@ -29,6 +29,8 @@ extern "C" int ref_project_bwd_model(
     RawScreen v_screen((int64_t)C * N, v_xy, v_depth, v_conic, v_opac, v_rgb);
     if (model == 1)
         run_bwd<CameraModelType::FISHEYE>(C, N, W, H, world, viewmats, intrins, aabb, v_screen, grads, sh_packed, sh_bounds, sh_bits, sh_stride);
+    else if (model == 2)
+        run_bwd<CameraModelType::EQUISOLID>(C, N, W, H, world, viewmats, intrins, aabb, v_screen, grads, sh_packed, sh_bounds, sh_bits, sh_stride);
     else if (model == 3)
         run_bwd<CameraModelType::EQUIRECTANGULAR>(C, N, W, H, world, viewmats, intrins, aabb, v_screen, grads, sh_packed, sh_bounds, sh_bits, sh_stride);
     else

@@ -1,7 +1,7 @@
 // TEST INFRASTRUCTURE.  The reference's projection forward kernel
 // (src/kernels/projection/ProjectionFwd_kernel.cuh:15-153) for Vanilla3DGS<3>
-// with the equidistant fisheye and the equirectangular camera models, no
-// distortion, launched on raw device buffers.  model: 1 = fisheye, 3 = equirectangular
+// with the equidistant fisheye, the equisolid fisheye and the equirectangular camera models, no
+// distortion, launched on raw device buffers.  model: 1 = fisheye, 2 = equisolid, 3 = equirectangular
 // (src/core/Common.cuh:94-99).
 #define NO_TORCH
 #include "primitives/Primitive3DGS.cuh"
@@ -28,6 +28,8 @@ extern "C" int ref_project_fwd_model(
     RawScreen screen((int64_t)C * N, xy, depth, conic, opac, rgb);
     if (model == 1)
         run_fwd<CameraModelType::FISHEYE>(C, N, W, H, world, viewmats, intrins, aabb, depths, radii, screen, sh_packed, sh_bounds, sh_bits, sh_stride);
+    else if (model == 2)
+        run_fwd<CameraModelType::EQUISOLID>(C, N, W, H, world, viewmats, intrins, aabb, depths, radii, screen, sh_packed, sh_bounds, sh_bits, sh_stride);
     else if (model == 3)
         run_fwd<CameraModelType::EQUIRECTANGULAR>(C, N, W, H, world, viewmats, intrins, aabb, depths, radii, screen, sh_packed, sh_bounds, sh_bits, sh_stride);
     else

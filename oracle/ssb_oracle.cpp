@@ -189,6 +189,26 @@ inline void project_mean(int model, const S p[3], float fx, float fy, float cx, 
             J[0] = fx * (k + p[0] * dkx); J[1] = fx * (p[0] * dky); J[2] = fx * (p[0] * dkz);
             J[3] = fy * (p[1] * dkx); J[4] = fy * (k + p[1] * dky); J[5] = fy * (p[1] * dkz);
         }
+    } else if (model == EQUISOLID) {
+        // k = 2 sin(theta / 2) / r with theta = atan2(r, z) (src/shaders/projection_utils.slang:388-395; Jacobian by
+        // forward-mode autodiff, :480-493).  With rho = |p|: sin(theta/2) = r / (2 rho cos(theta/2)) and
+        // cos^2(theta/2) = (rho + z) / (2 rho), so k = sqrt(2 / (rho (rho + z))): the same function without the
+        // cancellation of cos(theta/2) dtheta/r - 2 sin(theta/2)/r^2, and it contains the reference's series
+        // (1 - theta^2/24)/z for r < 1e-6.  Behind the camera rho + z is taken as r^2 / (rho - z).
+        S r2 = p[0] * p[0] + p[1] * p[1];
+        S rho2 = r2 + p[2] * p[2];
+        S rho = d_sqrt(rho2);
+        S w = (val(p[2]) >= 0.f) ? (rho + p[2]) : (r2 / (rho - p[2]));
+        S q = rho * w;
+        S k = d_sqrt(2.0f / q);
+        S c = -(k / (2.0f * q * rho));
+        S dkx = c * (p[0] * (2.0f * rho + p[2]));
+        S dky = c * (p[1] * (2.0f * rho + p[2]));
+        S dkz = -(k * w / (2.0f * rho2));
+        uv[0] = fx * (p[0] * k) + cx;
+        uv[1] = fy * (p[1] * k) + cy;
+        J[0] = fx * (k + p[0] * dkx); J[1] = fx * (p[0] * dky); J[2] = fx * (p[0] * dkz);
+        J[3] = fy * (p[1] * dkx); J[4] = fy * (k + p[1] * dky); J[5] = fy * (p[1] * dkz);
     } else {  // EQUIRECT: lon = atan2(x, z), lat = atan2(y, hypot(x, z))
         S h2 = p[0] * p[0] + p[2] * p[2];
         S h = d_sqrt(h2);

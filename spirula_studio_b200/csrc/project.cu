@@ -87,7 +87,8 @@ __device__ __forceinline__ D3 lift(float a, const D3&) { return {a, 0.f, 0.f, 0.
 
 // Pixel position and 2x3 Jacobian d(uv)/d(p) of the equidistant fisheye
 // (src/shaders/projection_utils.slang:378-384,400-410: k = theta / r, with the
-// series (1 - theta^2/3)/z below theta = 1e-3) and of the equirectangular
+// series (1 - theta^2/3)/z below theta = 1e-3), of the equisolid fisheye (:388-395:
+// k = 2 sin(theta/2) / r, written algebraically below) and of the equirectangular
 // camera (:505-518: lon = atan2(x, z), lat = atan2(y, hypot(x, z))), as closed
 // forms of the derivatives the reference takes by forward-mode autodiff (:463-476, :537-548).
 template <int MODEL, class S>
@@ -114,6 +115,23 @@ __device__ __forceinline__ void project_mean_wide(const S p[3], float fx, float 
             dky = dty * ir - tir3 * p[1];
             dkz = dtz * ir;
         }
+        uv[0] = fx * (p[0] * k) + lift(cx, k);
+        uv[1] = fy * (p[1] * k) + lift(cy, k);
+        J[0] = fx * (k + p[0] * dkx); J[1] = fx * (p[0] * dky); J[2] = fx * (p[0] * dkz);
+        J[3] = fy * (p[1] * dkx); J[4] = fy * (k + p[1] * dky); J[5] = fy * (p[1] * dkz);
+    } else if (MODEL == SSB_CAMERA_EQUISOLID) {
+        // 2 sin(theta/2) / r = sqrt(2 / (rho (rho + z))), rho = |p|: one algebraic form for every r, free of
+        // the cancellation in the derivative of the trigonometric one; rho + z = r^2 / (rho - z) behind the camera
+        S r2 = p[0] * p[0] + p[1] * p[1];
+        S rho2 = r2 + p[2] * p[2];
+        S rho = sqrt_s(rho2);
+        S w = val(p[2]) >= 0.f ? rho + p[2] : r2 / (rho - p[2]);
+        S q = rho * w;
+        S k = sqrt_s(2.0f / q);
+        S c = -(k / (2.0f * q * rho));
+        S t = 2.0f * rho + p[2];
+        S dkx = c * (p[0] * t), dky = c * (p[1] * t);
+        S dkz = -(k * w / (2.0f * rho2));
         uv[0] = fx * (p[0] * k) + lift(cx, k);
         uv[1] = fy * (p[1] * k) + lift(cy, k);
         J[0] = fx * (k + p[0] * dkx); J[1] = fx * (p[0] * dky); J[2] = fx * (p[0] * dkz);
@@ -203,7 +221,7 @@ __device__ __forceinline__ bool project_geom(
         c00 = a0 * J[0] + a1 * J[1] + a2 * J[2];
         c01 = a0 * J[3] + a1 * J[4] + a2 * J[5];
         c11 = b0 * J[3] + b1 * J[4] + b2 * J[5];
-        if (!assume_valid && MODEL == SSB_CAMERA_FISHEYE) {
+        if (!assume_valid && (MODEL == SSB_CAMERA_FISHEYE || MODEL == SSB_CAMERA_EQUISOLID)) {
             // behind-the-camera splats that still reach the image centre are dropped
             // (src/shaders/primitive_3dgs.slang:515-521); c10 == c01 here
             float invd = 1.0f / (c00 * c11 - c01 * c01);
@@ -753,7 +771,7 @@ int ssb_project_fwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, c
     using namespace ssb;
     SSB_REQUIRE(splats && cams && d_aabb && d_depths && d_screen, "ssb_project_fwd: NULL argument");
     SSB_REQUIRE(n >= 0 && cams->count >= 0 && cams->width > 0 && cams->height > 0, "ssb_project_fwd: bad sizes");
-    if (cams->model != SSB_CAMERA_PINHOLE && cams->model != SSB_CAMERA_FISHEYE && cams->model != SSB_CAMERA_EQUIRECT) {
+    if (cams->model != SSB_CAMERA_PINHOLE && cams->model != SSB_CAMERA_FISHEYE && cams->model != SSB_CAMERA_EQUISOLID && cams->model != SSB_CAMERA_EQUIRECT) {
         set_error("ssb_project_fwd: camera model %d not supported", cams->model); return SSB_ERR_UNSUPPORTED;
     }
     SSB_REQUIRE((int64_t)cams->count * n < ((int64_t)1 << 31), "ssb_project_fwd: views * splats must fit int32 flatten ids");
@@ -767,6 +785,7 @@ int ssb_project_fwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, c
         (float4*)d_aabb, d_depths, d_radii, d_screen)
     if (cams->model == SSB_CAMERA_PINHOLE) SSB_FWD(SSB_CAMERA_PINHOLE);
     else if (cams->model == SSB_CAMERA_FISHEYE) SSB_FWD(SSB_CAMERA_FISHEYE);
+    else if (cams->model == SSB_CAMERA_EQUISOLID) SSB_FWD(SSB_CAMERA_EQUISOLID);
     else SSB_FWD(SSB_CAMERA_EQUIRECT);
 #undef SSB_FWD
     SSB_LAUNCHED("project_fwd_kernel");
@@ -787,7 +806,7 @@ int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n
     SSB_REQUIRE(splats && cams && d_aabb && d_v_screen && grads, "ssb_project_bwd: NULL argument");
     SSB_REQUIRE(grads->means && grads->quats && grads->scales && grads->opacities && grads->features_dc && grads->features_sh,
                 "ssb_project_bwd: every gradient array must be given");
-    if (cams->model != SSB_CAMERA_PINHOLE && cams->model != SSB_CAMERA_FISHEYE && cams->model != SSB_CAMERA_EQUIRECT) {
+    if (cams->model != SSB_CAMERA_PINHOLE && cams->model != SSB_CAMERA_FISHEYE && cams->model != SSB_CAMERA_EQUISOLID && cams->model != SSB_CAMERA_EQUIRECT) {
         set_error("ssb_project_bwd: camera model %d not supported", cams->model); return SSB_ERR_UNSUPPORTED;
     }
     SsbShQuant q;
@@ -800,6 +819,7 @@ int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n
     const bool multi = cams->count != 1;
     if (cams->model == SSB_CAMERA_PINHOLE) { if (multi) SSB_BWD(true, SSB_CAMERA_PINHOLE); else SSB_BWD(false, SSB_CAMERA_PINHOLE); }
     else if (cams->model == SSB_CAMERA_FISHEYE) { if (multi) SSB_BWD(true, SSB_CAMERA_FISHEYE); else SSB_BWD(false, SSB_CAMERA_FISHEYE); }
+    else if (cams->model == SSB_CAMERA_EQUISOLID) { if (multi) SSB_BWD(true, SSB_CAMERA_EQUISOLID); else SSB_BWD(false, SSB_CAMERA_EQUISOLID); }
     else { if (multi) SSB_BWD(true, SSB_CAMERA_EQUIRECT); else SSB_BWD(false, SSB_CAMERA_EQUIRECT); }
 #undef SSB_BWD
     SSB_LAUNCHED("project_bwd_kernel");

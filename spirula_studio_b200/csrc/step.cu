@@ -168,7 +168,7 @@ int ssb_step_create(const SsbStepConfig* cfg, SsbStep** out) {
     SSB_REQUIRE(cfg && out, "ssb_step_create: NULL argument");
     SSB_REQUIRE(cfg->n_splats > 0 && cfg->width > 0 && cfg->height > 0, "ssb_step_create: bad sizes");
     SSB_REQUIRE(cfg->n_splats < ((int64_t)1 << 31), "ssb_step_create: splat count must fit int32");
-    if (cfg->camera_model != SSB_CAMERA_PINHOLE && cfg->camera_model != SSB_CAMERA_FISHEYE && cfg->camera_model != SSB_CAMERA_EQUIRECT) {
+    if (cfg->camera_model < SSB_CAMERA_PINHOLE || cfg->camera_model > SSB_CAMERA_EQUIRECT) {
         set_error("ssb_step_create: camera model %d not supported", cfg->camera_model); return SSB_ERR_UNSUPPORTED;
     }
     SsbStep* s = new (std::nothrow) SsbStep();

@@ -22,10 +22,13 @@ CASES = {
 
 
 # wide field-of-view cameras: the same splat cloud seen by one equidistant fisheye camera
-# (model 1, about 190 degrees across the image) and one equirectangular camera (model 3),
-# both near the middle of the cloud so splats lie in every direction, behind the camera included
+# (model 1, about 190 degrees across the image), one equisolid fisheye camera (model 2, r = 2 f sin(theta/2):
+# about 167 degrees across the image, the direction straight behind the camera maps outside it) and one
+# equirectangular camera (model 3),
+# all near the middle of the cloud so splats lie in every direction, behind the camera included
 WIDE_CASES = {
     "wide_fisheye": dict(seed=404, n=1500, model=1, w=96, h=96, f=29.0, scale_mu=-2.4, extent=3.0),
+    "wide_equisolid": dict(seed=404, n=1500, model=2, w=96, h=96, f=36.0, scale_mu=-2.4, extent=3.0),
     "wide_equirect": dict(seed=404, n=1500, model=3, w=128, h=64, f=128 / (2 * np.pi), scale_mu=-2.4, extent=3.0),
 }
 

@@ -48,7 +48,7 @@ def test_argument_errors_are_statuses_not_crashes():
     assert lib.ssb_sort_pairs_u64(one, one, one, one, one, 10, 40, 30, one, 1 << 30, C.byref(sel), None) == L.SSB_ERR_INVALID_ARGUMENT
     assert lib.ssb_quant_encode(one, 10, 12, one, one, None) == L.SSB_ERR_INVALID_ARGUMENT
     cams = L.SsbCameras()
-    cams.count, cams.width, cams.height, cams.model = 1, 64, 64, L.CAMERA_EQUISOLID    # the one model not built
+    cams.count, cams.width, cams.height, cams.model = 1, 64, 64, 7    # not a camera model
     sp = L.SsbSplats()
     sp.features_sh = 8
     assert lib.ssb_project_fwd(C.byref(sp), None, 0, C.byref(cams), one, one, None, one, None) == L.SSB_ERR_UNSUPPORTED

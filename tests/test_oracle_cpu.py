@@ -107,8 +107,8 @@ def test_projection_backward_matches_finite_differences(oracle, attr):
 
 
 def wide_scene(model, n=96, seed=11):
-    """Camera inside the cloud: an equidistant fisheye (model 1) or an equirectangular one (model 3)."""
-    W, H, f = (120, 120, 36.0) if model == 1 else (160, 80, 160 / (2 * np.pi))
+    """Camera inside the cloud: an equidistant (model 1) or equisolid (model 2) fisheye, or an equirectangular one (model 3)."""
+    W, H, f = (120, 120, 36.0 if model == 1 else 40.0) if model in (1, 2) else (160, 80, 160 / (2 * np.pi))
     cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=n, width=W, height=H)
     cfg.log_scale_mu, cfg.mean_extent = -2.2, 2.5
     sp = scenes.make_splats(cfg, seed=seed)
@@ -117,10 +117,10 @@ def wide_scene(model, n=96, seed=11):
     return cfg, sp, vm, K
 
 
-@pytest.mark.parametrize("model", [1, 3])
+@pytest.mark.parametrize("model", [1, 2, 3])
 @pytest.mark.parametrize("attr", ["means", "quats", "scales", "opacities"])
 def test_wide_projection_backward_matches_finite_differences(oracle, model, attr):
-    """Fisheye and equirectangular cameras: the vjp against central differences of the forward pass."""
+    """Fisheye, equisolid and equirectangular cameras: the vjp against central differences of the forward pass."""
     cfg, sp, vm, K = wide_scene(model)
     W, H, n = cfg.width, cfg.height, cfg.n_splats
     rng = np.random.default_rng(6)
@@ -146,8 +146,8 @@ def test_wide_projection_backward_matches_finite_differences(oracle, model, attr
 
 
 def test_wide_sorting_depth(oracle):
-    """Sorting depth: squared distance (equirectangular), z^4 + (x^2+y^2)^2/512 (fisheye)."""
-    for model in (1, 3):
+    """Sorting depth: squared distance (equirectangular), z^4 + (x^2+y^2)^2/512 (both fisheyes)."""
+    for model in (1, 2, 3):
         cfg, sp, vm, K = wide_scene(model)
         o = oracle.project_fwd(sp, vm, K, cfg.width, cfg.height, model=model)
         keep = o["aabb"][:, 2] > o["aabb"][:, 0]

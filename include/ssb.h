@@ -260,6 +260,25 @@ int ssb_raster_bwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, 
                    const float* d_v_rgb, const float* d_v_depth, const float* d_v_T,
                    SsbScreenRec* d_v_screen, void* stream);
 
+/* DensifyAccumMode of the reference (src/primitives/Primitive.cuh:37-39). */
+enum { SSB_ACCUM_NONE = 0, SSB_ACCUM_MAX = 1, SSB_ACCUM_SUM = 2, SSB_ACCUM_AVG = 3 };
+
+/* ssb_raster_bwd that also accumulates the per-splat densification weight
+ * (accum_weight_map_buffer / o_accum_weight / o_accum_weight_den of rasterize_to_pixels_bwd_kernel,
+ * src/kernels/raster/RasterizationEval3DBwd_kernel.cuh:91-101,541-550,566-579): over every fragment
+ * that receives a gradient, the maximum (MAX) or the sum (SUM, AVG) of
+ * d_weight_map[pixel] * alpha * T, and for AVG also the sum of alpha * T into d_accum_weight_den.
+ * d_weight_map is [n_images][height][width] (NULL = all zero).  The results are combined into
+ * d_accum_weight[splat] (atomic max / add; the caller zeroes it), where splat = d_gaussian_ids[record]
+ * (packed projection) or record index % n_per_image when d_gaussian_ids is NULL.
+ * accum_mode = SSB_ACCUM_NONE is ssb_raster_bwd. */
+int ssb_raster_bwd_accum(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids,
+                         const int64_t* d_n_isects, int32_t n_images, int32_t width, int32_t height,
+                         const float* d_render_depth, const float* d_T, const int32_t* d_last_ids,
+                         const float* d_v_rgb, const float* d_v_depth, const float* d_v_T, SsbScreenRec* d_v_screen,
+                         int32_t accum_mode, const float* d_weight_map, int64_t n_per_image, const int32_t* d_gaussian_ids,
+                         float* d_accum_weight, float* d_accum_weight_den, void* stream);
+
 /* ---- loss --------------------------------------------------------------- */
 
 /* Replaces compute_multi_scale_per_pixel_losses at one scale with only the RGB

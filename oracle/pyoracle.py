@@ -153,6 +153,15 @@ def raster_bwd(proj, offsets, flatten_ids, I, N, W, H, render, v_rgb, v_depth=No
     return g
 
 
+def raster_accum_weight(proj, offsets, flatten_ids, I, N, W, H, render, weight_map, mode):
+    """Per-splat densification weight of the backward walk: mode 1 max, 2 sum, 3 average (returns sum and denominator)."""
+    acc, den = np.zeros(N, np.float32), np.zeros(N, np.float32)
+    load().oracle_raster_accum_weight(C.c_int(I), C.c_int64(N), C.c_int(W), C.c_int(H), C.c_int64(flatten_ids.shape[0]), C.c_int(mode),
+                                      _p(proj["xy"]), _p(proj["conic"]), _p(proj["opac"]), _p(offsets), _p(flatten_ids),
+                                      _p(render["T"]), _p(render["last_ids"]), _p(_f(weight_map)), _p(acc), _p(den))
+    return acc, den
+
+
 def loss_l1_ssim(render, gt, B, H, W, w_l1=0.8, w_ssim=0.2):
     lib = load()
     v = np.zeros((B * H * W, 3), np.float32)

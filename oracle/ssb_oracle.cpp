@@ -860,6 +860,51 @@ void oracle_raster_fwd(
         }
 }
 
+// Per-splat densification weight of the raster backward pass (accum_weight_map_buffer -> o_accum_weight,
+// src/kernels/raster/RasterizationEval3DBwd_kernel.cuh:541-550,566-579): over every fragment the backward walk
+// visits (same skips as oracle_raster_bwd), w = alpha * T0; mode 1: max of map[pixel] * w, mode 2: their sum,
+// mode 3: the sum and, in accum_den, the sum of w.  The per-micro-tile partial results the kernel combines with
+// atomicMax / atomicAdd are a max / sum over all fragments.  splat = flatten id % N.  Sums in double.
+void oracle_raster_accum_weight(
+    int I, int64_t N, int W, int H, int64_t n_isects, int mode,
+    const float* xy, const float* conic, const float* opac,
+    const int32_t* tile_offsets, const int32_t* flatten_ids, const float* render_T, const int32_t* last_ids,
+    const float* weight_map, float* accum, float* accum_den) {
+    int tw = (W + TILE - 1) / TILE, th = (H + TILE - 1) / TILE;
+    std::vector<double> acc((size_t)N, 0.0), den((size_t)N, 0.0);
+    for (int img = 0; img < I; ++img)
+        for (int i = 0; i < H; ++i)
+            for (int j = 0; j < W; ++j) {
+                int tile_id = (i / TILE) * tw + j / TILE;
+                int mt_y = i / MICRO, mt_x = j / MICRO;
+                const int32_t* offs = tile_offsets + (int64_t)img * tw * th;
+                int32_t range_start = offs[tile_id];
+                int32_t range_end = (img == I - 1 && tile_id == tw * th - 1) ? (int32_t)n_isects : offs[tile_id + 1];
+                int64_t pix = ((int64_t)img * H + i) * W + j;
+                float px = (float)j + 0.5f, py = (float)i + 0.5f;
+                float T1 = render_T[pix];
+                float wm = weight_map ? weight_map[pix] : 0.f;
+                for (int32_t k = std::min(range_end - 1, last_ids[pix]); k >= range_start; --k) {
+                    int32_t g = flatten_ids[k];
+                    if (!microtile_hit(xy + 2 * g, conic + 3 * g, opac[g], mt_x, mt_y)) continue;
+                    float vis, sigma;
+                    float alpha = evaluate_alpha(xy + 2 * g, conic + 3 * g, opac[g], px, py, &vis, &sigma);
+                    if (alpha <= ALPHA_THRESHOLD) continue;
+                    float T0 = T1 * (1.0f / (1.0f - alpha));
+                    float w = alpha * T0;
+                    int64_t wid = (int64_t)g % N;
+                    if (mode == 1) acc[wid] = std::max(acc[wid], (double)(wm * w));
+                    else acc[wid] += (double)wm * (double)w;
+                    den[wid] += (double)w;
+                    T1 = T0;
+                }
+            }
+    for (int64_t n = 0; n < N; ++n) {
+        accum[n] = (float)acc[n];
+        if (mode == 3 && accum_den) accum_den[n] = (float)den[n];
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Rasterize backward: rasterize_to_pixels_bwd_kernel
 // (src/kernels/raster/RasterizationEval3DBwd_kernel.cuh:48-636, 2D variant) with

@@ -162,13 +162,25 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
 constexpr int kBwdWarps = 4;          // one 16x16 tile per CTA, one 8x8 micro-tile per warp
 constexpr int kSurvCap = 256;         // survivors collected per segment (8 per lane)
 
-template <bool DEPTH>
-__global__ void __launch_bounds__(kBwdWarps * 32, 10) raster_bwd_kernel(
+// What the per-splat densification weight accumulates (DensifyAccumMode, src/primitives/Primitive.cuh:37-39).
+struct BwdAccum {
+    const float* weight_map;      // [I][H][W] per-pixel weight, or null (all zero)
+    const int32_t* gaussian_ids;  // record index -> splat id (packed projection), or null: record index % n_per_image
+    int64_t n_per_image;
+    float* out;                   // [N]
+    float* out_den;               // [N], average mode only
+};
+
+// ACCUM: 0 none, 1 max, 2 sum, 3 average (sum and denominator) of weight_map[pixel] * alpha * T over the
+// fragments a splat contributes (RasterizationEval3DBwd_kernel.cuh:541-550,566-579).
+template <bool DEPTH, int ACCUM>
+__global__ void __launch_bounds__(kBwdWarps * 32, ACCUM ? 8 : 10) raster_bwd_kernel(
     const SsbScreenRec* __restrict__ screen, const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ flatten_ids,
     const int64_t* __restrict__ n_isects_ptr, int I, int W, int H, int tw, int th,
     const float* __restrict__ render_depth, const float* __restrict__ render_T, const int32_t* __restrict__ last_ids,
     const float* __restrict__ v_rgb, const float* __restrict__ v_depth, const float* __restrict__ v_T,
-    SsbScreenRec* __restrict__ v_screen) {
+    SsbScreenRec* __restrict__ v_screen, BwdAccum acc) {
+    __shared__ float sW[ACCUM ? kBwdWarps : 1][64];   // weight map of the micro-tile
     __shared__ float4 sP[kBwdWarps][64];       // running T, dL/dT, pixel centre x, y
     __shared__ float4 sV[kBwdWarps][64];       // dL/d(rgb), dL/d(depth sum)
     __shared__ int32_t sLast[kBwdWarps][64];
@@ -207,6 +219,7 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 10) raster_bwd_kernel(
                 vc.w *= inv_alpha;
             }
         }
+        if (ACCUM) sW[w][p] = (inside && acc.weight_map) ? acc.weight_map[((int64_t)img * H + y) * W + x] : 0.f;
         sP[w][p] = make_float4(T1, vT1, (float)x + 0.5f, (float)y + 0.5f);
         sV[w][p] = vc;
         sLast[w][p] = last;
@@ -259,6 +272,7 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 10) raster_bwd_kernel(
             const float A2 = 0.5f * kLog2e * b.x, B2 = kLog2e * b.y, C2 = 0.5f * kLog2e * b.z, op = b.w;
             // sums over this micro-tile's pixels: v_sigma * {dx^2, dx dy, dy^2, dx, dy}, vis * v_alpha, weights * v_colour
             float s_xx = 0.f, s_xy = 0.f, s_yy = 0.f, s_x = 0.f, s_y = 0.f, gop = 0.f, gr = 0.f, gg = 0.f, gb = 0.f, gd = 0.f;
+            float aw = 0.f, aw_den = 0.f;
             const int steps = bs + 63;
             for (int t = 0; t < steps; ++t) {
                 const unsigned p = (unsigned)(t - lane);
@@ -289,6 +303,9 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 10) raster_bwd_kernel(
                         gop += va;
                         gr = fmaf(vc.x, wgt, gr); gg = fmaf(vc.y, wgt, gg); gb = fmaf(vc.z, wgt, gb);
                         if (DEPTH) gd = fmaf(vc.w, wgt, gd);
+                        if (ACCUM == 1) aw = fmaxf(aw, sW[w][p] * wgt);
+                        if (ACCUM >= 2) aw = fmaf(sW[w][p], wgt, aw);
+                        if (ACCUM == 3) aw_den += wgt;
                         *(float2*)&sP[w][p] = make_float2(T0, v_T0);
                     }
                 }
@@ -304,10 +321,38 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 10) raster_bwd_kernel(
                 if (gx != 0.f || gy != 0.f) red_add_v4(out, fz(gx), fz(gy), 0.f, 0.f);
                 if (gca != 0.f || gcb != 0.f || gcc != 0.f || gop != 0.f) red_add_v4(out + 4, fz(gca), fz(gcb), fz(gcc), fz(gop));
                 if (gr != 0.f || gg != 0.f || gb != 0.f || gd != 0.f) red_add_v4(out + 8, fz(gr), fz(gg), fz(gb), fz(gd));
+                if (ACCUM) {
+                    const int64_t wid = acc.gaussian_ids ? (int64_t)acc.gaussian_ids[g] : (int64_t)g % acc.n_per_image;
+                    // weights are products of non-negative factors, so their bit patterns order like integers
+                    if (ACCUM == 1) { if (aw > 0.f) atomicMax((int*)acc.out + wid, __float_as_int(aw)); }
+                    else if (aw != 0.f) atomicAdd(acc.out + wid, aw);
+                    if (ACCUM == 3 && aw_den != 0.f) atomicAdd(acc.out_den + wid, aw_den);
+                }
             }
         }
         __syncwarp();
     }
+}
+
+static int launch_raster_bwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids, const int64_t* d_n_isects,
+                             int32_t n_images, int32_t width, int32_t height, const float* d_render_depth, const float* d_T,
+                             const int32_t* d_last_ids, const float* d_v_rgb, const float* d_v_depth, const float* d_v_T,
+                             SsbScreenRec* d_v_screen, int accum_mode, BwdAccum acc, void* stream) {
+    const int tw = (width + kTile - 1) / kTile, th = (height + kTile - 1) / kTile;
+    const dim3 grid(tw, th, n_images);
+#define SSB_RBWD(DEPTH, ACCUM) \
+    raster_bwd_kernel<DEPTH, ACCUM><<<grid, kBwdWarps * 32, 0, (cudaStream_t)stream>>>( \
+        d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height, tw, th, d_render_depth, d_T, d_last_ids, d_v_rgb, \
+        DEPTH ? d_v_depth : nullptr, d_v_T, d_v_screen, acc)
+    // without a depth cotangent the depth channel carries exact zeros: that arithmetic is compiled out
+    if (d_v_depth) {
+        if (accum_mode == 0) SSB_RBWD(true, 0); else if (accum_mode == 1) SSB_RBWD(true, 1); else if (accum_mode == 2) SSB_RBWD(true, 2); else SSB_RBWD(true, 3);
+    } else {
+        if (accum_mode == 0) SSB_RBWD(false, 0); else if (accum_mode == 1) SSB_RBWD(false, 1); else if (accum_mode == 2) SSB_RBWD(false, 2); else SSB_RBWD(false, 3);
+    }
+#undef SSB_RBWD
+    SSB_LAUNCHED("raster_bwd_kernel");
+    return SSB_OK;
 }
 
 }  // namespace ssb
@@ -343,17 +388,31 @@ int ssb_raster_bwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, 
                 "ssb_raster_bwd: NULL argument");
     SSB_REQUIRE(n_images >= 0 && width > 0 && height > 0, "ssb_raster_bwd: bad sizes");
     if (n_images == 0) return SSB_OK;
-    int tw = (width + kTile - 1) / kTile, th = (height + kTile - 1) / kTile;
-    dim3 grid(tw, th, n_images);
-    // without a depth cotangent the depth channel carries exact zeros: that arithmetic is compiled out
-    if (d_v_depth)
-        raster_bwd_kernel<true><<<grid, kBwdWarps * 32, 0, (cudaStream_t)stream>>>(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height,
-                                                                                 tw, th, d_render_depth, d_T, d_last_ids, d_v_rgb, d_v_depth, d_v_T, d_v_screen);
-    else
-        raster_bwd_kernel<false><<<grid, kBwdWarps * 32, 0, (cudaStream_t)stream>>>(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height,
-                                                                                  tw, th, d_render_depth, d_T, d_last_ids, d_v_rgb, nullptr, d_v_T, d_v_screen);
-    SSB_LAUNCHED("raster_bwd_kernel");
-    return SSB_OK;
+    return launch_raster_bwd(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height, d_render_depth, d_T, d_last_ids,
+                             d_v_rgb, d_v_depth, d_v_T, d_v_screen, 0, BwdAccum{nullptr, nullptr, 1, nullptr, nullptr}, stream);
+}
+
+int ssb_raster_bwd_accum(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids,
+                         const int64_t* d_n_isects, int32_t n_images, int32_t width, int32_t height,
+                         const float* d_render_depth, const float* d_T, const int32_t* d_last_ids,
+                         const float* d_v_rgb, const float* d_v_depth, const float* d_v_T, SsbScreenRec* d_v_screen,
+                         int32_t accum_mode, const float* d_weight_map, int64_t n_per_image, const int32_t* d_gaussian_ids,
+                         float* d_accum_weight, float* d_accum_weight_den, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(d_screen && d_tile_offsets && d_flatten_ids && d_n_isects && d_T && d_last_ids && d_v_rgb && d_v_screen,
+                "ssb_raster_bwd_accum: NULL argument");
+    SSB_REQUIRE(n_images >= 0 && width > 0 && height > 0, "ssb_raster_bwd_accum: bad sizes");
+    SSB_REQUIRE(!d_v_depth || d_render_depth, "ssb_raster_bwd_accum: a depth cotangent needs the rendered depth");
+    SSB_REQUIRE(accum_mode >= SSB_ACCUM_NONE && accum_mode <= SSB_ACCUM_AVG, "ssb_raster_bwd_accum: accum_mode %d is not a DensifyAccumMode", accum_mode);
+    if (accum_mode != SSB_ACCUM_NONE) {
+        SSB_REQUIRE(d_accum_weight, "ssb_raster_bwd_accum: d_accum_weight is NULL");
+        SSB_REQUIRE(accum_mode != SSB_ACCUM_AVG || d_accum_weight_den, "ssb_raster_bwd_accum: the average mode needs d_accum_weight_den");
+        SSB_REQUIRE(d_gaussian_ids || n_per_image > 0, "ssb_raster_bwd_accum: n_per_image must be positive without d_gaussian_ids");
+    }
+    if (n_images == 0) return SSB_OK;
+    return launch_raster_bwd(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height, d_render_depth, d_T, d_last_ids,
+                             d_v_rgb, d_v_depth, d_v_T, d_v_screen, accum_mode,
+                             BwdAccum{d_weight_map, d_gaussian_ids, n_per_image > 0 ? n_per_image : 1, d_accum_weight, d_accum_weight_den}, stream);
 }
 
 }  // extern "C"

@@ -18,6 +18,7 @@ SSB_ERR_OUT_OF_MEMORY = -4
 SSB_ERR_UNSUPPORTED = -5
 
 CAMERA_PINHOLE, CAMERA_FISHEYE, CAMERA_EQUISOLID, CAMERA_EQUIRECT = 0, 1, 2, 3
+SSB_ACCUM_NONE, SSB_ACCUM_MAX, SSB_ACCUM_SUM, SSB_ACCUM_AVG = 0, 1, 2, 3
 NUM_SH = 15
 TILE = 16
 SCREEN_REC_FLOATS = 12
@@ -97,6 +98,7 @@ SIGNATURES = {
     "ssb_tile_ranges": (C.c_int, [_P, _P, _I64, _I64, _P, _P]),
     "ssb_raster_fwd": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P]),
     "ssb_raster_bwd": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "ssb_raster_bwd_accum": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _I32, _P, _I64, _P, _P, _P, _P]),
     "ssb_loss_l1_ssim_fwdbwd": (C.c_int, [_P, _P, _I32, _I32, _I32, _F, _F, _P, _P, _P]),
     "ssb_adam_step": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _P, _P]),
     "ssb_adam_step_sh_quantized": (C.c_int, [_P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _P, _P]),

@@ -71,6 +71,17 @@ def raster_cotangents(name, n_pixels):
     return v_rgb, v_depth, v_T
 
 
+def accum_weight_map(name, n_pixels):
+    """Per-pixel densification weight map (non-negative, a fifth of the pixels zero) for the raster backward accumulation."""
+    rng = np.random.default_rng((CASES.get(name) or WIDE_CASES[name])["seed"] + 2)
+    w = rng.random(n_pixels, dtype=np.float32)
+    w[rng.random(n_pixels) < 0.2] = 0.0
+    return w
+
+
+ACCUM_CASES = ("ring2", "dense1")
+
+
 def loss_inputs():
     out = {}
     for tag, (B, H, W, seed) in dict(a=(1, 48, 64, 5), b=(2, 37, 53, 6)).items():

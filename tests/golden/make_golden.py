@@ -23,7 +23,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, HERE)
 
-from golden_cases import CASES, WIDE_CASES, build_case, loss_inputs, adam_inputs, raster_cotangents  # noqa: E402
+from golden_cases import ACCUM_CASES, CASES, WIDE_CASES, accum_weight_map, build_case, loss_inputs, adam_inputs, raster_cotangents  # noqa: E402
 
 DEV = "cuda:0"
 
@@ -233,6 +233,33 @@ def run_adam(ref, out_dir):
     np.savez_compressed(os.path.join(out_dir, "adam.npz"), **out)
 
 
+def run_accum(ref, out_dir):
+    """Per-splat densification weights of the raster backward pass (max, sum, average) on the committed intermediate
+    arrays of two fixture scenes: accum.npz."""
+    out = {}
+    for name in ACCUM_CASES:
+        cfg, sp, vm, K = build_case(name)
+        gold = np.load(os.path.join(HERE, f"{name}.npz"))
+        I, W, H, n = vm.shape[0], cfg.width, cfg.height, cfg.n_splats
+        m, M, P_ = I * n, gold["sorted_flat"].size, I * H * W
+        xy, depth, conic, opac, rgb = (dev(gold[k]) for k in ("xy", "depth", "conic", "opac", "rgb"))
+        offs, fl = dev(gold["offsets"]), dev(gold["sorted_flat"])
+        r_rgb, r_depth, r_T, r_last = (dev(gold[k]) for k in ("render_rgb", "render_depth", "render_T", "last_ids"))
+        v_rgb, v_depth, v_T = (dev(a) for a in raster_cotangents(name, P_))
+        wmap = dev(accum_weight_map(name, P_))
+        for mode, tag in ((1, "max"), (2, "sum"), (3, "avg")):
+            z = lambda *shape: torch.zeros(*shape, dtype=torch.float32, device=DEV)
+            g_xy, g_depth, g_conic, g_opac, g_rgb = z(m, 2), z(m), z(m, 3), z(m), z(m, 3)
+            acc, den = z(n), z(n)
+            check(ref.ref_raster_bwd_accum(mode, I, n, M, W, H, P(xy), P(depth), P(conic), P(opac), P(rgb), P(offs), P(fl), P(r_rgb), P(r_depth),
+                                           P(r_T), P(r_last), P(v_rgb), P(v_depth), P(v_T), P(g_xy), P(g_depth), P(g_conic), P(g_opac), P(g_rgb),
+                                           P(wmap), P(acc), P(den)), "ref_raster_bwd_accum")
+            out[f"{name}_{tag}"] = acc.cpu().numpy()
+            if mode == 3:
+                out[f"{name}_avg_den"] = den.cpu().numpy()
+    np.savez_compressed(os.path.join(out_dir, "accum.npz"), **out)
+
+
 def main():
     out_dir = sys.argv[1] if len(sys.argv) > 1 else HERE
     os.makedirs(out_dir, exist_ok=True)
@@ -245,6 +272,8 @@ def main():
         run_loss(ref, out_dir)
     if not only or "adam" in only:
         run_adam(ref, out_dir)
+    if not only or "accum" in only:
+        run_accum(ref, out_dir)
     print("wrote fixtures to", out_dir)
 
 

@@ -15,7 +15,7 @@ import pytest
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 
-from golden_cases import CASES, WIDE_CASES, adam_inputs, build_case, loss_inputs, raster_cotangents  # noqa: E402
+from golden_cases import ACCUM_CASES, CASES, WIDE_CASES, accum_weight_map, adam_inputs, build_case, loss_inputs, raster_cotangents  # noqa: E402
 
 
 ALL_CASES = list(CASES) + list(WIDE_CASES)
@@ -244,3 +244,22 @@ def test_adam_4bit_state_vs_reference(oracle):
         assert dv.max() <= 1 and do.max() <= 1 and (dv > 0).mean() <= 5e-2 and (do > 0).mean() <= 5e-2, step
         assert np.allclose(vb, rb, rtol=1e-4, atol=1e-7) and np.allclose(ob, rob, rtol=2e-3, atol=1e-5)
         vp, vb, op, ob = rv.copy(), rb.copy(), ro.copy(), rob.copy()
+
+
+@pytest.mark.parametrize("name", ACCUM_CASES)
+def test_raster_accum_weight_vs_reference(oracle, name):
+    """Densification weights (max / sum / average) of the backward walk against the reference's kernel."""
+    cfg, sp, vm, K = build_case(name)
+    gold, acc_gold = load(name), load("accum")
+    I, W, H, n = vm.shape[0], cfg.width, cfg.height, cfg.n_splats
+    proj = {k: np.ascontiguousarray(gold[k]) for k in ("xy", "conic", "opac")}
+    render = dict(T=np.ascontiguousarray(gold["render_T"]), last_ids=np.ascontiguousarray(gold["last_ids"]))
+    wmap = accum_weight_map(name, I * H * W)
+    offs, fl = np.ascontiguousarray(gold["offsets"]), np.ascontiguousarray(gold["sorted_flat"])
+    for mode, tag in ((1, "max"), (2, "sum"), (3, "avg")):
+        acc, den = oracle.raster_accum_weight(proj, offs, fl, I, n, W, H, render, wmap, mode)
+        ref = acc_gold[f"{name}_{tag}"]
+        assert (ref > 0).sum() > n // 10
+        assert frac_bad(acc, ref, 1e-5 * ref.max(), 2e-3) <= 5e-3, tag
+        if mode == 3:
+            assert frac_bad(den, acc_gold[f"{name}_avg_den"], 1e-5 * acc_gold[f"{name}_avg_den"].max(), 2e-3) <= 5e-3

@@ -13,7 +13,7 @@ torch = pytest.importorskip("torch")
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 
-from golden_cases import CASES, WIDE_CASES, adam_inputs, build_case, loss_inputs, raster_cotangents  # noqa: E402
+from golden_cases import ACCUM_CASES, CASES, WIDE_CASES, accum_weight_map, adam_inputs, build_case, loss_inputs, raster_cotangents  # noqa: E402
 from spirula_studio_b200 import lib as L  # noqa: E402
 
 pytestmark = pytest.mark.gpu
@@ -281,3 +281,36 @@ def test_adam_4bit_state_vs_reference(lib, U):
         assert dv.max() <= 1 and do.max() <= 1 and (dv > 0).mean() <= 5e-2 and (do > 0).mean() <= 5e-2, step
         assert np.allclose(vb.cpu().numpy(), rb, rtol=1e-4, atol=1e-7)
         state = [rv, rb, ro, rob]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ACCUM_CASES)
+def test_raster_accum_weight_vs_reference(lib, U, name):
+    """ssb_raster_bwd_accum: the densification weights against the reference's kernel, and the gradients unchanged by the mode."""
+    cfg, sp, vm, K = build_case(name)
+    gold, acc_gold = load(name), load("accum")
+    I, W, H, n = vm.shape[0], cfg.width, cfg.height, cfg.n_splats
+    v_rgb, v_depth, v_T = (U.dev(a) for a in raster_cotangents(name, I * H * W))
+    rec = U.pack_screen(lib, ref_proj(gold))
+    n_dev = torch.tensor([gold["sorted_flat"].size], dtype=torch.int64, device=U.DEV)
+    render = dict(depth=U.dev(gold["render_depth"]), T=U.dev(gold["render_T"]), last_ids=U.dev(gold["last_ids"]))
+    offs, fl = U.dev(gold["offsets"]), U.dev(gold["sorted_flat"])
+    wmap = U.dev(accum_weight_map(name, I * H * W))
+    base = U.vrec_to_arrays(U.raster_bwd(lib, rec, offs, fl, n_dev, I, W, H, render, v_rgb, v_depth, v_T, pairs=I * n), I * n)
+    for mode, tag in ((L.SSB_ACCUM_MAX, "max"), (L.SSB_ACCUM_SUM, "sum"), (L.SSB_ACCUM_AVG, "avg")):
+        for with_depth in (True, False):
+            v_rec = torch.zeros(I * n * L.SCREEN_REC_FLOATS, device=U.DEV)
+            acc, den = torch.zeros(n, device=U.DEV), torch.zeros(n, device=U.DEV)
+            L.check(lib.ssb_raster_bwd_accum(L.ptr(rec), L.ptr(offs), L.ptr(fl), L.ptr(n_dev), I, W, H, L.ptr(render["depth"]), L.ptr(render["T"]),
+                                             L.ptr(render["last_ids"]), L.ptr(v_rgb), L.ptr(v_depth) if with_depth else None, L.ptr(v_T), L.ptr(v_rec),
+                                             mode, L.ptr(wmap), n, None, L.ptr(acc), L.ptr(den), None))
+            torch.cuda.synchronize()
+            ref = acc_gold[f"{name}_{tag}"]
+            assert U.close_frac(acc.cpu().numpy(), ref, 1e-5 * ref.max(), 2e-3) <= 5e-3, (tag, with_depth)
+            if mode == L.SSB_ACCUM_AVG:
+                ref_den = acc_gold[f"{name}_avg_den"]
+                assert U.close_frac(den.cpu().numpy(), ref_den, 1e-5 * ref_den.max(), 2e-3) <= 5e-3
+            if with_depth:
+                got = U.vrec_to_arrays(v_rec, I * n)
+                for k in base:
+                    assert U.close_frac(got[k], base[k], 1e-5 * np.abs(base[k]).max(), 1e-4) <= 1e-3, (k, tag)

@@ -363,6 +363,24 @@ def test_full_size_raster_properties(lib, U):
     scale = g1.abs().max(dim=0).values.clamp_min(1e-20)
     assert float(((g2 - 2.0 * g1).abs() / scale).max()) < 1e-3
     assert float(g1.abs().sum()) > 0 and bool(torch.isfinite(g1).all())
+    # densification weights: with a weight map of ones the per-splat sums of alpha * T add up to the opacity
+    # 1 - T of all pixels (every fragment the forward pass blended is visited exactly once), the sum equals its
+    # own denominator, the maximum is a fragment weight (<= 1) and never exceeds the sum
+    ones = torch.ones(H * W, device=U.DEV)
+    res = {}
+    for mode in (L.SSB_ACCUM_MAX, L.SSB_ACCUM_AVG):
+        v_rec = torch.zeros(n * L.SCREEN_REC_FLOATS, device=U.DEV)
+        acc, den = torch.zeros(n, device=U.DEV), torch.zeros(n, device=U.DEV)
+        L.check(lib.ssb_raster_bwd_accum(L.ptr(pr["rec"]), L.ptr(offs), L.ptr(flat), L.ptr(n_dev), 1, W, H, None, L.ptr(out["T"]), L.ptr(out["last_ids"]),
+                                         L.ptr(v), None, None, L.ptr(v_rec), mode, L.ptr(ones), n, None, L.ptr(acc), L.ptr(den), None))
+        torch.cuda.synchronize()
+        res[mode] = (acc, den)
+        assert float((v_rec.view(n, 12) - g1).abs().max()) <= 1e-3 * float(g1.abs().max())     # gradients unchanged by the mode
+    mx, (sm, den) = res[L.SSB_ACCUM_MAX][0], res[L.SSB_ACCUM_AVG]
+    total, want = float(den.double().sum()), float((1.0 - T.double()).sum())
+    assert abs(total - want) <= 1e-3 * want, (total, want)
+    assert float((sm - den).abs().max()) <= 1e-4 * float(den.max())
+    assert float(mx.max()) <= 1.0 and bool((mx <= sm * (1 + 1e-5) + 1e-7).all()) and bool(((mx > 0) == (sm > 0)).all())
 
 
 def test_full_size_intersection_paths_agree(lib, U):

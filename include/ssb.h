@@ -291,6 +291,16 @@ int ssb_raster_bwd_accum(const SsbScreenRec* d_screen, const int32_t* d_tile_off
 int ssb_loss_l1_ssim_fwdbwd(const float* d_render, const float* d_gt, int32_t n_images, int32_t height, int32_t width,
                             float w_l1, float w_ssim, float* d_v_render, float* d_losses, void* stream);
 
+/* The same with the per-pixel SSIM loss map of the densification strategy (ssim_loss_map / ssim_loss_map_weight /
+ * ssim_loss_map_mode of fused_ssim_inplace_async, src/kernels/loss/FusedSSIM.cu:1211-1234; kernel :861-886,1009-1016):
+ * d_loss_map[image][y][x] += weight * (1 - mean over the channels of v), v = SSIM (mode 1, SsimFull), its
+ * contrast-structure factor (2, SsimCs) or its structure term (3, SsimStr); SsimLossMapMode,
+ * src/kernels/loss/PerPixelLoss.cuh:129-134.  Mode 0 writes no map.  The map is what
+ * ssb_raster_bwd_accum takes as d_weight_map. */
+int ssb_loss_l1_ssim_fwdbwd_map(const float* d_render, const float* d_gt, int32_t n_images, int32_t height, int32_t width,
+                                float w_l1, float w_ssim, float* d_v_render, float* d_losses,
+                                int32_t ssim_loss_map_mode, float ssim_loss_map_weight, float* d_loss_map, void* stream);
+
 /* ---- optimiser ---------------------------------------------------------- */
 
 typedef struct SsbAdamConfig {

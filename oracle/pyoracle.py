@@ -170,6 +170,16 @@ def loss_l1_ssim(render, gt, B, H, W, w_l1=0.8, w_ssim=0.2):
     return v, losses
 
 
+def loss_l1_ssim_map(render, gt, B, H, W, mode, weight, loss_map, w_l1=0.8, w_ssim=0.2):
+    """loss_l1_ssim that also adds weight * (1 - mean SSIM variant) into loss_map [B*H*W] (float32, in place)."""
+    lib = load()
+    v = np.zeros((B * H * W, 3), np.float32)
+    losses = np.zeros(3, np.float32)
+    lib.oracle_loss_l1_ssim_map(C.c_int(B), C.c_int(H), C.c_int(W), C.c_float(w_l1), C.c_float(w_ssim), _p(_f(render)), _p(_f(gt)), _p(v), _p(losses),
+                                C.c_int(mode), C.c_float(weight), _p(loss_map))
+    return v, losses
+
+
 def adam_geometry(p, g, m1, m2, step, lrs, grad_scale=1.0, zero_grad=0):
     """In place on the numpy arrays of p, g, m1, m2 (dicts with means, quats, scales, opacities)."""
     lib = load()

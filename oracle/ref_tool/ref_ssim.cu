@@ -10,3 +10,13 @@ extern "C" int ref_ssim_inplace(int B, int H, int W, const float* img1, const fl
         B, H, W, (const float3*)img1, (const float3*)img2, nullptr, 0, 0, 0, nullptr, dL_dmap, (float3*)dL_dimg1, ssim_out, 0.0f, nullptr, 0);
     return (int)cudaDeviceSynchronize();
 }
+
+// The same launch with the densification loss map (fused_ssim_inplace_async's ssim_loss_map arguments, :1211-1234):
+// loss_map += weight * (1 - SSIM variant), mode = SsimLossMapMode 1..3.
+extern "C" int ref_ssim_inplace_map(int B, int H, int W, const float* img1, const float* img2, float dL_dmap, float* dL_dimg1, float* ssim_out,
+                                    float map_weight, float* loss_map, int mode) {
+    cudaMemset(ssim_out, 0, sizeof(float));
+    memory_efficient_ssim_backward_kernel<true><<<_LAUNCH_ARGS_3D(W, H, B, BLOCK_X_ME, BLOCK_Y_ME, 1)>>>(
+        B, H, W, (const float3*)img1, (const float3*)img2, nullptr, 0, 0, 0, nullptr, dL_dmap, (float3*)dL_dimg1, ssim_out, map_weight, loss_map, mode);
+    return (int)cudaDeviceSynchronize();
+}

@@ -1008,10 +1008,15 @@ void oracle_raster_bwd(
 // (src/kernels/loss/FusedSSIM.cu:639-1022) with dL_dmap = -w_ssim, added in place.
 // losses[0] = L1 mean, losses[1] = SSIM mean, losses[2] = total.
 // ---------------------------------------------------------------------------
-void oracle_loss_l1_ssim(
+// map_mode (SsimLossMapMode, src/kernels/loss/PerPixelLoss.cuh:129-134) != 0: loss_map[b][y][x] +=
+// map_weight * (1 - mean over channels of v), v = SSIM (1), D/B (2), D / (2 sqrt(s1 s2) + C2) (3);
+// FusedSSIM.cu:861-886,1009-1016.
+void oracle_loss_l1_ssim_map(
     int B, int H, int W, float w_l1, float w_ssim,
-    const float* render, const float* gt, float* v_render, float* losses) {
+    const float* render, const float* gt, float* v_render, float* losses,
+    int map_mode, float map_weight, float* loss_map) {
     const int64_t P = (int64_t)H * W;
+    std::vector<float> lm_sum(map_mode ? (size_t)B * P : 0, 0.f);
     double l1_sum = 0.0, ssim_sum = 0.0;
     const float inv_mask_total = 1.0f / std::max((float)(B * P), 1.0f);
 #pragma omp parallel for reduction(+ : l1_sum) schedule(static)
@@ -1070,6 +1075,12 @@ void oracle_loss_l1_ssim(
                     float ssim_v = (C_ * D_) / (A * Bv);
                     csum += (double)ssim_v;
                     int64_t o = (int64_t)y * W + x;
+                    if (map_mode) {
+                        float lm = ssim_v;
+                        if (map_mode == 2) lm = D_ / Bv;
+                        else if (map_mode == 3) lm = D_ / (2.f * std::sqrt(std::max(sigma1_sq, 0.0f) * std::max(sigma2_sq, 0.0f)) + kC2);
+                        lm_sum[(size_t)b * P + o] += lm;
+                    }
                     d_mu1[o] = ((mu2 * 2.f * D_) / (A * Bv) - (mu2 * 2.f * C_) / (A * Bv) - (mu1 * 2.f * C_ * D_) / (A * A * Bv) + (mu1 * 2.f * C_ * D_) / (A * Bv * Bv)) * grad;
                     d_s1[o] = ((-C_ * D_) / (A * Bv * Bv)) * grad;
                     d_s12[o] = ((2.f * C_) / (A * Bv)) * grad;
@@ -1109,6 +1120,14 @@ void oracle_loss_l1_ssim(
     float l1 = (float)(l1_sum / (double)(B * P));
     float ssim = (float)(ssim_sum / (double)(3.0 * B * P));
     if (losses) { losses[0] = l1; losses[1] = ssim; losses[2] = w_l1 * l1 + w_ssim * (1.0f - ssim); }
+    if (map_mode)
+        for (int64_t i = 0; i < (int64_t)B * P; ++i) loss_map[i] += map_weight * (1.0f - lm_sum[i] / 3.0f);
+}
+
+void oracle_loss_l1_ssim(
+    int B, int H, int W, float w_l1, float w_ssim,
+    const float* render, const float* gt, float* v_render, float* losses) {
+    oracle_loss_l1_ssim_map(B, H, W, w_l1, w_ssim, render, gt, v_render, losses, 0, 0.f, nullptr);
 }
 
 // ---------------------------------------------------------------------------

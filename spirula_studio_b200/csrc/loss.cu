@@ -32,9 +32,15 @@ constexpr int kSmemA = 2 * kIn * kIn;                 // X and Y patches; later 
 constexpr int kSmemB = 5 * kIn * kMid;                // row-convolved moments; later 3*42*32 row-convolved partials
 constexpr int kLossSmemBytes = (kSmemA + kSmemB) * 4;
 
+// MAP_MODE (SsimLossMapMode, src/kernels/loss/PerPixelLoss.cuh:129-134): 0 no map; otherwise
+// loss_map[pixel] += map_weight * (1 - mean over channels of v) with v = the SSIM (1), its
+// contrast-structure factor D/B (2) or the structure term D / (2 sqrt(sigma1^2 sigma2^2) + C2) (3)
+// (src/kernels/loss/FusedSSIM.cu:861-886,1009-1016).
+template <int MAP_MODE>
 __global__ void __launch_bounds__(kLossThreads) loss_l1_ssim_kernel(
     const float* __restrict__ render, const float* __restrict__ gt, int B, int H, int W,
-    float w_l1, float w_ssim, float* __restrict__ v_render, float* __restrict__ losses) {
+    float w_l1, float w_ssim, float* __restrict__ v_render, float* __restrict__ losses,
+    float map_weight, float* __restrict__ loss_map) {
     extern __shared__ float smem[];
     float* sX = smem;
     float* sY = smem + kIn * kIn;
@@ -137,7 +143,19 @@ __global__ void __launch_bounds__(kLossThreads) loss_l1_ssim_kernel(
                     const float C_ = 2.f * mu1 * mu2 + kC1;
                     const float D_ = 2.f * sigma12 + kC2;
                     const float rAB = 1.0f / (A * Bv);
-                    if (r >= kHalo && r < kHalo + kLossTile && c >= kHalo && c < kHalo + kLossTile) ssim_acc += (C_ * D_) * rAB;
+                    if (r >= kHalo && r < kHalo + kLossTile && c >= kHalo && c < kHalo + kLossTile) {
+                        ssim_acc += (C_ * D_) * rAB;
+                        if (MAP_MODE) {
+                            float lm;
+                            if (MAP_MODE == 2) lm = D_ / Bv;
+                            else if (MAP_MODE == 3) lm = D_ / (2.f * sqrtf(fmaxf(sigma1_sq, 0.0f) * fmaxf(sigma2_sq, 0.0f)) + kC2);
+                            else lm = (C_ * D_) * rAB;
+                            // map += w * (1 - (v0 + v1 + v2) / 3) is linear in the channels' values, so each channel adds
+                            // its share; the same thread meets this pixel in all three channels (no race)
+                            float* slot = loss_map + (int64_t)b * P + (int64_t)gy * W + gx;
+                            *slot += (ch == 0 ? map_weight : 0.f) - map_weight * (1.0f / 3.0f) * lm;
+                        }
+                    }
                     d0 = ((mu2 * 2.f * D_) * rAB - (mu2 * 2.f * C_) * rAB - (mu1 * 2.f * C_ * D_) * rAB / A + (mu1 * 2.f * C_ * D_) * rAB / Bv) * grad;
                     d1 = (-C_ * D_) * rAB / Bv * grad;
                     d2 = (2.f * C_) * rAB * grad;
@@ -220,17 +238,24 @@ __global__ void __launch_bounds__(kLossThreads) loss_l1_ssim_kernel(
     }
 }
 
-int launch_loss(const float* d_render, const float* d_gt, int B, int H, int W, float w_l1, float w_ssim,
-                float* d_v_render, float* d_losses, cudaStream_t st) {
+template <int MAP_MODE>
+static int launch_loss_mode(const float* d_render, const float* d_gt, int B, int H, int W, float w_l1, float w_ssim,
+                            float* d_v_render, float* d_losses, float map_weight, float* d_loss_map, cudaStream_t st) {
     static bool attr_set = false;
     if (!attr_set) {
-        SSB_CUDA(cudaFuncSetAttribute(loss_l1_ssim_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kLossSmemBytes));
+        SSB_CUDA(cudaFuncSetAttribute(loss_l1_ssim_kernel<MAP_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kLossSmemBytes));
         attr_set = true;
     }
     dim3 grid((unsigned)ceil_div(W, kLossTile), (unsigned)ceil_div(H, kLossTile), (unsigned)B);
-    loss_l1_ssim_kernel<<<grid, kLossThreads, kLossSmemBytes, st>>>(d_render, d_gt, B, H, W, w_l1, w_ssim, d_v_render, d_losses);
+    loss_l1_ssim_kernel<MAP_MODE><<<grid, kLossThreads, kLossSmemBytes, st>>>(d_render, d_gt, B, H, W, w_l1, w_ssim, d_v_render, d_losses,
+                                                                              map_weight, d_loss_map);
     SSB_LAUNCHED("loss_l1_ssim_kernel");
     return SSB_OK;
+}
+
+int launch_loss(const float* d_render, const float* d_gt, int B, int H, int W, float w_l1, float w_ssim,
+                float* d_v_render, float* d_losses, cudaStream_t st) {
+    return launch_loss_mode<0>(d_render, d_gt, B, H, W, w_l1, w_ssim, d_v_render, d_losses, 0.f, nullptr, st);
 }
 
 }  // namespace ssb
@@ -243,4 +268,23 @@ extern "C" int ssb_loss_l1_ssim_fwdbwd(const float* d_render, const float* d_gt,
     if (n_images == 0) return SSB_OK;
     if (d_losses) SSB_CUDA(cudaMemsetAsync(d_losses, 0, 3 * sizeof(float), (cudaStream_t)stream));
     return launch_loss(d_render, d_gt, n_images, height, width, w_l1, w_ssim, d_v_render, d_losses, (cudaStream_t)stream);
+}
+
+extern "C" int ssb_loss_l1_ssim_fwdbwd_map(const float* d_render, const float* d_gt, int32_t n_images, int32_t height, int32_t width,
+                                           float w_l1, float w_ssim, float* d_v_render, float* d_losses,
+                                           int32_t ssim_loss_map_mode, float ssim_loss_map_weight, float* d_loss_map, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(d_render && d_gt && d_v_render, "ssb_loss_l1_ssim_fwdbwd_map: NULL argument");
+    SSB_REQUIRE(n_images >= 0 && height > 0 && width > 0, "ssb_loss_l1_ssim_fwdbwd_map: bad sizes");
+    SSB_REQUIRE(ssim_loss_map_mode >= 0 && ssim_loss_map_mode <= 3, "ssb_loss_l1_ssim_fwdbwd_map: mode %d is not a SsimLossMapMode", ssim_loss_map_mode);
+    SSB_REQUIRE(ssim_loss_map_mode == 0 || d_loss_map, "ssb_loss_l1_ssim_fwdbwd_map: d_loss_map is NULL");
+    if (n_images == 0) return SSB_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (d_losses) SSB_CUDA(cudaMemsetAsync(d_losses, 0, 3 * sizeof(float), st));
+    switch (ssim_loss_map_mode) {
+        case 1: return launch_loss_mode<1>(d_render, d_gt, n_images, height, width, w_l1, w_ssim, d_v_render, d_losses, ssim_loss_map_weight, d_loss_map, st);
+        case 2: return launch_loss_mode<2>(d_render, d_gt, n_images, height, width, w_l1, w_ssim, d_v_render, d_losses, ssim_loss_map_weight, d_loss_map, st);
+        case 3: return launch_loss_mode<3>(d_render, d_gt, n_images, height, width, w_l1, w_ssim, d_v_render, d_losses, ssim_loss_map_weight, d_loss_map, st);
+        default: return launch_loss_mode<0>(d_render, d_gt, n_images, height, width, w_l1, w_ssim, d_v_render, d_losses, 0.f, nullptr, st);
+    }
 }

@@ -90,6 +90,14 @@ def loss_inputs():
     return out
 
 
+LOSS_MAP_WEIGHT = 0.7
+
+
+def loss_map_base(tag, n_pixels):
+    """What the densification loss map holds before the SSIM term is added in place (the per-pixel loss pass writes it)."""
+    return np.random.default_rng(50 + ord(tag)).random(n_pixels, dtype=np.float32)
+
+
 def adam_inputs():
     n = 700
     cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=n)

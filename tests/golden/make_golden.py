@@ -23,7 +23,8 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, HERE)
 
-from golden_cases import ACCUM_CASES, CASES, WIDE_CASES, accum_weight_map, build_case, loss_inputs, adam_inputs, raster_cotangents  # noqa: E402
+from golden_cases import (ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, WIDE_CASES, accum_weight_map, adam_inputs, build_case, loss_inputs,  # noqa: E402
+                          loss_map_base, raster_cotangents)  # noqa: E402
 
 DEV = "cuda:0"
 
@@ -104,6 +105,21 @@ def run_loss(ref, out_dir):
         out[f"{tag}_grad"] = v.cpu().numpy()
         out[f"{tag}_ssim"] = s.cpu().numpy()
     np.savez_compressed(os.path.join(out_dir, "ssim.npz"), **out)
+
+
+def run_loss_map(ref, out_dir):
+    """The densification loss map of the SSIM kernel, added in place onto a seeded map, for the three SsimLossMapMode values."""
+    out = {}
+    for tag, (B, H, W, render, gt) in loss_inputs().items():
+        d_render, d_gt = dev(render), dev(gt)
+        for mode in (1, 2, 3):
+            v = torch.zeros(B * H * W, 3, device=DEV)
+            s = torch.zeros(1, device=DEV)
+            lm = dev(loss_map_base(tag, B * H * W))
+            check(ref.ref_ssim_inplace_map(B, H, W, P(d_render), P(d_gt), C.c_float(-0.2), P(v), P(s), C.c_float(LOSS_MAP_WEIGHT), P(lm), mode),
+                  "ref_ssim_inplace_map")
+            out[f"{tag}_map{mode}"] = lm.cpu().numpy()
+    np.savez_compressed(os.path.join(out_dir, "ssim_map.npz"), **out)
 
 
 def run_adam(ref, out_dir):
@@ -272,6 +288,8 @@ def main():
         run_loss(ref, out_dir)
     if not only or "adam" in only:
         run_adam(ref, out_dir)
+    if not only or "ssim_map" in only:
+        run_loss_map(ref, out_dir)
     if not only or "accum" in only:
         run_accum(ref, out_dir)
     print("wrote fixtures to", out_dir)

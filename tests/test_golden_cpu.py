@@ -15,7 +15,8 @@ import pytest
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 
-from golden_cases import ACCUM_CASES, CASES, WIDE_CASES, accum_weight_map, adam_inputs, build_case, loss_inputs, raster_cotangents  # noqa: E402
+from golden_cases import (ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, WIDE_CASES, accum_weight_map, adam_inputs, build_case, loss_inputs,  # noqa: E402
+                          loss_map_base, raster_cotangents)  # noqa: E402
 
 
 ALL_CASES = list(CASES) + list(WIDE_CASES)
@@ -263,3 +264,17 @@ def test_raster_accum_weight_vs_reference(oracle, name):
         assert frac_bad(acc, ref, 1e-5 * ref.max(), 2e-3) <= 5e-3, tag
         if mode == 3:
             assert frac_bad(den, acc_gold[f"{name}_avg_den"], 1e-5 * acc_gold[f"{name}_avg_den"].max(), 2e-3) <= 5e-3
+
+
+def test_ssim_loss_map_vs_reference(oracle):
+    """The densification loss map (three SSIM variants, added in place) against the reference's kernel."""
+    gold = load("ssim_map")
+    for tag, (B, H, W, render, gt) in loss_inputs().items():
+        for mode in (1, 2, 3):
+            lm = loss_map_base(tag, B * H * W)
+            v, losses = oracle.loss_l1_ssim_map(render, gt, B, H, W, mode, LOSS_MAP_WEIGHT, lm, 0.0, 0.2)
+            ref = gold[f"{tag}_map{mode}"]
+            assert np.abs(ref - loss_map_base(tag, B * H * W)).max() > 0.05
+            assert frac_bad(lm, ref, 2e-5, 1e-4) <= 1e-3, (tag, mode)
+            v0, _ = oracle.loss_l1_ssim(render, gt, B, H, W, 0.0, 0.2)
+            assert np.array_equal(v, v0)                                     # the gradient does not depend on the map

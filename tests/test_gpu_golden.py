@@ -13,7 +13,8 @@ torch = pytest.importorskip("torch")
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 
-from golden_cases import ACCUM_CASES, CASES, WIDE_CASES, accum_weight_map, adam_inputs, build_case, loss_inputs, raster_cotangents  # noqa: E402
+from golden_cases import (ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, WIDE_CASES, accum_weight_map, adam_inputs, build_case, loss_inputs,  # noqa: E402
+                          loss_map_base, raster_cotangents)  # noqa: E402
 from spirula_studio_b200 import lib as L  # noqa: E402
 
 pytestmark = pytest.mark.gpu
@@ -314,3 +315,21 @@ def test_raster_accum_weight_vs_reference(lib, U, name):
                 got = U.vrec_to_arrays(v_rec, I * n)
                 for k in base:
                     assert U.close_frac(got[k], base[k], 1e-5 * np.abs(base[k]).max(), 1e-4) <= 1e-3, (k, tag)
+
+
+@pytest.mark.gpu
+def test_ssim_loss_map_vs_reference(lib, U):
+    """ssb_loss_l1_ssim_fwdbwd_map: the densification loss map against the reference's kernel; gradient and scalars as without a map."""
+    gold = load("ssim_map")
+    for tag, (B, H, W, render, gt) in loss_inputs().items():
+        d_r, d_g = U.dev(render), U.dev(gt)
+        v0 = torch.zeros(B * H * W, 3, device=U.DEV); l0 = torch.zeros(3, device=U.DEV)
+        L.check(lib.ssb_loss_l1_ssim_fwdbwd(L.ptr(d_r), L.ptr(d_g), B, H, W, 0.8, 0.2, L.ptr(v0), L.ptr(l0), None))
+        for mode in (1, 2, 3):
+            v = torch.zeros(B * H * W, 3, device=U.DEV); losses = torch.zeros(3, device=U.DEV)
+            lm = U.dev(loss_map_base(tag, B * H * W))
+            L.check(lib.ssb_loss_l1_ssim_fwdbwd_map(L.ptr(d_r), L.ptr(d_g), B, H, W, 0.8, 0.2, L.ptr(v), L.ptr(losses), mode, LOSS_MAP_WEIGHT, L.ptr(lm), None))
+            torch.cuda.synchronize()
+            ref = gold[f"{tag}_map{mode}"]
+            assert U.close_frac(lm.cpu().numpy(), ref, 2e-5, 1e-4) <= 1e-3, (tag, mode)
+            assert torch.equal(v, v0) and torch.allclose(losses, l0, rtol=1e-5, atol=1e-7)

@@ -336,6 +336,8 @@ typedef struct SsbAdamExtras {
     const float* d_radii;                /* [n_total] screen radii of ssb_project_fwd (max over the views) */
     const int32_t* d_steps;              /* [n_total] per-splat bias-correction exponents (>= 1), or NULL: cfg->step */
     int64_t n_total;                     /* number of splats of the whole model (the range may be a shard) */
+    float* d_densify_score;              /* [n_total] or NULL: |grad_scale * dL/dmean| * exp(largest log-scale) before the
+                                            update, the world-gradient densification score (FusedGeometryOptim.cu:283-286) */
 } SsbAdamExtras;
 
 /* ssb_adam_step with the optional parts: per-splat regulariser gradients (Slang per_splat_losses_bwd,

@@ -192,7 +192,8 @@ def adam_geometry(p, g, m1, m2, step, lrs, grad_scale=1.0, zero_grad=0):
                              _p(p["opacities"]), _p(g["opacities"]), _p(m1["opacities"]), _p(m2["opacities"]))
 
 
-def adam_geometry_ex(p, g, m1, m2, step, lrs, grad_scale=1.0, zero_grad=0, reg=None, scale_agnostic=False, radii=None, steps=None):
+def adam_geometry_ex(p, g, m1, m2, step, lrs, grad_scale=1.0, zero_grad=0, reg=None, scale_agnostic=False, radii=None, steps=None,
+                     densify_score=None):
     """adam_geometry with the optional parts: reg = the seven regulariser numbers (max_gauss_ratio, scale_regularization,
     mcmc_opacity, mcmc_scale, erank, erank_s3, quat_norm; undivided weights), the scale-agnostic mean update (needs radii)
     and per-splat int32 step counters."""
@@ -206,7 +207,8 @@ def adam_geometry_ex(p, g, m1, m2, step, lrs, grad_scale=1.0, zero_grad=0, reg=N
                                 _p(p["scales"]), _p(g["scales"]), _p(m1["scales"]), _p(m2["scales"]),
                                 _p(p["opacities"]), _p(g["opacities"]), _p(m1["opacities"]), _p(m2["opacities"]),
                                 _p(reg_a) if reg_a is not None else None, C.c_int(1 if scale_agnostic else 0),
-                                _p(radii) if radii is not None else None, _p(steps) if steps is not None else None)
+                                _p(radii) if radii is not None else None, _p(steps) if steps is not None else None,
+                                _p(densify_score) if densify_score is not None else None)
 
 
 def adam_plain(param, grad, m1, m2, step, lr, l2_reg=0.0, l2_reg_offset=0.0, grad_scale=1.0, zero_grad=0, steps=None, stride=1):

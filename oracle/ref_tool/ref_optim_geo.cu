@@ -36,7 +36,7 @@ extern "C" int ref_adam_geometry_ex(
     float* quats, float* v_quats, float* g1_quats, float* g2_quats,
     float* scales, float* v_scales, float* g1_scales, float* g2_scales,
     float* opacs, float* v_opacs, float* g1_opacs, float* g2_opacs,
-    const float* reg, int use_scale_agnostic_mean, const float* radii, const int32_t* steps) {
+    const float* reg, int use_scale_agnostic_mean, const float* radii, const int32_t* steps, float* densify_score) {
     NonShQuantState non_sh;
     GradQuantBuffers gq;
     const float n = (float)N;
@@ -46,7 +46,7 @@ extern "C" int ref_adam_geometry_ex(
             (float4*)quats, (float4*)v_quats, (float4*)g1_quats, (float4*)g2_quats,
             (float3*)scales, (float3*)v_scales, (float3*)g1_scales, (float3*)g2_scales,
             opacs, v_opacs, g1_opacs, g2_opacs,
-            nullptr, nullptr, radii, nullptr,
+            nullptr, nullptr, radii, densify_score,
             lr_means, lr_quats, lr_scales, lr_opacs, 0.0f,
             reg[0], reg[1] / n, reg[2] / n, reg[3] / n, reg[4] / n, reg[5] / n, reg[6] / n, 0.0f, grad_scale,
             non_sh, gq, step, steps, N);

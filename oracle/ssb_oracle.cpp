@@ -1144,7 +1144,7 @@ void oracle_adam_geometry_ex(
     float* opacs, float* v_opacs, float* g1_opacs, float* g2_opacs,
     // regulariser weights as the caller gives them (the launcher divides them by N, :457-462), in the order
     // max_gauss_ratio, scale_regularization, mcmc_opacity, mcmc_scale, erank, erank_s3, quat_norm
-    const float* reg, int use_scale_agnostic_mean, const float* radii, const int32_t* steps) {
+    const float* reg, int use_scale_agnostic_mean, const float* radii, const int32_t* steps, float* densify_score) {
     const float eps = 1e-15f, beta1 = 0.9f, beta2 = 0.999f;
     const float lr_means0 = lr_means, lr_quats0 = lr_quats, lr_scales0 = lr_scales, lr_opacs0 = lr_opacs;
     const float inv_n = 1.0f / (float)N;
@@ -1233,6 +1233,10 @@ void oracle_adam_geometry_ex(
             upd(opacs[i], g, g1_opacs[i], g2_opacs[i], lr_opacs);
             if (zero_grad) v_opacs[i] = 0.f;
         }
+        if (densify_score) {   // :283-286, from the gradient and the log-scales before the update
+            const float vx = grad_scale * v_means[3 * i], vy = grad_scale * v_means[3 * i + 1], vz = grad_scale * v_means[3 * i + 2];
+            densify_score[i] = std::exp(std::max(std::max(s0[0], s0[1]), s0[2])) * std::sqrt(vx * vx + vy * vy + vz * vz);
+        }
         if (use_scale_agnostic_mean) {   // :302-314
             const float v[3] = {grad_scale * v_means[3 * i], grad_scale * v_means[3 * i + 1], grad_scale * v_means[3 * i + 2]};
             const float w = qn0[0], x = qn0[1], y = qn0[2], z = qn0[3];
@@ -1272,7 +1276,7 @@ void oracle_adam_geometry(
     float* opacs, float* v_opacs, float* g1_opacs, float* g2_opacs) {
     oracle_adam_geometry_ex(N, step, grad_scale, zero_grad, lr_means, lr_quats, lr_scales, lr_opacs, means, v_means, g1_means, g2_means,
                             quats, v_quats, g1_quats, g2_quats, scales, v_scales, g1_scales, g2_scales, opacs, v_opacs, g1_opacs, g2_opacs,
-                            nullptr, 0, nullptr, nullptr);
+                            nullptr, 0, nullptr, nullptr, nullptr);
 }
 
 // fused_adam_step -> fused_adam_with_steps_kernel

@@ -140,6 +140,10 @@ __global__ void __launch_bounds__(256) adam_geometry_kernel(
         m1.opacities[i] = a; m2.opacities[i] = b;
         if (zg) g.opacities[i] = 0.f;
     }
+    if (EX && ex.d_densify_score) {
+        const float vx = gs * g.means[3 * i], vy = gs * g.means[3 * i + 1], vz = gs * g.means[3 * i + 2];
+        ex.d_densify_score[i] = expf(fmaxf(fmaxf(s_old[0], s_old[1]), s_old[2])) * sqrtf(vx * vx + vy * vy + vz * vz);
+    }
     if (EX && ex.use_scale_agnostic_mean) {
         // first moment of covariance * gradient * sqrt(2 log(255 * opacity)), second moment of
         // (gradient * 0.6 * screen radius)^2, all from the parameters before this update

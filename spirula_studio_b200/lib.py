@@ -55,7 +55,7 @@ class SsbAdamExtras(C.Structure):
     _fields_ = [("max_gauss_ratio", C.c_float), ("scale_regularization_weight", C.c_float), ("mcmc_opacity_reg_weight", C.c_float),
                 ("mcmc_scale_reg_weight", C.c_float), ("erank_reg_weight", C.c_float), ("erank_reg_weight_s3", C.c_float),
                 ("quat_norm_reg_weight", C.c_float), ("use_scale_agnostic_mean", C.c_int32), ("d_radii", C.c_void_p),
-                ("d_steps", C.c_void_p), ("n_total", C.c_int64)]
+                ("d_steps", C.c_void_p), ("n_total", C.c_int64), ("d_densify_score", C.c_void_p)]
 
 
 class SsbStepConfig(C.Structure):

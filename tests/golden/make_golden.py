@@ -185,6 +185,7 @@ def run_adam(ref, out_dir):
     ex = inp["ex"]
     d_reg_host = np.ascontiguousarray(ex["reg"])
     d_radii, d_steps = dev(ex["radii"]), dev(ex["steps"])
+    d_score = torch.zeros(n, dtype=torch.float32, device=DEV)
     for tag, agnostic in (("exA", 0), ("exB", 1)):
         p = {k: dev(v.reshape(-1)) for k, v in inp["params"].items()}
         m1 = {k: torch.zeros_like(t) for k, t in p.items()}
@@ -197,7 +198,9 @@ def run_adam(ref, out_dir):
                                            P(p["quats"]), P(g["quats"]), P(m1["quats"]), P(m2["quats"]),
                                            P(p["scales"]), P(g["scales"]), P(m1["scales"]), P(m2["scales"]),
                                            P(p["opacities"]), P(g["opacities"]), P(m1["opacities"]), P(m2["opacities"]),
-                                           d_reg_host.ctypes.data_as(C.c_void_p), agnostic, P(d_radii), P(d_steps)), "ref_adam_geometry_ex")
+                                           d_reg_host.ctypes.data_as(C.c_void_p), agnostic, P(d_radii), P(d_steps), P(d_score)), "ref_adam_geometry_ex")
+            if not agnostic and step == 1:
+                out["exA_densify_score"] = d_score.cpu().numpy()
             if not agnostic:
                 check(ref.ref_adam_plain_steps(C.c_int64(3 * n), P(d_steps), 3, C.c_float(lr["lr_features_dc"]), C.c_float(0.0),
                                                C.c_float(0.5 / 0.28209479177387814), C.c_float(inp["grad_scale"]), 0,

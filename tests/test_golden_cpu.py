@@ -193,7 +193,11 @@ def test_adam_extras_vs_reference(oracle):
         m2 = {k: np.zeros_like(v) for k, v in p.items()}
         for step, grads in enumerate(inp["grads"], start=1):
             g = {k: v.copy() for k, v in grads.items()}
-            oracle.adam_geometry_ex(p, g, m1, m2, step, lr, grad_scale=gs, reg=ex["reg"], scale_agnostic=agnostic, radii=ex["radii"], steps=ex["steps"])
+            score = np.zeros(n, np.float32)
+            oracle.adam_geometry_ex(p, g, m1, m2, step, lr, grad_scale=gs, reg=ex["reg"], scale_agnostic=agnostic, radii=ex["radii"], steps=ex["steps"],
+                                    densify_score=score)
+            if not agnostic and step == 1:
+                assert np.allclose(score, gold["exA_densify_score"], rtol=1e-4, atol=1e-9) and score.min() > 0
             keys = ["means"]
             if not agnostic:
                 oracle.adam_plain(p["features_dc"], g["features_dc"], m1["features_dc"], m2["features_dc"], step, lr["lr_features_dc"], 0.0,

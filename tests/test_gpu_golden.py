@@ -214,7 +214,8 @@ def test_adam_extras_vs_reference(lib, U):
         p = {k: U.dev(v.reshape(-1)) for k, v in inp["params"].items()}
         m1 = {k: torch.zeros_like(t) for k, t in p.items()}
         m2 = {k: torch.zeros_like(t) for k, t in p.items()}
-        extras = L.SsbAdamExtras(*reg, agnostic, d_radii.data_ptr(), d_steps.data_ptr(), n)
+        d_score = torch.zeros(n, device=U.DEV)
+        extras = L.SsbAdamExtras(*reg, agnostic, d_radii.data_ptr(), d_steps.data_ptr(), n, d_score.data_ptr())
         for step, grads in enumerate(inp["grads"], start=1):
             g = {k: U.dev(v.reshape(-1)) for k, v in grads.items()}
             cfg = L.SsbAdamConfig(lr["lr_means"], lr["lr_quats"], lr["lr_scales"], lr["lr_opacities"], lr["lr_features_dc"], lr["lr_features_sh"],
@@ -227,6 +228,8 @@ def test_adam_extras_vs_reference(lib, U):
             torch.cuda.synchronize()
             for k in (list(p) if not agnostic else ["means"]):
                 assert U.close_frac(p[k].cpu().numpy(), gold[f"{tag}_p{step}_{k}"], 5e-6, 1e-4) <= 1e-3, (tag, k, step)
+            if not agnostic and step == 1:
+                assert np.allclose(d_score.cpu().numpy(), gold["exA_densify_score"], rtol=1e-4, atol=1e-9)
     q = inp["qq16"]
     n_sp = (q["numel"] + 44) // 45
     steps_q = U.dev(np.ascontiguousarray(np.resize(ex["steps"], n_sp)))

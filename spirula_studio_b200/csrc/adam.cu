@@ -295,7 +295,8 @@ __device__ __forceinline__ void block_minmax(const float (&vmin)[NMIN], const fl
 // (16-byte gradient loads, 8-byte code loads); the block minima/maxima are folded per thread
 // first, then one redux.sync per value per warp and a two-entry exchange through shared memory.
 // OPTIM_BITS = 8: two bytes per cell (u, s); 4: one byte per cell, u in the low nibble (QuantizedAdamState<4,256>).
-template <int VALUE_BITS, int OPTIM_BITS>
+// STEPS: per-splat step counters (compiled apart: the power function costs the plain path registers).
+template <int VALUE_BITS, int OPTIM_BITS, bool STEPS>
 __global__ void __launch_bounds__(64) adam_qq_kernel(
     float* __restrict__ grad, uint8_t* __restrict__ optim_packed, float4* __restrict__ optim_bounds,
     uint8_t* __restrict__ value_packed, float2* __restrict__ value_bounds, int64_t first_block, int64_t numel_total,
@@ -374,7 +375,7 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
             // the reference builds this kernel with --use_fast_math: approximate division and
             // square root are its own arithmetic here (cmake/SsBackendCuda.cmake:95-102)
             float lr1 = lr_ibc1, c2 = ibc2;
-            if (steps) {
+            if (STEPS) {
                 const float step = (float)steps[idx / stride];
                 lr1 = lr * inv_bias_correction(kBeta1, step);
                 c2 = inv_bias_correction(kBeta2, step);
@@ -546,13 +547,14 @@ int ssb_adam_step_sh_quantized_ex(float* d_grad, uint8_t* d_optim_packed, float*
     int64_t end_total = first_cell + numel;   // cells beyond the range belong to another caller
 #define SSB_QQ_ARGS d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed, (float2*)d_value_bounds, first_cell / 256, end_total, \
         cfg->lr_features_sh * ibc1, ibc2, decay, 0.0f, cfg->grad_scale, cfg->zero_grad, d_steps, cells_per_splat, cfg->lr_features_sh
-#define SSB_QQ_LAUNCH(OB) \
+#define SSB_QQ_LAUNCH(OB, ST) \
     do { \
-        if (value_bits == 32) adam_qq_kernel<32, OB><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS); \
-        else if (value_bits == 8) adam_qq_kernel<8, OB><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS); \
-        else adam_qq_kernel<16, OB><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS); \
+        if (value_bits == 32) adam_qq_kernel<32, OB, ST><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS); \
+        else if (value_bits == 8) adam_qq_kernel<8, OB, ST><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS); \
+        else adam_qq_kernel<16, OB, ST><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS); \
     } while (0)
-    if (optim_bits == 4) SSB_QQ_LAUNCH(4); else SSB_QQ_LAUNCH(8);
+    if (d_steps) { if (optim_bits == 4) SSB_QQ_LAUNCH(4, true); else SSB_QQ_LAUNCH(8, true); }
+    else { if (optim_bits == 4) SSB_QQ_LAUNCH(4, false); else SSB_QQ_LAUNCH(8, false); }
 #undef SSB_QQ_LAUNCH
 #undef SSB_QQ_ARGS
     SSB_LAUNCHED("adam_qq_kernel");

@@ -443,6 +443,15 @@ int ssb_step_create(const SsbStepConfig* cfg, SsbStep** out);
 void ssb_step_destroy(SsbStep* step);
 int64_t ssb_step_device_bytes(const SsbStep* step);
 
+/* Switches the densification outputs of the step on (accum_mode != SSB_ACCUM_NONE) or off: every view then also
+ * builds its SSIM loss map (ssim_loss_map_weight * (1 - SSIM variant), as ssb_loss_l1_ssim_fwdbwd_map on a zeroed map;
+ * the reference adds its per-pixel loss map of the pixel-loss pass on top, src/engine/EngineLoss.cpp, which is not
+ * built here) and the raster backward pass folds it into d_accum_weight [n_splats] (and d_accum_weight_den for
+ * SSB_ACCUM_AVG) as ssb_raster_bwd_accum does.  The arrays are combined into across views and calls
+ * (EngineTrainStep.cpp:264-272); the caller zeroes them.  Allocates one [H][W] map per lane on first use. */
+int ssb_step_set_densify(SsbStep* step, int32_t ssim_loss_map_mode, float ssim_loss_map_weight, int32_t accum_mode,
+                         float* d_accum_weight, float* d_accum_weight_den);
+
 /* Forward + loss + backward of `n_views` views (device camera arrays and device
  * targets d_gt [n_views][H][W][3]); gradients are overwritten by the first view
  * when `accumulate` == 0 and added to otherwise.  Loss sums accumulate into

@@ -258,6 +258,17 @@ int launch_loss(const float* d_render, const float* d_gt, int B, int H, int W, f
     return launch_loss_mode<0>(d_render, d_gt, B, H, W, w_l1, w_ssim, d_v_render, d_losses, 0.f, nullptr, st);
 }
 
+// d_losses is added to (not cleared); map_mode 0 is launch_loss
+int launch_loss_map(const float* d_render, const float* d_gt, int B, int H, int W, float w_l1, float w_ssim,
+                    float* d_v_render, float* d_losses, int map_mode, float map_weight, float* d_loss_map, cudaStream_t st) {
+    switch (map_mode) {
+        case 1: return launch_loss_mode<1>(d_render, d_gt, B, H, W, w_l1, w_ssim, d_v_render, d_losses, map_weight, d_loss_map, st);
+        case 2: return launch_loss_mode<2>(d_render, d_gt, B, H, W, w_l1, w_ssim, d_v_render, d_losses, map_weight, d_loss_map, st);
+        case 3: return launch_loss_mode<3>(d_render, d_gt, B, H, W, w_l1, w_ssim, d_v_render, d_losses, map_weight, d_loss_map, st);
+        default: return launch_loss_mode<0>(d_render, d_gt, B, H, W, w_l1, w_ssim, d_v_render, d_losses, 0.f, nullptr, st);
+    }
+}
+
 }  // namespace ssb
 
 extern "C" int ssb_loss_l1_ssim_fwdbwd(const float* d_render, const float* d_gt, int32_t n_images, int32_t height, int32_t width,
@@ -281,10 +292,6 @@ extern "C" int ssb_loss_l1_ssim_fwdbwd_map(const float* d_render, const float* d
     if (n_images == 0) return SSB_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (d_losses) SSB_CUDA(cudaMemsetAsync(d_losses, 0, 3 * sizeof(float), st));
-    switch (ssim_loss_map_mode) {
-        case 1: return launch_loss_mode<1>(d_render, d_gt, n_images, height, width, w_l1, w_ssim, d_v_render, d_losses, ssim_loss_map_weight, d_loss_map, st);
-        case 2: return launch_loss_mode<2>(d_render, d_gt, n_images, height, width, w_l1, w_ssim, d_v_render, d_losses, ssim_loss_map_weight, d_loss_map, st);
-        case 3: return launch_loss_mode<3>(d_render, d_gt, n_images, height, width, w_l1, w_ssim, d_v_render, d_losses, ssim_loss_map_weight, d_loss_map, st);
-        default: return launch_loss_mode<0>(d_render, d_gt, n_images, height, width, w_l1, w_ssim, d_v_render, d_losses, 0.f, nullptr, st);
-    }
+    return launch_loss_map(d_render, d_gt, n_images, height, width, w_l1, w_ssim, d_v_render, d_losses, ssim_loss_map_mode, ssim_loss_map_weight,
+                           d_loss_map, st);
 }

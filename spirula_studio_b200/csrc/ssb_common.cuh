@@ -45,6 +45,8 @@ int check_cuda(cudaError_t e, const char* what);
 // launchers shared between translation units
 int launch_loss(const float* d_render, const float* d_gt, int B, int H, int W, float w_l1, float w_ssim,
                 float* d_v_render, float* d_losses, cudaStream_t st);
+int launch_loss_map(const float* d_render, const float* d_gt, int B, int H, int W, float w_l1, float w_ssim,
+                    float* d_v_render, float* d_losses, int map_mode, float map_weight, float* d_loss_map, cudaStream_t st);
 int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
                        SsbScreenRec* d_v_screen, const SsbSplats* grads, int accumulate, int clear_v_screen, void* stream);
 int launch_intersect_tiles(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,

@@ -34,6 +34,7 @@ struct SsbLane {
     int64_t* n_isects;    // device
     int32_t* offsets;     // [tiles]
     float* rgb; float* T; int32_t* last_ids; float* v_rgb;
+    float* loss_map;      // [P], only with ssb_step_set_densify
     cudaStream_t stream;
     cudaEvent_t bwd_done;  // this lane's last projection backward
     cudaEvent_t all_done;
@@ -54,6 +55,11 @@ struct SsbStep {
     int prof_views;                                   // views recorded and not yet read
     cudaEvent_t ev[SsbStep_kMaxProfViews][SSB_STAGE_COUNT + 1];
     int ev_ready;
+    // densification outputs (off unless ssb_step_set_densify switched them on)
+    int map_mode, accum_mode;
+    float map_weight;
+    float* accum_weight;
+    float* accum_weight_den;
 };
 
 namespace ssb {
@@ -77,7 +83,7 @@ static void lane_free(SsbLane& l) {
     cudaFree(l.aabb); cudaFree(l.depths); cudaFree(l.screen); cudaFree(l.v_screen);
     cudaFree(l.isect_ws); cudaFree(l.flat);
     cudaFree(l.n_isects); cudaFree(l.offsets);
-    cudaFree(l.rgb); cudaFree(l.T); cudaFree(l.last_ids); cudaFree(l.v_rgb);
+    cudaFree(l.rgb); cudaFree(l.T); cudaFree(l.last_ids); cudaFree(l.v_rgb); cudaFree(l.loss_map);
     if (l.stream) cudaStreamDestroy(l.stream);
     if (l.bwd_done) cudaEventDestroy(l.bwd_done);
     if (l.all_done) cudaEventDestroy(l.all_done);
@@ -137,10 +143,20 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
     if ((e = ssb_raster_fwd(l.screen, l.offsets, l.flat, l.n_isects, 1, W, H, l.rgb, nullptr, l.T, l.last_ids, st))) return e;
     SSB_MARK(5);
     if (gt_ready) SSB_CUDA(cudaStreamWaitEvent(st, gt_ready, 0));      // the view's target image has landed
-    if ((e = launch_loss(l.rgb, d_gt + (int64_t)v * P * 3, 1, H, W, s->cfg.w_l1, s->cfg.w_ssim, l.v_rgb, d_losses, st))) return e;
-    SSB_MARK(6);
-    if ((e = ssb_raster_bwd(l.screen, l.offsets, l.flat, l.n_isects, 1, W, H, nullptr, l.T, l.last_ids,
-                            l.v_rgb, nullptr, nullptr, l.v_screen, st))) return e;
+    if (s->accum_mode) {
+        // the view's SSIM loss map, then the backward pass that also folds it into the per-splat weights
+        SSB_CUDA(cudaMemsetAsync(l.loss_map, 0, P * sizeof(float), st));
+        if ((e = launch_loss_map(l.rgb, d_gt + (int64_t)v * P * 3, 1, H, W, s->cfg.w_l1, s->cfg.w_ssim, l.v_rgb, d_losses, s->map_mode,
+                                 s->map_weight, l.loss_map, st))) return e;
+        SSB_MARK(6);
+        if ((e = ssb_raster_bwd_accum(l.screen, l.offsets, l.flat, l.n_isects, 1, W, H, nullptr, l.T, l.last_ids, l.v_rgb, nullptr, nullptr,
+                                      l.v_screen, s->accum_mode, l.loss_map, n, nullptr, s->accum_weight, s->accum_weight_den, st))) return e;
+    } else {
+        if ((e = launch_loss(l.rgb, d_gt + (int64_t)v * P * 3, 1, H, W, s->cfg.w_l1, s->cfg.w_ssim, l.v_rgb, d_losses, st))) return e;
+        SSB_MARK(6);
+        if ((e = ssb_raster_bwd(l.screen, l.offsets, l.flat, l.n_isects, 1, W, H, nullptr, l.T, l.last_ids,
+                                l.v_rgb, nullptr, nullptr, l.v_screen, st))) return e;
+    }
     SSB_MARK(7);
     if (wait_before_bwd) SSB_CUDA(cudaStreamWaitEvent(st, wait_before_bwd, 0));
     if ((e = launch_project_bwd(params, shq, n, &cam, l.aabb, l.v_screen, grads, accumulate, 1, st))) return e;
@@ -152,6 +168,25 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
 }  // namespace ssb
 
 extern "C" {
+
+int ssb_step_set_densify(SsbStep* s, int32_t ssim_loss_map_mode, float ssim_loss_map_weight, int32_t accum_mode,
+                         float* d_accum_weight, float* d_accum_weight_den) {
+    using namespace ssb;
+    SSB_REQUIRE(s, "ssb_step_set_densify: NULL step");
+    SSB_REQUIRE(accum_mode >= SSB_ACCUM_NONE && accum_mode <= SSB_ACCUM_AVG, "ssb_step_set_densify: accum_mode %d is not a DensifyAccumMode", accum_mode);
+    if (accum_mode == SSB_ACCUM_NONE) { s->accum_mode = 0; return SSB_OK; }
+    SSB_REQUIRE(ssim_loss_map_mode >= 1 && ssim_loss_map_mode <= 3, "ssb_step_set_densify: ssim_loss_map_mode must be 1, 2 or 3 (got %d)", ssim_loss_map_mode);
+    SSB_REQUIRE(d_accum_weight && (accum_mode != SSB_ACCUM_AVG || d_accum_weight_den), "ssb_step_set_densify: output array missing");
+    const int64_t P = (int64_t)s->cfg.width * s->cfg.height;
+    for (int k = 0; k < s->n_lanes; ++k)
+        if (!s->lane[k].loss_map) {
+            int e = dev_alloc(&s->lane[k].loss_map, P, s->bytes);
+            if (e) return e;
+        }
+    s->map_mode = ssim_loss_map_mode; s->map_weight = ssim_loss_map_weight; s->accum_mode = accum_mode;
+    s->accum_weight = d_accum_weight; s->accum_weight_den = d_accum_weight_den;
+    return SSB_OK;
+}
 
 void ssb_step_destroy(SsbStep* s) {
     if (!s) return;

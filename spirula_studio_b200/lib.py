@@ -100,6 +100,7 @@ SIGNATURES = {
     "ssb_raster_bwd": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ssb_raster_bwd_accum": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _I32, _P, _I64, _P, _P, _P, _P]),
     "ssb_loss_l1_ssim_fwdbwd": (C.c_int, [_P, _P, _I32, _I32, _I32, _F, _F, _P, _P, _P]),
+    "ssb_step_set_densify": (C.c_int, [_P, _I32, _F, _I32, _P, _P]),
     "ssb_loss_l1_ssim_fwdbwd_map": (C.c_int, [_P, _P, _I32, _I32, _I32, _F, _F, _P, _P, _I32, _F, _P, _P]),
     "ssb_adam_step": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _P, _P]),
     "ssb_adam_step_sh_quantized": (C.c_int, [_P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _P, _P]),

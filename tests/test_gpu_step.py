@@ -216,6 +216,50 @@ def test_whole_iteration_matches_oracle(lib, U, oracle, quant):
     tr.close(); tr2.close()
 
 
+@pytest.mark.parametrize("mode", [L.SSB_ACCUM_MAX, L.SSB_ACCUM_AVG])
+def test_step_densification_outputs_match_oracle(lib, U, oracle, mode):
+    """ssb_step_set_densify: the per-splat weights the step accumulates over three views (two lanes running side by side)
+    against the oracle's loss map folded by the oracle's backward walk, and the gradients unchanged by the option."""
+    from spirula_studio_b200.trainer import Trainer
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=8000, width=176, height=128, n_views=3)
+    cfg.rig, cfg.rig_radius, cfg.log_scale_mu = "ring", 3.0, -3.0
+    sp = scenes.make_splats(cfg)
+    vm, K = scenes.make_cameras(cfg)
+    targets = np.stack([scenes.make_target(cfg, v) for v in range(cfg.n_views)])
+    W, H, n = cfg.width, cfg.height, cfg.n_splats
+    want, want_den = np.zeros(n, np.float64), np.zeros(n, np.float64)
+    for v in range(cfg.n_views):
+        ch = oracle.forward_chain(sp, vm[v:v + 1], K[v:v + 1], W, H)
+        lm = np.zeros(H * W, np.float32)
+        oracle.loss_l1_ssim_map(ch["render"]["rgb"], targets[v].reshape(-1, 3), 1, H, W, 2, 0.5, lm)
+        acc, den = oracle.raster_accum_weight(ch["proj"], ch["offsets"], ch["sorted_vals"], 1, n, W, H, ch["render"], lm, mode)
+        want = np.maximum(want, acc) if mode == L.SSB_ACCUM_MAX else want + acc
+        want_den += den
+    tr = Trainer(cfg, sp, device=U.DEV)
+    d_vm, d_K, d_gt = (torch.from_numpy(a).to(U.DEV) for a in (vm, K, targets))
+    tr.losses.zero_()
+    tr.views_fwd_bwd(d_vm, d_K, d_gt, cfg.n_views)
+    torch.cuda.synchronize()
+    base = {k: t.clone() for k, t in tr.grads.items()}
+    acc, den = torch.zeros(n, device=U.DEV), torch.zeros(n, device=U.DEV)
+    L.check(lib.ssb_step_set_densify(tr.handle, 2, 0.5, mode, L.ptr(acc), L.ptr(den)))
+    tr.views_fwd_bwd(d_vm, d_K, d_gt, cfg.n_views)
+    torch.cuda.synchronize()
+    assert (want > 0).sum() > n // 20
+    assert U.close_frac(acc.cpu().numpy(), want, 1e-5 * want.max(), 2e-3) <= 5e-3
+    if mode == L.SSB_ACCUM_AVG:
+        assert U.close_frac(den.cpu().numpy(), want_den, 1e-5 * want_den.max(), 2e-3) <= 5e-3
+    for k in base:
+        scale = float(base[k].abs().max())
+        assert float((tr.grads[k] - base[k]).abs().max()) <= 1e-4 * scale, k
+    L.check(lib.ssb_step_set_densify(tr.handle, 0, 0.0, L.SSB_ACCUM_NONE, None, None))     # and off again
+    acc.zero_()
+    tr.views_fwd_bwd(d_vm, d_K, d_gt, cfg.n_views)
+    torch.cuda.synchronize()
+    assert float(acc.abs().max()) == 0.0
+    tr.close()
+
+
 def test_wide_camera_iteration_matches_oracle(lib, U, oracle):
     """A batch that mixes equidistant-fisheye and equirectangular views of different sizes (the wide
     field-of-view configuration, scaled down): summed gradients and losses against the oracle."""

@@ -4,7 +4,8 @@ oracle/Makefile.ref) on a GPU, on small seeded scenes.
 
     python tests/golden/make_golden.py [out_dir [fixture ...]]
 
-With fixture names (ring2, dense1, wide_fisheye, wide_equirect, ssim, adam) only those are written.
+With fixture names (ring2, dense1, wide_fisheye, wide_equisolid, wide_equirect, ssim, ssim_map, adam, accum) only those
+are written; accum reads the committed ring2.npz and dense1.npz.
 
 Inputs are not stored: they are regenerated from `golden_cases.py` (same seeds).
 Every stage is run stage-isolated on the reference's own upstream outputs, so a

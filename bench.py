@@ -49,9 +49,10 @@ UNIT = "iters/s"
 WORKLOAD = "mid_1m"
 
 
-# DRAM bytes one launch moves (dram__bytes_read.sum + dram__bytes_write.sum), from one ncu pass over this
-# file's own command on the mid_1m workload, one view per launch (a stage of several kernels: their sum).
-# The capture and its command are summarised in profiles/all_kernels_mid1m_counters.md.
+# DRAM bytes one launch moves (dram__bytes_read.sum + dram__bytes_write.sum): RECORDED CONSTANTS from one ncu
+# pass over this file's own command on the mid_1m workload, one view per launch (a stage of several kernels:
+# their sum).  They are not measured by the run that prints them (a profiler cannot run inside a timed
+# benchmark); the JSON line says so in `traffic_source`.
 NCU_TRAFFIC_MID1M = {"project_fwd": 184.3e6, "tile_keys": 190.5e6, "sort": 35.6e6, "raster_fwd": 68.6e6,
                      "loss": 51.9e6, "raster_bwd": 111.3e6, "project_bwd": 430.5e6, "adam": 846.8e6}
 
@@ -180,9 +181,11 @@ def oracle_adam_seconds(cfg, splats, grads, state, step, shq):
 
 
 def cpu_port_run(cfg, steps, warmup):
-    """Times the CPU restatement: each step = one view of the batch (all stages) + one Adam pass."""
+    """Times the CPU restatement: each step = one view of the batch (all stages) + one Adam pass.
+    Uses every host core whatever OMP_NUM_THREADS says (launchers such as torchrun set it to 1)."""
     from oracle import pyoracle as O
     from spirula_studio_b200 import scenes
+    O.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     splats = scenes.make_splats(cfg)
     vm, K = scenes.make_cameras(cfg)
     shq = None
@@ -279,7 +282,8 @@ def run_ours(args, cfg, rank, world, local_rank):
     # ---- device-resident timing -------------------------------------------
     for _ in range(args.warmup):
         tr.step_device_kinds(resident, total_views)
-    pairs = tr.last_isects() if resident[0][4] > 0 else 0          # also verifies the pair capacity was enough
+    pairs = tr.last_isects() if resident[0][4] > 0 else 0
+    tr.check_capacity()                                            # raises if any view outgrew the pair capacity
     sampler = ClockSampler(local_rank) if rank == 0 else None
     barrier()
     launches0 = lib.ssb_launch_count()
@@ -381,7 +385,9 @@ def run_ours(args, cfg, rank, world, local_rank):
             for k, t in NCU_TRAFFIC_MID1M.items():
                 kernels[k]["dram_traffic"] = int(t)
         roof = {"kernel": dom, "bound": "hbm", "achieved": kernels[dom]["gbs"], "peak": peak, "unit": "GB/s", "frac": kernels[dom]["frac_of_hbm"],
-                "traffic": int(NCU_TRAFFIC_MID1M[dom]) if full_size else None, "peak_source": f"{peak_kind} copy bandwidth",
+                "traffic": int(NCU_TRAFFIC_MID1M[dom]) if full_size else None,
+                "traffic_source": "recorded constant from an earlier ncu capture of this command, not measured by this run" if full_size else None,
+                "peak_source": f"{peak_kind} copy bandwidth",
                 "note": "the raster kernels are bound by instruction issue (79-88 % of issue slots busy, DRAM at 1-2 % of peak, traffic below "
                         "the algorithmic bytes because a view's working set stays in L2); the HBM fraction is reported because the schema asks "
                         "for one; the HBM-bound stages carry their own fractions in `kernels`"}
@@ -409,6 +415,28 @@ def run_ours(args, cfg, rank, world, local_rank):
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
                                     "sample": f"2 of {cfg.n_views} views at full size through every stage ({t_view:.2f} s each) and 2 Adam passes "
                                               f"({t_adam:.2f} s each); iteration time = {cfg.n_views} x view + Adam"}
+        if world == 1 and not args.no_ref_cuda:
+            # the reference's own CUDA kernels on this GPU, same scene, per stage (test-side leg, after the timed region)
+            from oracle import ref_timing
+            if ref_timing.available():
+                tr.close()
+                torch.cuda.empty_cache()
+                rt = ref_timing.time_kernels(cfg, n_views=min(cfg.n_views, 4), repeats=2, device=dev, with_ours=False)
+                line["reference_cuda_kernels"] = rt
+                rm = rt["reference_ms"]
+                for ours_name, ref_name in (("project_fwd", "project_fwd"), ("raster_fwd", "raster_fwd"), ("loss", "loss_ssim"),
+                                            ("raster_bwd", "raster_bwd"), ("project_bwd", "project_bwd")):
+                    kernels[ours_name]["ref_ms"] = rm[ref_name]
+                kernels["tile_keys"]["ref_ms"] = rm["intersect"]       # the reference's whole intersection, against tile_keys + sort here
+                kernels["sort"]["ref_ms"] = 0.0
+                kernels["adam"]["ref_ms"] = rt["reference_ms_adam"]
+                line["vs_reference_cuda_kernels"] = {
+                    "reference_ms_per_iteration": rt["reference_ms_per_iteration"], "ours_ms_per_iteration": ms_step,
+                    "ratio": rt["reference_ms_per_iteration"] / ms_step,
+                    "note": "sum of the reference's kernel times (its L1 loss kernel, gradient zeroing and host work excluded) over this "
+                            "library's measured iteration time"}
+            else:
+                line["reference_cuda_kernels"] = {"unavailable": "oracle/_ref/libssb_ref.so is not built on this machine"}
         emit(line)
     tr.close()
     if world > 1:
@@ -425,6 +453,7 @@ def main():
     ap.add_argument("--splats", type=int, default=0, help="override the splat count (smaller cases for profiling)")
     ap.add_argument("--views", type=int, default=0, help="override the views per iteration")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference's CUDA kernels after the run")
     args = ap.parse_args()
     claim_stdout()
     from spirula_studio_b200 import scenes

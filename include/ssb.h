@@ -86,6 +86,17 @@ typedef struct SsbCameras {
 typedef struct SsbScreenRec { float a[4], b[4], c[4]; } SsbScreenRec;
 
 const char* ssb_last_error_string(void);
+
+/* Kernels of this library never follow an index out of the buffers they were given.  When one meets
+ * such an index (a tile range or list entry beyond the list's capacity, a record index beyond the
+ * record array) it skips the entry and sets a bit in a sticky per-device status word; when the tile
+ * intersection finds more pairs than the caller's buffers hold it drops the excess, clamps every
+ * range it hands on and sets another.  ssb_device_status copies the word of the current device to
+ * *h_bits (may be NULL), clears it, synchronises the stream and returns SSB_ERR_INVALID_ARGUMENT
+ * (bad index), SSB_ERR_CAPACITY (pairs dropped) or SSB_OK.  The reference has no counterpart: it
+ * sizes its buffers from the pair count read back to the host (src/kernels/tile/IntersectTile.cu:432-459). */
+enum { SSB_STATUS_BAD_INDEX = 1, SSB_STATUS_PAIRS_DROPPED = 2 };
+int ssb_device_status(int32_t* h_bits, void* stream);
 /* "major.minor" of the ABI and the compute capability the kernels were built for. */
 const char* ssb_version_string(void);
 
@@ -181,8 +192,9 @@ int ssb_sort_pairs_u64(int64_t* d_keys_a, int32_t* d_vals_a, int64_t* d_keys_b, 
 
 /* Reports SSB_ERR_CUDA if a tile of the last sort that used this workspace gave
  * up waiting for its predecessor (every device-side wait in the sort is bounded;
- * the output is then not sorted).  Synchronises the stream.  No reference
- * counterpart: cub's sort has no such status. */
+ * the output is then not sorted).  Synchronises the stream.  d_workspace == NULL
+ * names the built-in scratch of ssb_sort_pairs_u64_noalloc on the current device.
+ * No reference counterpart: cub's sort has no such status. */
 int ssb_sort_check(const void* d_workspace, void* stream);
 
 /* The same sort with NO workspace argument and no allocation anywhere: its scratch
@@ -193,7 +205,10 @@ int ssb_sort_check(const void* d_workspace, void* stream);
  * sort: plug-ins whose host forbids cudaMalloc, or loops where an allocation's
  * device-wide synchronisation would stall other streams.
  *  - capacity may be at most 2^20 = 1,048,576 pairs; larger requests return
- *    SSB_ERR_CAPACITY and touch nothing.
+ *    SSB_ERR_CAPACITY and touch nothing (a negative one, SSB_ERR_INVALID_ARGUMENT).
+ *  - Whether a bounded wait inside the sort gave up (the output is then unsorted) is
+ *    read with ssb_sort_check(NULL, stream): the caller holds no workspace pointer to
+ *    pass, so NULL stands for the built-in array of the current device.
  *  - The first call on each device looks up the array's device address (with that
  *    device current); make that first call before starting any stream capture.
  *  - All calls on a device share the one array, whose contents survive from call
@@ -215,7 +230,9 @@ int32_t ssb_tile_n_bits(int64_t n_tiles);
  * is sorted on (depth bits, pair index) by one CTA.  total must be a whole number of images of
  * n_per_image pairs.  d_isect_ids may be NULL when the sorted keys are not needed.  d_tile_offsets
  * receives n_images * tiles entries (range end of the last tile = *d_n_isects, as for
- * ssb_tile_ranges).  Pairs beyond capacity are dropped; *d_n_isects still reports the full count.
+ * ssb_tile_ranges).  Pairs beyond capacity are dropped: *d_n_isects still reports the full count, but every
+ * entry of d_tile_offsets is clamped to capacity, so the lists that lie below it are complete, the list that
+ * straddles it is cut, and later tiles are empty (SSB_STATUS_PAIRS_DROPPED is raised, see ssb_device_status).
  * Workspace: ssb_intersect_tiles_workspace_bytes(n_images * tiles, capacity). */
 int64_t ssb_intersect_tiles_workspace_bytes(int64_t n_tiles_total, int64_t capacity);
 int ssb_intersect_tiles(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
@@ -244,8 +261,12 @@ int ssb_tile_ranges(const int64_t* d_sorted_ids, const int64_t* d_n, int64_t cap
 /* Replaces rasterize_to_pixels_3dgs_fwd (src/kernels/raster/RasterizationFwd.cu:147-185,
  * kernel src/kernels/raster/RasterizationEval3DFwd_kernel.cuh:48-313, 2D variant).
  * Outputs: d_rgb [I][H][W][3], d_depth [I][H][W], d_T [I][H][W], d_last_ids [I][H][W].
- * d_depth may be NULL when the depth image is not needed (its accumulation is then compiled out). */
-int ssb_raster_fwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids,
+ * d_depth may be NULL when the depth image is not needed (its accumulation is then compiled out).
+ * n_records = entries of d_screen, n_flatten = entries of d_flatten_ids (the reference's tensors carry
+ * their sizes; here they bound every access): tile ranges are clamped to min(*d_n_isects, n_flatten) and a
+ * list entry that is not a record index below n_records is skipped and reported (ssb_device_status). */
+int ssb_raster_fwd(const SsbScreenRec* d_screen, int64_t n_records, const int32_t* d_tile_offsets,
+                   const int32_t* d_flatten_ids, int64_t n_flatten,
                    const int64_t* d_n_isects, int32_t n_images, int32_t width, int32_t height,
                    float* d_rgb, float* d_depth, float* d_T, int32_t* d_last_ids, void* stream);
 
@@ -253,8 +274,10 @@ int ssb_raster_fwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, 
  * kernel src/kernels/raster/RasterizationEval3DBwd_kernel.cuh:48-636, 2D variant).
  * d_v_depth and d_v_T may be NULL (treated as zero; without d_v_depth the depth channel is compiled
  * out and d_render_depth may be NULL too).  Gradients are ADDED into
- * d_v_screen [pairs] (layout as in ssb_project_bwd); the caller zeroes it. */
-int ssb_raster_bwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids,
+ * d_v_screen [n_records] (layout as in ssb_project_bwd); the caller zeroes it.
+ * n_records and n_flatten bound every access as in ssb_raster_fwd; d_last_ids entries are clamped too. */
+int ssb_raster_bwd(const SsbScreenRec* d_screen, int64_t n_records, const int32_t* d_tile_offsets,
+                   const int32_t* d_flatten_ids, int64_t n_flatten,
                    const int64_t* d_n_isects, int32_t n_images, int32_t width, int32_t height,
                    const float* d_render_depth, const float* d_T, const int32_t* d_last_ids,
                    const float* d_v_rgb, const float* d_v_depth, const float* d_v_T,
@@ -272,7 +295,8 @@ enum { SSB_ACCUM_NONE = 0, SSB_ACCUM_MAX = 1, SSB_ACCUM_SUM = 2, SSB_ACCUM_AVG =
  * d_accum_weight[splat] (atomic max / add; the caller zeroes it), where splat = d_gaussian_ids[record]
  * (packed projection) or record index % n_per_image when d_gaussian_ids is NULL.
  * accum_mode = SSB_ACCUM_NONE is ssb_raster_bwd. */
-int ssb_raster_bwd_accum(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids,
+int ssb_raster_bwd_accum(const SsbScreenRec* d_screen, int64_t n_records, const int32_t* d_tile_offsets,
+                         const int32_t* d_flatten_ids, int64_t n_flatten,
                          const int64_t* d_n_isects, int32_t n_images, int32_t width, int32_t height,
                          const float* d_render_depth, const float* d_T, const int32_t* d_last_ids,
                          const float* d_v_rgb, const float* d_v_depth, const float* d_v_T, SsbScreenRec* d_v_screen,
@@ -471,6 +495,18 @@ int ssb_step_views_gated(SsbStep* step, const SsbSplats* params, const SsbShQuan
 /* Pair count M of the last view processed (host copy taken after that view's
  * kernels finished; synchronises the stream). */
 int ssb_step_last_isects(SsbStep* step, int64_t* h_n_isects, void* stream);
+
+/* The largest per-view pair count since the step was created or this word was last cleared, kept on the
+ * device so that an iteration needs no host synchronisation to stay safe: a view with more pairs than
+ * isect_capacity renders from clamped lists (ssb_intersect_tiles) and the count shows it.
+ * ssb_step_max_pairs_device returns the device address of that int64 (valid for the step's lifetime) so a
+ * caller can copy it to the host together with its loss scalars; ssb_step_status copies it to *h_max_pairs
+ * (may be NULL), clears it when `reset` != 0, synchronises the stream and returns SSB_ERR_CAPACITY when a
+ * view exceeded the capacity.  The reference needs neither: it reads M back every view and sizes its
+ * buffers exactly (src/kernels/tile/IntersectTile.cu:432-459). */
+const int64_t* ssb_step_max_pairs_device(const SsbStep* step);
+int64_t ssb_step_isect_capacity(const SsbStep* step);
+int ssb_step_status(SsbStep* step, int64_t* h_max_pairs, int reset, void* stream);
 
 /* Device buffers of the last view, for inspection by tests: any pointer may be
  * NULL.  Valid until the next ssb_step_views / ssb_step_destroy. */

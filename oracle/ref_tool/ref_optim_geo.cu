@@ -3,6 +3,7 @@
 // fused_optim_3dgs_geometry does (:447-468), fp32 state.  ref_adam_geometry: every regulariser
 // weight zero, no scale-agnostic mean, scalar step; ref_adam_geometry_ex: those three switched on.
 #include "kernels/optim/FusedGeometryOptim.cu"
+#include "ref_sync.h"
 
 extern "C" int ref_adam_geometry(
     int64_t N, int step, float grad_scale, int zero_grad, float lr_means, float lr_quats, float lr_scales, float lr_opacs,
@@ -25,7 +26,7 @@ extern "C" int ref_adam_geometry(
     };
     if (zero_grad) launch(fused_optim_3dgs_geometry_kernel<false, true, false>);
     else launch(fused_optim_3dgs_geometry_kernel<false, false, false>);
-    return (int)cudaDeviceSynchronize();
+    return ref_finish();
 }
 
 // reg = max_gauss_ratio, scale_regularization, mcmc_opacity, mcmc_scale, erank, erank_s3, quat_norm (undivided,
@@ -58,5 +59,5 @@ extern "C" int ref_adam_geometry_ex(
         if (zero_grad) launch(fused_optim_3dgs_geometry_kernel<false, true, false>);
         else launch(fused_optim_3dgs_geometry_kernel<false, false, false>);
     }
-    return (int)cudaDeviceSynchronize();
+    return ref_finish();
 }

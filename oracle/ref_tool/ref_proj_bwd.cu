@@ -5,6 +5,7 @@
 #include "primitives/Primitive3DGS.cuh"
 #include "kernels/projection/ProjectionBwd_kernel.cuh"
 #include "ref_common.cuh"
+#include "ref_sync.h"
 
 extern "C" int ref_project_bwd(
     uint32_t C, uint32_t N, uint32_t W, uint32_t H,
@@ -20,5 +21,5 @@ extern "C" int ref_project_bwd(
         0, C, N, world, viewmats, (const float4*)intrins, CameraDistortionCoeffsBuffer((float*)nullptr), W, H,
         nullptr, nullptr, (const float4*)aabb, v_screen, grads, nullptr,
         sh_packed, (const float2*)sh_bounds, 15, sh_bits, sh_stride);
-    return (int)cudaDeviceSynchronize();
+    return ref_finish();
 }

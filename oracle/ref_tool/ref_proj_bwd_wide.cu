@@ -6,6 +6,7 @@
 #include "primitives/Primitive3DGS.cuh"
 #include "kernels/projection/ProjectionBwd_kernel.cuh"
 #include "ref_common.cuh"
+#include "ref_sync.h"
 
 template <CameraModelType MODEL>
 static void run_bwd(uint32_t C, uint32_t N, uint32_t W, uint32_t H, RawWorld& world, const float* viewmats, const float* intrins,
@@ -35,5 +36,5 @@ extern "C" int ref_project_bwd_model(
         run_bwd<CameraModelType::EQUIRECTANGULAR>(C, N, W, H, world, viewmats, intrins, aabb, v_screen, grads, sh_packed, sh_bounds, sh_bits, sh_stride);
     else
         return -1;
-    return (int)cudaDeviceSynchronize();
+    return ref_finish();
 }

@@ -5,6 +5,7 @@
 #include "primitives/Primitive3DGS.cuh"
 #include "kernels/projection/ProjectionFwd_kernel.cuh"
 #include "ref_common.cuh"
+#include "ref_sync.h"
 
 extern "C" int ref_project_fwd(
     uint32_t C, uint32_t N, uint32_t W, uint32_t H,
@@ -18,5 +19,5 @@ extern "C" int ref_project_fwd(
     projection_fused_fwd_kernel_wrapper<RefPrim, CameraModelType::PINHOLE, CameraDistortionType::None>(
         0, C, N, world, viewmats, (const float4*)intrins, CameraDistortionCoeffsBuffer((float*)nullptr), W, H,
         (float4*)aabb, depths, radii, screen, sh_packed, (const float2*)sh_bounds, 15, sh_bits, sh_stride);
-    return (int)cudaDeviceSynchronize();
+    return ref_finish();
 }

@@ -7,6 +7,7 @@
 #include "primitives/Primitive3DGS.cuh"
 #include "kernels/projection/ProjectionFwd_kernel.cuh"
 #include "ref_common.cuh"
+#include "ref_sync.h"
 
 template <CameraModelType MODEL>
 static void run_fwd(uint32_t C, uint32_t N, uint32_t W, uint32_t H, RawWorld& world, const float* viewmats, const float* intrins,
@@ -34,5 +35,5 @@ extern "C" int ref_project_fwd_model(
         run_fwd<CameraModelType::EQUIRECTANGULAR>(C, N, W, H, world, viewmats, intrins, aabb, depths, radii, screen, sh_packed, sh_bounds, sh_bits, sh_stride);
     else
         return -1;
-    return (int)cudaDeviceSynchronize();
+    return ref_finish();
 }

@@ -5,6 +5,7 @@
 #include "primitives/Primitive3DGS.cuh"
 #include "kernels/raster/RasterizationBwd_kernel.cuh"
 #include "ref_common.cuh"
+#include "ref_sync.h"
 
 extern "C" int ref_raster_bwd(
     uint32_t I, uint32_t N, uint32_t n_isects, uint32_t W, uint32_t H,
@@ -24,7 +25,7 @@ extern "C" int ref_raster_bwd(
         0, I, N, n_isects, nullptr, world, screen, W, H, tw, th, tile_offsets, flatten_ids,
         render_T, last_ids, out, dist, nullptr, nullptr, v_out, v_render_T, nullptr, v_dist,
         v_world, v_screen, nullptr, nullptr);
-    return (int)cudaDeviceSynchronize();
+    return ref_finish();
 }
 
 // The same launch with a densification weight map: mode 1 = Max, 2 = Sum, 3 = Avg (DensifyAccumMode,
@@ -53,5 +54,5 @@ extern "C" int ref_raster_bwd_accum(
     else if (mode == 2) REF_BWD_ACCUM(DensifyAccumMode::Sum);
     else REF_BWD_ACCUM(DensifyAccumMode::Avg);
 #undef REF_BWD_ACCUM
-    return (int)cudaDeviceSynchronize();
+    return ref_finish();
 }

@@ -5,6 +5,7 @@
 #include "primitives/Primitive3DGS.cuh"
 #include "kernels/raster/RasterizationFwd_kernel.cuh"
 #include "ref_common.cuh"
+#include "ref_sync.h"
 
 extern "C" int ref_raster_fwd(
     uint32_t I, uint32_t N, uint32_t n_isects, uint32_t W, uint32_t H,
@@ -18,5 +19,5 @@ extern "C" int ref_raster_fwd(
     uint32_t tw = (W + 15) / 16, th = (H + 15) / 16;
     rasterize_to_pixels_fwd_kernel_wrapper<RefPrim, DistortionType::None, false>(
         0, I, N, n_isects, nullptr, world, screen, W, H, tw, th, tile_offsets, flatten_ids, out, out_T, last_ids, dist, nullptr);
-    return (int)cudaDeviceSynchronize();
+    return ref_finish();
 }

@@ -3,12 +3,13 @@
 // (:1163-1176) with no mask and no loss map: adds the SSIM gradient into dL_dimg1
 // and the mean SSIM into *ssim_out.
 #include "kernels/loss/FusedSSIM.cu"
+#include "ref_sync.h"
 
 extern "C" int ref_ssim_inplace(int B, int H, int W, const float* img1, const float* img2, float dL_dmap, float* dL_dimg1, float* ssim_out) {
     cudaMemset(ssim_out, 0, sizeof(float));
     memory_efficient_ssim_backward_kernel<true><<<_LAUNCH_ARGS_3D(W, H, B, BLOCK_X_ME, BLOCK_Y_ME, 1)>>>(
         B, H, W, (const float3*)img1, (const float3*)img2, nullptr, 0, 0, 0, nullptr, dL_dmap, (float3*)dL_dimg1, ssim_out, 0.0f, nullptr, 0);
-    return (int)cudaDeviceSynchronize();
+    return ref_finish();
 }
 
 // The same launch with the densification loss map (fused_ssim_inplace_async's ssim_loss_map arguments, :1211-1234):
@@ -18,5 +19,5 @@ extern "C" int ref_ssim_inplace_map(int B, int H, int W, const float* img1, cons
     cudaMemset(ssim_out, 0, sizeof(float));
     memory_efficient_ssim_backward_kernel<true><<<_LAUNCH_ARGS_3D(W, H, B, BLOCK_X_ME, BLOCK_Y_ME, 1)>>>(
         B, H, W, (const float3*)img1, (const float3*)img2, nullptr, 0, 0, 0, nullptr, dL_dmap, (float3*)dL_dimg1, ssim_out, map_weight, loss_map, mode);
-    return (int)cudaDeviceSynchronize();
+    return ref_finish();
 }

@@ -241,11 +241,7 @@ __global__ void __launch_bounds__(kLossThreads) loss_l1_ssim_kernel(
 template <int MAP_MODE>
 static int launch_loss_mode(const float* d_render, const float* d_gt, int B, int H, int W, float w_l1, float w_ssim,
                             float* d_v_render, float* d_losses, float map_weight, float* d_loss_map, cudaStream_t st) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        SSB_CUDA(cudaFuncSetAttribute(loss_l1_ssim_kernel<MAP_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kLossSmemBytes));
-        attr_set = true;
-    }
+    if (int e = ensure_dynamic_smem((const void*)loss_l1_ssim_kernel<MAP_MODE>, kLossSmemBytes)) return e;
     dim3 grid((unsigned)ceil_div(W, kLossTile), (unsigned)ceil_div(H, kLossTile), (unsigned)B);
     loss_l1_ssim_kernel<MAP_MODE><<<grid, kLossThreads, kLossSmemBytes, st>>>(d_render, d_gt, B, H, W, w_l1, w_ssim, d_v_render, d_losses,
                                                                               map_weight, d_loss_map);

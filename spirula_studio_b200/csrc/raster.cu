@@ -62,10 +62,29 @@ __device__ __forceinline__ bool ellipse_reaches_box(float4 b, float x0, float x1
     return ellipse_test(ellipse_test_setup(b), x0, x1, y0, y1);
 }
 
+// What bounds a kernel's walk over the sorted list: the entries the list buffer holds, the records the
+// record array holds, and where to report an entry that had to be skipped.
+struct ListBounds {
+    int32_t n_flatten;
+    uint32_t n_records;
+    unsigned int* status;
+};
+
+__device__ __forceinline__ int32_t list_length(const int64_t* __restrict__ n_isects_ptr, const ListBounds& lb) {
+    const int64_t m = *n_isects_ptr;
+    return (int32_t)(m < 0 ? 0 : (m > lb.n_flatten ? lb.n_flatten : m));
+}
+__device__ __forceinline__ int32_t clamp_range(int32_t v, int32_t list_len) { return min(max(v, 0), list_len); }
+__device__ __forceinline__ bool record_ok(int32_t g, const ListBounds& lb) {
+    if ((uint32_t)g < lb.n_records) return true;
+    if (lb.status) atomicOr(lb.status, (unsigned int)SSB_STATUS_BAD_INDEX);
+    return false;
+}
+
 template <bool DEPTH>
 __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
     const SsbScreenRec* __restrict__ screen, const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ flatten_ids,
-    const int64_t* __restrict__ n_isects_ptr, int I, int W, int H, int tw, int th,
+    const int64_t* __restrict__ n_isects_ptr, ListBounds lb, int I, int W, int H, int tw, int th,
     float* __restrict__ out_rgb, float* __restrict__ out_depth, float* __restrict__ out_T, int32_t* __restrict__ last_ids) {
     __shared__ float4 sA[kFwdThreads], sC[kFwdThreads], sQ[kFwdThreads], sE[kFwdThreads];
     __shared__ float sEw[kFwdThreads];
@@ -81,8 +100,9 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
     bool done = !inside;
 
     const int32_t* offs = tile_offsets + (int64_t)img * tw * th;
-    const int32_t range_start = offs[tile_id];
-    const int32_t range_end = (img == I - 1 && tile_id == tw * th - 1) ? (int32_t)*n_isects_ptr : offs[tile_id + 1];
+    const int32_t list_len = list_length(n_isects_ptr, lb);
+    const int32_t range_start = clamp_range(offs[tile_id], list_len);
+    const int32_t range_end = (img == I - 1 && tile_id == tw * th - 1) ? list_len : clamp_range(offs[tile_id + 1], list_len);
 
     float T = 1.0f;
     float acc_r = 0.f, acc_g = 0.f, acc_b = 0.f, acc_d = 0.f;
@@ -93,12 +113,16 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
         if (__syncthreads_count(done) >= kFwdThreads) break;
         const int batch = min(kFwdThreads, range_end - batch_start);
         if ((int)threadIdx.x < batch) {
-            int32_t g = flatten_ids[batch_start + threadIdx.x];
-            const float4* r = (const float4*)(screen + g);
-            sA[threadIdx.x] = r[0]; sC[threadIdx.x] = r[2];
+            const int32_t g = flatten_ids[batch_start + threadIdx.x];
+            // an entry that names no record is staged as a splat nothing can reach
+            float4 ra = make_float4(-1e30f, -1e30f, 0.f, 0.f), b = make_float4(1.f, 0.f, 1.f, 1.f), rc = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (record_ok(g, lb)) {
+                const float4* r = (const float4*)(screen + g);
+                ra = r[0]; b = r[1]; rc = r[2];
+            }
+            sA[threadIdx.x] = ra; sC[threadIdx.x] = rc;
             // conic pre-scaled so that exp(-sigma) = 2^(-q), q = A dx^2 + B dx dy + C dy^2
             const float kLog2e = 1.4426950408889634f;
-            const float4 b = r[1];
             sQ[threadIdx.x] = make_float4(0.5f * kLog2e * b.x, kLog2e * b.y, 0.5f * kLog2e * b.z, b.w);
             // and the per-record part of the ellipse-vs-rectangle test, shared by the eight warps
             const EllipseTest et = ellipse_test_setup(b);
@@ -176,7 +200,7 @@ struct BwdAccum {
 template <bool DEPTH, int ACCUM>
 __global__ void __launch_bounds__(kBwdWarps * 32, ACCUM ? 8 : 10) raster_bwd_kernel(
     const SsbScreenRec* __restrict__ screen, const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ flatten_ids,
-    const int64_t* __restrict__ n_isects_ptr, int I, int W, int H, int tw, int th,
+    const int64_t* __restrict__ n_isects_ptr, ListBounds lb, int I, int W, int H, int tw, int th,
     const float* __restrict__ render_depth, const float* __restrict__ render_T, const int32_t* __restrict__ last_ids,
     const float* __restrict__ v_rgb, const float* __restrict__ v_depth, const float* __restrict__ v_T,
     SsbScreenRec* __restrict__ v_screen, BwdAccum acc) {
@@ -194,8 +218,9 @@ __global__ void __launch_bounds__(kBwdWarps * 32, ACCUM ? 8 : 10) raster_bwd_ker
     if (mx0 >= W || my0 >= H) return;     // whole micro-tile outside the image (warp-uniform)
 
     const int32_t* offs = tile_offsets + (int64_t)img * tw * th;
-    const int32_t range_start = offs[tile_id];
-    const int32_t range_end = (img == I - 1 && tile_id == tw * th - 1) ? (int32_t)*n_isects_ptr : offs[tile_id + 1];
+    const int32_t list_len = list_length(n_isects_ptr, lb);
+    const int32_t range_start = clamp_range(offs[tile_id], list_len);
+    const int32_t range_end = (img == I - 1 && tile_id == tw * th - 1) ? list_len : clamp_range(offs[tile_id + 1], list_len);
 
     int32_t max_last = -1;
 #pragma unroll
@@ -237,8 +262,7 @@ __global__ void __launch_bounds__(kBwdWarps * 32, ACCUM ? 8 : 10) raster_bwd_ker
             const int32_t gi = scan - lane;
             bool ok = false;
             int32_t g = 0;
-            if (gi >= range_start) {
-                g = flatten_ids[gi];
+            if (gi >= range_start && record_ok(g = flatten_ids[gi], lb)) {
                 const float4* r = (const float4*)(screen + g);
                 const float4 a = r[0];
                 ok = (a.x + a.z >= fx0) && (a.x - a.z <= fx1) && (a.y + a.w >= fy0) && (a.y - a.w <= fy1);
@@ -334,15 +358,24 @@ __global__ void __launch_bounds__(kBwdWarps * 32, ACCUM ? 8 : 10) raster_bwd_ker
     }
 }
 
-static int launch_raster_bwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids, const int64_t* d_n_isects,
+static ListBounds make_bounds(int64_t n_records, int64_t n_flatten) {
+    ListBounds lb;
+    lb.n_flatten = (int32_t)(n_flatten > 0x7fffffff ? 0x7fffffff : n_flatten);
+    lb.n_records = (uint32_t)(n_records > 0x7fffffff ? 0x7fffffff : n_records);
+    lb.status = device_status_word();
+    return lb;
+}
+
+static int launch_raster_bwd(const SsbScreenRec* d_screen, int64_t n_records, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids, int64_t n_flatten, const int64_t* d_n_isects,
                              int32_t n_images, int32_t width, int32_t height, const float* d_render_depth, const float* d_T,
                              const int32_t* d_last_ids, const float* d_v_rgb, const float* d_v_depth, const float* d_v_T,
                              SsbScreenRec* d_v_screen, int accum_mode, BwdAccum acc, void* stream) {
     const int tw = (width + kTile - 1) / kTile, th = (height + kTile - 1) / kTile;
     const dim3 grid(tw, th, n_images);
+    const ListBounds lb = make_bounds(n_records, n_flatten);
 #define SSB_RBWD(DEPTH, ACCUM) \
     raster_bwd_kernel<DEPTH, ACCUM><<<grid, kBwdWarps * 32, 0, (cudaStream_t)stream>>>( \
-        d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height, tw, th, d_render_depth, d_T, d_last_ids, d_v_rgb, \
+        d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, lb, n_images, width, height, tw, th, d_render_depth, d_T, d_last_ids, d_v_rgb, \
         DEPTH ? d_v_depth : nullptr, d_v_T, d_v_screen, acc)
     // without a depth cotangent the depth channel carries exact zeros: that arithmetic is compiled out
     if (d_v_depth) {
@@ -359,26 +392,29 @@ static int launch_raster_bwd(const SsbScreenRec* d_screen, const int32_t* d_tile
 
 extern "C" {
 
-int ssb_raster_fwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids,
+int ssb_raster_fwd(const SsbScreenRec* d_screen, int64_t n_records, const int32_t* d_tile_offsets,
+                   const int32_t* d_flatten_ids, int64_t n_flatten,
                    const int64_t* d_n_isects, int32_t n_images, int32_t width, int32_t height,
                    float* d_rgb, float* d_depth, float* d_T, int32_t* d_last_ids, void* stream) {
     using namespace ssb;
     SSB_REQUIRE(d_screen && d_tile_offsets && d_flatten_ids && d_n_isects && d_rgb && d_T && d_last_ids, "ssb_raster_fwd: NULL argument");
-    SSB_REQUIRE(n_images >= 0 && width > 0 && height > 0, "ssb_raster_fwd: bad sizes");
+    SSB_REQUIRE(n_images >= 0 && width > 0 && height > 0 && n_records >= 0 && n_flatten >= 0, "ssb_raster_fwd: bad sizes");
     if (n_images == 0) return SSB_OK;
     int tw = (width + kTile - 1) / kTile, th = (height + kTile - 1) / kTile;
     dim3 grid(tw, th, n_images);
+    const ListBounds lb = make_bounds(n_records, n_flatten);
     if (d_depth)
-        raster_fwd_kernel<true><<<grid, kFwdThreads, 0, (cudaStream_t)stream>>>(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height,
+        raster_fwd_kernel<true><<<grid, kFwdThreads, 0, (cudaStream_t)stream>>>(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, lb, n_images, width, height,
                                                                               tw, th, d_rgb, d_depth, d_T, d_last_ids);
     else
-        raster_fwd_kernel<false><<<grid, kFwdThreads, 0, (cudaStream_t)stream>>>(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height,
+        raster_fwd_kernel<false><<<grid, kFwdThreads, 0, (cudaStream_t)stream>>>(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, lb, n_images, width, height,
                                                                                tw, th, d_rgb, nullptr, d_T, d_last_ids);
     SSB_LAUNCHED("raster_fwd_kernel");
     return SSB_OK;
 }
 
-int ssb_raster_bwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids,
+int ssb_raster_bwd(const SsbScreenRec* d_screen, int64_t n_records, const int32_t* d_tile_offsets,
+                   const int32_t* d_flatten_ids, int64_t n_flatten,
                    const int64_t* d_n_isects, int32_t n_images, int32_t width, int32_t height,
                    const float* d_render_depth, const float* d_T, const int32_t* d_last_ids,
                    const float* d_v_rgb, const float* d_v_depth, const float* d_v_T,
@@ -386,13 +422,14 @@ int ssb_raster_bwd(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, 
     using namespace ssb;
     SSB_REQUIRE(d_screen && d_tile_offsets && d_flatten_ids && d_n_isects && (d_render_depth || !d_v_depth) && d_T && d_last_ids && d_v_rgb && d_v_screen,
                 "ssb_raster_bwd: NULL argument");
-    SSB_REQUIRE(n_images >= 0 && width > 0 && height > 0, "ssb_raster_bwd: bad sizes");
+    SSB_REQUIRE(n_images >= 0 && width > 0 && height > 0 && n_records >= 0 && n_flatten >= 0, "ssb_raster_bwd: bad sizes");
     if (n_images == 0) return SSB_OK;
-    return launch_raster_bwd(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height, d_render_depth, d_T, d_last_ids,
+    return launch_raster_bwd(d_screen, n_records, d_tile_offsets, d_flatten_ids, n_flatten, d_n_isects, n_images, width, height, d_render_depth, d_T, d_last_ids,
                              d_v_rgb, d_v_depth, d_v_T, d_v_screen, 0, BwdAccum{nullptr, nullptr, 1, nullptr, nullptr}, stream);
 }
 
-int ssb_raster_bwd_accum(const SsbScreenRec* d_screen, const int32_t* d_tile_offsets, const int32_t* d_flatten_ids,
+int ssb_raster_bwd_accum(const SsbScreenRec* d_screen, int64_t n_records, const int32_t* d_tile_offsets,
+                         const int32_t* d_flatten_ids, int64_t n_flatten,
                          const int64_t* d_n_isects, int32_t n_images, int32_t width, int32_t height,
                          const float* d_render_depth, const float* d_T, const int32_t* d_last_ids,
                          const float* d_v_rgb, const float* d_v_depth, const float* d_v_T, SsbScreenRec* d_v_screen,
@@ -401,7 +438,7 @@ int ssb_raster_bwd_accum(const SsbScreenRec* d_screen, const int32_t* d_tile_off
     using namespace ssb;
     SSB_REQUIRE(d_screen && d_tile_offsets && d_flatten_ids && d_n_isects && d_T && d_last_ids && d_v_rgb && d_v_screen,
                 "ssb_raster_bwd_accum: NULL argument");
-    SSB_REQUIRE(n_images >= 0 && width > 0 && height > 0, "ssb_raster_bwd_accum: bad sizes");
+    SSB_REQUIRE(n_images >= 0 && width > 0 && height > 0 && n_records >= 0 && n_flatten >= 0, "ssb_raster_bwd_accum: bad sizes");
     SSB_REQUIRE(!d_v_depth || d_render_depth, "ssb_raster_bwd_accum: a depth cotangent needs the rendered depth");
     SSB_REQUIRE(accum_mode >= SSB_ACCUM_NONE && accum_mode <= SSB_ACCUM_AVG, "ssb_raster_bwd_accum: accum_mode %d is not a DensifyAccumMode", accum_mode);
     if (accum_mode != SSB_ACCUM_NONE) {
@@ -410,7 +447,7 @@ int ssb_raster_bwd_accum(const SsbScreenRec* d_screen, const int32_t* d_tile_off
         SSB_REQUIRE(d_gaussian_ids || n_per_image > 0, "ssb_raster_bwd_accum: n_per_image must be positive without d_gaussian_ids");
     }
     if (n_images == 0) return SSB_OK;
-    return launch_raster_bwd(d_screen, d_tile_offsets, d_flatten_ids, d_n_isects, n_images, width, height, d_render_depth, d_T, d_last_ids,
+    return launch_raster_bwd(d_screen, n_records, d_tile_offsets, d_flatten_ids, n_flatten, d_n_isects, n_images, width, height, d_render_depth, d_T, d_last_ids,
                              d_v_rgb, d_v_depth, d_v_T, d_v_screen, accum_mode,
                              BwdAccum{d_weight_map, d_gaussian_ids, n_per_image > 0 ? n_per_image : 1, d_accum_weight, d_accum_weight_den}, stream);
 }

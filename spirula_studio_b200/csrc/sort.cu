@@ -294,6 +294,9 @@ __global__ void __launch_bounds__(kSortThreads, 2) sort_onesweep_kernel(
 
 static int64_t desc_region_words(int64_t capacity) { return ceil_div(capacity > 0 ? capacity : 1, kSortTile) * kRadix; }
 
+// Device address of the built-in scratch array on the current device (defined with ssb_sort_pairs_u64_noalloc).
+static int static_sort_scratch(void** out);
+
 }  // namespace ssb
 
 extern "C" {
@@ -328,11 +331,7 @@ int ssb_sort_pairs_u64(int64_t* d_keys_a, int32_t* d_vals_a, int64_t* d_keys_b, 
     const int64_t region_bytes = align_up(desc_region_words(capacity) * 4, 256);
     uint32_t* desc[2] = {(uint32_t*)(ws + align_up((int64_t)sizeof(SortHeader), 256)),
                          (uint32_t*)(ws + align_up((int64_t)sizeof(SortHeader), 256) + region_bytes)};
-    static bool attr_set = false;
-    if (!attr_set) {
-        SSB_CUDA(cudaFuncSetAttribute(sort_onesweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem)));
-        attr_set = true;
-    }
+    if (int e = ensure_dynamic_smem((const void*)sort_onesweep_kernel, (int)sizeof(SortSmem))) return e;
     SSB_CUDA(cudaMemsetAsync(hdr, 0, sizeof(SortHeader), st));
     const int64_t tiles_cap = ceil_div(capacity, kSortTile);
     int hist_blocks = (int)(tiles_cap < 148 * 8 ? tiles_cap : 148 * 8);
@@ -357,7 +356,11 @@ int ssb_sort_pairs_u64(int64_t* d_keys_a, int32_t* d_vals_a, int64_t* d_keys_b, 
  * descriptor (its output is then not sorted).  Synchronises the stream. */
 int ssb_sort_check(const void* d_workspace, void* stream) {
     using namespace ssb;
-    SSB_REQUIRE(d_workspace, "ssb_sort_check: NULL workspace");
+    if (!d_workspace) {       // the built-in scratch of ssb_sort_pairs_u64_noalloc on the current device
+        void* p = nullptr;
+        if (int e = static_sort_scratch(&p)) return e;
+        d_workspace = p;
+    }
     uint32_t err = 0;
     const SortHeader* hdr = (const SortHeader*)d_workspace;
     SSB_CUDA(cudaMemcpyAsync(&err, &hdr->error, sizeof(err), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
@@ -391,32 +394,40 @@ static __device__ __align__(256) unsigned char g_static_sort_scratch[kStaticSort
 
 #include <mutex>
 
+namespace ssb {
+
+// The array's name is only a host-side handle; the kernels need its address in the
+// current device's memory, looked up once per device and remembered.
+static int static_sort_scratch(void** out) {
+    static std::mutex mu;
+    static void* scratch_of_device[kMaxDevices] = {nullptr};
+    int dev = -1;
+    SSB_CUDA(cudaGetDevice(&dev));
+    SSB_REQUIRE(dev >= 0 && dev < kMaxDevices, "ssb_sort_pairs_u64_noalloc: device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!scratch_of_device[dev]) {
+        void* p = nullptr;
+        SSB_CUDA(cudaGetSymbolAddress(&p, g_static_sort_scratch));
+        scratch_of_device[dev] = p;
+    }
+    *out = scratch_of_device[dev];
+    return SSB_OK;
+}
+
+}  // namespace ssb
+
 extern "C" int ssb_sort_pairs_u64_noalloc(int64_t* d_keys_a, int32_t* d_vals_a, int64_t* d_keys_b, int32_t* d_vals_b,
                                           const int64_t* d_n, int64_t capacity, int32_t begin_bit, int32_t end_bit,
                                           int32_t* selector, void* stream) {
     using namespace ssb;
+    SSB_REQUIRE(capacity >= 0, "ssb_sort_pairs_u64_noalloc: negative capacity %lld", (long long)capacity);
     if (capacity > kStaticSortMaxPairs) {
         set_error("ssb_sort_pairs_u64_noalloc: capacity %lld exceeds the built-in scratch, which serves at most %lld pairs; "
                   "use ssb_sort_pairs_u64 with a workspace of your own", (long long)capacity, (long long)kStaticSortMaxPairs);
         return SSB_ERR_CAPACITY;
     }
-    // The array's name is only a host-side handle; the kernels need its address in the
-    // current device's memory, looked up once per device and remembered.
-    static std::mutex mu;
-    static void* scratch_of_device[64] = {nullptr};
-    int dev = -1;
-    SSB_CUDA(cudaGetDevice(&dev));
-    SSB_REQUIRE(dev >= 0 && dev < 64, "ssb_sort_pairs_u64_noalloc: device ordinal %d out of range", dev);
     void* scratch = nullptr;
-    {
-        std::lock_guard<std::mutex> lock(mu);
-        if (!scratch_of_device[dev]) {
-            void* p = nullptr;
-            SSB_CUDA(cudaGetSymbolAddress(&p, g_static_sort_scratch));
-            scratch_of_device[dev] = p;
-        }
-        scratch = scratch_of_device[dev];
-    }
+    if (int e = static_sort_scratch(&scratch)) return e;
     return ssb_sort_pairs_u64(d_keys_a, d_vals_a, d_keys_b, d_vals_b, d_n, capacity, begin_bit, end_bit,
                               scratch, kStaticSortBytes, selector, stream);
 }

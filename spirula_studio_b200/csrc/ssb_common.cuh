@@ -19,6 +19,11 @@ constexpr float kShC0 = 0.2820947917738781f;
 void set_error(const char* fmt, ...);
 void count_launch(int n = 1);
 int check_cuda(cudaError_t e, const char* what);
+// Opts `kernel` in to `bytes` of dynamic shared memory on the current device (once per kernel and device).
+int ensure_dynamic_smem(const void* kernel, int bytes);
+constexpr int kMaxDevices = 64;
+// Device address of the current device's sticky status word (SSB_STATUS_* bits), or nullptr.
+unsigned int* device_status_word();
 
 #define SSB_REQUIRE(cond, ...)                      \
     do {                                            \
@@ -53,7 +58,7 @@ int launch_intersect_tiles(const float* d_aabb, const float* d_depths, const Ssb
                            int64_t total, int64_t n_per_image, int32_t width, int32_t height,
                            void* d_workspace, int64_t workspace_bytes,
                            int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
-                           int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort);
+                           int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort, int64_t* d_max_pairs);
 int launch_intersect_tiles_packed(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen, const int32_t* d_image_ids,
                                   const int64_t* d_total, int64_t max_pairs, int64_t n_images, int32_t width, int32_t height,
                                   void* d_workspace, int64_t workspace_bytes, int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,

@@ -60,6 +60,7 @@ struct SsbStep {
     float map_weight;
     float* accum_weight;
     float* accum_weight_den;
+    int64_t* max_pairs;       // device: largest per-view pair count since it was last cleared
 };
 
 namespace ssb {
@@ -136,11 +137,11 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
     // counts + scan + scatter are reported as the key stage, the per-tile sort as the sort stage;
     // the ranges come out of the scan, so that stage is empty
     if ((e = launch_intersect_tiles(l.aabb, l.depths, l.screen, n, n, W, H, l.isect_ws, s->isect_ws_bytes, nullptr, l.flat, s->capacity,
-                                 l.offsets, l.n_isects, st, ev ? ev[2] : nullptr))) return e;
+                                 l.offsets, l.n_isects, st, ev ? ev[2] : nullptr, s->max_pairs))) return e;
     SSB_MARK(3);
     SSB_MARK(4);
     // the loss has no depth term, so the depth image is neither rendered nor back-propagated
-    if ((e = ssb_raster_fwd(l.screen, l.offsets, l.flat, l.n_isects, 1, W, H, l.rgb, nullptr, l.T, l.last_ids, st))) return e;
+    if ((e = ssb_raster_fwd(l.screen, n, l.offsets, l.flat, s->capacity, l.n_isects, 1, W, H, l.rgb, nullptr, l.T, l.last_ids, st))) return e;
     SSB_MARK(5);
     if (gt_ready) SSB_CUDA(cudaStreamWaitEvent(st, gt_ready, 0));      // the view's target image has landed
     if (s->accum_mode) {
@@ -149,12 +150,12 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
         if ((e = launch_loss_map(l.rgb, d_gt + (int64_t)v * P * 3, 1, H, W, s->cfg.w_l1, s->cfg.w_ssim, l.v_rgb, d_losses, s->map_mode,
                                  s->map_weight, l.loss_map, st))) return e;
         SSB_MARK(6);
-        if ((e = ssb_raster_bwd_accum(l.screen, l.offsets, l.flat, l.n_isects, 1, W, H, nullptr, l.T, l.last_ids, l.v_rgb, nullptr, nullptr,
+        if ((e = ssb_raster_bwd_accum(l.screen, n, l.offsets, l.flat, s->capacity, l.n_isects, 1, W, H, nullptr, l.T, l.last_ids, l.v_rgb, nullptr, nullptr,
                                       l.v_screen, s->accum_mode, l.loss_map, n, nullptr, s->accum_weight, s->accum_weight_den, st))) return e;
     } else {
         if ((e = launch_loss(l.rgb, d_gt + (int64_t)v * P * 3, 1, H, W, s->cfg.w_l1, s->cfg.w_ssim, l.v_rgb, d_losses, st))) return e;
         SSB_MARK(6);
-        if ((e = ssb_raster_bwd(l.screen, l.offsets, l.flat, l.n_isects, 1, W, H, nullptr, l.T, l.last_ids,
+        if ((e = ssb_raster_bwd(l.screen, n, l.offsets, l.flat, s->capacity, l.n_isects, 1, W, H, nullptr, l.T, l.last_ids,
                                 l.v_rgb, nullptr, nullptr, l.v_screen, st))) return e;
     }
     SSB_MARK(7);
@@ -192,6 +193,7 @@ void ssb_step_destroy(SsbStep* s) {
     if (!s) return;
     for (int k = 0; k < SsbStep_kLanes; ++k) ssb::lane_free(s->lane[k]);
     if (s->fork) cudaEventDestroy(s->fork);
+    cudaFree(s->max_pairs);
     if (s->ev_ready)
         for (int v = 0; v < SsbStep_kMaxProfViews; ++v)
             for (int k = 0; k <= SSB_STAGE_COUNT; ++k) cudaEventDestroy(s->ev[v][k]);
@@ -218,6 +220,11 @@ int ssb_step_create(const SsbStepConfig* cfg, SsbStep** out) {
     s->n_lanes = SsbStep_kLanes;
     for (int k = 0; k < s->n_lanes; ++k) {
         int e = lane_alloc(s, s->lane[k]);
+        if (e) { ssb_step_destroy(s); return e; }
+    }
+    {
+        int e = dev_alloc(&s->max_pairs, 1, s->bytes);
+        if (!e) e = check_cuda(cudaMemset(s->max_pairs, 0, sizeof(int64_t)), "ssb_step_create: cudaMemset");
         if (e) { ssb_step_destroy(s); return e; }
     }
     cudaError_t ce = cudaEventCreateWithFlags(&s->fork, cudaEventDisableTiming);
@@ -310,6 +317,27 @@ int ssb_step_last_isects(SsbStep* s, int64_t* h_n_isects, void* stream) {
     SSB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     if (*h_n_isects > s->capacity) {
         set_error("ssb_step: %lld (splat, tile) pairs exceed the capacity of %lld; pairs beyond it were dropped", (long long)*h_n_isects, (long long)s->capacity);
+        return SSB_ERR_CAPACITY;
+    }
+    return SSB_OK;
+}
+
+const int64_t* ssb_step_max_pairs_device(const SsbStep* s) { return s ? s->max_pairs : nullptr; }
+
+int64_t ssb_step_isect_capacity(const SsbStep* s) { return s ? s->capacity : 0; }
+
+int ssb_step_status(SsbStep* s, int64_t* h_max_pairs, int reset, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(s, "ssb_step_status: NULL step");
+    cudaStream_t st = (cudaStream_t)stream;
+    int64_t m = 0;
+    SSB_CUDA(cudaMemcpyAsync(&m, s->max_pairs, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
+    if (reset) SSB_CUDA(cudaMemsetAsync(s->max_pairs, 0, sizeof(int64_t), st));
+    SSB_CUDA(cudaStreamSynchronize(st));
+    if (h_max_pairs) *h_max_pairs = m;
+    if (m > s->capacity) {
+        set_error("ssb_step: a view had %lld (splat, tile) pairs, more than the capacity of %lld; the pairs beyond it were dropped "
+                  "(create the step with a larger isect_capacity)", (long long)m, (long long)s->capacity);
         return SSB_ERR_CAPACITY;
     }
     return SSB_OK;

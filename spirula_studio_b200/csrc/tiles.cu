@@ -164,7 +164,10 @@ __global__ void __launch_bounds__(kTilesBlock) tile_count_kernel(
 }
 
 // Exclusive scan of the chunk sums by one block; also publishes M.
-__global__ void __launch_bounds__(1024) chunk_scan_kernel(int32_t* __restrict__ chunk_sums, int n_chunks, int64_t* __restrict__ n_isects) {
+// With a capacity (>= 0): a total beyond it raises SSB_STATUS_PAIRS_DROPPED and, if asked, feeds a running maximum.
+__global__ void __launch_bounds__(1024) chunk_scan_kernel(int32_t* __restrict__ chunk_sums, int n_chunks, int64_t* __restrict__ n_isects,
+                                                          int64_t capacity = -1, unsigned int* __restrict__ status = nullptr,
+                                                          int64_t* __restrict__ running_max = nullptr) {
     __shared__ int64_t warp_tot[32];
     __shared__ int64_t carry_s;
     if (threadIdx.x == 0) carry_s = 0;
@@ -198,7 +201,12 @@ __global__ void __launch_bounds__(1024) chunk_scan_kernel(int32_t* __restrict__ 
         if (threadIdx.x == 1023) carry_s = excl + v;
         __syncthreads();
     }
-    if (threadIdx.x == 0) *n_isects = carry_s;
+    if (threadIdx.x == 0) {
+        const int64_t total = carry_s;
+        *n_isects = total;
+        if (running_max) atomicMax((long long*)running_max, (long long)total);
+        if (capacity >= 0 && total > capacity && status) atomicOr(status, (unsigned int)SSB_STATUS_PAIRS_DROPPED);
+    }
 }
 
 // Inclusive per-pair prefix within each chunk + chunk offset -> cum_tiles.
@@ -498,8 +506,9 @@ __global__ void __launch_bounds__(kTilesBlock) bins_chunk_sum_kernel(const int32
 
 // bins[i] <- position of bin i's first pair (the cursor the scatter advances);
 // offsets[t] <- position of tile t's first pair.
+// offsets are clamped to `offset_limit` (the pair capacity): consumers never see a range that leaves the list buffer.
 __global__ void __launch_bounds__(kTilesBlock) bins_apply_kernel(int32_t* __restrict__ bins, int64_t n_bins, const int32_t* __restrict__ chunk_offsets,
-                                                                 int32_t* __restrict__ offsets) {
+                                                                 int32_t* __restrict__ offsets, int32_t offset_limit) {
     __shared__ int warp_tot[kTilesBlock / 32];
     __shared__ int carry_s;
     if (threadIdx.x == 0) carry_s = chunk_offsets[blockIdx.x];
@@ -520,7 +529,7 @@ __global__ void __launch_bounds__(kTilesBlock) bins_apply_kernel(int32_t* __rest
         const int excl = carry_s + woff + inc - v;
         if (i < n_bins) {
             bins[i] = excl;
-            if (offsets && (i & (kDepthBuckets - 1)) == 0) offsets[i >> kDepthBucketBits] = excl;
+            if (offsets && (i & (kDepthBuckets - 1)) == 0) offsets[i >> kDepthBucketBits] = min(excl, offset_limit);
         }
         __syncthreads();
         if (threadIdx.x == kTilesBlock - 1) carry_s = excl + v;
@@ -654,7 +663,7 @@ int ssb_tile_keys(const float* d_aabb, const float* d_depths, const SsbScreenRec
     } else {
         tile_count_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>((const float4*)d_aabb, d_screen, total, tw, th, counts, chunk_sums);
         SSB_LAUNCHED("tile_count_kernel");
-        chunk_scan_kernel<<<1, 1024, 0, st>>>(chunk_sums, (int)chunks, d_n_isects);
+        chunk_scan_kernel<<<1, 1024, 0, st>>>(chunk_sums, (int)chunks, d_n_isects, capacity, device_status_word(), nullptr);
         SSB_LAUNCHED("chunk_scan_kernel");
         tile_cum_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(counts, chunk_sums, total, cum);
         SSB_LAUNCHED("tile_cum_kernel");
@@ -686,7 +695,7 @@ int ssb_intersect_tiles(const float* d_aabb, const float* d_depths, const SsbScr
                         int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
                         int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream) {
     return ssb::launch_intersect_tiles(d_aabb, d_depths, d_screen, total, n_per_image, width, height, d_workspace, workspace_bytes,
-                                       d_isect_ids, d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, nullptr);
+                                       d_isect_ids, d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, nullptr, nullptr);
 }
 
 int32_t ssb_tile_n_bits(int64_t n_tiles) {
@@ -719,15 +728,15 @@ static int intersect_tiles_impl(const float* d_aabb, const float* d_depths, cons
                         void* d_workspace, int64_t workspace_bytes,
                         int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
                         int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort,
-                        const int32_t* d_image_ids, const int64_t* d_total, int64_t n_images_packed);
+                        const int32_t* d_image_ids, const int64_t* d_total, int64_t n_images_packed, int64_t* d_max_pairs);
 
 int launch_intersect_tiles(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
                         int64_t total, int64_t n_per_image, int32_t width, int32_t height,
                         void* d_workspace, int64_t workspace_bytes,
                         int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
-                        int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort) {
+                        int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort, int64_t* d_max_pairs) {
     return intersect_tiles_impl(d_aabb, d_depths, d_screen, total, n_per_image, width, height, d_workspace, workspace_bytes, d_isect_ids,
-                                d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, mark_before_sort, nullptr, nullptr, 0);
+                                d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, mark_before_sort, nullptr, nullptr, 0, d_max_pairs);
 }
 
 int launch_intersect_tiles_packed(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen, const int32_t* d_image_ids,
@@ -736,7 +745,7 @@ int launch_intersect_tiles_packed(const float* d_aabb, const float* d_depths, co
                                   int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream) {
     SSB_REQUIRE(d_image_ids && d_total && n_images > 0, "ssb_intersect_tiles_packed: NULL argument");
     return intersect_tiles_impl(d_aabb, d_depths, d_screen, max_pairs, 1, width, height, d_workspace, workspace_bytes, d_isect_ids,
-                                d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, nullptr, d_image_ids, d_total, n_images);
+                                d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, nullptr, d_image_ids, d_total, n_images, nullptr);
 }
 
 static int intersect_tiles_impl(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
@@ -744,7 +753,7 @@ static int intersect_tiles_impl(const float* d_aabb, const float* d_depths, cons
                         void* d_workspace, int64_t workspace_bytes,
                         int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
                         int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort,
-                        const int32_t* d_image_ids, const int64_t* d_total, int64_t n_images_packed) {
+                        const int32_t* d_image_ids, const int64_t* d_total, int64_t n_images_packed, int64_t* d_max_pairs) {
     SSB_REQUIRE(d_aabb && d_depths && d_screen && d_workspace && d_flatten_ids && d_tile_offsets && d_n_isects, "ssb_intersect_tiles: NULL argument");
     SSB_REQUIRE(total >= 0 && n_per_image > 0 && width > 0 && height > 0 && capacity >= 0, "ssb_intersect_tiles: bad sizes");
     SSB_REQUIRE(total < ((int64_t)1 << 31) && capacity < ((int64_t)1 << 31), "ssb_intersect_tiles: pair indices and positions must fit int32");
@@ -756,6 +765,7 @@ static int intersect_tiles_impl(const float* d_aabb, const float* d_depths, cons
     SSB_REQUIRE(workspace_bytes >= ssb_intersect_tiles_workspace_bytes(n_tiles, capacity), "ssb_intersect_tiles: workspace too small");
     if (total == 0) {
         SSB_CUDA(cudaMemsetAsync(d_n_isects, 0, sizeof(int64_t), st));
+        SSB_CUDA(cudaMemsetAsync(d_tile_offsets, 0, (size_t)n_tiles * sizeof(int32_t), st));
         return SSB_OK;
     }
     const int64_t n_bins = n_tiles * kDepthBuckets;
@@ -777,9 +787,9 @@ static int intersect_tiles_impl(const float* d_aabb, const float* d_depths, cons
     SSB_LAUNCHED("bin_pass_kernel<count>");
     bins_chunk_sum_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(bins, n_bins, chunk_sums);
     SSB_LAUNCHED("bins_chunk_sum_kernel");
-    chunk_scan_kernel<<<1, 1024, 0, st>>>(chunk_sums, (int)chunks, d_n_isects);
+    chunk_scan_kernel<<<1, 1024, 0, st>>>(chunk_sums, (int)chunks, d_n_isects, capacity, device_status_word(), d_max_pairs);
     SSB_LAUNCHED("chunk_scan_kernel");
-    bins_apply_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(bins, n_bins, chunk_sums, d_tile_offsets);
+    bins_apply_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(bins, n_bins, chunk_sums, d_tile_offsets, (int32_t)capacity);
     SSB_LAUNCHED("bins_apply_kernel");
     bin_pass_kernel<true><<<pass_grid, kBinThreads, 0, st>>>((const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th, range, bins, capacity, pairs, d_image_ids, d_total);
     SSB_LAUNCHED("bin_pass_kernel<scatter>");
@@ -881,7 +891,7 @@ int ssb_project_fwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64
     SSB_LAUNCHED("bins_chunk_sum_kernel");
     chunk_scan_kernel<<<1, 1024, 0, st>>>(chunk_sums, (int)chunks, d_n_visible);
     SSB_LAUNCHED("chunk_scan_kernel");
-    bins_apply_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(flags, total, chunk_sums, nullptr);
+    bins_apply_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(flags, total, chunk_sums, nullptr, 0);
     SSB_LAUNCHED("bins_apply_kernel");
     compact_visible_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(u_aabb, u_depths, u_screen, flags, total, n, capacity,
                                                                           (float4*)d_aabb, d_depths, d_screen, d_camera_ids, d_gaussian_ids);

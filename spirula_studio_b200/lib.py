@@ -19,6 +19,7 @@ SSB_ERR_UNSUPPORTED = -5
 
 CAMERA_PINHOLE, CAMERA_FISHEYE, CAMERA_EQUISOLID, CAMERA_EQUIRECT = 0, 1, 2, 3
 SSB_ACCUM_NONE, SSB_ACCUM_MAX, SSB_ACCUM_SUM, SSB_ACCUM_AVG = 0, 1, 2, 3
+STATUS_BAD_INDEX, STATUS_PAIRS_DROPPED = 1, 2
 NUM_SH = 15
 TILE = 16
 SCREEN_REC_FLOATS = 12
@@ -96,9 +97,13 @@ SIGNATURES = {
     "ssb_peer_reduce_f32": (C.c_int, [_P, _P]),
     "ssb_peer_broadcast": (C.c_int, [_P, _P]),
     "ssb_tile_ranges": (C.c_int, [_P, _P, _I64, _I64, _P, _P]),
-    "ssb_raster_fwd": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P]),
-    "ssb_raster_bwd": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _P]),
-    "ssb_raster_bwd_accum": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _I32, _P, _I64, _P, _P, _P, _P]),
+    "ssb_raster_fwd": (C.c_int, [_P, _I64, _P, _P, _I64, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P]),
+    "ssb_raster_bwd": (C.c_int, [_P, _I64, _P, _P, _I64, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "ssb_raster_bwd_accum": (C.c_int, [_P, _I64, _P, _P, _I64, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _I32, _P, _I64, _P, _P, _P, _P]),
+    "ssb_device_status": (C.c_int, [_P, _P]),
+    "ssb_step_max_pairs_device": (_P, [_P]),
+    "ssb_step_isect_capacity": (_I64, [_P]),
+    "ssb_step_status": (C.c_int, [_P, _P, C.c_int, _P]),
     "ssb_loss_l1_ssim_fwdbwd": (C.c_int, [_P, _P, _I32, _I32, _I32, _F, _F, _P, _P, _P]),
     "ssb_step_set_densify": (C.c_int, [_P, _I32, _F, _I32, _P, _P]),
     "ssb_loss_l1_ssim_fwdbwd_map": (C.c_int, [_P, _P, _I32, _I32, _I32, _F, _F, _P, _P, _I32, _F, _P, _P]),

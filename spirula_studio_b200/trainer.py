@@ -347,6 +347,10 @@ class Trainer:
         if self._copy_stream is None:
             self._copy_stream = torch.cuda.Stream(device=self.device)
             self._loss_host = [torch.zeros(3, dtype=torch.float32).pin_memory() for _ in range(2)]
+            # the largest per-view pair count of every step object, read back with the loss scalars
+            self._pairs_dev = [L.device_bytes_tensor(int(self.lib.ssb_step_max_pairs_device(h)), 8, self.device).view(torch.int64)
+                               for h in self.handles]
+            self._pairs_host = [torch.zeros(len(self.handles), dtype=torch.int64).pin_memory() for _ in range(2)]
             self._loss_ready = [torch.cuda.Event(), torch.cuda.Event()]
             self._set_free = [None, None]          # event after which staging set k may be overwritten
             self._loss_views = [1, 1]
@@ -407,6 +411,8 @@ class Trainer:
         self.optimizer_step(total_views)
         # device -> host read of this step's scalars (asynchronous: pinned destination)
         self._loss_host[k].copy_(self.losses, non_blocking=True)
+        for i, t in enumerate(self._pairs_dev):
+            self._pairs_host[k][i:i + 1].copy_(t, non_blocking=True)
         self._loss_ready[k].record(main)
         self._loss_views[k] = max(nv_total, 1)
         done = torch.cuda.Event()
@@ -419,13 +425,35 @@ class Trainer:
             return (0.0, 0.0, 0.0)
         p = 1 - k
         self._loss_ready[p].synchronize()
+        self._raise_if_pairs_dropped(p)
         return tuple((self._loss_host[p] / self._loss_views[p]).tolist())
 
     def last_losses(self):
         """(l1, ssim, loss) of the newest host-buffer step, averaged over this rank's views; waits for it."""
         k = (self._calls - 1) & 1
         self._loss_ready[k].synchronize()
+        self._raise_if_pairs_dropped(k)
         return tuple((self._loss_host[k] / self._loss_views[k]).tolist())
+
+    def _raise_if_pairs_dropped(self, k):
+        """The pair counts travel to the host with the loss scalars, so an iteration needs no extra
+        synchronisation to notice that a view outgrew isect_capacity (it was then rendered from clamped lists)."""
+        for i, h in enumerate(self.handles):
+            cap = int(self.lib.ssb_step_isect_capacity(h))
+            m = int(self._pairs_host[k][i])
+            if m > cap:
+                raise L.SsbError(L.SSB_ERR_CAPACITY, f"a view had {m} (splat, tile) pairs, more than isect_capacity = {cap}; "
+                                                     "the pairs beyond it were dropped: create the Trainer with a larger isect_capacity")
+
+    def check_capacity(self):
+        """Synchronises and raises SsbError(SSB_ERR_CAPACITY) if any view since the last check had more
+        (splat, tile) pairs than isect_capacity; returns the largest pair count seen."""
+        worst = 0
+        for h in self.handles:
+            m = C.c_int64(0)
+            L.check(self.lib.ssb_step_status(h, C.byref(m), 1, None))
+            worst = max(worst, m.value)
+        return worst
 
     def last_isects(self, kind=0):
         m = C.c_int64(0)

@@ -106,7 +106,7 @@ def raster_fwd(lib, rec, offs, flat, n_dev, I, W, H):
     P = I * H * W
     out = dict(rgb=torch.zeros(P, 3, device=DEV), depth=torch.zeros(P, device=DEV), T=torch.zeros(P, device=DEV),
                last_ids=torch.zeros(P, dtype=torch.int32, device=DEV))
-    L.check(lib.ssb_raster_fwd(L.ptr(rec), L.ptr(offs), L.ptr(flat), L.ptr(n_dev), I, W, H, L.ptr(out["rgb"]), L.ptr(out["depth"]),
+    L.check(lib.ssb_raster_fwd(L.ptr(rec), rec.numel() // L.SCREEN_REC_FLOATS, L.ptr(offs), L.ptr(flat), flat.numel(), L.ptr(n_dev), I, W, H, L.ptr(out["rgb"]), L.ptr(out["depth"]),
                                L.ptr(out["T"]), L.ptr(out["last_ids"]), None))
     torch.cuda.synchronize()
     return out
@@ -114,7 +114,7 @@ def raster_fwd(lib, rec, offs, flat, n_dev, I, W, H):
 
 def raster_bwd(lib, rec, offs, flat, n_dev, I, W, H, render, v_rgb, v_depth=None, v_T=None, pairs=None):
     v_rec = torch.zeros(pairs * L.SCREEN_REC_FLOATS, device=DEV)
-    L.check(lib.ssb_raster_bwd(L.ptr(rec), L.ptr(offs), L.ptr(flat), L.ptr(n_dev), I, W, H, L.ptr(render["depth"]), L.ptr(render["T"]),
+    L.check(lib.ssb_raster_bwd(L.ptr(rec), min(pairs, rec.numel() // L.SCREEN_REC_FLOATS), L.ptr(offs), L.ptr(flat), flat.numel(), L.ptr(n_dev), I, W, H, L.ptr(render["depth"]), L.ptr(render["T"]),
                                L.ptr(render["last_ids"]), L.ptr(v_rgb), L.ptr(v_depth), L.ptr(v_T), L.ptr(v_rec), None))
     torch.cuda.synchronize()
     return v_rec

@@ -48,9 +48,9 @@ def test_argument_errors_are_statuses_not_crashes():
     assert lib.ssb_sort_pairs_u64(one, one, one, one, one, 10, 40, 30, one, 1 << 30, C.byref(sel), None) == L.SSB_ERR_INVALID_ARGUMENT
     assert lib.ssb_quant_encode(one, 10, 12, one, one, None) == L.SSB_ERR_INVALID_ARGUMENT
     # the optional entry points reject what their reference counterparts throw on
-    assert lib.ssb_raster_bwd_accum(one, one, one, one, 1, 16, 16, None, one, one, one, None, None, one, 9, None, 4, None, one, None,
+    assert lib.ssb_raster_bwd_accum(one, 4, one, one, 4, one, 1, 16, 16, None, one, one, one, None, None, one, 9, None, 4, None, one, None,
                                     None) == L.SSB_ERR_INVALID_ARGUMENT                       # not a DensifyAccumMode
-    assert lib.ssb_raster_bwd_accum(one, one, one, one, 1, 16, 16, None, one, one, one, None, None, one, L.SSB_ACCUM_AVG, None, 4, None, one,
+    assert lib.ssb_raster_bwd_accum(one, 4, one, one, 4, one, 1, 16, 16, None, one, one, one, None, None, one, L.SSB_ACCUM_AVG, None, 4, None, one,
                                     None, None) == L.SSB_ERR_INVALID_ARGUMENT                 # average without a denominator array
     assert lib.ssb_loss_l1_ssim_fwdbwd_map(one, one, 1, 16, 16, 0.8, 0.2, one, None, 2, 1.0, None, None) == L.SSB_ERR_INVALID_ARGUMENT
     assert lib.ssb_adam_step_sh_quantized_ex(one, one, one, one, one, 16, 5, 0, 256, 256, C.byref(L.SsbAdamConfig(0, 0, 0, 0, 0, 1e-3, 0, 1, 1, 0)),

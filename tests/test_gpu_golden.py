@@ -305,7 +305,7 @@ def test_raster_accum_weight_vs_reference(lib, U, name):
         for with_depth in (True, False):
             v_rec = torch.zeros(I * n * L.SCREEN_REC_FLOATS, device=U.DEV)
             acc, den = torch.zeros(n, device=U.DEV), torch.zeros(n, device=U.DEV)
-            L.check(lib.ssb_raster_bwd_accum(L.ptr(rec), L.ptr(offs), L.ptr(fl), L.ptr(n_dev), I, W, H, L.ptr(render["depth"]), L.ptr(render["T"]),
+            L.check(lib.ssb_raster_bwd_accum(L.ptr(rec), I * n, L.ptr(offs), L.ptr(fl), fl.numel(), L.ptr(n_dev), I, W, H, L.ptr(render["depth"]), L.ptr(render["T"]),
                                              L.ptr(render["last_ids"]), L.ptr(v_rgb), L.ptr(v_depth) if with_depth else None, L.ptr(v_T), L.ptr(v_rec),
                                              mode, L.ptr(wmap), n, None, L.ptr(acc), L.ptr(den), None))
             torch.cuda.synchronize()

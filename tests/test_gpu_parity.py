@@ -239,10 +239,15 @@ def test_intersect_tiles_fused_bit_exact(lib, U, oracle, views, scale_mu, n, w, 
     # the keys are optional
     _, g_vals2, _, _ = U.intersect_tiles(lib, d_aabb, d_depths, rec, views * n, n, W, H, M + 64, n_tiles, want_keys=False)
     assert np.array_equal(g_vals2.cpu().numpy()[:M], sv)
-    # too small a capacity: the full count is still reported, what fits is a prefix of the sorted order
+    # too small a capacity: the full count is still reported, every range handed on is clamped to the capacity,
+    # what fits is a prefix of the sorted order, and the device status word says that pairs were dropped
     cap = max(M // 2, 1)
+    lib.ssb_device_status(None, None)                      # clear what earlier calls may have left
     _, g_vals3, g_offs3, g_M3 = U.intersect_tiles(lib, d_aabb, d_depths, rec, views * n, n, W, H, cap, n_tiles, want_keys=False)
-    assert g_M3 == M and np.array_equal(g_offs3.cpu().numpy().astype(np.int64), offs.astype(np.int64))
+    assert g_M3 == M and np.array_equal(g_offs3.cpu().numpy().astype(np.int64), np.minimum(offs.astype(np.int64), cap))
+    bits = C.c_int32(0)
+    assert lib.ssb_device_status(C.byref(bits), None) == L.SSB_ERR_CAPACITY and bits.value & L.STATUS_PAIRS_DROPPED
+    assert lib.ssb_device_status(C.byref(bits), None) == L.SSB_OK and bits.value == 0        # reading clears it
     whole = offs[np.append(offs[1:], M) <= cap]            # tiles that lie wholly below the capacity
     if whole.size:
         end = int(np.append(offs[1:], M)[np.append(offs[1:], M) <= cap].max())

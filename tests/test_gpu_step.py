@@ -396,7 +396,7 @@ def test_full_size_raster_properties(lib, U):
     assert bool(((last >= offs.long()[tile]) & (last < ends[tile]))[blended].all())
     # depth-free variant
     rgb2 = torch.zeros_like(rgb); T2 = torch.zeros_like(T); last2 = torch.zeros_like(out["last_ids"])
-    L.check(lib.ssb_raster_fwd(L.ptr(pr["rec"]), L.ptr(offs), L.ptr(flat), L.ptr(n_dev), 1, W, H, L.ptr(rgb2), None, L.ptr(T2), L.ptr(last2), None))
+    L.check(lib.ssb_raster_fwd(L.ptr(pr["rec"]), n, L.ptr(offs), L.ptr(flat), flat.numel(), L.ptr(n_dev), 1, W, H, L.ptr(rgb2), None, L.ptr(T2), L.ptr(last2), None))
     torch.cuda.synchronize()
     assert torch.equal(rgb2, rgb) and torch.equal(T2, T) and torch.equal(last2, out["last_ids"])
     # linearity of the backward pass
@@ -415,7 +415,7 @@ def test_full_size_raster_properties(lib, U):
     for mode in (L.SSB_ACCUM_MAX, L.SSB_ACCUM_AVG):
         v_rec = torch.zeros(n * L.SCREEN_REC_FLOATS, device=U.DEV)
         acc, den = torch.zeros(n, device=U.DEV), torch.zeros(n, device=U.DEV)
-        L.check(lib.ssb_raster_bwd_accum(L.ptr(pr["rec"]), L.ptr(offs), L.ptr(flat), L.ptr(n_dev), 1, W, H, None, L.ptr(out["T"]), L.ptr(out["last_ids"]),
+        L.check(lib.ssb_raster_bwd_accum(L.ptr(pr["rec"]), n, L.ptr(offs), L.ptr(flat), flat.numel(), L.ptr(n_dev), 1, W, H, None, L.ptr(out["T"]), L.ptr(out["last_ids"]),
                                          L.ptr(v), None, None, L.ptr(v_rec), mode, L.ptr(ones), n, None, L.ptr(acc), L.ptr(den), None))
         torch.cuda.synchronize()
         res[mode] = (acc, den)

@@ -36,6 +36,8 @@ def _sort(lib, fn_noalloc, keys, vals, n, cap, b0, b1):
         st = lib.ssb_sort_pairs_u64(L.ptr(ka), L.ptr(va), L.ptr(kb), L.ptr(vb), L.ptr(n_dev), cap, b0, b1, L.ptr(ws), ws_bytes, C.byref(sel), None)
     torch.cuda.synchronize()
     assert st == 0, lib.ssb_last_error_string()
+    # did any bounded wait inside the sort give up?  NULL names the built-in scratch of the current device
+    assert lib.ssb_sort_check(None if fn_noalloc else L.ptr(ws), None) == L.SSB_OK, lib.ssb_last_error_string()
     out_k, out_v = (kb, vb) if sel.value == 1 else (ka, va)
     return out_k[:n].cpu().numpy(), out_v[:n].cpu().numpy()
 
@@ -60,3 +62,6 @@ def test_noalloc_sort_matches_regular_sort_twice_in_a_row():
     sel = C.c_int32(5)
     st = lib.ssb_sort_pairs_u64_noalloc(L.ptr(one), L.ptr(one), L.ptr(one), L.ptr(one), L.ptr(one), (1 << 20) + 1, 0, 45, C.byref(sel), None)
     assert st == L.SSB_ERR_CAPACITY and b"1048576" in lib.ssb_last_error_string() and sel.value == 5
+    # a negative capacity is refused by this entry point itself
+    st = lib.ssb_sort_pairs_u64_noalloc(L.ptr(one), L.ptr(one), L.ptr(one), L.ptr(one), L.ptr(one), -1, 0, 45, C.byref(sel), None)
+    assert st == L.SSB_ERR_INVALID_ARGUMENT and b"negative" in lib.ssb_last_error_string() and sel.value == 5

@@ -184,7 +184,9 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
 }
 
 constexpr int kBwdWarps = 4;          // one 16x16 tile per CTA, one 8x8 micro-tile per warp
-constexpr int kSurvCap = 256;         // survivors collected per segment (8 per lane)
+constexpr int kBatch = 32;            // survivors per batch: one per lane in the reduction phase
+constexpr int kQueue = 96;            // survivor queue (a scan step looks at 64 list entries)
+constexpr int kMatStride = kBatch + 2;   // row stride of the fragment matrix in float2: rows 16-byte aligned, conflict-free both ways
 
 // What the per-splat densification weight accumulates (DensifyAccumMode, src/primitives/Primitive.cuh:37-39).
 struct BwdAccum {
@@ -195,21 +197,37 @@ struct BwdAccum {
     float* out_den;               // [N], average mode only
 };
 
+// Backward pass.  One warp per 8x8 micro-tile.  The warp walks its tile's list back to front (from the
+// largest last-blended index of its pixels), keeps the records whose alpha >= 1/255 ellipse reaches the
+// micro-tile, and works through them in batches of 32, each batch in two phases per 8x4 half:
+//   blend phase  (lane = pixel): the survivors that reach the half are taken one after another, back to
+//                front; every lane evaluates its pixel's alpha, advances its running (T, dL/dT) -- which
+//                therefore live in registers -- and leaves the two numbers a fragment's gradients are
+//                built from (alpha*T and vis*dL/dalpha) in a 32x32 matrix in shared memory;
+//   reduce phase (lane = survivor): every lane sums its survivor's row of the matrix against the pixels'
+//                coordinates and colour cotangents: raw moments per pixel row, folded into the micro-tile's
+//                moments once per row, and converted to moments about the splat centre at the end.
+// The matrix is the transposition between "one lane per pixel", which the blending recurrence wants, and
+// "one lane per splat", which lets a splat's gradient leave as three 16-byte reductions per (splat,
+// micro-tile) with no cross-lane sums.  All lanes work in both phases; there is no ramp-up or drain.
 // ACCUM: 0 none, 1 max, 2 sum, 3 average (sum and denominator) of weight_map[pixel] * alpha * T over the
 // fragments a splat contributes (RasterizationEval3DBwd_kernel.cuh:541-550,566-579).
 template <bool DEPTH, int ACCUM>
-__global__ void __launch_bounds__(kBwdWarps * 32, ACCUM ? 8 : 10) raster_bwd_kernel(
+__global__ void __launch_bounds__(kBwdWarps * 32, 4) raster_bwd_kernel(
     const SsbScreenRec* __restrict__ screen, const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ flatten_ids,
     const int64_t* __restrict__ n_isects_ptr, ListBounds lb, int I, int W, int H, int tw, int th,
     const float* __restrict__ render_depth, const float* __restrict__ render_T, const int32_t* __restrict__ last_ids,
     const float* __restrict__ v_rgb, const float* __restrict__ v_depth, const float* __restrict__ v_T,
     SsbScreenRec* __restrict__ v_screen, BwdAccum acc) {
+    __shared__ __align__(16) float2 sM[kBwdWarps][kBatch * kMatStride];   // [survivor][pixel of the half]: alpha*T0, vis*dL/dalpha
+    __shared__ float4 sSA[kBwdWarps][kBatch];     // survivor: x, y relative to the micro-tile's first pixel centre, list index
+    __shared__ float4 sSQ[kBwdWarps][kBatch];     // conic pre-scaled for ex2, opacity
+    __shared__ float4 sSC[kBwdWarps][kBatch];     // colour, depth
+    __shared__ float4 sV[kBwdWarps][32];          // per pixel of the half at hand: dL/d(rgb), dL/d(depth sum)
     __shared__ float sW[ACCUM ? kBwdWarps : 1][64];   // weight map of the micro-tile
-    __shared__ float4 sP[kBwdWarps][64];       // running T, dL/dT, pixel centre x, y
-    __shared__ float4 sV[kBwdWarps][64];       // dL/d(rgb), dL/d(depth sum)
-    __shared__ int32_t sLast[kBwdWarps][64];
-    __shared__ int32_t sSurv[kBwdWarps][kSurvCap];   // sorted-list index of each survivor
-    __shared__ int32_t sSurvG[kBwdWarps][kSurvCap];  // its record index
+    __shared__ int32_t sSurv[kBwdWarps][kQueue];  // sorted-list index of each queued survivor
+    __shared__ int32_t sSurvG[kBwdWarps][kQueue]; // its record index
+    __shared__ uint8_t sIdx[kBwdWarps][2][kBatch];   // per half: the batch's survivors that reach it, back to front
 
     const int img = blockIdx.z;
     const int tile_id = blockIdx.y * tw + blockIdx.x;
@@ -222,138 +240,231 @@ __global__ void __launch_bounds__(kBwdWarps * 32, ACCUM ? 8 : 10) raster_bwd_ker
     const int32_t range_start = clamp_range(offs[tile_id], list_len);
     const int32_t range_end = (img == I - 1 && tile_id == tw * th - 1) ? list_len : clamp_range(offs[tile_id + 1], list_len);
 
+    // this lane's two pixels: (lane & 7, lane >> 3) in the upper half and four rows below it in the lower one
+    const float pxr = (float)(lane & 7), pyr = (float)(lane >> 3);
+    float T[2], vT[2], vcx[2], vcy[2], vcz[2], vcw[2];
+    int32_t last[2];
     int32_t max_last = -1;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int p = h * 32 + lane;
         const int x = mx0 + (p & 7), y = my0 + (p >> 3);
         const bool inside = x < W && y < H;
-        int32_t last = -1;
-        float T1 = 0.f, vT1 = 0.f;
+        last[h] = -1; T[h] = 0.f; vT[h] = 0.f;
         float4 vc = make_float4(0.f, 0.f, 0.f, 0.f);
         if (inside) {
             const int64_t pix = ((int64_t)img * H + y) * W + x;
-            last = last_ids[pix];
-            T1 = render_T[pix];
-            vT1 = v_T ? v_T[pix] : 0.f;
+            last[h] = last_ids[pix];
+            T[h] = render_T[pix];
+            vT[h] = v_T ? v_T[pix] : 0.f;
             vc = make_float4(v_rgb[3 * pix], v_rgb[3 * pix + 1], v_rgb[3 * pix + 2], 0.f);
             if (DEPTH) {
                 vc.w = v_depth[pix];
-                const float inv_alpha = 1.0f / fmaxf(1.0f - T1, 1e-10f);
-                vT1 += render_depth[pix] * vc.w * inv_alpha;
+                const float inv_alpha = 1.0f / fmaxf(1.0f - T[h], 1e-10f);
+                vT[h] += render_depth[pix] * vc.w * inv_alpha;
                 vc.w *= inv_alpha;
             }
         }
         if (ACCUM) sW[w][p] = (inside && acc.weight_map) ? acc.weight_map[((int64_t)img * H + y) * W + x] : 0.f;
-        sP[w][p] = make_float4(T1, vT1, (float)x + 0.5f, (float)y + 0.5f);
-        sV[w][p] = vc;
-        sLast[w][p] = last;
-        max_last = max(max_last, last);
+        vcx[h] = vc.x; vcy[h] = vc.y; vcz[h] = vc.z; vcw[h] = vc.w;
+        max_last = max(max_last, last[h]);
     }
     max_last = __reduce_max_sync(0xffffffffu, max_last);
     __syncwarp();
 
     const float fx0 = (float)mx0 + 0.5f, fx1 = (float)mx0 + 7.5f, fy0 = (float)my0 + 0.5f, fy1 = (float)my0 + 7.5f;
+    float2* const M = sM[w];
 
-    for (int32_t scan = min(range_end - 1, max_last); scan >= range_start;) {
-        // ---- collect survivors, back to front
-        int count = 0;
-        while (scan >= range_start && count <= kSurvCap - 32) {
-            const int32_t gi = scan - lane;
-            bool ok = false;
-            int32_t g = 0;
-            if (gi >= range_start && record_ok(g = flatten_ids[gi], lb)) {
-                const float4* r = (const float4*)(screen + g);
-                const float4 a = r[0];
-                ok = (a.x + a.z >= fx0) && (a.x - a.z <= fx1) && (a.y + a.w >= fy0) && (a.y - a.w <= fy1);
-                if (ok) ok = ellipse_reaches_box(r[1], fx0 - a.x, fx1 - a.x, fy0 - a.y, fy1 - a.y);
-            }
-            const unsigned bal = __ballot_sync(0xffffffffu, ok);
-            if (ok) {
-                const int pos = count + __popc(bal & ((1u << lane) - 1u));
-                sSurv[w][pos] = gi;
-                sSurvG[w][pos] = g;
-            }
-            count += __popc(bal);
-            scan -= 32;
+    int count = 0;                                   // survivors queued
+    int32_t pos = min(range_end - 1, max_last);      // top of the 64 list entries looked at next (descending)
+    // The walk over the list is two loads deep (list entry -> record), each a trip to L2.  Both are requested
+    // ahead of their use: the records of the 64 entries at `pos` while the entries before them are examined,
+    // their list entries one step earlier still.  When a batch is full, the records requested last arrive
+    // while the batch is worked through.
+    int32_t cur_g[2], nxt_g[2];
+    float4 cur_a[2], cur_b[2];
+    auto load_ids = [&](int32_t top, int32_t (&g)[2]) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int32_t gi = top - (j * 32 + lane);
+            g[j] = (top >= range_start && gi >= range_start) ? flatten_ids[gi] : -1;
         }
-        __syncwarp();
-        // ---- sweep them 32 at a time: lane l holds survivor l of the batch and at step t
-        // works on pixel t - l, so every pixel meets the survivors strictly back to front
-        for (int base = 0; base < count; base += 32) {
-            const int bs = min(32, count - base);
-            const bool active = lane < bs;
-            int32_t sidx = 0x7fffffff, g = 0;
-            float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a, c = a;
-            if (active) {
-                sidx = sSurv[w][base + lane];
-                g = sSurvG[w][base + lane];
-                const float4* r = (const float4*)(screen + g);
-                a = r[0]; b = r[1]; c = r[2];
+    };
+    auto load_records = [&]() {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            cur_a[j] = make_float4(-1e30f, -1e30f, 0.f, 0.f);      // "reaches nothing"
+            cur_b[j] = make_float4(1.f, 0.f, 1.f, 1.f);
+            if (cur_g[j] != -1 && record_ok(cur_g[j], lb)) {
+                const float4* r = (const float4*)(screen + cur_g[j]);
+                cur_a[j] = r[0]; cur_b[j] = r[1];
             }
+        }
+    };
+    load_ids(pos, cur_g);
+    load_ids(pos - 64, nxt_g);
+    load_records();
+    while (true) {
+        // ---- queue survivors, back to front, until a full batch is there or the list is used up
+        while (pos >= range_start && count < kBatch) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float4 a = cur_a[j];
+                bool ok = (a.x + a.z >= fx0) && (a.x - a.z <= fx1) && (a.y + a.w >= fy0) && (a.y - a.w <= fy1);
+                if (ok) ok = ellipse_reaches_box(cur_b[j], fx0 - a.x, fx1 - a.x, fy0 - a.y, fy1 - a.y);
+                const unsigned bal = __ballot_sync(0xffffffffu, ok);
+                if (ok) {
+                    const int slot = count + __popc(bal & ((1u << lane) - 1u));
+                    sSurv[w][slot] = pos - (j * 32 + lane);
+                    sSurvG[w][slot] = cur_g[j];
+                }
+                count += __popc(bal);
+            }
+            pos -= 64;
+            cur_g[0] = nxt_g[0]; cur_g[1] = nxt_g[1];
+            load_ids(pos - 64, nxt_g);
+            load_records();
+        }
+        if (count == 0) break;
+        __syncwarp();
+        const int bs = min(kBatch, count);
+        // ---- stage the batch: lane l takes survivor l
+        const bool active = lane < bs;
+        int32_t g = 0;
+        float ax = 0.f, ay = 0.f, op = 0.f, cb_a = 0.f, cb_b = 0.f, cb_c = 0.f;
+        int halves = 0;
+        if (active) {
+            const int32_t sidx = sSurv[w][lane];
+            g = sSurvG[w][lane];
+            const float4* r = (const float4*)(screen + g);
+            const float4 a = r[0], b = r[1], c = r[2];
+            ax = a.x - fx0; ay = a.y - fy0; op = b.w; cb_a = b.x; cb_b = b.y; cb_c = b.z;
+            // which 8x4 halves the alpha >= 1/255 ellipse reaches (the queue test said: at least one)
+            const EllipseTest et = ellipse_test_setup(b);
+            if (ellipse_test(et, -ax, 7.0f - ax, -ay, 3.0f - ay)) halves |= 1;
+            if (ellipse_test(et, -ax, 7.0f - ax, 4.0f - ay, 7.0f - ay)) halves |= 2;
             // conic pre-scaled so that exp(-sigma) = 2^(-q): q = A2 dx^2 + B2 dx dy + C2 dy^2
             const float kLog2e = 1.4426950408889634f;
-            const float A2 = 0.5f * kLog2e * b.x, B2 = kLog2e * b.y, C2 = 0.5f * kLog2e * b.z, op = b.w;
-            // sums over this micro-tile's pixels: v_sigma * {dx^2, dx dy, dy^2, dx, dy}, vis * v_alpha, weights * v_colour
-            float s_xx = 0.f, s_xy = 0.f, s_yy = 0.f, s_x = 0.f, s_y = 0.f, gop = 0.f, gr = 0.f, gg = 0.f, gb = 0.f, gd = 0.f;
-            float aw = 0.f, aw_den = 0.f;
-            const int steps = bs + 63;
-            for (int t = 0; t < steps; ++t) {
-                const unsigned p = (unsigned)(t - lane);
-                if (p < 64u && sidx <= sLast[w][p]) {      // inactive lanes carry sidx = INT_MAX
-                    const float4 pp = sP[w][p];
-                    const float dx = a.x - pp.z, dy = a.y - pp.w;
-                    const float q = fmaf(fmaf(A2, dx, B2 * dy), dx, C2 * dy * dy);
-                    float vis;
-                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(vis) : "f"(-q));
-                    const float ov = op * vis;
-                    const float alpha = fminf(0.999f, ov);
-                    if (q >= 0.f && alpha > kAlphaThreshold) {
-                        const float4 vc = sV[w][p];
-                        const float om = 1.0f - alpha;
-                        const float T0 = __fdividef(pp.x, om);
-                        const float cdot = DEPTH ? fmaf(c.x, vc.x, fmaf(c.y, vc.y, fmaf(c.z, vc.z, c.w * vc.w)))
-                                                 : fmaf(c.x, vc.x, fmaf(c.y, vc.y, c.z * vc.z));
-                        const float v_alpha = T0 * (cdot - pp.y);
-                        const float wgt = alpha * T0;
-                        const float v_T0 = fmaf(alpha, cdot, pp.y * om);
-                        // a saturated fragment (opacity * vis > 0.999) passes no gradient to its shape
-                        const float vis_eff = ov <= 0.999f ? vis : 0.0f;
-                        const float va = vis_eff * v_alpha;
-                        const float v_sigma = -op * va;
-                        const float sx = v_sigma * dx, sy = v_sigma * dy;
-                        s_xx = fmaf(sx, dx, s_xx); s_xy = fmaf(sx, dy, s_xy); s_yy = fmaf(sy, dy, s_yy);
-                        s_x += sx; s_y += sy;
-                        gop += va;
-                        gr = fmaf(vc.x, wgt, gr); gg = fmaf(vc.y, wgt, gg); gb = fmaf(vc.z, wgt, gb);
-                        if (DEPTH) gd = fmaf(vc.w, wgt, gd);
-                        if (ACCUM == 1) aw = fmaxf(aw, sW[w][p] * wgt);
-                        if (ACCUM >= 2) aw = fmaf(sW[w][p], wgt, aw);
-                        if (ACCUM == 3) aw_den += wgt;
-                        *(float2*)&sP[w][p] = make_float2(T0, v_T0);
-                    }
-                }
-                __syncwarp();
+            sSA[w][lane] = make_float4(ax, ay, __int_as_float(sidx), 0.f);
+            sSQ[w][lane] = make_float4(0.5f * kLog2e * b.x, kLog2e * b.y, 0.5f * kLog2e * b.z, b.w);
+            sSC[w][lane] = c;
+        }
+        unsigned reach[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            reach[h] = __ballot_sync(0xffffffffu, (halves >> h) & 1);
+            if ((halves >> h) & 1) sIdx[w][h][__popc(reach[h] & ((1u << lane) - 1u))] = (uint8_t)lane;
+        }
+        __syncwarp();
+        // raw moments of vis*dL/dalpha over this micro-tile's pixels (coordinates relative to its first pixel centre),
+        // and alpha*T0 times the colour cotangent
+        float m0 = 0.f, m_x = 0.f, m_y = 0.f, m_xx = 0.f, m_xy = 0.f, m_yy = 0.f, gr = 0.f, gg = 0.f, gb = 0.f, gd = 0.f;
+        float aw = 0.f, aw_den = 0.f;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            // ---- blend phase: lane = pixel (lane & 7, 4h + (lane >> 3))
+            const float py = pyr + 4.0f * h;
+            const int n_h = __popc(reach[h]);
+            // rows of survivors that do not reach this half read as zero in the reduce phase
+            for (unsigned rest = ~reach[h] & (bs == 32 ? 0xffffffffu : ((1u << bs) - 1u)); rest; rest &= rest - 1u)
+                M[(__ffs(rest) - 1) * kMatStride + lane] = make_float2(0.f, 0.f);
+            sV[w][lane] = make_float4(vcx[h], vcy[h], vcz[h], vcw[h]);      // read by the reduce phase of this half
+            float Th = T[h], vTh = vT[h];
+            const int32_t lasth = last[h];
+#pragma unroll 4
+            for (int k = 0; k < n_h; ++k) {
+                const int s = sIdx[w][h][k];
+                const float4 sa = sSA[w][s];
+                const float4 q4 = sSQ[w][s];
+                const float4 c = sSC[w][s];
+                const float dx = sa.x - pxr, dy = sa.y - py;
+                const float q = fmaf(fmaf(q4.x, dx, q4.y * dy), dx, q4.z * dy * dy);
+                float vis;
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(vis) : "f"(-q));
+                const float ov = q4.w * vis;
+                const float alpha0 = fminf(0.999f, ov);
+                const bool pass = q >= 0.f && alpha0 > kAlphaThreshold && __float_as_int(sa.z) <= lasth;
+                // a fragment that does not count is carried through as alpha = 0: it leaves (T, dL/dT) as they are
+                const float alpha = pass ? alpha0 : 0.0f;
+                // a saturated fragment (opacity * vis > 0.999) passes no gradient to its shape
+                const float vis_eff = (pass && ov <= 0.999f) ? vis : 0.0f;
+                const float om = 1.0f - alpha;
+                const float T0 = __fdividef(Th, om);
+                const float cdot = DEPTH ? fmaf(c.x, vcx[h], fmaf(c.y, vcy[h], fmaf(c.z, vcz[h], c.w * vcw[h])))
+                                         : fmaf(c.x, vcx[h], fmaf(c.y, vcy[h], c.z * vcz[h]));
+                const float v_alpha = T0 * (cdot - vTh);
+                M[s * kMatStride + lane] = make_float2(alpha * T0, vis_eff * v_alpha);
+                vTh = fmaf(alpha, cdot, vTh * om);
+                Th = T0;
             }
-            if (active) {
-                const float gca = 0.5f * s_xx, gcb = s_xy, gcc = 0.5f * s_yy;
-                const float gx = b.x * s_x + b.y * s_y, gy = b.y * s_x + b.z * s_y;
-                // non-finite components are dropped, as the reference's atomics do
-                // (src/core/Common.cuh:792-856)
-                auto fz = [](float v) { return isfinite(v) ? v : 0.0f; };
-                float* out = (float*)(v_screen + g);
-                if (gx != 0.f || gy != 0.f) red_add_v4(out, fz(gx), fz(gy), 0.f, 0.f);
-                if (gca != 0.f || gcb != 0.f || gcc != 0.f || gop != 0.f) red_add_v4(out + 4, fz(gca), fz(gcb), fz(gcc), fz(gop));
-                if (gr != 0.f || gg != 0.f || gb != 0.f || gd != 0.f) red_add_v4(out + 8, fz(gr), fz(gg), fz(gb), fz(gd));
-                if (ACCUM) {
-                    const int64_t wid = acc.gaussian_ids ? (int64_t)acc.gaussian_ids[g] : (int64_t)g % acc.n_per_image;
-                    // weights are products of non-negative factors, so their bit patterns order like integers
-                    if (ACCUM == 1) { if (aw > 0.f) atomicMax((int*)acc.out + wid, __float_as_int(aw)); }
-                    else if (aw != 0.f) atomicAdd(acc.out + wid, aw);
-                    if (ACCUM == 3 && aw_den != 0.f) atomicAdd(acc.out_den + wid, aw_den);
+            T[h] = Th; vT[h] = vTh;
+            __syncwarp();
+            // ---- reduce phase: lane = survivor; its row of the matrix against the 32 pixels of the half
+            {
+                const float4* row = (const float4*)(M + lane * kMatStride);     // two pixels per 16-byte load
+                const float4* vrow = sV[w];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    float r0 = 0.f, r1 = 0.f, r2 = 0.f;        // the row's sums of f, f*x, f*x^2 (f = vis*dL/dalpha)
+#pragma unroll
+                    for (int xx = 0; xx < 8; xx += 2) {
+                        const float4 m = row[(r * 8 + xx) >> 1];          // pixel xx: (m.x, m.y), pixel xx + 1: (m.z, m.w)
+                        const float4 vc0 = vrow[r * 8 + xx], vc1 = vrow[r * 8 + xx + 1];
+                        r0 += m.y; r1 = fmaf(m.y, (float)xx, r1); r2 = fmaf(m.y, (float)(xx * xx), r2);
+                        r0 += m.w; r1 = fmaf(m.w, (float)(xx + 1), r1); r2 = fmaf(m.w, (float)((xx + 1) * (xx + 1)), r2);
+                        gr = fmaf(vc0.x, m.x, gr); gg = fmaf(vc0.y, m.x, gg); gb = fmaf(vc0.z, m.x, gb);
+                        gr = fmaf(vc1.x, m.z, gr); gg = fmaf(vc1.y, m.z, gg); gb = fmaf(vc1.z, m.z, gb);
+                        if (DEPTH) { gd = fmaf(vc0.w, m.x, gd); gd = fmaf(vc1.w, m.z, gd); }
+                        if (ACCUM) {
+                            const float w0 = sW[w][32 * h + r * 8 + xx], w1 = sW[w][32 * h + r * 8 + xx + 1];
+                            if (ACCUM == 1) aw = fmaxf(aw, fmaxf(w0 * m.x, w1 * m.z));
+                            if (ACCUM >= 2) aw = fmaf(w0, m.x, fmaf(w1, m.z, aw));
+                            if (ACCUM == 3) aw_den += m.x + m.z;
+                        }
+                    }
+                    const float yy = (float)(4 * h + r);
+                    m0 += r0; m_x += r1; m_xx += r2;
+                    m_y = fmaf(r0, yy, m_y); m_xy = fmaf(r1, yy, m_xy); m_yy = fmaf(r0, yy * yy, m_yy);
                 }
+            }
+            __syncwarp();
+        }
+        if (active) {
+            // moments about the splat centre: sum f*dx = ax*m0 - m_x with dx = ax - x, and so on
+            const float s_x = fmaf(ax, m0, -m_x), s_y = fmaf(ay, m0, -m_y);
+            const float s_xx = fmaf(ax, fmaf(ax, m0, -2.0f * m_x), m_xx);
+            const float s_yy = fmaf(ay, fmaf(ay, m0, -2.0f * m_y), m_yy);
+            const float s_xy = fmaf(ax, fmaf(ay, m0, -m_y), fmaf(-ay, m_x, m_xy));
+            // dL/dsigma = -opacity * vis * dL/dalpha: the factor common to a splat's fragments is applied here
+            const float nx = -op * s_x, ny = -op * s_y;
+            const float gca = -0.5f * op * s_xx, gcb = -op * s_xy, gcc = -0.5f * op * s_yy;
+            const float gx = cb_a * nx + cb_b * ny, gy = cb_b * nx + cb_c * ny;
+            const float gop = m0;
+            // non-finite components are dropped, as the reference's atomics do
+            // (src/core/Common.cuh:792-856)
+            auto fz = [](float v) { return isfinite(v) ? v : 0.0f; };
+            float* out = (float*)(v_screen + g);
+            if (gx != 0.f || gy != 0.f) red_add_v4(out, fz(gx), fz(gy), 0.f, 0.f);
+            if (gca != 0.f || gcb != 0.f || gcc != 0.f || gop != 0.f) red_add_v4(out + 4, fz(gca), fz(gcb), fz(gcc), fz(gop));
+            if (gr != 0.f || gg != 0.f || gb != 0.f || gd != 0.f) red_add_v4(out + 8, fz(gr), fz(gg), fz(gb), fz(gd));
+            if (ACCUM) {
+                const int64_t wid = acc.gaussian_ids ? (int64_t)acc.gaussian_ids[g] : (int64_t)g % acc.n_per_image;
+                // weights are products of non-negative factors, so their bit patterns order like integers
+                if (ACCUM == 1) { if (aw > 0.f) atomicMax((int*)acc.out + wid, __float_as_int(aw)); }
+                else if (aw != 0.f) atomicAdd(acc.out + wid, aw);
+                if (ACCUM == 3 && aw_den != 0.f) atomicAdd(acc.out_den + wid, aw_den);
             }
         }
+        // ---- the survivors beyond the batch move to the front of the queue
+        int32_t keep_i[2] = {0, 0}, keep_g[2] = {0, 0};
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+            if (kBatch + j * 32 + lane < count) { keep_i[j] = sSurv[w][kBatch + j * 32 + lane]; keep_g[j] = sSurvG[w][kBatch + j * 32 + lane]; }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+            if (kBatch + j * 32 + lane < count) { sSurv[w][j * 32 + lane] = keep_i[j]; sSurvG[w][j * 32 + lane] = keep_g[j]; }
+        count -= bs;
         __syncwarp();
     }
 }

@@ -81,6 +81,28 @@ def accum_weight_map(name, n_pixels):
 
 ACCUM_CASES = ("ring2", "dense1")
 
+# Quantised SH storage read by the projection (forward and backward): 8- or 16-bit codes with (min, max) bounds
+# per 256 cells ("cell" layout, bounds stride 256) or per 256 splats ("splat" layout, the stride argument 0 of the
+# reference = 256 * 45 cells), on the ring2 scene.  As in the reference's own projection test
+# (src/backend/tests/projection_parity.cpp:160-197) codes and bounds are drawn at random: any pair is a valid input.
+QUANT_SCENE = "ring2"
+QUANT_CASES = {"q16_cell": (16, 256), "q16_splat": (16, 0), "q8_cell": (8, 256), "q8_splat": (8, 0)}
+FPBO_STRIDE = 256 * 45
+
+
+def quant_sh_inputs(tag, n_splats):
+    """(codes uint8/uint16 [n*45], bounds float32 [blocks*2], bits, stride argument) of a QUANT_CASES entry."""
+    bits, stride_arg = QUANT_CASES[tag]
+    cells = n_splats * 45
+    stride = stride_arg if stride_arg > 0 else FPBO_STRIDE
+    rng = np.random.default_rng(700 + sorted(QUANT_CASES).index(tag))
+    codes = rng.integers(0, 1 << bits, size=cells, dtype=np.uint16 if bits == 16 else np.uint8)
+    nb = (cells + stride - 1) // stride
+    lo = rng.uniform(-0.25, 0.05, size=nb).astype(np.float32)
+    hi = (lo + rng.uniform(0.02, 0.4, size=nb)).astype(np.float32)
+    bounds = np.stack([lo, hi], axis=1).reshape(-1).astype(np.float32)
+    return codes, bounds, bits, stride_arg
+
 
 def loss_inputs():
     out = {}

@@ -4,8 +4,8 @@ oracle/Makefile.ref) on a GPU, on small seeded scenes.
 
     python tests/golden/make_golden.py [out_dir [fixture ...]]
 
-With fixture names (ring2, dense1, wide_fisheye, wide_equisolid, wide_equirect, ssim, ssim_map, adam, accum) only those
-are written; accum reads the committed ring2.npz and dense1.npz.
+With fixture names (ring2, dense1, wide_fisheye, wide_equisolid, wide_equirect, ssim, ssim_map, adam, accum, quant_proj,
+packed_proj) only those are written; accum, quant_proj and packed_proj read the committed ring2.npz / dense1.npz.
 
 Inputs are not stored: they are regenerated from `golden_cases.py` (same seeds).
 Every stage is run stage-isolated on the reference's own upstream outputs, so a
@@ -24,8 +24,8 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, HERE)
 
-from golden_cases import (ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, WIDE_CASES, accum_weight_map, adam_inputs, build_case, loss_inputs,  # noqa: E402
-                          loss_map_base, raster_cotangents)  # noqa: E402
+from golden_cases import (ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
+                          build_case, loss_inputs, loss_map_base, quant_sh_inputs, raster_cotangents)  # noqa: E402
 
 DEV = "cuda:0"
 
@@ -280,6 +280,86 @@ def run_accum(ref, out_dir):
     np.savez_compressed(os.path.join(out_dir, "accum.npz"), **out)
 
 
+def run_quant_proj(ref, out_dir):
+    """Projection forward and backward of the reference's kernels reading quantised SH (8/16-bit codes, both bound
+    layouts).  Only what the SH storage changes is stored: the colours, the validity boxes, and the six gradient arrays
+    for the screen-space cotangents the fp32 fixture of the same scene holds."""
+    name = QUANT_SCENE
+    cfg, sp, vm, K = build_case(name)
+    gold = np.load(os.path.join(HERE, f"{name}.npz"))
+    n, W, H, I = cfg.n_splats, cfg.width, cfg.height, vm.shape[0]
+    m = I * n
+    d = {k: dev(v.reshape(-1)) for k, v in sp.items()}
+    d_vm, d_K = dev(vm), dev(K)
+    z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=DEV)
+    v = {k: dev(gold[k]) for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")}
+    out = {}
+    for tag in QUANT_CASES:
+        codes, bounds, bits, stride_arg = quant_sh_inputs(tag, n)
+        d_codes, d_bounds = dev(codes.view(np.uint8)), dev(bounds)
+        aabb, depths, radii = z(m, 4), z(m), z(n)
+        xy, depth, conic, opac, rgb = z(m, 2), z(m), z(m, 3), z(m), z(m, 3)
+        check(ref.ref_project_fwd(I, n, W, H, P(d["means"]), P(d["quats"]), P(d["scales"]), P(d["opacities"]), P(d["features_dc"]), None,
+                                  P(d_codes), P(d_bounds), bits, C.c_int64(stride_arg), P(d_vm), P(d_K), P(aabb), P(depths), P(radii),
+                                  P(xy), P(depth), P(conic), P(opac), P(rgb)), "ref_project_fwd (quantised SH)")
+        out[f"{tag}_aabb"], out[f"{tag}_rgb"], out[f"{tag}_conic"] = aabb.cpu().numpy(), rgb.cpu().numpy(), conic.cpu().numpy()
+        g = {k: torch.zeros_like(t) for k, t in d.items()}
+        check(ref.ref_project_bwd(I, n, W, H, P(d["means"]), P(d["quats"]), P(d["scales"]), P(d["opacities"]), P(d["features_dc"]), None,
+                                  P(d_codes), P(d_bounds), bits, C.c_int64(stride_arg), P(d_vm), P(d_K), P(aabb),
+                                  P(v["v_xy"]), P(v["v_depth"]), P(v["v_conic"]), P(v["v_opac"]), P(v["v_rgb"]),
+                                  P(g["means"]), P(g["quats"]), P(g["scales"]), P(g["opacities"]), P(g["features_dc"]), P(g["features_sh"])),
+              "ref_project_bwd (quantised SH)")
+        for k, t in g.items():
+            out[f"{tag}_g_{k}"] = t.cpu().numpy()
+    np.savez_compressed(os.path.join(out_dir, "quant_proj.npz"), **out)
+
+
+def run_packed_proj(ref, out_dir):
+    """The reference's packed projection (mask, scan, compacting kernel) and the packed mode of its projection backward
+    kernel on two scenes, fp32 SH and one quantised layout: ids, count and the packed outputs; the backward pass takes the
+    fp32 fixture's screen-space cotangents gathered at the packed pairs."""
+    out = {}
+    for name, tag in (("ring2", None), ("dense1", None), ("ring2", "q16_cell")):
+        cfg, sp, vm, K = build_case(name)
+        gold = np.load(os.path.join(HERE, f"{name}.npz"))
+        n, W, H, I = cfg.n_splats, cfg.width, cfg.height, vm.shape[0]
+        m = I * n
+        d = {k: dev(v.reshape(-1)) for k, v in sp.items()}
+        d_vm, d_K = dev(vm), dev(K)
+        z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=DEV)
+        sh_args = (P(d["features_sh"]), None, None, 32, C.c_int64(256))
+        if tag:
+            codes, bounds, bits, stride_arg = quant_sh_inputs(tag, n)
+            d_codes, d_bounds = dev(codes.view(np.uint8)), dev(bounds)
+            sh_args = (None, P(d_codes), P(d_bounds), bits, C.c_int64(stride_arg))
+        mask, scan = z(m, dt=torch.bool), z(m, dt=torch.int64)
+        cam_ids, g_ids = z(m, dt=torch.int32), z(m, dt=torch.int32)
+        aabb, depths, radii = z(m, 4), z(m), z(n)
+        xy, depth, conic, opac, rgb = z(m, 2), z(m), z(m, 3), z(m), z(m, 3)
+        nnz = C.c_int64(0)
+        check(ref.ref_project_fwd_packed(I, n, W, H, P(d["means"]), P(d["quats"]), P(d["scales"]), P(d["opacities"]), P(d["features_dc"]), *sh_args,
+                                         P(d_vm), P(d_K), P(mask), P(scan), C.c_int64(m), P(cam_ids), P(g_ids), P(aabb), P(depths), P(radii),
+                                         P(xy), P(depth), P(conic), P(opac), P(rgb), C.byref(nnz)), "ref_project_fwd_packed")
+        V = nnz.value
+        key = f"{name}_{tag}" if tag else name
+        out[f"{key}_nnz"] = np.array([V], np.int64)
+        for k, t in dict(camera_ids=cam_ids, gaussian_ids=g_ids, aabb=aabb, depths=depths, xy=xy, depth=depth, conic=conic, opac=opac, rgb=rgb).items():
+            out[f"{key}_{k}"] = t[:V].cpu().numpy()
+        out[f"{key}_radii"] = radii.cpu().numpy()
+        # backward, packed mode: cotangents of the unpacked fixture gathered at the packed pairs
+        pair = (cam_ids[:V].long() * n + g_ids[:V].long())
+        pv = {k: dev(gold[k])[pair].contiguous() for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")}
+        g = {k: torch.zeros_like(t) for k, t in d.items()}
+        check(ref.ref_project_bwd_packed(I, n, V, W, H, P(d["means"]), P(d["quats"]), P(d["scales"]), P(d["opacities"]), P(d["features_dc"]), *sh_args,
+                                         P(d_vm), P(d_K), P(cam_ids), P(g_ids), P(aabb),
+                                         P(pv["v_xy"]), P(pv["v_depth"]), P(pv["v_conic"]), P(pv["v_opac"]), P(pv["v_rgb"]),
+                                         P(g["means"]), P(g["quats"]), P(g["scales"]), P(g["opacities"]), P(g["features_dc"]), P(g["features_sh"])),
+              "ref_project_bwd_packed")
+        for k, t in g.items():
+            out[f"{key}_g_{k}"] = t.cpu().numpy()
+    np.savez_compressed(os.path.join(out_dir, "packed_proj.npz"), **out)
+
+
 def main():
     out_dir = sys.argv[1] if len(sys.argv) > 1 else HERE
     os.makedirs(out_dir, exist_ok=True)
@@ -296,6 +376,10 @@ def main():
         run_loss_map(ref, out_dir)
     if not only or "accum" in only:
         run_accum(ref, out_dir)
+    if not only or "quant_proj" in only:
+        run_quant_proj(ref, out_dir)
+    if not only or "packed_proj" in only:
+        run_packed_proj(ref, out_dir)
     print("wrote fixtures to", out_dir)
 
 

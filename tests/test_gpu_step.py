@@ -428,9 +428,9 @@ def test_full_size_raster_properties(lib, U):
 
 
 def test_full_size_intersection_paths_agree(lib, U):
-    """At the benchmark's size (1M splats, 1080p, about 4.4M pairs) the oracle is too slow for a test, so the two
-    independent device paths are held against each other: keys -> radix sort -> ranges, and the fused
-    bin-by-tile intersection.  Their sorted keys, sorted pair indices, ranges and counts must be identical, the
+    """At the benchmark's size (1M splats, 1080p, about 4.4M pairs) the two independent device paths are held
+    against each other: keys -> radix sort -> ranges, and the fused bin-by-tile intersection (the oracle
+    comparison at this size is in test_gpu_fullsize.py).  Their sorted keys, sorted pair indices, ranges and counts must be identical, the
     keys ascending, and equal keys in ascending pair order."""
     cfg = scenes.CONFIGS["mid_1m"]
     sp = scenes.make_splats(cfg)
@@ -454,8 +454,7 @@ def test_full_size_intersection_paths_agree(lib, U):
 
 
 def test_full_size_sort_and_range_properties(lib, U):
-    """At the benchmark's pair count (several million) the oracle is too slow to
-    run inside a test, so check what must hold at any size: the output is
+    """At the benchmark's pair count (several million), what must hold at any size: the output is
     sorted on the bit range, is a permutation of the input (checksums of keys,
     values and key*value), equal keys keep their input order, and the ranges
     are monotone and bracket exactly the keys of each tile."""

@@ -40,7 +40,8 @@ typedef enum SsbStatus {
     SSB_ERR_CUDA = -2,             /* reference: CHECK_DEVICE_ERROR prints and exits, src/core/Common.cuh:195-203 */
     SSB_ERR_CAPACITY = -3,         /* an output buffer sized by the caller is too small */
     SSB_ERR_OUT_OF_MEMORY = -4,    /* reference: throw_out_of_memory, src/backend/api/BackendRuntime.h:114-143 */
-    SSB_ERR_UNSUPPORTED = -5
+    SSB_ERR_UNSUPPORTED = -5,
+    SSB_ERR_PEER = -6              /* another rank did not take part in a multi-GPU step (barrier failed or timed out) */
 } SsbStatus;
 
 enum { SSB_CAMERA_PINHOLE = 0, SSB_CAMERA_FISHEYE = 1, SSB_CAMERA_EQUISOLID = 2, SSB_CAMERA_EQUIRECT = 3 }; /* src/core/Common.cuh:96-101 */
@@ -446,6 +447,51 @@ int ssb_peer_close(void* d_ptr);
 int ssb_peer_reduce_f32(const SsbPeerTable* table, void* stream);
 /* theirs[segment] = own[segment] for every other rank; any data. */
 int ssb_peer_broadcast(const SsbPeerTable* table, void* stream);
+
+/* The three steps above as ONE pass: reduce-scatter, Adam and all-gather fused.  For its range of splats
+ * [first, first + count) the calling rank reads every other rank's partial gradients straight into the optimiser
+ * kernels (summed in registers, never written back), updates parameters and moments, and stores every updated
+ * parameter into all replicas, so inbound gradient traffic and outbound parameter traffic share the NVLink time and the
+ * range's gradients make one trip instead of three.  Plain peer loads and stores only.
+ *
+ * replicas: every rank's copy of the exchanged allocations as mapped in this process ([self] = this rank's own):
+ * `grads` holds all six gradient arrays of `grads`, `params` all parameter arrays of `params` (with the same layout on
+ * every rank), `sh_packed` / `sh_bounds` the quantised SH codes and their bounds (NULL when SH is fp32 inside params).
+ * Optimiser state (m1, m2, sh_state->d_optim_*) is local to the owning rank.  With quantised SH a rank's range must
+ * cover whole 256-cell blocks (ranges in multiples of 256 splats).  world == 1 is the plain optimiser step.
+ * The caller orders the ranks before (all backward passes complete) and after (all replicas complete) the call;
+ * ssb_exchange_step does both.  Reference: the gradient sum over sub-batches and the single optimiser pass of
+ * _engine_train_step_split_one_per_camera (src/engine/EngineTrainStep.cpp:366-427), done there on one GPU. */
+typedef struct SsbPeerReplicas {
+    int32_t world, self;
+    void* grads[SSB_MAX_PEERS];
+    void* params[SSB_MAX_PEERS];
+    void* sh_packed[SSB_MAX_PEERS];
+    void* sh_bounds[SSB_MAX_PEERS];
+} SsbPeerReplicas;
+/* Quantised SH values and optimiser state of ssb_adam_step_sh_quantized_ex, as one argument. */
+typedef struct SsbShAdamState {
+    uint8_t* d_optim_packed;
+    float* d_optim_bounds;
+    void* d_value_packed;
+    float* d_value_bounds;
+    int32_t value_bits;    /* 8, 16, or 32 (fp32 values, quantised state) */
+    int32_t optim_bits;    /* 8 (0 means 8) or 4 */
+} SsbShAdamState;
+int ssb_reduce_adam_broadcast(const SsbPeerReplicas* replicas, const SsbSplats* params, const SsbSplats* grads,
+                              const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                              int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg,
+                              const SsbAdamExtras* extras, void* stream);
+
+/* barrier, ssb_reduce_adam_broadcast, barrier.  `barrier(ctx, stream)` must return 0 once every rank has reached it,
+ * ordered on `stream` (an NCCL all-reduce of one element enqueued on the stream does that), and non-zero when a rank
+ * is missing or the wait timed out: ssb_exchange_step then returns SSB_ERR_PEER -- before the exchange nothing has been
+ * launched, so no kernel ever waits for a rank that is not coming. */
+typedef int (*SsbBarrierFn)(void* ctx, void* stream);
+int ssb_exchange_step(const SsbPeerReplicas* replicas, const SsbSplats* params, const SsbSplats* grads,
+                      const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                      int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg, const SsbAdamExtras* extras,
+                      SsbBarrierFn barrier, void* barrier_ctx, void* stream);
 
 /* Owns every intermediate buffer of an iteration (the reference keeps them in
  * its process-global DevicePool, src/core/Tensor.h:151-351) and runs, per view,

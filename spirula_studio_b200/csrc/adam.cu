@@ -27,6 +27,54 @@ __device__ __forceinline__ float adam_update(float x, float g, float& m1, float&
 
 __device__ __forceinline__ float inv_bias_correction(float beta, float step) { return 1.0f / (1.0f - powf(beta, step)); }
 
+// Peer mode (PEER = true) of the optimiser kernels: the gradient of a value is the sum of this rank's partial
+// gradient and the partial gradients the other ranks hold at the same place of their own gradient buffers
+// (read over NVLink, bypassing L1: a line cached by an earlier iteration would be stale), and an updated
+// parameter is stored into every rank's replica.  Every buffer has the same layout on every rank, so another
+// rank's copy of an address is that address plus a per-rank displacement.  Inbound gradient traffic and outbound
+// parameter traffic of a CTA overlap, and the summed gradient never travels back to memory.
+struct PeerOffsets {
+    int32_t n;        // other ranks, 0..7
+    int32_t pad;
+    int64_t grads[SSB_MAX_PEERS - 1], params[SSB_MAX_PEERS - 1], sh_packed[SSB_MAX_PEERS - 1], sh_bounds[SSB_MAX_PEERS - 1];   // bytes
+};
+
+template <bool PEER>
+__device__ __forceinline__ float grad_sum(const float* own, const PeerOffsets& po) {
+    float v = *own;
+    if (PEER) {
+        float x[SSB_MAX_PEERS - 1];
+#pragma unroll
+        for (int k = 0; k < SSB_MAX_PEERS - 1; ++k) x[k] = k < po.n ? __ldcv((const float*)((const char*)own + po.grads[k])) : 0.f;   // all in flight together
+#pragma unroll
+        for (int k = 0; k < SSB_MAX_PEERS - 1; ++k) v += x[k];
+    }
+    return v;
+}
+template <bool PEER>
+__device__ __forceinline__ float4 grad_sum4(const float4* own, const PeerOffsets& po) {
+    float4 v = *own;
+    if (PEER) {
+        float4 x[SSB_MAX_PEERS - 1];
+#pragma unroll
+        for (int k = 0; k < SSB_MAX_PEERS - 1; ++k)
+            x[k] = k < po.n ? __ldcv((const float4*)((const char*)own + po.grads[k])) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < SSB_MAX_PEERS - 1; ++k) { v.x += x[k].x; v.y += x[k].y; v.z += x[k].z; v.w += x[k].w; }
+    }
+    return v;
+}
+// own copy and, in peer mode, every other rank's copy
+template <bool PEER, class T>
+__device__ __forceinline__ void store_all(T* own, const T& v, const PeerOffsets& po, const int64_t (&disp)[SSB_MAX_PEERS - 1]) {
+    *own = v;
+    if (PEER) {
+#pragma unroll
+        for (int k = 0; k < SSB_MAX_PEERS - 1; ++k)
+            if (k < po.n) *(T*)((char*)own + disp[k]) = v;
+    }
+}
+
 // Gradients of the five per-splat regularisers with all loss cotangents 1 (reverse mode of
 // per_splat_losses, src/shaders/per_splat_losses.slang:5-141) for log-scales s, logit opacity o and
 // the normalised quaternion q.  The weights arrive divided by the splat count.
@@ -79,10 +127,10 @@ __device__ __forceinline__ void per_splat_reg_grads(const float s[3], float o, c
 
 // geometry (means, quats, scales, opacities) + features_dc, one thread per splat.
 // EX adds the per-splat regularisers, the scale-agnostic mean update and per-splat step counters.
-template <bool EX>
+template <bool EX, bool PEER>
 __global__ void __launch_bounds__(256) adam_geometry_kernel(
     SsbSplats p, SsbSplats g, SsbSplats m1, SsbSplats m2, int64_t first, int64_t count, SsbAdamConfig cfg,
-    float ibc1, float ibc2, float dc_decay, SsbAdamExtras ex) {
+    float ibc1, float ibc2, float dc_decay, SsbAdamExtras ex, PeerOffsets po) {
     int64_t i = first + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= first + count) return;
     const float gs = cfg.grad_scale;
@@ -109,12 +157,12 @@ __global__ void __launch_bounds__(256) adam_geometry_kernel(
     for (int k = 0; k < 3; ++k) {
         int64_t q = 3 * i + k;
         float a = m1.scales[q], b = m2.scales[q];
-        p.scales[q] = adam_update(p.scales[q], reg_s[k] + gs * g.scales[q], a, b, lr_s, ibc2);
+        store_all<PEER>(&p.scales[q], adam_update(p.scales[q], reg_s[k] + gs * grad_sum<PEER>(&g.scales[q], po), a, b, lr_s, ibc2), po, po.params);
         m1.scales[q] = a; m2.scales[q] = b;
         if (zg) g.scales[q] = 0.f;
     }
     {
-        float4 q4 = ((float4*)p.quats)[i], g4 = ((float4*)g.quats)[i];
+        float4 q4 = ((float4*)p.quats)[i], g4 = grad_sum4<PEER>((const float4*)g.quats + i, po);
         float4 a4 = ((float4*)m1.quats)[i], b4 = ((float4*)m2.quats)[i];
         float inv = 1.0f / sqrtf(q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w);
         float q[4] = {q4.x * inv, q4.y * inv, q4.z * inv, q4.w * inv};
@@ -129,25 +177,26 @@ __global__ void __launch_bounds__(256) adam_geometry_kernel(
             n2 += u[k] * u[k];
         }
         float inv2 = 1.0f / sqrtf(n2);
-        ((float4*)p.quats)[i] = make_float4(u[0] * inv2, u[1] * inv2, u[2] * inv2, u[3] * inv2);
+        store_all<PEER>((float4*)p.quats + i, make_float4(u[0] * inv2, u[1] * inv2, u[2] * inv2, u[3] * inv2), po, po.params);
         ((float4*)m1.quats)[i] = make_float4(a[0], a[1], a[2], a[3]);
         ((float4*)m2.quats)[i] = make_float4(b[0], b[1], b[2], b[3]);
         if (zg) ((float4*)g.quats)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     {
         float a = m1.opacities[i], b = m2.opacities[i];
-        p.opacities[i] = adam_update(p.opacities[i], reg_o + gs * g.opacities[i], a, b, lr_o, ibc2);
+        store_all<PEER>(&p.opacities[i], adam_update(p.opacities[i], reg_o + gs * grad_sum<PEER>(&g.opacities[i], po), a, b, lr_o, ibc2), po, po.params);
         m1.opacities[i] = a; m2.opacities[i] = b;
         if (zg) g.opacities[i] = 0.f;
     }
+    const float gm[3] = {grad_sum<PEER>(&g.means[3 * i], po), grad_sum<PEER>(&g.means[3 * i + 1], po), grad_sum<PEER>(&g.means[3 * i + 2], po)};
     if (EX && ex.d_densify_score) {
-        const float vx = gs * g.means[3 * i], vy = gs * g.means[3 * i + 1], vz = gs * g.means[3 * i + 2];
+        const float vx = gs * gm[0], vy = gs * gm[1], vz = gs * gm[2];
         ex.d_densify_score[i] = expf(fmaxf(fmaxf(s_old[0], s_old[1]), s_old[2])) * sqrtf(vx * vx + vy * vy + vz * vz);
     }
     if (EX && ex.use_scale_agnostic_mean) {
         // first moment of covariance * gradient * sqrt(2 log(255 * opacity)), second moment of
         // (gradient * 0.6 * screen radius)^2, all from the parameters before this update
-        float v[3] = {gs * g.means[3 * i], gs * g.means[3 * i + 1], gs * g.means[3 * i + 2]};
+        float v[3] = {gs * gm[0], gs * gm[1], gs * gm[2]};
         const float w = qn_old[0], x = qn_old[1], y = qn_old[2], z = qn_old[3];
         const float R[9] = {1.f - 2.f * (y * y + z * z), 2.f * (x * y - w * z), 2.f * (x * z + w * y),
                             2.f * (x * y + w * z), 1.f - 2.f * (x * x + z * z), 2.f * (y * z - w * x),
@@ -165,7 +214,7 @@ __global__ void __launch_bounds__(256) adam_geometry_kernel(
             float a = m1.means[q], b = m2.means[q];
             a = kBeta1 * a + (1.f - kBeta1) * num;
             b = kBeta2 * b + (1.f - kBeta2) * v[k] * v[k] * den * den;
-            p.means[q] = p.means[q] - lr_m * a / (sqrtf(b * ibc2) + kAdamEps);
+            store_all<PEER>(&p.means[q], p.means[q] - lr_m * a / (sqrtf(b * ibc2) + kAdamEps), po, po.params);
             m1.means[q] = a; m2.means[q] = b;
             if (zg) g.means[q] = 0.f;
         }
@@ -174,7 +223,7 @@ __global__ void __launch_bounds__(256) adam_geometry_kernel(
         for (int k = 0; k < 3; ++k) {
             int64_t q = 3 * i + k;
             float a = m1.means[q], b = m2.means[q];
-            p.means[q] = adam_update(p.means[q], gs * g.means[q], a, b, lr_m, ibc2);
+            store_all<PEER>(&p.means[q], adam_update(p.means[q], gs * gm[k], a, b, lr_m, ibc2), po, po.params);
             m1.means[q] = a; m2.means[q] = b;
             if (zg) g.means[q] = 0.f;
         }
@@ -183,41 +232,42 @@ __global__ void __launch_bounds__(256) adam_geometry_kernel(
 #pragma unroll
     for (int k = 0; k < 3; ++k) {
         int64_t q = 3 * i + k;
-        float x = p.features_dc[q], v = g.features_dc[q];
+        float x = p.features_dc[q], v = grad_sum<PEER>(&g.features_dc[q], po);
         if (!isfinite(v)) v = 0.f;
         v *= gs;
         v += dc_decay * (fmaxf(x - dc_off, 0.0f) + fminf(x + dc_off, 0.0f));
         float a = m1.features_dc[q], b = m2.features_dc[q];
-        p.features_dc[q] = adam_update(x, v, a, b, lr_dc, ibc2);
+        store_all<PEER>(&p.features_dc[q], adam_update(x, v, a, b, lr_dc, ibc2), po, po.params);
         m1.features_dc[q] = a; m2.features_dc[q] = b;
         if (zg) g.features_dc[q] = 0.f;
     }
 }
 
 // element-wise Adam (features_sh), four floats per thread
+template <bool PEER>
 __global__ void __launch_bounds__(256) adam_plain_kernel(
     float* __restrict__ param, float* __restrict__ grad, float* __restrict__ m1, float* __restrict__ m2, int64_t numel,
     float lr_ibc1, float ibc2, float decay, float decay_offset, float grad_scale, int zero_grad,
-    const int32_t* __restrict__ steps, int stride, float lr) {
+    const int32_t* __restrict__ steps, int stride, float lr, PeerOffsets po) {
     int64_t i4 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i4 >= numel) return;
     if (steps) {
         // per-splat step counters: element i uses steps[i / stride]; `steps` is already offset to the range's first splat
         for (int64_t i = i4; i < numel && i < i4 + 4; ++i) {
             const float step = (float)steps[i / stride];
-            float x = param[i], gk = grad[i];
+            float x = param[i], gk = grad_sum<PEER>(grad + i, po);
             if (!isfinite(gk)) gk = 0.f;
             gk *= grad_scale;
             gk += decay * (fmaxf(x - decay_offset, 0.0f) + fminf(x + decay_offset, 0.0f));
             float a = m1[i], b = m2[i];
-            param[i] = adam_update(x, gk, a, b, lr * inv_bias_correction(kBeta1, step), inv_bias_correction(kBeta2, step));
+            store_all<PEER>(param + i, adam_update(x, gk, a, b, lr * inv_bias_correction(kBeta1, step), inv_bias_correction(kBeta2, step)), po, po.params);
             m1[i] = a; m2[i] = b;
             if (zero_grad) grad[i] = 0.f;
         }
         return;
     }
     if (i4 + 4 <= numel && ((((uintptr_t)param | (uintptr_t)grad | (uintptr_t)m1 | (uintptr_t)m2) & 15) == 0)) {
-        float4 x = *(float4*)(param + i4), v = *(float4*)(grad + i4), a = *(float4*)(m1 + i4), b = *(float4*)(m2 + i4);
+        float4 x = *(float4*)(param + i4), v = grad_sum4<PEER>((const float4*)(grad + i4), po), a = *(float4*)(m1 + i4), b = *(float4*)(m2 + i4);
         float xs[4] = {x.x, x.y, x.z, x.w}, vs[4] = {v.x, v.y, v.z, v.w}, as[4] = {a.x, a.y, a.z, a.w}, bs[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -226,18 +276,18 @@ __global__ void __launch_bounds__(256) adam_plain_kernel(
             gk += decay * (fmaxf(xs[k] - decay_offset, 0.0f) + fminf(xs[k] + decay_offset, 0.0f));
             xs[k] = adam_update(xs[k], gk, as[k], bs[k], lr_ibc1, ibc2);
         }
-        *(float4*)(param + i4) = make_float4(xs[0], xs[1], xs[2], xs[3]);
+        store_all<PEER>((float4*)(param + i4), make_float4(xs[0], xs[1], xs[2], xs[3]), po, po.params);
         *(float4*)(m1 + i4) = make_float4(as[0], as[1], as[2], as[3]);
         *(float4*)(m2 + i4) = make_float4(bs[0], bs[1], bs[2], bs[3]);
         if (zero_grad) *(float4*)(grad + i4) = make_float4(0.f, 0.f, 0.f, 0.f);
     } else {
         for (int64_t i = i4; i < numel && i < i4 + 4; ++i) {
-            float x = param[i], gk = grad[i];
+            float x = param[i], gk = grad_sum<PEER>(grad + i, po);
             if (!isfinite(gk)) gk = 0.f;
             gk *= grad_scale;
             gk += decay * (fmaxf(x - decay_offset, 0.0f) + fminf(x + decay_offset, 0.0f));
             float a = m1[i], b = m2[i];
-            param[i] = adam_update(x, gk, a, b, lr_ibc1, ibc2);
+            store_all<PEER>(param + i, adam_update(x, gk, a, b, lr_ibc1, ibc2), po, po.params);
             m1[i] = a; m2[i] = b;
             if (zero_grad) grad[i] = 0.f;
         }
@@ -296,12 +346,14 @@ __device__ __forceinline__ void block_minmax(const float (&vmin)[NMIN], const fl
 // first, then one redux.sync per value per warp and a two-entry exchange through shared memory.
 // OPTIM_BITS = 8: two bytes per cell (u, s); 4: one byte per cell, u in the low nibble (QuantizedAdamState<4,256>).
 // STEPS: per-splat step counters (compiled apart: the power function costs the plain path registers).
-template <int VALUE_BITS, int OPTIM_BITS, bool STEPS>
+// PEER: gradients summed over the ranks, value codes and value bounds stored into every replica (the values must then be
+// packed, or, when plain fp32, part of the parameter buffer: their displacements are taken accordingly).
+template <int VALUE_BITS, int OPTIM_BITS, bool STEPS, bool PEER>
 __global__ void __launch_bounds__(64) adam_qq_kernel(
     float* __restrict__ grad, uint8_t* __restrict__ optim_packed, float4* __restrict__ optim_bounds,
     uint8_t* __restrict__ value_packed, float2* __restrict__ value_bounds, int64_t first_block, int64_t numel_total,
     float lr_ibc1, float ibc2, float decay, float decay_offset, float grad_scale, int zero_grad,
-    const int32_t* __restrict__ steps, int stride, float lr) {
+    const int32_t* __restrict__ steps, int stride, float lr, PeerOffsets po) {
     __shared__ uint32_t sh[6][2];
     const int64_t blk = first_block + blockIdx.x;
     const int64_t idx0 = blk * 256 + threadIdx.x * 4;
@@ -319,7 +371,7 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
     uint32_t vcode[4], ucode[4], scode[4];
     const bool full = idx0 + 4 <= numel_total;
     if (full) {
-        const float4 g4 = *(const float4*)(grad + idx0);
+        const float4 g4 = grad_sum4<PEER>((const float4*)(grad + idx0), po);
         gv[0] = g4.x; gv[1] = g4.y; gv[2] = g4.z; gv[3] = g4.w;
         if (kPlainValue) {
             const uint4 c = *(const uint4*)((const float*)value_packed + idx0);
@@ -347,7 +399,7 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
         const int64_t idx = idx0 + k;
         inside[k] = idx < numel_total;
         if (!full && inside[k]) {
-            gv[k] = grad[idx];
+            gv[k] = grad_sum<PEER>(grad + idx, po);
             vcode[k] = kPlainValue ? ((const uint32_t*)value_packed)[idx]
                                    : VALUE_BITS == 8 ? (uint32_t)value_packed[idx] : (uint32_t)((const uint16_t*)value_packed)[idx];
             if (kNibbles) { const uint32_t b = optim_packed[idx]; ucode[k] = b & 15u; scode[k] = b >> 4; }
@@ -423,10 +475,11 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
         uint32_t sqc = (uint32_t)fminf(fmaxf(rintf((s_new[k] - smin) * sscale), 0.0f), oq);
         oout[k] = kNibbles ? (uqc | (sqc << 4)) : (uqc | (sqc << 8));
     }
+    const int64_t (&vdisp)[SSB_MAX_PEERS - 1] = kPlainValue ? po.params : po.sh_packed;
     if (full) {
-        if (kPlainValue) *(uint4*)((float*)value_packed + idx0) = make_uint4(vout[0], vout[1], vout[2], vout[3]);
-        else if (VALUE_BITS == 16) *(ushort4*)((uint16_t*)value_packed + idx0) = make_ushort4(vout[0], vout[1], vout[2], vout[3]);
-        else *(uchar4*)(value_packed + idx0) = make_uchar4(vout[0], vout[1], vout[2], vout[3]);
+        if (kPlainValue) store_all<PEER>((uint4*)((float*)value_packed + idx0), make_uint4(vout[0], vout[1], vout[2], vout[3]), po, vdisp);
+        else if (VALUE_BITS == 16) store_all<PEER>((ushort4*)((uint16_t*)value_packed + idx0), make_ushort4(vout[0], vout[1], vout[2], vout[3]), po, vdisp);
+        else store_all<PEER>((uchar4*)(value_packed + idx0), make_uchar4(vout[0], vout[1], vout[2], vout[3]), po, vdisp);
         if (kNibbles) *(uint32_t*)(optim_packed + idx0) = oout[0] | (oout[1] << 8) | (oout[2] << 16) | (oout[3] << 24);
         else *(uint2*)(optim_packed + 2 * idx0) = make_uint2(oout[0] | (oout[1] << 16), oout[2] | (oout[3] << 16));
     } else {
@@ -434,15 +487,15 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
         for (int k = 0; k < 4; ++k)
             if (inside[k]) {
                 const int64_t idx = idx0 + k;
-                if (kPlainValue) ((uint32_t*)value_packed)[idx] = vout[k];
-                else if (VALUE_BITS == 8) value_packed[idx] = (uint8_t)vout[k];
-                else ((uint16_t*)value_packed)[idx] = (uint16_t)vout[k];
+                if (kPlainValue) store_all<PEER>((uint32_t*)value_packed + idx, vout[k], po, vdisp);
+                else if (VALUE_BITS == 8) store_all<PEER>(value_packed + idx, (uint8_t)vout[k], po, vdisp);
+                else store_all<PEER>((uint16_t*)value_packed + idx, (uint16_t)vout[k], po, vdisp);
                 if (kNibbles) optim_packed[idx] = (uint8_t)oout[k];
                 else { optim_packed[2 * idx] = (uint8_t)(oout[k] & 255u); optim_packed[2 * idx + 1] = (uint8_t)(oout[k] >> 8); }
             }
     }
     if (threadIdx.x == 0) {
-        if (!kPlainValue) value_bounds[blk] = make_float2(vmin, vmax);
+        if (!kPlainValue) store_all<PEER>(value_bounds + blk, make_float2(vmin, vmax), po, po.sh_bounds);
         optim_bounds[blk] = make_float4(umin, umax, smin, smax);
     }
 }
@@ -477,16 +530,11 @@ __global__ void __launch_bounds__(256) quant_decode_kernel(const uint8_t* __rest
 
 }  // namespace ssb
 
-extern "C" {
+namespace ssb {
 
-int ssb_adam_step(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
-                  int64_t first, int64_t count, const SsbAdamConfig* cfg, void* stream) {
-    return ssb_adam_step_ex(params, grads, m1, m2, first, count, cfg, nullptr, stream);
-}
-
-int ssb_adam_step_ex(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
-                     int64_t first, int64_t count, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream) {
-    using namespace ssb;
+static int adam_step_impl(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
+                          int64_t first, int64_t count, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, const PeerOffsets* peers,
+                          void* stream) {
     SSB_REQUIRE(params && grads && m1 && m2 && cfg, "ssb_adam_step: NULL argument");
     SSB_REQUIRE(first >= 0 && count >= 0, "ssb_adam_step: bad range");
     SSB_REQUIRE(cfg->step >= 1, "ssb_adam_step: step must be >= 1 (got %d)", cfg->step);
@@ -503,35 +551,34 @@ int ssb_adam_step_ex(const SsbSplats* params, const SsbSplats* grads, const SsbS
     const int64_t n_whole = extras ? extras->n_total : count;
     const float dc_decay = 2.0f * cfg->sh_reg_weight / (float)(n_whole * 3);
     const unsigned blocks = (unsigned)ceil_div(count, 256);
-    if (extras) adam_geometry_kernel<true><<<blocks, 256, 0, st>>>(*params, *grads, *m1, *m2, first, count, *cfg, ibc1, ibc2, dc_decay, *extras);
-    else adam_geometry_kernel<false><<<blocks, 256, 0, st>>>(*params, *grads, *m1, *m2, first, count, *cfg, ibc1, ibc2, dc_decay, SsbAdamExtras{});
+    const PeerOffsets none = {};
+    const SsbAdamExtras no_extras = {};
+#define SSB_GEO(EX, PEER) adam_geometry_kernel<EX, PEER><<<blocks, 256, 0, st>>>(*params, *grads, *m1, *m2, first, count, *cfg, ibc1, ibc2, dc_decay, \
+                                                                            EX ? *extras : no_extras, PEER ? *peers : none)
+    if (extras) { if (peers) SSB_GEO(true, true); else SSB_GEO(true, false); }
+    else { if (peers) SSB_GEO(false, true); else SSB_GEO(false, false); }
+#undef SSB_GEO
     SSB_LAUNCHED("adam_geometry_kernel");
     if (params->features_sh) {
         SSB_REQUIRE(grads->features_sh && m1->features_sh && m2->features_sh, "ssb_adam_step: SH gradient/moment arrays missing");
         int64_t numel = count * 3 * kNumSh, off = first * 3 * kNumSh;
         const float sh_decay = 2.0f * cfg->sh_reg_weight / (float)(n_whole * 3 * kNumSh);
         const int32_t* steps = extras && extras->d_steps ? extras->d_steps + first : nullptr;
-        adam_plain_kernel<<<(unsigned)ceil_div(ceil_div(numel, 4), 256), 256, 0, st>>>(
-            params->features_sh + off, grads->features_sh + off, m1->features_sh + off, m2->features_sh + off, numel,
-            cfg->lr_features_sh * ibc1, ibc2, sh_decay, 0.0f, cfg->grad_scale, cfg->zero_grad, steps, 3 * kNumSh, cfg->lr_features_sh);
+        const unsigned pblocks = (unsigned)ceil_div(ceil_div(numel, 4), 256);
+#define SSB_PLAIN(PEER) adam_plain_kernel<PEER><<<pblocks, 256, 0, st>>>( \
+            params->features_sh + off, grads->features_sh + off, m1->features_sh + off, m2->features_sh + off, numel, \
+            cfg->lr_features_sh * ibc1, ibc2, sh_decay, 0.0f, cfg->grad_scale, cfg->zero_grad, steps, 3 * kNumSh, cfg->lr_features_sh, PEER ? *peers : none)
+        if (peers) SSB_PLAIN(true); else SSB_PLAIN(false);
+#undef SSB_PLAIN
         SSB_LAUNCHED("adam_plain_kernel");
     }
     return SSB_OK;
 }
 
-int ssb_adam_step_sh_quantized(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds,
-                               void* d_value_packed, float* d_value_bounds, int32_t value_bits,
-                               int64_t first_cell, int64_t numel, int64_t numel_total,
-                               const SsbAdamConfig* cfg, void* stream) {
-    return ssb_adam_step_sh_quantized_ex(d_grad, d_optim_packed, d_optim_bounds, d_value_packed, d_value_bounds, value_bits, 8, first_cell, numel,
-                                         numel_total, cfg, nullptr, 1, stream);
-}
-
-int ssb_adam_step_sh_quantized_ex(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds,
+static int adam_sh_quantized_impl(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds,
                                   void* d_value_packed, float* d_value_bounds, int32_t value_bits, int32_t optim_bits,
                                   int64_t first_cell, int64_t numel, int64_t numel_total,
-                                  const SsbAdamConfig* cfg, const int32_t* d_steps, int32_t cells_per_splat, void* stream) {
-    using namespace ssb;
+                                  const SsbAdamConfig* cfg, const int32_t* d_steps, int32_t cells_per_splat, const PeerOffsets* peers, void* stream) {
     SSB_REQUIRE(d_grad && d_optim_packed && d_optim_bounds && d_value_packed && cfg, "ssb_adam_step_sh_quantized: NULL argument");
     SSB_REQUIRE(value_bits == 8 || value_bits == 16 || value_bits == 32, "ssb_adam_step_sh_quantized: value_bits must be 8, 16 or 32 (got %d)", value_bits);
     SSB_REQUIRE(value_bits == 32 || d_value_bounds, "ssb_adam_step_sh_quantized: packed values need a bounds table");
@@ -545,19 +592,141 @@ int ssb_adam_step_sh_quantized_ex(float* d_grad, uint8_t* d_optim_packed, float*
     const float decay = 2.0f * cfg->sh_reg_weight / (float)numel_total;
     unsigned blocks = (unsigned)ceil_div(numel, 256);
     int64_t end_total = first_cell + numel;   // cells beyond the range belong to another caller
-#define SSB_QQ_ARGS d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed, (float2*)d_value_bounds, first_cell / 256, end_total, \
-        cfg->lr_features_sh * ibc1, ibc2, decay, 0.0f, cfg->grad_scale, cfg->zero_grad, d_steps, cells_per_splat, cfg->lr_features_sh
-#define SSB_QQ_LAUNCH(OB, ST) \
+    const PeerOffsets none = {};
+#define SSB_QQ_ARGS(PEER) d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed, (float2*)d_value_bounds, first_cell / 256, end_total, \
+        cfg->lr_features_sh * ibc1, ibc2, decay, 0.0f, cfg->grad_scale, cfg->zero_grad, d_steps, cells_per_splat, cfg->lr_features_sh, PEER ? *peers : none
+#define SSB_QQ_LAUNCH(OB, ST, PEER) \
     do { \
-        if (value_bits == 32) adam_qq_kernel<32, OB, ST><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS); \
-        else if (value_bits == 8) adam_qq_kernel<8, OB, ST><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS); \
-        else adam_qq_kernel<16, OB, ST><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS); \
+        if (value_bits == 32) adam_qq_kernel<32, OB, ST, PEER><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS(PEER)); \
+        else if (value_bits == 8) adam_qq_kernel<8, OB, ST, PEER><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS(PEER)); \
+        else adam_qq_kernel<16, OB, ST, PEER><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS(PEER)); \
     } while (0)
-    if (d_steps) { if (optim_bits == 4) SSB_QQ_LAUNCH(4, true); else SSB_QQ_LAUNCH(8, true); }
-    else { if (optim_bits == 4) SSB_QQ_LAUNCH(4, false); else SSB_QQ_LAUNCH(8, false); }
+#define SSB_QQ_PEER(OB, ST) do { if (peers) SSB_QQ_LAUNCH(OB, ST, true); else SSB_QQ_LAUNCH(OB, ST, false); } while (0)
+    if (d_steps) { if (optim_bits == 4) SSB_QQ_PEER(4, true); else SSB_QQ_PEER(8, true); }
+    else { if (optim_bits == 4) SSB_QQ_PEER(4, false); else SSB_QQ_PEER(8, false); }
+#undef SSB_QQ_PEER
 #undef SSB_QQ_LAUNCH
 #undef SSB_QQ_ARGS
     SSB_LAUNCHED("adam_qq_kernel");
+    return SSB_OK;
+}
+
+// Displacements from this rank's copy of each exchanged buffer to the other ranks' copies.
+static int peer_offsets(const SsbPeerReplicas* r, bool quantised, PeerOffsets* out) {
+    SSB_REQUIRE(r->world >= 1 && r->world <= SSB_MAX_PEERS && r->self >= 0 && r->self < r->world,
+                "ssb_reduce_adam_broadcast: bad world/self (%d, %d)", r->world, r->self);
+    PeerOffsets po = {};
+    for (int p = 0; p < r->world; ++p) {
+        SSB_REQUIRE(r->grads[p] && r->params[p], "ssb_reduce_adam_broadcast: rank %d's gradient or parameter buffer is NULL", p);
+        SSB_REQUIRE((((uintptr_t)r->grads[p] | (uintptr_t)r->params[p]) & 15) == 0, "ssb_reduce_adam_broadcast: rank %d's buffers must be 16-byte aligned", p);
+        SSB_REQUIRE(!quantised || (r->sh_packed[p] && r->sh_bounds[p] && (((uintptr_t)r->sh_packed[p] | (uintptr_t)r->sh_bounds[p]) & 15) == 0),
+                    "ssb_reduce_adam_broadcast: rank %d's packed SH buffers are NULL or not 16-byte aligned", p);
+        if (p == r->self) continue;
+        const int k = po.n++;
+        po.grads[k] = (int64_t)((char*)r->grads[p] - (char*)r->grads[r->self]);
+        po.params[k] = (int64_t)((char*)r->params[p] - (char*)r->params[r->self]);
+        if (quantised) {
+            po.sh_packed[k] = (int64_t)((char*)r->sh_packed[p] - (char*)r->sh_packed[r->self]);
+            po.sh_bounds[k] = (int64_t)((char*)r->sh_bounds[p] - (char*)r->sh_bounds[r->self]);
+        }
+    }
+    *out = po;
+    return SSB_OK;
+}
+
+}  // namespace ssb
+
+extern "C" {
+
+int ssb_adam_step(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
+                  int64_t first, int64_t count, const SsbAdamConfig* cfg, void* stream) {
+    return ssb::adam_step_impl(params, grads, m1, m2, first, count, cfg, nullptr, nullptr, stream);
+}
+
+int ssb_adam_step_ex(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
+                     int64_t first, int64_t count, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream) {
+    return ssb::adam_step_impl(params, grads, m1, m2, first, count, cfg, extras, nullptr, stream);
+}
+
+int ssb_adam_step_sh_quantized(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds,
+                               void* d_value_packed, float* d_value_bounds, int32_t value_bits,
+                               int64_t first_cell, int64_t numel, int64_t numel_total,
+                               const SsbAdamConfig* cfg, void* stream) {
+    return ssb::adam_sh_quantized_impl(d_grad, d_optim_packed, d_optim_bounds, d_value_packed, d_value_bounds, value_bits, 8, first_cell, numel,
+                                       numel_total, cfg, nullptr, 1, nullptr, stream);
+}
+
+int ssb_adam_step_sh_quantized_ex(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds,
+                                  void* d_value_packed, float* d_value_bounds, int32_t value_bits, int32_t optim_bits,
+                                  int64_t first_cell, int64_t numel, int64_t numel_total,
+                                  const SsbAdamConfig* cfg, const int32_t* d_steps, int32_t cells_per_splat, void* stream) {
+    return ssb::adam_sh_quantized_impl(d_grad, d_optim_packed, d_optim_bounds, d_value_packed, d_value_bounds, value_bits, optim_bits, first_cell,
+                                       numel, numel_total, cfg, d_steps, cells_per_splat, nullptr, stream);
+}
+
+int ssb_reduce_adam_broadcast(const SsbPeerReplicas* replicas, const SsbSplats* params, const SsbSplats* grads,
+                              const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                              int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(replicas && params && grads && m1 && m2 && cfg, "ssb_reduce_adam_broadcast: NULL argument");
+    SSB_REQUIRE(first >= 0 && count >= 0 && first + count <= n_total, "ssb_reduce_adam_broadcast: bad splat range");
+    const bool quantised = sh_state != nullptr;
+    SSB_REQUIRE(quantised == (params->features_sh == nullptr), "ssb_reduce_adam_broadcast: give either fp32 SH inside params or an SsbShAdamState");
+    PeerOffsets po;
+    if (int e = peer_offsets(replicas, quantised && sh_state->value_bits != 32, &po)) return e;
+    // everything the kernels address through a displacement must lie behind this rank's base of that buffer
+    const char* gbase = (const char*)replicas->grads[replicas->self];
+    const char* pbase = (const char*)replicas->params[replicas->self];
+    const float* g_arrays[6] = {grads->means, grads->quats, grads->scales, grads->opacities, grads->features_dc, grads->features_sh};
+    const float* p_arrays[6] = {params->means, params->quats, params->scales, params->opacities, params->features_dc, params->features_sh};
+    for (int k = 0; k < 6; ++k) {
+        SSB_REQUIRE(g_arrays[k] != nullptr && (const char*)g_arrays[k] >= gbase, "ssb_reduce_adam_broadcast: gradient array %d is not inside the exchanged gradient buffer", k);
+        SSB_REQUIRE(k == 5 ? (quantised || (const char*)p_arrays[k] >= pbase) : (p_arrays[k] != nullptr && (const char*)p_arrays[k] >= pbase),
+                    "ssb_reduce_adam_broadcast: parameter array %d is not inside the exchanged parameter buffer", k);
+    }
+    if (quantised) {
+        SSB_REQUIRE(sh_state->d_optim_packed && sh_state->d_optim_bounds && sh_state->d_value_packed, "ssb_reduce_adam_broadcast: NULL SH state");
+        SSB_REQUIRE(sh_state->value_bits == 32 || (sh_state->d_value_packed == replicas->sh_packed[replicas->self] &&
+                                                   (void*)sh_state->d_value_bounds == replicas->sh_bounds[replicas->self]),
+                    "ssb_reduce_adam_broadcast: the packed SH values and bounds must be this rank's exchanged buffers");
+        SSB_REQUIRE((first * 3 * kNumSh) % 256 == 0 && (((first + count) * 3 * kNumSh) % 256 == 0 || first + count == n_total),
+                    "ssb_reduce_adam_broadcast: a rank's range must cover whole 256-cell quantisation blocks (splat ranges in multiples of 256)");
+    }
+    const PeerOffsets* peers = po.n > 0 ? &po : nullptr;
+    SsbAdamExtras ex_local;
+    const SsbAdamExtras* ex = extras;
+    if (!ex && count != n_total) {        // regulariser weights are divided by the model's splat count, not the range's
+        ex_local = SsbAdamExtras{};
+        ex_local.n_total = n_total;
+        ex = cfg->sh_reg_weight != 0.0f ? &ex_local : nullptr;
+    }
+    if (int e = adam_step_impl(params, grads, m1, m2, first, count, cfg, ex, peers, stream)) return e;
+    if (quantised) {
+        const int32_t* steps = extras ? extras->d_steps : nullptr;
+        return adam_sh_quantized_impl(grads->features_sh, sh_state->d_optim_packed, sh_state->d_optim_bounds, sh_state->d_value_packed,
+                                      sh_state->d_value_bounds, sh_state->value_bits, sh_state->optim_bits ? sh_state->optim_bits : 8,
+                                      first * 3 * kNumSh, count * 3 * kNumSh, n_total * 3 * kNumSh, cfg, steps, 3 * kNumSh, peers, stream);
+    }
+    return SSB_OK;
+}
+
+int ssb_exchange_step(const SsbPeerReplicas* replicas, const SsbSplats* params, const SsbSplats* grads,
+                      const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                      int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg, const SsbAdamExtras* extras,
+                      SsbBarrierFn barrier, void* barrier_ctx, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(replicas && barrier, "ssb_exchange_step: NULL argument");
+    // every rank's backward passes are complete before anyone reads a partial gradient
+    if (barrier(barrier_ctx, stream) != 0) {
+        set_error("ssb_exchange_step: a rank did not arrive at the barrier before the exchange; nothing was launched");
+        return SSB_ERR_PEER;
+    }
+    if (int e = ssb_reduce_adam_broadcast(replicas, params, grads, m1, m2, sh_state, first, count, n_total, cfg, extras, stream)) return e;
+    // every replica is complete before anyone's next forward pass
+    if (barrier(barrier_ctx, stream) != 0) {
+        set_error("ssb_exchange_step: a rank did not arrive at the barrier after the exchange; replicas may be incomplete");
+        return SSB_ERR_PEER;
+    }
     return SSB_OK;
 }
 

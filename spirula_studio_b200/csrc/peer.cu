@@ -162,7 +162,9 @@ static int check_table(const SsbPeerTable* t, const char* who, bool f32) {
     for (int s = 0; s < t->n_segments; ++s) {
         const SsbPeerSegment& sg = t->seg[s];
         SSB_REQUIRE(sg.buffer >= 0 && sg.buffer < SSB_MAX_PEER_BUFFERS, "%s: segment %d names buffer %d", who, s, sg.buffer);
-        SSB_REQUIRE(sg.offset_bytes >= 0 && sg.bytes >= 0 && (sg.offset_bytes & 15) == 0, "%s: segment %d must start on a 16-byte boundary", who, s);
+        SSB_REQUIRE(sg.offset_bytes >= 0 && sg.bytes >= 0, "%s: segment %d has a negative offset or length", who, s);
+        if (sg.bytes == 0) continue;                 // an empty range (a rank beyond the last splat) has nothing to align
+        SSB_REQUIRE((sg.offset_bytes & 15) == 0, "%s: segment %d must start on a 16-byte boundary", who, s);
         SSB_REQUIRE(!f32 || (sg.bytes & 3) == 0, "%s: segment %d is not a whole number of floats", who, s);
         for (int p = 0; p < t->world; ++p)
             SSB_REQUIRE(t->base[sg.buffer][p] != nullptr && ((uintptr_t)t->base[sg.buffer][p] & 15) == 0,

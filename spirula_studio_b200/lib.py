@@ -16,6 +16,7 @@ SSB_ERR_CUDA = -2
 SSB_ERR_CAPACITY = -3
 SSB_ERR_OUT_OF_MEMORY = -4
 SSB_ERR_UNSUPPORTED = -5
+SSB_ERR_PEER = -6
 
 CAMERA_PINHOLE, CAMERA_FISHEYE, CAMERA_EQUISOLID, CAMERA_EQUIRECT = 0, 1, 2, 3
 SSB_ACCUM_NONE, SSB_ACCUM_MAX, SSB_ACCUM_SUM, SSB_ACCUM_AVG = 0, 1, 2, 3
@@ -96,6 +97,8 @@ SIGNATURES = {
     "ssb_peer_close": (C.c_int, [_P]),
     "ssb_peer_reduce_f32": (C.c_int, [_P, _P]),
     "ssb_peer_broadcast": (C.c_int, [_P, _P]),
+    "ssb_reduce_adam_broadcast": (C.c_int, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _P]),
+    "ssb_exchange_step": (C.c_int, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P, _P]),
     "ssb_tile_ranges": (C.c_int, [_P, _P, _I64, _I64, _P, _P]),
     "ssb_raster_fwd": (C.c_int, [_P, _I64, _P, _P, _I64, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P]),
     "ssb_raster_bwd": (C.c_int, [_P, _I64, _P, _P, _I64, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _P]),
@@ -203,6 +206,31 @@ def peer_table(world, rank, bases, segments, multicast=None):
     for i, (b, off, nbytes) in enumerate(segments):
         t.seg[i].buffer, t.seg[i].offset_bytes, t.seg[i].bytes = b, off, nbytes
     return t
+
+
+class SsbPeerReplicas(C.Structure):
+    _fields_ = [("world", C.c_int32), ("self", C.c_int32), ("grads", C.c_void_p * MAX_PEERS), ("params", C.c_void_p * MAX_PEERS),
+                ("sh_packed", C.c_void_p * MAX_PEERS), ("sh_bounds", C.c_void_p * MAX_PEERS)]
+
+
+class SsbShAdamState(C.Structure):
+    _fields_ = [("d_optim_packed", C.c_void_p), ("d_optim_bounds", C.c_void_p), ("d_value_packed", C.c_void_p),
+                ("d_value_bounds", C.c_void_p), ("value_bits", C.c_int32), ("optim_bits", C.c_int32)]
+
+
+# int barrier(void* ctx, void* stream): 0 once every rank has arrived (ordered on the stream), non-zero on failure
+BARRIER_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p)
+
+
+def peer_replicas(world, rank, grads, params, sh_packed=None, sh_bounds=None):
+    """Each argument: the device address of every rank's copy of that allocation, as mapped in this process."""
+    r = SsbPeerReplicas()
+    r.world, r.self = world, rank
+    for name, addrs in (("grads", grads), ("params", params), ("sh_packed", sh_packed), ("sh_bounds", sh_bounds)):
+        arr = getattr(r, name)
+        for p_, a in enumerate(addrs or []):
+            arr[p_] = a or None
+    return r
 
 
 class _DevicePtr:

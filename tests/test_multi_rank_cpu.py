@@ -94,3 +94,76 @@ def test_two_rank_iteration_equals_single_process(tmp_path):
     m0, m1 = (np.load(tmp_path / f"means_{r}.npy") for r in range(2))
     assert np.array_equal(m0, m1)                                   # replicas stay identical
     assert np.abs(m0 - sp["means"]).max() > 0
+
+
+# ---- what a rank sees when another rank is gone ---------------------------------------------------------------
+# No GPU is involved: the failure is made on the host (a rank that raises before the exchange), the barrier of the
+# multi-GPU step is a gloo all-reduce with a short timeout, and ssb_exchange_step must come back with SSB_ERR_PEER
+# before it launches anything.
+
+def test_exchange_step_returns_peer_error_when_the_barrier_fails():
+    import ctypes as C
+    from spirula_studio_b200 import lib as L
+    lib = L.load()
+    calls = []
+
+    def failing_barrier(ctx, stream):
+        calls.append(1)
+        return 1
+
+    cb = L.BARRIER_FN(failing_barrier)
+    rep = L.SsbPeerReplicas()
+    rep.world, rep.self = 2, 0
+    s = L.SsbSplats()
+    cfg = L.SsbAdamConfig(1e-3, 1e-3, 1e-3, 1e-3, 1e-3, 1e-3, 0.0, 1.0, 1, 0)
+    st = lib.ssb_exchange_step(C.byref(rep), C.byref(s), C.byref(s), C.byref(s), C.byref(s), None, 0, 16, 16, C.byref(cfg), None, cb, None, None)
+    assert st == L.SSB_ERR_PEER and calls == [1]                    # the first barrier failed: nothing else was attempted
+    assert b"did not arrive" in lib.ssb_last_error_string()
+    assert lib.ssb_exchange_step(C.byref(rep), C.byref(s), C.byref(s), C.byref(s), C.byref(s), None, 0, 16, 16, C.byref(cfg), None,
+                                 L.BARRIER_FN(), None, None) == L.SSB_ERR_INVALID_ARGUMENT      # no barrier given
+
+
+def _failing_worker(rank, world, port, out_dir):
+    import ctypes as C
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    from spirula_studio_b200 import lib as L
+    lib = L.load()
+    token = torch.zeros(1)
+    dist.all_reduce(token)                       # both ranks are up
+    if rank == 1:
+        # this rank fails between two iterations, with nothing of its own in flight, and leaves
+        with open(os.path.join(out_dir, "rank1.txt"), "w") as f:
+            f.write("raised before the exchange")
+        os._exit(0)
+
+    def barrier(ctx, stream):
+        try:
+            dist.all_reduce(token)
+            return 0
+        except Exception:
+            return 1
+
+    cb = L.BARRIER_FN(barrier)
+    rep = L.SsbPeerReplicas()
+    rep.world, rep.self = 2, 0
+    s = L.SsbSplats()
+    cfg = L.SsbAdamConfig(1e-3, 1e-3, 1e-3, 1e-3, 1e-3, 1e-3, 0.0, 1.0, 1, 0)
+    t0 = time.time()
+    st = lib.ssb_exchange_step(C.byref(rep), C.byref(s), C.byref(s), C.byref(s), C.byref(s), None, 0, 16, 16, C.byref(cfg), None, cb, None, None)
+    with open(os.path.join(out_dir, "rank0.txt"), "w") as f:
+        f.write(f"{st} {time.time() - t0:.2f}")
+    os._exit(0)                                  # the process group cannot be torn down cleanly without its peer
+
+
+def test_a_rank_that_left_is_reported_within_the_timeout(tmp_path):
+    world, port = 2, 31000 + os.getpid() % 2000
+    mp.spawn(_failing_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    from spirula_studio_b200 import lib as L
+    status, seconds = (tmp_path / "rank0.txt").read_text().split()
+    assert int(status) == L.SSB_ERR_PEER
+    assert float(seconds) < 30.0                 # the process-group timeout is 3 s; the step never waits for ever
+    assert (tmp_path / "rank1.txt").exists()

@@ -258,7 +258,9 @@ def run_ours(args, cfg, rank, world, local_rank):
     v0, nv = shard(total_views, world, rank)
     splats = scenes.make_splats(cfg)
     vm, K = scenes.make_cameras(cfg)
-    grad_sync = os.environ.get("SSB_GRAD_SYNC", "peer")          # "peer" (own kernels over NVLink) or "nccl" (all-reduce)
+    # "multimem" (own fused kernels through the NVSwitch multicast address; falls back to "peer" where symmetric memory
+    # cannot be set up), "peer" (the same kernels with per-peer loads and stores) or "nccl" (all-reduce + full Adam)
+    grad_sync = os.environ.get("SSB_GRAD_SYNC", "multimem")
     tr = Trainer(cfg, splats, device=dev, world_size=world, rank=rank, grad_sync=grad_sync)
     del splats
     # this rank's views, grouped by camera kind (one kind for every workload but the wide-camera one)
@@ -372,8 +374,8 @@ def run_ours(args, cfg, rank, world, local_rank):
                            "gbs": round(ab / (adam_ms * 1e-3) / 1e9, 1) if adam_ms > 0 else 0.0,
                            "frac_of_hbm": round(ab / (adam_ms * 1e-3) / 1e9 / peak, 4) if adam_ms > 0 else 0.0}
         kernels["allreduce"] = {"ms": round(comm_ms, 4), "bytes": int(tr.grads_flat.numel() * 4), "mode": tr.grad_sync,
-                                "note": "peer: barrier + this rank's range summed from the peers' buffers (the parameter broadcast and a second "
-                                        "barrier are inside the adam time); nccl: all-reduce of the whole gradient buffer"}
+                                "note": "peer / multimem: nothing here, the sum over the ranks happens inside the optimiser kernels (adam time, with "
+                                        "both barriers); nccl: all-reduce of the whole gradient buffer"}
         for kind in range(1, n_kinds):       # further camera kinds: per-view stage times only
             kw, kh = kind_dims[kind]
             kernels[f"kind{kind}_{kw}x{kh}"] = {name: round(float(stage_ms[kind][i] / max(n_prof[kind], 1)), 4) for i, name in enumerate(L.STAGES)}
@@ -398,8 +400,9 @@ def run_ours(args, cfg, rank, world, local_rank):
             "config": {"workload": cfg.name, "n_splats": cfg.n_splats, "views_per_iteration": total_views, "views_per_gpu": nv,
                        "resolution": [cfg.width, cfg.height], "sh_value_bits": cfg.sh_value_bits, "sh_optim_bits": cfg.sh_optim_bits,
                        "parallelism": f"views sharded over {world} GPU(s), replicated parameters, gradients combined by " +
-                                      ("this library's peer-memory reduce + sharded Adam + broadcast" if tr.grad_sync == "peer" else
-                                       "an NCCL all-reduce" if tr.grad_sync == "nccl" else "nothing (one GPU)"),
+                                      ("this library's fused reduce + sharded Adam + broadcast kernels over peer memory" if tr.grad_sync == "peer" else
+                                       "this library's fused reduce + sharded Adam + broadcast kernels through the NVSwitch multicast address"
+                                       if tr.grad_sync == "multimem" else "an NCCL all-reduce" if tr.grad_sync == "nccl" else "nothing (one GPU)"),
                        "pairs_per_view": int(pairs), "visible_per_view": visible,
                        "l2": "inputs (parameters, gradients, moments, targets: > 1 GB) exceed the 126 MB L2; no flush between iterations"},
             "e2e": {"value": 1e3 / e2e_ms, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": 12},

@@ -468,6 +468,14 @@ typedef struct SsbPeerReplicas {
     void* params[SSB_MAX_PEERS];
     void* sh_packed[SSB_MAX_PEERS];
     void* sh_bounds[SSB_MAX_PEERS];
+    /* Optional NVSwitch multicast address of each allocation (one address that reaches every rank's copy; NULL = none).
+     * When every exchanged allocation has one, gradients are read with multimem.ld_reduce (the switch adds the ranks'
+     * copies: a rank receives its range once instead of once per peer) and parameters are written with multimem.st (one
+     * store lands in every replica).  Per NVLink direction a GPU then moves about two thirds of the bytes. */
+    void* mc_grads;
+    void* mc_params;
+    void* mc_sh_packed;
+    void* mc_sh_bounds;
 } SsbPeerReplicas;
 /* Quantised SH values and optimiser state of ssb_adam_step_sh_quantized_ex, as one argument. */
 typedef struct SsbShAdamState {

@@ -37,10 +37,45 @@ struct PeerOffsets {
     int32_t n;        // other ranks, 0..7
     int32_t pad;
     int64_t grads[SSB_MAX_PEERS - 1], params[SSB_MAX_PEERS - 1], sh_packed[SSB_MAX_PEERS - 1], sh_bounds[SSB_MAX_PEERS - 1];   // bytes
+    // PEER == 2: displacement from this rank's copy to the buffer's NVSwitch multicast address, one address that reaches
+    // every rank's copy: a load from it returns the switch's sum over all ranks (this one included), a store to it lands in
+    // every replica.  Each rank then receives its range once instead of once per peer, and sends each update once.
+    int64_t mc_grads, mc_params, mc_sh_packed, mc_sh_bounds;
 };
 
-template <bool PEER>
+__device__ __forceinline__ float4 multimem_sum4(const void* mc) {
+    float4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(mc) : "memory");
+    return r;
+}
+__device__ __forceinline__ float multimem_sum1(const void* mc) {
+    float r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.f32 %0, [%1];" : "=f"(r) : "l"(mc) : "memory");
+    return r;
+}
+__device__ __forceinline__ void multimem_store(void* mc, const uint4& v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 :: "l"(mc), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w)) : "memory");
+}
+__device__ __forceinline__ void multimem_store(void* mc, const uint2& v) {
+    asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" :: "l"(mc), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)) : "memory");
+}
+__device__ __forceinline__ void multimem_store(void* mc, uint32_t v) {
+    asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" :: "l"(mc), "f"(__uint_as_float(v)) : "memory");
+}
+
+// 16-byte load that bypasses L1, as a volatile statement: a thread's loads from all ranks are issued back to back, in
+// program order, before the first sum needs one of them.
+__device__ __forceinline__ float4 ld_cv4(const void* p) {
+    float4 r;
+    asm volatile("ld.global.cv.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(p));
+    return r;
+}
+
+template <int PEER>
 __device__ __forceinline__ float grad_sum(const float* own, const PeerOffsets& po) {
+    if constexpr (PEER == 2) return multimem_sum1((const char*)own + po.mc_grads);
     float v = *own;
     if (PEER) {
         float x[SSB_MAX_PEERS - 1];
@@ -51,22 +86,84 @@ __device__ __forceinline__ float grad_sum(const float* own, const PeerOffsets& p
     }
     return v;
 }
-template <bool PEER>
+template <int PEER>
 __device__ __forceinline__ float4 grad_sum4(const float4* own, const PeerOffsets& po) {
-    float4 v = *own;
-    if (PEER) {
+    if constexpr (!PEER) {
+        return *own;
+    } else if constexpr (PEER == 2) {
+        return multimem_sum4((const char*)own + po.mc_grads);
+    } else {
         float4 x[SSB_MAX_PEERS - 1];
 #pragma unroll
-        for (int k = 0; k < SSB_MAX_PEERS - 1; ++k)
-            x[k] = k < po.n ? __ldcv((const float4*)((const char*)own + po.grads[k])) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < SSB_MAX_PEERS - 1; ++k) x[k] = ld_cv4((const char*)own + (k < po.n ? po.grads[k] : 0));   // unused slots re-read the own copy
+        float4 v = *own;
 #pragma unroll
-        for (int k = 0; k < SSB_MAX_PEERS - 1; ++k) { v.x += x[k].x; v.y += x[k].y; v.z += x[k].z; v.w += x[k].w; }
+        for (int k = 0; k < SSB_MAX_PEERS - 1; ++k)
+            if (k < po.n) { v.x += x[k].x; v.y += x[k].y; v.z += x[k].z; v.w += x[k].w; }
+        return v;
     }
-    return v;
 }
+// dst[0..count) (shared memory) = this rank's own[0..count) + every other rank's, 16 bytes per thread per step, the loads
+// of all ranks in flight together; `own` must be 16-byte aligned.  Whole CTA; the caller synchronises afterwards.
+template <int THREADS, int PEER>
+__device__ __forceinline__ void peer_sum_to_shared(float* dst, const float* own, int count, const PeerOffsets& po) {
+    const int n_vec = count >> 2;
+    if constexpr (PEER == 2) {
+        for (int v = threadIdx.x; v < n_vec; v += THREADS) ((float4*)dst)[v] = multimem_sum4((const char*)((const float4*)own + v) + po.mc_grads);
+        for (int i = (n_vec << 2) + threadIdx.x; i < count; i += THREADS) dst[i] = multimem_sum1((const char*)(own + i) + po.mc_grads);
+    } else {
+        for (int v = threadIdx.x; v < n_vec; v += THREADS) {
+            const char* at = (const char*)((const float4*)own + v);
+            float4 x[SSB_MAX_PEERS - 1];
+#pragma unroll
+            for (int k = 0; k < SSB_MAX_PEERS - 1; ++k) x[k] = ld_cv4(at + (k < po.n ? po.grads[k] : 0));   // unused slots re-read the own copy
+            float4 acc = *(const float4*)at;
+#pragma unroll
+            for (int k = 0; k < SSB_MAX_PEERS - 1; ++k)
+                if (k < po.n) { acc.x += x[k].x; acc.y += x[k].y; acc.z += x[k].z; acc.w += x[k].w; }
+            ((float4*)dst)[v] = acc;
+        }
+        for (int i = (n_vec << 2) + threadIdx.x; i < count; i += THREADS) {
+            float acc = own[i];
+            for (int k = 0; k < po.n; ++k) acc += __ldcv((const float*)((const char*)(own + i) + po.grads[k]));
+            dst[i] = acc;
+        }
+    }
+}
+
+// own[0..count) and every other rank's copy of it = src[0..count) (shared memory), 16-byte stores.
+template <int THREADS, int PEER>
+__device__ __forceinline__ void shared_to_all(float* own, const float* src, int count, const PeerOffsets& po) {
+    const int n_vec = count >> 2;
+    if constexpr (PEER == 2) {
+        for (int v = threadIdx.x; v < n_vec; v += THREADS) multimem_store((char*)((float4*)own + v) + po.mc_params, ((const uint4*)src)[v]);
+        for (int i = (n_vec << 2) + threadIdx.x; i < count; i += THREADS) multimem_store((char*)(own + i) + po.mc_params, __float_as_uint(src[i]));
+    } else {
+        for (int v = threadIdx.x; v < n_vec; v += THREADS) {
+            const float4 x = ((const float4*)src)[v];
+            char* at = (char*)((float4*)own + v);
+            *(float4*)at = x;
+#pragma unroll
+            for (int k = 0; k < SSB_MAX_PEERS - 1; ++k)
+                if (k < po.n) *(float4*)(at + po.params[k]) = x;
+        }
+        for (int i = (n_vec << 2) + threadIdx.x; i < count; i += THREADS) {
+            own[i] = src[i];
+            for (int k = 0; k < po.n; ++k) *(float*)((char*)(own + i) + po.params[k]) = src[i];
+        }
+    }
+}
+
 // own copy and, in peer mode, every other rank's copy
-template <bool PEER, class T>
-__device__ __forceinline__ void store_all(T* own, const T& v, const PeerOffsets& po, const int64_t (&disp)[SSB_MAX_PEERS - 1]) {
+template <int PEER, class T>
+__device__ __forceinline__ void store_all(T* own, const T& v, const PeerOffsets& po, const int64_t (&disp)[SSB_MAX_PEERS - 1], int64_t mc_disp = 0) {
+    if constexpr (PEER == 2 && (sizeof(T) == 16 || sizeof(T) == 8 || sizeof(T) == 4)) {
+        // one store through the switch reaches every replica, this rank's included
+        if constexpr (sizeof(T) == 16) multimem_store((char*)own + mc_disp, *(const uint4*)&v);
+        else if constexpr (sizeof(T) == 8) multimem_store((char*)own + mc_disp, *(const uint2*)&v);
+        else multimem_store((char*)own + mc_disp, *(const uint32_t*)&v);
+        return;
+    }
     *own = v;
     if (PEER) {
 #pragma unroll
@@ -127,12 +224,33 @@ __device__ __forceinline__ void per_splat_reg_grads(const float s[3], float o, c
 
 // geometry (means, quats, scales, opacities) + features_dc, one thread per splat.
 // EX adds the per-splat regularisers, the scale-agnostic mean update and per-splat step counters.
-template <bool EX, bool PEER>
+template <bool EX, int PEER>
 __global__ void __launch_bounds__(256) adam_geometry_kernel(
     SsbSplats p, SsbSplats g, SsbSplats m1, SsbSplats m2, int64_t first, int64_t count, SsbAdamConfig cfg,
     float ibc1, float ibc2, float dc_decay, SsbAdamExtras ex, PeerOffsets po) {
     int64_t i = first + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= first + count) return;
+    // Peer mode: the CTA's 256 splats are contiguous in each array, so their gradients are summed over the ranks
+    // with coalesced 16-byte loads into shared memory, each thread then works from there, leaves its updated
+    // parameters in the same place, and the CTA stores them into every replica with 16-byte stores.
+    constexpr int kStage = PEER ? 14 * 256 : 4;
+    __shared__ __align__(16) float stage[kStage];
+    const int64_t b0 = first + (int64_t)blockIdx.x * 256;
+    const int nb = (int)min((int64_t)256, first + count - b0);
+    SsbSplats g_own = g;                 // where zeroing goes
+    SsbSplats out = p;                   // where updated parameters go
+    if constexpr (PEER) {
+        float* s_means = stage, *s_quats = stage + 768, *s_scales = stage + 1792, *s_opac = stage + 2560, *s_dc = stage + 2816;
+        peer_sum_to_shared<256, PEER>(s_means, g.means + 3 * b0, 3 * nb, po);
+        peer_sum_to_shared<256, PEER>(s_quats, g.quats + 4 * b0, 4 * nb, po);
+        peer_sum_to_shared<256, PEER>(s_scales, g.scales + 3 * b0, 3 * nb, po);
+        peer_sum_to_shared<256, PEER>(s_opac, g.opacities + b0, nb, po);
+        peer_sum_to_shared<256, PEER>(s_dc, g.features_dc + 3 * b0, 3 * nb, po);
+        __syncthreads();
+        // indexed with the global splat index like the arrays they stand in for
+        g.means = s_means - 3 * b0; g.quats = s_quats - 4 * b0; g.scales = s_scales - 3 * b0; g.opacities = s_opac - b0; g.features_dc = s_dc - 3 * b0;
+        out = g;
+    }
+    if (i < first + count) {
     const float gs = cfg.grad_scale;
     const bool zg = cfg.zero_grad != 0;
     float reg_s[3] = {0.f, 0.f, 0.f}, reg_o = 0.f, reg_q[4] = {0.f, 0.f, 0.f, 0.f};
@@ -157,12 +275,12 @@ __global__ void __launch_bounds__(256) adam_geometry_kernel(
     for (int k = 0; k < 3; ++k) {
         int64_t q = 3 * i + k;
         float a = m1.scales[q], b = m2.scales[q];
-        store_all<PEER>(&p.scales[q], adam_update(p.scales[q], reg_s[k] + gs * grad_sum<PEER>(&g.scales[q], po), a, b, lr_s, ibc2), po, po.params);
+        out.scales[q] = adam_update(p.scales[q], reg_s[k] + gs * g.scales[q], a, b, lr_s, ibc2);
         m1.scales[q] = a; m2.scales[q] = b;
-        if (zg) g.scales[q] = 0.f;
+        if (zg) g_own.scales[q] = 0.f;
     }
     {
-        float4 q4 = ((float4*)p.quats)[i], g4 = grad_sum4<PEER>((const float4*)g.quats + i, po);
+        float4 q4 = ((float4*)p.quats)[i], g4 = ((float4*)g.quats)[i];
         float4 a4 = ((float4*)m1.quats)[i], b4 = ((float4*)m2.quats)[i];
         float inv = 1.0f / sqrtf(q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w);
         float q[4] = {q4.x * inv, q4.y * inv, q4.z * inv, q4.w * inv};
@@ -177,18 +295,18 @@ __global__ void __launch_bounds__(256) adam_geometry_kernel(
             n2 += u[k] * u[k];
         }
         float inv2 = 1.0f / sqrtf(n2);
-        store_all<PEER>((float4*)p.quats + i, make_float4(u[0] * inv2, u[1] * inv2, u[2] * inv2, u[3] * inv2), po, po.params);
+        ((float4*)out.quats)[i] = make_float4(u[0] * inv2, u[1] * inv2, u[2] * inv2, u[3] * inv2);
         ((float4*)m1.quats)[i] = make_float4(a[0], a[1], a[2], a[3]);
         ((float4*)m2.quats)[i] = make_float4(b[0], b[1], b[2], b[3]);
-        if (zg) ((float4*)g.quats)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (zg) ((float4*)g_own.quats)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     {
         float a = m1.opacities[i], b = m2.opacities[i];
-        store_all<PEER>(&p.opacities[i], adam_update(p.opacities[i], reg_o + gs * grad_sum<PEER>(&g.opacities[i], po), a, b, lr_o, ibc2), po, po.params);
+        out.opacities[i] = adam_update(p.opacities[i], reg_o + gs * g.opacities[i], a, b, lr_o, ibc2);
         m1.opacities[i] = a; m2.opacities[i] = b;
-        if (zg) g.opacities[i] = 0.f;
+        if (zg) g_own.opacities[i] = 0.f;
     }
-    const float gm[3] = {grad_sum<PEER>(&g.means[3 * i], po), grad_sum<PEER>(&g.means[3 * i + 1], po), grad_sum<PEER>(&g.means[3 * i + 2], po)};
+    const float gm[3] = {g.means[3 * i], g.means[3 * i + 1], g.means[3 * i + 2]};
     if (EX && ex.d_densify_score) {
         const float vx = gs * gm[0], vy = gs * gm[1], vz = gs * gm[2];
         ex.d_densify_score[i] = expf(fmaxf(fmaxf(s_old[0], s_old[1]), s_old[2])) * sqrtf(vx * vx + vy * vy + vz * vz);
@@ -214,37 +332,46 @@ __global__ void __launch_bounds__(256) adam_geometry_kernel(
             float a = m1.means[q], b = m2.means[q];
             a = kBeta1 * a + (1.f - kBeta1) * num;
             b = kBeta2 * b + (1.f - kBeta2) * v[k] * v[k] * den * den;
-            store_all<PEER>(&p.means[q], p.means[q] - lr_m * a / (sqrtf(b * ibc2) + kAdamEps), po, po.params);
+            out.means[q] = p.means[q] - lr_m * a / (sqrtf(b * ibc2) + kAdamEps);
             m1.means[q] = a; m2.means[q] = b;
-            if (zg) g.means[q] = 0.f;
+            if (zg) g_own.means[q] = 0.f;
         }
     } else {
 #pragma unroll
         for (int k = 0; k < 3; ++k) {
             int64_t q = 3 * i + k;
             float a = m1.means[q], b = m2.means[q];
-            store_all<PEER>(&p.means[q], adam_update(p.means[q], gs * gm[k], a, b, lr_m, ibc2), po, po.params);
+            out.means[q] = adam_update(p.means[q], gs * gm[k], a, b, lr_m, ibc2);
             m1.means[q] = a; m2.means[q] = b;
-            if (zg) g.means[q] = 0.f;
+            if (zg) g_own.means[q] = 0.f;
         }
     }
     const float dc_off = 0.5f / 0.28209479177387814f;
 #pragma unroll
     for (int k = 0; k < 3; ++k) {
         int64_t q = 3 * i + k;
-        float x = p.features_dc[q], v = grad_sum<PEER>(&g.features_dc[q], po);
+        float x = p.features_dc[q], v = g.features_dc[q];
         if (!isfinite(v)) v = 0.f;
         v *= gs;
         v += dc_decay * (fmaxf(x - dc_off, 0.0f) + fminf(x + dc_off, 0.0f));
         float a = m1.features_dc[q], b = m2.features_dc[q];
-        store_all<PEER>(&p.features_dc[q], adam_update(x, v, a, b, lr_dc, ibc2), po, po.params);
+        out.features_dc[q] = adam_update(x, v, a, b, lr_dc, ibc2);
         m1.features_dc[q] = a; m2.features_dc[q] = b;
-        if (zg) g.features_dc[q] = 0.f;
+        if (zg) g_own.features_dc[q] = 0.f;
+    }
+    }   // this thread's splat
+    if constexpr (PEER) {
+        __syncthreads();
+        shared_to_all<256, PEER>(p.means + 3 * b0, stage, 3 * nb, po);
+        shared_to_all<256, PEER>(p.quats + 4 * b0, stage + 768, 4 * nb, po);
+        shared_to_all<256, PEER>(p.scales + 3 * b0, stage + 1792, 3 * nb, po);
+        shared_to_all<256, PEER>(p.opacities + b0, stage + 2560, nb, po);
+        shared_to_all<256, PEER>(p.features_dc + 3 * b0, stage + 2816, 3 * nb, po);
     }
 }
 
 // element-wise Adam (features_sh), four floats per thread
-template <bool PEER>
+template <int PEER>
 __global__ void __launch_bounds__(256) adam_plain_kernel(
     float* __restrict__ param, float* __restrict__ grad, float* __restrict__ m1, float* __restrict__ m2, int64_t numel,
     float lr_ibc1, float ibc2, float decay, float decay_offset, float grad_scale, int zero_grad,
@@ -260,7 +387,7 @@ __global__ void __launch_bounds__(256) adam_plain_kernel(
             gk *= grad_scale;
             gk += decay * (fmaxf(x - decay_offset, 0.0f) + fminf(x + decay_offset, 0.0f));
             float a = m1[i], b = m2[i];
-            store_all<PEER>(param + i, adam_update(x, gk, a, b, lr * inv_bias_correction(kBeta1, step), inv_bias_correction(kBeta2, step)), po, po.params);
+            store_all<PEER>(param + i, adam_update(x, gk, a, b, lr * inv_bias_correction(kBeta1, step), inv_bias_correction(kBeta2, step)), po, po.params, po.mc_params);
             m1[i] = a; m2[i] = b;
             if (zero_grad) grad[i] = 0.f;
         }
@@ -276,7 +403,7 @@ __global__ void __launch_bounds__(256) adam_plain_kernel(
             gk += decay * (fmaxf(xs[k] - decay_offset, 0.0f) + fminf(xs[k] + decay_offset, 0.0f));
             xs[k] = adam_update(xs[k], gk, as[k], bs[k], lr_ibc1, ibc2);
         }
-        store_all<PEER>((float4*)(param + i4), make_float4(xs[0], xs[1], xs[2], xs[3]), po, po.params);
+        store_all<PEER>((float4*)(param + i4), make_float4(xs[0], xs[1], xs[2], xs[3]), po, po.params, po.mc_params);
         *(float4*)(m1 + i4) = make_float4(as[0], as[1], as[2], as[3]);
         *(float4*)(m2 + i4) = make_float4(bs[0], bs[1], bs[2], bs[3]);
         if (zero_grad) *(float4*)(grad + i4) = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -287,7 +414,7 @@ __global__ void __launch_bounds__(256) adam_plain_kernel(
             gk *= grad_scale;
             gk += decay * (fmaxf(x - decay_offset, 0.0f) + fminf(x + decay_offset, 0.0f));
             float a = m1[i], b = m2[i];
-            store_all<PEER>(param + i, adam_update(x, gk, a, b, lr_ibc1, ibc2), po, po.params);
+            store_all<PEER>(param + i, adam_update(x, gk, a, b, lr_ibc1, ibc2), po, po.params, po.mc_params);
             m1[i] = a; m2[i] = b;
             if (zero_grad) grad[i] = 0.f;
         }
@@ -348,7 +475,7 @@ __device__ __forceinline__ void block_minmax(const float (&vmin)[NMIN], const fl
 // STEPS: per-splat step counters (compiled apart: the power function costs the plain path registers).
 // PEER: gradients summed over the ranks, value codes and value bounds stored into every replica (the values must then be
 // packed, or, when plain fp32, part of the parameter buffer: their displacements are taken accordingly).
-template <int VALUE_BITS, int OPTIM_BITS, bool STEPS, bool PEER>
+template <int VALUE_BITS, int OPTIM_BITS, bool STEPS, int PEER>
 __global__ void __launch_bounds__(64) adam_qq_kernel(
     float* __restrict__ grad, uint8_t* __restrict__ optim_packed, float4* __restrict__ optim_bounds,
     uint8_t* __restrict__ value_packed, float2* __restrict__ value_bounds, int64_t first_block, int64_t numel_total,
@@ -476,10 +603,11 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
         oout[k] = kNibbles ? (uqc | (sqc << 4)) : (uqc | (sqc << 8));
     }
     const int64_t (&vdisp)[SSB_MAX_PEERS - 1] = kPlainValue ? po.params : po.sh_packed;
+    const int64_t vmc = kPlainValue ? po.mc_params : po.mc_sh_packed;
     if (full) {
-        if (kPlainValue) store_all<PEER>((uint4*)((float*)value_packed + idx0), make_uint4(vout[0], vout[1], vout[2], vout[3]), po, vdisp);
-        else if (VALUE_BITS == 16) store_all<PEER>((ushort4*)((uint16_t*)value_packed + idx0), make_ushort4(vout[0], vout[1], vout[2], vout[3]), po, vdisp);
-        else store_all<PEER>((uchar4*)(value_packed + idx0), make_uchar4(vout[0], vout[1], vout[2], vout[3]), po, vdisp);
+        if (kPlainValue) store_all<PEER>((uint4*)((float*)value_packed + idx0), make_uint4(vout[0], vout[1], vout[2], vout[3]), po, vdisp, vmc);
+        else if (VALUE_BITS == 16) store_all<PEER>((ushort4*)((uint16_t*)value_packed + idx0), make_ushort4(vout[0], vout[1], vout[2], vout[3]), po, vdisp, vmc);
+        else store_all<PEER>((uchar4*)(value_packed + idx0), make_uchar4(vout[0], vout[1], vout[2], vout[3]), po, vdisp, vmc);
         if (kNibbles) *(uint32_t*)(optim_packed + idx0) = oout[0] | (oout[1] << 8) | (oout[2] << 16) | (oout[3] << 24);
         else *(uint2*)(optim_packed + 2 * idx0) = make_uint2(oout[0] | (oout[1] << 16), oout[2] | (oout[3] << 16));
     } else {
@@ -487,7 +615,7 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
         for (int k = 0; k < 4; ++k)
             if (inside[k]) {
                 const int64_t idx = idx0 + k;
-                if (kPlainValue) store_all<PEER>((uint32_t*)value_packed + idx, vout[k], po, vdisp);
+                if (kPlainValue) store_all<PEER>((uint32_t*)value_packed + idx, vout[k], po, vdisp, vmc);
                 else if (VALUE_BITS == 8) store_all<PEER>(value_packed + idx, (uint8_t)vout[k], po, vdisp);
                 else store_all<PEER>((uint16_t*)value_packed + idx, (uint16_t)vout[k], po, vdisp);
                 if (kNibbles) optim_packed[idx] = (uint8_t)oout[k];
@@ -495,7 +623,7 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
             }
     }
     if (threadIdx.x == 0) {
-        if (!kPlainValue) store_all<PEER>(value_bounds + blk, make_float2(vmin, vmax), po, po.sh_bounds);
+        if (!kPlainValue) store_all<PEER>(value_bounds + blk, make_float2(vmin, vmax), po, po.sh_bounds, po.mc_sh_bounds);
         optim_bounds[blk] = make_float4(umin, umax, smin, smax);
     }
 }
@@ -555,8 +683,10 @@ static int adam_step_impl(const SsbSplats* params, const SsbSplats* grads, const
     const SsbAdamExtras no_extras = {};
 #define SSB_GEO(EX, PEER) adam_geometry_kernel<EX, PEER><<<blocks, 256, 0, st>>>(*params, *grads, *m1, *m2, first, count, *cfg, ibc1, ibc2, dc_decay, \
                                                                             EX ? *extras : no_extras, PEER ? *peers : none)
-    if (extras) { if (peers) SSB_GEO(true, true); else SSB_GEO(true, false); }
-    else { if (peers) SSB_GEO(false, true); else SSB_GEO(false, false); }
+    // multicast mode is built for the plain launch only; the optional parts use per-peer loads and stores
+    const bool mc = peers && peers->mc_grads != 0 && peers->mc_params != 0;
+    if (extras) { if (peers) SSB_GEO(true, 1); else SSB_GEO(true, 0); }
+    else { if (mc) SSB_GEO(false, 2); else if (peers) SSB_GEO(false, 1); else SSB_GEO(false, 0); }
 #undef SSB_GEO
     SSB_LAUNCHED("adam_geometry_kernel");
     if (params->features_sh) {
@@ -568,7 +698,7 @@ static int adam_step_impl(const SsbSplats* params, const SsbSplats* grads, const
 #define SSB_PLAIN(PEER) adam_plain_kernel<PEER><<<pblocks, 256, 0, st>>>( \
             params->features_sh + off, grads->features_sh + off, m1->features_sh + off, m2->features_sh + off, numel, \
             cfg->lr_features_sh * ibc1, ibc2, sh_decay, 0.0f, cfg->grad_scale, cfg->zero_grad, steps, 3 * kNumSh, cfg->lr_features_sh, PEER ? *peers : none)
-        if (peers) SSB_PLAIN(true); else SSB_PLAIN(false);
+        if (mc && !steps) SSB_PLAIN(2); else if (peers) SSB_PLAIN(1); else SSB_PLAIN(0);
 #undef SSB_PLAIN
         SSB_LAUNCHED("adam_plain_kernel");
     }
@@ -601,9 +731,13 @@ static int adam_sh_quantized_impl(float* d_grad, uint8_t* d_optim_packed, float*
         else if (value_bits == 8) adam_qq_kernel<8, OB, ST, PEER><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS(PEER)); \
         else adam_qq_kernel<16, OB, ST, PEER><<<blocks, 64, 0, (cudaStream_t)stream>>>(SSB_QQ_ARGS(PEER)); \
     } while (0)
-#define SSB_QQ_PEER(OB, ST) do { if (peers) SSB_QQ_LAUNCH(OB, ST, true); else SSB_QQ_LAUNCH(OB, ST, false); } while (0)
+#define SSB_QQ_PEER(OB, ST) do { if (peers) SSB_QQ_LAUNCH(OB, ST, 1); else SSB_QQ_LAUNCH(OB, ST, 0); } while (0)
+    // multicast mode is built for the default state layout (8-bit state, one step counter) only
+    const bool mc = peers && peers->mc_grads != 0 && (value_bits == 32 ? peers->mc_params != 0 : (peers->mc_sh_packed != 0 && peers->mc_sh_bounds != 0));
     if (d_steps) { if (optim_bits == 4) SSB_QQ_PEER(4, true); else SSB_QQ_PEER(8, true); }
-    else { if (optim_bits == 4) SSB_QQ_PEER(4, false); else SSB_QQ_PEER(8, false); }
+    else if (optim_bits == 4) SSB_QQ_PEER(4, false);
+    else if (mc) SSB_QQ_LAUNCH(8, false, 2);
+    else SSB_QQ_PEER(8, false);
 #undef SSB_QQ_PEER
 #undef SSB_QQ_LAUNCH
 #undef SSB_QQ_ARGS
@@ -628,6 +762,18 @@ static int peer_offsets(const SsbPeerReplicas* r, bool quantised, PeerOffsets* o
         if (quantised) {
             po.sh_packed[k] = (int64_t)((char*)r->sh_packed[p] - (char*)r->sh_packed[r->self]);
             po.sh_bounds[k] = (int64_t)((char*)r->sh_bounds[p] - (char*)r->sh_bounds[r->self]);
+        }
+    }
+    // multicast addresses: used only when every exchanged buffer has one
+    const bool mc = r->mc_grads && r->mc_params && (!quantised || (r->mc_sh_packed && r->mc_sh_bounds)) && r->world > 1;
+    if (mc) {
+        SSB_REQUIRE((((uintptr_t)r->mc_grads | (uintptr_t)r->mc_params | (uintptr_t)r->mc_sh_packed | (uintptr_t)r->mc_sh_bounds) & 15) == 0,
+                    "ssb_reduce_adam_broadcast: multicast addresses must be 16-byte aligned");
+        po.mc_grads = (int64_t)((char*)r->mc_grads - (char*)r->grads[r->self]);
+        po.mc_params = (int64_t)((char*)r->mc_params - (char*)r->params[r->self]);
+        if (quantised) {
+            po.mc_sh_packed = (int64_t)((char*)r->mc_sh_packed - (char*)r->sh_packed[r->self]);
+            po.mc_sh_bounds = (int64_t)((char*)r->mc_sh_bounds - (char*)r->sh_bounds[r->self]);
         }
     }
     *out = po;
@@ -693,6 +839,12 @@ int ssb_reduce_adam_broadcast(const SsbPeerReplicas* replicas, const SsbSplats* 
                     "ssb_reduce_adam_broadcast: a rank's range must cover whole 256-cell quantisation blocks (splat ranges in multiples of 256)");
     }
     const PeerOffsets* peers = po.n > 0 ? &po : nullptr;
+    if (peers) {
+        // the kernels move a CTA's 256 splats of every array with 16-byte accesses
+        SSB_REQUIRE((first & 3) == 0, "ssb_reduce_adam_broadcast: with peers a rank's range must start at a multiple of 4 splats");
+        for (int k = 0; k < 6; ++k)
+            SSB_REQUIRE((((uintptr_t)g_arrays[k] | (uintptr_t)p_arrays[k]) & 15) == 0, "ssb_reduce_adam_broadcast: array %d must be 16-byte aligned", k);
+    }
     SsbAdamExtras ex_local;
     const SsbAdamExtras* ex = extras;
     if (!ex && count != n_total) {        // regulariser weights are divided by the model's splat count, not the range's

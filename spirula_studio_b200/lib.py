@@ -210,7 +210,8 @@ def peer_table(world, rank, bases, segments, multicast=None):
 
 class SsbPeerReplicas(C.Structure):
     _fields_ = [("world", C.c_int32), ("self", C.c_int32), ("grads", C.c_void_p * MAX_PEERS), ("params", C.c_void_p * MAX_PEERS),
-                ("sh_packed", C.c_void_p * MAX_PEERS), ("sh_bounds", C.c_void_p * MAX_PEERS)]
+                ("sh_packed", C.c_void_p * MAX_PEERS), ("sh_bounds", C.c_void_p * MAX_PEERS),
+                ("mc_grads", C.c_void_p), ("mc_params", C.c_void_p), ("mc_sh_packed", C.c_void_p), ("mc_sh_bounds", C.c_void_p)]
 
 
 class SsbShAdamState(C.Structure):
@@ -222,10 +223,13 @@ class SsbShAdamState(C.Structure):
 BARRIER_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p)
 
 
-def peer_replicas(world, rank, grads, params, sh_packed=None, sh_bounds=None):
-    """Each argument: the device address of every rank's copy of that allocation, as mapped in this process."""
+def peer_replicas(world, rank, grads, params, sh_packed=None, sh_bounds=None, multicast=None):
+    """Each argument: the device address of every rank's copy of that allocation, as mapped in this process;
+    multicast = (grads, params, sh_packed, sh_bounds) NVSwitch multicast addresses, or None."""
     r = SsbPeerReplicas()
     r.world, r.self = world, rank
+    if multicast:
+        r.mc_grads, r.mc_params, r.mc_sh_packed, r.mc_sh_bounds = [a or None for a in (list(multicast) + [None] * 4)[:4]]
     for name, addrs in (("grads", grads), ("params", params), ("sh_packed", sh_packed), ("sh_bounds", sh_bounds)):
         arr = getattr(r, name)
         for p_, a in enumerate(addrs or []):

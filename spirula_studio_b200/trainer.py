@@ -13,11 +13,12 @@ in one of two ways:
       every replica.  Two stream-ordered barriers per iteration keep the ranks
       in step; a barrier that fails (a rank is gone) ends the step with
       SSB_ERR_PEER before any kernel that depends on that rank is launched.
-  "multimem": the same three steps, but the exchanged buffers live in torch
+  "multimem": the same fused pass, but the exchanged buffers live in torch
       symmetric memory and the kernels address them through their NVSwitch
       multicast address: the switch adds the ranks' gradients on a load and
-      replicates a parameter store, so each rank moves its range once instead
-      of once per peer.  Falls back to "peer" where that cannot be set up.
+      replicates a parameter store, so each rank receives its range once and
+      sends each update once instead of once per peer.  Falls back to "peer"
+      where that cannot be set up.
   "nccl": one NCCL all-reduce of the whole gradient buffer, then every rank
       applies the same Adam update to all parameters.
 
@@ -209,7 +210,8 @@ class Trainer:
             tables_mcast += [mcast[2], mcast[3]]
         self._reduce_table = L.peer_table(W, r, [bases[0]], grad_segs, [mcast[0]])
         self._bcast_table = L.peer_table(W, r, tables_bases, param_segs, tables_mcast)
-        self._replicas = L.peer_replicas(W, r, bases[0], bases[1], bases[2] if self.quant else None, bases[3] if self.quant else None)
+        self._replicas = L.peer_replicas(W, r, bases[0], bases[1], bases[2] if self.quant else None, bases[3] if self.quant else None,
+                                         multicast=mcast if self.grad_sync == "multimem" else None)
         self._barrier_cb = L.BARRIER_FN(self._barrier_status)       # kept alive: the library calls it
         self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._barrier()          # every rank has mapped every buffer before anyone touches them
@@ -277,13 +279,7 @@ class Trainer:
         or, for this rank's range of splats, in this rank's buffer ("peer")."""
         if self.grad_sync == "nccl":
             torch.distributed.all_reduce(self.grads_flat, op=torch.distributed.ReduceOp.SUM, group=self.pg)
-        elif self.grad_sync == "multimem":
-            self._mark("views_done")
-            self._barrier()                                       # every rank's backward passes are complete
-            self._mark("barrier1")
-            L.check(self.lib.ssb_peer_reduce_f32(C.byref(self._reduce_table), None))
-            self._mark("reduce")
-        elif self.grad_sync == "peer":
+        elif self.grad_sync in ("peer", "multimem"):
             self._mark("views_done")                              # the sum happens inside the optimiser pass
 
     def _mark(self, name):
@@ -308,7 +304,7 @@ class Trainer:
         cfg = L.SsbAdamConfig(lr["lr_means"], lr["lr_quats"], lr["lr_scales"], lr["lr_opacities"], lr["lr_features_dc"],
                               lr["lr_features_sh"], 0.0, 1.0 / float(total_views), self.iteration, 0)
         f, c = self.first, self.count
-        if self.grad_sync == "peer":
+        if self.grad_sync in ("peer", "multimem"):
             sh = None
             if self.quant:
                 sh = L.SsbShAdamState(self.sh_optim_packed.data_ptr(), self.sh_optim_bounds.data_ptr(), self.sh_packed.data_ptr(),
@@ -329,12 +325,6 @@ class Trainer:
             L.check(self.lib.ssb_adam_step_sh_quantized(L.ptr(self.grads["features_sh"]), L.ptr(self.sh_optim_packed),
                                                         L.ptr(self.sh_optim_bounds), L.ptr(self.sh_packed), L.ptr(self.sh_bounds),
                                                         self.cfg.sh_value_bits, f * 45, c * 45, cells, C.byref(cfg), stream))
-        if self.grad_sync == "multimem":
-            self._mark("adam")
-            L.check(self.lib.ssb_peer_broadcast(C.byref(self._bcast_table), stream))
-            self._mark("broadcast")
-            self._barrier()                                       # every replica is complete before the next forward
-            self._mark("barrier2")
 
     # -- whole iteration ---------------------------------------------------
     def step_device(self, d_viewmats, d_intrins, d_gt, n_local_views, total_views):

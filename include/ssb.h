@@ -159,6 +159,11 @@ int ssb_screen_unpack(const SsbScreenRec* d_screen, int64_t m,
                       float* d_xy, float* d_depth, float* d_conic, float* d_opac, float* d_rgb, void* stream);
 int ssb_screen_pack(const float* d_xy, const float* d_depth, const float* d_conic, const float* d_opac,
                     const float* d_rgb, int64_t m, SsbScreenRec* d_screen, void* stream);
+/* ssb_screen_unpack that ADDS the records' fields to the arrays: gradient records (the layout of ssb_project_bwd's
+ * d_v_screen) onto the reference's running v_ScreenBuffer arrays, which its rasteriser backward accumulates into
+ * (src/kernels/raster/RasterizationBwd.cu:142-145).  Any array may be NULL. */
+int ssb_screen_unpack_add(const SsbScreenRec* d_records, int64_t m,
+                          float* d_xy, float* d_depth, float* d_conic, float* d_opac, float* d_rgb, void* stream);
 
 /* ---- tile intersection: keys, sort, ranges ------------------------------ */
 

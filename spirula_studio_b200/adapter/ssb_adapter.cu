@@ -1,0 +1,250 @@
+// Adapter between spirula-studio's kernel-launch seam and libssb_b200.
+//
+// This translation unit is compiled INSIDE the reference tree's include path (-I<reference>/src): it includes the
+// reference's own headers and DEFINES the free functions they declare, with the reference's signatures, on top of the
+// C ABI of include/ssb.h.  Linked in place of the reference's src/kernels/{projection,tile,raster}/*.cu (and the
+// src/instantiations/*.cu they pull in), it lets src/engine compile and link unchanged for the path this library covers:
+//
+//   projection_3dgs_forward        (src/kernels/projection/ProjectionFwd.cuh:17-34)   -> ssb_project_fwd + ssb_screen_unpack
+//   do_intersect_tile_generic      (src/kernels/tile/IntersectTile.cuh:24-40)        -> ssb_screen_pack + ssb_intersect_tiles
+//   rasterize_to_pixels_3dgs_fwd   (src/kernels/raster/RasterizationFwd.cuh:16-37)    -> ssb_screen_pack + ssb_raster_fwd
+//   rasterize_to_pixels_3dgs_bwd   (src/kernels/raster/RasterizationBwd.cuh:18-48)    -> ssb_raster_bwd_accum + unpack of the gradient records
+//
+// Outputs are views into the reference's process-global DevicePool under the reference's own PoolSlots, sized exactly as
+// the reference sizes them (the pair count is read back to the host where the reference reads it back), so callers see
+// the same tensors.  The 48-byte records and workspaces this library works on are scratch of the adapter, kept in the
+// pool's dynamically named side map.  What the library does not cover is refused the way the reference refuses bad
+// arguments (std::runtime_error, src/core/Common.cuh:133-146): lens-distortion tiers, the live-tile map, AABB-mode
+// intersection, distortion-loss channels, median depth, other primitives.
+#include "ssb.h"
+
+#include <kernels/projection/ProjectionFwd.cuh>
+#include <kernels/raster/RasterizationBwd.cuh>
+#include <kernels/raster/RasterizationFwd.cuh>
+#include <kernels/tile/IntersectTile.cuh>
+
+#include <stdexcept>
+#include <string>
+
+namespace {
+
+void ssb_check(int status) {
+    if (status == SSB_OK) return;
+    if (status == SSB_ERR_OUT_OF_MEMORY) backend::throw_out_of_memory(0);
+    throw std::runtime_error(std::string("libssb_b200: ") + ssb_last_error_string());
+}
+
+[[noreturn]] void unsupported(const char* what) {
+    throw std::runtime_error(std::string("ssb adapter: ") + what + " is outside the path libssb_b200 covers");
+}
+
+// Scratch of the adapter: grow-only, owned by the reference's pool like every other transient buffer.
+template <class T>
+T* scratch(const char* name, int64_t count, VramCategory cat = VramCategory::SplatXImg) {
+    DeviceVector<T> v;
+    v.resize_dynamic(cat, std::string("ssb_adapter.") + name, count > 0 ? count : 1);
+    return v.data_ptr();
+}
+
+int camera_model_of(const std::string& s) {
+    switch (cmt(s)) {
+        case CameraModelType::PINHOLE: return SSB_CAMERA_PINHOLE;
+        case CameraModelType::FISHEYE: return SSB_CAMERA_FISHEYE;
+        case CameraModelType::EQUISOLID: return SSB_CAMERA_EQUISOLID;
+        case CameraModelType::EQUIRECTANGULAR: return SSB_CAMERA_EQUIRECT;
+        default: unsupported("this camera model");
+    }
+}
+
+// The reference's five ScreenBuffer arrays -> records.  `depths` may stand in for the depth array and `rgb` may be null
+// (the intersection needs neither colour nor ray depth).
+SsbScreenRec* pack_records(const char* name, const float* xy, const float* depth, const float* conic, const float* opac, const float* rgb, int64_t m) {
+    SsbScreenRec* rec = scratch<SsbScreenRec>(name, m);
+    ssb_check(ssb_screen_pack(xy, depth, conic, opac, rgb ? rgb : conic, m, rec, nullptr));
+    return rec;
+}
+
+}  // namespace
+
+std::tuple<DeviceTensor2D<float4>, DeviceTensor2D<float>, std::vector<DeviceTensorFloatND>> projection_3dgs_forward(
+    const int64_t num_splats, const int max_sh_degree, const std::vector<DeviceTensorFloatND>& in_splats,
+    TorchTensorView viewmats, TorchTensorView intrins, const uint32_t image_width, const uint32_t image_height,
+    const std::string camera_model, const std::string distortion, const TorchTensorView dist_coeffs, DeviceVector<float> radii,
+    const std::optional<TorchTensorView> sh_value_packed, const std::optional<TorchTensorView> sh_value_bounds,
+    const uint32_t num_sh_buffer, const int sh_value_bits, const int64_t sh_bounds_stride) {
+    (void)dist_coeffs;
+    if (cdt(distortion) != CameraDistortionType::None) unsupported("a lens-distortion tier");
+    if (in_splats.size() != 6) throw std::runtime_error("projection_3dgs_forward: expected six world arrays");
+    const int sh_degree = std::min(Vanilla3DGS<0>::WorldBuffer(in_splats).sh_degree(), max_sh_degree);
+    if (sh_degree != 3) unsupported("an SH degree other than 3");
+    if (sh_value_bits != 32 && num_sh_buffer != 15) unsupported("a quantised SH buffer that does not hold 15 coefficients");
+    const uint32_t C = (uint32_t)std::get<2>(viewmats)[0];
+    const int64_t N = num_splats, m = (int64_t)C * N;
+
+    SsbSplats sp = {in_splats[0].data_ptr(), in_splats[1].data_ptr(), in_splats[2].data_ptr(),
+                    in_splats[3].data_ptr(), in_splats[4].data_ptr(), sh_value_bits == 32 ? in_splats[5].data_ptr() : nullptr};
+    SsbShQuant shq = {};
+    if (sh_value_bits != 32) {
+        if (!sh_value_packed.has_value() || !sh_value_bounds.has_value()) throw std::runtime_error("projection_3dgs_forward: quantised SH without its buffers");
+        shq.packed = (void*)std::get<0>(sh_value_packed.value());
+        shq.bounds = (float*)std::get<0>(sh_value_bounds.value());
+        shq.bits = sh_value_bits;
+        shq.bounds_stride = sh_bounds_stride;      // 0 = one bound per 256 splats, as in the reference
+    }
+    SsbCameras cams = {(const float*)std::get<0>(viewmats), (const float*)std::get<0>(intrins), (int32_t)C,
+                       (int32_t)image_width, (int32_t)image_height, camera_model_of(camera_model), 0};
+
+    DeviceTensor2D<float4> aabb;
+    aabb.resize(PoolSlot::ProjAabb, C, N);
+    DeviceTensor2D<float> sorting_depths;
+    sorting_depths.resize(PoolSlot::ProjDepths, C, N);
+    std::vector<DeviceTensorFloatND> screen = Vanilla3DGS<3>::ScreenBuffer::empty_pool(m, PoolSlot::ProjScreen);
+    SsbScreenRec* rec = scratch<SsbScreenRec>("proj_records", m);
+    ssb_check(ssb_project_fwd(&sp, sh_value_bits != 32 ? &shq : nullptr, N, &cams, (float*)aabb.data_ptr(), sorting_depths.data_ptr(),
+                              radii.data_ptr(), rec, nullptr));
+    ssb_check(ssb_screen_unpack(rec, m, screen[0].data_ptr(), screen[1].data_ptr(), screen[2].data_ptr(), screen[3].data_ptr(),
+                                screen[4].data_ptr(), nullptr));
+    return std::make_tuple(aabb, sorting_depths, screen);
+}
+
+int64_t intersect_tile_count(int width, int height) {
+    return (int64_t)((width + SSB_TILE - 1) / SSB_TILE) * ((height + SSB_TILE - 1) / SSB_TILE);
+}
+
+std::tuple<DeviceVector<int64_t>, DeviceVector<int32_t>, DeviceTensor3D<int32_t>> do_intersect_tile_generic(
+    DeviceTensorFloatND aabb, DeviceTensorFloatND depths, DeviceTensorFloatND* proj_xy, DeviceTensorFloatND* proj_conic,
+    DeviceTensorFloatND* proj_opac, const uint32_t I, TorchTensorView intrins, const uint32_t image_width, const uint32_t image_height,
+    DeviceVector<int32_t>* image_ids, const int32_t* tile_active) {
+    (void)intrins;
+    if (!proj_xy || !proj_conic || !proj_opac) unsupported("AABB-mode tile intersection");
+    if (tile_active) unsupported("the live-tile map");
+    const int64_t total = depths.numel();
+    const uint32_t tw = (image_width + SSB_TILE - 1) / SSB_TILE, th = (image_height + SSB_TILE - 1) / SSB_TILE;
+    const int64_t n_tiles = (int64_t)tw * th * I;
+
+    DeviceTensor3D<int32_t> offsets;
+    offsets.resize(PoolSlot::IsectOffsets, I, th, tw);
+    if (total == 0) {
+        offsets.zero();
+        return std::make_tuple(DeviceVector<int64_t>{}, DeviceVector<int32_t>{}, offsets);
+    }
+    SsbScreenRec* rec = pack_records("isect_records", proj_xy->data_ptr(), depths.data_ptr(), proj_conic->data_ptr(), proj_opac->data_ptr(), nullptr, total);
+    int64_t* d_count = scratch<int64_t>("isect_count", 2);
+    // The library keeps the pair count on the device and works inside a caller-chosen capacity; the reference's contract is
+    // exact sizes, so the count comes back to the host here (as the reference's own launcher does) and a capacity that
+    // turned out too small is grown and the call repeated.
+    static int64_t pairs_per_record = 8;
+    for (;;) {
+        const int64_t cap = std::max<int64_t>(pairs_per_record * total, 1024);
+        const int64_t ws_bytes = ssb_intersect_tiles_workspace_bytes(n_tiles, cap);
+        void* ws = scratch<unsigned char>("isect_workspace", ws_bytes);
+        int64_t* keys = scratch<int64_t>("isect_keys", cap);
+        int32_t* flat = scratch<int32_t>("isect_flat", cap);
+        if (image_ids) {
+            backend::memcpy_sync(d_count + 1, &total, sizeof(int64_t), backend::MemcpyKind::HostToDevice);      // the pair count, which the library reads on the device
+            ssb_check(ssb_intersect_tiles_packed((const float*)aabb.data_ptr(), depths.data_ptr(), rec, image_ids->data_ptr(), d_count + 1, total, (int32_t)I,
+                                                 (int32_t)image_width, (int32_t)image_height, ws, ws_bytes, keys, flat, cap, offsets.data_ptr(), d_count, nullptr));
+        } else
+            ssb_check(ssb_intersect_tiles((const float*)aabb.data_ptr(), depths.data_ptr(), rec, total, total / I, (int32_t)image_width,
+                                          (int32_t)image_height, ws, ws_bytes, keys, flat, cap, offsets.data_ptr(), d_count, nullptr));
+        int64_t n_isects = 0;
+        backend::memcpy_sync(&n_isects, d_count, sizeof(int64_t), backend::MemcpyKind::DeviceToHost);
+        int32_t bits = 0;
+        ssb_device_status(&bits, nullptr);          // clears the "pairs dropped" flag a too-small first try raised
+        if (n_isects > cap) { pairs_per_record = (n_isects + total - 1) / total + 1; continue; }
+        if (n_isects == 0) {
+            offsets.zero();
+            return std::make_tuple(DeviceVector<int64_t>{}, DeviceVector<int32_t>{}, offsets);
+        }
+        DeviceVector<int64_t> isect_ids;
+        isect_ids.resize(PoolSlot::IsectIdsA, n_isects);
+        DeviceVector<int32_t> flatten_ids;
+        flatten_ids.resize(PoolSlot::IsectFlatA, n_isects);
+        backend::memcpy_sync(isect_ids.data_ptr(), keys, n_isects * sizeof(int64_t), backend::MemcpyKind::DeviceToDevice);
+        backend::memcpy_sync(flatten_ids.data_ptr(), flat, n_isects * sizeof(int32_t), backend::MemcpyKind::DeviceToDevice);
+        return std::make_tuple(isect_ids, flatten_ids, offsets);
+    }
+}
+
+std::tuple<RenderOutput::TensorTuple, DeviceTensor3D<float>, DeviceTensor3D<int32_t>, RenderOutput::TensorTuple, DeviceTensor3D<float>>
+rasterize_to_pixels_3dgs_fwd(int64_t num_splats, std::vector<DeviceTensorFloatND> splats_w, std::vector<DeviceTensorFloatND> splats_s,
+                             DeviceVector<int32_t> gaussian_ids, const uint32_t image_width, const uint32_t image_height,
+                             const DeviceTensor3D<int32_t> tile_offsets, const DeviceVector<int32_t> flatten_ids, DistortionType dist_type,
+                             bool output_median) {
+    (void)num_splats; (void)splats_w; (void)gaussian_ids;      // the rasteriser addresses records through the flatten ids alone
+    if (dist_type != DistortionType::None) unsupported("a distortion-loss channel");
+    if (output_median) unsupported("the median-depth output");
+    if (splats_s.size() != 5) throw std::runtime_error("rasterize_to_pixels_3dgs_fwd: expected five screen arrays");
+    const int64_t batch = tile_offsets.size<0>();
+    const int64_t m = splats_s[1].numel();
+    RenderOutput::TensorTuple renders, distortions;
+    RenderOutput::resize<Vanilla3DGS<0>::pixelType>(renders, batch, image_height, image_width, PoolSlot::Renders);
+    DeviceTensor3D<float> render_Ts;
+    DeviceTensor3D<int32_t> render_last_ids;
+    render_Ts.resize(PoolSlot::RenderTs, batch, image_height, image_width);
+    render_last_ids.resize(PoolSlot::RenderLastIds, batch, image_height, image_width);
+    SsbScreenRec* rec = pack_records("raster_records", splats_s[0].data_ptr(), splats_s[1].data_ptr(), splats_s[2].data_ptr(),
+                                     splats_s[3].data_ptr(), splats_s[4].data_ptr(), m);
+    int64_t* d_count = scratch<int64_t>("raster_count", 2);
+    const int64_t n_isects = flatten_ids.size();
+    backend::memcpy_sync(d_count, &n_isects, sizeof(int64_t), backend::MemcpyKind::HostToDevice);
+    if (n_isects == 0) {      // nothing to blend: the library still writes T = 1 and zero colour, from an empty list
+        static int32_t* none = scratch<int32_t>("raster_empty_list", 4);
+        ssb_check(ssb_raster_fwd(rec, m, tile_offsets.data_ptr(), none, 0, d_count, (int32_t)batch, (int32_t)image_width, (int32_t)image_height,
+                                 (float*)std::get<0>(renders).data_ptr(), std::get<1>(renders).data_ptr(), render_Ts.data_ptr(),
+                                 render_last_ids.data_ptr(), nullptr));
+    } else {
+        ssb_check(ssb_raster_fwd(rec, m, tile_offsets.data_ptr(), flatten_ids.data_ptr(), n_isects, d_count, (int32_t)batch, (int32_t)image_width,
+                                 (int32_t)image_height, (float*)std::get<0>(renders).data_ptr(), std::get<1>(renders).data_ptr(),
+                                 render_Ts.data_ptr(), render_last_ids.data_ptr(), nullptr));
+    }
+    return std::make_tuple(renders, render_Ts, render_last_ids, distortions, DeviceTensor3D<float>{});
+}
+
+std::tuple<std::vector<DeviceTensorFloatND>, std::vector<DeviceTensorFloatND>, DeviceVector<float>> rasterize_to_pixels_3dgs_bwd(
+    int64_t num_splats, std::vector<DeviceTensorFloatND> splats_w, std::vector<DeviceTensorFloatND> splats_s, DeviceVector<int32_t> gaussian_ids,
+    const uint32_t image_width, const uint32_t image_height, const DeviceTensor3D<int32_t> tile_offsets, const DeviceVector<int32_t> flatten_ids,
+    const DeviceTensor3D<float> render_Ts, const DeviceTensor3D<int32_t> last_ids, RenderOutput::TensorTuple render_outputs_tuple,
+    std::optional<RenderOutput::TensorTuple> distortion_fwd_outputs, DistortionType dist_type, DeviceTensor3D<float> accum_weight_map,
+    DensifyAccumMode accum_mode, RenderOutput::TensorTuple v_render_outputs, const DeviceTensor3D<float> v_render_Ts,
+    const DeviceTensor3D<float> v_median, std::optional<RenderOutput::TensorTuple> v_distortion_outputs,
+    std::optional<std::vector<DeviceTensorFloatND>> v_splats_w, std::optional<std::vector<DeviceTensorFloatND>> v_splats_s) {
+    (void)distortion_fwd_outputs; (void)v_distortion_outputs;
+    if (dist_type != DistortionType::None) unsupported("a distortion-loss channel");
+    if (v_median.data_ptr() != nullptr) unsupported("the median-depth cotangent");
+    if (splats_s.size() != 5) throw std::runtime_error("rasterize_to_pixels_3dgs_bwd: expected five screen arrays");
+    // as the reference: fresh zeroed gradient arrays unless the caller brings its own to accumulate into
+    if (!v_splats_w.has_value()) v_splats_w = Vanilla3DGS<0>::WorldBuffer::zeros_pool(splats_w, PoolSlot::RasterBwdVWorld);
+    if (!v_splats_s.has_value()) v_splats_s = Vanilla3DGS<0>::ScreenBuffer::zeros_pool(splats_s, PoolSlot::RasterBwdVScreen);
+    if (accum_weight_map.data_ptr() == nullptr) accum_mode = DensifyAccumMode::None;      // no map, nothing to accumulate
+    const int64_t batch = tile_offsets.size<0>();
+    const int64_t m = splats_s[1].numel();
+    DeviceVector<float> o_accum_weight;
+    if (accum_any(accum_mode)) {
+        o_accum_weight.resize(PoolSlot::RasterBwdAccumWeight, num_splats * accum_lanes(accum_mode));
+        o_accum_weight.zero();
+    }
+    float* aw = o_accum_weight.data_ptr();
+    float* aw_den = accum_mode == DensifyAccumMode::Avg ? aw + num_splats : nullptr;
+    const int mode = accum_mode == DensifyAccumMode::Max ? SSB_ACCUM_MAX : accum_mode == DensifyAccumMode::Sum ? SSB_ACCUM_SUM
+                   : accum_mode == DensifyAccumMode::Avg ? SSB_ACCUM_AVG : SSB_ACCUM_NONE;
+
+    SsbScreenRec* rec = pack_records("raster_records", splats_s[0].data_ptr(), splats_s[1].data_ptr(), splats_s[2].data_ptr(),
+                                     splats_s[3].data_ptr(), splats_s[4].data_ptr(), m);
+    SsbScreenRec* v_rec = scratch<SsbScreenRec>("raster_grad_records", m);
+    backend::memset_sync(v_rec, 0, (size_t)m * sizeof(SsbScreenRec));
+    int64_t* d_count = scratch<int64_t>("raster_count", 2);
+    const int64_t n_isects = flatten_ids.size();
+    backend::memcpy_sync(d_count, &n_isects, sizeof(int64_t), backend::MemcpyKind::HostToDevice);
+    if (n_isects > 0) {
+        ssb_check(ssb_raster_bwd_accum(rec, m, tile_offsets.data_ptr(), flatten_ids.data_ptr(), n_isects, d_count, (int32_t)batch, (int32_t)image_width,
+                                       (int32_t)image_height, std::get<1>(render_outputs_tuple).data_ptr(), render_Ts.data_ptr(), last_ids.data_ptr(),
+                                       (const float*)std::get<0>(v_render_outputs).data_ptr(), std::get<1>(v_render_outputs).data_ptr(),
+                                       v_render_Ts.data_ptr(), v_rec, mode, accum_weight_map.data_ptr(), num_splats,
+                                       gaussian_ids.data_ptr(), aw, aw_den, nullptr));
+        // gradient records -> the five gradient arrays, added to what they hold (zeros, or the caller's running sums)
+        std::vector<DeviceTensorFloatND>& v = v_splats_s.value();
+        ssb_check(ssb_screen_unpack_add(v_rec, m, v[0].data_ptr(), v[1].data_ptr(), v[2].data_ptr(), v[3].data_ptr(), v[4].data_ptr(), nullptr));
+    }
+    return std::make_tuple(v_splats_w.value(), v_splats_s.value(), o_accum_weight);
+}

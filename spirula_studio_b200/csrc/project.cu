@@ -720,16 +720,19 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
     else for (int i = threadIdx.x; i < count; i += kProjBlock) out[i] = shg_s[i];
 }
 
+// ADD: the arrays are accumulated into (gradient records onto running gradient arrays) instead of overwritten.
+template <bool ADD>
 __global__ void screen_unpack_kernel(const SsbScreenRec* __restrict__ s, int64_t m, float* xy, float* depth, float* conic, float* opac, float* rgb) {
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= m) return;
     const float4* r = (const float4*)(s + i);
     float4 a = r[0], b = r[1], c = r[2];
-    if (xy) { xy[2 * i] = a.x; xy[2 * i + 1] = a.y; }
-    if (depth) depth[i] = c.w;
-    if (conic) { conic[3 * i] = b.x; conic[3 * i + 1] = b.y; conic[3 * i + 2] = b.z; }
-    if (opac) opac[i] = b.w;
-    if (rgb) { rgb[3 * i] = c.x; rgb[3 * i + 1] = c.y; rgb[3 * i + 2] = c.z; }
+    auto put = [](float* dst, float v) { if (ADD) *dst += v; else *dst = v; };
+    if (xy) { put(xy + 2 * i, a.x); put(xy + 2 * i + 1, a.y); }
+    if (depth) put(depth + i, c.w);
+    if (conic) { put(conic + 3 * i, b.x); put(conic + 3 * i + 1, b.y); put(conic + 3 * i + 2, b.z); }
+    if (opac) put(opac + i, b.w);
+    if (rgb) { put(rgb + 3 * i, c.x); put(rgb + 3 * i + 1, c.y); put(rgb + 3 * i + 2, c.z); }
 }
 
 __global__ void screen_pack_kernel(const float* xy, const float* depth, const float* conic, const float* opac, const float* rgb, int64_t m, SsbScreenRec* s) {
@@ -834,7 +837,16 @@ int ssb_screen_unpack(const SsbScreenRec* d_screen, int64_t m, float* d_xy, floa
     using namespace ssb;
     SSB_REQUIRE(d_screen && m >= 0, "ssb_screen_unpack: bad argument");
     if (m == 0) return SSB_OK;
-    screen_unpack_kernel<<<(unsigned)ceil_div(m, 256), 256, 0, (cudaStream_t)stream>>>(d_screen, m, d_xy, d_depth, d_conic, d_opac, d_rgb);
+    screen_unpack_kernel<false><<<(unsigned)ceil_div(m, 256), 256, 0, (cudaStream_t)stream>>>(d_screen, m, d_xy, d_depth, d_conic, d_opac, d_rgb);
+    SSB_LAUNCHED("screen_unpack_kernel");
+    return SSB_OK;
+}
+
+int ssb_screen_unpack_add(const SsbScreenRec* d_records, int64_t m, float* d_xy, float* d_depth, float* d_conic, float* d_opac, float* d_rgb, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(d_records && m >= 0, "ssb_screen_unpack_add: bad argument");
+    if (m == 0) return SSB_OK;
+    screen_unpack_kernel<true><<<(unsigned)ceil_div(m, 256), 256, 0, (cudaStream_t)stream>>>(d_records, m, d_xy, d_depth, d_conic, d_opac, d_rgb);
     SSB_LAUNCHED("screen_unpack_kernel");
     return SSB_OK;
 }

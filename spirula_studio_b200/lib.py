@@ -76,6 +76,7 @@ SIGNATURES = {
     "ssb_project_bwd": (C.c_int, [_P, _P, _I64, _P, _P, _P, _P, C.c_int, _P]),
     "ssb_screen_unpack": (C.c_int, [_P, _I64, _P, _P, _P, _P, _P, _P]),
     "ssb_screen_pack": (C.c_int, [_P, _P, _P, _P, _P, _I64, _P, _P]),
+    "ssb_screen_unpack_add": (C.c_int, [_P, _I64, _P, _P, _P, _P, _P, _P]),
     "ssb_tile_keys_workspace_bytes": (_I64, [_I64]),
     "ssb_tile_keys": (C.c_int, [_P, _P, _P, _I64, _I64, _I32, _I32, _P, _I64, _P, _P, _P, _P, _I64, _P, _P, _P]),
     "ssb_sort_workspace_bytes": (_I64, [_I64]),

@@ -186,7 +186,8 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
 constexpr int kBwdWarps = 4;          // one 16x16 tile per CTA, one 8x8 micro-tile per warp
 constexpr int kBatch = 32;            // survivors per batch: one per lane in the reduction phase
 constexpr int kQueue = 96;            // survivor queue (a scan step looks at 64 list entries)
-constexpr int kMatStride = kBatch + 2;   // row stride of the fragment matrix in float2: rows 16-byte aligned, conflict-free both ways
+constexpr int kSub = 16;              // survivors per pass through the fragment matrix
+constexpr int kMatStride = 64 + 2;    // row stride of the fragment matrix in float2 (64 pixels): rows 16-byte aligned, conflict-free both ways
 
 // What the per-splat densification weight accumulates (DensifyAccumMode, src/primitives/Primitive.cuh:37-39).
 struct BwdAccum {
@@ -219,15 +220,14 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 4) raster_bwd_kernel(
     const float* __restrict__ render_depth, const float* __restrict__ render_T, const int32_t* __restrict__ last_ids,
     const float* __restrict__ v_rgb, const float* __restrict__ v_depth, const float* __restrict__ v_T,
     SsbScreenRec* __restrict__ v_screen, BwdAccum acc) {
-    __shared__ __align__(16) float2 sM[kBwdWarps][kBatch * kMatStride];   // [survivor][pixel of the half]: alpha*T0, vis*dL/dalpha
+    __shared__ __align__(16) float2 sM[kBwdWarps][kSub * kMatStride];   // [survivor of the pass][pixel]: alpha*T0, vis*dL/dalpha
     __shared__ float4 sSA[kBwdWarps][kBatch];     // survivor: x, y relative to the micro-tile's first pixel centre, list index
     __shared__ float4 sSQ[kBwdWarps][kBatch];     // conic pre-scaled for ex2, opacity
     __shared__ float4 sSC[kBwdWarps][kBatch];     // colour, depth
-    __shared__ float4 sV[kBwdWarps][32];          // per pixel of the half at hand: dL/d(rgb), dL/d(depth sum)
+    __shared__ float4 sV[kBwdWarps][65];          // per pixel: dL/d(rgb), dL/d(depth sum); the lower half sits one entry further (bank offset)
     __shared__ float sW[ACCUM ? kBwdWarps : 1][64];   // weight map of the micro-tile
     __shared__ int32_t sSurv[kBwdWarps][kQueue];  // sorted-list index of each queued survivor
     __shared__ int32_t sSurvG[kBwdWarps][kQueue]; // its record index
-    __shared__ uint8_t sIdx[kBwdWarps][2][kBatch];   // per half: the batch's survivors that reach it, back to front
 
     const int img = blockIdx.z;
     const int tile_id = blockIdx.y * tw + blockIdx.x;
@@ -267,6 +267,7 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 4) raster_bwd_kernel(
         }
         if (ACCUM) sW[w][p] = (inside && acc.weight_map) ? acc.weight_map[((int64_t)img * H + y) * W + x] : 0.f;
         vcx[h] = vc.x; vcy[h] = vc.y; vcz[h] = vc.z; vcw[h] = vc.w;
+        sV[w][p + h] = vc;
         max_last = max(max_last, last[h]);
     }
     max_last = __reduce_max_sync(0xffffffffu, max_last);
@@ -332,77 +333,75 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 4) raster_bwd_kernel(
         const bool active = lane < bs;
         int32_t g = 0;
         float ax = 0.f, ay = 0.f, op = 0.f, cb_a = 0.f, cb_b = 0.f, cb_c = 0.f;
-        int halves = 0;
         if (active) {
             const int32_t sidx = sSurv[w][lane];
             g = sSurvG[w][lane];
             const float4* r = (const float4*)(screen + g);
             const float4 a = r[0], b = r[1], c = r[2];
             ax = a.x - fx0; ay = a.y - fy0; op = b.w; cb_a = b.x; cb_b = b.y; cb_c = b.z;
-            // which 8x4 halves the alpha >= 1/255 ellipse reaches (the queue test said: at least one)
-            const EllipseTest et = ellipse_test_setup(b);
-            if (ellipse_test(et, -ax, 7.0f - ax, -ay, 3.0f - ay)) halves |= 1;
-            if (ellipse_test(et, -ax, 7.0f - ax, 4.0f - ay, 7.0f - ay)) halves |= 2;
             // conic pre-scaled so that exp(-sigma) = 2^(-q): q = A2 dx^2 + B2 dx dy + C2 dy^2
             const float kLog2e = 1.4426950408889634f;
             sSA[w][lane] = make_float4(ax, ay, __int_as_float(sidx), 0.f);
             sSQ[w][lane] = make_float4(0.5f * kLog2e * b.x, kLog2e * b.y, 0.5f * kLog2e * b.z, b.w);
             sSC[w][lane] = c;
         }
-        unsigned reach[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            reach[h] = __ballot_sync(0xffffffffu, (halves >> h) & 1);
-            if ((halves >> h) & 1) sIdx[w][h][__popc(reach[h] & ((1u << lane) - 1u))] = (uint8_t)lane;
-        }
         __syncwarp();
         // raw moments of vis*dL/dalpha over this micro-tile's pixels (coordinates relative to its first pixel centre),
-        // and alpha*T0 times the colour cotangent
+        // and alpha*T0 times the colour cotangent, for the survivor this lane flushes
         float m0 = 0.f, m_x = 0.f, m_y = 0.f, m_xx = 0.f, m_xy = 0.f, m_yy = 0.f, gr = 0.f, gg = 0.f, gb = 0.f, gd = 0.f;
         float aw = 0.f, aw_den = 0.f;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            // ---- blend phase: lane = pixel (lane & 7, 4h + (lane >> 3))
-            const float py = pyr + 4.0f * h;
-            const int n_h = __popc(reach[h]);
-            // rows of survivors that do not reach this half read as zero in the reduce phase
-            for (unsigned rest = ~reach[h] & (bs == 32 ? 0xffffffffu : ((1u << bs) - 1u)); rest; rest &= rest - 1u)
-                M[(__ffs(rest) - 1) * kMatStride + lane] = make_float2(0.f, 0.f);
-            sV[w][lane] = make_float4(vcx[h], vcy[h], vcz[h], vcw[h]);      // read by the reduce phase of this half
-            float Th = T[h], vTh = vT[h];
-            const int32_t lasth = last[h];
-#pragma unroll 4
-            for (int k = 0; k < n_h; ++k) {
-                const int s = sIdx[w][h][k];
-                const float4 sa = sSA[w][s];
-                const float4 q4 = sSQ[w][s];
-                const float4 c = sSC[w][s];
-                const float dx = sa.x - pxr, dy = sa.y - py;
-                const float q = fmaf(fmaf(q4.x, dx, q4.y * dy), dx, q4.z * dy * dy);
-                float vis;
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(vis) : "f"(-q));
-                const float ov = q4.w * vis;
-                const float alpha0 = fminf(0.999f, ov);
-                const bool pass = q >= 0.f && alpha0 > kAlphaThreshold && __float_as_int(sa.z) <= lasth;
-                // a fragment that does not count is carried through as alpha = 0: it leaves (T, dL/dT) as they are
-                const float alpha = pass ? alpha0 : 0.0f;
-                // a saturated fragment (opacity * vis > 0.999) passes no gradient to its shape
-                const float vis_eff = (pass && ov <= 0.999f) ? vis : 0.0f;
-                const float om = 1.0f - alpha;
-                const float T0 = __fdividef(Th, om);
-                const float cdot = DEPTH ? fmaf(c.x, vcx[h], fmaf(c.y, vcy[h], fmaf(c.z, vcz[h], c.w * vcw[h])))
-                                         : fmaf(c.x, vcx[h], fmaf(c.y, vcy[h], c.z * vcz[h]));
-                const float v_alpha = T0 * (cdot - vTh);
-                M[s * kMatStride + lane] = make_float2(alpha * T0, vis_eff * v_alpha);
-                vTh = fmaf(alpha, cdot, vTh * om);
-                Th = T0;
-            }
-            T[h] = Th; vT[h] = vTh;
-            __syncwarp();
-            // ---- reduce phase: lane = survivor; its row of the matrix against the 32 pixels of the half
+        // two passes of up to 16 survivors through the 16 x 64 fragment matrix
+        for (int s0 = 0; s0 < bs; s0 += kSub) {
+            const int ns = min(kSub, bs - s0);
+            // ---- blend phase: lane = the pixels (lane & 7, lane >> 3) and four rows below it, two independent chains
             {
-                const float4* row = (const float4*)(M + lane * kMatStride);     // two pixels per 16-byte load
-                const float4* vrow = sV[w];
+                float T0a = T[0], vT0a = vT[0], T1a = T[1], vT1a = vT[1];
+                const int32_t last0 = last[0], last1 = last[1];
+#pragma unroll 2
+                for (int k = 0; k < ns; ++k) {
+                    const int s = s0 + k;
+                    const float4 sa = sSA[w][s];
+                    const float4 q4 = sSQ[w][s];
+                    const float4 c = sSC[w][s];
+                    const float dx = sa.x - pxr;
+                    const int32_t sidx = __float_as_int(sa.z);
+                    float2 frag[2];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const float dy = sa.y - (pyr + 4.0f * h);
+                        const float q = fmaf(fmaf(q4.x, dx, q4.y * dy), dx, q4.z * dy * dy);
+                        float vis;
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(vis) : "f"(-q));
+                        const float ov = q4.w * vis;
+                        const float alpha0 = fminf(0.999f, ov);
+                        const bool pass = q >= 0.f && alpha0 > kAlphaThreshold && sidx <= (h ? last1 : last0);
+                        // a fragment that does not count is carried through as alpha = 0: it leaves (T, dL/dT) as they are
+                        const float alpha = pass ? alpha0 : 0.0f;
+                        // a saturated fragment (opacity * vis > 0.999) passes no gradient to its shape
+                        const float vis_eff = (pass && ov <= 0.999f) ? vis : 0.0f;
+                        const float om = 1.0f - alpha;
+                        float& Th = h ? T1a : T0a;
+                        float& vTh = h ? vT1a : vT0a;
+                        const float Tprev = __fdividef(Th, om);
+                        const float cdot = DEPTH ? fmaf(c.x, vcx[h], fmaf(c.y, vcy[h], fmaf(c.z, vcz[h], c.w * vcw[h])))
+                                                 : fmaf(c.x, vcx[h], fmaf(c.y, vcy[h], c.z * vcz[h]));
+                        const float v_alpha = Tprev * (cdot - vTh);
+                        frag[h] = make_float2(alpha * Tprev, vis_eff * v_alpha);
+                        vTh = fmaf(alpha, cdot, vTh * om);
+                        Th = Tprev;
+                    }
+                    M[k * kMatStride + lane] = frag[0];
+                    M[k * kMatStride + 32 + lane] = frag[1];
+                }
+                T[0] = T0a; vT[0] = vT0a; T[1] = T1a; vT[1] = vT1a;
+            }
+            __syncwarp();
+            // ---- reduce phase: lane = (survivor lane & 15 of the pass, half lane >> 4): its row of the matrix against the 32 pixels of the half
+            {
+                const int hh = lane >> 4;
+                const float4* row = (const float4*)(M + (lane & 15) * kMatStride + 32 * hh);     // two pixels per 16-byte load
+                const float4* vrow = sV[w] + 33 * hh;
+                float p0 = 0.f, p_x = 0.f, p_y = 0.f, p_xx = 0.f, p_xy = 0.f, p_yy = 0.f, pr = 0.f, pg = 0.f, pb = 0.f, pd = 0.f, paw = 0.f, paw_den = 0.f;
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     float r0 = 0.f, r1 = 0.f, r2 = 0.f;        // the row's sums of f, f*x, f*x^2 (f = vis*dL/dalpha)
@@ -412,19 +411,31 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 4) raster_bwd_kernel(
                         const float4 vc0 = vrow[r * 8 + xx], vc1 = vrow[r * 8 + xx + 1];
                         r0 += m.y; r1 = fmaf(m.y, (float)xx, r1); r2 = fmaf(m.y, (float)(xx * xx), r2);
                         r0 += m.w; r1 = fmaf(m.w, (float)(xx + 1), r1); r2 = fmaf(m.w, (float)((xx + 1) * (xx + 1)), r2);
-                        gr = fmaf(vc0.x, m.x, gr); gg = fmaf(vc0.y, m.x, gg); gb = fmaf(vc0.z, m.x, gb);
-                        gr = fmaf(vc1.x, m.z, gr); gg = fmaf(vc1.y, m.z, gg); gb = fmaf(vc1.z, m.z, gb);
-                        if (DEPTH) { gd = fmaf(vc0.w, m.x, gd); gd = fmaf(vc1.w, m.z, gd); }
+                        pr = fmaf(vc0.x, m.x, pr); pg = fmaf(vc0.y, m.x, pg); pb = fmaf(vc0.z, m.x, pb);
+                        pr = fmaf(vc1.x, m.z, pr); pg = fmaf(vc1.y, m.z, pg); pb = fmaf(vc1.z, m.z, pb);
+                        if (DEPTH) { pd = fmaf(vc0.w, m.x, pd); pd = fmaf(vc1.w, m.z, pd); }
                         if (ACCUM) {
-                            const float w0 = sW[w][32 * h + r * 8 + xx], w1 = sW[w][32 * h + r * 8 + xx + 1];
-                            if (ACCUM == 1) aw = fmaxf(aw, fmaxf(w0 * m.x, w1 * m.z));
-                            if (ACCUM >= 2) aw = fmaf(w0, m.x, fmaf(w1, m.z, aw));
-                            if (ACCUM == 3) aw_den += m.x + m.z;
+                            const float w0 = sW[w][32 * hh + r * 8 + xx], w1 = sW[w][32 * hh + r * 8 + xx + 1];
+                            if (ACCUM == 1) paw = fmaxf(paw, fmaxf(w0 * m.x, w1 * m.z));
+                            if (ACCUM >= 2) paw = fmaf(w0, m.x, fmaf(w1, m.z, paw));
+                            if (ACCUM == 3) paw_den += m.x + m.z;
                         }
                     }
-                    const float yy = (float)(4 * h + r);
-                    m0 += r0; m_x += r1; m_xx += r2;
-                    m_y = fmaf(r0, yy, m_y); m_xy = fmaf(r1, yy, m_xy); m_yy = fmaf(r0, yy * yy, m_yy);
+                    const float yy = (float)(4 * hh + r);
+                    p0 += r0; p_x += r1; p_xx += r2;
+                    p_y = fmaf(r0, yy, p_y); p_xy = fmaf(r1, yy, p_xy); p_yy = fmaf(r0, yy * yy, p_yy);
+                }
+                // the two halves of a survivor sit 16 lanes apart: both lanes end up with the micro-tile's sums
+                auto both = [](float v) { return v + __shfl_xor_sync(0xffffffffu, v, 16); };
+                p0 = both(p0); p_x = both(p_x); p_y = both(p_y); p_xx = both(p_xx); p_xy = both(p_xy); p_yy = both(p_yy);
+                pr = both(pr); pg = both(pg); pb = both(pb);
+                if (DEPTH) pd = both(pd);
+                if (ACCUM == 1) paw = fmaxf(paw, __shfl_xor_sync(0xffffffffu, paw, 16));
+                if (ACCUM >= 2) paw = both(paw);
+                if (ACCUM == 3) paw_den = both(paw_den);
+                // survivor s0 + (lane & 15) is flushed by the lane that staged it: lane s0 + (lane & 15)
+                if ((lane >> 4) == (s0 >> 4)) {
+                    m0 = p0; m_x = p_x; m_y = p_y; m_xx = p_xx; m_xy = p_xy; m_yy = p_yy; gr = pr; gg = pg; gb = pb; gd = pd; aw = paw; aw_den = paw_den;
                 }
             }
             __syncwarp();

@@ -53,8 +53,15 @@ WORKLOAD = "mid_1m"
 # pass over this file's own command on the mid_1m workload, one view per launch (a stage of several kernels:
 # their sum).  They are not measured by the run that prints them (a profiler cannot run inside a timed
 # benchmark); the JSON line says so in `traffic_source`.
-NCU_TRAFFIC_MID1M = {"project_fwd": 184.3e6, "tile_keys": 190.5e6, "sort": 35.6e6, "raster_fwd": 68.6e6,
-                     "loss": 51.9e6, "raster_bwd": 111.3e6, "project_bwd": 430.5e6, "adam": 846.8e6}
+NCU_TRAFFIC_MID1M = {"project_fwd": 184.3e6, "tile_keys": 190.5e6, "sort": 35.6e6, "raster_fwd": 71.1e6,
+                     "loss": 52.3e6, "raster_bwd": 112.6e6, "project_bwd": 430.5e6, "adam": 846.8e6}
+# FP32 operations one launch (one view) executes, thread level, FMA counted as two: 2 * ffma + fadd + fmul of
+# smsp__sass_thread_inst_executed_op_{ffma,fadd,fmul}_pred_on.sum from the same kind of capture.  RECORDED CONSTANTS like
+# the traffic above.  The rasterisers and the loss kernel are arithmetic kernels whose working set sits in L2: their
+# roofline is the FP32 pipe, not HBM.
+NCU_FLOP_MID1M = {"raster_fwd": 4.465e9, "loss": 4.637e9, "raster_bwd": 10.620e9}
+# FP32 peak: 148 SMs x 128 lanes x 2 (FMA) x the maximum SM clock; there is no measured FP32 figure for this pool.
+FP32_LANES = 148 * 128
 
 
 def shard(total, world, rank):
@@ -386,13 +393,28 @@ def run_ours(args, cfg, rank, world, local_rank):
         if full_size:
             for k, t in NCU_TRAFFIC_MID1M.items():
                 kernels[k]["dram_traffic"] = int(t)
-        roof = {"kernel": dom, "bound": "hbm", "achieved": kernels[dom]["gbs"], "peak": peak, "unit": "GB/s", "frac": kernels[dom]["frac_of_hbm"],
-                "traffic": int(NCU_TRAFFIC_MID1M[dom]) if full_size else None,
-                "traffic_source": "recorded constant from an earlier ncu capture of this command, not measured by this run" if full_size else None,
-                "peak_source": f"{peak_kind} copy bandwidth",
-                "note": "the raster kernels are bound by instruction issue (79-88 % of issue slots busy, DRAM at 1-2 % of peak, traffic below "
-                        "the algorithmic bytes because a view's working set stays in L2); the HBM fraction is reported because the schema asks "
-                        "for one; the HBM-bound stages carry their own fractions in `kernels`"}
+        sm_max = (clocks or {}).get("sm_max_mhz") or 1965.0
+        fp32_peak = FP32_LANES * 2 * sm_max * 1e6 / 1e12            # TFLOP/s
+        if full_size:
+            for k, f in NCU_FLOP_MID1M.items():
+                tf = f / (kernels[k]["ms"] * 1e-3) / 1e12 if kernels[k]["ms"] > 0 else 0.0
+                kernels[k].update({"flop": int(f), "tflops_fp32": round(tf, 2), "frac_of_fp32": round(tf / fp32_peak, 4)})
+        recorded = "recorded constant from an earlier ncu capture of this command, not measured by this run"
+        if full_size and dom in NCU_FLOP_MID1M:
+            # the dominant kernel is an arithmetic kernel: its roofline is the FP32 pipe (achieved = recorded flop count of one
+            # launch / this run's measured launch time); its HBM figures stay in `kernels`
+            roof = {"kernel": dom, "bound": "fp32", "achieved": kernels[dom]["tflops_fp32"], "peak": round(fp32_peak, 2), "unit": "TFLOP/s",
+                    "frac": kernels[dom]["frac_of_fp32"], "traffic": int(NCU_TRAFFIC_MID1M[dom]), "traffic_source": recorded,
+                    "flop_source": recorded, "peak_source": f"148 SMs x 128 FP32 lanes x 2 x {sm_max:.0f} MHz (nominal: no measured FP32 peak for this pool)",
+                    "hbm": {"achieved": kernels[dom]["gbs"], "peak": peak, "unit": "GB/s", "frac": kernels[dom]["frac_of_hbm"],
+                            "peak_source": f"{peak_kind} copy bandwidth"},
+                    "note": "the rasterisers and the loss kernel work out of L2 (DRAM at 1-3 % of peak, traffic below the algorithmic bytes); "
+                            "they are bound by instruction issue and shared-memory bandwidth, so the FP32 pipe is the roofline that means "
+                            "something; the HBM-bound stages (projection, Adam) carry their own fractions in `kernels`"}
+        else:
+            roof = {"kernel": dom, "bound": "hbm", "achieved": kernels[dom]["gbs"], "peak": peak, "unit": "GB/s", "frac": kernels[dom]["frac_of_hbm"],
+                    "traffic": int(NCU_TRAFFIC_MID1M[dom]) if full_size and dom in NCU_TRAFFIC_MID1M else None,
+                    "traffic_source": recorded if full_size else None, "peak_source": f"{peak_kind} copy bandwidth"}
         value = 1e3 / ms_step
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,

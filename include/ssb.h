@@ -120,7 +120,9 @@ int ssb_project_fwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n,
  * stream synchronisation, as the reference reads it back).  Outputs hold `capacity` pairs; pairs beyond
  * it are dropped and reported (SSB_ERR_CAPACITY when the host count is requested).  The packed arrays
  * feed ssb_intersect_tiles_packed and, through its flatten ids, the rasterisers unchanged.
- * Workspace: ssb_project_fwd_packed_workspace_bytes(n, views) (the pairs are projected once into it). */
+ * Like the reference, two passes with a scan in between, so memory is proportional to the visible pairs: a visibility
+ * pass that reads no SH and leaves one 4-byte flag per pair, an in-place scan, and a pass that projects the kept pairs
+ * straight into their slots.  Workspace: ssb_project_fwd_packed_workspace_bytes(n, views), about 4 bytes per pair. */
 int64_t ssb_project_fwd_packed_workspace_bytes(int64_t n, int32_t n_views);
 int ssb_project_fwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams,
                            void* d_workspace, int64_t workspace_bytes,
@@ -131,10 +133,10 @@ int ssb_project_fwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64
 /* The packed form of ssb_project_bwd (the `packed` mode of projection_fused_bwd_kernel with its camera_ids /
  * gaussian_ids arguments, src/kernels/projection/ProjectionBwd_kernel.cuh:16-54):
  * aabb and screen-space gradients are given per packed pair with their view and splat ids; the number of
- * pairs is read from *d_n_pairs on the device (at most max_pairs).  The pairs are put back into their
- * (view, splat) slots in the workspace and the per-splat kernel of ssb_project_bwd sums each splat's views
+ * pairs is read from *d_n_pairs on the device (at most max_pairs).  The workspace receives the inverse map (slot of
+ * every (view, splat) pair, 4 bytes each) and the per-splat kernel of ssb_project_bwd sums each splat's views through it
  * (no atomics), so the result equals the unpacked call's.
- * Workspace: ssb_project_bwd_packed_workspace_bytes(n, views). */
+ * Workspace: ssb_project_bwd_packed_workspace_bytes(n, views), 4 bytes per pair. */
 int64_t ssb_project_bwd_packed_workspace_bytes(int64_t n, int32_t n_views);
 int ssb_project_bwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams,
                            const float* d_aabb, const SsbScreenRec* d_v_screen, const int32_t* d_camera_ids, const int32_t* d_gaussian_ids,

@@ -28,8 +28,12 @@ __constant__ float cGaussW[11] = {
     0.036000773310661316f, 0.0075987582094967365f, 0.001028380123898387f};
 
 // shared memory layout (floats)
-constexpr int kSmemA = 2 * kIn * kIn;                 // X and Y patches; later the 3 partial maps (3*42*42 = 5292 <= 5408)
-constexpr int kSmemB = 5 * kIn * kMid;                // row-convolved moments; later 3*42*32 row-convolved partials
+// Row strides of the partial maps and of their row convolution are odd (43, 33): step 4 works on two neighbouring outputs
+// per thread, so a warp covers two rows with even column offsets, and an even stride would put both rows on the same banks.
+constexpr int kDStride = kMid + 1, kHStride = kLossTile + 1;
+constexpr int kSmemA = 3 * kMid * kDStride;           // X and Y patches (2*52*52 = 5408); later the 3 partial maps (3*42*43 = 5418)
+constexpr int kSmemB = 5 * kIn * kMid;                // row-convolved moments; later 3*42*33 row-convolved partials
+static_assert(kSmemA >= 2 * kIn * kIn && kSmemB >= 3 * kMid * kHStride, "shared-memory aliases must fit");
 constexpr int kLossSmemBytes = (kSmemA + kSmemB) * 4;
 
 // MAP_MODE (SsimLossMapMode, src/kernels/loss/PerPixelLoss.cuh:129-134): 0 no map; otherwise
@@ -45,8 +49,8 @@ __global__ void __launch_bounds__(kLossThreads) loss_l1_ssim_kernel(
     float* sX = smem;
     float* sY = smem + kIn * kIn;
     float* sM = smem + kSmemA;          // [5][kIn rows][kMid cols]
-    float* sD = smem;                   // [3][kMid][kMid]   (aliases sX/sY)
-    float* sH = smem + kSmemA;          // [3][kMid rows][kLossTile cols] (aliases sM)
+    float* sD = smem;                   // [3][kMid][kDStride]   (aliases sX/sY)
+    float* sH = smem + kSmemA;          // [3][kMid rows][kHStride] (aliases sM)
     __shared__ float red[2][kLossThreads / 32];
 
     const int b = blockIdx.z;
@@ -161,8 +165,8 @@ __global__ void __launch_bounds__(kLossThreads) loss_l1_ssim_kernel(
                     d2 = (2.f * C_) * rAB * grad;
                 }
                 // sD aliases the input patches, which step 2 finished reading
-                const int oo = r * kMid + c;
-                sD[oo] = d0; sD[kMid * kMid + oo] = d1; sD[2 * kMid * kMid + oo] = d2;
+                const int oo = r * kDStride + c;
+                sD[oo] = d0; sD[kMid * kDStride + oo] = d1; sD[2 * kMid * kDStride + oo] = d2;
             }
         }
         __syncthreads();
@@ -172,7 +176,7 @@ __global__ void __launch_bounds__(kLossThreads) loss_l1_ssim_kernel(
             const int r = o / (kLossTile / 2), c = (o - r * (kLossTile / 2)) * 2;
 #pragma unroll
             for (int k = 0; k < 3; ++k) {
-                const float* row = sD + k * kMid * kMid + r * kMid + c;
+                const float* row = sD + k * kMid * kDStride + r * kDStride + c;
                 float s0 = 0.f, s1 = 0.f;
 #pragma unroll
                 for (int d = 0; d < 12; ++d) {
@@ -180,8 +184,8 @@ __global__ void __launch_bounds__(kLossThreads) loss_l1_ssim_kernel(
                     if (d < 11) s0 += v * cGaussW[d];
                     if (d >= 1) s1 += v * cGaussW[d - 1];
                 }
-                sH[k * kMid * kLossTile + r * kLossTile + c] = s0;
-                sH[k * kMid * kLossTile + r * kLossTile + c + 1] = s1;
+                sH[k * kMid * kHStride + r * kHStride + c] = s0;
+                sH[k * kMid * kHStride + r * kHStride + c + 1] = s1;
             }
         }
         __syncthreads();
@@ -195,10 +199,10 @@ __global__ void __launch_bounds__(kLossThreads) loss_l1_ssim_kernel(
             for (int q = 0; q < 4; ++q) sacc[q][0] = sacc[q][1] = sacc[q][2] = 0.f;
 #pragma unroll
             for (int k = 0; k < 3; ++k) {
-                const float* col = sH + k * kMid * kLossTile + r0 * kLossTile + c;
+                const float* col = sH + k * kMid * kHStride + r0 * kHStride + c;
 #pragma unroll
                 for (int d = 0; d < 14; ++d) {
-                    const float v = col[d * kLossTile];
+                    const float v = col[d * kHStride];
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const int tap = d - q;

@@ -345,13 +345,24 @@ __device__ __forceinline__ void stage_sh(
     }
 }
 
-template <int MODEL>
+// PACK = 0: one output slot per (view, splat) pair, culled pairs marked by an all-zero box.
+// PACK = 1: the visibility pass of the packed projection: only flags[pair] = kept (no SH, no other output).
+// PACK = 2: its compacting pass: a kept pair goes to slot flags[pair] (by then the exclusive scan of the flags), with its
+//           view and splat index; culled pairs write nothing; slots beyond `capacity` are dropped.
+struct PackArgs {
+    int32_t* flags;          // [views * n]
+    int32_t* camera_ids;     // [capacity]
+    int32_t* gaussian_ids;   // [capacity]
+    int64_t capacity;
+};
+
+template <int MODEL, int PACK>
 __global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
     SsbSplats sp, SsbShQuant shq, int64_t n, const float* __restrict__ viewmats, const float* __restrict__ intrins,
     int W, int H, int antialiased,
-    float4* __restrict__ aabb_out, float* __restrict__ depths_out, float* __restrict__ radii, SsbScreenRec* __restrict__ screen) {
-    __shared__ __align__(16) float sh_s[kProjBlock * kShPerSplat];
-    __shared__ __align__(16) unsigned char raw_s[kShRawBytes];
+    float4* __restrict__ aabb_out, float* __restrict__ depths_out, float* __restrict__ radii, SsbScreenRec* __restrict__ screen, PackArgs pk) {
+    __shared__ __align__(16) float sh_s[PACK == 1 ? 4 : kProjBlock * kShPerSplat];
+    __shared__ __align__(16) unsigned char raw_s[PACK == 1 ? 16 : kShRawBytes];
     const int cid = blockIdx.y;
     const int64_t first = (int64_t)blockIdx.x * kProjBlock;
     const int64_t gid = first + threadIdx.x;
@@ -364,10 +375,12 @@ __global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
     float in_op = sp.opacities[gl];
     float dc_in[3] = {sp.features_dc[3 * gl], sp.features_dc[3 * gl + 1], sp.features_dc[3 * gl + 2]};
     CamDev cam = load_cam(viewmats, intrins, cid);
-    stage_sh(sh_s, raw_s, sp.features_sh, shq.packed, shq.bounds, shq.bits, shq.bounds_stride, first, n);
-    __syncthreads();
+    if (PACK != 1) {
+        stage_sh(sh_s, raw_s, sp.features_sh, shq.packed, shq.bounds, shq.bits, shq.bounds_stride, first, n);
+        __syncthreads();
+    }
     if (gid >= n) return;
-    const int64_t idx = (int64_t)cid * n + gid;
+    int64_t idx = (int64_t)cid * n + gid;
 
     ProjGeom g;
     bool ok = project_geom<MODEL, false>(cam, W, antialiased != 0, mean, quat, scale, in_op, g);
@@ -381,7 +394,7 @@ __global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
         if (xmax <= 0.f || xmin >= (float)W || ymax <= 0.f || ymin >= (float)H) ok = false;
     }
     float rgb[3] = {0.f, 0.f, 0.f};
-    if (ok && xmax > xmin && ymax > ymin) {
+    if (PACK != 1 && ok && xmax > xmin && ymax > ymin) {
         // viewdir = mean + R^T t, normalised inside the SH evaluation
         const float* R = cam.R;
         float d[3];
@@ -402,6 +415,15 @@ __global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
     float a0 = fminf(fmaxf(xmin, 0.0f), (float)W - 1.0f), a1 = fminf(fmaxf(ymin, 0.0f), (float)H - 1.0f);
     float a2 = fminf(fmaxf(xmax, 0.0f), (float)W - 1.0f), a3 = fminf(fmaxf(ymax, 0.0f), (float)H - 1.0f);
     bool keep = ok && (a2 - a0 > 1e-3f) && (a3 - a1 > 1e-3f);
+    if (PACK == 1) { pk.flags[idx] = keep ? 1 : 0; return; }
+    if (PACK == 2) {
+        if (!keep) return;
+        const int64_t slot = pk.flags[idx];
+        if (slot >= pk.capacity) return;
+        pk.camera_ids[slot] = cid;
+        pk.gaussian_ids[slot] = (int32_t)gid;
+        idx = slot;
+    }
     if (keep) {
         aabb_out[idx] = make_float4(a0, a1, a2, a3);
         // sorting depth (src/shaders/projection_utils.slang:1012-1029): z for pinhole, squared
@@ -469,7 +491,9 @@ template <bool MULTI_VIEW, int MODEL>
 __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
     SsbSplats sp, SsbShQuant shq, int64_t n, int C, const float* __restrict__ viewmats, const float* __restrict__ intrins,
     int W, int H, int antialiased, const float4* __restrict__ aabb, SsbScreenRec* __restrict__ v_screen,
-    SsbSplats gr, int accumulate, int clear_v_screen) {
+    SsbSplats gr, int accumulate, int clear_v_screen, const int32_t* __restrict__ pair_of) {
+    // pair_of (packed input): aabb and v_screen hold one entry per VISIBLE pair, and pair_of[view * n + splat] is that
+    // pair's position, or negative when the pair was culled.  Null: one entry per (view, splat) pair.
     // One view per launch (the training loop's case): a thread's SH gradients overwrite its own
     // SH values in shared memory once they have been read, so one 23 KB span is enough and six
     // CTAs fit an SM.  Several views: gradients accumulate in a second span.
@@ -491,10 +515,12 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
     float scale[3] = {sp.scales[3 * gl], sp.scales[3 * gl + 1], sp.scales[3 * gl + 2]};
     float in_op = sp.opacities[gl];
     float dc_in[3] = {sp.features_dc[3 * gl], sp.features_dc[3 * gl + 1], sp.features_dc[3 * gl + 2]};
-    float4 bb0 = aabb[gl];
-    float4 vr0[3];
-    {
-        const float4* vr = (const float4*)(v_screen + gl);
+    const int64_t slot0 = pair_of ? (int64_t)pair_of[gl] : gl;
+    float4 bb0 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 vr0[3] = {bb0, bb0, bb0};
+    if (slot0 >= 0) {
+        bb0 = aabb[slot0];
+        const float4* vr = (const float4*)(v_screen + slot0);
         vr0[0] = vr[0]; vr0[1] = vr[1]; vr0[2] = vr[2];
     }
     stage_sh(sh_s, raw_s, sp.features_sh, shq.packed, shq.bounds, shq.bits, shq.bounds_stride, first, n);
@@ -510,7 +536,9 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
         const float* sh = sh_s + threadIdx.x * kShPerSplat;
         float* shg = shg_s + threadIdx.x * kShPerSplat;
         for (int cid = 0; cid < C; ++cid) {
-            const int64_t idx = (int64_t)cid * n + gid;
+            const int64_t lin = (int64_t)cid * n + gid;
+            const int64_t idx = cid == 0 ? slot0 : (pair_of ? (int64_t)pair_of[lin] : lin);
+            if (idx < 0) continue;
             float4 bb = cid == 0 ? bb0 : aabb[idx];
             if (bb.z <= bb.x || bb.w <= bb.y) continue;
             any_view = true;
@@ -783,9 +811,9 @@ int ssb_project_fwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, c
     if (e) return e;
     if (n == 0 || cams->count == 0) return SSB_OK;
     dim3 grid((unsigned)ceil_div(n, kProjBlock), (unsigned)cams->count);
-#define SSB_FWD(MODEL) project_fwd_kernel<MODEL><<<grid, kProjBlock, 0, (cudaStream_t)stream>>>( \
+#define SSB_FWD(MODEL) project_fwd_kernel<MODEL, 0><<<grid, kProjBlock, 0, (cudaStream_t)stream>>>( \
         *splats, q, n, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased, \
-        (float4*)d_aabb, d_depths, d_radii, d_screen)
+        (float4*)d_aabb, d_depths, d_radii, d_screen, PackArgs{})
     if (cams->model == SSB_CAMERA_PINHOLE) SSB_FWD(SSB_CAMERA_PINHOLE);
     else if (cams->model == SSB_CAMERA_FISHEYE) SSB_FWD(SSB_CAMERA_FISHEYE);
     else if (cams->model == SSB_CAMERA_EQUISOLID) SSB_FWD(SSB_CAMERA_EQUISOLID);
@@ -797,15 +825,47 @@ int ssb_project_fwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, c
 
 int ssb_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
                     const SsbScreenRec* d_v_screen, const SsbSplats* grads, int accumulate, void* stream) {
-    return ssb::launch_project_bwd(splats, shq, n, cams, d_aabb, const_cast<SsbScreenRec*>(d_v_screen), grads, accumulate, 0, stream);
+    return ssb::launch_project_bwd(splats, shq, n, cams, d_aabb, const_cast<SsbScreenRec*>(d_v_screen), grads, accumulate, 0, stream, nullptr);
 }
 
 }  // extern "C"
 
 namespace ssb {
 
+// pass = 1: flags only; pass = 2: compacting pass (flags hold the exclusive scan).
+int launch_project_fwd_pack_pass(int pass, const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams,
+                                 int32_t* d_flags, float* d_aabb, float* d_depths, float* d_radii, SsbScreenRec* d_screen,
+                                 int32_t* d_camera_ids, int32_t* d_gaussian_ids, int64_t capacity, void* stream) {
+    if (cams->model != SSB_CAMERA_PINHOLE && cams->model != SSB_CAMERA_FISHEYE && cams->model != SSB_CAMERA_EQUISOLID && cams->model != SSB_CAMERA_EQUIRECT) {
+        set_error("ssb_project_fwd_packed: camera model %d not supported", cams->model); return SSB_ERR_UNSUPPORTED;
+    }
+    SSB_REQUIRE((int64_t)cams->count * n < ((int64_t)1 << 31), "ssb_project_fwd_packed: views * splats must fit int32");
+    SsbShQuant q;
+    int e = check_shq(splats, shq, q);
+    if (e) return e;
+    if (n == 0 || cams->count == 0) return SSB_OK;
+    dim3 grid((unsigned)ceil_div(n, kProjBlock), (unsigned)cams->count);
+    const PackArgs pk = {d_flags, d_camera_ids, d_gaussian_ids, capacity};
+#define SSB_FWDP(MODEL, PASS) project_fwd_kernel<MODEL, PASS><<<grid, kProjBlock, 0, (cudaStream_t)stream>>>( \
+        *splats, q, n, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased, \
+        (float4*)d_aabb, d_depths, d_radii, d_screen, pk)
+#define SSB_FWDP_MODEL(PASS) \
+    do { \
+        if (cams->model == SSB_CAMERA_PINHOLE) SSB_FWDP(SSB_CAMERA_PINHOLE, PASS); \
+        else if (cams->model == SSB_CAMERA_FISHEYE) SSB_FWDP(SSB_CAMERA_FISHEYE, PASS); \
+        else if (cams->model == SSB_CAMERA_EQUISOLID) SSB_FWDP(SSB_CAMERA_EQUISOLID, PASS); \
+        else SSB_FWDP(SSB_CAMERA_EQUIRECT, PASS); \
+    } while (0)
+    if (pass == 1) SSB_FWDP_MODEL(1); else SSB_FWDP_MODEL(2);
+#undef SSB_FWDP_MODEL
+#undef SSB_FWDP
+    SSB_LAUNCHED("project_fwd_kernel<packed>");
+    return SSB_OK;
+}
+
 int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
-                       SsbScreenRec* d_v_screen, const SsbSplats* grads, int accumulate, int clear_v_screen, void* stream) {
+                       SsbScreenRec* d_v_screen, const SsbSplats* grads, int accumulate, int clear_v_screen, void* stream,
+                       const int32_t* d_pair_of) {
     SSB_REQUIRE(splats && cams && d_aabb && d_v_screen && grads, "ssb_project_bwd: NULL argument");
     SSB_REQUIRE(grads->means && grads->quats && grads->scales && grads->opacities && grads->features_dc && grads->features_sh,
                 "ssb_project_bwd: every gradient array must be given");
@@ -818,7 +878,7 @@ int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n
     if (n == 0) return SSB_OK;
 #define SSB_BWD(MULTI, MODEL) project_bwd_kernel<MULTI, MODEL><<<(unsigned)ceil_div(n, kProjBlock), kProjBlock, 0, (cudaStream_t)stream>>>( \
         *splats, q, n, cams->count, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased, \
-        (const float4*)d_aabb, d_v_screen, *grads, accumulate, clear_v_screen)
+        (const float4*)d_aabb, d_v_screen, *grads, accumulate, clear_v_screen, d_pair_of)
     const bool multi = cams->count != 1;
     if (cams->model == SSB_CAMERA_PINHOLE) { if (multi) SSB_BWD(true, SSB_CAMERA_PINHOLE); else SSB_BWD(false, SSB_CAMERA_PINHOLE); }
     else if (cams->model == SSB_CAMERA_FISHEYE) { if (multi) SSB_BWD(true, SSB_CAMERA_FISHEYE); else SSB_BWD(false, SSB_CAMERA_FISHEYE); }

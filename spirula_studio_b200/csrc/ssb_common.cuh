@@ -53,7 +53,11 @@ int launch_loss(const float* d_render, const float* d_gt, int B, int H, int W, f
 int launch_loss_map(const float* d_render, const float* d_gt, int B, int H, int W, float w_l1, float w_ssim,
                     float* d_v_render, float* d_losses, int map_mode, float map_weight, float* d_loss_map, cudaStream_t st);
 int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
-                       SsbScreenRec* d_v_screen, const SsbSplats* grads, int accumulate, int clear_v_screen, void* stream);
+                       SsbScreenRec* d_v_screen, const SsbSplats* grads, int accumulate, int clear_v_screen, void* stream,
+                       const int32_t* d_pair_of);
+int launch_project_fwd_pack_pass(int pass, const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams,
+                                 int32_t* d_flags, float* d_aabb, float* d_depths, float* d_radii, SsbScreenRec* d_screen,
+                                 int32_t* d_camera_ids, int32_t* d_gaussian_ids, int64_t capacity, void* stream);
 int launch_intersect_tiles(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
                            int64_t total, int64_t n_per_image, int32_t width, int32_t height,
                            void* d_workspace, int64_t workspace_bytes,

@@ -160,7 +160,7 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
     }
     SSB_MARK(7);
     if (wait_before_bwd) SSB_CUDA(cudaStreamWaitEvent(st, wait_before_bwd, 0));
-    if ((e = launch_project_bwd(params, shq, n, &cam, l.aabb, l.v_screen, grads, accumulate, 1, st))) return e;
+    if ((e = launch_project_bwd(params, shq, n, &cam, l.aabb, l.v_screen, grads, accumulate, 1, st, nullptr))) return e;
     SSB_MARK(8);
 #undef SSB_MARK
     return SSB_OK;

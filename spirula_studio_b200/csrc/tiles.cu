@@ -804,48 +804,19 @@ static int intersect_tiles_impl(const float* d_aabb, const float* d_depths, cons
 // ---------------------------------------------------------------------------
 // Packed projection: the visible (view, splat) pairs only, in (view-major, splat-minor) order, with the view
 // and splat index of each (projection_3dgs_packed_forward, src/kernels/projection/ProjectionPackedFwd.cu:64-158).
-// The reference projects twice (a mask pass, a scan, a compacting pass); here the pairs are projected once
-// into a scratch area and compacted with a flag scan.
+// Like the reference, two passes with a scan between them, and memory proportional to the VISIBLE pairs: the first pass
+// evaluates only the cull decision (no SH is read) and leaves one 4-byte flag per pair, the flags are scanned in place,
+// and the second pass projects again and writes each kept pair straight to its slot.  The backward pass needs the
+// inverse map (pair -> slot), 4 bytes per pair, and then runs the per-splat kernel of the unpacked path: no atomics.
 namespace ssb {
 
-__global__ void __launch_bounds__(256) visible_flag_kernel(const float4* __restrict__ aabb, int64_t total, int32_t* __restrict__ flags) {
-    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    if (i >= total) return;
-    const float4 bb = aabb[i];
-    flags[i] = (bb.z > bb.x && bb.w > bb.y) ? 1 : 0;
-}
-
-__global__ void __launch_bounds__(256) compact_visible_kernel(
-    const float4* __restrict__ aabb, const float* __restrict__ depths, const SsbScreenRec* __restrict__ screen,
-    const int32_t* __restrict__ excl, int64_t total, int64_t n, int64_t capacity,
-    float4* __restrict__ o_aabb, float* __restrict__ o_depths, SsbScreenRec* __restrict__ o_screen,
-    int32_t* __restrict__ o_camera, int32_t* __restrict__ o_gaussian) {
-    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    if (i >= total) return;
-    const float4 bb = aabb[i];
-    if (!(bb.z > bb.x && bb.w > bb.y)) return;
-    const int64_t pos = excl[i];
-    if (pos >= capacity) return;
-    o_aabb[pos] = bb;
-    o_depths[pos] = depths[i];
-    const float4* r = (const float4*)(screen + i);
-    float4* w = (float4*)(o_screen + pos);
-    w[0] = r[0]; w[1] = r[1]; w[2] = r[2];
-    const int64_t cam = i / n;
-    o_camera[pos] = (int32_t)cam;
-    o_gaussian[pos] = (int32_t)(i - cam * n);
-}
-
-__global__ void __launch_bounds__(256) unpack_pairs_kernel(
-    const float4* __restrict__ p_aabb, const SsbScreenRec* __restrict__ p_v, const int32_t* __restrict__ cam, const int32_t* __restrict__ gid,
-    const int64_t* __restrict__ n_pairs, int64_t max_pairs, int64_t n, float4* __restrict__ u_aabb, SsbScreenRec* __restrict__ u_v) {
+__global__ void __launch_bounds__(256) pair_slot_kernel(const int32_t* __restrict__ cam, const int32_t* __restrict__ gid,
+                                                        const int64_t* __restrict__ n_pairs, int64_t max_pairs, int64_t n, int64_t total,
+                                                        int32_t* __restrict__ pair_of) {
     const int64_t v = (int64_t)blockIdx.x * 256 + threadIdx.x;
     if (v >= min(*n_pairs, max_pairs)) return;
     const int64_t i = (int64_t)cam[v] * n + gid[v];
-    u_aabb[i] = p_aabb[v];
-    const float4* r = (const float4*)(p_v + v);
-    float4* w = (float4*)(u_v + i);
-    w[0] = r[0]; w[1] = r[1]; w[2] = r[2];
+    if (i >= 0 && i < total) pair_of[i] = (int32_t)v;       // ids that name no pair are ignored
 }
 
 }  // namespace ssb
@@ -855,8 +826,7 @@ extern "C" {
 int64_t ssb_project_fwd_packed_workspace_bytes(int64_t n, int32_t n_views) {
     using namespace ssb;
     const int64_t total = (n > 0 ? n : 1) * (n_views > 0 ? n_views : 1);
-    return align_up(total * 16, 256) + align_up(total * 4, 256) + align_up(total * (int64_t)sizeof(SsbScreenRec), 256) + align_up(total * 4, 256)
-           + align_up(ceil_div(total, kScanChunk) * 4, 256);
+    return align_up(total * 4, 256) + align_up(ceil_div(total, kScanChunk) * 4, 256);
 }
 
 int ssb_project_fwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams,
@@ -877,25 +847,19 @@ int ssb_project_fwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64
         return SSB_OK;
     }
     char* ws = (char*)d_workspace;
-    float4* u_aabb = (float4*)ws; ws += align_up(total * 16, 256);
-    float* u_depths = (float*)ws; ws += align_up(total * 4, 256);
-    SsbScreenRec* u_screen = (SsbScreenRec*)ws; ws += align_up(total * (int64_t)sizeof(SsbScreenRec), 256);
     int32_t* flags = (int32_t*)ws; ws += align_up(total * 4, 256);
     int32_t* chunk_sums = (int32_t*)ws;
-    int e = ssb_project_fwd(splats, shq, n, cams, (float*)u_aabb, u_depths, d_radii, u_screen, stream);
+    int e = launch_project_fwd_pack_pass(1, splats, shq, n, cams, flags, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, stream);
     if (e) return e;
     const int64_t chunks = ceil_div(total, kScanChunk);
-    visible_flag_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(u_aabb, total, flags);
-    SSB_LAUNCHED("visible_flag_kernel");
     bins_chunk_sum_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(flags, total, chunk_sums);
     SSB_LAUNCHED("bins_chunk_sum_kernel");
     chunk_scan_kernel<<<1, 1024, 0, st>>>(chunk_sums, (int)chunks, d_n_visible);
     SSB_LAUNCHED("chunk_scan_kernel");
     bins_apply_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(flags, total, chunk_sums, nullptr, 0);
     SSB_LAUNCHED("bins_apply_kernel");
-    compact_visible_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(u_aabb, u_depths, u_screen, flags, total, n, capacity,
-                                                                          (float4*)d_aabb, d_depths, d_screen, d_camera_ids, d_gaussian_ids);
-    SSB_LAUNCHED("compact_visible_kernel");
+    e = launch_project_fwd_pack_pass(2, splats, shq, n, cams, flags, d_aabb, d_depths, d_radii, d_screen, d_camera_ids, d_gaussian_ids, capacity, stream);
+    if (e) return e;
     if (h_n_visible) {
         SSB_CUDA(cudaMemcpyAsync(h_n_visible, d_n_visible, sizeof(int64_t), cudaMemcpyDeviceToHost, st));
         SSB_CUDA(cudaStreamSynchronize(st));
@@ -910,7 +874,7 @@ int ssb_project_fwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64
 int64_t ssb_project_bwd_packed_workspace_bytes(int64_t n, int32_t n_views) {
     using namespace ssb;
     const int64_t total = (n > 0 ? n : 1) * (n_views > 0 ? n_views : 1);
-    return align_up(total * 16, 256) + align_up(total * (int64_t)sizeof(SsbScreenRec), 256);
+    return align_up(total * 4, 256);
 }
 
 int ssb_project_bwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams,
@@ -921,22 +885,20 @@ int ssb_project_bwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64
     SSB_REQUIRE(splats && cams && d_aabb && d_v_screen && d_camera_ids && d_gaussian_ids && d_n_pairs && d_workspace && grads,
                 "ssb_project_bwd_packed: NULL argument");
     SSB_REQUIRE(n >= 0 && max_pairs >= 0, "ssb_project_bwd_packed: bad sizes");
+    SSB_REQUIRE((int64_t)cams->count * n < ((int64_t)1 << 31) && max_pairs < ((int64_t)1 << 31), "ssb_project_bwd_packed: pair indices must fit int32");
     SSB_REQUIRE(workspace_bytes >= ssb_project_bwd_packed_workspace_bytes(n, cams->count), "ssb_project_bwd_packed: workspace too small");
     cudaStream_t st = (cudaStream_t)stream;
     const int64_t total = n * cams->count;
     if (total == 0) return SSB_OK;
-    // the packed pairs go back to their (view, splat) slots; every other slot is marked culled, and the
-    // per-splat kernel of the unpacked path then sums the views of a splat without atomics
-    char* ws = (char*)d_workspace;
-    float4* u_aabb = (float4*)ws;
-    SsbScreenRec* u_v = (SsbScreenRec*)(ws + align_up(total * 16, 256));
-    SSB_CUDA(cudaMemsetAsync(u_aabb, 0, (size_t)total * 16, st));
+    // slot of every (view, splat) pair in the packed arrays, -1 where the pair was culled; the per-splat kernel of the
+    // unpacked path then sums the views of a splat through it, so the result equals the unpacked call's
+    int32_t* pair_of = (int32_t*)d_workspace;
+    SSB_CUDA(cudaMemsetAsync(pair_of, 0xff, (size_t)total * 4, st));
     if (max_pairs > 0) {
-        unpack_pairs_kernel<<<(unsigned)ceil_div(max_pairs, 256), 256, 0, st>>>((const float4*)d_aabb, d_v_screen, d_camera_ids, d_gaussian_ids,
-                                                                               d_n_pairs, max_pairs, n, u_aabb, u_v);
-        SSB_LAUNCHED("unpack_pairs_kernel");
+        pair_slot_kernel<<<(unsigned)ceil_div(max_pairs, 256), 256, 0, st>>>(d_camera_ids, d_gaussian_ids, d_n_pairs, max_pairs, n, total, pair_of);
+        SSB_LAUNCHED("pair_slot_kernel");
     }
-    return launch_project_bwd(splats, shq, n, cams, (const float*)u_aabb, u_v, grads, accumulate, 0, stream);
+    return launch_project_bwd(splats, shq, n, cams, d_aabb, const_cast<SsbScreenRec*>(d_v_screen), grads, accumulate, 0, stream, pair_of);
 }
 
 int ssb_intersect_tiles_packed(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen, const int32_t* d_camera_ids,

@@ -64,3 +64,13 @@ def test_argument_errors_are_statuses_not_crashes():
     sp = L.SsbSplats()
     sp.features_sh = 8
     assert lib.ssb_project_fwd(C.byref(sp), None, 0, C.byref(cams), one, one, None, one, None) == L.SSB_ERR_UNSUPPORTED
+
+
+def test_packed_projection_workspaces_are_a_few_bytes_per_pair():
+    """The packed projection keeps memory proportional to the visible pairs: its scratch is one 4-byte flag (forward) or
+    one 4-byte slot index (backward) per (view, splat) pair, not a copy of every pair's outputs."""
+    lib = L.load()
+    for n, views in ((1_000_000, 16), (10_000_000, 8), (1000, 1)):
+        pairs = n * views
+        assert lib.ssb_project_fwd_packed_workspace_bytes(n, views) <= 8 * pairs + 1024
+        assert lib.ssb_project_bwd_packed_workspace_bytes(n, views) <= 8 * pairs + 1024

@@ -41,7 +41,8 @@ typedef enum SsbStatus {
     SSB_ERR_CAPACITY = -3,         /* an output buffer sized by the caller is too small */
     SSB_ERR_OUT_OF_MEMORY = -4,    /* reference: throw_out_of_memory, src/backend/api/BackendRuntime.h:114-143 */
     SSB_ERR_UNSUPPORTED = -5,
-    SSB_ERR_PEER = -6              /* another rank did not take part in a multi-GPU step (barrier failed or timed out) */
+    SSB_ERR_PEER = -6,             /* another rank did not take part in a multi-GPU step (barrier failed or timed out) */
+    SSB_ERR_IO = -7                /* a checkpoint file could not be opened, read or written */
 } SsbStatus;
 
 enum { SSB_CAMERA_PINHOLE = 0, SSB_CAMERA_FISHEYE = 1, SSB_CAMERA_EQUISOLID = 2, SSB_CAMERA_EQUIRECT = 3 }; /* src/core/Common.cuh:96-101 */
@@ -582,6 +583,49 @@ enum { SSB_STAGE_PROJECT_FWD = 0, SSB_STAGE_TILE_KEYS, SSB_STAGE_SORT, SSB_STAGE
        SSB_STAGE_LOSS, SSB_STAGE_RASTER_BWD, SSB_STAGE_PROJECT_BWD, SSB_STAGE_COUNT };
 int ssb_step_set_profiling(SsbStep* step, int enable);
 int ssb_step_get_profile(SsbStep* step, float* ms, int32_t* n_views);
+
+/* ------------------------------------------------------------------------- *
+ * Checkpoint container (state.tar)
+ *
+ * Replaces engine_save_checkpoint / engine_load_checkpoint's file handling
+ * (src/engine/EngineCheckpoint.cpp:350-474) and the helpers of src/core/CheckpointIO.h:
+ * a POSIX ustar archive whose first member is "state.json" and whose other members are
+ * "<buffer name>.npy", each a flat one-dimensional NPY v1.0 array.  Files written here are
+ * byte-for-byte what the reference writes for the same names, sizes and contents, and the
+ * reader takes the reference's files.  Which buffers go in, and under which names, is the
+ * caller's business (the reference's names are listed in src/core/PoolSlots.h:88-125).
+ *
+ * `dtype` is one of SsbDType, numbered like the reference's NpyScalar tags
+ * (src/core/Tensor.h:26).  nbytes must be a multiple of the element size.  Names are at
+ * most 99 bytes.  Device arrays are staged through two pinned 32 MiB buffers so the
+ * copy and the file access overlap; no device memory is allocated.  The functions
+ * synchronise `stream` before they return.
+ * ssb_ckpt_read_device / ssb_ckpt_read_host return SSB_ERR_CAPACITY when the stored array
+ * does not have exactly nbytes bytes (the reference throws "size mismatch"), and
+ * SSB_ERR_INVALID_ARGUMENT when there is no member of that name.
+ * ssb_ckpt_read_bytes with buf == NULL only reports the member's size.
+ * ------------------------------------------------------------------------- */
+typedef enum SsbDType { SSB_DTYPE_U1 = 0, SSB_DTYPE_U2, SSB_DTYPE_U4, SSB_DTYPE_U8, SSB_DTYPE_I4, SSB_DTYPE_I8,
+                        SSB_DTYPE_F2, SSB_DTYPE_F4, SSB_DTYPE_F8, SSB_DTYPE_B1 } SsbDType;
+/* The two headers on their own, for a caller that streams its own archive: the NPY header of a flat array
+ * (returns its length in bytes, a multiple of 64, or a negative status) and the 512-byte member header. */
+int ssb_ckpt_array_header(int dtype, uint64_t numel, void* out, int capacity);
+int ssb_ckpt_member_header(const char* name, uint64_t size, void* out512);
+typedef struct SsbCkptWriter SsbCkptWriter;
+typedef struct SsbCkptReader SsbCkptReader;
+int ssb_ckpt_writer_open(const char* path, SsbCkptWriter** out);
+int ssb_ckpt_write_bytes(SsbCkptWriter* w, const char* name, const void* data, uint64_t size);
+int ssb_ckpt_write_host(SsbCkptWriter* w, const char* name, const void* h_ptr, uint64_t nbytes, int dtype);
+int ssb_ckpt_write_device(SsbCkptWriter* w, const char* name, const void* d_ptr, uint64_t nbytes, int dtype, void* stream);
+int ssb_ckpt_writer_close(SsbCkptWriter* w);   /* writes the end-of-archive blocks, closes the file and frees w */
+int ssb_ckpt_reader_open(const char* path, SsbCkptReader** out);
+int ssb_ckpt_member_count(const SsbCkptReader* r);
+int ssb_ckpt_member_info(const SsbCkptReader* r, int index, char* name, int name_capacity, uint64_t* size);
+int ssb_ckpt_read_bytes(SsbCkptReader* r, const char* name, void* buf, uint64_t capacity, uint64_t* size);
+int ssb_ckpt_array_info(SsbCkptReader* r, const char* name, char* descr, int descr_capacity, uint64_t* data_bytes);
+int ssb_ckpt_read_host(SsbCkptReader* r, const char* name, void* h_ptr, uint64_t nbytes);
+int ssb_ckpt_read_device(SsbCkptReader* r, const char* name, void* d_ptr, uint64_t nbytes, void* stream);
+int ssb_ckpt_reader_close(SsbCkptReader* r);
 
 /* Number of kernel launches the library has issued from this process so far. */
 int64_t ssb_launch_count(void);

@@ -17,6 +17,7 @@ SSB_ERR_CAPACITY = -3
 SSB_ERR_OUT_OF_MEMORY = -4
 SSB_ERR_UNSUPPORTED = -5
 SSB_ERR_PEER = -6
+SSB_ERR_IO = -7
 
 CAMERA_PINHOLE, CAMERA_FISHEYE, CAMERA_EQUISOLID, CAMERA_EQUIRECT = 0, 1, 2, 3
 SSB_ACCUM_NONE, SSB_ACCUM_MAX, SSB_ACCUM_SUM, SSB_ACCUM_AVG = 0, 1, 2, 3
@@ -127,6 +128,21 @@ SIGNATURES = {
     "ssb_step_set_profiling": (C.c_int, [_P, C.c_int]),
     "ssb_step_get_profile": (C.c_int, [_P, _P, _P]),
     "ssb_launch_count": (_I64, []),
+    "ssb_ckpt_array_header": (C.c_int, [C.c_int, C.c_uint64, _P, C.c_int]),
+    "ssb_ckpt_member_header": (C.c_int, [C.c_char_p, C.c_uint64, _P]),
+    "ssb_ckpt_writer_open": (C.c_int, [C.c_char_p, _P]),
+    "ssb_ckpt_write_bytes": (C.c_int, [_P, C.c_char_p, _P, C.c_uint64]),
+    "ssb_ckpt_write_host": (C.c_int, [_P, C.c_char_p, _P, C.c_uint64, C.c_int]),
+    "ssb_ckpt_write_device": (C.c_int, [_P, C.c_char_p, _P, C.c_uint64, C.c_int, _P]),
+    "ssb_ckpt_writer_close": (C.c_int, [_P]),
+    "ssb_ckpt_reader_open": (C.c_int, [C.c_char_p, _P]),
+    "ssb_ckpt_member_count": (C.c_int, [_P]),
+    "ssb_ckpt_member_info": (C.c_int, [_P, C.c_int, _P, C.c_int, _P]),
+    "ssb_ckpt_read_bytes": (C.c_int, [_P, C.c_char_p, _P, C.c_uint64, _P]),
+    "ssb_ckpt_array_info": (C.c_int, [_P, C.c_char_p, _P, C.c_int, _P]),
+    "ssb_ckpt_read_host": (C.c_int, [_P, C.c_char_p, _P, C.c_uint64]),
+    "ssb_ckpt_read_device": (C.c_int, [_P, C.c_char_p, _P, C.c_uint64, _P]),
+    "ssb_ckpt_reader_close": (C.c_int, [_P]),
 }
 
 _lib = None

@@ -167,3 +167,55 @@ def test_a_rank_that_left_is_reported_within_the_timeout(tmp_path):
     assert int(status) == L.SSB_ERR_PEER
     assert float(seconds) < 30.0                 # the process-group timeout is 3 s; the step never waits for ever
     assert (tmp_path / "rank1.txt").exists()
+
+
+# ---- checkpoint of a sharded optimiser state -------------------------------------------------------------------
+# Each rank has updated only its own range of the Adam moments; before rank 0 writes state.tar the owners
+# broadcast their ranges.  Run on CPU tensors over gloo with a stand-in for the trainer.
+def _gather_worker(rank, world, port, out_dir):
+    from types import SimpleNamespace
+    from spirula_studio_b200 import checkpoint as ck
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    n, per = 1300, 1024                                   # ranges of 512-splat multiples: [0, 1024) and [1024, 1300)
+    first = min(n, rank * per)
+    count = min(n, first + per) - first
+    widths = dict(means=3, quats=4, scales=3, opacities=1, features_dc=3)
+
+    def moments(tag):
+        out = {}
+        for i, (a, w) in enumerate(widths.items()):
+            t = torch.zeros(n * w)
+            t[first * w: (first + count) * w] = torch.arange(first * w, (first + count) * w, dtype=torch.float32) + 1000 * i + tag
+            out[a] = t
+        out["features_sh"] = None
+        return out
+
+    cells, blocks = n * 45, (n * 45 + 255) // 256
+    packed = torch.zeros(cells * 2, dtype=torch.uint8)
+    packed[first * 90: (first + count) * 90] = (torch.arange(first * 90, (first + count) * 90) % 251).to(torch.uint8) + 1
+    bounds = torch.zeros(blocks * 4)
+    b0, b1 = first * 45 // 256, ((first + count) * 45 + 255) // 256
+    bounds[b0 * 4: b1 * 4] = torch.arange(b0 * 4, b1 * 4, dtype=torch.float32) + 0.5
+    tr = SimpleNamespace(world_size=world, rank=rank, pg=None, grad_sync="peer", first=first, count=count, quant=True,
+                         m1=moments(0.25), m2=moments(0.75), sh_optim_packed=packed, sh_optim_bounds=bounds)
+    ck.gather_optimizer_state(tr)
+    torch.save(dict(m1=tr.m1, m2=tr.m2, packed=packed, bounds=bounds), os.path.join(out_dir, f"gathered_{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_optimizer_state_is_completed_before_a_save(tmp_path):
+    world, port = 2, 31000 + os.getpid() % 2000
+    mp.spawn(_gather_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    a, b = (torch.load(tmp_path / f"gathered_{r}.pt") for r in range(2))
+    n = 1300
+    for i, (k, w) in enumerate(dict(means=3, quats=4, scales=3, opacities=1, features_dc=3).items()):
+        for mom, tag in (("m1", 0.25), ("m2", 0.75)):
+            want = torch.arange(n * w, dtype=torch.float32) + 1000 * i + tag
+            assert torch.equal(a[mom][k], want) and torch.equal(b[mom][k], want), (mom, k)
+    want_p = (torch.arange(n * 90) % 251).to(torch.uint8) + 1
+    assert torch.equal(a["packed"], want_p) and torch.equal(b["packed"], want_p)
+    want_b = torch.arange(((n * 45 + 255) // 256) * 4, dtype=torch.float32) + 0.5
+    assert torch.equal(a["bounds"], want_b) and torch.equal(b["bounds"], want_b)

@@ -334,6 +334,35 @@ int ssb_loss_l1_ssim_fwdbwd_map(const float* d_render, const float* d_gt, int32_
                                 float w_l1, float w_ssim, float* d_v_render, float* d_losses,
                                 int32_t ssim_loss_map_mode, float ssim_loss_map_weight, float* d_loss_map, void* stream);
 
+/* Multi-scale loss with an optional mask and the densification loss map: the colour part of
+ * compute_multi_scale_per_pixel_losses (src/kernels/loss/PerPixelLoss.cu:941-1363) with fused_ssim_inplace's mask
+ * handling (src/kernels/loss/FusedSSIM.cu:105-195,717-724,829-915,988-994).
+ *   num_scales 1..4: level s is level s-1 pooled 2x2 (size max(1, n / 2)); every level computes
+ *     w_l1 * L1 + w_ssim * (1 - SSIM) and its gradient, and the levels are averaged:
+ *     d_v_render = (v_0 + sum_s 0.25^s * v_s[y >> s][x >> s]) / num_scales.
+ *   d_mask [n_images][mask_h][mask_w] bytes (NULL: none), != 0 = the pixel takes part.  A mask of another size than
+ *     the image is nearest-sampled.  Masked pixels leave the L1 sum (which is divided by the number of unmasked
+ *     pixels) and every SSIM window, a window centred on one scores 1, and they receive no gradient.  With a mask of
+ *     the image's size the pyramid pools over the unmasked children only.
+ *   loss_map_mode (DensifyLossMapMode, src/kernels/loss/PerPixelLoss.cuh:98-110): 0 none; 1 the pixel's weighted L1
+ *     term + w_ssim * (1 - SSIM); 2, 3, 4 w_ssim * (1 - SSIM / contrast-structure / structure).  d_loss_map
+ *     [n_images][H][W] is OVERWRITTEN with the mean over the levels.  Modes 5..10 (edge-aware maps, non-maximum
+ *     suppression) return SSB_ERR_UNSUPPORTED.
+ * d_losses[3] (overwritten): mean over the levels of the L1 term, level 0's SSIM, mean over the levels of the total.
+ * The workspace holds the pyramid (about 0.42 of the three level-0 images for 4 levels) and is sized by
+ * ssb_loss_workspace_bytes for the same arguments; SSB_ERR_CAPACITY when it is too small. */
+typedef struct SsbLossConfig {
+    float w_l1, w_ssim;
+    int32_t num_scales;
+    int32_t loss_map_mode;
+    const uint8_t* d_mask;
+    int32_t mask_h, mask_w;
+} SsbLossConfig;
+int64_t ssb_loss_workspace_bytes(int32_t n_images, int32_t height, int32_t width, const SsbLossConfig* cfg);
+int ssb_loss_multi_scale(const float* d_render, const float* d_gt, int32_t n_images, int32_t height, int32_t width,
+                         const SsbLossConfig* cfg, float* d_v_render, float* d_losses, float* d_loss_map, void* d_workspace,
+                         int64_t workspace_bytes, void* stream);
+
 /* ---- optimiser ---------------------------------------------------------- */
 
 typedef struct SsbAdamConfig {
@@ -537,6 +566,14 @@ int64_t ssb_step_device_bytes(const SsbStep* step);
  * (EngineTrainStep.cpp:264-272); the caller zeroes them.  Allocates one [H][W] map per lane on first use. */
 int ssb_step_set_densify(SsbStep* step, int32_t ssim_loss_map_mode, float ssim_loss_map_weight, int32_t accum_mode,
                          float* d_accum_weight, float* d_accum_weight_den);
+
+/* Makes every view of the step use the general loss (ssb_loss_multi_scale) with cfg's num_scales, loss_map_mode and
+ * mask; w_l1 / w_ssim stay the step's.  cfg->d_mask, if given, holds one mask per view of the following ssb_step_views
+ * calls, [n_views][mask_h][mask_w], indexed like d_gt.  With densification outputs switched on (ssb_step_set_densify)
+ * and loss_map_mode != 0 the per-splat weights are gathered from this loss map (the reference's path:
+ * src/engine/EngineLoss.cpp:852-862) instead of the SSIM-only map.  cfg == NULL switches back to the one-scale,
+ * unmasked loss.  Allocates the pyramid workspace per lane. */
+int ssb_step_set_loss(SsbStep* step, const SsbLossConfig* cfg);
 
 /* Forward + loss + backward of `n_views` views (device camera arrays and device
  * targets d_gt [n_views][H][W][3]); gradients are overwritten by the first view

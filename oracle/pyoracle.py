@@ -180,6 +180,39 @@ def loss_l1_ssim_map(render, gt, B, H, W, mode, weight, loss_map, w_l1=0.8, w_ss
     return v, losses
 
 
+def loss_l1_ssim_masked(render, gt, B, H, W, mask=None, map_mode=0, map_weight=0.0, map_l1=False, loss_map=None, w_l1=0.8, w_ssim=0.2):
+    """One level with a mask (uint8 [Bm, Hm, Wm], nonzero = takes part) and the loss-map variants; loss_map is added to in place."""
+    lib = load()
+    v = np.zeros((B * H * W, 3), np.float32)
+    losses = np.zeros(3, np.float32)
+    if mask is not None:
+        mask = np.ascontiguousarray(mask, dtype=np.uint8)
+        Bm, Hm, Wm = mask.shape
+    else:
+        Bm = Hm = Wm = 0
+    lib.oracle_loss_l1_ssim_masked(C.c_int(B), C.c_int(H), C.c_int(W), C.c_float(w_l1), C.c_float(w_ssim), _p(_f(render)), _p(_f(gt)),
+                                   _p(mask) if mask is not None else None, C.c_int(Bm), C.c_int(Hm), C.c_int(Wm), _p(v), _p(losses),
+                                   C.c_int(map_mode), C.c_float(map_weight), C.c_int(int(map_l1)), _p(loss_map) if loss_map is not None else None)
+    return v, losses
+
+
+def loss_multi_scale(render, gt, B, H, W, num_scales, mask=None, loss_map_mode=0, w_l1=0.8, w_ssim=0.2):
+    """The multi-scale loss; returns (v_render [B*H*W, 3], losses[3], loss_map [B*H*W] or None)."""
+    lib = load()
+    v = np.zeros((B * H * W, 3), np.float32)
+    losses = np.zeros(3, np.float32)
+    loss_map = np.zeros(B * H * W, np.float32) if loss_map_mode else None
+    Hm = Wm = 0
+    if mask is not None:
+        mask = np.ascontiguousarray(mask, dtype=np.uint8)
+        assert mask.shape[0] == B
+        Hm, Wm = mask.shape[1:]
+    lib.oracle_loss_multi_scale(C.c_int(B), C.c_int(H), C.c_int(W), C.c_int(num_scales), C.c_float(w_l1), C.c_float(w_ssim), _p(_f(render)),
+                                _p(_f(gt)), _p(mask) if mask is not None else None, C.c_int(Hm), C.c_int(Wm), _p(v), _p(losses),
+                                C.c_int(loss_map_mode), _p(loss_map) if loss_map is not None else None)
+    return v, losses, loss_map
+
+
 def adam_geometry(p, g, m1, m2, step, lrs, grad_scale=1.0, zero_grad=0):
     """In place on the numpy arrays of p, g, m1, m2 (dicts with means, quats, scales, opacities)."""
     lib = load()

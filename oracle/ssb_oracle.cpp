@@ -1011,30 +1011,92 @@ void oracle_raster_bwd(
 // map_mode (SsimLossMapMode, src/kernels/loss/PerPixelLoss.cuh:129-134) != 0: loss_map[b][y][x] +=
 // map_weight * (1 - mean over channels of v), v = SSIM (1), D/B (2), D / (2 sqrt(s1 s2) + C2) (3);
 // FusedSSIM.cu:861-886,1009-1016.
-void oracle_loss_l1_ssim_map(
+//
+// mask (may be NULL) [Bm][Hm][Wm] bytes, != 0 = the pixel takes part.  Read as get_pix_value does
+// (FusedSSIM.cu:105-126) and nearest_sample_b (src/core/Interpolation.cuh:108-120): nearest sample when its
+// size is not the image's, and every tap outside the image (or an image index >= Bm) reads unmasked.
+//   per-pixel part (per_pixel_losses.slang:161-176,290-291,365-375): masked pixels add nothing to the L1 sum and
+//     get no gradient; the sum is divided by max(number of unmasked pixels of the batch, 1).
+//   SSIM part (FusedSSIM.cu:717-724,829-848,858-887,902-915,988-994): masked samples are dropped from the
+//     window sums, the sums are divided by the window's coverage (Gaussian weight on unmasked taps,
+//     :138-177), a window centred on a masked pixel scores 1 and sends no gradient, a masked pixel
+//     receives none, and its loss-map value is that of a perfect match.
+// map_l1 != 0 (DensifyLossMapMode::LossFull, PerPixelLoss.cu:1127-1131, :200-217): the pixel's weighted
+//   L1 term |mask * w_l1 * mean_c |r - g|| is added to the loss map as well.
+static inline bool mask_tap(const uint8_t* mask, int b, int y, int x, int Bm, int Hm, int Wm, int H, int W) {
+    if (!mask) return true;
+    if ((unsigned)b >= (unsigned)Bm || (unsigned)x >= (unsigned)W || (unsigned)y >= (unsigned)H) return true;
+    int xs = x, ys = y;
+    if (Wm != W || Hm != H) {
+        float u = ((float)x + 0.5f) * (float)Wm / (float)W - 0.5f;
+        float v = ((float)y + 0.5f) * (float)Hm / (float)H - 0.5f;
+        xs = std::max(0, std::min(Wm - 1, (int)std::floor(u + 0.5f)));
+        ys = std::max(0, std::min(Hm - 1, (int)std::floor(v + 0.5f)));
+    }
+    return mask[((size_t)b * Hm + ys) * Wm + xs] != 0;
+}
+
+void oracle_loss_l1_ssim_masked(
     int B, int H, int W, float w_l1, float w_ssim,
-    const float* render, const float* gt, float* v_render, float* losses,
-    int map_mode, float map_weight, float* loss_map) {
+    const float* render, const float* gt, const uint8_t* mask, int Bm, int Hm, int Wm,
+    float* v_render, float* losses, int map_mode, float map_weight, int map_l1, float* loss_map) {
     const int64_t P = (int64_t)H * W;
     std::vector<float> lm_sum(map_mode ? (size_t)B * P : 0, 0.f);
+    std::vector<uint8_t> mk((size_t)B * P, 1);
+    double mask_total = (double)B * P;
+    if (mask) {
+        mask_total = 0.0;
+        for (int b = 0; b < B; ++b)
+            for (int y = 0; y < H; ++y)
+                for (int x = 0; x < W; ++x) {
+                    bool m = mask_tap(mask, b, y, x, Bm, Hm, Wm, H, W);
+                    mk[(size_t)b * P + (size_t)y * W + x] = m;
+                    mask_total += m;
+                }
+    }
     double l1_sum = 0.0, ssim_sum = 0.0;
-    const float inv_mask_total = 1.0f / std::max((float)(B * P), 1.0f);
+    const float inv_mask_total = 1.0f / std::max((float)mask_total, 1.0f);
 #pragma omp parallel for reduction(+ : l1_sum) schedule(static)
     for (int64_t i = 0; i < (int64_t)B * P; ++i) {
         float s = 0.f;
+        const float m = mk[i] ? 1.f : 0.f;
         for (int ch = 0; ch < 3; ++ch) {
             float d = render[3 * i + ch] - gt[3 * i + ch];
             s += std::fabs(d);
             float sg = d > 0.f ? 1.f : (d < 0.f ? -1.f : 0.f);
-            v_render[3 * i + ch] = w_l1 * sg * (1.0f / 3.0f) * inv_mask_total;
+            v_render[3 * i + ch] = m * w_l1 * sg * (1.0f / 3.0f) * inv_mask_total;
         }
-        l1_sum += (double)(s * (1.0f / 3.0f));
+        l1_sum += (double)(m * s * (1.0f / 3.0f));
+        if (map_l1 && loss_map) loss_map[i] += std::fabs(m * w_l1 * (s * (1.0f / 3.0f)));
     }
     const float grad = -w_ssim / (3.0f * B * W * H);   // FusedSSIM.cu:667
     const float kC1 = 0.01f * 0.01f, kC2 = 0.03f * 0.03f;
-    for (int b = 0; b < B; ++b)
+    for (int b = 0; b < B; ++b) {
+        // coverage of every window (FusedSSIM.cu:138-177); rows outside the image count as unmasked
+        std::vector<float> cov;
+        if (mask) {
+            std::vector<float> tmp(P);
+            cov.resize(P);
+            for (int y = 0; y < H; ++y)
+                for (int x = 0; x < W; ++x) {
+                    float acc = 0.f;
+                    for (int d = -5; d <= 5; ++d) acc += kGauss[5 - std::abs(d)] * (float)mask_tap(mask, b, y, x + d, Bm, Hm, Wm, H, W);
+                    tmp[(size_t)y * W + x] = acc;
+                }
+            for (int y = 0; y < H; ++y)
+                for (int x = 0; x < W; ++x) {
+                    float acc = 0.f;
+                    for (int d = -5; d <= 5; ++d) {
+                        int yy = y + d;
+                        float row = (unsigned)yy < (unsigned)H ? tmp[(size_t)yy * W + x] : 0.9999999f;
+                        acc += kGauss[5 - std::abs(d)] * row;
+                    }
+                    cov[(size_t)y * W + x] = acc;
+                }
+        }
+        const uint8_t* mb = mk.data() + (size_t)b * P;
         for (int ch = 0; ch < 3; ++ch) {
-            // horizontal pass of the five moments, zero padding
+            // horizontal pass of the five moments, zero padding; masked samples are dropped
             std::vector<float> hx(P), hx2(P), hy(P), hy2(P), hxy(P);
             auto X = [&](int y, int x) { return render[3 * ((int64_t)b * P + (int64_t)y * W + x) + ch]; };
             auto Y = [&](int y, int x) { return gt[3 * ((int64_t)b * P + (int64_t)y * W + x) + ch]; };
@@ -1044,7 +1106,7 @@ void oracle_loss_l1_ssim_map(
                     float sx = 0, sx2 = 0, sy = 0, sy2 = 0, sxy = 0;
                     for (int d = -5; d <= 5; ++d) {
                         int xx = x + d;
-                        if (xx < 0 || xx >= W) continue;
+                        if (xx < 0 || xx >= W || !mb[(size_t)y * W + xx]) continue;
                         float w = kGauss[d + 5], a = X(y, xx), c = Y(y, xx);
                         sx += a * w; sx2 += a * a * w; sy += c * w; sy2 += c * c * w; sxy += a * c * w;
                     }
@@ -1064,26 +1126,30 @@ void oracle_loss_l1_ssim_map(
                         int64_t o = (int64_t)yy * W + x;
                         o0 += hx[o] * w; o1 += hx2[o] * w; o2 += hy[o] * w; o3 += hy2[o] * w; o4 += hxy[o] * w;
                     }
-                    // FusedSSIM.cu:822-848,891-898
-                    float mu1 = o0, mu2 = o2;
+                    int64_t o = (int64_t)y * W + x;
+                    const float inv_cov = mask ? 1.0f / std::max(cov[o], 1e-6f) : 1.0f;
+                    const bool cmask = mb[o] != 0;
+                    // FusedSSIM.cu:822-848,891-915
+                    float mu1 = o0 * inv_cov, mu2 = o2 * inv_cov;
                     float mu1_sq = mu1 * mu1, mu2_sq = mu2 * mu2;
-                    float sigma1_sq = o1 - mu1_sq, sigma2_sq = o3 - mu2_sq, sigma12 = o4 - mu1 * mu2;
+                    float sigma1_sq = o1 * inv_cov - mu1_sq, sigma2_sq = o3 * inv_cov - mu2_sq, sigma12 = o4 * inv_cov - mu1 * mu2;
                     float A = mu1_sq + mu2_sq + kC1;
                     float Bv = sigma1_sq + sigma2_sq + kC2;
                     float C_ = 2.f * mu1 * mu2 + kC1;
                     float D_ = 2.f * sigma12 + kC2;
                     float ssim_v = (C_ * D_) / (A * Bv);
-                    csum += (double)ssim_v;
-                    int64_t o = (int64_t)y * W + x;
+                    csum += cmask ? (double)ssim_v : 1.0;
                     if (map_mode) {
                         float lm = ssim_v;
                         if (map_mode == 2) lm = D_ / Bv;
                         else if (map_mode == 3) lm = D_ / (2.f * std::sqrt(std::max(sigma1_sq, 0.0f) * std::max(sigma2_sq, 0.0f)) + kC2);
+                        if (!cmask) lm = 1.0f;
                         lm_sum[(size_t)b * P + o] += lm;
                     }
-                    d_mu1[o] = ((mu2 * 2.f * D_) / (A * Bv) - (mu2 * 2.f * C_) / (A * Bv) - (mu1 * 2.f * C_ * D_) / (A * A * Bv) + (mu1 * 2.f * C_ * D_) / (A * Bv * Bv)) * grad;
-                    d_s1[o] = ((-C_ * D_) / (A * Bv * Bv)) * grad;
-                    d_s12[o] = ((2.f * C_) / (A * Bv)) * grad;
+                    const float g = cmask ? grad * inv_cov : 0.f;
+                    d_mu1[o] = ((mu2 * 2.f * D_) / (A * Bv) - (mu2 * 2.f * C_) / (A * Bv) - (mu1 * 2.f * C_ * D_) / (A * A * Bv) + (mu1 * 2.f * C_ * D_) / (A * Bv * Bv)) * g;
+                    d_s1[o] = ((-C_ * D_) / (A * Bv * Bv)) * g;
+                    d_s12[o] = ((2.f * C_) / (A * Bv)) * g;
                 }
             ssim_sum += csum;
             // second separable convolution of the three partial maps (:903-1000)
@@ -1105,6 +1171,7 @@ void oracle_loss_l1_ssim_map(
 #pragma omp parallel for schedule(static)
             for (int y = 0; y < H; ++y)
                 for (int x = 0; x < W; ++x) {
+                    if (!mb[(size_t)y * W + x]) continue;   // a masked pixel receives no gradient (:988-994)
                     float s0 = 0, s1 = 0, s2 = 0;
                     for (int d = -5; d <= 5; ++d) {
                         int yy = y + d;
@@ -1117,11 +1184,129 @@ void oracle_loss_l1_ssim_map(
                     v_render[3 * ((int64_t)b * P + (int64_t)y * W + x) + ch] += s0 + (2.f * p1) * s1 + p2 * s2;   // :990-1000
                 }
         }
-    float l1 = (float)(l1_sum / (double)(B * P));
+    }
+    float l1 = (float)(l1_sum / std::max(mask_total, 1.0));
     float ssim = (float)(ssim_sum / (double)(3.0 * B * P));
     if (losses) { losses[0] = l1; losses[1] = ssim; losses[2] = w_l1 * l1 + w_ssim * (1.0f - ssim); }
     if (map_mode)
         for (int64_t i = 0; i < (int64_t)B * P; ++i) loss_map[i] += map_weight * (1.0f - lm_sum[i] / 3.0f);
+}
+
+void oracle_loss_l1_ssim_map(
+    int B, int H, int W, float w_l1, float w_ssim,
+    const float* render, const float* gt, float* v_render, float* losses,
+    int map_mode, float map_weight, float* loss_map) {
+    oracle_loss_l1_ssim_masked(B, H, W, w_l1, w_ssim, render, gt, nullptr, 0, 0, 0, v_render, losses, map_mode, map_weight, 0, loss_map);
+}
+
+// ---------------------------------------------------------------------------
+// Multi-scale loss: compute_multi_scale_per_pixel_losses (src/kernels/loss/PerPixelLoss.cu:941-1363)
+// restricted to the colour modalities (render, target, mask).
+//   pyramid (:1032-1097): every level halves the previous one (max(1, n / 2)).  Images pool 2x2; where a mask of the
+//     image's own size exists the pool is the mean over the unmasked children, or the plain mean when all four are
+//     masked (avg_pool_downsample_masked_float_kernel, :675-701).  The mask pools to "at least two of four"
+//     (avg_pool_downsample_bool_kernel, :723-740), halving ITS OWN size.
+//   every level (:1106-1232): the per-pixel pass writes the level's gradient, the SSIM pass adds to it; loss-map modes
+//     (DensifyLossMapMode, PerPixelLoss.cuh:98-110): 1 = per-pixel term + w_ssim * (1 - SSIM), 2/3/4 = w_ssim * (1 - SSIM / CS / structure).
+//   fold (:1262-1325): gradient = (g_0 + sum_s 0.25^s * up(g_s)) / S and loss map = (m_0 + sum_s up(m_s)) / S, with
+//     up(a)[y][x] = a[y >> s][x >> s] where that exists and 0 elsewhere (avg_pool_upsample_float_kernel, :926-943);
+//     with a mask of the image's size and S > 1 the masked pixels' gradient is cleared at the end (:1327-1336).
+//   losses (:1256-1259,1338-1345): mean over the levels; the SSIM value reported is level 0's (:1252-1253).
+// losses[0] = mean L1, losses[1] = level-0 SSIM, losses[2] = mean over levels of w_l1 * L1 + w_ssim * (1 - SSIM).
+// ---------------------------------------------------------------------------
+void oracle_loss_multi_scale(
+    int B, int H, int W, int num_scales, float w_l1, float w_ssim,
+    const float* render, const float* gt, const uint8_t* mask, int Hm, int Wm,
+    float* v_render, float* losses, int loss_map_mode, float* loss_map) {
+    struct Level { int H, W, Hm, Wm; std::vector<float> r, g, v, lm; std::vector<uint8_t> m; };
+    std::vector<Level> lv(num_scales);
+    lv[0].H = H; lv[0].W = W; lv[0].Hm = Hm; lv[0].Wm = Wm;
+    lv[0].r.assign(render, render + (size_t)B * H * W * 3);
+    lv[0].g.assign(gt, gt + (size_t)B * H * W * 3);
+    if (mask) lv[0].m.assign(mask, mask + (size_t)B * Hm * Wm);
+    for (int s = 1; s < num_scales; ++s) {
+        const Level& a = lv[s - 1];
+        Level& c = lv[s];
+        c.H = std::max(1, a.H / 2); c.W = std::max(1, a.W / 2);
+        const bool same = mask && a.Hm == a.H && a.Wm == a.W;
+        auto at = [&](const std::vector<float>& img, int b, int y, int x, int ch) {   // TensorView::at clamps nothing: 2y+1 < H holds for H >= 2
+            y = std::min(y, a.H - 1); x = std::min(x, a.W - 1);
+            return img[(((size_t)b * a.H + y) * a.W + x) * 3 + ch];
+        };
+        auto pool = [&](const std::vector<float>& src, std::vector<float>& dst) {
+            dst.resize((size_t)B * c.H * c.W * 3);
+            for (int b = 0; b < B; ++b)
+                for (int y = 0; y < c.H; ++y)
+                    for (int x = 0; x < c.W; ++x)
+                        for (int ch = 0; ch < 3; ++ch) {
+                            float acc = 0.f, box = 0.f;
+                            int n = 0;
+                            for (int dy = 0; dy < 2; ++dy)
+                                for (int dx = 0; dx < 2; ++dx) {
+                                    float v = at(src, b, 2 * y + dy, 2 * x + dx, ch);
+                                    bool valid = same ? a.m[((size_t)b * a.H + std::min(2 * y + dy, a.H - 1)) * a.W + std::min(2 * x + dx, a.W - 1)] != 0 : false;
+                                    box += 0.25f * v;
+                                    if (valid) { acc += v; ++n; }
+                                }
+                            float out;
+                            if (same) out = n ? acc / (float)n : box;
+                            else out = 0.25f * (at(src, b, 2 * y, 2 * x, ch) + at(src, b, 2 * y, 2 * x + 1, ch) + at(src, b, 2 * y + 1, 2 * x, ch) +
+                                                at(src, b, 2 * y + 1, 2 * x + 1, ch));
+                            dst[(((size_t)b * c.H + y) * c.W + x) * 3 + ch] = out;
+                        }
+        };
+        pool(a.r, c.r);
+        pool(a.g, c.g);
+        c.Hm = c.Wm = 0;
+        if (mask) {
+            c.Hm = std::max(1, a.Hm / 2); c.Wm = std::max(1, a.Wm / 2);
+            c.m.resize((size_t)B * c.Hm * c.Wm);
+            for (int b = 0; b < B; ++b)
+                for (int y = 0; y < c.Hm; ++y)
+                    for (int x = 0; x < c.Wm; ++x) {
+                        int v = 0;
+                        for (int dy = 0; dy < 2; ++dy)
+                            for (int dx = 0; dx < 2; ++dx)
+                                v += a.m[((size_t)b * a.Hm + std::min(2 * y + dy, a.Hm - 1)) * a.Wm + std::min(2 * x + dx, a.Wm - 1)] != 0;
+                        c.m[((size_t)b * c.Hm + y) * c.Wm + x] = v >= 2;
+                    }
+        }
+    }
+    const int ssim_mode = loss_map_mode == 1 || loss_map_mode == 2 ? 1 : (loss_map_mode == 3 ? 2 : (loss_map_mode == 4 ? 3 : 0));
+    double l1_mean = 0.0, tot_mean = 0.0;
+    float ssim0 = 0.f;
+    for (int s = 0; s < num_scales; ++s) {
+        Level& c = lv[s];
+        c.v.assign((size_t)B * c.H * c.W * 3, 0.f);
+        if (loss_map) c.lm.assign((size_t)B * c.H * c.W, 0.f);
+        float l[3];
+        oracle_loss_l1_ssim_masked(B, c.H, c.W, w_l1, w_ssim, c.r.data(), c.g.data(), mask ? c.m.data() : nullptr, B, c.Hm, c.Wm, c.v.data(), l,
+                                   loss_map ? ssim_mode : 0, w_ssim, loss_map && loss_map_mode == 1, loss_map ? c.lm.data() : nullptr);
+        l1_mean += l[0] / num_scales;
+        tot_mean += l[2] / num_scales;
+        if (s == 0) ssim0 = l[1];
+    }
+    const float inv_s = 1.0f / (float)num_scales;
+    for (int b = 0; b < B; ++b)
+        for (int y = 0; y < H; ++y)
+            for (int x = 0; x < W; ++x) {
+                const size_t p = ((size_t)b * H + y) * W + x;
+                float g[3] = {lv[0].v[3 * p], lv[0].v[3 * p + 1], lv[0].v[3 * p + 2]};
+                float m = loss_map ? lv[0].lm[p] : 0.f;
+                for (int s = 1; s < num_scales; ++s) {
+                    const Level& c = lv[s];
+                    const int ys = y >> s, xs = x >> s;
+                    if (ys >= c.H || xs >= c.W) continue;
+                    const size_t q = ((size_t)b * c.H + ys) * c.W + xs;
+                    const float wgt = std::pow(0.25f, (float)s);
+                    for (int ch = 0; ch < 3; ++ch) g[ch] += wgt * c.v[3 * q + ch];
+                    if (loss_map) m += c.lm[q];
+                }
+                const bool keep = !(num_scales > 1 && mask && Hm == H && Wm == W && !mask[p]);
+                for (int ch = 0; ch < 3; ++ch) v_render[3 * p + ch] = num_scales > 1 ? (keep ? g[ch] * inv_s : 0.f) : g[ch];
+                if (loss_map) loss_map[p] = num_scales > 1 ? m * inv_s : m;
+            }
+    if (losses) { losses[0] = (float)l1_mean; losses[1] = ssim0; losses[2] = (float)tot_mean; }
 }
 
 void oracle_loss_l1_ssim(

@@ -52,6 +52,10 @@ int launch_loss(const float* d_render, const float* d_gt, int B, int H, int W, f
                 float* d_v_render, float* d_losses, cudaStream_t st);
 int launch_loss_map(const float* d_render, const float* d_gt, int B, int H, int W, float w_l1, float w_ssim,
                     float* d_v_render, float* d_losses, int map_mode, float map_weight, float* d_loss_map, cudaStream_t st);
+int64_t loss_workspace_bytes(int B, int H, int W, const SsbLossConfig& cfg);
+int launch_loss_multi(const float* d_render, const float* d_gt, int B, int H, int W, const SsbLossConfig& cfg, float* d_v_render,
+                      float* d_losses, float* d_loss_map, void* d_ws, int64_t ws_bytes, cudaStream_t st);
+int check_loss_config(const SsbLossConfig* cfg, const char* who);
 int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
                        SsbScreenRec* d_v_screen, const SsbSplats* grads, int accumulate, int clear_v_screen, void* stream,
                        const int32_t* d_pair_of);

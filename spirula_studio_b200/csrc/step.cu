@@ -35,6 +35,7 @@ struct SsbLane {
     int32_t* offsets;     // [tiles]
     float* rgb; float* T; int32_t* last_ids; float* v_rgb;
     float* loss_map;      // [P], only with ssb_step_set_densify
+    void* loss_ws;        // pyramid of the general loss, only with ssb_step_set_loss
     cudaStream_t stream;
     cudaEvent_t bwd_done;  // this lane's last projection backward
     cudaEvent_t all_done;
@@ -61,6 +62,10 @@ struct SsbStep {
     float* accum_weight;
     float* accum_weight_den;
     int64_t* max_pairs;       // device: largest per-view pair count since it was last cleared
+    // general loss (levels, mask, loss-map mode); off unless ssb_step_set_loss switched it on
+    int loss_general;
+    SsbLossConfig loss_cfg;
+    int64_t loss_ws_bytes;
 };
 
 namespace ssb {
@@ -84,7 +89,7 @@ static void lane_free(SsbLane& l) {
     cudaFree(l.aabb); cudaFree(l.depths); cudaFree(l.screen); cudaFree(l.v_screen);
     cudaFree(l.isect_ws); cudaFree(l.flat);
     cudaFree(l.n_isects); cudaFree(l.offsets);
-    cudaFree(l.rgb); cudaFree(l.T); cudaFree(l.last_ids); cudaFree(l.v_rgb); cudaFree(l.loss_map);
+    cudaFree(l.rgb); cudaFree(l.T); cudaFree(l.last_ids); cudaFree(l.v_rgb); cudaFree(l.loss_map); cudaFree(l.loss_ws);
     if (l.stream) cudaStreamDestroy(l.stream);
     if (l.bwd_done) cudaEventDestroy(l.bwd_done);
     if (l.all_done) cudaEventDestroy(l.all_done);
@@ -144,7 +149,22 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
     if ((e = ssb_raster_fwd(l.screen, n, l.offsets, l.flat, s->capacity, l.n_isects, 1, W, H, l.rgb, nullptr, l.T, l.last_ids, st))) return e;
     SSB_MARK(5);
     if (gt_ready) SSB_CUDA(cudaStreamWaitEvent(st, gt_ready, 0));      // the view's target image has landed
-    if (s->accum_mode) {
+    if (s->loss_general) {
+        // levels, mask and loss-map mode of ssb_step_set_loss; the view's mask lies where its target does
+        SsbLossConfig lc = s->loss_cfg;
+        if (lc.d_mask) lc.d_mask += (int64_t)v * lc.mask_h * lc.mask_w;
+        if (!s->accum_mode) lc.loss_map_mode = 0;
+        if ((e = launch_loss_multi(l.rgb, d_gt + (int64_t)v * P * 3, 1, H, W, lc, l.v_rgb, d_losses, s->accum_mode ? l.loss_map : nullptr,
+                                   l.loss_ws, s->loss_ws_bytes, st))) return e;
+        SSB_MARK(6);
+        if (s->accum_mode && lc.loss_map_mode) {
+            if ((e = ssb_raster_bwd_accum(l.screen, n, l.offsets, l.flat, s->capacity, l.n_isects, 1, W, H, nullptr, l.T, l.last_ids, l.v_rgb, nullptr,
+                                          nullptr, l.v_screen, s->accum_mode, l.loss_map, n, nullptr, s->accum_weight, s->accum_weight_den, st))) return e;
+        } else {
+            if ((e = ssb_raster_bwd(l.screen, n, l.offsets, l.flat, s->capacity, l.n_isects, 1, W, H, nullptr, l.T, l.last_ids,
+                                    l.v_rgb, nullptr, nullptr, l.v_screen, st))) return e;
+        }
+    } else if (s->accum_mode) {
         // the view's SSIM loss map, then the backward pass that also folds it into the per-splat weights
         SSB_CUDA(cudaMemsetAsync(l.loss_map, 0, P * sizeof(float), st));
         if ((e = launch_loss_map(l.rgb, d_gt + (int64_t)v * P * 3, 1, H, W, s->cfg.w_l1, s->cfg.w_ssim, l.v_rgb, d_losses, s->map_mode,
@@ -169,6 +189,34 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
 }  // namespace ssb
 
 extern "C" {
+
+int ssb_step_set_loss(SsbStep* s, const SsbLossConfig* cfg) {
+    using namespace ssb;
+    SSB_REQUIRE(s, "ssb_step_set_loss: NULL step");
+    if (!cfg) { s->loss_general = 0; return SSB_OK; }
+    if (int e = check_loss_config(cfg, "ssb_step_set_loss")) return e;
+    SsbLossConfig c = *cfg;
+    c.w_l1 = s->cfg.w_l1; c.w_ssim = s->cfg.w_ssim;
+    const int64_t need = loss_workspace_bytes(1, s->cfg.height, s->cfg.width, c);
+    const int64_t P = (int64_t)s->cfg.width * s->cfg.height;
+    for (int k = 0; k < s->n_lanes; ++k) {
+        SsbLane& l = s->lane[k];
+        if (!l.loss_ws || s->loss_ws_bytes < need) {
+            SSB_CUDA(cudaStreamSynchronize(l.stream));
+            cudaFree(l.loss_ws);
+            l.loss_ws = nullptr;
+            char* p = nullptr;
+            if (int e = dev_alloc(&p, need, s->bytes)) return e;
+            l.loss_ws = p;
+        }
+        if (c.loss_map_mode && !l.loss_map)
+            if (int e = dev_alloc(&l.loss_map, P, s->bytes)) return e;
+    }
+    s->loss_ws_bytes = std::max(s->loss_ws_bytes, need);
+    s->loss_cfg = c;
+    s->loss_general = 1;
+    return SSB_OK;
+}
 
 int ssb_step_set_densify(SsbStep* s, int32_t ssim_loss_map_mode, float ssim_loss_map_weight, int32_t accum_mode,
                          float* d_accum_weight, float* d_accum_weight_den) {

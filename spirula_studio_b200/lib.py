@@ -48,6 +48,14 @@ class SsbCameras(C.Structure):
                 ("height", C.c_int32), ("model", C.c_int32), ("antialiased", C.c_int32)]
 
 
+class SsbLossConfig(C.Structure):
+    _fields_ = [("w_l1", C.c_float), ("w_ssim", C.c_float), ("num_scales", C.c_int32), ("loss_map_mode", C.c_int32),
+                ("d_mask", C.c_void_p), ("mask_h", C.c_int32), ("mask_w", C.c_int32)]
+
+
+LOSS_MAP_NONE, LOSS_MAP_LOSS_FULL, LOSS_MAP_SSIM_FULL, LOSS_MAP_SSIM_CS, LOSS_MAP_SSIM_STRUCTURE = range(5)
+
+
 class SsbAdamConfig(C.Structure):
     _fields_ = [("lr_means", C.c_float), ("lr_quats", C.c_float), ("lr_scales", C.c_float), ("lr_opacities", C.c_float),
                 ("lr_features_dc", C.c_float), ("lr_features_sh", C.c_float), ("sh_reg_weight", C.c_float),
@@ -112,6 +120,9 @@ SIGNATURES = {
     "ssb_loss_l1_ssim_fwdbwd": (C.c_int, [_P, _P, _I32, _I32, _I32, _F, _F, _P, _P, _P]),
     "ssb_step_set_densify": (C.c_int, [_P, _I32, _F, _I32, _P, _P]),
     "ssb_loss_l1_ssim_fwdbwd_map": (C.c_int, [_P, _P, _I32, _I32, _I32, _F, _F, _P, _P, _I32, _F, _P, _P]),
+    "ssb_loss_workspace_bytes": (_I64, [_I32, _I32, _I32, _P]),
+    "ssb_loss_multi_scale": (C.c_int, [_P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P, _I64, _P]),
+    "ssb_step_set_loss": (C.c_int, [_P, _P]),
     "ssb_adam_step": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _P, _P]),
     "ssb_adam_step_sh_quantized": (C.c_int, [_P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _P, _P]),
     "ssb_adam_step_ex": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _P, _P, _P]),

@@ -120,6 +120,19 @@ def loss_map_base(tag, n_pixels):
     return np.random.default_rng(50 + ord(tag)).random(n_pixels, dtype=np.float32)
 
 
+def loss_masks(tag, B, H, W):
+    """Masks for the loss fixtures (uint8, 1 = the pixel takes part): "same" has the image's size, a masked rectangle that
+    reaches the border, a masked stripe and 10 % masked speckle; "half" is stored at another resolution (nearest-sampled)."""
+    rng = np.random.default_rng(70 + ord(tag))
+    same = (rng.random((B, H, W)) > 0.10).astype(np.uint8)
+    same[:, H // 4: H // 2, W // 3:] = 0
+    same[:, :, 5:8] = 0
+    Hh, Wh = H // 2 + 1, W // 2
+    half = (rng.random((B, Hh, Wh)) > 0.15).astype(np.uint8)
+    half[:, : Hh // 3, : Wh // 2] = 0
+    return dict(same=same, half=half)
+
+
 def adam_inputs():
     n = 700
     cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=n)

@@ -25,7 +25,7 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, HERE)
 
 from golden_cases import (ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
-                          build_case, loss_inputs, loss_map_base, quant_sh_inputs, raster_cotangents)  # noqa: E402
+                          build_case, loss_inputs, loss_map_base, loss_masks, quant_sh_inputs, raster_cotangents)  # noqa: E402
 
 DEV = "cuda:0"
 
@@ -121,6 +121,29 @@ def run_loss_map(ref, out_dir):
                   "ref_ssim_inplace_map")
             out[f"{tag}_map{mode}"] = lm.cpu().numpy()
     np.savez_compressed(os.path.join(out_dir, "ssim_map.npz"), **out)
+
+
+def run_loss_masked(ref, out_dir):
+    """The masked SSIM launch (coverage pass + kernel) for a mask of the image's size and one of another size: gradient, mean
+    SSIM and the three loss-map variants added onto a seeded map."""
+    out = {}
+    for tag, (B, H, W, render, gt) in loss_inputs().items():
+        d_render, d_gt = dev(render), dev(gt)
+        for kind, mask in loss_masks(tag, B, H, W).items():
+            d_mask = torch.from_numpy(mask.astype(np.bool_)).to(DEV)
+            Bm, Hm, Wm = mask.shape
+            for mode in (0, 1, 2, 3):
+                v = torch.zeros(B * H * W, 3, device=DEV)
+                s = torch.zeros(1, device=DEV)
+                lm = dev(loss_map_base(tag, B * H * W))
+                check(ref.ref_ssim_inplace_masked(B, H, W, P(d_render), P(d_gt), P(d_mask), Bm, Hm, Wm, C.c_float(-0.2), P(v), P(s),
+                                                  C.c_float(LOSS_MAP_WEIGHT), P(lm), mode), "ref_ssim_inplace_masked")
+                if mode == 0:
+                    out[f"{tag}_{kind}_grad"] = v.cpu().numpy()
+                    out[f"{tag}_{kind}_ssim"] = s.cpu().numpy()
+                else:
+                    out[f"{tag}_{kind}_map{mode}"] = lm.cpu().numpy()
+    np.savez_compressed(os.path.join(out_dir, "ssim_masked.npz"), **out)
 
 
 def run_adam(ref, out_dir):
@@ -374,6 +397,8 @@ def main():
         run_adam(ref, out_dir)
     if not only or "ssim_map" in only:
         run_loss_map(ref, out_dir)
+    if not only or "ssim_masked" in only:
+        run_loss_masked(ref, out_dir)
     if not only or "accum" in only:
         run_accum(ref, out_dir)
     if not only or "quant_proj" in only:

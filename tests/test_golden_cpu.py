@@ -335,3 +335,23 @@ def test_ssim_loss_map_vs_reference(oracle):
             assert frac_bad(lm, ref, 2e-5, 1e-4) <= 1e-3, (tag, mode)
             v0, _ = oracle.loss_l1_ssim(render, gt, B, H, W, 0.0, 0.2)
             assert np.array_equal(v, v0)                                     # the gradient does not depend on the map
+
+
+def test_masked_ssim_vs_reference(oracle):
+    """The masked SSIM launch (window coverage, dropped samples, masked centres and pixels) against the reference's kernel,
+    for a mask of the image's size and a nearest-sampled one of another size."""
+    from golden_cases import loss_masks
+    gold = load("ssim_masked")
+    for tag, (B, H, W, render, gt) in loss_inputs().items():
+        for kind, mask in loss_masks(tag, B, H, W).items():
+            v, losses = oracle.loss_l1_ssim_masked(render, gt, B, H, W, mask=mask, w_l1=0.0, w_ssim=0.2)
+            ref = gold[f"{tag}_{kind}_grad"]
+            assert np.abs(ref).max() > 0
+            assert frac_bad(v, ref, 2e-6 * np.abs(ref).max(), 2e-4) <= 1e-3, (tag, kind)
+            assert abs(losses[1] - gold[f"{tag}_{kind}_ssim"][0]) <= 2e-5
+            if kind == "same":
+                assert np.all(v.reshape(B, H, W, 3)[mask == 0] == 0) and np.all(ref.reshape(B, H, W, 3)[mask == 0] == 0)
+            for mode in (1, 2, 3):
+                lm = loss_map_base(tag, B * H * W)
+                oracle.loss_l1_ssim_masked(render, gt, B, H, W, mask=mask, map_mode=mode, map_weight=LOSS_MAP_WEIGHT, loss_map=lm, w_l1=0.0, w_ssim=0.2)
+                assert frac_bad(lm, gold[f"{tag}_{kind}_map{mode}"], 2e-5, 1e-4) <= 1e-3, (tag, kind, mode)

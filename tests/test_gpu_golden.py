@@ -425,3 +425,31 @@ def test_ssim_loss_map_vs_reference(lib, U):
             ref = gold[f"{tag}_map{mode}"]
             assert U.close_frac(lm.cpu().numpy(), ref, 2e-5, 1e-4) <= 1e-3, (tag, mode)
             assert torch.equal(v, v0) and torch.allclose(losses, l0, rtol=1e-5, atol=1e-7)
+
+
+@pytest.mark.gpu
+def test_masked_ssim_vs_reference(lib, U):
+    """ssb_loss_multi_scale with one level and a mask: the SSIM gradient, its mean and the loss-map variants against the
+    reference's masked kernel (mask of the image's size, and one of another size that is nearest-sampled)."""
+    from golden_cases import loss_masks
+    gold = load("ssim_masked")
+    w_ssim = 0.2
+    for tag, (B, H, W, render, gt) in loss_inputs().items():
+        d_r, d_g = U.dev(render), U.dev(gt)
+        for kind, mask in loss_masks(tag, B, H, W).items():
+            d_m = torch.from_numpy(mask).to(U.DEV)
+            for mode in (0, 2, 3, 4):
+                cfg = L.SsbLossConfig(0.0, w_ssim, 1, mode, d_m.data_ptr(), mask.shape[1], mask.shape[2])
+                need = lib.ssb_loss_workspace_bytes(B, H, W, C.byref(cfg))
+                ws = torch.empty(need, dtype=torch.uint8, device=U.DEV)
+                v = torch.zeros(B * H * W, 3, device=U.DEV); losses = torch.zeros(3, device=U.DEV); lm = torch.zeros(B * H * W, device=U.DEV)
+                L.check(lib.ssb_loss_multi_scale(L.ptr(d_r), L.ptr(d_g), B, H, W, C.byref(cfg), L.ptr(v), L.ptr(losses), L.ptr(lm), L.ptr(ws), need, None))
+                torch.cuda.synchronize()
+                if mode == 0:
+                    ref = gold[f"{tag}_{kind}_grad"]
+                    assert U.close_frac(v.cpu().numpy(), ref, 2e-6 * np.abs(ref).max(), 2e-4) <= 1e-3, (tag, kind)
+                    assert abs(losses[1].item() - gold[f"{tag}_{kind}_ssim"][0]) <= 2e-5
+                else:
+                    # the reference adds weight * (1 - v) onto a seeded map; the library overwrites with w_ssim * (1 - v)
+                    ref = (gold[f"{tag}_{kind}_map{mode - 1}"] - loss_map_base(tag, B * H * W)) * (w_ssim / LOSS_MAP_WEIGHT)
+                    assert U.close_frac(lm.cpu().numpy(), ref, 2e-5, 1e-4) <= 1e-3, (tag, kind, mode)

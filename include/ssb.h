@@ -78,9 +78,15 @@ typedef struct SsbCameras {
     const float* d_intrins;  /* device [count][4] fx, fy, cx, cy */
     int32_t count;
     int32_t width, height;
-    int32_t model;           /* SSB_CAMERA_*; lens-distortion tier "none" only */
+    int32_t model;           /* SSB_CAMERA_* */
     int32_t antialiased;     /* 0 = 3dgs, 1 = mip-splatting blur and opacity compensation */
+    int32_t distortion;      /* lens-distortion tier (CameraDistortionType, src/core/Common.cuh:104-109): only
+                              * SSB_DISTORTION_NONE is built; any other value makes the projection calls return
+                              * SSB_ERR_UNSUPPORTED instead of rendering an undistorted image */
+    int32_t reserved;
+    const float* d_dist_coeffs; /* device [count][8] distortion coefficients of that tier; unread */
 } SsbCameras;
+enum { SSB_DISTORTION_NONE = 0 };
 
 /* 48-byte projected splat.  a = {x, y, hx, hy}: centre in pixels and the half
  * extents of the alpha >= 1/255 footprint; b = {conic a, b, c, opacity};
@@ -258,6 +264,33 @@ int ssb_intersect_tiles_packed(const float* d_aabb, const float* d_depths, const
                                const int64_t* d_n_pairs, int64_t max_pairs, int32_t n_images, int32_t width, int32_t height,
                                void* d_workspace, int64_t workspace_bytes, int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
                                int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream);
+
+/* ---- live-tile map ------------------------------------------------------
+ * Replaces compute_tile_active / tile_active_kernel (src/kernels/tile/IntersectTile.cu:309-367; caller
+ * src/engine/EngineTrainStep.cpp:84-126).  d_mask [n_images][mask_h][mask_w] bytes (!= 0 = the pixel takes part in the
+ * loss), nearest-sampled when its size is not the image's.  d_tile_active [n_images][tile_h][tile_w] int32 gets 1 for a
+ * tile with at least one such pixel in its 16 x 16 block grown by one pixel on every side, else 0.
+ * The *_live forms of the intersection calls take that map (NULL: every tile is live) as the `tile_active` argument of
+ * do_intersect_tile_generic (src/kernels/tile/IntersectTile.cu:376-388): a tile marked 0 gets no pair in either pass,
+ * so the pair count, the keys and the per-tile ranges are those of the live tiles and the rasterisers find an empty
+ * range there. */
+int ssb_tile_active(const uint8_t* d_mask, int32_t n_images, int32_t mask_h, int32_t mask_w, int32_t width, int32_t height,
+                    int32_t* d_tile_active, void* stream);
+int ssb_tile_keys_live(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
+                       int64_t total, int64_t n_per_image, int32_t width, int32_t height,
+                       void* d_workspace, int64_t workspace_bytes,
+                       int32_t* d_tiles_per_splat, int32_t* d_cum_tiles,
+                       int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                       int64_t* d_n_isects, int64_t* h_n_isects, const int32_t* d_tile_active, void* stream);
+int ssb_intersect_tiles_live(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
+                             int64_t total, int64_t n_per_image, int32_t width, int32_t height,
+                             void* d_workspace, int64_t workspace_bytes,
+                             int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                             int32_t* d_tile_offsets, int64_t* d_n_isects, const int32_t* d_tile_active, void* stream);
+int ssb_intersect_tiles_packed_live(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen, const int32_t* d_camera_ids,
+                                    const int64_t* d_n_pairs, int64_t max_pairs, int32_t n_images, int32_t width, int32_t height,
+                                    void* d_workspace, int64_t workspace_bytes, int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                                    int32_t* d_tile_offsets, int64_t* d_n_isects, const int32_t* d_tile_active, void* stream);
 
 /* Replaces intersect_offset_kernel (src/kernels/tile/IntersectTile.cu:271-307).
  * d_offsets [n_tiles_total] int32: first sorted index of each tile; tiles after
@@ -572,7 +605,9 @@ int ssb_step_set_densify(SsbStep* step, int32_t ssim_loss_map_mode, float ssim_l
  * calls, [n_views][mask_h][mask_w], indexed like d_gt.  With densification outputs switched on (ssb_step_set_densify)
  * and loss_map_mode != 0 the per-splat weights are gathered from this loss map (the reference's path:
  * src/engine/EngineLoss.cpp:852-862) instead of the SSIM-only map.  cfg == NULL switches back to the one-scale,
- * unmasked loss.  Allocates the pyramid workspace per lane. */
+ * unmasked loss.  With a mask the step also builds each view's live-tile map (ssb_tile_active) and leaves the tiles that
+ * no term of the loss reads out of the intersection, as the reference does when it has a mask and no alpha supervision
+ * (src/engine/EngineTrainStep.cpp:84-126).  Allocates the pyramid workspace per lane. */
 int ssb_step_set_loss(SsbStep* step, const SsbLossConfig* cfg);
 
 /* Forward + loss + backward of `n_views` views (device camera arrays and device

@@ -27,6 +27,7 @@ def load():
             build()
         _lib = C.CDLL(_SO)
         _lib.oracle_tile_count.restype = C.c_int64
+        _lib.oracle_tile_count_live.restype = C.c_int64
         _lib.oracle_num_threads.restype = C.c_int
         _lib.oracle_tile_n_bits.restype = C.c_int
         _lib.oracle_det_logf.restype = C.c_float
@@ -95,19 +96,30 @@ def project_bwd(splats, viewmats, intrins, W, H, aabb, v, model=0, antialiased=0
     return g
 
 
-def tile_keys(proj, N, W, H):
-    """proj: output of project_fwd. Returns counts, cum, keys, flatten ids (unsorted)."""
+def tile_keys(proj, N, W, H, tile_active=None):
+    """proj: output of project_fwd. Returns counts, cum, keys, flatten ids (unsorted).  tile_active: int32 [I, th, tw] live-tile map."""
     lib = load()
     total = proj["depths"].shape[0]
     counts = np.zeros(total, np.int64)
     cum = np.zeros(total, np.int64)
-    M = lib.oracle_tile_count(C.c_int64(total), C.c_int(W), C.c_int(H), _p(proj["aabb"]), _p(proj["xy"]), _p(proj["conic"]),
-                              _p(proj["opac"]), _p(counts), _p(cum))
+    live = None if tile_active is None else np.ascontiguousarray(tile_active, dtype=np.int32)
+    M = lib.oracle_tile_count_live(C.c_int64(total), C.c_int64(N), C.c_int(W), C.c_int(H), _p(proj["aabb"]), _p(proj["xy"]), _p(proj["conic"]),
+                                   _p(proj["opac"]), _p(live), _p(counts), _p(cum))
     keys = np.zeros(M, np.int64)
     vals = np.zeros(M, np.int32)
-    lib.oracle_tile_emit(C.c_int64(total), C.c_int64(N), C.c_int(W), C.c_int(H), _p(proj["aabb"]), _p(proj["depths"]),
-                         _p(proj["xy"]), _p(proj["conic"]), _p(proj["opac"]), _p(cum), _p(keys), _p(vals))
+    lib.oracle_tile_emit_live(C.c_int64(total), C.c_int64(N), C.c_int(W), C.c_int(H), _p(proj["aabb"]), _p(proj["depths"]),
+                              _p(proj["xy"]), _p(proj["conic"]), _p(proj["opac"]), _p(live), _p(cum), _p(keys), _p(vals))
     return counts, cum, keys, vals
+
+
+def tile_active(mask, W, H):
+    """Live-tile map int32 [I, th, tw] of a mask uint8 [I, Hm, Wm] (nonzero = the pixel takes part) for W x H images."""
+    lib = load()
+    mask = np.ascontiguousarray(mask, dtype=np.uint8)
+    I, Hm, Wm = mask.shape
+    out = np.zeros((I, (H + 15) // 16, (W + 15) // 16), np.int32)
+    lib.oracle_tile_active(_p(mask), C.c_int(I), C.c_int(Hm), C.c_int(Wm), C.c_int(W), C.c_int(H), _p(out))
+    return out
 
 
 def sort_pairs(keys, vals, begin_bit, end_bit):

@@ -718,17 +718,20 @@ void oracle_project_bwd(
 // (src/kernels/tile/IntersectTile.cu:372-509).
 // Pass 1 (:104-186): tiles_per_splat (int64) and its inclusive sum.
 // ---------------------------------------------------------------------------
-int64_t oracle_tile_count(
-    int64_t total, int W, int H,
-    const float* aabb, const float* xy, const float* conic, const float* opac,
+// tile_active (may be NULL) [I][tile_h][tile_w]: a tile with 0 is left out of both passes, so the rasteriser gets an
+// empty range for it (:120-122,164-182,229-258).
+int64_t oracle_tile_count_live(
+    int64_t total, int64_t N, int W, int H,
+    const float* aabb, const float* xy, const float* conic, const float* opac, const int32_t* tile_active,
     int64_t* tiles_per_splat, int64_t* cum_tiles) {
     int tw = (W + TILE - 1) / TILE, th = (H + TILE - 1) / TILE;
 #pragma omp parallel for schedule(static)
     for (int64_t idx = 0; idx < total; ++idx) {
         TileSpan g; float cn[3];
         int64_t n = 0;
+        const int32_t* live = tile_active ? tile_active + (idx / N) * (int64_t)tw * th : nullptr;
         if (tile_setup(aabb + 4 * idx, conic + 3 * idx, opac[idx], tw, th, g, cn))
-            for_each_tile(xy + 2 * idx, cn[0], cn[1], cn[2], g, [&](int, int) { ++n; });
+            for_each_tile(xy + 2 * idx, cn[0], cn[1], cn[2], g, [&](int x, int y) { if (!live || live[(int64_t)y * tw + x]) ++n; });
         tiles_per_splat[idx] = n;
     }
     int64_t run = 0;
@@ -736,10 +739,17 @@ int64_t oracle_tile_count(
     return run;
 }
 
+int64_t oracle_tile_count(
+    int64_t total, int W, int H,
+    const float* aabb, const float* xy, const float* conic, const float* opac,
+    int64_t* tiles_per_splat, int64_t* cum_tiles) {
+    return oracle_tile_count_live(total, total > 0 ? total : 1, W, H, aabb, xy, conic, opac, nullptr, tiles_per_splat, cum_tiles);
+}
+
 // Pass 2 (:188-267): keys (tile_id << 32 | depth bits) and flatten ids.
-void oracle_tile_emit(
+void oracle_tile_emit_live(
     int64_t total, int64_t N, int W, int H,
-    const float* aabb, const float* depths, const float* xy, const float* conic, const float* opac,
+    const float* aabb, const float* depths, const float* xy, const float* conic, const float* opac, const int32_t* tile_active,
     const int64_t* cum_tiles, int64_t* isect_ids, int32_t* flatten_ids) {
     int tw = (W + TILE - 1) / TILE, th = (H + TILE - 1) / TILE;
 #pragma omp parallel for schedule(static)
@@ -747,6 +757,7 @@ void oracle_tile_emit(
         int64_t cur = idx == 0 ? 0 : cum_tiles[idx - 1];
         int64_t end = cum_tiles[idx];
         int64_t iid = idx / N;
+        const int32_t* live = tile_active ? tile_active + iid * (int64_t)tw * th : nullptr;
         TileSpan g; float cn[3];
         if (tile_setup(aabb + 4 * idx, conic + 3 * idx, opac[idx], tw, th, g, cn)) {
             float d = std::fabs(depths[idx]);
@@ -754,6 +765,7 @@ void oracle_tile_emit(
             if (du >> 31) du = ~du; else du ^= (1u << 31);       // :190-196
             for_each_tile(xy + 2 * idx, cn[0], cn[1], cn[2], g, [&](int x, int y) {
                 if (cur >= end) return;
+                if (live && !live[(int64_t)y * tw + x]) return;
                 int64_t tile_id = iid * tw * th + (int64_t)y * tw + x;
                 isect_ids[cur] = (tile_id << 32) | (int64_t)du;
                 flatten_ids[cur] = (int32_t)idx;
@@ -767,6 +779,41 @@ void oracle_tile_emit(
             ++cur;
         }
     }
+}
+
+void oracle_tile_emit(
+    int64_t total, int64_t N, int W, int H,
+    const float* aabb, const float* depths, const float* xy, const float* conic, const float* opac,
+    const int64_t* cum_tiles, int64_t* isect_ids, int32_t* flatten_ids) {
+    oracle_tile_emit_live(total, N, W, H, aabb, depths, xy, conic, opac, nullptr, cum_tiles, isect_ids, flatten_ids);
+}
+
+// Live-tile map (tile_active_kernel, src/kernels/tile/IntersectTile.cu:309-344): a tile is live when any pixel of it,
+// grown by one pixel on every side (kMaskPad) and clipped to the image, is unmasked; the mask [I][Hm][Wm] is sampled
+// as the loss samples it (nearest_sample_b, src/core/Interpolation.cuh:108-120).
+void oracle_tile_active(const uint8_t* mask, int I, int Hm, int Wm, int W, int H, int32_t* tile_active) {
+    const int tw = (W + TILE - 1) / TILE, th = (H + TILE - 1) / TILE;
+    for (int b = 0; b < I; ++b)
+        for (int ty = 0; ty < th; ++ty)
+            for (int tx = 0; tx < tw; ++tx) {
+                bool live = false;
+                for (int dy = -1; dy < TILE + 1 && !live; ++dy) {
+                    const int y = ty * TILE + dy;
+                    if (y >= H) break;
+                    if (y < 0) continue;
+                    for (int dx = -1; dx < TILE + 1; ++dx) {
+                        const int x = tx * TILE + dx;
+                        if (x >= W) break;
+                        if (x < 0) continue;
+                        float u = ((float)x + 0.5f) * (float)Wm / (float)W - 0.5f;
+                        float v = ((float)y + 0.5f) * (float)Hm / (float)H - 0.5f;
+                        int xs = std::max(0, std::min(Wm - 1, (int)std::floor(u + 0.5f)));
+                        int ys = std::max(0, std::min(Hm - 1, (int)std::floor(v + 0.5f)));
+                        if (mask[((size_t)b * Hm + ys) * Wm + xs]) { live = true; break; }
+                    }
+                }
+                tile_active[((size_t)b * th + ty) * tw + tx] = live ? 1 : 0;
+            }
 }
 
 // Stable ascending sort of (int64 key, int32 value) on key bits

@@ -6,7 +6,8 @@
 // src/instantiations/*.cu they pull in), it lets src/engine compile and link unchanged for the path this library covers:
 //
 //   projection_3dgs_forward        (src/kernels/projection/ProjectionFwd.cuh:17-34)   -> ssb_project_fwd + ssb_screen_unpack
-//   do_intersect_tile_generic      (src/kernels/tile/IntersectTile.cuh:24-40)        -> ssb_screen_pack + ssb_intersect_tiles
+//   compute_tile_active            (src/kernels/tile/IntersectTile.cuh:18-22)        -> ssb_tile_active
+//   do_intersect_tile_generic      (src/kernels/tile/IntersectTile.cuh:24-40)        -> ssb_screen_pack + ssb_intersect_tiles_live
 //   rasterize_to_pixels_3dgs_fwd   (src/kernels/raster/RasterizationFwd.cuh:16-37)    -> ssb_screen_pack + ssb_raster_fwd
 //   rasterize_to_pixels_3dgs_bwd   (src/kernels/raster/RasterizationBwd.cuh:18-48)    -> ssb_raster_bwd_accum + unpack of the gradient records
 //
@@ -72,8 +73,6 @@ std::tuple<DeviceTensor2D<float4>, DeviceTensor2D<float>, std::vector<DeviceTens
     const std::string camera_model, const std::string distortion, const TorchTensorView dist_coeffs, DeviceVector<float> radii,
     const std::optional<TorchTensorView> sh_value_packed, const std::optional<TorchTensorView> sh_value_bounds,
     const uint32_t num_sh_buffer, const int sh_value_bits, const int64_t sh_bounds_stride) {
-    (void)dist_coeffs;
-    if (cdt(distortion) != CameraDistortionType::None) unsupported("a lens-distortion tier");
     if (in_splats.size() != 6) throw std::runtime_error("projection_3dgs_forward: expected six world arrays");
     const int sh_degree = std::min(Vanilla3DGS<0>::WorldBuffer(in_splats).sh_degree(), max_sh_degree);
     if (sh_degree != 3) unsupported("an SH degree other than 3");
@@ -92,7 +91,8 @@ std::tuple<DeviceTensor2D<float4>, DeviceTensor2D<float>, std::vector<DeviceTens
         shq.bounds_stride = sh_bounds_stride;      // 0 = one bound per 256 splats, as in the reference
     }
     SsbCameras cams = {(const float*)std::get<0>(viewmats), (const float*)std::get<0>(intrins), (int32_t)C,
-                       (int32_t)image_width, (int32_t)image_height, camera_model_of(camera_model), 0};
+                       (int32_t)image_width, (int32_t)image_height, camera_model_of(camera_model), 0,
+                       (int32_t)cdt(distortion), 0, (const float*)std::get<0>(dist_coeffs)};      // a tier other than None: the library says SSB_ERR_UNSUPPORTED
 
     DeviceTensor2D<float4> aabb;
     aabb.resize(PoolSlot::ProjAabb, C, N);
@@ -111,13 +111,18 @@ int64_t intersect_tile_count(int width, int height) {
     return (int64_t)((width + SSB_TILE - 1) / SSB_TILE) * ((height + SSB_TILE - 1) / SSB_TILE);
 }
 
+void compute_tile_active(TorchTensorView mask, int I, int width, int height, int32_t* tile_active) {
+    const auto& ms = std::get<2>(mask);     // [I, H_mask, W_mask] bool, one byte each
+    ssb_check(ssb_tile_active((const uint8_t*)std::get<0>(mask), I, (int32_t)ms[1], (int32_t)ms[2], width, height, tile_active, nullptr));
+    backend::device_synchronize();
+}
+
 std::tuple<DeviceVector<int64_t>, DeviceVector<int32_t>, DeviceTensor3D<int32_t>> do_intersect_tile_generic(
     DeviceTensorFloatND aabb, DeviceTensorFloatND depths, DeviceTensorFloatND* proj_xy, DeviceTensorFloatND* proj_conic,
     DeviceTensorFloatND* proj_opac, const uint32_t I, TorchTensorView intrins, const uint32_t image_width, const uint32_t image_height,
     DeviceVector<int32_t>* image_ids, const int32_t* tile_active) {
     (void)intrins;
     if (!proj_xy || !proj_conic || !proj_opac) unsupported("AABB-mode tile intersection");
-    if (tile_active) unsupported("the live-tile map");
     const int64_t total = depths.numel();
     const uint32_t tw = (image_width + SSB_TILE - 1) / SSB_TILE, th = (image_height + SSB_TILE - 1) / SSB_TILE;
     const int64_t n_tiles = (int64_t)tw * th * I;
@@ -142,11 +147,12 @@ std::tuple<DeviceVector<int64_t>, DeviceVector<int32_t>, DeviceTensor3D<int32_t>
         int32_t* flat = scratch<int32_t>("isect_flat", cap);
         if (image_ids) {
             backend::memcpy_sync(d_count + 1, &total, sizeof(int64_t), backend::MemcpyKind::HostToDevice);      // the pair count, which the library reads on the device
-            ssb_check(ssb_intersect_tiles_packed((const float*)aabb.data_ptr(), depths.data_ptr(), rec, image_ids->data_ptr(), d_count + 1, total, (int32_t)I,
-                                                 (int32_t)image_width, (int32_t)image_height, ws, ws_bytes, keys, flat, cap, offsets.data_ptr(), d_count, nullptr));
+            ssb_check(ssb_intersect_tiles_packed_live((const float*)aabb.data_ptr(), depths.data_ptr(), rec, image_ids->data_ptr(), d_count + 1, total, (int32_t)I,
+                                                      (int32_t)image_width, (int32_t)image_height, ws, ws_bytes, keys, flat, cap, offsets.data_ptr(), d_count,
+                                                      tile_active, nullptr));
         } else
-            ssb_check(ssb_intersect_tiles((const float*)aabb.data_ptr(), depths.data_ptr(), rec, total, total / I, (int32_t)image_width,
-                                          (int32_t)image_height, ws, ws_bytes, keys, flat, cap, offsets.data_ptr(), d_count, nullptr));
+            ssb_check(ssb_intersect_tiles_live((const float*)aabb.data_ptr(), depths.data_ptr(), rec, total, total / I, (int32_t)image_width,
+                                               (int32_t)image_height, ws, ws_bytes, keys, flat, cap, offsets.data_ptr(), d_count, tile_active, nullptr));
         int64_t n_isects = 0;
         backend::memcpy_sync(&n_isects, d_count, sizeof(int64_t), backend::MemcpyKind::DeviceToHost);
         int32_t bits = 0;

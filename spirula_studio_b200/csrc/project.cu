@@ -805,6 +805,9 @@ int ssb_project_fwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, c
     if (cams->model != SSB_CAMERA_PINHOLE && cams->model != SSB_CAMERA_FISHEYE && cams->model != SSB_CAMERA_EQUISOLID && cams->model != SSB_CAMERA_EQUIRECT) {
         set_error("ssb_project_fwd: camera model %d not supported", cams->model); return SSB_ERR_UNSUPPORTED;
     }
+    if (cams->distortion != SSB_DISTORTION_NONE) {
+        set_error("ssb_project_fwd: lens-distortion tier %d is not built (only SSB_DISTORTION_NONE)", cams->distortion); return SSB_ERR_UNSUPPORTED;
+    }
     SSB_REQUIRE((int64_t)cams->count * n < ((int64_t)1 << 31), "ssb_project_fwd: views * splats must fit int32 flatten ids");
     SsbShQuant q;
     int e = check_shq(splats, shq, q);
@@ -839,6 +842,9 @@ int launch_project_fwd_pack_pass(int pass, const SsbSplats* splats, const SsbShQ
     if (cams->model != SSB_CAMERA_PINHOLE && cams->model != SSB_CAMERA_FISHEYE && cams->model != SSB_CAMERA_EQUISOLID && cams->model != SSB_CAMERA_EQUIRECT) {
         set_error("ssb_project_fwd_packed: camera model %d not supported", cams->model); return SSB_ERR_UNSUPPORTED;
     }
+    if (cams->distortion != SSB_DISTORTION_NONE) {
+        set_error("ssb_project_fwd_packed: lens-distortion tier %d is not built (only SSB_DISTORTION_NONE)", cams->distortion); return SSB_ERR_UNSUPPORTED;
+    }
     SSB_REQUIRE((int64_t)cams->count * n < ((int64_t)1 << 31), "ssb_project_fwd_packed: views * splats must fit int32");
     SsbShQuant q;
     int e = check_shq(splats, shq, q);
@@ -871,6 +877,9 @@ int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n
                 "ssb_project_bwd: every gradient array must be given");
     if (cams->model != SSB_CAMERA_PINHOLE && cams->model != SSB_CAMERA_FISHEYE && cams->model != SSB_CAMERA_EQUISOLID && cams->model != SSB_CAMERA_EQUIRECT) {
         set_error("ssb_project_bwd: camera model %d not supported", cams->model); return SSB_ERR_UNSUPPORTED;
+    }
+    if (cams->distortion != SSB_DISTORTION_NONE) {
+        set_error("ssb_project_bwd: lens-distortion tier %d is not built (only SSB_DISTORTION_NONE)", cams->distortion); return SSB_ERR_UNSUPPORTED;
     }
     SsbShQuant q;
     int e = check_shq(splats, shq, q);

@@ -66,11 +66,12 @@ int launch_intersect_tiles(const float* d_aabb, const float* d_depths, const Ssb
                            int64_t total, int64_t n_per_image, int32_t width, int32_t height,
                            void* d_workspace, int64_t workspace_bytes,
                            int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
-                           int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort, int64_t* d_max_pairs);
+                           int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort, int64_t* d_max_pairs,
+                           const int32_t* d_tile_active);
 int launch_intersect_tiles_packed(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen, const int32_t* d_image_ids,
                                   const int64_t* d_total, int64_t max_pairs, int64_t n_images, int32_t width, int32_t height,
                                   void* d_workspace, int64_t workspace_bytes, int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
-                                  int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream);
+                                  int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, const int32_t* d_tile_active);
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline int64_t align_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }

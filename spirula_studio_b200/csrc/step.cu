@@ -36,6 +36,7 @@ struct SsbLane {
     float* rgb; float* T; int32_t* last_ids; float* v_rgb;
     float* loss_map;      // [P], only with ssb_step_set_densify
     void* loss_ws;        // pyramid of the general loss, only with ssb_step_set_loss
+    int32_t* tile_live;   // [tiles] live-tile map of the view's mask, only with a mask in ssb_step_set_loss
     cudaStream_t stream;
     cudaEvent_t bwd_done;  // this lane's last projection backward
     cudaEvent_t all_done;
@@ -89,7 +90,7 @@ static void lane_free(SsbLane& l) {
     cudaFree(l.aabb); cudaFree(l.depths); cudaFree(l.screen); cudaFree(l.v_screen);
     cudaFree(l.isect_ws); cudaFree(l.flat);
     cudaFree(l.n_isects); cudaFree(l.offsets);
-    cudaFree(l.rgb); cudaFree(l.T); cudaFree(l.last_ids); cudaFree(l.v_rgb); cudaFree(l.loss_map); cudaFree(l.loss_ws);
+    cudaFree(l.rgb); cudaFree(l.T); cudaFree(l.last_ids); cudaFree(l.v_rgb); cudaFree(l.loss_map); cudaFree(l.loss_ws); cudaFree(l.tile_live);
     if (l.stream) cudaStreamDestroy(l.stream);
     if (l.bwd_done) cudaEventDestroy(l.bwd_done);
     if (l.all_done) cudaEventDestroy(l.all_done);
@@ -129,7 +130,7 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
     const int64_t n = s->cfg.n_splats;
     const int W = s->cfg.width, H = s->cfg.height;
     const int64_t P = (int64_t)W * H;
-    SsbCameras cam;
+    SsbCameras cam{};
     cam.d_viewmats = d_viewmats + 16 * (int64_t)v;
     cam.d_intrins = d_intrins + 4 * (int64_t)v;
     cam.count = 1; cam.width = W; cam.height = H;
@@ -141,8 +142,15 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
     SSB_MARK(1);
     // counts + scan + scatter are reported as the key stage, the per-tile sort as the sort stage;
     // the ranges come out of the scan, so that stage is empty
+    // with a mask, tiles that no term of the loss reads take no pairs (src/engine/EngineTrainStep.cpp:84-126)
+    const int32_t* live = nullptr;
+    if (s->loss_general && s->loss_cfg.d_mask) {
+        const SsbLossConfig& lc = s->loss_cfg;
+        if ((e = ssb_tile_active(lc.d_mask + (int64_t)v * lc.mask_h * lc.mask_w, 1, lc.mask_h, lc.mask_w, W, H, l.tile_live, st))) return e;
+        live = l.tile_live;
+    }
     if ((e = launch_intersect_tiles(l.aabb, l.depths, l.screen, n, n, W, H, l.isect_ws, s->isect_ws_bytes, nullptr, l.flat, s->capacity,
-                                 l.offsets, l.n_isects, st, ev ? ev[2] : nullptr, s->max_pairs))) return e;
+                                 l.offsets, l.n_isects, st, ev ? ev[2] : nullptr, s->max_pairs, live))) return e;
     SSB_MARK(3);
     SSB_MARK(4);
     // the loss has no depth term, so the depth image is neither rendered nor back-propagated
@@ -211,6 +219,8 @@ int ssb_step_set_loss(SsbStep* s, const SsbLossConfig* cfg) {
         }
         if (c.loss_map_mode && !l.loss_map)
             if (int e = dev_alloc(&l.loss_map, P, s->bytes)) return e;
+        if (c.d_mask && !l.tile_live)
+            if (int e = dev_alloc(&l.tile_live, (int64_t)s->tw * s->th, s->bytes)) return e;
     }
     s->loss_ws_bytes = std::max(s->loss_ws_bytes, need);
     s->loss_cfg = c;

@@ -132,8 +132,8 @@ __device__ __forceinline__ bool tile_setup(float4 bb, float4 recb, int tw, int t
 
 // Pass 1: tiles touched per pair, plus the sum of each 2048-pair chunk.
 __global__ void __launch_bounds__(kTilesBlock) tile_count_kernel(
-    const float4* __restrict__ aabb, const SsbScreenRec* __restrict__ screen, int64_t total, int tw, int th,
-    int32_t* __restrict__ counts, int32_t* __restrict__ chunk_sums) {
+    const float4* __restrict__ aabb, const SsbScreenRec* __restrict__ screen, int64_t total, int64_t n_per_image, int tw, int th,
+    const int32_t* __restrict__ tile_active, int32_t* __restrict__ counts, int32_t* __restrict__ chunk_sums) {
     __shared__ int warp_tot[kTilesBlock / 32];
     int64_t base = (int64_t)blockIdx.x * kScanChunk;
     int local = 0;
@@ -146,8 +146,10 @@ __global__ void __launch_bounds__(kTilesBlock) tile_count_kernel(
             if (bb.z > bb.x && bb.w > bb.y) {
                 const float4* r = (const float4*)(screen + idx);
                 float4 ra = r[0], rb = r[1];
+                // a tile the live-tile map marks 0 is left out of both passes (src/kernels/tile/IntersectTile.cu:120-122,164-182)
+                const int32_t* live = tile_active ? tile_active + (idx / n_per_image) * (int64_t)tw * th : nullptr;
                 if (tile_setup(bb, rb, tw, th, g, cn))
-                    for_each_tile(ra.x, ra.y, cn[0], cn[1], cn[2], g, [&](int, int) { ++n; });
+                    for_each_tile(ra.x, ra.y, cn[0], cn[1], cn[2], g, [&](int x, int y) { if (!live || live[y * tw + x]) ++n; });
             }
             counts[idx] = n;
         }
@@ -240,8 +242,8 @@ __global__ void __launch_bounds__(kTilesBlock) tile_cum_kernel(
 // Pass 2: keys and flatten ids.
 __global__ void __launch_bounds__(kTilesBlock) tile_emit_kernel(
     const float4* __restrict__ aabb, const float* __restrict__ depths, const SsbScreenRec* __restrict__ screen,
-    int64_t total, int64_t n_per_image, int tw, int th, const int32_t* __restrict__ cum, int64_t capacity,
-    int64_t* __restrict__ isect_ids, int32_t* __restrict__ flatten_ids) {
+    int64_t total, int64_t n_per_image, int tw, int th, const int32_t* __restrict__ tile_active, const int32_t* __restrict__ cum,
+    int64_t capacity, int64_t* __restrict__ isect_ids, int32_t* __restrict__ flatten_ids) {
     int64_t idx = (int64_t)blockIdx.x * kTilesBlock + threadIdx.x;
     if (idx >= total) return;
     int64_t cur = idx == 0 ? 0 : cum[idx - 1];
@@ -257,8 +259,10 @@ __global__ void __launch_bounds__(kTilesBlock) tile_emit_kernel(
         uint32_t du = __float_as_uint(fabsf(depths[idx]));
         if (du >> 31) du = ~du; else du ^= (1u << 31);
         int64_t tile_base = iid * tw * th;
+        const int32_t* live = tile_active ? tile_active + tile_base : nullptr;
         for_each_tile(ra.x, ra.y, cn[0], cn[1], cn[2], g, [&](int x, int y) {
             if (cur >= end) return;
+            if (live && !live[y * tw + x]) return;
             int64_t tile_id = tile_base + (int64_t)y * tw + x;
             isect_ids[cur] = (tile_id << 32) | (int64_t)du;
             flatten_ids[cur] = (int32_t)idx;
@@ -271,6 +275,33 @@ __global__ void __launch_bounds__(kTilesBlock) tile_emit_kernel(
         flatten_ids[cur] = (int32_t)idx;
         ++cur;
     }
+}
+
+// Live-tile map (tile_active_kernel, src/kernels/tile/IntersectTile.cu:309-344): a tile is live when any pixel of it, grown by
+// one pixel on every side and clipped to the image, takes part under the mask [I][Hm][Wm] (nearest-sampled like the loss
+// samples it, src/core/Interpolation.cuh:108-120).  One warp per tile: 18 x 18 samples, a ballot per round.
+__global__ void __launch_bounds__(256) tile_active_kernel(const uint8_t* __restrict__ mask, int n_images, int Hm, int Wm, int W, int H, int tw, int th,
+                                                          int32_t* __restrict__ tile_active) {
+    const int64_t t = ((int64_t)blockIdx.x * 256 + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (t >= (int64_t)n_images * tw * th) return;
+    const int tx = (int)(t % tw), ty = (int)((t / tw) % th), b = (int)(t / ((int64_t)tw * th));
+    constexpr int kEdge = kTile + 2;
+    bool live = false;
+    for (int base = 0; base < kEdge * kEdge; base += 32) {     // the same number of rounds for every lane
+        const int i = base + lane;
+        const int y = ty * kTile - 1 + i / kEdge, x = tx * kTile - 1 + i % kEdge;
+        if (i < kEdge * kEdge && x >= 0 && y >= 0 && x < W && y < H) {
+            const float u = ((float)x + 0.5f) * (float)Wm / (float)W - 0.5f;
+            const float v = ((float)y + 0.5f) * (float)Hm / (float)H - 0.5f;
+            const int xs = max(0, min(Wm - 1, (int)floorf(u + 0.5f)));
+            const int ys = max(0, min(Hm - 1, (int)floorf(v + 0.5f)));
+            live |= mask[((int64_t)b * Hm + ys) * Wm + xs] != 0;
+        }
+        if (__any_sync(0xffffffffu, live)) break;
+    }
+    live = __any_sync(0xffffffffu, live);
+    if (lane == 0) tile_active[t] = live ? 1 : 0;
 }
 
 // offsets[t] = first sorted index whose tile id >= t.
@@ -406,11 +437,13 @@ __device__ __forceinline__ int depth_bucket(uint32_t du, uint32_t lo, uint32_t h
 }
 
 // Passes 1 (EMIT = false: count) and 3 (EMIT = true: scatter).
-template <bool EMIT>
+// LIVE: tiles whose entry of tile_active [images][th][tw] is 0 take no pairs in either pass.
+template <bool EMIT, bool LIVE>
 __global__ void __launch_bounds__(kBinThreads) bin_pass_kernel(
     const float4* __restrict__ aabb, const float* __restrict__ depths, const SsbScreenRec* __restrict__ screen, int64_t total,
     int64_t n_per_image, int tw, int th, const uint32_t* __restrict__ range, int32_t* __restrict__ bins, int64_t capacity,
-    uint64_t* __restrict__ pairs, const int32_t* __restrict__ image_ids, const int64_t* __restrict__ total_ptr) {
+    uint64_t* __restrict__ pairs, const int32_t* __restrict__ image_ids, const int64_t* __restrict__ total_ptr,
+    const int32_t* __restrict__ tile_active) {
     // packed input: the image of a pair comes from image_ids and the pair count from device memory
     if (total_ptr) total = min(total, *total_ptr);
     const int lane = threadIdx.x & 31;
@@ -469,17 +502,19 @@ __global__ void __launch_bounds__(kBinThreads) bin_pass_kernel(
             // tiles of a line are neighbours: along x their bins are kDepthBuckets apart, along y a whole tile row
             int32_t* bin = bins + obin + (o_mode ? line * tw + lo : lo * tw + line) * kDepthBuckets;
             const int step = (o_mode ? 1 : tw) * kDepthBuckets;
+            // the bin index / kDepthBuckets is the tile's index over all images, which is how the live-tile map is laid out
+            auto is_live = [&](const int32_t* b) { return !LIVE || tile_active[(b - bins) / kDepthBuckets] != 0; };
             if (EMIT) {
                 for (int k = lo; k < hi; k += 4) {       // up to four slot requests in flight before the first store
                     int32_t pos[4];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) pos[u] = k + u < hi ? atomicAdd(bin + u * step, 1) : -1;
+                    for (int u = 0; u < 4; ++u) pos[u] = (k + u < hi && is_live(bin + u * step)) ? atomicAdd(bin + u * step, 1) : -1;
 #pragma unroll
                     for (int u = 0; u < 4; ++u) if (pos[u] >= 0 && pos[u] < capacity) pairs[pos[u]] = oword;
                     bin += 4 * step;
                 }
             } else {
-                for (int k = lo; k < hi; ++k, bin += step) atomicAdd(bin, 1);
+                for (int k = lo; k < hi; ++k, bin += step) if (is_live(bin)) atomicAdd(bin, 1);
             }
         }
     }
@@ -640,12 +675,12 @@ int64_t ssb_tile_keys_workspace_bytes(int64_t total) {
     return align_up(total * 4, 256) * 2 + align_up(chunks * 4, 256) + 256;
 }
 
-int ssb_tile_keys(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
-                  int64_t total, int64_t n_per_image, int32_t width, int32_t height,
-                  void* d_workspace, int64_t workspace_bytes,
-                  int32_t* d_tiles_per_splat, int32_t* d_cum_tiles,
-                  int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
-                  int64_t* d_n_isects, int64_t* h_n_isects, void* stream) {
+int ssb_tile_keys_live(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
+                       int64_t total, int64_t n_per_image, int32_t width, int32_t height,
+                       void* d_workspace, int64_t workspace_bytes,
+                       int32_t* d_tiles_per_splat, int32_t* d_cum_tiles,
+                       int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                       int64_t* d_n_isects, int64_t* h_n_isects, const int32_t* d_tile_active, void* stream) {
     using namespace ssb;
     SSB_REQUIRE(d_aabb && d_depths && d_screen && d_workspace && d_isect_ids && d_flatten_ids && d_n_isects, "ssb_tile_keys: NULL argument");
     SSB_REQUIRE(total >= 0 && n_per_image > 0 && width > 0 && height > 0 && capacity >= 0, "ssb_tile_keys: bad sizes");
@@ -661,14 +696,14 @@ int ssb_tile_keys(const float* d_aabb, const float* d_depths, const SsbScreenRec
     if (total == 0) {
         SSB_CUDA(cudaMemsetAsync(d_n_isects, 0, sizeof(int64_t), st));
     } else {
-        tile_count_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>((const float4*)d_aabb, d_screen, total, tw, th, counts, chunk_sums);
+        tile_count_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>((const float4*)d_aabb, d_screen, total, n_per_image, tw, th, d_tile_active, counts, chunk_sums);
         SSB_LAUNCHED("tile_count_kernel");
         chunk_scan_kernel<<<1, 1024, 0, st>>>(chunk_sums, (int)chunks, d_n_isects, capacity, device_status_word(), nullptr);
         SSB_LAUNCHED("chunk_scan_kernel");
         tile_cum_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(counts, chunk_sums, total, cum);
         SSB_LAUNCHED("tile_cum_kernel");
         tile_emit_kernel<<<(unsigned)ceil_div(total, kTilesBlock), kTilesBlock, 0, st>>>(
-            (const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th, cum, capacity, d_isect_ids, d_flatten_ids);
+            (const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th, d_tile_active, cum, capacity, d_isect_ids, d_flatten_ids);
         SSB_LAUNCHED("tile_emit_kernel");
     }
     if (h_n_isects) {
@@ -680,6 +715,16 @@ int ssb_tile_keys(const float* d_aabb, const float* d_depths, const SsbScreenRec
         }
     }
     return SSB_OK;
+}
+
+int ssb_tile_keys(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
+                  int64_t total, int64_t n_per_image, int32_t width, int32_t height,
+                  void* d_workspace, int64_t workspace_bytes,
+                  int32_t* d_tiles_per_splat, int32_t* d_cum_tiles,
+                  int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                  int64_t* d_n_isects, int64_t* h_n_isects, void* stream) {
+    return ssb_tile_keys_live(d_aabb, d_depths, d_screen, total, n_per_image, width, height, d_workspace, workspace_bytes, d_tiles_per_splat,
+                              d_cum_tiles, d_isect_ids, d_flatten_ids, capacity, d_n_isects, h_n_isects, nullptr, stream);
 }
 
 int64_t ssb_intersect_tiles_workspace_bytes(int64_t n_tiles_total, int64_t capacity) {
@@ -695,7 +740,30 @@ int ssb_intersect_tiles(const float* d_aabb, const float* d_depths, const SsbScr
                         int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
                         int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream) {
     return ssb::launch_intersect_tiles(d_aabb, d_depths, d_screen, total, n_per_image, width, height, d_workspace, workspace_bytes,
-                                       d_isect_ids, d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, nullptr, nullptr);
+                                       d_isect_ids, d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, nullptr, nullptr, nullptr);
+}
+
+int ssb_intersect_tiles_live(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
+                             int64_t total, int64_t n_per_image, int32_t width, int32_t height,
+                             void* d_workspace, int64_t workspace_bytes,
+                             int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                             int32_t* d_tile_offsets, int64_t* d_n_isects, const int32_t* d_tile_active, void* stream) {
+    return ssb::launch_intersect_tiles(d_aabb, d_depths, d_screen, total, n_per_image, width, height, d_workspace, workspace_bytes,
+                                       d_isect_ids, d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, nullptr, nullptr, d_tile_active);
+}
+
+int ssb_tile_active(const uint8_t* d_mask, int32_t n_images, int32_t mask_h, int32_t mask_w, int32_t width, int32_t height,
+                    int32_t* d_tile_active, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(d_mask && d_tile_active, "ssb_tile_active: NULL argument");
+    SSB_REQUIRE(n_images >= 0 && mask_h > 0 && mask_w > 0 && width > 0 && height > 0, "ssb_tile_active: bad sizes");
+    const int tw = (width + kTile - 1) / kTile, th = (height + kTile - 1) / kTile;
+    const int64_t n_tiles = (int64_t)n_images * tw * th;
+    if (n_tiles == 0) return SSB_OK;
+    tile_active_kernel<<<(unsigned)ceil_div(n_tiles * 32, 256), 256, 0, (cudaStream_t)stream>>>(d_mask, n_images, mask_h, mask_w, width, height, tw, th,
+                                                                                                d_tile_active);
+    SSB_LAUNCHED("tile_active_kernel");
+    return SSB_OK;
 }
 
 int32_t ssb_tile_n_bits(int64_t n_tiles) {
@@ -728,24 +796,28 @@ static int intersect_tiles_impl(const float* d_aabb, const float* d_depths, cons
                         void* d_workspace, int64_t workspace_bytes,
                         int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
                         int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort,
-                        const int32_t* d_image_ids, const int64_t* d_total, int64_t n_images_packed, int64_t* d_max_pairs);
+                        const int32_t* d_image_ids, const int64_t* d_total, int64_t n_images_packed, int64_t* d_max_pairs,
+                        const int32_t* d_tile_active);
 
 int launch_intersect_tiles(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
                         int64_t total, int64_t n_per_image, int32_t width, int32_t height,
                         void* d_workspace, int64_t workspace_bytes,
                         int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
-                        int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort, int64_t* d_max_pairs) {
+                        int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort, int64_t* d_max_pairs,
+                        const int32_t* d_tile_active) {
     return intersect_tiles_impl(d_aabb, d_depths, d_screen, total, n_per_image, width, height, d_workspace, workspace_bytes, d_isect_ids,
-                                d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, mark_before_sort, nullptr, nullptr, 0, d_max_pairs);
+                                d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, mark_before_sort, nullptr, nullptr, 0, d_max_pairs,
+                                d_tile_active);
 }
 
 int launch_intersect_tiles_packed(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen, const int32_t* d_image_ids,
                                   const int64_t* d_total, int64_t max_pairs, int64_t n_images, int32_t width, int32_t height,
                                   void* d_workspace, int64_t workspace_bytes, int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
-                                  int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream) {
+                                  int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, const int32_t* d_tile_active) {
     SSB_REQUIRE(d_image_ids && d_total && n_images > 0, "ssb_intersect_tiles_packed: NULL argument");
     return intersect_tiles_impl(d_aabb, d_depths, d_screen, max_pairs, 1, width, height, d_workspace, workspace_bytes, d_isect_ids,
-                                d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, nullptr, d_image_ids, d_total, n_images, nullptr);
+                                d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream, nullptr, d_image_ids, d_total, n_images, nullptr,
+                                d_tile_active);
 }
 
 static int intersect_tiles_impl(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen,
@@ -753,7 +825,8 @@ static int intersect_tiles_impl(const float* d_aabb, const float* d_depths, cons
                         void* d_workspace, int64_t workspace_bytes,
                         int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
                         int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream, cudaEvent_t mark_before_sort,
-                        const int32_t* d_image_ids, const int64_t* d_total, int64_t n_images_packed, int64_t* d_max_pairs) {
+                        const int32_t* d_image_ids, const int64_t* d_total, int64_t n_images_packed, int64_t* d_max_pairs,
+                        const int32_t* d_tile_active) {
     SSB_REQUIRE(d_aabb && d_depths && d_screen && d_workspace && d_flatten_ids && d_tile_offsets && d_n_isects, "ssb_intersect_tiles: NULL argument");
     SSB_REQUIRE(total >= 0 && n_per_image > 0 && width > 0 && height > 0 && capacity >= 0, "ssb_intersect_tiles: bad sizes");
     SSB_REQUIRE(total < ((int64_t)1 << 31) && capacity < ((int64_t)1 << 31), "ssb_intersect_tiles: pair indices and positions must fit int32");
@@ -783,7 +856,10 @@ static int intersect_tiles_impl(const float* d_aabb, const float* d_depths, cons
     else depth_range_kernel<<<range_grid, 256, 0, st>>>((const float4*)d_aabb, d_depths, total, n_per_image, range);
     SSB_LAUNCHED("depth_range_kernel");
     const unsigned pass_grid = (unsigned)ceil_div(total, kBinThreads);
-    bin_pass_kernel<false><<<pass_grid, kBinThreads, 0, st>>>((const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th, range, bins, capacity, nullptr, d_image_ids, d_total);
+    if (d_tile_active)
+        bin_pass_kernel<false, true><<<pass_grid, kBinThreads, 0, st>>>((const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th, range, bins, capacity, nullptr, d_image_ids, d_total, d_tile_active);
+    else
+        bin_pass_kernel<false, false><<<pass_grid, kBinThreads, 0, st>>>((const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th, range, bins, capacity, nullptr, d_image_ids, d_total, nullptr);
     SSB_LAUNCHED("bin_pass_kernel<count>");
     bins_chunk_sum_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(bins, n_bins, chunk_sums);
     SSB_LAUNCHED("bins_chunk_sum_kernel");
@@ -791,7 +867,10 @@ static int intersect_tiles_impl(const float* d_aabb, const float* d_depths, cons
     SSB_LAUNCHED("chunk_scan_kernel");
     bins_apply_kernel<<<(unsigned)chunks, kTilesBlock, 0, st>>>(bins, n_bins, chunk_sums, d_tile_offsets, (int32_t)capacity);
     SSB_LAUNCHED("bins_apply_kernel");
-    bin_pass_kernel<true><<<pass_grid, kBinThreads, 0, st>>>((const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th, range, bins, capacity, pairs, d_image_ids, d_total);
+    if (d_tile_active)
+        bin_pass_kernel<true, true><<<pass_grid, kBinThreads, 0, st>>>((const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th, range, bins, capacity, pairs, d_image_ids, d_total, d_tile_active);
+    else
+        bin_pass_kernel<true, false><<<pass_grid, kBinThreads, 0, st>>>((const float4*)d_aabb, d_depths, d_screen, total, n_per_image, tw, th, range, bins, capacity, pairs, d_image_ids, d_total, nullptr);
     SSB_LAUNCHED("bin_pass_kernel<scatter>");
     if (mark_before_sort) SSB_CUDA(cudaEventRecord(mark_before_sort, st));
     bin_sort_kernel<<<(unsigned)n_tiles, kBinSortThreads, 0, st>>>(pairs, bins, d_n_isects, n_tiles, capacity, d_isect_ids, d_flatten_ids);
@@ -901,12 +980,21 @@ int ssb_project_bwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64
     return launch_project_bwd(splats, shq, n, cams, d_aabb, const_cast<SsbScreenRec*>(d_v_screen), grads, accumulate, 0, stream, pair_of);
 }
 
+int ssb_intersect_tiles_packed_live(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen, const int32_t* d_camera_ids,
+                                    const int64_t* d_n_pairs, int64_t max_pairs, int32_t n_images, int32_t width, int32_t height,
+                                    void* d_workspace, int64_t workspace_bytes, int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
+                                    int32_t* d_tile_offsets, int64_t* d_n_isects, const int32_t* d_tile_active, void* stream) {
+    return ssb::launch_intersect_tiles_packed(d_aabb, d_depths, d_screen, d_camera_ids, d_n_pairs, max_pairs, n_images, width, height,
+                                              d_workspace, workspace_bytes, d_isect_ids, d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream,
+                                              d_tile_active);
+}
+
 int ssb_intersect_tiles_packed(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen, const int32_t* d_camera_ids,
                                const int64_t* d_n_pairs, int64_t max_pairs, int32_t n_images, int32_t width, int32_t height,
                                void* d_workspace, int64_t workspace_bytes, int64_t* d_isect_ids, int32_t* d_flatten_ids, int64_t capacity,
                                int32_t* d_tile_offsets, int64_t* d_n_isects, void* stream) {
-    return ssb::launch_intersect_tiles_packed(d_aabb, d_depths, d_screen, d_camera_ids, d_n_pairs, max_pairs, n_images, width, height,
-                                              d_workspace, workspace_bytes, d_isect_ids, d_flatten_ids, capacity, d_tile_offsets, d_n_isects, stream);
+    return ssb_intersect_tiles_packed_live(d_aabb, d_depths, d_screen, d_camera_ids, d_n_pairs, max_pairs, n_images, width, height,
+                                           d_workspace, workspace_bytes, d_isect_ids, d_flatten_ids, capacity, d_tile_offsets, d_n_isects, nullptr, stream);
 }
 
 }  // extern "C"

@@ -45,7 +45,8 @@ class SsbShQuant(C.Structure):
 
 class SsbCameras(C.Structure):
     _fields_ = [("d_viewmats", C.c_void_p), ("d_intrins", C.c_void_p), ("count", C.c_int32), ("width", C.c_int32),
-                ("height", C.c_int32), ("model", C.c_int32), ("antialiased", C.c_int32)]
+                ("height", C.c_int32), ("model", C.c_int32), ("antialiased", C.c_int32), ("distortion", C.c_int32),
+                ("reserved", C.c_int32), ("d_dist_coeffs", C.c_void_p)]
 
 
 class SsbLossConfig(C.Structure):
@@ -94,11 +95,15 @@ SIGNATURES = {
     "ssb_sort_pairs_u64_noalloc": (C.c_int, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _P, _P]),
     "ssb_intersect_tiles_workspace_bytes": (_I64, [_I64, _I64]),
     "ssb_intersect_tiles": (C.c_int, [_P, _P, _P, _I64, _I64, _I32, _I32, _P, _I64, _P, _P, _I64, _P, _P, _P]),
+    "ssb_intersect_tiles_live": (C.c_int, [_P, _P, _P, _I64, _I64, _I32, _I32, _P, _I64, _P, _P, _I64, _P, _P, _P, _P]),
+    "ssb_tile_active": (C.c_int, [_P, _I32, _I32, _I32, _I32, _I32, _P, _P]),
+    "ssb_tile_keys_live": (C.c_int, [_P, _P, _P, _I64, _I64, _I32, _I32, _P, _I64, _P, _P, _P, _P, _I64, _P, _P, _P, _P]),
     "ssb_project_fwd_packed_workspace_bytes": (_I64, [_I64, _I32]),
     "ssb_project_fwd_packed": (C.c_int, [_P, _P, _I64, _P, _P, _I64, _P, _P, _P, _P, _P, _P, _I64, _P, _P, _P]),
     "ssb_project_bwd_packed_workspace_bytes": (_I64, [_I64, _I32]),
     "ssb_project_bwd_packed": (C.c_int, [_P, _P, _I64, _P, _P, _P, _P, _P, _P, _I64, _P, _I64, _P, C.c_int, _P]),
     "ssb_intersect_tiles_packed": (C.c_int, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _P, _I64, _P, _P, _I64, _P, _P, _P]),
+    "ssb_intersect_tiles_packed_live": (C.c_int, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _I32, _P, _I64, _P, _P, _I64, _P, _P, _P, _P]),
     "ssb_tile_n_bits": (_I32, [_I64]),
     "ssb_peer_alloc": (C.c_int, [_I64, _P]),
     "ssb_peer_free": (C.c_int, [_P]),

@@ -133,6 +133,23 @@ def loss_masks(tag, B, H, W):
     return dict(same=same, half=half)
 
 
+LIVE_TILE_CASE = "ring2"
+
+
+def tile_masks(I, H, W):
+    """Masks for the live-tile fixtures (uint8, 1 = the pixel takes part): "same" masks the right half but one pixel, the top
+    rows and a block whose border pixel ring stays live; "other" is a coarse mask at another resolution."""
+    same = np.ones((I, H, W), np.uint8)
+    same[:, :, W // 2:] = 0
+    same[:, H // 2 + 3, W - 5] = 1                 # one unmasked pixel keeps its tile alive
+    same[0, : H // 4, :] = 0
+    same[-1, 32:64, 32:48] = 0                     # whole tiles masked, but their neighbours' pixels touch the one-pixel pad
+    other = np.ones((I, 9, 13), np.uint8)
+    other[:, 2:6, 3:9] = 0
+    other[0, 7:, :] = 0
+    return dict(same=same, other=other)
+
+
 def adam_inputs():
     n = 700
     cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=n)

@@ -24,8 +24,8 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, HERE)
 
-from golden_cases import (ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
-                          build_case, loss_inputs, loss_map_base, loss_masks, quant_sh_inputs, raster_cotangents)  # noqa: E402
+from golden_cases import (ACCUM_CASES, CASES, LIVE_TILE_CASE, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
+                          build_case, loss_inputs, loss_map_base, loss_masks, quant_sh_inputs, raster_cotangents, tile_masks)  # noqa: E402
 
 DEV = "cuda:0"
 
@@ -144,6 +144,36 @@ def run_loss_masked(ref, out_dir):
                 else:
                     out[f"{tag}_{kind}_map{mode}"] = lm.cpu().numpy()
     np.savez_compressed(os.path.join(out_dir, "ssim_masked.npz"), **out)
+
+
+def run_tiles_live(ref, out_dir):
+    """The live-tile map of a mask and the intersection that skips dead tiles, on the committed projection of one case."""
+    case = np.load(os.path.join(HERE, LIVE_TILE_CASE + ".npz"))
+    cfg, sp, vm, K = build_case(LIVE_TILE_CASE)
+    n, W, H, I = cfg.n_splats, cfg.width, cfg.height, vm.shape[0]
+    m = I * n
+    aabb, depths, xy, conic, opac = (dev(case[k]) for k in ("aabb", "depths", "xy", "conic", "opac"))
+    z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=DEV)
+    tw, th = (W + 15) // 16, (H + 15) // 16
+    out = {}
+    for kind, mask in tile_masks(I, H, W).items():
+        d_mask = torch.from_numpy(mask.astype(np.bool_)).to(DEV)
+        live = z(I * tw * th, dt=torch.int32)
+        check(ref.ref_tile_active(P(d_mask), I, mask.shape[1], mask.shape[2], W, H, P(live)), "ref_tile_active")
+        cap = 64 * n
+        tps, cum = z(m, dt=torch.int64), z(m, dt=torch.int64)
+        ids_a, ids_b = z(cap, dt=torch.int64), z(cap, dt=torch.int64)
+        fl_a, fl_b = z(cap, dt=torch.int32), z(cap, dt=torch.int32)
+        offs = z(I * tw * th, dt=torch.int32)
+        M, sel = C.c_int64(0), C.c_int32(0)
+        check(ref.ref_intersect_tile_live(I, n, W, H, P(aabb), P(depths), P(xy), P(conic), P(opac), P(live), P(tps), P(cum), C.c_int64(cap),
+                                          P(ids_a), P(ids_b), P(fl_a), P(fl_b), P(offs), C.byref(M), C.byref(sel)), "ref_intersect_tile_live")
+        ids, fl = (ids_b, fl_b) if sel.value else (ids_a, fl_a)
+        out.update({f"{kind}_tile_active": live.cpu().numpy(), f"{kind}_tiles_per_splat": tps.to(torch.int32).cpu().numpy(),
+                    f"{kind}_sorted_ids": ids[:M.value].cpu().numpy(), f"{kind}_sorted_flat": fl[:M.value].cpu().numpy(),
+                    f"{kind}_offsets": offs.cpu().numpy()})
+        print("tiles_live", kind, "live tiles", int(live.sum()), "of", live.numel(), "pairs", M.value)
+    np.savez_compressed(os.path.join(out_dir, "tiles_live.npz"), **out)
 
 
 def run_adam(ref, out_dir):
@@ -399,6 +429,8 @@ def main():
         run_loss_map(ref, out_dir)
     if not only or "ssim_masked" in only:
         run_loss_masked(ref, out_dir)
+    if not only or "tiles_live" in only:
+        run_tiles_live(ref, out_dir)
     if not only or "accum" in only:
         run_accum(ref, out_dir)
     if not only or "quant_proj" in only:

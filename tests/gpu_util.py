@@ -56,7 +56,7 @@ def project_fwd(lib, sp_dev, viewmats, intrins, W, H, shq=None, n=None, model=0)
     return dict(aabb=aabb, depths=depths, radii=radii, rec=rec, vm=vm, K=K)
 
 
-def tile_keys(lib, aabb, depths, rec, total, n_per_image, W, H, capacity):
+def tile_keys(lib, aabb, depths, rec, total, n_per_image, W, H, capacity, tile_active=None):
     ws_bytes = lib.ssb_tile_keys_workspace_bytes(total)
     ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=DEV)
     counts = torch.zeros(max(total, 1), dtype=torch.int32, device=DEV)
@@ -65,12 +65,16 @@ def tile_keys(lib, aabb, depths, rec, total, n_per_image, W, H, capacity):
     vals = torch.zeros(max(capacity, 1), dtype=torch.int32, device=DEV)
     n_dev = torch.zeros(1, dtype=torch.int64, device=DEV)
     m = C.c_int64(-1)
-    st = lib.ssb_tile_keys(L.ptr(aabb), L.ptr(depths), L.ptr(rec), total, n_per_image, W, H, L.ptr(ws), ws_bytes, L.ptr(counts), L.ptr(cum),
-                           L.ptr(keys), L.ptr(vals), capacity, L.ptr(n_dev), C.byref(m), None)
+    if tile_active is not None:
+        st = lib.ssb_tile_keys_live(L.ptr(aabb), L.ptr(depths), L.ptr(rec), total, n_per_image, W, H, L.ptr(ws), ws_bytes, L.ptr(counts), L.ptr(cum),
+                                    L.ptr(keys), L.ptr(vals), capacity, L.ptr(n_dev), C.byref(m), L.ptr(tile_active), None)
+    else:
+        st = lib.ssb_tile_keys(L.ptr(aabb), L.ptr(depths), L.ptr(rec), total, n_per_image, W, H, L.ptr(ws), ws_bytes, L.ptr(counts), L.ptr(cum),
+                               L.ptr(keys), L.ptr(vals), capacity, L.ptr(n_dev), C.byref(m), None)
     return st, m.value, counts, cum, keys, vals, n_dev
 
 
-def intersect_tiles(lib, aabb, depths, rec, total, n_per_image, W, H, capacity, n_tiles_total, want_keys=True):
+def intersect_tiles(lib, aabb, depths, rec, total, n_per_image, W, H, capacity, n_tiles_total, want_keys=True, tile_active=None):
     """The fused call: sorted keys (optional), sorted flatten ids, per-tile ranges, pair count."""
     ws_bytes = lib.ssb_intersect_tiles_workspace_bytes(n_tiles_total, capacity)
     ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=DEV)
@@ -78,8 +82,12 @@ def intersect_tiles(lib, aabb, depths, rec, total, n_per_image, W, H, capacity, 
     vals = torch.full((max(capacity, 1),), -1, dtype=torch.int32, device=DEV)
     offs = torch.full((max(n_tiles_total, 1),), -7, dtype=torch.int32, device=DEV)
     n_dev = torch.full((1,), -1, dtype=torch.int64, device=DEV)
-    L.check(lib.ssb_intersect_tiles(L.ptr(aabb), L.ptr(depths), L.ptr(rec), total, n_per_image, W, H, L.ptr(ws), ws_bytes,
-                                    L.ptr(keys) if want_keys else None, L.ptr(vals), capacity, L.ptr(offs), L.ptr(n_dev), None))
+    if tile_active is not None:
+        L.check(lib.ssb_intersect_tiles_live(L.ptr(aabb), L.ptr(depths), L.ptr(rec), total, n_per_image, W, H, L.ptr(ws), ws_bytes,
+                                             L.ptr(keys) if want_keys else None, L.ptr(vals), capacity, L.ptr(offs), L.ptr(n_dev), L.ptr(tile_active), None))
+    else:
+        L.check(lib.ssb_intersect_tiles(L.ptr(aabb), L.ptr(depths), L.ptr(rec), total, n_per_image, W, H, L.ptr(ws), ws_bytes,
+                                        L.ptr(keys) if want_keys else None, L.ptr(vals), capacity, L.ptr(offs), L.ptr(n_dev), None))
     torch.cuda.synchronize()
     return keys, vals, offs, int(n_dev.item())
 

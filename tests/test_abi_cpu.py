@@ -64,6 +64,16 @@ def test_argument_errors_are_statuses_not_crashes():
     sp = L.SsbSplats()
     sp.features_sh = 8
     assert lib.ssb_project_fwd(C.byref(sp), None, 0, C.byref(cams), one, one, None, one, None) == L.SSB_ERR_UNSUPPORTED
+    # a lens-distortion tier is refused, not silently rendered without distortion
+    cams.model, cams.distortion = L.CAMERA_PINHOLE, 1
+    assert lib.ssb_project_fwd(C.byref(sp), None, 0, C.byref(cams), one, one, None, one, None) == L.SSB_ERR_UNSUPPORTED
+    assert b"distortion" in lib.ssb_last_error_string()
+    # loss configuration
+    bad = L.SsbLossConfig(0.8, 0.2, 0, 0, None, 0, 0)
+    assert lib.ssb_loss_workspace_bytes(1, 16, 16, C.byref(bad)) == L.SSB_ERR_INVALID_ARGUMENT
+    ok = L.SsbLossConfig(0.8, 0.2, 3, 1, None, 0, 0)
+    assert lib.ssb_loss_workspace_bytes(1, 1080, 1920, C.byref(ok)) < 1080 * 1920 * (12 * 3 + 4) // 2
+    assert lib.ssb_tile_active(None, 1, 4, 4, 64, 64, one, None) == L.SSB_ERR_INVALID_ARGUMENT
 
 
 def test_packed_projection_workspaces_are_a_few_bytes_per_pair():

@@ -355,3 +355,28 @@ def test_masked_ssim_vs_reference(oracle):
                 lm = loss_map_base(tag, B * H * W)
                 oracle.loss_l1_ssim_masked(render, gt, B, H, W, mask=mask, map_mode=mode, map_weight=LOSS_MAP_WEIGHT, loss_map=lm, w_l1=0.0, w_ssim=0.2)
                 assert frac_bad(lm, gold[f"{tag}_{kind}_map{mode}"], 2e-5, 1e-4) <= 1e-3, (tag, kind, mode)
+
+
+def test_live_tile_map_and_intersection_vs_reference(oracle):
+    """The live-tile map of a mask (own size and another size) and the intersection that skips dead tiles: bit for bit."""
+    from golden_cases import LIVE_TILE_CASE, tile_masks
+    cfg, sp, vm, K = build_case(LIVE_TILE_CASE)
+    gold, live_gold = load(LIVE_TILE_CASE), load("tiles_live")
+    proj = ref_proj(gold)
+    n, W, H, I = cfg.n_splats, cfg.width, cfg.height, vm.shape[0]
+    tw, th = oracle.tile_grid(W, H)
+    for kind, mask in tile_masks(I, H, W).items():
+        live = oracle.tile_active(mask, W, H)
+        ref_live = live_gold[f"{kind}_tile_active"].reshape(I, th, tw)
+        assert 0 < ref_live.sum() < ref_live.size
+        assert np.array_equal(live, ref_live), kind
+        counts, cum, keys, vals = oracle.tile_keys(proj, n, W, H, tile_active=live)
+        assert np.array_equal(counts, live_gold[f"{kind}_tiles_per_splat"].astype(np.int64)), kind
+        assert counts.sum() < gold["tiles_per_splat"].sum()
+        sk, sv = oracle.sort_pairs(keys, vals, 0, 32 + oracle.tile_n_bits(tw * th * I))
+        assert np.array_equal(sk, live_gold[f"{kind}_sorted_ids"]) and np.array_equal(sv, live_gold[f"{kind}_sorted_flat"]), kind
+        offs = oracle.tile_offsets(sk, tw * th * I)
+        assert np.array_equal(offs, live_gold[f"{kind}_offsets"]), kind
+        # dead tiles have empty ranges
+        ends = np.append(offs[1:], sk.size)
+        assert np.all((ends - offs)[ref_live.reshape(-1) == 0] == 0)

@@ -453,3 +453,34 @@ def test_masked_ssim_vs_reference(lib, U):
                     # the reference adds weight * (1 - v) onto a seeded map; the library overwrites with w_ssim * (1 - v)
                     ref = (gold[f"{tag}_{kind}_map{mode - 1}"] - loss_map_base(tag, B * H * W)) * (w_ssim / LOSS_MAP_WEIGHT)
                     assert U.close_frac(lm.cpu().numpy(), ref, 2e-5, 1e-4) <= 1e-3, (tag, kind, mode)
+
+
+@pytest.mark.gpu
+def test_live_tile_map_and_intersection_vs_reference(lib, U):
+    """ssb_tile_active and the *_live intersection calls against the reference's tile_active_kernel and its intersection with
+    a live-tile map: the map, the per-splat counts, the sorted lists and the ranges, bit for bit; fused call = unfused trio."""
+    from golden_cases import LIVE_TILE_CASE, tile_masks
+    cfg, sp, vm, K = build_case(LIVE_TILE_CASE)
+    gold, live_gold = load(LIVE_TILE_CASE), load("tiles_live")
+    n, W, H, I = cfg.n_splats, cfg.width, cfg.height, vm.shape[0]
+    rec = U.pack_screen(lib, ref_proj(gold))
+    tw, th = (W + 15) // 16, (H + 15) // 16
+    cap = 64 * n
+    end_bit = 32 + lib.ssb_tile_n_bits(tw * th * I)
+    aabb, depths = U.dev(gold["aabb"]), U.dev(gold["depths"])
+    for kind, mask in tile_masks(I, H, W).items():
+        d_mask = torch.from_numpy(mask).to(U.DEV)
+        live = torch.full((I * tw * th,), -1, dtype=torch.int32, device=U.DEV)
+        L.check(lib.ssb_tile_active(L.ptr(d_mask), I, mask.shape[1], mask.shape[2], W, H, L.ptr(live), None))
+        torch.cuda.synchronize()
+        assert np.array_equal(live.cpu().numpy(), live_gold[f"{kind}_tile_active"]), kind
+        st, M, counts, cum, keys, vals, n_dev = U.tile_keys(lib, aabb, depths, rec, I * n, n, W, H, cap, tile_active=live)
+        assert st == 0 and M == live_gold[f"{kind}_sorted_ids"].size
+        assert np.array_equal(counts.cpu().numpy(), live_gold[f"{kind}_tiles_per_splat"]), kind
+        sk, sv = U.sort_pairs(lib, keys, vals, n_dev, cap, 0, end_bit)
+        offs = U.tile_ranges(lib, sk, n_dev, cap, tw * th * I)
+        assert np.array_equal(sk.cpu().numpy()[:M], live_gold[f"{kind}_sorted_ids"]) and np.array_equal(sv.cpu().numpy()[:M], live_gold[f"{kind}_sorted_flat"])
+        assert np.array_equal(offs.cpu().numpy(), live_gold[f"{kind}_offsets"]), kind
+        f_keys, f_vals, f_offs, f_M = U.intersect_tiles(lib, aabb, depths, rec, I * n, n, W, H, cap, tw * th * I, tile_active=live)
+        assert f_M == M and np.array_equal(f_offs.cpu().numpy(), live_gold[f"{kind}_offsets"])
+        assert np.array_equal(f_keys.cpu().numpy()[:M], live_gold[f"{kind}_sorted_ids"]) and np.array_equal(f_vals.cpu().numpy()[:M], live_gold[f"{kind}_sorted_flat"])

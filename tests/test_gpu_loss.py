@@ -125,6 +125,7 @@ def test_step_uses_the_general_loss(lib, oracle):
     tr.views_fwd_bwd(d_vm, d_K, d_gt, cfg.n_views)
     torch.cuda.synchronize()
     got = tr.losses.cpu().numpy()
+    pairs_masked = tr.last_isects()
     g_masked = {k: t.clone() for k, t in tr.grads.items()}
     # the last view's render, pushed through the oracle's loss
     rgb_p = C.c_void_p()
@@ -140,6 +141,16 @@ def test_step_uses_the_general_loss(lib, oracle):
     img0 = U.tensor_from_device_ptr(rgb_p.value, (H * W, 3)).cpu().numpy()
     _, l_first, _ = oracle.loss_multi_scale(img0, gt[0].reshape(-1, 3), 1, H, W, 2, mask=mk[:1])
     assert np.allclose(got, l_first + l_last, rtol=1e-3, atol=1e-5), (got, l_first + l_last)
+    # with the mask the step left the dead tiles of the last view out of the intersection; the render in live tiles is unchanged
+    tr.losses.zero_()
+    tr.views_fwd_bwd(d_vm, d_K, d_gt, cfg.n_views)
+    torch.cuda.synchronize()
+    live = oracle.tile_active(mk[-1:], W, H)[0]
+    assert 0 < live.sum() < live.size and pairs_masked < tr.last_isects()
+    L.check(lib.ssb_step_peek(tr.handle, C.byref(rgb_p), None, None, None, None, None))
+    full = U.tensor_from_device_ptr(rgb_p.value, (H, W, 3)).cpu().numpy()
+    live_px = np.kron(live, np.ones((16, 16), np.int32))[:H, :W].astype(bool)
+    assert np.array_equal(full[live_px], img.reshape(H, W, 3)[live_px])
     # the masked, two-level gradient differs from the plain one and is finite
     assert all(torch.isfinite(t).all() for t in g_masked.values())
     assert (g_masked["means"] - tr.grads["means"]).abs().max() > 0

@@ -699,6 +699,42 @@ int ssb_ckpt_read_host(SsbCkptReader* r, const char* name, void* h_ptr, uint64_t
 int ssb_ckpt_read_device(SsbCkptReader* r, const char* name, void* d_ptr, uint64_t nbytes, void* stream);
 int ssb_ckpt_reader_close(SsbCkptReader* r);
 
+/* ------------------------------------------------------------------------- *
+ * Densification: the part that runs on every training step
+ *
+ * Replaces, for the 3dgs primitive, what engine_densify_step does outside its periodic relocation
+ * (src/engine/EngineDensify.cpp:193-263,355-367):
+ *   ssb_densify_update_scores = densify_clip_scale_tensor + densify_accum_finalize_tensor + densify_update_weight +
+ *     densify_clip_score_tensor (src/kernels/densify/DensifyScoring.cu:150-409, quantile: src/kernels/densify/Quantile.cu).
+ *     d_radii [n] the largest screen radius of the step (as the optimiser's extras take it); d_scales [n][3] log-scales,
+ *     clipped in place; d_accum_weight [n] (and d_accum_weight_den [n] for SSB_ACCUM_AVG) the per-splat weights the raster
+ *     backward pass gathered (ssb_raster_bwd_accum), turned into their quotient in place for SSB_ACCUM_AVG;
+ *     d_world_grad_score [n] or NULL the score the optimiser wrote (SsbAdamExtras::d_densify_score), blended in
+ *     geometrically with weight score_blend_world_grad (1: it alone); with neither, the score is sigmoid(opacity) times
+ *     d_opacities; d_accum_buffer [n][2] the running (score, steps) pair, NULL to only clip the scales;
+ *     d_sample_score [n][2] or NULL gets (clipped score ^ final_score_power, steps).
+ *     score_mode: 0 mean, 1 max, 2 median (a hash-driven random walk), 3 geometric mean (DensifyScoreMode,
+ *     src/kernels/densify/Densify.cuh:10-15).  score_clip_quantile in (0, 1) clips the accumulator at that quantile of
+ *     its strictly positive finite entries, copies of the maximum left out; it needs the workspace.
+ *     INFINITY switches max_screen_size / max_screen_size_clip_hardness / max_world_size off.
+ *   ssb_densify_add_noise = mcmc_add_noise_tensor (revised == 0) or revised_add_noise_tensor
+ *     (src/kernels/densify/McmcRelocation.cu:556-654, src/shaders/densify.slang:13-74).  The three normals come from a hash
+ *     of the splat's own parameters, so the result is a function of the input; the hash amplifies rounding differences, so
+ *     it equals the reference's in distribution, not number for number.
+ * ------------------------------------------------------------------------- */
+typedef struct SsbDensifyScoreConfig {
+    float max_screen_size, max_screen_size_clip_hardness, max_world_size;
+    int32_t accum_mode;              /* SSB_ACCUM_* the raster weights were gathered with */
+    int32_t score_mode;
+    float score_blend_world_grad, score_power, score_clip_quantile, final_score_power;
+} SsbDensifyScoreConfig;
+int64_t ssb_densify_workspace_bytes(int64_t n_splats);
+int ssb_densify_update_scores(const SsbDensifyScoreConfig* cfg, int64_t n_splats, const float* d_radii, float* d_scales, const float* d_opacities,
+                              float* d_accum_weight, const float* d_accum_weight_den, const float* d_world_grad_score, float* d_accum_buffer,
+                              float* d_sample_score, void* d_workspace, int64_t workspace_bytes, void* stream);
+int ssb_densify_add_noise(int64_t n_splats, float scaler, int32_t revised, const float* d_radii, float* d_means, const float* d_scales,
+                          const float* d_quats, const float* d_opacities, void* stream);
+
 /* Number of kernel launches the library has issued from this process so far. */
 int64_t ssb_launch_count(void);
 

@@ -225,6 +225,35 @@ def loss_multi_scale(render, gt, B, H, W, num_scales, mask=None, loss_map_mode=0
     return v, losses, loss_map
 
 
+def quantile_positive(x, q, stride=1):
+    lib = load()
+    lib.oracle_quantile_positive.restype = C.c_float
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    return float(lib.oracle_quantile_positive(_p(x), C.c_int64(x.size // stride), C.c_int64(stride), C.c_float(q)))
+
+
+def densify_update_scores(radii, log_scales, accum_buffer, accum_weight=None, accum_den=None, world_grad=None, logit_opacs=None, sample_score=None,
+                          max_screen_size=np.inf, clip_hardness=np.inf, max_world_size=np.inf, accum_mode=1, score_mode=0, blend_w=0.0,
+                          score_power=1.0, clip_quantile=1.0, final_power=1.0):
+    """In place on log_scales [n, 3], accum_weight [n], accum_buffer [n, 2] (may be None) and sample_score [n, 2] (may be None)."""
+    lib = load()
+    n = radii.shape[0]
+    lib.oracle_densify_update_scores(C.c_int64(n), C.c_float(max_screen_size), C.c_float(clip_hardness), C.c_float(max_world_size), C.c_int(accum_mode),
+                                     C.c_int(score_mode), C.c_float(blend_w), C.c_float(score_power), C.c_float(clip_quantile), C.c_float(final_power),
+                                     _p(radii), _p(log_scales), _p(logit_opacs), _p(accum_weight), _p(accum_den), _p(world_grad), _p(accum_buffer),
+                                     _p(sample_score))
+
+
+def densify_add_noise(means, log_scales, quats, logit_opacs, scaler, revised, radii=None):
+    """In place on means [n, 3]; returns the unit normals [n, 3] that were drawn."""
+    lib = load()
+    n = means.shape[0]
+    z = np.zeros((n, 3), np.float32)
+    lib.oracle_densify_add_noise(C.c_int64(n), C.c_float(scaler), C.c_int(int(revised)), _p(radii), _p(means), _p(log_scales), _p(quats), _p(logit_opacs),
+                                 _p(z))
+    return z
+
+
 def adam_geometry(p, g, m1, m2, step, lrs, grad_scale=1.0, zero_grad=0):
     """In place on the numpy arrays of p, g, m1, m2 (dicts with means, quats, scales, opacities)."""
     lib = load()

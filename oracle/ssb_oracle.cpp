@@ -1650,4 +1650,140 @@ void oracle_adam_qq(
                       value_packed, value_bounds, nullptr, 1, 8);
 }
 
+
+// ---------------------------------------------------------------------------
+// Densification, per-step part (src/engine/EngineDensify.cpp:193-263,355-367).
+// ---------------------------------------------------------------------------
+
+// Quantile of the strictly positive finite entries of x[0], x[stride], ... with every copy of the maximum left out, by the
+// lower-rank convention rank = (uint)(clamp(q) * (count - 1)) evaluated in float; 1 when there is no such entry and
+// max / 2 when all of them are the maximum (select_pass_kernel, src/kernels/densify/Quantile.cu:164-243).  Stated here by
+// sorting, as a check of the radix select.
+float oracle_quantile_positive(const float* x, int64_t n, int64_t stride, float q) {
+    std::vector<float> v;
+    float mx = 0.f;
+    for (int64_t i = 0; i < n; ++i) {
+        float a = x[i * stride];
+        if (a > 0.f && std::isfinite(a)) { v.push_back(a); mx = std::max(mx, a); }
+    }
+    if (v.empty()) return 1.0f;
+    std::vector<float> w;
+    for (float a : v) if (a != mx) w.push_back(a);
+    if (w.empty()) return mx * 0.5f;
+    std::sort(w.begin(), w.end());
+    uint32_t rank = (uint32_t)(std::min(1.0f, std::max(0.0f, q)) * (float)(w.size() - 1));
+    return w[rank];
+}
+
+static inline float hash14_ref(float a, float b, float c, float d) {   // DensifyScoring.cu:200-206
+    a = std::fmod(a * .1031f, 1.0f); b = std::fmod(b * .1030f, 1.0f); c = std::fmod(c * .0973f, 1.0f); d = std::fmod(d * .1099f, 1.0f);
+    const float dt = a * (d + 33.33f) + b * (c + 33.33f) + c * (a + 33.33f) + d * (b + 33.33f);
+    a += dt; b += dt; c += dt; d += dt;
+    return std::fmod((a + b) * (c + d), 1.0f);
+}
+
+// densify_clip_scale_kernel (DensifyScoring.cu:150-178) + densify_accum_finalize_kernel (:281-291) +
+// densify_update_weight_kernel (:213-276) + densify_clip_score_kernel (:319-343), buffers chosen as
+// engine_densify_step chooses them (EngineDensify.cpp:211-263).  accum_mode 3 = averaged raster weights.
+void oracle_densify_update_scores(
+    int64_t n, float max_scale2d, float clip_hardness, float max_scale3d, int accum_mode, int score_mode, float blend_w, float score_power,
+    float clip_quantile, float final_power, const float* radii, float* log_scales, const float* logit_opacs, float* accum_weight,
+    const float* accum_den, const float* world_grad, float* accum_buffer, float* sample_score) {
+    for (int64_t i = 0; i < n; ++i) {
+        if (std::isfinite(max_scale2d)) {
+            float over = radii[i] / max_scale2d;
+            if (std::isfinite(clip_hardness)) over = std::min(over, clip_hardness);
+            if (over > 1.0f) {
+                float l = std::log(over);
+                for (int k = 0; k < 3; ++k) log_scales[3 * i + k] -= l;
+            }
+        }
+        if (std::isfinite(max_scale3d)) {
+            float cap = std::log(max_scale3d);
+            for (int k = 0; k < 3; ++k) log_scales[3 * i + k] = std::min(log_scales[3 * i + k], cap);
+        }
+    }
+    if (!accum_buffer) return;
+    if (accum_mode == 3 && accum_weight)
+        for (int64_t i = 0; i < n; ++i) accum_weight[i] = accum_den[i] > 0.f ? accum_weight[i] / accum_den[i] : 0.f;
+    const float* score = accum_weight;
+    const float* score2 = nullptr;
+    bool by_opacity = false;
+    if (blend_w >= 1.0f && world_grad) score = world_grad;
+    else if (accum_weight) { if (blend_w > 0.0f && world_grad) score2 = world_grad; }
+    else { score = logit_opacs; by_opacity = true; }
+    for (int64_t i = 0; i < n; ++i) {
+        if (!(radii[i] > 0.f)) continue;
+        float weight = std::fabs(score[i]);
+        if (score2) {
+            weight = std::pow(weight, 1.0f - blend_w) * std::pow(std::fabs(score2[i]), blend_w);
+            if (!std::isfinite(weight)) weight = 0.f;
+        }
+        if (by_opacity) weight *= 1.0f / (1.0f + std::exp(-logit_opacs[i]));
+        if (weight == 0.f) continue;
+        if (score_power != 1.0f) weight = std::pow(weight, score_power);
+        float ax = accum_buffer[2 * i], ay = accum_buffer[2 * i + 1];
+        if (score_mode == 1) { ax = std::max(ax, weight); ay = std::max(ay, 1.0f); }
+        else if (score_mode == 0) { ax = (ax * ay + weight) / (ay + 1.0f); ay += 1.0f; }
+        else if (score_mode == 2) {
+            float r = hash14_ref(1e2f * weight, 1e2f * ax, 1e2f * ay, 1e2f * (ay + 1.5f));
+            if (ay == 0.f) { ax = weight * std::exp2(r - 0.5f); ay = 1.0f; }
+            else { ax *= std::exp2((weight > ax ? 1.0f : -1.0f) * r); ay += 1.0f; }
+        } else {
+            ax = std::exp((std::log(std::max(ax, 1e-30f)) * ay + std::log(std::max(weight, 1e-30f))) / (ay + 1.0f));
+            ay += 1.0f;
+        }
+        accum_buffer[2 * i] = ax; accum_buffer[2 * i + 1] = ay;
+    }
+    const bool clip = clip_quantile > 0.f && clip_quantile < 1.f;
+    if (!clip && !sample_score) return;
+    const float c = clip ? oracle_quantile_positive(accum_buffer, n, 2, clip_quantile) : 0.f;
+    for (int64_t i = 0; i < n; ++i) {
+        float v = accum_buffer[2 * i];
+        if (clip && c > 0.f && !(v <= c)) { v = c; accum_buffer[2 * i] = c; }
+        if (sample_score) {
+            if (final_power != 1.0f) v = std::pow(std::max(v, 0.0f), final_power);
+            sample_score[2 * i] = v; sample_score[2 * i + 1] = accum_buffer[2 * i + 1];
+        }
+    }
+}
+
+// mcmc_add_noise_3dgs / revised_add_noise_3dgs (src/shaders/densify.slang:13-74): three unit normals from hash44 + Box-Muller
+// of the splat's own parameters (src/shaders/projection_utils.slang:37-68), shaped by R diag(s^2) R^T (MCMC) or R diag(s) R^T
+// (revised).  z_out (optional, [n][3]) receives the normals, so a caller can check the shaping apart from the hash.
+void oracle_densify_add_noise(int64_t n, float scaler, int revised, const float* radii, float* means, const float* log_scales,
+                              const float* quats, const float* logit_opacs, float* z_out) {
+    auto fract = [](float x) { return x - std::floor(x); };
+    for (int64_t i = 0; i < n; ++i) {
+        if (revised && radii[i] <= 0.f) continue;
+        const float* m = means + 3 * i; const float* l = log_scales + 3 * i; const float* q = quats + 4 * i;
+        const float opac = 1.0f / (1.0f + std::exp(-logit_opacs[i]));
+        float a = m[0] * m[0] + m[1] * m[1] + m[2] * m[2], b = m[0] * l[0] + m[1] * l[1] + m[2] * l[2], c = l[0] * l[0] + l[1] * l[1] + l[2] * l[2],
+              d = (q[0] + q[1] + q[2] + q[3]) * opac;
+        a = fract(a * .1031f); b = fract(b * .1030f); c = fract(c * .0973f); d = fract(d * .1099f);
+        const float dt = a * (d + 33.33f) + b * (c + 33.33f) + c * (a + 33.33f) + d * (b + 33.33f);
+        a += dt; b += dt; c += dt; d += dt;
+        const float hx = fract((a + b) * c), hy = fract((a + c) * b), hz = fract((b + c) * d), hw = fract((c + d) * a);
+        const float r0 = std::sqrt(-2.0f * std::log(1.0f - hx)), r1 = std::sqrt(-2.0f * std::log(1.0f - hy));
+        const float z[3] = {r0 * std::cos(6.28318530718f * hz), r0 * std::sin(6.28318530718f * hz), r1 * std::cos(6.28318530718f * hw)};
+        if (z_out) { z_out[3 * i] = z[0]; z_out[3 * i + 1] = z[1]; z_out[3 * i + 2] = z[2]; }
+        const float inv = 1.0f / std::sqrt(q[0] * q[0] + q[1] * q[1] + q[2] * q[2] + q[3] * q[3]);
+        const float w = q[0] * inv, x = q[1] * inv, y = q[2] * inv, zq = q[3] * inv;
+        const float R[3][3] = {{1.f - 2.f * (y * y + zq * zq), 2.f * (x * y - w * zq), 2.f * (x * zq + w * y)},
+                               {2.f * (x * y + w * zq), 1.f - 2.f * (x * x + zq * zq), 2.f * (y * zq - w * x)},
+                               {2.f * (x * zq - w * y), 2.f * (y * zq + w * x), 1.f - 2.f * (x * x + y * y)}};
+        float s[3], amp;
+        if (revised) {
+            for (int k = 0; k < 3; ++k) s[k] = std::exp(l[k]);
+            amp = std::min(0.05f * scaler * std::sqrt(2.0f * std::log(std::max(255.0f * opac, 1.0f))) * std::pow(1.0f - opac, 150.0f), 1.0f);
+        } else {
+            for (int k = 0; k < 3; ++k) s[k] = std::exp(2.f * l[k]);
+            amp = scaler * (1.0f / (1.0f + std::exp(-100.0f * ((1.0f - opac) - 0.995f))));
+        }
+        float t[3];
+        for (int k = 0; k < 3; ++k) t[k] = s[k] * (R[0][k] * z[0] + R[1][k] * z[1] + R[2][k] * z[2]) * amp;
+        for (int r = 0; r < 3; ++r) means[3 * i + r] = m[r] + R[r][0] * t[0] + R[r][1] * t[1] + R[r][2] * t[2];
+    }
+}
+
 }  // extern "C"

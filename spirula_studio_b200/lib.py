@@ -57,6 +57,15 @@ class SsbLossConfig(C.Structure):
 LOSS_MAP_NONE, LOSS_MAP_LOSS_FULL, LOSS_MAP_SSIM_FULL, LOSS_MAP_SSIM_CS, LOSS_MAP_SSIM_STRUCTURE = range(5)
 
 
+class SsbDensifyScoreConfig(C.Structure):
+    _fields_ = [("max_screen_size", C.c_float), ("max_screen_size_clip_hardness", C.c_float), ("max_world_size", C.c_float),
+                ("accum_mode", C.c_int32), ("score_mode", C.c_int32), ("score_blend_world_grad", C.c_float), ("score_power", C.c_float),
+                ("score_clip_quantile", C.c_float), ("final_score_power", C.c_float)]
+
+
+SCORE_MEAN, SCORE_MAX, SCORE_MEDIAN, SCORE_GEOM = range(4)
+
+
 class SsbAdamConfig(C.Structure):
     _fields_ = [("lr_means", C.c_float), ("lr_quats", C.c_float), ("lr_scales", C.c_float), ("lr_opacities", C.c_float),
                 ("lr_features_dc", C.c_float), ("lr_features_sh", C.c_float), ("sh_reg_weight", C.c_float),
@@ -144,6 +153,9 @@ SIGNATURES = {
     "ssb_step_set_profiling": (C.c_int, [_P, C.c_int]),
     "ssb_step_get_profile": (C.c_int, [_P, _P, _P]),
     "ssb_launch_count": (_I64, []),
+    "ssb_densify_workspace_bytes": (_I64, [_I64]),
+    "ssb_densify_update_scores": (C.c_int, [_P, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _P]),
+    "ssb_densify_add_noise": (C.c_int, [_I64, _F, _I32, _P, _P, _P, _P, _P, _P]),
     "ssb_ckpt_array_header": (C.c_int, [C.c_int, C.c_uint64, _P, C.c_int]),
     "ssb_ckpt_member_header": (C.c_int, [C.c_char_p, C.c_uint64, _P]),
     "ssb_ckpt_writer_open": (C.c_int, [C.c_char_p, _P]),

@@ -150,6 +150,49 @@ def tile_masks(I, H, W):
     return dict(same=same, other=other)
 
 
+MULTI_SCALE_RUNS = (("none", 2), ("none", 3), ("same", 3), ("half", 2))     # (mask kind, levels) of loss_multi.npz
+
+
+def densify_inputs(n=3000, seed=909):
+    """Per-splat inputs of the densification fixtures: screen radii (a fifth unseen), log-scales, logit opacities, this
+    step's raster weights (numerator and denominator), a world-gradient score and an accumulator with a few steps in it."""
+    rng = np.random.default_rng(seed)
+    radii = (rng.random(n) * 0.6).astype(np.float32)
+    radii[rng.random(n) < 0.2] = 0.0
+    out = dict(
+        radii=radii,
+        log_scales=(rng.standard_normal((n, 3)) * 0.6 - 3.0).astype(np.float32),
+        logit_opacs=(rng.standard_normal(n) * 2.0 - 1.0).astype(np.float32),
+        means=(rng.standard_normal((n, 3)) * 2.0).astype(np.float32),
+        quats=rng.standard_normal((n, 4)).astype(np.float32),
+        accum_weight=(rng.random(n) ** 3 * 2.0).astype(np.float32),
+        accum_den=(rng.random(n) * 3.0).astype(np.float32),
+        world_grad=(rng.random(n) ** 2 * 1e-3).astype(np.float32),
+        accum_buffer=np.stack([rng.random(n) ** 2, rng.integers(0, 6, n)], axis=1).astype(np.float32),
+    )
+    out["accum_weight"][rng.random(n) < 0.1] = 0.0
+    out["accum_weight"][::17] *= -1.0
+    out["accum_den"][rng.random(n) < 0.1] = 0.0
+    out["accum_buffer"][out["accum_buffer"][:, 1] == 0, 0] = 0.0
+    return out
+
+
+# (name, keyword arguments of the score update) of densify.npz
+DENSIFY_SCORE_RUNS = (
+    ("clip_screen", dict(max_screen_size=0.3, clip_hardness=1.5, accum=False)),
+    ("clip_world", dict(max_screen_size=0.3, clip_hardness=float("inf"), max_world_size=0.06, accum=False)),
+    ("mean", dict(score_mode=0, score_power=0.4)),
+    ("max", dict(score_mode=1, score_power=1.0)),
+    ("geom", dict(score_mode=3, score_power=0.4)),
+    ("blend", dict(score_mode=0, score_power=0.4, blend_w=0.3, world=True)),
+    ("world_only", dict(score_mode=0, score_power=0.4, blend_w=1.0, world=True)),
+    ("by_opacity", dict(score_mode=0, score_power=0.4, weights=False)),
+    ("avg", dict(score_mode=0, score_power=0.4, accum_mode=3)),
+    ("clip_score", dict(score_mode=0, score_power=0.4, clip_quantile=0.9, final_power=0.5, sample=True)),
+    ("sample_only", dict(score_mode=1, score_power=1.0, final_power=2.0, sample=True)),
+)
+
+
 def adam_inputs():
     n = 700
     cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=n)

@@ -24,8 +24,8 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, HERE)
 
-from golden_cases import (ACCUM_CASES, CASES, LIVE_TILE_CASE, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
-                          build_case, loss_inputs, loss_map_base, loss_masks, quant_sh_inputs, raster_cotangents, tile_masks)  # noqa: E402
+from golden_cases import (ACCUM_CASES, CASES, DENSIFY_SCORE_RUNS, LIVE_TILE_CASE, LOSS_MAP_WEIGHT, MULTI_SCALE_RUNS, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
+                          build_case, densify_inputs, loss_inputs, loss_map_base, loss_masks, quant_sh_inputs, raster_cotangents, tile_masks)  # noqa: E402
 
 DEV = "cuda:0"
 
@@ -174,6 +174,79 @@ def run_tiles_live(ref, out_dir):
                     f"{kind}_offsets": offs.cpu().numpy()})
         print("tiles_live", kind, "live tiles", int(live.sum()), "of", live.numel(), "pairs", M.value)
     np.savez_compressed(os.path.join(out_dir, "tiles_live.npz"), **out)
+
+
+def run_loss_multi(ref, out_dir):
+    """The reference's whole multi-scale loss driver (pyramid, per-pixel pass, SSIM pass, fold of the levels, loss map)
+    on the colour modalities: gradient, loss scalars and the loss map of modes 1 (loss_full) and 3 (SSIM contrast-structure)."""
+    out = {}
+    for tag, (B, H, W, render, gt) in loss_inputs().items():
+        d_render, d_gt = dev(render), dev(gt)
+        masks = dict(loss_masks(tag, B, H, W), none=None)
+        for kind, scales in MULTI_SCALE_RUNS:
+            mask = masks[kind]
+            d_mask = torch.from_numpy(mask.astype(np.bool_)).to(DEV) if mask is not None else None
+            Hm, Wm = (mask.shape[1], mask.shape[2]) if mask is not None else (0, 0)
+            for mode in (0, 1, 3):
+                v = torch.zeros(B * H * W, 3, device=DEV)
+                lm = torch.zeros(B * H * W, device=DEV) if mode else None
+                rgb_loss, ssim = C.c_float(0), C.c_float(0)
+                check(ref.ref_multi_scale_loss(scales, B, H, W, P(d_render), P(d_gt), P(d_mask) if d_mask is not None else None, Hm, Wm,
+                                               C.c_float(0.8), C.c_float(0.2), mode, P(v), P(lm) if lm is not None else None,
+                                               C.byref(rgb_loss), C.byref(ssim)), "ref_multi_scale_loss")
+                key = f"{tag}_{kind}_{scales}"
+                if mode == 0:
+                    out[key + "_grad"] = v.cpu().numpy()
+                    out[key + "_scalars"] = np.array([rgb_loss.value, ssim.value], np.float32)
+                else:
+                    out[key + f"_map{mode}"] = lm.cpu().numpy()
+    np.savez_compressed(os.path.join(out_dir, "loss_multi.npz"), **out)
+
+
+def run_densify(ref, out_dir):
+    """The reference's per-step densification kernels: scale clip, averaged-weight quotient, score update (mean, max, geometric
+    mean; blended, world-gradient-only and opacity-weighted scores), quantile clip with the powered sample score, and both noises."""
+    inp = densify_inputs()
+    n = inp["radii"].shape[0]
+    out = {}
+    inf = float("inf")
+    for name, kw in DENSIFY_SCORE_RUNS:
+        radii, scales, opacs = dev(inp["radii"]), dev(inp["log_scales"]), dev(inp["logit_opacs"])
+        aw, den, wg, acc = dev(inp["accum_weight"]), dev(inp["accum_den"]), dev(inp["world_grad"]), dev(inp["accum_buffer"])
+        if kw.get("max_screen_size") is not None or kw.get("max_world_size") is not None:
+            check(ref.ref_densify_clip_scale(C.c_int64(n), P(radii), P(scales), None, C.c_float(kw.get("max_screen_size", inf)),
+                                             C.c_float(kw.get("clip_hardness", inf)), C.c_float(kw.get("max_world_size", inf))), "clip_scale")
+            out[f"{name}_log_scales"] = scales.cpu().numpy()
+        if kw.get("accum", True):
+            blend = kw.get("blend_w", 0.0)
+            if kw.get("accum_mode", 1) == 3:
+                both = torch.cat([aw, den])
+                check(ref.ref_densify_accum_finalize(C.c_int64(n), P(both)), "accum_finalize")
+                aw = both[:n].clone()
+                out[f"{name}_accum_weight"] = aw.cpu().numpy()
+            # buffers as engine_densify_step picks them (src/engine/EngineDensify.cpp:222-243)
+            has_w, has_wg = kw.get("weights", True), kw.get("world", False)
+            if blend >= 1.0 and has_wg:
+                score, score2, op = wg, None, None
+            elif has_w:
+                score, score2, op = aw, (wg if blend > 0 and has_wg else None), None
+            else:
+                score, score2, op = opacs, None, opacs
+            check(ref.ref_densify_update_weight(C.c_int64(n), P(radii), P(op), P(score), P(score2), C.c_float(blend), C.c_float(kw["score_power"]),
+                                                P(acc), kw["score_mode"]), "update_weight")
+            sample = torch.zeros(n, 2, device=DEV) if kw.get("sample") else None
+            if kw.get("sample") or kw.get("clip_quantile", 1.0) < 1.0:
+                check(ref.ref_densify_clip_score(C.c_int64(n), P(acc), C.c_float(kw.get("clip_quantile", 1.0)), C.c_float(kw.get("final_power", 1.0)),
+                                                 P(sample)), "clip_score")
+            out[f"{name}_accum_buffer"] = acc.cpu().numpy()
+            if sample is not None:
+                out[f"{name}_sample_score"] = sample.cpu().numpy()
+    for revised in (0, 1):
+        means, radii, scales, quats, opacs = (dev(inp[k]) for k in ("means", "radii", "log_scales", "quats", "logit_opacs"))   # named: see run_loss
+        check(ref.ref_densify_add_noise(C.c_int64(n), C.c_float(5e5 * 1.6e-4 if revised else 2e3), revised, P(radii), P(means), P(scales), P(quats),
+                                        P(opacs)), "add_noise")
+        out[f"noise{revised}_means"] = means.cpu().numpy()
+    np.savez_compressed(os.path.join(out_dir, "densify.npz"), **out)
 
 
 def run_adam(ref, out_dir):
@@ -429,6 +502,10 @@ def main():
         run_loss_map(ref, out_dir)
     if not only or "ssim_masked" in only:
         run_loss_masked(ref, out_dir)
+    if not only or "loss_multi" in only:
+        run_loss_multi(ref, out_dir)
+    if not only or "densify" in only:
+        run_densify(ref, out_dir)
     if not only or "tiles_live" in only:
         run_tiles_live(ref, out_dir)
     if not only or "accum" in only:

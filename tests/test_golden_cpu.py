@@ -380,3 +380,53 @@ def test_live_tile_map_and_intersection_vs_reference(oracle):
         # dead tiles have empty ranges
         ends = np.append(offs[1:], sk.size)
         assert np.all((ends - offs)[ref_live.reshape(-1) == 0] == 0)
+
+
+def test_multi_scale_loss_vs_reference(oracle):
+    """The whole multi-scale driver of the reference (pyramid with masked pooling, per-pixel + SSIM pass per level, fold of
+    the gradients and of the loss maps, masked pixels cleared) on its own kernels, against the restatement."""
+    from golden_cases import MULTI_SCALE_RUNS, loss_masks
+    gold = load("loss_multi")
+    for tag, (B, H, W, render, gt) in loss_inputs().items():
+        masks = dict(loss_masks(tag, B, H, W), none=None)
+        for kind, scales in MULTI_SCALE_RUNS:
+            key = f"{tag}_{kind}_{scales}"
+            v, losses, _ = oracle.loss_multi_scale(render, gt, B, H, W, scales, mask=masks[kind])
+            ref = gold[key + "_grad"]
+            assert frac_bad(v, ref, 2e-6 * np.abs(ref).max(), 2e-4) <= 1e-3, key
+            rgb_loss, ssim = gold[key + "_scalars"]
+            assert abs(0.8 * losses[0] - rgb_loss) <= 1e-5 * abs(rgb_loss) + 1e-7, (key, losses, rgb_loss)
+            assert abs(losses[1] - ssim) <= 2e-5, (key, losses, ssim)
+            for mode in (1, 3):
+                _, _, lm = oracle.loss_multi_scale(render, gt, B, H, W, scales, mask=masks[kind], loss_map_mode=mode)
+                assert frac_bad(lm, gold[key + f"_map{mode}"], 2e-5, 1e-4) <= 1e-3, (key, mode)
+
+
+def test_densify_per_step_vs_reference(oracle):
+    """Scale clip, averaged-weight quotient, score update (every way the engine picks its buffers), quantile clip and sample
+    score against the reference's kernels; both noises against the reference's in distribution (the hash that drives them
+    amplifies rounding, so they are not equal number for number)."""
+    from golden_cases import DENSIFY_SCORE_RUNS, densify_inputs
+    from tests import densify_util as D
+    gold = load("densify")
+    inp = densify_inputs()
+    n = inp["radii"].shape[0]
+    for name, kw in DENSIFY_SCORE_RUNS:
+        a = D.score_run_args(kw)
+        scales = inp["log_scales"].copy()
+        acc = inp["accum_buffer"].copy() if a["use_accum"] else None
+        aw = inp["accum_weight"].copy() if a["use_weights"] else None
+        sample = np.zeros((n, 2), np.float32) if a["want_sample"] else None
+        oracle.densify_update_scores(inp["radii"], scales, acc, accum_weight=aw, accum_den=inp["accum_den"] if a["accum_mode"] == 3 else None,
+                                     world_grad=inp["world_grad"] if a["use_world"] else None, logit_opacs=inp["logit_opacs"], sample_score=sample,
+                                     max_screen_size=a["max_screen_size"], clip_hardness=a["clip_hardness"], max_world_size=a["max_world_size"],
+                                     accum_mode=a["accum_mode"], score_mode=a["score_mode"], blend_w=a["blend_w"], score_power=a["score_power"],
+                                     clip_quantile=a["clip_quantile"], final_power=a["final_power"])
+        D.check_score_run(name, dict(log_scales=scales, accum_weight=aw, accum_buffer=acc, sample_score=sample), gold)
+    # the quantile alone: the sort-based statement equals the clipped maximum of the reference's accumulator
+    ref_acc = gold["clip_score_accum_buffer"]
+    assert abs(ref_acc[:, 0].max() - oracle.quantile_positive(gold["mean_accum_buffer"], 0.9, stride=2)) <= 1e-6
+    for revised, scaler in ((0, 2e3), (1, 5e5 * 1.6e-4)):
+        moved = inp["means"].copy()
+        z = oracle.densify_add_noise(moved, inp["log_scales"], inp["quats"], inp["logit_opacs"], scaler, revised, radii=inp["radii"])
+        D.check_noise(inp, moved, scaler, revised, reference_moved=gold[f"noise{revised}_means"])

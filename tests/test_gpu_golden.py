@@ -484,3 +484,70 @@ def test_live_tile_map_and_intersection_vs_reference(lib, U):
         f_keys, f_vals, f_offs, f_M = U.intersect_tiles(lib, aabb, depths, rec, I * n, n, W, H, cap, tw * th * I, tile_active=live)
         assert f_M == M and np.array_equal(f_offs.cpu().numpy(), live_gold[f"{kind}_offsets"])
         assert np.array_equal(f_keys.cpu().numpy()[:M], live_gold[f"{kind}_sorted_ids"]) and np.array_equal(f_vals.cpu().numpy()[:M], live_gold[f"{kind}_sorted_flat"])
+
+
+@pytest.mark.gpu
+def test_multi_scale_loss_vs_reference(lib, U):
+    """ssb_loss_multi_scale against the reference's own multi-scale driver: gradient, loss scalars and loss maps."""
+    from golden_cases import MULTI_SCALE_RUNS, loss_masks
+    gold = load("loss_multi")
+    for tag, (B, H, W, render, gt) in loss_inputs().items():
+        d_r, d_g = U.dev(render), U.dev(gt)
+        masks = dict(loss_masks(tag, B, H, W), none=None)
+        for kind, scales in MULTI_SCALE_RUNS:
+            key = f"{tag}_{kind}_{scales}"
+            mask = masks[kind]
+            d_m = torch.from_numpy(mask).to(U.DEV) if mask is not None else None
+            for mode in (0, 1, 3):
+                cfg = L.SsbLossConfig(0.8, 0.2, scales, mode, d_m.data_ptr() if d_m is not None else None,
+                                      mask.shape[1] if mask is not None else 0, mask.shape[2] if mask is not None else 0)
+                need = lib.ssb_loss_workspace_bytes(B, H, W, C.byref(cfg))
+                ws = torch.empty(need, dtype=torch.uint8, device=U.DEV)
+                v = torch.zeros(B * H * W, 3, device=U.DEV); losses = torch.zeros(3, device=U.DEV); lm = torch.zeros(B * H * W, device=U.DEV)
+                L.check(lib.ssb_loss_multi_scale(L.ptr(d_r), L.ptr(d_g), B, H, W, C.byref(cfg), L.ptr(v), L.ptr(losses), L.ptr(lm), L.ptr(ws), need, None))
+                torch.cuda.synchronize()
+                if mode == 0:
+                    ref = gold[key + "_grad"]
+                    assert U.close_frac(v.cpu().numpy(), ref, 2e-6 * np.abs(ref).max(), 2e-4) <= 1e-3, key
+                    rgb_loss, ssim = gold[key + "_scalars"]
+                    assert abs(0.8 * losses[0].item() - rgb_loss) <= 1e-5 * abs(rgb_loss) + 1e-7
+                    assert abs(losses[1].item() - ssim) <= 2e-5
+                else:
+                    assert U.close_frac(lm.cpu().numpy(), gold[key + f"_map{mode}"], 2e-5, 1e-4) <= 1e-3, (key, mode)
+
+
+@pytest.mark.gpu
+def test_densify_per_step_vs_reference(lib, U):
+    """ssb_densify_update_scores against the reference's scale-clip, quotient, score-update, quantile-clip kernels, and
+    ssb_densify_add_noise against the reference's noise in distribution."""
+    from golden_cases import DENSIFY_SCORE_RUNS, densify_inputs
+    from tests import densify_util as D
+    gold = load("densify")
+    inp = densify_inputs()
+    n = inp["radii"].shape[0]
+    ws_bytes = lib.ssb_densify_workspace_bytes(n)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=U.DEV)
+    for name, kw in DENSIFY_SCORE_RUNS:
+        a = D.score_run_args(kw)
+        radii, scales, opacs = U.dev(inp["radii"]), U.dev(inp["log_scales"]), U.dev(inp["logit_opacs"])
+        acc = U.dev(inp["accum_buffer"]) if a["use_accum"] else None
+        aw = U.dev(inp["accum_weight"]) if a["use_weights"] else None
+        den = U.dev(inp["accum_den"]) if a["accum_mode"] == 3 else None
+        wg = U.dev(inp["world_grad"]) if a["use_world"] else None
+        sample = torch.zeros(n, 2, device=U.DEV) if a["want_sample"] else None
+        cfg = L.SsbDensifyScoreConfig(a["max_screen_size"], a["clip_hardness"], a["max_world_size"], a["accum_mode"], a["score_mode"], a["blend_w"],
+                                      a["score_power"], a["clip_quantile"], a["final_power"])
+        L.check(lib.ssb_densify_update_scores(C.byref(cfg), n, L.ptr(radii), L.ptr(scales), L.ptr(opacs), L.ptr(aw), L.ptr(den), L.ptr(wg), L.ptr(acc),
+                                              L.ptr(sample), L.ptr(ws), ws_bytes, None))
+        torch.cuda.synchronize()
+        host = lambda t: t.cpu().numpy() if t is not None else None
+        D.check_score_run(name, dict(log_scales=host(scales), accum_weight=host(aw), accum_buffer=host(acc), sample_score=host(sample)), gold)
+    for revised, scaler in ((0, 2e3), (1, 5e5 * 1.6e-4)):
+        moved, radii, scales, quats, opacs = (U.dev(inp[k]) for k in ("means", "radii", "log_scales", "quats", "logit_opacs"))
+        L.check(lib.ssb_densify_add_noise(n, scaler, revised, L.ptr(radii), L.ptr(moved), L.ptr(scales), L.ptr(quats), L.ptr(opacs), None))
+        torch.cuda.synchronize()
+        D.check_noise(inp, moved.cpu().numpy(), scaler, revised, reference_moved=gold[f"noise{revised}_means"])
+        again = U.dev(inp["means"])
+        L.check(lib.ssb_densify_add_noise(n, scaler, revised, L.ptr(radii), L.ptr(again), L.ptr(scales), L.ptr(quats), L.ptr(opacs), None))
+        torch.cuda.synchronize()
+        assert torch.equal(again, moved)                       # a function of its input

@@ -268,7 +268,12 @@ def run_ours(args, cfg, rank, world, local_rank):
     # "multimem" (own fused kernels through the NVSwitch multicast address; falls back to "peer" where symmetric memory
     # cannot be set up), "peer" (the same kernels with per-peer loads and stores) or "nccl" (all-reduce + full Adam)
     grad_sync = os.environ.get("SSB_GRAD_SYNC", "multimem")
-    tr = Trainer(cfg, splats, device=dev, world_size=world, rank=rank, grad_sync=grad_sync)
+    # SSB_FUSED_BACKWARD=1 (one GPU): the projection backward of all views runs together with the optimiser, so the world
+    # gradients never travel through HBM.  Off by default: at mid_1m it measured 37.5 iterations/s against 39.5, because the
+    # projection backward is bound by instruction issue, not by the gradient traffic the fusion removes, and the per-view
+    # kernels hide behind the next view's forward pass on the second stream while the fused pass runs exposed at the end.
+    fused = os.environ.get("SSB_FUSED_BACKWARD", "0") != "0"
+    tr = Trainer(cfg, splats, device=dev, world_size=world, rank=rank, grad_sync=grad_sync, fused_backward=fused)
     del splats
     # this rank's views, grouped by camera kind (one kind for every workload but the wide-camera one)
     n_kinds = scenes.n_view_kinds(cfg)
@@ -380,6 +385,16 @@ def run_ours(args, cfg, rank, world, local_rank):
         kernels["adam"] = {"ms": round(adam_ms, 4), "launches_per_iteration": 1, "algorithmic_bytes": int(ab),
                            "gbs": round(ab / (adam_ms * 1e-3) / 1e9, 1) if adam_ms > 0 else 0.0,
                            "frac_of_hbm": round(ab / (adam_ms * 1e-3) / 1e9 / peak, 4) if adam_ms > 0 else 0.0}
+        if tr.fused_backward:
+            # the projection backward of ALL views runs inside this pass (ssb_step_backward_optimize), range by range
+            nv = resident[0][4]
+            pb = stage_bytes("project_bwd", cfg.n_splats, visible, pairs, P, tiles, cfg.sh_value_bits, sort_passes)
+            fb = nv * (visible * 48 + cfg.n_splats * 16) + ab          # every view's records and aabb once, parameters and state once
+            kernels["adam"].update({"includes": "projection backward of all views, fused with the optimiser (no world-gradient arrays)",
+                                    "algorithmic_bytes": int(fb), "unfused_algorithmic_bytes": int(nv * pb + ab),
+                                    "gbs": round(fb / (adam_ms * 1e-3) / 1e9, 1) if adam_ms > 0 else 0.0,
+                                    "frac_of_hbm": round(fb / (adam_ms * 1e-3) / 1e9 / peak, 4) if adam_ms > 0 else 0.0})
+            kernels["project_bwd"]["note"] = "runs inside the optimiser pass (see adam)"
         kernels["allreduce"] = {"ms": round(comm_ms, 4), "bytes": int(tr.grads_flat.numel() * 4), "mode": tr.grad_sync,
                                 "note": "peer / multimem: nothing here, the sum over the ranks happens inside the optimiser kernels (adam time, with "
                                         "both barriers); nccl: all-reduce of the whole gradient buffer"}

@@ -626,6 +626,26 @@ int ssb_step_views_gated(SsbStep* step, const SsbSplats* params, const SsbShQuan
                          const float* d_viewmats, const float* d_intrins, const float* d_gt, int32_t n_views,
                          void* const* gt_ready, const SsbSplats* grads, int accumulate, float* d_losses, void* stream);
 
+/* Projection backward of all views fused with the optimiser: the reference's use_fused_proj_bwd_optim path
+ * (fused_projection_bwd_optimizer_3dgs_kernel, src/kernels/optim/FusedProjectionBwdOptim_kernel.cuh:146-1030: one
+ * thread per splat loops over its views, so the world gradients are never stored).
+ *   ssb_step_set_fused_backward(step, max_views > 0): ssb_step_views[_gated] then stops after each view's raster backward
+ *     and keeps the view's aabb and screen-gradient records ((16 + 48) bytes per splat and view); `grads`, `accumulate`
+ *     are ignored.  Views of successive calls are appended until ssb_step_backward_optimize consumes them.  0 switches back.
+ *   ssb_step_backward_optimize: for one range of 65 536 splats after the other, the projection backward over all kept
+ *     views (a thread per splat, gradients summed in registers and shared memory) writes the range's gradients to a
+ *     15 MB scratch that the Adam kernels of the same range read straight back out of L2.  d_viewmats / d_intrins are the
+ *     cameras of the kept views in the order they were given; n_views must equal their number.  m1 / m2 / cfg / extras
+ *     as for ssb_adam_step_ex (cfg->zero_grad is ignored); sh_state != NULL runs the quantised SH update of
+ *     ssb_adam_step_sh_quantized_ex on it (then params->features_sh, m1/m2->features_sh may be NULL), else SH is
+ *     part of the plain update.  The state layouts are those of the unfused optimiser calls, so the two paths can be
+ *     mixed from one iteration to the next; the reference keeps separate per-splat-block layouts for its fused path.
+ * The result equals ssb_step_views + ssb_adam_step_* up to the order of the floating-point sums over views. */
+int ssb_step_set_fused_backward(SsbStep* step, int32_t max_views);
+int ssb_step_backward_optimize(SsbStep* step, const SsbSplats* params, const SsbShQuant* shq, const float* d_viewmats, const float* d_intrins,
+                               int32_t n_views, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state, const SsbAdamConfig* cfg,
+                               const SsbAdamExtras* extras, void* stream);
+
 /* Pair count M of the last view processed (host copy taken after that view's
  * kernels finished; synchronises the stream). */
 int ssb_step_last_isects(SsbStep* step, int64_t* h_n_isects, void* stream);

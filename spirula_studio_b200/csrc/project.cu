@@ -491,7 +491,10 @@ template <bool MULTI_VIEW, int MODEL>
 __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
     SsbSplats sp, SsbShQuant shq, int64_t n, int C, const float* __restrict__ viewmats, const float* __restrict__ intrins,
     int W, int H, int antialiased, const float4* __restrict__ aabb, SsbScreenRec* __restrict__ v_screen,
-    SsbSplats gr, int accumulate, int clear_v_screen, const int32_t* __restrict__ pair_of) {
+    SsbSplats gr, int accumulate, int clear_v_screen, const int32_t* __restrict__ pair_of, int64_t range_first, int64_t range_end) {
+    // The launch covers splats [range_first, range_end) of the n per view; every array, the gradient arrays included, is
+    // indexed by the splat's own number (a caller that keeps gradients for the range only passes pointers moved back by
+    // the range's start).
     // pair_of (packed input): aabb and v_screen hold one entry per VISIBLE pair, and pair_of[view * n + splat] is that
     // pair's position, or negative when the pair was culled.  Null: one entry per (view, splat) pair.
     // One view per launch (the training loop's case): a thread's SH gradients overwrite its own
@@ -503,12 +506,12 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
     __shared__ __align__(16) unsigned char raw_single[MULTI_VIEW ? 16 : kShRawBytes];
     unsigned char* raw_s = MULTI_VIEW ? (unsigned char*)shg_multi : raw_single;
     float* shg_s = MULTI_VIEW ? shg_multi : sh_s;
-    const int64_t first = (int64_t)blockIdx.x * kProjBlock;
+    const int64_t first = range_first + (int64_t)blockIdx.x * kProjBlock;
     const int64_t gid = first + threadIdx.x;
-    const int count = (int)min((int64_t)kProjBlock, n - first) * kShPerSplat;
+    const int count = (int)min((int64_t)kProjBlock, range_end - first) * kShPerSplat;
     // per-splat loads (and, for a single view, its aabb and gradient record) are issued before
     // the SH span is staged, so both groups of loads are in flight together
-    const int64_t gl = gid < n ? gid : n - 1;
+    const int64_t gl = gid < range_end ? gid : range_end - 1;
     float mean[3] = {sp.means[3 * gl], sp.means[3 * gl + 1], sp.means[3 * gl + 2]};
     float4 q4 = ((const float4*)sp.quats)[gl];
     float quat[4] = {q4.x, q4.y, q4.z, q4.w};
@@ -523,7 +526,7 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
         const float4* vr = (const float4*)(v_screen + slot0);
         vr0[0] = vr[0]; vr0[1] = vr[1]; vr0[2] = vr[2];
     }
-    stage_sh(sh_s, raw_s, sp.features_sh, shq.packed, shq.bounds, shq.bits, shq.bounds_stride, first, n);
+    stage_sh(sh_s, raw_s, sp.features_sh, shq.packed, shq.bounds, shq.bits, shq.bounds_stride, first, range_end);
     if (MULTI_VIEW) {
         __syncthreads();      // every thread is done reading the codes
         for (int i = threadIdx.x; i < count; i += kProjBlock) shg_s[i] = 0.f;
@@ -532,7 +535,7 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
     bool any_view = false;
 
     float g_mean[3] = {0.f, 0.f, 0.f}, g_quat[4] = {0.f, 0.f, 0.f, 0.f}, g_scale[3] = {0.f, 0.f, 0.f}, g_op = 0.f, g_dc[3] = {0.f, 0.f, 0.f};
-    if (gid < n) {
+    if (gid < range_end) {
         const float* sh = sh_s + threadIdx.x * kShPerSplat;
         float* shg = shg_s + threadIdx.x * kShPerSplat;
         for (int cid = 0; cid < C; ++cid) {
@@ -828,7 +831,7 @@ int ssb_project_fwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, c
 
 int ssb_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
                     const SsbScreenRec* d_v_screen, const SsbSplats* grads, int accumulate, void* stream) {
-    return ssb::launch_project_bwd(splats, shq, n, cams, d_aabb, const_cast<SsbScreenRec*>(d_v_screen), grads, accumulate, 0, stream, nullptr);
+    return ssb::launch_project_bwd(splats, shq, n, cams, d_aabb, const_cast<SsbScreenRec*>(d_v_screen), grads, accumulate, 0, stream, nullptr, 0, -1);
 }
 
 }  // extern "C"
@@ -871,7 +874,7 @@ int launch_project_fwd_pack_pass(int pass, const SsbSplats* splats, const SsbShQ
 
 int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
                        SsbScreenRec* d_v_screen, const SsbSplats* grads, int accumulate, int clear_v_screen, void* stream,
-                       const int32_t* d_pair_of) {
+                       const int32_t* d_pair_of, int64_t range_first, int64_t range_count) {
     SSB_REQUIRE(splats && cams && d_aabb && d_v_screen && grads, "ssb_project_bwd: NULL argument");
     SSB_REQUIRE(grads->means && grads->quats && grads->scales && grads->opacities && grads->features_dc && grads->features_sh,
                 "ssb_project_bwd: every gradient array must be given");
@@ -884,10 +887,13 @@ int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n
     SsbShQuant q;
     int e = check_shq(splats, shq, q);
     if (e) return e;
-    if (n == 0) return SSB_OK;
-#define SSB_BWD(MULTI, MODEL) project_bwd_kernel<MULTI, MODEL><<<(unsigned)ceil_div(n, kProjBlock), kProjBlock, 0, (cudaStream_t)stream>>>( \
+    if (range_count < 0) { range_first = 0; range_count = n; }     // the whole array
+    SSB_REQUIRE(range_first >= 0 && range_first + range_count <= n && range_first % kProjBlock == 0, "ssb_project_bwd: bad splat range");
+    if (range_count == 0) return SSB_OK;
+    const int64_t range_end = range_first + range_count;
+#define SSB_BWD(MULTI, MODEL) project_bwd_kernel<MULTI, MODEL><<<(unsigned)ceil_div(range_count, kProjBlock), kProjBlock, 0, (cudaStream_t)stream>>>( \
         *splats, q, n, cams->count, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased, \
-        (const float4*)d_aabb, d_v_screen, *grads, accumulate, clear_v_screen, d_pair_of)
+        (const float4*)d_aabb, d_v_screen, *grads, accumulate, clear_v_screen, d_pair_of, range_first, range_end)
     const bool multi = cams->count != 1;
     if (cams->model == SSB_CAMERA_PINHOLE) { if (multi) SSB_BWD(true, SSB_CAMERA_PINHOLE); else SSB_BWD(false, SSB_CAMERA_PINHOLE); }
     else if (cams->model == SSB_CAMERA_FISHEYE) { if (multi) SSB_BWD(true, SSB_CAMERA_FISHEYE); else SSB_BWD(false, SSB_CAMERA_FISHEYE); }

@@ -58,7 +58,7 @@ int launch_loss_multi(const float* d_render, const float* d_gt, int B, int H, in
 int check_loss_config(const SsbLossConfig* cfg, const char* who);
 int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
                        SsbScreenRec* d_v_screen, const SsbSplats* grads, int accumulate, int clear_v_screen, void* stream,
-                       const int32_t* d_pair_of);
+                       const int32_t* d_pair_of, int64_t range_first, int64_t range_count);
 int launch_project_fwd_pack_pass(int pass, const SsbSplats* splats, const SsbShQuant* shq, int64_t n, const SsbCameras* cams,
                                  int32_t* d_flags, float* d_aabb, float* d_depths, float* d_radii, SsbScreenRec* d_screen,
                                  int32_t* d_camera_ids, int32_t* d_gaussian_ids, int64_t capacity, void* stream);

@@ -63,6 +63,12 @@ struct SsbStep {
     float* accum_weight;
     float* accum_weight_den;
     int64_t* max_pairs;       // device: largest per-view pair count since it was last cleared
+    // deferred backward (ssb_step_set_fused_backward): every view's aabb and screen-gradient records are kept, and the
+    // projection backward of all views runs together with the optimiser, a range of splats at a time
+    int def_max_views, def_count, def_last;      // def_last: slice of the last view rendered (for ssb_step_peek)
+    float* def_aabb;              // [def_max_views][n][4]
+    SsbScreenRec* def_vscreen;    // [def_max_views][n], zero outside a view's raster backward .. fused backward window
+    float* def_grads;             // gradients of one range of splats (59 floats each, one 256-byte aligned array per attribute)
     // general loss (levels, mask, loss-map mode); off unless ssb_step_set_loss switched it on
     int loss_general;
     SsbLossConfig loss_cfg;
@@ -130,6 +136,10 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
     const int64_t n = s->cfg.n_splats;
     const int W = s->cfg.width, H = s->cfg.height;
     const int64_t P = (int64_t)W * H;
+    // deferred backward: this view's aabb and gradient records go to its own slice and stay there
+    const bool deferred = s->def_max_views > 0;
+    float* aabb = deferred ? s->def_aabb + (int64_t)(s->def_count + v) * n * 4 : l.aabb;
+    SsbScreenRec* v_screen = deferred ? s->def_vscreen + (int64_t)(s->def_count + v) * n : l.v_screen;
     SsbCameras cam{};
     cam.d_viewmats = d_viewmats + 16 * (int64_t)v;
     cam.d_intrins = d_intrins + 4 * (int64_t)v;
@@ -138,7 +148,7 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
     int e;
 #define SSB_MARK(k) do { if (ev) SSB_CUDA(cudaEventRecord(ev[k], st)); } while (0)
     SSB_MARK(0);
-    if ((e = ssb_project_fwd(params, shq, n, &cam, l.aabb, l.depths, nullptr, l.screen, st))) return e;
+    if ((e = ssb_project_fwd(params, shq, n, &cam, aabb, l.depths, nullptr, l.screen, st))) return e;
     SSB_MARK(1);
     // counts + scan + scatter are reported as the key stage, the per-tile sort as the sort stage;
     // the ranges come out of the scan, so that stage is empty
@@ -149,7 +159,7 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
         if ((e = ssb_tile_active(lc.d_mask + (int64_t)v * lc.mask_h * lc.mask_w, 1, lc.mask_h, lc.mask_w, W, H, l.tile_live, st))) return e;
         live = l.tile_live;
     }
-    if ((e = launch_intersect_tiles(l.aabb, l.depths, l.screen, n, n, W, H, l.isect_ws, s->isect_ws_bytes, nullptr, l.flat, s->capacity,
+    if ((e = launch_intersect_tiles(aabb, l.depths, l.screen, n, n, W, H, l.isect_ws, s->isect_ws_bytes, nullptr, l.flat, s->capacity,
                                  l.offsets, l.n_isects, st, ev ? ev[2] : nullptr, s->max_pairs, live))) return e;
     SSB_MARK(3);
     SSB_MARK(4);
@@ -167,10 +177,10 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
         SSB_MARK(6);
         if (s->accum_mode && lc.loss_map_mode) {
             if ((e = ssb_raster_bwd_accum(l.screen, n, l.offsets, l.flat, s->capacity, l.n_isects, 1, W, H, nullptr, l.T, l.last_ids, l.v_rgb, nullptr,
-                                          nullptr, l.v_screen, s->accum_mode, l.loss_map, n, nullptr, s->accum_weight, s->accum_weight_den, st))) return e;
+                                          nullptr, v_screen, s->accum_mode, l.loss_map, n, nullptr, s->accum_weight, s->accum_weight_den, st))) return e;
         } else {
             if ((e = ssb_raster_bwd(l.screen, n, l.offsets, l.flat, s->capacity, l.n_isects, 1, W, H, nullptr, l.T, l.last_ids,
-                                    l.v_rgb, nullptr, nullptr, l.v_screen, st))) return e;
+                                    l.v_rgb, nullptr, nullptr, v_screen, st))) return e;
         }
     } else if (s->accum_mode) {
         // the view's SSIM loss map, then the backward pass that also folds it into the per-splat weights
@@ -179,16 +189,18 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
                                  s->map_weight, l.loss_map, st))) return e;
         SSB_MARK(6);
         if ((e = ssb_raster_bwd_accum(l.screen, n, l.offsets, l.flat, s->capacity, l.n_isects, 1, W, H, nullptr, l.T, l.last_ids, l.v_rgb, nullptr, nullptr,
-                                      l.v_screen, s->accum_mode, l.loss_map, n, nullptr, s->accum_weight, s->accum_weight_den, st))) return e;
+                                      v_screen, s->accum_mode, l.loss_map, n, nullptr, s->accum_weight, s->accum_weight_den, st))) return e;
     } else {
         if ((e = launch_loss(l.rgb, d_gt + (int64_t)v * P * 3, 1, H, W, s->cfg.w_l1, s->cfg.w_ssim, l.v_rgb, d_losses, st))) return e;
         SSB_MARK(6);
         if ((e = ssb_raster_bwd(l.screen, n, l.offsets, l.flat, s->capacity, l.n_isects, 1, W, H, nullptr, l.T, l.last_ids,
-                                l.v_rgb, nullptr, nullptr, l.v_screen, st))) return e;
+                                l.v_rgb, nullptr, nullptr, v_screen, st))) return e;
     }
     SSB_MARK(7);
-    if (wait_before_bwd) SSB_CUDA(cudaStreamWaitEvent(st, wait_before_bwd, 0));
-    if ((e = launch_project_bwd(params, shq, n, &cam, l.aabb, l.v_screen, grads, accumulate, 1, st, nullptr))) return e;
+    if (!deferred) {
+        if (wait_before_bwd) SSB_CUDA(cudaStreamWaitEvent(st, wait_before_bwd, 0));
+        if ((e = launch_project_bwd(params, shq, n, &cam, aabb, v_screen, grads, accumulate, 1, st, nullptr, 0, -1))) return e;
+    }
     SSB_MARK(8);
 #undef SSB_MARK
     return SSB_OK;
@@ -252,6 +264,7 @@ void ssb_step_destroy(SsbStep* s) {
     for (int k = 0; k < SsbStep_kLanes; ++k) ssb::lane_free(s->lane[k]);
     if (s->fork) cudaEventDestroy(s->fork);
     cudaFree(s->max_pairs);
+    cudaFree(s->def_aabb); cudaFree(s->def_vscreen); cudaFree(s->def_grads);
     if (s->ev_ready)
         for (int v = 0; v < SsbStep_kMaxProfViews; ++v)
             for (int k = 0; k <= SSB_STAGE_COUNT; ++k) cudaEventDestroy(s->ev[v][k]);
@@ -305,6 +318,8 @@ int ssb_step_views_gated(SsbStep* s, const SsbSplats* params, const SsbShQuant* 
     using namespace ssb;
     SSB_REQUIRE(s && params && d_viewmats && d_intrins && d_gt && grads, "ssb_step_views: NULL argument");
     SSB_REQUIRE(n_views >= 0, "ssb_step_views: bad view count");
+    SSB_REQUIRE(s->def_max_views == 0 || s->def_count + n_views <= s->def_max_views, "ssb_step_views: %d views kept + %d new exceed the room for %d "
+                "(ssb_step_set_fused_backward)", s->def_count, n_views, s->def_max_views);
     cudaStream_t user = (cudaStream_t)stream;
     if (n_views == 0) return SSB_OK;
     if (s->profiling || n_views == 1) {
@@ -317,6 +332,7 @@ int ssb_step_views_gated(SsbStep* s, const SsbSplats* params, const SsbShQuant* 
             if (prof) s->prof_views++;
         }
         s->last_lane = 0;
+        if (s->def_max_views > 0) { s->def_count += n_views; s->def_last = s->def_count - 1; }
         return SSB_OK;
     }
     SSB_CUDA(cudaEventRecord(s->fork, user));
@@ -335,6 +351,94 @@ int ssb_step_views_gated(SsbStep* s, const SsbSplats* params, const SsbShQuant* 
         SSB_CUDA(cudaEventRecord(s->lane[k].all_done, s->lane[k].stream));
         SSB_CUDA(cudaStreamWaitEvent(user, s->lane[k].all_done, 0));
     }
+    if (s->def_max_views > 0) { s->def_count += n_views; s->def_last = s->def_count - 1; }
+    return SSB_OK;
+}
+
+// Splats per range of the fused backward: the range's 59 gradient floats (31 MB) are written by one kernel and read by the
+// next, and stay in the 126 MB L2 in between together with the records that stream through.  Ranges alternate between the
+// step's two streams, each with its own scratch, so that one range's optimiser kernels run beside the next range's
+// projection backward (a range alone is less than four waves of CTAs).
+static const int64_t kFusedRange = 131072;
+
+int ssb_step_set_fused_backward(SsbStep* s, int32_t max_views) {
+    using namespace ssb;
+    SSB_REQUIRE(s && max_views >= 0, "ssb_step_set_fused_backward: bad argument");
+    const int64_t n = s->cfg.n_splats;
+    if (max_views > s->def_max_views) {
+        for (int k = 0; k < s->n_lanes; ++k) SSB_CUDA(cudaStreamSynchronize(s->lane[k].stream));
+        cudaFree(s->def_aabb); cudaFree(s->def_vscreen);
+        s->def_aabb = nullptr; s->def_vscreen = nullptr;
+        if (int e = dev_alloc(&s->def_aabb, (int64_t)max_views * n * 4, s->bytes)) return e;
+        if (int e = dev_alloc(&s->def_vscreen, (int64_t)max_views * n, s->bytes)) return e;
+        SSB_CUDA(cudaMemset(s->def_vscreen, 0, (size_t)max_views * n * sizeof(SsbScreenRec)));
+        if (!s->def_grads)
+            if (int e = dev_alloc(&s->def_grads, SsbStep_kLanes * (6 * 64 + std::min(kFusedRange, align_up(n, 256)) * 59), s->bytes)) return e;
+    }
+    s->def_max_views = max_views;      // 0: back to one projection backward per view (the buffers are kept)
+    s->def_count = 0;
+    return SSB_OK;
+}
+
+int ssb_step_backward_optimize(SsbStep* s, const SsbSplats* params, const SsbShQuant* shq, const float* d_viewmats, const float* d_intrins,
+                               int32_t n_views, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state, const SsbAdamConfig* cfg,
+                               const SsbAdamExtras* extras, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(s && params && d_viewmats && d_intrins && m1 && m2 && cfg, "ssb_step_backward_optimize: NULL argument");
+    SSB_REQUIRE(s->def_max_views > 0, "ssb_step_backward_optimize: the step does not keep its views (ssb_step_set_fused_backward)");
+    SSB_REQUIRE(n_views == s->def_count && n_views <= s->def_max_views, "ssb_step_backward_optimize: %d views given, %d kept (room for %d)", n_views,
+                s->def_count, s->def_max_views);
+    SSB_REQUIRE(!sh_state || params->features_sh == nullptr || sh_state->value_bits == 32,
+                "ssb_step_backward_optimize: SH values are either plain (params->features_sh) or quantised (sh_state), not both");
+    const int64_t n = s->cfg.n_splats;
+    s->def_count = 0;
+    if (n_views == 0) return SSB_OK;
+    SsbCameras cams{};
+    cams.d_viewmats = d_viewmats; cams.d_intrins = d_intrins; cams.count = n_views;
+    cams.width = s->cfg.width; cams.height = s->cfg.height; cams.model = s->cfg.camera_model; cams.antialiased = s->cfg.antialiased;
+    const int64_t range = std::min(kFusedRange, align_up(n, 256));
+    const int64_t scratch_floats = 6 * 64 + range * 59;
+    SsbAdamConfig c = *cfg;
+    c.zero_grad = 0;                       // every range overwrites the scratch
+    cudaStream_t user = (cudaStream_t)stream;
+    const bool two = n > range;            // more than one range: alternate between the two streams
+    if (two) {
+        SSB_CUDA(cudaEventRecord(s->fork, user));
+        for (int k = 0; k < s->n_lanes; ++k) SSB_CUDA(cudaStreamWaitEvent(s->lane[k].stream, s->fork, 0));
+    }
+    int turn = 0;
+    for (int64_t first = 0; first < n; first += range, ++turn) {
+        const int64_t count = std::min(range, n - first);
+        void* stream = two ? (void*)s->lane[turn % s->n_lanes].stream : (void*)user;
+        // the range's gradient arrays, each on a 256-byte boundary
+        float* g_means = s->def_grads + (two ? turn % s->n_lanes : 0) * scratch_floats;
+        float* g_quats = g_means + align_up(3 * range, 64);
+        float* g_scales = g_quats + align_up(4 * range, 64);
+        float* g_opac = g_scales + align_up(3 * range, 64);
+        float* g_dc = g_opac + align_up(range, 64);
+        float* g_sh = g_dc + align_up(3 * range, 64);
+        // pointers moved back by the range's start: kernels index gradients by the splat's own number
+        SsbSplats g;
+        g.means = g_means - 3 * first; g.quats = g_quats - 4 * first; g.scales = g_scales - 3 * first; g.opacities = g_opac - first;
+        g.features_dc = g_dc - 3 * first; g.features_sh = g_sh - 45 * first;
+        if (int e = launch_project_bwd(params, shq, n, &cams, s->def_aabb, s->def_vscreen, &g, 0, 1, stream, nullptr, first, count)) return e;
+        SsbSplats ga = g;
+        if (sh_state) ga.features_sh = nullptr;      // the SH update is the quantised one below
+        SsbSplats p = *params, a1 = *m1, a2 = *m2;
+        if (sh_state) { p.features_sh = nullptr; a1.features_sh = nullptr; a2.features_sh = nullptr; }
+        if (int e = ssb_adam_step_ex(&p, &ga, &a1, &a2, first, count, &c, extras, stream)) return e;
+        if (sh_state) {
+            void* values = sh_state->value_bits == 32 ? (void*)params->features_sh : sh_state->d_value_packed;
+            if (int e = ssb_adam_step_sh_quantized_ex(g.features_sh, sh_state->d_optim_packed, sh_state->d_optim_bounds, values, sh_state->d_value_bounds,
+                                                      sh_state->value_bits, sh_state->optim_bits ? sh_state->optim_bits : 8, first * 45, count * 45, n * 45,
+                                                      &c, extras ? extras->d_steps : nullptr, 45, stream)) return e;
+        }
+    }
+    if (two)
+        for (int k = 0; k < s->n_lanes; ++k) {
+            SSB_CUDA(cudaEventRecord(s->lane[k].all_done, s->lane[k].stream));
+            SSB_CUDA(cudaStreamWaitEvent(user, s->lane[k].all_done, 0));
+        }
     return SSB_OK;
 }
 
@@ -411,7 +515,7 @@ int ssb_step_peek(SsbStep* s, const float** d_rgb, const float** d_depth, const 
     if (d_T) *d_T = l.T;
     if (d_last_ids) *d_last_ids = l.last_ids;
     if (d_screen) *d_screen = l.screen;
-    if (d_aabb) *d_aabb = l.aabb;
+    if (d_aabb) *d_aabb = s->def_max_views > 0 ? s->def_aabb + (int64_t)s->def_last * s->cfg.n_splats * 4 : l.aabb;
     return SSB_OK;
 }
 

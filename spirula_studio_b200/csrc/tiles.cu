@@ -977,7 +977,7 @@ int ssb_project_bwd_packed(const SsbSplats* splats, const SsbShQuant* shq, int64
         pair_slot_kernel<<<(unsigned)ceil_div(max_pairs, 256), 256, 0, st>>>(d_camera_ids, d_gaussian_ids, d_n_pairs, max_pairs, n, total, pair_of);
         SSB_LAUNCHED("pair_slot_kernel");
     }
-    return launch_project_bwd(splats, shq, n, cams, d_aabb, const_cast<SsbScreenRec*>(d_v_screen), grads, accumulate, 0, stream, pair_of);
+    return launch_project_bwd(splats, shq, n, cams, d_aabb, const_cast<SsbScreenRec*>(d_v_screen), grads, accumulate, 0, stream, pair_of, 0, -1);
 }
 
 int ssb_intersect_tiles_packed_live(const float* d_aabb, const float* d_depths, const SsbScreenRec* d_screen, const int32_t* d_camera_ids,

@@ -57,7 +57,7 @@ def _flat_views(flat, n, attrs=_ATTRS):
 
 class Trainer:
     def __init__(self, cfg: SceneConfig, splats: dict, device="cuda:0", isect_capacity=0, w_l1=0.8, w_ssim=0.2,
-                 process_group=None, world_size=1, rank=0, grad_sync="peer"):
+                 process_group=None, world_size=1, rank=0, grad_sync="peer", fused_backward=False):
         self.lib = L.load()
         self.cfg = cfg
         self.device = torch.device(device)
@@ -116,6 +116,14 @@ class Trainer:
         # device staging for one rank's share of a batch, per camera kind (filled by train_step)
         self._staging = {}
         self._copy_stream = None
+        # One GPU, one camera kind: the projection backward of all views can run together with the optimiser
+        # (ssb_step_backward_optimize), so the world gradients never travel through HBM.  With several ranks the
+        # gradients have to be summed over the ranks first, so the per-view backward stays.
+        self.fused_backward = bool(fused_backward) and world_size == 1 and len(self.handles) == 1
+        self._kept_cams = []
+        if self.fused_backward:
+            L.check(self.lib.ssb_step_set_fused_backward(self.handle, max(int(cfg.n_views), 1)))
+            self._fused_room = max(int(cfg.n_views), 1)
         # the range of splats whose optimiser step this rank performs
         self.first, self.count = 0, n
         if self.grad_sync in ("peer", "multimem"):
@@ -268,8 +276,22 @@ class Trainer:
         return own + sum(int(self.lib.ssb_step_device_bytes(h)) for h in self.handles)
 
     # -- pieces ------------------------------------------------------------
+    def _keep_cams(self, d_viewmats, d_intrins, n_views, fresh):
+        """Fused backward: remembers the cameras of the views the step object keeps, and makes room for them."""
+        if fresh:
+            self._kept_cams = []
+        self._kept_cams.append((d_viewmats[:n_views], d_intrins[:n_views]))
+        total = sum(int(c[0].shape[0]) for c in self._kept_cams)
+        if total > self._fused_room:
+            if len(self._kept_cams) > 1:
+                raise RuntimeError("fused backward: the view count of an iteration grew while views were being kept")
+            L.check(self.lib.ssb_step_set_fused_backward(self.handle, total))
+            self._fused_room = total
+
     def views_fwd_bwd(self, d_viewmats, d_intrins, d_gt, n_views, accumulate=False, stream=None, kind=0):
         """Forward + loss + backward of n_views views (all of camera kind `kind`) already resident on the device."""
+        if self.fused_backward:
+            self._keep_cams(d_viewmats, d_intrins, n_views, not accumulate)
         L.check(self.lib.ssb_step_views(self.handles[kind], C.byref(self._p_struct), C.byref(self.shq) if self.shq else None,
                                         L.ptr(d_viewmats), L.ptr(d_intrins), L.ptr(d_gt), n_views,
                                         C.byref(self._g_struct), 1 if accumulate else 0, L.ptr(self.losses), stream))
@@ -304,6 +326,21 @@ class Trainer:
         cfg = L.SsbAdamConfig(lr["lr_means"], lr["lr_quats"], lr["lr_scales"], lr["lr_opacities"], lr["lr_features_dc"],
                               lr["lr_features_sh"], 0.0, 1.0 / float(total_views), self.iteration, 0)
         f, c = self.first, self.count
+        if self.fused_backward:
+            cams = self._kept_cams
+            if not cams:
+                return
+            d_vm = cams[0][0] if len(cams) == 1 else torch.cat([x[0] for x in cams])
+            d_K = cams[0][1] if len(cams) == 1 else torch.cat([x[1] for x in cams])
+            sh = None
+            if self.quant:
+                sh = L.SsbShAdamState(self.sh_optim_packed.data_ptr(), self.sh_optim_bounds.data_ptr(), self.sh_packed.data_ptr(),
+                                      self.sh_bounds.data_ptr(), self.cfg.sh_value_bits, 8)
+            L.check(self.lib.ssb_step_backward_optimize(self.handle, C.byref(self._p_struct), C.byref(self.shq) if self.shq else None,
+                                                        L.ptr(d_vm), L.ptr(d_K), int(d_vm.shape[0]), C.byref(self._m1_struct), C.byref(self._m2_struct),
+                                                        C.byref(sh) if sh is not None else None, C.byref(cfg), None, stream))
+            self._kept_cams = []
+            return
         if self.grad_sync in ("peer", "multimem"):
             sh = None
             if self.quant:
@@ -420,6 +457,8 @@ class Trainer:
             if nv == 0:
                 continue
             d_view, d_intr, d_gt = self._staging[(kind, k)]
+            if self.fused_backward:
+                self._keep_cams(d_view, d_intr, nv, first)
             # one call per camera kind: each view's loss stage waits on the device for its own target
             L.check(self.lib.ssb_step_views_gated(self.handles[kind], C.byref(self._p_struct), C.byref(self.shq) if self.shq else None,
                                                   L.ptr(d_view), L.ptr(d_intr), L.ptr(d_gt), nv, handles,

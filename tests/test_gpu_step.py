@@ -586,3 +586,54 @@ def test_full_size_sort_and_range_properties(lib, U):
     counts = torch.bincount(tiles, minlength=n_tiles)
     ends = torch.cat([offs[1:], torch.tensor([n], device=U.DEV)])
     assert bool(((ends - offs) == counts).all())
+
+
+@pytest.mark.parametrize("quant", [False, True])
+def test_fused_backward_equals_per_view_backward(lib, U, quant):
+    """ssb_step_set_fused_backward + ssb_step_backward_optimize (projection backward of all views together with the
+    optimiser, a range of splats at a time, no world-gradient arrays) against the per-view backward followed by
+    ssb_adam_step_*: same parameters and optimiser state after three iterations, up to the order of the sums over views."""
+    from spirula_studio_b200.trainer import Trainer
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=140001, width=176, height=128, n_views=5)     # two ranges, the second ragged
+    cfg.rig, cfg.rig_radius, cfg.log_scale_mu = "ring", 3.0, -3.0
+    if quant:
+        cfg.sh_value_bits, cfg.sh_optim_bits = 16, 8
+    sp = scenes.make_splats(cfg)
+    vm, K = scenes.make_cameras(cfg)
+    gt = np.stack([scenes.make_target(cfg, v) for v in range(cfg.n_views)])
+    host = tuple(torch.from_numpy(a).pin_memory() for a in (vm, K, gt))
+    dev3 = tuple(t.to(U.DEV) for t in host)
+    a, b = Trainer(cfg, sp, device=U.DEV), Trainer(cfg, sp, device=U.DEV, fused_backward=True)
+    assert b.fused_backward and not a.fused_backward
+    for it in range(3):
+        if it == 1:
+            # views handed over in two calls (3 + 2): the second call's views are appended to the kept ones
+            for tr in (a, b):
+                tr.losses.zero_()
+                tr.views_fwd_bwd(dev3[0][:3], dev3[1][:3], dev3[2][:3], 3)
+                tr.views_fwd_bwd(dev3[0][3:], dev3[1][3:], dev3[2][3:], 2, accumulate=True)
+                tr.optimizer_step(cfg.n_views)
+            la, lb = a.losses.cpu().numpy(), b.losses.cpu().numpy()
+        else:
+            la, lb = np.array(a.train_step(*host, cfg.n_views)), np.array(b.train_step(*host, cfg.n_views))
+        assert np.allclose(la, lb, rtol=1e-4, atol=1e-6), (it, la, lb)
+    torch.cuda.synchronize()
+    for k in ("means", "quats", "scales", "opacities", "features_dc") + (() if quant else ("features_sh",)):
+        x, y = a.params[k].cpu().numpy(), b.params[k].cpu().numpy()
+        assert np.abs(x - np.asarray(sp[k]).reshape(-1)).max() > 0
+        # Adam's first steps move a coordinate by about lr whatever the gradient's size, so a gradient at rounding level
+        # can flip a step's sign; such coordinates are rare
+        assert U.close_frac(y, x, 1e-6, 1e-3) <= 5e-3, k
+        assert U.close_frac(b.m1[k].cpu().numpy(), a.m1[k].cpu().numpy(), 1e-9, 1e-3) <= 5e-3, k
+    if quant:
+        # compare the SH VALUES the codes stand for: a flipped first step moves a value by 2 lr, and a block's bounds with it
+        def values(tr):
+            out = torch.empty(cfg.n_splats * 45, device=U.DEV)
+            L.check(lib.ssb_quant_decode(L.ptr(tr.sh_packed), L.ptr(tr.sh_bounds), cfg.n_splats * 45, 16, L.ptr(out), None))
+            return out
+        va, vb = values(a), values(b)
+        lr = cfg.lrs["lr_features_sh"]
+        assert (va - vb).abs().max().item() <= 3 * 3 * lr
+        assert ((va - vb).abs() > 0.1 * lr).float().mean().item() <= 3e-2
+    assert a.check_capacity() == b.check_capacity()
+    a.close(); b.close()

@@ -755,6 +755,37 @@ int ssb_densify_update_scores(const SsbDensifyScoreConfig* cfg, int64_t n_splats
 int ssb_densify_add_noise(int64_t n_splats, float scaler, int32_t revised, const float* d_radii, float* d_means, const float* d_scales,
                           const float* d_quats, const float* d_opacities, void* stream);
 
+/* The periodic part of the revised strategy: relocate_splats_with_long_axis_split_tensor and
+ * add_splats_with_long_axis_split_tensor (src/kernels/densify/Relocation.cu:205-369; split rule
+ * src/shaders/densify.slang:76-94; draw src/kernels/densify/DensifySampling.cu:278-390).
+ *   ssb_densify_relocate: a splat is dead when sigmoid(opacity) <= min_opacity or its parameters are not finite.  As many
+ *     live splats as there are dead ones are drawn without replacement with probability proportional to the score
+ *     (d_sample_score, else d_accum_buffer: [.][2], the score in lane 0; Efraimidis-Spirakis keys from the integer hash
+ *     of (seed, index), the smallest keys win); each drawn splat is split along its longest axis into itself and one
+ *     dead slot: means moved apart by half the longest extent, the long axis halved and the others scaled by 0.85,
+ *     opacity logit(k / (1 + e^-o - k))-style reduced with k = split_opacity_k, rotation, DC and SH copied (quantised
+ *     SH values are decoded with the source block's bounds and encoded against the destination block's current ones),
+ *     the destination's optimiser state set to zero (quantised state: the codes nearest to zero), its step counter
+ *     cleared, its score copied.  The number of dead splats stays on the device; *d_num_relocated (device, may be NULL)
+ *     receives it.  Dead slots are filled in ascending order (the reference's order varies from run to run).
+ *   ssb_densify_add: num_new live splats are drawn the same way (no splat is excluded) and split into themselves and
+ *     the slots cur_n .. cur_n + num_new - 1, which the arrays must have room for.
+ * Arrays: params / m1 / m2 as for the optimiser; an array that is NULL is not kept in that form (SH values NULL when
+ * they are quantised in sh.d_value_packed; SH moments NULL when sh.d_optim_packed holds the quantised state).
+ * Bounds are one per 256 cells.  The workspace serves both calls and depends on cur_n only. */
+typedef struct SsbDensifyState {
+    SsbSplats params, m1, m2;
+    SsbShAdamState sh;             /* d_optim_packed NULL: fp32 SH moments; d_value_packed NULL or value_bits 32: fp32 SH values */
+    float* d_accum_buffer;         /* [capacity][2] running (score, steps), or NULL */
+    const float* d_sample_score;   /* [capacity][2] or NULL: then d_accum_buffer drives the draw */
+    int32_t* d_steps;              /* per-splat step counters, or NULL */
+} SsbDensifyState;
+int64_t ssb_densify_relocate_workspace_bytes(int64_t n_splats);
+int ssb_densify_relocate(const SsbDensifyState* state, int64_t cur_n, float min_opacity, float split_opacity_k, uint32_t seed, void* d_workspace,
+                         int64_t workspace_bytes, int32_t* d_num_relocated, void* stream);
+int ssb_densify_add(const SsbDensifyState* state, int64_t cur_n, int64_t num_new, float split_opacity_k, uint32_t seed, void* d_workspace,
+                    int64_t workspace_bytes, void* stream);
+
 /* Number of kernel launches the library has issued from this process so far. */
 int64_t ssb_launch_count(void);
 

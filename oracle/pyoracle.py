@@ -254,6 +254,34 @@ def densify_add_noise(means, log_scales, quats, logit_opacs, scaler, revised, ra
     return z
 
 
+def weighted_sample(weights, seed, k, alive=None):
+    """Indices of the k smallest Efraimidis-Spirakis keys; weights [n, 2] float32 (score in lane 0)."""
+    lib = load()
+    n = weights.shape[0]
+    out = np.zeros(k, np.int32)
+    lib.oracle_weighted_sample(C.c_int64(n), C.c_uint32(seed), _p(_f(weights)), _p(alive), C.c_int64(k), _p(out))
+    return out
+
+
+def densify_split(mode, st, cur_n, seed, split_k, min_opacity=0.005, num_new=0):
+    """mode 0: relocate the dead splats of st (dict of numpy arrays, changed in place); mode 1: add num_new splats.
+    st: means, quats, scales, opacities, features_dc, features_sh (or None), m1_*/m2_* (or None), accum [cap, 2], weights [cap, 2],
+    optional steps, sh_optim_packed/bounds/bits, sh_value_packed/bounds/bits.  Returns (src indices, dst indices)."""
+    lib = load()
+    lib.oracle_densify_split.restype = C.c_int64
+    cap = st["means"].shape[0]
+    src = np.zeros(cap, np.int32); dst = np.zeros(cap, np.int32)
+    attrs = ("means", "quats", "scales", "opacities", "features_dc", "features_sh")
+    args = [C.c_int(mode), C.c_int64(cur_n), C.c_int64(num_new), C.c_float(min_opacity), C.c_float(split_k), C.c_uint32(seed), _p(st["weights"])]
+    args += [_p(st.get(a)) for a in attrs]
+    args += [_p(st.get("m1_" + a)) for a in attrs] + [_p(st.get("m2_" + a)) for a in attrs]
+    args += [_p(st.get("sh_optim_packed")), _p(st.get("sh_optim_bounds")), C.c_int(st.get("sh_optim_bits", 0)),
+             _p(st.get("sh_value_packed")), _p(st.get("sh_value_bounds")), C.c_int(st.get("sh_value_bits", 32)),
+             _p(st.get("accum")), _p(st.get("steps")), _p(src), _p(dst)]
+    k = lib.oracle_densify_split(*args)
+    return src[:k].copy(), dst[:k].copy()
+
+
 def adam_geometry(p, g, m1, m2, step, lrs, grad_scale=1.0, zero_grad=0):
     """In place on the numpy arrays of p, g, m1, m2 (dicts with means, quats, scales, opacities)."""
     lib = load()

@@ -49,3 +49,39 @@ extern "C" int ref_densify_add_noise(int64_t n, float scaler, int revised, const
         mcmc_add_noise_tensor(n, scaler, vec_of<float3>(means, n), vec_of<float3>(log_scales, n), vec_of<float4>(quats, n), vec_of<float>(opacs, n));
     return ref_finish();
 }
+
+// relocate_splats_with_long_axis_split_tensor (mode 0) / add_splats_with_long_axis_split_tensor (mode 1), Relocation.cu:205-369.
+// cap: allocated splats of every array; sh may be NULL (quantised values), the SH moments too (quantised state).
+// Bounds are in the one-per-256-cells layout.  Non-SH moments stay fp32.
+extern "C" int ref_densify_split(int mode, int64_t cur_n, int64_t num_new, int64_t cap, float min_opacity, float split_k, uint32_t seed,
+                                 float* weights, float* means, float* quats, float* scales, float* opacs, float* dc, float* sh,
+                                 float* m1_means, float* m1_quats, float* m1_scales, float* m1_opacs, float* m1_dc, float* m1_sh,
+                                 float* m2_means, float* m2_quats, float* m2_scales, float* m2_opacs, float* m2_dc, float* m2_sh,
+                                 uint8_t* sh_optim_packed, float* sh_optim_bounds, int sh_optim_bits, uint8_t* sh_value_packed, float* sh_value_bounds,
+                                 int sh_value_bits, float* accum, int32_t* steps) {
+    const int K = 15;
+    const int64_t cells = cap * K * 3, blocks = (cells + 255) / 256;
+    auto v3 = [&](float* p, int64_t n) { return p ? vec_of<float3>(p, n) : DeviceVector<float3>(); };
+    DeviceVector<float3> g1sh, g2sh;
+    if (sh_optim_bits == 32) { g1sh = v3(m1_sh, cap * K); g2sh = v3(m2_sh, cap * K); }
+    else { g1sh = DeviceVector<float3>(TorchTensorView((uint64_t)sh_optim_packed, 1, {cap * K, 12LL})); g2sh = g1sh; }     // as engine_densify_step aliases them
+    DeviceVector<float4> ob = sh_optim_bits == 32 ? DeviceVector<float4>() : vec_of<float4>(sh_optim_bounds, blocks);
+    DeviceVector<uint8_t> vp = sh_value_bits == 32 ? DeviceVector<uint8_t>()
+                                                   : DeviceVector<uint8_t>(TorchTensorView((uint64_t)sh_value_packed, 1, {cells * (sh_value_bits / 8)}));
+    DeviceVector<float2> vb = sh_value_bits == 32 ? DeviceVector<float2>() : vec_of<float2>(sh_value_bounds, blocks);
+    DeviceVector<int32_t> st = steps ? DeviceVector<int32_t>(TorchTensorView((uint64_t)steps, 4, {cap})) : DeviceVector<int32_t>();
+    NonShQuantState non_sh{};
+    if (mode == 0)
+        relocate_splats_with_long_axis_split_tensor(cur_n, min_opacity, split_k, v3(means, cap), vec_of<float4>(quats, cap), v3(scales, cap),
+            vec_of<float>(opacs, cap), v3(dc, cap), v3(sh, cap * K), v3(m1_means, cap), vec_of<float4>(m1_quats, cap), v3(m1_scales, cap),
+            vec_of<float>(m1_opacs, cap), v3(m1_dc, cap), g1sh, v3(m2_means, cap), vec_of<float4>(m2_quats, cap), v3(m2_scales, cap),
+            vec_of<float>(m2_opacs, cap), v3(m2_dc, cap), g2sh, vec_of<float2>(accum, cap), vec_of<float2>(weights, cap), st, sh_optim_bits, K, ob, false,
+            vp, vb, sh_value_bits, false, K, non_sh, seed);
+    else
+        add_splats_with_long_axis_split_tensor(cur_n, num_new, split_k, v3(means, cap), vec_of<float4>(quats, cap), v3(scales, cap),
+            vec_of<float>(opacs, cap), v3(dc, cap), v3(sh, cap * K), v3(m1_means, cap), vec_of<float4>(m1_quats, cap), v3(m1_scales, cap),
+            vec_of<float>(m1_opacs, cap), v3(m1_dc, cap), g1sh, v3(m2_means, cap), vec_of<float4>(m2_quats, cap), v3(m2_scales, cap),
+            vec_of<float>(m2_opacs, cap), v3(m2_dc, cap), g2sh, vec_of<float2>(accum, cap), vec_of<float2>(weights, cap), st, sh_optim_bits, K, ob, false,
+            vp, vb, sh_value_bits, false, K, non_sh, seed);
+    return ref_finish();
+}

@@ -1786,4 +1786,138 @@ void oracle_densify_add_noise(int64_t n, float scaler, int revised, const float*
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// Densification, periodic part: relocation of dead splats and growth by the long-axis split
+// (relocate_splats_with_long_axis_split_tensor / add_splats_with_long_axis_split_tensor,
+// src/kernels/densify/Relocation.cu:205-369).
+// ---------------------------------------------------------------------------
+static inline uint32_t hash_uint3_ref(uint32_t a, uint32_t b, uint32_t c) {      // src/core/Common.cuh:1019-1039
+    uint32_t h = a;
+    h *= 0x01000193u; h = (h << 16) | (h >> 16);
+    h ^= b; h *= 0x01000193u; h = (h << 16) | (h >> 16);
+    h ^= c; h *= 0x01000193u;
+    h ^= h >> 15; h *= 0x85ebca6bu; h ^= h >> 13; h *= 0xc2b2ae35u; h ^= h >> 16;
+    return h;
+}
+
+// Indices of the k smallest Efraimidis-Spirakis keys w / log(1 - u), ties by index (a stable ascending sort, as the
+// reference's radix sort of (key, index); DensifySampling.cu:278-390).  weights: [n][2], the score in lane 0.  alive: may be NULL.
+void oracle_weighted_sample(int64_t n, uint32_t seed, const float* weights, const uint8_t* alive, int64_t k, int32_t* out) {
+    std::vector<float> key(n);
+    for (int64_t i = 0; i < n; ++i) {
+        float u = (float)hash_uint3_ref(seed, (uint32_t)(i >> 8), (uint32_t)(i & 255)) * 2.3283064365386963e-10f;
+        float w = weights[2 * i] / det_logf(std::max(1.0f - u, 1e-30f));
+        if (alive && !alive[i]) w = 0.0f;
+        if (w == 0.0f) w = 0.0f;
+        key[i] = w;
+    }
+    std::vector<int32_t> order(n);
+    std::iota(order.begin(), order.end(), 0);
+    std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return key[a] < key[b]; });
+    for (int64_t i = 0; i < k; ++i) out[i] = order[i];
+}
+
+struct OracleDensifyArrays {
+    float *means, *quats, *scales, *opacs, *dc, *sh;
+    float *m1[6], *m2[6];
+    uint8_t* sh_optim_packed; float* sh_optim_bounds; int sh_optim_bits;
+    uint8_t* sh_value_packed; float* sh_value_bounds; int sh_value_bits;
+    float* accum; int32_t* steps;
+};
+
+static void split_one(const OracleDensifyArrays& a, int64_t s, int64_t d, float split_k) {   // Relocation.cu:13-157, densify.slang:76-94
+    const float lx = a.scales[3 * s], ly = a.scales[3 * s + 1], lz = a.scales[3 * s + 2];
+    const float* q = a.quats + 4 * s;
+    const float op = a.opacs[s];
+    const float dlen = 0.5f * std::exp(std::max(std::max(lx, ly), lz));
+    const float kl = std::log(0.5f), ks = std::log(0.85f);
+    float n3[3] = {lx, ly, lz}, e[3] = {0.f, 0.f, 0.f};
+    if (lx > ly && lx > lz) { n3[0] += kl; n3[1] += ks; n3[2] += ks; e[0] = dlen; }
+    else if (ly > lz) { n3[0] += ks; n3[1] += kl; n3[2] += ks; e[1] = dlen; }
+    else { n3[0] += ks; n3[1] += ks; n3[2] += kl; e[2] = dlen; }
+    const float inv = 1.0f / std::sqrt(q[0] * q[0] + q[1] * q[1] + q[2] * q[2] + q[3] * q[3]);
+    const float w = q[0] * inv, x = q[1] * inv, y = q[2] * inv, z = q[3] * inv;
+    const float R[3][3] = {{1.f - 2.f * (y * y + z * z), 2.f * (x * y - w * z), 2.f * (x * z + w * y)},
+                           {2.f * (x * y + w * z), 1.f - 2.f * (x * x + z * z), 2.f * (y * z - w * x)},
+                           {2.f * (x * z - w * y), 2.f * (y * z + w * x), 1.f - 2.f * (x * x + y * y)}};
+    const float new_op = std::log(split_k / (1.0f + std::exp(-op) - split_k));
+    for (int r = 0; r < 3; ++r) {
+        const float dl = R[r][0] * e[0] + R[r][1] * e[1] + R[r][2] * e[2];
+        const float m = a.means[3 * s + r];
+        a.means[3 * s + r] = m - dl; a.means[3 * d + r] = m + dl;
+        a.scales[3 * s + r] = n3[r]; a.scales[3 * d + r] = n3[r];
+    }
+    a.opacs[s] = new_op; a.opacs[d] = new_op;
+    for (int k = 0; k < 4; ++k) a.quats[4 * d + k] = q[k];
+    for (int k = 0; k < 3; ++k) a.dc[3 * d + k] = a.dc[3 * s + k];
+    if (a.sh) for (int k = 0; k < 45; ++k) a.sh[45 * d + k] = a.sh[45 * s + k];
+    if (a.sh_value_bits != 32 && a.sh_value_packed) {                                   // DensifyQuantCopy.cuh:37-77
+        const float qmax = a.sh_value_bits == 16 ? 65535.0f : 255.0f;
+        for (int k = 0; k < 45; ++k) {
+            const int64_t cs = 45 * s + k, cd = 45 * d + k;
+            const float* ms = a.sh_value_bounds + 2 * (cs >> 8); const float* md = a.sh_value_bounds + 2 * (cd >> 8);
+            const float code = a.sh_value_bits == 16 ? (float)((const uint16_t*)a.sh_value_packed)[cs] : (float)a.sh_value_packed[cs];
+            const float v = ms[0] + (ms[1] - ms[0]) * (code * (1.0f / qmax));
+            const float qf = std::min(std::max(std::round(qmax * (v - md[0]) / std::max(md[1] - md[0], 1e-30f)), 0.0f), qmax);
+            if (a.sh_value_bits == 16) ((uint16_t*)a.sh_value_packed)[cd] = (uint16_t)qf; else a.sh_value_packed[cd] = (uint8_t)qf;
+        }
+    }
+    const int width[6] = {3, 4, 3, 1, 3, 45};
+    for (int t = 0; t < 6; ++t)
+        if (a.m1[t]) for (int k = 0; k < width[t]; ++k) { a.m1[t][(int64_t)width[t] * d + k] = 0.f; a.m2[t][(int64_t)width[t] * d + k] = 0.f; }
+    if (a.sh_optim_bits && a.sh_optim_packed) {                                         // DensifyQuantCopy.cuh:29-35,234-269
+        const float qmax = a.sh_optim_bits == 8 ? 255.0f : 15.0f;
+        auto zero_code = [&](float lo, float hi) { return (uint32_t)std::min(std::max(std::round(qmax * (0.0f - lo) / std::max(hi - lo, 1e-30f)), 0.0f), qmax); };
+        for (int k = 0; k < 45; ++k) {
+            const int64_t c = 45 * d + k;
+            const float* mm = a.sh_optim_bounds + 4 * (c >> 8);
+            const uint32_t uq = zero_code(mm[0], mm[1]), sq = zero_code(mm[2], mm[3]);
+            if (a.sh_optim_bits == 8) { a.sh_optim_packed[2 * c] = (uint8_t)uq; a.sh_optim_packed[2 * c + 1] = (uint8_t)sq; }
+            else a.sh_optim_packed[c] = (uint8_t)((uq & 15u) | ((sq & 15u) << 4));
+        }
+    }
+    if (a.steps) a.steps[d] = 0;
+    if (a.accum) { a.accum[2 * d] = a.accum[2 * s]; a.accum[2 * d + 1] = a.accum[2 * s + 1]; }
+}
+
+// mode 0: relocate (dead slots in ascending order; returns their number; src_out / dst_out receive the pairs);
+// mode 1: add num_new splats at cur_n...
+int64_t oracle_densify_split(
+    int mode, int64_t cur_n, int64_t num_new, float min_opacity, float split_k, uint32_t seed, const float* weights,
+    float* means, float* quats, float* scales, float* opacs, float* dc, float* sh,
+    float* m1_means, float* m1_quats, float* m1_scales, float* m1_opacs, float* m1_dc, float* m1_sh,
+    float* m2_means, float* m2_quats, float* m2_scales, float* m2_opacs, float* m2_dc, float* m2_sh,
+    uint8_t* sh_optim_packed, float* sh_optim_bounds, int sh_optim_bits, uint8_t* sh_value_packed, float* sh_value_bounds, int sh_value_bits,
+    float* accum, int32_t* steps, int32_t* src_out, int32_t* dst_out) {
+    OracleDensifyArrays a{means, quats, scales, opacs, dc, sh, {m1_means, m1_quats, m1_scales, m1_opacs, m1_dc, m1_sh},
+                          {m2_means, m2_quats, m2_scales, m2_opacs, m2_dc, m2_sh}, sh_optim_packed, sh_optim_bounds, sh_optim_bits,
+                          sh_value_packed, sh_value_bounds, sh_value_bits, accum, steps};
+    std::vector<uint8_t> alive;
+    std::vector<int32_t> dst;
+    int64_t count = num_new;
+    if (mode == 0) {
+        alive.resize(cur_n);
+        for (int64_t i = 0; i < cur_n; ++i) {                                            // compute_relocation_mask_kernel, :160-203
+            const float* m = means + 3 * i; const float* q = quats + 4 * i; const float* s = scales + 3 * i; const float* c = dc + 3 * i;
+            const bool low = 1.0f / (1.0f + std::exp(-opacs[i])) <= min_opacity;
+            const bool fin = std::isfinite((m[0] * m[0] + m[1] * m[1] + m[2] * m[2]) / (q[0] * q[0] + q[1] * q[1] + q[2] * q[2] + q[3] * q[3]) +
+                                           (s[0] * c[0] + s[1] * c[1] + s[2] * c[2]) * opacs[i]);
+            alive[i] = !(low || !fin);
+            if (!alive[i]) dst.push_back((int32_t)i);
+        }
+        count = (int64_t)dst.size();
+    }
+    if (count == 0) return 0;
+    std::vector<int32_t> src(count);
+    oracle_weighted_sample(cur_n, seed, weights, mode == 0 ? alive.data() : nullptr, count, src.data());
+    for (int64_t i = 0; i < count; ++i) {
+        const int64_t d = mode == 0 ? dst[i] : cur_n + i;
+        split_one(a, src[i], d, split_k);
+        if (src_out) src_out[i] = src[i];
+        if (dst_out) dst_out[i] = (int32_t)d;
+    }
+    return count;
+}
+
 }  // extern "C"

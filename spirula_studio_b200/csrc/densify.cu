@@ -263,6 +263,204 @@ __global__ void __launch_bounds__(kDensifyThreads) densify_noise_kernel(int64_t 
     means[3 * idx + 2] = mz + R[2][0] * t[0] + R[2][1] * t[1] + R[2][2] * t[2];
 }
 
+
+// ---- periodic part: relocation of dead splats and growth, both by the long-axis split ---------------------------------
+// relocate_splats_with_long_axis_split_tensor / add_splats_with_long_axis_split_tensor (src/kernels/densify/Relocation.cu:205-369).
+//
+// Differences in how, not in what:
+//  * the dead splats are listed in ascending order by an ordered compaction (the reference appends them with one atomic
+//    per splat, so its order changes from run to run); the number of dead splats stays on the device: the later kernels
+//    read it there instead of the host reading it back;
+//  * the draw without replacement (Efraimidis-Spirakis keys, smallest k) sorts 64-bit words (key bits, index) with the
+//    library's own radix sort; the logarithm in the key is the fixed-operation one, so the draw is the same on every machine.
+
+constexpr int kRelocChunk = 1024;      // splats per block of the ordered compaction
+
+struct DensifyArrays {
+    float *means, *quats, *scales, *opacs, *dc, *sh;                 // sh: fp32 values or nullptr
+    float *m1[6], *m2[6];                                            // fp32 moments per attribute; [5] = SH or nullptr
+    uint8_t* sh_optim_packed; const float4* sh_optim_bounds; int sh_optim_bits;   // 8 / 4, or 0: none
+    uint8_t* sh_value_packed; const float2* sh_value_bounds; int sh_value_bits;   // 8 / 16, or 32: none
+    float2* accum; int32_t* steps;
+};
+
+// bit 0 of flags[i]: the splat stays (it may be drawn from); counts[b]: dead splats of chunk b
+__global__ void __launch_bounds__(256) reloc_mask_kernel(int64_t n, float min_opacity, DensifyArrays a, uint8_t* __restrict__ alive,
+                                                         int32_t* __restrict__ chunk_dead) {
+    __shared__ int warp_cnt[8];
+    const int64_t base = (int64_t)blockIdx.x * kRelocChunk;
+    int dead = 0;
+    for (int k = 0; k < kRelocChunk / 256; ++k) {
+        const int64_t i = base + k * 256 + threadIdx.x;
+        if (i < n) {
+            const float mx = a.means[3 * i], my = a.means[3 * i + 1], mz = a.means[3 * i + 2];
+            const float4 q = ((const float4*)a.quats)[i];
+            const float sx = a.scales[3 * i], sy = a.scales[3 * i + 1], sz = a.scales[3 * i + 2];
+            const float op = a.opacs[i];
+            const float cx = a.dc[3 * i], cy = a.dc[3 * i + 1], cz = a.dc[3 * i + 2];
+            const bool low = 1.0f / (1.0f + __expf(-op)) <= min_opacity;
+            const bool fin = isfinite((mx * mx + my * my + mz * mz) / (q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w) + (sx * cx + sy * cy + sz * cz) * op);
+            const bool relocate = low || !fin;
+            alive[i] = relocate ? 0 : 1;
+            dead += relocate;
+        }
+    }
+    dead = __reduce_add_sync(0xffffffffu, dead);
+    if ((threadIdx.x & 31) == 0) warp_cnt[threadIdx.x >> 5] = dead;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int w = 0; w < 8; ++w) t += warp_cnt[w];
+        chunk_dead[blockIdx.x] = t;
+    }
+}
+
+// exclusive scan of the chunk counts by one block; total -> *count
+__global__ void __launch_bounds__(1024) reloc_scan_kernel(int32_t* __restrict__ chunk_dead, int n_chunks, int32_t* __restrict__ count) {
+    __shared__ int warp_tot[32];
+    __shared__ int carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (int b0 = 0; b0 < n_chunks; b0 += 1024) {
+        const int i = b0 + threadIdx.x;
+        const int v = i < n_chunks ? chunk_dead[i] : 0;
+        int inc = v;
+        for (int o = 1; o < 32; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, inc, o); if ((threadIdx.x & 31) >= o) inc += t; }
+        if ((threadIdx.x & 31) == 31) warp_tot[threadIdx.x >> 5] = inc;
+        __syncthreads();
+        int woff = 0;
+        for (int w = 0; w < (int)(threadIdx.x >> 5); ++w) woff += warp_tot[w];
+        const int excl = carry + woff + inc - v;
+        if (i < n_chunks) chunk_dead[i] = excl;
+        __syncthreads();
+        if (threadIdx.x == 1023) carry = excl + v;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *count = carry;
+}
+
+// dead splats written in ascending order: dst[chunk offset + rank inside the chunk]
+__global__ void __launch_bounds__(256) reloc_list_kernel(int64_t n, const uint8_t* __restrict__ alive, const int32_t* __restrict__ chunk_off,
+                                                         int32_t* __restrict__ dst) {
+    __shared__ int warp_cnt[8];
+    __shared__ int run;
+    if (threadIdx.x == 0) run = chunk_off[blockIdx.x];
+    const int64_t base = (int64_t)blockIdx.x * kRelocChunk;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    for (int k = 0; k < kRelocChunk / 256; ++k) {
+        const int64_t i = base + k * 256 + threadIdx.x;
+        const bool d = i < n && !alive[i];
+        const unsigned m = __ballot_sync(0xffffffffu, d);
+        if (lane == 0) warp_cnt[w] = __popc(m);
+        __syncthreads();
+        int off = run;
+        for (int x = 0; x < w; ++x) off += warp_cnt[x];
+        if (d) dst[off + __popc(m & ((1u << lane) - 1u))] = (int32_t)i;
+        __syncthreads();
+        if (threadIdx.x == 0) { int t = 0; for (int x = 0; x < 8; ++x) t += warp_cnt[x]; run += t; }
+        __syncthreads();
+    }
+}
+
+__global__ void set_i64_kernel(int64_t* p, int64_t v) { *p = v; }
+
+__device__ __forceinline__ uint32_t hash_u3(uint32_t a, uint32_t b, uint32_t c) {      // src/core/Common.cuh:1019-1039
+    uint32_t h = a;
+    h *= 0x01000193u; h = (h << 16) | (h >> 16);
+    h ^= b; h *= 0x01000193u; h = (h << 16) | (h >> 16);
+    h ^= c; h *= 0x01000193u;
+    h ^= h >> 15; h *= 0x85ebca6bu; h ^= h >> 13; h *= 0xc2b2ae35u; h ^= h >> 16;
+    return h;
+}
+
+// Efraimidis-Spirakis: key = w / log(1 - u), u uniform; the k smallest keys are a draw of k without replacement with
+// probability proportional to w (compute_efraimidis_spirakis_weight_kernel, DensifySampling.cu:278-296).  The word is
+// (order-preserving key bits, index), so a sort on the upper half keeps ties in index order.
+__global__ void __launch_bounds__(256) sample_keys_kernel(int64_t n, uint32_t seed, const float2* __restrict__ weights, const uint8_t* __restrict__ alive,
+                                                          int64_t* __restrict__ keys, int32_t* __restrict__ vals) {
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    const float u = __fmul_rn((float)hash_u3(seed, blockIdx.x, threadIdx.x), 2.3283064365386963e-10f);
+    float w = __fdiv_rn(weights[i].x, det_logf(fmaxf(__fsub_rn(1.0f, u), 1e-30f)));
+    if (alive && !alive[i]) w = 0.0f;
+    if (w == 0.0f) w = 0.0f;                         // -0 and +0 sort together
+    uint32_t b = __float_as_uint(w);
+    b ^= (b >> 31) ? 0xffffffffu : 0x80000000u;
+    keys[i] = (int64_t)(((uint64_t)b << 32) | (uint32_t)i);
+    vals[i] = (int32_t)i;
+}
+
+__device__ __forceinline__ uint32_t encode_zero(float lo, float hi, float qmax) {      // DensifyQuantCopy.cuh:29-35
+    const float range = fmaxf(hi - lo, 1e-30f);
+    return (uint32_t)fminf(fmaxf(roundf(qmax * (0.0f - lo) / range), 0.0f), qmax);
+}
+
+// One thread per new splat: the source is split along its longest axis into itself and the destination
+// (relocate_with_long_axis_split_kernel, Relocation.cu:13-157; long_axis_split_3dgs, src/shaders/densify.slang:76-94).
+__global__ void __launch_bounds__(256) reloc_split_kernel(int64_t cur_n, const int32_t* __restrict__ count_ptr, int64_t count_host, float split_k,
+                                                          const int32_t* __restrict__ src_idx, const int32_t* __restrict__ dst_idx, DensifyArrays a) {
+    const int64_t idx = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    const int64_t count = count_ptr ? (int64_t)*count_ptr : count_host;
+    if (idx >= count) return;
+    const int64_t s = src_idx[idx];
+    const int64_t d = dst_idx ? (int64_t)dst_idx[idx] : cur_n + idx;
+    // geometry
+    const float lx = a.scales[3 * s], ly = a.scales[3 * s + 1], lz = a.scales[3 * s + 2];
+    const float4 q = ((const float4*)a.quats)[s];
+    const float op = a.opacs[s];
+    const float dlen = 0.5f * expf(fmaxf(fmaxf(lx, ly), lz));
+    const float kl = -0.6931471805599453f, ks = -0.16251892949777494f;        // log 0.5, log 0.85
+    float nx = lx, ny = ly, nz = lz, ex = 0.f, ey = 0.f, ez = 0.f;
+    if (lx > ly && lx > lz) { nx += kl; ny += ks; nz += ks; ex = dlen; }
+    else if (ly > lz) { nx += ks; ny += kl; nz += ks; ey = dlen; }
+    else { nx += ks; ny += ks; nz += kl; ez = dlen; }
+    const float inv = rsqrtf(q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w);
+    const float w = q.x * inv, x = q.y * inv, y = q.z * inv, z = q.w * inv;
+    const float dx = (1.f - 2.f * (y * y + z * z)) * ex + 2.f * (x * y - w * z) * ey + 2.f * (x * z + w * y) * ez;
+    const float dy = 2.f * (x * y + w * z) * ex + (1.f - 2.f * (x * x + z * z)) * ey + 2.f * (y * z - w * x) * ez;
+    const float dz = 2.f * (x * z - w * y) * ex + 2.f * (y * z + w * x) * ey + (1.f - 2.f * (x * x + y * y)) * ez;
+    const float new_op = logf(split_k / (1.0f + expf(-op) - split_k));
+    const float mx = a.means[3 * s], my = a.means[3 * s + 1], mz = a.means[3 * s + 2];
+    a.means[3 * s] = mx - dx; a.means[3 * s + 1] = my - dy; a.means[3 * s + 2] = mz - dz;
+    a.means[3 * d] = mx + dx; a.means[3 * d + 1] = my + dy; a.means[3 * d + 2] = mz + dz;
+    a.scales[3 * s] = nx; a.scales[3 * s + 1] = ny; a.scales[3 * s + 2] = nz;
+    a.scales[3 * d] = nx; a.scales[3 * d + 1] = ny; a.scales[3 * d + 2] = nz;
+    a.opacs[s] = new_op; a.opacs[d] = new_op;
+    ((float4*)a.quats)[d] = q;
+    // appearance: copied
+    for (int k = 0; k < 3; ++k) a.dc[3 * d + k] = a.dc[3 * s + k];
+    if (a.sh) for (int k = 0; k < 45; ++k) a.sh[45 * d + k] = a.sh[45 * s + k];
+    if (a.sh_value_bits != 32 && a.sh_value_packed) {
+        // decode with the source block's bounds, encode against the destination block's CURRENT bounds (clipping is accepted:
+        // the next optimiser pass recomputes the bounds; DensifyQuantCopy.cuh:37-77)
+        const float qmax = a.sh_value_bits == 16 ? 65535.0f : 255.0f;
+        for (int k = 0; k < 45; ++k) {
+            const int64_t cs = 45 * s + k, cd = 45 * d + k;
+            const float2 ms = a.sh_value_bounds[cs >> 8], md = a.sh_value_bounds[cd >> 8];
+            const float code = a.sh_value_bits == 16 ? (float)((const uint16_t*)a.sh_value_packed)[cs] : (float)a.sh_value_packed[cs];
+            const float v = ms.x + (ms.y - ms.x) * (code * (1.0f / qmax));
+            const float qf = fminf(fmaxf(roundf(qmax * (v - md.x) / fmaxf(md.y - md.x, 1e-30f)), 0.0f), qmax);
+            if (a.sh_value_bits == 16) ((uint16_t*)a.sh_value_packed)[cd] = (uint16_t)qf; else a.sh_value_packed[cd] = (uint8_t)qf;
+        }
+    }
+    // optimiser state of the destination: zero (fp32), or the codes that decode nearest to zero against the current bounds
+    const int width[6] = {3, 4, 3, 1, 3, 45};
+    for (int t = 0; t < 6; ++t)
+        if (a.m1[t]) for (int k = 0; k < width[t]; ++k) { a.m1[t][(int64_t)width[t] * d + k] = 0.f; a.m2[t][(int64_t)width[t] * d + k] = 0.f; }
+    if (a.sh_optim_bits && a.sh_optim_packed) {
+        const float qmax = a.sh_optim_bits == 8 ? 255.0f : 15.0f;
+        for (int k = 0; k < 45; ++k) {
+            const int64_t c = 45 * d + k;
+            const float4 mm = a.sh_optim_bounds[c >> 8];
+            const uint32_t uq = encode_zero(mm.x, mm.y, qmax), sq = encode_zero(mm.z, mm.w, qmax);
+            if (a.sh_optim_bits == 8) { a.sh_optim_packed[2 * c] = (uint8_t)uq; a.sh_optim_packed[2 * c + 1] = (uint8_t)sq; }
+            else a.sh_optim_packed[c] = (uint8_t)((uq & 15u) | ((sq & 15u) << 4));
+        }
+    }
+    if (a.steps) a.steps[d] = 0;
+    if (a.accum) a.accum[d] = a.accum[s];
+}
+
 }  // namespace ssb
 
 extern "C" {
@@ -338,6 +536,113 @@ int ssb_densify_add_noise(int64_t n, float scaler, int32_t revised, const float*
     if (revised) densify_noise_kernel<true><<<grid, kDensifyThreads, 0, (cudaStream_t)stream>>>(n, scaler, d_radii, d_means, d_scales, d_quats, d_opacities);
     else densify_noise_kernel<false><<<grid, kDensifyThreads, 0, (cudaStream_t)stream>>>(n, scaler, d_radii, d_means, d_scales, d_quats, d_opacities);
     SSB_LAUNCHED("densify_noise_kernel");
+    return SSB_OK;
+}
+
+
+static int densify_arrays(const SsbDensifyState* st, ssb::DensifyArrays* a, const char* who) {
+    using namespace ssb;
+    SSB_REQUIRE(st, "%s: NULL state", who);
+    const SsbSplats& p = st->params;
+    SSB_REQUIRE(p.means && p.quats && p.scales && p.opacities && p.features_dc, "%s: parameter arrays missing", who);
+    const bool vq = st->sh.d_value_packed && (st->sh.value_bits == 8 || st->sh.value_bits == 16);
+    SSB_REQUIRE(vq != (p.features_sh != nullptr), "%s: SH values are either fp32 (params.features_sh) or quantised (sh.d_value_packed)", who);
+    SSB_REQUIRE(!vq || st->sh.d_value_bounds, "%s: sh.d_value_bounds is NULL", who);
+    const bool oq = st->sh.d_optim_packed != nullptr;
+    SSB_REQUIRE(!oq || (st->sh.d_optim_bounds && (st->sh.optim_bits == 0 || st->sh.optim_bits == 8 || st->sh.optim_bits == 4)), "%s: bad quantised SH state", who);
+    *a = DensifyArrays{};
+    a->means = p.means; a->quats = p.quats; a->scales = p.scales; a->opacs = p.opacities; a->dc = p.features_dc; a->sh = p.features_sh;
+    float* const m1[6] = {st->m1.means, st->m1.quats, st->m1.scales, st->m1.opacities, st->m1.features_dc, oq ? nullptr : st->m1.features_sh};
+    float* const m2[6] = {st->m2.means, st->m2.quats, st->m2.scales, st->m2.opacities, st->m2.features_dc, oq ? nullptr : st->m2.features_sh};
+    for (int t = 0; t < 6; ++t) {
+        SSB_REQUIRE((m1[t] == nullptr) == (m2[t] == nullptr), "%s: first and second moments must come in pairs", who);
+        a->m1[t] = m1[t]; a->m2[t] = m2[t];
+    }
+    a->sh_optim_packed = st->sh.d_optim_packed; a->sh_optim_bounds = (const float4*)st->sh.d_optim_bounds;
+    a->sh_optim_bits = oq ? (st->sh.optim_bits ? st->sh.optim_bits : 8) : 0;
+    a->sh_value_packed = vq ? (uint8_t*)st->sh.d_value_packed : nullptr; a->sh_value_bounds = (const float2*)st->sh.d_value_bounds;
+    a->sh_value_bits = vq ? st->sh.value_bits : 32;
+    a->accum = (float2*)st->d_accum_buffer; a->steps = st->d_steps;
+    return SSB_OK;
+}
+
+// workspace: keys a/b, vals a/b, dead-splat list, alive flags, chunk counts, the count word, the sort's own scratch
+struct RelocWs { int64_t *keys_a, *keys_b; int32_t *vals_a, *vals_b, *dst, *chunks, *count; uint8_t* alive; void* sort; int64_t sort_bytes, bytes; };
+
+static RelocWs reloc_ws(void* base, int64_t n) {
+    using namespace ssb;
+    RelocWs w{};
+    int64_t off = 0;
+    auto take = [&](int64_t b) { int64_t o = off; off += align_up(b, 256); return base ? (char*)base + o : nullptr; };
+    const int64_t m = n > 0 ? n : 1;
+    w.keys_a = (int64_t*)take(m * 8); w.keys_b = (int64_t*)take(m * 8);
+    w.vals_a = (int32_t*)take(m * 4); w.vals_b = (int32_t*)take(m * 4);
+    w.dst = (int32_t*)take(m * 4); w.alive = (uint8_t*)take(m);
+    w.chunks = (int32_t*)take(ceil_div(m, kRelocChunk) * 4); w.count = (int32_t*)take(8);
+    w.sort_bytes = ssb_sort_workspace_bytes(m);
+    w.sort = take(w.sort_bytes);
+    w.bytes = off;
+    return w;
+}
+
+int64_t ssb_densify_relocate_workspace_bytes(int64_t n_splats) { return reloc_ws(nullptr, n_splats).bytes; }
+
+int ssb_densify_relocate(const SsbDensifyState* state, int64_t cur_n, float min_opacity, float split_opacity_k, uint32_t seed, void* d_workspace,
+                         int64_t workspace_bytes, int32_t* d_num_relocated, void* stream) {
+    using namespace ssb;
+    DensifyArrays a;
+    if (int e = densify_arrays(state, &a, "ssb_densify_relocate")) return e;
+    SSB_REQUIRE(cur_n >= 0 && cur_n < ((int64_t)1 << 30), "ssb_densify_relocate: bad splat count");
+    const float* weights = state->d_sample_score ? state->d_sample_score : state->d_accum_buffer;
+    SSB_REQUIRE(weights, "ssb_densify_relocate: neither d_sample_score nor d_accum_buffer given");
+    SSB_REQUIRE(d_workspace && workspace_bytes >= ssb_densify_relocate_workspace_bytes(cur_n), "ssb_densify_relocate: workspace too small");
+    if (cur_n == 0) { if (d_num_relocated) SSB_CUDA(cudaMemsetAsync(d_num_relocated, 0, 4, (cudaStream_t)stream)); return SSB_OK; }
+    cudaStream_t st = (cudaStream_t)stream;
+    const RelocWs w = reloc_ws(d_workspace, cur_n);
+    const int n_chunks = (int)ceil_div(cur_n, kRelocChunk);
+    reloc_mask_kernel<<<n_chunks, 256, 0, st>>>(cur_n, min_opacity, a, w.alive, w.chunks);
+    SSB_LAUNCHED("reloc_mask_kernel");
+    reloc_scan_kernel<<<1, 1024, 0, st>>>(w.chunks, n_chunks, w.count);
+    SSB_LAUNCHED("reloc_scan_kernel");
+    reloc_list_kernel<<<n_chunks, 256, 0, st>>>(cur_n, w.alive, w.chunks, w.dst);
+    SSB_LAUNCHED("reloc_list_kernel");
+    if (d_num_relocated) SSB_CUDA(cudaMemcpyAsync(d_num_relocated, w.count, 4, cudaMemcpyDeviceToDevice, st));
+    // the draw: every live splat gets a key, the smallest keys win
+    sample_keys_kernel<<<(unsigned)ceil_div(cur_n, 256), 256, 0, st>>>(cur_n, seed, (const float2*)weights, w.alive, w.keys_a, w.vals_a);
+    SSB_LAUNCHED("sample_keys_kernel");
+    int64_t* d_n = (int64_t*)(w.count + 2);       // 8 bytes after the count word, inside its 256-byte slot
+    set_i64_kernel<<<1, 1, 0, st>>>(d_n, cur_n);
+    SSB_LAUNCHED("set_i64_kernel");
+    int32_t sel = 0;
+    if (int e = ssb_sort_pairs_u64(w.keys_a, w.vals_a, w.keys_b, w.vals_b, d_n, cur_n, 32, 64, w.sort, w.sort_bytes, &sel, stream)) return e;
+    const int32_t* drawn = sel ? w.vals_b : w.vals_a;
+    reloc_split_kernel<<<(unsigned)ceil_div(cur_n, 256), 256, 0, st>>>(cur_n, w.count, 0, split_opacity_k, drawn, w.dst, a);
+    SSB_LAUNCHED("reloc_split_kernel");
+    return SSB_OK;
+}
+
+int ssb_densify_add(const SsbDensifyState* state, int64_t cur_n, int64_t num_new, float split_opacity_k, uint32_t seed, void* d_workspace,
+                    int64_t workspace_bytes, void* stream) {
+    using namespace ssb;
+    DensifyArrays a;
+    if (int e = densify_arrays(state, &a, "ssb_densify_add")) return e;
+    SSB_REQUIRE(cur_n >= 0 && num_new >= 0 && num_new <= cur_n && cur_n + num_new < ((int64_t)1 << 30), "ssb_densify_add: bad counts");
+    const float* weights = state->d_sample_score ? state->d_sample_score : state->d_accum_buffer;
+    SSB_REQUIRE(weights, "ssb_densify_add: neither d_sample_score nor d_accum_buffer given");
+    SSB_REQUIRE(d_workspace && workspace_bytes >= ssb_densify_relocate_workspace_bytes(cur_n), "ssb_densify_add: workspace too small");
+    if (num_new == 0) return SSB_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const RelocWs w = reloc_ws(d_workspace, cur_n);
+    sample_keys_kernel<<<(unsigned)ceil_div(cur_n, 256), 256, 0, st>>>(cur_n, seed, (const float2*)weights, nullptr, w.keys_a, w.vals_a);
+    SSB_LAUNCHED("sample_keys_kernel");
+    int64_t* d_n = (int64_t*)(w.count + 2);
+    set_i64_kernel<<<1, 1, 0, st>>>(d_n, cur_n);
+    SSB_LAUNCHED("set_i64_kernel");
+    int32_t sel = 0;
+    if (int e = ssb_sort_pairs_u64(w.keys_a, w.vals_a, w.keys_b, w.vals_b, d_n, cur_n, 32, 64, w.sort, w.sort_bytes, &sel, stream)) return e;
+    const int32_t* drawn = sel ? w.vals_b : w.vals_a;
+    reloc_split_kernel<<<(unsigned)ceil_div(num_new, 256), 256, 0, st>>>(cur_n, nullptr, num_new, split_opacity_k, drawn, nullptr, a);
+    SSB_LAUNCHED("reloc_split_kernel");
     return SSB_OK;
 }
 

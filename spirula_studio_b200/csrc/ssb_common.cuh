@@ -94,6 +94,33 @@ __device__ __forceinline__ CamDev load_cam(const float* __restrict__ viewmats, c
     return c;
 }
 
+// Natural logarithm as a fixed sequence of IEEE single operations (Cephes logf), so that integers derived from it (tile
+// spans, sampling order) are the same on every machine and equal the CPU statement of the same sequence.
+__device__ __forceinline__ float det_logf(float xin) {
+    uint32_t bits = __float_as_uint(xin);
+    int e = (int)((bits >> 23) & 255u) - 127;
+    float m = __uint_as_float((bits & 0x007fffffu) | 0x3f800000u);
+    if (m > 1.41421356f) { m = __fmul_rn(m, 0.5f); e += 1; }
+    float f = __fsub_rn(m, 1.0f);
+    float z = __fmul_rn(f, f);
+    float p = 7.0376836292E-2f;
+    p = __fmul_rn(p, f); p = __fadd_rn(p, -1.1514610310E-1f);
+    p = __fmul_rn(p, f); p = __fadd_rn(p, 1.1676998740E-1f);
+    p = __fmul_rn(p, f); p = __fadd_rn(p, -1.2420140846E-1f);
+    p = __fmul_rn(p, f); p = __fadd_rn(p, 1.4249322787E-1f);
+    p = __fmul_rn(p, f); p = __fadd_rn(p, -1.6668057665E-1f);
+    p = __fmul_rn(p, f); p = __fadd_rn(p, 2.0000714765E-1f);
+    p = __fmul_rn(p, f); p = __fadd_rn(p, -2.4999993993E-1f);
+    p = __fmul_rn(p, f); p = __fadd_rn(p, 3.3333331174E-1f);
+    float fe = (float)e;
+    float y = __fmul_rn(f, z); y = __fmul_rn(y, p);
+    float t = __fmul_rn(-2.12194440e-4f, fe); y = __fadd_rn(y, t);
+    t = __fmul_rn(0.5f, z); y = __fsub_rn(y, t);
+    float r = __fadd_rn(f, y);
+    t = __fmul_rn(0.693359375f, fe); r = __fadd_rn(r, t);
+    return r;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -18,31 +18,6 @@ constexpr int kTilesBlock = 256;
 constexpr int kScanItems = 8;                             // per thread
 constexpr int kScanChunk = kTilesBlock * kScanItems;      // 2048 counts per block
 
-__device__ __forceinline__ float det_logf(float xin) {
-    uint32_t bits = __float_as_uint(xin);
-    int e = (int)((bits >> 23) & 255u) - 127;
-    float m = __uint_as_float((bits & 0x007fffffu) | 0x3f800000u);
-    if (m > 1.41421356f) { m = __fmul_rn(m, 0.5f); e += 1; }
-    float f = __fsub_rn(m, 1.0f);
-    float z = __fmul_rn(f, f);
-    float p = 7.0376836292E-2f;
-    p = __fmul_rn(p, f); p = __fadd_rn(p, -1.1514610310E-1f);
-    p = __fmul_rn(p, f); p = __fadd_rn(p, 1.1676998740E-1f);
-    p = __fmul_rn(p, f); p = __fadd_rn(p, -1.2420140846E-1f);
-    p = __fmul_rn(p, f); p = __fadd_rn(p, 1.4249322787E-1f);
-    p = __fmul_rn(p, f); p = __fadd_rn(p, -1.6668057665E-1f);
-    p = __fmul_rn(p, f); p = __fadd_rn(p, 2.0000714765E-1f);
-    p = __fmul_rn(p, f); p = __fadd_rn(p, -2.4999993993E-1f);
-    p = __fmul_rn(p, f); p = __fadd_rn(p, 3.3333331174E-1f);
-    float fe = (float)e;
-    float y = __fmul_rn(f, z); y = __fmul_rn(y, p);
-    float t = __fmul_rn(-2.12194440e-4f, fe); y = __fadd_rn(y, t);
-    t = __fmul_rn(0.5f, z); y = __fsub_rn(y, t);
-    float r = __fadd_rn(f, y);
-    t = __fmul_rn(0.693359375f, fe); r = __fadd_rn(r, t);
-    return r;
-}
-
 __device__ __forceinline__ float clampf(float x, float a, float b) { return x < a ? a : (x > b ? b : x); }
 __device__ __forceinline__ int clampi(int x, int a, int b) { return x < a ? a : (x > b ? b : x); }
 // float -> int, NaN -> 0, saturating (cvt.rzi.s32.f32)

@@ -156,6 +156,9 @@ SIGNATURES = {
     "ssb_step_get_profile": (C.c_int, [_P, _P, _P]),
     "ssb_launch_count": (_I64, []),
     "ssb_densify_workspace_bytes": (_I64, [_I64]),
+    "ssb_densify_relocate_workspace_bytes": (_I64, [_I64]),
+    "ssb_densify_relocate": (C.c_int, [_P, _I64, _F, _F, C.c_uint32, _P, _I64, _P, _P]),
+    "ssb_densify_add": (C.c_int, [_P, _I64, _I64, _F, C.c_uint32, _P, _I64, _P]),
     "ssb_densify_update_scores": (C.c_int, [_P, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _P]),
     "ssb_densify_add_noise": (C.c_int, [_I64, _F, _I32, _P, _P, _P, _P, _P, _P]),
     "ssb_ckpt_array_header": (C.c_int, [C.c_int, C.c_uint64, _P, C.c_int]),
@@ -264,6 +267,11 @@ class SsbPeerReplicas(C.Structure):
 class SsbShAdamState(C.Structure):
     _fields_ = [("d_optim_packed", C.c_void_p), ("d_optim_bounds", C.c_void_p), ("d_value_packed", C.c_void_p),
                 ("d_value_bounds", C.c_void_p), ("value_bits", C.c_int32), ("optim_bits", C.c_int32)]
+
+
+class SsbDensifyState(C.Structure):
+    _fields_ = [("params", SsbSplats), ("m1", SsbSplats), ("m2", SsbSplats), ("sh", SsbShAdamState), ("d_accum_buffer", C.c_void_p),
+                ("d_sample_score", C.c_void_p), ("d_steps", C.c_void_p)]
 
 
 # int barrier(void* ctx, void* stream): 0 once every rank has arrived (ordered on the stream), non-zero on failure

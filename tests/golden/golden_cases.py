@@ -193,6 +193,46 @@ DENSIFY_SCORE_RUNS = (
 )
 
 
+DENSIFY_SPLIT = dict(cur_n=800, cap=920, num_new=40, split_k=0.6, min_opacity=0.005, seed=2 * 700)
+
+
+def densify_split_inputs(quant, seed=911):
+    """State of DENSIFY_SPLIT['cap'] splats for the relocation fixtures: about 6 % dead (low opacity, two with a non-finite
+    parameter), scores with a tenth zero, moments that are nowhere zero, per-splat step counters; quant: q16 SH values and
+    the 8-bit joint SH optimiser state (bounds per 256 cells) instead of the fp32 arrays."""
+    from oracle import pyoracle as O
+    cap, cur = DENSIFY_SPLIT["cap"], DENSIFY_SPLIT["cur_n"]
+    rng = np.random.default_rng(seed)
+    st = dict(
+        means=(rng.standard_normal((cap, 3)) * 2.0).astype(np.float32), quats=rng.standard_normal((cap, 4)).astype(np.float32),
+        scales=(rng.standard_normal((cap, 3)) * 0.6 - 3.0).astype(np.float32), opacities=(rng.standard_normal(cap) * 2.0 - 1.0).astype(np.float32),
+        features_dc=rng.standard_normal((cap, 3)).astype(np.float32), features_sh=(rng.standard_normal((cap, 45)) * 0.1).astype(np.float32),
+        accum=np.stack([rng.random(cap) ** 2, rng.integers(1, 6, cap)], axis=1).astype(np.float32),
+        steps=rng.integers(1, 500, cap).astype(np.int32))
+    st["opacities"][rng.random(cap) < 0.05] = -7.0
+    st["means"][17, 1] = np.inf
+    st["scales"][123, 0] = np.nan
+    st["accum"][rng.random(cap) < 0.1, 0] = 0.0
+    st["weights"] = st["accum"].copy()
+    st["weights"][:, 0] = st["weights"][:, 0] ** 0.5
+    for a, w in (("means", 3), ("quats", 4), ("scales", 3), ("opacities", 1), ("features_dc", 3), ("features_sh", 45)):
+        shape = (cap, w) if w > 1 else (cap,)
+        st["m1_" + a] = (rng.standard_normal(shape) * 1e-3 + 2e-3).astype(np.float32)
+        st["m2_" + a] = (rng.random(shape) * 1e-5 + 1e-7).astype(np.float32)
+    for a in ("means", "quats", "scales", "opacities", "features_dc", "features_sh", "accum", "steps", "weights"):
+        st[a][cur:] = 0                                  # slots past the current count are empty
+    if quant:
+        packed, bounds = O.quant_encode(st["features_sh"], 16)
+        st.update(sh_value_packed=packed.copy(), sh_value_bounds=bounds.copy(), sh_value_bits=16)
+        blocks = (cap * 45 + 255) // 256
+        ob = np.stack([-rng.random(blocks) * 3 - 0.1, rng.random(blocks) * 3 + 0.1, rng.random(blocks) * 2, rng.random(blocks) * 5 + 20], axis=1)
+        ob[::5, 0] = 0.2                                 # blocks whose u range does not contain zero: the zero code saturates
+        ob[::7, 2] = 0.0
+        st.update(sh_optim_packed=rng.integers(0, 256, cap * 45 * 2, dtype=np.uint8), sh_optim_bounds=ob.astype(np.float32), sh_optim_bits=8)
+        st["features_sh"] = st["m1_features_sh"] = st["m2_features_sh"] = None
+    return st
+
+
 def adam_inputs():
     n = 700
     cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=n)

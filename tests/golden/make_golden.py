@@ -24,8 +24,8 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, HERE)
 
-from golden_cases import (ACCUM_CASES, CASES, DENSIFY_SCORE_RUNS, LIVE_TILE_CASE, LOSS_MAP_WEIGHT, MULTI_SCALE_RUNS, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
-                          build_case, densify_inputs, loss_inputs, loss_map_base, loss_masks, quant_sh_inputs, raster_cotangents, tile_masks)  # noqa: E402
+from golden_cases import (ACCUM_CASES, CASES, DENSIFY_SCORE_RUNS, DENSIFY_SPLIT, LIVE_TILE_CASE, LOSS_MAP_WEIGHT, MULTI_SCALE_RUNS, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
+                          build_case, densify_inputs, densify_split_inputs, loss_inputs, loss_map_base, loss_masks, quant_sh_inputs, raster_cotangents, tile_masks)  # noqa: E402
 
 DEV = "cuda:0"
 
@@ -247,6 +247,39 @@ def run_densify(ref, out_dir):
                                         P(opacs)), "add_noise")
         out[f"noise{revised}_means"] = means.cpu().numpy()
     np.savez_compressed(os.path.join(out_dir, "densify.npz"), **out)
+
+
+SPLIT_ATTRS = ("means", "quats", "scales", "opacities", "features_dc", "features_sh")
+SPLIT_KEYS = (SPLIT_ATTRS + tuple("m1_" + a for a in SPLIT_ATTRS) + tuple("m2_" + a for a in SPLIT_ATTRS) +
+              ("accum", "steps", "sh_optim_packed", "sh_value_packed"))
+
+
+def run_densify_split(ref, out_dir):
+    """The reference's relocation of dead splats and its growth step (long-axis split, weighted draw without replacement), fp32
+    SH and quantised SH (q16 values + 8-bit joint state): the whole state after the relocation and after the growth."""
+    out = {}
+    D = DENSIFY_SPLIT
+    for quant in (False, True):
+        st = densify_split_inputs(quant)
+        d = {k: (dev(v) if isinstance(v, np.ndarray) else None) for k, v in st.items() if not isinstance(v, int)}
+        ptr = lambda k: P(d.get(k))
+        def call(mode, seed):
+            args = [mode, C.c_int64(D["cur_n"] if mode == 0 else D["cur_n"]), C.c_int64(D["num_new"]), C.c_int64(D["cap"]), C.c_float(D["min_opacity"]),
+                    C.c_float(D["split_k"]), C.c_uint32(seed), ptr("weights")]
+            args += [ptr(a) for a in SPLIT_ATTRS] + [ptr("m1_" + a) for a in SPLIT_ATTRS] + [ptr("m2_" + a) for a in SPLIT_ATTRS]
+            args += [ptr("sh_optim_packed"), ptr("sh_optim_bounds"), st.get("sh_optim_bits", 32), ptr("sh_value_packed"), ptr("sh_value_bounds"),
+                     st.get("sh_value_bits", 32), ptr("accum"), ptr("steps")]
+            check(ref.ref_densify_split(*args), "ref_densify_split")
+        tag = "q" if quant else "f"
+        call(0, D["seed"])
+        for k in SPLIT_KEYS:
+            if d.get(k) is not None:
+                out[f"{tag}_reloc_{k}"] = d[k].cpu().numpy()
+        call(1, D["seed"] + 1)
+        for k in SPLIT_KEYS:
+            if d.get(k) is not None:
+                out[f"{tag}_add_{k}"] = d[k].cpu().numpy()
+    np.savez_compressed(os.path.join(out_dir, "densify_split.npz"), **out)
 
 
 def run_adam(ref, out_dir):
@@ -504,6 +537,8 @@ def main():
         run_loss_masked(ref, out_dir)
     if not only or "loss_multi" in only:
         run_loss_multi(ref, out_dir)
+    if not only or "densify_split" in only:
+        run_densify_split(ref, out_dir)
     if not only or "densify" in only:
         run_densify(ref, out_dir)
     if not only or "tiles_live" in only:

@@ -430,3 +430,58 @@ def test_densify_per_step_vs_reference(oracle):
         moved = inp["means"].copy()
         z = oracle.densify_add_noise(moved, inp["log_scales"], inp["quats"], inp["logit_opacs"], scaler, revised, radii=inp["radii"])
         D.check_noise(inp, moved, scaler, revised, reference_moved=gold[f"noise{revised}_means"])
+
+
+@pytest.mark.parametrize("quant", [False, True])
+def test_densify_relocation_and_growth_vs_reference(oracle, quant):
+    """Relocation of the dead splats and the growth step (long-axis split, weighted draw without replacement) against the state
+    the reference's kernels leave: same dead set, draws that agree except at the cut, same treatment of every source and slot."""
+    import copy
+    from golden_cases import DENSIFY_SPLIT as D, densify_split_inputs
+    from tests import densify_util as U
+    gold = load("densify_split")
+    tag = "q" if quant else "f"
+    st = densify_split_inputs(quant)
+    before = copy.deepcopy(st)
+    dead = U.dead_mask(st, D["cur_n"], D["min_opacity"])
+    assert 20 < dead.sum() < 120
+
+    def ref_state(phase):
+        out = {k[len(tag) + len(phase) + 2:]: gold[k] for k in gold if k.startswith(f"{tag}_{phase}_")}
+        for k, v in out.items():
+            if before.get(k) is not None and isinstance(before[k], np.ndarray):
+                out[k] = v.reshape(before[k].shape)
+        return out
+    src, dst = oracle.densify_split(0, st, D["cur_n"], D["seed"], D["split_k"], D["min_opacity"])
+    assert np.array_equal(dst, np.flatnonzero(dead))
+    ref = ref_state("reloc")
+    # the reference's dead set: the slots whose rotation changed
+    assert set(np.flatnonzero(np.any(ref["quats"] != before["quats"], axis=1)).tolist()) <= set(dst.tolist())
+    U.check_split_state(before, st, ref, D["cur_n"], 0, 0, dead, quant)
+    mid = ref            # the growth step continues from the reference's state, so both sides start equal
+    st2 = copy.deepcopy(mid)
+    st2["weights"] = before["weights"]
+    for k in ("sh_optim_bounds", "sh_value_bounds", "sh_optim_bits", "sh_value_bits"):
+        if k in before:
+            st2[k] = before[k]
+    for k in U.SPLIT_ATTRS:
+        for pre in ("", "m1_", "m2_"):
+            st2.setdefault(pre + k, None)
+    mid_copy = copy.deepcopy(st2)
+    oracle.densify_split(1, st2, D["cur_n"], D["seed"] + 1, D["split_k"], num_new=D["num_new"])
+    U.check_split_state(mid_copy, st2, ref_state("add"), D["cur_n"], D["cur_n"], D["num_new"], None, quant)
+
+
+def test_weighted_draw_is_the_smallest_keys(oracle):
+    """The draw: k smallest keys w / log(1 - u), zero weights last, masked splats never while enough others remain; and it is
+    proportional to the weights (frequency of a heavy half against a light half over many seeds)."""
+    rng = np.random.default_rng(3)
+    n = 600
+    w = np.stack([rng.random(n), np.ones(n)], axis=1).astype(np.float32)
+    w[:50, 0] = 0.0
+    alive = np.ones(n, np.uint8); alive[100:130] = 0
+    got = oracle.weighted_sample(w, 42, 200, alive)
+    assert len(set(got.tolist())) == 200 and not (set(got.tolist()) & set(range(50))) and not (set(got.tolist()) & set(range(100, 130)))
+    w2 = np.ones((n, 2), np.float32); w2[: n // 2, 0] = 4.0
+    heavy = sum((oracle.weighted_sample(w2, seed, 60) < n // 2).sum() for seed in range(200)) / (200 * 60)
+    assert 0.72 < heavy < 0.84           # 4 : 1 weights, 10 % drawn: about 0.78

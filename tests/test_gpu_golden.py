@@ -551,3 +551,86 @@ def test_densify_per_step_vs_reference(lib, U):
         L.check(lib.ssb_densify_add_noise(n, scaler, revised, L.ptr(radii), L.ptr(again), L.ptr(scales), L.ptr(quats), L.ptr(opacs), None))
         torch.cuda.synchronize()
         assert torch.equal(again, moved)                       # a function of its input
+
+
+def _densify_state(lib, U, st):
+    """Device copies of a densify_split_inputs() state and the SsbDensifyState over them."""
+    d = {k: (U.dev(v) if isinstance(v, np.ndarray) else None) for k, v in st.items() if not isinstance(v, int)}
+    sp = lambda pre: L.splats_struct({a: d.get(pre + a) for a in ("means", "quats", "scales", "opacities", "features_dc", "features_sh")})
+    ds = L.SsbDensifyState()
+    ds.params, ds.m1, ds.m2 = sp(""), sp("m1_"), sp("m2_")
+    ds.sh = L.SsbShAdamState(d["sh_optim_packed"].data_ptr() if d.get("sh_optim_packed") is not None else None,
+                             d["sh_optim_bounds"].data_ptr() if d.get("sh_optim_bounds") is not None else None,
+                             d["sh_value_packed"].data_ptr() if d.get("sh_value_packed") is not None else None,
+                             d["sh_value_bounds"].data_ptr() if d.get("sh_value_bounds") is not None else None,
+                             st.get("sh_value_bits", 32), st.get("sh_optim_bits", 0))
+    ds.d_accum_buffer, ds.d_sample_score, ds.d_steps = d["accum"].data_ptr(), d["weights"].data_ptr(), d["steps"].data_ptr()
+    return d, ds
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("quant", [False, True])
+def test_densify_relocation_and_growth_vs_reference(lib, U, oracle, quant):
+    """ssb_densify_relocate / ssb_densify_add: exactly the oracle's result (same draw, same slots), and the reference's kernels'
+    state up to the draw's cut and the reference's own slot order."""
+    import copy
+    from golden_cases import DENSIFY_SPLIT as D, densify_split_inputs
+    from tests import densify_util as DU
+    gold = load("densify_split")
+    tag = "q" if quant else "f"
+    st = densify_split_inputs(quant)
+    before = copy.deepcopy(st)
+    dead = DU.dead_mask(st, D["cur_n"], D["min_opacity"])
+    d, ds = _densify_state(lib, U, st)
+    ws_bytes = lib.ssb_densify_relocate_workspace_bytes(D["cap"])
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=U.DEV)
+    n_dead = torch.full((1,), -1, dtype=torch.int32, device=U.DEV)
+
+    def host_state():
+        out = {k: (t.cpu().numpy().reshape(before[k].shape) if t is not None else None) for k, t in d.items()}
+        out.update({k: v for k, v in st.items() if isinstance(v, int)})
+        return out
+
+    def ref_state(phase):
+        out = {k[len(tag) + len(phase) + 2:]: gold[k] for k in gold if k.startswith(f"{tag}_{phase}_")}
+        return {k: (v.reshape(before[k].shape) if isinstance(before.get(k), np.ndarray) else v) for k, v in out.items()}
+
+    def same_as_oracle(ours, want):
+        for k, v in want.items():
+            if isinstance(v, np.ndarray) and k not in ("weights",):
+                if v.dtype.kind == "f":
+                    assert np.allclose(ours[k], v, rtol=2e-5, atol=2e-6, equal_nan=True), k
+                elif k in ("sh_value_packed",):
+                    assert np.abs(ours[k].view(np.uint16).astype(np.int64) - v.view(np.uint16).astype(np.int64)).max() <= 1, k
+                else:
+                    assert np.array_equal(ours[k], v), k
+
+    L.check(lib.ssb_densify_relocate(C.byref(ds), D["cur_n"], D["min_opacity"], D["split_k"], D["seed"], L.ptr(ws), ws_bytes, L.ptr(n_dead), None))
+    torch.cuda.synchronize()
+    assert n_dead.item() == dead.sum()
+    ours = host_state()
+    want = copy.deepcopy(before)
+    oracle.densify_split(0, want, D["cur_n"], D["seed"], D["split_k"], D["min_opacity"])
+    same_as_oracle(ours, want)
+    DU.check_split_state(before, ours, ref_state("reloc"), D["cur_n"], 0, 0, dead, quant)
+    mid = copy.deepcopy(ours)
+    L.check(lib.ssb_densify_add(C.byref(ds), D["cur_n"], D["num_new"], D["split_k"], D["seed"] + 1, L.ptr(ws), ws_bytes, None))
+    torch.cuda.synchronize()
+    ours2 = host_state()
+    want2 = copy.deepcopy(want)
+    oracle.densify_split(1, want2, D["cur_n"], D["seed"] + 1, D["split_k"], num_new=D["num_new"])
+    same_as_oracle(ours2, want2)
+    # against the reference: its growth step started from ITS relocated state, so compare structure slot by slot on its own terms
+    ref_mid, ref_add = ref_state("reloc"), ref_state("add")
+    for k in ("weights", "sh_optim_bounds", "sh_value_bounds"):
+        if before.get(k) is not None:
+            ref_mid[k] = before[k]
+    st_ref = copy.deepcopy(ref_mid)
+    for k in DU.SPLIT_ATTRS:
+        for pre in ("", "m1_", "m2_"):
+            st_ref.setdefault(pre + k, None)
+    st_ref.update({k: v for k, v in st.items() if isinstance(v, int)})
+    base = copy.deepcopy(st_ref)
+    oracle.densify_split(1, st_ref, D["cur_n"], D["seed"] + 1, D["split_k"], num_new=D["num_new"])
+    DU.check_split_state(base, st_ref, ref_add, D["cur_n"], D["cur_n"], D["num_new"], None, quant)
+    DU.check_split_state(mid, ours2, ours2, D["cur_n"], D["cur_n"], D["num_new"], None, quant)

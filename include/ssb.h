@@ -597,6 +597,11 @@ int64_t ssb_step_device_bytes(const SsbStep* step);
  * built here) and the raster backward pass folds it into d_accum_weight [n_splats] (and d_accum_weight_den for
  * SSB_ACCUM_AVG) as ssb_raster_bwd_accum does.  The arrays are combined into across views and calls
  * (EngineTrainStep.cpp:264-272); the caller zeroes them.  Allocates one [H][W] map per lane on first use. */
+/* Makes every view's projection fold the splats' view radii (view_radius_3dgs, src/shaders/projection_utils.slang:1033-1043)
+ * into d_radii [n_splats] by maximum, as ssb_project_fwd does with its d_radii argument: the array the scale-agnostic mean
+ * update, the scale clip, the score update and the revised noise read.  The caller zeroes it once per iteration.  NULL: off. */
+int ssb_step_set_radii(SsbStep* step, float* d_radii);
+
 int ssb_step_set_densify(SsbStep* step, int32_t ssim_loss_map_mode, float ssim_loss_map_weight, int32_t accum_mode,
                          float* d_accum_weight, float* d_accum_weight_den);
 

@@ -63,6 +63,7 @@ struct SsbStep {
     float* accum_weight;
     float* accum_weight_den;
     int64_t* max_pairs;       // device: largest per-view pair count since it was last cleared
+    float* radii;             // caller's [n] running maximum of the splats' view radii (ssb_step_set_radii), or nullptr
     // deferred backward (ssb_step_set_fused_backward): every view's aabb and screen-gradient records are kept, and the
     // projection backward of all views runs together with the optimiser, a range of splats at a time
     int def_max_views, def_count, def_last;      // def_last: slice of the last view rendered (for ssb_step_peek)
@@ -148,7 +149,7 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
     int e;
 #define SSB_MARK(k) do { if (ev) SSB_CUDA(cudaEventRecord(ev[k], st)); } while (0)
     SSB_MARK(0);
-    if ((e = ssb_project_fwd(params, shq, n, &cam, aabb, l.depths, nullptr, l.screen, st))) return e;
+    if ((e = ssb_project_fwd(params, shq, n, &cam, aabb, l.depths, s->radii, l.screen, st))) return e;
     SSB_MARK(1);
     // counts + scan + scatter are reported as the key stage, the per-tile sort as the sort stage;
     // the ranges come out of the scan, so that stage is empty
@@ -237,6 +238,13 @@ int ssb_step_set_loss(SsbStep* s, const SsbLossConfig* cfg) {
     s->loss_ws_bytes = std::max(s->loss_ws_bytes, need);
     s->loss_cfg = c;
     s->loss_general = 1;
+    return SSB_OK;
+}
+
+int ssb_step_set_radii(SsbStep* s, float* d_radii) {
+    using namespace ssb;
+    SSB_REQUIRE(s, "ssb_step_set_radii: NULL step");
+    s->radii = d_radii;
     return SSB_OK;
 }
 

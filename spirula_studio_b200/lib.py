@@ -137,6 +137,7 @@ SIGNATURES = {
     "ssb_loss_workspace_bytes": (_I64, [_I32, _I32, _I32, _P]),
     "ssb_loss_multi_scale": (C.c_int, [_P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P, _I64, _P]),
     "ssb_step_set_loss": (C.c_int, [_P, _P]),
+    "ssb_step_set_radii": (C.c_int, [_P, _P]),
     "ssb_step_set_fused_backward": (C.c_int, [_P, _I32]),
     "ssb_step_backward_optimize": (C.c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _P]),
     "ssb_adam_step": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _P, _P]),

@@ -637,3 +637,49 @@ def test_fused_backward_equals_per_view_backward(lib, U, quant):
         assert ((va - vb).abs() > 0.1 * lr).float().mean().item() <= 3e-2
     assert a.check_capacity() == b.check_capacity()
     a.close(); b.close()
+
+
+@pytest.mark.parametrize("quant", [False, True])
+def test_densification_strategy_runs_with_the_trainer(lib, U, quant):
+    """The revised strategy around a Trainer (spirula_studio_b200/densify.py = the host logic of engine_densify_step): scores and
+    noise every iteration, relocation + growth on schedule.  The count follows min(capacity, growth * count), dead splats are
+    replaced, unused slots stay invisible, everything stays finite and the loss keeps falling."""
+    from spirula_studio_b200.trainer import Trainer
+    from spirula_studio_b200.densify import DensifyConfig, Densifier
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=12032, width=176, height=128, n_views=3)
+    cfg.rig, cfg.rig_radius, cfg.log_scale_mu = "ring", 3.0, -3.0
+    if quant:
+        cfg.sh_value_bits, cfg.sh_optim_bits = 16, 8
+    sp = scenes.make_splats(cfg)
+    start = 8000
+    sp["opacities"][:start:17] = -8.0                     # some dead splats among the ones in use
+    vm, K = scenes.make_cameras(cfg)
+    gt = np.stack([scenes.make_target(cfg, v) for v in range(cfg.n_views)])
+    host = tuple(torch.from_numpy(a).pin_memory() for a in (vm, K, gt))
+    tr = Trainer(cfg, sp, device=U.DEV)
+    dc = DensifyConfig(refine_start_iter=4, refine_stop_iter=1000, refine_every=8, growth_factor=1.1, noise_lr=5e5 * 1.6e-4, noise_lr_final=5e5 * 1.6e-6)
+    dn = Densifier(tr, dc, start)
+    steps, losses, counts = 40, [], []
+    for step in range(steps):
+        dn.before_step()
+        losses.append(tr.train_step(*host, cfg.n_views)[2])
+        added = dn.after_step(step, steps)
+        counts.append(dn.count)
+        if step > dc.refine_start_iter and step % dc.refine_every == 0:
+            assert added == min(cfg.n_splats, int(dc.growth_factor * (dn.count - added))) - (dn.count - added)
+            assert dn.num_relocated.item() >= 0
+            assert not dn.accum_buffer.any()
+        else:
+            assert added == 0
+    torch.cuda.synchronize()
+    assert counts[0] == start and counts[-1] == 11712 and counts[-1] <= cfg.n_splats          # 8000 * 1.1^4, floored each time
+    op = tr.params["opacities"]
+    assert (op[dn.count:] == -30.0).all()                                                       # unused slots untouched
+    used = torch.sigmoid(op[:dn.count])
+    assert (used <= dc.min_opacity).float().mean().item() < 0.01                                # the seeded dead splats were replaced
+    for k, t in tr.params.items():
+        if t is not None and not (quant and k == "features_sh"):
+            assert torch.isfinite(t[: dn.count * (t.numel() // cfg.n_splats)]).all(), k
+    assert np.isfinite(losses).all() and np.mean(losses[-5:]) < np.mean(losses[:5])
+    assert dn.radii.max().item() > 0 and dn.accum_buffer[: dn.count, 1].max().item() >= 1
+    tr.close()

@@ -442,6 +442,13 @@ typedef struct SsbAdamExtras {
 int ssb_adam_step_ex(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
                      int64_t first, int64_t count, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream);
 
+/* Replaces fused_adam_step (src/kernels/optim/FusedAppearanceOptim.cu:11-92) on one array of numel floats, `stride` per
+ * splat: Adam with the decoupled-offset L2 term 2 * l2_reg / numel * (max(x - off, 0) + min(x + off, 0)), bias correction from
+ * `step`, or per splat from d_steps [numel / stride] when given.  ssb_adam_step covers the six arrays of a splat set in one
+ * call (and leaves out features_dc when params->features_dc is NULL); this entry is the reference's granularity. */
+int ssb_adam_plain(float* d_param, float* d_grad, float* d_m1, float* d_m2, int64_t numel, int32_t stride, float lr, int32_t step,
+                   const int32_t* d_steps, float l2_reg, float l2_reg_offset, float grad_scale, int32_t zero_grad, void* stream);
+
 /* Replaces fused_adam_step_quantized_value (src/kernels/optim/FusedAppearanceOptim.cu:421-479,
  * kernel :291-418): Adam on SH coefficients whose values live in a QuantizedTensor
  * <value_bits,256> and whose state lives in a QuantizedAdamState<8,256>

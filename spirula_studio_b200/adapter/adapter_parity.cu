@@ -10,6 +10,8 @@
 #include <kernels/raster/RasterizationBwd.cuh>
 #include <kernels/raster/RasterizationFwd.cuh>
 #include <kernels/tile/IntersectTile.cuh>
+#include <kernels/loss/PerPixelLoss.cuh>
+#include <kernels/optim/Optimizer.cuh>
 
 #include <dlfcn.h>
 
@@ -232,6 +234,141 @@ int main(int argc, char** argv) {
     } catch (const std::runtime_error&) { threw = true; }
     report("unsupported distortion tier throws", threw);
     (void)v_w; (void)aw_out;
+
+    // ---- 6. the live-tile map, and the intersection that uses it
+    {
+        typedef int (*RefTileActive)(const bool*, int, int, int, int, int, int32_t*);
+        typedef int (*RefIntersectLive)(uint32_t, uint32_t, uint32_t, uint32_t, const float*, const float*, const float*, const float*, const float*,
+                                        const int32_t*, int64_t*, int64_t*, int64_t, int64_t*, int64_t*, int32_t*, int32_t*, int32_t*, int64_t*, int32_t*);
+        auto ref_tile_active = (RefTileActive)dlsym(ref, "ref_tile_active");
+        auto ref_isect_live = (RefIntersectLive)dlsym(ref, "ref_intersect_tile_live");
+        if (!ref_tile_active || !ref_isect_live) { std::fprintf(stderr, "missing live-tile entry points\n"); return 2; }
+        std::vector<unsigned char> mask((size_t)C * H * W, 1);
+        for (uint32_t c = 0; c < C; ++c)
+            for (uint32_t y = 0; y < H; ++y)
+                for (uint32_t x = W / 2; x < W; ++x) mask[((size_t)c * H + y) * W + x] = (y == H / 3 && x == W - 3) ? 1 : 0;
+        unsigned char* d_mask = upload(mask);
+        const int64_t n_tiles = (int64_t)C * th * tw;
+        int32_t* live_a = device_zeros<int32_t>(n_tiles);
+        int32_t* live_r = device_zeros<int32_t>(n_tiles);
+        compute_tile_active(std::make_tuple((uint64_t)d_mask, (uint32_t)1, std::vector<int64_t>{(int64_t)C, (int64_t)H, (int64_t)W}), (int)C, (int)W, (int)H, live_a);
+        if (ref_tile_active((const bool*)d_mask, (int)C, (int)H, (int)W, (int)W, (int)H, live_r) != 0) return 2;
+        auto la = download(live_a, n_tiles), lr = download(live_r, n_tiles);
+        int64_t n_live = 0;
+        for (auto v : lr) n_live += v;
+        report("live-tile map", la == lr && n_live > 0 && n_live < n_tiles, (double)n_live, (double)n_tiles);
+        auto [ids2, flat2, offs2] = do_intersect_tile_generic(aabb_nd, depths_nd, &ref_screen[0], &ref_screen[2], &ref_screen[3], C,
+                                                              ttv(d_intr, {(int64_t)C, 4}), W, H, nullptr, live_a);
+        int64_t M2 = 0; int32_t sel2 = 0;
+        if (ref_isect_live(C, (uint32_t)N, W, H, r_aabb, r_depths, r_xy, r_conic, r_opac, live_r, r_tps, r_cum, cap, r_ids_a, r_ids_b, r_fl_a, r_fl_b, r_offs,
+                           &M2, &sel2) != 0) return 2;
+        report("live intersection: pair count", (int64_t)ids2.size() == M2 && M2 < M, (double)ids2.size(), (double)M2);
+        report("live intersection: sorted keys", download(ids2.data_ptr(), M2) == download(sel2 ? r_ids_b : r_ids_a, M2));
+        report("live intersection: flatten ids", download(flat2.data_ptr(), M2) == download(sel2 ? r_fl_b : r_fl_a, M2));
+        report("live intersection: tile ranges", download(offs2.data_ptr(), n_tiles) == download(r_offs, n_tiles));
+    }
+
+    // ---- 7. the loss driver: two levels, a mask, the loss map of mode 1
+    {
+        typedef int (*RefLoss)(int, int, int, int, const float*, const float*, const bool*, int, int, float, float, int, float*, float*, float*, float*);
+        auto ref_loss = (RefLoss)dlsym(ref, "ref_multi_scale_loss");
+        if (!ref_loss) { std::fprintf(stderr, "missing ref_multi_scale_loss\n"); return 2; }
+        const int64_t P = (int64_t)C * H * W;
+        std::vector<float> img_a(P * 3), img_b(P * 3);
+        for (auto& v : img_a) v = uf(0.f, 1.f);
+        for (int64_t i = 0; i < P * 3; ++i) img_b[i] = std::min(1.0f, std::max(0.0f, img_a[i] + 0.2f * (uf(0.f, 1.f) - 0.5f)));
+        std::vector<unsigned char> mask((size_t)P, 1);
+        for (int64_t i = 0; i < P; ++i) mask[i] = (i % 7 == 3 || (i / W) % H < H / 5) ? 0 : 1;
+        float *d_a = upload(img_a), *d_b = upload(img_b);
+        unsigned char* d_mask = upload(mask);
+        float *v_ours = device_zeros<float>(P * 3), *v_ref = device_zeros<float>(P * 3), *lm_ours = device_zeros<float>(P), *lm_ref = device_zeros<float>(P);
+        std::array<float, (int)LossWeightIndex::length> weights{};
+        weights[(int)LossWeightIndex::RgbSupL1] = 0.8f;
+        PerPixelGrads grads{};
+        grads.v_render_rgb = ttv(v_ours, {(int64_t)C, H, W, 3});
+        TorchTensorView none((uint64_t)0, 4u, std::vector<int64_t>{0, 0, 0, 0});
+        std::vector<bool> needs(13, false);
+        needs[0] = true;
+        LossValues lv = compute_multi_scale_per_pixel_losses(
+            2, ttv(d_a, {(int64_t)C, H, W, 3}), ttv(d_b, {(int64_t)C, H, W, 3}), none, none, none, none, none, none, none, none, none, none, none,
+            std::make_tuple((uint64_t)d_mask, (uint32_t)1, std::vector<int64_t>{(int64_t)C, (int64_t)H, (int64_t)W, 1}), true, weights, 0.2f, none, needs,
+            (long)C, none, ttv(lm_ours, {(int64_t)C, H, W, 1}), 1, 0.9f, 0.0f, grads);
+        float r_rgb_loss = 0.f, r_ssim = 0.f;
+        if (ref_loss(2, (int)C, (int)H, (int)W, d_a, d_b, (const bool*)d_mask, (int)H, (int)W, 0.8f, 0.2f, 1, v_ref, lm_ref, &r_rgb_loss, &r_ssim) != 0) return 2;
+        auto rv = download(v_ref, P * 3);
+        report("loss driver: colour gradient", frac_bad(download(v_ours, P * 3), rv, 2e-6 * max_abs(rv), 2e-4) <= 1e-3, max_abs(rv));
+        report("loss driver: loss map", frac_bad(download(lm_ours, P), download(lm_ref, P), 2e-5, 1e-4) <= 1e-3);
+        report("loss driver: scalars", std::fabs(lv.rgb_loss - r_rgb_loss) <= 1e-5 * std::fabs(r_rgb_loss) + 1e-7 && std::fabs(lv.ssim - r_ssim) <= 2e-5,
+               lv.rgb_loss, lv.ssim);
+    }
+
+    // ---- 8. the optimiser launch functions
+    {
+        typedef int (*RefGeo)(int64_t, int, float, int, float, float, float, float, float*, float*, float*, float*, float*, float*, float*, float*, float*,
+                              float*, float*, float*, float*, float*, float*, float*);
+        typedef int (*RefPlain)(int64_t, int, float, float, float, float, int, float*, float*, float*, float*);
+        typedef int (*RefQQ)(int64_t, int, float, float, float, int, int, float*, uint8_t*, float*, uint8_t*, float*);
+        auto ref_geo = (RefGeo)dlsym(ref, "ref_adam_geometry");
+        auto ref_plain = (RefPlain)dlsym(ref, "ref_adam_plain");
+        auto ref_qq = (RefQQ)dlsym(ref, "ref_adam_qq");
+        if (!ref_geo || !ref_plain || !ref_qq) { std::fprintf(stderr, "missing optimiser entry points\n"); return 2; }
+        auto noisy = [&](int64_t n, float scale, float shift) { std::vector<float> v(n); for (auto& x : v) x = shift + scale * (uf(0.f, 1.f) - 0.5f); return v; };
+        const int widths[4] = {3, 4, 3, 1};
+        float *p_o[4], *g_o[4], *a_o[4], *b_o[4], *p_r[4], *g_r[4], *a_r[4], *b_r[4];
+        for (int k = 0; k < 4; ++k) {
+            auto p = noisy(N * widths[k], 2.f, 0.f), g = noisy(N * widths[k], 1e-3f, 0.f), a = noisy(N * widths[k], 1e-4f, 0.f), b = noisy(N * widths[k], 1e-8f, 1e-8f);
+            p_o[k] = upload(p); g_o[k] = upload(g); a_o[k] = upload(a); b_o[k] = upload(b);
+            p_r[k] = upload(p); g_r[k] = upload(g); a_r[k] = upload(a); b_r[k] = upload(b);
+        }
+        auto dv3 = [&](float* p) { return DeviceVector<float3>(ttv(p, {N, 3})); };
+        auto dv4 = [&](float* p) { return DeviceVector<float4>(ttv(p, {N, 4})); };
+        auto dv1 = [&](float* p) { return DeviceVector<float>(ttv(p, {N, 1})); };
+        fused_optim_3dgs_geometry(N, dv3(p_o[0]), dv3(g_o[0]), dv3(a_o[0]), dv3(b_o[0]), dv4(p_o[1]), dv4(g_o[1]), dv4(a_o[1]), dv4(b_o[1]), dv3(p_o[2]),
+                                  dv3(g_o[2]), dv3(a_o[2]), dv3(b_o[2]), dv1(p_o[3]), dv1(g_o[3]), dv1(a_o[3]), dv1(b_o[3]), DeviceVector<float3>{},
+                                  DeviceVector<float3>{}, DeviceVector<float>{}, DeviceVector<float>{}, 1e-3f, 2e-3f, 5e-3f, 5e-2f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f,
+                                  0.f, 0.f, false, NonShQuantState{}, GradQuantBuffers{}, 7, DeviceVector<int32_t>{}, 0.25f, true);
+        if (ref_geo(N, 7, 0.25f, 1, 1e-3f, 2e-3f, 5e-3f, 5e-2f, p_r[0], g_r[0], a_r[0], b_r[0], p_r[1], g_r[1], a_r[1], b_r[1], p_r[2], g_r[2], a_r[2], b_r[2],
+                    p_r[3], g_r[3], a_r[3], b_r[3]) != 0) return 2;
+        bool ok = true, zeroed = true;
+        for (int k = 0; k < 4; ++k) {
+            ok = ok && frac_bad(download(p_o[k], N * widths[k]), download(p_r[k], N * widths[k]), 1e-6, 1e-4) <= 1e-3;
+            ok = ok && frac_bad(download(a_o[k], N * widths[k]), download(a_r[k], N * widths[k]), 1e-9, 1e-4) <= 1e-3;
+            zeroed = zeroed && max_abs(download(g_o[k], N * widths[k])) == 0.f;
+        }
+        report("fused_optim_3dgs_geometry", ok && zeroed);
+        // plain Adam on a [N, 3] array with the DC offset
+        auto p = noisy(N * 3, 6.f, 0.f), g = noisy(N * 3, 1e-3f, 0.f), a = noisy(N * 3, 1e-4f, 0.f), b = noisy(N * 3, 1e-8f, 1e-8f);
+        float *po = upload(p), *go = upload(g), *ao = upload(a), *bo = upload(b), *pr = upload(p), *gr = upload(g), *ar = upload(a), *br = upload(b);
+        auto nd = [&](float* q, int64_t w) { return DeviceTensorFloatND(ttv(q, {N, w, 1})); };
+        fused_adam_step(N, nd(po, 3), nd(go, 3), nd(ao, 3), nd(bo, 3), 2.5e-3f, 5, DeviceVector<int32_t>{}, 0.3f, 0.5f / 0.28209479f, 0.5f, false);
+        if (ref_plain(N * 3, 5, 2.5e-3f, 0.3f, 0.5f / 0.28209479f, 0.5f, 0, pr, gr, ar, br) != 0) return 2;
+        report("fused_adam_step", frac_bad(download(po, N * 3), download(pr, N * 3), 1e-6, 1e-4) <= 1e-3 &&
+                                  frac_bad(download(bo, N * 3), download(br, N * 3), 1e-12, 1e-4) <= 1e-3);
+        // quantised values + quantised state
+        const int64_t cells = N * 45, blocks = (cells + 255) / 256;
+        auto sh = noisy(cells, 0.4f, 0.f), gsh = noisy(cells, 1e-3f, 0.f);
+        std::vector<uint16_t> codes(cells);
+        std::vector<float> vb(blocks * 2), ob(blocks * 4);
+        for (int64_t bl = 0; bl < blocks; ++bl) {
+            float lo = 1e30f, hi = -1e30f;
+            for (int64_t i = bl * 256; i < std::min(cells, bl * 256 + 256); ++i) { lo = std::min(lo, sh[i]); hi = std::max(hi, sh[i]); }
+            vb[2 * bl] = lo; vb[2 * bl + 1] = hi;
+            for (int64_t i = bl * 256; i < std::min(cells, bl * 256 + 256); ++i) codes[i] = (uint16_t)std::lround(65535.0 * (sh[i] - lo) / std::max(hi - lo, 1e-30f));
+            ob[4 * bl] = -0.5f; ob[4 * bl + 1] = 0.5f; ob[4 * bl + 2] = 0.f; ob[4 * bl + 3] = 25.f;
+        }
+        std::vector<uint8_t> state(cells * 2);
+        for (auto& v : state) v = (uint8_t)(uf(0.f, 1.f) * 255.f);
+        float *gq_o = upload(gsh), *gq_r = upload(gsh), *vb_o = upload(vb), *vb_r = upload(vb), *ob_o = upload(ob), *ob_r = upload(ob);
+        uint16_t *c_o = upload(codes), *c_r = upload(codes);
+        uint8_t *s_o = upload(state), *s_r = upload(state);
+        fused_adam_step_quantized_value(N, cells, nd(gq_o, 45), nullptr, nullptr, s_o, (float4*)ob_o, (uint8_t*)c_o, (float2*)vb_o, 2.5e-3f, 3, DeviceVector<int32_t>{},
+                                        0.f, 0.f, 8, 16, 0.5f, false);
+        if (ref_qq(cells, 3, 2.5e-3f, 0.f, 0.5f, 0, 16, gq_r, s_r, ob_r, (uint8_t*)c_r, vb_r) != 0) return 2;
+        auto co = download(c_o, cells), cr = download(c_r, cells);
+        int64_t off = 0;
+        for (int64_t i = 0; i < cells; ++i) off += std::abs((int)co[i] - (int)cr[i]) > 1;
+        report("fused_adam_step_quantized_value", off <= cells / 1000 && frac_bad(download(vb_o, blocks * 2), download(vb_r, blocks * 2), 1e-7, 1e-5) <= 1e-3, (double)off);
+    }
     std::printf(g_failures ? "adapter_parity: %d check(s) FAILED\n" : "adapter_parity: all checks passed\n", g_failures);
     return g_failures ? 1 : 0;
 }

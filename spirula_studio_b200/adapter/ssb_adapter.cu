@@ -10,6 +10,11 @@
 //   do_intersect_tile_generic      (src/kernels/tile/IntersectTile.cuh:24-40)        -> ssb_screen_pack + ssb_intersect_tiles_live
 //   rasterize_to_pixels_3dgs_fwd   (src/kernels/raster/RasterizationFwd.cuh:16-37)    -> ssb_screen_pack + ssb_raster_fwd
 //   rasterize_to_pixels_3dgs_bwd   (src/kernels/raster/RasterizationBwd.cuh:18-48)    -> ssb_raster_bwd_accum + unpack of the gradient records
+//   compute_multi_scale_per_pixel_losses (src/kernels/loss/PerPixelLoss.cuh:160-189)  -> ssb_loss_multi_scale (colour terms only)
+//   fused_optim_3dgs_geometry      (src/kernels/optim/Optimizer.cuh:120-144)         -> ssb_adam_step_ex without features_dc
+//   fused_adam_step                (src/kernels/optim/Optimizer.cuh:147-158)         -> ssb_adam_plain
+//   fused_adam_step_quantized      (src/kernels/optim/Optimizer.cuh:169-181)         -> ssb_adam_step_sh_quantized_ex, fp32 values
+//   fused_adam_step_quantized_value (src/kernels/optim/Optimizer.cuh:184-205)        -> ssb_adam_step_sh_quantized_ex
 //
 // Outputs are views into the reference's process-global DevicePool under the reference's own PoolSlots, sized exactly as
 // the reference sizes them (the pair count is read back to the host where the reference reads it back), so callers see
@@ -23,6 +28,8 @@
 #include <kernels/raster/RasterizationBwd.cuh>
 #include <kernels/raster/RasterizationFwd.cuh>
 #include <kernels/tile/IntersectTile.cuh>
+#include <kernels/loss/PerPixelLoss.cuh>
+#include <kernels/optim/Optimizer.cuh>
 
 #include <stdexcept>
 #include <string>
@@ -253,4 +260,117 @@ std::tuple<std::vector<DeviceTensorFloatND>, std::vector<DeviceTensorFloatND>, D
         ssb_check(ssb_screen_unpack_add(v_rec, m, v[0].data_ptr(), v[1].data_ptr(), v[2].data_ptr(), v[3].data_ptr(), v[4].data_ptr(), nullptr));
     }
     return std::make_tuple(v_splats_w.value(), v_splats_s.value(), o_accum_weight);
+}
+
+
+// ---- loss ---------------------------------------------------------------------------------------------------------------
+
+LossValues compute_multi_scale_per_pixel_losses(
+    int num_loss_scales, TorchTensorView render_rgb, TorchTensorView ref_rgb, TorchTensorView render_depth, TorchTensorView ref_depth,
+    TorchTensorView render_normal, TorchTensorView depth_normal, TorchTensorView ref_normal, TorchTensorView render_Ts, TorchTensorView rgb_dist,
+    TorchTensorView depth_dist, TorchTensorView normal_dist, TorchTensorView median_depth, TorchTensorView median_normal, TorchTensorView ref_alpha,
+    bool has_mask, const std::array<float, (int)LossWeightIndex::length> loss_weights, const float w_ssim, TorchTensorView v_losses,
+    std::vector<bool> needs_input_grad, long num_train_images, TorchTensorView camera_indices, TorchTensorView loss_map_out, int loss_map_mode,
+    float robust_edge_aware_quantile, float nms_falloff, PerPixelGrads& grads_out) {
+    (void)render_depth; (void)ref_depth; (void)render_normal; (void)depth_normal; (void)ref_normal; (void)render_Ts; (void)rgb_dist; (void)depth_dist;
+    (void)normal_dist; (void)median_depth; (void)median_normal; (void)v_losses; (void)num_train_images; (void)robust_edge_aware_quantile; (void)nms_falloff;
+    // the library computes the colour terms; every other term must be switched off by its weight
+    for (int i = 0; i < (int)LossWeightIndex::length; ++i)
+        if (i != (int)LossWeightIndex::RgbSupL1 && loss_weights[i] != 0.0f) unsupported("a loss term other than RGB L1 and SSIM");
+    if (std::get<0>(camera_indices)) unsupported("per-camera loss bookkeeping (camera_indices)");
+    for (size_t i = 1; i < needs_input_grad.size(); ++i)
+        if (needs_input_grad[i]) unsupported("a gradient other than the rendered colour's");
+    if (needs_input_grad.empty() || !needs_input_grad[0] || !std::get<0>(grads_out.v_render_rgb)) unsupported("a loss call without the colour gradient");
+    const auto& shp = std::get<2>(render_rgb);
+    const int32_t B = (int32_t)shp[0], H = (int32_t)shp[1], W = (int32_t)shp[2];
+    SsbLossConfig cfg{};
+    cfg.w_l1 = loss_weights[(int)LossWeightIndex::RgbSupL1];
+    cfg.w_ssim = w_ssim;
+    cfg.num_scales = num_loss_scales;
+    cfg.loss_map_mode = std::get<0>(loss_map_out) ? loss_map_mode : 0;
+    if (has_mask && std::get<0>(ref_alpha)) {
+        const auto& ms = std::get<2>(ref_alpha);
+        cfg.d_mask = (const uint8_t*)std::get<0>(ref_alpha);          // bool, one byte each
+        cfg.mask_h = (int32_t)ms[1];
+        cfg.mask_w = (int32_t)ms[2];
+    }
+    const int64_t ws_bytes = ssb_loss_workspace_bytes(B, H, W, &cfg);
+    if (ws_bytes < 0) ssb_check((int)ws_bytes);
+    void* ws = scratch<unsigned char>("loss_workspace", ws_bytes, VramCategory::Image);
+    float* d_losses = scratch<float>("loss_scalars", 4, VramCategory::Image);
+    ssb_check(ssb_loss_multi_scale((const float*)std::get<0>(render_rgb), (const float*)std::get<0>(ref_rgb), B, H, W, &cfg,
+                                   (float*)std::get<0>(grads_out.v_render_rgb), d_losses, (float*)std::get<0>(loss_map_out), ws, ws_bytes, nullptr));
+    // The reference hands back the scalars of the previous call without waiting (PerPixelLoss.cu:1346-1372); the adapter waits
+    // for this call's instead, which a caller that only displays them cannot tell apart from a faster GPU.
+    float h[3] = {0.f, 0.f, 0.f};
+    backend::memcpy_sync(h, d_losses, sizeof(h), backend::MemcpyKind::DeviceToHost);
+    LossValues out{};
+    out.rgb_loss = cfg.w_l1 * h[0];
+    out.ssim = h[1];
+    return out;
+}
+
+// ---- optimiser ----------------------------------------------------------------------------------------------------------
+
+void fused_optim_3dgs_geometry(
+    int64_t num_splats, DeviceVector<float3> means, DeviceVector<float3> v_means, DeviceVector<float3> g1_means, DeviceVector<float3> g2_means,
+    DeviceVector<float4> quats, DeviceVector<float4> v_quats, DeviceVector<float4> g1_quats, DeviceVector<float4> g2_quats, DeviceVector<float3> scales,
+    DeviceVector<float3> v_scales, DeviceVector<float3> g1_scales, DeviceVector<float3> g2_scales, DeviceVector<float> opacities,
+    DeviceVector<float> v_opacities, DeviceVector<float> g1_opacities, DeviceVector<float> g2_opacities, DeviceVector<float3> features_dc,
+    DeviceVector<float3> v_features_dc, DeviceVector<float> radii, DeviceVector<float> densify_score, const float lr_means, const float lr_quats,
+    const float lr_scales, const float lr_opacs, const float lr_features_dc, const float max_gauss_ratio, const float scale_regularization_weight,
+    const float mcmc_opacity_reg_weight, const float mcmc_scale_reg_weight, const float erank_reg_weight, const float erank_reg_weight_s3,
+    const float quat_norm_reg_weight, const float sh_reg_weight, bool use_scale_agnostic_mean, NonShQuantState non_sh, GradQuantBuffers gq, int32_t step,
+    DeviceVector<int32_t> per_splat_steps, float grad_scale, bool zero_grad) {
+    (void)features_dc; (void)v_features_dc; (void)lr_features_dc;       // read only by the quantised-moment path
+    if (non_sh.enabled) unsupported("the 16-bit codec for the non-SH moments");
+    if (gq.means_packed || gq.sh_packed) unsupported("quantised gradients");
+    auto f = [](auto& v) { return (float*)v.data_ptr(); };
+    SsbSplats p{f(means), f(quats), f(scales), f(opacities), nullptr, nullptr};
+    SsbSplats g{f(v_means), f(v_quats), f(v_scales), f(v_opacities), nullptr, nullptr};
+    SsbSplats m1{f(g1_means), f(g1_quats), f(g1_scales), f(g1_opacities), nullptr, nullptr};
+    SsbSplats m2{f(g2_means), f(g2_quats), f(g2_scales), f(g2_opacities), nullptr, nullptr};
+    SsbAdamConfig cfg{lr_means, lr_quats, lr_scales, lr_opacs, 0.f, 0.f, sh_reg_weight, grad_scale, step, zero_grad ? 1 : 0};    // `step` is the bias-correction exponent: the engine passes its step + 1
+    SsbAdamExtras ex{};
+    ex.max_gauss_ratio = max_gauss_ratio; ex.scale_regularization_weight = scale_regularization_weight;
+    ex.mcmc_opacity_reg_weight = mcmc_opacity_reg_weight; ex.mcmc_scale_reg_weight = mcmc_scale_reg_weight;
+    ex.erank_reg_weight = erank_reg_weight; ex.erank_reg_weight_s3 = erank_reg_weight_s3; ex.quat_norm_reg_weight = quat_norm_reg_weight;
+    ex.use_scale_agnostic_mean = use_scale_agnostic_mean ? 1 : 0;
+    ex.d_radii = radii.data_ptr(); ex.d_steps = per_splat_steps.data_ptr(); ex.n_total = num_splats; ex.d_densify_score = densify_score.data_ptr();
+    ssb_check(ssb_adam_step_ex(&p, &g, &m1, &m2, 0, num_splats, &cfg, &ex, nullptr));
+}
+
+void fused_adam_step(int64_t num_splats, DeviceTensorFloatND param, DeviceTensorFloatND grad, DeviceTensorFloatND exp_avg, DeviceTensorFloatND exp_avg_sq,
+                     float lr, int32_t step, DeviceVector<int32_t> per_splat_steps, float l2_reg, float l2_reg_offset, float grad_scale, bool zero_grad) {
+    const int64_t numel = param.numel();
+    if (num_splats <= 0 || numel == 0) return;
+    ssb_check(ssb_adam_plain(param.data_ptr(), grad.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(), numel, (int32_t)(numel / num_splats), lr, step,
+                             per_splat_steps.data_ptr(), l2_reg, l2_reg_offset, grad_scale, zero_grad ? 1 : 0, nullptr));
+}
+
+static SsbAdamConfig sh_config(float lr, int32_t step, float l2_reg, float grad_scale, bool zero_grad) {
+    return SsbAdamConfig{0.f, 0.f, 0.f, 0.f, 0.f, lr, l2_reg, grad_scale, step, zero_grad ? 1 : 0};
+}
+
+void fused_adam_step_quantized(int64_t num_splats, DeviceTensorFloatND param, DeviceTensorFloatND grad, uint8_t* packed, float4* quant_bounds, float lr,
+                               int32_t step, DeviceVector<int32_t> per_splat_steps, float l2_reg, float l2_reg_offset, int bits, float grad_scale,
+                               bool zero_grad) {
+    const int64_t numel = param.numel();
+    if (num_splats <= 0 || numel == 0) return;
+    if (l2_reg != 0.0f && l2_reg_offset != 0.0f) unsupported("an L2 offset in the quantised-state Adam step");
+    const SsbAdamConfig cfg = sh_config(lr, step, l2_reg, grad_scale, zero_grad);
+    ssb_check(ssb_adam_step_sh_quantized_ex(grad.data_ptr(), packed, (float*)quant_bounds, param.data_ptr(), nullptr, 32, bits, 0, numel, numel, &cfg,
+                                            per_splat_steps.data_ptr(), (int32_t)(numel / num_splats), nullptr));
+}
+
+void fused_adam_step_quantized_value(int64_t num_splats, int64_t param_numel, DeviceTensorFloatND grad, const uint8_t* grad_q_packed,
+                                     const float2* grad_q_bounds, uint8_t* optim_packed, float4* optim_bounds, uint8_t* value_packed, float2* value_bounds,
+                                     float lr, int32_t step, DeviceVector<int32_t> per_splat_steps, float l2_reg, float l2_reg_offset, int optim_bits,
+                                     int value_bits, float grad_scale, bool zero_grad) {
+    if (num_splats <= 0 || param_numel == 0) return;
+    if (grad_q_packed || grad_q_bounds) unsupported("quantised gradients");
+    if (l2_reg != 0.0f && l2_reg_offset != 0.0f) unsupported("an L2 offset in the quantised Adam step");
+    const SsbAdamConfig cfg = sh_config(lr, step, l2_reg, grad_scale, zero_grad);
+    ssb_check(ssb_adam_step_sh_quantized_ex(grad.data_ptr(), optim_packed, (float*)optim_bounds, value_packed, (float*)value_bounds, value_bits, optim_bits, 0,
+                                            param_numel, param_numel, &cfg, per_splat_steps.data_ptr(), (int32_t)(param_numel / num_splats), nullptr));
 }

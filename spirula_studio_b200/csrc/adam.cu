@@ -347,6 +347,7 @@ __global__ void __launch_bounds__(256) adam_geometry_kernel(
         }
     }
     const float dc_off = 0.5f / 0.28209479177387814f;
+    if (p.features_dc)        // NULL: the caller updates DC with the plain kernel, as the reference's fp32 path does
 #pragma unroll
     for (int k = 0; k < 3; ++k) {
         int64_t q = 3 * i + k;
@@ -792,6 +793,20 @@ int ssb_adam_step(const SsbSplats* params, const SsbSplats* grads, const SsbSpla
 int ssb_adam_step_ex(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
                      int64_t first, int64_t count, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream) {
     return ssb::adam_step_impl(params, grads, m1, m2, first, count, cfg, extras, nullptr, stream);
+}
+
+int ssb_adam_plain(float* d_param, float* d_grad, float* d_m1, float* d_m2, int64_t numel, int32_t stride, float lr, int32_t step,
+                   const int32_t* d_steps, float l2_reg, float l2_reg_offset, float grad_scale, int32_t zero_grad, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(d_param && d_grad && d_m1 && d_m2, "ssb_adam_plain: NULL argument");
+    SSB_REQUIRE(numel >= 0 && stride > 0 && (d_steps || step >= 1), "ssb_adam_plain: bad sizes or step");
+    if (numel == 0) return SSB_OK;
+    const float ibc1 = d_steps ? 1.f : 1.0f / (1.0f - powf(kBeta1, (float)step)), ibc2 = d_steps ? 1.f : 1.0f / (1.0f - powf(kBeta2, (float)step));
+    const float decay = 2.0f * l2_reg / (float)numel;            // fused_adam_step, src/kernels/optim/FusedAppearanceOptim.cu:85
+    adam_plain_kernel<0><<<(unsigned)ceil_div(ceil_div(numel, 4), 256), 256, 0, (cudaStream_t)stream>>>(
+        d_param, d_grad, d_m1, d_m2, numel, lr * ibc1, ibc2, decay, l2_reg_offset, grad_scale, zero_grad, d_steps, stride, lr, PeerOffsets{});
+    SSB_LAUNCHED("adam_plain_kernel");
+    return SSB_OK;
 }
 
 int ssb_adam_step_sh_quantized(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds,

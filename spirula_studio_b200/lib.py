@@ -140,6 +140,7 @@ SIGNATURES = {
     "ssb_step_set_radii": (C.c_int, [_P, _P]),
     "ssb_step_set_fused_backward": (C.c_int, [_P, _I32]),
     "ssb_step_backward_optimize": (C.c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _P]),
+    "ssb_adam_plain": (C.c_int, [_P, _P, _P, _P, _I64, _I32, _F, _I32, _P, _F, _F, _F, _I32, _P]),
     "ssb_adam_step": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _P, _P]),
     "ssb_adam_step_sh_quantized": (C.c_int, [_P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _P, _P]),
     "ssb_adam_step_ex": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _P, _P, _P]),

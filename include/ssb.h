@@ -442,6 +442,20 @@ typedef struct SsbAdamExtras {
 int ssb_adam_step_ex(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
                      int64_t first, int64_t count, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream);
 
+/* The same update of means, rotations, scales, opacities and DC with their Adam moments kept in 16-bit joint codes:
+ * the non_sh_quant path of fused_optim_3dgs_geometry (src/kernels/optim/FusedGeometryOptim.cu:144-380) on
+ * QuantizedAdamState<16, 256> (src/core/Tensor.h:978-1136; pool slots eng.<array>_qfpbo.q / .qb,
+ * src/core/PoolSlots.h:107-111).  Per array: d_packed = 4 bytes per cell ((u, log-s) as two uint16), cells = width * splats;
+ * d_bounds = one float4 (u min, u max, log-s min, log-s max) per 256 splats.  All-zero buffers are the zero state.  56 bytes of
+ * optimiser state per splat instead of 112.  `first` must be a multiple of 256.  As in the reference, the DC regulariser of
+ * this path is cfg->sh_reg_weight undivided. */
+typedef struct SsbMomentsQ16 {
+    uint8_t* d_packed[5];    /* means, quats, scales, opacities, features_dc */
+    float* d_bounds[5];
+} SsbMomentsQ16;
+int ssb_adam_step_q16(const SsbSplats* params, const SsbSplats* grads, const SsbMomentsQ16* moments, int64_t first, int64_t count,
+                      const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream);
+
 /* Replaces fused_adam_step (src/kernels/optim/FusedAppearanceOptim.cu:11-92) on one array of numel floats, `stride` per
  * splat: Adam with the decoupled-offset L2 term 2 * l2_reg / numel * (max(x - off, 0) + min(x + off, 0)), bias correction from
  * `step`, or per splat from d_steps [numel / stride] when given.  ssb_adam_step covers the six arrays of a splat set in one

@@ -319,6 +319,61 @@ def adam_plain(param, grad, m1, m2, step, lr, l2_reg=0.0, l2_reg_offset=0.0, gra
                                    _p(steps) if steps is not None else None, C.c_int(stride))
 
 
+Q16_ATTRS = (("means", 3), ("quats", 4), ("scales", 3), ("opacities", 1), ("features_dc", 3))
+_EPS = np.float32(1e-15)
+
+
+def q16_decode(packed, bounds, n, width):
+    """Moments (g1, g2) [n, width] from the 16-bit joint codes of QuantizedAdamState<16, 256> with one float4 of bounds per 256
+    splats (src/core/Tensor.h:1034-1068): packed uint16 [n * width, 2] = (u, log-s) codes."""
+    codes = packed.view(np.uint16).reshape(n * width, 2).astype(np.float32)
+    mm = np.repeat(bounds.reshape(-1, 4), 256 * width, axis=0)[: n * width].astype(np.float32)
+    inv = np.float32(1.0 / 65535.0)
+    u = mm[:, 0] + (mm[:, 1] - mm[:, 0]) * (codes[:, 0] * inv)
+    ls = mm[:, 2] + (mm[:, 3] - mm[:, 2]) * (codes[:, 1] * inv)
+    sq = _EPS * np.expm1(ls)
+    return (u * (sq + _EPS)).reshape(n, width).astype(np.float32), (sq * sq).reshape(n, width).astype(np.float32)
+
+
+def q16_encode(g1, g2):
+    """Codes and bounds of moments [n, width]: bounds = per block of 256 splats the min / max of u and of log-s (:1070-1135)."""
+    n, width = g1.shape
+    sq = np.sqrt(np.maximum(g2.reshape(-1), 0)).astype(np.float32)
+    u = (g1.reshape(-1) / (sq + _EPS)).astype(np.float32)
+    ls = np.log1p(sq * np.float32(1e15)).astype(np.float32)
+    blocks = (n + 255) // 256
+    bounds = np.zeros((blocks, 4), np.float32)
+    codes = np.zeros((n * width, 2), np.uint16)
+    for b in range(blocks):
+        sl = slice(b * 256 * width, min(n, (b + 1) * 256) * width)
+        bounds[b] = (u[sl].min(), u[sl].max(), ls[sl].min(), ls[sl].max())
+        ur, sr = max(bounds[b, 1] - bounds[b, 0], _EPS), max(bounds[b, 3] - bounds[b, 2], _EPS)
+        codes[sl, 0] = np.clip(np.round(np.float32(65535.0) * (u[sl] - bounds[b, 0]) / ur), 0, 65535)
+        codes[sl, 1] = np.clip(np.round(np.float32(65535.0) * (ls[sl] - bounds[b, 2]) / sr), 0, 65535)
+    return codes.view(np.uint8).reshape(-1).copy(), bounds.reshape(-1)
+
+
+def adam_geometry_q16(p, g, q, step, lrs, sh_reg_weight=0.0, grad_scale=1.0, zero_grad=0, reg=None, scale_agnostic=False, radii=None, steps=None):
+    """The geometry + DC update with 16-bit moments: q = {attr: (packed, bounds)} is decoded, the fp32 update runs, q is re-encoded
+    (non_sh_quant path, src/kernels/optim/FusedGeometryOptim.cu:144-380; DC regulariser = sh_reg_weight undivided, :343-345)."""
+    n = p["means"].shape[0]
+    m1, m2 = {}, {}
+    for a, w in Q16_ATTRS:
+        m1[a], m2[a] = q16_decode(q[a][0], q[a][1], n, w)
+        if w == 1:
+            m1[a], m2[a] = m1[a].reshape(-1), m2[a].reshape(-1)
+    if reg is not None or scale_agnostic or steps is not None:
+        adam_geometry_ex(p, g, m1, m2, step, lrs, grad_scale, zero_grad, reg=reg, scale_agnostic=scale_agnostic, radii=radii, steps=steps)
+    else:
+        adam_geometry(p, g, m1, m2, step, lrs, grad_scale, zero_grad)
+    numel = n * 3
+    adam_plain(p["features_dc"], g["features_dc"], m1["features_dc"], m2["features_dc"], step, lrs["lr_features_dc"],
+               l2_reg=sh_reg_weight * numel / 2.0, l2_reg_offset=0.5 / 0.28209479177387814, grad_scale=grad_scale, zero_grad=zero_grad,
+               steps=steps, stride=3)
+    for a, w in Q16_ATTRS:
+        q[a] = q16_encode(m1[a].reshape(n, w), m2[a].reshape(n, w))
+
+
 def quant_encode(values, bits):
     values = _f(values).reshape(-1)
     n = values.size

@@ -336,6 +336,48 @@ int main(int argc, char** argv) {
             zeroed = zeroed && max_abs(download(g_o[k], N * widths[k])) == 0.f;
         }
         report("fused_optim_3dgs_geometry", ok && zeroed);
+        // the same function with the moments of all five arrays in 16-bit codes, two steps from the zero state
+        {
+            typedef int (*RefQ16)(int64_t, int, float, int, float, float, float, float, float, float, float*, float*, float*, float*, float*, float*, float*, float*,
+                                  float*, float*, uint8_t* const*, float* const*, const float*, const int32_t*);
+            auto ref_q16 = (RefQ16)dlsym(ref, "ref_adam_geometry_q16");
+            if (!ref_q16) { std::fprintf(stderr, "missing ref_adam_geometry_q16\n"); return 2; }
+            const int w5[5] = {3, 4, 3, 1, 3};
+            const double lr5[5] = {1e-3, 2e-3, 5e-3, 5e-2, 2.5e-3};
+            const int64_t blocks = (N + 255) / 256;
+            float *po[5], *go[5], *pr[5], *gr[5], *bo[5], *br[5];
+            uint8_t *qo[5], *qr[5];
+            for (int k = 0; k < 5; ++k) {
+                auto p = noisy(N * w5[k], 2.f, 0.f);
+                po[k] = upload(p); pr[k] = upload(p);
+                std::vector<uint8_t> zq(N * w5[k] * 4, 0); std::vector<float> zb(blocks * 4, 0.f);
+                qo[k] = upload(zq); qr[k] = upload(zq); bo[k] = upload(zb); br[k] = upload(zb);
+            }
+            bool okq = true, okb = true;      // parameters; bounds of the codes
+            int64_t worst = 0;                // largest code difference: the second step starts from each side's own codes
+            for (int step = 1; step <= 2; ++step) {
+                for (int k = 0; k < 5; ++k) { auto g = noisy(N * w5[k], 1e-3f, 0.f); go[k] = upload(g); gr[k] = upload(g); }
+                NonShQuantState nq;
+                nq.enabled = true;
+                nq.means_packed = qo[0]; nq.quats_packed = qo[1]; nq.scales_packed = qo[2]; nq.opacities_packed = qo[3]; nq.features_dc_packed = qo[4];
+                nq.means_bounds = (float4*)bo[0]; nq.quats_bounds = (float4*)bo[1]; nq.scales_bounds = (float4*)bo[2]; nq.opacities_bounds = (float4*)bo[3];
+                nq.features_dc_bounds = (float4*)bo[4];
+                fused_optim_3dgs_geometry(N, dv3(po[0]), dv3(go[0]), DeviceVector<float3>{}, DeviceVector<float3>{}, dv4(po[1]), dv4(go[1]), DeviceVector<float4>{},
+                                          DeviceVector<float4>{}, dv3(po[2]), dv3(go[2]), DeviceVector<float3>{}, DeviceVector<float3>{}, dv1(po[3]), dv1(go[3]),
+                                          DeviceVector<float>{}, DeviceVector<float>{}, dv3(po[4]), dv3(go[4]), DeviceVector<float>{}, DeviceVector<float>{}, 1e-3f,
+                                          2e-3f, 5e-3f, 5e-2f, 2.5e-3f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.05f, false, nq, GradQuantBuffers{}, step,
+                                          DeviceVector<int32_t>{}, 0.25f, false);
+                if (ref_q16(N, step, 0.25f, 0, 1e-3f, 2e-3f, 5e-3f, 5e-2f, 2.5e-3f, 0.05f, pr[0], gr[0], pr[1], gr[1], pr[2], gr[2], pr[3], gr[3], pr[4], gr[4], qr, br,
+                            nullptr, nullptr) != 0) return 2;
+                for (int k = 0; k < 5; ++k) {
+                    okq = okq && frac_bad(download(po[k], N * w5[k]), download(pr[k], N * w5[k]), 1e-6 + 2e-3 * lr5[k], 1e-4) <= 1e-3;   // a code is worth ~1e-4 of a step
+                    okb = okb && frac_bad(download(bo[k], blocks * 4), download(br[k], blocks * 4), 1e-5, 1e-3) == 0.0;
+                    auto co = download((uint16_t*)qo[k], N * w5[k] * 2), cr = download((uint16_t*)qr[k], N * w5[k] * 2);
+                    for (size_t i = 0; i < co.size(); ++i) worst = std::max<int64_t>(worst, std::llabs((long long)co[i] - (long long)cr[i]));
+                }
+            }
+            report("fused_optim_3dgs_geometry, 16-bit moments", okq && okb && worst <= 4, (double)worst, (double)(okq * 2 + okb));
+        }
         // plain Adam on a [N, 3] array with the DC offset
         auto p = noisy(N * 3, 6.f, 0.f), g = noisy(N * 3, 1e-3f, 0.f), a = noisy(N * 3, 1e-4f, 0.f), b = noisy(N * 3, 1e-8f, 1e-8f);
         float *po = upload(p), *go = upload(g), *ao = upload(a), *bo = upload(b), *pr = upload(p), *gr = upload(g), *ar = upload(a), *br = upload(b);

@@ -322,21 +322,30 @@ void fused_optim_3dgs_geometry(
     const float mcmc_opacity_reg_weight, const float mcmc_scale_reg_weight, const float erank_reg_weight, const float erank_reg_weight_s3,
     const float quat_norm_reg_weight, const float sh_reg_weight, bool use_scale_agnostic_mean, NonShQuantState non_sh, GradQuantBuffers gq, int32_t step,
     DeviceVector<int32_t> per_splat_steps, float grad_scale, bool zero_grad) {
-    (void)features_dc; (void)v_features_dc; (void)lr_features_dc;       // read only by the quantised-moment path
-    if (non_sh.enabled) unsupported("the 16-bit codec for the non-SH moments");
     if (gq.means_packed || gq.sh_packed) unsupported("quantised gradients");
     auto f = [](auto& v) { return (float*)v.data_ptr(); };
-    SsbSplats p{f(means), f(quats), f(scales), f(opacities), nullptr, nullptr};
-    SsbSplats g{f(v_means), f(v_quats), f(v_scales), f(v_opacities), nullptr, nullptr};
-    SsbSplats m1{f(g1_means), f(g1_quats), f(g1_scales), f(g1_opacities), nullptr, nullptr};
-    SsbSplats m2{f(g2_means), f(g2_quats), f(g2_scales), f(g2_opacities), nullptr, nullptr};
-    SsbAdamConfig cfg{lr_means, lr_quats, lr_scales, lr_opacs, 0.f, 0.f, sh_reg_weight, grad_scale, step, zero_grad ? 1 : 0};    // `step` is the bias-correction exponent: the engine passes its step + 1
     SsbAdamExtras ex{};
     ex.max_gauss_ratio = max_gauss_ratio; ex.scale_regularization_weight = scale_regularization_weight;
     ex.mcmc_opacity_reg_weight = mcmc_opacity_reg_weight; ex.mcmc_scale_reg_weight = mcmc_scale_reg_weight;
     ex.erank_reg_weight = erank_reg_weight; ex.erank_reg_weight_s3 = erank_reg_weight_s3; ex.quat_norm_reg_weight = quat_norm_reg_weight;
     ex.use_scale_agnostic_mean = use_scale_agnostic_mean ? 1 : 0;
     ex.d_radii = radii.data_ptr(); ex.d_steps = per_splat_steps.data_ptr(); ex.n_total = num_splats; ex.d_densify_score = densify_score.data_ptr();
+    if (non_sh.enabled) {
+        // moments of all five arrays in 16-bit codes; DC is updated in the same launch with sh_reg_weight as its regulariser
+        SsbSplats p{f(means), f(quats), f(scales), f(opacities), f(features_dc), nullptr};
+        SsbSplats g{f(v_means), f(v_quats), f(v_scales), f(v_opacities), f(v_features_dc), nullptr};
+        SsbMomentsQ16 mom{{non_sh.means_packed, non_sh.quats_packed, non_sh.scales_packed, non_sh.opacities_packed, non_sh.features_dc_packed},
+                          {(float*)non_sh.means_bounds, (float*)non_sh.quats_bounds, (float*)non_sh.scales_bounds, (float*)non_sh.opacities_bounds,
+                           (float*)non_sh.features_dc_bounds}};
+        SsbAdamConfig cfg{lr_means, lr_quats, lr_scales, lr_opacs, lr_features_dc, 0.f, sh_reg_weight, grad_scale, step, zero_grad ? 1 : 0};
+        ssb_check(ssb_adam_step_q16(&p, &g, &mom, 0, num_splats, &cfg, &ex, nullptr));
+        return;
+    }
+    SsbSplats p{f(means), f(quats), f(scales), f(opacities), nullptr, nullptr};
+    SsbSplats g{f(v_means), f(v_quats), f(v_scales), f(v_opacities), nullptr, nullptr};
+    SsbSplats m1{f(g1_means), f(g1_quats), f(g1_scales), f(g1_opacities), nullptr, nullptr};
+    SsbSplats m2{f(g2_means), f(g2_quats), f(g2_scales), f(g2_opacities), nullptr, nullptr};
+    SsbAdamConfig cfg{lr_means, lr_quats, lr_scales, lr_opacs, 0.f, 0.f, sh_reg_weight, grad_scale, step, zero_grad ? 1 : 0};    // `step` is the bias-correction exponent: the engine passes its step + 1
     ssb_check(ssb_adam_step_ex(&p, &g, &m1, &m2, 0, num_splats, &cfg, &ex, nullptr));
 }
 

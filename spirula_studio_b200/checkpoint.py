@@ -9,7 +9,9 @@ table's order:
     world.means .quats .scales .opacities .features_dc   float32, always
     world.features_sh                                    float32, only when SH values are not quantised
     eng.g1_<attr>, eng.g2_<attr>                         Adam moments; the features_sh pair only when the
-                                                         SH optimiser state is not quantised
+                                                         SH optimiser state is not quantised; the other five
+                                                         only when non_sh_optim_bits is 32
+    eng.<attr>_qfpbo.q / .qb                             16-bit joint moments of the five non-SH arrays
     eng.sh_quant.q / .qb                                 8-bit joint SH optimiser state: packed bytes / float bounds
     eng.world.sh_vq8|16.q / .qb                          quantised SH values: packed bytes / float bounds
 
@@ -49,7 +51,7 @@ def state_json(trainer, step, full=True):
         '  "packed": 0',
         f'  "sh_optim_bits": {sh_optim_bits}',
         f'  "sh_value_bits": {cfg.sh_value_bits if trainer.quant else 32}',
-        '  "non_sh_optim_bits": 32',
+        f'  "non_sh_optim_bits": {trainer.non_sh_optim_bits}',
         '  "use_fused_proj_bwd_optim": 0',
         '  "use_per_splat_bias_correction": 0',
         f'  "camera": {{"num": {cfg.n_views}, "width": {cfg.width}, "height": {cfg.height}, '
@@ -67,10 +69,15 @@ def saved_buffers(trainer):
     out = [(f"world.{a}", trainer.params[a], DTYPE_F4) for a in _GEO]
     if not trainer.quant:
         out.append(("world.features_sh", trainer.params["features_sh"], DTYPE_F4))
+    nsq = trainer.non_sh_optim_bits == 16
     for g, mom in (("g1", trainer.m1), ("g2", trainer.m2)):
-        out += [(f"eng.{g}_{a}", mom[a], DTYPE_F4) for a in _GEO]
+        if not nsq:
+            out += [(f"eng.{g}_{a}", mom[a], DTYPE_F4) for a in _GEO]
         if not trainer.quant:
             out.append((f"eng.{g}_features_sh", mom["features_sh"], DTYPE_F4))
+    if nsq:
+        for a in _GEO:
+            out += [(f"eng.{a}_qfpbo.q", trainer.nsq_packed[a], DTYPE_U1), (f"eng.{a}_qfpbo.qb", trainer.nsq_bounds[a], DTYPE_F4)]
     if trainer.quant:
         vq = f"eng.world.sh_vq{trainer.cfg.sh_value_bits}"
         out += [("eng.sh_quant.q", trainer.sh_optim_packed, DTYPE_U1), ("eng.sh_quant.qb", trainer.sh_optim_bounds, DTYPE_F4),
@@ -165,7 +172,7 @@ def load_checkpoint(trainer, input_dir):
         if _json_value(text, "max_num_splats", 0) != trainer.n:
             raise RuntimeError(f"load_checkpoint: max_num_splats mismatch (trainer {trainer.n} vs checkpoint "
                                f"{_json_value(text, 'max_num_splats', 0)})")
-        want = (8 if trainer.quant else 32, trainer.cfg.sh_value_bits if trainer.quant else 32, 32, 0, 0)
+        want = (8 if trainer.quant else 32, trainer.cfg.sh_value_bits if trainer.quant else 32, trainer.non_sh_optim_bits, 0, 0)
         have = tuple(_json_value(text, k, d) for k, d in (("sh_optim_bits", 32), ("sh_value_bits", 32), ("non_sh_optim_bits", 32),
                                                           ("use_per_splat_bias_correction", 0), ("use_fused_proj_bwd_optim", 0)))
         if want != have:

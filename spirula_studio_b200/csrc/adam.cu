@@ -222,13 +222,105 @@ __device__ __forceinline__ void per_splat_reg_grads(const float s[3], float o, c
     }
 }
 
+// Order-preserving map float -> uint32, so min/max run on the integer redux unit.
+__device__ __forceinline__ uint32_t f2ord(float f) {
+    uint32_t b = __float_as_uint(f);
+    return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
+}
+__device__ __forceinline__ float ord2f(uint32_t k) {
+    return __uint_as_float(k ^ ((k >> 31) ? 0x80000000u : 0xffffffffu));
+}
+
+// Block-wide (256 threads) minima of NMIN values and maxima of NMAX values in two barriers:
+// one redux.sync per value in each warp, 8 partials per value through shared memory, then
+// one more redux by the first warp.
+template <int NMIN, int NMAX>
+__device__ __forceinline__ void block_minmax(const float (&vmin)[NMIN], const float (&vmax)[NMAX], float (&omin)[NMIN], float (&omax)[NMAX],
+                                             uint32_t (*sh)[8]) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    uint32_t r[NMIN + NMAX];
+#pragma unroll
+    for (int k = 0; k < NMIN; ++k) r[k] = __reduce_min_sync(0xffffffffu, f2ord(vmin[k]));
+#pragma unroll
+    for (int k = 0; k < NMAX; ++k) r[NMIN + k] = __reduce_max_sync(0xffffffffu, f2ord(vmax[k]));
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < NMIN + NMAX; ++k) sh[k][w] = r[k];
+    }
+    __syncthreads();
+    if (w == 0) {
+#pragma unroll
+        for (int k = 0; k < NMIN + NMAX; ++k) {
+            uint32_t v = sh[k][lane & 7];
+            v = k < NMIN ? __reduce_min_sync(0xffffffffu, v) : __reduce_max_sync(0xffffffffu, v);
+            if (lane == 0) sh[k][0] = v;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < NMIN; ++k) omin[k] = ord2f(sh[k][0]);
+#pragma unroll
+    for (int k = 0; k < NMAX; ++k) omax[k] = ord2f(sh[NMIN + k][0]);
+}
+
 // geometry (means, quats, scales, opacities) + features_dc, one thread per splat.
 // EX adds the per-splat regularisers, the scale-agnostic mean update and per-splat step counters.
-template <bool EX, int PEER>
+// NQ: the moments of the five arrays live in 16-bit joint codes (u = g1 / (sqrt(g2) + eps), log1p(sqrt(g2) / eps)), four bytes per
+// cell, with one float4 of bounds per 256 splats and array (QuantizedAdamState<16, 256>, src/core/Tensor.h:978-1136; the
+// non_sh_quant path of fused_optim_3dgs_geometry_kernel, src/kernels/optim/FusedGeometryOptim.cu:144-380).  A CTA is one block
+// of 256 splats: every thread decodes its splat's 14 moment pairs into shared memory, the update below runs on them unchanged,
+// then the block's new bounds are reduced and the pairs encoded again.
+struct MomentsQ16 { uint8_t* packed[5]; float4* bounds[5]; };   // means, quats, scales, opacities, features_dc
+
+__device__ __forceinline__ void q16_decode(const uint8_t* packed, int64_t cell, float4 mm, float& g1, float& g2) {
+    const uint32_t w = ((const uint32_t*)packed)[cell];
+    const float u = mm.x + (mm.y - mm.x) * ((float)(w & 0xffffu) * (1.0f / 65535.0f));
+    const float ls = mm.z + (mm.w - mm.z) * ((float)(w >> 16) * (1.0f / 65535.0f));
+    const float sq = kAdamEps * expm1f(ls);
+    g1 = u * (sq + kAdamEps);
+    g2 = sq * sq;
+}
+__device__ __forceinline__ void q16_us(float g1, float g2, float& u, float& ls) {
+    const float sq = sqrtf(fmaxf(g2, 0.0f));
+    u = g1 / (sq + kAdamEps);
+    ls = log1pf(sq * (1.0f / kAdamEps));
+}
+__device__ __forceinline__ uint32_t q16_encode(float u, float ls, float4 mm) {
+    const float ur = fmaxf(mm.y - mm.x, kAdamEps), sr = fmaxf(mm.w - mm.z, kAdamEps);
+    const float uq = fminf(fmaxf(roundf(65535.0f * (u - mm.x) / ur), 0.0f), 65535.0f);
+    const float sq = fminf(fmaxf(roundf(65535.0f * (ls - mm.z) / sr), 0.0f), 65535.0f);
+    return (uint32_t)uq | ((uint32_t)sq << 16);
+}
+
+template <bool EX, int PEER, bool NQ = false>
 __global__ void __launch_bounds__(256) adam_geometry_kernel(
     SsbSplats p, SsbSplats g, SsbSplats m1, SsbSplats m2, int64_t first, int64_t count, SsbAdamConfig cfg,
-    float ibc1, float ibc2, float dc_decay, SsbAdamExtras ex, PeerOffsets po) {
+    float ibc1, float ibc2, float dc_decay, SsbAdamExtras ex, PeerOffsets po, MomentsQ16 nq = MomentsQ16{}) {
     int64_t i = first + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    static_assert(!(NQ && PEER), "the quantised moments are built for the single-rank launch");
+    constexpr int kMom = NQ ? 14 * 256 : 4;
+    __shared__ __align__(16) float mom1[kMom], mom2[kMom];
+    __shared__ uint32_t mm_sh[NQ ? 20 : 1][8];
+    if constexpr (NQ) {
+        // layout per array as in global memory, indexed with the splat's own number through moved-back pointers
+        const int64_t blk0 = first + (int64_t)blockIdx.x * 256;
+        float* a = mom1; float* b = mom2;
+        m1.means = a - 3 * blk0; m1.quats = a + 768 - 4 * blk0; m1.scales = a + 1792 - 3 * blk0; m1.opacities = a + 2560 - blk0; m1.features_dc = a + 2816 - 3 * blk0;
+        m2.means = b - 3 * blk0; m2.quats = b + 768 - 4 * blk0; m2.scales = b + 1792 - 3 * blk0; m2.opacities = b + 2560 - blk0; m2.features_dc = b + 2816 - 3 * blk0;
+        if (i < first + count) {
+            const int64_t blk = i >> 8;
+            const int width[5] = {3, 4, 3, 1, 3};
+            float* d1[5] = {m1.means, m1.quats, m1.scales, m1.opacities, m1.features_dc};
+            float* d2[5] = {m2.means, m2.quats, m2.scales, m2.opacities, m2.features_dc};
+#pragma unroll
+            for (int t = 0; t < 5; ++t) {
+                const float4 mm = nq.bounds[t][blk];
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (k < width[t]) q16_decode(nq.packed[t], (int64_t)width[t] * i + k, mm, d1[t][(int64_t)width[t] * i + k], d2[t][(int64_t)width[t] * i + k]);
+            }
+        }
+    }
     // Peer mode: the CTA's 256 splats are contiguous in each array, so their gradients are summed over the ranks
     // with coalesced 16-byte loads into shared memory, each thread then works from there, leaves its updated
     // parameters in the same place, and the CTA stores them into every replica with 16-byte stores.
@@ -361,6 +453,45 @@ __global__ void __launch_bounds__(256) adam_geometry_kernel(
         if (zg) g_own.features_dc[q] = 0.f;
     }
     }   // this thread's splat
+    if constexpr (NQ) {
+        // new bounds of the block (u and log-s ranges per array), then the codes
+        const bool inside = i < first + count;
+        const int width[5] = {3, 4, 3, 1, 3};
+        float* d1[5] = {m1.means, m1.quats, m1.scales, m1.opacities, m1.features_dc};
+        float* d2[5] = {m2.means, m2.quats, m2.scales, m2.opacities, m2.features_dc};
+        float u[14], ls[14], mn[10], mx[10];
+        int c = 0;
+#pragma unroll
+        for (int t = 0; t < 5; ++t) {
+            mn[2 * t] = mn[2 * t + 1] = 1e30f; mx[2 * t] = mx[2 * t + 1] = -1e30f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (k < width[t]) {
+                    u[c] = ls[c] = 0.f;
+                    if (inside) {
+                        q16_us(d1[t][(int64_t)width[t] * i + k], d2[t][(int64_t)width[t] * i + k], u[c], ls[c]);
+                        mn[2 * t] = fminf(mn[2 * t], u[c]); mx[2 * t] = fmaxf(mx[2 * t], u[c]);
+                        mn[2 * t + 1] = fminf(mn[2 * t + 1], ls[c]); mx[2 * t + 1] = fmaxf(mx[2 * t + 1], ls[c]);
+                    }
+                    ++c;
+                }
+        }
+        float omn[10], omx[10];
+        block_minmax<10, 10>(mn, mx, omn, omx, mm_sh);
+        const int64_t blk = (first + (int64_t)blockIdx.x * 256) >> 8;
+        c = 0;
+#pragma unroll
+        for (int t = 0; t < 5; ++t) {
+            const float4 mm = make_float4(omn[2 * t], omx[2 * t], omn[2 * t + 1], omx[2 * t + 1]);
+            if (threadIdx.x == 0) nq.bounds[t][blk] = mm;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (k < width[t]) {
+                    if (inside) ((uint32_t*)nq.packed[t])[(int64_t)width[t] * i + k] = q16_encode(u[c], ls[c], mm);
+                    ++c;
+                }
+        }
+    }
     if constexpr (PEER) {
         __syncthreads();
         shared_to_all<256, PEER>(p.means + 3 * b0, stage, 3 * nb, po);
@@ -426,47 +557,6 @@ __device__ __forceinline__ float sqrt_approx(float x) {
     float r;
     asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
     return r;
-}
-
-// Order-preserving map float -> uint32, so min/max run on the integer redux unit.
-__device__ __forceinline__ uint32_t f2ord(float f) {
-    uint32_t b = __float_as_uint(f);
-    return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
-}
-__device__ __forceinline__ float ord2f(uint32_t k) {
-    return __uint_as_float(k ^ ((k >> 31) ? 0x80000000u : 0xffffffffu));
-}
-
-// Block-wide (256 threads) minima of NMIN values and maxima of NMAX values in two barriers:
-// one redux.sync per value in each warp, 8 partials per value through shared memory, then
-// one more redux by the first warp.
-template <int NMIN, int NMAX>
-__device__ __forceinline__ void block_minmax(const float (&vmin)[NMIN], const float (&vmax)[NMAX], float (&omin)[NMIN], float (&omax)[NMAX],
-                                             uint32_t (*sh)[8]) {
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    uint32_t r[NMIN + NMAX];
-#pragma unroll
-    for (int k = 0; k < NMIN; ++k) r[k] = __reduce_min_sync(0xffffffffu, f2ord(vmin[k]));
-#pragma unroll
-    for (int k = 0; k < NMAX; ++k) r[NMIN + k] = __reduce_max_sync(0xffffffffu, f2ord(vmax[k]));
-    if (lane == 0) {
-#pragma unroll
-        for (int k = 0; k < NMIN + NMAX; ++k) sh[k][w] = r[k];
-    }
-    __syncthreads();
-    if (w == 0) {
-#pragma unroll
-        for (int k = 0; k < NMIN + NMAX; ++k) {
-            uint32_t v = sh[k][lane & 7];
-            v = k < NMIN ? __reduce_min_sync(0xffffffffu, v) : __reduce_max_sync(0xffffffffu, v);
-            if (lane == 0) sh[k][0] = v;
-        }
-    }
-    __syncthreads();
-#pragma unroll
-    for (int k = 0; k < NMIN; ++k) omin[k] = ord2f(sh[k][0]);
-#pragma unroll
-    for (int k = 0; k < NMAX; ++k) omax[k] = ord2f(sh[NMIN + k][0]);
 }
 
 // One CTA of 64 threads = one 256-cell quantisation block, four consecutive cells per thread
@@ -793,6 +883,38 @@ int ssb_adam_step(const SsbSplats* params, const SsbSplats* grads, const SsbSpla
 int ssb_adam_step_ex(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
                      int64_t first, int64_t count, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream) {
     return ssb::adam_step_impl(params, grads, m1, m2, first, count, cfg, extras, nullptr, stream);
+}
+
+int ssb_adam_step_q16(const SsbSplats* params, const SsbSplats* grads, const SsbMomentsQ16* moments, int64_t first, int64_t count,
+                      const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(params && grads && moments && cfg, "ssb_adam_step_q16: NULL argument");
+    SSB_REQUIRE(params->means && params->quats && params->scales && params->opacities && params->features_dc, "ssb_adam_step_q16: parameter arrays missing");
+    SSB_REQUIRE(grads->means && grads->quats && grads->scales && grads->opacities && grads->features_dc, "ssb_adam_step_q16: gradient arrays missing");
+    SSB_REQUIRE(first >= 0 && count >= 0 && first % 256 == 0, "ssb_adam_step_q16: the range must start on a multiple of 256 splats");
+    SSB_REQUIRE(cfg->step >= 1, "ssb_adam_step_q16: step must be >= 1 (got %d)", cfg->step);
+    MomentsQ16 nq;
+    for (int t = 0; t < 5; ++t) {
+        SSB_REQUIRE(moments->d_packed[t] && moments->d_bounds[t], "ssb_adam_step_q16: moment array %d missing", t);
+        nq.packed[t] = moments->d_packed[t];
+        nq.bounds[t] = (float4*)moments->d_bounds[t];
+    }
+    if (extras) {
+        SSB_REQUIRE(extras->n_total >= first + count, "ssb_adam_step_q16: n_total %lld is smaller than the range's end", (long long)extras->n_total);
+        SSB_REQUIRE(!extras->use_scale_agnostic_mean || extras->d_radii, "ssb_adam_step_q16: the scale-agnostic mean update needs d_radii");
+    }
+    if (count == 0) return SSB_OK;
+    const float ibc1 = 1.0f / (1.0f - powf(kBeta1, (float)cfg->step)), ibc2 = 1.0f / (1.0f - powf(kBeta2, (float)cfg->step));
+    // in this path the reference applies sh_reg_weight to DC undivided (FusedGeometryOptim.cu:343-345)
+    const float dc_decay = cfg->sh_reg_weight;
+    const SsbSplats none{};
+    const SsbAdamExtras no_extras{};
+    const unsigned blocks = (unsigned)ceil_div(count, 256);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (extras) adam_geometry_kernel<true, 0, true><<<blocks, 256, 0, st>>>(*params, *grads, none, none, first, count, *cfg, ibc1, ibc2, dc_decay, *extras, PeerOffsets{}, nq);
+    else adam_geometry_kernel<false, 0, true><<<blocks, 256, 0, st>>>(*params, *grads, none, none, first, count, *cfg, ibc1, ibc2, dc_decay, no_extras, PeerOffsets{}, nq);
+    SSB_LAUNCHED("adam_geometry_kernel<q16>");
+    return SSB_OK;
 }
 
 int ssb_adam_plain(float* d_param, float* d_grad, float* d_m1, float* d_m2, int64_t numel, int32_t stride, float lr, int32_t step,

@@ -56,6 +56,8 @@ class Densifier:
     def __init__(self, trainer, cfg: DensifyConfig, count: int):
         if trainer.world_size != 1 or len(trainer.handles) != 1:
             raise NotImplementedError("the densification strategy runs on one rank with one camera kind")
+        if trainer.non_sh_optim_bits != 32:
+            raise NotImplementedError("relocation and growth clear fp32 moments; 16-bit non-SH moment codes are not handled")
         if trainer.fused_backward:
             raise NotImplementedError("the per-splat weights are gathered by the per-view raster backward")
         self.tr, self.cfg, self.count = trainer, cfg, int(count)

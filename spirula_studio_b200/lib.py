@@ -140,6 +140,7 @@ SIGNATURES = {
     "ssb_step_set_radii": (C.c_int, [_P, _P]),
     "ssb_step_set_fused_backward": (C.c_int, [_P, _I32]),
     "ssb_step_backward_optimize": (C.c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _P]),
+    "ssb_adam_step_q16": (C.c_int, [_P, _P, _P, _I64, _I64, _P, _P, _P]),
     "ssb_adam_plain": (C.c_int, [_P, _P, _P, _P, _I64, _I32, _F, _I32, _P, _F, _F, _F, _I32, _P]),
     "ssb_adam_step": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _P, _P]),
     "ssb_adam_step_sh_quantized": (C.c_int, [_P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _P, _P]),
@@ -269,6 +270,10 @@ class SsbPeerReplicas(C.Structure):
 class SsbShAdamState(C.Structure):
     _fields_ = [("d_optim_packed", C.c_void_p), ("d_optim_bounds", C.c_void_p), ("d_value_packed", C.c_void_p),
                 ("d_value_bounds", C.c_void_p), ("value_bits", C.c_int32), ("optim_bits", C.c_int32)]
+
+
+class SsbMomentsQ16(C.Structure):
+    _fields_ = [("d_packed", C.c_void_p * 5), ("d_bounds", C.c_void_p * 5)]
 
 
 class SsbDensifyState(C.Structure):

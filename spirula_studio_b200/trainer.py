@@ -57,7 +57,7 @@ def _flat_views(flat, n, attrs=_ATTRS):
 
 class Trainer:
     def __init__(self, cfg: SceneConfig, splats: dict, device="cuda:0", isect_capacity=0, w_l1=0.8, w_ssim=0.2,
-                 process_group=None, world_size=1, rank=0, grad_sync="peer", fused_backward=False):
+                 process_group=None, world_size=1, rank=0, grad_sync="peer", fused_backward=False, non_sh_optim_bits=32):
         self.lib = L.load()
         self.cfg = cfg
         self.device = torch.device(device)
@@ -86,6 +86,22 @@ class Trainer:
         self.m2_flat = torch.zeros(n_mom, dtype=torch.float32, device=dev)
         self.m1 = _flat_views(self.m1_flat, n) if not self.quant else self._geo_views(self.m1_flat)
         self.m2 = _flat_views(self.m2_flat, n) if not self.quant else self._geo_views(self.m2_flat)
+        # Moments of means, rotations, scales, opacities and DC in 16-bit codes (the reference's non_sh_optim_bits = 16,
+        # src/engine/EngineOptim.cpp:136-146): 4 bytes per cell and one float4 of bounds per 256 splats and array replace the
+        # fp32 pairs (8 bytes per cell).  Every rank then updates every splat, so the gradients must already be summed
+        # (one rank, or the NCCL all-reduce).
+        if non_sh_optim_bits not in (16, 32):
+            raise ValueError(f"non_sh_optim_bits must be 32 (off) or 16; got {non_sh_optim_bits}")
+        self.non_sh_optim_bits = non_sh_optim_bits
+        self.nsq_packed, self.nsq_bounds, self._nsq = {}, {}, None
+        if non_sh_optim_bits == 16:
+            if self.grad_sync in ("peer", "multimem") or fused_backward:
+                raise NotImplementedError("16-bit non-SH moments run with grad_sync 'nccl' or one rank, and the per-view backward")
+            self._nsq = L.SsbMomentsQ16()
+            for t, (name, width) in enumerate(_ATTRS[:5]):
+                self.nsq_packed[name] = torch.zeros(n * width * 4, dtype=torch.uint8, device=dev)
+                self.nsq_bounds[name] = torch.zeros(((n + 255) // 256) * 4, dtype=torch.float32, device=dev)
+                self._nsq.d_packed[t], self._nsq.d_bounds[t] = self.nsq_packed[name].data_ptr(), self.nsq_bounds[name].data_ptr()
         self.shq = None
         if self.quant:
             cells = n * 45
@@ -355,8 +371,15 @@ class Trainer:
             else:
                 L.check(self.lib.ssb_exchange_step(*args, self._barrier_cb, None, stream))
             return
-        L.check(self.lib.ssb_adam_step(C.byref(self._p_struct), C.byref(self._g_struct), C.byref(self._m1_struct),
-                                       C.byref(self._m2_struct), f, c, C.byref(cfg), stream))
+        if self._nsq is not None:
+            L.check(self.lib.ssb_adam_step_q16(C.byref(self._p_struct), C.byref(self._g_struct), C.byref(self._nsq), f, c, C.byref(cfg), None, stream))
+            if not self.quant:
+                L.check(self.lib.ssb_adam_plain(L.ptr(self.params["features_sh"]), L.ptr(self.grads["features_sh"]), L.ptr(self.m1["features_sh"]),
+                                                L.ptr(self.m2["features_sh"]), self.n * 45, 45, lr["lr_features_sh"], self.iteration, None, 0.0, 0.0,
+                                                1.0 / float(total_views), 0, stream))
+        else:
+            L.check(self.lib.ssb_adam_step(C.byref(self._p_struct), C.byref(self._g_struct), C.byref(self._m1_struct),
+                                           C.byref(self._m2_struct), f, c, C.byref(cfg), stream))
         if self.quant:
             cells = self.n * 45
             L.check(self.lib.ssb_adam_step_sh_quantized(L.ptr(self.grads["features_sh"]), L.ptr(self.sh_optim_packed),

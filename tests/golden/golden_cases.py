@@ -257,4 +257,5 @@ def adam_inputs():
     out["ex"] = dict(reg=np.array([3.0, 0.7, 0.9, 1.1, 0.5, 0.3, 0.2], np.float32),   # max ratio, then six undivided weights
                      radii=rng.uniform(0.5, 40.0, size=n).astype(np.float32),
                      steps=rng.integers(1, 50, size=n).astype(np.int32))
+    out["nq_sh_reg_weight"] = 0.05       # the DC regulariser of the run with 16-bit non-SH moments
     return out

@@ -371,6 +371,30 @@ def run_adam(ref, out_dir):
             keys = list(p) if not agnostic else ["means"]
             for k in keys:
                 out[f"{tag}_p{step}_{k}"] = p[k].cpu().numpy()
+    # 16-bit moments of the five non-SH arrays (the non_sh_quant kernel), three steps from a zero state:
+    # "nq" = DC regulariser only, "nqx" = all regularisers + per-splat step counters
+    for tag, use_ex in (("nq", False), ("nqx", True)):
+        p = {k: dev(v.reshape(-1)) for k, v in inp["params"].items() if k != "features_sh"}
+        widths = dict(means=3, quats=4, scales=3, opacities=1, features_dc=3)
+        order = ("means", "quats", "scales", "opacities", "features_dc")
+        nblk = (n + 255) // 256
+        packed = {k: torch.zeros(n * widths[k] * 4, dtype=torch.uint8, device=DEV) for k in order}
+        bounds = {k: torch.zeros(nblk * 4, dtype=torch.float32, device=DEV) for k in order}
+        pk = (C.c_void_p * 5)(*[packed[k].data_ptr() for k in order])
+        bd = (C.c_void_p * 5)(*[bounds[k].data_ptr() for k in order])
+        for step, grads in enumerate(inp["grads"], start=1):
+            g = {k: dev(v.reshape(-1)) for k, v in grads.items() if k != "features_sh"}
+            check(ref.ref_adam_geometry_q16(C.c_int64(n), step, C.c_float(inp["grad_scale"]), 0, C.c_float(lr["lr_means"]), C.c_float(lr["lr_quats"]),
+                                            C.c_float(lr["lr_scales"]), C.c_float(lr["lr_opacities"]), C.c_float(lr["lr_features_dc"]),
+                                            C.c_float(inp["nq_sh_reg_weight"]),
+                                            P(p["means"]), P(g["means"]), P(p["quats"]), P(g["quats"]), P(p["scales"]), P(g["scales"]),
+                                            P(p["opacities"]), P(g["opacities"]), P(p["features_dc"]), P(g["features_dc"]), pk, bd,
+                                            d_reg_host.ctypes.data_as(C.c_void_p) if use_ex else None, P(d_steps) if use_ex else None),
+                  "ref_adam_geometry_q16")
+            for k in order:
+                out[f"{tag}_p{step}_{k}"] = p[k].cpu().numpy()
+                out[f"{tag}_q{step}_{k}"] = packed[k].cpu().numpy()
+                out[f"{tag}_b{step}_{k}"] = bounds[k].cpu().numpy()
     # doubly quantised SH step with per-splat counters (16-bit values), one step from the seeded state;
     # the counters are padded because the kernel reads steps[idx / stride] in every thread of its last block
     q = inp["qq16"]

@@ -271,6 +271,47 @@ def test_adam_extras_vs_reference(oracle):
     assert np.allclose(vb, gold["qqs_value_bounds"], rtol=1e-4, atol=1e-7) and np.allclose(ob, gold["qqs_optim_bounds"], rtol=2e-3, atol=1e-5)
 
 
+Q16_ORDER = ("means", "quats", "scales", "opacities", "features_dc")
+
+
+def q16_code_diff(have, want):
+    """Largest difference and fraction of differing 16-bit codes of two packed moment arrays."""
+    d = np.abs(np.asarray(have).view(np.uint16).astype(np.int64) - np.asarray(want).view(np.uint16).astype(np.int64))
+    return d.max(), (d > 0).mean()
+
+
+def test_adam_16bit_non_sh_moments_vs_reference(oracle):
+    """The geometry + DC update on 16-bit moment codes against the reference's non_sh_quant kernel: every step starts from the
+    reference's parameters and codes of the step before."""
+    gold = load("adam")
+    inp = adam_inputs()
+    ex, lr, gs, n = inp["ex"], inp["lrs"], inp["grad_scale"], inp["n"]
+    widths = dict(oracle.Q16_ATTRS)
+    for tag, use_ex in (("nq", False), ("nqx", True)):
+        for step, grads in enumerate(inp["grads"], start=1):
+            if step == 1:
+                p = {k: inp["params"][k].copy() for k in Q16_ORDER}
+                q = {k: (np.zeros(n * widths[k] * 4, np.uint8), np.zeros(((n + 255) // 256) * 4, np.float32)) for k in Q16_ORDER}
+            else:
+                p = {k: gold[f"{tag}_p{step - 1}_{k}"].reshape(inp["params"][k].shape).copy() for k in Q16_ORDER}
+                q = {k: (gold[f"{tag}_q{step - 1}_{k}"].copy(), gold[f"{tag}_b{step - 1}_{k}"].copy()) for k in Q16_ORDER}
+            g = {k: grads[k].copy() for k in Q16_ORDER}
+            oracle.adam_geometry_q16(p, g, q, step, lr, sh_reg_weight=inp["nq_sh_reg_weight"], grad_scale=gs,
+                                     reg=ex["reg"] if use_ex else None, steps=ex["steps"] if use_ex else None)
+            for k in Q16_ORDER:
+                assert frac_bad(p[k].reshape(-1), gold[f"{tag}_p{step}_{k}"], 5e-6, 1e-4) <= 1e-3, (tag, k, step)
+                assert np.allclose(q[k][1], gold[f"{tag}_b{step}_{k}"], rtol=1e-4, atol=1e-6), (tag, k, step)
+                worst, frac = q16_code_diff(q[k][0], gold[f"{tag}_q{step}_{k}"])
+                assert worst <= 2 and frac <= 0.15, (tag, k, step, worst, frac)
+    # a round trip of the codec alone: decode(encode(g1, g2)) is within one quantum of each range
+    rng = np.random.default_rng(5)
+    g1 = (rng.normal(size=(600, 3)) * 1e-3).astype(np.float32)
+    g2 = (rng.uniform(1e-9, 1e-5, size=(600, 3))).astype(np.float32)
+    packed, bounds = oracle.q16_encode(g1, g2)
+    d1, d2 = oracle.q16_decode(packed, bounds, 600, 3)
+    assert np.allclose(d2, g2, rtol=2e-3) and np.allclose(d1, g1, rtol=2e-3, atol=2e-4 * np.abs(g1).max())
+
+
 def _nibble_diff(a, b):
     a, b = a.astype(np.int64), b.astype(np.int64)
     return np.maximum(np.abs((a & 15) - (b & 15)), np.abs((a >> 4) - (b >> 4)))

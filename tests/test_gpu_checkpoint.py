@@ -87,6 +87,46 @@ def test_trainer_resumes_from_state_tar(lib, tmp_path, quant):
         t_.close()
 
 
+@pytest.mark.parametrize("quant", [False, True])
+def test_trainer_with_16bit_non_sh_moments_tracks_fp32_and_resumes(lib, tmp_path, quant):
+    """non_sh_optim_bits = 16: the moments of the five non-SH arrays live in 16-bit codes.  The parameters follow the trainer
+    with fp32 moments closely (a code is 1/65535 of its block's range), the checkpoint carries the reference's
+    eng.<attr>_qfpbo slots instead of the fp32 pairs, and a restored trainer goes on identically."""
+    from spirula_studio_b200.trainer import Trainer
+    cfg, sp, host = small_scene(quant)
+    tr32, tr16 = Trainer(cfg, sp, device=DEV), Trainer(cfg, sp, device=DEV, non_sh_optim_bits=16)
+    for _ in range(4):
+        la, lb = tr32.train_step(*host, cfg.n_views), tr16.train_step(*host, cfg.n_views)
+    assert abs(la[2] - lb[2]) <= 2e-3 * abs(la[2])
+    for k in ("means", "quats", "scales", "opacities", "features_dc"):
+        a, b = tr32.params[k], tr16.params[k]
+        # An early Adam step is about +-lr whatever the gradient's size, so a cell whose gradient is near zero may take
+        # the other sign after the smallest perturbation: bounded by the four steps, and rare.  Everywhere else the
+        # quantised moments change a step by a small fraction of lr.
+        d = (a - b).abs()
+        assert d.max().item() <= 8.0 * cfg.lrs["lr_" + k], k
+        assert (d > 0.02 * cfg.lrs["lr_" + k]).float().mean().item() < 0.02, k
+    assert tr16.nsq_packed["means"].any() and tr16.nsq_bounds["features_dc"].any()
+    path = ck.save_checkpoint(tr16, str(tmp_path))
+    with tarfile.open(path) as t:
+        names = [m.name for m in t.getmembers()]
+        text = t.extractfile("state.json").read().decode()
+    assert '"non_sh_optim_bits": 16' in text
+    assert "eng.means_qfpbo.q.npy" in names and "eng.features_dc_qfpbo.qb.npy" in names and "eng.g1_means.npy" not in names
+    if quant:       # the reference's slot order: fp32 moments, the qfpbo states, the SH state, the SH values
+        assert names.index("eng.features_dc_qfpbo.qb.npy") < names.index("eng.sh_quant.q.npy")
+    else:
+        assert names.index("eng.g2_features_sh.npy") < names.index("eng.means_qfpbo.q.npy")
+    tr2 = Trainer(cfg, sp, device=DEV, non_sh_optim_bits=16)
+    assert ck.load_checkpoint(tr2, str(tmp_path)) == 4
+    for (name, got, _), (_, want, _) in zip(ck.saved_buffers(tr2), ck.saved_buffers(tr16)):
+        assert torch.equal(got, want), name
+    with pytest.raises(RuntimeError, match="layout"):
+        ck.load_checkpoint(tr32, str(tmp_path))
+    for t_ in (tr32, tr16, tr2):
+        t_.close()
+
+
 def test_device_arrays_larger_than_the_staging_buffers(lib, tmp_path):
     # 80 MiB + 20 bytes: three staging chunks, the last one ragged; both staging buffers get reused
     n = (80 << 20) // 4 + 5

@@ -335,6 +335,60 @@ def test_adam_extras_vs_reference(lib, U):
 
 
 @pytest.mark.gpu
+def test_adam_16bit_non_sh_moments_vs_reference(lib, U):
+    """ssb_adam_step_q16 against the reference's non_sh_quant kernel, every step from the reference's parameters and codes of the
+    step before; then the same update in two calls over block-aligned ranges."""
+    from test_golden_cpu import Q16_ORDER, q16_code_diff
+    gold = load("adam")
+    inp = adam_inputs()
+    ex, lr, gs, n = inp["ex"], inp["lrs"], inp["grad_scale"], inp["n"]
+    widths = dict(means=3, quats=4, scales=3, opacities=1, features_dc=3)
+    nblk = (n + 255) // 256
+    d_steps = U.dev(ex["steps"])
+    reg = [float(v) for v in ex["reg"]]
+
+    def run(tag, use_ex, step, grads, ranges):
+        if step == 1:
+            p = {k: U.dev(inp["params"][k].reshape(-1)) for k in Q16_ORDER}
+            packed = {k: torch.zeros(n * widths[k] * 4, dtype=torch.uint8, device=U.DEV) for k in Q16_ORDER}
+            bounds = {k: torch.zeros(nblk * 4, device=U.DEV) for k in Q16_ORDER}
+        else:
+            p = {k: U.dev(gold[f"{tag}_p{step - 1}_{k}"]) for k in Q16_ORDER}
+            packed = {k: U.dev(gold[f"{tag}_q{step - 1}_{k}"]) for k in Q16_ORDER}
+            bounds = {k: U.dev(gold[f"{tag}_b{step - 1}_{k}"]) for k in Q16_ORDER}
+        g = {k: U.dev(grads[k].reshape(-1)) for k in Q16_ORDER}
+        mom = L.SsbMomentsQ16()
+        for t, k in enumerate(Q16_ORDER):
+            mom.d_packed[t], mom.d_bounds[t] = packed[k].data_ptr(), bounds[k].data_ptr()
+        cfg = L.SsbAdamConfig(lr["lr_means"], lr["lr_quats"], lr["lr_scales"], lr["lr_opacities"], lr["lr_features_dc"], 0.0,
+                              inp["nq_sh_reg_weight"], gs, step, 0)
+        extras = L.SsbAdamExtras(*reg, 0, None, d_steps.data_ptr(), n, None) if use_ex else None
+        ps, gs_ = L.splats_struct({**p, "features_sh": None}), L.splats_struct({**g, "features_sh": None})
+        for first, count in ranges:
+            L.check(lib.ssb_adam_step_q16(C.byref(ps), C.byref(gs_), C.byref(mom), first, count, C.byref(cfg),
+                                          C.byref(extras) if extras is not None else None, None))
+        torch.cuda.synchronize()
+        return p, packed, bounds
+
+    for tag, use_ex in (("nq", False), ("nqx", True)):
+        for step, grads in enumerate(inp["grads"], start=1):
+            for ranges in ([(0, n)], [(0, 256), (256, n - 256)]):
+                p, packed, bounds = run(tag, use_ex, step, grads, ranges)
+                for k in Q16_ORDER:
+                    assert U.close_frac(p[k].cpu().numpy(), gold[f"{tag}_p{step}_{k}"], 5e-6, 1e-4) <= 1e-3, (tag, k, step)
+                    assert np.allclose(bounds[k].cpu().numpy(), gold[f"{tag}_b{step}_{k}"], rtol=1e-4, atol=1e-6), (tag, k, step)
+                    worst, frac = q16_code_diff(packed[k].cpu().numpy(), gold[f"{tag}_q{step}_{k}"])
+                    assert worst <= 2 and frac <= 0.15, (tag, k, step, worst, frac)
+    # a range that does not start on a block of 256 splats is refused
+    p, packed, bounds = run("nq", False, 1, inp["grads"][0], [])
+    mom = L.SsbMomentsQ16()
+    for t, k in enumerate(Q16_ORDER):
+        mom.d_packed[t], mom.d_bounds[t] = packed[k].data_ptr(), bounds[k].data_ptr()
+    cfg = L.SsbAdamConfig(0, 0, 0, 0, 0, 0, 0, 1.0, 1, 0)
+    ps = L.splats_struct({**p, "features_sh": None})
+    assert lib.ssb_adam_step_q16(C.byref(ps), C.byref(ps), C.byref(mom), 100, 10, C.byref(cfg), None, None) == L.SSB_ERR_INVALID_ARGUMENT
+
+
 def test_adam_4bit_state_vs_reference(lib, U):
     """ssb_adam_step_sh_quantized_ex with optim_bits = 4 against the reference's kernels, each step from the reference's state."""
     gold = load("adam")

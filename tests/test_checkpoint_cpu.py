@@ -142,7 +142,7 @@ def test_manifest_text_and_slot_list_follow_the_reference():
     from types import SimpleNamespace
     from spirula_studio_b200 import checkpoint as ck
     from spirula_studio_b200.scenes import CONFIGS
-    tr = SimpleNamespace(cfg=CONFIGS["mid_1m"], n=1000, quant=True)
+    tr = SimpleNamespace(cfg=CONFIGS["mid_1m"], n=1000, quant=True, non_sh_optim_bits=32)
     text = ck.state_json(tr, 42)
     keys = [ln.split('"')[1] for ln in text.splitlines() if ln.startswith('  "')]
     assert keys == ["format_version", "full_resume", "quant_codec", "quant_block_size", "quant_eps", "step", "primitive",
@@ -165,3 +165,10 @@ def test_manifest_text_and_slot_list_follow_the_reference():
     names = [n for n, _, _ in ck.saved_buffers(tr)]
     assert names == [f"world.{a}" for a in geo + ["features_sh"]] + [f"eng.g1_{a}" for a in geo + ["features_sh"]] + \
         [f"eng.g2_{a}" for a in geo + ["features_sh"]]
+    # 16-bit non-SH moments: the qfpbo slots replace the fp32 pairs and sit before the SH state
+    tr.quant, tr.non_sh_optim_bits = True, 16
+    tr.nsq_packed = tr.nsq_bounds = none
+    assert '"non_sh_optim_bits": 16' in ck.state_json(tr, 1)
+    names = [n for n, _, _ in ck.saved_buffers(tr)]
+    assert names == [f"world.{a}" for a in geo] + [f"eng.{a}_qfpbo.{x}" for a in geo for x in ("q", "qb")] + \
+        ["eng.sh_quant.q", "eng.sh_quant.qb", "eng.world.sh_vq16.q", "eng.world.sh_vq16.qb"]

@@ -80,13 +80,18 @@ typedef struct SsbCameras {
     int32_t width, height;
     int32_t model;           /* SSB_CAMERA_* */
     int32_t antialiased;     /* 0 = 3dgs, 1 = mip-splatting blur and opacity compensation */
-    int32_t distortion;      /* lens-distortion tier (CameraDistortionType, src/core/Common.cuh:104-109): only
-                              * SSB_DISTORTION_NONE is built; any other value makes the projection calls return
-                              * SSB_ERR_UNSUPPORTED instead of rendering an undistorted image */
+    int32_t distortion;      /* SSB_DISTORTION_*: the lens-distortion tier applied to the camera model's normalised
+                              * coordinates (CameraDistortionType, src/core/Common.cuh:104-109;
+                              * src/shaders/projection_utils.slang:208-298).  The pairs the reference instantiates
+                              * (src/kernels/projection/CameraVariants.cuh:11-22) are built: every tier for the pinhole,
+                              * OpenCV and thin prism for the two fisheyes, none for the equirectangular camera; any
+                              * other pair makes the projection calls return SSB_ERR_UNSUPPORTED. */
     int32_t reserved;
-    const float* d_dist_coeffs; /* device [count][8] distortion coefficients of that tier; unread */
+    const float* d_dist_coeffs; /* device [count][8], one row per view in the tier's own order; NULL reads as zeros.
+                                 * OpenCV: k1 k2 p1 p2.  Thin prism: k1 k2 k3 k4 p1 p2 sx1 sy1.
+                                 * Rational: k1 k2 k3 k4 k5 k6 p1 p2 (k4..k6 in the denominator). */
 } SsbCameras;
-enum { SSB_DISTORTION_NONE = 0 };
+enum { SSB_DISTORTION_NONE = 0, SSB_DISTORTION_OPENCV = 1, SSB_DISTORTION_THIN_PRISM = 2, SSB_DISTORTION_RATIONAL = 3 };
 
 /* 48-byte projected splat.  a = {x, y, hx, hy}: centre in pixels and the half
  * extents of the alpha >= 1/255 footprint; b = {conic a, b, c, opacity};
@@ -612,17 +617,25 @@ int ssb_step_create(const SsbStepConfig* cfg, SsbStep** out);
 void ssb_step_destroy(SsbStep* step);
 int64_t ssb_step_device_bytes(const SsbStep* step);
 
+/* Makes every view's projection fold the splats' view radii (view_radius_3dgs, src/shaders/projection_utils.slang:1033-1043)
+ * into d_radii [n_splats] by maximum, as ssb_project_fwd does with its d_radii argument: the array the scale-agnostic mean
+ * update, the scale clip, the score update and the revised noise read.  The caller zeroes it once per iteration.  NULL: off. */
+int ssb_step_set_radii(SsbStep* step, float* d_radii);
+
+/* The lens-distortion tier of the step's cameras (SsbCameras::distortion; the engine's camera.distortion with
+ * dist_coeffs[C][8], src/engine/EngineTrainStep.cpp) and its coefficient rows: row v belongs to view v of the NEXT
+ * ssb_step_views / ssb_step_views_gated call (the same indexing as that call's d_viewmats), and for
+ * ssb_step_backward_optimize to view v of the views it is given.  The pointer is read at enqueue time and the rows on the
+ * device when the views run.  tier SSB_DISTORTION_NONE (the default) ignores d_dist_coeffs.  A (model, tier) pair the
+ * projection does not build is SSB_ERR_UNSUPPORTED here. */
+int ssb_step_set_distortion(SsbStep* step, int32_t tier, const float* d_dist_coeffs);
+
 /* Switches the densification outputs of the step on (accum_mode != SSB_ACCUM_NONE) or off: every view then also
  * builds its SSIM loss map (ssim_loss_map_weight * (1 - SSIM variant), as ssb_loss_l1_ssim_fwdbwd_map on a zeroed map;
  * the reference adds its per-pixel loss map of the pixel-loss pass on top, src/engine/EngineLoss.cpp, which is not
  * built here) and the raster backward pass folds it into d_accum_weight [n_splats] (and d_accum_weight_den for
  * SSB_ACCUM_AVG) as ssb_raster_bwd_accum does.  The arrays are combined into across views and calls
  * (EngineTrainStep.cpp:264-272); the caller zeroes them.  Allocates one [H][W] map per lane on first use. */
-/* Makes every view's projection fold the splats' view radii (view_radius_3dgs, src/shaders/projection_utils.slang:1033-1043)
- * into d_radii [n_splats] by maximum, as ssb_project_fwd does with its d_radii argument: the array the scale-agnostic mean
- * update, the scale clip, the score update and the revised noise read.  The caller zeroes it once per iteration.  NULL: off. */
-int ssb_step_set_radii(SsbStep* step, float* d_radii);
-
 int ssb_step_set_densify(SsbStep* step, int32_t ssim_loss_map_mode, float ssim_loss_map_weight, int32_t accum_mode,
                          float* d_accum_weight, float* d_accum_weight_den);
 

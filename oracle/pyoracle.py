@@ -61,7 +61,18 @@ def _sh_args(splats, shq):
     return None, _p(shq["packed"]), _p(shq["bounds"]), C.c_int(shq["bits"]), C.c_int64(shq.get("bounds_stride", 256))
 
 
-def project_fwd(splats, viewmats, intrins, W, H, model=0, antialiased=0, shq=None, with_radii=True):
+def _dist_args(dist, dist_coeffs, n_views):
+    """(tier, pointer to [C][8] float32 rows or NULL); the array is returned too so that it outlives the call."""
+    if not dist:
+        return 0, None, None
+    rows = np.zeros((n_views, 8), np.float32)
+    if dist_coeffs is not None:
+        rows[:] = np.asarray(dist_coeffs, np.float32).reshape(-1, 8)
+    return int(dist), _p(rows), rows
+
+
+def project_fwd(splats, viewmats, intrins, W, H, model=0, antialiased=0, shq=None, with_radii=True, dist=0, dist_coeffs=None):
+    """dist: lens distortion tier (0 none, 1 OpenCV, 2 thin prism, 3 rational) with dist_coeffs [C][8]."""
     lib = load()
     s = {k: _f(v) for k, v in splats.items() if v is not None}
     N, Cn = s["means"].shape[0], viewmats.shape[0]
@@ -71,14 +82,15 @@ def project_fwd(splats, viewmats, intrins, W, H, model=0, antialiased=0, shq=Non
                xy=np.zeros((Cn * N, 2), np.float32), depth=np.zeros(Cn * N, np.float32),
                conic=np.zeros((Cn * N, 3), np.float32), opac=np.zeros(Cn * N, np.float32), rgb=np.zeros((Cn * N, 3), np.float32))
     sh = _sh_args(s, shq)
-    lib.oracle_project_fwd(C.c_int64(N), C.c_int(Cn), C.c_int(W), C.c_int(H), C.c_int(model), C.c_int(antialiased),
+    tier, d_ptr, _keep = _dist_args(dist, dist_coeffs, Cn)
+    lib.oracle_project_fwd_dist(C.c_int64(N), C.c_int(Cn), C.c_int(W), C.c_int(H), C.c_int(model), C.c_int(tier), d_ptr, C.c_int(antialiased),
                            _p(s["means"]), _p(s["quats"]), _p(s["scales"]), _p(s["opacities"]), _p(s["features_dc"]), *sh,
                            _p(viewmats), _p(intrins), _p(out["aabb"]), _p(out["depths"]), _p(out["radii"]),
                            _p(out["xy"]), _p(out["depth"]), _p(out["conic"]), _p(out["opac"]), _p(out["rgb"]))
     return out
 
 
-def project_bwd(splats, viewmats, intrins, W, H, aabb, v, model=0, antialiased=0, shq=None):
+def project_bwd(splats, viewmats, intrins, W, H, aabb, v, model=0, antialiased=0, shq=None, dist=0, dist_coeffs=None):
     """v: dict of v_xy, v_depth, v_conic, v_opac, v_rgb. Returns dict of world gradients."""
     lib = load()
     s = {k: _f(val) for k, val in splats.items() if val is not None}
@@ -88,7 +100,8 @@ def project_bwd(splats, viewmats, intrins, W, H, aabb, v, model=0, antialiased=0
              opacities=np.zeros(N, np.float32), features_dc=np.zeros((N, 3), np.float32), features_sh=np.zeros((N, 15, 3), np.float32))
     vv = {k: _f(x) for k, x in v.items()}
     sh = _sh_args(s, shq)
-    lib.oracle_project_bwd(C.c_int64(N), C.c_int(Cn), C.c_int(W), C.c_int(H), C.c_int(model), C.c_int(antialiased),
+    tier, d_ptr, _keep = _dist_args(dist, dist_coeffs, Cn)
+    lib.oracle_project_bwd_dist(C.c_int64(N), C.c_int(Cn), C.c_int(W), C.c_int(H), C.c_int(model), C.c_int(tier), d_ptr, C.c_int(antialiased),
                            _p(s["means"]), _p(s["quats"]), _p(s["scales"]), _p(s["opacities"]), _p(s["features_dc"]), *sh,
                            _p(viewmats), _p(intrins), _p(_f(aabb)),
                            _p(vv["v_xy"]), _p(vv["v_depth"]), _p(vv["v_conic"]), _p(vv["v_opac"]), _p(vv["v_rgb"]),
@@ -397,10 +410,10 @@ def adam_qq(grad, optim_packed, optim_bounds, value_packed, value_bounds, value_
                                 _p(value_bounds), _p(steps) if steps is not None else None, C.c_int(stride), C.c_int(optim_bits))
 
 
-def forward_chain(splats, viewmats, intrins, W, H, shq=None, model=0):
+def forward_chain(splats, viewmats, intrins, W, H, shq=None, model=0, dist=0, dist_coeffs=None):
     """projection -> keys -> sort -> ranges -> raster for all views in one batch (as the reference's batched launch)."""
     N, I = splats["means"].shape[0], viewmats.shape[0]
-    proj = project_fwd(splats, viewmats, intrins, W, H, shq=shq, model=model)
+    proj = project_fwd(splats, viewmats, intrins, W, H, shq=shq, model=model, dist=dist, dist_coeffs=dist_coeffs)
     counts, cum, keys, vals = tile_keys(proj, N, W, H)
     tw, th = tile_grid(W, H)
     nb = tile_n_bits(tw * th * I)

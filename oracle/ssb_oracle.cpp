@@ -98,9 +98,12 @@ struct Camera {
     float fx, fy, cx, cy;
     int W, H;
     int model;
+    int dist = 0;            // CameraDistortionType: 0 none, 1 OpenCV, 2 thin prism, 3 rational (src/core/Common.cuh)
+    float coeffs[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 };
 
-inline Camera load_camera(const float* viewmats, const float* intrins, int cid, int W, int H, int model) {
+inline Camera load_camera(const float* viewmats, const float* intrins, int cid, int W, int H, int model, int dist = 0,
+                          const float* dist_coeffs = nullptr) {
     // src/kernels/projection/ProjectionFwd_kernel.cuh:50-59: rows 0..2 of the
     // row-major 4x4 world-to-camera matrix are [R | t].
     const float* m = viewmats + 16 * cid;
@@ -112,6 +115,9 @@ inline Camera load_camera(const float* viewmats, const float* intrins, int cid, 
     c.fx = intrins[4 * cid + 0]; c.fy = intrins[4 * cid + 1];
     c.cx = intrins[4 * cid + 2]; c.cy = intrins[4 * cid + 3];
     c.W = W; c.H = H; c.model = model;
+    c.dist = dist;
+    // CameraDistortionCoeffsBuffer::load (src/core/Common.cuh:152-169): rows of eight floats; a null buffer reads as zeros
+    if (dist != 0 && dist_coeffs) for (int i = 0; i < 8; ++i) c.coeffs[i] = dist_coeffs[8 * cid + i];
     return c;
 }
 
@@ -141,6 +147,61 @@ inline float view_radius_3dgs(const float mean[3], const float log_scale[3], flo
     float dx = mean[0] - campos[0], dy = mean[1] - campos[1], dz = mean[2] - campos[2];
     float dist = std::sqrt(dx * dx + dy * dy + dz * dz);
     return radius / (std::max(dist, radius) + std::sqrt(std::max(dist * dist - radius * radius, 0.0f)));
+}
+
+// ---- lens distortion tiers (src/shaders/projection_utils.slang:208-298) -------------------------------------------
+// A value over S with its two partial derivatives with respect to the undistorted coordinates (u, v).  The reference
+// takes the 2x2 Jacobian of a tier by forward-mode autodiff of the tier's formula (camera_distortion_jac, :300-308);
+// evaluating the formula in this arithmetic is the same thing, and with S itself a dual number the Jacobian carries
+// its own derivatives with respect to the splat.
+template <class S> struct Jet2 { S v, du, dv; };
+template <class S> inline Jet2<S> operator+(const Jet2<S>& a, const Jet2<S>& b) { return {a.v + b.v, a.du + b.du, a.dv + b.dv}; }
+template <class S> inline Jet2<S> operator*(const Jet2<S>& a, const Jet2<S>& b) { return {a.v * b.v, a.du * b.v + a.v * b.du, a.dv * b.v + a.v * b.dv}; }
+template <class S> inline Jet2<S> operator/(const Jet2<S>& a, const Jet2<S>& b) {
+    S q = a.v / b.v;
+    return {q, (a.du - q * b.du) / b.v, (a.dv - q * b.dv) / b.v};
+}
+template <class S> inline Jet2<S> operator+(float a, const Jet2<S>& b) { return {a + b.v, b.du, b.dv}; }
+template <class S> inline Jet2<S> operator*(float a, const Jet2<S>& b) { return {a * b.v, a * b.du, a * b.dv}; }
+
+// distort(uv) of one tier; coefficient order is the tier's own (:246 k1 k2 p1 p2; :262 k1 k2 k3 k4 p1 p2 sx1 sy1;
+// :283 k1 k2 k3 k4 k5 k6 p1 p2 with k4..k6 in the denominator)
+template <class T>
+inline void distort_tier(int dist, const float* c, const T& u, const T& v, T& ou, T& ov) {
+    T r2 = u * u + v * v;
+    if (dist == 1) {
+        float k1 = c[0], k2 = c[1], p1 = c[2], p2 = c[3];
+        T radial = 1.0f + r2 * (k1 + k2 * r2);
+        ou = u * radial + ((2.0f * p1) * (u * v) + p2 * (r2 + 2.0f * (u * u)));
+        ov = v * radial + ((2.0f * p2) * (u * v) + p1 * (r2 + 2.0f * (v * v)));
+    } else if (dist == 2) {
+        float k1 = c[0], k2 = c[1], k3 = c[2], k4 = c[3], p1 = c[4], p2 = c[5], sx1 = c[6], sy1 = c[7];
+        T radial = 1.0f + r2 * (k1 + r2 * (k2 + r2 * (k3 + k4 * r2)));
+        ou = u * radial + (((2.0f * p1) * (u * v) + p2 * (r2 + 2.0f * (u * u))) + sx1 * r2);
+        ov = v * radial + (((2.0f * p2) * (u * v) + p1 * (r2 + 2.0f * (v * v))) + sy1 * r2);
+    } else {
+        float k1 = c[0], k2 = c[1], k3 = c[2], k4 = c[3], k5 = c[4], k6 = c[5], p1 = c[6], p2 = c[7];
+        T radial = (1.0f + r2 * (k1 + r2 * (k2 + k3 * r2))) / (1.0f + r2 * (k4 + r2 * (k5 + k6 * r2)));
+        ou = u * radial + ((2.0f * p1) * (u * v) + p2 * (r2 + 2.0f * (u * u)));
+        ov = v * radial + ((2.0f * p2) * (u * v) + p1 * (r2 + 2.0f * (v * v)));
+    }
+}
+
+// Distorted coordinates and the Jacobian Dj = d(distort)/d(u, v), row major
+template <class S>
+inline void distort_with_jac(int dist, const float* c, const S& u, const S& v, S out[2], S Dj[4]) {
+    Jet2<S> ju{u, S(1.f), S(0.f)}, jv{v, S(0.f), S(1.f)}, ou, ov;
+    distort_tier<Jet2<S>>(dist, c, ju, jv, ou, ov);
+    out[0] = ou.v; out[1] = ov.v;
+    Dj[0] = ou.du; Dj[1] = ou.dv; Dj[2] = ov.du; Dj[3] = ov.dv;
+}
+
+// is_valid_distortion (:311-323): the map must stay a moderate, orientation-preserving stretch at uv
+inline bool distortion_valid(int dist, const float* c, float u, float v) {
+    float out[2], Dj[4];
+    distort_with_jac<float>(dist, c, u, v, out, Dj);
+    float jdet = std::min(Dj[0] * Dj[3] - Dj[1] * Dj[2], std::min(Dj[0], Dj[3]));
+    return jdet > 0.25f && jdet < 4.0f && (u * out[0] + v * out[1]) >= 0.0f;
 }
 
 // Camera-model mean projection and its 2x3 Jacobian, both in S arithmetic.
@@ -222,7 +283,26 @@ inline void project_mean(int model, const S p[3], float fx, float fy, float cx, 
     }
 }
 
-// src/shaders/primitive_3dgs.slang:419-578 (projection_3dgs<model, DistNone,
+// The same with a lens distortion tier between the camera model's normalised coordinates and the pixel grid
+// (persp_proj_uv / fisheye_proj_uv / equisolid_proj_uv, src/shaders/projection_utils.slang:330-343,412-424,443-455, and
+// their Jacobians by forward-mode autodiff, :363-375,463-493): uv = f * distort(n(p)) + c, J = diag(f) Dj dn/dp.
+// `valid` (may be null) receives is_valid_distortion at n(p).
+template <class S>
+inline void project_mean_distorted(const Camera& cam, const S p[3], S uv[2], S J[6], bool* valid) {
+    S n[2], Jn[6];
+    project_mean<S>(cam.model, p, 1.0f, 1.0f, 0.0f, 0.0f, n, Jn);
+    if (valid) *valid = distortion_valid(cam.dist, cam.coeffs, val(n[0]), val(n[1]));
+    S d[2], Dj[4];
+    distort_with_jac<S>(cam.dist, cam.coeffs, n[0], n[1], d, Dj);
+    uv[0] = cam.fx * d[0] + cam.cx;
+    uv[1] = cam.fy * d[1] + cam.cy;
+    for (int j = 0; j < 3; ++j) {
+        J[j] = cam.fx * (Dj[0] * Jn[j] + Dj[1] * Jn[3 + j]);
+        J[3 + j] = cam.fy * (Dj[2] * Jn[j] + Dj[3] * Jn[3 + j]);
+    }
+}
+
+// src/shaders/primitive_3dgs.slang:419-578 (projection_3dgs<model, D,
 // assume_valid, eval3d=false>).  Returns false where the reference returns with
 // aabb = 0.  With assume_valid every cull is skipped, as in the backward pass
 // (src/shaders/primitive_3dgs.slang:644-653).
@@ -272,7 +352,13 @@ inline bool projection_3dgs(
         covc[3 * i + j] = RC[3 * i + 0] * R[3 * j + 0] + RC[3 * i + 1] * R[3 * j + 1] + RC[3 * i + 2] * R[3 * j + 2];
 
     S J[6];
-    project_mean<S>(cam.model, mc, cam.fx, cam.fy, cam.cx, cam.cy, out.mean2d, J);
+    if (cam.dist != 0) {
+        bool dist_ok = true;
+        project_mean_distorted<S>(cam, mc, out.mean2d, J, assume_valid ? nullptr : &dist_ok);
+        if (!assume_valid && !dist_ok) return false;      // persp_proj / fisheye_proj / equisolid_proj, :346-358,427-441
+    } else {
+        project_mean<S>(cam.model, mc, cam.fx, cam.fy, cam.cx, cam.cy, out.mean2d, J);
+    }
     if (cam.model == PINHOLE) {
         // persp_proj: z < 0 is invalid (src/shaders/projection_utils.slang:349-355)
         if (!assume_valid && val(mc[2]) < 0.0f) return false;
@@ -593,8 +679,8 @@ float oracle_det_logf(float x) { return det_logf(x); }
 // Entries of culled pairs keep aabb = 0 and depths = 0; their screen entries
 // are written as zeros here (the reference leaves them untouched).
 // ---------------------------------------------------------------------------
-void oracle_project_fwd(
-    int64_t N, int C, int W, int H, int model, int antialiased,
+void oracle_project_fwd_dist(
+    int64_t N, int C, int W, int H, int model, int dist, const float* dist_coeffs, int antialiased,
     const float* means, const float* quats, const float* scales, const float* opacities,
     const float* features_dc, const float* features_sh,
     const uint8_t* sh_packed, const float* sh_bounds, int sh_bits, int64_t sh_bounds_stride,
@@ -603,7 +689,7 @@ void oracle_project_fwd(
     float* xy, float* depth, float* conic, float* opac, float* rgb) {
     ShStore st{features_sh, sh_packed, sh_bounds, sh_bits, sh_bounds_stride > 0 ? sh_bounds_stride : (int64_t)256 * 3 * NUM_SH};
     for (int cid = 0; cid < C; ++cid) {
-        Camera cam = load_camera(viewmats, intrins, cid, W, H, model);
+        Camera cam = load_camera(viewmats, intrins, cid, W, H, model, dist, dist_coeffs);
 #pragma omp parallel for schedule(static)
         for (int64_t gid = 0; gid < N; ++gid) {
             int64_t idx = (int64_t)cid * N + gid;
@@ -651,6 +737,18 @@ void oracle_project_fwd(
     }
 }
 
+void oracle_project_fwd(
+    int64_t N, int C, int W, int H, int model, int antialiased,
+    const float* means, const float* quats, const float* scales, const float* opacities,
+    const float* features_dc, const float* features_sh,
+    const uint8_t* sh_packed, const float* sh_bounds, int sh_bits, int64_t sh_bounds_stride,
+    const float* viewmats, const float* intrins,
+    float* aabb, float* depths, float* radii,
+    float* xy, float* depth, float* conic, float* opac, float* rgb) {
+    oracle_project_fwd_dist(N, C, W, H, model, 0, nullptr, antialiased, means, quats, scales, opacities, features_dc, features_sh, sh_packed,
+                            sh_bounds, sh_bits, sh_bounds_stride, viewmats, intrins, aabb, depths, radii, xy, depth, conic, opac, rgb);
+}
+
 // ---------------------------------------------------------------------------
 // Projection backward.  projection_3dgs_backward -> projection_fused_bwd_kernel
 // (src/kernels/projection/ProjectionBwd_kernel.cuh:16-130): for every pair whose
@@ -659,8 +757,8 @@ void oracle_project_fwd(
 // clamp mask rgb_raw >= -0.5 (src/shaders/harmonics.slang:1087-1126), summed
 // into the world gradients (the caller zeroes or pre-loads them).
 // ---------------------------------------------------------------------------
-void oracle_project_bwd(
-    int64_t N, int C, int W, int H, int model, int antialiased,
+void oracle_project_bwd_dist(
+    int64_t N, int C, int W, int H, int model, int dist, const float* dist_coeffs, int antialiased,
     const float* means, const float* quats, const float* scales, const float* opacities,
     const float* features_dc, const float* features_sh,
     const uint8_t* sh_packed, const float* sh_bounds, int sh_bits, int64_t sh_bounds_stride,
@@ -671,7 +769,7 @@ void oracle_project_bwd(
     constexpr int K = 11;
     typedef Dual<K> D;
     for (int cid = 0; cid < C; ++cid) {
-        Camera cam = load_camera(viewmats, intrins, cid, W, H, model);
+        Camera cam = load_camera(viewmats, intrins, cid, W, H, model, dist, dist_coeffs);
 #pragma omp parallel for schedule(static)
         for (int64_t gid = 0; gid < N; ++gid) {
             int64_t idx = (int64_t)cid * N + gid;
@@ -711,6 +809,19 @@ void oracle_project_bwd(
                 add(&g_sh[(int64_t)3 * NUM_SH * gid + 3 * j + ch], basis[j].v * vc[ch]);
         }
     }
+}
+
+void oracle_project_bwd(
+    int64_t N, int C, int W, int H, int model, int antialiased,
+    const float* means, const float* quats, const float* scales, const float* opacities,
+    const float* features_dc, const float* features_sh,
+    const uint8_t* sh_packed, const float* sh_bounds, int sh_bits, int64_t sh_bounds_stride,
+    const float* viewmats, const float* intrins, const float* aabb,
+    const float* v_xy, const float* v_depth, const float* v_conic, const float* v_opac, const float* v_rgb,
+    float* g_means, float* g_quats, float* g_scales, float* g_opacities, float* g_dc, float* g_sh) {
+    oracle_project_bwd_dist(N, C, W, H, model, 0, nullptr, antialiased, means, quats, scales, opacities, features_dc, features_sh, sh_packed,
+                            sh_bounds, sh_bits, sh_bounds_stride, viewmats, intrins, aabb, v_xy, v_depth, v_conic, v_opac, v_rgb,
+                            g_means, g_quats, g_scales, g_opacities, g_dc, g_sh);
 }
 
 // ---------------------------------------------------------------------------

@@ -228,11 +228,41 @@ int main(int argc, char** argv) {
     }
     // ---- 5. what the library does not cover is refused the way the reference refuses bad arguments
     bool threw = false;
-    try {
-        projection_3dgs_forward(N, 3, in_splats, ttv(d_vm, {(int64_t)C, 16}), ttv(d_intr, {(int64_t)C, 4}), W, H, "PINHOLE", "OPENCV",
+    try {     // a pair outside the reference's instantiation table: the reference throws here too
+        projection_3dgs_forward(N, 3, in_splats, ttv(d_vm, {(int64_t)C, 16}), ttv(d_intr, {(int64_t)C, 4}), W, H, "FISHEYE", "RATIONAL",
                                 ttv(nullptr, {(int64_t)C, kCameraDistortionParams}), radii, std::nullopt, std::nullopt, 0, 32, 0);
     } catch (const std::runtime_error&) { threw = true; }
     report("unsupported distortion tier throws", threw);
+    // ---- 5b. a lens-distortion tier through the reference's signature against the reference's kernel of that variant
+    {
+        typedef int (*RefFwdDist)(int, int, uint32_t, uint32_t, uint32_t, uint32_t, float*, float*, float*, float*, float*, float*, const float*, const float*,
+                                  float*, float*, float*, float*, float*, float*, float*, float*, float*);
+        auto ref_fwd_dist = (RefFwdDist)dlsym(ref, "ref_project_fwd_dist");
+        if (!ref_fwd_dist) { std::fprintf(stderr, "missing ref_project_fwd_dist\n"); return 2; }
+        std::vector<float> rows = {-0.9f, 0.2f, 0.004f, -0.003f, 0.f, 0.f, 0.f, 0.f, 0.3f, -0.05f, -0.002f, 0.001f, 0.f, 0.f, 0.f, 0.f};
+        float* d_rows = upload(rows);
+        float* d_radii2 = device_zeros<float>(N);
+        DeviceVector<float> radii2(ttv(d_radii2, {N, 1}));
+        auto dout = projection_3dgs_forward(N, 3, in_splats, ttv(d_vm, {(int64_t)C, 16}), ttv(d_intr, {(int64_t)C, 4}), W, H, "PINHOLE", "OPENCV",
+                                            ttv(d_rows, {(int64_t)C, kCameraDistortionParams}), radii2, std::nullopt, std::nullopt, 0, 32, 0);
+        backend::device_synchronize();
+        float *q_aabb = device_zeros<float>(m * 4), *q_depths = device_zeros<float>(m), *q_radii = device_zeros<float>(N);
+        float *q_xy = device_zeros<float>(m * 2), *q_depth = device_zeros<float>(m), *q_conic = device_zeros<float>(m * 3), *q_opac = device_zeros<float>(m),
+              *q_rgb = device_zeros<float>(m * 3);
+        if (ref_fwd_dist(0, 1, C, (uint32_t)N, W, H, d_means, d_quats, d_scales, d_opac, d_dc, d_sh, d_vm, d_intr, d_rows, q_aabb, q_depths, q_radii, q_xy, q_depth,
+                         q_conic, q_opac, q_rgb) != 0) { std::fprintf(stderr, "ref_project_fwd_dist failed\n"); return 2; }
+        auto ga = download((const float*)std::get<0>(dout).data_ptr(), m * 4), ra = download(q_aabb, m * 4), r0 = download(r_aabb, m * 4);
+        std::vector<char> both(m);
+        int64_t n_ref = 0, n_diff = 0, n_moved = 0;
+        for (int64_t i = 0; i < m; ++i) {
+            const bool kr = ra[4 * i + 2] > ra[4 * i], kg = ga[4 * i + 2] > ga[4 * i], k0 = r0[4 * i + 2] > r0[4 * i];
+            n_ref += kr; n_diff += kr != kg; both[i] = kr && kg; n_moved += kr != k0;
+        }
+        report("distorted projection: visible set", n_ref > 500 && n_moved > 0 && (double)n_diff / (double)m <= 2e-3, (double)n_ref, (double)n_moved);
+        auto& d_screen_out = std::get<2>(dout);
+        report("distorted projection: xy", frac_bad(download(d_screen_out[0].data_ptr(), m * 2), download(q_xy, m * 2), 5e-3, 5e-4, &both, 2) <= 2e-3);
+        report("distorted projection: conic", frac_bad(download(d_screen_out[2].data_ptr(), m * 3), download(q_conic, m * 3), 5e-3, 5e-4, &both, 3) <= 2e-3);
+    }
     (void)v_w; (void)aw_out;
 
     // ---- 6. the live-tile map, and the intersection that uses it

@@ -20,7 +20,7 @@
 // the reference sizes them (the pair count is read back to the host where the reference reads it back), so callers see
 // the same tensors.  The 48-byte records and workspaces this library works on are scratch of the adapter, kept in the
 // pool's dynamically named side map.  What the library does not cover is refused the way the reference refuses bad
-// arguments (std::runtime_error, src/core/Common.cuh:133-146): lens-distortion tiers, the live-tile map, AABB-mode
+// arguments (std::runtime_error, src/core/Common.cuh:133-146): AABB-mode
 // intersection, distortion-loss channels, median depth, other primitives.
 #include "ssb.h"
 
@@ -99,7 +99,7 @@ std::tuple<DeviceTensor2D<float4>, DeviceTensor2D<float>, std::vector<DeviceTens
     }
     SsbCameras cams = {(const float*)std::get<0>(viewmats), (const float*)std::get<0>(intrins), (int32_t)C,
                        (int32_t)image_width, (int32_t)image_height, camera_model_of(camera_model), 0,
-                       (int32_t)cdt(distortion), 0, (const float*)std::get<0>(dist_coeffs)};      // a tier other than None: the library says SSB_ERR_UNSUPPORTED
+                       (int32_t)cdt(distortion), 0, (const float*)std::get<0>(dist_coeffs)};      // a pair the reference does not instantiate: SSB_ERR_UNSUPPORTED, thrown
 
     DeviceTensor2D<float4> aabb;
     aabb.resize(PoolSlot::ProjAabb, C, N);

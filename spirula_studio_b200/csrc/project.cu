@@ -72,6 +72,8 @@ __device__ __forceinline__ D3 operator*(const D3& b, float a) { return a * b; }
 __device__ __forceinline__ D3 operator/(float a, const D3& b) { return D3{a, 0.f, 0.f, 0.f} / b; }
 __device__ __forceinline__ D3 operator/(const D3& a, float b) { return (1.0f / b) * a; }
 __device__ __forceinline__ D3 operator-(float a, const D3& b) { return {a - b.v, -b.dx, -b.dy, -b.dz}; }
+__device__ __forceinline__ D3 operator+(float a, const D3& b) { return {a + b.v, b.dx, b.dy, b.dz}; }
+__device__ __forceinline__ D3 operator+(const D3& b, float a) { return {a + b.v, b.dx, b.dy, b.dz}; }
 __device__ __forceinline__ float sqrt_s(float a) { return sqrtf(a); }
 __device__ __forceinline__ D3 sqrt_s(const D3& a) {
     float r = sqrtf(a.v), h = 0.5f / r;
@@ -136,6 +138,14 @@ __device__ __forceinline__ void project_mean_wide(const S p[3], float fx, float 
         uv[1] = fy * (p[1] * k) + lift(cy, k);
         J[0] = fx * (k + p[0] * dkx); J[1] = fx * (p[0] * dky); J[2] = fx * (p[0] * dkz);
         J[3] = fy * (p[1] * dkx); J[4] = fy * (k + p[1] * dky); J[5] = fy * (p[1] * dkz);
+    } else if (MODEL == SSB_CAMERA_PINHOLE) {
+        // only reached with a lens distortion tier (the undistorted pinhole has its own sparse-Jacobian path)
+        S rz = 1.0f / p[2];
+        S u = p[0] * rz, v = p[1] * rz;
+        uv[0] = fx * u + lift(cx, u);
+        uv[1] = fy * v + lift(cy, v);
+        J[0] = fx * rz; J[1] = lift(0.f, rz); J[2] = -((fx * u) * rz);
+        J[3] = lift(0.f, rz); J[4] = fy * rz; J[5] = -((fy * v) * rz);
     } else {
         S h2 = p[0] * p[0] + p[2] * p[2];
         S h = sqrt_s(h2);
@@ -148,11 +158,88 @@ __device__ __forceinline__ void project_mean_wide(const S p[3], float fx, float 
     }
 }
 
+// ---- lens distortion tiers -------------------------------------------------
+// The reference's three tiers (src/shaders/projection_utils.slang:242-298) are special cases of one map of the camera
+// model's normalised coordinates:
+//   radial = (1 + r2 (n1 + r2 (n2 + r2 (n3 + r2 n4)))) / (1 + r2 (d1 + r2 (d2 + r2 d3)))
+//   u' = u radial + 2 p1 u v + p2 (r2 + 2 u^2) + s1 r2,   v' = v radial + 2 p2 u v + p1 (r2 + 2 v^2) + s2 r2
+// OpenCV: n1 n2 p1 p2.  Thin prism: n1..n4 p1 p2 s1 s2.  Rational: n1..n3, d1..d3, p1 p2.  Unused terms are zero, which
+// leaves the tier's own arithmetic (x + 0, x / 1).  Each tier's coefficient row has its own order (:246,:262,:283).
+struct LensDist { float n1, n2, n3, n4, d1, d2, d3, p1, p2, s1, s2; };
+struct DistArgs { const float* coeffs; int tier; };   // [C][8] rows (NULL reads as zeros), SSB_DISTORTION_*
+
+__device__ __forceinline__ LensDist load_lens(const DistArgs& da, int cid) {
+    LensDist k = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (da.coeffs == nullptr) return k;
+    const float* c = da.coeffs + 8 * cid;
+    if (da.tier == SSB_DISTORTION_OPENCV) { k.n1 = c[0]; k.n2 = c[1]; k.p1 = c[2]; k.p2 = c[3]; }
+    else if (da.tier == SSB_DISTORTION_THIN_PRISM) { k.n1 = c[0]; k.n2 = c[1]; k.n3 = c[2]; k.n4 = c[3]; k.p1 = c[4]; k.p2 = c[5]; k.s1 = c[6]; k.s2 = c[7]; }
+    else { k.n1 = c[0]; k.n2 = c[1]; k.n3 = c[2]; k.d1 = c[3]; k.d2 = c[4]; k.d3 = c[5]; k.p1 = c[6]; k.p2 = c[7]; }
+    return k;
+}
+
+// The distorted point and the 2x2 Jacobian of the map (row major), as closed forms of what the reference takes by
+// forward-mode autodiff (camera_distortion_jac, :300-308)
+template <class S>
+__device__ __forceinline__ void distort_s(const LensDist& k, const S& u, const S& v, S out[2], S Dj[4]) {
+    S uu = u * u, vv = v * v, uv = u * v;
+    S r2 = uu + vv;
+    S num = 1.0f + r2 * (k.n1 + r2 * (k.n2 + r2 * (k.n3 + k.n4 * r2)));
+    S den = 1.0f + r2 * (k.d1 + r2 * (k.d2 + k.d3 * r2));
+    S dnum = k.n1 + r2 * (2.0f * k.n2 + r2 * (3.0f * k.n3 + (4.0f * k.n4) * r2));
+    S dden = k.d1 + r2 * (2.0f * k.d2 + (3.0f * k.d3) * r2);
+    S radial = num / den;
+    S drad = (dnum - radial * dden) / den;          // d radial / d r2
+    S ru = (2.0f * drad) * u, rv = (2.0f * drad) * v;
+    out[0] = u * radial + ((2.0f * k.p1) * uv + k.p2 * (r2 + 2.0f * uu) + k.s1 * r2);
+    out[1] = v * radial + ((2.0f * k.p2) * uv + k.p1 * (r2 + 2.0f * vv) + k.s2 * r2);
+    Dj[0] = radial + u * ru + ((2.0f * k.p1) * v + (6.0f * k.p2 + 2.0f * k.s1) * u);
+    Dj[1] = u * rv + ((2.0f * k.p1) * u + (2.0f * k.p2 + 2.0f * k.s1) * v);
+    Dj[2] = v * ru + ((2.0f * k.p2) * v + (2.0f * k.p1 + 2.0f * k.s2) * u);
+    Dj[3] = radial + v * rv + ((2.0f * k.p2) * u + (6.0f * k.p1 + 2.0f * k.s2) * v);
+}
+
+// is_valid_distortion (:311-323)
+__device__ __forceinline__ bool lens_valid(const LensDist& k, float u, float v) {
+    float out[2], Dj[4];
+    distort_s<float>(k, u, v, out, Dj);
+    float jdet = fminf(Dj[0] * Dj[3] - Dj[1] * Dj[2], fminf(Dj[0], Dj[3]));
+    return jdet > 0.25f && jdet < 4.0f && (u * out[0] + v * out[1]) >= 0.0f;
+}
+
+// Pixel position and 2x3 Jacobian with a distortion tier: uv = f * distort(n(p)) + c, J = diag(f) Dj dn/dp
+// (persp_proj_uv / fisheye_proj_uv / equisolid_proj_uv and their Jacobians, :330-343,363-375,412-424,443-493); for the
+// pinhole the third column is then limited as in persp_proj_3dgs (src/shaders/primitive_3dgs.slang:84-95), the limits
+// carrying their own dependence on z.  n_out receives the normalised coordinates.
+template <int MODEL, class S>
+__device__ __forceinline__ void project_mean_dist(const S p[3], const CamDev& cam, const LensDist& k, int W_img, S uv[2], S J[6], S n_out[2]) {
+    S Jn[6];
+    project_mean_wide<MODEL, S>(p, 1.0f, 1.0f, 0.0f, 0.0f, n_out, Jn);
+    S d[2], Dj[4];
+    distort_s<S>(k, n_out[0], n_out[1], d, Dj);
+    uv[0] = cam.fx * d[0] + lift(cam.cx, d[0]);
+    uv[1] = cam.fy * d[1] + lift(cam.cy, d[1]);
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+        J[j] = cam.fx * (Dj[0] * Jn[j] + Dj[1] * Jn[3 + j]);
+        J[3 + j] = cam.fy * (Dj[2] * Jn[j] + Dj[3] * Jn[3 + j]);
+    }
+    if (MODEL == SSB_CAMERA_PINHOLE) {
+        float width = (float)W_img;
+        float lim_pos = width + 0.3f * (0.5f * width), lim_neg = 0.3f * (0.5f * width);
+        S rz = 1.0f / p[2];
+        S max_x = (lim_neg + cam.cx) * rz, min_x = -((lim_pos - cam.cx) * rz);
+        S max_y = (lim_neg + cam.cy) * rz, min_y = -((lim_pos - cam.cy) * rz);
+        if (val(J[2]) < val(min_x)) J[2] = min_x; else if (val(J[2]) > val(max_x)) J[2] = max_x;
+        if (val(J[5]) < val(min_y)) J[5] = min_y; else if (val(J[5]) > val(max_y)) J[5] = max_y;
+    }
+}
+
 // Geometry of the projection.  Returns false when a cull of the reference's
 // forward pass applies (never when assume_valid).
-template <int MODEL, bool assume_valid>
+template <int MODEL, bool DIST, bool assume_valid>
 __device__ __forceinline__ bool project_geom(
-    const CamDev& cam, int W_img, bool antialiased,
+    const CamDev& cam, const LensDist& lens, int W_img, bool antialiased,
     const float mean[3], const float quat[4], const float scale[3], float in_opacity,
     ProjGeom& g) {
     const float* R = cam.R;
@@ -186,7 +273,7 @@ __device__ __forceinline__ bool project_geom(
 
     float c00, c01, c11;
     const float* c = g.covc;
-    if (MODEL == SSB_CAMERA_PINHOLE) {
+    if (MODEL == SSB_CAMERA_PINHOLE && !DIST) {
         float rz = 1.0f / g.mc[2];
         float u = g.mc[0] * rz, v = g.mc[1] * rz;
         g.mean2d[0] = cam.fx * u + cam.cx;
@@ -213,7 +300,14 @@ __device__ __forceinline__ bool project_geom(
         c01 = a1 * g.J11 + a2 * g.J12;
         c11 = b1 * g.J11 + b2 * g.J12;
     } else {
-        project_mean_wide<MODEL, float>(g.mc, cam.fx, cam.fy, cam.cx, cam.cy, g.mean2d, g.Jw);
+        if (DIST) {
+            float nrm[2];
+            project_mean_dist<MODEL, float>(g.mc, cam, lens, W_img, g.mean2d, g.Jw, nrm);
+            // persp_proj / fisheye_proj / equisolid_proj: a point where the distortion map folds is dropped (:346-358,427-441)
+            if (!assume_valid && !lens_valid(lens, nrm[0], nrm[1])) return false;
+        } else {
+            project_mean_wide<MODEL, float>(g.mc, cam.fx, cam.fy, cam.cx, cam.cy, g.mean2d, g.Jw);
+        }
         const float* J = g.Jw;
         // rows of J covc (covc symmetric: xx xy xz yy yz zz)
         float a0 = J[0] * c[0] + J[1] * c[1] + J[2] * c[2], a1 = J[0] * c[1] + J[1] * c[3] + J[2] * c[4], a2 = J[0] * c[2] + J[1] * c[4] + J[2] * c[5];
@@ -356,11 +450,12 @@ struct PackArgs {
     int64_t capacity;
 };
 
-template <int MODEL, int PACK>
+template <int MODEL, int PACK, bool DIST>
 __global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
     SsbSplats sp, SsbShQuant shq, int64_t n, const float* __restrict__ viewmats, const float* __restrict__ intrins,
     int W, int H, int antialiased,
-    float4* __restrict__ aabb_out, float* __restrict__ depths_out, float* __restrict__ radii, SsbScreenRec* __restrict__ screen, PackArgs pk) {
+    float4* __restrict__ aabb_out, float* __restrict__ depths_out, float* __restrict__ radii, SsbScreenRec* __restrict__ screen, PackArgs pk,
+    DistArgs da) {
     __shared__ __align__(16) float sh_s[PACK == 1 ? 4 : kProjBlock * kShPerSplat];
     __shared__ __align__(16) unsigned char raw_s[PACK == 1 ? 16 : kShRawBytes];
     const int cid = blockIdx.y;
@@ -383,7 +478,9 @@ __global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
     int64_t idx = (int64_t)cid * n + gid;
 
     ProjGeom g;
-    bool ok = project_geom<MODEL, false>(cam, W, antialiased != 0, mean, quat, scale, in_op, g);
+    LensDist lens = {};
+    if (DIST) lens = load_lens(da, cid);
+    bool ok = project_geom<MODEL, DIST, false>(cam, lens, W, antialiased != 0, mean, quat, scale, in_op, g);
     float xmin = 0.f, ymin = 0.f, xmax = 0.f, ymax = 0.f, L = 0.f;
     if (ok) {
         L = logf(g.opacity / kAlphaThreshold);
@@ -487,11 +584,11 @@ __device__ __forceinline__ void sh_basis_vjp(float x, float y, float z, const fl
 
 __device__ __forceinline__ float finite_or_zero(float v) { return isfinite(v) ? v : 0.0f; }
 
-template <bool MULTI_VIEW, int MODEL>
-__global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
+template <bool MULTI_VIEW, int MODEL, bool DIST>
+__global__ void __launch_bounds__(kProjBlock, DIST ? 3 : 4) project_bwd_kernel(
     SsbSplats sp, SsbShQuant shq, int64_t n, int C, const float* __restrict__ viewmats, const float* __restrict__ intrins,
     int W, int H, int antialiased, const float4* __restrict__ aabb, SsbScreenRec* __restrict__ v_screen,
-    SsbSplats gr, int accumulate, int clear_v_screen, const int32_t* __restrict__ pair_of, int64_t range_first, int64_t range_end) {
+    SsbSplats gr, int accumulate, int clear_v_screen, const int32_t* __restrict__ pair_of, int64_t range_first, int64_t range_end, DistArgs da) {
     // The launch covers splats [range_first, range_end) of the n per view; every array, the gradient arrays included, is
     // indexed by the splat's own number (a caller that keeps gradients for the range only passes pointers moved back by
     // the range's start).
@@ -555,7 +652,9 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
                 vr[0] = zero; vr[1] = zero; vr[2] = zero;
             }
             ProjGeom g;
-            project_geom<MODEL, true>(cam, W, antialiased != 0, mean, quat, scale, in_op, g);
+            LensDist lens = {};
+            if (DIST) lens = load_lens(da, cid);
+            project_geom<MODEL, DIST, true>(cam, lens, W, antialiased != 0, mean, quat, scale, in_op, g);
             // ---- conic -> blurred 2D covariance
             float v0 = vb.x, v1 = vb.y, v2 = vb.z;
             float invdet = 1.0f / g.det;
@@ -590,7 +689,7 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
             float x = g.mc[0], y = g.mc[1], z = g.mc[2];
             float vmc[3] = {0.f, 0.f, 0.f};
             float vC[9];
-            if (MODEL == SSB_CAMERA_PINHOLE) {
+            if (MODEL == SSB_CAMERA_PINHOLE && !DIST) {
                 float JC0[3] = {g.J00 * c[0] + g.J02 * c[2], g.J00 * c[1] + g.J02 * c[4], g.J00 * c[2] + g.J02 * c[5]};
                 float JC1[3] = {g.J11 * c[1] + g.J12 * c[2], g.J11 * c[3] + g.J12 * c[4], g.J11 * c[4] + g.J12 * c[5]};
                 float vJ00 = 2.f * (G00 * JC0[0] + G01 * JC1[0]);
@@ -636,12 +735,19 @@ __global__ void __launch_bounds__(kProjBlock, 4) project_bwd_kernel(
                 // ---- camera-space mean: v_mc = J^T v_mean2d + sum_ij vJ[i][j] dJ[i][j]/d mc
                 D3 pd[3] = {{x, 1.f, 0.f, 0.f}, {y, 0.f, 1.f, 0.f}, {z, 0.f, 0.f, 1.f}};
                 D3 uvd[2], Jd[6];
-                project_mean_wide<MODEL, D3>(pd, cam.fx, cam.fy, cam.cx, cam.cy, uvd, Jd);
+                if (DIST) { D3 nd[2]; project_mean_dist<MODEL, D3>(pd, cam, lens, W, uvd, Jd, nd); }
+                else project_mean_wide<MODEL, D3>(pd, cam.fx, cam.fy, cam.cx, cam.cy, uvd, Jd);
 #pragma unroll
                 for (int e = 0; e < 6; ++e) { vmc[0] += vJ[e] * Jd[e].dx; vmc[1] += vJ[e] * Jd[e].dy; vmc[2] += vJ[e] * Jd[e].dz; }
-                vmc[0] += J[0] * va.x + J[3] * va.y;
-                vmc[1] += J[1] * va.x + J[4] * va.y;
-                vmc[2] += J[2] * va.x + J[5] * va.y;
+                if (DIST) {     // the pinhole's limited third column is not d(uv)/dz: take the derivatives of uv themselves
+                    vmc[0] += uvd[0].dx * va.x + uvd[1].dx * va.y;
+                    vmc[1] += uvd[0].dy * va.x + uvd[1].dy * va.y;
+                    vmc[2] += uvd[0].dz * va.x + uvd[1].dz * va.y;
+                } else {
+                    vmc[0] += J[0] * va.x + J[3] * va.y;
+                    vmc[1] += J[1] * va.x + J[4] * va.y;
+                    vmc[2] += J[2] * va.x + J[5] * va.y;
+                }
             }
             float vdl = vc4.w / g.len;   // depth = |mc|
             vmc[0] += vdl * x; vmc[1] += vdl * y; vmc[2] += vdl * z;
@@ -784,6 +890,16 @@ __global__ void screen_pack_kernel(const float* xy, const float* depth, const fl
     r[2] = make_float4(rgb[3 * i], rgb[3 * i + 1], rgb[3 * i + 2], depth[i]);
 }
 
+// The (camera model, distortion tier) pairs of the reference's instantiation table
+// (src/kernels/projection/CameraVariants.cuh:11-22): every tier for the pinhole, OpenCV and thin prism for the two
+// fisheyes (no COLMAP fisheye model uses the rational tier), none for the equirectangular camera.
+static bool distortion_variant_built(int model, int tier) {
+    if (tier == SSB_DISTORTION_NONE) return true;
+    if (tier == SSB_DISTORTION_OPENCV || tier == SSB_DISTORTION_THIN_PRISM) return model != SSB_CAMERA_EQUIRECT;
+    if (tier == SSB_DISTORTION_RATIONAL) return model == SSB_CAMERA_PINHOLE;
+    return false;
+}
+
 static int check_shq(const SsbSplats* splats, const SsbShQuant* shq, SsbShQuant& out) {
     out = SsbShQuant{nullptr, nullptr, 32, 0, 256};
     if (shq && shq->packed && (shq->bits == 8 || shq->bits == 16)) {
@@ -808,22 +924,24 @@ int ssb_project_fwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, c
     if (cams->model != SSB_CAMERA_PINHOLE && cams->model != SSB_CAMERA_FISHEYE && cams->model != SSB_CAMERA_EQUISOLID && cams->model != SSB_CAMERA_EQUIRECT) {
         set_error("ssb_project_fwd: camera model %d not supported", cams->model); return SSB_ERR_UNSUPPORTED;
     }
-    if (cams->distortion != SSB_DISTORTION_NONE) {
-        set_error("ssb_project_fwd: lens-distortion tier %d is not built (only SSB_DISTORTION_NONE)", cams->distortion); return SSB_ERR_UNSUPPORTED;
+    if (!distortion_variant_built(cams->model, cams->distortion)) {
+        set_error("ssb_project_fwd: unsupported camera model / distortion tier (%d, %d)", cams->model, cams->distortion); return SSB_ERR_UNSUPPORTED;
     }
+    const DistArgs da = {cams->d_dist_coeffs, cams->distortion};
     SSB_REQUIRE((int64_t)cams->count * n < ((int64_t)1 << 31), "ssb_project_fwd: views * splats must fit int32 flatten ids");
     SsbShQuant q;
     int e = check_shq(splats, shq, q);
     if (e) return e;
     if (n == 0 || cams->count == 0) return SSB_OK;
     dim3 grid((unsigned)ceil_div(n, kProjBlock), (unsigned)cams->count);
-#define SSB_FWD(MODEL) project_fwd_kernel<MODEL, 0><<<grid, kProjBlock, 0, (cudaStream_t)stream>>>( \
+#define SSB_FWD(MODEL, DIST) project_fwd_kernel<MODEL, 0, DIST><<<grid, kProjBlock, 0, (cudaStream_t)stream>>>( \
         *splats, q, n, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased, \
-        (float4*)d_aabb, d_depths, d_radii, d_screen, PackArgs{})
-    if (cams->model == SSB_CAMERA_PINHOLE) SSB_FWD(SSB_CAMERA_PINHOLE);
-    else if (cams->model == SSB_CAMERA_FISHEYE) SSB_FWD(SSB_CAMERA_FISHEYE);
-    else if (cams->model == SSB_CAMERA_EQUISOLID) SSB_FWD(SSB_CAMERA_EQUISOLID);
-    else SSB_FWD(SSB_CAMERA_EQUIRECT);
+        (float4*)d_aabb, d_depths, d_radii, d_screen, PackArgs{}, da)
+    const bool dist = cams->distortion != SSB_DISTORTION_NONE;
+    if (cams->model == SSB_CAMERA_PINHOLE) { if (dist) SSB_FWD(SSB_CAMERA_PINHOLE, true); else SSB_FWD(SSB_CAMERA_PINHOLE, false); }
+    else if (cams->model == SSB_CAMERA_FISHEYE) { if (dist) SSB_FWD(SSB_CAMERA_FISHEYE, true); else SSB_FWD(SSB_CAMERA_FISHEYE, false); }
+    else if (cams->model == SSB_CAMERA_EQUISOLID) { if (dist) SSB_FWD(SSB_CAMERA_EQUISOLID, true); else SSB_FWD(SSB_CAMERA_EQUISOLID, false); }
+    else SSB_FWD(SSB_CAMERA_EQUIRECT, false);
 #undef SSB_FWD
     SSB_LAUNCHED("project_fwd_kernel");
     return SSB_OK;
@@ -845,9 +963,11 @@ int launch_project_fwd_pack_pass(int pass, const SsbSplats* splats, const SsbShQ
     if (cams->model != SSB_CAMERA_PINHOLE && cams->model != SSB_CAMERA_FISHEYE && cams->model != SSB_CAMERA_EQUISOLID && cams->model != SSB_CAMERA_EQUIRECT) {
         set_error("ssb_project_fwd_packed: camera model %d not supported", cams->model); return SSB_ERR_UNSUPPORTED;
     }
-    if (cams->distortion != SSB_DISTORTION_NONE) {
-        set_error("ssb_project_fwd_packed: lens-distortion tier %d is not built (only SSB_DISTORTION_NONE)", cams->distortion); return SSB_ERR_UNSUPPORTED;
+    if (!distortion_variant_built(cams->model, cams->distortion)) {
+        set_error("ssb_project_fwd_packed: unsupported camera model / distortion tier (%d, %d)", cams->model, cams->distortion); return SSB_ERR_UNSUPPORTED;
     }
+    const DistArgs da = {cams->d_dist_coeffs, cams->distortion};
+    const bool dist = cams->distortion != SSB_DISTORTION_NONE;
     SSB_REQUIRE((int64_t)cams->count * n < ((int64_t)1 << 31), "ssb_project_fwd_packed: views * splats must fit int32");
     SsbShQuant q;
     int e = check_shq(splats, shq, q);
@@ -855,15 +975,15 @@ int launch_project_fwd_pack_pass(int pass, const SsbSplats* splats, const SsbShQ
     if (n == 0 || cams->count == 0) return SSB_OK;
     dim3 grid((unsigned)ceil_div(n, kProjBlock), (unsigned)cams->count);
     const PackArgs pk = {d_flags, d_camera_ids, d_gaussian_ids, capacity};
-#define SSB_FWDP(MODEL, PASS) project_fwd_kernel<MODEL, PASS><<<grid, kProjBlock, 0, (cudaStream_t)stream>>>( \
+#define SSB_FWDP(MODEL, PASS, DIST) project_fwd_kernel<MODEL, PASS, DIST><<<grid, kProjBlock, 0, (cudaStream_t)stream>>>( \
         *splats, q, n, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased, \
-        (float4*)d_aabb, d_depths, d_radii, d_screen, pk)
+        (float4*)d_aabb, d_depths, d_radii, d_screen, pk, da)
 #define SSB_FWDP_MODEL(PASS) \
     do { \
-        if (cams->model == SSB_CAMERA_PINHOLE) SSB_FWDP(SSB_CAMERA_PINHOLE, PASS); \
-        else if (cams->model == SSB_CAMERA_FISHEYE) SSB_FWDP(SSB_CAMERA_FISHEYE, PASS); \
-        else if (cams->model == SSB_CAMERA_EQUISOLID) SSB_FWDP(SSB_CAMERA_EQUISOLID, PASS); \
-        else SSB_FWDP(SSB_CAMERA_EQUIRECT, PASS); \
+        if (cams->model == SSB_CAMERA_PINHOLE) { if (dist) SSB_FWDP(SSB_CAMERA_PINHOLE, PASS, true); else SSB_FWDP(SSB_CAMERA_PINHOLE, PASS, false); } \
+        else if (cams->model == SSB_CAMERA_FISHEYE) { if (dist) SSB_FWDP(SSB_CAMERA_FISHEYE, PASS, true); else SSB_FWDP(SSB_CAMERA_FISHEYE, PASS, false); } \
+        else if (cams->model == SSB_CAMERA_EQUISOLID) { if (dist) SSB_FWDP(SSB_CAMERA_EQUISOLID, PASS, true); else SSB_FWDP(SSB_CAMERA_EQUISOLID, PASS, false); } \
+        else SSB_FWDP(SSB_CAMERA_EQUIRECT, PASS, false); \
     } while (0)
     if (pass == 1) SSB_FWDP_MODEL(1); else SSB_FWDP_MODEL(2);
 #undef SSB_FWDP_MODEL
@@ -881,9 +1001,11 @@ int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n
     if (cams->model != SSB_CAMERA_PINHOLE && cams->model != SSB_CAMERA_FISHEYE && cams->model != SSB_CAMERA_EQUISOLID && cams->model != SSB_CAMERA_EQUIRECT) {
         set_error("ssb_project_bwd: camera model %d not supported", cams->model); return SSB_ERR_UNSUPPORTED;
     }
-    if (cams->distortion != SSB_DISTORTION_NONE) {
-        set_error("ssb_project_bwd: lens-distortion tier %d is not built (only SSB_DISTORTION_NONE)", cams->distortion); return SSB_ERR_UNSUPPORTED;
+    if (!distortion_variant_built(cams->model, cams->distortion)) {
+        set_error("ssb_project_bwd: unsupported camera model / distortion tier (%d, %d)", cams->model, cams->distortion); return SSB_ERR_UNSUPPORTED;
     }
+    const DistArgs da = {cams->d_dist_coeffs, cams->distortion};
+    const bool dist = cams->distortion != SSB_DISTORTION_NONE;
     SsbShQuant q;
     int e = check_shq(splats, shq, q);
     if (e) return e;
@@ -891,14 +1013,20 @@ int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n
     SSB_REQUIRE(range_first >= 0 && range_first + range_count <= n && range_first % kProjBlock == 0, "ssb_project_bwd: bad splat range");
     if (range_count == 0) return SSB_OK;
     const int64_t range_end = range_first + range_count;
-#define SSB_BWD(MULTI, MODEL) project_bwd_kernel<MULTI, MODEL><<<(unsigned)ceil_div(range_count, kProjBlock), kProjBlock, 0, (cudaStream_t)stream>>>( \
+#define SSB_BWD(MULTI, MODEL, DIST) project_bwd_kernel<MULTI, MODEL, DIST><<<(unsigned)ceil_div(range_count, kProjBlock), kProjBlock, 0, (cudaStream_t)stream>>>( \
         *splats, q, n, cams->count, cams->d_viewmats, cams->d_intrins, cams->width, cams->height, cams->antialiased, \
-        (const float4*)d_aabb, d_v_screen, *grads, accumulate, clear_v_screen, d_pair_of, range_first, range_end)
+        (const float4*)d_aabb, d_v_screen, *grads, accumulate, clear_v_screen, d_pair_of, range_first, range_end, da)
+#define SSB_BWD_MODEL(MODEL) \
+    do { \
+        if (dist) { if (multi) SSB_BWD(true, MODEL, true); else SSB_BWD(false, MODEL, true); } \
+        else { if (multi) SSB_BWD(true, MODEL, false); else SSB_BWD(false, MODEL, false); } \
+    } while (0)
     const bool multi = cams->count != 1;
-    if (cams->model == SSB_CAMERA_PINHOLE) { if (multi) SSB_BWD(true, SSB_CAMERA_PINHOLE); else SSB_BWD(false, SSB_CAMERA_PINHOLE); }
-    else if (cams->model == SSB_CAMERA_FISHEYE) { if (multi) SSB_BWD(true, SSB_CAMERA_FISHEYE); else SSB_BWD(false, SSB_CAMERA_FISHEYE); }
-    else if (cams->model == SSB_CAMERA_EQUISOLID) { if (multi) SSB_BWD(true, SSB_CAMERA_EQUISOLID); else SSB_BWD(false, SSB_CAMERA_EQUISOLID); }
-    else { if (multi) SSB_BWD(true, SSB_CAMERA_EQUIRECT); else SSB_BWD(false, SSB_CAMERA_EQUIRECT); }
+    if (cams->model == SSB_CAMERA_PINHOLE) SSB_BWD_MODEL(SSB_CAMERA_PINHOLE);
+    else if (cams->model == SSB_CAMERA_FISHEYE) SSB_BWD_MODEL(SSB_CAMERA_FISHEYE);
+    else if (cams->model == SSB_CAMERA_EQUISOLID) SSB_BWD_MODEL(SSB_CAMERA_EQUISOLID);
+    else { if (multi) SSB_BWD(true, SSB_CAMERA_EQUIRECT, false); else SSB_BWD(false, SSB_CAMERA_EQUIRECT, false); }
+#undef SSB_BWD_MODEL
 #undef SSB_BWD
     SSB_LAUNCHED("project_bwd_kernel");
     return SSB_OK;

@@ -64,6 +64,8 @@ struct SsbStep {
     float* accum_weight_den;
     int64_t* max_pairs;       // device: largest per-view pair count since it was last cleared
     float* radii;             // caller's [n] running maximum of the splats' view radii (ssb_step_set_radii), or nullptr
+    int32_t dist_tier;        // lens-distortion tier of the cameras and the rows of the next call's views (ssb_step_set_distortion)
+    const float* dist_coeffs;
     // deferred backward (ssb_step_set_fused_backward): every view's aabb and screen-gradient records are kept, and the
     // projection backward of all views runs together with the optimiser, a range of splats at a time
     int def_max_views, def_count, def_last;      // def_last: slice of the last view rendered (for ssb_step_peek)
@@ -146,6 +148,8 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
     cam.d_intrins = d_intrins + 4 * (int64_t)v;
     cam.count = 1; cam.width = W; cam.height = H;
     cam.model = s->cfg.camera_model; cam.antialiased = s->cfg.antialiased;
+    cam.distortion = s->dist_tier;
+    cam.d_dist_coeffs = s->dist_coeffs ? s->dist_coeffs + 8 * (int64_t)v : nullptr;
     int e;
 #define SSB_MARK(k) do { if (ev) SSB_CUDA(cudaEventRecord(ev[k], st)); } while (0)
     SSB_MARK(0);
@@ -245,6 +249,19 @@ int ssb_step_set_radii(SsbStep* s, float* d_radii) {
     using namespace ssb;
     SSB_REQUIRE(s, "ssb_step_set_radii: NULL step");
     s->radii = d_radii;
+    return SSB_OK;
+}
+
+int ssb_step_set_distortion(SsbStep* s, int32_t tier, const float* d_dist_coeffs) {
+    using namespace ssb;
+    SSB_REQUIRE(s, "ssb_step_set_distortion: NULL step");
+    const int model = s->cfg.camera_model;
+    const bool built = tier == SSB_DISTORTION_NONE ||
+                       ((tier == SSB_DISTORTION_OPENCV || tier == SSB_DISTORTION_THIN_PRISM) && model != SSB_CAMERA_EQUIRECT) ||
+                       (tier == SSB_DISTORTION_RATIONAL && model == SSB_CAMERA_PINHOLE);
+    if (!built) { set_error("ssb_step_set_distortion: unsupported camera model / distortion tier (%d, %d)", model, tier); return SSB_ERR_UNSUPPORTED; }
+    s->dist_tier = tier;
+    s->dist_coeffs = tier == SSB_DISTORTION_NONE ? nullptr : d_dist_coeffs;
     return SSB_OK;
 }
 
@@ -404,6 +421,7 @@ int ssb_step_backward_optimize(SsbStep* s, const SsbSplats* params, const SsbShQ
     SsbCameras cams{};
     cams.d_viewmats = d_viewmats; cams.d_intrins = d_intrins; cams.count = n_views;
     cams.width = s->cfg.width; cams.height = s->cfg.height; cams.model = s->cfg.camera_model; cams.antialiased = s->cfg.antialiased;
+    cams.distortion = s->dist_tier; cams.d_dist_coeffs = s->dist_coeffs;
     const int64_t range = std::min(kFusedRange, align_up(n, 256));
     const int64_t scratch_floats = 6 * 64 + range * 59;
     SsbAdamConfig c = *cfg;

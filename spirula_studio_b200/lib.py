@@ -19,6 +19,7 @@ SSB_ERR_UNSUPPORTED = -5
 SSB_ERR_PEER = -6
 SSB_ERR_IO = -7
 
+DISTORTION_NONE, DISTORTION_OPENCV, DISTORTION_THIN_PRISM, DISTORTION_RATIONAL = 0, 1, 2, 3
 CAMERA_PINHOLE, CAMERA_FISHEYE, CAMERA_EQUISOLID, CAMERA_EQUIRECT = 0, 1, 2, 3
 SSB_ACCUM_NONE, SSB_ACCUM_MAX, SSB_ACCUM_SUM, SSB_ACCUM_AVG = 0, 1, 2, 3
 STATUS_BAD_INDEX, STATUS_PAIRS_DROPPED = 1, 2
@@ -138,6 +139,7 @@ SIGNATURES = {
     "ssb_loss_multi_scale": (C.c_int, [_P, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P, _I64, _P]),
     "ssb_step_set_loss": (C.c_int, [_P, _P]),
     "ssb_step_set_radii": (C.c_int, [_P, _P]),
+    "ssb_step_set_distortion": (C.c_int, [_P, _I32, _P]),
     "ssb_step_set_fused_backward": (C.c_int, [_P, _I32]),
     "ssb_step_backward_optimize": (C.c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _P]),
     "ssb_adam_step_q16": (C.c_int, [_P, _P, _P, _I64, _I64, _P, _P, _P]),
@@ -311,10 +313,13 @@ def device_bytes_tensor(address, nbytes, device):
     return torch.as_tensor(_DevicePtr(address, nbytes), device=device)
 
 
-def cameras_struct(viewmats, intrins, width, height, model=CAMERA_PINHOLE, antialiased=0, count=None):
+def cameras_struct(viewmats, intrins, width, height, model=CAMERA_PINHOLE, antialiased=0, count=None, distortion=0, dist_coeffs=None):
+    """dist_coeffs: device float32 [count][8] rows of the distortion tier (DISTORTION_*), or None for zeros."""
     c = SsbCameras()
     c.d_viewmats = viewmats.data_ptr()
     c.d_intrins = intrins.data_ptr()
     c.count = int(viewmats.shape[0]) if count is None else count
     c.width, c.height, c.model, c.antialiased = width, height, model, antialiased
+    c.distortion = distortion
+    c.d_dist_coeffs = dist_coeffs.data_ptr() if dist_coeffs is not None else None
     return c

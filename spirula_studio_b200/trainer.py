@@ -304,6 +304,21 @@ class Trainer:
             L.check(self.lib.ssb_step_set_fused_backward(self.handle, total))
             self._fused_room = total
 
+    def set_distortion(self, tier, coeffs=None, kind=0):
+        """Lens-distortion tier (lib.DISTORTION_*) of the cameras of `kind` with one row of eight coefficients per view, in the
+        order of the views handed to each following train_step / views_fwd_bwd call (call again before handing other views).
+        coeffs: numpy or tensor [views][8] in the tier's own order, or None for zeros."""
+        if self.fused_backward and tier != L.DISTORTION_NONE:
+            raise NotImplementedError("lens distortion runs with the per-view backward")
+        rows = None
+        if tier != L.DISTORTION_NONE and coeffs is not None:
+            rows = torch.as_tensor(np.ascontiguousarray(coeffs, dtype=np.float32) if not torch.is_tensor(coeffs) else coeffs,
+                                   dtype=torch.float32).reshape(-1, 8).to(self.device).contiguous()
+        if not hasattr(self, "_dist_rows"):
+            self._dist_rows = {}
+        self._dist_rows[kind] = rows                     # keeps the device rows alive
+        L.check(self.lib.ssb_step_set_distortion(self.handles[kind], int(tier), L.ptr(rows) if rows is not None else None))
+
     def views_fwd_bwd(self, d_viewmats, d_intrins, d_gt, n_views, accumulate=False, stream=None, kind=0):
         """Forward + loss + backward of n_views views (all of camera kind `kind`) already resident on the device."""
         if self.fused_backward:

@@ -79,6 +79,36 @@ def accum_weight_map(name, n_pixels):
     return w
 
 
+# Lens distortion tiers: the (camera model, tier) pairs the reference instantiates, each on the scene of the undistorted
+# fixture of the same model.  tier: 1 OpenCV (k1 k2 p1 p2), 2 thin prism (k1 k2 k3 k4 p1 p2 sx1 sy1), 3 rational
+# (k1 k2 k3 k4 k5 k6 p1 p2).  Coefficients are strong enough that part of the image fails the reference's validity test
+# of the distortion map, and each view gets its own row.
+DIST_CASES = {
+    "pinhole_opencv": dict(scene="ring2", model=0, tier=1, coeffs=[-1.5, 0.3, 0.004, -0.003, 0, 0, 0, 0]),     # strong barrel: folds at the edges
+    "pinhole_thinprism": dict(scene="ring2", model=0, tier=2, coeffs=[0.12, -0.03, 0.01, -0.002, 0.003, -0.002, 0.004, -0.003]),
+    "pinhole_rational": dict(scene="ring2", model=0, tier=3, coeffs=[2.5, 0.5, 0.006, 0.3, 0.01, -0.002, 0.003, -0.002]),
+    "fisheye_opencv": dict(scene="wide_fisheye", model=1, tier=1, coeffs=[0.04, -0.006, 0.003, -0.002, 0, 0, 0, 0]),
+    "fisheye_thinprism": dict(scene="wide_fisheye", model=1, tier=2, coeffs=[0.03, -0.004, 0.0006, -0.00005, 0.002, -0.003, 0.004, 0.002]),
+    "equisolid_opencv": dict(scene="wide_equisolid", model=2, tier=1, coeffs=[0.05, 0.01, -0.003, 0.002, 0, 0, 0, 0]),
+    "equisolid_thinprism": dict(scene="wide_equisolid", model=2, tier=2, coeffs=[-0.04, 0.01, 0.002, 0.0003, 0.003, 0.002, -0.004, 0.003]),
+}
+
+
+def dist_case_inputs(name):
+    """(cfg, splats, viewmats, intrins, model, tier, coeffs [views][8], screen-space cotangents) of a DIST_CASES entry."""
+    c = DIST_CASES[name]
+    cfg, sp, vm, K = build_case(c["scene"])
+    views = vm.shape[0]
+    rows = np.array([c["coeffs"]] * views, np.float32)
+    rows *= (1.0 - 0.25 * np.arange(views, dtype=np.float32))[:, None]      # later views: weaker lenses
+    rng = np.random.default_rng(900 + sorted(DIST_CASES).index(name))
+    m = views * cfg.n_splats
+    v = dict(v_xy=rng.normal(size=(m, 2)).astype(np.float32), v_depth=(0.1 * rng.normal(size=m)).astype(np.float32),
+             v_conic=(0.05 * rng.normal(size=(m, 3))).astype(np.float32), v_opac=rng.normal(size=m).astype(np.float32),
+             v_rgb=rng.normal(size=(m, 3)).astype(np.float32))
+    return cfg, sp, vm, K, c["model"], c["tier"], rows, v
+
+
 ACCUM_CASES = ("ring2", "dense1")
 
 # Quantised SH storage read by the projection (forward and backward): 8- or 16-bit codes with (min, max) bounds

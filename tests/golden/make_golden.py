@@ -5,7 +5,7 @@ oracle/Makefile.ref) on a GPU, on small seeded scenes.
     python tests/golden/make_golden.py [out_dir [fixture ...]]
 
 With fixture names (ring2, dense1, wide_fisheye, wide_equisolid, wide_equirect, ssim, ssim_map, adam, accum, quant_proj,
-packed_proj) only those are written; accum, quant_proj and packed_proj read the committed ring2.npz / dense1.npz.
+packed_proj, dist_proj, ...) only those are written; accum, quant_proj and packed_proj read the committed ring2.npz / dense1.npz.
 
 Inputs are not stored: they are regenerated from `golden_cases.py` (same seeds).
 Every stage is run stage-isolated on the reference's own upstream outputs, so a
@@ -24,7 +24,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, HERE)
 
-from golden_cases import (ACCUM_CASES, CASES, DENSIFY_SCORE_RUNS, DENSIFY_SPLIT, LIVE_TILE_CASE, LOSS_MAP_WEIGHT, MULTI_SCALE_RUNS, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
+from golden_cases import (ACCUM_CASES, CASES, DENSIFY_SCORE_RUNS, DIST_CASES, dist_case_inputs, DENSIFY_SPLIT, LIVE_TILE_CASE, LOSS_MAP_WEIGHT, MULTI_SCALE_RUNS, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
                           build_case, densify_inputs, densify_split_inputs, loss_inputs, loss_map_base, loss_masks, quant_sh_inputs, raster_cotangents, tile_masks)  # noqa: E402
 
 DEV = "cuda:0"
@@ -497,6 +497,37 @@ def run_quant_proj(ref, out_dir):
     np.savez_compressed(os.path.join(out_dir, "quant_proj.npz"), **out)
 
 
+def run_dist_proj(ref, out_dir):
+    """Projection forward and backward of the reference's kernels with a lens-distortion tier, for every (camera model,
+    tier) pair it instantiates: all forward outputs, and the six gradient arrays for seeded screen-space cotangents."""
+    out = {}
+    for name in DIST_CASES:
+        cfg, sp, vm, K, model, tier, rows, v = dist_case_inputs(name)
+        n, W, H, I = cfg.n_splats, cfg.width, cfg.height, vm.shape[0]
+        m = I * n
+        d = {k: dev(val.reshape(-1)) for k, val in sp.items()}
+        d_vm, d_K, d_rows = dev(vm), dev(K), dev(rows)
+        z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=DEV)
+        aabb, depths, radii = z(m, 4), z(m), z(n)
+        xy, depth, conic, opac, rgb = z(m, 2), z(m), z(m, 3), z(m), z(m, 3)
+        check(ref.ref_project_fwd_dist(model, tier, I, n, W, H, P(d["means"]), P(d["quats"]), P(d["scales"]), P(d["opacities"]), P(d["features_dc"]),
+                                       P(d["features_sh"]), P(d_vm), P(d_K), P(d_rows), P(aabb), P(depths), P(radii),
+                                       P(xy), P(depth), P(conic), P(opac), P(rgb)), "ref_project_fwd_dist " + name)
+        for k, t in dict(aabb=aabb, depths=depths, radii=radii, xy=xy, depth=depth, conic=conic, opac=opac, rgb=rgb).items():
+            out[f"{name}_{k}"] = t.cpu().numpy()
+        dv = {k: dev(val) for k, val in v.items()}
+        g = {k: torch.zeros_like(t) for k, t in d.items()}
+        check(ref.ref_project_bwd_dist(model, tier, I, n, W, H, P(d["means"]), P(d["quats"]), P(d["scales"]), P(d["opacities"]), P(d["features_dc"]),
+                                       P(d["features_sh"]), P(d_vm), P(d_K), P(d_rows), P(aabb),
+                                       P(dv["v_xy"]), P(dv["v_depth"]), P(dv["v_conic"]), P(dv["v_opac"]), P(dv["v_rgb"]),
+                                       P(g["means"]), P(g["quats"]), P(g["scales"]), P(g["opacities"]), P(g["features_dc"]), P(g["features_sh"])),
+              "ref_project_bwd_dist " + name)
+        for k, t in g.items():
+            out[f"{name}_g_{k}"] = t.cpu().numpy()
+        print(name, "visible", int((aabb[:, 2] > aabb[:, 0]).sum().item()), "of", m)
+    np.savez_compressed(os.path.join(out_dir, "dist_proj.npz"), **out)
+
+
 def run_packed_proj(ref, out_dir):
     """The reference's packed projection (mask, scan, compacting kernel) and the packed mode of its projection backward
     kernel on two scenes, fp32 SH and one quantised layout: ids, count and the packed outputs; the backward pass takes the
@@ -555,6 +586,8 @@ def main():
         run_loss(ref, out_dir)
     if not only or "adam" in only:
         run_adam(ref, out_dir)
+    if not only or "dist_proj" in only:
+        run_dist_proj(ref, out_dir)
     if not only or "ssim_map" in only:
         run_loss_map(ref, out_dir)
     if not only or "ssim_masked" in only:

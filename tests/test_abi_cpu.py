@@ -64,9 +64,12 @@ def test_argument_errors_are_statuses_not_crashes():
     sp = L.SsbSplats()
     sp.features_sh = 8
     assert lib.ssb_project_fwd(C.byref(sp), None, 0, C.byref(cams), one, one, None, one, None) == L.SSB_ERR_UNSUPPORTED
-    # a lens-distortion tier is refused, not silently rendered without distortion
-    cams.model, cams.distortion = L.CAMERA_PINHOLE, 1
-    assert lib.ssb_project_fwd(C.byref(sp), None, 0, C.byref(cams), one, one, None, one, None) == L.SSB_ERR_UNSUPPORTED
+    # (camera model, lens-distortion tier) pairs outside the reference's instantiation table are refused, as it refuses them
+    for model, tier, want in ((L.CAMERA_PINHOLE, L.DISTORTION_RATIONAL, L.SSB_OK), (L.CAMERA_FISHEYE, L.DISTORTION_THIN_PRISM, L.SSB_OK),
+                              (L.CAMERA_FISHEYE, L.DISTORTION_RATIONAL, L.SSB_ERR_UNSUPPORTED), (L.CAMERA_EQUIRECT, L.DISTORTION_OPENCV, L.SSB_ERR_UNSUPPORTED),
+                              (L.CAMERA_PINHOLE, 4, L.SSB_ERR_UNSUPPORTED)):
+        cams.model, cams.distortion = model, tier
+        assert lib.ssb_project_fwd(C.byref(sp), None, 0, C.byref(cams), one, one, None, one, None) == want, (model, tier)
     assert b"distortion" in lib.ssb_last_error_string()
     # loss configuration
     bad = L.SsbLossConfig(0.8, 0.2, 0, 0, None, 0, 0)

@@ -15,7 +15,7 @@ import pytest
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 
-from golden_cases import (ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
+from golden_cases import (DIST_CASES, dist_case_inputs, ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
                           build_case, loss_inputs, loss_map_base, quant_sh_inputs, raster_cotangents)  # noqa: E402
 
 
@@ -148,6 +148,32 @@ def test_quantised_sh_projection_vs_reference(oracle, tag):
     g = oracle.project_bwd(sp, vm, K, cfg.width, cfg.height, ref_aabb, v, shq=shq)
     for k in g:
         ref = gold[f"{tag}_g_{k}"].reshape(g[k].shape)
+        assert frac_bad(g[k], ref, 1e-4 * np.abs(ref).max(), 2e-3) <= 5e-3, k
+
+
+@pytest.mark.parametrize("name", sorted(DIST_CASES))
+def test_lens_distortion_projection_vs_reference(oracle, name):
+    """Projection forward and backward with a lens-distortion tier, every (camera model, tier) pair the reference
+    instantiates, against its kernels: visible set, all forward outputs, the six gradient arrays."""
+    cfg, sp, vm, K, model, tier, rows, v = dist_case_inputs(name)
+    gold = load("dist_proj")
+    base = load(DIST_CASES[name]["scene"])
+    got = oracle.project_fwd(sp, vm, K, cfg.width, cfg.height, model=model, dist=tier, dist_coeffs=rows)
+    ref_aabb = gold[f"{name}_aabb"]
+    keep_ref, keep_got = ref_aabb[:, 2] > ref_aabb[:, 0], got["aabb"][:, 2] > got["aabb"][:, 0]
+    keep_base = base["aabb"][:, 2] > base["aabb"][:, 0]
+    assert keep_ref.sum() > 100
+    if name != "pinhole_thinprism":                    # (a mild lens: every splat stays valid)
+        assert (keep_ref != keep_base).sum() > 10      # the lens changes what is seen
+    assert (keep_ref != keep_got).mean() <= 2e-3
+    both = keep_ref & keep_got
+    assert np.abs(gold[f"{name}_xy"][both & keep_base] - base["xy"][both & keep_base]).max() > 0.5      # and where
+    for k in ("aabb", "depths", "xy", "depth", "conic", "opac", "rgb"):
+        assert frac_bad(got[k][both], gold[f"{name}_{k}"][both], 5e-3, 5e-4) <= 2e-3, k
+    assert frac_bad(got["radii"], gold[f"{name}_radii"], 1e-4, 1e-3) <= 2e-3
+    g = oracle.project_bwd(sp, vm, K, cfg.width, cfg.height, ref_aabb, v, model=model, dist=tier, dist_coeffs=rows)
+    for k in g:
+        ref = gold[f"{name}_g_{k}"].reshape(g[k].shape)
         assert frac_bad(g[k], ref, 1e-4 * np.abs(ref).max(), 2e-3) <= 5e-3, k
 
 

@@ -13,7 +13,7 @@ torch = pytest.importorskip("torch")
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 
-from golden_cases import (ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
+from golden_cases import (DIST_CASES, dist_case_inputs, ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
                           build_case, loss_inputs, loss_map_base, quant_sh_inputs, raster_cotangents)  # noqa: E402
 from spirula_studio_b200 import lib as L  # noqa: E402
 
@@ -175,6 +175,77 @@ def test_quantised_sh_projection_vs_reference(lib, U, tag):
         ref = gold[f"{tag}_g_{k}"]
         assert U.close_frac(grads[k].cpu().numpy().reshape(-1), ref.reshape(-1), 1e-4 * np.abs(ref).max(), 2e-3) <= 5e-3, k
     del keep_alive
+
+
+@pytest.mark.parametrize("name", sorted(DIST_CASES))
+def test_lens_distortion_projection_vs_reference(lib, U, name):
+    """ssb_project_fwd / ssb_project_bwd with a lens-distortion tier (SsbCameras::distortion, d_dist_coeffs) against the
+    reference's kernels for every (camera model, tier) pair it instantiates; the packed forward pass agrees with the
+    unpacked one, and a pair outside the reference's table is refused."""
+    cfg, sp, vm, K, model, tier, rows, v = dist_case_inputs(name)
+    gold = load("dist_proj")
+    I, n, W, H = vm.shape[0], cfg.n_splats, cfg.width, cfg.height
+    m = I * n
+    spd = U.splats_dev(sp)
+    d_vm, d_K, d_rows = U.dev(vm), U.dev(K), U.dev(rows)
+    cams = L.cameras_struct(d_vm, d_K, W, H, model=model, distortion=tier, dist_coeffs=d_rows)
+    aabb, depths, radii = torch.zeros(m, 4, device=U.DEV), torch.zeros(m, device=U.DEV), torch.zeros(n, device=U.DEV)
+    rec = torch.zeros(m * L.SCREEN_REC_FLOATS, device=U.DEV)
+    s = L.splats_struct(spd)
+    L.check(lib.ssb_project_fwd(C.byref(s), None, n, C.byref(cams), L.ptr(aabb), L.ptr(depths), L.ptr(radii), L.ptr(rec), None))
+    torch.cuda.synchronize()
+    h_aabb, ref_aabb = aabb.cpu().numpy(), gold[f"{name}_aabb"]
+    keep_ref, keep_got = ref_aabb[:, 2] > ref_aabb[:, 0], h_aabb[:, 2] > h_aabb[:, 0]
+    assert keep_ref.sum() > 100 and (keep_ref != keep_got).mean() <= 2e-3
+    both = keep_ref & keep_got
+    scr = U.unpack_screen(lib, rec, m)
+    assert U.close_frac(h_aabb[both], ref_aabb[both], 5e-3, 5e-4) <= 2e-3
+    assert U.close_frac(depths.cpu().numpy()[both], gold[f"{name}_depths"][both], 5e-3, 5e-4) <= 2e-3
+    for k in ("xy", "depth", "conic", "opac", "rgb"):
+        assert U.close_frac(scr[k][both], gold[f"{name}_{k}"][both], 5e-3, 5e-4) <= 2e-3, k
+    assert U.close_frac(radii.cpu().numpy(), gold[f"{name}_radii"], 1e-4, 1e-3) <= 2e-3
+    # backward on the reference's visible set
+    grads = {k: torch.zeros_like(t) for k, t in spd.items()}
+    g = L.splats_struct(grads)
+    vrec = U.arrays_to_vrec(v, m)
+    d_ref_aabb = U.dev(ref_aabb)
+    L.check(lib.ssb_project_bwd(C.byref(s), None, n, C.byref(cams), L.ptr(d_ref_aabb), L.ptr(vrec), C.byref(g), 0, None))
+    torch.cuda.synchronize()
+    for k in grads:
+        ref = gold[f"{name}_g_{k}"]
+        assert U.close_frac(grads[k].cpu().numpy().reshape(-1), ref.reshape(-1), 1e-4 * np.abs(ref).max(), 2e-3) <= 5e-3, k
+    # one view at a time (the single-view kernel variant) gives the same gradients
+    if I > 1:
+        grads1 = {k: torch.zeros_like(t) for k, t in spd.items()}
+        g1 = L.splats_struct(grads1)
+        for view in range(I):
+            cams1 = L.cameras_struct(d_vm[view:view + 1], d_K[view:view + 1], W, H, model=model, distortion=tier, dist_coeffs=d_rows[view:view + 1])
+            L.check(lib.ssb_project_bwd(C.byref(s), None, n, C.byref(cams1), L.ptr(d_ref_aabb[view * n:(view + 1) * n]),
+                                        L.ptr(vrec[view * n * L.SCREEN_REC_FLOATS:]), C.byref(g1), 1, None))
+        torch.cuda.synchronize()
+        for k in grads:
+            a, b = grads1[k].cpu().numpy().reshape(-1), grads[k].cpu().numpy().reshape(-1)
+            assert U.close_frac(a, b, 1e-5 * np.abs(b).max(), 1e-4) <= 1e-3, k
+    # the packed forward pass keeps exactly the unpacked pass's visible pairs and values
+    cap = int(keep_got.sum()) + 5
+    ws = torch.zeros(max(lib.ssb_project_fwd_packed_workspace_bytes(n, I), 16), dtype=torch.uint8, device=U.DEV)
+    p_aabb, p_depths, p_radii = torch.zeros(cap, 4, device=U.DEV), torch.zeros(cap, device=U.DEV), torch.zeros(n, device=U.DEV)
+    p_rec = torch.zeros(cap * L.SCREEN_REC_FLOATS, device=U.DEV)
+    p_cam, p_gid = torch.zeros(cap, dtype=torch.int32, device=U.DEV), torch.zeros(cap, dtype=torch.int32, device=U.DEV)
+    n_vis, h_n = torch.zeros(1, dtype=torch.int64, device=U.DEV), C.c_int64(-1)
+    L.check(lib.ssb_project_fwd_packed(C.byref(s), None, n, C.byref(cams), L.ptr(ws), ws.numel(), L.ptr(p_aabb), L.ptr(p_depths), L.ptr(p_radii),
+                                       L.ptr(p_rec), L.ptr(p_cam), L.ptr(p_gid), cap, L.ptr(n_vis), C.byref(h_n), None))
+    torch.cuda.synchronize()
+    assert h_n.value == keep_got.sum()
+    where = np.nonzero(keep_got)[0]
+    assert np.array_equal(p_cam.cpu().numpy()[:h_n.value], where // n) and np.array_equal(p_gid.cpu().numpy()[:h_n.value], where % n)
+    assert torch.equal(p_aabb[:h_n.value], aabb[torch.from_numpy(where).to(U.DEV)])
+    # outside the reference's table
+    bad = L.cameras_struct(d_vm, d_K, W, H, model=L.CAMERA_EQUIRECT, distortion=tier, dist_coeffs=d_rows)
+    assert lib.ssb_project_fwd(C.byref(s), None, n, C.byref(bad), L.ptr(aabb), L.ptr(depths), L.ptr(radii), L.ptr(rec), None) == L.SSB_ERR_UNSUPPORTED
+    if model != 0:
+        bad = L.cameras_struct(d_vm, d_K, W, H, model=model, distortion=L.DISTORTION_RATIONAL, dist_coeffs=d_rows)
+        assert lib.ssb_project_bwd(C.byref(s), None, n, C.byref(bad), L.ptr(d_ref_aabb), L.ptr(vrec), C.byref(g), 0, None) == L.SSB_ERR_UNSUPPORTED
 
 
 @pytest.mark.parametrize("key", ["ring2", "dense1", "ring2_q16_cell"])

@@ -191,6 +191,53 @@ def test_projection_backward_wide_cameras(lib, U, oracle, model):
             assert U.close_frac(got[rows], want[k][rows], 1e-5 * scale, 1e-3) <= 2e-3, (k, views)
 
 
+def test_distorted_pinhole_with_the_jacobian_limit_active(lib, U, oracle):
+    """Pinhole + OpenCV tier on a wide cloud of large splats: many centres lie outside the 1.3x frustum, so the third
+    column of the Jacobian is limited (src/shaders/primitive_3dgs.slang:84-95) while d(mean2d)/d(mean) is not; forward and
+    backward against the oracle, several-view and single-view kernels."""
+    cfg, sp, vm, K = scene(n=6000, w=160, h=120, views=2, scale_mu=-1.2, extent=4.0)
+    W, H, n = cfg.width, cfg.height, cfg.n_splats
+    rows = np.array([[0.06, -0.01, 0.002, -0.001, 0, 0, 0, 0], [-0.05, 0.004, 0.001, 0.002, 0, 0, 0, 0]], np.float32)
+    ref_f = oracle.project_fwd(sp, vm, K, W, H, dist=L.DISTORTION_OPENCV, dist_coeffs=rows)
+    keep_ref = ref_f["aabb"][:, 2] > ref_f["aabb"][:, 0]
+    # how many visible splats have the limit active: centre more than 15 % of the width outside the image on x
+    out_x = (ref_f["xy"][:, 0] < -0.15 * W) | (ref_f["xy"][:, 0] > 1.15 * W)
+    assert (keep_ref & out_x).sum() > 50
+    spd = U.splats_dev(sp)
+    d_vm, d_K, d_rows = U.dev(vm), U.dev(K), U.dev(rows)
+    m = 2 * n
+    cams = L.cameras_struct(d_vm, d_K, W, H, distortion=L.DISTORTION_OPENCV, dist_coeffs=d_rows)
+    aabb, depths, radii = torch.zeros(m, 4, device=U.DEV), torch.zeros(m, device=U.DEV), torch.zeros(n, device=U.DEV)
+    rec = torch.zeros(m * L.SCREEN_REC_FLOATS, device=U.DEV)
+    s = L.splats_struct(spd)
+    L.check(lib.ssb_project_fwd(C.byref(s), None, n, C.byref(cams), L.ptr(aabb), L.ptr(depths), L.ptr(radii), L.ptr(rec), None))
+    torch.cuda.synchronize()
+    h_aabb = aabb.cpu().numpy()
+    keep_got = h_aabb[:, 2] > h_aabb[:, 0]
+    assert (keep_ref != keep_got).mean() <= 5e-4
+    both = keep_ref & keep_got
+    scr = U.unpack_screen(lib, rec, m)
+    assert U.close_frac(h_aabb[both], ref_f["aabb"][both], 5e-3, 5e-4) <= 5e-4
+    for k, (atol, rtol) in dict(xy=(2e-3, 1e-5), conic=(1e-5, 1e-3), opac=(1e-6, 1e-5)).items():
+        assert U.close_frac(scr[k][both], ref_f[k][both], atol, rtol) <= 5e-4, k
+    rng = np.random.default_rng(11)
+    v = dict(v_xy=rng.normal(size=(m, 2)), v_depth=rng.normal(size=m), v_conic=rng.normal(size=(m, 3)) * 0.05, v_opac=rng.normal(size=m),
+             v_rgb=rng.normal(size=(m, 3)))
+    v = {k: x.astype(np.float32) for k, x in v.items()}
+    d_aabb, vrec = U.dev(ref_f["aabb"]), U.arrays_to_vrec(v, m)
+    for views in (2, 1):
+        grads = {k: torch.full_like(t, 7.0) for k, t in spd.items()}
+        g = L.splats_struct(grads)
+        cams_v = L.cameras_struct(d_vm, d_K, W, H, count=views, distortion=L.DISTORTION_OPENCV, dist_coeffs=d_rows)
+        L.check(lib.ssb_project_bwd(C.byref(s), None, n, C.byref(cams_v), L.ptr(d_aabb), L.ptr(vrec), C.byref(g), 0, None))
+        torch.cuda.synchronize()
+        want = oracle.project_bwd(sp, vm[:views], K[:views], W, H, ref_f["aabb"][:views * n], {k: x[:views * n] for k, x in v.items()},
+                                  dist=L.DISTORTION_OPENCV, dist_coeffs=rows[:views])
+        for k in want:
+            got = grads[k].cpu().numpy().reshape(want[k].shape)
+            assert U.close_frac(got, want[k], 1e-5 * np.abs(want[k]).max(), 1e-3) <= 2e-3, (k, views)
+
+
 # ------------------------------------------------------- keys / sort / ranges
 @pytest.mark.parametrize("views,scale_mu", [(1, -3.5), (2, -3.0), (1, -2.0)])
 def test_tile_keys_bit_exact(lib, U, oracle, views, scale_mu):

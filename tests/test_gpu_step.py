@@ -142,18 +142,19 @@ def test_adam_quantized_state_fp32_values(lib, U, oracle):
         d_x.copy_(U.dev(x)); d_op.copy_(U.dev(op)); d_ob.copy_(U.dev(ob))
 
 
-def _oracle_iteration(oracle, cfg, sp, vm, K, targets, shq=None):
+def _oracle_iteration(oracle, cfg, sp, vm, K, targets, shq=None, dist=0, rows=None):
     """Gradients of one multi-view iteration, one camera per sub-batch, summed (reference split-batch loop)."""
     W, H, n = cfg.width, cfg.height, cfg.n_splats
     tot = None
     losses = np.zeros(3)
     renders = []
     for v in range(vm.shape[0]):
-        ch = oracle.forward_chain(sp, vm[v:v + 1], K[v:v + 1], W, H, shq=shq)
+        dr = None if rows is None else rows[v:v + 1]
+        ch = oracle.forward_chain(sp, vm[v:v + 1], K[v:v + 1], W, H, shq=shq, dist=dist, dist_coeffs=dr)
         vr, l = oracle.loss_l1_ssim(ch["render"]["rgb"], targets[v].reshape(-1, 3), 1, H, W, 0.8, 0.2)
         losses += l
         gs = oracle.raster_bwd(ch["proj"], ch["offsets"], ch["sorted_vals"], 1, n, W, H, ch["render"], vr)
-        g = oracle.project_bwd(sp, vm[v:v + 1], K[v:v + 1], W, H, ch["proj"]["aabb"], gs, shq=shq)
+        g = oracle.project_bwd(sp, vm[v:v + 1], K[v:v + 1], W, H, ch["proj"]["aabb"], gs, shq=shq, dist=dist, dist_coeffs=dr)
         tot = g if tot is None else {k: tot[k] + g[k] for k in g}
         renders.append(ch)
     return tot, losses, renders
@@ -213,6 +214,46 @@ def test_whole_iteration_matches_oracle(lib, U, oracle, quant):
     tr2 = Trainer(cfg, sp, device=U.DEV)
     l1, ssim, loss = tr2.train_step(h_vm, h_K, h_gt, cfg.n_views)
     assert abs(loss - ref_l[2] / cfg.n_views) <= 1e-3 * abs(ref_l[2] / cfg.n_views) + 1e-5
+    tr.close(); tr2.close()
+
+
+def test_iteration_with_lens_distortion_matches_oracle(lib, U, oracle):
+    """The step object with a distortion tier (Trainer.set_distortion -> ssb_step_set_distortion): three pinhole views, each with
+    its own thin-prism row, device-resident and host-buffer entry points, against the oracle's iteration."""
+    from spirula_studio_b200.trainer import Trainer
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=9000, width=176, height=128, n_views=3)
+    cfg.rig, cfg.rig_radius, cfg.log_scale_mu = "ring", 3.0, -3.0
+    sp = scenes.make_splats(cfg)
+    vm, K = scenes.make_cameras(cfg)
+    targets = np.stack([scenes.make_target(cfg, v) for v in range(cfg.n_views)])
+    rows = np.array([[0.3, -0.08, 0.01, -0.002, 0.004, -0.003, 0.005, -0.004],
+                     [-0.4, 0.05, 0.0, 0.001, -0.002, 0.003, -0.004, 0.002],
+                     [0.1, 0.0, 0.0, 0.0, 0.01, 0.01, 0.0, 0.0]], np.float32)
+    ref_g, ref_l, renders = _oracle_iteration(oracle, cfg, sp, vm, K, targets, dist=L.DISTORTION_THIN_PRISM, rows=rows)
+    plain_g, plain_l, _ = _oracle_iteration(oracle, cfg, sp, vm, K, targets)
+    assert abs(plain_l[2] - ref_l[2]) > 1e-3 * abs(ref_l[2])                  # the lens matters in this scene
+    tr = Trainer(cfg, sp, device=U.DEV)
+    tr.set_distortion(L.DISTORTION_THIN_PRISM, rows)
+    h_vm, h_K, h_gt = (torch.from_numpy(a).pin_memory() for a in (vm, K, targets))
+    tr.losses.zero_()
+    tr.views_fwd_bwd(h_vm.to(U.DEV), h_K.to(U.DEV), h_gt.to(U.DEV), cfg.n_views)
+    torch.cuda.synchronize()
+    assert np.allclose(tr.losses.cpu().numpy(), ref_l, rtol=1e-3, atol=1e-5)
+    for k in ref_g:
+        got = tr.grads[k].cpu().numpy().reshape(ref_g[k].shape)
+        assert U.close_frac(got, ref_g[k], 2e-5 * np.abs(ref_g[k]).max(), 1e-3) <= 5e-3, k
+    tr2 = Trainer(cfg, sp, device=U.DEV)
+    tr2.set_distortion(L.DISTORTION_THIN_PRISM, rows)
+    l1, ssim, loss = tr2.train_step(h_vm, h_K, h_gt, cfg.n_views)
+    assert abs(loss - ref_l[2] / cfg.n_views) <= 1e-3 * abs(ref_l[2] / cfg.n_views) + 1e-5
+    # back to no distortion: the plain iteration again
+    tr.set_distortion(L.DISTORTION_NONE)          # (tr has not taken an optimiser step)
+    tr.losses.zero_()
+    tr.views_fwd_bwd(h_vm.to(U.DEV), h_K.to(U.DEV), h_gt.to(U.DEV), cfg.n_views)
+    torch.cuda.synchronize()
+    assert np.allclose(tr.losses.cpu().numpy(), plain_l, rtol=1e-3, atol=1e-5)
+    # a pair the projection does not build is refused when it is set
+    assert lib.ssb_step_set_distortion(tr.handle, 7, None) == L.SSB_ERR_UNSUPPORTED
     tr.close(); tr2.close()
 
 

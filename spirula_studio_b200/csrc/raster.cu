@@ -4,27 +4,20 @@
 // src/kernels/raster/RasterizationEval3DBwd_kernel.cuh:48-636 (2D variant) with
 // the fragment math of src/primitives/Primitive3DGS.cuh:250-300.
 //
-// Forward: one 256-thread CTA per tile, one thread per pixel, warp w owning an
-// 8x4 pixel rectangle.  The tile's list is staged 256 records at a time in
-// shared memory (one 48-byte gather per thread); each warp then ballots the
-// staged records against its own rectangle using the record's alpha >= 1/255
-// half extents and walks only the records that can touch it, with a warp-wide
+// Forward: one 128-thread CTA per tile, warp w owning an 8x8 micro-tile and a lane two of its pixels.  The tile's list is
+// staged 256 records at a time in shared memory (48-byte gathers); each warp then ballots the staged records against its
+// own micro-tile using the record's alpha >= 1/255 ellipse and walks only the records that can touch it, with a warp-wide
 // early exit once every lane's transmittance is spent.
 //
-// Backward: one warp per 8x8 micro-tile, thread = splat.  The warp scans the
-// tile list back to front (starting at the largest last-blended index of its
-// pixels), keeps the records whose alpha >= 1/255 ellipse reaches the
-// micro-tile, and sweeps them 32 at a time diagonally across the 64 pixels whose
-// running (T, dL/dT) live in shared memory: lane l holds survivor l of the batch
-// and at step t works on pixel t-l, so each pixel meets the survivors strictly
-// back to front.  A splat's ten gradient
-// components accumulate in registers and leave as three 16-byte vector
-// reductions per (splat, micro-tile) -- no per-pixel atomics.
+// Backward: one warp per 8x8 micro-tile.  The warp scans the tile list back to front (starting at the largest
+// last-blended index of its pixels), keeps the records whose alpha >= 1/255 ellipse reaches the micro-tile, and works
+// through them 32 at a time in two phases: a blend phase with lane = pixel that leaves each (survivor, pixel) fragment in a
+// shared-memory matrix, and a reduce phase with lane = survivor that sums its row.  A splat's ten gradient components
+// leave as three 16-byte vector reductions per (splat, micro-tile) -- no per-pixel atomics.
 #include "ssb_common.cuh"
 
 namespace ssb {
 
-constexpr int kFwdThreads = 256;
 constexpr float kTransmitThreshold = 1e-4f;
 
 __device__ __forceinline__ float eval_alpha(float4 a, float4 b, float px, float py, float& vis, float& sigma, float& dx, float& dy) {
@@ -81,56 +74,64 @@ __device__ __forceinline__ bool record_ok(int32_t g, const ListBounds& lb) {
     return false;
 }
 
+// Forward pass: a CTA of four warps per 16x16 tile, each warp one 8x8 micro-tile, a lane the two pixels (j, i) and
+// (j, i + 4).  The tile's list is staged 256 records at a time; every warp keeps the records whose alpha >= 1/255 ellipse
+// reaches its micro-tile (in list order) and blends those.  The three shared-memory loads, the list indexing and the loop
+// control of a surviving record are spent once for both pixels of a lane, and each lane carries two independent blend
+// chains (one pixel per lane with eight warps per tile measured 0.446 ms per 1080p view against 0.396 ms).
+constexpr int kFwdThreads = 128;
+constexpr int kFwdBatch = 256;
+
 template <bool DEPTH>
 __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
     const SsbScreenRec* __restrict__ screen, const int32_t* __restrict__ tile_offsets, const int32_t* __restrict__ flatten_ids,
     const int64_t* __restrict__ n_isects_ptr, ListBounds lb, int I, int W, int H, int tw, int th,
     float* __restrict__ out_rgb, float* __restrict__ out_depth, float* __restrict__ out_T, int32_t* __restrict__ last_ids) {
-    __shared__ float4 sA[kFwdThreads], sC[kFwdThreads], sQ[kFwdThreads], sE[kFwdThreads];
-    __shared__ float sEw[kFwdThreads];
-    __shared__ uint8_t hits[kFwdThreads / 32][kFwdThreads];
+    __shared__ float4 sA[kFwdBatch], sC[kFwdBatch], sQ[kFwdBatch], sE[kFwdBatch];
+    __shared__ float sEw[kFwdBatch];
+    __shared__ uint8_t hits[kFwdThreads / 32][kFwdBatch];
 
     const int img = blockIdx.z;
     const int tile_id = blockIdx.y * tw + blockIdx.x;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const int rx0 = blockIdx.x * kTile + (w & 1) * 8, ry0 = blockIdx.y * kTile + (w >> 1) * 4;
-    const int j = rx0 + (lane & 7), i = ry0 + (lane >> 3);
-    const float px = (float)j + 0.5f, py = (float)i + 0.5f;
-    const bool inside = (i < H && j < W);
-    bool done = !inside;
+    const int rx0 = blockIdx.x * kTile + (w & 1) * 8, ry0 = blockIdx.y * kTile + (w >> 1) * 8;
+    const int j = rx0 + (lane & 7), i0 = ry0 + (lane >> 3), i1 = i0 + 4;
+    const float px = (float)j + 0.5f, py0 = (float)i0 + 0.5f, py1 = (float)i1 + 0.5f;
+    const bool in0 = (i0 < H && j < W), in1 = (i1 < H && j < W);
+    bool done0 = !in0, done1 = !in1;
 
     const int32_t* offs = tile_offsets + (int64_t)img * tw * th;
     const int32_t list_len = list_length(n_isects_ptr, lb);
     const int32_t range_start = clamp_range(offs[tile_id], list_len);
     const int32_t range_end = (img == I - 1 && tile_id == tw * th - 1) ? list_len : clamp_range(offs[tile_id + 1], list_len);
 
-    float T = 1.0f;
-    float acc_r = 0.f, acc_g = 0.f, acc_b = 0.f, acc_d = 0.f;
-    int32_t cur_idx = 0;
-    const float fx0 = (float)rx0 + 0.5f, fx1 = (float)rx0 + 7.5f, fy0 = (float)ry0 + 0.5f, fy1 = (float)ry0 + 3.5f;
+    float T0 = 1.0f, T1 = 1.0f;
+    float r0 = 0.f, g0 = 0.f, b0 = 0.f, d0 = 0.f, r1 = 0.f, g1 = 0.f, b1 = 0.f, d1 = 0.f;
+    int32_t cur0 = 0, cur1 = 0;
+    const float fx0 = (float)rx0 + 0.5f, fx1 = (float)rx0 + 7.5f, fy0 = (float)ry0 + 0.5f, fy1 = (float)ry0 + 7.5f;
+    const float kLog2e = 1.4426950408889634f;
 
-    for (int32_t batch_start = range_start; batch_start < range_end; batch_start += kFwdThreads) {
-        if (__syncthreads_count(done) >= kFwdThreads) break;
-        const int batch = min(kFwdThreads, range_end - batch_start);
-        if ((int)threadIdx.x < batch) {
-            const int32_t g = flatten_ids[batch_start + threadIdx.x];
-            // an entry that names no record is staged as a splat nothing can reach
-            float4 ra = make_float4(-1e30f, -1e30f, 0.f, 0.f), b = make_float4(1.f, 0.f, 1.f, 1.f), rc = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (record_ok(g, lb)) {
-                const float4* r = (const float4*)(screen + g);
-                ra = r[0]; b = r[1]; rc = r[2];
+    for (int32_t batch_start = range_start; batch_start < range_end; batch_start += kFwdBatch) {
+        if (__syncthreads_count(done0 && done1) >= kFwdThreads) break;
+        const int batch = min(kFwdBatch, range_end - batch_start);
+#pragma unroll
+        for (int h = 0; h < kFwdBatch / kFwdThreads; ++h) {
+            const int e = threadIdx.x + h * kFwdThreads;
+            if (e < batch) {
+                const int32_t g = flatten_ids[batch_start + e];
+                float4 ra = make_float4(-1e30f, -1e30f, 0.f, 0.f), b = make_float4(1.f, 0.f, 1.f, 1.f), rc = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (record_ok(g, lb)) {
+                    const float4* r = (const float4*)(screen + g);
+                    ra = r[0]; b = r[1]; rc = r[2];
+                }
+                sA[e] = ra; sC[e] = rc;
+                sQ[e] = make_float4(0.5f * kLog2e * b.x, kLog2e * b.y, 0.5f * kLog2e * b.z, b.w);
+                const EllipseTest et = ellipse_test_setup(b);
+                sE[e] = make_float4(et.a, et.bb2, et.c, et.wx);
+                sEw[e] = et.wy;
             }
-            sA[threadIdx.x] = ra; sC[threadIdx.x] = rc;
-            // conic pre-scaled so that exp(-sigma) = 2^(-q), q = A dx^2 + B dx dy + C dy^2
-            const float kLog2e = 1.4426950408889634f;
-            sQ[threadIdx.x] = make_float4(0.5f * kLog2e * b.x, kLog2e * b.y, 0.5f * kLog2e * b.z, b.w);
-            // and the per-record part of the ellipse-vs-rectangle test, shared by the eight warps
-            const EllipseTest et = ellipse_test_setup(b);
-            sE[threadIdx.x] = make_float4(et.a, et.bb2, et.c, et.wx);
-            sEw[threadIdx.x] = et.wy;
         }
         __syncthreads();
-        // records that can reach this warp's 8x4 rectangle, in list order
         int n_hit = 0;
         for (int c = 0; c < batch; c += 32) {
             int e = c + lane;
@@ -151,35 +152,59 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
         __syncwarp();
 #pragma unroll 8
         for (int k = 0; k < n_hit; ++k) {
-            if ((k & 7) == 0 && __all_sync(0xffffffffu, done)) break;
+            if ((k & 7) == 0 && __all_sync(0xffffffffu, done0 && done1)) break;
             const int e = hits[w][k];
             const float4 a = sA[e], b = sQ[e];
-            const float dx = a.x - px, dy = a.y - py;
-            const float q = fmaf(fmaf(b.x, dx, b.y * dy), dx, b.z * dy * dy);
-            float vis;
-            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(vis) : "f"(-q));
-            const float alpha = fminf(0.999f, b.w * vis);
-            if (done || !(q >= 0.f) || alpha <= kAlphaThreshold) continue;
-            const float next_T = T * (1.0f - alpha);
-            if (next_T > kTransmitThreshold) {
-                const float4 c = sC[e];
-                const float wgt = alpha * T;
-                acc_r += c.x * wgt; acc_g += c.y * wgt; acc_b += c.z * wgt;
-                if (DEPTH) acc_d += c.w * wgt;
-                cur_idx = batch_start + e;
-                T = next_T;
-            } else {
-                done = true;
+            const float dx = a.x - px, dya = a.y - py0, dyb = a.y - py1;
+            const float qa = fmaf(fmaf(b.x, dx, b.y * dya), dx, b.z * dya * dya);
+            const float qb = fmaf(fmaf(b.x, dx, b.y * dyb), dx, b.z * dyb * dyb);
+            float va, vb;
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(va) : "f"(-qa));
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(vb) : "f"(-qb));
+            const float alpha_a = fminf(0.999f, b.w * va), alpha_b = fminf(0.999f, b.w * vb);
+            const bool ca = !(done0 || !(qa >= 0.f) || alpha_a <= kAlphaThreshold);
+            const bool cb = !(done1 || !(qb >= 0.f) || alpha_b <= kAlphaThreshold);
+            if (!(ca || cb)) continue;
+            const float4 c = sC[e];
+            if (ca) {
+                const float next_T = T0 * (1.0f - alpha_a);
+                if (next_T > kTransmitThreshold) {
+                    const float wgt = alpha_a * T0;
+                    r0 += c.x * wgt; g0 += c.y * wgt; b0 += c.z * wgt;
+                    if (DEPTH) d0 += c.w * wgt;
+                    cur0 = batch_start + e;
+                    T0 = next_T;
+                } else {
+                    done0 = true;
+                }
+            }
+            if (cb) {
+                const float next_T = T1 * (1.0f - alpha_b);
+                if (next_T > kTransmitThreshold) {
+                    const float wgt = alpha_b * T1;
+                    r1 += c.x * wgt; g1 += c.y * wgt; b1 += c.z * wgt;
+                    if (DEPTH) d1 += c.w * wgt;
+                    cur1 = batch_start + e;
+                    T1 = next_T;
+                } else {
+                    done1 = true;
+                }
             }
         }
     }
-    if (inside) {
-        const int64_t pix = ((int64_t)img * H + i) * W + j;
-        out_T[pix] = T;
-        const float invW = 1.0f / fmaxf(1.0f - T, 1e-10f);
-        out_rgb[3 * pix] = acc_r; out_rgb[3 * pix + 1] = acc_g; out_rgb[3 * pix + 2] = acc_b;
-        if (DEPTH) out_depth[pix] = acc_d * invW;
-        last_ids[pix] = cur_idx;
+    if (in0) {
+        const int64_t pix = ((int64_t)img * H + i0) * W + j;
+        out_T[pix] = T0;
+        out_rgb[3 * pix] = r0; out_rgb[3 * pix + 1] = g0; out_rgb[3 * pix + 2] = b0;
+        if (DEPTH) out_depth[pix] = d0 * (1.0f / fmaxf(1.0f - T0, 1e-10f));
+        last_ids[pix] = cur0;
+    }
+    if (in1) {
+        const int64_t pix = ((int64_t)img * H + i1) * W + j;
+        out_T[pix] = T1;
+        out_rgb[3 * pix] = r1; out_rgb[3 * pix + 1] = g1; out_rgb[3 * pix + 2] = b1;
+        if (DEPTH) out_depth[pix] = d1 * (1.0f / fmaxf(1.0f - T1, 1e-10f));
+        last_ids[pix] = cur1;
     }
 }
 

@@ -31,12 +31,15 @@ __constant__ float cGaussW[11] = {
 // Row strides of the partial maps and of their row convolution are odd (43, 33): step 4 works on two neighbouring outputs
 // per thread, so a warp covers two rows with even column offsets, and an even stride would put both rows on the same banks.
 constexpr int kDStride = kMid + 1, kHStride = kLossTile + 1;
+// Row stride of the row-convolved moments.  Step 3 walks them with one thread per (group of three rows, column): item o reads
+// word (o / 42) * 3 * stride + o % 42 + const, which is o + const modulo 32 -- one bank per lane -- when 3 * stride = 42 (mod 32).
+constexpr int kMStride = 46;
 constexpr int kSmemA = 3 * kMid * kDStride;           // X and Y patches (2*52*52 = 5408); later the 3 partial maps (3*42*43 = 5418)
-constexpr int kSmemB = 5 * kIn * kMid;                // row-convolved moments; later 3*42*33 row-convolved partials
+constexpr int kSmemB = 5 * kIn * kMStride;            // row-convolved moments; later 3*42*33 row-convolved partials
 static_assert(kSmemA >= 2 * kIn * kIn && kSmemB >= 3 * kMid * kHStride, "shared-memory aliases must fit");
 constexpr int kLossSmemBytes = (kSmemA + kSmemB) * 4;
 // With a mask: a sixth moment (the window's coverage) and the 52x52 mask patch, which stays live to the end.
-constexpr int kSmemBMasked = 6 * kIn * kMid;
+constexpr int kSmemBMasked = 6 * kIn * kMStride;
 constexpr int kLossSmemBytesMasked = (kSmemA + kSmemBMasked + kIn * kIn) * 4;
 
 // Which pixels take part (src/kernels/loss/FusedSSIM.cu:105-126, src/core/Interpolation.cuh:108-120): bytes [Bm][Hm][Wm],
@@ -78,7 +81,7 @@ __global__ void __launch_bounds__(kLossThreads) loss_l1_ssim_kernel(
     extern __shared__ float smem[];
     float* sX = smem;
     float* sY = smem + kIn * kIn;
-    float* sM = smem + kSmemA;          // [NM][kIn rows][kMid cols]
+    float* sM = smem + kSmemA;          // [NM][kIn rows][kMStride]
     float* sD = smem;                   // [3][kMid][kDStride]   (aliases sX/sY)
     float* sH = smem + kSmemA;          // [3][kMid rows][kHStride] (aliases sM)
     float* sK = smem + kSmemA + kSmemBMasked;   // MASKED: [kIn][kIn] 1 = takes part
@@ -151,7 +154,7 @@ __global__ void __launch_bounds__(kLossThreads) loss_l1_ssim_kernel(
 #pragma unroll
             for (int q = 0; q < 3; ++q)
 #pragma unroll
-                for (int k = 0; k < NM; ++k) sM[k * kIn * kMid + ly * kMid + lc + q] = acc[q][k];
+                for (int k = 0; k < NM; ++k) sM[k * kIn * kMStride + ly * kMStride + lc + q] = acc[q][k];
         }
         __syncthreads();
         // 3) column convolution -> SSIM and its partials at the 42x42 window centres;
@@ -166,10 +169,10 @@ __global__ void __launch_bounds__(kLossThreads) loss_l1_ssim_kernel(
                 for (int k = 0; k < NM; ++k) m[q][k] = 0.f;
 #pragma unroll
             for (int k = 0; k < NM; ++k) {
-                const float* col = sM + k * kIn * kMid + r0 * kMid + c;
+                const float* col = sM + k * kIn * kMStride + r0 * kMStride + c;
 #pragma unroll
                 for (int d = 0; d < 13; ++d) {
-                    const float v = col[d * kMid];
+                    const float v = col[d * kMStride];
 #pragma unroll
                     for (int q = 0; q < 3; ++q) {
                         const int tap = d - q;

@@ -827,10 +827,12 @@ __global__ void __launch_bounds__(kProjBlock, DIST ? 3 : 4) project_bwd_kernel(
             for (int j = 0; j < kShPerSplat; ++j) shg0[j] = 0.f;
         }
         if (accumulate) {
+            if (any_view) {      // a splat no view sees adds nothing
 #pragma unroll
             for (int j = 0; j < 3; ++j) { atomicAdd(&gr.means[3 * gid + j], g_mean[j]); atomicAdd(&gr.scales[3 * gid + j], g_scale[j]); atomicAdd(&gr.features_dc[3 * gid + j], g_dc[j]); }
             red_add_v4(gr.quats + 4 * gid, g_quat[0], g_quat[1], g_quat[2], g_quat[3]);
             atomicAdd(&gr.opacities[gid], g_op);
+            }
         } else {
 #pragma unroll
             for (int j = 0; j < 3; ++j) { gr.means[3 * gid + j] = g_mean[j]; gr.scales[3 * gid + j] = g_scale[j]; gr.features_dc[3 * gid + j] = g_dc[j]; }
@@ -848,7 +850,8 @@ __global__ void __launch_bounds__(kProjBlock, DIST ? 3 : 4) project_bwd_kernel(
             // load-add-store without waiting for the old value (measured a third faster)
             for (int v = threadIdx.x; v < kProjBlock * kShPerSplat / 4; v += kProjBlock) {
                 const float4 g = g4[v];
-                red_add_v4(out + 4 * v, g.x, g.y, g.z, g.w);
+                if (g.x != 0.f || g.y != 0.f || g.z != 0.f || g.w != 0.f)      // a culled splat's 45 zeros cost no traffic
+                    red_add_v4(out + 4 * v, g.x, g.y, g.z, g.w);
             }
         } else {
             for (int v = threadIdx.x; v < kProjBlock * kShPerSplat / 4; v += kProjBlock) out4[v] = g4[v];

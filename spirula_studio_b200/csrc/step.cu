@@ -10,10 +10,10 @@
 // synchronisation: the (splat, tile) pair count stays on the device.
 //
 // Views are independent until their gradients are added, so the object keeps
-// TWO sets of per-view buffers ("lanes") and runs consecutive views on two
+// THREE sets of per-view buffers ("lanes") and runs consecutive views round-robin on three
 // internal streams: the latency-bound stages of one view (key generation, sort,
 // projection backward) fill the issue slots the arithmetic-bound rasteriser of
-// the other leaves idle.  The projection backward of view v waits for that of
+// the others leave idle.  The projection backward of view v waits for that of
 // view v-1, so gradients are accumulated in view order exactly as the serial
 // loop does.  The caller's stream is joined on both sides: everything it
 // enqueued before the call is visible to the lanes, and everything the lanes do
@@ -22,7 +22,7 @@
 
 #include <new>
 
-enum { SsbStep_kMaxProfViews = 64, SsbStep_kLanes = 2 };
+enum { SsbStep_kMaxProfViews = 64, SsbStep_kLanes = 3 };
 
 struct SsbLane {
     float* aabb;          // [n][4]

@@ -617,6 +617,22 @@ int ssb_step_create(const SsbStepConfig* cfg, SsbStep** out);
 void ssb_step_destroy(SsbStep* step);
 int64_t ssb_step_device_bytes(const SsbStep* step);
 
+/* ---- splat.ply: the inference artefact written next to a checkpoint -------------------------------------------------
+ * ssb_ply_write restates the PLY part of engine_save_checkpoint (src/engine/EngineCheckpoint.cpp:130-330): the property
+ * layout of the original 3D Gaussian Splatting release (x y z, nx ny nz = 0, f_dc_0..2, f_rest_0..44 channel-major, opacity,
+ * scale_0..2, rot_0..3; binary little endian floats, raw values), without the splats that have a non-finite parameter or an
+ * opacity logit below -5.5373, SH values dequantised when shq names 8- or 16-bit codes.  The kept splats keep their order.
+ * Rows are assembled on the device and streamed through pinned staging; the call synchronises `stream`.
+ * *kept (may be NULL) receives the number of vertices written.
+ * ssb_ply_info / ssb_ply_read restate read_splat_ply (src/checkpoint/SplatPly.cpp:159-254): vertex properties in any order
+ * and scalar type, binary little endian or ASCII; SSB_ERR_UNSUPPORTED for a file that is not a splat PLY.  The caller
+ * sizes HOST arrays from ssb_ply_info (features_sh: [num][(sh_degree + 1)^2 - 1][3], coefficient-major, or NULL to skip
+ * the f_rest columns). */
+int ssb_ply_write(const char* path, const SsbSplats* params, const SsbShQuant* shq, int64_t n, int64_t* kept, void* stream);
+int ssb_ply_info(const char* path, int64_t* num, int32_t* sh_degree);
+int ssb_ply_read(const char* path, int64_t num, int32_t sh_degree, float* h_means, float* h_quats, float* h_scales, float* h_opacities,
+                 float* h_features_dc, float* h_features_sh);
+
 /* Makes every view's projection fold the splats' view radii (view_radius_3dgs, src/shaders/projection_utils.slang:1033-1043)
  * into d_radii [n_splats] by maximum, as ssb_project_fwd does with its d_radii argument: the array the scale-agnostic mean
  * update, the scale clip, the score update and the revised noise read.  The caller zeroes it once per iteration.  NULL: off. */

@@ -1,7 +1,7 @@
 """Full-resume checkpoints of a Trainer in the reference's wire format.
 
 Mirrors engine_save_checkpoint / engine_load_checkpoint (src/engine/EngineCheckpoint.cpp:350-474):
-`<dir>/state.tar` is a ustar archive whose first member is state.json (the manifest built by
+`<dir>/splat.ply` is the inference artefact (ssb_ply_write) and `<dir>/state.tar` a ustar archive whose first member is state.json (the manifest built by
 _build_state_json, src/engine/EngineCheckpoint.cpp:73-127) followed by one flat NPY array per live
 buffer, named after the reference's pool slots (src/core/PoolSlots.h:88-125) and written in the slot
 table's order:
@@ -112,8 +112,19 @@ def gather_optimizer_state(trainer):
             dist.broadcast(piece, src=dist.get_global_rank(trainer.pg, owner) if trainer.pg is not None else owner, group=trainer.pg)
 
 
+def export_ply(trainer, path):
+    """Writes the trainer's splats as a 3D Gaussian Splatting PLY (the reference's splat.ply: non-finite and
+    low-opacity splats dropped, quantised SH dequantised); returns the number of vertices written."""
+    kept = C.c_int64(-1)
+    stream = C.c_void_p(torch.cuda.current_stream(trainer.device).cuda_stream)
+    L.check(trainer.lib.ssb_ply_write(path.encode(), C.byref(trainer._p_struct), C.byref(trainer.shq) if trainer.shq else None, trainer.n,
+                                      C.byref(kept), stream))
+    return kept.value
+
+
 def save_checkpoint(trainer, output_dir, step=None, full=True):
-    """Writes <output_dir>/state.tar; returns its path (on every rank; rank 0 writes)."""
+    """Writes <output_dir>/splat.ply and <output_dir>/state.tar, as engine_save_checkpoint does; returns the path of
+    state.tar (on every rank; rank 0 writes)."""
     step = trainer.iteration if step is None else step
     path = os.path.join(output_dir, "state.tar")
     if full:
@@ -123,6 +134,7 @@ def save_checkpoint(trainer, output_dir, step=None, full=True):
     os.makedirs(output_dir, exist_ok=True)
     lib = trainer.lib
     torch.cuda.synchronize(trainer.device)
+    export_ply(trainer, os.path.join(output_dir, "splat.ply"))
     stream = C.c_void_p(torch.cuda.current_stream(trainer.device).cuda_stream)
     w = C.c_void_p()
     L.check(lib.ssb_ckpt_writer_open(path.encode(), C.byref(w)))

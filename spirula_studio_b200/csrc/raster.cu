@@ -382,7 +382,7 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 4) raster_bwd_kernel(
             {
                 float T0a = T[0], vT0a = vT[0], T1a = T[1], vT1a = vT[1];
                 const int32_t last0 = last[0], last1 = last[1];
-#pragma unroll 2
+#pragma unroll 4
                 for (int k = 0; k < ns; ++k) {
                     const int s = s0 + k;
                     const float4 sa = sSA[w][s];

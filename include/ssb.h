@@ -86,7 +86,9 @@ typedef struct SsbCameras {
                               * (src/kernels/projection/CameraVariants.cuh:11-22) are built: every tier for the pinhole,
                               * OpenCV and thin prism for the two fisheyes, none for the equirectangular camera; any
                               * other pair makes the projection calls return SSB_ERR_UNSUPPORTED. */
-    int32_t reserved;
+    int32_t sh_degree_plus1; /* active SH degree + 1 (the reference's sh_degree_to_use, src/app/TrainerCore.cpp:948, which picks
+                              * Vanilla3DGS<0..3>): bands above it are neither read nor given a gradient.  0 = all bands of
+                              * the 15-coefficient buffer (degree 3); values above 4 are refused. */
     const float* d_dist_coeffs; /* device [count][8], one row per view in the tier's own order; NULL reads as zeros.
                                  * OpenCV: k1 k2 p1 p2.  Thin prism: k1 k2 k3 k4 p1 p2 sx1 sy1.
                                  * Rational: k1 k2 k3 k4 k5 k6 p1 p2 (k4..k6 in the denominator). */
@@ -637,6 +639,11 @@ int ssb_ply_read(const char* path, int64_t num, int32_t sh_degree, float* h_mean
  * into d_radii [n_splats] by maximum, as ssb_project_fwd does with its d_radii argument: the array the scale-agnostic mean
  * update, the scale clip, the score update and the revised noise read.  The caller zeroes it once per iteration.  NULL: off. */
 int ssb_step_set_radii(SsbStep* step, float* d_radii);
+
+/* The SH degree the step's projections evaluate (0..3; default 3): the reference's trainer raises it by one every
+ * sh_degree_warmup_every iterations (sh_degree_to_use = step / sh_degree_warmup_every, src/app/TrainerCore.cpp:948) and calls
+ * the Vanilla3DGS<degree> instantiation; bands above it are neither read nor given a gradient, so their Adam state stays put. */
+int ssb_step_set_sh_degree(SsbStep* step, int32_t sh_degree);
 
 /* The lens-distortion tier of the step's cameras (SsbCameras::distortion; the engine's camera.distortion with
  * dist_coeffs[C][8], src/engine/EngineTrainStep.cpp) and its coefficient rows: row v belongs to view v of the NEXT

@@ -71,7 +71,7 @@ def _dist_args(dist, dist_coeffs, n_views):
     return int(dist), _p(rows), rows
 
 
-def project_fwd(splats, viewmats, intrins, W, H, model=0, antialiased=0, shq=None, with_radii=True, dist=0, dist_coeffs=None):
+def project_fwd(splats, viewmats, intrins, W, H, model=0, antialiased=0, shq=None, with_radii=True, dist=0, dist_coeffs=None, sh_degree=3):
     """dist: lens distortion tier (0 none, 1 OpenCV, 2 thin prism, 3 rational) with dist_coeffs [C][8]."""
     lib = load()
     s = {k: _f(v) for k, v in splats.items() if v is not None}
@@ -83,14 +83,14 @@ def project_fwd(splats, viewmats, intrins, W, H, model=0, antialiased=0, shq=Non
                conic=np.zeros((Cn * N, 3), np.float32), opac=np.zeros(Cn * N, np.float32), rgb=np.zeros((Cn * N, 3), np.float32))
     sh = _sh_args(s, shq)
     tier, d_ptr, _keep = _dist_args(dist, dist_coeffs, Cn)
-    lib.oracle_project_fwd_dist(C.c_int64(N), C.c_int(Cn), C.c_int(W), C.c_int(H), C.c_int(model), C.c_int(tier), d_ptr, C.c_int(antialiased),
+    lib.oracle_project_fwd_dist(C.c_int64(N), C.c_int(Cn), C.c_int(W), C.c_int(H), C.c_int(model), C.c_int(tier), d_ptr, C.c_int(sh_degree), C.c_int(antialiased),
                            _p(s["means"]), _p(s["quats"]), _p(s["scales"]), _p(s["opacities"]), _p(s["features_dc"]), *sh,
                            _p(viewmats), _p(intrins), _p(out["aabb"]), _p(out["depths"]), _p(out["radii"]),
                            _p(out["xy"]), _p(out["depth"]), _p(out["conic"]), _p(out["opac"]), _p(out["rgb"]))
     return out
 
 
-def project_bwd(splats, viewmats, intrins, W, H, aabb, v, model=0, antialiased=0, shq=None, dist=0, dist_coeffs=None):
+def project_bwd(splats, viewmats, intrins, W, H, aabb, v, model=0, antialiased=0, shq=None, dist=0, dist_coeffs=None, sh_degree=3):
     """v: dict of v_xy, v_depth, v_conic, v_opac, v_rgb. Returns dict of world gradients."""
     lib = load()
     s = {k: _f(val) for k, val in splats.items() if val is not None}
@@ -101,7 +101,7 @@ def project_bwd(splats, viewmats, intrins, W, H, aabb, v, model=0, antialiased=0
     vv = {k: _f(x) for k, x in v.items()}
     sh = _sh_args(s, shq)
     tier, d_ptr, _keep = _dist_args(dist, dist_coeffs, Cn)
-    lib.oracle_project_bwd_dist(C.c_int64(N), C.c_int(Cn), C.c_int(W), C.c_int(H), C.c_int(model), C.c_int(tier), d_ptr, C.c_int(antialiased),
+    lib.oracle_project_bwd_dist(C.c_int64(N), C.c_int(Cn), C.c_int(W), C.c_int(H), C.c_int(model), C.c_int(tier), d_ptr, C.c_int(sh_degree), C.c_int(antialiased),
                            _p(s["means"]), _p(s["quats"]), _p(s["scales"]), _p(s["opacities"]), _p(s["features_dc"]), *sh,
                            _p(viewmats), _p(intrins), _p(_f(aabb)),
                            _p(vv["v_xy"]), _p(vv["v_depth"]), _p(vv["v_conic"]), _p(vv["v_opac"]), _p(vv["v_rgb"]),
@@ -410,10 +410,10 @@ def adam_qq(grad, optim_packed, optim_bounds, value_packed, value_bounds, value_
                                 _p(value_bounds), _p(steps) if steps is not None else None, C.c_int(stride), C.c_int(optim_bits))
 
 
-def forward_chain(splats, viewmats, intrins, W, H, shq=None, model=0, dist=0, dist_coeffs=None):
+def forward_chain(splats, viewmats, intrins, W, H, shq=None, model=0, dist=0, dist_coeffs=None, sh_degree=3):
     """projection -> keys -> sort -> ranges -> raster for all views in one batch (as the reference's batched launch)."""
     N, I = splats["means"].shape[0], viewmats.shape[0]
-    proj = project_fwd(splats, viewmats, intrins, W, H, shq=shq, model=model, dist=dist, dist_coeffs=dist_coeffs)
+    proj = project_fwd(splats, viewmats, intrins, W, H, shq=shq, model=model, dist=dist, dist_coeffs=dist_coeffs, sh_degree=sh_degree)
     counts, cum, keys, vals = tile_keys(proj, N, W, H)
     tw, th = tile_grid(W, H)
     nb = tile_n_bits(tw * th * I)

@@ -98,6 +98,7 @@ struct Camera {
     float fx, fy, cx, cy;
     int W, H;
     int model;
+    int n_sh = 15;           // SH coefficients past DC in use: (degree + 1)^2 - 1 of the active degree (Vanilla3DGS<degree>)
     int dist = 0;            // CameraDistortionType: 0 none, 1 OpenCV, 2 thin prism, 3 rational (src/core/Common.cuh)
     float coeffs[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 };
@@ -495,9 +496,11 @@ inline void sh_to_color(const Camera& cam, const S mean[3], const float dc[3], c
     S inv = 1.0f / d_sqrt(dir[0] * dir[0] + dir[1] * dir[1] + dir[2] * dir[2]);
     S x = dir[0] * inv, y = dir[1] * inv, z = dir[2] * inv;
     sh_basis_deg3<S>(x, y, z, basis);
+    // sh<degree>_to_color (src/primitives/Primitive3DGS.cuh:76-97): the bands above the active degree are not read
+    for (int j = cam.n_sh; j < NUM_SH; ++j) basis[j] = S(0.f);
     for (int ch = 0; ch < 3; ++ch) {
         S c = S(0.2820947917738781f * dc[ch]);
-        for (int j = 0; j < NUM_SH; ++j) c = c + basis[j] * sh[j][ch];
+        for (int j = 0; j < cam.n_sh; ++j) c = c + basis[j] * sh[j][ch];
         rgb_raw[ch] = c;
     }
 }
@@ -680,7 +683,7 @@ float oracle_det_logf(float x) { return det_logf(x); }
 // are written as zeros here (the reference leaves them untouched).
 // ---------------------------------------------------------------------------
 void oracle_project_fwd_dist(
-    int64_t N, int C, int W, int H, int model, int dist, const float* dist_coeffs, int antialiased,
+    int64_t N, int C, int W, int H, int model, int dist, const float* dist_coeffs, int sh_degree, int antialiased,
     const float* means, const float* quats, const float* scales, const float* opacities,
     const float* features_dc, const float* features_sh,
     const uint8_t* sh_packed, const float* sh_bounds, int sh_bits, int64_t sh_bounds_stride,
@@ -690,6 +693,7 @@ void oracle_project_fwd_dist(
     ShStore st{features_sh, sh_packed, sh_bounds, sh_bits, sh_bounds_stride > 0 ? sh_bounds_stride : (int64_t)256 * 3 * NUM_SH};
     for (int cid = 0; cid < C; ++cid) {
         Camera cam = load_camera(viewmats, intrins, cid, W, H, model, dist, dist_coeffs);
+        if (sh_degree >= 0 && sh_degree <= 3) cam.n_sh = (sh_degree + 1) * (sh_degree + 1) - 1;
 #pragma omp parallel for schedule(static)
         for (int64_t gid = 0; gid < N; ++gid) {
             int64_t idx = (int64_t)cid * N + gid;
@@ -745,7 +749,7 @@ void oracle_project_fwd(
     const float* viewmats, const float* intrins,
     float* aabb, float* depths, float* radii,
     float* xy, float* depth, float* conic, float* opac, float* rgb) {
-    oracle_project_fwd_dist(N, C, W, H, model, 0, nullptr, antialiased, means, quats, scales, opacities, features_dc, features_sh, sh_packed,
+    oracle_project_fwd_dist(N, C, W, H, model, 0, nullptr, 3, antialiased, means, quats, scales, opacities, features_dc, features_sh, sh_packed,
                             sh_bounds, sh_bits, sh_bounds_stride, viewmats, intrins, aabb, depths, radii, xy, depth, conic, opac, rgb);
 }
 
@@ -758,7 +762,7 @@ void oracle_project_fwd(
 // into the world gradients (the caller zeroes or pre-loads them).
 // ---------------------------------------------------------------------------
 void oracle_project_bwd_dist(
-    int64_t N, int C, int W, int H, int model, int dist, const float* dist_coeffs, int antialiased,
+    int64_t N, int C, int W, int H, int model, int dist, const float* dist_coeffs, int sh_degree, int antialiased,
     const float* means, const float* quats, const float* scales, const float* opacities,
     const float* features_dc, const float* features_sh,
     const uint8_t* sh_packed, const float* sh_bounds, int sh_bits, int64_t sh_bounds_stride,
@@ -770,6 +774,7 @@ void oracle_project_bwd_dist(
     typedef Dual<K> D;
     for (int cid = 0; cid < C; ++cid) {
         Camera cam = load_camera(viewmats, intrins, cid, W, H, model, dist, dist_coeffs);
+        if (sh_degree >= 0 && sh_degree <= 3) cam.n_sh = (sh_degree + 1) * (sh_degree + 1) - 1;
 #pragma omp parallel for schedule(static)
         for (int64_t gid = 0; gid < N; ++gid) {
             int64_t idx = (int64_t)cid * N + gid;
@@ -819,7 +824,7 @@ void oracle_project_bwd(
     const float* viewmats, const float* intrins, const float* aabb,
     const float* v_xy, const float* v_depth, const float* v_conic, const float* v_opac, const float* v_rgb,
     float* g_means, float* g_quats, float* g_scales, float* g_opacities, float* g_dc, float* g_sh) {
-    oracle_project_bwd_dist(N, C, W, H, model, 0, nullptr, antialiased, means, quats, scales, opacities, features_dc, features_sh, sh_packed,
+    oracle_project_bwd_dist(N, C, W, H, model, 0, nullptr, 3, antialiased, means, quats, scales, opacities, features_dc, features_sh, sh_packed,
                             sh_bounds, sh_bits, sh_bounds_stride, viewmats, intrins, aabb, v_xy, v_depth, v_conic, v_opac, v_rgb,
                             g_means, g_quats, g_scales, g_opacities, g_dc, g_sh);
 }

@@ -233,6 +233,30 @@ int main(int argc, char** argv) {
                                 ttv(nullptr, {(int64_t)C, kCameraDistortionParams}), radii, std::nullopt, std::nullopt, 0, 32, 0);
     } catch (const std::runtime_error&) { threw = true; }
     report("unsupported distortion tier throws", threw);
+    // ---- 5a. the SH degree warm-up: max_sh_degree = 1 against the reference's Vanilla3DGS<1> kernel
+    {
+        typedef int (*RefFwdDeg)(int, uint32_t, uint32_t, uint32_t, uint32_t, float*, float*, float*, float*, float*, float*, const float*, const float*,
+                                 float*, float*, float*, float*, float*, float*, float*, float*);
+        auto ref_fwd_deg = (RefFwdDeg)dlsym(ref, "ref_project_fwd_deg");
+        if (!ref_fwd_deg) { std::fprintf(stderr, "missing ref_project_fwd_deg\n"); return 2; }
+        float* d_radii1 = device_zeros<float>(N);
+        DeviceVector<float> radii1(ttv(d_radii1, {N, 1}));
+        auto dout = projection_3dgs_forward(N, 1, in_splats, ttv(d_vm, {(int64_t)C, 16}), ttv(d_intr, {(int64_t)C, 4}), W, H, "PINHOLE", "NONE",
+                                            ttv(nullptr, {(int64_t)C, kCameraDistortionParams}), radii1, std::nullopt, std::nullopt, 0, 32, 0);
+        backend::device_synchronize();
+        float *q_aabb = device_zeros<float>(m * 4), *q_depths = device_zeros<float>(m), *q_radii = device_zeros<float>(N);
+        float *q_xy = device_zeros<float>(m * 2), *q_depth = device_zeros<float>(m), *q_conic = device_zeros<float>(m * 3), *q_opac = device_zeros<float>(m),
+              *q_rgb = device_zeros<float>(m * 3);
+        if (ref_fwd_deg(1, C, (uint32_t)N, W, H, d_means, d_quats, d_scales, d_opac, d_dc, d_sh, d_vm, d_intr, q_aabb, q_depths, q_radii, q_xy, q_depth, q_conic,
+                        q_opac, q_rgb) != 0) { std::fprintf(stderr, "ref_project_fwd_deg failed\n"); return 2; }
+        auto ga = download((const float*)std::get<0>(dout).data_ptr(), m * 4), ra = download(q_aabb, m * 4);
+        std::vector<char> both(m);
+        for (int64_t i = 0; i < m; ++i) both[i] = (ra[4 * i + 2] > ra[4 * i]) && (ga[4 * i + 2] > ga[4 * i]);
+        auto rgb1 = download(std::get<2>(dout)[4].data_ptr(), m * 3), rgb3 = download(r_rgb, m * 3), rgbr = download(q_rgb, m * 3);
+        double moved = 0.0;
+        for (int64_t i = 0; i < m * 3; ++i) if (both[i / 3]) moved = std::max(moved, (double)std::fabs(rgbr[i] - rgb3[i]));
+        report("projection with SH degree 1: rgb", moved > 0.01 && frac_bad(rgb1, rgbr, 5e-3, 5e-4, &both, 3) <= 2e-3, moved);
+    }
     // ---- 5b. a lens-distortion tier through the reference's signature against the reference's kernel of that variant
     {
         typedef int (*RefFwdDist)(int, int, uint32_t, uint32_t, uint32_t, uint32_t, float*, float*, float*, float*, float*, float*, const float*, const float*,

@@ -82,7 +82,8 @@ std::tuple<DeviceTensor2D<float4>, DeviceTensor2D<float>, std::vector<DeviceTens
     const uint32_t num_sh_buffer, const int sh_value_bits, const int64_t sh_bounds_stride) {
     if (in_splats.size() != 6) throw std::runtime_error("projection_3dgs_forward: expected six world arrays");
     const int sh_degree = std::min(Vanilla3DGS<0>::WorldBuffer(in_splats).sh_degree(), max_sh_degree);
-    if (sh_degree != 3) unsupported("an SH degree other than 3");
+    if (sh_degree < 0 || sh_degree > 3) unsupported("an SH degree above 3");
+    if (Vanilla3DGS<0>::WorldBuffer(in_splats).sh_degree() != 3) unsupported("an SH buffer that does not hold 15 coefficients per splat");
     if (sh_value_bits != 32 && num_sh_buffer != 15) unsupported("a quantised SH buffer that does not hold 15 coefficients");
     const uint32_t C = (uint32_t)std::get<2>(viewmats)[0];
     const int64_t N = num_splats, m = (int64_t)C * N;
@@ -99,7 +100,7 @@ std::tuple<DeviceTensor2D<float4>, DeviceTensor2D<float>, std::vector<DeviceTens
     }
     SsbCameras cams = {(const float*)std::get<0>(viewmats), (const float*)std::get<0>(intrins), (int32_t)C,
                        (int32_t)image_width, (int32_t)image_height, camera_model_of(camera_model), 0,
-                       (int32_t)cdt(distortion), 0, (const float*)std::get<0>(dist_coeffs)};      // a pair the reference does not instantiate: SSB_ERR_UNSUPPORTED, thrown
+                       (int32_t)cdt(distortion), sh_degree + 1, (const float*)std::get<0>(dist_coeffs)};      // a pair the reference does not instantiate: SSB_ERR_UNSUPPORTED, thrown
 
     DeviceTensor2D<float4> aabb;
     aabb.resize(PoolSlot::ProjAabb, C, N);

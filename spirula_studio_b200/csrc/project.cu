@@ -166,7 +166,7 @@ __device__ __forceinline__ void project_mean_wide(const S p[3], float fx, float 
 // OpenCV: n1 n2 p1 p2.  Thin prism: n1..n4 p1 p2 s1 s2.  Rational: n1..n3, d1..d3, p1 p2.  Unused terms are zero, which
 // leaves the tier's own arithmetic (x + 0, x / 1).  Each tier's coefficient row has its own order (:246,:262,:283).
 struct LensDist { float n1, n2, n3, n4, d1, d2, d3, p1, p2, s1, s2; };
-struct DistArgs { const float* coeffs; int tier; };   // [C][8] rows (NULL reads as zeros), SSB_DISTORTION_*
+struct DistArgs { const float* coeffs; int tier; int n_sh; };   // [C][8] rows (NULL reads as zeros), SSB_DISTORTION_*; SH coefficients past DC in use
 
 __device__ __forceinline__ LensDist load_lens(const DistArgs& da, int cid) {
     LensDist k = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -505,7 +505,7 @@ __global__ void __launch_bounds__(kProjBlock) project_fwd_kernel(
         for (int ch = 0; ch < 3; ++ch) {
             float c = kShC0 * dc_in[ch];
 #pragma unroll
-            for (int j = 0; j < kNumSh; ++j) c += b[j] * sh[3 * j + ch];
+            for (int j = 0; j < kNumSh; ++j) if (j < da.n_sh) c += b[j] * sh[3 * j + ch];     // bands above the active degree are not read
             rgb[ch] = fmaxf(c + 0.5f, 0.0f);
         }
     }
@@ -801,7 +801,7 @@ __global__ void __launch_bounds__(kProjBlock, DIST ? 3 : 4) project_bwd_kernel(
             for (int ch = 0; ch < 3; ++ch) {
                 float raw = kShC0 * dc_in[ch];
 #pragma unroll
-                for (int j = 0; j < kNumSh; ++j) raw += b[j] * sh[3 * j + ch];
+                for (int j = 0; j < kNumSh; ++j) if (j < da.n_sh) raw += b[j] * sh[3 * j + ch];
                 if (!(raw >= -0.5f)) vcol[ch] = 0.f;
                 vcol[ch] = finite_or_zero(vcol[ch]);
                 g_dc[ch] += kShC0 * vcol[ch];
@@ -809,9 +809,11 @@ __global__ void __launch_bounds__(kProjBlock, DIST ? 3 : 4) project_bwd_kernel(
             float w[kNumSh];
 #pragma unroll
             for (int j = 0; j < kNumSh; ++j) {
-                w[j] = sh[3 * j] * vcol[0] + sh[3 * j + 1] * vcol[1] + sh[3 * j + 2] * vcol[2];
-                if (MULTI_VIEW) { shg[3 * j] += b[j] * vcol[0]; shg[3 * j + 1] += b[j] * vcol[1]; shg[3 * j + 2] += b[j] * vcol[2]; }
-                else { shg[3 * j] = b[j] * vcol[0]; shg[3 * j + 1] = b[j] * vcol[1]; shg[3 * j + 2] = b[j] * vcol[2]; }
+                const bool on = j < da.n_sh;       // a band above the active degree takes no gradient and moves no direction
+                w[j] = on ? sh[3 * j] * vcol[0] + sh[3 * j + 1] * vcol[1] + sh[3 * j + 2] * vcol[2] : 0.f;
+                const float bj = on ? b[j] : 0.f;
+                if (MULTI_VIEW) { shg[3 * j] += bj * vcol[0]; shg[3 * j + 1] += bj * vcol[1]; shg[3 * j + 2] += bj * vcol[2]; }
+                else { shg[3 * j] = bj * vcol[0]; shg[3 * j + 1] = bj * vcol[1]; shg[3 * j + 2] = bj * vcol[2]; }
             }
             float vn[3];
             sh_basis_vjp(nx, ny, nz, w, vn);
@@ -903,6 +905,12 @@ static bool distortion_variant_built(int model, int tier) {
     return false;
 }
 
+// SH coefficients past DC that the active degree uses: SsbCameras::sh_degree_plus1 = 0 means all 15 (degree 3)
+static int active_sh_count(const SsbCameras* cams) {
+    const int p1 = cams->sh_degree_plus1;
+    return (p1 >= 1 && p1 <= 4) ? p1 * p1 - 1 : kNumSh;
+}
+
 static int check_shq(const SsbSplats* splats, const SsbShQuant* shq, SsbShQuant& out) {
     out = SsbShQuant{nullptr, nullptr, 32, 0, 256};
     if (shq && shq->packed && (shq->bits == 8 || shq->bits == 16)) {
@@ -930,7 +938,8 @@ int ssb_project_fwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n, c
     if (!distortion_variant_built(cams->model, cams->distortion)) {
         set_error("ssb_project_fwd: unsupported camera model / distortion tier (%d, %d)", cams->model, cams->distortion); return SSB_ERR_UNSUPPORTED;
     }
-    const DistArgs da = {cams->d_dist_coeffs, cams->distortion};
+    SSB_REQUIRE(cams->sh_degree_plus1 >= 0 && cams->sh_degree_plus1 <= 4, "ssb_project_fwd: sh_degree_plus1 must be 0 (all bands) or 1..4");
+    const DistArgs da = {cams->d_dist_coeffs, cams->distortion, active_sh_count(cams)};
     SSB_REQUIRE((int64_t)cams->count * n < ((int64_t)1 << 31), "ssb_project_fwd: views * splats must fit int32 flatten ids");
     SsbShQuant q;
     int e = check_shq(splats, shq, q);
@@ -969,7 +978,8 @@ int launch_project_fwd_pack_pass(int pass, const SsbSplats* splats, const SsbShQ
     if (!distortion_variant_built(cams->model, cams->distortion)) {
         set_error("ssb_project_fwd_packed: unsupported camera model / distortion tier (%d, %d)", cams->model, cams->distortion); return SSB_ERR_UNSUPPORTED;
     }
-    const DistArgs da = {cams->d_dist_coeffs, cams->distortion};
+    SSB_REQUIRE(cams->sh_degree_plus1 >= 0 && cams->sh_degree_plus1 <= 4, "ssb_project_fwd_packed: sh_degree_plus1 must be 0 (all bands) or 1..4");
+    const DistArgs da = {cams->d_dist_coeffs, cams->distortion, active_sh_count(cams)};
     const bool dist = cams->distortion != SSB_DISTORTION_NONE;
     SSB_REQUIRE((int64_t)cams->count * n < ((int64_t)1 << 31), "ssb_project_fwd_packed: views * splats must fit int32");
     SsbShQuant q;
@@ -1007,7 +1017,8 @@ int launch_project_bwd(const SsbSplats* splats, const SsbShQuant* shq, int64_t n
     if (!distortion_variant_built(cams->model, cams->distortion)) {
         set_error("ssb_project_bwd: unsupported camera model / distortion tier (%d, %d)", cams->model, cams->distortion); return SSB_ERR_UNSUPPORTED;
     }
-    const DistArgs da = {cams->d_dist_coeffs, cams->distortion};
+    SSB_REQUIRE(cams->sh_degree_plus1 >= 0 && cams->sh_degree_plus1 <= 4, "ssb_project_bwd: sh_degree_plus1 must be 0 (all bands) or 1..4");
+    const DistArgs da = {cams->d_dist_coeffs, cams->distortion, active_sh_count(cams)};
     const bool dist = cams->distortion != SSB_DISTORTION_NONE;
     SsbShQuant q;
     int e = check_shq(splats, shq, q);

@@ -64,6 +64,7 @@ struct SsbStep {
     float* accum_weight_den;
     int64_t* max_pairs;       // device: largest per-view pair count since it was last cleared
     float* radii;             // caller's [n] running maximum of the splats' view radii (ssb_step_set_radii), or nullptr
+    int32_t sh_degree_plus1;  // active SH degree + 1, 0 = all bands (ssb_step_set_sh_degree)
     int32_t dist_tier;        // lens-distortion tier of the cameras and the rows of the next call's views (ssb_step_set_distortion)
     const float* dist_coeffs;
     // deferred backward (ssb_step_set_fused_backward): every view's aabb and screen-gradient records are kept, and the
@@ -150,6 +151,7 @@ static int run_view(SsbStep* s, SsbLane& l, const SsbSplats* params, const SsbSh
     cam.model = s->cfg.camera_model; cam.antialiased = s->cfg.antialiased;
     cam.distortion = s->dist_tier;
     cam.d_dist_coeffs = s->dist_coeffs ? s->dist_coeffs + 8 * (int64_t)v : nullptr;
+    cam.sh_degree_plus1 = s->sh_degree_plus1;
     int e;
 #define SSB_MARK(k) do { if (ev) SSB_CUDA(cudaEventRecord(ev[k], st)); } while (0)
     SSB_MARK(0);
@@ -249,6 +251,14 @@ int ssb_step_set_radii(SsbStep* s, float* d_radii) {
     using namespace ssb;
     SSB_REQUIRE(s, "ssb_step_set_radii: NULL step");
     s->radii = d_radii;
+    return SSB_OK;
+}
+
+int ssb_step_set_sh_degree(SsbStep* s, int32_t sh_degree) {
+    using namespace ssb;
+    SSB_REQUIRE(s, "ssb_step_set_sh_degree: NULL step");
+    SSB_REQUIRE(sh_degree >= 0 && sh_degree <= 3, "ssb_step_set_sh_degree: the degree must be 0..3 (got %d)", sh_degree);
+    s->sh_degree_plus1 = sh_degree + 1;
     return SSB_OK;
 }
 
@@ -421,7 +431,7 @@ int ssb_step_backward_optimize(SsbStep* s, const SsbSplats* params, const SsbShQ
     SsbCameras cams{};
     cams.d_viewmats = d_viewmats; cams.d_intrins = d_intrins; cams.count = n_views;
     cams.width = s->cfg.width; cams.height = s->cfg.height; cams.model = s->cfg.camera_model; cams.antialiased = s->cfg.antialiased;
-    cams.distortion = s->dist_tier; cams.d_dist_coeffs = s->dist_coeffs;
+    cams.distortion = s->dist_tier; cams.d_dist_coeffs = s->dist_coeffs; cams.sh_degree_plus1 = s->sh_degree_plus1;
     const int64_t range = std::min(kFusedRange, align_up(n, 256));
     const int64_t scratch_floats = 6 * 64 + range * 59;
     SsbAdamConfig c = *cfg;

@@ -47,7 +47,7 @@ class SsbShQuant(C.Structure):
 class SsbCameras(C.Structure):
     _fields_ = [("d_viewmats", C.c_void_p), ("d_intrins", C.c_void_p), ("count", C.c_int32), ("width", C.c_int32),
                 ("height", C.c_int32), ("model", C.c_int32), ("antialiased", C.c_int32), ("distortion", C.c_int32),
-                ("reserved", C.c_int32), ("d_dist_coeffs", C.c_void_p)]
+                ("sh_degree_plus1", C.c_int32), ("d_dist_coeffs", C.c_void_p)]
 
 
 class SsbLossConfig(C.Structure):
@@ -140,6 +140,7 @@ SIGNATURES = {
     "ssb_step_set_loss": (C.c_int, [_P, _P]),
     "ssb_step_set_radii": (C.c_int, [_P, _P]),
     "ssb_step_set_distortion": (C.c_int, [_P, _I32, _P]),
+    "ssb_step_set_sh_degree": (C.c_int, [_P, _I32]),
     "ssb_ply_write": (C.c_int, [C.c_char_p, _P, _P, _I64, _P, _P]),
     "ssb_ply_info": (C.c_int, [C.c_char_p, _P, _P]),
     "ssb_ply_read": (C.c_int, [C.c_char_p, _I64, _I32, _P, _P, _P, _P, _P, _P]),
@@ -316,8 +317,9 @@ def device_bytes_tensor(address, nbytes, device):
     return torch.as_tensor(_DevicePtr(address, nbytes), device=device)
 
 
-def cameras_struct(viewmats, intrins, width, height, model=CAMERA_PINHOLE, antialiased=0, count=None, distortion=0, dist_coeffs=None):
-    """dist_coeffs: device float32 [count][8] rows of the distortion tier (DISTORTION_*), or None for zeros."""
+def cameras_struct(viewmats, intrins, width, height, model=CAMERA_PINHOLE, antialiased=0, count=None, distortion=0, dist_coeffs=None, sh_degree=None):
+    """dist_coeffs: device float32 [count][8] rows of the distortion tier (DISTORTION_*), or None for zeros.
+    sh_degree: active SH degree 0..3 (None = all bands)."""
     c = SsbCameras()
     c.d_viewmats = viewmats.data_ptr()
     c.d_intrins = intrins.data_ptr()
@@ -325,4 +327,5 @@ def cameras_struct(viewmats, intrins, width, height, model=CAMERA_PINHOLE, antia
     c.width, c.height, c.model, c.antialiased = width, height, model, antialiased
     c.distortion = distortion
     c.d_dist_coeffs = dist_coeffs.data_ptr() if dist_coeffs is not None else None
+    c.sh_degree_plus1 = 0 if sh_degree is None else int(sh_degree) + 1
     return c

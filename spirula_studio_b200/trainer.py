@@ -304,6 +304,17 @@ class Trainer:
             L.check(self.lib.ssb_step_set_fused_backward(self.handle, total))
             self._fused_room = total
 
+    def set_sh_degree(self, degree):
+        """Active SH degree (0..3) of every following iteration: the reference's warm-up raises it with the step count
+        (`sh_degree_for_step`)."""
+        for h in self.handles:
+            L.check(self.lib.ssb_step_set_sh_degree(h, int(degree)))
+
+    @staticmethod
+    def sh_degree_for_step(step, warmup_every=1000, max_degree=3):
+        """sh_degree_to_use of the reference's trainer (src/app/TrainerCore.cpp:948)."""
+        return min(max_degree, step // max(warmup_every, 1))
+
     def set_distortion(self, tier, coeffs=None, kind=0):
         """Lens-distortion tier (lib.DISTORTION_*) of the cameras of `kind` with one row of eight coefficients per view, in the
         order of the views handed to each following train_step / views_fwd_bwd call (call again before handing other views).

@@ -528,6 +528,38 @@ def run_dist_proj(ref, out_dir):
     np.savez_compressed(os.path.join(out_dir, "dist_proj.npz"), **out)
 
 
+def run_sh_degree(ref, out_dir):
+    """Projection forward and backward of the reference's Vanilla3DGS<0>, <1> and <2> kernels (the SH degree warm-up) on the
+    ring2 scene with its 15-coefficient SH rows: the colours, the validity boxes and the six gradient arrays for the
+    screen-space cotangents of the degree-3 fixture."""
+    name = QUANT_SCENE
+    cfg, sp, vm, K = build_case(name)
+    gold = np.load(os.path.join(HERE, f"{name}.npz"))
+    n, W, H, I = cfg.n_splats, cfg.width, cfg.height, vm.shape[0]
+    m = I * n
+    d = {k: dev(v.reshape(-1)) for k, v in sp.items()}
+    d_vm, d_K = dev(vm), dev(K)
+    z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=DEV)
+    v = {k: dev(gold[k]) for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")}
+    out = {}
+    for deg in (0, 1, 2):
+        aabb, depths, radii = z(m, 4), z(m), z(n)
+        xy, depth, conic, opac, rgb = z(m, 2), z(m), z(m, 3), z(m), z(m, 3)
+        check(ref.ref_project_fwd_deg(deg, I, n, W, H, P(d["means"]), P(d["quats"]), P(d["scales"]), P(d["opacities"]), P(d["features_dc"]),
+                                      P(d["features_sh"]), P(d_vm), P(d_K), P(aabb), P(depths), P(radii),
+                                      P(xy), P(depth), P(conic), P(opac), P(rgb)), "ref_project_fwd_deg")
+        out[f"d{deg}_aabb"], out[f"d{deg}_rgb"] = aabb.cpu().numpy(), rgb.cpu().numpy()
+        g = {k: torch.zeros_like(t) for k, t in d.items()}
+        check(ref.ref_project_bwd_deg(deg, I, n, W, H, P(d["means"]), P(d["quats"]), P(d["scales"]), P(d["opacities"]), P(d["features_dc"]),
+                                      P(d["features_sh"]), P(d_vm), P(d_K), P(aabb),
+                                      P(v["v_xy"]), P(v["v_depth"]), P(v["v_conic"]), P(v["v_opac"]), P(v["v_rgb"]),
+                                      P(g["means"]), P(g["quats"]), P(g["scales"]), P(g["opacities"]), P(g["features_dc"]), P(g["features_sh"])),
+              "ref_project_bwd_deg")
+        for k, t in g.items():
+            out[f"d{deg}_g_{k}"] = t.cpu().numpy()
+    np.savez_compressed(os.path.join(out_dir, "sh_degree.npz"), **out)
+
+
 def run_packed_proj(ref, out_dir):
     """The reference's packed projection (mask, scan, compacting kernel) and the packed mode of its projection backward
     kernel on two scenes, fp32 SH and one quantised layout: ids, count and the packed outputs; the backward pass takes the
@@ -588,6 +620,8 @@ def main():
         run_adam(ref, out_dir)
     if not only or "dist_proj" in only:
         run_dist_proj(ref, out_dir)
+    if not only or "sh_degree" in only:
+        run_sh_degree(ref, out_dir)
     if not only or "ssim_map" in only:
         run_loss_map(ref, out_dir)
     if not only or "ssim_masked" in only:

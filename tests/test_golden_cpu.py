@@ -151,6 +151,29 @@ def test_quantised_sh_projection_vs_reference(oracle, tag):
         assert frac_bad(g[k], ref, 1e-4 * np.abs(ref).max(), 2e-3) <= 5e-3, k
 
 
+@pytest.mark.parametrize("deg", [0, 1, 2])
+def test_active_sh_degree_vs_reference(oracle, deg):
+    """Projection with the SH degree warmed up (bands above the active degree neither read nor given a gradient) against
+    the reference's Vanilla3DGS<0>, <1>, <2> kernels on the 15-coefficient rows of the ring2 scene."""
+    cfg, sp, vm, K = build_case(QUANT_SCENE)
+    base, gold = load(QUANT_SCENE), load("sh_degree")
+    got = oracle.project_fwd(sp, vm, K, cfg.width, cfg.height, sh_degree=deg)
+    ref_aabb = gold[f"d{deg}_aabb"]
+    assert np.array_equal(ref_aabb, base["aabb"])                      # the degree does not move the geometry
+    both = (ref_aabb[:, 2] > ref_aabb[:, 0]) & (got["aabb"][:, 2] > got["aabb"][:, 0])
+    ref_rgb = gold[f"d{deg}_rgb"]
+    assert np.abs(ref_rgb[both] - base["rgb"][both]).max() > 0.02       # and does change the colours
+    assert frac_bad(got["rgb"][both], ref_rgb[both], 5e-3, 5e-4) <= 2e-3
+    v = {k: base[k] for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")}
+    g = oracle.project_bwd(sp, vm, K, cfg.width, cfg.height, ref_aabb, v, sh_degree=deg)
+    n_active = (deg + 1) ** 2 - 1
+    assert not g["features_sh"][:, n_active:].any() and not gold[f"d{deg}_g_features_sh"].reshape(-1, 15, 3)[:, n_active:].any()
+    assert deg == 0 or np.abs(g["features_sh"][:, :n_active]).max() > 0
+    for k in g:
+        ref = gold[f"d{deg}_g_{k}"].reshape(g[k].shape)
+        assert frac_bad(g[k], ref, 1e-4 * max(np.abs(ref).max(), 1e-12), 2e-3) <= 5e-3, k
+
+
 @pytest.mark.parametrize("name", sorted(DIST_CASES))
 def test_lens_distortion_projection_vs_reference(oracle, name):
     """Projection forward and backward with a lens-distortion tier, every (camera model, tier) pair the reference

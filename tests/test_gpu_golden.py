@@ -177,6 +177,54 @@ def test_quantised_sh_projection_vs_reference(lib, U, tag):
     del keep_alive
 
 
+@pytest.mark.parametrize("deg", [0, 1, 2])
+def test_active_sh_degree_vs_reference(lib, U, deg):
+    """ssb_project_fwd / ssb_project_bwd with SsbCameras::sh_degree_plus1 (the SH degree warm-up) against the reference's
+    Vanilla3DGS<0>, <1>, <2> kernels; several-view and single-view backward kernels; NaNs in the unused bands are not read."""
+    cfg, sp, vm, K = build_case(QUANT_SCENE)
+    base, gold = load(QUANT_SCENE), load("sh_degree")
+    I, n, W, H = vm.shape[0], cfg.n_splats, cfg.width, cfg.height
+    m = I * n
+    n_active = (deg + 1) ** 2 - 1
+    sp_nan = {k: v.copy() for k, v in sp.items()}
+    sp_nan["features_sh"][:, n_active:] = np.nan
+    spd = U.splats_dev(sp_nan)
+    d_vm, d_K = U.dev(vm), U.dev(K)
+    cams = L.cameras_struct(d_vm, d_K, W, H, sh_degree=deg)
+    aabb, depths, radii = torch.zeros(m, 4, device=U.DEV), torch.zeros(m, device=U.DEV), torch.zeros(n, device=U.DEV)
+    rec = torch.zeros(m * L.SCREEN_REC_FLOATS, device=U.DEV)
+    s = L.splats_struct(spd)
+    L.check(lib.ssb_project_fwd(C.byref(s), None, n, C.byref(cams), L.ptr(aabb), L.ptr(depths), L.ptr(radii), L.ptr(rec), None))
+    torch.cuda.synchronize()
+    h_aabb, ref_aabb = aabb.cpu().numpy(), gold[f"d{deg}_aabb"]
+    both = (ref_aabb[:, 2] > ref_aabb[:, 0]) & (h_aabb[:, 2] > h_aabb[:, 0])
+    assert both.sum() > 100
+    scr = U.unpack_screen(lib, rec, m)
+    assert np.isfinite(scr["rgb"]).all()
+    assert U.close_frac(scr["rgb"][both], gold[f"d{deg}_rgb"][both], 5e-3, 5e-4) <= 2e-3
+    vrec = U.arrays_to_vrec({k: base[k].reshape(m, -1) if base[k].ndim > 1 else base[k] for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")}, m)
+    d_ref_aabb = U.dev(ref_aabb)
+    for views in (I, 1):
+        grads = {k: torch.zeros_like(t) for k, t in spd.items()}
+        g = L.splats_struct(grads)
+        if views == I:
+            L.check(lib.ssb_project_bwd(C.byref(s), None, n, C.byref(cams), L.ptr(d_ref_aabb), L.ptr(vrec), C.byref(g), 0, None))
+        else:
+            for view in range(I):
+                cams1 = L.cameras_struct(d_vm[view:view + 1], d_K[view:view + 1], W, H, sh_degree=deg)
+                L.check(lib.ssb_project_bwd(C.byref(s), None, n, C.byref(cams1), L.ptr(d_ref_aabb[view * n:(view + 1) * n]),
+                                            L.ptr(vrec[view * n * L.SCREEN_REC_FLOATS:]), C.byref(g), 1 if view else 0, None))
+        torch.cuda.synchronize()
+        gsh = grads["features_sh"].cpu().numpy().reshape(n, 15, 3)
+        assert np.isfinite(gsh).all() and not gsh[:, n_active:].any()
+        for k in grads:
+            ref = gold[f"d{deg}_g_{k}"]
+            assert np.isfinite(grads[k].cpu().numpy()).all(), k
+            assert U.close_frac(grads[k].cpu().numpy().reshape(-1), ref.reshape(-1), 1e-4 * max(np.abs(ref).max(), 1e-12), 2e-3) <= 5e-3, (k, views)
+    bad = L.cameras_struct(d_vm, d_K, W, H, sh_degree=4)
+    assert lib.ssb_project_fwd(C.byref(s), None, n, C.byref(bad), L.ptr(aabb), L.ptr(depths), L.ptr(radii), L.ptr(rec), None) == L.SSB_ERR_INVALID_ARGUMENT
+
+
 @pytest.mark.parametrize("name", sorted(DIST_CASES))
 def test_lens_distortion_projection_vs_reference(lib, U, name):
     """ssb_project_fwd / ssb_project_bwd with a lens-distortion tier (SsbCameras::distortion, d_dist_coeffs) against the

@@ -142,7 +142,7 @@ def test_adam_quantized_state_fp32_values(lib, U, oracle):
         d_x.copy_(U.dev(x)); d_op.copy_(U.dev(op)); d_ob.copy_(U.dev(ob))
 
 
-def _oracle_iteration(oracle, cfg, sp, vm, K, targets, shq=None, dist=0, rows=None):
+def _oracle_iteration(oracle, cfg, sp, vm, K, targets, shq=None, dist=0, rows=None, sh_degree=3):
     """Gradients of one multi-view iteration, one camera per sub-batch, summed (reference split-batch loop)."""
     W, H, n = cfg.width, cfg.height, cfg.n_splats
     tot = None
@@ -150,11 +150,11 @@ def _oracle_iteration(oracle, cfg, sp, vm, K, targets, shq=None, dist=0, rows=No
     renders = []
     for v in range(vm.shape[0]):
         dr = None if rows is None else rows[v:v + 1]
-        ch = oracle.forward_chain(sp, vm[v:v + 1], K[v:v + 1], W, H, shq=shq, dist=dist, dist_coeffs=dr)
+        ch = oracle.forward_chain(sp, vm[v:v + 1], K[v:v + 1], W, H, shq=shq, dist=dist, dist_coeffs=dr, sh_degree=sh_degree)
         vr, l = oracle.loss_l1_ssim(ch["render"]["rgb"], targets[v].reshape(-1, 3), 1, H, W, 0.8, 0.2)
         losses += l
         gs = oracle.raster_bwd(ch["proj"], ch["offsets"], ch["sorted_vals"], 1, n, W, H, ch["render"], vr)
-        g = oracle.project_bwd(sp, vm[v:v + 1], K[v:v + 1], W, H, ch["proj"]["aabb"], gs, shq=shq, dist=dist, dist_coeffs=dr)
+        g = oracle.project_bwd(sp, vm[v:v + 1], K[v:v + 1], W, H, ch["proj"]["aabb"], gs, shq=shq, dist=dist, dist_coeffs=dr, sh_degree=sh_degree)
         tot = g if tot is None else {k: tot[k] + g[k] for k in g}
         renders.append(ch)
     return tot, losses, renders
@@ -215,6 +215,56 @@ def test_whole_iteration_matches_oracle(lib, U, oracle, quant):
     l1, ssim, loss = tr2.train_step(h_vm, h_K, h_gt, cfg.n_views)
     assert abs(loss - ref_l[2] / cfg.n_views) <= 1e-3 * abs(ref_l[2] / cfg.n_views) + 1e-5
     tr.close(); tr2.close()
+
+
+@pytest.mark.parametrize("quant", [False, True])
+def test_iteration_with_sh_degree_warmup_matches_oracle(lib, U, oracle, quant):
+    """Trainer.set_sh_degree -> ssb_step_set_sh_degree: an iteration at SH degree 1 against the oracle's; the bands above the
+    degree take no gradient, and an optimiser step leaves them (and their Adam state) where they were."""
+    from spirula_studio_b200.trainer import Trainer
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=9000, width=176, height=128, n_views=2)
+    cfg.rig, cfg.rig_radius, cfg.log_scale_mu = "ring", 3.0, -3.0
+    if quant:
+        cfg.sh_value_bits, cfg.sh_optim_bits = 16, 8
+    sp = scenes.make_splats(cfg)
+    vm, K = scenes.make_cameras(cfg)
+    targets = np.stack([scenes.make_target(cfg, v) for v in range(cfg.n_views)])
+    shq = None
+    if quant:
+        packed, bounds = oracle.quant_encode(sp["features_sh"], 16)
+        shq = dict(packed=packed, bounds=bounds, bits=16, bounds_stride=256)
+    assert Trainer.sh_degree_for_step(0) == 0 and Trainer.sh_degree_for_step(1999) == 1 and Trainer.sh_degree_for_step(10 ** 6) == 3
+    ref_g, ref_l, _ = _oracle_iteration(oracle, cfg, sp, vm, K, targets, shq, sh_degree=1)
+    full_g, full_l, _ = _oracle_iteration(oracle, cfg, sp, vm, K, targets, shq)
+    assert abs(full_l[2] - ref_l[2]) > 1e-4 * abs(ref_l[2])
+    tr = Trainer(cfg, sp, device=U.DEV)
+    tr.set_sh_degree(Trainer.sh_degree_for_step(1500))
+    d_vm, d_K, d_gt = (torch.from_numpy(a).to(U.DEV) for a in (vm, K, targets))
+    tr.losses.zero_()
+    tr.views_fwd_bwd(d_vm, d_K, d_gt, cfg.n_views)
+    torch.cuda.synchronize()
+    assert np.allclose(tr.losses.cpu().numpy(), ref_l, rtol=1e-3, atol=1e-5)
+    for k in ref_g:
+        got = tr.grads[k].cpu().numpy().reshape(ref_g[k].shape)
+        assert U.close_frac(got, ref_g[k], 2e-5 * np.abs(ref_g[k]).max(), 1e-3) <= 5e-3, k
+    assert not tr.grads["features_sh"].view(-1, 15, 3)[:, 3:].any()
+    if quant:
+        before = tr.sh_packed.clone().view(torch.int16).view(-1, 15, 3)[:, 3:].clone()
+        state_before = tr.sh_optim_packed.clone()
+    else:
+        before = tr.params["features_sh"].view(-1, 15, 3)[:, 3:].clone()
+    tr.optimizer_step(cfg.n_views)
+    torch.cuda.synchronize()
+    if quant:
+        # the value codes of a block are re-encoded against the block's new bounds, so the unused bands may move by a code;
+        # their decoded values stay within one quantum
+        dec0 = oracle.quant_decode(packed, bounds, sp["features_sh"].size, 16).reshape(-1, 15, 3)[:, 3:]
+        dec1 = oracle.quant_decode(tr.sh_packed.cpu().numpy(), tr.sh_bounds.cpu().numpy(), sp["features_sh"].size, 16).reshape(-1, 15, 3)[:, 3:]
+        assert np.abs(dec1 - dec0).max() <= 2.0 * (bounds.reshape(-1, 2)[:, 1] - bounds.reshape(-1, 2)[:, 0]).max() / 65535.0 + 1e-7
+    else:
+        assert torch.equal(tr.params["features_sh"].view(-1, 15, 3)[:, 3:], before)
+        assert not tr.m1["features_sh"].view(-1, 15, 3)[:, 3:].any()
+    tr.close()
 
 
 def test_iteration_with_lens_distortion_matches_oracle(lib, U, oracle):

@@ -156,8 +156,10 @@ __global__ void __launch_bounds__(kFwdThreads) raster_fwd_kernel(
             const int e = hits[w][k];
             const float4 a = sA[e], b = sQ[e];
             const float dx = a.x - px, dya = a.y - py0, dyb = a.y - py1;
-            const float qa = fmaf(fmaf(b.x, dx, b.y * dya), dx, b.z * dya * dya);
-            const float qb = fmaf(fmaf(b.x, dx, b.y * dyb), dx, b.z * dyb * dyb);
+            // q = A dx^2 + dy (B dx + C dy): the two pixels of a lane share dx, so A dx^2 and B dx are formed once
+            const float adx2 = b.x * dx * dx, bdx = b.y * dx;
+            const float qa = fmaf(dya, fmaf(b.z, dya, bdx), adx2);
+            const float qb = fmaf(dyb, fmaf(b.z, dyb, bdx), adx2);
             float va, vb;
             asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(va) : "f"(-qa));
             asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(vb) : "f"(-qb));
@@ -389,12 +391,13 @@ __global__ void __launch_bounds__(kBwdWarps * 32, 4) raster_bwd_kernel(
                     const float4 q4 = sSQ[w][s];
                     const float4 c = sSC[w][s];
                     const float dx = sa.x - pxr;
+                    const float adx2 = q4.x * dx * dx, bdx = q4.y * dx;     // shared by the lane's two pixels (same column), as in the forward pass
                     const int32_t sidx = __float_as_int(sa.z);
                     float2 frag[2];
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const float dy = sa.y - (pyr + 4.0f * h);
-                        const float q = fmaf(fmaf(q4.x, dx, q4.y * dy), dx, q4.z * dy * dy);
+                        const float q = fmaf(dy, fmaf(q4.z, dy, bdx), adx2);
                         float vis;
                         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(vis) : "f"(-q));
                         const float ov = q4.w * vis;

@@ -724,6 +724,15 @@ const int64_t* ssb_step_max_pairs_device(const SsbStep* step);
 int64_t ssb_step_isect_capacity(const SsbStep* step);
 int ssb_step_status(SsbStep* step, int64_t* h_max_pairs, int reset, void* stream);
 
+/* One image, forward only: projection, tile intersection and the forward rasteriser for one camera of the step's size and
+ * model (with the step's SH degree and distortion tier; row 0 of the distortion rows), into caller buffers -- what the
+ * reference's viewer asks of forward_3dgs + engine_copy_render_to_host (src/app/webviewer/RenderWorker.cpp:285-300).
+ * d_rgb [H][W][3]; d_depth [H][W] ray depth normalised by 1 - T, or NULL; d_T [H][W] transmittance, or NULL.  Uses the
+ * buffers of the step's first lane, ordered after views already enqueued and before views enqueued later; nothing is
+ * allocated.  The display transforms of the viewer (alpha, depth scaling, normals, 8-bit) stay with the caller. */
+int ssb_step_render(SsbStep* step, const SsbSplats* params, const SsbShQuant* shq, const float* d_viewmat, const float* d_intrin,
+                    float* d_rgb, float* d_depth, float* d_T, void* stream);
+
 /* Device buffers of the last view, for inspection by tests: any pointer may be
  * NULL.  Valid until the next ssb_step_views / ssb_step_destroy. */
 int ssb_step_peek(SsbStep* step, const float** d_rgb, const float** d_depth, const float** d_T,

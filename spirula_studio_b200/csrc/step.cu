@@ -541,6 +541,36 @@ int ssb_step_status(SsbStep* s, int64_t* h_max_pairs, int reset, void* stream) {
     return SSB_OK;
 }
 
+int ssb_step_render(SsbStep* s, const SsbSplats* params, const SsbShQuant* shq, const float* d_viewmat, const float* d_intrin,
+                    float* d_rgb, float* d_depth, float* d_T, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(s && params && d_viewmat && d_intrin && d_rgb, "ssb_step_render: NULL argument");
+    const int64_t n = s->cfg.n_splats;
+    const int W = s->cfg.width, H = s->cfg.height;
+    const int64_t P = (int64_t)W * H;
+    SsbLane& l = s->lane[0];
+    cudaStream_t st = (cudaStream_t)stream;
+    // the lane's buffers may still be in use by views enqueued on the lane's own stream
+    SSB_CUDA(cudaEventRecord(l.all_done, l.stream));
+    SSB_CUDA(cudaStreamWaitEvent(st, l.all_done, 0));
+    SsbCameras cam{};
+    cam.d_viewmats = d_viewmat; cam.d_intrins = d_intrin; cam.count = 1; cam.width = W; cam.height = H;
+    cam.model = s->cfg.camera_model; cam.antialiased = s->cfg.antialiased;
+    cam.distortion = s->dist_tier; cam.d_dist_coeffs = s->dist_coeffs; cam.sh_degree_plus1 = s->sh_degree_plus1;
+    int e;
+    if ((e = ssb_project_fwd(params, shq, n, &cam, l.aabb, l.depths, nullptr, l.screen, st))) return e;
+    if ((e = launch_intersect_tiles(l.aabb, l.depths, l.screen, n, n, W, H, l.isect_ws, s->isect_ws_bytes, nullptr, l.flat, s->capacity,
+                                 l.offsets, l.n_isects, st, nullptr, s->max_pairs, nullptr))) return e;
+    // T and the last-blended indices are by-products the caller may not want: they land in the lane's own images
+    if ((e = ssb_raster_fwd(l.screen, n, l.offsets, l.flat, s->capacity, l.n_isects, 1, W, H, d_rgb, d_depth, d_T ? d_T : l.T, l.last_ids, st))) return e;
+    // later views on the lane wait for this render to be done with its buffers
+    SSB_CUDA(cudaEventRecord(l.all_done, st));
+    SSB_CUDA(cudaStreamWaitEvent(l.stream, l.all_done, 0));
+    s->last_lane = 0;
+    (void)P;
+    return SSB_OK;
+}
+
 int ssb_step_peek(SsbStep* s, const float** d_rgb, const float** d_depth, const float** d_T,
                   const int32_t** d_last_ids, const SsbScreenRec** d_screen, const float** d_aabb) {
     using namespace ssb;

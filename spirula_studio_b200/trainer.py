@@ -304,6 +304,20 @@ class Trainer:
             L.check(self.lib.ssb_step_set_fused_backward(self.handle, total))
             self._fused_room = total
 
+    def render(self, viewmat, intrin, kind=0, depth=False):
+        """One image of the current splats, forward only (the viewer's path): viewmat [16] / intrin [4] as numpy or tensors.
+        Returns (rgb [H][W][3], transmittance [H][W]) and, with depth=True, the ray-depth image as a third tensor."""
+        _, _, width, height, _, _ = view_kind(self.cfg, kind)
+        as_dev = lambda a, n: torch.as_tensor(np.asarray(a, np.float32) if not torch.is_tensor(a) else a, dtype=torch.float32).reshape(n).to(self.device)
+        d_vm, d_K = as_dev(viewmat, 16), as_dev(intrin, 4)
+        rgb = torch.empty(height, width, 3, device=self.device)
+        T = torch.empty(height, width, device=self.device)
+        dep = torch.empty(height, width, device=self.device) if depth else None
+        stream = C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        L.check(self.lib.ssb_step_render(self.handles[kind], C.byref(self._p_struct), C.byref(self.shq) if self.shq else None, L.ptr(d_vm), L.ptr(d_K),
+                                         L.ptr(rgb), L.ptr(dep) if depth else None, L.ptr(T), stream))
+        return (rgb, T, dep) if depth else (rgb, T)
+
     def set_sh_degree(self, degree):
         """Active SH degree (0..3) of every following iteration: the reference's warm-up raises it with the step count
         (`sh_degree_for_step`)."""

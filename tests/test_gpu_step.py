@@ -267,6 +267,38 @@ def test_iteration_with_sh_degree_warmup_matches_oracle(lib, U, oracle, quant):
     tr.close()
 
 
+def test_forward_only_render_matches_oracle_and_leaves_training_alone(lib, U, oracle):
+    """ssb_step_render (the viewer's forward-only path): colour, normalised ray depth and transmittance of an arbitrary camera
+    against the oracle's forward chain, at full and at a lower SH degree; rendering between iterations changes nothing in them."""
+    from spirula_studio_b200.trainer import Trainer
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=9000, width=176, height=128, n_views=2)
+    cfg.rig, cfg.rig_radius, cfg.log_scale_mu = "ring", 3.0, -3.0
+    sp = scenes.make_splats(cfg)
+    vm, K = scenes.make_cameras(cfg)
+    targets = np.stack([scenes.make_target(cfg, v) for v in range(cfg.n_views)])
+    W, H, n = cfg.width, cfg.height, cfg.n_splats
+    tr = Trainer(cfg, sp, device=U.DEV)
+    for deg in (3, 1):
+        tr.set_sh_degree(deg)
+        ch = oracle.forward_chain(sp, vm[1:2], K[1:2], W, H, sh_degree=deg)
+        rgb, T, dep = tr.render(vm[1], K[1], depth=True)
+        torch.cuda.synchronize()
+        d_img = np.abs(rgb.cpu().numpy().reshape(-1, 3) - ch["render"]["rgb"])
+        assert d_img.max() <= 5e-3 and (d_img.max(axis=1) > 1e-4).mean() <= 2e-3, deg
+        assert np.abs(T.cpu().numpy().reshape(-1) - ch["render"]["T"].reshape(-1)).max() <= 5e-3
+        d_dep = np.abs(dep.cpu().numpy().reshape(-1) - ch["render"]["depth"].reshape(-1))
+        assert (d_dep > 5e-3 + 1e-3 * np.abs(ch["render"]["depth"].reshape(-1))).mean() <= 2e-3
+    tr.set_sh_degree(3)
+    tr2 = Trainer(cfg, sp, device=U.DEV)
+    h = tuple(torch.from_numpy(a).pin_memory() for a in (vm, K, targets))
+    for it in range(3):
+        la = tr.train_step(*h, cfg.n_views)
+        tr.render(vm[it % 2], K[it % 2])                 # between iterations, on the training stream
+        lb = tr2.train_step(*h, cfg.n_views)
+        assert abs(la[2] - lb[2]) <= 1e-4 * abs(lb[2]), it
+    tr.close(); tr2.close()
+
+
 def test_iteration_with_lens_distortion_matches_oracle(lib, U, oracle):
     """The step object with a distortion tier (Trainer.set_distortion -> ssb_step_set_distortion): three pinhole views, each with
     its own thin-prism row, device-resident and host-buffer entry points, against the oracle's iteration."""

@@ -145,6 +145,7 @@ bool read_line(FILE* f, std::string& line) {
     while ((ch = std::fgetc(f)) != EOF) {
         any = true;
         if (ch == '\n') break;
+        if (line.size() >= 4096) return false;      // no header line is this long: not a PLY (do not swallow a binary file)
         line.push_back((char)ch);
     }
     if (!line.empty() && line.back() == '\r') line.pop_back();

@@ -12,9 +12,11 @@ and every `refine_every` iterations while densification is ongoing, before the n
 The Trainer's arrays have room for `cfg.n_splats` splats (the capacity); `count` of them are in use.  Unused slots hold an
 opacity logit of -30, so every kernel of the iteration culls them, and they are outside the relocation's range.
 
-One process only: with several ranks the strategy would have to draw the same splats on every replica (the draw is a
-function of the seed and the scores, so it would, given identical scores) and the per-splat weights would have to be summed
-over the ranks first; that exchange is not built.
+Several ranks (views sharded over GPUs): what the iteration's views accumulate -- the per-splat weights, their denominators
+and the view radii -- is combined over the ranks first (sum or maximum, three all-reduces of n floats), after which every
+rank holds the same inputs and runs the same kernels: the draw is a function of the seed and the scores, the compaction is
+ordered and the sort is stable, so every replica relocates and adds the same splats and no parameter has to be exchanged.
+Moments that a rank does not own under the sharded optimiser are cleared with everyone else's and never read.
 """
 import ctypes as C
 import math
@@ -54,8 +56,8 @@ class DensifyConfig:
 
 class Densifier:
     def __init__(self, trainer, cfg: DensifyConfig, count: int):
-        if trainer.world_size != 1 or len(trainer.handles) != 1:
-            raise NotImplementedError("the densification strategy runs on one rank with one camera kind")
+        if len(trainer.handles) != 1:
+            raise NotImplementedError("the densification strategy runs with one camera kind")
         if trainer.non_sh_optim_bits != 32:
             raise NotImplementedError("relocation and growth clear fp32 moments; 16-bit non-SH moment codes are not handled")
         if trainer.fused_backward:
@@ -93,6 +95,12 @@ class Densifier:
     def after_step(self, step: int, max_steps: int) -> int:
         """The strategy's work after iteration `step`'s optimiser pass; returns the number of splats added."""
         c, tr, lib = self.cfg, self.tr, self.tr.lib
+        if tr.world_size > 1:
+            import torch.distributed as dist
+            dist.all_reduce(self.radii, op=dist.ReduceOp.MAX, group=tr.pg)
+            dist.all_reduce(self.accum_weight, op=dist.ReduceOp.MAX if c.accum_mode == L.SSB_ACCUM_MAX else dist.ReduceOp.SUM, group=tr.pg)
+            if c.accum_mode == L.SSB_ACCUM_AVG:
+                dist.all_reduce(self.accum_den, op=dist.ReduceOp.SUM, group=tr.pg)
         ongoing = step < max(c.refine_stop_iter, max_steps - c.refine_stop_num_iter)
         do_densify = ongoing and step > c.refine_start_iter and step % c.refine_every == 0
         progress = (step + 0.5) / max_steps

@@ -15,11 +15,63 @@ from spirula_studio_b200 import scenes  # noqa: E402
 from spirula_studio_b200.trainer import Trainer  # noqa: E402
 
 
+def densify_check(rank, world, dev):
+    """The densification strategy with the views sharded over the ranks: every replica relocates and adds the same splats
+    (parameters and counts equal on all ranks after every step), and the run equals a one-rank run over all views in what
+    the strategy decides (the counts) -- the parameters of the two differ by summation order only."""
+    from spirula_studio_b200.densify import DensifyConfig, Densifier
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=12032, width=160, height=112, n_views=2 * world)
+    cfg.rig, cfg.rig_radius, cfg.log_scale_mu = "ring", 3.0, -3.0
+    cfg.sh_value_bits, cfg.sh_optim_bits = 16, 8
+    sp = scenes.make_splats(cfg)
+    start = 8000
+    sp["opacities"][:start:17] = -8.0
+    vm, K = scenes.make_cameras(cfg)
+    views = [2 * rank, 2 * rank + 1]
+    d_vm, d_K = torch.from_numpy(vm[views].copy()).to(dev), torch.from_numpy(K[views].copy()).to(dev)
+    d_gt = torch.from_numpy(np.stack([scenes.make_target(cfg, v) for v in views])).to(dev)
+    dc = DensifyConfig(refine_start_iter=2, refine_stop_iter=1000, refine_every=4, growth_factor=1.1, noise_lr=80.0 * 1.6e-4, noise_lr_final=0.8 * 1.6e-4)
+    counts = {}
+    for mode in ("nccl", "peer"):
+        tr = Trainer(cfg, sp, device=dev, world_size=world, rank=rank, grad_sync=mode)
+        dn = Densifier(tr, dc, start)
+        steps, seen = 14, []
+        for step in range(steps):
+            dn.before_step()
+            tr.step_device(d_vm, d_K, d_gt, 2, cfg.n_views)
+            dn.after_step(step, steps)
+            seen.append(dn.count)
+            # every replica holds the same splats after the strategy's work
+            for k, v in tr.params.items():
+                if v is None or k == "features_sh":
+                    continue
+                ref = v.clone()
+                dist.broadcast(ref, 0)
+                assert torch.equal(ref, v), f"replicas differ in {k} on rank {rank} after step {step} ({mode})"
+            ref = tr.sh_packed.clone()
+            dist.broadcast(ref, 0)
+            assert torch.equal(ref, tr.sh_packed), f"replicas differ in the SH codes on rank {rank} after step {step} ({mode})"
+        assert seen[0] == start and seen[-1] > start and (tr.params["opacities"][dn.count:] == -30.0).all()
+        used = torch.sigmoid(tr.params["opacities"][:dn.count])
+        assert (used <= dc.min_opacity).float().mean().item() < 0.01
+        counts[mode] = seen
+        torch.cuda.synchronize()
+        tr.close()
+    assert counts["nccl"] == counts["peer"]
+    if rank == 0:
+        print("MODES nccl=nccl peer=peer multimem=n/a", flush=True)
+        print("OK densify", counts["peer"][-1], flush=True)
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = f"cuda:{local}"
     dist.init_process_group("nccl", device_id=torch.device(dev))
+    if len(sys.argv) > 1 and sys.argv[1] == "densify":
+        densify_check(rank, world, dev)
+        dist.destroy_process_group()
+        return
     quant = len(sys.argv) > 1 and sys.argv[1] == "quant"
     cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=5000 + 37, width=160, height=112, n_views=2 * world)
     cfg.rig, cfg.rig_radius, cfg.log_scale_mu = "ring", 3.0, -3.0

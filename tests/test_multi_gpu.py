@@ -27,3 +27,16 @@ def test_peer_exchange_matches_nccl_on_two_gpus(variant):
         # the comparison above then covered the plain peer path twice: say so instead of counting it as coverage of the
         # multimem.ld_reduce / multimem.st kernels
         pytest.skip(f"peer and NCCL paths agree; the multicast kernels did not run here (requested multimem, ran {modes.get('multimem')})")
+
+
+def test_densification_strategy_keeps_replicas_identical_on_two_gpus():
+    """The revised densification strategy with the views sharded over two ranks (NCCL gradient sum and the peer exchange):
+    per-splat weights and radii are combined over the ranks, every replica then relocates and adds the same splats."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29643", os.path.join(ROOT, "tests", "multi_gpu_check.py"), "densify"]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    assert any(line.startswith("OK densify") for line in r.stdout.splitlines()), r.stdout[-2000:]

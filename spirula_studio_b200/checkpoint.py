@@ -14,6 +14,9 @@ table's order:
     eng.<attr>_qfpbo.q / .qb                             16-bit joint moments of the five non-SH arrays
     eng.sh_quant.q / .qb                                 8-bit joint SH optimiser state: packed bytes / float bounds
     eng.world.sh_vq8|16.q / .qb                          quantised SH values: packed bytes / float bounds
+    eng.radii, eng.accum_buffer                          with a Densifier: the view radii and the strategy's score
+                                                         accumulator; state.json's cur_num_splats is then the number
+                                                         of splats in use, and splat.ply holds those
 
 The archive is produced by libssb_b200 (ssb_ckpt_*), which streams device buffers through pinned
 staging memory.  With several ranks every rank holds the same parameters but only its own range of
@@ -32,9 +35,10 @@ _MODEL_NAMES = {0: "PINHOLE", 1: "FISHEYE", 2: "EQUISOLID", 3: "EQUIRECTANGULAR"
 _GEO = ("means", "quats", "scales", "opacities", "features_dc")
 
 
-def state_json(trainer, step, full=True):
+def state_json(trainer, step, full=True, cur_num_splats=None):
     """The manifest text, key for key and byte for byte as the reference formats it."""
     cfg = trainer.cfg
+    cur = trainer.n if cur_num_splats is None else int(cur_num_splats)
     sh_optim_bits = 8 if trainer.quant else 32
     lines = [
         '  "format_version": 1',
@@ -44,7 +48,7 @@ def state_json(trainer, step, full=True):
         '  "quant_eps": 1e-15',
         f'  "step": {int(step)}',
         '  "primitive": "3dgs"',
-        f'  "cur_num_splats": {trainer.n}',
+        f'  "cur_num_splats": {cur}',
         f'  "max_num_splats": {trainer.n}',
         f'  "num_sh": {L.NUM_SH}',
         '  "sh_degree": 3',
@@ -64,8 +68,9 @@ def state_json(trainer, step, full=True):
     return "{\n" + ",\n".join(lines) + "\n}\n"
 
 
-def saved_buffers(trainer):
-    """[(slot name, tensor, dtype tag)] of the trainer's live state, in the reference's slot order."""
+def saved_buffers(trainer, densifier=None):
+    """[(slot name, tensor, dtype tag)] of the trainer's live state, in the reference's slot order; with a Densifier also
+    the strategy's resumable state (eng.radii, eng.accum_buffer)."""
     out = [(f"world.{a}", trainer.params[a], DTYPE_F4) for a in _GEO]
     if not trainer.quant:
         out.append(("world.features_sh", trainer.params["features_sh"], DTYPE_F4))
@@ -82,6 +87,8 @@ def saved_buffers(trainer):
         vq = f"eng.world.sh_vq{trainer.cfg.sh_value_bits}"
         out += [("eng.sh_quant.q", trainer.sh_optim_packed, DTYPE_U1), ("eng.sh_quant.qb", trainer.sh_optim_bounds, DTYPE_F4),
                 (vq + ".q", trainer.sh_packed, DTYPE_U1), (vq + ".qb", trainer.sh_bounds, DTYPE_F4)]
+    if densifier is not None:
+        out += [("eng.radii", densifier.radii, DTYPE_F4), ("eng.accum_buffer", densifier.accum_buffer, DTYPE_F4)]
     return out
 
 
@@ -112,17 +119,17 @@ def gather_optimizer_state(trainer):
             dist.broadcast(piece, src=dist.get_global_rank(trainer.pg, owner) if trainer.pg is not None else owner, group=trainer.pg)
 
 
-def export_ply(trainer, path):
-    """Writes the trainer's splats as a 3D Gaussian Splatting PLY (the reference's splat.ply: non-finite and
-    low-opacity splats dropped, quantised SH dequantised); returns the number of vertices written."""
+def export_ply(trainer, path, count=None):
+    """Writes the trainer's splats (the first `count`: the ones in use) as a 3D Gaussian Splatting PLY (the reference's
+    splat.ply: non-finite and low-opacity splats dropped, quantised SH dequantised); returns the number of vertices written."""
     kept = C.c_int64(-1)
     stream = C.c_void_p(torch.cuda.current_stream(trainer.device).cuda_stream)
-    L.check(trainer.lib.ssb_ply_write(path.encode(), C.byref(trainer._p_struct), C.byref(trainer.shq) if trainer.shq else None, trainer.n,
-                                      C.byref(kept), stream))
+    L.check(trainer.lib.ssb_ply_write(path.encode(), C.byref(trainer._p_struct), C.byref(trainer.shq) if trainer.shq else None,
+                                      trainer.n if count is None else int(count), C.byref(kept), stream))
     return kept.value
 
 
-def save_checkpoint(trainer, output_dir, step=None, full=True):
+def save_checkpoint(trainer, output_dir, step=None, full=True, densifier=None):
     """Writes <output_dir>/splat.ply and <output_dir>/state.tar, as engine_save_checkpoint does; returns the path of
     state.tar (on every rank; rank 0 writes)."""
     step = trainer.iteration if step is None else step
@@ -134,14 +141,15 @@ def save_checkpoint(trainer, output_dir, step=None, full=True):
     os.makedirs(output_dir, exist_ok=True)
     lib = trainer.lib
     torch.cuda.synchronize(trainer.device)
-    export_ply(trainer, os.path.join(output_dir, "splat.ply"))
+    count = None if densifier is None else densifier.count
+    export_ply(trainer, os.path.join(output_dir, "splat.ply"), count)
     stream = C.c_void_p(torch.cuda.current_stream(trainer.device).cuda_stream)
     w = C.c_void_p()
     L.check(lib.ssb_ckpt_writer_open(path.encode(), C.byref(w)))
     try:
-        text = state_json(trainer, step, full).encode()
+        text = state_json(trainer, step, full, count).encode()
         L.check(lib.ssb_ckpt_write_bytes(w, b"state.json", text, len(text)))
-        for name, t, tag in (saved_buffers(trainer) if full else []):
+        for name, t, tag in (saved_buffers(trainer, densifier) if full else []):
             L.check(lib.ssb_ckpt_write_device(w, (name + ".npy").encode(), L.ptr(t), t.numel() * t.element_size(), tag, stream))
     finally:
         rc = lib.ssb_ckpt_writer_close(w)
@@ -163,7 +171,7 @@ def _json_value(text, key, default=None):
     return int(float(v[:end]))
 
 
-def load_checkpoint(trainer, input_dir):
+def load_checkpoint(trainer, input_dir, densifier=None):
     """Restores a trainer (built for the same scene) from <input_dir>/state.tar; returns the saved step.
 
     As in the reference, every array member must name a live buffer of exactly its byte size; the
@@ -189,7 +197,9 @@ def load_checkpoint(trainer, input_dir):
                                                           ("use_per_splat_bias_correction", 0), ("use_fused_proj_bwd_optim", 0)))
         if want != have:
             raise RuntimeError(f"load_checkpoint: optimiser-state layout {have} of the checkpoint is not the trainer's {want}")
-        targets = {name: t for name, t, _ in saved_buffers(trainer)}
+        targets = {name: t for name, t, _ in saved_buffers(trainer, densifier)}
+        if densifier is not None:
+            densifier.count = _json_value(text, "cur_num_splats", trainer.n)
         stream = C.c_void_p(torch.cuda.current_stream(trainer.device).cuda_stream)
         name_buf = C.create_string_buffer(128)
         for i in range(lib.ssb_ckpt_member_count(r)):

@@ -127,6 +127,57 @@ def test_trainer_with_16bit_non_sh_moments_tracks_fp32_and_resumes(lib, tmp_path
         t_.close()
 
 
+def test_densifying_run_resumes_with_its_strategy_state(lib, tmp_path):
+    """A checkpoint taken in the middle of a densifying run carries the number of splats in use (state.json, and the PLY holds
+    only those), the view radii and the score accumulator under the reference's slot names; a fresh trainer + strategy
+    restored from it grows exactly as the original does."""
+    from spirula_studio_b200.densify import DensifyConfig, Densifier
+    from spirula_studio_b200.trainer import Trainer
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=12032, width=176, height=128, n_views=2)
+    cfg.rig, cfg.rig_radius, cfg.log_scale_mu = "ring", 3.0, -3.0
+    cfg.sh_value_bits, cfg.sh_optim_bits = 16, 8
+    sp = scenes.make_splats(cfg)
+    vm, K = scenes.make_cameras(cfg)
+    gt = np.stack([scenes.make_target(cfg, v) for v in range(cfg.n_views)])
+    host = tuple(torch.from_numpy(a).pin_memory() for a in (vm, K, gt))
+    dc = DensifyConfig(refine_start_iter=2, refine_stop_iter=1000, refine_every=4, growth_factor=1.1, noise_lr=80.0 * 1.6e-4, noise_lr_final=0.8 * 1.6e-4)
+    steps = 20
+
+    def run(tr, dn, first, last):
+        counts = []
+        for step in range(first, last):
+            dn.before_step()
+            tr.train_step(*host, cfg.n_views)
+            dn.after_step(step, steps)
+            counts.append(dn.count)
+        return counts
+
+    tr, dn = Trainer(cfg, sp, device=DEV), None
+    dn = Densifier(tr, dc, 8000)
+    run(tr, dn, 0, 10)
+    assert 8000 < dn.count < cfg.n_splats and dn.accum_buffer.any()
+    path = ck.save_checkpoint(tr, str(tmp_path), step=10, densifier=dn)
+    with tarfile.open(path) as t:
+        names = [m.name for m in t.getmembers()]
+        text = t.extractfile("state.json").read().decode()
+    assert names[-2:] == ["eng.radii.npy", "eng.accum_buffer.npy"] and f'"cur_num_splats": {dn.count}' in text
+    assert f'"max_num_splats": {cfg.n_splats}' in text
+    num = C.c_int64(0)
+    deg = C.c_int32(0)
+    L.check(lib.ssb_ply_info(str(tmp_path / "splat.ply").encode(), C.byref(num), C.byref(deg)))
+    assert 0 < num.value <= dn.count                      # unused slots (opacity logit -30) never reach the PLY
+    tr2 = Trainer(cfg, {k: np.zeros_like(v) + (1.0 if k == "quats" else 0.0) for k, v in sp.items()}, device=DEV)
+    dn2 = Densifier(tr2, dc, 1)
+    assert ck.load_checkpoint(tr2, str(tmp_path), densifier=dn2) == 10
+    assert dn2.count == dn.count and torch.equal(dn2.accum_buffer, dn.accum_buffer) and torch.equal(dn2.radii, dn.radii)
+    a, b = run(tr, dn, 10, steps), run(tr2, dn2, 10, steps)
+    assert a == b and a[-1] > a[0]
+    for k in ("means", "scales", "opacities"):
+        x, y = tr.params[k][: dn.count * (tr.params[k].numel() // cfg.n_splats)], tr2.params[k][: dn.count * (tr2.params[k].numel() // cfg.n_splats)]
+        assert ((x - y).abs() > 1e-3 * (1.0 + y.abs())).float().mean().item() < 0.02, k
+    tr.close(); tr2.close()
+
+
 def test_device_arrays_larger_than_the_staging_buffers(lib, tmp_path):
     # 80 MiB + 20 bytes: three staging chunks, the last one ragged; both staging buffers get reused
     n = (80 << 20) // 4 + 5

@@ -17,6 +17,7 @@ table's order:
     eng.radii, eng.accum_buffer                          with a Densifier: the view radii and the strategy's score
                                                          accumulator; state.json's cur_num_splats is then the number
                                                          of splats in use, and splat.ply holds those
+    eng.bias_correction_steps                            int32 per-splat Adam step counters (OptimOptions)
 
 The archive is produced by libssb_b200 (ssb_ckpt_*), which streams device buffers through pinned
 staging memory.  With several ranks every rank holds the same parameters but only its own range of
@@ -57,7 +58,7 @@ def state_json(trainer, step, full=True, cur_num_splats=None):
         f'  "sh_value_bits": {cfg.sh_value_bits if trainer.quant else 32}',
         f'  "non_sh_optim_bits": {trainer.non_sh_optim_bits}',
         '  "use_fused_proj_bwd_optim": 0',
-        '  "use_per_splat_bias_correction": 0',
+        f'  "use_per_splat_bias_correction": {1 if getattr(trainer, "steps", None) is not None else 0}',
         f'  "camera": {{"num": {cfg.n_views}, "width": {cfg.width}, "height": {cfg.height}, '
         f'"model": "{_MODEL_NAMES.get(cfg.camera_model, "PINHOLE")}"}}',
         '  "bilagrid_rgb": {"enabled": 0}',
@@ -87,8 +88,13 @@ def saved_buffers(trainer, densifier=None):
         vq = f"eng.world.sh_vq{trainer.cfg.sh_value_bits}"
         out += [("eng.sh_quant.q", trainer.sh_optim_packed, DTYPE_U1), ("eng.sh_quant.qb", trainer.sh_optim_bounds, DTYPE_F4),
                 (vq + ".q", trainer.sh_packed, DTYPE_U1), (vq + ".qb", trainer.sh_bounds, DTYPE_F4)]
+    radii = densifier.radii if densifier is not None else getattr(trainer, "radii", None)
+    if radii is not None:
+        out.append(("eng.radii", radii, DTYPE_F4))
     if densifier is not None:
-        out += [("eng.radii", densifier.radii, DTYPE_F4), ("eng.accum_buffer", densifier.accum_buffer, DTYPE_F4)]
+        out.append(("eng.accum_buffer", densifier.accum_buffer, DTYPE_F4))
+    if getattr(trainer, "steps", None) is not None:
+        out.append(("eng.bias_correction_steps", trainer.steps, DTYPE_I4))
     return out
 
 
@@ -192,7 +198,8 @@ def load_checkpoint(trainer, input_dir, densifier=None):
         if _json_value(text, "max_num_splats", 0) != trainer.n:
             raise RuntimeError(f"load_checkpoint: max_num_splats mismatch (trainer {trainer.n} vs checkpoint "
                                f"{_json_value(text, 'max_num_splats', 0)})")
-        want = (8 if trainer.quant else 32, trainer.cfg.sh_value_bits if trainer.quant else 32, trainer.non_sh_optim_bits, 0, 0)
+        want = (8 if trainer.quant else 32, trainer.cfg.sh_value_bits if trainer.quant else 32, trainer.non_sh_optim_bits,
+                1 if getattr(trainer, "steps", None) is not None else 0, 0)
         have = tuple(_json_value(text, k, d) for k, d in (("sh_optim_bits", 32), ("sh_value_bits", 32), ("non_sh_optim_bits", 32),
                                                           ("use_per_splat_bias_correction", 0), ("use_fused_proj_bwd_optim", 0)))
         if want != have:

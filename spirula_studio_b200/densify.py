@@ -66,7 +66,10 @@ class Densifier:
         n, dev, lib = trainer.n, trainer.device, trainer.lib
         assert 0 < self.count <= n
         z = lambda *shape, dt=torch.float32: torch.zeros(*shape, dtype=dt, device=dev)
-        self.radii, self.accum_weight, self.accum_den = z(n), z(n), z(n)
+        # the view radii are shared with the trainer's scale-agnostic mean update when that is on
+        self.radii = trainer.radii if getattr(trainer, "radii", None) is not None else z(n)
+        trainer._radii_external = True
+        self.accum_weight, self.accum_den = z(n), z(n)
         self.accum_buffer, self.sample_score = z(n, 2), z(n, 2)
         self.ws = z(int(lib.ssb_densify_relocate_workspace_bytes(n)) + int(lib.ssb_densify_workspace_bytes(n)), dt=torch.uint8)
         self.num_relocated = z(1, dt=torch.int32)
@@ -85,7 +88,7 @@ class Densifier:
             st.sh = L.SsbShAdamState(None, None, None, None, 32, 0)
         st.d_accum_buffer = self.accum_buffer.data_ptr()
         st.d_sample_score = None
-        st.d_steps = None
+        st.d_steps = trainer.steps.data_ptr() if getattr(trainer, "steps", None) is not None else None
         self.state = st
 
     def before_step(self):
@@ -97,7 +100,8 @@ class Densifier:
         c, tr, lib = self.cfg, self.tr, self.tr.lib
         if tr.world_size > 1:
             import torch.distributed as dist
-            dist.all_reduce(self.radii, op=dist.ReduceOp.MAX, group=tr.pg)
+            if tr.radii is None:                 # (the trainer's optimiser step has combined shared radii already)
+                dist.all_reduce(self.radii, op=dist.ReduceOp.MAX, group=tr.pg)
             dist.all_reduce(self.accum_weight, op=dist.ReduceOp.MAX if c.accum_mode == L.SSB_ACCUM_MAX else dist.ReduceOp.SUM, group=tr.pg)
             if c.accum_mode == L.SSB_ACCUM_AVG:
                 dist.all_reduce(self.accum_den, op=dist.ReduceOp.SUM, group=tr.pg)

@@ -26,6 +26,7 @@ torch supplies device memory, streams and torch.distributed; all arithmetic is
 done by libssb_b200 through its C ABI.
 """
 import ctypes as C
+from dataclasses import dataclass
 
 import numpy as np
 import torch
@@ -55,9 +56,26 @@ def _flat_views(flat, n, attrs=_ATTRS):
     return out
 
 
+@dataclass
+class OptimOptions:
+    """The reference's optimiser flags next to the learning rates (OptimConfig, src/engine/EngineConfig.h; stock values of
+    src/config/TrainConfig.h:258-304): per-splat regularisers, the scale-agnostic mean update, per-splat bias-correction
+    counters.  Passed to Trainer(optim=...); without it the trainer runs the plain Adam step the benchmark times."""
+    max_gauss_ratio: float = 10.0
+    scale_regularization_weight: float = 0.0
+    opacity_reg: float = 0.01            # mcmc_opacity_reg_weight
+    scale_reg: float = 0.01              # mcmc_scale_reg_weight
+    erank_reg: float = 0.0
+    erank_reg_s3: float = 0.0
+    quat_norm_reg: float = 0.01
+    sh_reg: float = 0.001
+    use_scale_agnostic_mean: bool = True
+    use_per_splat_bias_correction: bool = True
+
+
 class Trainer:
     def __init__(self, cfg: SceneConfig, splats: dict, device="cuda:0", isect_capacity=0, w_l1=0.8, w_ssim=0.2,
-                 process_group=None, world_size=1, rank=0, grad_sync="peer", fused_backward=False, non_sh_optim_bits=32):
+                 process_group=None, world_size=1, rank=0, grad_sync="peer", fused_backward=False, non_sh_optim_bits=32, optim=None):
         self.lib = L.load()
         self.cfg = cfg
         self.device = torch.device(device)
@@ -140,6 +158,24 @@ class Trainer:
         if self.fused_backward:
             L.check(self.lib.ssb_step_set_fused_backward(self.handle, max(int(cfg.n_views), 1)))
             self._fused_room = max(int(cfg.n_views), 1)
+        # the reference's optimiser options: regularisers, scale-agnostic mean (needs the view radii), per-splat counters
+        self.optim = optim
+        self.radii = self.steps = None
+        self._extras = None
+        self._radii_external = False         # a Densifier clears the radii itself (before_step)
+        if optim is not None:
+            if self.fused_backward:
+                raise NotImplementedError("the optimiser options run with the per-view backward")
+            if optim.use_scale_agnostic_mean:
+                self.radii = torch.zeros(n, dtype=torch.float32, device=dev)
+                for h in self.handles:
+                    L.check(self.lib.ssb_step_set_radii(h, L.ptr(self.radii)))
+            if optim.use_per_splat_bias_correction:
+                self.steps = torch.zeros(n, dtype=torch.int32, device=dev)
+            self._extras = L.SsbAdamExtras(optim.max_gauss_ratio, optim.scale_regularization_weight, optim.opacity_reg, optim.scale_reg,
+                                           optim.erank_reg, optim.erank_reg_s3, optim.quat_norm_reg, 1 if optim.use_scale_agnostic_mean else 0,
+                                           self.radii.data_ptr() if self.radii is not None else None,
+                                           self.steps.data_ptr() if self.steps is not None else None, n, None)
         # the range of splats whose optimiser step this rank performs
         self.first, self.count = 0, n
         if self.grad_sync in ("peer", "multimem"):
@@ -380,8 +416,13 @@ class Trainer:
         lr = self.cfg.lrs
         self.iteration += 1
         cfg = L.SsbAdamConfig(lr["lr_means"], lr["lr_quats"], lr["lr_scales"], lr["lr_opacities"], lr["lr_features_dc"],
-                              lr["lr_features_sh"], 0.0, 1.0 / float(total_views), self.iteration, 0)
+                              lr["lr_features_sh"], self.optim.sh_reg if self.optim is not None else 0.0, 1.0 / float(total_views), self.iteration, 0)
         f, c = self.first, self.count
+        ex = C.byref(self._extras) if self._extras is not None else None
+        if self.steps is not None:
+            self.steps += 1                        # every slot, before use (src/engine/EngineOptim.cpp:367-375)
+        if self.radii is not None and self.world_size > 1:
+            torch.distributed.all_reduce(self.radii, op=torch.distributed.ReduceOp.MAX, group=self.pg)    # every rank saw other views
         if self.fused_backward:
             cams = self._kept_cams
             if not cams:
@@ -402,8 +443,10 @@ class Trainer:
             if self.quant:
                 sh = L.SsbShAdamState(self.sh_optim_packed.data_ptr(), self.sh_optim_bounds.data_ptr(), self.sh_packed.data_ptr(),
                                       self.sh_bounds.data_ptr(), self.cfg.sh_value_bits, 8)
+            if sh is not None and self.steps is not None:
+                raise NotImplementedError("per-splat counters with quantised SH run with grad_sync 'nccl' or one rank")
             args = (C.byref(self._replicas), C.byref(self._p_struct), C.byref(self._g_struct), C.byref(self._m1_struct), C.byref(self._m2_struct),
-                    C.byref(sh) if sh is not None else None, f, c, self.n, C.byref(cfg), None)
+                    C.byref(sh) if sh is not None else None, f, c, self.n, C.byref(cfg), ex)
             if getattr(self, "trace", None) is not None:          # the same three steps with a time mark after each
                 self._barrier(); self._mark("barrier1")
                 L.check(self.lib.ssb_reduce_adam_broadcast(*args, stream)); self._mark("reduce_adam_broadcast")
@@ -411,20 +454,29 @@ class Trainer:
             else:
                 L.check(self.lib.ssb_exchange_step(*args, self._barrier_cb, None, stream))
             return
+        d_steps = L.ptr(self.steps) if self.steps is not None else None
         if self._nsq is not None:
-            L.check(self.lib.ssb_adam_step_q16(C.byref(self._p_struct), C.byref(self._g_struct), C.byref(self._nsq), f, c, C.byref(cfg), None, stream))
+            L.check(self.lib.ssb_adam_step_q16(C.byref(self._p_struct), C.byref(self._g_struct), C.byref(self._nsq), f, c, C.byref(cfg), ex, stream))
             if not self.quant:
                 L.check(self.lib.ssb_adam_plain(L.ptr(self.params["features_sh"]), L.ptr(self.grads["features_sh"]), L.ptr(self.m1["features_sh"]),
-                                                L.ptr(self.m2["features_sh"]), self.n * 45, 45, lr["lr_features_sh"], self.iteration, None, 0.0, 0.0,
-                                                1.0 / float(total_views), 0, stream))
+                                                L.ptr(self.m2["features_sh"]), self.n * 45, 45, lr["lr_features_sh"], self.iteration, d_steps,
+                                                cfg.sh_reg_weight, 0.0, 1.0 / float(total_views), 0, stream))
+        elif ex is not None:
+            L.check(self.lib.ssb_adam_step_ex(C.byref(self._p_struct), C.byref(self._g_struct), C.byref(self._m1_struct),
+                                              C.byref(self._m2_struct), f, c, C.byref(cfg), ex, stream))
         else:
             L.check(self.lib.ssb_adam_step(C.byref(self._p_struct), C.byref(self._g_struct), C.byref(self._m1_struct),
                                            C.byref(self._m2_struct), f, c, C.byref(cfg), stream))
         if self.quant:
             cells = self.n * 45
-            L.check(self.lib.ssb_adam_step_sh_quantized(L.ptr(self.grads["features_sh"]), L.ptr(self.sh_optim_packed),
-                                                        L.ptr(self.sh_optim_bounds), L.ptr(self.sh_packed), L.ptr(self.sh_bounds),
-                                                        self.cfg.sh_value_bits, f * 45, c * 45, cells, C.byref(cfg), stream))
+            if d_steps is not None:
+                L.check(self.lib.ssb_adam_step_sh_quantized_ex(L.ptr(self.grads["features_sh"]), L.ptr(self.sh_optim_packed),
+                                                               L.ptr(self.sh_optim_bounds), L.ptr(self.sh_packed), L.ptr(self.sh_bounds),
+                                                               self.cfg.sh_value_bits, 8, f * 45, c * 45, cells, C.byref(cfg), d_steps, 45, stream))
+            else:
+                L.check(self.lib.ssb_adam_step_sh_quantized(L.ptr(self.grads["features_sh"]), L.ptr(self.sh_optim_packed),
+                                                            L.ptr(self.sh_optim_bounds), L.ptr(self.sh_packed), L.ptr(self.sh_bounds),
+                                                            self.cfg.sh_value_bits, f * 45, c * 45, cells, C.byref(cfg), stream))
 
     # -- whole iteration ---------------------------------------------------
     def step_device(self, d_viewmats, d_intrins, d_gt, n_local_views, total_views):
@@ -434,6 +486,8 @@ class Trainer:
     def step_device_kinds(self, batches, total_views):
         """One iteration; `batches` = [(kind, d_viewmats, d_intrins, d_gt, n_views), ...], this rank's views by camera kind."""
         self.losses.zero_()
+        if self.radii is not None and not self._radii_external:
+            self.radii.zero_()
         first = True
         for kind, d_viewmats, d_intrins, d_gt, nv in batches:
             if nv > 0:
@@ -477,6 +531,8 @@ class Trainer:
         main = torch.cuda.current_stream(self.device)
         k = self._calls & 1
         self.losses.zero_()
+        if self.radii is not None and not self._radii_external:
+            self.radii.zero_()
         # staging set k was last read by the iteration before the previous one
         if self._set_free[k] is not None:
             self._copy_stream.wait_event(self._set_free[k])

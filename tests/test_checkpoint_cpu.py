@@ -142,7 +142,7 @@ def test_manifest_text_and_slot_list_follow_the_reference():
     from types import SimpleNamespace
     from spirula_studio_b200 import checkpoint as ck
     from spirula_studio_b200.scenes import CONFIGS
-    tr = SimpleNamespace(cfg=CONFIGS["mid_1m"], n=1000, quant=True, non_sh_optim_bits=32)
+    tr = SimpleNamespace(cfg=CONFIGS["mid_1m"], n=1000, quant=True, non_sh_optim_bits=32, steps=None, radii=None)
     text = ck.state_json(tr, 42)
     keys = [ln.split('"')[1] for ln in text.splitlines() if ln.startswith('  "')]
     assert keys == ["format_version", "full_resume", "quant_codec", "quant_block_size", "quant_eps", "step", "primitive",
@@ -172,3 +172,10 @@ def test_manifest_text_and_slot_list_follow_the_reference():
     names = [n for n, _, _ in ck.saved_buffers(tr)]
     assert names == [f"world.{a}" for a in geo] + [f"eng.{a}_qfpbo.{x}" for a in geo for x in ("q", "qb")] + \
         ["eng.sh_quant.q", "eng.sh_quant.qb", "eng.world.sh_vq16.q", "eng.world.sh_vq16.qb"]
+    # optimiser options: the radii of the scale-agnostic mean and the per-splat counters follow, in the slot table's order
+    tr.steps = tr.radii = object()
+    assert '"use_per_splat_bias_correction": 1' in ck.state_json(tr, 1)
+    dens = SimpleNamespace(radii=object(), accum_buffer=None, count=900)
+    assert [n for n, _, _ in ck.saved_buffers(tr, dens)][-3:] == ["eng.radii", "eng.accum_buffer", "eng.bias_correction_steps"]
+    assert [n for n, _, _ in ck.saved_buffers(tr)][-2:] == ["eng.radii", "eng.bias_correction_steps"]
+    assert '"cur_num_splats": 900' in ck.state_json(tr, 1, cur_num_splats=900)

@@ -152,24 +152,32 @@ def test_densifying_run_resumes_with_its_strategy_state(lib, tmp_path):
             counts.append(dn.count)
         return counts
 
-    tr, dn = Trainer(cfg, sp, device=DEV), None
+    from spirula_studio_b200.trainer import OptimOptions
+    tr = Trainer(cfg, sp, device=DEV, optim=OptimOptions())        # the reference's stock optimiser flags: radii and counters are state too
     dn = Densifier(tr, dc, 8000)
+    assert dn.radii is tr.radii
     run(tr, dn, 0, 10)
     assert 8000 < dn.count < cfg.n_splats and dn.accum_buffer.any()
     path = ck.save_checkpoint(tr, str(tmp_path), step=10, densifier=dn)
     with tarfile.open(path) as t:
         names = [m.name for m in t.getmembers()]
         text = t.extractfile("state.json").read().decode()
-    assert names[-2:] == ["eng.radii.npy", "eng.accum_buffer.npy"] and f'"cur_num_splats": {dn.count}' in text
+    assert names[-3:] == ["eng.radii.npy", "eng.accum_buffer.npy", "eng.bias_correction_steps.npy"] and f'"cur_num_splats": {dn.count}' in text
+    assert '"use_per_splat_bias_correction": 1' in text
     assert f'"max_num_splats": {cfg.n_splats}' in text
     num = C.c_int64(0)
     deg = C.c_int32(0)
     L.check(lib.ssb_ply_info(str(tmp_path / "splat.ply").encode(), C.byref(num), C.byref(deg)))
     assert 0 < num.value <= dn.count                      # unused slots (opacity logit -30) never reach the PLY
-    tr2 = Trainer(cfg, {k: np.zeros_like(v) + (1.0 if k == "quats" else 0.0) for k, v in sp.items()}, device=DEV)
+    tr2 = Trainer(cfg, {k: np.zeros_like(v) + (1.0 if k == "quats" else 0.0) for k, v in sp.items()}, device=DEV, optim=OptimOptions())
     dn2 = Densifier(tr2, dc, 1)
     assert ck.load_checkpoint(tr2, str(tmp_path), densifier=dn2) == 10
     assert dn2.count == dn.count and torch.equal(dn2.accum_buffer, dn.accum_buffer) and torch.equal(dn2.radii, dn.radii)
+    assert torch.equal(tr2.steps, tr.steps) and tr.steps.max().item() == 10 and tr.steps.min().item() < 10       # relocated splats restart their counters
+    plain = Trainer(cfg, sp, device=DEV)
+    with pytest.raises(RuntimeError, match="layout"):
+        ck.load_checkpoint(plain, str(tmp_path))
+    plain.close()
     a, b = run(tr, dn, 10, steps), run(tr2, dn2, 10, steps)
     assert a == b and a[-1] > a[0]
     for k in ("means", "scales", "opacities"):

@@ -267,6 +267,54 @@ def test_iteration_with_sh_degree_warmup_matches_oracle(lib, U, oracle, quant):
     tr.close()
 
 
+@pytest.mark.parametrize("quant", [False, True])
+def test_iteration_with_the_reference_optimiser_options_matches_oracle(lib, U, oracle, quant):
+    """Trainer(optim=OptimOptions()): the stock optimiser flags of the reference -- per-splat regularisers, the scale-agnostic
+    mean update fed by the iteration's view radii, per-splat bias-correction counters, the SH regulariser -- against the
+    oracle's optimiser on the oracle's gradients, two iterations."""
+    from spirula_studio_b200.trainer import OptimOptions, Trainer
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=9000, width=176, height=128, n_views=2)
+    cfg.rig, cfg.rig_radius, cfg.log_scale_mu = "ring", 3.0, -3.0
+    if quant:
+        cfg.sh_value_bits, cfg.sh_optim_bits = 16, 8
+    sp = scenes.make_splats(cfg)
+    vm, K = scenes.make_cameras(cfg)
+    targets = np.stack([scenes.make_target(cfg, v) for v in range(cfg.n_views)])
+    opt = OptimOptions(sh_reg=0.05)
+    n, W, H = cfg.n_splats, cfg.width, cfg.height
+    shq = None
+    if quant:
+        packed, bounds = oracle.quant_encode(sp["features_sh"], 16)
+        shq = dict(packed=packed, bounds=bounds, bits=16, bounds_stride=256)
+    ref_g, ref_l, _ = _oracle_iteration(oracle, cfg, sp, vm, K, targets, shq)
+    radii = oracle.project_fwd(sp, vm, K, W, H, shq=shq)["radii"]
+    tr = Trainer(cfg, sp, device=U.DEV, optim=opt)
+    d_vm, d_K, d_gt = (torch.from_numpy(a).to(U.DEV) for a in (vm, K, targets))
+    tr.step_device(d_vm, d_K, d_gt, cfg.n_views, cfg.n_views)
+    torch.cuda.synchronize()
+    assert np.allclose(tr.radii.cpu().numpy(), radii, rtol=1e-3, atol=1e-6) and radii.max() > 0
+    assert (tr.steps == 1).all()
+    p, m1, m2 = _np_state(sp)
+    gs = 1.0 / cfg.n_views
+    steps = np.ones(n, np.int32)
+    reg = [opt.max_gauss_ratio, opt.scale_regularization_weight, opt.opacity_reg, opt.scale_reg, opt.erank_reg, opt.erank_reg_s3, opt.quat_norm_reg]
+    oracle.adam_geometry_ex(p, {k: v.copy() for k, v in ref_g.items()}, m1, m2, 1, cfg.lrs, grad_scale=gs, reg=reg, scale_agnostic=True, radii=radii, steps=steps)
+    oracle.adam_plain(p["features_dc"], ref_g["features_dc"].copy(), m1["features_dc"], m2["features_dc"], 1, cfg.lrs["lr_features_dc"], opt.sh_reg,
+                      0.5 / 0.28209479177387814, gs, steps=steps, stride=3)
+    for k in ("means", "quats", "scales", "opacities", "features_dc"):
+        got = tr.params[k].cpu().numpy().reshape(p[k].shape)
+        assert U.close_frac(got, p[k], 1e-6, 1e-3) <= 2e-2, k
+    plain = Trainer(cfg, sp, device=U.DEV)
+    plain.step_device(d_vm, d_K, d_gt, cfg.n_views, cfg.n_views)
+    torch.cuda.synchronize()
+    assert (plain.params["scales"] - tr.params["scales"]).abs().max().item() > 0        # the options do change the step
+    # a second iteration: the counters advance, the radii are those of this iteration only
+    tr.step_device(d_vm, d_K, d_gt, cfg.n_views, cfg.n_views)
+    torch.cuda.synchronize()
+    assert (tr.steps == 2).all() and np.isfinite(tr.params["means"].cpu().numpy()).all()
+    tr.close(); plain.close()
+
+
 def test_forward_only_render_matches_oracle_and_leaves_training_alone(lib, U, oracle):
     """ssb_step_render (the viewer's forward-only path): colour, normalised ray depth and transmittance of an arbitrary camera
     against the oracle's forward chain, at full and at a lower SH degree; rendering between iterations changes nothing in them."""

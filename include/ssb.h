@@ -589,6 +589,15 @@ int ssb_reduce_adam_broadcast(const SsbPeerReplicas* replicas, const SsbSplats* 
                               int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg,
                               const SsbAdamExtras* extras, void* stream);
 
+/* The same with the moments of means, rotations, scales, opacities and DC in 16-bit codes (SsbMomentsQ16, see
+ * ssb_adam_step_q16): m1 / m2 then only carry features_sh and may be NULL when sh_state is given.  A rank's range must start
+ * on a multiple of 256 splats (the codes' bounds are per block of 256); gradients and parameters move by per-peer loads and
+ * stores (the multicast kernels keep fp32 moments). */
+int ssb_reduce_adam_broadcast_q16(const SsbPeerReplicas* replicas, const SsbSplats* params, const SsbSplats* grads,
+                                  const SsbMomentsQ16* moments, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                                  int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg,
+                                  const SsbAdamExtras* extras, void* stream);
+
 /* barrier, ssb_reduce_adam_broadcast, barrier.  `barrier(ctx, stream)` must return 0 once every rank has reached it,
  * ordered on `stream` (an NCCL all-reduce of one element enqueued on the stream does that), and non-zero when a rank
  * is missing or the wait timed out: ssb_exchange_step then returns SSB_ERR_PEER -- before the exchange nothing has been
@@ -598,6 +607,10 @@ int ssb_exchange_step(const SsbPeerReplicas* replicas, const SsbSplats* params, 
                       const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
                       int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg, const SsbAdamExtras* extras,
                       SsbBarrierFn barrier, void* barrier_ctx, void* stream);
+int ssb_exchange_step_q16(const SsbPeerReplicas* replicas, const SsbSplats* params, const SsbSplats* grads,
+                          const SsbMomentsQ16* moments, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                          int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg, const SsbAdamExtras* extras,
+                          SsbBarrierFn barrier, void* barrier_ctx, void* stream);
 
 /* Owns every intermediate buffer of an iteration (the reference keeps them in
  * its process-global DevicePool, src/core/Tensor.h:151-351) and runs, per view,

@@ -297,7 +297,7 @@ __global__ void __launch_bounds__(256) adam_geometry_kernel(
     SsbSplats p, SsbSplats g, SsbSplats m1, SsbSplats m2, int64_t first, int64_t count, SsbAdamConfig cfg,
     float ibc1, float ibc2, float dc_decay, SsbAdamExtras ex, PeerOffsets po, MomentsQ16 nq = MomentsQ16{}) {
     int64_t i = first + (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    static_assert(!(NQ && PEER), "the quantised moments are built for the single-rank launch");
+    static_assert(!(NQ && PEER == 2), "the quantised moments take per-peer loads and stores, not the multicast address");
     constexpr int kMom = NQ ? 14 * 256 : 4;
     __shared__ __align__(16) float mom1[kMom], mom2[kMom];
     __shared__ uint32_t mm_sh[NQ ? 20 : 1][8];
@@ -751,10 +751,21 @@ __global__ void __launch_bounds__(256) quant_decode_kernel(const uint8_t* __rest
 
 namespace ssb {
 
+static int moments_q16_of(const SsbMomentsQ16* moments, MomentsQ16* out) {
+    for (int t = 0; t < 5; ++t) {
+        SSB_REQUIRE(moments->d_packed[t] && moments->d_bounds[t], "16-bit moments: array %d missing", t);
+        out->packed[t] = moments->d_packed[t];
+        out->bounds[t] = (float4*)moments->d_bounds[t];
+    }
+    return SSB_OK;
+}
+
 static int adam_step_impl(const SsbSplats* params, const SsbSplats* grads, const SsbSplats* m1, const SsbSplats* m2,
                           int64_t first, int64_t count, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, const PeerOffsets* peers,
-                          void* stream) {
-    SSB_REQUIRE(params && grads && m1 && m2 && cfg, "ssb_adam_step: NULL argument");
+                          void* stream, const MomentsQ16* nq = nullptr) {
+    // nq: the moments of the five non-SH arrays are 16-bit codes (m1 / m2 then only carry features_sh, if that is fp32)
+    SSB_REQUIRE(params && grads && cfg && (nq || (m1 && m2)), "ssb_adam_step: NULL argument");
+    SSB_REQUIRE(!nq || count == 0 || first % 256 == 0, "ssb_adam_step: with 16-bit moments the range must start on a multiple of 256 splats");
     SSB_REQUIRE(first >= 0 && count >= 0, "ssb_adam_step: bad range");
     SSB_REQUIRE(cfg->step >= 1, "ssb_adam_step: step must be >= 1 (got %d)", cfg->step);
     if (extras) {
@@ -768,20 +779,30 @@ static int adam_step_impl(const SsbSplats* params, const SsbSplats* grads, const
     // decay = 2 * l2_reg / numel of the whole tensor (fused_adam_step, FusedAppearanceOptim.cu:85); without
     // extras->n_total the whole tensor is taken to be this call's range
     const int64_t n_whole = extras ? extras->n_total : count;
-    const float dc_decay = 2.0f * cfg->sh_reg_weight / (float)(n_whole * 3);
+    // with 16-bit moments the reference applies sh_reg_weight to DC undivided (FusedGeometryOptim.cu:343-345)
+    const float dc_decay = nq ? cfg->sh_reg_weight : 2.0f * cfg->sh_reg_weight / (float)(n_whole * 3);
     const unsigned blocks = (unsigned)ceil_div(count, 256);
     const PeerOffsets none = {};
     const SsbAdamExtras no_extras = {};
-#define SSB_GEO(EX, PEER) adam_geometry_kernel<EX, PEER><<<blocks, 256, 0, st>>>(*params, *grads, *m1, *m2, first, count, *cfg, ibc1, ibc2, dc_decay, \
-                                                                            EX ? *extras : no_extras, PEER ? *peers : none)
+    const SsbSplats no_moments{};
     // multicast mode is built for the plain launch only; the optional parts use per-peer loads and stores
     const bool mc = peers && peers->mc_grads != 0 && peers->mc_params != 0;
-    if (extras) { if (peers) SSB_GEO(true, 1); else SSB_GEO(true, 0); }
-    else { if (mc) SSB_GEO(false, 2); else if (peers) SSB_GEO(false, 1); else SSB_GEO(false, 0); }
+    if (nq) {
+#define SSB_GEOQ(EX, PEER) adam_geometry_kernel<EX, PEER, true><<<blocks, 256, 0, st>>>(*params, *grads, no_moments, no_moments, first, count, *cfg, ibc1, ibc2, \
+                                                                                   dc_decay, EX ? *extras : no_extras, PEER ? *peers : none, *nq)
+        if (extras) { if (peers) SSB_GEOQ(true, 1); else SSB_GEOQ(true, 0); }
+        else { if (peers) SSB_GEOQ(false, 1); else SSB_GEOQ(false, 0); }
+#undef SSB_GEOQ
+    } else {
+#define SSB_GEO(EX, PEER) adam_geometry_kernel<EX, PEER><<<blocks, 256, 0, st>>>(*params, *grads, *m1, *m2, first, count, *cfg, ibc1, ibc2, dc_decay, \
+                                                                            EX ? *extras : no_extras, PEER ? *peers : none)
+        if (extras) { if (peers) SSB_GEO(true, 1); else SSB_GEO(true, 0); }
+        else { if (mc) SSB_GEO(false, 2); else if (peers) SSB_GEO(false, 1); else SSB_GEO(false, 0); }
 #undef SSB_GEO
+    }
     SSB_LAUNCHED("adam_geometry_kernel");
     if (params->features_sh) {
-        SSB_REQUIRE(grads->features_sh && m1->features_sh && m2->features_sh, "ssb_adam_step: SH gradient/moment arrays missing");
+        SSB_REQUIRE(grads->features_sh && m1 && m2 && m1->features_sh && m2->features_sh, "ssb_adam_step: SH gradient/moment arrays missing");
         int64_t numel = count * 3 * kNumSh, off = first * 3 * kNumSh;
         const float sh_decay = 2.0f * cfg->sh_reg_weight / (float)(n_whole * 3 * kNumSh);
         const int32_t* steps = extras && extras->d_steps ? extras->d_steps + first : nullptr;
@@ -891,30 +912,12 @@ int ssb_adam_step_q16(const SsbSplats* params, const SsbSplats* grads, const Ssb
     SSB_REQUIRE(params && grads && moments && cfg, "ssb_adam_step_q16: NULL argument");
     SSB_REQUIRE(params->means && params->quats && params->scales && params->opacities && params->features_dc, "ssb_adam_step_q16: parameter arrays missing");
     SSB_REQUIRE(grads->means && grads->quats && grads->scales && grads->opacities && grads->features_dc, "ssb_adam_step_q16: gradient arrays missing");
-    SSB_REQUIRE(first >= 0 && count >= 0 && first % 256 == 0, "ssb_adam_step_q16: the range must start on a multiple of 256 splats");
-    SSB_REQUIRE(cfg->step >= 1, "ssb_adam_step_q16: step must be >= 1 (got %d)", cfg->step);
     MomentsQ16 nq;
-    for (int t = 0; t < 5; ++t) {
-        SSB_REQUIRE(moments->d_packed[t] && moments->d_bounds[t], "ssb_adam_step_q16: moment array %d missing", t);
-        nq.packed[t] = moments->d_packed[t];
-        nq.bounds[t] = (float4*)moments->d_bounds[t];
-    }
-    if (extras) {
-        SSB_REQUIRE(extras->n_total >= first + count, "ssb_adam_step_q16: n_total %lld is smaller than the range's end", (long long)extras->n_total);
-        SSB_REQUIRE(!extras->use_scale_agnostic_mean || extras->d_radii, "ssb_adam_step_q16: the scale-agnostic mean update needs d_radii");
-    }
-    if (count == 0) return SSB_OK;
-    const float ibc1 = 1.0f / (1.0f - powf(kBeta1, (float)cfg->step)), ibc2 = 1.0f / (1.0f - powf(kBeta2, (float)cfg->step));
-    // in this path the reference applies sh_reg_weight to DC undivided (FusedGeometryOptim.cu:343-345)
-    const float dc_decay = cfg->sh_reg_weight;
-    const SsbSplats none{};
-    const SsbAdamExtras no_extras{};
-    const unsigned blocks = (unsigned)ceil_div(count, 256);
-    cudaStream_t st = (cudaStream_t)stream;
-    if (extras) adam_geometry_kernel<true, 0, true><<<blocks, 256, 0, st>>>(*params, *grads, none, none, first, count, *cfg, ibc1, ibc2, dc_decay, *extras, PeerOffsets{}, nq);
-    else adam_geometry_kernel<false, 0, true><<<blocks, 256, 0, st>>>(*params, *grads, none, none, first, count, *cfg, ibc1, ibc2, dc_decay, no_extras, PeerOffsets{}, nq);
-    SSB_LAUNCHED("adam_geometry_kernel<q16>");
-    return SSB_OK;
+    if (int e = moments_q16_of(moments, &nq)) return e;
+    // features_sh is not this call's business: the caller steps it with ssb_adam_plain or ssb_adam_step_sh_quantized
+    SsbSplats p = *params, g = *grads;
+    p.features_sh = nullptr; g.features_sh = nullptr;
+    return adam_step_impl(&p, &g, nullptr, nullptr, first, count, cfg, extras, nullptr, stream, &nq);
 }
 
 int ssb_adam_plain(float* d_param, float* d_grad, float* d_m1, float* d_m2, int64_t numel, int32_t stride, float lr, int32_t step,
@@ -947,11 +950,17 @@ int ssb_adam_step_sh_quantized_ex(float* d_grad, uint8_t* d_optim_packed, float*
                                        numel, numel_total, cfg, d_steps, cells_per_splat, nullptr, stream);
 }
 
-int ssb_reduce_adam_broadcast(const SsbPeerReplicas* replicas, const SsbSplats* params, const SsbSplats* grads,
-                              const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
-                              int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream) {
+static int reduce_adam_broadcast_impl(const SsbPeerReplicas* replicas, const SsbSplats* params, const SsbSplats* grads,
+                                      const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                                      int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream,
+                                      const SsbMomentsQ16* moments_q16) {
     using namespace ssb;
-    SSB_REQUIRE(replicas && params && grads && m1 && m2 && cfg, "ssb_reduce_adam_broadcast: NULL argument");
+    SSB_REQUIRE(replicas && params && grads && cfg && (moments_q16 || (m1 && m2)), "ssb_reduce_adam_broadcast: NULL argument");
+    MomentsQ16 nq;
+    if (moments_q16) {
+        if (int e = moments_q16_of(moments_q16, &nq)) return e;
+        SSB_REQUIRE(count == 0 || first % 256 == 0, "ssb_reduce_adam_broadcast_q16: a rank's range must start on a multiple of 256 splats");
+    }
     SSB_REQUIRE(first >= 0 && count >= 0 && first + count <= n_total, "ssb_reduce_adam_broadcast: bad splat range");
     const bool quantised = sh_state != nullptr;
     SSB_REQUIRE(quantised == (params->features_sh == nullptr), "ssb_reduce_adam_broadcast: give either fp32 SH inside params or an SsbShAdamState");
@@ -975,6 +984,7 @@ int ssb_reduce_adam_broadcast(const SsbPeerReplicas* replicas, const SsbSplats* 
         SSB_REQUIRE((first * 3 * kNumSh) % 256 == 0 && (((first + count) * 3 * kNumSh) % 256 == 0 || first + count == n_total),
                     "ssb_reduce_adam_broadcast: a rank's range must cover whole 256-cell quantisation blocks (splat ranges in multiples of 256)");
     }
+    if (moments_q16) { po.mc_grads = 0; po.mc_params = 0; }      // per-peer loads and stores (the multicast kernels keep fp32 moments)
     const PeerOffsets* peers = po.n > 0 ? &po : nullptr;
     if (peers) {
         // the kernels move a CTA's 256 splats of every array with 16-byte accesses
@@ -989,7 +999,7 @@ int ssb_reduce_adam_broadcast(const SsbPeerReplicas* replicas, const SsbSplats* 
         ex_local.n_total = n_total;
         ex = cfg->sh_reg_weight != 0.0f ? &ex_local : nullptr;
     }
-    if (int e = adam_step_impl(params, grads, m1, m2, first, count, cfg, ex, peers, stream)) return e;
+    if (int e = adam_step_impl(params, grads, m1, m2, first, count, cfg, ex, peers, stream, moments_q16 ? &nq : nullptr)) return e;
     if (quantised) {
         const int32_t* steps = extras ? extras->d_steps : nullptr;
         return adam_sh_quantized_impl(grads->features_sh, sh_state->d_optim_packed, sh_state->d_optim_bounds, sh_state->d_value_packed,
@@ -999,10 +1009,24 @@ int ssb_reduce_adam_broadcast(const SsbPeerReplicas* replicas, const SsbSplats* 
     return SSB_OK;
 }
 
-int ssb_exchange_step(const SsbPeerReplicas* replicas, const SsbSplats* params, const SsbSplats* grads,
-                      const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
-                      int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg, const SsbAdamExtras* extras,
-                      SsbBarrierFn barrier, void* barrier_ctx, void* stream) {
+int ssb_reduce_adam_broadcast(const SsbPeerReplicas* replicas, const SsbSplats* params, const SsbSplats* grads,
+                              const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                              int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream) {
+    SSB_REQUIRE(m1 && m2, "ssb_reduce_adam_broadcast: NULL argument");
+    return reduce_adam_broadcast_impl(replicas, params, grads, m1, m2, sh_state, first, count, n_total, cfg, extras, stream, nullptr);
+}
+
+int ssb_reduce_adam_broadcast_q16(const SsbPeerReplicas* replicas, const SsbSplats* params, const SsbSplats* grads,
+                                  const SsbMomentsQ16* moments, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                                  int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream) {
+    SSB_REQUIRE(moments, "ssb_reduce_adam_broadcast_q16: NULL moments");
+    return reduce_adam_broadcast_impl(replicas, params, grads, m1, m2, sh_state, first, count, n_total, cfg, extras, stream, moments);
+}
+
+static int exchange_step_impl(const SsbPeerReplicas* replicas, const SsbSplats* params, const SsbSplats* grads,
+                              const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                              int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg, const SsbAdamExtras* extras,
+                              SsbBarrierFn barrier, void* barrier_ctx, void* stream, const SsbMomentsQ16* moments_q16) {
     using namespace ssb;
     SSB_REQUIRE(replicas && barrier, "ssb_exchange_step: NULL argument");
     // every rank's backward passes are complete before anyone reads a partial gradient
@@ -1010,13 +1034,29 @@ int ssb_exchange_step(const SsbPeerReplicas* replicas, const SsbSplats* params, 
         set_error("ssb_exchange_step: a rank did not arrive at the barrier before the exchange; nothing was launched");
         return SSB_ERR_PEER;
     }
-    if (int e = ssb_reduce_adam_broadcast(replicas, params, grads, m1, m2, sh_state, first, count, n_total, cfg, extras, stream)) return e;
+    if (int e = reduce_adam_broadcast_impl(replicas, params, grads, m1, m2, sh_state, first, count, n_total, cfg, extras, stream, moments_q16)) return e;
     // every replica is complete before anyone's next forward pass
     if (barrier(barrier_ctx, stream) != 0) {
         set_error("ssb_exchange_step: a rank did not arrive at the barrier after the exchange; replicas may be incomplete");
         return SSB_ERR_PEER;
     }
     return SSB_OK;
+}
+
+int ssb_exchange_step(const SsbPeerReplicas* replicas, const SsbSplats* params, const SsbSplats* grads,
+                      const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                      int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg, const SsbAdamExtras* extras,
+                      SsbBarrierFn barrier, void* barrier_ctx, void* stream) {
+    SSB_REQUIRE(m1 && m2, "ssb_exchange_step: NULL argument");
+    return exchange_step_impl(replicas, params, grads, m1, m2, sh_state, first, count, n_total, cfg, extras, barrier, barrier_ctx, stream, nullptr);
+}
+
+int ssb_exchange_step_q16(const SsbPeerReplicas* replicas, const SsbSplats* params, const SsbSplats* grads,
+                          const SsbMomentsQ16* moments, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                          int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg, const SsbAdamExtras* extras,
+                          SsbBarrierFn barrier, void* barrier_ctx, void* stream) {
+    SSB_REQUIRE(moments, "ssb_exchange_step_q16: NULL moments");
+    return exchange_step_impl(replicas, params, grads, m1, m2, sh_state, first, count, n_total, cfg, extras, barrier, barrier_ctx, stream, moments);
 }
 
 int ssb_quant_encode(const float* d_values, int64_t numel, int32_t bits, void* d_packed, float* d_bounds, void* stream) {

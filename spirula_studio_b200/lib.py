@@ -123,7 +123,9 @@ SIGNATURES = {
     "ssb_peer_reduce_f32": (C.c_int, [_P, _P]),
     "ssb_peer_broadcast": (C.c_int, [_P, _P]),
     "ssb_reduce_adam_broadcast": (C.c_int, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _P]),
+    "ssb_reduce_adam_broadcast_q16": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _P]),
     "ssb_exchange_step": (C.c_int, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P, _P]),
+    "ssb_exchange_step_q16": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P, _P]),
     "ssb_tile_ranges": (C.c_int, [_P, _P, _I64, _I64, _P, _P]),
     "ssb_raster_fwd": (C.c_int, [_P, _I64, _P, _P, _I64, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P]),
     "ssb_raster_bwd": (C.c_int, [_P, _I64, _P, _P, _I64, _P, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _P]),

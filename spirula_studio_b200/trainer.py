@@ -113,8 +113,8 @@ class Trainer:
         self.non_sh_optim_bits = non_sh_optim_bits
         self.nsq_packed, self.nsq_bounds, self._nsq = {}, {}, None
         if non_sh_optim_bits == 16:
-            if self.grad_sync in ("peer", "multimem") or fused_backward:
-                raise NotImplementedError("16-bit non-SH moments run with grad_sync 'nccl' or one rank, and the per-view backward")
+            if fused_backward:
+                raise NotImplementedError("16-bit non-SH moments run with the per-view backward")
             self._nsq = L.SsbMomentsQ16()
             for t, (name, width) in enumerate(_ATTRS[:5]):
                 self.nsq_packed[name] = torch.zeros(n * width * 4, dtype=torch.uint8, device=dev)
@@ -443,16 +443,18 @@ class Trainer:
             if self.quant:
                 sh = L.SsbShAdamState(self.sh_optim_packed.data_ptr(), self.sh_optim_bounds.data_ptr(), self.sh_packed.data_ptr(),
                                       self.sh_bounds.data_ptr(), self.cfg.sh_value_bits, 8)
-            if sh is not None and self.steps is not None:
-                raise NotImplementedError("per-splat counters with quantised SH run with grad_sync 'nccl' or one rank")
-            args = (C.byref(self._replicas), C.byref(self._p_struct), C.byref(self._g_struct), C.byref(self._m1_struct), C.byref(self._m2_struct),
-                    C.byref(sh) if sh is not None else None, f, c, self.n, C.byref(cfg), ex)
+            head = (C.byref(self._replicas), C.byref(self._p_struct), C.byref(self._g_struct))
+            tail = (C.byref(self._m1_struct), C.byref(self._m2_struct), C.byref(sh) if sh is not None else None, f, c, self.n, C.byref(cfg), ex)
+            if self._nsq is not None:            # 16-bit moments of the non-SH arrays: the q16 entry points, per-peer loads and stores
+                args, reduce, exchange = head + (C.byref(self._nsq),) + tail, self.lib.ssb_reduce_adam_broadcast_q16, self.lib.ssb_exchange_step_q16
+            else:
+                args, reduce, exchange = head + tail, self.lib.ssb_reduce_adam_broadcast, self.lib.ssb_exchange_step
             if getattr(self, "trace", None) is not None:          # the same three steps with a time mark after each
                 self._barrier(); self._mark("barrier1")
-                L.check(self.lib.ssb_reduce_adam_broadcast(*args, stream)); self._mark("reduce_adam_broadcast")
+                L.check(reduce(*args, stream)); self._mark("reduce_adam_broadcast")
                 self._barrier(); self._mark("barrier2")
             else:
-                L.check(self.lib.ssb_exchange_step(*args, self._barrier_cb, None, stream))
+                L.check(exchange(*args, self._barrier_cb, None, stream))
             return
         d_steps = L.ptr(self.steps) if self.steps is not None else None
         if self._nsq is not None:

@@ -72,7 +72,8 @@ def main():
         densify_check(rank, world, dev)
         dist.destroy_process_group()
         return
-    quant = len(sys.argv) > 1 and sys.argv[1] == "quant"
+    stock = len(sys.argv) > 1 and sys.argv[1] == "stock"     # the reference's stock optimiser state on top of quantised SH
+    quant = stock or (len(sys.argv) > 1 and sys.argv[1] == "quant")
     cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=5000 + 37, width=160, height=112, n_views=2 * world)
     cfg.rig, cfg.rig_radius, cfg.log_scale_mu = "ring", 3.0, -3.0
     if quant:
@@ -85,7 +86,11 @@ def main():
     d_gt = torch.from_numpy(np.stack([scenes.make_target(cfg, v) for v in views])).to(dev)
     out, ran = {}, {}
     for mode in ("nccl", "peer", "multimem"):
-        tr = Trainer(cfg, sp, device=dev, world_size=world, rank=rank, grad_sync=mode)
+        extra = {}
+        if stock:
+            from spirula_studio_b200.trainer import OptimOptions
+            extra = dict(non_sh_optim_bits=16, optim=OptimOptions())
+        tr = Trainer(cfg, sp, device=dev, world_size=world, rank=rank, grad_sync=mode, **extra)
         for _ in range(3):
             tr.step_device(d_vm, d_K, d_gt, 2, cfg.n_views)
         torch.cuda.synchronize()
@@ -106,9 +111,18 @@ def main():
             d = np.abs(a16 - b16)
             # 16-bit codes after three steps: a few quanta (of 65535 per block range) where the summation orders -- of the
             # ranks, and of the float atomics inside each rank's backward passes, which differ run to run -- rounded differently
-            assert d.max() <= 32 and (d > 0).mean() < 2e-2, (k, d.max(), (d > 0).mean())
+            if stock:
+                # the means of the two runs drift apart faster here (see below), and with them the view directions the SH
+                # gradients are taken at: early Adam steps are +-lr, so a flipped sign moves a value by ~1 % of its block's range
+                assert d.max() <= 2000 and (d > 64).mean() < 5e-2, (k, d.max(), (d > 64).mean())
+            else:
+                assert d.max() <= 32 and (d > 0).mean() < 2e-2, (k, d.max(), (d > 0).mean())
             continue
         tol = 1e-6 + 1e-4 * b.abs()
+        if stock and k in sp:
+            # the scale-agnostic mean update takes steps far above the learning rate for distant splats, and 16-bit moment
+            # codes round a reordered gradient sum differently: allow a tenth of the distance a parameter has moved
+            tol = tol + 0.1 * (b - torch.from_numpy(sp[k].reshape(-1)).to(b.device).double()).abs()
         bad = ((a - b).abs() > tol).double().mean().item()
         worst = max(worst, (a - b).abs().max().item())
         # summation order differs between the two paths; a first Adam steps amplify sign flips of tiny gradients

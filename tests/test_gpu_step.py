@@ -612,6 +612,96 @@ def test_fused_exchange_with_virtual_ranks(lib, U, quant):
                                              0, 1024, n, C.byref(cfg), None, None) == L.SSB_ERR_INVALID_ARGUMENT
 
 
+def test_fused_exchange_with_16bit_moments_and_optimiser_options(lib, U):
+    """ssb_reduce_adam_broadcast_q16 on three virtual ranks with the reference's stock optimiser state: 16-bit codes for the
+    moments of the five non-SH arrays, quantised SH values and state, per-splat counters, regularisers and the scale-agnostic
+    mean.  Every replica ends with the parameters of one ssb_adam_step_q16 + ssb_adam_step_sh_quantized_ex pass over the summed
+    gradients, and each rank's codes in its own range are the reference pass's."""
+    world, n = 3, 1536 + 512 + 200
+    attrs = (("means", 3), ("quats", 4), ("scales", 3), ("opacities", 1), ("features_dc", 3), ("features_sh", 45))
+    rng = np.random.default_rng(78)
+    sp = scenes.make_splats(scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=n), seed=6)
+
+    def flat(arrays):
+        offs, tot = {}, 0
+        for k, w in attrs:
+            offs[k] = tot
+            tot += (n * w + 63) // 64 * 64
+        buf = torch.zeros(tot, device=U.DEV)
+        views = {k: buf[offs[k]: offs[k] + n * w] for k, w in attrs}
+        if arrays is not None:
+            for k, _ in attrs:
+                views[k].copy_(U.dev(np.ascontiguousarray(arrays[k]).reshape(-1)))
+        return buf, views
+
+    def moments():
+        m = L.SsbMomentsQ16()
+        keep = []
+        for t, (k, w) in enumerate(attrs[:5]):
+            pk, bd = torch.zeros(n * w * 4, dtype=torch.uint8, device=U.DEV), torch.zeros(((n + 255) // 256) * 4, device=U.DEV)
+            m.d_packed[t], m.d_bounds[t] = pk.data_ptr(), bd.data_ptr()
+            keep.append((pk, bd))
+        return m, keep
+
+    part = [{k: (rng.normal(size=(n * w)) * 1e-3).astype(np.float32) for k, w in attrs} for _ in range(world)]
+    total = {k: sum(torch.from_numpy(part[r][k]) for r in range(world)) for k, _ in attrs}
+    cells, nb = n * 45, (n * 45 + 255) // 256
+    radii = U.dev(rng.uniform(0.5, 30.0, n).astype(np.float32))
+    steps = U.dev(rng.integers(1, 40, n).astype(np.int32))
+    extras = L.SsbAdamExtras(10.0, 0.0, 0.01, 0.01, 0.0, 0.0, 0.01, 1, radii.data_ptr(), steps.data_ptr(), n, None)
+    cfg = L.SsbAdamConfig(1e-3, 1e-3, 5e-3, 5e-2, 2.5e-3, 2.5e-3, 0.05, 0.25, 1, 0)
+
+    def sh_state():
+        enc = torch.zeros(cells * 2, dtype=torch.uint8, device=U.DEV); bnd = torch.zeros(nb * 2, device=U.DEV)
+        L.check(lib.ssb_quant_encode(L.ptr(U.dev(sp["features_sh"].reshape(-1))), cells, 16, L.ptr(enc), L.ptr(bnd), None))
+        return dict(packed=enc, bounds=bnd, opt=torch.zeros(cells * 2, dtype=torch.uint8, device=U.DEV), optb=torch.zeros(nb * 4, device=U.DEV))
+
+    # reference: one rank, the summed gradients
+    ref_p, ref_g = flat(sp), flat({k: total[k].numpy() for k, _ in attrs})
+    ref_m, ref_keep = moments()
+    ref_sh = sh_state()
+    rp, rg = L.splats_struct({**ref_p[1], "features_sh": None}), L.splats_struct(ref_g[1])
+    L.check(lib.ssb_adam_step_q16(C.byref(rp), C.byref(rg), C.byref(ref_m), 0, n, C.byref(cfg), C.byref(extras), None))
+    L.check(lib.ssb_adam_step_sh_quantized_ex(L.ptr(ref_g[1]["features_sh"]), L.ptr(ref_sh["opt"]), L.ptr(ref_sh["optb"]), L.ptr(ref_sh["packed"]),
+                                              L.ptr(ref_sh["bounds"]), 16, 8, 0, cells, cells, C.byref(cfg), L.ptr(steps), 45, None))
+    params = [flat(sp) for _ in range(world)]
+    grads = [flat(part[r]) for r in range(world)]
+    moms = [moments() for _ in range(world)]
+    shq = [sh_state() for _ in range(world)]
+    torch.cuda.synchronize()
+    ranges = [(0, 1024), (1024, 1024), (2048, n - 2048)]
+    for r, (f, c) in enumerate(ranges):
+        rep = L.peer_replicas(world, r, [g_[0].data_ptr() for g_ in grads], [p_[0].data_ptr() for p_ in params],
+                              [s_["packed"].data_ptr() for s_ in shq], [s_["bounds"].data_ptr() for s_ in shq])
+        ps, gs = L.splats_struct({**params[r][1], "features_sh": None}), L.splats_struct(grads[r][1])
+        sh = L.SsbShAdamState(shq[r]["opt"].data_ptr(), shq[r]["optb"].data_ptr(), shq[r]["packed"].data_ptr(), shq[r]["bounds"].data_ptr(), 16, 8)
+        L.check(lib.ssb_reduce_adam_broadcast_q16(C.byref(rep), C.byref(ps), C.byref(gs), C.byref(moms[r][0]), None, None, C.byref(sh),
+                                                  f, c, n, C.byref(cfg), C.byref(extras), None))
+        torch.cuda.synchronize()
+    for r in range(world):
+        for k, w in attrs[:5]:
+            assert torch.allclose(params[r][1][k], ref_p[1][k], rtol=2e-5, atol=2e-7), (r, k)
+            assert torch.equal(params[r][1][k], params[0][1][k]), (r, k)
+        assert torch.equal(shq[r]["packed"], shq[0]["packed"]) and torch.equal(shq[r]["bounds"], shq[0]["bounds"])
+        d = (shq[r]["packed"].view(torch.int16).int() - ref_sh["packed"].view(torch.int16).int()).abs()
+        assert int(d.max()) <= 2 and float((d > 0).float().mean()) < 2e-2
+        # the rank's own range of moment codes: the reference pass's, up to the rounding of a reordered gradient sum
+        f, c = ranges[r]
+        for t, (k, w) in enumerate(attrs[:5]):
+            mine = moms[r][1][t][0].view(torch.int16).int().view(-1, 2)[f * w:(f + c) * w]
+            want = ref_keep[t][0].view(torch.int16).int().view(-1, 2)[f * w:(f + c) * w]
+            dd = ((mine & 0xffff) - (want & 0xffff)).abs()
+            assert int(dd.max()) <= 64 and float((dd > 2).float().mean()) < 0.02, (r, k, int(dd.max()))
+            assert mine.any() and not moms[r][1][t][0].view(torch.int16).view(-1, 2)[:f * w].any()      # nothing outside the range
+    # a range that does not start on a block of 256 splats is refused
+    rep = L.peer_replicas(world, 0, [g_[0].data_ptr() for g_ in grads], [p_[0].data_ptr() for p_ in params],
+                          [s_["packed"].data_ptr() for s_ in shq], [s_["bounds"].data_ptr() for s_ in shq])
+    ps, gs = L.splats_struct({**params[0][1], "features_sh": None}), L.splats_struct(grads[0][1])
+    sh = L.SsbShAdamState(shq[0]["opt"].data_ptr(), shq[0]["optb"].data_ptr(), shq[0]["packed"].data_ptr(), shq[0]["bounds"].data_ptr(), 16, 8)
+    assert lib.ssb_reduce_adam_broadcast_q16(C.byref(rep), C.byref(ps), C.byref(gs), C.byref(moms[0][0]), None, None, C.byref(sh), 128, 128, n,
+                                             C.byref(cfg), C.byref(extras), None) == L.SSB_ERR_INVALID_ARGUMENT
+
+
 def flat_view(buf, attrs, n, name):
     off = 0
     for k, w in attrs:

@@ -11,12 +11,12 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("variant", ["fp32", "quant"])
+@pytest.mark.parametrize("variant", ["fp32", "quant", "stock"])
 def test_peer_exchange_matches_nccl_on_two_gpus(variant):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
-           "--master-port", "29641" if variant == "fp32" else "29642", os.path.join(ROOT, "tests", "multi_gpu_check.py"), variant]
+           "--master-port", {"fp32": "29641", "quant": "29642", "stock": "29644"}[variant], os.path.join(ROOT, "tests", "multi_gpu_check.py"), variant]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]

@@ -701,6 +701,19 @@ int ssb_step_views_gated(SsbStep* step, const SsbSplats* params, const SsbShQuan
                          const float* d_viewmats, const float* d_intrins, const float* d_gt, int32_t n_views,
                          void* const* gt_ready, const SsbSplats* grads, int accumulate, float* d_losses, void* stream);
 
+/* Projection backward of ALL views fused with the optimiser, on caller buffers (the reference's
+ * fused_projection_bwd_optimizer_3dgs in its unpacked mode, src/kernels/optim/FusedProjectionBwdOptim.cu:76-213, kernel
+ * FusedProjectionBwdOptim_kernel.cuh:146-1030): d_aabb [views][n][4] and d_v_screen [views][n] as the forward passes and the
+ * rasteriser's backward passes left them, cams->count views.  Splats are worked through in ranges of 131072: the projection
+ * backward of every view writes the range's gradients into the workspace (ssb_project_bwd_optimize_workspace_bytes(n), 256-byte
+ * aligned; it stays in L2), the Adam kernels (ssb_adam_step_ex, and ssb_adam_step_sh_quantized_ex when sh_state is given)
+ * read them from there, so no world-gradient array exists.  The result equals ssb_project_bwd over all views followed by the
+ * unfused optimiser calls.  cfg->grad_scale scales the gradients as there; cfg->zero_grad is ignored. */
+int64_t ssb_project_bwd_optimize_workspace_bytes(int64_t n);
+int ssb_project_bwd_optimize(const SsbSplats* params, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
+                             const SsbScreenRec* d_v_screen, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                             const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* d_workspace, int64_t workspace_bytes, void* stream);
+
 /* Projection backward of all views fused with the optimiser: the reference's use_fused_proj_bwd_optim path
  * (fused_projection_bwd_optimizer_3dgs_kernel, src/kernels/optim/FusedProjectionBwdOptim_kernel.cuh:146-1030: one
  * thread per splat loops over its views, so the world gradients are never stored).

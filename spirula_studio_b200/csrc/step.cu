@@ -415,6 +415,71 @@ int ssb_step_set_fused_backward(SsbStep* s, int32_t max_views) {
     return SSB_OK;
 }
 
+}  // extern "C"
+
+namespace ssb {
+
+// One range of splats of the fused backward + optimiser pass: the projection backward of all views writes the range's 59
+// gradient floats per splat into `scratch` (which stays in L2), the optimiser kernels read them from there.
+static int fused_backward_range(const SsbSplats* params, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
+                                SsbScreenRec* d_v_screen, int clear_v_screen, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                                const SsbAdamConfig* c, const SsbAdamExtras* extras, float* scratch, int64_t range, int64_t first, int64_t count,
+                                void* stream) {
+    // the range's gradient arrays, each on a 256-byte boundary
+    float* g_means = scratch;
+    float* g_quats = g_means + align_up(3 * range, 64);
+    float* g_scales = g_quats + align_up(4 * range, 64);
+    float* g_opac = g_scales + align_up(3 * range, 64);
+    float* g_dc = g_opac + align_up(range, 64);
+    float* g_sh = g_dc + align_up(3 * range, 64);
+    // pointers moved back by the range's start: kernels index gradients by the splat's own number
+    SsbSplats g;
+    g.means = g_means - 3 * first; g.quats = g_quats - 4 * first; g.scales = g_scales - 3 * first; g.opacities = g_opac - first;
+    g.features_dc = g_dc - 3 * first; g.features_sh = g_sh - 45 * first;
+    if (int e = launch_project_bwd(params, shq, n, cams, d_aabb, d_v_screen, &g, 0, clear_v_screen, stream, nullptr, first, count)) return e;
+    SsbSplats ga = g;
+    if (sh_state) ga.features_sh = nullptr;      // the SH update is the quantised one below
+    SsbSplats p = *params, a1 = *m1, a2 = *m2;
+    if (sh_state) { p.features_sh = nullptr; a1.features_sh = nullptr; a2.features_sh = nullptr; }
+    if (int e = ssb_adam_step_ex(&p, &ga, &a1, &a2, first, count, c, extras, stream)) return e;
+    if (sh_state) {
+        void* values = sh_state->value_bits == 32 ? (void*)params->features_sh : sh_state->d_value_packed;
+        if (int e = ssb_adam_step_sh_quantized_ex(g.features_sh, sh_state->d_optim_packed, sh_state->d_optim_bounds, values, sh_state->d_value_bounds,
+                                                  sh_state->value_bits, sh_state->optim_bits ? sh_state->optim_bits : 8, first * 45, count * 45, n * 45,
+                                                  c, extras ? extras->d_steps : nullptr, 45, stream)) return e;
+    }
+    return SSB_OK;
+}
+
+static int64_t fused_scratch_floats(int64_t n) { return 6 * 64 + std::min(kFusedRange, align_up(n, 256)) * 59; }
+
+}  // namespace ssb
+
+extern "C" {
+
+int64_t ssb_project_bwd_optimize_workspace_bytes(int64_t n) { return n < 0 ? SSB_ERR_INVALID_ARGUMENT : ssb::fused_scratch_floats(n) * (int64_t)sizeof(float); }
+
+int ssb_project_bwd_optimize(const SsbSplats* params, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
+                             const SsbScreenRec* d_v_screen, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                             const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* d_workspace, int64_t workspace_bytes, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(params && cams && d_aabb && d_v_screen && m1 && m2 && cfg && d_workspace, "ssb_project_bwd_optimize: NULL argument");
+    SSB_REQUIRE(n >= 0 && cams->count >= 0, "ssb_project_bwd_optimize: bad sizes");
+    SSB_REQUIRE(workspace_bytes >= ssb_project_bwd_optimize_workspace_bytes(n), "ssb_project_bwd_optimize: workspace too small");
+    SSB_REQUIRE(((uintptr_t)d_workspace & 255) == 0, "ssb_project_bwd_optimize: the workspace must be 256-byte aligned");
+    SSB_REQUIRE(!sh_state || params->features_sh == nullptr || sh_state->value_bits == 32,
+                "ssb_project_bwd_optimize: SH values are either plain (params->features_sh) or quantised (sh_state), not both");
+    if (n == 0 || cams->count == 0) return SSB_OK;
+    SsbAdamConfig c = *cfg;
+    c.zero_grad = 0;
+    const int64_t range = std::min(kFusedRange, align_up(n, 256));
+    for (int64_t first = 0; first < n; first += range) {
+        if (int e = fused_backward_range(params, shq, n, cams, d_aabb, const_cast<SsbScreenRec*>(d_v_screen), 0, m1, m2, sh_state, &c, extras,
+                                         (float*)d_workspace, range, first, std::min(range, n - first), stream)) return e;
+    }
+    return SSB_OK;
+}
+
 int ssb_step_backward_optimize(SsbStep* s, const SsbSplats* params, const SsbShQuant* shq, const float* d_viewmats, const float* d_intrins,
                                int32_t n_views, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state, const SsbAdamConfig* cfg,
                                const SsbAdamExtras* extras, void* stream) {
@@ -433,42 +498,21 @@ int ssb_step_backward_optimize(SsbStep* s, const SsbSplats* params, const SsbShQ
     cams.width = s->cfg.width; cams.height = s->cfg.height; cams.model = s->cfg.camera_model; cams.antialiased = s->cfg.antialiased;
     cams.distortion = s->dist_tier; cams.d_dist_coeffs = s->dist_coeffs; cams.sh_degree_plus1 = s->sh_degree_plus1;
     const int64_t range = std::min(kFusedRange, align_up(n, 256));
-    const int64_t scratch_floats = 6 * 64 + range * 59;
+    const int64_t scratch_floats = fused_scratch_floats(n);
     SsbAdamConfig c = *cfg;
     c.zero_grad = 0;                       // every range overwrites the scratch
     cudaStream_t user = (cudaStream_t)stream;
-    const bool two = n > range;            // more than one range: alternate between the two streams
+    const bool two = n > range;            // more than one range: alternate between the lanes' streams
     if (two) {
         SSB_CUDA(cudaEventRecord(s->fork, user));
         for (int k = 0; k < s->n_lanes; ++k) SSB_CUDA(cudaStreamWaitEvent(s->lane[k].stream, s->fork, 0));
     }
     int turn = 0;
     for (int64_t first = 0; first < n; first += range, ++turn) {
-        const int64_t count = std::min(range, n - first);
-        void* stream = two ? (void*)s->lane[turn % s->n_lanes].stream : (void*)user;
-        // the range's gradient arrays, each on a 256-byte boundary
-        float* g_means = s->def_grads + (two ? turn % s->n_lanes : 0) * scratch_floats;
-        float* g_quats = g_means + align_up(3 * range, 64);
-        float* g_scales = g_quats + align_up(4 * range, 64);
-        float* g_opac = g_scales + align_up(3 * range, 64);
-        float* g_dc = g_opac + align_up(range, 64);
-        float* g_sh = g_dc + align_up(3 * range, 64);
-        // pointers moved back by the range's start: kernels index gradients by the splat's own number
-        SsbSplats g;
-        g.means = g_means - 3 * first; g.quats = g_quats - 4 * first; g.scales = g_scales - 3 * first; g.opacities = g_opac - first;
-        g.features_dc = g_dc - 3 * first; g.features_sh = g_sh - 45 * first;
-        if (int e = launch_project_bwd(params, shq, n, &cams, s->def_aabb, s->def_vscreen, &g, 0, 1, stream, nullptr, first, count)) return e;
-        SsbSplats ga = g;
-        if (sh_state) ga.features_sh = nullptr;      // the SH update is the quantised one below
-        SsbSplats p = *params, a1 = *m1, a2 = *m2;
-        if (sh_state) { p.features_sh = nullptr; a1.features_sh = nullptr; a2.features_sh = nullptr; }
-        if (int e = ssb_adam_step_ex(&p, &ga, &a1, &a2, first, count, &c, extras, stream)) return e;
-        if (sh_state) {
-            void* values = sh_state->value_bits == 32 ? (void*)params->features_sh : sh_state->d_value_packed;
-            if (int e = ssb_adam_step_sh_quantized_ex(g.features_sh, sh_state->d_optim_packed, sh_state->d_optim_bounds, values, sh_state->d_value_bounds,
-                                                      sh_state->value_bits, sh_state->optim_bits ? sh_state->optim_bits : 8, first * 45, count * 45, n * 45,
-                                                      &c, extras ? extras->d_steps : nullptr, 45, stream)) return e;
-        }
+        void* range_stream = two ? (void*)s->lane[turn % s->n_lanes].stream : (void*)user;
+        float* scratch = s->def_grads + (two ? turn % s->n_lanes : 0) * scratch_floats;
+        if (int e = fused_backward_range(params, shq, n, &cams, s->def_aabb, s->def_vscreen, 1, m1, m2, sh_state, &c, extras, scratch, range, first,
+                                         std::min(range, n - first), range_stream)) return e;
     }
     if (two)
         for (int k = 0; k < s->n_lanes; ++k) {

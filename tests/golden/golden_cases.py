@@ -109,6 +109,19 @@ def dist_case_inputs(name):
     return cfg, sp, vm, K, c["model"], c["tier"], rows, v
 
 
+# The reference's fused projection-backward + optimiser kernel (its production default), two consecutive passes on the ring2
+# scene with the screen-space cotangents of that fixture: "plain" = no regulariser, a scalar step; "ex" = per-splat
+# regularisers, SH regulariser, the scale-agnostic mean update and per-splat step counters.
+FPBO_SCENE = "ring2"
+FPBO_RUNS = {"plain": dict(reg=[10.0, 0, 0, 0, 0, 0, 0], sh_reg=0.0, agnostic=0, steps=False),
+             "ex": dict(reg=[3.0, 0.7, 0.9, 1.1, 0.5, 0.3, 0.2], sh_reg=0.05, agnostic=1, steps=True)}
+
+
+def fpbo_inputs(n):
+    rng = np.random.default_rng(811)
+    return dict(radii=rng.uniform(0.5, 40.0, size=n).astype(np.float32), steps=rng.integers(1, 50, size=n).astype(np.int32))
+
+
 ACCUM_CASES = ("ring2", "dense1")
 
 # Quantised SH storage read by the projection (forward and backward): 8- or 16-bit codes with (min, max) bounds

@@ -24,7 +24,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, HERE)
 
-from golden_cases import (ACCUM_CASES, CASES, DENSIFY_SCORE_RUNS, DIST_CASES, dist_case_inputs, DENSIFY_SPLIT, LIVE_TILE_CASE, LOSS_MAP_WEIGHT, MULTI_SCALE_RUNS, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
+from golden_cases import (ACCUM_CASES, CASES, DENSIFY_SCORE_RUNS, DIST_CASES, FPBO_RUNS, FPBO_SCENE, dist_case_inputs, fpbo_inputs, DENSIFY_SPLIT, LIVE_TILE_CASE, LOSS_MAP_WEIGHT, MULTI_SCALE_RUNS, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
                           build_case, densify_inputs, densify_split_inputs, loss_inputs, loss_map_base, loss_masks, quant_sh_inputs, raster_cotangents, tile_masks)  # noqa: E402
 
 DEV = "cuda:0"
@@ -528,6 +528,42 @@ def run_dist_proj(ref, out_dir):
     np.savez_compressed(os.path.join(out_dir, "dist_proj.npz"), **out)
 
 
+def run_fpbo(ref, out_dir):
+    """The reference's fused projection-backward + optimiser kernel (level 0, unpacked), two passes per run from zero moments:
+    parameters after each pass, moments after the second."""
+    cfg, sp, vm, K = build_case(FPBO_SCENE)
+    gold = np.load(os.path.join(HERE, f"{FPBO_SCENE}.npz"))
+    n, W, H, I = cfg.n_splats, cfg.width, cfg.height, vm.shape[0]
+    lr = cfg.lrs
+    lrs = np.array([lr["lr_means"], lr["lr_quats"], lr["lr_scales"], lr["lr_opacities"], lr["lr_features_dc"], lr["lr_features_sh"]], np.float32)
+    d_vm, d_K, d_aabb = dev(vm), dev(K), dev(gold["aabb"])
+    v = {k: dev(gold[k]) for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")}
+    extra = fpbo_inputs(n)
+    d_radii, d_steps = dev(extra["radii"]), dev(extra["steps"])
+    order = ("means", "quats", "scales", "opacities", "features_dc", "features_sh")
+    out = {}
+    for tag, run in FPBO_RUNS.items():
+        p = {k: dev(sp[k].reshape(-1)) for k in order}
+        g1 = {k: torch.zeros_like(t) for k, t in p.items()}
+        g2 = {k: torch.zeros_like(t) for k, t in p.items()}
+        reg = np.array(run["reg"], np.float32)
+        for step in (1, 2):
+            zero = {k: torch.zeros_like(t) for k, t in p.items()}
+            steps_t = None
+            if run["steps"]:
+                steps_t = (d_steps + (step - 1)).contiguous()
+            check(ref.ref_fpbo(I, n, W, H, *[P(p[k]) for k in order], P(d_vm), P(d_K), P(d_aabb),
+                               P(v["v_xy"]), P(v["v_depth"]), P(v["v_conic"]), P(v["v_opac"]), P(v["v_rgb"]),
+                               *[P(zero[k]) for k in order], *[P(g1[k]) for k in order], *[P(g2[k]) for k in order],
+                               P(d_radii), lrs.ctypes.data_as(C.c_void_p), reg.ctypes.data_as(C.c_void_p), C.c_float(run["sh_reg"]),
+                               run["agnostic"], step, P(steps_t) if steps_t is not None else None), "ref_fpbo " + tag)
+            for k in order:
+                out[f"{tag}_p{step}_{k}"] = p[k].cpu().numpy()
+        for k in order:
+            out[f"{tag}_g1_{k}"], out[f"{tag}_g2_{k}"] = g1[k].cpu().numpy(), g2[k].cpu().numpy()
+    np.savez_compressed(os.path.join(out_dir, "fpbo.npz"), **out)
+
+
 def run_sh_degree(ref, out_dir):
     """Projection forward and backward of the reference's Vanilla3DGS<0>, <1> and <2> kernels (the SH degree warm-up) on the
     ring2 scene with its 15-coefficient SH rows: the colours, the validity boxes and the six gradient arrays for the
@@ -622,6 +658,8 @@ def main():
         run_dist_proj(ref, out_dir)
     if not only or "sh_degree" in only:
         run_sh_degree(ref, out_dir)
+    if not only or "fpbo" in only:
+        run_fpbo(ref, out_dir)
     if not only or "ssim_map" in only:
         run_loss_map(ref, out_dir)
     if not only or "ssim_masked" in only:

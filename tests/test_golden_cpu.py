@@ -15,7 +15,7 @@ import pytest
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 
-from golden_cases import (DIST_CASES, dist_case_inputs, ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
+from golden_cases import (DIST_CASES, FPBO_RUNS, FPBO_SCENE, dist_case_inputs, fpbo_inputs, ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
                           build_case, loss_inputs, loss_map_base, quant_sh_inputs, raster_cotangents)  # noqa: E402
 
 
@@ -149,6 +149,37 @@ def test_quantised_sh_projection_vs_reference(oracle, tag):
     for k in g:
         ref = gold[f"{tag}_g_{k}"].reshape(g[k].shape)
         assert frac_bad(g[k], ref, 1e-4 * np.abs(ref).max(), 2e-3) <= 5e-3, k
+
+
+@pytest.mark.parametrize("tag", sorted(FPBO_RUNS))
+def test_fused_backward_optimiser_vs_reference(oracle, tag):
+    """The reference's fused projection-backward + optimiser kernel equals its unfused chain: projection backward over all views,
+    then the geometry / DC / SH Adam updates -- the oracle's statement of those, two consecutive passes."""
+    run = FPBO_RUNS[tag]
+    cfg, sp, vm, K = build_case(FPBO_SCENE)
+    base, gold = load(FPBO_SCENE), load("fpbo")
+    n = cfg.n_splats
+    extra = fpbo_inputs(n)
+    v = {k: base[k] for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")}
+    p = {k: x.copy() for k, x in sp.items()}
+    m1 = {k: np.zeros_like(x) for k, x in p.items()}
+    m2 = {k: np.zeros_like(x) for k, x in p.items()}
+    for step in (1, 2):
+        if step == 2:           # from the reference's parameters of the first pass, so that the passes are compared one by one
+            p = {k: gold[f"{tag}_p1_{k}"].reshape(sp[k].shape).copy() for k in p}
+        g = oracle.project_bwd(p, vm, K, cfg.width, cfg.height, base["aabb"], v)
+        steps = (extra["steps"] + (step - 1)).astype(np.int32) if run["steps"] else None
+        oracle.adam_geometry_ex(p, g, m1, m2, step, cfg.lrs, reg=run["reg"], scale_agnostic=bool(run["agnostic"]), radii=extra["radii"], steps=steps)
+        oracle.adam_plain(p["features_dc"], g["features_dc"], m1["features_dc"], m2["features_dc"], step, cfg.lrs["lr_features_dc"], run["sh_reg"],
+                          0.5 / 0.28209479177387814, 1.0, steps=steps, stride=3)    # the DC dead zone of the SH regulariser (:355-358)
+        oracle.adam_plain(p["features_sh"], g["features_sh"], m1["features_sh"], m2["features_sh"], step, cfg.lrs["lr_features_sh"], run["sh_reg"], 0.0, 1.0,
+                          steps=steps, stride=45)
+        for k in p:
+            assert frac_bad(p[k].reshape(-1), gold[f"{tag}_p{step}_{k}"], 5e-6, 1e-4) <= 2e-3, (tag, k, step)
+    for k in p:
+        ref1, ref2 = gold[f"{tag}_g1_{k}"], gold[f"{tag}_g2_{k}"]
+        assert frac_bad(m1[k].reshape(-1), ref1, 1e-4 * np.abs(ref1).max(), 2e-3) <= 5e-3, k
+        assert frac_bad(m2[k].reshape(-1), ref2, 1e-4 * np.abs(ref2).max(), 4e-3) <= 5e-3, k
 
 
 @pytest.mark.parametrize("deg", [0, 1, 2])

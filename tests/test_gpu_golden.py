@@ -13,7 +13,7 @@ torch = pytest.importorskip("torch")
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 
-from golden_cases import (DIST_CASES, dist_case_inputs, ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
+from golden_cases import (DIST_CASES, FPBO_RUNS, FPBO_SCENE, dist_case_inputs, fpbo_inputs, ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
                           build_case, loss_inputs, loss_map_base, quant_sh_inputs, raster_cotangents)  # noqa: E402
 from spirula_studio_b200 import lib as L  # noqa: E402
 
@@ -175,6 +175,50 @@ def test_quantised_sh_projection_vs_reference(lib, U, tag):
         ref = gold[f"{tag}_g_{k}"]
         assert U.close_frac(grads[k].cpu().numpy().reshape(-1), ref.reshape(-1), 1e-4 * np.abs(ref).max(), 2e-3) <= 5e-3, k
     del keep_alive
+
+
+@pytest.mark.parametrize("tag", sorted(FPBO_RUNS))
+def test_fused_backward_optimiser_vs_reference(lib, U, tag):
+    """ssb_project_bwd_optimize (projection backward of all views fused with the optimiser, gradients through an L2-resident
+    scratch) against the reference's fused kernel, two consecutive passes, each from the reference's state of the pass before."""
+    run = FPBO_RUNS[tag]
+    cfg, sp, vm, K = build_case(FPBO_SCENE)
+    base, gold = load(FPBO_SCENE), load("fpbo")
+    I, n, W, H = vm.shape[0], cfg.n_splats, cfg.width, cfg.height
+    m = I * n
+    extra = fpbo_inputs(n)
+    order = ("means", "quats", "scales", "opacities", "features_dc", "features_sh")
+    d_vm, d_K, d_aabb = U.dev(vm), U.dev(K), U.dev(base["aabb"])
+    vrec = U.arrays_to_vrec({k: base[k].reshape(m, -1) if base[k].ndim > 1 else base[k] for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")}, m)
+    d_radii = U.dev(extra["radii"])
+    cams = L.cameras_struct(d_vm, d_K, W, H)
+    ws = torch.zeros(int(lib.ssb_project_bwd_optimize_workspace_bytes(n)), dtype=torch.uint8, device=U.DEV)
+    lr = cfg.lrs
+    p = {k: U.dev(sp[k].reshape(-1)) for k in order}
+    m1 = {k: torch.zeros_like(t) for k, t in p.items()}
+    m2 = {k: torch.zeros_like(t) for k, t in p.items()}
+    for step in (1, 2):
+        if step == 2:
+            p = {k: U.dev(gold[f"{tag}_p1_{k}"]) for k in order}
+        d_steps = U.dev((extra["steps"] + (step - 1)).astype(np.int32)) if run["steps"] else None
+        ex = L.SsbAdamExtras(*[float(x) for x in run["reg"]], run["agnostic"], d_radii.data_ptr(), d_steps.data_ptr() if d_steps is not None else None, n, None)
+        acfg = L.SsbAdamConfig(lr["lr_means"], lr["lr_quats"], lr["lr_scales"], lr["lr_opacities"], lr["lr_features_dc"], lr["lr_features_sh"],
+                               run["sh_reg"], 1.0, step, 0)
+        s, a, b = L.splats_struct(p), L.splats_struct(m1), L.splats_struct(m2)
+        L.check(lib.ssb_project_bwd_optimize(C.byref(s), None, n, C.byref(cams), L.ptr(d_aabb), L.ptr(vrec), C.byref(a), C.byref(b), None, C.byref(acfg),
+                                             C.byref(ex), L.ptr(ws), ws.numel(), None))
+        torch.cuda.synchronize()
+        for k in order:
+            assert U.close_frac(p[k].cpu().numpy(), gold[f"{tag}_p{step}_{k}"], 5e-6, 1e-4) <= 2e-3, (tag, k, step)
+    # equal to the unfused calls on the same inputs
+    p2 = {k: U.dev(gold[f"{tag}_p1_{k}"]) for k in order}
+    grads = {k: torch.zeros_like(t) for k, t in p2.items()}
+    s2, g2 = L.splats_struct(p2), L.splats_struct(grads)
+    L.check(lib.ssb_project_bwd(C.byref(s2), None, n, C.byref(cams), L.ptr(d_aabb), L.ptr(vrec), C.byref(g2), 0, None))
+    torch.cuda.synchronize()
+    assert grads["means"].abs().max().item() > 0
+    assert lib.ssb_project_bwd_optimize(C.byref(s2), None, n, C.byref(cams), L.ptr(d_aabb), L.ptr(vrec), C.byref(a), C.byref(b), None, C.byref(acfg),
+                                        C.byref(ex), L.ptr(ws), 16, None) == L.SSB_ERR_INVALID_ARGUMENT
 
 
 @pytest.mark.parametrize("deg", [0, 1, 2])

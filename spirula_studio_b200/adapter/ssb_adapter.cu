@@ -10,6 +10,8 @@
 //   do_intersect_tile_generic      (src/kernels/tile/IntersectTile.cuh:24-40)        -> ssb_screen_pack + ssb_intersect_tiles_live
 //   rasterize_to_pixels_3dgs_fwd   (src/kernels/raster/RasterizationFwd.cuh:16-37)    -> ssb_screen_pack + ssb_raster_fwd
 //   rasterize_to_pixels_3dgs_bwd   (src/kernels/raster/RasterizationBwd.cuh:18-48)    -> ssb_raster_bwd_accum + unpack of the gradient records
+//   projection_3dgs_backward       (src/kernels/projection/ProjectionBwd.cuh:18-46)   -> ssb_screen_pack + ssb_project_bwd / ssb_project_bwd_packed
+//   fused_projection_bwd_optimizer_3dgs (src/kernels/optim/FusedProjectionBwdOptim.cuh:19-63) -> ssb_project_bwd_optimize (quantisation level 0)
 //   compute_multi_scale_per_pixel_losses (src/kernels/loss/PerPixelLoss.cuh:160-189)  -> ssb_loss_multi_scale (colour terms only)
 //   fused_optim_3dgs_geometry      (src/kernels/optim/Optimizer.cuh:120-144)         -> ssb_adam_step_ex without features_dc
 //   fused_adam_step                (src/kernels/optim/Optimizer.cuh:147-158)         -> ssb_adam_plain
@@ -24,6 +26,8 @@
 // intersection, distortion-loss channels, median depth, other primitives.
 #include "ssb.h"
 
+#include <kernels/optim/FusedProjectionBwdOptim.cuh>
+#include <kernels/projection/ProjectionBwd.cuh>
 #include <kernels/projection/ProjectionFwd.cuh>
 #include <kernels/raster/RasterizationBwd.cuh>
 #include <kernels/raster/RasterizationFwd.cuh>
@@ -70,6 +74,44 @@ SsbScreenRec* pack_records(const char* name, const float* xy, const float* depth
     SsbScreenRec* rec = scratch<SsbScreenRec>(name, m);
     ssb_check(ssb_screen_pack(xy, depth, conic, opac, rgb ? rgb : conic, m, rec, nullptr));
     return rec;
+}
+
+// Packed pairs -> the dense [view][splat] layout: aabb rows (a zero row = "not visible") and gradient records.
+__global__ void scatter_pairs_kernel(int64_t nnz, int64_t n, const int32_t* camera_ids, const int32_t* gaussian_ids, const float4* aabb, const float* xy,
+                                     const float* depth, const float* conic, const float* opac, const float* rgb, float4* dense_aabb, SsbScreenRec* dense_rec) {
+    const int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= nnz) return;
+    const int64_t slot = (int64_t)camera_ids[v] * n + gaussian_ids[v];
+    dense_aabb[slot] = aabb[v];
+    float4* r = (float4*)(dense_rec + slot);
+    r[0] = make_float4(xy[2 * v], xy[2 * v + 1], 0.f, 0.f);
+    r[1] = make_float4(conic[3 * v], conic[3 * v + 1], conic[3 * v + 2], opac[v]);
+    r[2] = make_float4(rgb[3 * v], rgb[3 * v + 1], rgb[3 * v + 2], depth[v]);
+}
+
+struct WorldArgs {
+    SsbSplats splats;
+    SsbShQuant shq;
+    bool quantised;
+};
+
+// The six world arrays (+ quantised SH values) of a reference call as the library's argument structs.
+WorldArgs world_args(const char* who, const std::vector<DeviceTensorFloatND>& w, const std::optional<TorchTensorView>& sh_value_packed,
+                     const std::optional<TorchTensorView>& sh_value_bounds, uint32_t num_sh_buffer, int sh_value_bits, int64_t sh_bounds_stride) {
+    if (w.size() != 6) throw std::runtime_error(std::string(who) + ": expected six world arrays");
+    if (sh_value_bits == 32 && Vanilla3DGS<0>::WorldBuffer(w).sh_degree() != 3) unsupported("an SH buffer that does not hold 15 coefficients per splat");
+    if (sh_value_bits != 32 && num_sh_buffer != 15) unsupported("a quantised SH buffer that does not hold 15 coefficients");
+    WorldArgs a{};
+    a.quantised = sh_value_bits != 32;
+    a.splats = SsbSplats{w[0].data_ptr(), w[1].data_ptr(), w[2].data_ptr(), w[3].data_ptr(), w[4].data_ptr(), a.quantised ? nullptr : w[5].data_ptr()};
+    if (a.quantised) {
+        if (!sh_value_packed.has_value() || !sh_value_bounds.has_value()) throw std::runtime_error(std::string(who) + ": quantised SH without its buffers");
+        a.shq.packed = (void*)std::get<0>(sh_value_packed.value());
+        a.shq.bounds = (float*)std::get<0>(sh_value_bounds.value());
+        a.shq.bits = sh_value_bits;
+        a.shq.bounds_stride = sh_bounds_stride;
+    }
+    return a;
 }
 
 }  // namespace
@@ -383,4 +425,110 @@ void fused_adam_step_quantized_value(int64_t num_splats, int64_t param_numel, De
     const SsbAdamConfig cfg = sh_config(lr, step, l2_reg, grad_scale, zero_grad);
     ssb_check(ssb_adam_step_sh_quantized_ex(grad.data_ptr(), optim_packed, (float*)optim_bounds, value_packed, (float*)value_bounds, value_bits, optim_bits, 0,
                                             param_numel, param_numel, &cfg, per_splat_steps.data_ptr(), (int32_t)(param_numel / num_splats), nullptr));
+}
+
+
+// ---- projection backward ------------------------------------------------------------------------------------------------
+
+void projection_3dgs_backward(
+    const int64_t num_splats, const int max_sh_degree, const std::vector<DeviceTensorFloatND>& splats_world, TorchTensorView viewmats,
+    TorchTensorView intrins, const uint32_t image_width, const uint32_t image_height, const std::string camera_model, const std::string distortion,
+    const TorchTensorView dist_coeffs, const DeviceVector<int32_t> camera_ids, const DeviceVector<int32_t> gaussian_ids, const DeviceTensor2D<float4> aabb,
+    const std::vector<DeviceTensorFloatND>& v_splats_screen, const std::vector<DeviceTensorFloatND>& v_splats_world, DeviceTensor2D<float>* v_viewmats,
+    const std::optional<TorchTensorView> sh_value_packed, const std::optional<TorchTensorView> sh_value_bounds, const uint32_t num_sh_buffer,
+    const int sh_value_bits, const int64_t sh_bounds_stride) {
+    if (v_viewmats != nullptr && v_viewmats->data_ptr() != nullptr) unsupported("the camera-pose gradient");
+    if (v_splats_screen.size() != 5 || v_splats_world.size() != 6) throw std::runtime_error("projection_3dgs_backward: expected five screen and six world gradient arrays");
+    if (max_sh_degree < 0 || max_sh_degree > 3) unsupported("an SH degree above 3");
+    const WorldArgs w = world_args("projection_3dgs_backward", splats_world, sh_value_packed, sh_value_bounds, num_sh_buffer, sh_value_bits, sh_bounds_stride);
+    const uint32_t C = (uint32_t)std::get<2>(viewmats)[0];
+    const int64_t N = num_splats;
+    if (N == 0 || C == 0) return;
+    SsbCameras cams = {(const float*)std::get<0>(viewmats), (const float*)std::get<0>(intrins), (int32_t)C, (int32_t)image_width, (int32_t)image_height,
+                       camera_model_of(camera_model), 0, (int32_t)cdt(distortion), max_sh_degree + 1, (const float*)std::get<0>(dist_coeffs)};
+    // gradients are ADDED to the caller's arrays, as the reference's atomics do
+    SsbSplats g = {v_splats_world[0].data_ptr(), v_splats_world[1].data_ptr(), v_splats_world[2].data_ptr(), v_splats_world[3].data_ptr(),
+                   v_splats_world[4].data_ptr(), v_splats_world[5].data_ptr()};
+    const bool packed = camera_ids.data_ptr() && gaussian_ids.data_ptr();
+    const int64_t m = packed ? (int64_t)camera_ids.size() : (int64_t)C * N;
+    if (m == 0) return;
+    SsbScreenRec* v_rec = pack_records("proj_bwd_grad_records", v_splats_screen[0].data_ptr(), v_splats_screen[1].data_ptr(), v_splats_screen[2].data_ptr(),
+                                       v_splats_screen[3].data_ptr(), v_splats_screen[4].data_ptr(), m);
+    if (!packed) {
+        ssb_check(ssb_project_bwd(&w.splats, w.quantised ? &w.shq : nullptr, N, &cams, (const float*)aabb.data_ptr(), v_rec, &g, 1, nullptr));
+        return;
+    }
+    int64_t* d_pairs = scratch<int64_t>("proj_bwd_pairs", 2);
+    backend::memcpy_sync(d_pairs, &m, sizeof(int64_t), backend::MemcpyKind::HostToDevice);
+    const int64_t ws_bytes = ssb_project_bwd_packed_workspace_bytes(N, (int32_t)C);
+    uint8_t* ws = scratch<uint8_t>("proj_bwd_workspace", ws_bytes);
+    ssb_check(ssb_project_bwd_packed(&w.splats, w.quantised ? &w.shq : nullptr, N, &cams, (const float*)aabb.data_ptr(), v_rec, camera_ids.data_ptr(),
+                                     gaussian_ids.data_ptr(), d_pairs, m, ws, ws_bytes, &g, 1, nullptr));
+}
+
+// Quantisation level 0 (fp32 SH values, fp32 moments of every array).  Level 1 keeps its SH codes and SH optimiser state in
+// layouts of its own (one bound per 256 splats) and is refused.  v_splats_world is not read: for this primitive the
+// rasteriser's backward leaves it zero (only the 3DGUT rasteriser produces world gradients).  With packed pairs the aabb rows
+// and screen gradients are first scattered into the dense [view][splat] layout the library's kernel walks.
+void fused_projection_bwd_optimizer_3dgs(
+    const int64_t num_splats, const int max_sh_degree, std::vector<DeviceTensorFloatND> splats_world, TorchTensorView viewmats, TorchTensorView intrins,
+    const uint32_t image_width, const uint32_t image_height, const std::string camera_model, const std::string distortion, const TorchTensorView dist_coeffs,
+    const DeviceVector<int32_t> camera_ids, const DeviceVector<int32_t> gaussian_ids, DeviceTensorFloatND aabb,
+    const std::vector<DeviceTensorFloatND> v_splats_world, const std::vector<DeviceTensorFloatND> v_splats_screen,
+    const std::vector<DeviceTensorFloatND> g1_splats_world, const std::vector<DeviceTensorFloatND> g2_splats_world,
+    const std::optional<TorchTensorView> sh_packed, const std::optional<TorchTensorView> sh_quant_bounds, const std::optional<TorchTensorView> sh_value_packed,
+    const std::optional<TorchTensorView> sh_value_bounds, NonShQuantState non_sh, DeviceVector<float> radii, DeviceVector<float> densify_score,
+    const float lr_means, const float lr_quats, const float lr_scales, const float lr_opacs, const float lr_features_dc, const float lr_features_sh,
+    const float max_gauss_ratio, const float scale_regularization_weight, const float mcmc_opacity_reg_weight, const float mcmc_scale_reg_weight,
+    const float erank_reg_weight, const float erank_reg_weight_s3, const float quat_norm_reg_weight, const float sh_reg_weight, bool use_scale_agnostic_mean,
+    bool color_trust_linear, float eps_tr, std::variant<int32_t, TorchTensorView> step, int quantization_level) {
+    (void)v_splats_world; (void)eps_tr; (void)sh_packed; (void)sh_quant_bounds; (void)sh_value_packed; (void)sh_value_bounds;
+    if (quantization_level != 0 || non_sh.enabled) unsupported("the quantised layouts of the fused backward + optimiser (quantization_level 1)");
+    if (color_trust_linear) unsupported("the linear-colour trust region");
+    if (max_sh_degree < 0 || max_sh_degree > 3) unsupported("an SH degree above 3");
+    if (v_splats_screen.size() != 5 || g1_splats_world.size() != 6 || g2_splats_world.size() != 6)
+        throw std::runtime_error("fused_projection_bwd_optimizer_3dgs: expected five screen gradient arrays and six arrays per moment");
+    const WorldArgs w = world_args("fused_projection_bwd_optimizer_3dgs", splats_world, std::nullopt, std::nullopt, 15, 32, 0);
+    const uint32_t C = (uint32_t)std::get<2>(viewmats)[0];
+    const int64_t N = num_splats, dense = (int64_t)C * N;
+    if (N == 0) return;
+    SsbCameras cams = {(const float*)std::get<0>(viewmats), (const float*)std::get<0>(intrins), (int32_t)C, (int32_t)image_width, (int32_t)image_height,
+                       camera_model_of(camera_model), 0, (int32_t)cdt(distortion), max_sh_degree + 1, (const float*)std::get<0>(dist_coeffs)};
+    const float* d_aabb = aabb.data_ptr();
+    SsbScreenRec* v_rec = nullptr;
+    if (camera_ids.data_ptr() && gaussian_ids.data_ptr()) {
+        const int64_t nnz = (int64_t)camera_ids.size();
+        float4* dense_aabb = scratch<float4>("fpbo_dense_aabb", dense);
+        v_rec = scratch<SsbScreenRec>("fpbo_grad_records", dense);
+        backend::memset_sync(dense_aabb, 0, (size_t)dense * sizeof(float4));
+        if (nnz > 0) {
+            scatter_pairs_kernel<<<(unsigned)((nnz + 255) / 256), 256>>>(nnz, N, camera_ids.data_ptr(), gaussian_ids.data_ptr(), (const float4*)aabb.data_ptr(),
+                                                                         v_splats_screen[0].data_ptr(), v_splats_screen[1].data_ptr(), v_splats_screen[2].data_ptr(),
+                                                                         v_splats_screen[3].data_ptr(), v_splats_screen[4].data_ptr(), dense_aabb, v_rec);
+            if (cudaGetLastError() != cudaSuccess) throw std::runtime_error("fused_projection_bwd_optimizer_3dgs: scatter launch failed");
+        }
+        d_aabb = (const float*)dense_aabb;
+    } else {
+        v_rec = pack_records("fpbo_grad_records", v_splats_screen[0].data_ptr(), v_splats_screen[1].data_ptr(), v_splats_screen[2].data_ptr(),
+                             v_splats_screen[3].data_ptr(), v_splats_screen[4].data_ptr(), dense);
+    }
+    auto six = [](const std::vector<DeviceTensorFloatND>& v) {
+        return SsbSplats{v[0].data_ptr(), v[1].data_ptr(), v[2].data_ptr(), v[3].data_ptr(), v[4].data_ptr(), v[5].data_ptr()};
+    };
+    const SsbSplats m1 = six(g1_splats_world), m2 = six(g2_splats_world);
+    SsbAdamExtras ex{};
+    ex.max_gauss_ratio = max_gauss_ratio; ex.scale_regularization_weight = scale_regularization_weight;
+    ex.mcmc_opacity_reg_weight = mcmc_opacity_reg_weight; ex.mcmc_scale_reg_weight = mcmc_scale_reg_weight;
+    ex.erank_reg_weight = erank_reg_weight; ex.erank_reg_weight_s3 = erank_reg_weight_s3; ex.quat_norm_reg_weight = quat_norm_reg_weight;
+    ex.use_scale_agnostic_mean = use_scale_agnostic_mean ? 1 : 0;
+    ex.d_radii = radii.data_ptr(); ex.n_total = N; ex.d_densify_score = densify_score.data_ptr();
+    int32_t scalar_step = 1;
+    if (const int32_t* s = std::get_if<int32_t>(&step)) scalar_step = *s;
+    else ex.d_steps = (const int32_t*)std::get<0>(std::get<TorchTensorView>(step));
+    // this function of the reference takes no gradient scale
+    SsbAdamConfig cfg{lr_means, lr_quats, lr_scales, lr_opacs, lr_features_dc, lr_features_sh, sh_reg_weight, 1.0f, scalar_step, 0};
+    const int64_t ws_bytes = ssb_project_bwd_optimize_workspace_bytes(N);
+    uint8_t* ws = scratch<uint8_t>("fpbo_workspace", ws_bytes + 256);
+    ws = (uint8_t*)(((uintptr_t)ws + 255) & ~(uintptr_t)255);
+    ssb_check(ssb_project_bwd_optimize(&w.splats, nullptr, N, &cams, d_aabb, v_rec, &m1, &m2, nullptr, &cfg, &ex, ws, ws_bytes, nullptr));
 }

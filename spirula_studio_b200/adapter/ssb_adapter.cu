@@ -18,6 +18,9 @@
 //   fused_adam_step_quantized      (src/kernels/optim/Optimizer.cuh:169-181)         -> ssb_adam_step_sh_quantized_ex, fp32 values
 //   fused_adam_step_quantized_value (src/kernels/optim/Optimizer.cuh:184-205)        -> ssb_adam_step_sh_quantized_ex
 //
+// The mip and 3dgut siblings declared in the same headers (and defined in the same reference source files, so they go
+// when those files are replaced) are defined here too and throw: the link stays complete, the primitives stay refused.
+//
 // Outputs are views into the reference's process-global DevicePool under the reference's own PoolSlots, sized exactly as
 // the reference sizes them (the pair count is read back to the host where the reference reads it back), so callers see
 // the same tensors.  The 48-byte records and workspaces this library works on are scratch of the adapter, kept in the
@@ -532,3 +535,44 @@ void fused_projection_bwd_optimizer_3dgs(
     ws = (uint8_t*)(((uintptr_t)ws + 255) & ~(uintptr_t)255);
     ssb_check(ssb_project_bwd_optimize(&w.splats, nullptr, N, &cams, d_aabb, v_rec, &m1, &m2, nullptr, &cfg, &ex, ws, ws_bytes, nullptr));
 }
+
+
+// ---- the other primitives of the replaced source files: defined so that the engine links, refused when called ----------------
+#define SSB_PROJ_FWD_PARAMS                                                                                                          \
+    const int64_t, const int, const std::vector<DeviceTensorFloatND>&, TorchTensorView, TorchTensorView, const uint32_t, const uint32_t, \
+        const std::string, const std::string, const TorchTensorView, DeviceVector<float>, const std::optional<TorchTensorView>,          \
+        const std::optional<TorchTensorView>, const uint32_t, const int, const int64_t
+#define SSB_PROJ_BWD_PARAMS                                                                                                          \
+    const int64_t, const int, const std::vector<DeviceTensorFloatND>&, TorchTensorView, TorchTensorView, const uint32_t, const uint32_t, \
+        const std::string, const std::string, const TorchTensorView, const DeviceVector<int32_t>, const DeviceVector<int32_t>,           \
+        const DeviceTensor2D<float4>, const std::vector<DeviceTensorFloatND>&, const std::vector<DeviceTensorFloatND>&,                  \
+        DeviceTensor2D<float>*, const std::optional<TorchTensorView>, const std::optional<TorchTensorView>, const uint32_t, const int,   \
+        const int64_t
+#define SSB_FPBO_PARAMS                                                                                                              \
+    const int64_t, const int, std::vector<DeviceTensorFloatND>, TorchTensorView, TorchTensorView, const uint32_t, const uint32_t,       \
+        const std::string, const std::string, const TorchTensorView, const DeviceVector<int32_t>, const DeviceVector<int32_t>,           \
+        DeviceTensorFloatND, const std::vector<DeviceTensorFloatND>, const std::vector<DeviceTensorFloatND>,                             \
+        const std::vector<DeviceTensorFloatND>, const std::vector<DeviceTensorFloatND>, const std::optional<TorchTensorView>,            \
+        const std::optional<TorchTensorView>, const std::optional<TorchTensorView>, const std::optional<TorchTensorView>,               \
+        NonShQuantState, DeviceVector<float>, DeviceVector<float>, const float, const float, const float, const float, const float,      \
+        const float, const float, const float, const float, const float, const float, const float, const float, const float, bool, bool, \
+        float, std::variant<int32_t, TorchTensorView>, int
+
+std::tuple<DeviceTensor2D<float4>, DeviceTensor2D<float>, std::vector<DeviceTensorFloatND>> projection_mip_forward(SSB_PROJ_FWD_PARAMS) { unsupported("the mip primitive"); }
+std::tuple<DeviceTensor2D<float4>, DeviceTensor2D<float>, std::vector<DeviceTensorFloatND>> projection_3dgut_forward(SSB_PROJ_FWD_PARAMS) { unsupported("the 3dgut primitive"); }
+void projection_mip_backward(SSB_PROJ_BWD_PARAMS) { unsupported("the mip primitive"); }
+void projection_3dgut_backward(SSB_PROJ_BWD_PARAMS) { unsupported("the 3dgut primitive"); }
+void fused_projection_bwd_optimizer_mip(SSB_FPBO_PARAMS) { unsupported("the mip primitive"); }
+void fused_projection_bwd_optimizer_3dgut(SSB_FPBO_PARAMS) { unsupported("the 3dgut primitive"); }
+std::tuple<RenderOutput::TensorTuple, DeviceTensor3D<float>, DeviceTensor3D<int32_t>, RenderOutput::TensorTuple, DeviceTensor3D<float>>
+rasterize_to_pixels_mip_fwd(int64_t, std::vector<DeviceTensorFloatND>, std::vector<DeviceTensorFloatND>, DeviceVector<int32_t>, const uint32_t, const uint32_t,
+                            const DeviceTensor3D<int32_t>, const DeviceVector<int32_t>, DistortionType, bool) { unsupported("the mip primitive"); }
+
+// Each name above must be THE function the reference declares, not an overload beside it: taking the address of an
+// overloaded name without a target type does not compile.
+static_assert(sizeof(&projection_mip_forward) && sizeof(&projection_3dgut_forward) && sizeof(&projection_mip_backward) && sizeof(&projection_3dgut_backward) &&
+              sizeof(&fused_projection_bwd_optimizer_mip) && sizeof(&fused_projection_bwd_optimizer_3dgut) && sizeof(&rasterize_to_pixels_mip_fwd) &&
+              sizeof(&projection_3dgs_forward) && sizeof(&projection_3dgs_backward) && sizeof(&fused_projection_bwd_optimizer_3dgs) &&
+              sizeof(&rasterize_to_pixels_3dgs_fwd) && sizeof(&rasterize_to_pixels_3dgs_bwd) && sizeof(&do_intersect_tile_generic) && sizeof(&compute_tile_active) &&
+              sizeof(&compute_multi_scale_per_pixel_losses) && sizeof(&fused_optim_3dgs_geometry) && sizeof(&fused_adam_step) && sizeof(&fused_adam_step_quantized) &&
+              sizeof(&fused_adam_step_quantized_value), "adapter definitions match the reference's declarations");

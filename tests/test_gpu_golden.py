@@ -210,13 +210,12 @@ def test_fused_backward_optimiser_vs_reference(lib, U, tag):
         torch.cuda.synchronize()
         for k in order:
             assert U.close_frac(p[k].cpu().numpy(), gold[f"{tag}_p{step}_{k}"], 5e-6, 1e-4) <= 2e-3, (tag, k, step)
-    # equal to the unfused calls on the same inputs
-    p2 = {k: U.dev(gold[f"{tag}_p1_{k}"]) for k in order}
-    grads = {k: torch.zeros_like(t) for k, t in p2.items()}
-    s2, g2 = L.splats_struct(p2), L.splats_struct(grads)
-    L.check(lib.ssb_project_bwd(C.byref(s2), None, n, C.byref(cams), L.ptr(d_aabb), L.ptr(vrec), C.byref(g2), 0, None))
-    torch.cuda.synchronize()
-    assert grads["means"].abs().max().item() > 0
+    for k in order:
+        ref1, ref2 = gold[f"{tag}_g1_{k}"], gold[f"{tag}_g2_{k}"]
+        assert U.close_frac(m1[k].cpu().numpy(), ref1, 1e-4 * np.abs(ref1).max(), 2e-3) <= 5e-3, (tag, k)
+        assert U.close_frac(m2[k].cpu().numpy(), ref2, 1e-4 * np.abs(ref2).max(), 4e-3) <= 5e-3, (tag, k)
+    # a workspace smaller than ssb_project_bwd_optimize_workspace_bytes is refused before anything is launched
+    s2 = L.splats_struct(p)
     assert lib.ssb_project_bwd_optimize(C.byref(s2), None, n, C.byref(cams), L.ptr(d_aabb), L.ptr(vrec), C.byref(a), C.byref(b), None, C.byref(acfg),
                                         C.byref(ex), L.ptr(ws), 16, None) == L.SSB_ERR_INVALID_ARGUMENT
 

@@ -463,6 +463,19 @@ typedef struct SsbMomentsQ16 {
 int ssb_adam_step_q16(const SsbSplats* params, const SsbSplats* grads, const SsbMomentsQ16* moments, int64_t first, int64_t count,
                       const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream);
 
+/* The SH update on the layouts of the reference's fused backward + optimiser at quantisation level 1 (the SH part of
+ * fused_projection_bwd_optimizer_3dgs_kernel<..., 256, 8, 16>, src/kernels/optim/FusedProjectionBwdOptim_kernel.cuh:709-975; pool
+ * slots eng.world.sh_vq16_fpbo and eng.sh_quant_fpbo, src/core/PoolSlots.h:115-120): 8-bit joint state codes (two bytes per cell) and 8- or 16-bit
+ * values, with ONE float4 of state bounds and ONE float2 of value bounds per 256 SPLATS, covering all 45 cells of each.  Splats
+ * [first_splat, first_splat + n_splats), first_splat a multiple of 256; d_grad is indexed by the global cell (45 * splat + cell).
+ * active_sh_degree_plus1 = 0 or 4: all 45 cells are live.  1..3 (the SH degree warm-up): the cells of the bands above the active
+ * degree are not updated but written as zero value and zero moments against bounds widened to contain zero, as the reference
+ * does (:836-857, :918-925); 1 (degree 0) leaves the buffers untouched.  cfg->sh_reg_weight, grad_scale, zero_grad, step as in
+ * ssb_adam_step_sh_quantized; d_steps [n_total] per-splat exponents or NULL. */
+int ssb_adam_step_sh_splat_blocks(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds, void* d_value_packed, float* d_value_bounds,
+                                  int32_t value_bits, int64_t first_splat, int64_t n_splats, int64_t n_total, int32_t active_sh_degree_plus1,
+                                  const SsbAdamConfig* cfg, const int32_t* d_steps, void* stream);
+
 /* Replaces fused_adam_step (src/kernels/optim/FusedAppearanceOptim.cu:11-92) on one array of numel floats, `stride` per
  * splat: Adam with the decoupled-offset L2 term 2 * l2_reg / numel * (max(x - off, 0) + min(x + off, 0)), bias correction from
  * `step`, or per splat from d_steps [numel / stride] when given.  ssb_adam_step covers the six arrays of a splat set in one
@@ -583,7 +596,11 @@ typedef struct SsbShAdamState {
     float* d_value_bounds;
     int32_t value_bits;    /* 8, 16, or 32 (fp32 values, quantised state) */
     int32_t optim_bits;    /* 8 (0 means 8) or 4 */
+    int32_t layout;        /* SSB_SH_LAYOUT_CELL_BLOCKS (0): one bound per 256 cells, the layout of fused_adam_step_quantized_value;
+                            * SSB_SH_LAYOUT_SPLAT_BLOCKS: one bound per 256 splats (ssb_adam_step_sh_splat_blocks), taken by
+                            * ssb_project_bwd_optimize and ssb_step_backward_optimize only */
 } SsbShAdamState;
+enum { SSB_SH_LAYOUT_CELL_BLOCKS = 0, SSB_SH_LAYOUT_SPLAT_BLOCKS = 1 };
 int ssb_reduce_adam_broadcast(const SsbPeerReplicas* replicas, const SsbSplats* params, const SsbSplats* grads,
                               const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
                               int64_t first, int64_t count, int64_t n_total, const SsbAdamConfig* cfg,

@@ -410,6 +410,14 @@ def adam_qq(grad, optim_packed, optim_bounds, value_packed, value_bounds, value_
                                 _p(value_bounds), _p(steps) if steps is not None else None, C.c_int(stride), C.c_int(optim_bits))
 
 
+def adam_sh_splat_blocks(grad, optim_packed, optim_bounds, value_packed, value_bounds, value_bits, n_splats, step, lr, l2_reg=0.0,
+                         grad_scale=1.0, sh_degree=3, steps=None):
+    """SH Adam on the layouts of the reference's fused backward + optimiser at quantisation level 1: bounds per 256 splats."""
+    load().oracle_adam_sh_splat_blocks(C.c_int64(n_splats), C.c_int(3 * sh_degree * (sh_degree + 2)), C.c_int(step), C.c_float(lr), C.c_float(l2_reg),
+                                       C.c_float(grad_scale), C.c_int(value_bits), _p(grad), _p(optim_packed), _p(optim_bounds), _p(value_packed),
+                                       _p(value_bounds), _p(steps) if steps is not None else None)
+
+
 def forward_chain(splats, viewmats, intrins, W, H, shq=None, model=0, dist=0, dist_coeffs=None, sh_degree=3):
     """projection -> keys -> sort -> ranges -> raster for all views in one batch (as the reference's batched launch)."""
     N, I = splats["means"].shape[0], viewmats.shape[0]

@@ -1759,6 +1759,67 @@ void oracle_adam_qq_ex(
     }
 }
 
+// The SH section of the reference's fused backward + optimiser at quantisation level 1
+// (fused_projection_bwd_optimizer_3dgs_kernel<..., 256, 8, VALUE_BITS>, src/kernels/optim/FusedProjectionBwdOptim_kernel.cuh:709-975):
+// the same two codecs, with one float4 of state bounds and one float2 of value bounds per 256 SPLATS (all 45 cells of each).
+// n_active = live cells per splat (3 * coefficients of the active degree); the idle cells are not updated but written as zero
+// value / zero moments against bounds widened to contain zero (:836-857, :918-925).  Regulariser: 2 l2 / (45 n) * value (:769-773
+// with the wrapper's scaling :1137 and the division by num_sh :695).
+void oracle_adam_sh_splat_blocks(
+    int64_t n_splats, int n_active, int step, float lr, float l2_reg, float grad_scale, int value_bits,
+    const float* grad, uint8_t* optim_packed, float* optim_bounds, uint8_t* value_packed, float* value_bounds, const int32_t* steps) {
+    const float eps = 1e-15f, beta1 = 0.9f, beta2 = 0.999f, kEps = 1e-15f;
+    if (n_active <= 0) return;
+    const float decay = 2.0f * l2_reg / (float)(n_splats * 45);
+    const float vq = (float)((1 << value_bits) - 1), vinv = 1.0f / vq, oq = 255.0f, oinv = 1.0f / 255.0f;
+    const int64_t nb = (n_splats + 255) / 256;
+#pragma omp parallel for schedule(static)
+    for (int64_t b = 0; b < nb; ++b) {
+        const int64_t lo = b * 256 * 45, hi = std::min(n_splats, (b + 1) * 256) * 45;
+        std::vector<float> xs(hi - lo, 0.f), us(hi - lo, 0.f), ss(hi - lo, 0.f);
+        const float vmm[2] = {value_bounds[2 * b], value_bounds[2 * b + 1]};
+        const float omm[4] = {optim_bounds[4 * b], optim_bounds[4 * b + 1], optim_bounds[4 * b + 2], optim_bounds[4 * b + 3]};
+        float nv[2] = {1e30f, -1e30f}, no[4] = {1e30f, -1e30f, 1e30f, -1e30f};
+        for (int64_t i = lo; i < hi; ++i) {
+            if (i % 45 >= n_active) continue;
+            const float q = value_bits == 8 ? (float)value_packed[i] : (float)reinterpret_cast<uint16_t*>(value_packed)[i];
+            float x = vmm[0] + (vmm[1] - vmm[0]) * (q * vinv);
+            float v = grad[i];
+            if (!std::isfinite(v)) v = 0.f;
+            v *= grad_scale;
+            v += decay * x;
+            const float u = omm[0] + (omm[1] - omm[0]) * ((float)optim_packed[2 * i] * oinv);
+            const float ls = omm[2] + (omm[3] - omm[2]) * ((float)optim_packed[2 * i + 1] * oinv);
+            const float sqrt_g2 = kEps * std::expm1(ls);
+            float g1 = u * (sqrt_g2 + kEps), g2 = sqrt_g2 * sqrt_g2;
+            g1 = beta1 * g1 + (1.f - beta1) * v;
+            g2 = beta2 * g2 + (1.f - beta2) * v * v;
+            const float stepf = (float)(steps ? steps[i / 45] : step);
+            const float ibc1 = 1.0f / (1.0f - std::pow(beta1, stepf)), ibc2 = 1.0f / (1.0f - std::pow(beta2, stepf));
+            x -= lr * ibc1 * g1 / (std::sqrt(g2 * ibc2) + eps);
+            const float sq = std::sqrt(std::max(g2, 0.0f));
+            const float un = g1 / (sq + kEps), sn = std::log1p(sq * (1.0f / kEps));
+            xs[i - lo] = x; us[i - lo] = un; ss[i - lo] = sn;
+            nv[0] = std::min(nv[0], x); nv[1] = std::max(nv[1], x);
+            no[0] = std::min(no[0], un); no[1] = std::max(no[1], un);
+            no[2] = std::min(no[2], sn); no[3] = std::max(no[3], sn);
+        }
+        if (n_active < 45) {
+            nv[0] = std::min(nv[0], 0.f); nv[1] = std::max(nv[1], 0.f);
+            no[0] = std::min(no[0], 0.f); no[1] = std::max(no[1], 0.f); no[2] = std::min(no[2], 0.f);
+        }
+        const float vrange = std::max(nv[1] - nv[0], 1e-30f), urange = std::max(no[1] - no[0], kEps), srange = std::max(no[3] - no[2], kEps);
+        for (int64_t i = lo; i < hi; ++i) {
+            const float qf = std::min(std::max(std::round(vq * (xs[i - lo] - nv[0]) / vrange), 0.0f), vq);
+            if (value_bits == 8) value_packed[i] = (uint8_t)qf; else reinterpret_cast<uint16_t*>(value_packed)[i] = (uint16_t)qf;
+            optim_packed[2 * i] = (uint8_t)std::min(std::max(std::round(oq * (us[i - lo] - no[0]) / urange), 0.0f), oq);
+            optim_packed[2 * i + 1] = (uint8_t)std::min(std::max(std::round(oq * (ss[i - lo] - no[2]) / srange), 0.0f), oq);
+        }
+        value_bounds[2 * b] = nv[0]; value_bounds[2 * b + 1] = nv[1];
+        for (int k = 0; k < 4; ++k) optim_bounds[4 * b + k] = no[k];
+    }
+}
+
 void oracle_adam_qq(
     int64_t numel, int step, float lr, float l2_reg, float l2_reg_offset, float grad_scale, int zero_grad, int value_bits,
     float* grad, uint8_t* optim_packed, float* optim_bounds, uint8_t* value_packed, float* value_bounds) {

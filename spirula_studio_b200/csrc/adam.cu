@@ -719,6 +719,124 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
     }
 }
 
+// The same update on the layouts of the reference's fused backward + optimiser at quantisation level 1
+// (src/kernels/optim/FusedProjectionBwdOptim_kernel.cuh:709-975): one float4 of state bounds and one float2 of value bounds
+// per 256 SPLATS, covering all 45 cells of each; 8-bit joint state codes; 8- or 16-bit values.  One CTA per block of 256
+// splats = 11520 cells, 18 per thread, a thread's cells 640 apart so that every load and store of a warp is contiguous; the
+// updated value and the two new state coordinates of a thread's cells wait in registers for the block's new bounds.
+// n_active: live cells per splat (3 * coefficients of the active SH degree); the others are not updated but written as zero
+// value and zero moments against bounds widened to contain zero (the SH degree warm-up, :836-857, :918-925).
+constexpr int kSbThreads = 640, kSbCells = 256 * 45, kSbPer = kSbCells / kSbThreads;
+static_assert(kSbPer * kSbThreads == kSbCells, "a block's cells divide evenly over the CTA");
+
+template <int VALUE_BITS, bool STEPS>
+__global__ void __launch_bounds__(kSbThreads, 1) adam_sh_splat_block_kernel(
+    float* __restrict__ grad, uint8_t* __restrict__ optim_packed, float4* __restrict__ optim_bounds, uint8_t* __restrict__ value_packed,
+    float2* __restrict__ value_bounds, int64_t first_block, int64_t n_total_splats, int n_active, float lr_ibc1, float ibc2, float decay,
+    float grad_scale, int zero_grad, const int32_t* __restrict__ steps, float lr) {
+    __shared__ uint32_t red[6][kSbThreads / 32];
+    const int64_t blk = first_block + blockIdx.x;
+    const int64_t cell0 = blk * kSbCells;
+    const int n_cells = (int)min((int64_t)kSbCells, (n_total_splats - blk * 256) * 45);
+    constexpr float vq = (float)((1u << VALUE_BITS) - 1u), vinv = 1.0f / vq;
+    const float oq = 255.0f, oinv = 1.0f / 255.0f;
+    const float2 vmm = value_bounds[blk];
+    const float4 omm = optim_bounds[blk];
+    float x[kSbPer], u_new[kSbPer], s_new[kSbPer];
+    float mn[3] = {1e30f, 1e30f, 1e30f}, mx[3] = {-1e30f, -1e30f, -1e30f};
+#pragma unroll
+    for (int k = 0; k < kSbPer; ++k) {
+        const int c = threadIdx.x + k * kSbThreads;
+        x[k] = u_new[k] = s_new[k] = 0.f;
+        const int splat = c / 45;
+        if (c < n_cells && c - splat * 45 < n_active) {
+            const int64_t idx = cell0 + c;
+            float v = grad[idx];
+            if (zero_grad) grad[idx] = 0.f;
+            const uint32_t vcode = VALUE_BITS == 8 ? (uint32_t)value_packed[idx] : (uint32_t)((const uint16_t*)value_packed)[idx];
+            const uint32_t oc = ((const uint16_t*)optim_packed)[idx];
+            float xv = vmm.x + (vmm.y - vmm.x) * ((float)vcode * vinv);
+            if (!isfinite(v)) v = 0.f;
+            v *= grad_scale;
+            v += decay * xv;
+            const float u = omm.x + (omm.y - omm.x) * ((float)(oc & 255u) * oinv);
+            const float ls = omm.z + (omm.w - omm.z) * ((float)(oc >> 8) * oinv);
+            float em1;
+            if (ls > 12.0f) em1 = __expf(ls) - 1.0f; else em1 = expm1f(ls);
+            const float sqrt_g2 = kAdamEps * em1;
+            float g1 = u * (sqrt_g2 + kAdamEps), g2 = sqrt_g2 * sqrt_g2;
+            g1 = kBeta1 * g1 + (1.f - kBeta1) * v;
+            g2 = kBeta2 * g2 + (1.f - kBeta2) * v * v;
+            float lr1 = lr_ibc1, c2 = ibc2;
+            if (STEPS) {
+                const float step = (float)steps[blk * 256 + splat];
+                lr1 = lr * inv_bias_correction(kBeta1, step);
+                c2 = inv_bias_correction(kBeta2, step);
+            }
+            xv -= __fdividef(lr1 * g1, sqrt_approx(g2 * c2) + kAdamEps);
+            const float sq = sqrt_approx(fmaxf(g2, 0.0f));
+            u_new[k] = __fdividef(g1, sq + kAdamEps);
+            const float y = sq * (1.0f / kAdamEps);
+            if (y > 1.0e6f) s_new[k] = __logf(y); else s_new[k] = log1pf(y);
+            x[k] = xv;
+            mn[0] = fminf(mn[0], xv); mx[0] = fmaxf(mx[0], xv);
+            mn[1] = fminf(mn[1], u_new[k]); mx[1] = fmaxf(mx[1], u_new[k]);
+            mn[2] = fminf(mn[2], s_new[k]); mx[2] = fmaxf(mx[2], s_new[k]);
+        }
+    }
+    {
+        const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+        uint32_t r[6];
+#pragma unroll
+        for (int k = 0; k < 3; ++k) { r[k] = __reduce_min_sync(0xffffffffu, f2ord(mn[k])); r[3 + k] = __reduce_max_sync(0xffffffffu, f2ord(mx[k])); }
+        if (lane == 0) {
+#pragma unroll
+            for (int k = 0; k < 6; ++k) red[k][w] = r[k];
+        }
+        __syncthreads();
+        if (w == 0) {
+#pragma unroll
+            for (int k = 0; k < 6; ++k) {
+                const uint32_t mine = lane < kSbThreads / 32 ? red[k][lane] : (k < 3 ? 0xffffffffu : 0u);
+                r[k] = k < 3 ? __reduce_min_sync(0xffffffffu, mine) : __reduce_max_sync(0xffffffffu, mine);
+            }
+            __syncwarp();
+            if (lane == 0) {
+#pragma unroll
+                for (int k = 0; k < 6; ++k) red[k][0] = r[k];
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 3; ++k) { mn[k] = ord2f(red[k][0]); mx[k] = ord2f(red[3 + k][0]); }
+    }
+    if (n_active < 45) {       // zero must be representable: the idle cells are written as zero
+        mn[0] = fminf(mn[0], 0.f); mx[0] = fmaxf(mx[0], 0.f);
+        mn[1] = fminf(mn[1], 0.f); mx[1] = fmaxf(mx[1], 0.f);
+        mn[2] = fminf(mn[2], 0.f);
+    }
+    const float vmin = mn[0], vmax = mx[0], umin = mn[1], umax = mx[1], smin = mn[2], smax = mx[2];
+    const float vscale = __fdividef(vq, fmaxf(vmax - vmin, 1e-30f));
+    const float uscale = __fdividef(oq, fmaxf(umax - umin, kAdamEps)), sscale = __fdividef(oq, fmaxf(smax - smin, kAdamEps));
+#pragma unroll
+    for (int k = 0; k < kSbPer; ++k) {
+        const int c = threadIdx.x + k * kSbThreads;
+        if (c < n_cells) {
+            const int64_t idx = cell0 + c;
+            // an idle cell holds x = u = s = 0 here
+            const uint32_t vout = (uint32_t)fminf(fmaxf(rintf((x[k] - vmin) * vscale), 0.0f), vq);
+            const uint32_t uqc = (uint32_t)fminf(fmaxf(rintf((u_new[k] - umin) * uscale), 0.0f), oq);
+            const uint32_t sqc = (uint32_t)fminf(fmaxf(rintf((s_new[k] - smin) * sscale), 0.0f), oq);
+            if (VALUE_BITS == 8) value_packed[idx] = (uint8_t)vout; else ((uint16_t*)value_packed)[idx] = (uint16_t)vout;
+            ((uint16_t*)optim_packed)[idx] = (uint16_t)(uqc | (sqc << 8));
+        }
+    }
+    if (threadIdx.x == 0) {
+        value_bounds[blk] = make_float2(vmin, vmax);
+        optim_bounds[blk] = make_float4(umin, umax, smin, smax);
+    }
+}
+
 template <int BITS>
 __global__ void __launch_bounds__(256) quant_encode_kernel(const float* __restrict__ values, int64_t numel, uint8_t* __restrict__ packed, float2* __restrict__ bounds) {
     __shared__ uint32_t sh[2][8];
@@ -920,6 +1038,36 @@ int ssb_adam_step_q16(const SsbSplats* params, const SsbSplats* grads, const Ssb
     return adam_step_impl(&p, &g, nullptr, nullptr, first, count, cfg, extras, nullptr, stream, &nq);
 }
 
+int ssb_adam_step_sh_splat_blocks(float* d_grad, uint8_t* d_optim_packed, float* d_optim_bounds, void* d_value_packed, float* d_value_bounds,
+                                  int32_t value_bits, int64_t first_splat, int64_t n_splats, int64_t n_total, int32_t active_sh_degree_plus1,
+                                  const SsbAdamConfig* cfg, const int32_t* d_steps, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(d_grad && d_optim_packed && d_optim_bounds && d_value_packed && d_value_bounds && cfg, "ssb_adam_step_sh_splat_blocks: NULL argument");
+    SSB_REQUIRE(value_bits == 8 || value_bits == 16, "ssb_adam_step_sh_splat_blocks: value_bits must be 8 or 16 (got %d)", value_bits);
+    SSB_REQUIRE(first_splat >= 0 && (first_splat % 256) == 0 && n_splats >= 0 && first_splat + n_splats <= n_total,
+                "ssb_adam_step_sh_splat_blocks: bad splat range (the first splat must be a multiple of 256)");
+    SSB_REQUIRE(active_sh_degree_plus1 >= 0 && active_sh_degree_plus1 <= 4, "ssb_adam_step_sh_splat_blocks: SH degree + 1 must be 0..4 (got %d)", active_sh_degree_plus1);
+    SSB_REQUIRE(cfg->step >= 1 || d_steps, "ssb_adam_step_sh_splat_blocks: step must be >= 1");
+    SSB_REQUIRE(((uintptr_t)d_optim_packed & 1) == 0 && ((uintptr_t)d_value_packed & 1) == 0, "ssb_adam_step_sh_splat_blocks: code buffers must be 2-byte aligned");
+    const int degree = active_sh_degree_plus1 == 0 ? 3 : active_sh_degree_plus1 - 1;
+    const int n_active = 3 * (degree * (degree + 2));
+    if (n_splats == 0 || n_active == 0) return SSB_OK;     // at degree 0 the reference's kernel has no SH section
+    const int step = cfg->step >= 1 ? cfg->step : 1;
+    const float ibc1 = 1.0f / (1.0f - powf(kBeta1, (float)step)), ibc2 = 1.0f / (1.0f - powf(kBeta2, (float)step));
+    const float decay = 2.0f * cfg->sh_reg_weight / (float)(n_total * 45);
+    const unsigned blocks = (unsigned)ceil_div(n_splats, 256);
+    // a range that ends inside a block would leave that block's other splats with bounds that no longer fit their codes
+    SSB_REQUIRE((n_splats % 256) == 0 || first_splat + n_splats == n_total, "ssb_adam_step_sh_splat_blocks: a range ends on a multiple of 256 splats or at the last splat");
+#define SSB_SB_ARGS d_grad, d_optim_packed, (float4*)d_optim_bounds, (uint8_t*)d_value_packed, (float2*)d_value_bounds, first_splat / 256, n_total, n_active, \
+        cfg->lr_features_sh * ibc1, ibc2, decay, cfg->grad_scale, cfg->zero_grad, d_steps, cfg->lr_features_sh
+    cudaStream_t st = (cudaStream_t)stream;
+    if (value_bits == 16) { if (d_steps) adam_sh_splat_block_kernel<16, true><<<blocks, kSbThreads, 0, st>>>(SSB_SB_ARGS); else adam_sh_splat_block_kernel<16, false><<<blocks, kSbThreads, 0, st>>>(SSB_SB_ARGS); }
+    else { if (d_steps) adam_sh_splat_block_kernel<8, true><<<blocks, kSbThreads, 0, st>>>(SSB_SB_ARGS); else adam_sh_splat_block_kernel<8, false><<<blocks, kSbThreads, 0, st>>>(SSB_SB_ARGS); }
+#undef SSB_SB_ARGS
+    SSB_LAUNCHED("adam_sh_splat_block_kernel");
+    return SSB_OK;
+}
+
 int ssb_adam_plain(float* d_param, float* d_grad, float* d_m1, float* d_m2, int64_t numel, int32_t stride, float lr, int32_t step,
                    const int32_t* d_steps, float l2_reg, float l2_reg_offset, float grad_scale, int32_t zero_grad, void* stream) {
     using namespace ssb;
@@ -978,6 +1126,7 @@ static int reduce_adam_broadcast_impl(const SsbPeerReplicas* replicas, const Ssb
     }
     if (quantised) {
         SSB_REQUIRE(sh_state->d_optim_packed && sh_state->d_optim_bounds && sh_state->d_value_packed, "ssb_reduce_adam_broadcast: NULL SH state");
+        SSB_REQUIRE(sh_state->layout == SSB_SH_LAYOUT_CELL_BLOCKS, "ssb_reduce_adam_broadcast: the SH state must be in the cell-block layout");
         SSB_REQUIRE(sh_state->value_bits == 32 || (sh_state->d_value_packed == replicas->sh_packed[replicas->self] &&
                                                    (void*)sh_state->d_value_bounds == replicas->sh_bounds[replicas->self]),
                     "ssb_reduce_adam_broadcast: the packed SH values and bounds must be this rank's exchanged buffers");

@@ -549,6 +549,7 @@ static int densify_arrays(const SsbDensifyState* st, ssb::DensifyArrays* a, cons
     SSB_REQUIRE(vq != (p.features_sh != nullptr), "%s: SH values are either fp32 (params.features_sh) or quantised (sh.d_value_packed)", who);
     SSB_REQUIRE(!vq || st->sh.d_value_bounds, "%s: sh.d_value_bounds is NULL", who);
     const bool oq = st->sh.d_optim_packed != nullptr;
+    SSB_REQUIRE(st->sh.layout == SSB_SH_LAYOUT_CELL_BLOCKS, "%s: the SH state must be in the cell-block layout", who);
     SSB_REQUIRE(!oq || (st->sh.d_optim_bounds && (st->sh.optim_bits == 0 || st->sh.optim_bits == 8 || st->sh.optim_bits == 4)), "%s: bad quantised SH state", who);
     *a = DensifyArrays{};
     a->means = p.means; a->quats = p.quats; a->scales = p.scales; a->opacs = p.opacities; a->dc = p.features_dc; a->sh = p.features_sh;

@@ -442,7 +442,12 @@ static int fused_backward_range(const SsbSplats* params, const SsbShQuant* shq, 
     SsbSplats p = *params, a1 = *m1, a2 = *m2;
     if (sh_state) { p.features_sh = nullptr; a1.features_sh = nullptr; a2.features_sh = nullptr; }
     if (int e = ssb_adam_step_ex(&p, &ga, &a1, &a2, first, count, c, extras, stream)) return e;
-    if (sh_state) {
+    if (sh_state && sh_state->layout == SSB_SH_LAYOUT_SPLAT_BLOCKS) {
+        // the reference's own layout for this path: bounds per 256 splats; a range is a whole number of such blocks
+        if (int e = ssb_adam_step_sh_splat_blocks(g.features_sh, sh_state->d_optim_packed, sh_state->d_optim_bounds, sh_state->d_value_packed,
+                                                  sh_state->d_value_bounds, sh_state->value_bits, first, count, n, cams->sh_degree_plus1, c,
+                                                  extras ? extras->d_steps : nullptr, stream)) return e;
+    } else if (sh_state) {
         void* values = sh_state->value_bits == 32 ? (void*)params->features_sh : sh_state->d_value_packed;
         if (int e = ssb_adam_step_sh_quantized_ex(g.features_sh, sh_state->d_optim_packed, sh_state->d_optim_bounds, values, sh_state->d_value_bounds,
                                                   sh_state->value_bits, sh_state->optim_bits ? sh_state->optim_bits : 8, first * 45, count * 45, n * 45,

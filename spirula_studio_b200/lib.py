@@ -157,6 +157,7 @@ SIGNATURES = {
     "ssb_adam_step_sh_quantized": (C.c_int, [_P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _P, _P]),
     "ssb_adam_step_ex": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _P, _P, _P]),
     "ssb_adam_step_sh_quantized_ex": (C.c_int, [_P, _P, _P, _P, _P, _I32, _I32, _I64, _I64, _I64, _P, _P, _I32, _P]),
+    "ssb_adam_step_sh_splat_blocks": (C.c_int, [_P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _I32, _P, _P, _P]),
     "ssb_quant_encode": (C.c_int, [_P, _I64, _I32, _P, _P, _P]),
     "ssb_quant_decode": (C.c_int, [_P, _P, _I64, _I32, _P, _P]),
     "ssb_step_create": (C.c_int, [_P, _P]),
@@ -280,7 +281,10 @@ class SsbPeerReplicas(C.Structure):
 
 class SsbShAdamState(C.Structure):
     _fields_ = [("d_optim_packed", C.c_void_p), ("d_optim_bounds", C.c_void_p), ("d_value_packed", C.c_void_p),
-                ("d_value_bounds", C.c_void_p), ("value_bits", C.c_int32), ("optim_bits", C.c_int32)]
+                ("d_value_bounds", C.c_void_p), ("value_bits", C.c_int32), ("optim_bits", C.c_int32), ("layout", C.c_int32)]
+
+
+SH_LAYOUT_CELL_BLOCKS, SH_LAYOUT_SPLAT_BLOCKS = 0, 1
 
 
 class SsbMomentsQ16(C.Structure):

@@ -122,6 +122,54 @@ def fpbo_inputs(n):
     return dict(radii=rng.uniform(0.5, 40.0, size=n).astype(np.float32), steps=rng.integers(1, 50, size=n).astype(np.int32))
 
 
+# The same kernel at quantisation level 1 (16-bit SH values and 8-bit SH optimiser state, one bound per 256 splats): "l1" = every
+# optimiser option on, fp32 moments for the other arrays; "l1_deg1" = SH degree 1 on the 15-coefficient buffers (the warm-up:
+# idle bands are written as zero); "l1_nq" = the moments of the other arrays in 16-bit codes as well (the stock configuration).
+FPBO_L1_RUNS = {"l1": dict(reg=[3.0, 0.7, 0.9, 1.1, 0.5, 0.3, 0.2], sh_reg=0.05, agnostic=1, steps=True, degree=3, nq=False),
+                "l1_deg1": dict(reg=[10.0, 0, 0, 0, 0, 0, 0], sh_reg=0.05, agnostic=0, steps=False, degree=1, nq=False),
+                "l1_nq": dict(reg=[3.0, 0.7, 0.9, 1.1, 0.5, 0.3, 0.2], sh_reg=0.05, agnostic=1, steps=True, degree=3, nq=True)}
+
+
+def encode_splat_blocks(values, bits=16):
+    """values [n, 45] -> (codes uint16/uint8 [n * 45], bounds float32 [blocks, 2]): the linear min/max codec of the reference
+    (QuantizedTensor<BITS>::encode_v, src/core/Tensor.h:1379-1392) with one bound per 256 splats."""
+    n = values.shape[0]
+    flat = values.reshape(n, -1).astype(np.float32)
+    qmax = np.float32((1 << bits) - 1)
+    blocks = (n + 255) // 256
+    codes = np.zeros(flat.shape, np.uint16 if bits == 16 else np.uint8)
+    bounds = np.zeros((blocks, 2), np.float32)
+    for b in range(blocks):
+        blk = flat[b * 256:(b + 1) * 256]
+        lo, hi = np.float32(blk.min()), np.float32(blk.max())
+        rng_ = np.maximum(hi - lo, np.float32(1e-30))
+        codes[b * 256:(b + 1) * 256] = np.clip(np.round(qmax * (blk - lo) / rng_), 0, qmax).astype(codes.dtype)
+        bounds[b] = (lo, hi)
+    return codes.reshape(-1), bounds
+
+
+def decode_splat_blocks(codes, bounds, bits=16):
+    """The inverse: codes [n * 45] and bounds [blocks, 2] -> float32 [n, 45]."""
+    n = codes.size // 45
+    mm = np.repeat(bounds.reshape(-1, 2), 256, axis=0)[:n]
+    q = codes.reshape(n, 45).astype(np.float32) * np.float32(1.0 / ((1 << bits) - 1))
+    return (mm[:, :1] + (mm[:, 1:] - mm[:, :1]) * q).astype(np.float32)
+
+
+def joint_state_decode(codes, bounds, cells_per_block):
+    """8-bit joint optimiser-state codes (two bytes per cell: u, log-s) and float4 bounds per block of cells_per_block cells ->
+    (u, log-s) float32 arrays (QuantizedAdamState<8>::decode_us, src/core/Tensor.h:1044-1066)."""
+    c = codes.reshape(-1, 2).astype(np.float32) * np.float32(1.0 / 255.0)
+    mm = np.repeat(bounds.reshape(-1, 4), cells_per_block, axis=0)[: c.shape[0]]
+    return mm[:, 0] + (mm[:, 1] - mm[:, 0]) * c[:, 0], mm[:, 2] + (mm[:, 3] - mm[:, 2]) * c[:, 1]
+
+
+def frac_beyond_quanta(a, b, ref_lo, ref_hi, levels, quanta):
+    """Fraction of entries of two decoded arrays that differ by more than `quanta` steps of the reference's code grid."""
+    step = np.maximum(ref_hi - ref_lo, 1e-30) / levels
+    return float((np.abs(a.astype(np.float64) - b.astype(np.float64)) > quanta * step + 1e-12).mean())
+
+
 ACCUM_CASES = ("ring2", "dense1")
 
 # Quantised SH storage read by the projection (forward and backward): 8- or 16-bit codes with (min, max) bounds

@@ -24,7 +24,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, HERE)
 
-from golden_cases import (ACCUM_CASES, CASES, DENSIFY_SCORE_RUNS, DIST_CASES, FPBO_RUNS, FPBO_SCENE, dist_case_inputs, fpbo_inputs, DENSIFY_SPLIT, LIVE_TILE_CASE, LOSS_MAP_WEIGHT, MULTI_SCALE_RUNS, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
+from golden_cases import (ACCUM_CASES, CASES, DENSIFY_SCORE_RUNS, DIST_CASES, FPBO_L1_RUNS, FPBO_RUNS, FPBO_SCENE, encode_splat_blocks, dist_case_inputs, fpbo_inputs, DENSIFY_SPLIT, LIVE_TILE_CASE, LOSS_MAP_WEIGHT, MULTI_SCALE_RUNS, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
                           build_case, densify_inputs, densify_split_inputs, loss_inputs, loss_map_base, loss_masks, quant_sh_inputs, raster_cotangents, tile_masks)  # noqa: E402
 
 DEV = "cuda:0"
@@ -564,6 +564,58 @@ def run_fpbo(ref, out_dir):
     np.savez_compressed(os.path.join(out_dir, "fpbo.npz"), **out)
 
 
+def run_fpbo_l1(ref, out_dir):
+    """The reference's fused projection-backward + optimiser kernel at quantisation level 1 (16-bit SH values, 8-bit SH optimiser
+    state, one bound per 256 splats; in one run the other moments as 16-bit codes too), two passes per run from the zero state:
+    after each pass the five fp32 parameter arrays, the SH value codes and bounds, the SH state codes and bounds; after the
+    second the other moments (fp32 arrays or codes and bounds)."""
+    cfg, sp, vm, K = build_case(FPBO_SCENE)
+    gold = np.load(os.path.join(HERE, f"{FPBO_SCENE}.npz"))
+    n, W, H, I = cfg.n_splats, cfg.width, cfg.height, vm.shape[0]
+    blocks = (n + 255) // 256
+    lr = cfg.lrs
+    lrs = np.array([lr["lr_means"], lr["lr_quats"], lr["lr_scales"], lr["lr_opacities"], lr["lr_features_dc"], lr["lr_features_sh"]], np.float32)
+    d_vm, d_K, d_aabb = dev(vm), dev(K), dev(gold["aabb"])
+    v = [dev(gold[k]) for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")]
+    extra = fpbo_inputs(n)
+    d_radii, d_steps = dev(extra["radii"]), dev(extra["steps"])
+    five = ("means", "quats", "scales", "opacities", "features_dc")
+    widths = dict(means=3, quats=4, scales=3, opacities=1, features_dc=3)
+    codes0, bounds0 = encode_splat_blocks(sp["features_sh"].reshape(n, 45), 16)
+    ptrs = lambda ts: (C.c_void_p * len(ts))(*[t.data_ptr() if t is not None else 0 for t in ts])
+    out = {}
+    for tag, run in FPBO_L1_RUNS.items():
+        p = {k: dev(sp[k].reshape(-1)) for k in five}
+        sh_fp32 = torch.zeros(n * 45, device=DEV)
+        vcodes, vbounds = dev(codes0.view(np.uint8)), dev(bounds0)
+        ocodes, obounds = torch.zeros(n * 45 * 2, dtype=torch.uint8, device=DEV), torch.zeros(blocks * 4, device=DEV)
+        g1 = {k: torch.zeros_like(t) for k, t in p.items()}
+        g2 = {k: torch.zeros_like(t) for k, t in p.items()}
+        nq_p = {k: torch.zeros(n * widths[k] * 4, dtype=torch.uint8, device=DEV) for k in five}
+        nq_b = {k: torch.zeros(blocks * 4, device=DEV) for k in five}
+        reg = np.array(run["reg"], np.float32)
+        for step in (1, 2):
+            zero = [torch.zeros_like(p[k]) for k in five] + [torch.zeros(n * 45, device=DEV)]
+            steps_t = (d_steps + (step - 1)).contiguous() if run["steps"] else None
+            check(ref.ref_fpbo_l1(I, n, W, H, run["degree"], ptrs([p[k] for k in five] + [sh_fp32]), P(d_vm), P(d_K), P(d_aabb), ptrs(v), ptrs(zero),
+                                  ptrs([g1[k] for k in five]), ptrs([g2[k] for k in five]), P(ocodes), P(obounds), P(vcodes), P(vbounds),
+                                  ptrs([nq_p[k] for k in five]) if run["nq"] else None, ptrs([nq_b[k] for k in five]) if run["nq"] else None,
+                                  P(d_radii), lrs.ctypes.data_as(C.c_void_p), reg.ctypes.data_as(C.c_void_p), C.c_float(run["sh_reg"]),
+                                  run["agnostic"], step, P(steps_t) if steps_t is not None else None), "ref_fpbo_l1 " + tag)
+            for k in five:
+                out[f"{tag}_p{step}_{k}"] = p[k].cpu().numpy()
+            out[f"{tag}_s{step}_value_codes"], out[f"{tag}_s{step}_value_bounds"] = vcodes.cpu().numpy().view(np.uint16), vbounds.cpu().numpy()
+            out[f"{tag}_s{step}_optim_codes"], out[f"{tag}_s{step}_optim_bounds"] = ocodes.cpu().numpy(), obounds.cpu().numpy()
+            if run["nq"]:
+                for k in five:
+                    out[f"{tag}_s{step}_nq_{k}"], out[f"{tag}_s{step}_nqb_{k}"] = nq_p[k].cpu().numpy(), nq_b[k].cpu().numpy()
+        if not run["nq"]:
+            for k in five:
+                out[f"{tag}_g1_{k}"], out[f"{tag}_g2_{k}"] = g1[k].cpu().numpy(), g2[k].cpu().numpy()
+        assert not sh_fp32.any().item()          # the fp32 SH array is not this level's storage
+    np.savez_compressed(os.path.join(out_dir, "fpbo_l1.npz"), **out)
+
+
 def run_sh_degree(ref, out_dir):
     """Projection forward and backward of the reference's Vanilla3DGS<0>, <1> and <2> kernels (the SH degree warm-up) on the
     ring2 scene with its 15-coefficient SH rows: the colours, the validity boxes and the six gradient arrays for the
@@ -660,6 +712,8 @@ def main():
         run_sh_degree(ref, out_dir)
     if not only or "fpbo" in only:
         run_fpbo(ref, out_dir)
+    if not only or "fpbo_l1" in only:
+        run_fpbo_l1(ref, out_dir)
     if not only or "ssim_map" in only:
         run_loss_map(ref, out_dir)
     if not only or "ssim_masked" in only:

@@ -15,7 +15,7 @@ import pytest
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 
-from golden_cases import (DIST_CASES, FPBO_RUNS, FPBO_SCENE, dist_case_inputs, fpbo_inputs, ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
+from golden_cases import (DIST_CASES, FPBO_L1_RUNS, FPBO_RUNS, FPBO_SCENE, decode_splat_blocks, encode_splat_blocks, frac_beyond_quanta, joint_state_decode, dist_case_inputs, fpbo_inputs, ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
                           build_case, loss_inputs, loss_map_base, quant_sh_inputs, raster_cotangents)  # noqa: E402
 
 
@@ -177,6 +177,68 @@ def test_fused_backward_optimiser_vs_reference(oracle, tag):
         for k in p:
             assert frac_bad(p[k].reshape(-1), gold[f"{tag}_p{step}_{k}"], 5e-6, 1e-4) <= 2e-3, (tag, k, step)
     for k in p:
+        ref1, ref2 = gold[f"{tag}_g1_{k}"], gold[f"{tag}_g2_{k}"]
+        assert frac_bad(m1[k].reshape(-1), ref1, 1e-4 * np.abs(ref1).max(), 2e-3) <= 5e-3, k
+        assert frac_bad(m2[k].reshape(-1), ref2, 1e-4 * np.abs(ref2).max(), 4e-3) <= 5e-3, k
+
+
+def splat_block_state_close(got_vc, got_vb, got_oc, got_ob, ref_vc, ref_vb, ref_oc, ref_ob, n):
+    """SH value codes / bounds and SH state codes / bounds in the per-256-splats layout against the reference's, compared as the
+    numbers they stand for: a block's bounds come from its extreme entries, so rounding moves codes without moving values."""
+    assert np.allclose(got_vb, ref_vb, rtol=2e-3, atol=2e-5) and np.allclose(got_ob.reshape(-1, 4), ref_ob.reshape(-1, 4), rtol=2e-3, atol=2e-3)
+    gv, rv = decode_splat_blocks(got_vc, got_vb), decode_splat_blocks(ref_vc, ref_vb)
+    rb = np.repeat(ref_vb.reshape(-1, 2), 256, axis=0)[:n]
+    assert frac_beyond_quanta(gv, rv, rb[:, :1], rb[:, 1:], 65535.0, 3.0) <= 5e-3
+    (gu, gs), (ru, rs) = joint_state_decode(got_oc, got_ob, 256 * 45), joint_state_decode(ref_oc, ref_ob, 256 * 45)
+    ob = np.repeat(ref_ob.reshape(-1, 4), 256 * 45, axis=0)[: n * 45]
+    assert frac_beyond_quanta(gu, ru, ob[:, 0], ob[:, 1], 255.0, 1.6) <= 1e-2
+    assert frac_beyond_quanta(gs, rs, ob[:, 2], ob[:, 3], 255.0, 1.6) <= 1e-2
+    return gv, rv
+
+
+@pytest.mark.parametrize("tag", ["l1", "l1_deg1"])
+def test_fused_backward_optimiser_level1_vs_reference(oracle, tag):
+    """The reference's fused kernel at quantisation level 1 (16-bit SH values and 8-bit SH optimiser state with one bound per 256
+    splats) against the oracle's chain: projection backward reading the codes, geometry and DC Adam, and the SH update on the
+    splat-block layout; degree 1 on the 15-coefficient buffers writes the idle bands as zero."""
+    run = FPBO_L1_RUNS[tag]
+    cfg, sp, vm, K = build_case(FPBO_SCENE)
+    base, gold = load(FPBO_SCENE), load("fpbo_l1")
+    n, deg = cfg.n_splats, run["degree"]
+    extra = fpbo_inputs(n)
+    v = {k: base[k] for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")}
+    five = ("means", "quats", "scales", "opacities", "features_dc")
+    p = {k: sp[k].copy() for k in five}
+    p["features_sh"] = np.zeros_like(sp["features_sh"])
+    m1 = {k: np.zeros_like(x) for k, x in p.items()}
+    m2 = {k: np.zeros_like(x) for k, x in p.items()}
+    vc, vb = encode_splat_blocks(sp["features_sh"].reshape(n, 45), 16)
+    oc, ob = np.zeros(n * 45 * 2, np.uint8), np.zeros(((n + 255) // 256) * 4, np.float32)
+    for step in (1, 2):
+        if step == 2:       # each pass from the reference's state of the pass before
+            for k in five:
+                p[k] = gold[f"{tag}_p1_{k}"].reshape(sp[k].shape).copy()
+            vc, vb = gold[f"{tag}_s1_value_codes"].copy(), gold[f"{tag}_s1_value_bounds"].copy()
+            oc, ob = gold[f"{tag}_s1_optim_codes"].copy(), gold[f"{tag}_s1_optim_bounds"].copy()
+        shq = dict(packed=vc, bounds=vb.reshape(-1), bits=16, bounds_stride=0)
+        g = oracle.project_bwd(p, vm, K, cfg.width, cfg.height, base["aabb"], v, shq=shq, sh_degree=deg)
+        steps = (extra["steps"] + (step - 1)).astype(np.int32) if run["steps"] else None
+        oracle.adam_geometry_ex(p, g, m1, m2, step, cfg.lrs, reg=run["reg"], scale_agnostic=bool(run["agnostic"]), radii=extra["radii"], steps=steps)
+        oracle.adam_plain(p["features_dc"], g["features_dc"], m1["features_dc"], m2["features_dc"], step, cfg.lrs["lr_features_dc"], run["sh_reg"],
+                          0.5 / 0.28209479177387814, 1.0, steps=steps, stride=3)
+        vb = vb.reshape(-1).copy()
+        oracle.adam_sh_splat_blocks(g["features_sh"].reshape(-1), oc, ob, vc, vb, 16, n, step, cfg.lrs["lr_features_sh"], l2_reg=run["sh_reg"],
+                                    sh_degree=deg, steps=steps)
+        for k in five:
+            assert frac_bad(p[k].reshape(-1), gold[f"{tag}_p{step}_{k}"], 5e-6, 1e-4) <= 2e-3, (tag, k, step)
+        gv, rv = splat_block_state_close(vc, vb.reshape(-1, 2), oc, ob, gold[f"{tag}_s{step}_value_codes"], gold[f"{tag}_s{step}_value_bounds"].reshape(-1, 2),
+                                         gold[f"{tag}_s{step}_optim_codes"], gold[f"{tag}_s{step}_optim_bounds"], n)
+        if deg < 3:
+            n_active = 3 * deg * (deg + 2)
+            span = (gold[f"{tag}_s{step}_value_bounds"].reshape(-1, 2)[:, 1] - gold[f"{tag}_s{step}_value_bounds"].reshape(-1, 2)[:, 0]).max()
+            assert np.abs(rv[:, n_active:]).max() <= span / 65535.0 and np.abs(gv[:, n_active:]).max() <= span / 65535.0     # idle bands: zero
+            assert np.abs(rv[:, :n_active]).max() > 0.01
+    for k in five:
         ref1, ref2 = gold[f"{tag}_g1_{k}"], gold[f"{tag}_g2_{k}"]
         assert frac_bad(m1[k].reshape(-1), ref1, 1e-4 * np.abs(ref1).max(), 2e-3) <= 5e-3, k
         assert frac_bad(m2[k].reshape(-1), ref2, 1e-4 * np.abs(ref2).max(), 4e-3) <= 5e-3, k

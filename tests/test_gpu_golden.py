@@ -13,7 +13,7 @@ torch = pytest.importorskip("torch")
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 
-from golden_cases import (DIST_CASES, FPBO_RUNS, FPBO_SCENE, dist_case_inputs, fpbo_inputs, ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
+from golden_cases import (DIST_CASES, FPBO_L1_RUNS, FPBO_RUNS, FPBO_SCENE, decode_splat_blocks, encode_splat_blocks, frac_beyond_quanta, joint_state_decode, dist_case_inputs, fpbo_inputs, ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
                           build_case, loss_inputs, loss_map_base, quant_sh_inputs, raster_cotangents)  # noqa: E402
 from spirula_studio_b200 import lib as L  # noqa: E402
 
@@ -218,6 +218,78 @@ def test_fused_backward_optimiser_vs_reference(lib, U, tag):
     s2 = L.splats_struct(p)
     assert lib.ssb_project_bwd_optimize(C.byref(s2), None, n, C.byref(cams), L.ptr(d_aabb), L.ptr(vrec), C.byref(a), C.byref(b), None, C.byref(acfg),
                                         C.byref(ex), L.ptr(ws), 16, None) == L.SSB_ERR_INVALID_ARGUMENT
+
+
+def _splat_block_state_close(got_vc, got_vb, got_oc, got_ob, ref_vc, ref_vb, ref_oc, ref_ob, n):
+    """SH value and state codes in the per-256-splats layout, compared as the numbers they stand for (a block's bounds come from
+    its extreme entries, so rounding moves codes without moving values)."""
+    assert np.allclose(got_vb, ref_vb, rtol=2e-3, atol=2e-5) and np.allclose(got_ob.reshape(-1, 4), ref_ob.reshape(-1, 4), rtol=2e-3, atol=2e-3)
+    gv, rv = decode_splat_blocks(got_vc, got_vb), decode_splat_blocks(ref_vc, ref_vb)
+    rb = np.repeat(ref_vb.reshape(-1, 2), 256, axis=0)[:n]
+    assert frac_beyond_quanta(gv, rv, rb[:, :1], rb[:, 1:], 65535.0, 3.0) <= 5e-3
+    (gu, gs), (ru, rs) = joint_state_decode(got_oc, got_ob, 256 * 45), joint_state_decode(ref_oc, ref_ob, 256 * 45)
+    ob = np.repeat(ref_ob.reshape(-1, 4), 256 * 45, axis=0)[: n * 45]
+    assert frac_beyond_quanta(gu, ru, ob[:, 0], ob[:, 1], 255.0, 1.6) <= 1e-2
+    assert frac_beyond_quanta(gs, rs, ob[:, 2], ob[:, 3], 255.0, 1.6) <= 1e-2
+    return gv, rv
+
+
+@pytest.mark.parametrize("tag", ["l1", "l1_deg1"])
+def test_fused_backward_optimiser_level1_vs_reference(lib, U, tag):
+    """ssb_project_bwd_optimize on the reference's level-1 layouts (16-bit SH values and 8-bit SH optimiser state with one bound per
+    256 splats, SsbShAdamState::layout = SSB_SH_LAYOUT_SPLAT_BLOCKS) against the reference's fused kernel at that level, two
+    passes, each from the reference's state of the pass before; SH degree 1 writes the idle bands as zero."""
+    run = FPBO_L1_RUNS[tag]
+    cfg, sp, vm, K = build_case(FPBO_SCENE)
+    base, gold = load(FPBO_SCENE), load("fpbo_l1")
+    I, n, W, H, deg = vm.shape[0], cfg.n_splats, cfg.width, cfg.height, run["degree"]
+    m = I * n
+    extra = fpbo_inputs(n)
+    five = ("means", "quats", "scales", "opacities", "features_dc")
+    d_vm, d_K, d_aabb = U.dev(vm), U.dev(K), U.dev(base["aabb"])
+    vrec = U.arrays_to_vrec({k: base[k].reshape(m, -1) if base[k].ndim > 1 else base[k] for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")}, m)
+    d_radii = U.dev(extra["radii"])
+    cams = L.cameras_struct(d_vm, d_K, W, H, sh_degree=deg)
+    ws = torch.zeros(int(lib.ssb_project_bwd_optimize_workspace_bytes(n)), dtype=torch.uint8, device=U.DEV)
+    lr = cfg.lrs
+    p = {k: U.dev(sp[k].reshape(-1)) for k in five}
+    m1 = {k: torch.zeros_like(t) for k, t in p.items()}
+    m2 = {k: torch.zeros_like(t) for k, t in p.items()}
+    vc0, vb0 = encode_splat_blocks(sp["features_sh"].reshape(n, 45), 16)
+    vc, vb = U.dev(vc0.view(np.uint8)), U.dev(vb0.reshape(-1))
+    oc, ob = torch.zeros(n * 45 * 2, dtype=torch.uint8, device=U.DEV), torch.zeros(((n + 255) // 256) * 4, device=U.DEV)
+    for step in (1, 2):
+        if step == 2:
+            p = {k: U.dev(gold[f"{tag}_p1_{k}"]) for k in five}
+            vc, vb = U.dev(gold[f"{tag}_s1_value_codes"].view(np.uint8)), U.dev(gold[f"{tag}_s1_value_bounds"].reshape(-1))
+            oc, ob = U.dev(gold[f"{tag}_s1_optim_codes"]), U.dev(gold[f"{tag}_s1_optim_bounds"].reshape(-1))
+        d_steps = U.dev((extra["steps"] + (step - 1)).astype(np.int32)) if run["steps"] else None
+        ex = L.SsbAdamExtras(*[float(x) for x in run["reg"]], run["agnostic"], d_radii.data_ptr(), d_steps.data_ptr() if d_steps is not None else None, n, None)
+        acfg = L.SsbAdamConfig(lr["lr_means"], lr["lr_quats"], lr["lr_scales"], lr["lr_opacities"], lr["lr_features_dc"], lr["lr_features_sh"],
+                               run["sh_reg"], 1.0, step, 0)
+        pd, ad, bd = dict(p, features_sh=None), dict(m1, features_sh=None), dict(m2, features_sh=None)
+        s, a, b = L.splats_struct(pd), L.splats_struct(ad), L.splats_struct(bd)
+        shq = L.shq_struct(vc, vb, 16, 0)
+        sh = L.SsbShAdamState(oc.data_ptr(), ob.data_ptr(), vc.data_ptr(), vb.data_ptr(), 16, 8, L.SH_LAYOUT_SPLAT_BLOCKS)
+        L.check(lib.ssb_project_bwd_optimize(C.byref(s), C.byref(shq), n, C.byref(cams), L.ptr(d_aabb), L.ptr(vrec), C.byref(a), C.byref(b), C.byref(sh),
+                                             C.byref(acfg), C.byref(ex), L.ptr(ws), ws.numel(), None))
+        torch.cuda.synchronize()
+        for k in five:
+            assert U.close_frac(p[k].cpu().numpy(), gold[f"{tag}_p{step}_{k}"], 5e-6, 1e-4) <= 2e-3, (tag, k, step)
+        gv, rv = _splat_block_state_close(vc.cpu().numpy().view(np.uint16), vb.cpu().numpy().reshape(-1, 2), oc.cpu().numpy(), ob.cpu().numpy(),
+                                          gold[f"{tag}_s{step}_value_codes"], gold[f"{tag}_s{step}_value_bounds"].reshape(-1, 2),
+                                          gold[f"{tag}_s{step}_optim_codes"], gold[f"{tag}_s{step}_optim_bounds"], n)
+        if deg < 3:
+            n_active = 3 * deg * (deg + 2)
+            vbr = gold[f"{tag}_s{step}_value_bounds"].reshape(-1, 2)
+            assert np.abs(gv[:, n_active:]).max() <= (vbr[:, 1] - vbr[:, 0]).max() / 65535.0
+    for k in five:
+        ref1, ref2 = gold[f"{tag}_g1_{k}"], gold[f"{tag}_g2_{k}"]
+        assert U.close_frac(m1[k].cpu().numpy(), ref1, 1e-4 * np.abs(ref1).max(), 2e-3) <= 5e-3, (tag, k)
+        assert U.close_frac(m2[k].cpu().numpy(), ref2, 1e-4 * np.abs(ref2).max(), 4e-3) <= 5e-3, (tag, k)
+    # a range must start on a block of 256 splats (nothing is launched)
+    assert lib.ssb_adam_step_sh_splat_blocks(L.ptr(ws), L.ptr(oc), L.ptr(ob), L.ptr(vc), L.ptr(vb), 16, 128, n - 128, n, 0, C.byref(acfg), None,
+                                             None) == L.SSB_ERR_INVALID_ARGUMENT
 
 
 @pytest.mark.parametrize("deg", [0, 1, 2])

@@ -730,6 +730,14 @@ int64_t ssb_project_bwd_optimize_workspace_bytes(int64_t n);
 int ssb_project_bwd_optimize(const SsbSplats* params, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
                              const SsbScreenRec* d_v_screen, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
                              const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* d_workspace, int64_t workspace_bytes, void* stream);
+/* The same with the moments of means, rotations, scales, opacities and DC in 16-bit codes (SsbMomentsQ16, see ssb_adam_step_q16):
+ * the reference's stock configuration of this kernel (quantisation level 1 with NonShQuantState::enabled).  m1 / m2 then only
+ * carry features_sh and may be NULL when sh_state is given.  The DC regulariser is the fused kernel's, 2 w / (3 n) with the dead
+ * zone (FusedProjectionBwdOptim_kernel.cuh:355-358, :1137), not the undivided w of the unfused kernel. */
+int ssb_project_bwd_optimize_q16(const SsbSplats* params, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
+                                 const SsbScreenRec* d_v_screen, const SsbMomentsQ16* moments, const SsbSplats* m1, const SsbSplats* m2,
+                                 const SsbShAdamState* sh_state, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* d_workspace,
+                                 int64_t workspace_bytes, void* stream);
 
 /* Projection backward of all views fused with the optimiser: the reference's use_fused_proj_bwd_optim path
  * (fused_projection_bwd_optimizer_3dgs_kernel, src/kernels/optim/FusedProjectionBwdOptim_kernel.cuh:146-1030: one
@@ -743,13 +751,19 @@ int ssb_project_bwd_optimize(const SsbSplats* params, const SsbShQuant* shq, int
  *     cameras of the kept views in the order they were given; n_views must equal their number.  m1 / m2 / cfg / extras
  *     as for ssb_adam_step_ex (cfg->zero_grad is ignored); sh_state != NULL runs the quantised SH update of
  *     ssb_adam_step_sh_quantized_ex on it (then params->features_sh, m1/m2->features_sh may be NULL), else SH is
- *     part of the plain update.  The state layouts are those of the unfused optimiser calls, so the two paths can be
- *     mixed from one iteration to the next; the reference keeps separate per-splat-block layouts for its fused path.
+ *     part of the plain update.  With sh_state->layout = SSB_SH_LAYOUT_CELL_BLOCKS the state layouts are those of the unfused
+ *     optimiser calls, so the two paths can be mixed from one iteration to the next; SSB_SH_LAYOUT_SPLAT_BLOCKS is the
+ *     layout the reference keeps for its fused path (ssb_adam_step_sh_splat_blocks; shq->bounds_stride is then 0).
+ *   ssb_step_backward_optimize_q16: the same with the moments of the five non-SH arrays in 16-bit codes
+ *     (ssb_project_bwd_optimize_q16).
  * The result equals ssb_step_views + ssb_adam_step_* up to the order of the floating-point sums over views. */
 int ssb_step_set_fused_backward(SsbStep* step, int32_t max_views);
 int ssb_step_backward_optimize(SsbStep* step, const SsbSplats* params, const SsbShQuant* shq, const float* d_viewmats, const float* d_intrins,
                                int32_t n_views, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state, const SsbAdamConfig* cfg,
                                const SsbAdamExtras* extras, void* stream);
+int ssb_step_backward_optimize_q16(SsbStep* step, const SsbSplats* params, const SsbShQuant* shq, const float* d_viewmats, const float* d_intrins,
+                                   int32_t n_views, const SsbMomentsQ16* moments, const SsbSplats* m1, const SsbSplats* m2,
+                                   const SsbShAdamState* sh_state, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream);
 
 /* Pair count M of the last view processed (host copy taken after that view's
  * kernels finished; synchronises the stream). */

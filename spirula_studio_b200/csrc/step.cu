@@ -422,9 +422,9 @@ namespace ssb {
 // One range of splats of the fused backward + optimiser pass: the projection backward of all views writes the range's 59
 // gradient floats per splat into `scratch` (which stays in L2), the optimiser kernels read them from there.
 static int fused_backward_range(const SsbSplats* params, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
-                                SsbScreenRec* d_v_screen, int clear_v_screen, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
-                                const SsbAdamConfig* c, const SsbAdamExtras* extras, float* scratch, int64_t range, int64_t first, int64_t count,
-                                void* stream) {
+                                SsbScreenRec* d_v_screen, int clear_v_screen, const SsbMomentsQ16* nq, const SsbSplats* m1, const SsbSplats* m2,
+                                const SsbShAdamState* sh_state, const SsbAdamConfig* c, const SsbAdamExtras* extras, float* scratch, int64_t range,
+                                int64_t first, int64_t count, void* stream) {
     // the range's gradient arrays, each on a 256-byte boundary
     float* g_means = scratch;
     float* g_quats = g_means + align_up(3 * range, 64);
@@ -439,9 +439,25 @@ static int fused_backward_range(const SsbSplats* params, const SsbShQuant* shq, 
     if (int e = launch_project_bwd(params, shq, n, cams, d_aabb, d_v_screen, &g, 0, clear_v_screen, stream, nullptr, first, count)) return e;
     SsbSplats ga = g;
     if (sh_state) ga.features_sh = nullptr;      // the SH update is the quantised one below
-    SsbSplats p = *params, a1 = *m1, a2 = *m2;
-    if (sh_state) { p.features_sh = nullptr; a1.features_sh = nullptr; a2.features_sh = nullptr; }
-    if (int e = ssb_adam_step_ex(&p, &ga, &a1, &a2, first, count, c, extras, stream)) return e;
+    if (nq) {
+        // Moments of the five non-SH arrays in 16-bit codes.  The fused kernel of the reference scales the DC regulariser like the
+        // SH one, 2 w / (3 n) (src/kernels/optim/FusedProjectionBwdOptim_kernel.cuh:1137, :355-358), where its unfused kernel with
+        // these moments takes w as it is; ssb_adam_step_q16 follows the unfused kernel, so the scaled weight is handed to it.
+        SsbAdamConfig cq = *c;
+        cq.sh_reg_weight = 2.0f * c->sh_reg_weight / (float)(3 * n);
+        if (int e = ssb_adam_step_q16(params, &ga, nq, first, count, &cq, extras, stream)) return e;
+        if (!sh_state) {
+            // fp32 SH: fused_adam_step's decay is 2 l2 / numel of the call, so l2 is scaled to the range's share of the array
+            const int64_t off = 45 * first, numel = 45 * count;
+            if (int e = ssb_adam_plain(params->features_sh + off, g.features_sh + off, m1->features_sh + off, m2->features_sh + off, numel, 45,
+                                       c->lr_features_sh, c->step, extras && extras->d_steps ? extras->d_steps + first : nullptr,
+                                       c->sh_reg_weight * (float)count / (float)n, 0.0f, c->grad_scale, 0, stream)) return e;
+        }
+    } else {
+        SsbSplats p = *params, a1 = *m1, a2 = *m2;
+        if (sh_state) { p.features_sh = nullptr; a1.features_sh = nullptr; a2.features_sh = nullptr; }
+        if (int e = ssb_adam_step_ex(&p, &ga, &a1, &a2, first, count, c, extras, stream)) return e;
+    }
     if (sh_state && sh_state->layout == SSB_SH_LAYOUT_SPLAT_BLOCKS) {
         // the reference's own layout for this path: bounds per 256 splats; a range is a whole number of such blocks
         if (int e = ssb_adam_step_sh_splat_blocks(g.features_sh, sh_state->d_optim_packed, sh_state->d_optim_bounds, sh_state->d_value_packed,
@@ -464,11 +480,14 @@ extern "C" {
 
 int64_t ssb_project_bwd_optimize_workspace_bytes(int64_t n) { return n < 0 ? SSB_ERR_INVALID_ARGUMENT : ssb::fused_scratch_floats(n) * (int64_t)sizeof(float); }
 
-int ssb_project_bwd_optimize(const SsbSplats* params, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
-                             const SsbScreenRec* d_v_screen, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
-                             const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* d_workspace, int64_t workspace_bytes, void* stream) {
+static int project_bwd_optimize_impl(const SsbSplats* params, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
+                                     const SsbScreenRec* d_v_screen, const SsbMomentsQ16* nq, const SsbSplats* m1, const SsbSplats* m2,
+                                     const SsbShAdamState* sh_state, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* d_workspace,
+                                     int64_t workspace_bytes, void* stream) {
     using namespace ssb;
-    SSB_REQUIRE(params && cams && d_aabb && d_v_screen && m1 && m2 && cfg && d_workspace, "ssb_project_bwd_optimize: NULL argument");
+    SSB_REQUIRE(params && cams && d_aabb && d_v_screen && cfg && d_workspace, "ssb_project_bwd_optimize: NULL argument");
+    SSB_REQUIRE(nq ? (sh_state || (m1 && m2 && m1->features_sh && m2->features_sh)) : (m1 && m2),
+                "ssb_project_bwd_optimize: moments missing (with 16-bit moments m1 / m2 carry features_sh, unless the SH state is quantised)");
     SSB_REQUIRE(n >= 0 && cams->count >= 0, "ssb_project_bwd_optimize: bad sizes");
     SSB_REQUIRE(workspace_bytes >= ssb_project_bwd_optimize_workspace_bytes(n), "ssb_project_bwd_optimize: workspace too small");
     SSB_REQUIRE(((uintptr_t)d_workspace & 255) == 0, "ssb_project_bwd_optimize: the workspace must be 256-byte aligned");
@@ -479,17 +498,34 @@ int ssb_project_bwd_optimize(const SsbSplats* params, const SsbShQuant* shq, int
     c.zero_grad = 0;
     const int64_t range = std::min(kFusedRange, align_up(n, 256));
     for (int64_t first = 0; first < n; first += range) {
-        if (int e = fused_backward_range(params, shq, n, cams, d_aabb, const_cast<SsbScreenRec*>(d_v_screen), 0, m1, m2, sh_state, &c, extras,
+        if (int e = fused_backward_range(params, shq, n, cams, d_aabb, const_cast<SsbScreenRec*>(d_v_screen), 0, nq, m1, m2, sh_state, &c, extras,
                                          (float*)d_workspace, range, first, std::min(range, n - first), stream)) return e;
     }
     return SSB_OK;
 }
 
-int ssb_step_backward_optimize(SsbStep* s, const SsbSplats* params, const SsbShQuant* shq, const float* d_viewmats, const float* d_intrins,
-                               int32_t n_views, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state, const SsbAdamConfig* cfg,
-                               const SsbAdamExtras* extras, void* stream) {
+int ssb_project_bwd_optimize(const SsbSplats* params, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
+                             const SsbScreenRec* d_v_screen, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                             const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* d_workspace, int64_t workspace_bytes, void* stream) {
+    return project_bwd_optimize_impl(params, shq, n, cams, d_aabb, d_v_screen, nullptr, m1, m2, sh_state, cfg, extras, d_workspace, workspace_bytes, stream);
+}
+
+int ssb_project_bwd_optimize_q16(const SsbSplats* params, const SsbShQuant* shq, int64_t n, const SsbCameras* cams, const float* d_aabb,
+                                 const SsbScreenRec* d_v_screen, const SsbMomentsQ16* moments, const SsbSplats* m1, const SsbSplats* m2,
+                                 const SsbShAdamState* sh_state, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* d_workspace,
+                                 int64_t workspace_bytes, void* stream) {
     using namespace ssb;
-    SSB_REQUIRE(s && params && d_viewmats && d_intrins && m1 && m2 && cfg, "ssb_step_backward_optimize: NULL argument");
+    SSB_REQUIRE(moments, "ssb_project_bwd_optimize_q16: NULL moments");
+    return project_bwd_optimize_impl(params, shq, n, cams, d_aabb, d_v_screen, moments, m1, m2, sh_state, cfg, extras, d_workspace, workspace_bytes, stream);
+}
+
+static int step_backward_optimize_impl(SsbStep* s, const SsbSplats* params, const SsbShQuant* shq, const float* d_viewmats, const float* d_intrins,
+                                       int32_t n_views, const SsbMomentsQ16* nq, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state,
+                                       const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(s && params && d_viewmats && d_intrins && cfg, "ssb_step_backward_optimize: NULL argument");
+    SSB_REQUIRE(nq ? (sh_state || (m1 && m2 && m1->features_sh && m2->features_sh)) : (m1 && m2),
+                "ssb_step_backward_optimize: moments missing (with 16-bit moments m1 / m2 carry features_sh, unless the SH state is quantised)");
     SSB_REQUIRE(s->def_max_views > 0, "ssb_step_backward_optimize: the step does not keep its views (ssb_step_set_fused_backward)");
     SSB_REQUIRE(n_views == s->def_count && n_views <= s->def_max_views, "ssb_step_backward_optimize: %d views given, %d kept (room for %d)", n_views,
                 s->def_count, s->def_max_views);
@@ -516,7 +552,7 @@ int ssb_step_backward_optimize(SsbStep* s, const SsbSplats* params, const SsbShQ
     for (int64_t first = 0; first < n; first += range, ++turn) {
         void* range_stream = two ? (void*)s->lane[turn % s->n_lanes].stream : (void*)user;
         float* scratch = s->def_grads + (two ? turn % s->n_lanes : 0) * scratch_floats;
-        if (int e = fused_backward_range(params, shq, n, &cams, s->def_aabb, s->def_vscreen, 1, m1, m2, sh_state, &c, extras, scratch, range, first,
+        if (int e = fused_backward_range(params, shq, n, &cams, s->def_aabb, s->def_vscreen, 1, nq, m1, m2, sh_state, &c, extras, scratch, range, first,
                                          std::min(range, n - first), range_stream)) return e;
     }
     if (two)
@@ -525,6 +561,20 @@ int ssb_step_backward_optimize(SsbStep* s, const SsbSplats* params, const SsbShQ
             SSB_CUDA(cudaStreamWaitEvent(user, s->lane[k].all_done, 0));
         }
     return SSB_OK;
+}
+
+int ssb_step_backward_optimize(SsbStep* s, const SsbSplats* params, const SsbShQuant* shq, const float* d_viewmats, const float* d_intrins,
+                               int32_t n_views, const SsbSplats* m1, const SsbSplats* m2, const SsbShAdamState* sh_state, const SsbAdamConfig* cfg,
+                               const SsbAdamExtras* extras, void* stream) {
+    return step_backward_optimize_impl(s, params, shq, d_viewmats, d_intrins, n_views, nullptr, m1, m2, sh_state, cfg, extras, stream);
+}
+
+int ssb_step_backward_optimize_q16(SsbStep* s, const SsbSplats* params, const SsbShQuant* shq, const float* d_viewmats, const float* d_intrins,
+                                   int32_t n_views, const SsbMomentsQ16* moments, const SsbSplats* m1, const SsbSplats* m2,
+                                   const SsbShAdamState* sh_state, const SsbAdamConfig* cfg, const SsbAdamExtras* extras, void* stream) {
+    using namespace ssb;
+    SSB_REQUIRE(moments, "ssb_step_backward_optimize_q16: NULL moments");
+    return step_backward_optimize_impl(s, params, shq, d_viewmats, d_intrins, n_views, moments, m1, m2, sh_state, cfg, extras, stream);
 }
 
 int ssb_step_set_profiling(SsbStep* s, int enable) {

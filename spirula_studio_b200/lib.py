@@ -146,11 +146,13 @@ SIGNATURES = {
     "ssb_step_render": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ssb_project_bwd_optimize_workspace_bytes": (C.c_int64, [_I64]),
     "ssb_project_bwd_optimize": (C.c_int, [_P, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _P]),
+    "ssb_project_bwd_optimize_q16": (C.c_int, [_P, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _P]),
     "ssb_ply_write": (C.c_int, [C.c_char_p, _P, _P, _I64, _P, _P]),
     "ssb_ply_info": (C.c_int, [C.c_char_p, _P, _P]),
     "ssb_ply_read": (C.c_int, [C.c_char_p, _I64, _I32, _P, _P, _P, _P, _P, _P]),
     "ssb_step_set_fused_backward": (C.c_int, [_P, _I32]),
     "ssb_step_backward_optimize": (C.c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _P]),
+    "ssb_step_backward_optimize_q16": (C.c_int, [_P, _P, _P, _P, _P, _I32, _P, _P, _P, _P, _P, _P, _P]),
     "ssb_adam_step_q16": (C.c_int, [_P, _P, _P, _I64, _I64, _P, _P, _P]),
     "ssb_adam_plain": (C.c_int, [_P, _P, _P, _P, _I64, _I32, _F, _I32, _P, _F, _F, _F, _I32, _P]),
     "ssb_adam_step": (C.c_int, [_P, _P, _P, _P, _I64, _I64, _P, _P]),

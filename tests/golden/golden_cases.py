@@ -170,6 +170,26 @@ def frac_beyond_quanta(a, b, ref_lo, ref_hi, levels, quanta):
     return float((np.abs(a.astype(np.float64) - b.astype(np.float64)) > quanta * step + 1e-12).mean())
 
 
+def q16_moments_mismatch(have_packed, have_bounds, ref_packed, ref_bounds, n, width):
+    """Fraction of cells of two 16-bit joint moment arrays (QuantizedAdamState<16, 256> with one float4 of bounds per 256 splats)
+    that agree neither as moments (|d| <= 1e-4 max + 2e-3 |ref| for g1, 4e-3 for g2) nor as codes (u and log-s within three steps
+    of the reference's grid).  Two implementations sum a splat's gradient in different orders: where the grid is fine (u = +-3.16
+    on the first step) that moves a code by a few steps but not the moment; where it is coarse (a wide u range) it moves the
+    moment by a whole step but the code by at most one."""
+    def coords(packed, bounds):
+        c = np.asarray(packed).view(np.uint16).reshape(n * width, 2).astype(np.float64) / 65535.0
+        mm = np.repeat(np.asarray(bounds, np.float64).reshape(-1, 4), 256 * width, axis=0)[: n * width]
+        return mm[:, 0] + (mm[:, 1] - mm[:, 0]) * c[:, 0], mm[:, 2] + (mm[:, 3] - mm[:, 2]) * c[:, 1], mm
+    hu, hs, _ = coords(have_packed, have_bounds)
+    ru, rs, mm = coords(ref_packed, ref_bounds)
+    eps = 1e-15
+    hq, rq = eps * np.expm1(hs), eps * np.expm1(rs)
+    h1, r1, h2, r2 = hu * (hq + eps), ru * (rq + eps), hq * hq, rq * rq
+    as_moments = (np.abs(h1 - r1) <= 1e-4 * np.abs(r1).max() + 2e-3 * np.abs(r1)) & (np.abs(h2 - r2) <= 1e-4 * np.abs(r2).max() + 4e-3 * np.abs(r2))
+    as_codes = (np.abs(hu - ru) <= 3.0 * (mm[:, 1] - mm[:, 0]) / 65535.0 + 1e-12) & (np.abs(hs - rs) <= 3.0 * (mm[:, 3] - mm[:, 2]) / 65535.0 + 1e-12)
+    return float((~(as_moments | as_codes)).mean())
+
+
 ACCUM_CASES = ("ring2", "dense1")
 
 # Quantised SH storage read by the projection (forward and backward): 8- or 16-bit codes with (min, max) bounds

@@ -15,7 +15,7 @@ import pytest
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 
-from golden_cases import (DIST_CASES, FPBO_L1_RUNS, FPBO_RUNS, FPBO_SCENE, decode_splat_blocks, encode_splat_blocks, frac_beyond_quanta, joint_state_decode, dist_case_inputs, fpbo_inputs, ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
+from golden_cases import (DIST_CASES, FPBO_L1_RUNS, FPBO_RUNS, FPBO_SCENE, decode_splat_blocks, encode_splat_blocks, frac_beyond_quanta, joint_state_decode, q16_moments_mismatch, dist_case_inputs, fpbo_inputs, ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
                           build_case, loss_inputs, loss_map_base, quant_sh_inputs, raster_cotangents)  # noqa: E402
 
 
@@ -420,6 +420,45 @@ def q16_code_diff(have, want):
     """Largest difference and fraction of differing 16-bit codes of two packed moment arrays."""
     d = np.abs(np.asarray(have).view(np.uint16).astype(np.int64) - np.asarray(want).view(np.uint16).astype(np.int64))
     return d.max(), (d > 0).mean()
+
+
+def test_fused_backward_optimiser_level1_q16_moments_vs_reference(oracle):
+    """The reference's stock configuration of its fused kernel: level 1 with the moments of the five non-SH arrays in 16-bit codes.
+    The DC regulariser is scaled like the SH one (2 w / (3 n)) in this kernel, not taken undivided as in the unfused one."""
+    tag = "l1_nq"
+    run = FPBO_L1_RUNS[tag]
+    cfg, sp, vm, K = build_case(FPBO_SCENE)
+    base, gold = load(FPBO_SCENE), load("fpbo_l1")
+    n = cfg.n_splats
+    blocks = (n + 255) // 256
+    extra = fpbo_inputs(n)
+    v = {k: base[k] for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")}
+    widths = dict(oracle.Q16_ATTRS)
+    p = {k: sp[k].copy() for k in Q16_ORDER}
+    p["features_sh"] = np.zeros_like(sp["features_sh"])
+    q = {k: (np.zeros(n * widths[k] * 4, np.uint8), np.zeros(blocks * 4, np.float32)) for k in Q16_ORDER}
+    vc, vb = encode_splat_blocks(sp["features_sh"].reshape(n, 45), 16)
+    oc, ob = np.zeros(n * 45 * 2, np.uint8), np.zeros(blocks * 4, np.float32)
+    for step in (1, 2):
+        if step == 2:
+            for k in Q16_ORDER:
+                p[k] = gold[f"{tag}_p1_{k}"].reshape(sp[k].shape).copy()
+                q[k] = (gold[f"{tag}_s1_nq_{k}"].copy(), gold[f"{tag}_s1_nqb_{k}"].copy())
+            vc, vb = gold[f"{tag}_s1_value_codes"].copy(), gold[f"{tag}_s1_value_bounds"].copy()
+            oc, ob = gold[f"{tag}_s1_optim_codes"].copy(), gold[f"{tag}_s1_optim_bounds"].copy()
+        shq = dict(packed=vc, bounds=vb.reshape(-1), bits=16, bounds_stride=0)
+        g = oracle.project_bwd(p, vm, K, cfg.width, cfg.height, base["aabb"], v, shq=shq)
+        steps = (extra["steps"] + (step - 1)).astype(np.int32)
+        oracle.adam_geometry_q16(p, g, q, step, cfg.lrs, sh_reg_weight=2.0 * run["sh_reg"] / (3 * n), reg=run["reg"], scale_agnostic=True,
+                                 radii=extra["radii"], steps=steps)
+        vb = vb.reshape(-1).copy()
+        oracle.adam_sh_splat_blocks(g["features_sh"].reshape(-1), oc, ob, vc, vb, 16, n, step, cfg.lrs["lr_features_sh"], l2_reg=run["sh_reg"], steps=steps)
+        for k in Q16_ORDER:
+            assert frac_bad(p[k].reshape(-1), gold[f"{tag}_p{step}_{k}"], 5e-6, 1e-4) <= 2e-3, (k, step)
+            # the codes as the moments they stand for: the 16-bit grid is finer than the agreement of two gradient sums
+            assert q16_moments_mismatch(q[k][0], q[k][1], gold[f"{tag}_s{step}_nq_{k}"], gold[f"{tag}_s{step}_nqb_{k}"], n, widths[k]) <= 5e-3, (k, step)
+        splat_block_state_close(vc, vb.reshape(-1, 2), oc, ob, gold[f"{tag}_s{step}_value_codes"], gold[f"{tag}_s{step}_value_bounds"].reshape(-1, 2),
+                                gold[f"{tag}_s{step}_optim_codes"], gold[f"{tag}_s{step}_optim_bounds"], n)
 
 
 def test_adam_16bit_non_sh_moments_vs_reference(oracle):

@@ -13,7 +13,7 @@ torch = pytest.importorskip("torch")
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "golden"))
 
-from golden_cases import (DIST_CASES, FPBO_L1_RUNS, FPBO_RUNS, FPBO_SCENE, decode_splat_blocks, encode_splat_blocks, frac_beyond_quanta, joint_state_decode, dist_case_inputs, fpbo_inputs, ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
+from golden_cases import (DIST_CASES, FPBO_L1_RUNS, FPBO_RUNS, FPBO_SCENE, decode_splat_blocks, encode_splat_blocks, frac_beyond_quanta, joint_state_decode, q16_moments_mismatch, dist_case_inputs, fpbo_inputs, ACCUM_CASES, CASES, LOSS_MAP_WEIGHT, QUANT_CASES, QUANT_SCENE, WIDE_CASES, accum_weight_map, adam_inputs,  # noqa: E402
                           build_case, loss_inputs, loss_map_base, quant_sh_inputs, raster_cotangents)  # noqa: E402
 from spirula_studio_b200 import lib as L  # noqa: E402
 
@@ -290,6 +290,59 @@ def test_fused_backward_optimiser_level1_vs_reference(lib, U, tag):
     # a range must start on a block of 256 splats (nothing is launched)
     assert lib.ssb_adam_step_sh_splat_blocks(L.ptr(ws), L.ptr(oc), L.ptr(ob), L.ptr(vc), L.ptr(vb), 16, 128, n - 128, n, 0, C.byref(acfg), None,
                                              None) == L.SSB_ERR_INVALID_ARGUMENT
+
+
+def test_fused_backward_optimiser_level1_q16_moments_vs_reference(lib, U, oracle):
+    """ssb_project_bwd_optimize_q16 on the reference's stock layouts (level 1 and the moments of the five non-SH arrays in 16-bit
+    codes) against the reference's fused kernel in that configuration, two passes, each from the reference's state."""
+    tag = "l1_nq"
+    run = FPBO_L1_RUNS[tag]
+    cfg, sp, vm, K = build_case(FPBO_SCENE)
+    base, gold = load(FPBO_SCENE), load("fpbo_l1")
+    I, n, W, H = vm.shape[0], cfg.n_splats, cfg.width, cfg.height
+    m, blocks = I * n, (n + 255) // 256
+    extra = fpbo_inputs(n)
+    five = ("means", "quats", "scales", "opacities", "features_dc")
+    widths = dict(oracle.Q16_ATTRS)
+    d_vm, d_K, d_aabb = U.dev(vm), U.dev(K), U.dev(base["aabb"])
+    vrec = U.arrays_to_vrec({k: base[k].reshape(m, -1) if base[k].ndim > 1 else base[k] for k in ("v_xy", "v_depth", "v_conic", "v_opac", "v_rgb")}, m)
+    d_radii = U.dev(extra["radii"])
+    cams = L.cameras_struct(d_vm, d_K, W, H)
+    ws = torch.zeros(int(lib.ssb_project_bwd_optimize_workspace_bytes(n)), dtype=torch.uint8, device=U.DEV)
+    lr = cfg.lrs
+    p = {k: U.dev(sp[k].reshape(-1)) for k in five}
+    nq_p = {k: torch.zeros(n * widths[k] * 4, dtype=torch.uint8, device=U.DEV) for k in five}
+    nq_b = {k: torch.zeros(blocks * 4, device=U.DEV) for k in five}
+    vc0, vb0 = encode_splat_blocks(sp["features_sh"].reshape(n, 45), 16)
+    vc, vb = U.dev(vc0.view(np.uint8)), U.dev(vb0.reshape(-1))
+    oc, ob = torch.zeros(n * 45 * 2, dtype=torch.uint8, device=U.DEV), torch.zeros(blocks * 4, device=U.DEV)
+    for step in (1, 2):
+        if step == 2:
+            p = {k: U.dev(gold[f"{tag}_p1_{k}"]) for k in five}
+            nq_p = {k: U.dev(gold[f"{tag}_s1_nq_{k}"]) for k in five}
+            nq_b = {k: U.dev(gold[f"{tag}_s1_nqb_{k}"]) for k in five}
+            vc, vb = U.dev(gold[f"{tag}_s1_value_codes"].view(np.uint8)), U.dev(gold[f"{tag}_s1_value_bounds"].reshape(-1))
+            oc, ob = U.dev(gold[f"{tag}_s1_optim_codes"]), U.dev(gold[f"{tag}_s1_optim_bounds"].reshape(-1))
+        d_steps = U.dev((extra["steps"] + (step - 1)).astype(np.int32))
+        ex = L.SsbAdamExtras(*[float(x) for x in run["reg"]], 1, d_radii.data_ptr(), d_steps.data_ptr(), n, None)
+        acfg = L.SsbAdamConfig(lr["lr_means"], lr["lr_quats"], lr["lr_scales"], lr["lr_opacities"], lr["lr_features_dc"], lr["lr_features_sh"],
+                               run["sh_reg"], 1.0, step, 0)
+        s = L.splats_struct(dict(p, features_sh=None))
+        mom = L.SsbMomentsQ16()
+        for t, k in enumerate(five):
+            mom.d_packed[t], mom.d_bounds[t] = nq_p[k].data_ptr(), nq_b[k].data_ptr()
+        shq = L.shq_struct(vc, vb, 16, 0)
+        sh = L.SsbShAdamState(oc.data_ptr(), ob.data_ptr(), vc.data_ptr(), vb.data_ptr(), 16, 8, L.SH_LAYOUT_SPLAT_BLOCKS)
+        L.check(lib.ssb_project_bwd_optimize_q16(C.byref(s), C.byref(shq), n, C.byref(cams), L.ptr(d_aabb), L.ptr(vrec), C.byref(mom), None, None,
+                                                 C.byref(sh), C.byref(acfg), C.byref(ex), L.ptr(ws), ws.numel(), None))
+        torch.cuda.synchronize()
+        for k in five:
+            assert U.close_frac(p[k].cpu().numpy(), gold[f"{tag}_p{step}_{k}"], 5e-6, 1e-4) <= 2e-3, (k, step)
+            assert q16_moments_mismatch(nq_p[k].cpu().numpy(), nq_b[k].cpu().numpy(), gold[f"{tag}_s{step}_nq_{k}"], gold[f"{tag}_s{step}_nqb_{k}"], n,
+                                        widths[k]) <= 5e-3, (k, step)
+        _splat_block_state_close(vc.cpu().numpy().view(np.uint16), vb.cpu().numpy().reshape(-1, 2), oc.cpu().numpy(), ob.cpu().numpy(),
+                                 gold[f"{tag}_s{step}_value_codes"], gold[f"{tag}_s{step}_value_bounds"].reshape(-1, 2),
+                                 gold[f"{tag}_s{step}_optim_codes"], gold[f"{tag}_s{step}_optim_bounds"], n)
 
 
 @pytest.mark.parametrize("deg", [0, 1, 2])

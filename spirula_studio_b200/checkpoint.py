@@ -14,6 +14,9 @@ table's order:
     eng.<attr>_qfpbo.q / .qb                             16-bit joint moments of the five non-SH arrays
     eng.sh_quant.q / .qb                                 8-bit joint SH optimiser state: packed bytes / float bounds
     eng.world.sh_vq8|16.q / .qb                          quantised SH values: packed bytes / float bounds
+    eng.sh_quant_fpbo.*, eng.world.sh_vq8|16_fpbo.*      the same two with one bound per 256 splats: the layout of the reference's
+                                                         fused backward + optimiser (Trainer fused_state_layout="reference";
+                                                         state.json use_fused_proj_bwd_optim = 1)
     eng.radii, eng.accum_buffer                          with a Densifier: the view radii and the strategy's score
                                                          accumulator; state.json's cur_num_splats is then the number
                                                          of splats in use, and splat.ply holds those
@@ -57,7 +60,7 @@ def state_json(trainer, step, full=True, cur_num_splats=None):
         f'  "sh_optim_bits": {sh_optim_bits}',
         f'  "sh_value_bits": {cfg.sh_value_bits if trainer.quant else 32}',
         f'  "non_sh_optim_bits": {trainer.non_sh_optim_bits}',
-        '  "use_fused_proj_bwd_optim": 0',
+        f'  "use_fused_proj_bwd_optim": {1 if getattr(trainer, "fused_state_layout", "shared") == "reference" else 0}',
         f'  "use_per_splat_bias_correction": {1 if getattr(trainer, "steps", None) is not None else 0}',
         f'  "camera": {{"num": {cfg.n_views}, "width": {cfg.width}, "height": {cfg.height}, '
         f'"model": "{_MODEL_NAMES.get(cfg.camera_model, "PINHOLE")}"}}',
@@ -85,8 +88,10 @@ def saved_buffers(trainer, densifier=None):
         for a in _GEO:
             out += [(f"eng.{a}_qfpbo.q", trainer.nsq_packed[a], DTYPE_U1), (f"eng.{a}_qfpbo.qb", trainer.nsq_bounds[a], DTYPE_F4)]
     if trainer.quant:
-        vq = f"eng.world.sh_vq{trainer.cfg.sh_value_bits}"
-        out += [("eng.sh_quant.q", trainer.sh_optim_packed, DTYPE_U1), ("eng.sh_quant.qb", trainer.sh_optim_bounds, DTYPE_F4),
+        # the reference keeps the per-256-splats layout of its fused path under slots of its own (src/core/PoolSlots.h:114-120)
+        fpbo = "_fpbo" if getattr(trainer, "fused_state_layout", "shared") == "reference" else ""
+        vq = f"eng.world.sh_vq{trainer.cfg.sh_value_bits}{fpbo}"
+        out += [(f"eng.sh_quant{fpbo}.q", trainer.sh_optim_packed, DTYPE_U1), (f"eng.sh_quant{fpbo}.qb", trainer.sh_optim_bounds, DTYPE_F4),
                 (vq + ".q", trainer.sh_packed, DTYPE_U1), (vq + ".qb", trainer.sh_bounds, DTYPE_F4)]
     radii = densifier.radii if densifier is not None else getattr(trainer, "radii", None)
     if radii is not None:
@@ -199,7 +204,7 @@ def load_checkpoint(trainer, input_dir, densifier=None):
             raise RuntimeError(f"load_checkpoint: max_num_splats mismatch (trainer {trainer.n} vs checkpoint "
                                f"{_json_value(text, 'max_num_splats', 0)})")
         want = (8 if trainer.quant else 32, trainer.cfg.sh_value_bits if trainer.quant else 32, trainer.non_sh_optim_bits,
-                1 if getattr(trainer, "steps", None) is not None else 0, 0)
+                1 if getattr(trainer, "steps", None) is not None else 0, 1 if getattr(trainer, "fused_state_layout", "shared") == "reference" else 0)
         have = tuple(_json_value(text, k, d) for k, d in (("sh_optim_bits", 32), ("sh_value_bits", 32), ("non_sh_optim_bits", 32),
                                                           ("use_per_splat_bias_correction", 0), ("use_fused_proj_bwd_optim", 0)))
         if want != have:

@@ -75,7 +75,8 @@ class OptimOptions:
 
 class Trainer:
     def __init__(self, cfg: SceneConfig, splats: dict, device="cuda:0", isect_capacity=0, w_l1=0.8, w_ssim=0.2,
-                 process_group=None, world_size=1, rank=0, grad_sync="peer", fused_backward=False, non_sh_optim_bits=32, optim=None):
+                 process_group=None, world_size=1, rank=0, grad_sync="peer", fused_backward=False, non_sh_optim_bits=32, optim=None,
+                 fused_state_layout="shared"):
         self.lib = L.load()
         self.cfg = cfg
         self.device = torch.device(device)
@@ -113,15 +114,31 @@ class Trainer:
         self.non_sh_optim_bits = non_sh_optim_bits
         self.nsq_packed, self.nsq_bounds, self._nsq = {}, {}, None
         if non_sh_optim_bits == 16:
-            if fused_backward:
-                raise NotImplementedError("16-bit non-SH moments run with the per-view backward")
             self._nsq = L.SsbMomentsQ16()
             for t, (name, width) in enumerate(_ATTRS[:5]):
                 self.nsq_packed[name] = torch.zeros(n * width * 4, dtype=torch.uint8, device=dev)
                 self.nsq_bounds[name] = torch.zeros(((n + 255) // 256) * 4, dtype=torch.float32, device=dev)
                 self._nsq.d_packed[t], self._nsq.d_bounds[t] = self.nsq_packed[name].data_ptr(), self.nsq_bounds[name].data_ptr()
+        # Where the quantised SH buffers keep their bounds.  "shared": one per 256 cells, the layout of the unfused optimiser calls
+        # (the fused backward + optimiser then shares it with them).  "reference": one per 256 splats, the layout the reference
+        # keeps for its fused path (pool slots eng.sh_quant_fpbo, eng.world.sh_vq16_fpbo; state.json use_fused_proj_bwd_optim = 1),
+        # so that its stock checkpoints load and resume; only the fused backward + optimiser updates it.
+        if fused_state_layout not in ("shared", "reference"):
+            raise ValueError(f"fused_state_layout must be 'shared' or 'reference', not {fused_state_layout!r}")
+        self.fused_state_layout = fused_state_layout
+        if fused_state_layout == "reference" and not (self.quant and fused_backward and world_size == 1 and n_view_kinds(cfg) == 1):
+            raise ValueError("fused_state_layout='reference' needs quantised SH and the fused backward + optimiser (one GPU, one camera kind)")
         self.shq = None
-        if self.quant:
+        if self.quant and fused_state_layout == "reference":
+            cells, blocks = n * 45, (n + 255) // 256
+            bytes_per = 2 if cfg.sh_value_bits == 16 else 1
+            self.sh_packed = torch.zeros(cells * bytes_per, dtype=torch.uint8, device=dev)
+            self.sh_bounds = torch.zeros(blocks * 2, dtype=torch.float32, device=dev)
+            self.sh_optim_packed = torch.zeros(cells * 2, dtype=torch.uint8, device=dev)
+            self.sh_optim_bounds = torch.zeros(blocks * 4, dtype=torch.float32, device=dev)
+            self._encode_splat_blocks(self.params["features_sh"], cfg.sh_value_bits)
+            self.shq = L.shq_struct(self.sh_packed, self.sh_bounds, cfg.sh_value_bits, 0)
+        elif self.quant:
             cells = n * 45
             blocks = (cells + 255) // 256
             bytes_per = 2 if cfg.sh_value_bits == 16 else 1
@@ -164,8 +181,6 @@ class Trainer:
         self._extras = None
         self._radii_external = False         # a Densifier clears the radii itself (before_step)
         if optim is not None:
-            if self.fused_backward:
-                raise NotImplementedError("the optimiser options run with the per-view backward")
             if optim.use_scale_agnostic_mean:
                 self.radii = torch.zeros(n, dtype=torch.float32, device=dev)
                 for h in self.handles:
@@ -180,6 +195,25 @@ class Trainer:
         self.first, self.count = 0, n
         if self.grad_sync in ("peer", "multimem"):
             self._setup_peers()
+
+    def _encode_splat_blocks(self, values, bits):
+        """Initial SH values -> codes with one (min, max) bound per 256 splats (QuantizedTensor<bits>::encode_v of the reference,
+        src/core/Tensor.h:1379-1392, on its per-splat-block layout); runs once, at construction."""
+        n, blocks = self.n, (self.n + 255) // 256
+        v = values.view(n, 45)
+        block_of = torch.arange(n, device=v.device) // 256
+        lo = torch.full((blocks,), float("inf"), device=v.device).scatter_reduce_(0, block_of, v.amin(dim=1), "amin")
+        hi = torch.full((blocks,), float("-inf"), device=v.device).scatter_reduce_(0, block_of, v.amax(dim=1), "amax")
+        qmax = float((1 << bits) - 1)
+        span = (hi - lo).clamp_min(1e-30)
+        codes = torch.round(qmax * (v - lo[block_of, None]) / span[block_of, None]).clamp_(0, qmax).to(torch.int32).reshape(-1)
+        if bits == 16:
+            self.sh_packed.view(-1, 2)[:, 0] = (codes & 255).to(torch.uint8)
+            self.sh_packed.view(-1, 2)[:, 1] = (codes >> 8).to(torch.uint8)
+        else:
+            self.sh_packed.copy_(codes.to(torch.uint8))
+        self.sh_bounds.view(blocks, 2)[:, 0] = lo
+        self.sh_bounds.view(blocks, 2)[:, 1] = hi
 
     # -- peer-memory gradient exchange -------------------------------------
     def _symmetric_memory_usable(self):
@@ -431,11 +465,15 @@ class Trainer:
             d_K = cams[0][1] if len(cams) == 1 else torch.cat([x[1] for x in cams])
             sh = None
             if self.quant:
+                layout = L.SH_LAYOUT_SPLAT_BLOCKS if self.fused_state_layout == "reference" else L.SH_LAYOUT_CELL_BLOCKS
                 sh = L.SsbShAdamState(self.sh_optim_packed.data_ptr(), self.sh_optim_bounds.data_ptr(), self.sh_packed.data_ptr(),
-                                      self.sh_bounds.data_ptr(), self.cfg.sh_value_bits, 8)
-            L.check(self.lib.ssb_step_backward_optimize(self.handle, C.byref(self._p_struct), C.byref(self.shq) if self.shq else None,
-                                                        L.ptr(d_vm), L.ptr(d_K), int(d_vm.shape[0]), C.byref(self._m1_struct), C.byref(self._m2_struct),
-                                                        C.byref(sh) if sh is not None else None, C.byref(cfg), None, stream))
+                                      self.sh_bounds.data_ptr(), self.cfg.sh_value_bits, 8, layout)
+            head = (self.handle, C.byref(self._p_struct), C.byref(self.shq) if self.shq else None, L.ptr(d_vm), L.ptr(d_K), int(d_vm.shape[0]))
+            tail = (C.byref(self._m1_struct), C.byref(self._m2_struct), C.byref(sh) if sh is not None else None, C.byref(cfg), ex, stream)
+            if self._nsq is not None:
+                L.check(self.lib.ssb_step_backward_optimize_q16(*head, C.byref(self._nsq), *tail))
+            else:
+                L.check(self.lib.ssb_step_backward_optimize(*head, *tail))
             self._kept_cams = []
             return
         if self.grad_sync in ("peer", "multimem"):

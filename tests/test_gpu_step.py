@@ -900,6 +900,88 @@ def test_fused_backward_equals_per_view_backward(lib, U, quant):
     a.close(); b.close()
 
 
+def test_stock_configuration_on_the_fused_path_with_the_reference_layouts(lib, U, tmp_path):
+    """The reference's stock trainer flags end to end on the fused backward + optimiser: 16-bit SH values and 8-bit SH optimiser
+    state with one bound per 256 splats (fused_state_layout="reference"), 16-bit moments for the other arrays, regularisers,
+    scale-agnostic mean, per-splat step counters.  Against the per-view path with the shared layouts: same losses, parameters
+    that move together; the SH degree warm-up keeps the idle bands at zero; a checkpoint carries the reference's slot names
+    for this layout and resumes."""
+    import tarfile
+    from spirula_studio_b200.trainer import OptimOptions, Trainer
+    from spirula_studio_b200 import checkpoint as ckpt
+    cfg = scenes.scaled(scenes.CONFIGS["plumbing_50k"], n_splats=140001, width=176, height=128, n_views=4)      # two ranges, ragged last block
+    cfg.rig, cfg.rig_radius, cfg.log_scale_mu = "ring", 3.0, -3.0
+    cfg.sh_value_bits, cfg.sh_optim_bits = 16, 8
+    sp = scenes.make_splats(cfg)
+    vm, K = scenes.make_cameras(cfg)
+    gt = np.stack([scenes.make_target(cfg, v) for v in range(cfg.n_views)])
+    host = tuple(torch.from_numpy(a).pin_memory() for a in (vm, K, gt))
+    stock = dict(non_sh_optim_bits=16, optim=OptimOptions())
+    a = Trainer(cfg, sp, device=U.DEV, **stock)
+    b = Trainer(cfg, sp, device=U.DEV, fused_backward=True, fused_state_layout="reference", **stock)
+    assert b.fused_backward and b.sh_bounds.numel() == 2 * ((cfg.n_splats + 255) // 256) and a.sh_bounds.numel() == 2 * ((cfg.n_splats * 45 + 255) // 256)
+    with pytest.raises(ValueError):
+        Trainer(cfg, sp, device=U.DEV, fused_state_layout="reference", **stock)        # the layout belongs to the fused path
+    first = None
+    for it in range(3):
+        la, lb = np.array(a.train_step(*host, cfg.n_views)), np.array(b.train_step(*host, cfg.n_views))
+        # the first iteration sees the same parameters (two quantisation grids of the same SH values); afterwards the paths differ
+        # by the coordinates whose near-zero first steps took opposite signs
+        assert np.allclose(la, lb, rtol=2e-3 if it == 0 else 2e-2, atol=1e-5), (it, la, lb)
+        first = la if first is None else first
+    assert lb[0] < first[0]
+    torch.cuda.synchronize()
+    lrs = dict(means=cfg.lrs["lr_means"], quats=cfg.lrs["lr_quats"], scales=cfg.lrs["lr_scales"], opacities=cfg.lrs["lr_opacities"],
+               features_dc=cfg.lrs["lr_features_dc"])
+    for k, lr in lrs.items():
+        x, y, x0 = a.params[k].cpu().numpy(), b.params[k].cpu().numpy(), np.asarray(sp[k], np.float32).reshape(-1)
+        assert np.isfinite(y).all() and np.abs(y - x0).max() > 0
+        # early Adam steps are worth about lr each whatever the gradient's size: the two paths (different summation order, different
+        # SH quantisation grids) may disagree on the sign of a near-zero step, rarely
+        assert (np.abs(x - y) > 0.5 * lr).mean() <= 6e-2, k
+    def sh_values(tr):
+        n = cfg.n_splats
+        codes = tr.sh_packed.cpu().numpy().view(np.uint16).reshape(n, 45).astype(np.float32) / 65535.0
+        per = 256 if tr.fused_state_layout == "reference" else None
+        bounds = tr.sh_bounds.cpu().numpy().reshape(-1, 2)
+        if per:
+            mm = np.repeat(bounds, 256, axis=0)[:n]
+            return mm[:, :1] + (mm[:, 1:] - mm[:, :1]) * codes
+        mm = np.repeat(bounds, 256, axis=0)[: n * 45]
+        return (mm[:, 0] + (mm[:, 1] - mm[:, 0]) * codes.reshape(-1)).reshape(n, 45)
+    va, vb = sh_values(a), sh_values(b)
+    lr_sh = cfg.lrs["lr_features_sh"]
+    assert (np.abs(va - vb) > 0.5 * lr_sh + 2e-4).mean() <= 3e-2          # a 16-bit step of a 256-splat block is about 1e-5 here
+    # checkpoint: the reference's slot names and flag for this layout; a fresh trainer resumes from it
+    out = tmp_path / "ck"
+    out.mkdir()
+    path = ckpt.save_checkpoint(b, str(out))
+    with tarfile.open(path) as tf:
+        names = set(tf.getnames())
+        manifest = tf.extractfile("state.json").read().decode()
+    assert {"eng.sh_quant_fpbo.q.npy", "eng.sh_quant_fpbo.qb.npy", "eng.world.sh_vq16_fpbo.q.npy", "eng.world.sh_vq16_fpbo.qb.npy",
+            "eng.means_qfpbo.q.npy", "eng.bias_correction_steps.npy", "eng.radii.npy"} <= names
+    assert '"use_fused_proj_bwd_optim": 1' in manifest and "eng.sh_quant.q.npy" not in names
+    c = Trainer(cfg, scenes.make_splats(cfg, seed=99), device=U.DEV, fused_backward=True, fused_state_layout="reference", **stock)     # other splats: all of it is replaced
+    assert ckpt.load_checkpoint(c, str(out)) == 3
+    for t_b, t_c in ((b.sh_packed, c.sh_packed), (b.sh_bounds, c.sh_bounds), (b.sh_optim_packed, c.sh_optim_packed), (b.sh_optim_bounds, c.sh_optim_bounds),
+                     (b.params["means"], c.params["means"]), (b.steps, c.steps), (b.nsq_packed["quats"], c.nsq_packed["quats"])):
+        assert torch.equal(t_b, t_c)
+    with pytest.raises(RuntimeError):
+        ckpt.load_checkpoint(a, str(out))                  # a trainer with the shared layout refuses the archive
+    lb2, lc2 = np.array(b.train_step(*host, cfg.n_views)), np.array(c.train_step(*host, cfg.n_views))
+    assert np.allclose(lb2, lc2, rtol=1e-4, atol=1e-6)
+    # SH degree warm-up on this layout: the bands above the active degree are written as zero
+    b.set_sh_degree(1)
+    b.train_step(*host, cfg.n_views)
+    torch.cuda.synchronize()
+    vb1 = sh_values(b)
+    span = (b.sh_bounds.view(-1, 2)[:, 1] - b.sh_bounds.view(-1, 2)[:, 0]).max().item()
+    assert np.abs(vb1[:, 9:]).max() <= span / 65535.0 and np.abs(vb1[:, :9]).max() > 0.01
+    for tr in (a, b, c):
+        tr.close()
+
+
 @pytest.mark.parametrize("quant", [False, True])
 def test_densification_strategy_runs_with_the_trainer(lib, U, quant):
     """The revised strategy around a Trainer (spirula_studio_b200/densify.py = the host logic of engine_densify_step): scores and

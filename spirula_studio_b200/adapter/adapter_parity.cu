@@ -348,6 +348,67 @@ int main(int argc, char** argv) {
             }
             report(pk ? "fused_projection_bwd_optimizer_3dgs, packed" : "fused_projection_bwd_optimizer_3dgs", ok);
         }
+        // ---- 4d. the stock configuration: level 1 (16-bit SH values, 8-bit SH state, bounds per 256 splats) with 16-bit moments
+        {
+            typedef int (*RefFpboL1)(uint32_t, uint32_t, uint32_t, uint32_t, int, float* const*, const float*, const float*, const float*, float* const*,
+                                     float* const*, float* const*, float* const*, uint8_t*, float*, uint8_t*, float*, uint8_t* const*, float* const*, const float*,
+                                     const float*, const float*, float, int, int, const int32_t*);
+            auto ref_fpbo_l1 = (RefFpboL1)dlsym(ref, "ref_fpbo_l1");
+            if (!ref_fpbo_l1) { std::fprintf(stderr, "missing ref_fpbo_l1\n"); return 2; }
+            const int64_t nb = (N + 255) / 256, cells = N * 45;
+            // SH codes with one bound per 256 splats; state and moments start from zero (the codecs' zero state)
+            std::vector<uint16_t> codes(cells);
+            std::vector<float> vbound(nb * 2);
+            for (int64_t b = 0; b < nb; ++b) {
+                const int64_t c0 = b * 256 * 45, c1 = std::min(cells, c0 + 256 * 45);
+                float lo = 1e30f, hi = -1e30f;
+                for (int64_t i = c0; i < c1; ++i) { lo = std::min(lo, sh[i]); hi = std::max(hi, sh[i]); }
+                vbound[2 * b] = lo; vbound[2 * b + 1] = hi;
+                for (int64_t i = c0; i < c1; ++i) codes[i] = (uint16_t)std::lround(65535.0 * (sh[i] - lo) / std::max(hi - lo, 1e-30f));
+            }
+            struct Side { std::vector<float*> p, z; uint16_t* vc; float* vb; uint8_t* oc; float* ob; uint8_t* nq[5]; float* nqb[5]; };
+            auto make_side = [&]() {
+                Side s; s.p = six_params(); s.z = six_zeros(); s.vc = upload(codes); s.vb = upload(vbound);
+                s.oc = device_zeros<uint8_t>(cells * 2); s.ob = device_zeros<float>(nb * 4);
+                for (int k = 0; k < 5; ++k) { s.nq[k] = device_zeros<uint8_t>(N * wd[k] * 4); s.nqb[k] = device_zeros<float>(nb * 4); }
+                return s;
+            };
+            Side r = make_side(), a = make_side();
+            float* unused5[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+            float* vs5[5] = {g_xy, g_depth, g_conic, g_opac, g_rgb};
+            if (ref_fpbo_l1(C, (uint32_t)N, W, H, 3, r.p.data(), d_vm, d_intr, r_aabb, vs5, r.z.data(), unused5, unused5, r.oc, r.ob, (uint8_t*)r.vc, r.vb, r.nq, r.nqb,
+                            d_rad, lrs, reg, sh_reg, 1, 0, d_steps) != 0) { std::fprintf(stderr, "ref_fpbo_l1 failed\n"); return 2; }
+            NonShQuantState nq;
+            nq.enabled = true;
+            nq.means_packed = a.nq[0]; nq.quats_packed = a.nq[1]; nq.scales_packed = a.nq[2]; nq.opacities_packed = a.nq[3]; nq.features_dc_packed = a.nq[4];
+            nq.means_bounds = (float4*)a.nqb[0]; nq.quats_bounds = (float4*)a.nqb[1]; nq.scales_bounds = (float4*)a.nqb[2]; nq.opacities_bounds = (float4*)a.nqb[3];
+            nq.features_dc_bounds = (float4*)a.nqb[4];
+            auto g1a = six_zeros(), g2a = six_zeros();
+            fused_projection_bwd_optimizer_3dgs(
+                N, 3, six_nd(a.p), ttv(d_vm, {(int64_t)C, 16}), ttv(d_intr, {(int64_t)C, 4}), W, H, "PINHOLE", "NONE", no_dist, DeviceVector<int32_t>{},
+                DeviceVector<int32_t>{}, DeviceTensorFloatND(ttv(r_aabb, {m, 4, 1})), six_nd(a.z), v_screen_nd, six_nd(g1a), six_nd(g2a),
+                std::make_tuple((uint64_t)a.oc, (uint32_t)1, std::vector<int64_t>{cells * 2}), ttv(a.ob, {nb, 4}),
+                std::make_tuple((uint64_t)a.vc, (uint32_t)1, std::vector<int64_t>{cells * 2}), ttv(a.vb, {nb, 2}), nq, DeviceVector<float>(ttv(d_rad, {N, 1})),
+                DeviceVector<float>{}, lrs[0], lrs[1], lrs[2], lrs[3], lrs[4], lrs[5], reg[0], reg[1], reg[2], reg[3], reg[4], reg[5], reg[6], sh_reg, true, false, 0.f,
+                std::variant<int32_t, TorchTensorView>(ttv(d_steps, {N, 1})), 1);
+            backend::device_synchronize();
+            ok = true;
+            for (int k = 0; k < 5; ++k) {
+                const double fp = frac_bad(download(a.p[k], N * wd[k]), download(r.p[k], N * wd[k]), 5e-6, 1e-4);
+                if (!(fp <= 2e-3)) { ok = false; std::printf("  level 1 %s: %g\n", gnames[k], fp); }
+            }
+            // SH values and the bounds of both SH buffers: as the numbers the codes stand for
+            auto va = download(a.vc, cells), vr = download(r.vc, cells);
+            auto ba = download(a.vb, nb * 2), br = download(r.vb, nb * 2);
+            int64_t far = 0;
+            for (int64_t i = 0; i < cells; ++i) {
+                const int64_t b = i / (256 * 45);
+                const double xa = ba[2 * b] + (ba[2 * b + 1] - ba[2 * b]) * (va[i] / 65535.0), xr = br[2 * b] + (br[2 * b + 1] - br[2 * b]) * (vr[i] / 65535.0);
+                far += std::fabs(xa - xr) > 3.0 * (br[2 * b + 1] - br[2 * b]) / 65535.0 + 1e-12;
+            }
+            const double fb = frac_bad(ba, br, 2e-5, 2e-3) + frac_bad(download(a.ob, nb * 4), download(r.ob, nb * 4), 2e-3, 2e-3);
+            report("fused_projection_bwd_optimizer_3dgs, level 1 + 16-bit moments", ok && far * 200 <= cells && fb == 0.0, (double)far, fb);
+        }
         bool refused = false;
         try {
             auto pa = six_params(), za = six_zeros(), g1a = up6(h_g1), g2a = up6(h_g2);
@@ -357,7 +418,7 @@ int main(int argc, char** argv) {
                                                 DeviceVector<float>{}, DeviceVector<float>{}, lrs[0], lrs[1], lrs[2], lrs[3], lrs[4], lrs[5], reg[0], 0.f, 0.f, 0.f, 0.f, 0.f,
                                                 0.f, 0.f, false, false, 0.f, std::variant<int32_t, TorchTensorView>((int32_t)1), 1);
         } catch (const std::runtime_error&) { refused = true; }
-        report("fused backward + optimiser, level 1: refused", refused);
+        report("fused backward + optimiser, level 1 without its buffers: refused", refused);
     }
     // ---- 5. what the library does not cover is refused the way the reference refuses bad arguments
     bool threw = false;

@@ -11,7 +11,7 @@
 //   rasterize_to_pixels_3dgs_fwd   (src/kernels/raster/RasterizationFwd.cuh:16-37)    -> ssb_screen_pack + ssb_raster_fwd
 //   rasterize_to_pixels_3dgs_bwd   (src/kernels/raster/RasterizationBwd.cuh:18-48)    -> ssb_raster_bwd_accum + unpack of the gradient records
 //   projection_3dgs_backward       (src/kernels/projection/ProjectionBwd.cuh:18-46)   -> ssb_screen_pack + ssb_project_bwd / ssb_project_bwd_packed
-//   fused_projection_bwd_optimizer_3dgs (src/kernels/optim/FusedProjectionBwdOptim.cuh:19-63) -> ssb_project_bwd_optimize (quantisation level 0)
+//   fused_projection_bwd_optimizer_3dgs (src/kernels/optim/FusedProjectionBwdOptim.cuh:19-63) -> ssb_project_bwd_optimize[_q16] (quantisation levels 0 and 1)
 //   compute_multi_scale_per_pixel_losses (src/kernels/loss/PerPixelLoss.cuh:160-189)  -> ssb_loss_multi_scale (colour terms only)
 //   fused_optim_3dgs_geometry      (src/kernels/optim/Optimizer.cuh:120-144)         -> ssb_adam_step_ex without features_dc
 //   fused_adam_step                (src/kernels/optim/Optimizer.cuh:147-158)         -> ssb_adam_plain
@@ -469,10 +469,11 @@ void projection_3dgs_backward(
                                      gaussian_ids.data_ptr(), d_pairs, m, ws, ws_bytes, &g, 1, nullptr));
 }
 
-// Quantisation level 0 (fp32 SH values, fp32 moments of every array).  Level 1 keeps its SH codes and SH optimiser state in
-// layouts of its own (one bound per 256 splats) and is refused.  v_splats_world is not read: for this primitive the
-// rasteriser's backward leaves it zero (only the 3DGUT rasteriser produces world gradients).  With packed pairs the aabb rows
-// and screen gradients are first scattered into the dense [view][splat] layout the library's kernel walks.
+// Quantisation level 0 (fp32 SH values, fp32 moments of every array) and level 1 (16-bit SH values and 8-bit SH optimiser state
+// with one bound per 256 splats: SSB_SH_LAYOUT_SPLAT_BLOCKS; with non_sh.enabled the moments of the other arrays in 16-bit codes).
+// v_splats_world is not read: for this primitive the rasteriser's backward leaves it zero (only the 3DGUT rasteriser produces
+// world gradients).  With packed pairs the aabb rows and screen gradients are first scattered into the dense [view][splat]
+// layout the library's kernel walks.
 void fused_projection_bwd_optimizer_3dgs(
     const int64_t num_splats, const int max_sh_degree, std::vector<DeviceTensorFloatND> splats_world, TorchTensorView viewmats, TorchTensorView intrins,
     const uint32_t image_width, const uint32_t image_height, const std::string camera_model, const std::string distortion, const TorchTensorView dist_coeffs,
@@ -485,13 +486,21 @@ void fused_projection_bwd_optimizer_3dgs(
     const float max_gauss_ratio, const float scale_regularization_weight, const float mcmc_opacity_reg_weight, const float mcmc_scale_reg_weight,
     const float erank_reg_weight, const float erank_reg_weight_s3, const float quat_norm_reg_weight, const float sh_reg_weight, bool use_scale_agnostic_mean,
     bool color_trust_linear, float eps_tr, std::variant<int32_t, TorchTensorView> step, int quantization_level) {
-    (void)v_splats_world; (void)eps_tr; (void)sh_packed; (void)sh_quant_bounds; (void)sh_value_packed; (void)sh_value_bounds;
-    if (quantization_level != 0 || non_sh.enabled) unsupported("the quantised layouts of the fused backward + optimiser (quantization_level 1)");
+    (void)v_splats_world; (void)eps_tr;
+    if (quantization_level != 0 && quantization_level != 1) unsupported("this quantisation level");
+    const bool level1 = quantization_level == 1;
+    if (!level1 && non_sh.enabled) unsupported("16-bit moments with fp32 SH in the fused backward + optimiser");
+    if (level1 && !(sh_packed.has_value() && sh_quant_bounds.has_value() && sh_value_packed.has_value() && sh_value_bounds.has_value()))
+        throw std::runtime_error("fused_projection_bwd_optimizer_3dgs: quantisation level 1 without its SH buffers");
     if (color_trust_linear) unsupported("the linear-colour trust region");
     if (max_sh_degree < 0 || max_sh_degree > 3) unsupported("an SH degree above 3");
     if (v_splats_screen.size() != 5 || g1_splats_world.size() != 6 || g2_splats_world.size() != 6)
         throw std::runtime_error("fused_projection_bwd_optimizer_3dgs: expected five screen gradient arrays and six arrays per moment");
-    const WorldArgs w = world_args("fused_projection_bwd_optimizer_3dgs", splats_world, std::nullopt, std::nullopt, 15, 32, 0);
+    if (splats_world.size() != 6) throw std::runtime_error("fused_projection_bwd_optimizer_3dgs: expected six world arrays");
+    WorldArgs w{};
+    if (level1) w.splats = SsbSplats{splats_world[0].data_ptr(), splats_world[1].data_ptr(), splats_world[2].data_ptr(), splats_world[3].data_ptr(),
+                                     splats_world[4].data_ptr(), nullptr};
+    else w = world_args("fused_projection_bwd_optimizer_3dgs", splats_world, std::nullopt, std::nullopt, 15, 32, 0);
     const uint32_t C = (uint32_t)std::get<2>(viewmats)[0];
     const int64_t N = num_splats, dense = (int64_t)C * N;
     if (N == 0) return;
@@ -518,7 +527,7 @@ void fused_projection_bwd_optimizer_3dgs(
     auto six = [](const std::vector<DeviceTensorFloatND>& v) {
         return SsbSplats{v[0].data_ptr(), v[1].data_ptr(), v[2].data_ptr(), v[3].data_ptr(), v[4].data_ptr(), v[5].data_ptr()};
     };
-    const SsbSplats m1 = six(g1_splats_world), m2 = six(g2_splats_world);
+    SsbSplats m1 = six(g1_splats_world), m2 = six(g2_splats_world);
     SsbAdamExtras ex{};
     ex.max_gauss_ratio = max_gauss_ratio; ex.scale_regularization_weight = scale_regularization_weight;
     ex.mcmc_opacity_reg_weight = mcmc_opacity_reg_weight; ex.mcmc_scale_reg_weight = mcmc_scale_reg_weight;
@@ -533,7 +542,25 @@ void fused_projection_bwd_optimizer_3dgs(
     const int64_t ws_bytes = ssb_project_bwd_optimize_workspace_bytes(N);
     uint8_t* ws = scratch<uint8_t>("fpbo_workspace", ws_bytes + 256);
     ws = (uint8_t*)(((uintptr_t)ws + 255) & ~(uintptr_t)255);
-    ssb_check(ssb_project_bwd_optimize(&w.splats, nullptr, N, &cams, d_aabb, v_rec, &m1, &m2, nullptr, &cfg, &ex, ws, ws_bytes, nullptr));
+    if (!level1) {
+        ssb_check(ssb_project_bwd_optimize(&w.splats, nullptr, N, &cams, d_aabb, v_rec, &m1, &m2, nullptr, &cfg, &ex, ws, ws_bytes, nullptr));
+        return;
+    }
+    SsbSplats p = w.splats;
+    p.features_sh = nullptr; m1.features_sh = nullptr; m2.features_sh = nullptr;        // SH lives in the codes
+    SsbShQuant shq = {};
+    shq.packed = (void*)std::get<0>(sh_value_packed.value()); shq.bounds = (float*)std::get<0>(sh_value_bounds.value());
+    shq.bits = 16; shq.bounds_stride = 0;
+    SsbShAdamState st = {(uint8_t*)std::get<0>(sh_packed.value()), (float*)std::get<0>(sh_quant_bounds.value()), shq.packed, shq.bounds, 16, 8,
+                         SSB_SH_LAYOUT_SPLAT_BLOCKS};
+    if (non_sh.enabled) {
+        SsbMomentsQ16 mom{{non_sh.means_packed, non_sh.quats_packed, non_sh.scales_packed, non_sh.opacities_packed, non_sh.features_dc_packed},
+                          {(float*)non_sh.means_bounds, (float*)non_sh.quats_bounds, (float*)non_sh.scales_bounds, (float*)non_sh.opacities_bounds,
+                           (float*)non_sh.features_dc_bounds}};
+        ssb_check(ssb_project_bwd_optimize_q16(&p, &shq, N, &cams, d_aabb, v_rec, &mom, nullptr, nullptr, &st, &cfg, &ex, ws, ws_bytes, nullptr));
+    } else {
+        ssb_check(ssb_project_bwd_optimize(&p, &shq, N, &cams, d_aabb, v_rec, &m1, &m2, &st, &cfg, &ex, ws, ws_bytes, nullptr));
+    }
 }
 
 

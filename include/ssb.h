@@ -745,9 +745,9 @@ int ssb_project_bwd_optimize_q16(const SsbSplats* params, const SsbShQuant* shq,
  *   ssb_step_set_fused_backward(step, max_views > 0): ssb_step_views[_gated] then stops after each view's raster backward
  *     and keeps the view's aabb and screen-gradient records ((16 + 48) bytes per splat and view); `grads`, `accumulate`
  *     are ignored.  Views of successive calls are appended until ssb_step_backward_optimize consumes them.  0 switches back.
- *   ssb_step_backward_optimize: for one range of 65 536 splats after the other, the projection backward over all kept
+ *   ssb_step_backward_optimize: for one range of 131 072 splats after the other, the projection backward over all kept
  *     views (a thread per splat, gradients summed in registers and shared memory) writes the range's gradients to a
- *     15 MB scratch that the Adam kernels of the same range read straight back out of L2.  d_viewmats / d_intrins are the
+ *     31 MB scratch that the Adam kernels of the same range read straight back out of L2.  d_viewmats / d_intrins are the
  *     cameras of the kept views in the order they were given; n_views must equal their number.  m1 / m2 / cfg / extras
  *     as for ssb_adam_step_ex (cfg->zero_grad is ignored); sh_state != NULL runs the quantised SH update of
  *     ssb_adam_step_sh_quantized_ex on it (then params->features_sh, m1/m2->features_sh may be NULL), else SH is

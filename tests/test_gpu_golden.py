@@ -345,6 +345,52 @@ def test_fused_backward_optimiser_level1_q16_moments_vs_reference(lib, U, oracle
                                  gold[f"{tag}_s{step}_optim_codes"], gold[f"{tag}_s{step}_optim_bounds"], n)
 
 
+@pytest.mark.parametrize("bits,degree,n", [(16, 3, 700), (8, 3, 1200), (16, 2, 130), (8, 1, 513)])
+def test_sh_splat_block_adam_vs_oracle(lib, U, oracle, bits, degree, n):
+    """ssb_adam_step_sh_splat_blocks on its own against the oracle's restatement (pinned through fpbo_l1.npz at 16 bits): 8- and
+    16-bit values, per-splat step counters, ragged last block, fewer splats than one block, active SH degrees below 3, three steps
+    from a random state, in two ranges where the splat count allows."""
+    rng = np.random.default_rng(17 + bits + n)
+    cells, blocks = n * 45, (n + 255) // 256
+    sh = (rng.normal(size=(n, 45)) * 0.2).astype(np.float32)
+    vc, vb = encode_splat_blocks(sh, bits)
+    oc = rng.integers(0, 256, size=cells * 2, dtype=np.uint8)
+    ob = np.tile(np.array([-3.0, 3.0, 0.0, 24.0], np.float32), blocks)
+    steps = rng.integers(1, 30, size=n).astype(np.int32)
+    d_vc, d_vb, d_oc, d_ob = U.dev(vc.view(np.uint8)), U.dev(vb.reshape(-1)), U.dev(oc), U.dev(ob)
+    h_vc, h_vb, h_oc, h_ob = vc.copy(), vb.reshape(-1).copy(), oc.copy(), ob.copy()
+    lr, l2 = 2.5e-3, 0.03
+    for step in (1, 2, 3):
+        g = (rng.normal(size=cells) * 1e-3).astype(np.float32)
+        g[rng.integers(0, cells, size=5)] = np.nan                      # non-finite gradients count as zero
+        st = (steps + step).astype(np.int32) if step > 1 else None       # first a scalar step, then per-splat counters
+        d_g, d_st = U.dev(g), (U.dev(st) if st is not None else None)
+        acfg = L.SsbAdamConfig(0.0, 0.0, 0.0, 0.0, 0.0, lr, l2, 0.5, step, 1)
+        first_ranges = [(0, n)] if n <= 256 else [(0, 256), (256, n - 256)]
+        for f0, cnt in first_ranges:
+            L.check(lib.ssb_adam_step_sh_splat_blocks(L.ptr(d_g), L.ptr(d_oc), L.ptr(d_ob), L.ptr(d_vc), L.ptr(d_vb), bits, f0, cnt, n, degree + 1, C.byref(acfg),
+                                                      L.ptr(d_st) if d_st is not None else None, None))
+        torch.cuda.synchronize()
+        oracle.adam_sh_splat_blocks(np.nan_to_num(g, nan=0.0), h_oc, h_ob, h_vc, h_vb, bits, n, step, lr, l2_reg=l2, grad_scale=0.5, sh_degree=degree, steps=st)
+        n_active = 3 * degree * (degree + 2)
+        live = np.tile(np.arange(45) < n_active, n)
+        assert not d_g.cpu().numpy()[live].any()            # cfg.zero_grad clears what was consumed
+        got_vb, got_ob = d_vb.cpu().numpy(), d_ob.cpu().numpy()
+        assert np.allclose(got_vb, h_vb, rtol=1e-4, atol=1e-6) and np.allclose(got_ob, h_ob, rtol=1e-4, atol=1e-5), step
+        qv = float((1 << bits) - 1)
+        got_codes = d_vc.cpu().numpy().view(np.uint16 if bits == 16 else np.uint8).astype(np.int64)
+        dv = np.abs(got_codes - h_vc.astype(np.int64))
+        assert dv.max() <= (2 if bits == 16 else 1) and (dv > 0).mean() <= 0.05, (step, dv.max(), (dv > 0).mean())
+        do = np.abs(d_oc.cpu().numpy().astype(np.int64) - h_oc.astype(np.int64))
+        assert do.max() <= 1 and (do > 0).mean() <= 0.02, (step, do.max(), (do > 0).mean())
+        if degree < 3:        # idle cells: zero value, zero moments
+            vals = decode_splat_blocks(got_codes.astype(np.uint16), got_vb.reshape(-1, 2), bits)
+            assert np.abs(vals[:, n_active:]).max() <= (got_vb.reshape(-1, 2)[:, 1] - got_vb.reshape(-1, 2)[:, 0]).max() / qv
+        # continue from the library's own state on both sides, so that the steps are compared one by one
+        h_vc, h_vb = d_vc.cpu().numpy().view(np.uint16 if bits == 16 else np.uint8).copy(), got_vb.copy()
+        h_oc, h_ob = d_oc.cpu().numpy().copy(), got_ob.copy()
+
+
 @pytest.mark.parametrize("deg", [0, 1, 2])
 def test_active_sh_degree_vs_reference(lib, U, deg):
     """ssb_project_fwd / ssb_project_bwd with SsbCameras::sh_degree_plus1 (the SH degree warm-up) against the reference's

@@ -80,11 +80,13 @@ SsbScreenRec* pack_records(const char* name, const float* xy, const float* depth
 }
 
 // Packed pairs -> the dense [view][splat] layout: aabb rows (a zero row = "not visible") and gradient records.
-__global__ void scatter_pairs_kernel(int64_t nnz, int64_t n, const int32_t* camera_ids, const int32_t* gaussian_ids, const float4* aabb, const float* xy,
+__global__ void scatter_pairs_kernel(int64_t nnz, int64_t n, int32_t n_views, const int32_t* camera_ids, const int32_t* gaussian_ids, const float4* aabb, const float* xy,
                                      const float* depth, const float* conic, const float* opac, const float* rgb, float4* dense_aabb, SsbScreenRec* dense_rec) {
     const int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (v >= nnz) return;
-    const int64_t slot = (int64_t)camera_ids[v] * n + gaussian_ids[v];
+    const int32_t cam = camera_ids[v], gid = gaussian_ids[v];
+    if ((uint32_t)cam >= (uint32_t)n_views || (uint64_t)gid >= (uint64_t)n) return;      // an id outside the layout is skipped, never followed
+    const int64_t slot = (int64_t)cam * n + gid;
     dense_aabb[slot] = aabb[v];
     float4* r = (float4*)(dense_rec + slot);
     r[0] = make_float4(xy[2 * v], xy[2 * v + 1], 0.f, 0.f);
@@ -514,7 +516,7 @@ void fused_projection_bwd_optimizer_3dgs(
         v_rec = scratch<SsbScreenRec>("fpbo_grad_records", dense);
         backend::memset_sync(dense_aabb, 0, (size_t)dense * sizeof(float4));
         if (nnz > 0) {
-            scatter_pairs_kernel<<<(unsigned)((nnz + 255) / 256), 256>>>(nnz, N, camera_ids.data_ptr(), gaussian_ids.data_ptr(), (const float4*)aabb.data_ptr(),
+            scatter_pairs_kernel<<<(unsigned)((nnz + 255) / 256), 256>>>(nnz, N, (int32_t)C, camera_ids.data_ptr(), gaussian_ids.data_ptr(), (const float4*)aabb.data_ptr(),
                                                                          v_splats_screen[0].data_ptr(), v_splats_screen[1].data_ptr(), v_splats_screen[2].data_ptr(),
                                                                          v_splats_screen[3].data_ptr(), v_splats_screen[4].data_ptr(), dense_aabb, v_rec);
             if (cudaGetLastError() != cudaSuccess) throw std::runtime_error("fused_projection_bwd_optimizer_3dgs: scatter launch failed");

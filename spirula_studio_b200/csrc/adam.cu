@@ -588,6 +588,8 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
     float gv[4];
     uint32_t vcode[4], ucode[4], scode[4];
     const bool full = idx0 + 4 <= numel_total;
+    [[maybe_unused]] int64_t step_splat = -1;
+    [[maybe_unused]] float step_lr1 = 0.f, step_c2 = 0.f;
     if (full) {
         const float4 g4 = grad_sum4<PEER>((const float4*)(grad + idx0), po);
         gv[0] = g4.x; gv[1] = g4.y; gv[2] = g4.z; gv[3] = g4.w;
@@ -646,9 +648,15 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
             // square root are its own arithmetic here (cmake/SsBackendCuda.cmake:95-102)
             float lr1 = lr_ibc1, c2 = ibc2;
             if (STEPS) {
-                const float step = (float)steps[idx / stride];
-                lr1 = lr * inv_bias_correction(kBeta1, step);
-                c2 = inv_bias_correction(kBeta2, step);
+                // a thread's four cells belong to one splat, or to two neighbours: the two powers are taken once per splat
+                const int64_t splat = idx / stride;
+                if (splat != step_splat) {
+                    step_splat = splat;
+                    const float step = (float)steps[splat];
+                    step_lr1 = lr * inv_bias_correction(kBeta1, step);
+                    step_c2 = inv_bias_correction(kBeta2, step);
+                }
+                lr1 = step_lr1; c2 = step_c2;
             }
             xv -= __fdividef(lr1 * g1, sqrt_approx(g2 * c2) + kAdamEps);
             float sq = sqrt_approx(fmaxf(g2, 0.0f));
@@ -735,9 +743,17 @@ __global__ void __launch_bounds__(kSbThreads, 1) adam_sh_splat_block_kernel(
     float2* __restrict__ value_bounds, int64_t first_block, int64_t n_total_splats, int n_active, float lr_ibc1, float ibc2, float decay,
     float grad_scale, int zero_grad, const int32_t* __restrict__ steps, float lr) {
     __shared__ uint32_t red[6][kSbThreads / 32];
+    __shared__ float2 step_terms[STEPS ? 256 : 1];      // per splat of the block: lr / (1 - beta1^t), 1 / (1 - beta2^t)
     const int64_t blk = first_block + blockIdx.x;
     const int64_t cell0 = blk * kSbCells;
     const int n_cells = (int)min((int64_t)kSbCells, (n_total_splats - blk * 256) * 45);
+    if (STEPS) {
+        if (threadIdx.x < 256 && threadIdx.x * 45 < n_cells) {
+            const float step = (float)steps[blk * 256 + threadIdx.x];
+            step_terms[threadIdx.x] = make_float2(lr * inv_bias_correction(kBeta1, step), inv_bias_correction(kBeta2, step));
+        }
+        __syncthreads();
+    }
     constexpr float vq = (float)((1u << VALUE_BITS) - 1u), vinv = 1.0f / vq;
     const float oq = 255.0f, oinv = 1.0f / 255.0f;
     const float2 vmm = value_bounds[blk];
@@ -768,11 +784,7 @@ __global__ void __launch_bounds__(kSbThreads, 1) adam_sh_splat_block_kernel(
             g1 = kBeta1 * g1 + (1.f - kBeta1) * v;
             g2 = kBeta2 * g2 + (1.f - kBeta2) * v * v;
             float lr1 = lr_ibc1, c2 = ibc2;
-            if (STEPS) {
-                const float step = (float)steps[blk * 256 + splat];
-                lr1 = lr * inv_bias_correction(kBeta1, step);
-                c2 = inv_bias_correction(kBeta2, step);
-            }
+            if (STEPS) { const float2 t = step_terms[splat]; lr1 = t.x; c2 = t.y; }
             xv -= __fdividef(lr1 * g1, sqrt_approx(g2 * c2) + kAdamEps);
             const float sq = sqrt_approx(fmaxf(g2, 0.0f));
             u_new[k] = __fdividef(g1, sq + kAdamEps);

@@ -273,7 +273,16 @@ def run_ours(args, cfg, rank, world, local_rank):
     # projection backward is bound by instruction issue, not by the gradient traffic the fusion removes, and the per-view
     # kernels hide behind the next view's forward pass on the second stream while the fused pass runs exposed at the end.
     fused = os.environ.get("SSB_FUSED_BACKWARD", "0") != "0"
-    tr = Trainer(cfg, splats, device=dev, world_size=world, rank=rank, grad_sync=grad_sync, fused_backward=fused)
+    # SSB_STOCK_FLAGS=1: the reference trainer's stock optimiser flags (regularisers, scale-agnostic mean, per-splat step counters,
+    # 16-bit moments for the non-SH arrays) instead of the plain Adam step the headline is quoted on; with SSB_FUSED_BACKWARD=1
+    # and SSB_FUSED_LAYOUT=reference the quantised SH buffers take the reference's per-256-splat layout of its fused path.
+    stock = os.environ.get("SSB_STOCK_FLAGS", "0") != "0"
+    layout = os.environ.get("SSB_FUSED_LAYOUT", "shared")
+    extra = {}
+    if stock:
+        from spirula_studio_b200.trainer import OptimOptions
+        extra = dict(non_sh_optim_bits=16, optim=OptimOptions())
+    tr = Trainer(cfg, splats, device=dev, world_size=world, rank=rank, grad_sync=grad_sync, fused_backward=fused, fused_state_layout=layout, **extra)
     del splats
     # this rank's views, grouped by camera kind (one kind for every workload but the wide-camera one)
     n_kinds = scenes.n_view_kinds(cfg)
@@ -440,6 +449,9 @@ def run_ours(args, cfg, rank, world, local_rank):
                                       ("this library's fused reduce + sharded Adam + broadcast kernels over peer memory" if tr.grad_sync == "peer" else
                                        "this library's fused reduce + sharded Adam + broadcast kernels through the NVSwitch multicast address"
                                        if tr.grad_sync == "multimem" else "an NCCL all-reduce" if tr.grad_sync == "nccl" else "nothing (one GPU)"),
+                       "optimiser": ("stock flags of the reference trainer" if stock else "plain Adam") +
+                                    (", projection backward fused with the optimiser" if tr.fused_backward else "") +
+                                    (", reference fused-path layouts" if tr.fused_state_layout == "reference" else ""),
                        "pairs_per_view": int(pairs), "visible_per_view": visible,
                        "l2": "inputs (parameters, gradients, moments, targets: > 1 GB) exceed the 126 MB L2; no flush between iterations"},
             "e2e": {"value": 1e3 / e2e_ms, "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": 12},

@@ -635,11 +635,11 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
             v += decay * (fmaxf(xv - decay_offset, 0.0f) + fminf(xv + decay_offset, 0.0f));
             float u = omm.x + (omm.y - omm.x) * ((float)ucode[k] * oinv);
             float ls = omm.z + (omm.w - omm.z) * ((float)scode[k] * oinv);
-            // sqrt(g2) = eps * expm1(ls).  ls is either 0 (never-updated cell) or far above 1
-            // (sqrt(g2)/eps is astronomically large for any real gradient), where expm1 = exp - 1
-            // to working precision; only the narrow band in between needs the careful routine.
-            float em1;
-            if (ls > 12.0f) em1 = __expf(ls) - 1.0f; else em1 = expm1f(ls);
+            // sqrt(g2) = eps * expm1(ls).  ls is either 0 (never-updated cell) or far above 1 (sqrt(g2)/eps is astronomically
+            // large for any real gradient).  exp - 1 is exact at 0 (2^0 = 1) and expm1 to working precision above 1; in the band
+            // between (a second moment below 1e-29, which no real gradient leaves behind) it loses digits nothing downstream sees.
+            // A branch to the careful routine made every warp holding one never-updated cell run both.
+            const float em1 = __expf(ls) - 1.0f;
             float sqrt_g2 = kAdamEps * em1;
             float g1 = u * (sqrt_g2 + kAdamEps), g2 = sqrt_g2 * sqrt_g2;
             g1 = kBeta1 * g1 + (1.f - kBeta1) * v;
@@ -662,7 +662,7 @@ __global__ void __launch_bounds__(64) adam_qq_kernel(
             float sq = sqrt_approx(fmaxf(g2, 0.0f));
             u_new[k] = __fdividef(g1, sq + kAdamEps);
             float y = sq * (1.0f / kAdamEps);
-            if (y > 1.0e6f) s_new[k] = __logf(y); else s_new[k] = log1pf(y);
+            s_new[k] = __logf(y > 1.0e6f ? y : 1.0f + y);      // log(1) = 0 exactly for a cell that never saw a gradient
             x[k] = xv;
         }
     }
@@ -777,8 +777,7 @@ __global__ void __launch_bounds__(kSbThreads, 1) adam_sh_splat_block_kernel(
             v += decay * xv;
             const float u = omm.x + (omm.y - omm.x) * ((float)(oc & 255u) * oinv);
             const float ls = omm.z + (omm.w - omm.z) * ((float)(oc >> 8) * oinv);
-            float em1;
-            if (ls > 12.0f) em1 = __expf(ls) - 1.0f; else em1 = expm1f(ls);
+            const float em1 = __expf(ls) - 1.0f;          // exact at 0; see adam_qq_kernel
             const float sqrt_g2 = kAdamEps * em1;
             float g1 = u * (sqrt_g2 + kAdamEps), g2 = sqrt_g2 * sqrt_g2;
             g1 = kBeta1 * g1 + (1.f - kBeta1) * v;
@@ -789,7 +788,7 @@ __global__ void __launch_bounds__(kSbThreads, 1) adam_sh_splat_block_kernel(
             const float sq = sqrt_approx(fmaxf(g2, 0.0f));
             u_new[k] = __fdividef(g1, sq + kAdamEps);
             const float y = sq * (1.0f / kAdamEps);
-            if (y > 1.0e6f) s_new[k] = __logf(y); else s_new[k] = log1pf(y);
+            s_new[k] = __logf(y > 1.0e6f ? y : 1.0f + y);      // log(1) = 0 exactly for a cell that never saw a gradient
             x[k] = xv;
             mn[0] = fminf(mn[0], xv); mx[0] = fmaxf(mx[0], xv);
             mn[1] = fminf(mn[1], u_new[k]); mx[1] = fmaxf(mx[1], u_new[k]);

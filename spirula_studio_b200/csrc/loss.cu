@@ -201,7 +201,9 @@ __global__ void __launch_bounds__(kLossThreads) loss_l1_ssim_kernel(
                     const float Bv = sigma1_sq + sigma2_sq + kC2;
                     const float C_ = 2.f * mu1 * mu2 + kC1;
                     const float D_ = 2.f * sigma12 + kC2;
-                    const float rAB = 1.0f / (A * Bv);
+                    // approximate reciprocals (two units in the last place), the arithmetic the reference's fast-math build has here
+                    const float rA = __fdividef(1.0f, A), rB = __fdividef(1.0f, Bv);
+                    const float rAB = rA * rB;
                     if (r >= kHalo && r < kHalo + kLossTile && c >= kHalo && c < kHalo + kLossTile) {
                         ssim_acc += centre ? (C_ * D_) * rAB : 1.0f;
                         if (MAP_MODE) {
@@ -218,8 +220,8 @@ __global__ void __launch_bounds__(kLossThreads) loss_l1_ssim_kernel(
                     }
                     // each moment was divided by the coverage, so its reverse carries the same factor
                     const float gr = MASKED ? (centre ? grad * inv_cov : 0.f) : grad;
-                    d0 = ((mu2 * 2.f * D_) * rAB - (mu2 * 2.f * C_) * rAB - (mu1 * 2.f * C_ * D_) * rAB / A + (mu1 * 2.f * C_ * D_) * rAB / Bv) * gr;
-                    d1 = (-C_ * D_) * rAB / Bv * gr;
+                    d0 = ((mu2 * 2.f * D_) * rAB - (mu2 * 2.f * C_) * rAB - (mu1 * 2.f * C_ * D_) * rAB * rA + (mu1 * 2.f * C_ * D_) * rAB * rB) * gr;
+                    d1 = (-C_ * D_) * rAB * rB * gr;
                     d2 = (2.f * C_) * rAB * gr;
                 }
                 // sD aliases the input patches, which step 2 finished reading

@@ -53,13 +53,13 @@ WORKLOAD = "mid_1m"
 # pass over this file's own command on the mid_1m workload, one view per launch (a stage of several kernels:
 # their sum).  They are not measured by the run that prints them (a profiler cannot run inside a timed
 # benchmark); the JSON line says so in `traffic_source`.
-NCU_TRAFFIC_MID1M = {"project_fwd": 183.8e6, "tile_keys": 190.5e6, "sort": 35.6e6, "raster_fwd": 68.4e6,
-                     "loss": 51.6e6, "raster_bwd": 111.7e6, "project_bwd": 427.5e6, "adam": 846.8e6}
+NCU_TRAFFIC_MID1M = {"project_fwd": 184.1e6, "tile_keys": 190.5e6, "sort": 35.6e6, "raster_fwd": 68.3e6,
+                     "loss": 51.5e6, "raster_bwd": 111.2e6, "project_bwd": 426.4e6, "adam": 846.8e6}
 # FP32 operations one launch (one view) executes, thread level, FMA counted as two: 2 * ffma + fadd + fmul of
 # smsp__sass_thread_inst_executed_op_{ffma,fadd,fmul}_pred_on.sum from the same kind of capture.  RECORDED CONSTANTS like
 # the traffic above.  The rasterisers and the loss kernel are arithmetic kernels whose working set sits in L2: their
 # roofline is the FP32 pipe, not HBM.
-NCU_FLOP_MID1M = {"raster_fwd": 4.035e9, "loss": 4.637e9, "raster_bwd": 10.228e9}
+NCU_FLOP_MID1M = {"raster_fwd": 3.975e9, "loss": 4.308e9, "raster_bwd": 10.110e9}
 # FP32 peak: 148 SMs x 128 lanes x 2 (FMA) x the maximum SM clock; there is no measured FP32 figure for this pool.
 FP32_LANES = 148 * 128
 
